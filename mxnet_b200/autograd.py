@@ -1,0 +1,280 @@
+"""Autograd: ``record/pause/train_mode/predict_mode``, ``mark_variables``, ``backward``, ``grad``, ``Function``.
+
+Reference: ``python/mxnet/autograd.py`` over ``Imperative::RecordOp/MarkVariables/Backward``
+(``src/imperative/imperative.cc:143-172,237-334,445-757``).  The tape is the tensor library's
+autograd graph; the recording flag decides whether operators run with graph construction on.
+
+Gradient buffers are owned by the array (``attach_grad``) and installed as the leaf's ``.grad``
+so accumulation happens *in place* into memory whose address never changes; that is what lets
+the fused KVStore kernels read gradients directly from flat buckets.  ``grad_req='write'`` is
+implemented by clearing buffers that were written by an earlier pass right before the next
+backward accumulates into them; ``'add'`` never clears.
+"""
+from __future__ import annotations
+
+import weakref
+
+import torch
+
+from . import _state
+from .base import MXNetError
+from .ndarray.ndarray import NDArray, _dirty_grads
+
+__all__ = ['set_recording', 'set_training', 'is_recording', 'is_training', 'record', 'pause', 'train_mode',
+           'predict_mode', 'mark_variables', 'backward', 'grad', 'get_symbol', 'Function']
+
+
+def set_recording(is_recording):
+    prev = _state.state.recording
+    _state.state.recording = bool(is_recording)
+    return prev
+
+
+def set_training(train_mode):
+    prev = _state.state.training
+    _state.state.training = bool(train_mode)
+    return prev
+
+
+def is_recording():
+    return _state.state.recording
+
+
+def is_training():
+    return _state.state.training
+
+
+class _RecordingStateScope(object):
+    def __init__(self, is_record, train_mode):
+        self._enter_is_record = is_record
+        self._enter_train_mode = train_mode
+        self._prev_is_record = None
+        self._prev_train_mode = None
+
+    def __enter__(self):
+        if self._enter_is_record is not None:
+            self._prev_is_record = set_recording(self._enter_is_record)
+        if self._enter_train_mode is not None:
+            self._prev_train_mode = set_training(self._enter_train_mode)
+        return self
+
+    def __exit__(self, ptype, value, trace):
+        if self._enter_is_record is not None and self._prev_is_record != self._enter_is_record:
+            set_recording(self._prev_is_record)
+        if self._enter_train_mode is not None and self._prev_train_mode != self._enter_train_mode:
+            set_training(self._prev_train_mode)
+
+
+def record(train_mode=True):
+    """Scope in which executed operators are recorded for differentiation."""
+    return _RecordingStateScope(True, train_mode)
+
+
+def pause(train_mode=False):
+    return _RecordingStateScope(False, train_mode)
+
+
+def train_mode():
+    return _RecordingStateScope(None, True)
+
+
+def predict_mode():
+    return _RecordingStateScope(None, False)
+
+
+def _make_hook(ref):
+    def hook(t):
+        var = ref()
+        if var is None:
+            return
+        buf = var._grad._data
+        g = t.grad
+        if g is not buf:
+            # the engine replaced the tensor (create_graph, dtype mismatch): fold it back
+            with torch.no_grad():
+                if var._grad_req == 'add' or var._fresh_grad:
+                    buf.add_(g.detach().to(buf.dtype))
+                else:
+                    buf.copy_(g.detach())
+            t.grad = buf
+        if not var._fresh_grad:
+            var._fresh_grad = True
+            if var._grad_req == 'write':
+                _dirty_grads.append(ref)
+    return hook
+
+
+def mark_variables(variables, gradients, grad_reqs='write'):
+    """Attach gradient buffers to arrays (``MXAutogradMarkVariables``)."""
+    if isinstance(variables, NDArray):
+        variables, gradients = [variables], [gradients]
+    if isinstance(grad_reqs, str):
+        grad_reqs = [grad_reqs] * len(variables)
+    for var, g, req in zip(variables, gradients, grad_reqs):
+        t = var._data
+        if t.grad_fn is not None or (t.requires_grad and not t.is_leaf):
+            t = t.detach()
+            var._data = t
+        old = getattr(var, '_hook', None)
+        if old is not None:
+            old.remove()
+            var._hook = None
+        var._grad_req = req
+        if req == 'null':
+            var._grad = None
+            if t.is_leaf:
+                t.requires_grad_(False)
+                t.grad = None
+            continue
+        if not (t.dtype.is_floating_point or t.dtype.is_complex):
+            raise MXNetError('attach_grad needs a floating point array, got %s' % t.dtype)
+        var._grad = g
+        var._fresh_grad = False
+        t.requires_grad_(True)
+        t.grad = g._data
+        var._hook = t.register_post_accumulate_grad_hook(_make_hook(weakref.ref(var)))
+
+
+def _clear_written():
+    """grad_req='write': buffers written by a previous pass start from zero again."""
+    if not _dirty_grads:
+        return
+    bufs = []
+    for ref in _dirty_grads:
+        var = ref()
+        if var is not None and var._grad is not None and var._fresh_grad:
+            var._fresh_grad = False
+            bufs.append(var._grad._data)
+    del _dirty_grads[:]
+    if bufs:
+        with torch.no_grad():
+            torch._foreach_zero_(bufs)
+
+
+def mark_grads_consumed(arrays):
+    """Tell autograd that the gradient buffers of ``arrays`` were consumed and already cleared
+    by the caller (the fused optimizer kernels zero them in the same pass)."""
+    for a in arrays:
+        a._fresh_grad = False
+
+
+def _head_grads(heads, head_grads):
+    out = []
+    for i, h in enumerate(heads):
+        hg = head_grads[i] if head_grads is not None else None
+        if hg is None:
+            out.append(torch.ones_like(h._data))
+        else:
+            out.append(hg._data if isinstance(hg, NDArray) else torch.as_tensor(hg, device=h._data.device))
+    return out
+
+
+def backward(heads, head_grads=None, retain_graph=False, train_mode=True):  # pylint: disable=redefined-outer-name
+    """Compute gradients of ``heads`` w.r.t. every marked variable (``MXAutogradBackwardEx``)."""
+    if isinstance(heads, NDArray):
+        heads = [heads]
+        if head_grads is not None and not isinstance(head_grads, (list, tuple)):
+            head_grads = [head_grads]
+    tensors = [h._data for h in heads]
+    for t in tensors:
+        if not t.requires_grad:
+            raise MXNetError('Cannot differentiate node because it is not in a computational graph. '
+                             'You need to set is_recording to true or use autograd.record() to save '
+                             'computational graphs for backward.')
+    _clear_written()
+    grads = _head_grads(heads, head_grads)
+    prev = set_training(train_mode)
+    try:
+        torch.autograd.backward(tensors, grads, retain_graph=retain_graph)
+    finally:
+        set_training(prev)
+
+
+def grad(heads, variables, head_grads=None, retain_graph=None, create_graph=False, train_mode=True):  # pylint: disable=redefined-outer-name
+    """Gradients of heads w.r.t. variables, returned as new arrays (supports higher order)."""
+    single = isinstance(variables, NDArray)
+    if isinstance(heads, NDArray):
+        heads = [heads]
+        if head_grads is not None and not isinstance(head_grads, (list, tuple)):
+            head_grads = [head_grads]
+    if single:
+        variables = [variables]
+    if retain_graph is None:
+        retain_graph = create_graph
+    prev = set_training(train_mode)
+    try:
+        with torch.enable_grad():
+            res = torch.autograd.grad([h._data for h in heads], [v._data for v in variables],
+                                      _head_grads(heads, head_grads), retain_graph=retain_graph,
+                                      create_graph=create_graph, allow_unused=True)
+    finally:
+        set_training(prev)
+    outs = []
+    for r, v in zip(res, variables):
+        if r is None:
+            r = torch.zeros_like(v._data)
+        outs.append(v.__class__._from_tensor(r, v._ctx))
+    return outs[0] if single else outs
+
+
+def get_symbol(x):
+    """Symbol that produced ``x`` if it was computed under deferred-compute tracing."""
+    if x._sym is None:
+        raise MXNetError('array was not produced under a tracing scope; use HybridBlock.export '
+                         'or mx._deferred_compute to obtain a Symbol')
+    return x._sym
+
+
+class Function(object):
+    """User-defined differentiable function (``python/mxnet/autograd.py`` ``Function``).
+
+    Subclass and implement ``forward`` and ``backward`` over arrays; ``save_for_backward`` keeps
+    tensors for the backward pass.  An instance may be called once.
+    """
+
+    def __init__(self):
+        self._used = False
+        self.saved_tensors = ()
+
+    def save_for_backward(self, *args):
+        self.saved_tensors = args
+
+    def forward(self, *inputs):
+        raise NotImplementedError()
+
+    def backward(self, *output_grads):
+        raise NotImplementedError()
+
+    def __call__(self, *inputs):
+        assert not self._used, 'Each Function instance can only be called once. Please create another instance.'
+        self._used = True
+        func = self
+        cls = inputs[0].__class__ if inputs else NDArray
+        ctxs = [i._ctx for i in inputs]
+
+        class _Bridge(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, *tensors):
+                with pause():
+                    outs = func.forward(*[cls._from_tensor(t.detach(), c) for t, c in zip(tensors, ctxs)])
+                ctx.single = not isinstance(outs, (list, tuple))
+                outs = [outs] if ctx.single else list(outs)
+                res = tuple(o._data for o in outs)
+                return res[0] if ctx.single else res
+
+            @staticmethod
+            def backward(ctx, *gouts):
+                with pause():
+                    gin = func.backward(*[cls._from_tensor(g, None) for g in gouts])
+                gin = [gin] if not isinstance(gin, (list, tuple)) else list(gin)
+                return tuple(g._data if g is not None else None for g in gin)
+
+        if _state.state.recording:
+            with torch.enable_grad():
+                res = _Bridge.apply(*[i._data for i in inputs])
+        else:
+            with torch.no_grad():
+                res = _Bridge.apply(*[i._data for i in inputs])
+        if isinstance(res, tuple):
+            return [cls._from_tensor(r, ctxs[0] if ctxs else None) for r in res]
+        return cls._from_tensor(res, ctxs[0] if ctxs else None)

@@ -1,0 +1,181 @@
+"""Base definitions shared by every module: error hierarchy, dtype tables, small helpers.
+
+Parity targets in the reference: ``python/mxnet/base.py`` (``MXNetError``, ``_Null``,
+``NotImplementedForSymbol``), ``python/mxnet/error.py`` (error registry) and the dtype enum of
+``3rdparty/mshadow/mshadow/base.h:352-364`` (``kFloat32=0 … kBfloat16=12``), which is the integer
+written into ``.params`` files and therefore has to keep its numbering.
+"""
+from __future__ import annotations
+
+import numpy as _np
+import torch
+
+__all__ = ['MXNetError', 'NotImplementedForSymbol', 'NotSupportedForSparseNDArray', '_Null',
+           'string_types', 'numeric_types', 'integer_types', 'classproperty']
+
+string_types = (str,)
+numeric_types = (float, int, _np.generic)
+integer_types = (int, _np.integer)
+
+
+class _NullType(object):
+    """Placeholder for "argument not given" (distinct from ``None``, which is a legal value)."""
+
+    def __repr__(self):
+        return '_Null'
+
+    def __bool__(self):
+        return False
+
+
+_Null = _NullType()
+
+
+class MXNetError(RuntimeError):
+    """Default error raised by the framework (reference: ``python/mxnet/base.py:93``)."""
+
+
+class NotImplementedForSymbol(MXNetError):
+    """Raised when an NDArray-only facility is used on a Symbol."""
+
+    def __init__(self, function, alias, *args):
+        super().__init__()
+        self.function = getattr(function, '__name__', str(function))
+        self.alias = alias
+        self.args = [str(type(a)) for a in args]
+
+    def __str__(self):
+        msg = 'Function {}'.format(self.function)
+        if self.alias:
+            msg += ' (namely operator "{}")'.format(self.alias)
+        if self.args:
+            msg += ' with arguments ({})'.format(', '.join(self.args))
+        msg += ' is not implemented for Symbol and only available in NDArray.'
+        return msg
+
+
+class NotSupportedForSparseNDArray(MXNetError):
+    """Raised when a dense-only facility is used on a sparse array."""
+
+    def __init__(self, function, alias, *args):
+        super().__init__()
+        self.function = getattr(function, '__name__', str(function))
+        self.alias = alias
+        self.args = [str(type(a)) for a in args]
+
+    def __str__(self):
+        return 'Function {} is not supported for SparseNDArray'.format(self.function)
+
+
+class classproperty(object):
+    def __init__(self, fget):
+        self.fget = fget
+
+    def __get__(self, obj, owner):
+        return self.fget(owner)
+
+
+# --------------------------------------------------------------------------------------------
+# dtype tables.  The integer flag is the on-disk encoding (mshadow TypeFlag).
+# --------------------------------------------------------------------------------------------
+_DTYPE_NP_TO_MX = {
+    None: -1,
+    _np.dtype('float32'): 0,
+    _np.dtype('float64'): 1,
+    _np.dtype('float16'): 2,
+    _np.dtype('uint8'): 3,
+    _np.dtype('int32'): 4,
+    _np.dtype('int8'): 5,
+    _np.dtype('int64'): 6,
+    _np.dtype('bool'): 7,
+    _np.dtype('int16'): 8,
+    _np.dtype('uint16'): 9,
+    _np.dtype('uint32'): 10,
+    _np.dtype('uint64'): 11,
+    # 12 is bfloat16; numpy has no native bf16 so it is keyed by name below
+}
+_DTYPE_MX_TO_NP = {v: k for k, v in _DTYPE_NP_TO_MX.items() if k is not None}
+BFLOAT16_FLAG = 12
+
+_TORCH_TO_NP = {
+    torch.float32: _np.dtype('float32'), torch.float64: _np.dtype('float64'),
+    torch.float16: _np.dtype('float16'), torch.uint8: _np.dtype('uint8'),
+    torch.int32: _np.dtype('int32'), torch.int8: _np.dtype('int8'),
+    torch.int64: _np.dtype('int64'), torch.bool: _np.dtype('bool'),
+    torch.int16: _np.dtype('int16'),
+}
+for _name in ('uint16', 'uint32', 'uint64'):
+    if hasattr(torch, _name):
+        _TORCH_TO_NP[getattr(torch, _name)] = _np.dtype(_name)
+_NP_TO_TORCH = {v: k for k, v in _TORCH_TO_NP.items()}
+
+_TORCH_TO_FLAG = {t: _DTYPE_NP_TO_MX[n] for t, n in _TORCH_TO_NP.items()}
+_TORCH_TO_FLAG[torch.bfloat16] = BFLOAT16_FLAG
+_FLAG_TO_TORCH = {v: k for k, v in _TORCH_TO_FLAG.items()}
+
+
+class _BFloat16Name(str):
+    """Stand-in dtype object for bfloat16 (NumPy has none).  Compares equal to 'bfloat16'."""
+    name = 'bfloat16'
+    itemsize = 2
+    kind = 'f'
+
+
+bfloat16 = _BFloat16Name('bfloat16')
+
+
+def to_torch_dtype(dtype):
+    """Accepts numpy dtypes, python types, strings, torch dtypes; returns a torch dtype."""
+    if dtype is None:
+        return None
+    if isinstance(dtype, torch.dtype):
+        return dtype
+    if isinstance(dtype, str) and dtype == 'bfloat16':
+        return torch.bfloat16
+    if dtype is bool:
+        return torch.bool
+    if dtype is int:
+        return torch.int64
+    if dtype is float:
+        return torch.float64
+    try:
+        return _NP_TO_TORCH[_np.dtype(dtype)]
+    except (KeyError, TypeError):
+        raise TypeError('unsupported dtype %r' % (dtype,))
+
+
+def to_numpy_dtype(dtype):
+    """Inverse of :func:`to_torch_dtype`; bfloat16 maps to the :data:`bfloat16` stand-in."""
+    if dtype is None:
+        return None
+    if isinstance(dtype, torch.dtype):
+        if dtype == torch.bfloat16:
+            return bfloat16
+        return _TORCH_TO_NP[dtype]
+    if isinstance(dtype, str) and dtype == 'bfloat16':
+        return bfloat16
+    return _np.dtype(dtype)
+
+
+def dtype_name(dtype):
+    d = to_numpy_dtype(dtype)
+    return d.name if d is not None else 'None'
+
+
+def dtype_flag(dtype):
+    """mshadow type flag for a dtype (any accepted spelling)."""
+    return _TORCH_TO_FLAG[to_torch_dtype(dtype)]
+
+
+def flag_to_torch(flag):
+    return _FLAG_TO_TORCH[int(flag)]
+
+
+def is_float_dtype(dtype):
+    return to_torch_dtype(dtype) in (torch.float16, torch.bfloat16, torch.float32, torch.float64)
+
+
+def check_call(ret):
+    """Kept for API familiarity: native calls here raise directly, so a non-zero code is an error."""
+    if ret != 0:
+        raise MXNetError('native call failed with code %d' % ret)

@@ -1,0 +1,138 @@
+"""Typed registry of the ``MXNET_*`` environment flags.
+
+The reference reads ~100 variables ad hoc through ``dmlc::GetEnv`` (documented in
+``docs/static_site/src/pages/api/faq/env_var.md``).  Here every flag is declared once with a type,
+a default and a one-line meaning, so ``mx.env.describe()`` lists them and tests can flip them with
+:func:`scope`, the counterpart of ``test_utils.environment()`` (``python/mxnet/test_utils.py:2352``)
+and of ``MXGetEnv/MXSetEnv`` (``src/c_api/c_api_test.cc:108-120``).
+"""
+import contextlib
+import os
+
+__all__ = ['declare', 'get', 'set', 'scope', 'describe', 'FLAGS']
+
+FLAGS = {}
+
+
+class _Flag(object):
+    __slots__ = ('name', 'type', 'default', 'doc')
+
+    def __init__(self, name, type_, default, doc):
+        self.name, self.type, self.default, self.doc = name, type_, default, doc
+
+    def parse(self, raw):
+        if self.type is bool:
+            return raw.strip().lower() not in ('0', 'false', 'off', 'no', '')
+        return self.type(raw)
+
+
+def declare(name, type_, default, doc=''):
+    FLAGS[name] = _Flag(name, type_, default, doc)
+    return FLAGS[name]
+
+
+def get(name, default=None):
+    """Current value of a flag (environment wins over the declared default)."""
+    flag = FLAGS.get(name)
+    raw = os.environ.get(name)
+    if flag is None:
+        return raw if raw is not None else default
+    if raw is None:
+        return flag.default if default is None else default
+    try:
+        return flag.parse(raw)
+    except (TypeError, ValueError):
+        return flag.default
+
+
+def set(name, value):  # pylint: disable=redefined-builtin
+    if value is None:
+        os.environ.pop(name, None)
+    else:
+        os.environ[name] = str(int(value)) if isinstance(value, bool) else str(value)
+
+
+@contextlib.contextmanager
+def scope(*args, **kwargs):
+    """``with env.scope('MXNET_X', '1'):`` or ``with env.scope(MXNET_X=1, MXNET_Y=None):``."""
+    if args:
+        assert len(args) == 2, 'scope(name, value) or scope(**flags)'
+        kwargs = dict(kwargs)
+        kwargs[args[0]] = args[1]
+    saved = {k: os.environ.get(k) for k in kwargs}
+    try:
+        for k, v in kwargs.items():
+            set(k, v)
+        yield
+    finally:
+        for k, v in saved.items():
+            set(k, v)
+
+
+def describe():
+    rows = []
+    for f in sorted(FLAGS.values(), key=lambda f: f.name):
+        rows.append('%-44s %-6s default=%-10r %s' % (f.name, f.type.__name__, f.default, f.doc))
+    return '\n'.join(rows)
+
+
+# ---- engine -------------------------------------------------------------------------------
+declare('MXNET_ENGINE_TYPE', str, 'ThreadedEnginePerDevice',
+        'NaiveEngine = fully synchronous; ThreadedEngine / ThreadedEnginePerDevice / ...Async = stream engine')
+declare('MXNET_CPU_WORKER_NTHREADS', int, 1, 'host worker threads of the native dependency engine')
+declare('MXNET_GPU_WORKER_NTHREADS', int, 2, 'compute streams per GPU')
+declare('MXNET_GPU_COPY_NTHREADS', int, 2, 'copy streams per GPU')
+declare('MXNET_CPU_PRIORITY_NTHREADS', int, 4, 'host threads serving prioritised tasks')
+declare('MXNET_EXEC_BULK_EXEC_INFERENCE', bool, True, 'bulk (graph-capture) inference segments')
+declare('MXNET_EXEC_BULK_EXEC_TRAIN', bool, True, 'bulk (graph-capture) training segments')
+declare('MXNET_EXEC_BULK_EXEC_MAX_NODE_TRAIN', int, 15, 'max nodes per bulked segment')
+declare('MXNET_ENABLE_CUDA_GRAPHS', bool, True, 'hybridize(static_alloc, static_shape) captures CUDA graphs')
+declare('MXNET_CUDA_GRAPHS_VERBOSE', bool, False, 'log graph capture / re-capture events')
+declare('MXNET_ENGINE_INFO', bool, False, 'verbose engine logging')
+# ---- memory -------------------------------------------------------------------------------
+declare('MXNET_GPU_MEM_POOL_TYPE', str, 'Naive', 'Naive (round to multiple) | Round (power of two) | Unpooled')
+declare('MXNET_CPU_MEM_POOL_TYPE', str, 'Naive', 'same choices for host memory')
+declare('MXNET_CPU_PINNED_MEM_POOL_TYPE', str, 'Naive', 'same choices for pinned host memory')
+declare('MXNET_GPU_MEM_POOL_RESERVE', int, 5, 'percent of device memory left unpooled')
+declare('MXNET_GPU_MEM_POOL_PAGE_SIZE', int, 4096, 'rounding granule of small allocations')
+declare('MXNET_GPU_MEM_LARGE_ALLOC_ROUND_SIZE', int, 2097152, 'rounding granule of large allocations')
+declare('MXNET_GPU_MEM_POOL_ROUND_LINEAR_CUTOFF', int, 24, 'log2 size above which Round pool goes linear')
+declare('MXNET_USE_NAIVE_STORAGE_MANAGER', bool, False, 'bypass pooling entirely')
+declare('MXNET_GPU_TEMP_COPY', int, 1, 'temp workspaces per GPU')
+declare('MXNET_CPU_TEMP_COPY', int, 4, 'temp workspaces per CPU')
+# ---- kvstore ------------------------------------------------------------------------------
+declare('MXNET_KVSTORE_REDUCTION_NTHREADS', int, 4, 'threads of the host tree-sum of kvstore local')
+declare('MXNET_KVSTORE_BIGARRAY_BOUND', int, 1000000, 'element count above which a key is sliced')
+declare('MXNET_KVSTORE_USETREE', bool, False, 'multi-root sliced reduce for kvstore device')
+declare('MXNET_KVSTORE_TREE_ARRAY_BOUND', int, 10000000, 'slice bound of the tree reduce')
+declare('MXNET_KVSTORE_SLICE_THRESHOLD', int, 40000, 'P3 slice size')
+declare('MXNET_KVSTORE_SERIAL_PUSH', bool, False, 'serialise pushes (debug)')
+declare('MXNET_ENABLE_GPU_P2P', bool, True, 'map peer memory for kvstore device/nccl')
+declare('MXNET_UPDATE_ON_KVSTORE', bool, True, 'default of Trainer.update_on_kvstore')
+declare('MXNET_KVSTORE_FUSED', bool, True, 'use the fused reduce-scatter+update+all-gather kernels')
+declare('MXNET_KVSTORE_BUCKET_MB', int, 32, 'gradient bucket size of the fused path')
+declare('MXNET_KVSTORE_WAIT_MS', int, 20000, 'bound of device-side peer waits before an error status')
+# ---- numerics -----------------------------------------------------------------------------
+declare('MXNET_SAFE_ACCUMULATION', bool, True, 'accumulate fp16 reductions in fp32')
+declare('MXNET_ENFORCE_DETERMINISM', bool, False, 'refuse non-deterministic kernels')
+declare('MXNET_CUDA_ALLOW_TENSOR_CORE', bool, True, 'allow tensor-core GEMM/conv')
+declare('MXNET_FC_TRUE_FP16', bool, False, 'accumulate FullyConnected in fp16 (never on tcgen05)')
+declare('MXNET_B200_KERNELS', bool, True, 'use the hand-written sm_100a kernels (0 = library path)')
+# ---- graph --------------------------------------------------------------------------------
+declare('MXNET_USE_FUSION', bool, True, 'pointwise fusion')
+declare('MXNET_ELIMINATE_COMMON_EXPR', bool, True, 'common-subexpression elimination on symbols')
+declare('MXNET_MEMORY_OPT', bool, False, 'recompute cheap activations in backward')
+declare('MXNET_BACKWARD_DO_MIRROR', bool, False, 'legacy spelling of MXNET_MEMORY_OPT')
+declare('MXNET_SUBGRAPH_BACKEND', str, '', 'default subgraph backend')
+# ---- profiler / misc ----------------------------------------------------------------------
+declare('MXNET_PROFILER_AUTOSTART', bool, False, 'start profiling at import')
+declare('MXNET_PROFILER_MODE', int, 0, 'bit mask: 1 symbolic, 2 imperative, 4 api, 8 memory')
+declare('MXNET_HOME', str, os.path.join(os.path.expanduser('~'), '.mxnet'), 'data / model cache')
+declare('MXNET_GLUON_REPO', str, 'https://apache-mxnet.s3-accelerate.dualstack.amazonaws.com/', 'model repo URL')
+declare('MXNET_LIBRARY_PATH', str, '', 'override for the native runtime library')
+declare('MXNET_MODULE_SEED', int, -1, 'test module seed')
+declare('MXNET_TEST_SEED', int, -1, 'test function seed')
+declare('MXNET_USE_OPERATOR_TUNING', bool, True, 'tune OpenMP use per CPU op')
+declare('MXNET_OMP_MAX_THREADS', int, 0, 'cap of intra-op host threads (0 = auto)')
+declare('MXNET_OPTIMIZER_AGGREGATION_SIZE', int, 4, 'tensors per multi-tensor optimizer call')
+declare('MXNET_STORAGE_FALLBACK_LOG_VERBOSE', bool, True, 'log dense fallbacks of sparse inputs')

@@ -1,0 +1,222 @@
+"""Operator registry and the single imperative entry point :func:`invoke`.
+
+The reference registers ~950 operator names with nnvm (``NNVM_REGISTER_OP`` …
+``include/mxnet/op_attr_types.h:215-382``) and funnels every call through
+``Imperative::Invoke`` (``src/imperative/imperative.cc:107-139``).  Here an operator is a Python
+callable over ``torch.Tensor`` arguments: array inputs first (by declared name), attributes as
+keyword arguments.  :func:`invoke` is the one place where
+
+* array wrappers are unwrapped / results wrapped (``mx.nd.NDArray`` or ``mx.np.ndarray``),
+* the autograd recording flag is mapped onto torch's grad mode,
+* the AMP cast policy, the profiler and op monitors hook in,
+* deferred-compute tracing records a graph node (``Imperative::RecordDeferredCompute``,
+  ``imperative.cc:336-382``) so ``HybridBlock.export`` can emit ``-symbol.json``.
+
+Attribute values are kept as Python objects at run time and are stringified with the reference's
+formatting only when a Symbol is serialised (``"(3, 3)"``, ``"True"``, ``"None"``).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _state
+from ..base import MXNetError
+
+__all__ = ['OpDef', 'register', 'get', 'has', 'list_ops', 'invoke', 'alias']
+
+_OPS = {}
+
+
+class OpDef(object):
+    """Description of one operator.
+
+    inputs   : tuple of array-argument names in positional order; a trailing name starting with
+               ``*`` makes the operator variadic (``Concat(*data, dim=1)``).
+    fn       : callable(*tensors, **attrs) -> Tensor | tuple[Tensor]
+    nout     : number of visible outputs (int) or callable(attrs) -> int
+    defaults : attribute defaults (used for JSON round trips and ``list_attr``).
+    """
+    __slots__ = ('name', 'fn', 'inputs', 'variadic', 'nout', 'defaults', 'aliases', 'aux', 'doc',
+                 'mutate', 'hidden_outputs')
+
+    def __init__(self, name, fn, inputs, nout=1, defaults=None, aux=(), mutate=(), doc=None):
+        self.name = name
+        self.fn = fn
+        inputs = tuple(inputs)
+        self.variadic = bool(inputs) and inputs[-1].startswith('*')
+        self.inputs = tuple(i.lstrip('*') for i in inputs)
+        self.nout = nout
+        self.defaults = dict(defaults or {})
+        self.aliases = []
+        self.aux = tuple(aux)          # names of inputs that are auxiliary states (BatchNorm moving stats)
+        self.mutate = tuple(mutate)    # names of inputs updated in place (optimizer ops)
+        self.doc = doc or (fn.__doc__ if fn is not None else None)
+
+    def num_outputs(self, attrs):
+        return self.nout(attrs) if callable(self.nout) else self.nout
+
+    def __repr__(self):
+        return '<OpDef %s%s>' % (self.name, self.inputs)
+
+
+def register(name, *aliases, inputs=('data',), nout=1, defaults=None, aux=(), mutate=()):
+    """Decorator: ``@register('FullyConnected', inputs=('data','weight','bias'))``."""
+    def deco(fn):
+        op = OpDef(name, fn, inputs, nout=nout, defaults=defaults, aux=aux, mutate=mutate)
+        _OPS[name] = op
+        for a in aliases:
+            _OPS[a] = op
+            op.aliases.append(a)
+        return fn
+    return deco
+
+
+def alias(name, *aliases):
+    op = _OPS[name]
+    for a in aliases:
+        _OPS[a] = op
+        op.aliases.append(a)
+
+
+def get(name):
+    try:
+        return _OPS[name]
+    except KeyError:
+        raise MXNetError('Operator %s is not registered' % name)
+
+
+def has(name):
+    return name in _OPS
+
+
+def list_ops():
+    return sorted(_OPS)
+
+
+# --------------------------------------------------------------------------------------------
+# array class plumbing (filled in by ndarray/ndarray.py and numpy/multiarray.py at import)
+# --------------------------------------------------------------------------------------------
+_array_classes = {}   # 'nd' -> NDArray, 'np' -> ndarray
+
+
+def _set_array_class(kind, cls):
+    _array_classes[kind] = cls
+
+
+def _wrap(t, kind, ctx=None):
+    return _array_classes[kind]._from_tensor(t, ctx)
+
+
+def invoke(op, args, attrs, out=None, kind=None):
+    """Run operator ``op`` (OpDef or name) on array wrappers ``args`` with attribute dict ``attrs``.
+
+    ``args`` may contain array wrappers, raw tensors, python scalars or ``None`` (optional
+    inputs).  Returns a wrapper, or a list of wrappers for multi-output operators.
+    """
+    if isinstance(op, str):
+        op = get(op)
+    st = _state.state
+    tensors = []
+    ctx = None
+    base = _array_classes['nd']
+    for a in args:
+        if isinstance(a, base):
+            if kind is None:
+                kind = a._kind
+            if ctx is None:
+                ctx = a._ctx
+            tensors.append(a._data)
+        else:
+            tensors.append(a)
+    if kind is None:
+        kind = 'np' if st.np_array else 'nd'
+    hook = _state.amp_hook
+    if hook is not None:
+        tensors = hook(op.name, tensors)
+    prof = _state.profiler_hook
+    pctx = prof(op.name) if prof is not None else None
+    if pctx is not None:
+        pctx.__enter__()
+    try:
+        if st.recording:
+            if torch.is_grad_enabled():
+                res = op.fn(*tensors, **attrs)
+            else:
+                with torch.enable_grad():
+                    res = op.fn(*tensors, **attrs)
+        else:
+            if torch.is_grad_enabled():
+                with torch.no_grad():
+                    res = op.fn(*tensors, **attrs)
+            else:
+                res = op.fn(*tensors, **attrs)
+    finally:
+        if pctx is not None:
+            pctx.__exit__(None, None, None)
+    multi = isinstance(res, (tuple, list))
+    if out is not None:
+        outs = out if isinstance(out, (list, tuple)) else [out]
+        ress = res if multi else [res]
+        for o, r in zip(outs, ress):
+            if o._data is not r:
+                with torch.no_grad():
+                    o._data.copy_(r)
+        result = out
+        wrapped = list(outs)
+    elif multi:
+        wrapped = [_wrap(r, kind, ctx) if isinstance(r, torch.Tensor) else r for r in res]
+        result = wrapped
+    else:
+        result = _wrap(res, kind, ctx) if isinstance(res, torch.Tensor) else res
+        wrapped = [result]
+    tracer = st.tracer
+    if tracer is not None:
+        tracer.record(op, args, attrs, wrapped)
+    mon = _state.op_monitor
+    if mon is not None:
+        mon(op.name, wrapped)
+    return result
+
+
+def make_frontend(op, kind):
+    """Build the user-facing function of an operator for one namespace (``mx.nd`` or ``mx.npx``).
+
+    Mirrors the code generation of ``python/mxnet/ndarray/register.py:116-270``: array arguments
+    may be given positionally or by keyword, attributes by keyword (or positionally after the
+    arrays), ``out=`` receives the result, ``name=`` is accepted and ignored imperatively.
+    """
+    if isinstance(op, str):
+        op = get(op)
+    in_names = op.inputs
+    attr_names = [k for k in op.defaults]
+
+    if op.variadic:
+        def frontend(*args, out=None, name=None, **kwargs):
+            arrays = []
+            for a in args:
+                if isinstance(a, (list, tuple)):
+                    arrays.extend(a)
+                else:
+                    arrays.append(a)
+            kwargs.pop('num_args', None)
+            return invoke(op, arrays, kwargs, out=out, kind=kind)
+    else:
+        n_in = len(in_names)
+
+        def frontend(*args, out=None, name=None, **kwargs):
+            arrays = list(args[:n_in])
+            extra = args[n_in:]
+            if len(arrays) < n_in:
+                arrays.extend([None] * (n_in - len(arrays)))
+            for i, nm in enumerate(in_names):
+                if nm in kwargs:
+                    arrays[i] = kwargs.pop(nm)
+            while arrays and arrays[-1] is None:
+                arrays.pop()
+            for k, v in zip(attr_names, extra):
+                kwargs[k] = v
+            return invoke(op, arrays, kwargs, out=out, kind=kind)
+    frontend.__name__ = op.name
+    frontend.__doc__ = op.doc
+    frontend._op = op
+    return frontend

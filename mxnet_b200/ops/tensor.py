@@ -1,0 +1,1622 @@
+"""Tensor operators: elementwise, broadcast, reductions, indexing, shape manipulation, linalg.
+
+Reference family: ``src/operator/tensor/*`` (42 kLoC; elementwise/broadcast/reduce kernels are
+NVRTC-generated there, ``elemwise_unary_op.cc``, ``elemwise_binary_broadcast_op.cc``,
+``reduce_rtc.cc``).  Here each operator is a function over ``torch.Tensor``; the ones that sit
+on a training hot path dispatch to the ahead-of-time sm_100a kernels in ``ops/cuda`` when the
+input is a CUDA tensor, everything else is served by the tensor library so that the whole op
+surface exists from the start.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as _np
+import torch
+import torch.nn.functional as F
+
+from .registry import register, alias
+from ..base import MXNetError, to_torch_dtype
+
+# ------------------------------------------------------------------------------------------
+# helpers
+# ------------------------------------------------------------------------------------------
+
+
+def _axes(axis, ndim, exclude=False):
+    if axis is None or axis == ():
+        ax = tuple(range(ndim))
+        return () if exclude else ax
+    if isinstance(axis, int):
+        axis = (axis,)
+    ax = tuple(sorted(a % ndim for a in axis))
+    if exclude:
+        ax = tuple(i for i in range(ndim) if i not in ax)
+    return ax
+
+
+def legacy_reshape_shape(src, target, reverse=False):
+    """Resolve MXNet's special reshape codes 0, -1, -2, -3, -4 (``src/operator/tensor/matrix_op-inl.h``)."""
+    src = list(src)
+    target = list(target)
+    if reverse:
+        src = src[::-1]
+        target = target[::-1]
+        # -4 triplets must keep (-4, a, b) order after reversal
+        fixed, i = [], 0
+        while i < len(target):
+            if i + 2 < len(target) and target[i + 2] == -4:
+                fixed.extend([-4, target[i + 1], target[i]])
+                i += 3
+            else:
+                fixed.append(target[i])
+                i += 1
+        target = fixed
+    out, si, i, infer = [], 0, 0, -1
+    while i < len(target):
+        t = target[i]
+        if t == 0:
+            out.append(src[si]); si += 1
+        elif t == -1:
+            infer = len(out); out.append(1); si += 1
+        elif t == -2:
+            out.extend(src[si:]); si = len(src)
+        elif t == -3:
+            out.append(src[si] * src[si + 1]); si += 2
+        elif t == -4:
+            a, b = target[i + 1], target[i + 2]
+            d = src[si]; si += 1
+            if a == -1:
+                a = d // b
+            if b == -1:
+                b = d // a
+            out.extend([a, b]); i += 2
+        else:
+            out.append(t); si += 1
+        i += 1
+    if infer >= 0:
+        total = 1
+        for s in src:
+            total *= s
+        known = 1
+        for j, s in enumerate(out):
+            if j != infer:
+                known *= s
+        out[infer] = total // known if known else 0
+    if reverse:
+        out = out[::-1]
+    return tuple(out)
+
+
+# ------------------------------------------------------------------------------------------
+# unary math
+# ------------------------------------------------------------------------------------------
+def _gammaln(x): return torch.lgamma(x)
+def _gamma(x):
+    return torch.special.gammaln(x).exp() * _gamma_sign(x)
+
+
+def _gamma_sign(x):
+    # sign of Gamma(x) for negative non-integers: (-1)^ceil(-x)
+    neg = x < 0
+    k = torch.ceil(-x)
+    s = torch.where((k % 2) == 1, -torch.ones_like(x), torch.ones_like(x))
+    return torch.where(neg, s, torch.ones_like(x))
+
+
+_UNARY = {
+    'abs': torch.abs, 'sign': torch.sign, 'sqrt': torch.sqrt, 'rsqrt': torch.rsqrt,
+    'cbrt': lambda x: torch.sign(x) * torch.abs(x).pow(1.0 / 3), 'rcbrt': lambda x: torch.sign(x) / torch.abs(x).pow(1.0 / 3),
+    'square': torch.square, 'reciprocal': torch.reciprocal, 'negative': torch.neg,
+    'exp': torch.exp, 'expm1': torch.expm1, 'log': torch.log, 'log10': torch.log10, 'log2': torch.log2,
+    'log1p': torch.log1p, 'sin': torch.sin, 'cos': torch.cos, 'tan': torch.tan, 'arcsin': torch.asin,
+    'arccos': torch.acos, 'arctan': torch.atan, 'sinh': torch.sinh, 'cosh': torch.cosh, 'tanh': torch.tanh,
+    'arcsinh': torch.asinh, 'arccosh': torch.acosh, 'arctanh': torch.atanh,
+    'degrees': torch.rad2deg, 'radians': torch.deg2rad, 'floor': torch.floor, 'ceil': torch.ceil,
+    'trunc': torch.trunc, 'rint': torch.round, 'round': lambda x: torch.sign(x) * torch.floor(torch.abs(x) + 0.5),
+    'fix': torch.trunc, 'erf': torch.erf, 'erfinv': torch.erfinv, 'gammaln': torch.lgamma, 'gamma': _gamma,
+    'digamma': torch.digamma, 'relu': torch.relu, 'sigmoid': torch.sigmoid, 'log_sigmoid': F.logsigmoid,
+    'softsign': F.softsign, 'mish': F.mish, 'logical_not': lambda x: (x == 0).to(x.dtype),
+    'identity': lambda x: x, 'stop_gradient': lambda x: x.detach(), 'make_loss': lambda x: x,
+    'isnan': torch.isnan, 'isinf': torch.isinf, 'isfinite': torch.isfinite,
+    'isposinf': torch.isposinf, 'isneginf': torch.isneginf,
+}
+
+
+def _reg_unary(name, fn):
+    def op(data):
+        if not data.dtype.is_floating_point and name not in (
+                'abs', 'sign', 'square', 'negative', 'relu', 'identity', 'stop_gradient', 'make_loss',
+                'logical_not', 'isnan', 'isinf', 'isfinite', 'isposinf', 'isneginf', 'floor', 'ceil', 'trunc',
+                'rint', 'round', 'fix'):
+            return fn(data.float())
+        return fn(data)
+    op.__name__ = name
+    register(name, '_npi_' + name, inputs=('data',))(op)
+
+
+for _n, _f in _UNARY.items():
+    _reg_unary(_n, _f)
+alias('identity', '_copy', '_npi_copy', '_npi_positive')
+alias('stop_gradient', 'BlockGrad', '_npx_stop_gradient')
+alias('make_loss', 'MakeLoss')
+alias('negative', '_npi_negative')
+alias('abs', '_npi_absolute', '_npi_fabs')
+alias('arcsin', '_npi_arcsin')
+alias('rint', '_npi_rint')
+alias('isnan', '_npi_isnan')
+register('_copy', inputs=('data',))(lambda data: data.clone())
+register('_npi_copy', inputs=('data',))(lambda data: data.clone())
+
+
+@register('_npi_around', 'round_np', inputs=('data',), defaults={'decimals': 0})
+def _around(data, decimals=0):
+    return torch.round(data, decimals=decimals)
+
+
+@register('_npi_invert', '_npi_bitwise_not', inputs=('data',))
+def _invert(data):
+    return torch.bitwise_not(data) if data.dtype != torch.bool else ~data
+
+
+@register('_npi_logical_not', inputs=('data',))
+def _np_logical_not(data):
+    return torch.logical_not(data)
+
+
+# ------------------------------------------------------------------------------------------
+# binary families
+# ------------------------------------------------------------------------------------------
+def _tdiv(a, b):
+    if isinstance(a, torch.Tensor) and not a.dtype.is_floating_point and \
+            (not isinstance(b, torch.Tensor) or not b.dtype.is_floating_point):
+        if isinstance(b, (float,)):
+            return torch.true_divide(a, b)
+        return torch.div(a, b, rounding_mode='trunc')
+    return torch.true_divide(a, b)
+
+
+def _mod(a, b):
+    # MXNet mod follows the sign of the divisor like python; result for b==0 is 0
+    if isinstance(b, torch.Tensor):
+        r = torch.remainder(a, torch.where(b == 0, torch.ones_like(b), b))
+        return torch.where(b == 0, torch.zeros_like(r), r)
+    if b == 0:
+        return torch.zeros_like(a) if isinstance(a, torch.Tensor) else 0
+    return torch.remainder(a, b)
+
+
+_BINARY = {
+    'add': torch.add, 'sub': torch.sub, 'mul': torch.mul, 'div': _tdiv, 'mod': _mod,
+    'power': torch.pow, 'maximum': torch.maximum, 'minimum': torch.minimum,
+    'hypot': torch.hypot, 'floordiv': lambda a, b: torch.floor_divide(a, b),
+}
+_COMPARE = {
+    'equal': torch.eq, 'not_equal': torch.ne, 'greater': torch.gt, 'greater_equal': torch.ge,
+    'lesser': torch.lt, 'lesser_equal': torch.le,
+}
+_LOGICAL = {
+    'logical_and': lambda a, b: torch.logical_and(a != 0, b != 0),
+    'logical_or': lambda a, b: torch.logical_or(a != 0, b != 0),
+    'logical_xor': lambda a, b: torch.logical_xor(a != 0, b != 0),
+}
+_BITWISE = {'bitwise_and': torch.bitwise_and, 'bitwise_or': torch.bitwise_or, 'bitwise_xor': torch.bitwise_xor,
+            'left_shift': torch.bitwise_left_shift, 'right_shift': torch.bitwise_right_shift}
+
+
+def _as_t(x, like):
+    if isinstance(x, torch.Tensor):
+        return x
+    return torch.as_tensor(x, device=like.device, dtype=like.dtype if not isinstance(x, float)
+                           or like.dtype.is_floating_point else torch.float32)
+
+
+def _promote(a, b):
+    """Operands of different dtype: NumPy-style promotion (only reachable from mx.np)."""
+    if isinstance(a, torch.Tensor) and isinstance(b, torch.Tensor) and a.dtype != b.dtype:
+        dt = torch.promote_types(a.dtype, b.dtype)
+        return a.to(dt), b.to(dt)
+    return a, b
+
+
+def _scalar_for(x, s):
+    """Python scalar operand: ints stay ints for int tensors, floats promote ints to float32."""
+    if isinstance(s, bool):
+        return s
+    if isinstance(s, float) and not x.dtype.is_floating_point:
+        return s
+    return s
+
+
+def _reg_binary(name, fn, legacy_names, result_bool=False, np_name=None):
+    np_name = np_name or name
+
+    def tt_legacy(lhs, rhs):
+        lhs, rhs = _promote(lhs, rhs)
+        r = fn(lhs, rhs)
+        return r.to(lhs.dtype) if result_bool else r
+
+    def tt_np(lhs, rhs):
+        lhs, rhs = _promote(lhs, rhs)
+        return fn(lhs, rhs)
+
+    def ts_legacy(data, scalar=0.0, is_int=None):
+        r = fn(data, _maybe_float(data, scalar))
+        return r.to(data.dtype) if result_bool else r
+
+    def rts_legacy(data, scalar=0.0, is_int=None):
+        s = torch.as_tensor(scalar, device=data.device,
+                            dtype=data.dtype if data.dtype.is_floating_point or isinstance(scalar, int) else torch.float32)
+        r = fn(s, data)
+        return r.to(data.dtype) if result_bool else r
+
+    def ts_np(data, scalar=0.0, is_int=None):
+        return fn(data, _maybe_float(data, scalar))
+
+    def rts_np(data, scalar=0.0, is_int=None):
+        s = torch.as_tensor(scalar, device=data.device,
+                            dtype=data.dtype if data.dtype.is_floating_point or isinstance(scalar, (int, bool))
+                            else torch.float32)
+        return fn(s, data)
+
+    for ln in legacy_names:
+        register('broadcast_' + ln, 'elemwise_' + ln, '_' + ln, inputs=('lhs', 'rhs'))(tt_legacy)
+    register('broadcast_' + name, inputs=('lhs', 'rhs'))(tt_legacy)
+    register('_%s_scalar' % name, inputs=('data',), defaults={'scalar': 0.0})(ts_legacy)
+    register('_r%s_scalar' % name, inputs=('data',), defaults={'scalar': 0.0})(rts_legacy)
+    for ln in legacy_names:
+        register('_%s_scalar' % ln, inputs=('data',), defaults={'scalar': 0.0})(ts_legacy)
+        register('_r%s_scalar' % ln, inputs=('data',), defaults={'scalar': 0.0})(rts_legacy)
+    register('_npi_' + np_name, inputs=('lhs', 'rhs'))(tt_np)
+    register('_npi_%s_scalar' % np_name, inputs=('data',), defaults={'scalar': 0.0})(ts_np)
+    register('_npi_r%s_scalar' % np_name, inputs=('data',), defaults={'scalar': 0.0})(rts_np)
+    if np_name != name:
+        register('_npi_' + name, inputs=('lhs', 'rhs'))(tt_np)
+        register('_npi_%s_scalar' % name, inputs=('data',), defaults={'scalar': 0.0})(ts_np)
+        register('_npi_r%s_scalar' % name, inputs=('data',), defaults={'scalar': 0.0})(rts_np)
+
+
+def _maybe_float(data, scalar):
+    if isinstance(scalar, float) and not data.dtype.is_floating_point and data.dtype != torch.bool:
+        return scalar
+    return scalar
+
+
+_reg_binary('add', torch.add, ['plus'])
+_reg_binary('sub', torch.sub, ['minus'], np_name='subtract')
+_reg_binary('mul', torch.mul, [], np_name='multiply')
+_reg_binary('div', _tdiv, [], np_name='true_divide')
+_reg_binary('mod', _mod, [])
+_reg_binary('power', torch.pow, [])
+_reg_binary('maximum', torch.maximum, [])
+_reg_binary('minimum', torch.minimum, [])
+_reg_binary('hypot', torch.hypot, [])
+_reg_binary('floordiv', torch.floor_divide, [], np_name='floor_divide')
+for _n, _f in _COMPARE.items():
+    _reg_binary(_n, _f, [], result_bool=True,
+                np_name={'lesser': 'less', 'lesser_equal': 'less_equal'}.get(_n, _n))
+for _n, _f in _LOGICAL.items():
+    _reg_binary(_n, _f, [], result_bool=True)
+for _n, _f in _BITWISE.items():
+    _reg_binary(_n, _f, [])
+alias('broadcast_add', 'broadcast_plus', 'elemwise_add', '_add', '_Plus', '_plus')
+alias('broadcast_sub', 'broadcast_minus', 'elemwise_sub', '_sub', '_Minus', '_minus')
+alias('broadcast_mul', 'elemwise_mul', '_mul', '_Mul')
+alias('broadcast_div', 'elemwise_div', '_div', '_Div')
+alias('broadcast_mod', '_mod', '_Mod')
+alias('broadcast_power', '_power', '_Power')
+alias('broadcast_maximum', '_maximum', '_Maximum')
+alias('broadcast_minimum', '_minimum', '_Minimum')
+alias('broadcast_hypot', '_hypot', '_Hypot')
+alias('broadcast_equal', '_equal')
+alias('broadcast_not_equal', '_not_equal')
+alias('broadcast_greater', '_greater')
+alias('broadcast_greater_equal', '_greater_equal')
+alias('broadcast_lesser', '_lesser')
+alias('broadcast_lesser_equal', '_lesser_equal')
+alias('broadcast_logical_and', '_logical_and')
+alias('broadcast_logical_or', '_logical_or')
+alias('broadcast_logical_xor', '_logical_xor')
+alias('_add_scalar', '_plus_scalar', '_PlusScalar')
+alias('_sub_scalar', '_minus_scalar', '_MinusScalar')
+alias('_rsub_scalar', '_rminus_scalar', '_RMinusScalar')
+alias('_mul_scalar', '_MulScalar')
+alias('_div_scalar', '_DivScalar')
+alias('_rdiv_scalar', '_RDivScalar')
+alias('_mod_scalar', '_ModScalar')
+alias('_rmod_scalar', '_RModScalar')
+alias('_power_scalar', '_PowerScalar')
+alias('_rpower_scalar', '_RPowerScalar')
+alias('_maximum_scalar', '_MaximumScalar')
+alias('_minimum_scalar', '_MinimumScalar')
+alias('_equal_scalar', '_EqualScalar')
+alias('_not_equal_scalar', '_NotEqualScalar')
+alias('_greater_scalar', '_GreaterScalar')
+alias('_greater_equal_scalar', '_GreaterEqualScalar')
+alias('_lesser_scalar', '_LesserScalar')
+alias('_lesser_equal_scalar', '_LesserEqualScalar')
+alias('_npi_true_divide', '_npi_divide')
+alias('_npi_true_divide_scalar', '_npi_divide_scalar')
+alias('_npi_rtrue_divide_scalar', '_npi_rdivide_scalar')
+
+
+@register('_npi_arctan2', 'arctan2', inputs=('lhs', 'rhs'))
+def _arctan2(lhs, rhs):
+    return torch.atan2(lhs, rhs)
+
+
+@register('_npi_copysign', inputs=('lhs', 'rhs'))
+def _copysign(lhs, rhs):
+    return torch.copysign(lhs, rhs)
+
+
+@register('_npi_ldexp', inputs=('lhs', 'rhs'))
+def _ldexp(lhs, rhs):
+    return lhs * torch.pow(torch.full_like(lhs, 2.0), rhs.to(lhs.dtype))
+
+
+@register('_npi_lcm', inputs=('lhs', 'rhs'))
+def _lcm(lhs, rhs):
+    return torch.lcm(lhs, rhs)
+
+
+@register('_npi_gcd', inputs=('lhs', 'rhs'))
+def _gcd(lhs, rhs):
+    return torch.gcd(lhs, rhs)
+
+
+@register('smooth_l1', inputs=('data',), defaults={'scalar': 1.0})
+def smooth_l1(data, scalar=1.0):
+    s2 = scalar * scalar
+    a = torch.abs(data)
+    return torch.where(a < 1.0 / s2, 0.5 * s2 * data * data, a - 0.5 / s2)
+
+
+@register('clip', '_npi_clip', inputs=('data',), defaults={'a_min': None, 'a_max': None})
+def clip(data, a_min=None, a_max=None):
+    return torch.clamp(data, min=a_min, max=a_max)
+
+
+@register('add_n', 'ElementWiseSum', '_grad_add', inputs=('*args',))
+def add_n(*args):
+    out = args[0]
+    if len(args) > 1:
+        out = torch.stack(args, 0).sum(0) if len(args) > 4 else sum(args[1:], args[0])
+    return out
+
+
+@register('where', '_npi_where', inputs=('condition', 'x', 'y'))
+def where(condition, x, y):
+    c = condition if condition.dtype == torch.bool else condition != 0
+    if not isinstance(x, torch.Tensor):
+        x = torch.as_tensor(x, device=c.device, dtype=y.dtype if isinstance(y, torch.Tensor) else torch.float32)
+    if not isinstance(y, torch.Tensor):
+        y = torch.as_tensor(y, device=c.device, dtype=x.dtype)
+    x, y = _promote(x, y)
+    if c.dim() == 1 and x.dim() > 1 and c.shape[0] == x.shape[0]:
+        c = c.reshape((-1,) + (1,) * (x.dim() - 1))
+    return torch.where(c, x, y)
+
+
+@register('Cast', 'cast', '_npi_cast', 'amp_cast', inputs=('data',), defaults={'dtype': 'float32'})
+def cast(data, dtype='float32'):
+    return data.to(to_torch_dtype(dtype))
+
+
+@register('amp_multicast', inputs=('*data',), nout=lambda a: a.get('num_outputs', 1),
+          defaults={'num_outputs': 1, 'cast_narrow': False})
+def amp_multicast(*data, num_outputs=None, cast_narrow=False):
+    fl = [d.dtype for d in data if d.dtype.is_floating_point]
+    if not fl:
+        return tuple(data)
+    order = [torch.float16, torch.bfloat16, torch.float32, torch.float64]
+    tgt = (min if cast_narrow else max)(fl, key=order.index)
+    return tuple(d.to(tgt) if d.dtype.is_floating_point else d for d in data)
+
+
+# ------------------------------------------------------------------------------------------
+# reductions
+# ------------------------------------------------------------------------------------------
+def _reg_reduce(name, fn, aliases=()):
+    def op(data, axis=None, keepdims=False, exclude=False, dtype=None, **_):
+        ax = _axes(axis, data.dim(), exclude)
+        if data.dim() == 0:
+            return data.clone()
+        r = fn(data, ax, keepdims)
+        if dtype is not None:
+            r = r.to(to_torch_dtype(dtype))
+        return r
+    op.__name__ = name
+    register(name, *aliases, inputs=('data',), defaults={'axis': None, 'keepdims': False, 'exclude': False})(op)
+
+
+def _acc(x):
+    """Reduce half-precision inputs in fp32 (``MXNET_SAFE_ACCUMULATION``)."""
+    return x.float() if x.dtype in (torch.float16, torch.bfloat16) else x
+
+
+def _sum(x, ax, kd):
+    if not ax:
+        return x.clone()
+    if x.dtype == torch.bool:
+        x = x.long()
+    return _acc(x).sum(ax, kd).to(x.dtype)
+
+
+def _mean(x, ax, kd):
+    if not ax:
+        return x.clone()
+    if not x.dtype.is_floating_point:
+        x = x.float()
+    return _acc(x).mean(ax, kd).to(x.dtype)
+
+
+def _prod(x, ax, kd):
+    r = x
+    for a in sorted(ax, reverse=True):
+        r = r.prod(a, keepdim=kd)
+    return r
+
+
+def _amax(x, ax, kd): return torch.amax(x, ax, kd) if ax else x.clone()
+def _amin(x, ax, kd): return torch.amin(x, ax, kd) if ax else x.clone()
+
+
+_reg_reduce('sum', _sum, ('sum_axis', '_npi_sum'))
+_reg_reduce('mean', _mean, ('_npi_mean',))
+_reg_reduce('prod', _prod, ('_npi_prod',))
+_reg_reduce('max', _amax, ('max_axis', '_npi_max', '_npi_amax'))
+_reg_reduce('min', _amin, ('min_axis', '_npi_min', '_npi_amin'))
+_reg_reduce('nansum', lambda x, ax, kd: torch.nan_to_num(x, nan=0.0).sum(ax, kd), ('_npi_nansum',))
+_reg_reduce('nanprod', lambda x, ax, kd: _prod(torch.nan_to_num(x, nan=1.0), ax, kd), ('_npi_nanprod',))
+_reg_reduce('_npi_all', lambda x, ax, kd: torch.all(x != 0, dim=ax, keepdim=kd) if ax else (x != 0))
+_reg_reduce('_npi_any', lambda x, ax, kd: torch.any(x != 0, dim=ax, keepdim=kd) if ax else (x != 0))
+
+
+@register('_npi_std', inputs=('data',), defaults={'axis': None, 'ddof': 0, 'keepdims': False})
+def _std(data, axis=None, ddof=0, keepdims=False, dtype=None):
+    return torch.std(data, dim=_axes(axis, data.dim()), correction=ddof, keepdim=keepdims)
+
+
+@register('_npi_var', inputs=('data',), defaults={'axis': None, 'ddof': 0, 'keepdims': False})
+def _var(data, axis=None, ddof=0, keepdims=False, dtype=None):
+    return torch.var(data, dim=_axes(axis, data.dim()), correction=ddof, keepdim=keepdims)
+
+
+@register('moments', inputs=('data',), nout=2, defaults={'axes': None, 'keepdims': False})
+def moments(data, axes=None, keepdims=False):
+    ax = _axes(axes, data.dim())
+    mean = data.mean(ax, keepdims)
+    var = data.var(ax, unbiased=False, keepdim=keepdims)
+    return mean, var
+
+
+@register('norm', inputs=('data',), defaults={'ord': 2, 'axis': None, 'keepdims': False})
+def norm(data, ord=2, axis=None, keepdims=False, out_dtype=None):
+    ax = _axes(axis, data.dim())
+    x = _acc(data)
+    if ord == 1:
+        r = x.abs().sum(ax, keepdims)
+    else:
+        r = torch.sqrt((x * x).sum(ax, keepdims))
+    return r.to(data.dtype if out_dtype is None else to_torch_dtype(out_dtype))
+
+
+def _arg_reduce(fn):
+    def op(data, axis=None, keepdims=False):
+        if axis is None:
+            r = fn(data.reshape(-1), 0)
+            if keepdims:
+                r = r.reshape((1,) * data.dim())
+        else:
+            r = fn(data, axis, keepdims)
+        return r
+    return op
+
+
+register('argmax', inputs=('data',), defaults={'axis': None, 'keepdims': False})(
+    lambda data, axis=None, keepdims=False: _arg_reduce(torch.argmax)(data, axis, keepdims).to(torch.float32))
+register('argmin', inputs=('data',), defaults={'axis': None, 'keepdims': False})(
+    lambda data, axis=None, keepdims=False: _arg_reduce(torch.argmin)(data, axis, keepdims).to(torch.float32))
+register('_npi_argmax', inputs=('data',), defaults={'axis': None, 'keepdims': False})(_arg_reduce(torch.argmax))
+register('_npi_argmin', inputs=('data',), defaults={'axis': None, 'keepdims': False})(_arg_reduce(torch.argmin))
+
+
+@register('argmax_channel', inputs=('data',))
+def argmax_channel(data):
+    return torch.argmax(data, -1).to(data.dtype)
+
+
+@register('_npi_cumsum', 'cumsum', inputs=('data',), defaults={'axis': None, 'dtype': None})
+def cumsum(data, axis=None, dtype=None):
+    if axis is None:
+        data, axis = data.reshape(-1), 0
+    return torch.cumsum(data, axis, dtype=to_torch_dtype(dtype))
+
+
+@register('_npi_cumprod', inputs=('data',), defaults={'axis': None, 'dtype': None})
+def cumprod(data, axis=None, dtype=None):
+    if axis is None:
+        data, axis = data.reshape(-1), 0
+    return torch.cumprod(data, axis, dtype=to_torch_dtype(dtype))
+
+
+@register('square_sum', '_square_sum', inputs=('data',), defaults={'axis': None, 'keepdims': False})
+def square_sum(data, axis=None, keepdims=False):
+    return (data * data).sum(_axes(axis, data.dim()), keepdims)
+
+
+@register('L2Normalization', inputs=('data',), defaults={'eps': 1e-10, 'mode': 'instance'})
+def l2_normalization(data, eps=1e-10, mode='instance'):
+    if mode == 'instance':
+        ax = tuple(range(1, data.dim()))
+    elif mode == 'channel':
+        ax = (1,)
+    else:
+        ax = tuple(range(2, data.dim()))
+    return data / torch.sqrt((data * data).sum(ax, True) + eps)
+
+
+# ------------------------------------------------------------------------------------------
+# shape manipulation
+# ------------------------------------------------------------------------------------------
+@register('Reshape', 'reshape', inputs=('data',), defaults={'shape': (), 'reverse': False})
+def reshape(data, shape=(), reverse=False, target_shape=None, keep_highest=False):
+    return data.reshape(legacy_reshape_shape(data.shape, shape, reverse))
+
+
+@register('_npi_reshape', '_np_reshape', '_npx_reshape', inputs=('a',), defaults={'newshape': (), 'order': 'C'})
+def np_reshape(a, newshape=(), order='C', reverse=False):
+    if isinstance(newshape, int):
+        newshape = (newshape,)
+    if any(s in (-2, -3, -4, -5, -6) for s in newshape):
+        return a.reshape(_npx_reshape_shape(a.shape, newshape, reverse))
+    return a.reshape(tuple(newshape))
+
+
+def _npx_reshape_shape(src, target, reverse=False):
+    """``npx.reshape`` codes: -2 copy dim, -3 skip (dim must be 1), -4 copy rest, -5 merge two, -6 split."""
+    src, target = list(src), list(target)
+    if reverse:
+        src, target = src[::-1], target[::-1]
+    out, si, i = [], 0, 0
+    while i < len(target):
+        t = target[i]
+        if t == -2:
+            out.append(src[si]); si += 1
+        elif t == -3:
+            si += 1
+        elif t == -4:
+            out.extend(src[si:]); si = len(src)
+        elif t == -5:
+            out.append(src[si] * src[si + 1]); si += 2
+        elif t == -6:
+            a, b = target[i + 1], target[i + 2]
+            d = src[si]; si += 1
+            a = d // b if a == -1 else a
+            b = d // a if b == -1 else b
+            out.extend([a, b]); i += 2
+        else:
+            out.append(t)
+            if t != -1:
+                si += 1
+            else:
+                si += 1
+        i += 1
+    if reverse:
+        out = out[::-1]
+    return tuple(out)
+
+
+@register('reshape_like', inputs=('lhs', 'rhs'))
+def reshape_like(lhs, rhs, lhs_begin=None, lhs_end=None, rhs_begin=None, rhs_end=None):
+    if lhs_begin is None and rhs_begin is None and lhs_end is None and rhs_end is None:
+        return lhs.reshape(rhs.shape)
+    lb = 0 if lhs_begin is None else lhs_begin % (lhs.dim() + 1)
+    le = lhs.dim() if lhs_end is None else lhs_end % (lhs.dim() + 1)
+    rb = 0 if rhs_begin is None else rhs_begin % (rhs.dim() + 1)
+    re_ = rhs.dim() if rhs_end is None else rhs_end % (rhs.dim() + 1)
+    return lhs.reshape(tuple(lhs.shape[:lb]) + tuple(rhs.shape[rb:re_]) + tuple(lhs.shape[le:]))
+
+
+@register('Flatten', 'flatten', inputs=('data',))
+def flatten(data):
+    return data.reshape(data.shape[0], -1) if data.dim() > 1 else data.reshape(-1, 1) if data.dim() == 1 else data
+
+
+@register('transpose', '_npi_transpose', inputs=('data',), defaults={'axes': None})
+def transpose(data, axes=None):
+    if axes is None or len(axes) == 0:
+        axes = tuple(range(data.dim()))[::-1]
+    return data.permute(tuple(axes))
+
+
+@register('expand_dims', '_npi_expand_dims', inputs=('data',), defaults={'axis': 0})
+def expand_dims(data, axis=0):
+    if isinstance(axis, (tuple, list)):
+        for a in sorted(axis):
+            data = data.unsqueeze(a)
+        return data
+    return data.unsqueeze(axis)
+
+
+@register('squeeze', '_npi_squeeze', inputs=('data',), defaults={'axis': None})
+def squeeze(data, axis=None):
+    if axis is None:
+        return data.squeeze()
+    if isinstance(axis, int):
+        axis = (axis,)
+    for a in axis:
+        if data.shape[a] != 1:
+            raise MXNetError('cannot select an axis to squeeze out which has size not equal to one')
+    return data.squeeze(tuple(axis))
+
+
+@register('SwapAxis', 'swapaxes', '_npi_swapaxes', inputs=('data',), defaults={'dim1': 0, 'dim2': 0})
+def swapaxes(data, dim1=0, dim2=0):
+    return data.transpose(dim1, dim2)
+
+
+@register('_npi_moveaxis', inputs=('a',), defaults={'source': 0, 'destination': 0})
+def np_moveaxis(a, source=0, destination=0):
+    return torch.movedim(a, source, destination)
+
+
+@register('_npi_rollaxis', inputs=('data',), defaults={'axis': 0, 'start': 0})
+def np_rollaxis(data, axis=0, start=0):
+    n = data.dim()
+    axis %= n
+    if start < 0:
+        start += n
+    if axis < start:
+        start -= 1
+    axes = list(range(n))
+    axes.remove(axis)
+    axes.insert(start, axis)
+    return data.permute(axes)
+
+
+@register('broadcast_to', '_npi_broadcast_to', inputs=('data',), defaults={'shape': ()})
+def broadcast_to(data, shape=()):
+    shape = tuple(shape)
+    if len(shape) == data.dim():
+        shape = tuple(s if s != 0 else d for s, d in zip(shape, data.shape))
+    return data.expand(shape)
+
+
+@register('broadcast_like', inputs=('lhs', 'rhs'), defaults={'lhs_axes': None, 'rhs_axes': None})
+def broadcast_like(lhs, rhs, lhs_axes=None, rhs_axes=None):
+    if lhs_axes is None:
+        return lhs.expand(rhs.shape)
+    shape = list(lhs.shape)
+    for la, ra in zip(lhs_axes, rhs_axes):
+        shape[la] = rhs.shape[ra]
+    return lhs.expand(shape)
+
+
+@register('broadcast_axis', 'broadcast_axes', inputs=('data',), defaults={'axis': (), 'size': ()})
+def broadcast_axis(data, axis=(), size=()):
+    if isinstance(axis, int):
+        axis, size = (axis,), (size,)
+    shape = list(data.shape)
+    for a, s in zip(axis, size):
+        shape[a] = s
+    return data.expand(shape)
+
+
+@register('Concat', 'concat', '_npi_concatenate', inputs=('*data',), defaults={'dim': 1, 'num_args': 1})
+def concat(*data, dim=1, axis=None, num_args=None):
+    if axis is not None:
+        dim = axis
+    if dim is None:
+        return torch.cat([d.reshape(-1) for d in data], 0)
+    dt = data[0].dtype
+    if any(d.dtype != dt for d in data):
+        for d in data[1:]:
+            dt = torch.promote_types(dt, d.dtype)
+        data = [d.to(dt) for d in data]
+    return torch.cat(data, dim)
+
+
+@register('_rnn_param_concat', inputs=('*data',), defaults={'dim': 0, 'num_args': 1})
+def rnn_param_concat(*data, dim=0, num_args=None):
+    return torch.cat([d.reshape(-1) for d in data], 0)
+
+
+@register('stack', '_npi_stack', inputs=('*data',), defaults={'axis': 0, 'num_args': 1})
+def stack(*data, axis=0, num_args=None):
+    return torch.stack(data, axis)
+
+
+for _nm, _fn in (('_npi_vstack', torch.vstack), ('_npi_hstack', torch.hstack), ('_npi_dstack', torch.dstack),
+                 ('_npi_column_stack', torch.column_stack)):
+    register(_nm, inputs=('*data',))(lambda *data, _f=_fn, num_args=None: _f(data))
+
+
+def _split_nout(attrs):
+    if 'num_outputs' in attrs:
+        return int(attrs['num_outputs'])
+    ios = attrs.get('indices_or_sections', attrs.get('indices', 1))
+    return ios if isinstance(ios, int) else len(ios) + 1
+
+
+@register('SliceChannel', 'split', inputs=('data',), nout=_split_nout,
+          defaults={'num_outputs': 1, 'axis': 1, 'squeeze_axis': False})
+def slice_channel(data, num_outputs=1, axis=1, squeeze_axis=False):
+    parts = torch.chunk(data, num_outputs, axis)
+    if squeeze_axis:
+        parts = [p.squeeze(axis) for p in parts]
+    return tuple(parts)
+
+
+@register('_split_v2', '_npi_split', inputs=('data',), nout=_split_nout,
+          defaults={'indices_or_sections': 1, 'axis': 0, 'squeeze_axis': False})
+def split_v2(data, indices_or_sections=1, axis=0, squeeze_axis=False, sections=0, indices=None):
+    ios = indices_or_sections
+    if isinstance(ios, int):
+        if data.shape[axis] % ios:
+            raise MXNetError('array split does not result in an equal division')
+        parts = torch.chunk(data, ios, axis)
+    else:
+        parts = torch.tensor_split(data, list(ios), axis)
+    if squeeze_axis:
+        parts = [p.squeeze(axis) for p in parts]
+    return tuple(parts)
+
+
+@register('_npi_array_split', inputs=('data',), nout=_split_nout, defaults={'indices_or_sections': 1, 'axis': 0})
+def array_split(data, indices_or_sections=1, axis=0):
+    ios = indices_or_sections
+    return tuple(torch.tensor_split(data, ios if isinstance(ios, int) else list(ios), axis))
+
+
+@register('slice', 'crop', inputs=('data',), defaults={'begin': (), 'end': (), 'step': None})
+def slice_op(data, begin=(), end=(), step=None):
+    if isinstance(begin, int):
+        begin, end = (begin,), (end,)
+    idx = []
+    step = step or (None,) * len(begin)
+    for b, e, s in zip(begin, end, list(step) + [None] * (len(begin) - len(step))):
+        idx.append(slice(b, e, s))
+    # negative steps are not supported by the tensor library's slicing: flip instead
+    out = data
+    for ax, sl in enumerate(idx):
+        if sl.step is not None and sl.step < 0:
+            n = data.shape[ax]
+            rng = range(n)[sl]
+            out = out.index_select(ax, torch.as_tensor(list(rng), device=data.device, dtype=torch.long))
+        else:
+            out = out[(slice(None),) * ax + (sl,)]
+    return out
+
+
+@register('slice_axis', inputs=('data',), defaults={'axis': 0, 'begin': 0, 'end': None})
+def slice_axis(data, axis=0, begin=0, end=None):
+    return data[(slice(None),) * (axis % data.dim()) + (slice(begin, end),)]
+
+
+@register('slice_like', inputs=('data', 'shape_like'), defaults={'axes': None})
+def slice_like(data, shape_like, axes=None):
+    axes = range(data.dim()) if not axes else [a % data.dim() for a in axes]
+    idx = [slice(None)] * data.dim()
+    for a in axes:
+        idx[a] = slice(0, shape_like.shape[a])
+    return data[tuple(idx)]
+
+
+@register('_slice_assign', '_crop_assign', inputs=('lhs', 'rhs'), defaults={'begin': (), 'end': (), 'step': None})
+def slice_assign(lhs, rhs, begin=(), end=(), step=None):
+    out = lhs.clone()
+    step = step or (None,) * len(begin)
+    out[tuple(slice(b, e, s) for b, e, s in zip(begin, end, step))] = rhs
+    return out
+
+
+@register('_slice_assign_scalar', '_crop_assign_scalar', inputs=('data',),
+          defaults={'scalar': 0.0, 'begin': (), 'end': (), 'step': None})
+def slice_assign_scalar(data, scalar=0.0, begin=(), end=(), step=None):
+    out = data.clone()
+    step = step or (None,) * len(begin)
+    out[tuple(slice(b, e, s) for b, e, s in zip(begin, end, step))] = scalar
+    return out
+
+
+@register('_index', inputs=('data',))
+def _index(data, key=None):
+    return data[key]
+
+
+@register('tile', '_npi_tile', inputs=('data',), defaults={'reps': ()})
+def tile(data, reps=()):
+    if isinstance(reps, int):
+        reps = (reps,)
+    return torch.tile(data, tuple(reps))
+
+
+@register('repeat', '_npi_repeat', '_npi_repeats', inputs=('data',), defaults={'repeats': 1, 'axis': None})
+def repeat(data, repeats=1, axis=None):
+    if axis is None:
+        return data.reshape(-1).repeat_interleave(repeats)
+    return data.repeat_interleave(repeats, axis)
+
+
+@register('reverse', 'flip', '_npi_flip', inputs=('data',), defaults={'axis': 0})
+def reverse(data, axis=0):
+    if axis is None:
+        axis = tuple(range(data.dim()))
+    if isinstance(axis, int):
+        axis = (axis,)
+    return torch.flip(data, tuple(axis))
+
+
+@register('_npi_roll', inputs=('data',), defaults={'shift': 0, 'axis': None})
+def roll(data, shift=0, axis=None):
+    return torch.roll(data, shift, axis)
+
+
+@register('_npi_rot90', inputs=('data',), defaults={'k': 1, 'axes': (0, 1)})
+def rot90(data, k=1, axes=(0, 1)):
+    return torch.rot90(data, k, tuple(axes))
+
+
+@register('depth_to_space', inputs=('data',), defaults={'block_size': 1})
+def depth_to_space(data, block_size=1):
+    n, c, h, w = data.shape
+    b = block_size
+    x = data.reshape(n, b, b, c // (b * b), h, w).permute(0, 3, 4, 1, 5, 2)
+    return x.reshape(n, c // (b * b), h * b, w * b)
+
+
+@register('space_to_depth', inputs=('data',), defaults={'block_size': 1})
+def space_to_depth(data, block_size=1):
+    n, c, h, w = data.shape
+    b = block_size
+    x = data.reshape(n, c, h // b, b, w // b, b).permute(0, 3, 5, 1, 2, 4)
+    return x.reshape(n, c * b * b, h // b, w // b)
+
+
+@register('zeros_like', '_npi_zeros_like', inputs=('data',))
+def zeros_like(data, dtype=None):
+    return torch.zeros_like(data, dtype=to_torch_dtype(dtype))
+
+
+@register('ones_like', '_npi_ones_like', inputs=('data',))
+def ones_like(data, dtype=None):
+    return torch.ones_like(data, dtype=to_torch_dtype(dtype))
+
+
+@register('_npi_full_like', 'full_like', inputs=('a',), defaults={'fill_value': 0.0, 'dtype': None})
+def full_like(a, fill_value=0.0, dtype=None):
+    return torch.full_like(a, fill_value, dtype=to_torch_dtype(dtype))
+
+
+@register('shape_array', inputs=('data',))
+def shape_array(data):
+    return torch.tensor(list(data.shape), dtype=torch.int64, device=data.device)
+
+
+@register('size_array', inputs=('data',))
+def size_array(data):
+    return torch.tensor([data.numel()], dtype=torch.int64, device=data.device)
+
+
+@register('diag', '_npi_diag', inputs=('data',), defaults={'k': 0, 'axis1': 0, 'axis2': 1})
+def diag(data, k=0, axis1=0, axis2=1):
+    if data.dim() == 1:
+        return torch.diag(data, k)
+    return torch.diagonal(data, k, axis1, axis2)
+
+
+@register('_npi_diagonal', inputs=('data',), defaults={'offset': 0, 'axis1': 0, 'axis2': 1})
+def diagonal(data, offset=0, axis1=0, axis2=1):
+    return torch.diagonal(data, offset, axis1, axis2)
+
+
+@register('_npi_tril', 'tril', inputs=('data',), defaults={'k': 0})
+def tril(data, k=0):
+    return torch.tril(data, k)
+
+
+@register('_npi_triu', 'triu', inputs=('data',), defaults={'k': 0})
+def triu(data, k=0):
+    return torch.triu(data, k)
+
+
+@register('_npi_trace', inputs=('data',), defaults={'offset': 0, 'axis1': 0, 'axis2': 1})
+def trace(data, offset=0, axis1=0, axis2=1):
+    return torch.diagonal(data, offset, axis1, axis2).sum(-1)
+
+
+@register('Pad', 'pad', inputs=('data',), defaults={'mode': 'constant', 'pad_width': (), 'constant_value': 0.0})
+def pad(data, mode='constant', pad_width=(), constant_value=0.0):
+    pw = list(pad_width)
+    pairs = [(pw[2 * i], pw[2 * i + 1]) for i in range(len(pw) // 2)]
+    flat = []
+    for lo, hi in reversed(pairs):
+        flat.extend([lo, hi])
+    while len(flat) >= 2 and flat[-1] == 0 and flat[-2] == 0 and len(flat) // 2 > data.dim() - 2 and mode != 'constant':
+        flat = flat[:-2]
+    tmode = {'constant': 'constant', 'edge': 'replicate', 'reflect': 'reflect'}[mode]
+    if tmode == 'constant':
+        return F.pad(data, flat, 'constant', constant_value)
+    return F.pad(data, flat, tmode)
+
+
+@register('_npi_pad', inputs=('data',), defaults={'pad_width': (), 'mode': 'constant', 'constant_values': 0.0})
+def np_pad(data, pad_width=(), mode='constant', constant_values=0.0, reflect_type='even'):
+    if isinstance(pad_width, int):
+        pad_width = ((pad_width, pad_width),) * data.dim()
+    pairs = [tuple(p) if isinstance(p, (tuple, list)) else (p, p) for p in pad_width]
+    if len(pairs) == 1 and data.dim() > 1:
+        pairs = pairs * data.dim()
+    if mode == 'constant':
+        flat = []
+        for lo, hi in reversed(pairs):
+            flat.extend([lo, hi])
+        return F.pad(data, flat, 'constant', constant_values)
+    a = _np.pad(data.detach().cpu().numpy(), pairs, mode=mode)
+    return torch.from_numpy(a).to(data.device)
+
+
+# ------------------------------------------------------------------------------------------
+# indexing
+# ------------------------------------------------------------------------------------------
+def _wrap_index(idx, n, mode):
+    idx = idx.long()
+    if mode == 'wrap':
+        return torch.remainder(idx, n)
+    return torch.clamp(idx, 0, n - 1)
+
+
+@register('take', '_npi_take', inputs=('a', 'indices'), defaults={'axis': 0, 'mode': 'clip'})
+def take(a, indices, axis=0, mode='clip'):
+    if axis is None:
+        a, axis = a.reshape(-1), 0
+    axis = axis % a.dim()
+    idx = _wrap_index(indices, a.shape[axis], mode)
+    out = torch.index_select(a, axis, idx.reshape(-1))
+    return out.reshape(tuple(a.shape[:axis]) + tuple(idx.shape) + tuple(a.shape[axis + 1:]))
+
+
+@register('pick', '_npx_pick', inputs=('data', 'index'), defaults={'axis': -1, 'keepdims': False, 'mode': 'clip'})
+def pick(data, index, axis=-1, keepdims=False, mode='clip'):
+    axis = axis % data.dim()
+    idx = _wrap_index(index, data.shape[axis], mode)
+    if idx.dim() == data.dim() - 1:
+        idx = idx.unsqueeze(axis)
+    out = torch.gather(data, axis, idx)
+    return out if keepdims else out.squeeze(axis)
+
+
+@register('gather_nd', '_npi_gather_nd', inputs=('data', 'indices'))
+def gather_nd(data, indices):
+    idx = indices.long()
+    return data[tuple(idx[i] for i in range(idx.shape[0]))]
+
+
+@register('scatter_nd', inputs=('data', 'indices'), defaults={'shape': ()})
+def scatter_nd(data, indices, shape=()):
+    out = torch.zeros(tuple(shape), dtype=data.dtype, device=data.device)
+    idx = indices.long()
+    out[tuple(idx[i] for i in range(idx.shape[0]))] = data
+    return out
+
+
+@register('_scatter_set_nd', inputs=('lhs', 'rhs', 'indices'), defaults={'shape': ()})
+def scatter_set_nd(lhs, rhs, indices, shape=()):
+    out = lhs.clone()
+    idx = indices.long()
+    out[tuple(idx[i] for i in range(idx.shape[0]))] = rhs
+    return out
+
+
+@register('_backward_gather_nd', inputs=('data', 'indices'), defaults={'shape': ()})
+def gather_nd_backward(data, indices, shape=()):
+    out = torch.zeros(tuple(shape), dtype=data.dtype, device=data.device)
+    idx = indices.long()
+    out.index_put_(tuple(idx[i] for i in range(idx.shape[0])), data, accumulate=True)
+    return out
+
+
+@register('one_hot', '_npx_one_hot', inputs=('indices',),
+          defaults={'depth': 1, 'on_value': 1.0, 'off_value': 0.0, 'dtype': 'float32'})
+def one_hot(indices, depth=1, on_value=1.0, off_value=0.0, dtype='float32'):
+    idx = indices.long()
+    valid = (idx >= 0) & (idx < depth)
+    oh = F.one_hot(torch.where(valid, idx, torch.zeros_like(idx)), depth).bool() & valid.unsqueeze(-1)
+    td = to_torch_dtype(dtype)
+    on = torch.as_tensor(on_value, dtype=td, device=idx.device)
+    off = torch.as_tensor(off_value, dtype=td, device=idx.device)
+    return torch.where(oh, on, off)
+
+
+@register('Embedding', '_npx_embedding', inputs=('data', 'weight'),
+          defaults={'input_dim': 0, 'output_dim': 0, 'dtype': 'float32', 'sparse_grad': False})
+def embedding(data, weight, input_dim=None, output_dim=None, dtype=None, sparse_grad=False):
+    idx = torch.clamp(data.long(), 0, weight.shape[0] - 1)
+    return F.embedding(idx, weight)
+
+
+@register('batch_take', inputs=('a', 'indices'))
+def batch_take(a, indices):
+    return torch.gather(a, 1, indices.long().unsqueeze(1)).squeeze(1)
+
+
+@register('boolean_mask', '_contrib_boolean_mask', '_npi_boolean_mask', inputs=('data', 'index'), defaults={'axis': 0})
+def boolean_mask(data, index, axis=0):
+    m = index != 0 if index.dtype != torch.bool else index
+    sel = torch.nonzero(m.reshape(-1)).reshape(-1)
+    return torch.index_select(data, axis, sel)
+
+
+@register('_npi_nonzero', inputs=('data',))
+def np_nonzero(data):
+    return torch.nonzero(data)
+
+
+@register('sort', '_npi_sort', inputs=('data',), defaults={'axis': -1, 'is_ascend': True})
+def sort(data, axis=-1, is_ascend=True):
+    if axis is None:
+        data, axis = data.reshape(-1), 0
+    return torch.sort(data, axis, descending=not is_ascend, stable=True)[0]
+
+
+@register('argsort', '_npi_argsort', inputs=('data',), defaults={'axis': -1, 'is_ascend': True, 'dtype': 'float32'})
+def argsort(data, axis=-1, is_ascend=True, dtype='float32'):
+    if axis is None:
+        data, axis = data.reshape(-1), 0
+    return torch.sort(data, axis, descending=not is_ascend, stable=True)[1].to(to_torch_dtype(dtype))
+
+
+def _topk_nout(attrs):
+    return 2 if attrs.get('ret_typ', 'indices') == 'both' else 1
+
+
+@register('topk', '_npx_topk', inputs=('data',), nout=_topk_nout,
+          defaults={'axis': -1, 'k': 1, 'ret_typ': 'indices', 'is_ascend': False, 'dtype': 'float32'})
+def topk(data, axis=-1, k=1, ret_typ='indices', is_ascend=False, dtype='float32'):
+    if axis is None:
+        data, axis = data.reshape(-1), 0
+    if k <= 0:
+        k = data.shape[axis]
+    vals, idx = torch.topk(data, k, dim=axis, largest=not is_ascend, sorted=True)
+    td = to_torch_dtype(dtype)
+    if ret_typ == 'value':
+        return vals
+    if ret_typ == 'indices':
+        return idx.to(td)
+    if ret_typ == 'both':
+        return vals, idx.to(td)
+    mask = torch.zeros_like(data)
+    return mask.scatter_(axis, idx, 1.0)
+
+
+@register('_npi_unique', inputs=('data',), nout=lambda a: 1 + bool(a.get('return_index')) +
+          bool(a.get('return_inverse')) + bool(a.get('return_counts')),
+          defaults={'return_index': False, 'return_inverse': False, 'return_counts': False, 'axis': None})
+def np_unique(data, return_index=False, return_inverse=False, return_counts=False, axis=None):
+    res = _np.unique(data.detach().cpu().numpy(), return_index, return_inverse, return_counts, axis)
+    if not isinstance(res, tuple):
+        return torch.from_numpy(res).to(data.device)
+    return tuple(torch.from_numpy(_np.ascontiguousarray(r)).to(data.device) for r in res)
+
+
+@register('histogram', '_histogram', '_npi_histogram', inputs=('data', 'bins'), nout=2,
+          defaults={'bin_cnt': None, 'range': None})
+def histogram(data, bins=None, bin_cnt=None, range=None):
+    x = data.detach().reshape(-1).double().cpu()
+    if bins is not None:
+        edges = bins.detach().double().cpu()
+        cnt, edges = torch.histogram(x, edges)
+    else:
+        cnt, edges = torch.histogram(x, int(bin_cnt), range=tuple(float(r) for r in range))
+    return cnt.to(torch.int64).to(data.device), edges.to(data.dtype if data.dtype.is_floating_point else torch.float32).to(data.device)
+
+
+@register('_ravel_multi_index', 'ravel_multi_index', inputs=('data',), defaults={'shape': ()})
+def ravel_multi_index(data, shape=()):
+    strides = []
+    acc = 1
+    for s in reversed(shape):
+        strides.append(acc)
+        acc *= s
+    st = torch.tensor(strides[::-1], dtype=data.dtype, device=data.device).reshape(-1, *([1] * (data.dim() - 1)))
+    return (data * st).sum(0)
+
+
+@register('_unravel_index', 'unravel_index', inputs=('data',), defaults={'shape': ()})
+def unravel_index(data, shape=()):
+    outs = []
+    rem = data.long()
+    for s in reversed(shape):
+        outs.append(rem % s)
+        rem = rem // s
+    return torch.stack(outs[::-1], 0).to(data.dtype)
+
+
+# ------------------------------------------------------------------------------------------
+# sequence ops (src/operator/sequence_mask.cc, sequence_last.cc, sequence_reverse.cc)
+# ------------------------------------------------------------------------------------------
+@register('SequenceMask', '_npx_sequence_mask', inputs=('data', 'sequence_length'),
+          defaults={'use_sequence_length': False, 'value': 0.0, 'axis': 0})
+def sequence_mask(data, sequence_length=None, use_sequence_length=False, value=0.0, axis=0):
+    if not use_sequence_length or sequence_length is None:
+        return data
+    T = data.shape[axis]
+    steps = torch.arange(T, device=data.device)
+    if axis == 0:
+        mask = steps[:, None] < sequence_length.to(steps.dtype)[None, :]
+    else:
+        mask = steps[None, :] < sequence_length.to(steps.dtype)[:, None]
+    mask = mask.reshape(mask.shape + (1,) * (data.dim() - 2))
+    return torch.where(mask, data, torch.as_tensor(value, dtype=data.dtype, device=data.device))
+
+
+@register('SequenceLast', inputs=('data', 'sequence_length'), defaults={'use_sequence_length': False, 'axis': 0})
+def sequence_last(data, sequence_length=None, use_sequence_length=False, axis=0):
+    if not use_sequence_length or sequence_length is None:
+        return data.select(axis, data.shape[axis] - 1)
+    idx = (sequence_length.long() - 1).clamp(min=0)
+    d = data if axis == 0 else data.transpose(0, 1)
+    return d[idx, torch.arange(d.shape[1], device=data.device)]
+
+
+@register('SequenceReverse', inputs=('data', 'sequence_length'), defaults={'use_sequence_length': False, 'axis': 0})
+def sequence_reverse(data, sequence_length=None, use_sequence_length=False, axis=0):
+    if not use_sequence_length or sequence_length is None:
+        return torch.flip(data, (0,))
+    T, N = data.shape[0], data.shape[1]
+    t = torch.arange(T, device=data.device)[:, None]
+    L = sequence_length.long()[None, :]
+    src = torch.where(t < L, L - 1 - t, t)
+    return data[src, torch.arange(N, device=data.device)[None, :]]
+
+
+# ------------------------------------------------------------------------------------------
+# linear algebra (cuBLAS / cuSOLVER call sites of src/operator/linalg_impl.h)
+# ------------------------------------------------------------------------------------------
+@register('dot', inputs=('lhs', 'rhs'), defaults={'transpose_a': False, 'transpose_b': False})
+def dot(lhs, rhs, transpose_a=False, transpose_b=False, forward_stype=None):
+    if lhs.dim() == 1 and rhs.dim() == 1:
+        return (lhs * rhs).sum()
+    a = lhs.reshape(lhs.shape[0], -1).t() if transpose_a else lhs
+    b = rhs.reshape(rhs.shape[0], -1).t() if transpose_b else rhs
+    if transpose_a:
+        a_lead = lhs.shape[1:]
+        a2 = a.reshape(-1, a.shape[-1]) if a.dim() > 2 else a
+    else:
+        a_lead = lhs.shape[:-1]
+        a2 = a.reshape(-1, a.shape[-1])
+    if transpose_b:
+        b_tail = rhs.shape[:-1] if rhs.dim() > 1 else ()
+        b2 = b
+    else:
+        b_tail = rhs.shape[1:]
+        b2 = b.reshape(b.shape[0], -1)
+    from . import gemm as _gemm
+    return _gemm.matmul(a2, b2).reshape(tuple(a_lead) + tuple(b_tail))
+
+
+@register('batch_dot', '_npx_batch_dot', inputs=('lhs', 'rhs'), defaults={'transpose_a': False, 'transpose_b': False})
+def batch_dot(lhs, rhs, transpose_a=False, transpose_b=False, forward_stype=None):
+    a = lhs.transpose(-1, -2) if transpose_a else lhs
+    b = rhs.transpose(-1, -2) if transpose_b else rhs
+    from . import gemm as _gemm
+    return _gemm.matmul(a, b)
+
+
+@register('_npi_matmul', inputs=('a', 'b'))
+def np_matmul(a, b):
+    a, b = _promote(a, b)
+    from . import gemm as _gemm
+    return _gemm.matmul(a, b)
+
+
+@register('_npi_dot', '_np_dot', inputs=('a', 'b'))
+def np_dot(a, b):
+    a, b = _promote(a, b)
+    if a.dim() == 0 or b.dim() == 0:
+        return a * b
+    if b.dim() == 1:
+        return torch.matmul(a, b)
+    if a.dim() <= 2 and b.dim() <= 2:
+        return torch.matmul(a, b)
+    return torch.tensordot(a, b, dims=([-1], [-2]))
+
+
+@register('_npi_tensordot', inputs=('a', 'b'), defaults={'a_axes_summed': (), 'b_axes_summed': ()})
+def np_tensordot(a, b, a_axes_summed=(), b_axes_summed=()):
+    return torch.tensordot(a, b, dims=(list(a_axes_summed), list(b_axes_summed)))
+
+
+@register('_npi_tensordot_int_axes', inputs=('a', 'b'), defaults={'axes': 2})
+def np_tensordot_int(a, b, axes=2):
+    return torch.tensordot(a, b, dims=axes)
+
+
+@register('_npi_einsum', inputs=('*data',), defaults={'subscripts': '', 'optimize': 0})
+def np_einsum(*data, subscripts='', optimize=0, num_args=None):
+    return torch.einsum(subscripts, *data)
+
+
+@register('_npi_kron', inputs=('a', 'b'))
+def np_kron(a, b):
+    return torch.kron(a, b)
+
+
+@register('_npi_outer', inputs=('a', 'b'))
+def np_outer(a, b):
+    return torch.outer(a.reshape(-1), b.reshape(-1))
+
+
+@register('_npi_inner', inputs=('a', 'b'))
+def np_inner(a, b):
+    return torch.inner(a, b)
+
+
+@register('_npi_vdot', inputs=('a', 'b'))
+def np_vdot(a, b):
+    return (a.reshape(-1) * b.reshape(-1)).sum()
+
+
+@register('_npi_cross', inputs=('a', 'b'), defaults={'axisa': -1, 'axisb': -1, 'axisc': -1})
+def np_cross(a, b, axisa=-1, axisb=-1, axisc=-1):
+    return torch.movedim(torch.linalg.cross(torch.movedim(a, axisa, -1), torch.movedim(b, axisb, -1)), -1, axisc)
+
+
+@register('khatri_rao', inputs=('*args',))
+def khatri_rao(*args, num_args=None):
+    out = args[0]
+    for m in args[1:]:
+        out = (out[:, None, :] * m[None, :, :]).reshape(-1, out.shape[1])
+    return out
+
+
+def _t(x, flag):
+    return x.transpose(-1, -2) if flag else x
+
+
+@register('_linalg_gemm', 'linalg_gemm', inputs=('A', 'B', 'C'),
+          defaults={'transpose_a': False, 'transpose_b': False, 'alpha': 1.0, 'beta': 1.0, 'axis': -2})
+def linalg_gemm(A, B, C, transpose_a=False, transpose_b=False, alpha=1.0, beta=1.0, axis=-2):
+    return alpha * torch.matmul(_t(A, transpose_a), _t(B, transpose_b)) + beta * C
+
+
+@register('_linalg_gemm2', 'linalg_gemm2', inputs=('A', 'B'),
+          defaults={'transpose_a': False, 'transpose_b': False, 'alpha': 1.0, 'axis': -2})
+def linalg_gemm2(A, B, transpose_a=False, transpose_b=False, alpha=1.0, axis=-2):
+    return alpha * torch.matmul(_t(A, transpose_a), _t(B, transpose_b))
+
+
+@register('_linalg_potrf', 'linalg_potrf', inputs=('A',))
+def linalg_potrf(A):
+    return torch.linalg.cholesky(A)
+
+
+@register('_linalg_potri', 'linalg_potri', inputs=('A',))
+def linalg_potri(A):
+    return torch.cholesky_inverse(A)
+
+
+@register('_linalg_trmm', 'linalg_trmm', inputs=('A', 'B'),
+          defaults={'transpose': False, 'rightside': False, 'lower': True, 'alpha': 1.0})
+def linalg_trmm(A, B, transpose=False, rightside=False, lower=True, alpha=1.0):
+    T = torch.tril(A) if lower else torch.triu(A)
+    T = _t(T, transpose)
+    return alpha * (torch.matmul(B, T) if rightside else torch.matmul(T, B))
+
+
+@register('_linalg_trsm', 'linalg_trsm', inputs=('A', 'B'),
+          defaults={'transpose': False, 'rightside': False, 'lower': True, 'alpha': 1.0})
+def linalg_trsm(A, B, transpose=False, rightside=False, lower=True, alpha=1.0):
+    upper = not lower
+    if transpose:
+        A = A.transpose(-1, -2)
+        upper = not upper
+    return torch.linalg.solve_triangular(A, alpha * B, upper=upper, left=not rightside)
+
+
+@register('_linalg_syrk', 'linalg_syrk', inputs=('A',), defaults={'transpose': False, 'alpha': 1.0})
+def linalg_syrk(A, transpose=False, alpha=1.0):
+    return alpha * (torch.matmul(A.transpose(-1, -2), A) if transpose else torch.matmul(A, A.transpose(-1, -2)))
+
+
+@register('_linalg_sumlogdiag', 'linalg_sumlogdiag', inputs=('A',))
+def linalg_sumlogdiag(A):
+    return torch.log(torch.diagonal(A, 0, -2, -1)).sum(-1)
+
+
+@register('_linalg_extractdiag', 'linalg_extractdiag', inputs=('A',), defaults={'offset': 0})
+def linalg_extractdiag(A, offset=0):
+    return torch.diagonal(A, offset, -2, -1)
+
+
+@register('_linalg_makediag', 'linalg_makediag', inputs=('A',), defaults={'offset': 0})
+def linalg_makediag(A, offset=0):
+    return torch.diag_embed(A, offset)
+
+
+@register('_linalg_extracttrian', 'linalg_extracttrian', inputs=('A',), defaults={'offset': 0, 'lower': True})
+def linalg_extracttrian(A, offset=0, lower=True):
+    n = A.shape[-1]
+    idx = torch.tril_indices(n, n, offset, device=A.device) if lower else torch.triu_indices(n, n, offset, device=A.device)
+    return A[..., idx[0], idx[1]]
+
+
+@register('_linalg_maketrian', 'linalg_maketrian', inputs=('A',), defaults={'offset': 0, 'lower': True})
+def linalg_maketrian(A, offset=0, lower=True):
+    m = A.shape[-1]
+    n = int((math.sqrt(8 * m + 1) - 1) / 2) + abs(offset)
+    idx = torch.tril_indices(n, n, offset, device=A.device) if lower else torch.triu_indices(n, n, offset, device=A.device)
+    out = torch.zeros(A.shape[:-1] + (n, n), dtype=A.dtype, device=A.device)
+    out[..., idx[0], idx[1]] = A
+    return out
+
+
+@register('_linalg_gelqf', 'linalg_gelqf', inputs=('A',), nout=2)
+def linalg_gelqf(A):
+    q, r = torch.linalg.qr(A.transpose(-1, -2), mode='reduced')
+    sign = torch.sign(torch.diagonal(r, 0, -2, -1))
+    sign = torch.where(sign == 0, torch.ones_like(sign), sign)
+    q = q * sign.unsqueeze(-2)
+    r = r * sign.unsqueeze(-1)
+    return q.transpose(-1, -2), r.transpose(-1, -2)
+
+
+@register('_linalg_syevd', 'linalg_syevd', inputs=('A',), nout=2)
+def linalg_syevd(A):
+    w, v = torch.linalg.eigh(A)
+    return v.transpose(-1, -2), w
+
+
+@register('_linalg_inverse', 'linalg_inverse', '_npi_inv', inputs=('A',))
+def linalg_inverse(A):
+    return torch.linalg.inv(A)
+
+
+@register('_linalg_det', 'linalg_det', '_npi_det', inputs=('A',))
+def linalg_det(A):
+    return torch.linalg.det(A)
+
+
+@register('_linalg_slogdet', 'linalg_slogdet', '_npi_slogdet', inputs=('A',), nout=2)
+def linalg_slogdet(A):
+    s, l = torch.linalg.slogdet(A)
+    return s, l
+
+
+@register('_npi_cholesky', inputs=('A',), defaults={'upper': False})
+def np_cholesky(A, upper=False, lower=True):
+    return torch.linalg.cholesky(A, upper=upper)
+
+
+@register('_npi_svd', inputs=('A',), nout=3)
+def np_svd(A):
+    u, s, vh = torch.linalg.svd(A, full_matrices=False)
+    return u, s, vh
+
+
+@register('_npi_qr', inputs=('A',), nout=2)
+def np_qr(A):
+    return torch.linalg.qr(A, mode='reduced')
+
+
+@register('_npi_eig', inputs=('A',), nout=2)
+def np_eig(A):
+    w, v = torch.linalg.eig(A)
+    return w.real, v.real
+
+
+@register('_npi_eigh', inputs=('A',), nout=2, defaults={'UPLO': 'L'})
+def np_eigh(A, UPLO='L', upper=False):
+    return torch.linalg.eigh(A, UPLO='U' if upper else UPLO)
+
+
+@register('_npi_eigvals', inputs=('A',))
+def np_eigvals(A):
+    return torch.linalg.eigvals(A).real
+
+
+@register('_npi_eigvalsh', inputs=('A',), defaults={'UPLO': 'L'})
+def np_eigvalsh(A, UPLO='L', upper=False):
+    return torch.linalg.eigvalsh(A, UPLO='U' if upper else UPLO)
+
+
+@register('_npi_solve', inputs=('A', 'B'))
+def np_solve(A, B):
+    return torch.linalg.solve(A, B)
+
+
+@register('_npi_lstsq', inputs=('A', 'B'), nout=4, defaults={'rcond': None})
+def np_lstsq(A, B, rcond=None, finfo_eps_32=None, finfo_eps_64=None, new_default=None):
+    x, res, rank, sv = _np.linalg.lstsq(A.detach().cpu().numpy(), B.detach().cpu().numpy(), rcond=rcond)
+    f = lambda v: torch.from_numpy(_np.asarray(v)).to(A.device)
+    return f(x), f(res), f(_np.asarray(rank)), f(sv)
+
+
+@register('_npi_pinv', '_npi_pinv_scalar_rcond', inputs=('A',), defaults={'rcond': 1e-15, 'hermitian': False})
+def np_pinv(A, rcond=1e-15, hermitian=False):
+    return torch.linalg.pinv(A, rtol=float(rcond), hermitian=hermitian)
+
+
+@register('_npi_matrix_rank', '_npi_matrix_rank_none_tol', inputs=('M',), defaults={'tol': None, 'hermitian': False})
+def np_matrix_rank(M, tol=None, hermitian=False, finfoEps32=None, finfoEps64=None):
+    return torch.linalg.matrix_rank(M, tol=tol, hermitian=hermitian)
+
+
+@register('_npi_tensorinv', inputs=('a',), defaults={'ind': 2})
+def np_tensorinv(a, ind=2):
+    return torch.linalg.tensorinv(a, ind)
+
+
+@register('_npi_tensorsolve', inputs=('a', 'b'), defaults={'a_axes': None})
+def np_tensorsolve(a, b, a_axes=None):
+    return torch.linalg.tensorsolve(a, b, dims=a_axes)
+
+
+@register('_npi_norm', inputs=('data',), defaults={'ord': None, 'axis': None, 'keepdims': False})
+def np_norm(data, ord=None, axis=None, keepdims=False, flag=None):
+    if isinstance(axis, list):
+        axis = tuple(axis)
+    if ord == 'inf':
+        ord = float('inf')
+    if ord == '-inf':
+        ord = -float('inf')
+    if axis is None and ord is None:
+        return torch.linalg.norm(data.reshape(-1), keepdim=False).reshape((1,) * data.dim()) if keepdims \
+            else torch.linalg.norm(data.reshape(-1))
+    if isinstance(axis, tuple) and len(axis) == 2:
+        return torch.linalg.matrix_norm(data, ord if ord is not None else 'fro', dim=axis, keepdim=keepdims)
+    if axis is None and data.dim() == 2 and ord is not None:
+        return torch.linalg.matrix_norm(data, ord, keepdim=keepdims)
+    return torch.linalg.vector_norm(data, 2 if ord is None else ord, dim=axis, keepdim=keepdims)
+
+
+# ------------------------------------------------------------------------------------------
+# init ops (no array inputs)
+# ------------------------------------------------------------------------------------------
+def _dev(ctx):
+    from ..device import current_device, Device
+    if ctx is None:
+        return current_device().torch_device
+    if isinstance(ctx, str):
+        name, _, idx = ctx.partition('(')
+        return Device(name, int(idx.rstrip(')') or 0)).torch_device
+    return ctx.torch_device
+
+
+@register('_zeros', '_npi_zeros', '_zeros_without_dtype', inputs=(), defaults={'shape': (), 'ctx': None, 'dtype': 'float32'})
+def _zeros(shape=(), ctx=None, dtype='float32'):
+    return torch.zeros(tuple(shape) if not isinstance(shape, int) else (shape,), dtype=to_torch_dtype(dtype or 'float32'), device=_dev(ctx))
+
+
+@register('_ones', '_npi_ones', inputs=(), defaults={'shape': (), 'ctx': None, 'dtype': 'float32'})
+def _ones(shape=(), ctx=None, dtype='float32'):
+    return torch.ones(tuple(shape) if not isinstance(shape, int) else (shape,), dtype=to_torch_dtype(dtype or 'float32'), device=_dev(ctx))
+
+
+@register('_full', '_npi_full', inputs=(), defaults={'shape': (), 'ctx': None, 'dtype': 'float32', 'value': 0.0})
+def _full(shape=(), ctx=None, dtype='float32', value=0.0):
+    return torch.full(tuple(shape) if not isinstance(shape, int) else (shape,), value, dtype=to_torch_dtype(dtype or 'float32'), device=_dev(ctx))
+
+
+@register('_arange', '_npi_arange', inputs=(), defaults={'start': 0, 'stop': None, 'step': 1.0, 'repeat': 1, 'ctx': None, 'dtype': 'float32'})
+def _arange(start=0, stop=None, step=1.0, repeat=1, infer_range=False, ctx=None, dtype='float32'):
+    if stop is None:
+        start, stop = 0, start
+    t = torch.arange(start, stop, step, dtype=to_torch_dtype(dtype or 'float32'), device=_dev(ctx))
+    return t.repeat_interleave(repeat) if repeat != 1 else t
+
+
+@register('_linspace', '_npi_linspace', inputs=(), defaults={'start': 0, 'stop': 1, 'num': 50, 'endpoint': True, 'ctx': None, 'dtype': 'float32'})
+def _linspace(start=0, stop=1, num=50, endpoint=True, ctx=None, dtype='float32'):
+    if endpoint:
+        return torch.linspace(start, stop, num, dtype=to_torch_dtype(dtype or 'float32'), device=_dev(ctx))
+    step = (stop - start) / num
+    return (torch.arange(num, device=_dev(ctx), dtype=torch.float64) * step + start).to(to_torch_dtype(dtype or 'float32'))
+
+
+@register('_npi_logspace', inputs=(), defaults={'start': 0, 'stop': 1, 'num': 50, 'endpoint': True, 'base': 10.0, 'ctx': None, 'dtype': 'float32'})
+def _logspace(start=0, stop=1, num=50, endpoint=True, base=10.0, ctx=None, dtype='float32'):
+    return torch.pow(base, _linspace(start, stop, num, endpoint, ctx, 'float64')).to(to_torch_dtype(dtype or 'float32'))
+
+
+@register('_eye', '_npi_eye', inputs=(), defaults={'N': 0, 'M': 0, 'k': 0, 'ctx': None, 'dtype': 'float32'})
+def _eye(N=0, M=0, k=0, ctx=None, dtype='float32'):
+    M = M or N
+    out = torch.zeros(N, M, dtype=to_torch_dtype(dtype or 'float32'), device=_dev(ctx))
+    n = min(N, M - k) if k >= 0 else min(N + k, M)
+    if n > 0:
+        i = torch.arange(n, device=out.device)
+        out[i + max(-k, 0), i + max(k, 0)] = 1
+    return out
+
+
+@register('_npi_identity', inputs=(), defaults={'shape': (), 'ctx': None, 'dtype': 'float32'})
+def _identity(shape=(), ctx=None, dtype='float32'):
+    return torch.eye(shape[0], dtype=to_torch_dtype(dtype or 'float32'), device=_dev(ctx))
+
+
+@register('_npi_tri', inputs=(), defaults={'N': 0, 'M': None, 'k': 0, 'ctx': None, 'dtype': 'float32'})
+def _tri(N=0, M=None, k=0, ctx=None, dtype='float32'):
+    return torch.tril(torch.ones(N, M or N, dtype=to_torch_dtype(dtype or 'float32'), device=_dev(ctx)), k)
+
+
+@register('_npi_indices', inputs=(), defaults={'dimensions': (), 'ctx': None, 'dtype': 'int64'})
+def _indices(dimensions=(), ctx=None, dtype='int64'):
+    grids = torch.meshgrid(*[torch.arange(d, device=_dev(ctx)) for d in dimensions], indexing='ij')
+    return torch.stack(grids, 0).to(to_torch_dtype(dtype))
+
+
+@register('_contrib_arange_like', '_npx_arange_like', 'arange_like', inputs=('data',),
+          defaults={'start': 0.0, 'step': 1.0, 'repeat': 1, 'axis': None})
+def arange_like(data, start=0.0, step=1.0, repeat=1, ctx=None, axis=None):
+    n = data.numel() if axis is None else data.shape[axis]
+    t = torch.arange(n, device=data.device, dtype=torch.float32) * step + start
+    t = t.to(data.dtype if data.dtype.is_floating_point else torch.float32)
+    return t.reshape(data.shape) if axis is None else t
+
+
+@register('_npi_meshgrid', inputs=('*data',), nout=lambda a: a.get('num_args', 1), defaults={'indexing': 'xy'})
+def np_meshgrid(*data, indexing='xy', num_args=None):
+    return tuple(torch.meshgrid(*data, indexing=indexing))
+
+
+@register('_npi_diff', inputs=('data',), defaults={'n': 1, 'axis': -1})
+def np_diff(data, n=1, axis=-1):
+    return torch.diff(data, n, axis)
+
+
+@register('_npi_ediff1d', inputs=('data',))
+def np_ediff1d(data):
+    return torch.diff(data.reshape(-1))
+
+
+@register('_npi_searchsorted', inputs=('a', 'v'), defaults={'side': 'left'})
+def np_searchsorted(a, v, side='left'):
+    return torch.searchsorted(a, v, side=side)
+
+
+@register('_npi_bincount', inputs=('data', 'weights'), defaults={'minlength': 0})
+def np_bincount(data, weights=None, minlength=0):
+    return torch.bincount(data.long(), weights, minlength)
+
+
+@register('_npi_interp', inputs=('xp', 'fp', 'x'))
+def np_interp(xp, fp, x, left=None, right=None, period=None):
+    r = _np.interp(x.cpu().numpy(), xp.cpu().numpy(), fp.cpu().numpy(), left, right, period)
+    return torch.from_numpy(_np.asarray(r)).to(x.device)
+
+
+@register('_npi_nan_to_num', inputs=('data',), defaults={'copy': True, 'nan': 0.0, 'posinf': None, 'neginf': None})
+def np_nan_to_num(data, copy=True, nan=0.0, posinf=None, neginf=None):
+    return torch.nan_to_num(data, nan, posinf, neginf)
+
+
+@register('_npi_percentile', inputs=('a', 'q'), defaults={'axis': None, 'interpolation': 'linear', 'keepdims': False, 'q_scalar': None})
+def np_percentile(a, q=None, axis=None, interpolation='linear', keepdims=False, q_scalar=None):
+    qq = q / 100.0 if q is not None else torch.as_tensor(q_scalar / 100.0, dtype=a.dtype, device=a.device)
+    if isinstance(axis, (tuple, list)):
+        if len(axis) == 1:
+            axis = axis[0]
+        else:
+            keep = [i for i in range(a.dim()) if i not in [x % a.dim() for x in axis]]
+            a = a.permute(keep + [x % a.dim() for x in axis]).reshape([a.shape[i] for i in keep] + [-1])
+            axis = -1
+    return torch.quantile(a, qq.to(a.dtype), dim=axis, keepdim=keepdims, interpolation=interpolation)
+
+
+@register('_npi_average', inputs=('a', 'weights'), defaults={'axis': None, 'returned': False, 'weighted': True})
+def np_average(a, weights=None, axis=None, returned=False, weighted=True):
+    if weights is None:
+        avg = a.mean(_axes(axis, a.dim()))
+        return (avg, torch.full_like(avg, a.numel() / max(avg.numel(), 1))) if returned else avg
+    ax = _axes(axis, a.dim())
+    w = weights
+    if w.shape != a.shape:
+        shape = [1] * a.dim()
+        shape[ax[0]] = -1
+        w = w.reshape(shape)
+    s = (w.expand_as(a)).sum(ax)
+    avg = (a * w).sum(ax) / s
+    return (avg, s) if returned else avg
