@@ -1,0 +1,205 @@
+"""Cached executor behind ``HybridBlock.hybridize()``.
+
+Reference: ``CachedOp`` (``src/imperative/cached_op.cc:385-899``: ``StaticForward`` with
+pre-allocated buffers and pre-built op segments; backward ``:901-1143``) and its optional CUDA-graph
+replay of bulked segments (``src/imperative/cuda_graphs.h:174-586``: one conventional warm-up run,
+then stream capture, re-capture when a pointer changes).
+
+Here the whole forward, and the whole backward, are each ONE captured CUDA graph replayed on static
+buffers when ``static_alloc`` and ``static_shape`` are set on a GPU: the first call with a given
+signature (training flag, input shapes/dtypes, parameter-storage version) runs eagerly, the second
+captures, later calls replay.  The pair is exposed to autograd as a single node (the counterpart of
+the ``_CachedOp`` / ``_backward_CachedOp`` tape node) whose inputs include every parameter, so
+gradients still land in the parameters' own buffers.  Anything that cannot be captured (host
+synchronisation inside ``forward``, data-dependent shapes) makes the block fall back to eager
+execution permanently, the analogue of the reference's split around incompatible operators.
+"""
+from __future__ import annotations
+
+import logging
+
+import torch
+
+from .. import _state, autograd, env
+from ..ndarray.ndarray import NDArray
+
+_log = logging.getLogger('mxnet_b200.cached_op')
+
+
+class _Graphed(object):
+    """Forward/backward graph pair for one call signature."""
+
+    def __init__(self, block, args, training, recording):
+        self.block = block
+        self.training, self.recording = training, recording
+        from .block import _flatten
+        flat, self.in_fmt = _flatten(args, 'input')
+        self.arg_slots = [i for i, a in enumerate(flat) if isinstance(a, NDArray)]
+        self.flat_template = list(flat)
+        arrays = [flat[i] for i in self.arg_slots]
+        self.cls = arrays[0].__class__
+        self.ctx = arrays[0]._ctx
+        dev = arrays[0]._data.device
+        params = [p for p in block.collect_params().values() if p._data is not None]
+        self.param_tensors = []
+        for p in params:
+            arr = p._data.get(self.ctx)
+            if arr is None:
+                arr = next(iter(p._data.values()))
+            if arr._data.requires_grad:
+                self.param_tensors.append(arr._data)
+        self.static_in = []
+        for a in arrays:
+            t = a._data.detach().clone()
+            if recording and a._data.requires_grad:
+                t.requires_grad_(True)
+            self.static_in.append(t)
+        self.grad_inputs = [t for t in self.static_in if t.requires_grad] + (self.param_tensors if recording else [])
+        self.pool = torch.cuda.graph_pool_handle()
+        self.fwd = torch.cuda.CUDAGraph()
+        stream = torch.cuda.Stream(device=dev)
+        stream.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(self.fwd, pool=self.pool, stream=stream):
+                outs = self._run_forward()
+        flat_out, self.out_fmt = _flatten(outs, 'output')
+        self.out_is_array = [isinstance(o, NDArray) for o in flat_out]
+        self.flat_out_template = list(flat_out)
+        self.static_out = [o._data for o in flat_out if isinstance(o, NDArray)]
+        self.bwd = None
+        if recording and self.grad_inputs and any(o.requires_grad for o in self.static_out):
+            self.out_needs_grad = [o.requires_grad for o in self.static_out]
+            self.static_gout = [torch.zeros_like(o) if o.requires_grad else None for o in self.static_out]
+            self.bwd = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream):
+                with torch.cuda.graph(self.bwd, pool=self.pool, stream=stream):
+                    gin = torch.autograd.grad([o for o in self.static_out if o.requires_grad], self.grad_inputs,
+                                              [g for g in self.static_gout if g is not None], allow_unused=True)
+            self.static_gin = list(gin)
+        torch.cuda.current_stream(dev).wait_stream(stream)
+        self.static_out_detached = [o.detach() for o in self.static_out]
+
+    def _run_forward(self):
+        flat = list(self.flat_template)
+        for slot, t in zip(self.arg_slots, self.static_in):
+            flat[slot] = self.cls._from_tensor(t, self.ctx)
+        from .block import _regroup
+        args, _ = _regroup(flat, self.in_fmt)
+        if not isinstance(args, (list, tuple)):
+            args = [args]
+        prev_r, prev_t = _state.state.recording, _state.state.training
+        _state.state.recording, _state.state.training = self.recording, self.training
+        try:
+            if self.recording:
+                with torch.enable_grad():
+                    return self.block.forward(*args)
+            with torch.no_grad():
+                return self.block.forward(*args)
+        finally:
+            _state.state.recording, _state.state.training = prev_r, prev_t
+
+    def __call__(self, args):
+        from .block import _flatten, _regroup
+        flat, _ = _flatten(args, 'input')
+        arrays = [flat[i] for i in self.arg_slots]
+        g = self
+
+        class _Replay(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, *tensors):
+                n = len(g.static_in)
+                for dst, src in zip(g.static_in, tensors[:n]):
+                    if dst.data_ptr() != src.data_ptr():
+                        dst.copy_(src)
+                g.fwd.replay()
+                return tuple(g.static_out_detached)
+
+            @staticmethod
+            def backward(ctx, *gouts):
+                for dst, src in zip(g.static_gout, gouts):
+                    if dst is not None and src is not None and dst.data_ptr() != src.data_ptr():
+                        dst.copy_(src)
+                g.bwd.replay()
+                n_in = len(g.static_in)
+                res, k = [], 0
+                for t in g.static_in:
+                    if t.requires_grad:
+                        gi = g.static_gin[k]
+                        res.append(gi.detach() if gi is not None else None)
+                        k += 1
+                    else:
+                        res.append(None)
+                for gi in g.static_gin[k:]:
+                    res.append(gi.detach() if gi is not None else None)
+                return tuple(res)
+
+        tensors = [a._data for a in arrays]
+        if self.bwd is not None and _state.state.recording:
+            with torch.enable_grad():
+                outs = _Replay.apply(*(tensors + self.param_tensors))
+        else:
+            with torch.no_grad():
+                for dst, src in zip(self.static_in, tensors):
+                    dst.copy_(src)
+                self.fwd.replay()
+                outs = tuple(self.static_out_detached)
+        flat_out, k = list(self.flat_out_template), 0
+        for i, is_arr in enumerate(self.out_is_array):
+            if is_arr:
+                flat_out[i] = self.cls._from_tensor(outs[k], self.ctx)
+                k += 1
+        res, _ = _regroup(flat_out, self.out_fmt)
+        return res
+
+
+class CachedOp(object):
+    """Per-block cache of executors keyed by call signature."""
+
+    def __init__(self, block, flags):
+        self.block = block
+        self.flags = dict(flags or {})
+        self._seen = {}
+        self._graphs = {}
+        self._disabled = False
+
+    def _use_graphs(self, arrays):
+        if self._disabled or not env.get('MXNET_ENABLE_CUDA_GRAPHS'):
+            return False
+        if not (self.flags.get('static_alloc') and self.flags.get('static_shape')):
+            return False
+        return bool(arrays) and all(a._data.is_cuda for a in arrays)
+
+    def _signature(self, flat):
+        from . import block as blk
+        sig = [blk._storage_version[0], _state.state.training, _state.state.recording]
+        for a in flat:
+            if isinstance(a, NDArray):
+                sig.append((tuple(a.shape), str(a._data.dtype), a._data.requires_grad))
+            else:
+                sig.append(repr(a))
+        return tuple(sig)
+
+    def __call__(self, *args):
+        from .block import _flatten
+        flat, _ = _flatten(args, 'input')
+        arrays = [a for a in flat if isinstance(a, NDArray)]
+        if not self._use_graphs(arrays):
+            return self.block._call_forward(*args)
+        sig = self._signature(flat)
+        g = self._graphs.get(sig)
+        if g is not None:
+            return g(args)
+        if sig not in self._seen:
+            self._seen[sig] = 1          # warm-up run with this signature stays eager
+            return self.block._call_forward(*args)
+        try:
+            g = _Graphed(self.block, args, _state.state.training, _state.state.recording)
+        except Exception as e:  # pylint: disable=broad-except
+            self._disabled = True
+            if env.get('MXNET_CUDA_GRAPHS_VERBOSE'):
+                _log.warning('CUDA graph capture failed (%s); block %s runs eagerly', e, type(self.block).__name__)
+            return self.block._call_forward(*args)
+        self._graphs[sig] = g
+        if env.get('MXNET_CUDA_GRAPHS_VERBOSE'):
+            _log.info('captured CUDA graphs for %s signature %s', type(self.block).__name__, sig[:3])
+        return g(args)

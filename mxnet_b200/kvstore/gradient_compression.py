@@ -1,0 +1,68 @@
+"""1-bit and 2-bit gradient compression with residual accumulation
+(``src/kvstore/gradient_compression-inl.h:45-215``).
+
+2-bit: each value of (gradient + residual) becomes one of {-threshold, 0, +threshold}; what was not
+sent stays in the residual.  1-bit: sign against the threshold, values are ±1.  Sixteen 2-bit codes
+(or thirty-two 1-bit codes) are packed per 32-bit word; the packed words are what would travel.
+"""
+import torch
+
+
+class GradientCompression(object):
+    def __init__(self, type='2bit', threshold=0.5):  # pylint: disable=redefined-builtin
+        if type not in ('1bit', '2bit'):
+            raise ValueError('Unknown type for gradient compression ' + str(type))
+        if type == '2bit' and threshold <= 0:
+            raise ValueError('threshold must be greater than 0')
+        self.type, self.threshold = type, float(threshold)
+        self._residual = {}
+
+    def get_params(self):
+        return {'type': self.type, 'threshold': self.threshold}
+
+    def compressed_size(self, n):
+        per_word = 16 if self.type == '2bit' else 32
+        return (n + per_word - 1) // per_word
+
+    def quantize(self, key, grad):
+        """Returns packed int32 codes; updates the residual kept for ``key``."""
+        g = grad.reshape(-1).float()
+        res = self._residual.get(key)
+        if res is None or res.shape != g.shape or res.device != g.device:
+            res = self._residual[key] = torch.zeros_like(g)
+        res.add_(g)
+        t = self.threshold
+        if self.type == '2bit':
+            pos, neg = res >= t, res <= -t
+            codes = torch.where(pos, 3, torch.where(neg, 2, 0)).to(torch.int64)
+            res.sub_(pos.float() * t).add_(neg.float() * t)
+            per, bits = 16, 2
+        else:
+            pos = res > t
+            codes = pos.to(torch.int64)
+            res.sub_(torch.where(pos, torch.ones_like(res), -torch.ones_like(res)))
+            per, bits = 32, 1
+        n = codes.numel()
+        pad = (-n) % per
+        if pad:
+            codes = torch.cat([codes, codes.new_zeros(pad)])
+        codes = codes.reshape(-1, per)
+        shifts = torch.arange(per, device=codes.device, dtype=torch.int64) * bits
+        packed = (codes << shifts).sum(1)
+        return (packed & 0xFFFFFFFF).to(torch.int64)
+
+    def dequantize(self, packed, n, dtype=torch.float32):
+        per, bits = (16, 2) if self.type == '2bit' else (32, 1)
+        shifts = torch.arange(per, device=packed.device, dtype=torch.int64) * bits
+        codes = ((packed.reshape(-1, 1) >> shifts) & ((1 << bits) - 1)).reshape(-1)[:n]
+        t = self.threshold
+        if self.type == '2bit':
+            out = torch.where(codes == 3, t, torch.where(codes == 2, -t, 0.0))
+        else:
+            out = torch.where(codes == 1, 1.0, -1.0)
+        return out.to(dtype)
+
+    def compress_roundtrip(self, key, grad):
+        """What the receiver reconstructs from this device's contribution."""
+        packed = self.quantize(key, grad)
+        return self.dequantize(packed, grad.numel(), grad.dtype).reshape(grad.shape)

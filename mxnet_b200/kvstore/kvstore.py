@@ -1,0 +1,262 @@
+"""Native KVStore: ``local`` / ``device`` / ``nccl`` / ``dist_*`` semantics.
+
+Reference: ``src/kvstore/kvstore_local.h`` (``PushImpl :232-277``, ``PullImpl :279-306``,
+``GroupKVPairs :436-465``), ``comm.h`` (CPU tree-sum ``:388-441``; device gather→sum→broadcast
+``:535-654``), ``kvstore_nccl.h`` (Reduce/Bcast), ``kvstore_dist.h`` (parameter server) and the
+Python wrapper ``python/mxnet/kvstore/kvstore.py``.
+
+Checklist kept: ``init`` once per key; ``push`` sums all values given for a key (list = one per
+device) then runs the updater ``(key, merged, stored)`` or overwrites; ``pull`` copies the stored
+value to every output; ``pushpull(key, value, out=None)`` defaults out to value; ``broadcast`` =
+init + pull; int or str keys, never mixed; higher ``priority`` first; ``nccl`` rejects sparse
+values and compression.
+
+Process model: inside one process a key may carry several replicas (one per device, CPU ids
+included).  Across processes (one per GPU, ``torch.distributed`` initialised) every store type
+sums over all ranks; the ``device``/``nccl`` stores of a Trainer use the fused peer-memory kernels
+of ``parallel.fused`` for dense half/float gradients and fall back to NCCL collectives otherwise.
+"""
+from __future__ import annotations
+
+import pickle
+
+import torch
+
+from .. import env
+from ..base import MXNetError
+from ..ndarray.ndarray import NDArray
+from ..ndarray import sparse as _sparse
+from ..optimizer import Updater, get_updater
+from .base import KVStoreBase, _ctype_key_value
+from .gradient_compression import GradientCompression
+
+__all__ = ['KVStore']
+
+_TYPES = ('local', 'device', 'nccl', 'dist_sync', 'dist_async', 'dist_device_sync', 'dist_sync_device', 'dist',
+          'local_allreduce_cpu', 'local_allreduce_device', 'local_update_cpu', 'dist_p3', 'p3')
+
+
+class KVStore(KVStoreBase):
+    def __init__(self, name='local'):
+        if name not in _TYPES:
+            raise MXNetError('Unknown KVStore type "%s"' % name)
+        self._type = name
+        self._store = {}
+        self._updater = None
+        self._updater_func = None
+        self._str_keys = None
+        self._compression = None
+        self._barrier_before_exit = True
+        from ..parallel import dist
+        self._dist = dist
+        if name.startswith('dist') or name == 'p3':
+            dist.ensure_initialized()
+
+    # ------------------------------------------------------------------ properties
+    @property
+    def type(self):
+        return self._type
+
+    @property
+    def rank(self):
+        return self._dist.rank() if self._dist.is_initialized() else 0
+
+    @property
+    def num_workers(self):
+        return self._dist.world_size() if self._dist.is_initialized() else 1
+
+    @staticmethod
+    def is_capable(capability):
+        if capability.lower() == KVStoreBase.OPTIMIZER:
+            return True
+        raise ValueError('Unknown capability: {}'.format(capability))
+
+    # ------------------------------------------------------------------ helpers
+    def _check_key(self, k):
+        is_str = isinstance(k, str)
+        if self._str_keys is None:
+            self._str_keys = is_str
+        elif self._str_keys != is_str:
+            raise MXNetError('inconsistent key types: string and integer keys cannot be mixed')
+
+    def _group(self, key, value):
+        """GroupKVPairs: duplicate keys are merged into per-key value lists."""
+        if isinstance(key, (list, tuple)):
+            if value is not None and len(key) != len(value):
+                raise MXNetError('key and value lists differ in length')
+            grouped, order = {}, []
+            for i, k in enumerate(key):
+                self._check_key(k)
+                v = value[i] if value is not None else None
+                if k not in grouped:
+                    grouped[k] = []
+                    order.append(k)
+                if isinstance(v, (list, tuple)):
+                    grouped[k].extend(v)
+                elif v is not None:
+                    grouped[k].append(v)
+            return [(k, grouped[k]) for k in order]
+        self._check_key(key)
+        if value is None:
+            return [(key, [])]
+        return [(key, list(value) if isinstance(value, (list, tuple)) else [value])]
+
+    def _reduce(self, key, values, target_ctx=None):
+        """Sum replicas on the device of the stored value (merge buffer), then across ranks."""
+        if self._type == 'nccl':
+            for v in values:
+                if getattr(v, '_stype', 'default') != 'default':
+                    raise MXNetError('kvstore nccl does not support sparse values')
+        first = values[0]
+        dev = first._data.device
+        if self._compression is not None and first._data.dtype == torch.float32:
+            parts = [self._compression.compress_roundtrip((key, i), v._data).to(dev) for i, v in enumerate(values)]
+        else:
+            parts = [v._data if v._data.device == dev else v._data.to(dev, non_blocking=True) for v in values]
+        if len(parts) == 1:
+            merged = parts[0].clone() if self._dist.is_initialized() and self._dist.world_size() > 1 else parts[0]
+        else:
+            acc = parts[0].float() if parts[0].dtype in (torch.float16, torch.bfloat16) else parts[0].clone()
+            for p in parts[1:]:
+                acc.add_(p.to(acc.dtype))
+            merged = acc.to(parts[0].dtype)
+        if self._dist.is_initialized() and self._dist.world_size() > 1 and \
+                (self._type.startswith('dist') or self._type in ('nccl', 'device', 'p3')):
+            merged = self._dist.all_reduce_sum(merged)
+        cls = first.__class__ if not isinstance(first, _sparse.BaseSparseNDArray) else NDArray
+        return cls._from_tensor(merged, first._ctx)
+
+    # ------------------------------------------------------------------ API
+    def init(self, key, value):
+        for k, vals in self._group(key, value):
+            if k in self._store:
+                raise MXNetError('duplicate init of key %s' % str(k))
+            v = vals[0]
+            stored = v.__class__._from_tensor(v._data.detach().clone(), v._ctx)
+            stored._stype = getattr(v, '_stype', 'default')
+            if self._dist.is_initialized() and self._dist.world_size() > 1 and self._type != 'local':
+                self._dist.broadcast_(stored._data, src=0)
+            self._store[k] = stored
+
+    def push(self, key, value, priority=0):
+        for k, vals in self._group(key, value):
+            if k not in self._store:
+                raise MXNetError('key %s has not been initialized' % str(k))
+            merged = self._reduce(k, vals)
+            stored = self._store[k]
+            if self._updater is not None:
+                if merged._data.device != stored._data.device:
+                    merged = merged.as_in_context(stored._ctx)
+                self._updater(k if not isinstance(k, str) else k, merged, stored)
+            else:
+                with torch.no_grad():
+                    if stored._data.shape != merged._data.shape:
+                        raise MXNetError('shape mismatch for key %s' % str(k))
+                    stored._data.copy_(merged._data)
+
+    def pull(self, key, out=None, priority=0, ignore_sparse=True):
+        assert out is not None
+        for k, outs in self._group(key, out):
+            if k not in self._store:
+                raise MXNetError('key %s has not been initialized' % str(k))
+            stored = self._store[k]
+            for o in outs:
+                if ignore_sparse and getattr(o, '_stype', 'default') != 'default':
+                    continue
+                with torch.no_grad():
+                    o._data.copy_(stored._data, non_blocking=True)
+
+    def pushpull(self, key, value, out=None, priority=0):
+        if out is None:
+            out = value
+        if self._updater is None:
+            # fast path without touching the stored value when no updater is installed
+            for (k, vals), (_, outs) in zip(self._group(key, value), self._group(key, out)):
+                merged = self._reduce(k, vals)
+                if k in self._store and self._store[k]._data.shape == merged._data.shape:
+                    with torch.no_grad():
+                        self._store[k]._data.copy_(merged._data)
+                for o in outs:
+                    with torch.no_grad():
+                        if o._data is not merged._data:
+                            o._data.copy_(merged._data, non_blocking=True)
+            return
+        self.push(key, value, priority)
+        self.pull(key, out, priority)
+
+    def broadcast(self, key, value, out, priority=0):
+        for k, vals in self._group(key, value):
+            if k not in self._store:
+                self.init(k, vals[0])
+            else:
+                with torch.no_grad():
+                    self._store[k]._data.copy_(vals[0]._data)
+        self.pull(key, out=out, priority=priority)
+
+    def row_sparse_pull(self, key, out=None, priority=0, row_ids=None):
+        """Pull only the rows named by ``row_ids`` (unique, sorted on device like ``kvstore_utils.cu``)."""
+        assert out is not None and row_ids is not None
+        groups = self._group(key, out)
+        if isinstance(row_ids, NDArray):
+            row_ids = [row_ids]
+        flat_ids = []
+        for (k, outs) in groups:
+            flat_ids.append([row_ids[min(len(flat_ids), len(row_ids) - 1)]] * len(outs) if len(row_ids) != len(outs)
+                            else row_ids)
+        for (k, outs), ids in zip(groups, flat_ids):
+            stored = self._store[k]
+            for o, rid in zip(outs, ids):
+                idx = torch.unique(rid._data.long().reshape(-1).to(stored._data.device))
+                res = torch.zeros_like(stored._data)
+                res[idx] = stored._data[idx]
+                with torch.no_grad():
+                    o._data.copy_(res.to(o._data.device))
+
+    def set_gradient_compression(self, compression_params):
+        if self._type == 'nccl':
+            raise MXNetError('Gradient compression is not supported for kvstore nccl')
+        if self._type == 'local':
+            raise MXNetError('Gradient compression is not supported for this type of kvstore')
+        self._compression = GradientCompression(**compression_params)
+
+    def set_optimizer(self, optimizer):
+        """Install an optimizer: updates then run where the merged value lives."""
+        self._set_updater(get_updater(optimizer))
+
+    def _set_updater(self, updater):
+        self._updater = updater
+
+    def set_updater(self, updater):
+        self._set_updater(updater)
+
+    def save_optimizer_states(self, fname, dump_optimizer=False):
+        assert self._updater is not None, 'Cannot save states for distributed training'
+        with open(fname, 'wb') as fout:
+            fout.write(self._updater.get_states(dump_optimizer))
+
+    def load_optimizer_states(self, fname):
+        assert self._updater is not None, 'Cannot load states for distributed training'
+        with open(fname, 'rb') as f:
+            self._updater.set_states(f.read())
+
+    def barrier(self):
+        from .. import engine
+        engine.waitall()
+        if self._dist.is_initialized():
+            self._dist.barrier()
+
+    _barrier = barrier
+
+    def _send_command_to_servers(self, head, body):
+        pass
+
+    def get_num_dead_node(self, node_id=0, timeout=60):
+        """Number of ranks whose heartbeat is older than ``timeout`` seconds (``kvstore.h:411``)."""
+        return self._dist.num_dead_nodes(timeout) if self._dist.is_initialized() else 0
+
+    def is_recovery(self):
+        import os
+        return os.environ.get('DMLC_IS_RECOVERY', '0') == '1'
+
+    def set_barrier_before_exit(self, flag):
+        self._barrier_before_exit = bool(flag)

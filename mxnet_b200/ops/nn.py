@@ -136,13 +136,13 @@ def _bn_nout(attrs):
     return 3 if attrs.get('output_mean_var') in (True, 'True', 1) else 1
 
 
-@register('BatchNorm', '_npx_batch_norm', 'BatchNorm_v1', inputs=('data', 'gamma', 'beta', 'moving_mean', 'moving_var'),
+@register('BatchNorm', '_npx_batch_norm', 'BatchNorm_v1', inputs=('data', 'gamma', 'beta', 'moving_mean', 'moving_var', 'residual'),
           nout=_bn_nout, aux=('moving_mean', 'moving_var'),
           defaults={'eps': 1e-3, 'momentum': 0.9, 'fix_gamma': True, 'use_global_stats': False,
                     'output_mean_var': False, 'axis': 1, 'cudnn_off': False})
-def batch_norm(data, gamma, beta, moving_mean, moving_var, eps=1e-3, momentum=0.9, fix_gamma=True,
+def batch_norm(data, gamma, beta, moving_mean, moving_var, residual=None, eps=1e-3, momentum=0.9, fix_gamma=True,
                use_global_stats=False, output_mean_var=False, axis=1, cudnn_off=False,
-               min_calib_range=None, max_calib_range=None, act_type=None, residual=None):
+               min_calib_range=None, max_calib_range=None, act_type=None):
     """Batch normalisation; ``act_type``/``residual`` select the fused BN(+add)+ReLU form used by
     the NHWC ResNet blocks (one pass over the activations instead of three)."""
     axis = axis % data.dim()
@@ -191,7 +191,7 @@ def sync_batch_norm(data, gamma, beta, moving_mean, moving_var, eps=1e-3, moment
     from ..parallel import dist
     training = _state.state.training and not use_global_stats
     if not training or not dist.is_initialized() or dist.world_size() == 1:
-        return batch_norm(data, gamma, beta, moving_mean, moving_var, eps, momentum, fix_gamma,
+        return batch_norm(data, gamma, beta, moving_mean, moving_var, None, eps, momentum, fix_gamma,
                           use_global_stats, output_mean_var, axis)
     if fix_gamma:
         gamma = torch.ones_like(gamma)

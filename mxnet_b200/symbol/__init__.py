@@ -1,0 +1,42 @@
+"""``mx.sym``: symbolic namespace; operator composition functions are generated from the registry
+(``python/mxnet/symbol/register.py``)."""
+import sys as _sys
+import types as _types
+
+from ..ops import registry as _reg
+from .symbol import *      # noqa: F401,F403
+from .symbol import Symbol, var, Variable, Group, load, load_json, fromjson, _op_frontend
+from . import passes, _trace   # noqa: F401
+
+
+def _populate():
+    mod = _sys.modules[__name__]
+    internal = _types.ModuleType(__name__ + '._internal')
+    contrib = _types.ModuleType(__name__ + '.contrib')
+    linalg = _types.ModuleType(__name__ + '.linalg')
+    image = _types.ModuleType(__name__ + '.image')
+    random = _types.ModuleType(__name__ + '.random')
+    op = _types.ModuleType(__name__ + '.op')
+    for name in _reg.list_ops():
+        fn = _op_frontend(_reg.get(name))
+        setattr(op, name, fn)
+        if name.startswith('_contrib_'):
+            setattr(contrib, name[len('_contrib_'):], fn)
+        elif name.startswith('_linalg_'):
+            setattr(linalg, name[len('_linalg_'):], fn)
+        elif name.startswith('_image_'):
+            setattr(image, name[len('_image_'):], fn)
+        elif name.startswith('_random_') or name.startswith('_sample_'):
+            setattr(random, name.split('_', 2)[2], fn)
+        if name.startswith('_'):
+            setattr(internal, name, fn)
+        elif not hasattr(mod, name):
+            setattr(mod, name, fn)
+    for m in (internal, contrib, linalg, image, random, op):
+        _sys.modules[m.__name__] = m
+    mod._internal, mod.contrib, mod.linalg, mod.image, mod.random, mod.op = internal, contrib, linalg, image, random, op
+
+
+_populate()
+from . import numpy as np          # noqa: E402,F401
+from . import numpy_extension as npx   # noqa: E402,F401
