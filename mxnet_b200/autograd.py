@@ -18,7 +18,7 @@ import torch
 
 from . import _state
 from .base import MXNetError
-from .ndarray.ndarray import NDArray, _dirty_grads
+from .ndarray.ndarray import NDArray
 
 __all__ = ['set_recording', 'set_training', 'is_recording', 'is_training', 'record', 'pause', 'train_mode',
            'predict_mode', 'mark_variables', 'backward', 'grad', 'get_symbol', 'Function']
@@ -82,25 +82,25 @@ def predict_mode():
     return _RecordingStateScope(None, False)
 
 
+_pass_id = [0]
+
+
 def _make_hook(ref):
-    def hook(t):
+    """Pre-accumulation hook of a marked leaf.  ``grad_req='write'``: the first gradient that reaches
+    the leaf in a new backward pass must replace what an earlier pass left in the buffer, so the
+    buffer is cleared right before the in-place accumulation.  Leaves that do not take part in a
+    pass keep their gradients, like in the reference where only the variables of the differentiated
+    graph are written."""
+    def hook(g):
         var = ref()
         if var is None:
-            return
-        buf = var._grad._data
-        g = t.grad
-        if g is not buf:
-            # the engine replaced the tensor (create_graph, dtype mismatch): fold it back
-            with torch.no_grad():
-                if var._grad_req == 'add' or var._fresh_grad:
-                    buf.add_(g.detach().to(buf.dtype))
-                else:
-                    buf.copy_(g.detach())
-            t.grad = buf
-        if not var._fresh_grad:
-            var._fresh_grad = True
-            if var._grad_req == 'write':
-                _dirty_grads.append(ref)
+            return None
+        cur = _pass_id[0]
+        if var._grad_req == 'write' and var._fresh_grad and var._grad_pass != cur:
+            var._grad._data.zero_()
+        var._fresh_grad = True
+        var._grad_pass = cur
+        return None
     return hook
 
 
@@ -132,23 +132,8 @@ def mark_variables(variables, gradients, grad_reqs='write'):
         var._fresh_grad = False
         t.requires_grad_(True)
         t.grad = g._data
-        var._hook = t.register_post_accumulate_grad_hook(_make_hook(weakref.ref(var)))
-
-
-def _clear_written():
-    """grad_req='write': buffers written by a previous pass start from zero again."""
-    if not _dirty_grads:
-        return
-    bufs = []
-    for ref in _dirty_grads:
-        var = ref()
-        if var is not None and var._grad is not None and var._fresh_grad:
-            var._fresh_grad = False
-            bufs.append(var._grad._data)
-    del _dirty_grads[:]
-    if bufs:
-        with torch.no_grad():
-            torch._foreach_zero_(bufs)
+        var._grad_pass = -1
+        var._hook = t.register_hook(_make_hook(weakref.ref(var)))
 
 
 def mark_grads_consumed(arrays):
@@ -181,7 +166,7 @@ def backward(heads, head_grads=None, retain_graph=False, train_mode=True):  # py
             raise MXNetError('Cannot differentiate node because it is not in a computational graph. '
                              'You need to set is_recording to true or use autograd.record() to save '
                              'computational graphs for backward.')
-    _clear_written()
+    _pass_id[0] += 1
     grads = _head_grads(heads, head_grads)
     prev = set_training(train_mode)
     try:

@@ -1,0 +1,5 @@
+"""``mx.contrib``: quantization, text utilities, tensorboard bridge, ONNX aliases."""
+from . import quantization, text, tensorboard
+from .. import onnx
+from ..ndarray import contrib as ndarray   # noqa: F401
+from ..ndarray import contrib as nd        # noqa: F401

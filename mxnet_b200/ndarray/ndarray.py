@@ -25,18 +25,13 @@ __all__ = ['NDArray', 'array', 'empty', 'zeros', 'ones', 'full', 'arange', 'conc
 
 _STORAGE_TYPE_STR = {0: 'default', 1: 'row_sparse', 2: 'csr'}
 
-# arrays whose 'write' gradient buffer holds a value from an earlier backward pass and must be
-# cleared before the next one accumulates into it (see autograd.backward)
-_dirty_grads = []
-
-
 def _torch_device_of(ctx):
     return ctx.torch_device if ctx is not None else current_device().torch_device
 
 
 class NDArray(object):
     """N-dimensional array on a device.  ``_kind`` selects legacy (``nd``) or NumPy (``np``) semantics."""
-    __slots__ = ('_data', '_ctx', '_grad', '_grad_req', '_stype', '_sym', '_fresh_grad', '_hook', '__weakref__')
+    __slots__ = ('_data', '_ctx', '_grad', '_grad_req', '_stype', '_sym', '_fresh_grad', '_hook', '_grad_pass', '__weakref__')
     _kind = 'nd'
     __array_priority__ = 1000.0
 
@@ -53,6 +48,7 @@ class NDArray(object):
         self._sym = None
         self._fresh_grad = False
         self._hook = None
+        self._grad_pass = -1
 
     @classmethod
     def _from_tensor(cls, t, ctx=None):
@@ -66,6 +62,7 @@ class NDArray(object):
         obj._sym = None
         obj._fresh_grad = False
         obj._hook = None
+        obj._grad_pass = -1
         return obj
 
     # ------------------------------------------------------------------ basic properties
