@@ -1,0 +1,215 @@
+#!/usr/bin/env python
+"""Headline benchmark: ResNet-50 v1b training throughput (img/s), AMP fp16, NHWC, batch 256 per GPU,
+multi-precision SGD momentum 0.9 / wd 1e-4, data parallel over N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Prints ONE JSON line (rank 0).  ``value`` is the whole-job img/s with inputs already on the device, timed
+with CUDA events (max over ranks).  ``e2e`` is the same training step driven through the public Gluon API
+including, every step, the host→device copy of that step's uint8 batch from pinned memory and a
+device→host read of the loss.  ``--impl reference`` reports why the reference cannot run here.
+"""
+import argparse
+import json
+import os
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+BASELINE_IMG_S_1GPU = 363.69      # ResNet-50 training, V100 fp32 batch 128, docs/static_site/.../perf.md:242-253
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--batch', type=int, default=256, help='images per GPU')
+    ap.add_argument('--image', type=int, default=224)
+    ap.add_argument('--classes', type=int, default=1000)
+    ap.add_argument('--graphs', type=int, default=int(os.environ.get('MXB_BENCH_GRAPHS', '1')),
+                    help='hybridize(static_alloc, static_shape): CUDA-graph replay of forward/backward')
+    ap.add_argument('--no-e2e', action='store_true')
+    return ap.parse_args()
+
+
+def reference_arm(args):
+    print(json.dumps({'impl': 'reference', 'unavailable':
+                      'reference is not installable offline: /root/reference has no setup.py/pyproject.toml at its root, '
+                      'python/setup.py needs a compiled libmxnet.so and the dmlc-core/tvm(nnvm)/ps-lite/cub submodules '
+                      'are empty, so it cannot be built (pip: "Neither setup.py nor pyproject.toml found")'}))
+    return 0
+
+
+def main():
+    args = parse()
+    if args.impl == 'reference':
+        return reference_arm(args)
+    import numpy as np
+    import torch
+    import mxnet_b200 as mx
+    from mxnet_b200 import amp, autograd, gluon
+    from mxnet_b200.models import resnet50_v1b
+    from mxnet_b200.ops import cuda as kernels
+    from mxnet_b200.parallel import dist
+    from mxnet_b200.utils import ClockSampler
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    if world > 1:
+        dist.ensure_initialized('nccl')
+    rank, local = dist.rank(), dist.local_rank()
+    torch.cuda.set_device(local)
+    ctx = mx.gpu(local)
+    torch.backends.cudnn.benchmark = True
+    mx.random.seed(1234 + rank)
+    np.random.seed(1234 + rank)
+
+    B, S, NC = args.batch, args.image, args.classes
+    global_batch = B * world
+    amp.init('float16')
+    net = resnet50_v1b(classes=NC, layout='NHWC', fused=True)
+    net.initialize(mx.init.Xavier(rnd_type='gaussian', factor_type='out', magnitude=2), ctx=ctx)
+    # fp16 weights everywhere (fp32 master copies live in the optimizer); BatchNorm statistics stay fp32
+    for p in net.collect_params().values():
+        if p.grad_req != 'null':
+            p.cast('float16')
+    loss_fn = gluon.loss.SoftmaxCrossEntropyLoss()
+    trainer = gluon.Trainer(net.collect_params(), 'sgd',
+                            {'learning_rate': 0.1 * global_batch / 256.0, 'momentum': 0.9, 'wd': 1e-4,
+                             'multi_precision': True}, kvstore='device')
+    amp.init_trainer(trainer)
+    if args.graphs:
+        net.hybridize(static_alloc=True, static_shape=True)
+
+    mean = torch.tensor([123.68, 116.28, 103.53], device=ctx.torch_device, dtype=torch.float16)
+    inv_std = torch.tensor([1 / 58.4, 1 / 57.12, 1 / 57.38], device=ctx.torch_device, dtype=torch.float16)
+
+    def preprocess(u8):
+        """uint8 NHWC batch on the device -> normalised fp16 NHWC."""
+        return mx.nd.NDArray._from_tensor((u8.to(torch.float16) - mean) * inv_std, ctx)
+
+    def train_step(x, y):
+        with autograd.record():
+            out = net(x)
+            loss = loss_fn(out, y)
+            with amp.scale_loss(loss, trainer) as scaled:
+                autograd.backward(scaled)
+        trainer.step(global_batch)
+        return loss
+
+    # synthetic data: pixel values from N(0,1) after normalisation, labels uniform in [0, classes)
+    n_host = 4
+    host_x = [torch.randint(0, 256, (B, S, S, 3), dtype=torch.uint8).pin_memory() for _ in range(n_host)]
+    host_y = [torch.randint(0, NC, (B,), dtype=torch.int64).pin_memory() for _ in range(n_host)]
+    dev_x = [preprocess(h.to(ctx.torch_device)) for h in host_x[:2]]
+    dev_y = [mx.nd.NDArray._from_tensor(h.to(ctx.torch_device), ctx) for h in host_y[:2]]
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=ctx.torch_device, dtype=torch.float64)
+        import torch.distributed as tdist
+        tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------------------------------------------------------- device-timed steps (inputs resident)
+    for i in range(max(args.warmup, 3)):
+        train_step(dev_x[i % 2], dev_y[i % 2])
+    barrier()
+    sampler = ClockSampler(local).start()
+    l0 = kernels.launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        loss = train_step(dev_x[i % 2], dev_y[i % 2])
+    e1.record()
+    barrier()
+    launches = kernels.launches() - l0
+    clocks = sampler.stop()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    value = global_batch * args.steps / (ms / 1000.0)
+    final_loss = float(loss.mean().asscalar())
+
+    # ---------------------------------------------------------------- end to end through the public API
+    e2e = None
+    if not args.no_e2e:
+        copy_stream = torch.cuda.Stream(device=ctx.torch_device)
+        loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+        h2d_bytes = host_x[0].numel() * host_x[0].element_size() + host_y[0].numel() * host_y[0].element_size()
+        d2h_bytes = loss_host.numel() * loss_host.element_size()
+        staged = [None, None]
+
+        def stage(i):
+            """Copy batch i to the device on the copy stream (overlaps the previous step's compute)."""
+            with torch.cuda.stream(copy_stream):
+                xb = host_x[i % n_host].to(ctx.torch_device, non_blocking=True)
+                yb = host_y[i % n_host].to(ctx.torch_device, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_stream)
+            staged[i % 2] = (xb, yb, ev)
+
+        def run(n, timed):
+            losses = []
+            stage(0)
+            for i in range(n):
+                xb, yb, ev = staged[i % 2]
+                torch.cuda.current_stream().wait_event(ev)
+                if i + 1 < n:
+                    stage(i + 1)
+                x = preprocess(xb)
+                y = mx.nd.NDArray._from_tensor(yb, ctx)
+                loss = train_step(x, y)
+                xb.record_stream(torch.cuda.current_stream())
+                yb.record_stream(torch.cuda.current_stream())
+                loss_host.copy_(loss.mean()._data.float().reshape(1), non_blocking=True)   # device -> host read of the result
+                torch.cuda.current_stream().synchronize() if not timed else None
+                losses.append(loss_host)
+            return losses
+        run(max(args.warmup, 3), False)
+        barrier()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        run(args.steps, True)
+        t1.record()
+        barrier()
+        ms_e2e = max_over_ranks(t0.elapsed_time(t1))
+        e2e = {'value': global_batch * args.steps / (ms_e2e / 1000.0), 'unit': 'img/s', 'ms_per_step': ms_e2e / args.steps,
+               'h2d_bytes_per_step': int(h2d_bytes), 'd2h_bytes_per_step': int(d2h_bytes),
+               'last_loss': float(loss_host.item())}
+
+    if rank == 0:
+        fused = trainer._fused is not None
+        out = {
+            'metric': 'resnet50_train_img_per_s', 'value': value, 'unit': 'img/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': max(args.warmup, 3), 'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': value / (BASELINE_IMG_S_1GPU * world), 'dtype': 'fp16', 'data': 'synthetic',
+            'config': {'model': 'resnet50_v1b', 'global_batch': global_batch, 'batch_per_gpu': B, 'image': S, 'layout': 'NHWC',
+                       'parallelism': 'dp%d' % world, 'optimizer': 'sgd momentum 0.9 wd 1e-4 multi-precision',
+                       'amp': 'fp16 dynamic loss scale (device resident)', 'fused_step': fused, 'cuda_graphs': bool(args.graphs),
+                       'l2': 'inputs larger than L2 (activations per step >> 126 MB); no explicit flush',
+                       'baseline_ref': 'V100 fp32 bs128 363.69 img/s per GPU (perf.md) x n_gpus'},
+            'clocks': {k: clocks[k] for k in ('sm_mhz', 'sm_max_mhz', 'reasons')},
+            'gpu_launches': int(launches), 'final_loss': final_loss, 'impl': 'ours',
+        }
+        if e2e is not None:
+            out['e2e'] = e2e
+        print(json.dumps(out))
+    if world > 1:
+        barrier()
+        dist.destroy()
+    return 0
+
+
+if __name__ == '__main__':
+    sys.exit(main())

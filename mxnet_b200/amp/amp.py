@@ -100,6 +100,16 @@ def init_trainer(optimizer_or_trainer):
         if _target == torch.bfloat16:
             loss_scaler._loss_scale = 1.0
             loss_scaler._max_loss_scale = 1.0
+        # bring up the optimizer path now when the parameters already exist, so that the loss scale can
+        # live on the device from the first step on
+        try:
+            tr = optimizer_or_trainer
+            if not tr._kv_initialized and tr._check_devices() is not None:
+                tr._init_kvstore()
+            if tr._fused is not None:
+                tr._fused.attach_scaler(loss_scaler)
+        except Exception:  # pylint: disable=broad-except
+            pass
     else:
         raise TypeError('optimizer_or_trainer should be a Gluon Trainer instance, instead is %s' % type(optimizer_or_trainer))
 
@@ -109,6 +119,17 @@ def scale_loss(loss, optimizer_or_trainer):
     """``with amp.scale_loss(loss, trainer) as scaled: autograd.backward(scaled)``."""
     scaler = optimizer_or_trainer._amp_loss_scaler
     assert scaler is not None, 'Loss scaler is not initialized, did you forget to call amp.init_trainer()?'
+    if scaler._device_state is not None:
+        # the scale lives on the device (fused optimizer step): multiply by the device scalar, the
+        # kernels divide it out again; the host never reads it, so there is no synchronisation here
+        optimizer_or_trainer._scale = optimizer_or_trainer._amp_original_scale
+        first = loss[0] if isinstance(loss, (list, tuple)) else loss
+        s_arr = first.__class__._from_tensor(scaler._device_state[0:1], first.context)
+        if isinstance(loss, (list, tuple)):
+            yield [l * s_arr.astype(l.dtype) if l.dtype != s_arr.dtype else l * s_arr for l in loss]
+        else:
+            yield loss * (s_arr.astype(loss.dtype) if loss.dtype != s_arr.dtype else s_arr)
+        return
     s = scaler.loss_scale
     optimizer_or_trainer._scale = optimizer_or_trainer._amp_original_scale / s
     if isinstance(loss, (list, tuple)):

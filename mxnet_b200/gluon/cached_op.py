@@ -55,13 +55,18 @@ class _Graphed(object):
                 t.requires_grad_(True)
             self.static_in.append(t)
         self.grad_inputs = [t for t in self.static_in if t.requires_grad] + (self.param_tensors if recording else [])
+        from ..ops import cuda as _kernels
+        self._kernels = _kernels
         self.pool = torch.cuda.graph_pool_handle()
         self.fwd = torch.cuda.CUDAGraph()
+        n0 = _kernels.launches()
         stream = torch.cuda.Stream(device=dev)
         stream.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(stream):
             with torch.cuda.graph(self.fwd, pool=self.pool, stream=stream):
                 outs = self._run_forward()
+        self.fwd_launches = _kernels.launches() - n0     # in-tree kernels recorded in the forward graph
+        self.bwd_launches = 0
         flat_out, self.out_fmt = _flatten(outs, 'output')
         self.out_is_array = [isinstance(o, NDArray) for o in flat_out]
         self.flat_out_template = list(flat_out)
@@ -71,11 +76,13 @@ class _Graphed(object):
             self.out_needs_grad = [o.requires_grad for o in self.static_out]
             self.static_gout = [torch.zeros_like(o) if o.requires_grad else None for o in self.static_out]
             self.bwd = torch.cuda.CUDAGraph()
+            n1 = _kernels.launches()
             with torch.cuda.stream(stream):
                 with torch.cuda.graph(self.bwd, pool=self.pool, stream=stream):
                     gin = torch.autograd.grad([o for o in self.static_out if o.requires_grad], self.grad_inputs,
                                               [g for g in self.static_gout if g is not None], allow_unused=True)
             self.static_gin = list(gin)
+            self.bwd_launches = _kernels.launches() - n1
         torch.cuda.current_stream(dev).wait_stream(stream)
         self.static_out_detached = [o.detach() for o in self.static_out]
 
@@ -112,6 +119,7 @@ class _Graphed(object):
                     if dst.data_ptr() != src.data_ptr():
                         dst.copy_(src)
                 g.fwd.replay()
+                g._kernels.count_launch(g.fwd_launches)
                 return tuple(g.static_out_detached)
 
             @staticmethod
@@ -120,6 +128,7 @@ class _Graphed(object):
                     if dst is not None and src is not None and dst.data_ptr() != src.data_ptr():
                         dst.copy_(src)
                 g.bwd.replay()
+                g._kernels.count_launch(g.bwd_launches)
                 n_in = len(g.static_in)
                 res, k = [], 0
                 for t in g.static_in:
@@ -142,6 +151,7 @@ class _Graphed(object):
                 for dst, src in zip(self.static_in, tensors):
                     dst.copy_(src)
                 self.fwd.replay()
+                self._kernels.count_launch(self.fwd_launches)
                 outs = tuple(self.static_out_detached)
         flat_out, k = list(self.flat_out_template), 0
         for i, is_arr in enumerate(self.out_is_array):

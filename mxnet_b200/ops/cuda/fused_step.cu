@@ -1,0 +1,396 @@
+// Fused gradient reduce-scatter + AMP unscale + inf/nan check + sharded optimizer update + weight
+// all-gather over NVLink peer memory, as two kernel launches per training step.
+//
+// What the reference does per step (python/mxnet/gluon/trainer.py:392-486, src/kvstore/kvstore_nccl.h:212-425,
+// src/kvstore/comm.h:535-654): one pushpull per parameter (ncclReduce to a root GPU, or P2P gather +
+// ElementwiseSum), a multi_all_finite pass with a blocking host read, multi_mp_sgd_mom_update launches of
+// at most 60 tensors, then ncclBcast / P2P copies of the weights.
+//
+// Here all parameters of a process live in one flat arena per GPU (weights, and gradients with the same
+// layout).  Rank r owns the contiguous shard r of the arena together with the fp32 master weights and
+// optimizer state of that shard only.
+//   kernel A (reduce):  waits until every rank has finished its backward pass, then each rank sums ITS
+//                       shard of the gradients by loading it from all ranks' arenas (plain 16-byte peer
+//                       loads over NVSwitch), scales by rescale/loss_scale, records inf/nan and the sum of
+//                       squares, keeps the reduced shard in fp32, and publishes {nonfinite, sumsq} to all ranks.
+//   kernel B (update):  waits for all ranks' results, decides the step globally (skip on overflow, global-norm
+//                       clipping coefficient), applies SGD-momentum / NAG on the fp32 master shard, writes the
+//                       new low-precision weights into EVERY rank's weight arena (peer stores = all-gather),
+//                       clears the local gradient arena, adapts the loss scale on the device, and returns
+//                       only after all ranks have finished writing.
+// Synchronisation is by step-numbered flags in a control block of every rank that peers write with
+// st.release.sys and the owner polls with ld.acquire.sys.  Every wait is bounded by a wall-clock budget; when
+// it expires the kernel records an error code in the control block, publishes "nonfinite" so that no rank
+// applies a partial update, and returns normally (no trap, the context stays usable).
+// Ranks run as separate processes on separate GPUs; the kernels never wait on another launch of the same GPU.
+#include "common.cuh"
+
+namespace mxb {
+
+constexpr int kMaxRanks = 8;
+
+enum StepMode { kModeSGD = 0, kModeNAG = 1, kModePlain = 2 };
+enum StepError { kOk = 0, kErrWaitReady = 1, kErrWaitReduced = 2, kErrWaitGather = 3 };
+
+struct __align__(256) Ctrl {
+  // written by peers (index = sender rank)
+  uint32_t ready[kMaxRanks];
+  uint32_t reduced[kMaxRanks];
+  uint32_t agdone[kMaxRanks];
+  float payload[kMaxRanks][4];
+  // local
+  uint32_t ticket_a, ticket_b;
+  uint32_t nonfinite;
+  float sumsq;
+  uint32_t status;          // first StepError seen (sticky until the host clears it)
+  uint32_t status_step;
+  float scale_state[4];     // [loss scale, clean steps, skipped steps total, last global grad norm]
+};
+
+struct StepParams {
+  const void* grads[kMaxRanks];     // gradient arenas of all ranks (own entry = local pointer)
+  void* weights[kMaxRanks];         // weight arenas of all ranks
+  Ctrl* ctrl[kMaxRanks];
+  int rank, nranks;
+  int64_t total;                    // arena length in elements (multiple of 8)
+  int64_t shard_begin, shard_end;   // this rank's shard [begin, end) in elements (multiples of 8)
+  float* gred;                      // fp32 reduced gradient of the shard
+  float* master;                    // fp32 master weights of the shard (null when weights are fp32)
+  float* mom;                       // momentum of the shard (null when momentum == 0)
+  const int64_t* seg_end;           // per-parameter end offsets in the arena (sorted)
+  const float* lr_mult;             // per-parameter multipliers
+  const float* wd_mult;
+  int nseg;
+  uint32_t step;
+  float rescale;                    // host part of the gradient scale (1 / batch size ...)
+  int use_loss_scale;               // 0 off, 1 divide by scale_state[0] and adapt it, 2 adapt only
+  float lr, wd, momentum, clip_gradient, max_norm;
+  float scale_window, scale_max;
+  int mode;
+  unsigned long long timeout_ns;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Threads 0..n-1 of the CTA each poll one flag until it reaches `step`; returns false on time-out.
+__device__ bool wait_flags(const uint32_t* flags, int n, uint32_t step, unsigned long long timeout_ns) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < n) {
+    const unsigned long long t0 = now_ns();
+    unsigned spins = 0;
+    while ((int32_t)(ld_acquire_sys(flags + threadIdx.x) - step) < 0) {
+      if ((++spins & 63u) == 0) {
+        if (now_ns() - t0 > timeout_ns) { ok = 0; break; }
+        __nanosleep(200);
+      }
+    }
+  }
+  __syncthreads();
+  return ok != 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) fused_reduce_kernel(const __grid_constant__ StepParams p) {
+  __shared__ float red[32];
+  Ctrl* me = p.ctrl[p.rank];
+  bool alive = true;
+  if (p.nranks > 1) {
+    if (blockIdx.x == 0 && threadIdx.x < p.nranks) st_release_sys(&p.ctrl[threadIdx.x]->ready[p.rank], p.step);
+    alive = wait_flags(me->ready, p.nranks, p.step, p.timeout_ns);
+    if (!alive && threadIdx.x == 0) { atomicCAS(&me->status, (uint32_t)kOk, (uint32_t)kErrWaitReady); me->status_step = p.step; }
+  }
+  float sumsq = 0.f;
+  bool bad = !alive;
+  if (alive) {
+    float scale = p.rescale;
+    if (p.use_loss_scale == 1) scale /= me->scale_state[0];   // 2: the host already folded 1/scale into rescale
+    constexpr int N = Vec16<T>::N;
+    const int64_t v0 = p.shard_begin / N, v1 = p.shard_end / N;
+    for (int64_t v = v0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < v1; v += (int64_t)gridDim.x * blockDim.x) {
+      Vec16<T> in[kMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < p.nranks) in[r] = ld16((const T*)p.grads[r] + v * N);
+      float acc[N];
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < p.nranks) {
+#pragma unroll
+          for (int j = 0; j < N; ++j) acc[j] += Cvt<T>::to_f(in[r].v[j]);
+        }
+      float* out = p.gred + (v * N - p.shard_begin);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        acc[j] *= scale;
+        bad |= !isfinite(acc[j]);
+        sumsq += acc[j] * acc[j];
+      }
+#pragma unroll
+      for (int j = 0; j < N; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+    }
+  }
+  sumsq = block_sum(sumsq, red);
+  const int any_bad = __syncthreads_or(bad ? 1 : 0);
+  if (threadIdx.x == 0) {
+    if (any_bad) atomicOr(&me->nonfinite, 1u);
+    atomicAdd(&me->sumsq, sumsq);
+    __threadfence();
+    const uint32_t ticket = atomicAdd(&me->ticket_a, 1u);
+    if (ticket == gridDim.x - 1) {           // last CTA of this rank: publish the shard's summary
+      __threadfence();
+      const float nf = (float)atomicOr(&me->nonfinite, 0u);
+      const float sq = atomicAdd(&me->sumsq, 0.f);
+      for (int r = 0; r < p.nranks; ++r) {
+        volatile float* dst = p.ctrl[r]->payload[p.rank];
+        dst[0] = nf;
+        dst[1] = sq;
+      }
+      __threadfence_system();
+      for (int r = 0; r < p.nranks; ++r) st_release_sys(&p.ctrl[r]->reduced[p.rank], p.step);
+      me->nonfinite = 0u;
+      me->sumsq = 0.f;
+      me->ticket_a = 0u;
+    }
+  }
+}
+
+__device__ __forceinline__ int find_segment(const int64_t* seg_end, int nseg, int64_t elem) {
+  int lo = 0, hi = nseg - 1;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (seg_end[mid] > elem) hi = mid; else lo = mid + 1;
+  }
+  return lo;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) fused_update_kernel(const __grid_constant__ StepParams p) {
+  Ctrl* me = p.ctrl[p.rank];
+  constexpr int N = Vec16<T>::N;
+  bool alive = wait_flags(me->reduced, p.nranks, p.step, p.timeout_ns);
+  if (!alive && threadIdx.x == 0) { atomicCAS(&me->status, (uint32_t)kOk, (uint32_t)kErrWaitReduced); me->status_step = p.step; }
+  float nonfinite = 0.f, sumsq = 0.f;
+  for (int r = 0; r < p.nranks; ++r) {
+    volatile float* src = me->payload[r];
+    nonfinite += src[0];
+    sumsq += src[1];
+  }
+  const bool skip = !alive || (nonfinite != 0.f);
+  float coef = 1.f;
+  if (p.max_norm > 0.f) coef = fminf(1.f, p.max_norm / (sqrtf(sumsq) + 1e-8f));
+  if (!skip) {
+    const int64_t v0 = p.shard_begin / N, v1 = p.shard_end / N;
+    for (int64_t v = v0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < v1; v += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t e = v * N, le = e - p.shard_begin;
+      float g[N];
+#pragma unroll
+      for (int j = 0; j < N; j += 4) {
+        float4 t = *reinterpret_cast<const float4*>(p.gred + le + j);
+        g[j] = t.x; g[j + 1] = t.y; g[j + 2] = t.z; g[j + 3] = t.w;
+      }
+      Vec16<T> out;
+      if (p.mode == kModePlain) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) out.v[j] = Cvt<T>::from_f(g[j]);
+        for (int r = 0; r < p.nranks; ++r) st16((T*)p.grads[r] + e, out);     // all-gather of the reduced gradient
+        continue;
+      }
+      const int seg = find_segment(p.seg_end, p.nseg, e);
+      const float lr = p.lr * p.lr_mult[seg], wd = p.wd * p.wd_mult[seg];
+      float w[N], m[N];
+      if (p.master) {
+#pragma unroll
+        for (int j = 0; j < N; j += 4) {
+          float4 t = *reinterpret_cast<const float4*>(p.master + le + j);
+          w[j] = t.x; w[j + 1] = t.y; w[j + 2] = t.z; w[j + 3] = t.w;
+        }
+      } else {
+        Vec16<T> cur = ld16((const T*)p.weights[p.rank] + e);
+#pragma unroll
+        for (int j = 0; j < N; ++j) w[j] = Cvt<T>::to_f(cur.v[j]);
+      }
+      if (p.mom) {
+#pragma unroll
+        for (int j = 0; j < N; j += 4) {
+          float4 t = *reinterpret_cast<const float4*>(p.mom + le + j);
+          m[j] = t.x; m[j + 1] = t.y; m[j + 2] = t.z; m[j + 3] = t.w;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        float gr = g[j] * coef;
+        if (p.clip_gradient >= 0.f) gr = fminf(fmaxf(gr, -p.clip_gradient), p.clip_gradient);
+        gr += wd * w[j];
+        if (p.mom) {
+          m[j] = p.momentum * m[j] - lr * gr;
+          w[j] += (p.mode == kModeNAG) ? (p.momentum * m[j] - lr * gr) : m[j];
+        } else {
+          w[j] -= lr * gr;
+        }
+        out.v[j] = Cvt<T>::from_f(w[j]);
+      }
+      if (p.master) {
+#pragma unroll
+        for (int j = 0; j < N; j += 4) *reinterpret_cast<float4*>(p.master + le + j) = make_float4(w[j], w[j + 1], w[j + 2], w[j + 3]);
+      }
+      if (p.mom) {
+#pragma unroll
+        for (int j = 0; j < N; j += 4) *reinterpret_cast<float4*>(p.mom + le + j) = make_float4(m[j], m[j + 1], m[j + 2], m[j + 3]);
+      }
+      for (int r = 0; r < p.nranks; ++r) st16((T*)p.weights[r] + e, out);       // all-gather of the new weights
+    }
+  }
+  if (p.mode != kModePlain) {
+    // every rank has finished reading this arena (all `reduced` flags seen): clear it for the next backward
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    T* ga = (T*)p.grads[p.rank];
+    const int64_t nv = p.total / N;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (int64_t)gridDim.x * blockDim.x)
+      *reinterpret_cast<uint4*>(ga + v * N) = z;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t ticket = atomicAdd(&me->ticket_b, 1u);
+    if (ticket == gridDim.x - 1) {
+      __threadfence();
+      me->scale_state[3] = sqrtf(sumsq);
+      if (p.use_loss_scale && p.mode != kModePlain) {
+        float s = me->scale_state[0], good = me->scale_state[1];
+        if (skip) { s = fmaxf(s * 0.5f, 1.f); good = 0.f; me->scale_state[2] += 1.f; }
+        else {
+          good += 1.f;
+          if (good >= p.scale_window) { s = fminf(s * 2.f, p.scale_max); good = 0.f; }
+        }
+        me->scale_state[0] = s;
+        me->scale_state[1] = good;
+      } else if (skip && p.mode != kModePlain) {
+        me->scale_state[2] += 1.f;
+      }
+      me->ticket_b = 0u;
+      if (p.nranks > 1) {
+        __threadfence_system();
+        for (int r = 0; r < p.nranks; ++r) st_release_sys(&p.ctrl[r]->agdone[p.rank], p.step);
+        // do not return before every rank's stores into this GPU's arena have landed
+        const unsigned long long t0 = now_ns();
+        for (int r = 0; r < p.nranks; ++r) {
+          unsigned spins = 0;
+          while ((int32_t)(ld_acquire_sys(&me->agdone[r]) - p.step) < 0) {
+            if ((++spins & 63u) == 0) {
+              if (now_ns() - t0 > p.timeout_ns) {
+                atomicCAS(&me->status, (uint32_t)kOk, (uint32_t)kErrWaitGather);
+                me->status_step = p.step;
+                r = p.nranks;
+                break;
+              }
+              __nanosleep(200);
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
+// A wait that nothing satisfies: used by tests of the time-out path (flag index `slot` of `ready`).
+__global__ void wait_probe_kernel(Ctrl* me, int slot, uint32_t step, unsigned long long timeout_ns) {
+  bool ok = wait_flags(me->ready + slot, 1, step, timeout_ns);
+  if (!ok && threadIdx.x == 0) { atomicCAS(&me->status, (uint32_t)kOk, (uint32_t)kErrWaitReady); me->status_step = step; }
+}
+
+}  // namespace mxb
+
+using namespace mxb;
+
+MXB_EXPORT int mxb_step_ctrl_bytes() { return (int)sizeof(Ctrl); }
+MXB_EXPORT int mxb_step_params_bytes() { return (int)sizeof(StepParams); }
+MXB_EXPORT int mxb_step_max_ranks() { return kMaxRanks; }
+// byte offsets inside Ctrl the host needs: status, status_step, scale_state
+MXB_EXPORT int mxb_step_ctrl_offset(int which) {
+  switch (which) {
+    case 0: return (int)offsetof(Ctrl, status);
+    case 1: return (int)offsetof(Ctrl, status_step);
+    case 2: return (int)offsetof(Ctrl, scale_state);
+    default: return -1;
+  }
+}
+
+static int step_grid(int64_t shard_elems, int64_t total, int n_per_vec) {
+  int64_t vecs = (shard_elems > total / 4 ? shard_elems : total / 4) / n_per_vec;
+  int64_t blocks = (vecs + 255) / 256;
+  int cap = sm_count() * 2;
+  if (blocks < 1) blocks = 1;
+  return (int)(blocks < cap ? blocks : cap);
+}
+
+// `params` is a host copy of StepParams filled by the caller.  dtype: storage type of the arenas.
+MXB_EXPORT int mxb_fused_reduce(int dtype, const void* params, void* stream) {
+  StepParams p = *static_cast<const StepParams*>(params);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (p.nranks < 1 || p.nranks > kMaxRanks) return -2;
+  if (dtype == kF32) fused_reduce_kernel<float><<<step_grid(p.shard_end - p.shard_begin, 0, 4), 256, 0, st>>>(p);
+  else if (dtype == kF16) fused_reduce_kernel<__half><<<step_grid(p.shard_end - p.shard_begin, 0, 8), 256, 0, st>>>(p);
+  else if (dtype == kBF16) fused_reduce_kernel<__nv_bfloat16><<<step_grid(p.shard_end - p.shard_begin, 0, 8), 256, 0, st>>>(p);
+  else return -1;
+  return (int)cudaGetLastError();
+}
+
+MXB_EXPORT int mxb_fused_update(int dtype, const void* params, void* stream) {
+  StepParams p = *static_cast<const StepParams*>(params);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (p.nranks < 1 || p.nranks > kMaxRanks) return -2;
+  if (dtype == kF32) fused_update_kernel<float><<<step_grid(p.shard_end - p.shard_begin, p.total, 4), 256, 0, st>>>(p);
+  else if (dtype == kF16) fused_update_kernel<__half><<<step_grid(p.shard_end - p.shard_begin, p.total, 8), 256, 0, st>>>(p);
+  else if (dtype == kBF16) fused_update_kernel<__nv_bfloat16><<<step_grid(p.shard_end - p.shard_begin, p.total, 8), 256, 0, st>>>(p);
+  else return -1;
+  return (int)cudaGetLastError();
+}
+
+MXB_EXPORT int mxb_wait_probe(void* ctrl, int slot, uint32_t step, unsigned long long timeout_ns, void* stream) {
+  wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(static_cast<Ctrl*>(ctrl), slot, step, timeout_ns);
+  return (int)cudaGetLastError();
+}
+
+// ---- peer-memory plumbing -------------------------------------------------------------------------------
+MXB_EXPORT int mxb_dev_alloc(void** ptr, uint64_t bytes) {
+  int rc = (int)cudaMalloc(ptr, bytes);
+  if (rc == 0) rc = (int)cudaMemset(*ptr, 0, bytes);
+  return rc;
+}
+MXB_EXPORT int mxb_dev_free(void* ptr) { return (int)cudaFree(ptr); }
+MXB_EXPORT int mxb_ipc_handle_bytes() { return (int)sizeof(cudaIpcMemHandle_t); }
+MXB_EXPORT int mxb_ipc_get_handle(void* ptr, void* out) {
+  cudaIpcMemHandle_t h;
+  int rc = (int)cudaIpcGetMemHandle(&h, ptr);
+  if (rc == 0) memcpy(out, &h, sizeof(h));
+  return rc;
+}
+MXB_EXPORT int mxb_ipc_open(const void* handle, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  return (int)cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+}
+MXB_EXPORT int mxb_ipc_close(void* ptr) { return (int)cudaIpcCloseMemHandle(ptr); }
+MXB_EXPORT int mxb_memcpy_d2h(void* dst, const void* src, uint64_t bytes, void* stream) {
+  return (int)cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+}
+MXB_EXPORT int mxb_memcpy_h2d(void* dst, const void* src, uint64_t bytes, void* stream) {
+  return (int)cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream);
+}
+MXB_EXPORT const char* mxb_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }

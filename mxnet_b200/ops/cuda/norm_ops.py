@@ -1,0 +1,115 @@
+"""BatchNorm (NHWC, fused ReLU/residual) and LayerNorm on the sm_100a kernels (``norm.cu``)."""
+import torch
+
+from . import lib, ptr, stream_ptr, count_launch, check
+from ._util import dt, f32
+
+
+def bn_supported(x):
+    c = x.shape[-1]
+    l = c // 8
+    return c % 8 == 0 and 1 <= l <= 256 and (l & (l - 1)) == 0 and x.numel() > 0
+
+
+class _BatchNormNHWC(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gamma, beta, rmean, rvar, residual, eps, momentum, training, relu):
+        L = lib()
+        C = x.shape[-1]
+        M = x.numel() // C
+        grid = L.mxb_bn_grid(M, C)
+        scratch = torch.empty((grid * 2 + 3) * C, dtype=torch.float32, device=x.device)
+        save_mean = torch.empty(C, dtype=torch.float32, device=x.device)
+        save_invstd = torch.empty(C, dtype=torch.float32, device=x.device)
+        y = torch.empty_like(x)
+        g32, b32 = f32(gamma), f32(beta)
+        res = residual.contiguous() if residual is not None else None
+        check(L.mxb_bn_forward(dt(x), ptr(x), ptr(res), ptr(g32), ptr(b32), ptr(rmean), ptr(rvar), ptr(save_mean),
+                               ptr(save_invstd), ptr(scratch), ptr(y), M, C, eps, momentum, 1 if training else 0,
+                               1 if relu else 0, stream_ptr(x.device)), 'bn_forward')
+        count_launch(3 if training else 2)
+        ctx.save_for_backward(x, y if relu else None, g32, save_mean, save_invstd)
+        ctx.relu, ctx.has_res, ctx.training = relu, residual is not None, training
+        ctx.gdtype, ctx.bdtype = gamma.dtype, beta.dtype
+        ctx.mark_non_differentiable(save_mean, save_invstd)
+        return y, save_mean, save_invstd
+
+    @staticmethod
+    def backward(ctx, dy, _gm, _gv):
+        x, y, g32, save_mean, save_invstd = ctx.saved_tensors
+        L = lib()
+        C = x.shape[-1]
+        M = x.numel() // C
+        dy = dy.contiguous()
+        if not ctx.training:
+            # inference statistics are constants: dx = dy' * gamma * invstd
+            d = dy
+            if ctx.relu:
+                d = d * (y > 0).to(d.dtype)
+            scale = (g32 * save_invstd).to(d.dtype)
+            dx = d * scale
+            xh = (x.float() - save_mean) * save_invstd
+            dgamma = (d.float() * xh).reshape(-1, C).sum(0)
+            dbeta = d.float().reshape(-1, C).sum(0)
+            return dx, dgamma.to(ctx.gdtype), dbeta.to(ctx.bdtype), None, None, (d if ctx.has_res else None), None, None, None, None
+        grid = L.mxb_bn_grid(M, C)
+        scratch = torch.empty((grid * 2 + 3) * C, dtype=torch.float32, device=x.device)
+        dx = torch.empty_like(x)
+        dres = torch.empty_like(x) if ctx.has_res else None
+        dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
+        dbeta = torch.empty(C, dtype=torch.float32, device=x.device)
+        check(L.mxb_bn_backward(dt(x), ptr(x), ptr(dy), ptr(y), ptr(g32), ptr(save_mean), ptr(save_invstd), ptr(scratch),
+                                ptr(dx), ptr(dres), ptr(dgamma), ptr(dbeta), M, C, 1 if ctx.relu else 0,
+                                stream_ptr(x.device)), 'bn_backward')
+        count_launch(3)
+        return dx, dgamma.to(ctx.gdtype), dbeta.to(ctx.bdtype), None, None, dres, None, None, None, None
+
+
+def batch_norm_nhwc(x, gamma, beta, rmean, rvar, eps, momentum, training, act_type, residual):
+    """Returns (y, mean, var) like the BatchNorm operator with ``output_mean_var``."""
+    y, mean, invstd = _BatchNormNHWC.apply(x, gamma, beta, rmean, rvar, residual, float(eps), float(momentum),
+                                           bool(training), act_type == 'relu')
+    var = 1.0 / (invstd * invstd) - eps
+    return y, mean, var
+
+
+def ln_supported(x):
+    return x.shape[-1] <= 2048 and x.numel() > 0
+
+
+class _LayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps):
+        L = lib()
+        C = x.shape[-1]
+        rows = x.numel() // C
+        y = torch.empty_like(x)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        g32, b32 = f32(gamma), f32(beta)
+        check(L.mxb_ln_forward(dt(x), ptr(x), ptr(g32), ptr(b32), ptr(y), ptr(mean), ptr(rstd), rows, C, eps,
+                               stream_ptr(x.device)), 'ln_forward')
+        count_launch(1)
+        ctx.save_for_backward(x, g32, mean, rstd)
+        ctx.gdtype, ctx.bdtype = gamma.dtype, beta.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, g32, mean, rstd = ctx.saved_tensors
+        L = lib()
+        C = x.shape[-1]
+        rows = x.numel() // C
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
+        dbeta = torch.empty(C, dtype=torch.float32, device=x.device)
+        scratch = torch.empty(L.mxb_ln_grid(rows) * 2 * C, dtype=torch.float32, device=x.device)
+        check(L.mxb_ln_backward(dt(x), ptr(x), ptr(dy), ptr(g32), ptr(mean), ptr(rstd), ptr(dx), ptr(dgamma), ptr(dbeta),
+                                ptr(scratch), rows, C, stream_ptr(x.device)), 'ln_backward')
+        count_launch(2)
+        return dx, dgamma.to(ctx.gdtype), dbeta.to(ctx.bdtype), None
+
+
+def layer_norm(x, gamma, beta, eps):
+    return _LayerNorm.apply(x, gamma, beta, float(eps))

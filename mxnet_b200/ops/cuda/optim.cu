@@ -1,0 +1,216 @@
+// Multi-tensor optimizer and reduction kernels for sm_100a.
+//
+// Reference behaviour: MultiSGDKernel (src/operator/optimizer_op-inl.h:201-250, at most 60 tensors
+// per launch), multi_all_finite (src/operator/all_finite.cu), multi_sum_sq
+// (src/operator/contrib/multi_sum_sq.cu).  The tensor table travels as a kernel argument (no
+// per-call host-to-device table copy, so launches are CUDA-graph capturable); work is split into
+// fixed-size chunks and every CTA walks chunks with a grid-stride loop, finding the owning tensor by
+// binary search over the chunk prefix sums.
+#include "common.cuh"
+
+namespace mxb {
+
+constexpr int kMaxTensors = 48;
+constexpr int kChunk = 8192;          // elements per chunk
+
+struct TensorTable {
+  void* w[kMaxTensors];               // weights (out)
+  const void* g[kMaxTensors];         // gradients
+  float* m[kMaxTensors];              // momentum (or null)
+  float* w32[kMaxTensors];            // fp32 master weights (or null)
+  float lr[kMaxTensors];
+  float wd[kMaxTensors];
+  int64_t n[kMaxTensors];
+  int chunk_start[kMaxTensors + 1];   // prefix sums of chunk counts
+  int count;
+};
+
+__device__ __forceinline__ int find_tensor(const int* chunk_start, int count, int chunk) {
+  int lo = 0, hi = count - 1;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (chunk_start[mid] <= chunk) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+// T: storage type of weights/gradients; master weights and momentum are fp32.
+template <typename T, bool kMom, bool kMP>
+__global__ void __launch_bounds__(256)
+multi_sgd_kernel(const __grid_constant__ TensorTable tab, float momentum, float rescale, float clip) {
+  const int total = tab.chunk_start[tab.count];
+  for (int chunk = blockIdx.x; chunk < total; chunk += gridDim.x) {
+    const int t = find_tensor(tab.chunk_start, tab.count, chunk);
+    const int64_t base = (int64_t)(chunk - tab.chunk_start[t]) * kChunk;
+    const int64_t n = tab.n[t];
+    T* w = (T*)tab.w[t];
+    const T* g = (const T*)tab.g[t];
+    float* m = tab.m[t];
+    float* w32 = tab.w32[t];
+    const float lr = tab.lr[t], wd = tab.wd[t];
+    for (int64_t i = base + threadIdx.x; i < base + kChunk && i < n; i += blockDim.x) {
+      float gr = Cvt<T>::to_f(g[i]) * rescale;
+      if (clip >= 0.f) gr = fminf(fmaxf(gr, -clip), clip);
+      float wv = kMP ? w32[i] : Cvt<T>::to_f(w[i]);
+      gr += wd * wv;
+      if (kMom) {
+        float mv = momentum * m[i] - lr * gr;
+        m[i] = mv;
+        wv += mv;
+      } else {
+        wv -= lr * gr;
+      }
+      if (kMP) w32[i] = wv;
+      w[i] = Cvt<T>::from_f(wv);
+    }
+  }
+}
+
+struct PtrTable {
+  const void* p[kMaxTensors];
+  int64_t n[kMaxTensors];
+  int dtype[kMaxTensors];
+  int chunk_start[kMaxTensors + 1];
+  int count;
+};
+
+__device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t i) {
+  if (dtype == kF32) return ((const float*)p)[i];
+  if (dtype == kF16) return __half2float(((const __half*)p)[i]);
+  return __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+
+// out[0] is multiplied towards 0 when any element is inf/nan (caller initialises it to 1).
+__global__ void __launch_bounds__(256) multi_all_finite_kernel(const __grid_constant__ PtrTable tab, float* out) {
+  const int total = tab.chunk_start[tab.count];
+  bool bad = false;
+  for (int chunk = blockIdx.x; chunk < total; chunk += gridDim.x) {
+    const int t = find_tensor(tab.chunk_start, tab.count, chunk);
+    const int64_t base = (int64_t)(chunk - tab.chunk_start[t]) * kChunk;
+    const int64_t n = tab.n[t];
+    for (int64_t i = base + threadIdx.x; i < base + kChunk && i < n; i += blockDim.x) {
+      float v = load_as_float(tab.p[t], tab.dtype[t], i);
+      bad |= !isfinite(v);
+    }
+  }
+  if (__syncthreads_or(bad) && threadIdx.x == 0) out[0] = 0.f;
+}
+
+// Stage 1 of sum of squares: one partial per (chunk); stage 2 sums the partials of each tensor in
+// chunk order, so the result does not depend on the grid size.
+__global__ void __launch_bounds__(256) multi_sum_sq_partial_kernel(const __grid_constant__ PtrTable tab, float* partial) {
+  __shared__ float red[32];
+  const int total = tab.chunk_start[tab.count];
+  for (int chunk = blockIdx.x; chunk < total; chunk += gridDim.x) {
+    const int t = find_tensor(tab.chunk_start, tab.count, chunk);
+    const int64_t base = (int64_t)(chunk - tab.chunk_start[t]) * kChunk;
+    const int64_t n = tab.n[t];
+    float s = 0.f;
+    for (int64_t i = base + threadIdx.x; i < base + kChunk && i < n; i += blockDim.x) {
+      float v = load_as_float(tab.p[t], tab.dtype[t], i);
+      s += v * v;
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) partial[chunk] = s;
+  }
+}
+
+__global__ void multi_sum_sq_final_kernel(const __grid_constant__ PtrTable tab, const float* partial, float* out, int out_offset) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  float s = 0.f;
+  for (int c = tab.chunk_start[t] + threadIdx.x; c < tab.chunk_start[t + 1]; c += blockDim.x) s += partial[c];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) out[out_offset + t] = s;
+}
+
+__global__ void set_float_kernel(float* p, float v) { *p = v; }
+
+inline int chunks_of(int64_t n) { return (int)((n + kChunk - 1) / kChunk); }
+
+}  // namespace mxb
+
+using namespace mxb;
+
+MXB_EXPORT int mxb_max_tensors() { return kMaxTensors; }
+MXB_EXPORT int mxb_chunk_elems() { return kChunk; }
+
+// dtype: storage type of weights and gradients.  moms / w32 may be null arrays.
+MXB_EXPORT int mxb_multi_sgd(int dtype, int count, void** w, void** g, float** m, float** w32, const float* lrs,
+                             const float* wds, const int64_t* sizes, float momentum, float rescale, float clip,
+                             void* stream) {
+  if (count > kMaxTensors || count <= 0) return -2;
+  TensorTable tab;
+  tab.count = count;
+  int acc = 0;
+  for (int i = 0; i < count; ++i) {
+    tab.w[i] = w[i]; tab.g[i] = g[i];
+    tab.m[i] = m ? m[i] : nullptr;
+    tab.w32[i] = w32 ? w32[i] : nullptr;
+    tab.lr[i] = lrs[i]; tab.wd[i] = wds[i]; tab.n[i] = sizes[i];
+    tab.chunk_start[i] = acc;
+    acc += chunks_of(sizes[i]);
+  }
+  tab.chunk_start[count] = acc;
+  int grid = acc < sm_count() * 8 ? acc : sm_count() * 8;
+  if (grid < 1) grid = 1;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool mom = m != nullptr, mp = w32 != nullptr;
+#define LAUNCH(T)                                                                                         \
+  if (mom && mp) multi_sgd_kernel<T, true, true><<<grid, 256, 0, st>>>(tab, momentum, rescale, clip);        \
+  else if (mom) multi_sgd_kernel<T, true, false><<<grid, 256, 0, st>>>(tab, momentum, rescale, clip);        \
+  else if (mp) multi_sgd_kernel<T, false, true><<<grid, 256, 0, st>>>(tab, momentum, rescale, clip);         \
+  else multi_sgd_kernel<T, false, false><<<grid, 256, 0, st>>>(tab, momentum, rescale, clip);
+  if (dtype == kF32) { LAUNCH(float) }
+  else if (dtype == kF16) { LAUNCH(__half) }
+  else if (dtype == kBF16) { LAUNCH(__nv_bfloat16) }
+  else return -1;
+#undef LAUNCH
+  return (int)cudaGetLastError();
+}
+
+static int fill_ptr_table(PtrTable* tab, int count, void** p, const int64_t* sizes, const int* dtypes) {
+  tab->count = count;
+  int acc = 0;
+  for (int i = 0; i < count; ++i) {
+    tab->p[i] = p[i]; tab->n[i] = sizes[i]; tab->dtype[i] = dtypes[i];
+    tab->chunk_start[i] = acc;
+    acc += chunks_of(sizes[i]);
+  }
+  tab->chunk_start[count] = acc;
+  return acc;
+}
+
+// out: one float, set to 1 by this call and cleared to 0 by the kernel when a non-finite value is found.
+MXB_EXPORT int mxb_multi_all_finite(int count, void** p, const int64_t* sizes, const int* dtypes, float* out, int init,
+                                    void* stream) {
+  if (count > kMaxTensors || count <= 0) return -2;
+  PtrTable tab;
+  int acc = fill_ptr_table(&tab, count, p, sizes, dtypes);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (init) set_float_kernel<<<1, 1, 0, st>>>(out, 1.f);
+  int grid = acc < sm_count() * 8 ? acc : sm_count() * 8;
+  if (grid < 1) grid = 1;
+  multi_all_finite_kernel<<<grid, 256, 0, st>>>(tab, out);
+  return (int)cudaGetLastError();
+}
+
+// Total chunk count for a set of sizes: the caller provides a scratch buffer of that many floats.
+MXB_EXPORT int mxb_sum_sq_chunks(int count, const int64_t* sizes) {
+  int acc = 0;
+  for (int i = 0; i < count; ++i) acc += chunks_of(sizes[i]);
+  return acc;
+}
+
+MXB_EXPORT int mxb_multi_sum_sq(int count, void** p, const int64_t* sizes, const int* dtypes, float* scratch, float* out,
+                                int out_offset, void* stream) {
+  if (count > kMaxTensors || count <= 0) return -2;
+  PtrTable tab;
+  int acc = fill_ptr_table(&tab, count, p, sizes, dtypes);
+  cudaStream_t st = (cudaStream_t)stream;
+  int grid = acc < sm_count() * 8 ? acc : sm_count() * 8;
+  if (grid < 1) grid = 1;
+  multi_sum_sq_partial_kernel<<<grid, 256, 0, st>>>(tab, scratch);
+  multi_sum_sq_final_kernel<<<count, 128, 0, st>>>(tab, scratch, out, out_offset);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,56 @@
+"""Multi-tensor optimizer / reduction launches (``optim.cu``)."""
+import ctypes as C
+
+import torch
+
+from . import lib, ptr, stream_ptr, count_launch, check
+from ._util import DT
+
+
+def _parr(tensors):
+    return (C.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
+def multi_sgd(ws, gs, moms, w32, lrs, wds, momentum, rescale, clip):
+    L = lib()
+    cap = L.mxb_max_tensors()
+    dtype = ws[0].dtype
+    for i in range(0, len(ws), cap):
+        sl = slice(i, i + cap)
+        w, g = ws[sl], gs[sl]
+        n = len(w)
+        m = _parr(moms[sl]) if moms is not None else None
+        mp = _parr(w32[sl]) if w32 is not None else None
+        check(L.mxb_multi_sgd(DT[dtype], n, _parr(w), _parr(g), m, mp, (C.c_float * n)(*lrs[sl]), (C.c_float * n)(*wds[sl]),
+                              (C.c_int64 * n)(*[t.numel() for t in w]), float(momentum), float(rescale),
+                              float(-1.0 if clip is None else clip), stream_ptr(w[0].device)), 'multi_sgd')
+        count_launch(1)
+
+
+def multi_all_finite(tensors):
+    L = lib()
+    cap = L.mxb_max_tensors()
+    out = torch.empty(1, dtype=torch.float32, device=tensors[0].device)
+    for i in range(0, len(tensors), cap):
+        ts = [t if t.is_contiguous() else t.contiguous() for t in tensors[i:i + cap]]
+        n = len(ts)
+        check(L.mxb_multi_all_finite(n, _parr(ts), (C.c_int64 * n)(*[t.numel() for t in ts]),
+                                     (C.c_int * n)(*[DT[t.dtype] for t in ts]), ptr(out), 1 if i == 0 else 0,
+                                     stream_ptr(out.device)), 'multi_all_finite')
+        count_launch(2 if i == 0 else 1)
+    return out
+
+
+def multi_sum_sq(tensors):
+    L = lib()
+    cap = L.mxb_max_tensors()
+    out = torch.empty(len(tensors), dtype=torch.float32, device=tensors[0].device)
+    for i in range(0, len(tensors), cap):
+        ts = [t if t.is_contiguous() else t.contiguous() for t in tensors[i:i + cap]]
+        n = len(ts)
+        sizes = (C.c_int64 * n)(*[t.numel() for t in ts])
+        scratch = torch.empty(max(1, L.mxb_sum_sq_chunks(n, sizes)), dtype=torch.float32, device=out.device)
+        check(L.mxb_multi_sum_sq(n, _parr(ts), sizes, (C.c_int * n)(*[DT[t.dtype] for t in ts]), ptr(scratch), ptr(out), i,
+                                 stream_ptr(out.device)), 'multi_sum_sq')
+        count_launch(2)
+    return out

@@ -1,0 +1,353 @@
+"""Fused data-parallel optimizer step over peer memory (host side of ``ops/cuda/fused_step.cu``).
+
+Replaces the per-parameter ``pushpull`` + ``multi_all_finite`` + ``multi_mp_sgd_mom_update`` + broadcast
+sequence of the reference Trainer (``python/mxnet/gluon/trainer.py:392-486``) by two kernel launches
+per step, with no NCCL call and no host synchronisation:
+
+* all trainable parameters of the process are re-homed into one flat *weight arena* and their
+  gradients into a *gradient arena* of identical layout (16-byte aligned segments), allocated with
+  ``cudaMalloc`` so the memory can be opened by the other ranks through CUDA IPC;
+* rank ``r`` owns shard ``r`` of the arena: fp32 master weights and momentum exist for that shard
+  only (optimizer state memory is divided by the number of GPUs);
+* ``step`` launches the reduce kernel (sum of this rank's shard over all ranks' gradient arenas,
+  unscale, inf/nan + sum-of-squares) and the update kernel (global skip/clip decision, SGD-momentum or
+  NAG on the master shard, new low-precision weights stored into every rank's arena, gradient arena
+  cleared, loss scale adapted on the device).
+
+The host only advances the step counter and the learning-rate schedule.  Device-side waits are
+bounded; a time-out is reported through a status word that the next ``step`` turns into an error.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from .. import autograd, env
+from ..base import MXNetError
+from . import dist
+
+_MAXR = 8
+MODE_SGD, MODE_NAG, MODE_PLAIN = 0, 1, 2
+_ERRORS = {1: 'waiting for the other ranks to finish their backward pass',
+           2: 'waiting for the other ranks to publish their reduced shard',
+           3: 'waiting for the other ranks to finish writing weights'}
+
+
+class StepParams(C.Structure):
+    _fields_ = [('grads', C.c_void_p * _MAXR), ('weights', C.c_void_p * _MAXR), ('ctrl', C.c_void_p * _MAXR),
+                ('rank', C.c_int), ('nranks', C.c_int), ('total', C.c_int64), ('shard_begin', C.c_int64),
+                ('shard_end', C.c_int64), ('gred', C.c_void_p), ('master', C.c_void_p), ('mom', C.c_void_p),
+                ('seg_end', C.c_void_p), ('lr_mult', C.c_void_p), ('wd_mult', C.c_void_p), ('nseg', C.c_int),
+                ('step', C.c_uint32), ('rescale', C.c_float), ('use_loss_scale', C.c_int), ('lr', C.c_float),
+                ('wd', C.c_float), ('momentum', C.c_float), ('clip_gradient', C.c_float), ('max_norm', C.c_float),
+                ('scale_window', C.c_float), ('scale_max', C.c_float), ('mode', C.c_int),
+                ('timeout_ns', C.c_ulonglong)]
+
+
+class _DevBuf(object):
+    """Zero-copy view of raw device memory for the tensor library."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {'shape': (int(nbytes),), 'typestr': '|u1', 'data': (int(ptr), False),
+                                         'version': 2, 'strides': None}
+
+
+def _lib():
+    from ..ops import cuda
+    return cuda.lib()
+
+
+def supports(optimizer, params):
+    """SGD / NAG on dense parameters of one floating dtype living on one CUDA device."""
+    from ..optimizer import optimizer as opt
+    if type(optimizer) not in (opt.SGD, opt.NAG):
+        return False
+    dtypes = set()
+    for p in params:
+        if p.grad_req == 'null':
+            continue
+        if p._data is None or p._stype != 'default' or p._grad_stype != 'default':
+            return False
+        arr = next(iter(p._data.values()))
+        if not arr._data.is_cuda:
+            return False
+        dtypes.add(arr._data.dtype)
+    if len(dtypes) != 1:
+        return False
+    dt = next(iter(dtypes))
+    if dt not in (torch.float16, torch.bfloat16, torch.float32):
+        return False
+    if dt != torch.float32 and not optimizer.multi_precision:
+        return False
+    return True
+
+
+class FusedStep(object):
+    def __init__(self, params, optimizer, ctx):
+        L = _lib()
+        assert L.mxb_step_params_bytes() == C.sizeof(StepParams), 'StepParams layout mismatch'
+        self.optimizer = optimizer
+        self.ctx = ctx
+        self.device = ctx.torch_device
+        torch.cuda.set_device(self.device)
+        self.params = [p for p in params if p.grad_req != 'null']
+        self.index = {id(p): i for i, p in enumerate(params)}
+        self.param_ids = [self.index[id(p)] for p in self.params]
+        arrs = [p._data[ctx] for p in self.params]
+        self.dtype = arrs[0]._data.dtype
+        self.esize = arrs[0]._data.element_size()
+        self.rank = dist.rank() if dist.is_initialized() else 0
+        self.nranks = dist.world_size() if dist.is_initialized() else 1
+        if self.nranks > _MAXR:
+            raise MXNetError('the fused step supports at most %d ranks per node' % _MAXR)
+        # ---- layout: every segment starts on a 16-byte boundary ------------------------------------
+        vec = 8
+        offs, cur = [], 0
+        for a in arrs:
+            offs.append(cur)
+            cur += (a._data.numel() + vec - 1) // vec * vec
+        gran = vec * self.nranks
+        self.total = (cur + gran - 1) // gran * gran
+        self.offsets = offs
+        self.sizes = [a._data.numel() for a in arrs]
+        shard = self.total // self.nranks
+        self.shard_begin, self.shard_end = self.rank * shard, (self.rank + 1) * shard
+        # ---- one IPC-exportable slab: [control block | weight arena | gradient arena] ---------------
+        self.ctrl_bytes = (L.mxb_step_ctrl_bytes() + 255) // 256 * 256
+        arena_bytes = self.total * self.esize
+        self.slab_bytes = self.ctrl_bytes + 2 * arena_bytes
+        ptr = C.c_void_p()
+        rc = L.mxb_dev_alloc(C.byref(ptr), self.slab_bytes)
+        if rc != 0:
+            raise MXNetError('cudaMalloc of the parameter arena failed: %s' % L.mxb_error_string(rc).decode())
+        self.slab = ptr.value
+        self._w_off, self._g_off = self.ctrl_bytes, self.ctrl_bytes + arena_bytes
+        self._buf = _DevBuf(self.slab, self.slab_bytes)
+        raw = torch.as_tensor(self._buf, device=self.device)
+        self._raw = raw
+        self.ctrl = raw[:self.ctrl_bytes]
+        self.weights = raw[self._w_off:self._w_off + arena_bytes].view(self.dtype)
+        self.grads = raw[self._g_off:self._g_off + arena_bytes].view(self.dtype)
+        for p, off, n in zip(self.params, offs, self.sizes):
+            shape = p._data[ctx]._data.shape
+            p._rebind(ctx, self.weights[off:off + n].view(shape), self.grads[off:off + n].view(shape))
+        # ---- peers ---------------------------------------------------------------------------------
+        self.peer_base = [self.slab] * self.nranks
+        self._opened = []
+        if self.nranks > 1:
+            hb = L.mxb_ipc_handle_bytes()
+            handle = C.create_string_buffer(hb)
+            rc = L.mxb_ipc_get_handle(C.c_void_p(self.slab), handle)
+            if rc != 0:
+                raise MXNetError('cudaIpcGetMemHandle failed: %s' % L.mxb_error_string(rc).decode())
+            layout = (self.total, [int(s) for s in self.sizes])
+            gathered = dist.all_gather_object((handle.raw, layout))
+            for r, (h, lay) in enumerate(gathered):
+                if lay != layout:
+                    raise MXNetError('rank %d has a different parameter layout than rank %d' % (r, self.rank))
+                if r == self.rank:
+                    continue
+                p2 = C.c_void_p()
+                rc = L.mxb_ipc_open(C.c_char_p(h), C.byref(p2))
+                if rc != 0:
+                    raise MXNetError('cudaIpcOpenMemHandle(rank %d) failed: %s' % (r, L.mxb_error_string(rc).decode()))
+                self.peer_base[r] = p2.value
+                self._opened.append(p2.value)
+            # every rank starts from rank 0's values
+            dist.broadcast_(self.weights, 0)
+        # ---- shard-local state ---------------------------------------------------------------------
+        n_shard = self.shard_end - self.shard_begin
+        self.gred = torch.zeros(n_shard, dtype=torch.float32, device=self.device)
+        self.master = None
+        if self.dtype != torch.float32:
+            self.master = self.weights[self.shard_begin:self.shard_end].float()
+        self.mom = torch.zeros(n_shard, dtype=torch.float32, device=self.device) if optimizer.momentum != 0.0 else None
+        seg_end = np.asarray([o + (s + vec - 1) // vec * vec for o, s in zip(offs, self.sizes)], dtype=np.int64)
+        seg_end[-1] = self.total
+        self.seg_end = torch.from_numpy(seg_end).to(self.device)
+        self.lr_mult = torch.tensor([p.lr_mult for p in self.params], dtype=torch.float32, device=self.device)
+        self.wd_mult = torch.tensor([p.wd_mult for p in self.params], dtype=torch.float32, device=self.device)
+        self.step_no = 0
+        self.timeout_ms = int(env.get('MXNET_KVSTORE_WAIT_MS'))
+        off_status = L.mxb_step_ctrl_offset(0)
+        off_scale = L.mxb_step_ctrl_offset(2)
+        self.status = self.ctrl[off_status:off_status + 8].view(torch.int32)        # [status, status_step]
+        self.scale_state = self.ctrl[off_scale:off_scale + 16].view(torch.float32)  # [scale, clean, skipped, norm]
+        self.scale_state[0] = 1.0
+        self._status_host = torch.zeros(2, dtype=torch.int32).pin_memory()
+        self._status_event = None
+        self._grad_arrays = [p._grad[ctx] for p in self.params]
+        self._scaler_attached = None
+        self.max_norm = -1.0
+        self._dt_code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[self.dtype]
+        from ..optimizer import optimizer as opt
+        self.mode = MODE_NAG if type(optimizer) is opt.NAG else MODE_SGD
+        if self.nranks > 1:
+            torch.cuda.synchronize(self.device)
+            dist.barrier()
+
+    # ------------------------------------------------------------------------------------------------
+    def set_global_norm_clip(self, max_norm):
+        """Clip by the global gradient norm inside the update kernel (``gluon.utils.clip_global_norm``
+        semantics: ``scale = min(1, max_norm / (norm + 1e-8))``); ``None`` turns it off."""
+        self.max_norm = -1.0 if max_norm is None else float(max_norm)
+
+    def _params(self, rescale, mode, use_ls, lr, wd):
+        sp = StepParams()
+        for r in range(self.nranks):
+            sp.grads[r] = self.peer_base[r] + self._g_off
+            sp.weights[r] = self.peer_base[r] + self._w_off
+            sp.ctrl[r] = self.peer_base[r]
+        sp.rank, sp.nranks, sp.total = self.rank, self.nranks, self.total
+        sp.shard_begin, sp.shard_end = self.shard_begin, self.shard_end
+        sp.gred = self.gred.data_ptr()
+        sp.master = self.master.data_ptr() if self.master is not None else None
+        sp.mom = self.mom.data_ptr() if self.mom is not None else None
+        sp.seg_end, sp.lr_mult, sp.wd_mult = self.seg_end.data_ptr(), self.lr_mult.data_ptr(), self.wd_mult.data_ptr()
+        sp.nseg = len(self.params)
+        sp.step = self.step_no
+        sp.rescale = rescale
+        sp.use_loss_scale = use_ls
+        opt = self.optimizer
+        sp.lr, sp.wd, sp.momentum = lr, wd, float(getattr(opt, 'momentum', 0.0))
+        sp.clip_gradient = -1.0 if opt.clip_gradient is None else float(opt.clip_gradient)
+        sp.max_norm = self.max_norm
+        sp.scale_window, sp.scale_max = 2000.0, float(2 ** 24)
+        if self._scaler_attached is not None:
+            sp.scale_window = float(self._scaler_attached._scale_seq_len)
+            sp.scale_max = float(self._scaler_attached._max_loss_scale)
+        sp.mode = mode
+        sp.timeout_ns = self.timeout_ms * 1000000
+        return sp
+
+    def _check_status(self):
+        ev = self._status_event
+        if ev is not None and ev.query():
+            self._status_event = None
+            code = int(self._status_host[0])
+            if code != 0:
+                step = int(self._status_host[1])
+                self.status.zero_()
+                raise MXNetError('fused optimizer step %d timed out after %d ms while %s (rank %d of %d)' % (
+                    step, self.timeout_ms, _ERRORS.get(code, 'waiting'), self.rank, self.nranks))
+
+    def _launch(self, rescale, mode, use_ls):
+        from ..ops import cuda
+        L = _lib()
+        self._check_status()
+        self.step_no += 1
+        opt = self.optimizer
+        if mode != MODE_PLAIN:
+            opt._update_count(self.param_ids)
+        lr = float(opt.learning_rate)
+        sp = self._params(float(rescale), mode, use_ls, lr, float(opt.wd))
+        st = cuda.stream_ptr(self.device)
+        rc = L.mxb_fused_reduce(self._dt_code, C.byref(sp), st)
+        if rc == 0:
+            rc = L.mxb_fused_update(self._dt_code, C.byref(sp), st)
+        if rc != 0:
+            raise MXNetError('fused step launch failed: %s' % L.mxb_error_string(rc).decode())
+        cuda.count_launch(2)
+        self._status_host.copy_(self.status, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self._status_event = ev
+
+    def _attach_scaler(self, scaler):
+        """Move the loss scale onto the device.  Returns the ``use_loss_scale`` code for this step: 1 when
+        the kernel divides by the device scale, 2 when the host already folded 1/scale into ``rescale``."""
+        if scaler is None:
+            return 0
+        if self._scaler_attached is scaler:
+            return 1
+        self.scale_state[0] = float(scaler._loss_scale)
+        self.scale_state[1] = float(scaler._unskipped)
+        scaler._device_state = self.scale_state
+        self._scaler_attached = scaler
+        return 2
+
+    def attach_scaler(self, scaler):
+        if scaler is not None and self._scaler_attached is not scaler:
+            self._attach_scaler(scaler)
+
+    def step(self, rescale, scaler=None):
+        use_ls = self._attach_scaler(scaler)
+        self._launch(rescale, self.mode, use_ls)
+        autograd.mark_grads_consumed(self._grad_arrays)
+
+    def allreduce_only(self):
+        """Sum the gradient arenas of all ranks in place (``Trainer.allreduce_grads``)."""
+        self._launch(1.0, MODE_PLAIN, 0)
+
+    def update_only(self, rescale, scaler=None):
+        """Update after ``allreduce_only``: every arena already holds the sum, so the reduction over
+        ranks is compensated by 1/nranks."""
+        use_ls = self._attach_scaler(scaler)
+        self._launch(rescale / self.nranks, self.mode, use_ls)
+        autograd.mark_grads_consumed(self._grad_arrays)
+
+    def wait_probe(self, timeout_ms=50):
+        """Launch a wait on a flag that nothing sets and return the status code it leaves behind (the
+        time-out path of the kernels, exercised without any other rank)."""
+        from ..ops import cuda
+        L = _lib()
+        self.status.zero_()
+        rc = L.mxb_wait_probe(C.c_void_p(self.slab), _MAXR - 1, 0x7fffffff, int(timeout_ms) * 1000000,
+                              cuda.stream_ptr(self.device))
+        if rc != 0:
+            raise MXNetError('probe launch failed')
+        torch.cuda.synchronize(self.device)
+        code = int(self.status[0].item())
+        self.status.zero_()
+        return code
+
+    # ---- optimizer state exchange with the generic Updater (checkpoints) ---------------------------------
+    def _gather(self, shard):
+        if self.nranks == 1:
+            return shard
+        parts = [torch.empty_like(shard) for _ in range(self.nranks)]
+        import torch.distributed as tdist
+        tdist.all_gather(parts, shard)
+        return torch.cat(parts)
+
+    def export_states(self, updater):
+        """Write the sharded state into ``updater.states`` in the layout the generic optimizers use
+        (``(master, momentum)`` per index for multi-precision, else ``momentum``)."""
+        from ..ndarray.ndarray import NDArray
+        master = self._gather(self.master) if self.master is not None else None
+        mom = self._gather(self.mom) if self.mom is not None else None
+        for p, idx, off, n in zip(self.params, self.param_ids, self.offsets, self.sizes):
+            shape = p._data[self.ctx]._data.shape
+            m = NDArray._from_tensor(mom[off:off + n].view(shape).clone(), self.ctx) if mom is not None else None
+            if master is not None:
+                updater.states[idx] = (NDArray._from_tensor(master[off:off + n].view(shape).clone(), self.ctx), m)
+            else:
+                updater.states[idx] = m
+            updater.states_synced[idx] = True
+
+    def import_states(self, updater, optimizer):
+        self.optimizer = optimizer
+        for p, idx, off, n in zip(self.params, self.param_ids, self.offsets, self.sizes):
+            st = updater.states.get(idx)
+            if st is None:
+                continue
+            master, mom = (st if isinstance(st, (tuple, list)) else (None, st))
+            lo, hi = max(off, self.shard_begin), min(off + n, self.shard_end)
+            if lo >= hi:
+                continue
+            src = slice(lo - off, hi - off)
+            dst = slice(lo - self.shard_begin, hi - self.shard_begin)
+            if master is not None and self.master is not None:
+                self.master[dst].copy_(master._data.reshape(-1)[src].to(self.device))
+            if mom is not None and self.mom is not None:
+                self.mom[dst].copy_(mom._data.reshape(-1)[src].to(self.device))
+
+    def __del__(self):
+        try:
+            L = _lib()
+            for p in self._opened:
+                L.mxb_ipc_close(C.c_void_p(p))
+        except Exception:  # pylint: disable=broad-except
+            pass

@@ -1,0 +1,367 @@
+"""Numerics of the hand-written sm_100a kernels against plain fp32 references of the same operators."""
+import numpy as np
+import pytest
+import torch
+
+import mxnet_b200 as mx
+from mxnet_b200 import autograd, gluon, nd
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device('cuda', 0)
+
+
+def _close(a, b, rtol, atol):
+    a, b = a.float().cpu().numpy(), b.float().cpu().numpy()
+    np.testing.assert_allclose(a, b, rtol=rtol, atol=atol)
+
+
+# ---------------------------------------------------------------------------------------- BatchNorm
+@pytest.mark.parametrize('C', [64, 256, 2048])
+@pytest.mark.parametrize('relu,res', [(False, False), (True, False), (True, True), (False, True)])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_batchnorm_nhwc_forward_backward(C, relu, res, dtype):
+    from mxnet_b200.ops.cuda import norm_ops
+    torch.manual_seed(0)
+    N, H, W = 4, 7, 9
+    x = (torch.randn(N, H, W, C, device=_dev()) * 2 + 0.5).to(dtype).requires_grad_(True)
+    r = torch.randn(N, H, W, C, device=_dev()).to(dtype).requires_grad_(True) if res else None
+    gamma = (torch.rand(C, device=_dev()) + 0.5).requires_grad_(True)
+    beta = torch.randn(C, device=_dev()).requires_grad_(True)
+    rm, rv = torch.zeros(C, device=_dev()), torch.ones(C, device=_dev())
+    y, mean, var = norm_ops.batch_norm_nhwc(x, gamma, beta, rm, rv, 1e-5, 0.9, True, 'relu' if relu else None, r)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    # fp32 reference on the same (rounded) inputs
+    xf = x.detach().float().requires_grad_(True)
+    rf = r.detach().float().requires_grad_(True) if res else None
+    g2, b2 = gamma.detach().clone().requires_grad_(True), beta.detach().clone().requires_grad_(True)
+    m = xf.mean((0, 1, 2))
+    v = xf.var((0, 1, 2), unbiased=False)
+    ref = (xf - m) * torch.rsqrt(v + 1e-5) * g2 + b2
+    if res:
+        ref = ref + rf
+    if relu:
+        ref = torch.relu(ref)
+    ref.backward(gy.float())
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.float16 else dict(rtol=6e-2, atol=6e-2)
+    _close(y, ref, **tol)
+    _close(mean, m, 1e-3, 1e-3)
+    _close(var, v, 1e-2, 1e-2)
+    _close(rm, 0.1 * m, 1e-3, 1e-3)
+    _close(rv, 0.9 + 0.1 * v, 1e-2, 1e-2)
+    _close(x.grad, xf.grad, **tol)
+    _close(gamma.grad, g2.grad, 3e-2, 0.3)
+    _close(beta.grad, b2.grad, 3e-2, 0.3)
+    if res:
+        _close(r.grad, rf.grad, **tol)
+
+
+def test_batchnorm_inference_uses_running_stats():
+    from mxnet_b200.ops.cuda import norm_ops
+    C = 128
+    x = torch.randn(2, 5, 5, C, device=_dev()).half()
+    gamma, beta = torch.rand(C, device=_dev()) + 0.5, torch.randn(C, device=_dev())
+    rm, rv = torch.randn(C, device=_dev()), torch.rand(C, device=_dev()) + 0.5
+    rm0, rv0 = rm.clone(), rv.clone()
+    y, _, _ = norm_ops.batch_norm_nhwc(x, gamma, beta, rm, rv, 1e-3, 0.9, False, None, None)
+    ref = (x.float() - rm0) * torch.rsqrt(rv0 + 1e-3) * gamma + beta
+    _close(y, ref, 1e-2, 1e-2)
+    _close(rm, rm0, 0, 0)
+    _close(rv, rv0, 0, 0)
+
+
+# ---------------------------------------------------------------------------------------- LayerNorm
+@pytest.mark.parametrize('shape', [(3, 128, 768), (17, 33), (5, 2048)])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float16, torch.bfloat16])
+def test_layernorm(shape, dtype):
+    from mxnet_b200.ops.cuda import norm_ops
+    torch.manual_seed(1)
+    C = shape[-1]
+    x = torch.randn(*shape, device=_dev()).to(dtype).requires_grad_(True)
+    g = (torch.rand(C, device=_dev()) + 0.5).requires_grad_(True)
+    b = torch.randn(C, device=_dev()).requires_grad_(True)
+    y = norm_ops.layer_norm(x, g, b, 1e-5)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xf = x.detach().float().requires_grad_(True)
+    g2, b2 = g.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    ref = torch.nn.functional.layer_norm(xf, (C,), g2, b2, 1e-5)
+    ref.backward(gy.float())
+    tol = {torch.float32: (1e-4, 1e-4), torch.float16: (2e-2, 2e-2), torch.bfloat16: (6e-2, 6e-2)}[dtype]
+    _close(y, ref, *tol)
+    _close(x.grad, xf.grad, *tol)
+    _close(g.grad, g2.grad, 3e-2, 0.2)
+    _close(b.grad, b2.grad, 3e-2, 0.2)
+
+
+# ---------------------------------------------------------------------------------------- softmax / CE
+@pytest.mark.parametrize('rows,C', [(64, 1000), (7, 33), (3, 30522)])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float16])
+@pytest.mark.parametrize('log', [False, True])
+def test_softmax(rows, C, dtype, log):
+    from mxnet_b200.ops.cuda import softmax_ops
+    torch.manual_seed(2)
+    x = (torch.randn(rows, C, device=_dev()) * 3).to(dtype).requires_grad_(True)
+    y = softmax_ops.softmax(x, log)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xf = x.detach().float().requires_grad_(True)
+    ref = torch.log_softmax(xf, -1) if log else torch.softmax(xf, -1)
+    ref.backward(gy.float())
+    tol = (1e-4, 1e-5) if dtype == torch.float32 else (1e-2, 2e-3)
+    _close(y, ref, *tol)
+    _close(x.grad, xf.grad, tol[0] * 3, tol[1] * 10)
+
+
+@pytest.mark.parametrize('rows,C', [(256, 1000), (40, 33278), (5, 17)])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float16, torch.bfloat16])
+def test_softmax_cross_entropy(rows, C, dtype):
+    from mxnet_b200.ops.cuda import softmax_ops
+    torch.manual_seed(3)
+    x = (torch.randn(rows, C, device=_dev()) * 2).to(dtype).requires_grad_(True)
+    lab = torch.randint(0, C, (rows,), device=_dev())
+    loss = softmax_ops.softmax_ce(x, lab, None)
+    w = torch.rand(rows, device=_dev())
+    (loss * w).sum().backward()
+    xf = x.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(xf, lab, reduction='none')
+    (ref * w).sum().backward()
+    tol = {torch.float32: (1e-4, 1e-4), torch.float16: (2e-3, 2e-3), torch.bfloat16: (2e-2, 2e-2)}[dtype]
+    _close(loss, ref, *tol)
+    _close(x.grad, xf.grad, tol[0] * 5, tol[1])
+
+
+def test_softmax_cross_entropy_ignore_label():
+    from mxnet_b200.ops.cuda import softmax_ops
+    x = torch.randn(6, 11, device=_dev(), requires_grad=True)
+    lab = torch.tensor([1, 3, 0, 3, 10, 3], device=_dev())
+    loss = softmax_ops.softmax_ce(x, lab, 3)
+    loss.sum().backward()
+    assert float(loss[1]) == 0.0 and float(loss[3]) == 0.0
+    assert float(x.grad[1].abs().sum()) == 0.0
+    ref = torch.nn.functional.cross_entropy(x.detach(), lab, reduction='none')
+    _close(loss[[0, 2, 4]], ref[[0, 2, 4]], 1e-4, 1e-5)
+
+
+# ---------------------------------------------------------------------------------------- multi-tensor ops
+def test_multi_mp_sgd_mom_matches_reference_rule():
+    from mxnet_b200.ops.cuda import optim_ops
+    torch.manual_seed(4)
+    shapes = [(1000,), (64, 3, 3, 64), (7,), (20000,)] * 15      # > one table
+    w32 = [torch.randn(*s, device=_dev()) for s in shapes]
+    w = [t.half() for t in w32]
+    g = [torch.randn(*s, device=_dev()).half() for s in shapes]
+    m = [torch.randn(*s, device=_dev()) * 0.1 for s in shapes]
+    lrs = [0.1 + 0.01 * (i % 3) for i in range(len(shapes))]
+    wds = [1e-4 * (i % 2) for i in range(len(shapes))]
+    ref_w, ref_m = [], []
+    for i in range(len(shapes)):
+        gr = (g[i].float() * 0.5).clamp(-1.0, 1.0) + wds[i] * w32[i]
+        mm = 0.9 * m[i] - lrs[i] * gr
+        ref_m.append(mm)
+        ref_w.append(w32[i] + mm)
+    optim_ops.multi_sgd(w, g, m, w32, lrs, wds, 0.9, 0.5, 1.0)
+    for i in range(len(shapes)):
+        _close(m[i], ref_m[i], 1e-5, 1e-6)
+        _close(w32[i], ref_w[i], 1e-5, 1e-6)
+        _close(w[i], ref_w[i].half(), 0, 0)
+
+
+def test_multi_all_finite_and_sum_sq():
+    from mxnet_b200.ops.cuda import optim_ops
+    ts = [torch.randn(n, device=_dev()).to(dt) for n, dt in
+          [(10, torch.float32), (100000, torch.float16), (33, torch.bfloat16)] * 20]
+    assert float(optim_ops.multi_all_finite(ts).item()) == 1.0
+    ss = optim_ops.multi_sum_sq(ts)
+    ref = torch.stack([(t.float() ** 2).sum() for t in ts])
+    _close(ss, ref, 1e-4, 1e-4)
+    ts[37][5] = float('inf')
+    assert float(optim_ops.multi_all_finite(ts).item()) == 0.0
+    ts[37][5] = float('nan')
+    assert float(optim_ops.multi_all_finite(ts).item()) == 0.0
+    # bitwise reproducible
+    a, b = optim_ops.multi_sum_sq(ts[:20]), optim_ops.multi_sum_sq(ts[:20])
+    assert torch.equal(a, b)
+
+
+# ---------------------------------------------------------------------------------------- tcgen05 GEMM
+@pytest.mark.parametrize('M,N,K', [(128, 128, 64), (256, 256, 512), (300, 136, 72), (1, 1000, 2048), (4096, 64, 64),
+                                   (130, 8, 8), (777, 264, 1032)])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_tcgen05_gemm_matches_fp32_reference(M, N, K, dtype):
+    from mxnet_b200.ops.cuda import gemm_ops
+    torch.manual_seed(5)
+    a = torch.randn(M, K, device=_dev()).to(dtype)
+    b = torch.randn(N, K, device=_dev()).to(dtype)
+    bias = torch.randn(N, device=_dev()).to(dtype)
+    d = gemm_ops.gemm_tn(a, b)
+    ref = a.float() @ b.float().t()
+    gemm_ops.check_errors()
+    tol = (1e-2, 1e-2 * K ** 0.5) if dtype == torch.float16 else (2e-2, 4e-2 * K ** 0.5)
+    _close(d, ref, *tol)
+    d2 = gemm_ops.gemm_tn(a, b, bias, 'relu')
+    _close(d2, torch.relu(ref + bias.float()), *tol)
+    gemm_ops.check_errors()
+
+
+def test_linear_autograd_through_tcgen05():
+    from mxnet_b200.ops.cuda import gemm_ops
+    torch.manual_seed(6)
+    x = torch.randn(64, 256, device=_dev()).half().requires_grad_(True)
+    w = (torch.randn(128, 256, device=_dev()) * 0.1).half().requires_grad_(True)
+    b = torch.randn(128, device=_dev()).half().requires_grad_(True)
+    y = gemm_ops.LinearFn.apply(x, w, b, None)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    ref = torch.nn.functional.linear(xf, wf, bf)
+    ref.backward(gy.float())
+    _close(y, ref, 1e-2, 5e-2)
+    _close(x.grad, xf.grad, 2e-2, 5e-2)
+    _close(w.grad, wf.grad, 2e-2, 1e-1)
+    _close(b.grad, bf.grad, 2e-2, 1e-1)
+    gemm_ops.check_errors()
+
+
+# ---------------------------------------------------------------------------------------- fused optimizer step
+def _tiny_net(ctx, dtype):
+    from mxnet_b200.gluon import nn
+    net = nn.HybridSequential()
+    net.add(nn.Dense(64, activation='relu', in_units=32), nn.Dense(10, in_units=64))
+    net.initialize(mx.init.Xavier(), ctx=ctx)
+    if dtype != 'float32':
+        net.cast(dtype)
+    return net
+
+
+@pytest.mark.parametrize('dtype', ['float16', 'float32'])
+def test_fused_step_matches_multi_precision_sgd(dtype):
+    ctx = mx.gpu(0)
+    net = _tiny_net(ctx, dtype)
+    params = list(net.collect_params().values())
+    ref_w = [p.data(ctx)._data.detach().float().clone() for p in params]
+    ref_m = [torch.zeros_like(w) for w in ref_w]
+    trainer = gluon.Trainer(net.collect_params(), 'sgd', {'learning_rate': 0.05, 'momentum': 0.9, 'wd': 1e-3,
+                                                          'multi_precision': dtype != 'float32'}, kvstore='device')
+    loss_fn = gluon.loss.SoftmaxCrossEntropyLoss()
+    x = nd.array(np.random.randn(16, 32).astype(dtype), ctx=ctx, dtype=dtype)
+    y = nd.array(np.random.randint(0, 10, (16,)), ctx=ctx)
+    for step in range(4):
+        with autograd.record():
+            loss = loss_fn(net(x), y)
+        loss.backward()
+        grads = [p.grad(ctx)._data.detach().float().clone() for p in params]
+        trainer.step(16)
+        assert trainer._fused is not None
+        for w, m, g in zip(ref_w, ref_m, grads):
+            gr = g / 16 + 1e-3 * w
+            m.mul_(0.9).add_(gr, alpha=-0.05)
+            w.add_(m)
+        for p, w in zip(params, ref_w):
+            tol = (1e-5, 1e-6) if dtype == 'float32' else (2e-3, 2e-3)
+            _close(p.data(ctx)._data, w, *tol)
+            # the step clears the gradient arena
+            assert float(p.grad(ctx)._data.abs().sum()) == 0.0
+
+
+def test_fused_step_skips_on_overflow_and_halves_loss_scale():
+    from mxnet_b200 import amp
+    ctx = mx.gpu(0)
+    amp._reset()
+    amp.init('float16')
+    try:
+        net = _tiny_net(ctx, 'float16')
+        trainer = gluon.Trainer(net.collect_params(), 'sgd', {'learning_rate': 0.1, 'momentum': 0.9,
+                                                              'multi_precision': True}, kvstore='device')
+        amp.init_trainer(trainer)
+        assert trainer._fused is not None
+        loss_fn = gluon.loss.SoftmaxCrossEntropyLoss()
+        x = nd.array(np.random.randn(8, 32).astype('float16'), ctx=ctx, dtype='float16')
+        y = nd.array(np.random.randint(0, 10, (8,)), ctx=ctx)
+        before = [p.data(ctx)._data.clone() for p in net.collect_params().values()]
+        with autograd.record():
+            loss = loss_fn(net(x), y)
+            with amp.scale_loss(loss, trainer) as scaled:
+                autograd.backward(scaled)
+        next(iter(net.collect_params().values())).grad(ctx)._data.view(-1)[0] = float('inf')
+        trainer.step(8)
+        torch.cuda.synchronize()
+        state = trainer._fused.scale_state.cpu()
+        assert float(state[0]) == 2. ** 15 and float(state[2]) == 1.0
+        for p, b in zip(net.collect_params().values(), before):
+            assert torch.equal(p.data(ctx)._data, b)
+        # a clean step afterwards updates the weights
+        with autograd.record():
+            loss = loss_fn(net(x), y)
+            with amp.scale_loss(loss, trainer) as scaled:
+                autograd.backward(scaled)
+        trainer.step(8)
+        torch.cuda.synchronize()
+        assert any(not torch.equal(p.data(ctx)._data, b) for p, b in zip(net.collect_params().values(), before))
+        assert float(trainer._fused.scale_state.cpu()[1]) == 1.0
+    finally:
+        amp._reset()
+
+
+def test_device_wait_times_out_with_status_not_a_hang():
+    ctx = mx.gpu(0)
+    net = _tiny_net(ctx, 'float32')
+    trainer = gluon.Trainer(net.collect_params(), 'sgd', {'learning_rate': 0.1}, kvstore='device')
+    trainer._init_kvstore()
+    assert trainer._fused is not None
+    code = trainer._fused.wait_probe(timeout_ms=20)
+    assert code == 1            # kErrWaitReady: the wait gave up and reported, the context is still usable
+    assert float(torch.ones(4, device='cuda').sum()) == 4.0
+
+
+# ---------------------------------------------------------------------------------------- model-level checks
+def test_resnet_block_kernels_match_library_path():
+    from mxnet_b200 import env
+    from mxnet_b200.gluon.model_zoo.vision.resnet import BottleneckV1
+    ctx = mx.gpu(0)
+    blk = BottleneckV1(64, 1, True, in_channels=32, layout='NHWC', fused=True, v1b=True)
+    blk.initialize(mx.init.Xavier(), ctx=ctx)
+    for p in blk.collect_params().values():
+        if p.grad_req != 'null':
+            p.cast('float16')
+    x = nd.array(np.random.randn(4, 8, 8, 32).astype('float16'), ctx=ctx, dtype='float16')
+    outs = []
+    for flag in ('1', '0'):
+        with env.scope('MXNET_B200_KERNELS', flag):
+            xx = x.copy()
+            xx.attach_grad()
+            for p in blk.collect_params().values():
+                if p.grad_req == 'null':
+                    p.set_data(nd.zeros(p.shape, ctx=ctx) if 'mean' in p.name else nd.ones(p.shape, ctx=ctx))
+            with autograd.record():
+                y = blk(xx)
+            y.backward(nd.ones(y.shape, ctx=ctx, dtype='float16'))
+            outs.append((y.asnumpy().astype('float32'), xx.grad.asnumpy().astype('float32')))
+    np.testing.assert_allclose(outs[0][0], outs[1][0], rtol=3e-2, atol=3e-2)
+    np.testing.assert_allclose(outs[0][1], outs[1][1], rtol=6e-2, atol=6e-2)
+
+
+def test_hybridize_cuda_graph_matches_eager():
+    from mxnet_b200.gluon import nn
+    ctx = mx.gpu(0)
+    net = nn.HybridSequential()
+    net.add(nn.Dense(64, activation='relu', in_units=32), nn.LayerNorm(in_channels=64), nn.Dense(8, in_units=64))
+    net.initialize(mx.init.Xavier(), ctx=ctx)
+    x = nd.array(np.random.randn(16, 32).astype('float32'), ctx=ctx)
+    with autograd.record():
+        ref = net(x)
+    ref.backward()
+    ref_out = ref.asnumpy()
+    ref_grads = [p.grad(ctx).asnumpy().copy() for p in net.collect_params().values()]
+    net.hybridize(static_alloc=True, static_shape=True)
+    for it in range(4):              # eager first call, warm-up, capture, replay
+        with autograd.record():
+            out = net(x)
+        out.backward()
+        np.testing.assert_allclose(out.asnumpy(), ref_out, rtol=1e-5, atol=1e-6)
+        for p, g in zip(net.collect_params().values(), ref_grads):
+            np.testing.assert_allclose(p.grad(ctx).asnumpy(), g, rtol=1e-4, atol=1e-5)
+    assert net._cached_op is not None and len(net._cached_op._graphs) == 1
