@@ -102,14 +102,12 @@ def init_trainer(optimizer_or_trainer):
             loss_scaler._max_loss_scale = 1.0
         # bring up the optimizer path now when the parameters already exist, so that the loss scale can
         # live on the device from the first step on
-        try:
-            tr = optimizer_or_trainer
-            if not tr._kv_initialized and tr._check_devices() is not None:
-                tr._init_kvstore()
-            if tr._fused is not None:
-                tr._fused.attach_scaler(loss_scaler)
-        except Exception:  # pylint: disable=broad-except
-            pass
+        tr = optimizer_or_trainer
+        ready = all(p._data is not None for p in tr._params)
+        if ready and not tr._kv_initialized:
+            tr._init_kvstore()
+        if tr._fused is not None:
+            tr._fused.attach_scaler(loss_scaler)
     else:
         raise TypeError('optimizer_or_trainer should be a Gluon Trainer instance, instead is %s' % type(optimizer_or_trainer))
 

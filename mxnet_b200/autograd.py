@@ -137,8 +137,8 @@ def mark_variables(variables, gradients, grad_reqs='write'):
 
 
 def mark_grads_consumed(arrays):
-    """Tell autograd that the gradient buffers of ``arrays`` were consumed and already cleared
-    by the caller (the fused optimizer kernels zero them in the same pass)."""
+    """Tell autograd that the gradient buffers attached to the variables ``arrays`` were consumed and
+    already cleared by the caller (the fused optimizer kernels zero them in the same pass)."""
     for a in arrays:
         a._fresh_grad = False
 
@@ -203,11 +203,39 @@ def grad(heads, variables, head_grads=None, retain_graph=None, create_graph=Fals
 
 
 def get_symbol(x):
-    """Symbol that produced ``x`` if it was computed under deferred-compute tracing."""
-    if x._sym is None:
-        raise MXNetError('array was not produced under a tracing scope; use HybridBlock.export '
-                         'or mx._deferred_compute to obtain a Symbol')
-    return x._sym
+    """Retrieve the recorded computation history of ``x`` as a Symbol
+    (python/mxnet/autograd.py:330-347, ``MXAutogradGetSymbol``).  Arrays that were not produced by a
+    recorded operator become variables ``var0, var1, ...`` in order of first use."""
+    from .symbol.symbol import Symbol, _Node, var
+    from .name import NameManager
+    from .ndarray.ndarray import NDArray
+    if x._sym is not None:
+        return Symbol([x._sym])
+    names = NameManager()
+    entries, nodes, leaves = {}, {}, []
+
+    def entry(a):
+        hit = entries.get(id(a))
+        if hit is not None:
+            return hit
+        prov = getattr(a, '_prov', None)
+        if prov is None:
+            v = var('var%d' % len(leaves))
+            leaves.append(a)
+            entries[id(a)] = v._outputs[0]
+            return entries[id(a)]
+        op, args, attrs, idx, nout = prov
+        key = id(prov[1])
+        node = nodes.get(key)
+        if node is None:
+            ins = [entry(i) for i in args if isinstance(i, NDArray)]
+            node = nodes[key] = _Node(op, names.get(None, op.name.lower().lstrip('_')), dict(attrs), ins, max(nout, 1))
+        entries[id(a)] = (node, idx)
+        return entries[id(a)]
+
+    if getattr(x, '_prov', None) is None:
+        raise MXNetError('array was not produced by a recorded operator')
+    return Symbol([entry(x)])
 
 
 class Function(object):

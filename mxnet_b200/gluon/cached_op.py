@@ -206,8 +206,7 @@ class CachedOp(object):
             g = _Graphed(self.block, args, _state.state.training, _state.state.recording)
         except Exception as e:  # pylint: disable=broad-except
             self._disabled = True
-            if env.get('MXNET_CUDA_GRAPHS_VERBOSE'):
-                _log.warning('CUDA graph capture failed (%s); block %s runs eagerly', e, type(self.block).__name__)
+            _log.warning('CUDA graph capture failed (%s); block %s runs eagerly', e, type(self.block).__name__)
             return self.block._call_forward(*args)
         self._graphs[sig] = g
         if env.get('MXNET_CUDA_GRAPHS_VERBOSE'):

@@ -71,6 +71,7 @@ class Trainer(object):
         self._distributed = None
         self._params_to_init = []
         self._fused = None
+        self._consumed_pass = {}
         self._amp_loss_scaler = None
         self._reset_kvstore()
 
@@ -233,6 +234,12 @@ class Trainer(object):
         if self._params_to_init:
             self._init_params()
         if self._fused is not None:
+            if not ignore_stale_grad:
+                for arr in self._fused._data_arrays:
+                    if not arr._fresh_grad:
+                        raise UserWarning('Gradient of a Parameter on device %s has not been updated by backward since '
+                                          'last `step`; call step with ignore_stale_grad=True to suppress this check'
+                                          % str(arr.context))
             self._fused.step(rescale_grad, self._amp_loss_scaler)
             return
         self._allreduce_grads()
@@ -277,6 +284,12 @@ class Trainer(object):
             return
         self._update(ignore_stale_grad)
 
+    def _is_fresh(self, arr):
+        """True when backward wrote this replica's gradient since the last update that consumed it
+        (the `_fresh_grad` flag of python/mxnet/gluon/trainer.py:437-458).  The write-mode hook needs
+        its own flag to stay set until the next pass, so consumption is tracked by backward-pass id."""
+        return arr._fresh_grad and self._consumed_pass.get(id(arr)) != arr._grad_pass
+
     def _update(self, ignore_stale_grad=False):
         loss_scaler = self._amp_loss_scaler
         if loss_scaler is not None:
@@ -290,13 +303,19 @@ class Trainer(object):
         for i, param in enumerate(self._params):
             if param.grad_req == 'null':
                 continue
-            if not ignore_stale_grad:
-                for data in param._check_and_get(param._data, list):
-                    if not data._fresh_grad and param.grad_req == 'write' and False:
-                        raise UserWarning('Gradient of Parameter `%s` on device %s has not been updated by backward '
-                                          'since last `step`.' % (param.name, str(data.context)))
-            for upd, arr, grad in zip(updates, param.list_data(), param.list_grad()):
-                upd.append((i, grad, arr))
+            datas = param._check_and_get(param._data, list)
+            fresh = [self._is_fresh(d) for d in datas]
+            if not ignore_stale_grad and not all(fresh):
+                d = datas[fresh.index(False)]
+                raise UserWarning(
+                    'Gradient of Parameter `%s` on device %s has not been updated by backward since last `step`. This '
+                    'could mean a bug in your model that made it only use a subset of the Parameters (Blocks) for this '
+                    'iteration. If you are intentionally only using a subset, call step with ignore_stale_grad=True to '
+                    'suppress this warning and skip updating of Parameters with stale gradient' % (param.name, str(d.context)))
+            for upd, arr, grad, ok in zip(updates, datas, param.list_grad(), fresh):
+                if ok:
+                    upd.append((i, grad, arr))
+                    self._consumed_pass[id(arr)] = arr._grad_pass
         for updater, upd in zip(self._updaters, updates):
             if upd:
                 i, g, w = zip(*upd)

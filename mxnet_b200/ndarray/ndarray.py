@@ -31,7 +31,7 @@ def _torch_device_of(ctx):
 
 class NDArray(object):
     """N-dimensional array on a device.  ``_kind`` selects legacy (``nd``) or NumPy (``np``) semantics."""
-    __slots__ = ('_data', '_ctx', '_grad', '_grad_req', '_stype', '_sym', '_fresh_grad', '_hook', '_grad_pass', '__weakref__')
+    __slots__ = ('_data', '_ctx', '_grad', '_grad_req', '_stype', '_sym', '_fresh_grad', '_hook', '_grad_pass', '_prov', '__weakref__')
     _kind = 'nd'
     __array_priority__ = 1000.0
 
@@ -641,12 +641,9 @@ def _to_tensor(src, ctx=None, dtype=None, default_float32=True):
 # ------------------------------------------------------------------------------------------
 def array(source_array, ctx=None, dtype=None, device=None):
     ctx = ctx or device
-    if isinstance(source_array, NDArray) and dtype is None:
-        dtype = source_array._data.dtype
-    elif isinstance(source_array, _np.ndarray) and dtype is None and source_array.dtype != _np.float64:
-        dtype = source_array.dtype if source_array.dtype.kind != 'O' else None
-        if dtype is not None and _np.dtype(dtype).kind in 'iu' and False:
-            dtype = None
+    if dtype is None:
+        # python/mxnet/ndarray/ndarray.py:3450-3453: an NDArray source keeps its dtype, anything else is float32
+        dtype = source_array._data.dtype if isinstance(source_array, NDArray) else _np.float32
     t = _to_tensor(source_array, ctx, dtype)
     return NDArray._from_tensor(t, ctx or current_device())
 
@@ -740,3 +737,25 @@ def waitall():
     """Block until all asynchronous work has finished and surface deferred errors (``MXNDArrayWaitAll``)."""
     from .. import engine
     engine.waitall()
+
+
+# Fluent methods that simply forward to the operator of the same name with the array as first input
+# (python/mxnet/ndarray/ndarray.py:1268-2420 lists them one by one).
+_FLUENT = ('reshape_like broadcast_axes broadcast_to broadcast_like pad swapaxes split_v2 argmax_channel abs sign flatten '
+           'shape_array size_array expand_dims transpose depth_to_space space_to_depth round rint fix floor ceil trunc sin '
+           'cos tan arcsin arccos arctan degrees radians sinh cosh tanh arcsinh arccosh arctanh exp expm1 log log10 log2 '
+           'log1p log_sigmoid sqrt rsqrt cbrt rcbrt square reciprocal relu sigmoid softmin squeeze mish').split()
+
+
+def _make_fluent(name):
+    def method(self, *args, **kwargs):
+        import sys
+        return getattr(sys.modules[__name__.rsplit('.', 1)[0]], name)(self, *args, **kwargs)
+    method.__name__ = name
+    method.__doc__ = 'Convenience fluent method for :py:func:`%s` with this array as the first input.' % name
+    return method
+
+
+for _name in _FLUENT:
+    if _name not in NDArray.__dict__:
+        setattr(NDArray, _name, _make_fluent(_name))

@@ -13,8 +13,10 @@ def declare(L):
         f.restype, f.argtypes = res, list(args)
     sig('mxb_bn_grid', i32, i64, i32)
     sig('mxb_ln_grid', i32, i64)
-    sig('mxb_bn_forward', i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, i32, i32, vp)
-    sig('mxb_bn_backward', i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, vp)
+    sig('mxb_bn_forward', i32, i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, i32, i32, vp)
+    sig('mxb_bn_backward', i32, i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, vp)
+    sig('mxb_maxpool_forward', i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp)
+    sig('mxb_maxpool_backward', i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp)
     sig('mxb_ln_forward', i32, i32, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp)
     sig('mxb_ln_backward', i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, vp)
     sig('mxb_softmax_forward', i32, i32, vp, vp, i64, i32, i32, vp)

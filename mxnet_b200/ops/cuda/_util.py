@@ -13,3 +13,23 @@ def dt(t):
 def f32(t):
     """fp32 contiguous view/copy of a small per-channel tensor."""
     return t if (t.dtype == torch.float32 and t.is_contiguous()) else t.float().contiguous()
+
+
+def require(t, name, numel=None, dtype=None, device=None, shape=None):
+    """Validate one kernel operand before its raw pointer crosses the C boundary: the kernels index
+    from the sizes they are told, so a mis-sized or misplaced tensor must fail here, in Python."""
+    if t is None:
+        raise ValueError('%s is required' % name)
+    if not t.is_cuda:
+        raise ValueError('%s must live on a CUDA device' % name)
+    if device is not None and t.device != device:
+        raise ValueError('%s is on %s, expected %s' % (name, t.device, device))
+    if not t.is_contiguous():
+        raise ValueError('%s must be contiguous' % name)
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError('%s has dtype %s, expected %s' % (name, t.dtype, dtype))
+    if numel is not None and t.numel() != numel:
+        raise ValueError('%s has %d elements, expected %d' % (name, t.numel(), numel))
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError('%s has shape %s, expected %s' % (name, tuple(t.shape), tuple(shape)))
+    return t

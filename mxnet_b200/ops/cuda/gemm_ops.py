@@ -7,7 +7,7 @@ descriptors and is served by the library GEMM for now."""
 import torch
 
 from . import lib, ptr, stream_ptr, count_launch, check
-from ._util import dt
+from ._util import dt, require
 
 _ACT = {None: 0, 'relu': 1, 'gelu': 2}
 _err = {}
@@ -40,6 +40,12 @@ def gemm_tn(a, b, bias=None, act=None, out=None):
         b = b.contiguous()
     M, K = a.shape
     N = b.shape[0]
+    require(a, 'a')
+    require(b, 'b', dtype=a.dtype, device=a.device, shape=(N, K))
+    if out is not None:
+        require(out, 'out', dtype=a.dtype, device=a.device, shape=(M, N))
+    if bias is not None:
+        require(bias, 'bias', numel=N, device=a.device)
     d = out if out is not None else torch.empty(M, N, dtype=a.dtype, device=a.device)
     if bias is not None and bias.dtype != a.dtype:
         bias = bias.to(a.dtype)

@@ -9,46 +9,82 @@
 // BatchNorm layout: x is [M, C] with C contiguous (M = N*H*W), C = 8*L with L a power of two <= 256.
 // Statistics are reduced in two deterministic stages: per-CTA partial sums into a scratch buffer
 // [grid][2][C], then a per-channel finalize kernel (no atomics, bitwise reproducible).
+//
+// Backward of BN+ReLU without a residual does not read y: the mask y > 0 is recomputed from x and the
+// per-channel scale/shift.  With a residual the mask comes from y.  dx is evaluated as
+// A[c]*dy' + B[c]*x + D[c] with three per-channel coefficients prepared by the finalize kernel.
 #include "common.cuh"
 
 namespace mxb {
 
 constexpr int kBnThreads = 256;
+enum BnRelu { kReluNone = 0, kReluFromX = 1, kReluFromY = 2 };
 
-template <typename T, bool kBackward, bool kRelu>
+__device__ __forceinline__ float load_param(const void* p, int dtype, int c) {
+  if (dtype == kF32) return static_cast<const float*>(p)[c];
+  if (dtype == kF16) return __half2float(static_cast<const __half*>(p)[c]);
+  return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[c]);
+}
+__device__ __forceinline__ void store_param(void* p, int dtype, int c, float v) {
+  if (dtype == kF32) static_cast<float*>(p)[c] = v;
+  else if (dtype == kF16) static_cast<__half*>(p)[c] = __float2half_rn(v);
+  else static_cast<__nv_bfloat16*>(p)[c] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ void load8(const float* p, float* out) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+
+// forward (kBackward = false): partial = {sum x, sum x^2}
+// backward: partial = {sum dy', sum dy' * xhat} with dy' = dy masked by the ReLU
+template <typename T, bool kBackward, int kRelu>
 __global__ void __launch_bounds__(kBnThreads)
 bn_reduce_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ y,
-                 const float* __restrict__ mean, const float* __restrict__ invstd, int64_t M, int C,
-                 float* __restrict__ partial) {
-  // forward: partial = {sum x, sum x^2};  backward: partial = {sum dy', sum dy' * xhat}
+                 const float* __restrict__ mean, const float* __restrict__ invstd, const float* __restrict__ scale,
+                 const float* __restrict__ shift, int64_t M, int C, float* __restrict__ partial) {
   __shared__ float sh[2][kBnThreads * 8];
   const int L = C >> 3;
   const int v = threadIdx.x % L, r = threadIdx.x / L, R = kBnThreads / L;
   float s[8], q[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) { s[j] = 0.f; q[j] = 0.f; }
-  float mu[8], is[8];
+  float mu[8], is[8], sc[8], sf[8];
   if (kBackward) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { mu[j] = mean[v * 8 + j]; is[j] = invstd[v * 8 + j]; }
+    load8(mean + v * 8, mu);
+    load8(invstd + v * 8, is);
+    if (kRelu == kReluFromX) { load8(scale + v * 8, sc); load8(shift + v * 8, sf); }
   }
-  for (int64_t row = (int64_t)blockIdx.x * R + r; row < M; row += (int64_t)gridDim.x * R) {
-    const int64_t off = row * C + v * 8;
-    Vec16<T> a = ld16(x + off);
+  const int64_t stride = (int64_t)gridDim.x * R;
+  for (int64_t row = (int64_t)blockIdx.x * R + r; row < M; row += 2 * stride) {
+    // two rows per trip keep more 16-byte loads in flight per thread
+    const int64_t off0 = row * C + v * 8;
+    const bool two = row + stride < M;
+    const int64_t off1 = two ? off0 + stride * C : off0;
+    Vec16<T> a0 = ld16(x + off0), a1 = ld16(x + off1);
     if (!kBackward) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { float f = Cvt<T>::to_f(a.v[j]); s[j] += f; q[j] += f * f; }
+      for (int j = 0; j < 8; ++j) {
+        const float f0 = Cvt<T>::to_f(a0.v[j]), f1 = two ? Cvt<T>::to_f(a1.v[j]) : 0.f;
+        s[j] += f0 + f1;
+        q[j] += f0 * f0 + f1 * f1;
+      }
     } else {
-      Vec16<T> g = ld16(dy + off);
-      Vec16<T> o;
-      if (kRelu) o = ld16(y + off);
+      Vec16<T> g0 = ld16(dy + off0), g1 = ld16(dy + off1), o0, o1;
+      if (kRelu == kReluFromY) { o0 = ld16(y + off0); o1 = ld16(y + off1); }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float d = Cvt<T>::to_f(g.v[j]);
-        if (kRelu && !(Cvt<T>::to_f(o.v[j]) > 0.f)) d = 0.f;
-        float xh = (Cvt<T>::to_f(a.v[j]) - mu[j]) * is[j];
-        s[j] += d;
-        q[j] += d * xh;
+        const float x0 = Cvt<T>::to_f(a0.v[j]), x1 = Cvt<T>::to_f(a1.v[j]);
+        float d0 = Cvt<T>::to_f(g0.v[j]), d1 = two ? Cvt<T>::to_f(g1.v[j]) : 0.f;
+        if (kRelu == kReluFromY) {
+          if (!(Cvt<T>::to_f(o0.v[j]) > 0.f)) d0 = 0.f;
+          if (!(Cvt<T>::to_f(o1.v[j]) > 0.f)) d1 = 0.f;
+        } else if (kRelu == kReluFromX) {
+          if (!(x0 * sc[j] + sf[j] > 0.f)) d0 = 0.f;
+          if (!(x1 * sc[j] + sf[j] > 0.f)) d1 = 0.f;
+        }
+        s[j] += d0 + d1;
+        q[j] += d0 * ((x0 - mu[j]) * is[j]) + d1 * ((x1 - mu[j]) * is[j]);
       }
     }
   }
@@ -66,32 +102,55 @@ bn_reduce_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __r
   }
 }
 
+// Sum the per-CTA partials of 32 channels with a (32 x 16) thread block: coalesced along the channel
+// axis, 16-way split along the partial axis, fixed-order tree in shared memory (deterministic).
+constexpr int kFinX = 32, kFinY = 16;
+__device__ __forceinline__ bool finalize_sums(const float* __restrict__ partial, int nblocks, int C, float& s, float& q) {
+  __shared__ float red[2][kFinY][kFinX];
+  const int c = blockIdx.x * kFinX + threadIdx.x;
+  float a = 0.f, b = 0.f;
+  if (c < C) {
+    for (int k = threadIdx.y; k < nblocks; k += kFinY) {
+      a += partial[((int64_t)k * 2) * C + c];
+      b += partial[((int64_t)k * 2 + 1) * C + c];
+    }
+  }
+  red[0][threadIdx.y][threadIdx.x] = a;
+  red[1][threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y != 0 || c >= C) return false;
+  s = 0.f; q = 0.f;
+#pragma unroll
+  for (int k = 0; k < kFinY; ++k) { s += red[0][k][threadIdx.x]; q += red[1][k][threadIdx.x]; }
+  return true;
+}
+
 // Forward finalize: statistics, running averages, fused scale/shift.
-__global__ void bn_fwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int C, int64_t M, float eps,
-                                       float momentum, const float* __restrict__ gamma, const float* __restrict__ beta,
-                                       float* __restrict__ running_mean, float* __restrict__ running_var,
-                                       float* __restrict__ save_mean, float* __restrict__ save_invstd,
-                                       float* __restrict__ scale, float* __restrict__ shift, int training) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+__global__ void __launch_bounds__(kFinX * kFinY)
+bn_fwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int C, int64_t M, float eps, float momentum,
+                       const void* __restrict__ gamma, const void* __restrict__ beta, int pdtype,
+                       float* __restrict__ running_mean, float* __restrict__ running_var, float* __restrict__ save_mean,
+                       float* __restrict__ save_invstd, float* __restrict__ scale, float* __restrict__ shift, int training) {
+  float s = 0.f, q = 0.f;
   float mean, var;
+  const int c = blockIdx.x * kFinX + threadIdx.x;
   if (training) {
-    float s = 0.f, q = 0.f;
-    for (int b = 0; b < nblocks; ++b) { s += partial[((int64_t)b * 2) * C + c]; q += partial[((int64_t)b * 2 + 1) * C + c]; }
+    if (!finalize_sums(partial, nblocks, C, s, q)) return;
     mean = s / (float)M;
     var = fmaxf(q / (float)M - mean * mean, 0.f);
     running_mean[c] = running_mean[c] * momentum + mean * (1.f - momentum);
     running_var[c] = running_var[c] * momentum + var * (1.f - momentum);
   } else {
+    if (threadIdx.y != 0 || c >= C) return;
     mean = running_mean[c];
     var = running_var[c];
   }
-  float is = rsqrtf(var + eps);
+  const float is = rsqrtf(var + eps);
   save_mean[c] = mean;
   save_invstd[c] = is;
-  float sc = gamma[c] * is;
+  const float sc = load_param(gamma, pdtype, c) * is;
   scale[c] = sc;
-  shift[c] = beta[c] - mean * sc;
+  shift[c] = load_param(beta, pdtype, c) - mean * sc;
 }
 
 template <typename T, bool kRelu, bool kRes>
@@ -102,10 +161,9 @@ bn_fwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ res, const fl
     const int c0 = (int)(i % L) * 8;
     Vec16<T> a = ld16(x + i * 8), o, rr;
     if (kRes) rr = ld16(res + i * 8);
-    const float4 s0 = *reinterpret_cast<const float4*>(scale + c0), s1 = *reinterpret_cast<const float4*>(scale + c0 + 4);
-    const float4 h0 = *reinterpret_cast<const float4*>(shift + c0), h1 = *reinterpret_cast<const float4*>(shift + c0 + 4);
-    const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-    const float sf[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+    float sc[8], sf[8];
+    load8(scale + c0, sc);
+    load8(shift + c0, sf);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float f = Cvt<T>::to_f(a.v[j]) * sc[j] + sf[j];
@@ -117,37 +175,46 @@ bn_fwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ res, const fl
   }
 }
 
-// Backward finalize: dgamma, dbeta and the three per-channel coefficients of dx.
-__global__ void bn_bwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int C, int64_t M,
-                                       const float* __restrict__ gamma, const float* __restrict__ invstd,
-                                       float* __restrict__ dgamma, float* __restrict__ dbeta, float* __restrict__ coef) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float s = 0.f, q = 0.f;
-  for (int b = 0; b < nblocks; ++b) { s += partial[((int64_t)b * 2) * C + c]; q += partial[((int64_t)b * 2 + 1) * C + c]; }
-  dbeta[c] = s;
-  dgamma[c] = q;
-  coef[c] = gamma[c] * invstd[c];
-  coef[C + c] = s / (float)M;
-  coef[2 * C + c] = q / (float)M;
+// Backward finalize: dgamma, dbeta and the per-channel coefficients of dx = A*dy' + B*x + D.
+// coef layout: [A | B | D], each C floats.
+__global__ void __launch_bounds__(kFinX * kFinY)
+bn_bwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int C, int64_t M, const void* __restrict__ gamma,
+                       int pdtype, const float* __restrict__ mean, const float* __restrict__ invstd,
+                       void* __restrict__ dgamma, void* __restrict__ dbeta, float* __restrict__ coef) {
+  float s, q;
+  if (!finalize_sums(partial, nblocks, C, s, q)) return;
+  const int c = blockIdx.x * kFinX + threadIdx.x;
+  store_param(dbeta, pdtype, c, s);
+  store_param(dgamma, pdtype, c, q);
+  const float is = invstd[c], mu = mean[c];
+  const float A = load_param(gamma, pdtype, c) * is;
+  const float ms = s / (float)M, mq = q / (float)M;
+  coef[c] = A;
+  coef[C + c] = -A * mq * is;
+  coef[2 * C + c] = A * (mu * is * mq - ms);
 }
 
-template <typename T, bool kRelu, bool kRes>
+template <typename T, int kRelu, bool kRes>
 __global__ void __launch_bounds__(256)
 bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ y,
-                    const float* __restrict__ mean, const float* __restrict__ invstd, const float* __restrict__ coef,
+                    const float* __restrict__ scale, const float* __restrict__ shift, const float* __restrict__ coef,
                     T* __restrict__ dx, T* __restrict__ dres, int64_t nvec, int L, int C) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
     const int c0 = (int)(i % L) * 8;
     Vec16<T> a = ld16(x + i * 8), g = ld16(dy + i * 8), o, od, yy;
-    if (kRelu) yy = ld16(y + i * 8);
+    if (kRelu == kReluFromY) yy = ld16(y + i * 8);
+    float A[8], B[8], D[8], sc[8], sf[8];
+    load8(coef + c0, A);
+    load8(coef + C + c0, B);
+    load8(coef + 2 * C + c0, D);
+    if (kRelu == kReluFromX) { load8(scale + c0, sc); load8(shift + c0, sf); }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int c = c0 + j;
+      const float xv = Cvt<T>::to_f(a.v[j]);
       float d = Cvt<T>::to_f(g.v[j]);
-      if (kRelu && !(Cvt<T>::to_f(yy.v[j]) > 0.f)) d = 0.f;
-      float xh = (Cvt<T>::to_f(a.v[j]) - mean[c]) * invstd[c];
-      o.v[j] = Cvt<T>::from_f(coef[c] * (d - coef[C + c] - xh * coef[2 * C + c]));
+      if (kRelu == kReluFromY) { if (!(Cvt<T>::to_f(yy.v[j]) > 0.f)) d = 0.f; }
+      else if (kRelu == kReluFromX) { if (!(xv * sc[j] + sf[j] > 0.f)) d = 0.f; }
+      o.v[j] = Cvt<T>::from_f(A[j] * d + B[j] * xv + D[j]);
       if (kRes) od.v[j] = Cvt<T>::from_f(d);
     }
     st16(dx + i * 8, o);
@@ -162,21 +229,27 @@ inline int bn_grid(int64_t M, int C) {
   return (int)(need < cap ? (need < 1 ? 1 : need) : cap);
 }
 
-template <typename T>
-int bn_forward_t(const T* x, const T* res, const float* gamma, const float* beta, float* rmean, float* rvar,
-                 float* save_mean, float* save_invstd, float* scratch, T* y, int64_t M, int C, float eps, float momentum,
-                 int training, int relu, cudaStream_t st) {
-  const int grid = bn_grid(M, C);
-  float* partial = scratch;                         // [grid][2][C]
-  float* scale = scratch + (int64_t)grid * 2 * C;   // [C]
-  float* shift = scale + C;                         // [C]
-  if (training) bn_reduce_kernel<T, false, false><<<grid, kBnThreads, 0, st>>>(x, nullptr, nullptr, nullptr, nullptr, M, C, partial);
-  bn_fwd_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(partial, grid, C, M, eps, momentum, gamma, beta, rmean, rvar,
-                                                          save_mean, save_invstd, scale, shift, training);
-  const int64_t nvec = M * (C >> 3);
+inline int apply_grid(int64_t nvec) {
   int64_t blocks = (nvec + 255) / 256;
   int64_t cap = (int64_t)sm_count() * 8;
-  int g2 = (int)(blocks < cap ? blocks : cap);
+  return (int)(blocks < cap ? blocks : cap);
+}
+
+// scratch layout (floats): [grid][2][C] partials | scale[C] | shift[C] | coef[3][C]
+template <typename T>
+int bn_forward_t(const T* x, const T* res, const void* gamma, const void* beta, int pdtype, float* rmean, float* rvar,
+                 float* save_mean, float* save_invstd, float* scale_shift, float* scratch, T* y, int64_t M, int C, float eps,
+                 float momentum, int training, int relu, cudaStream_t st) {
+  const int grid = bn_grid(M, C);
+  float* scale = scale_shift;
+  float* shift = scale_shift + C;
+  if (training)
+    bn_reduce_kernel<T, false, kReluNone><<<grid, kBnThreads, 0, st>>>(x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                                                                       M, C, scratch);
+  bn_fwd_finalize_kernel<<<(C + kFinX - 1) / kFinX, dim3(kFinX, kFinY), 0, st>>>(
+      scratch, grid, C, M, eps, momentum, gamma, beta, pdtype, rmean, rvar, save_mean, save_invstd, scale, shift, training);
+  const int64_t nvec = M * (C >> 3);
+  const int g2 = apply_grid(nvec);
   const int L = C >> 3;
   if (relu && res) bn_fwd_apply_kernel<T, true, true><<<g2, 256, 0, st>>>(x, res, scale, shift, y, nvec, L);
   else if (relu) bn_fwd_apply_kernel<T, true, false><<<g2, 256, 0, st>>>(x, res, scale, shift, y, nvec, L);
@@ -186,24 +259,31 @@ int bn_forward_t(const T* x, const T* res, const float* gamma, const float* beta
 }
 
 template <typename T>
-int bn_backward_t(const T* x, const T* dy, const T* y, const float* gamma, const float* save_mean,
-                  const float* save_invstd, float* scratch, T* dx, T* dres, float* dgamma, float* dbeta, int64_t M, int C,
-                  int relu, cudaStream_t st) {
+int bn_backward_t(const T* x, const T* dy, const T* y, const void* gamma, int pdtype, const float* save_mean,
+                  const float* save_invstd, const float* scale_shift, float* scratch, T* dx, T* dres, void* dgamma,
+                  void* dbeta, int64_t M, int C, int relu, cudaStream_t st) {
   const int grid = bn_grid(M, C);
   float* partial = scratch;
   float* coef = scratch + (int64_t)grid * 2 * C;    // [3][C]
-  if (relu) bn_reduce_kernel<T, true, true><<<grid, kBnThreads, 0, st>>>(x, dy, y, save_mean, save_invstd, M, C, partial);
-  else bn_reduce_kernel<T, true, false><<<grid, kBnThreads, 0, st>>>(x, dy, y, save_mean, save_invstd, M, C, partial);
-  bn_bwd_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(partial, grid, C, M, gamma, save_invstd, dgamma, dbeta, coef);
+  const float* scale = scale_shift;
+  const float* shift = scale_shift + C;
+  // a residual output means y = relu(bn(x) + res): the mask must come from y
+  const int mode = !relu ? kReluNone : (dres ? kReluFromY : kReluFromX);
+  if (mode == kReluFromY)
+    bn_reduce_kernel<T, true, kReluFromY><<<grid, kBnThreads, 0, st>>>(x, dy, y, save_mean, save_invstd, scale, shift, M, C, partial);
+  else if (mode == kReluFromX)
+    bn_reduce_kernel<T, true, kReluFromX><<<grid, kBnThreads, 0, st>>>(x, dy, y, save_mean, save_invstd, scale, shift, M, C, partial);
+  else
+    bn_reduce_kernel<T, true, kReluNone><<<grid, kBnThreads, 0, st>>>(x, dy, y, save_mean, save_invstd, scale, shift, M, C, partial);
+  bn_bwd_finalize_kernel<<<(C + kFinX - 1) / kFinX, dim3(kFinX, kFinY), 0, st>>>(partial, grid, C, M, gamma, pdtype, save_mean,
+                                                                               save_invstd, dgamma, dbeta, coef);
   const int64_t nvec = M * (C >> 3);
-  int64_t blocks = (nvec + 255) / 256;
-  int64_t cap = (int64_t)sm_count() * 8;
-  int g2 = (int)(blocks < cap ? blocks : cap);
+  const int g2 = apply_grid(nvec);
   const int L = C >> 3;
-  if (relu && dres) bn_bwd_apply_kernel<T, true, true><<<g2, 256, 0, st>>>(x, dy, y, save_mean, save_invstd, coef, dx, dres, nvec, L, C);
-  else if (relu) bn_bwd_apply_kernel<T, true, false><<<g2, 256, 0, st>>>(x, dy, y, save_mean, save_invstd, coef, dx, dres, nvec, L, C);
-  else if (dres) bn_bwd_apply_kernel<T, false, true><<<g2, 256, 0, st>>>(x, dy, y, save_mean, save_invstd, coef, dx, dres, nvec, L, C);
-  else bn_bwd_apply_kernel<T, false, false><<<g2, 256, 0, st>>>(x, dy, y, save_mean, save_invstd, coef, dx, dres, nvec, L, C);
+  if (mode == kReluFromY && dres) bn_bwd_apply_kernel<T, kReluFromY, true><<<g2, 256, 0, st>>>(x, dy, y, scale, shift, coef, dx, dres, nvec, L, C);
+  else if (mode == kReluFromX) bn_bwd_apply_kernel<T, kReluFromX, false><<<g2, 256, 0, st>>>(x, dy, y, scale, shift, coef, dx, dres, nvec, L, C);
+  else if (dres) bn_bwd_apply_kernel<T, kReluNone, true><<<g2, 256, 0, st>>>(x, dy, y, scale, shift, coef, dx, dres, nvec, L, C);
+  else bn_bwd_apply_kernel<T, kReluNone, false><<<g2, 256, 0, st>>>(x, dy, y, scale, shift, coef, dx, dres, nvec, L, C);
   return (int)cudaGetLastError();
 }
 
@@ -313,36 +393,43 @@ inline int ln_grid(int64_t rows) {
 
 using namespace mxb;
 
-// Number of CTAs the BatchNorm reductions use for (M, C): the caller sizes the scratch buffer as
-// (grid * 2 + 3) * C floats.
+// Number of CTAs the BatchNorm reductions use for (M, C); scratch sizes are stated at each entry point.
 MXB_EXPORT int mxb_bn_grid(int64_t M, int C) { return bn_grid(M, C); }
 MXB_EXPORT int mxb_ln_grid(int64_t rows) { return ln_grid(rows); }
 
-MXB_EXPORT int mxb_bn_forward(int dtype, const void* x, const void* res, const float* gamma, const float* beta,
-                              float* rmean, float* rvar, float* save_mean, float* save_invstd, float* scratch, void* y,
-                              int64_t M, int C, float eps, float momentum, int training, int relu, void* stream) {
+// x, res, y: [M, C] of `dtype` (fp16 / bf16).  gamma, beta: C values of `pdtype`.  rmean, rvar, save_mean,
+// save_invstd: C floats.  scale_shift: 2*C floats written here and read again by the backward pass.
+// scratch: mxb_bn_grid(M, C) * 2 * C floats.
+MXB_EXPORT int mxb_bn_forward(int dtype, const void* x, const void* res, const void* gamma, const void* beta, int pdtype,
+                              float* rmean, float* rvar, float* save_mean, float* save_invstd, float* scale_shift,
+                              float* scratch, void* y, int64_t M, int C, float eps, float momentum, int training, int relu,
+                              void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
+  if (pdtype != kF32 && pdtype != kF16 && pdtype != kBF16) return -1;
   if (dtype == kF16)
-    return bn_forward_t<__half>((const __half*)x, (const __half*)res, gamma, beta, rmean, rvar, save_mean, save_invstd,
-                                scratch, (__half*)y, M, C, eps, momentum, training, relu, st);
+    return bn_forward_t<__half>((const __half*)x, (const __half*)res, gamma, beta, pdtype, rmean, rvar, save_mean,
+                                save_invstd, scale_shift, scratch, (__half*)y, M, C, eps, momentum, training, relu, st);
   if (dtype == kBF16)
-    return bn_forward_t<__nv_bfloat16>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, gamma, beta, rmean, rvar,
-                                       save_mean, save_invstd, scratch, (__nv_bfloat16*)y, M, C, eps, momentum, training,
-                                       relu, st);
+    return bn_forward_t<__nv_bfloat16>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, gamma, beta, pdtype, rmean, rvar,
+                                       save_mean, save_invstd, scale_shift, scratch, (__nv_bfloat16*)y, M, C, eps, momentum,
+                                       training, relu, st);
   return -1;
 }
 
-MXB_EXPORT int mxb_bn_backward(int dtype, const void* x, const void* dy, const void* y, const float* gamma,
-                               const float* save_mean, const float* save_invstd, float* scratch, void* dx, void* dres,
-                               float* dgamma, float* dbeta, int64_t M, int C, int relu, void* stream) {
+// scratch: (mxb_bn_grid(M, C) * 2 + 3) * C floats.  dgamma, dbeta: C values of `pdtype`.  `y` is read only when
+// relu != 0 and dres != nullptr (the mask of BN+add+ReLU); `dres` receives the gradient of the residual input.
+MXB_EXPORT int mxb_bn_backward(int dtype, const void* x, const void* dy, const void* y, const void* gamma, int pdtype,
+                               const float* save_mean, const float* save_invstd, const float* scale_shift, float* scratch,
+                               void* dx, void* dres, void* dgamma, void* dbeta, int64_t M, int C, int relu, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
+  if (pdtype != kF32 && pdtype != kF16 && pdtype != kBF16) return -1;
   if (dtype == kF16)
-    return bn_backward_t<__half>((const __half*)x, (const __half*)dy, (const __half*)y, gamma, save_mean, save_invstd,
-                                 scratch, (__half*)dx, (__half*)dres, dgamma, dbeta, M, C, relu, st);
+    return bn_backward_t<__half>((const __half*)x, (const __half*)dy, (const __half*)y, gamma, pdtype, save_mean, save_invstd,
+                                 scale_shift, scratch, (__half*)dx, (__half*)dres, dgamma, dbeta, M, C, relu, st);
   if (dtype == kBF16)
     return bn_backward_t<__nv_bfloat16>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)y, gamma,
-                                        save_mean, save_invstd, scratch, (__nv_bfloat16*)dx, (__nv_bfloat16*)dres, dgamma,
-                                        dbeta, M, C, relu, st);
+                                        pdtype, save_mean, save_invstd, scale_shift, scratch, (__nv_bfloat16*)dx,
+                                        (__nv_bfloat16*)dres, dgamma, dbeta, M, C, relu, st);
   return -1;
 }
 

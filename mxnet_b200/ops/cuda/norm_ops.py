@@ -2,7 +2,7 @@
 import torch
 
 from . import lib, ptr, stream_ptr, count_launch, check
-from ._util import dt, f32
+from ._util import DT, dt, f32, require
 
 
 def bn_supported(x):
@@ -17,58 +17,73 @@ class _BatchNormNHWC(torch.autograd.Function):
         L = lib()
         C = x.shape[-1]
         M = x.numel() // C
-        grid = L.mxb_bn_grid(M, C)
-        scratch = torch.empty((grid * 2 + 3) * C, dtype=torch.float32, device=x.device)
-        save_mean = torch.empty(C, dtype=torch.float32, device=x.device)
-        save_invstd = torch.empty(C, dtype=torch.float32, device=x.device)
-        y = torch.empty_like(x)
-        g32, b32 = f32(gamma), f32(beta)
+        require(x, 'data')
+        if gamma.dtype != beta.dtype or gamma.dtype not in DT:
+            gamma, beta = gamma.float(), beta.float()
+        gamma, beta = gamma.contiguous(), beta.contiguous()
+        for t, name in ((gamma, 'gamma'), (beta, 'beta')):
+            require(t, name, numel=C, device=x.device)
+        for t, name in ((rmean, 'moving_mean'), (rvar, 'moving_var')):
+            require(t, name, numel=C, dtype=torch.float32, device=x.device)
         res = residual.contiguous() if residual is not None else None
-        check(L.mxb_bn_forward(dt(x), ptr(x), ptr(res), ptr(g32), ptr(b32), ptr(rmean), ptr(rvar), ptr(save_mean),
-                               ptr(save_invstd), ptr(scratch), ptr(y), M, C, eps, momentum, 1 if training else 0,
-                               1 if relu else 0, stream_ptr(x.device)), 'bn_forward')
+        if res is not None:
+            require(res, 'residual', dtype=x.dtype, device=x.device, shape=x.shape)
+        grid = L.mxb_bn_grid(M, C)
+        scratch = torch.empty(grid * 2 * C, dtype=torch.float32, device=x.device)
+        stats = torch.empty(4 * C, dtype=torch.float32, device=x.device)    # mean | invstd | scale | shift
+        save_mean, save_invstd, scale_shift = stats[:C], stats[C:2 * C], stats[2 * C:]
+        y = torch.empty_like(x)
+        check(L.mxb_bn_forward(dt(x), ptr(x), ptr(res), ptr(gamma), ptr(beta), dt(gamma), ptr(rmean), ptr(rvar),
+                               ptr(save_mean), ptr(save_invstd), ptr(scale_shift), ptr(scratch), ptr(y), M, C, eps,
+                               momentum, 1 if training else 0, 1 if relu else 0, stream_ptr(x.device)), 'bn_forward')
         count_launch(3 if training else 2)
-        ctx.save_for_backward(x, y if relu else None, g32, save_mean, save_invstd)
+        ctx.save_for_backward(x, y if (relu and residual is not None) or not training else None, gamma, stats)
         ctx.relu, ctx.has_res, ctx.training = relu, residual is not None, training
-        ctx.gdtype, ctx.bdtype = gamma.dtype, beta.dtype
+        ctx.set_materialize_grads(False)
         ctx.mark_non_differentiable(save_mean, save_invstd)
         return y, save_mean, save_invstd
 
     @staticmethod
     def backward(ctx, dy, _gm, _gv):
-        x, y, g32, save_mean, save_invstd = ctx.saved_tensors
+        x, y, gamma, stats = ctx.saved_tensors
+        if dy is None:
+            return (None,) * 10
         L = lib()
         C = x.shape[-1]
         M = x.numel() // C
-        dy = dy.contiguous()
+        save_mean, save_invstd, scale_shift = stats[:C], stats[C:2 * C], stats[2 * C:]
+        dy = require(dy.contiguous(), 'out_grad', dtype=x.dtype, device=x.device, shape=x.shape)
         if not ctx.training:
             # inference statistics are constants: dx = dy' * gamma * invstd
             d = dy
             if ctx.relu:
                 d = d * (y > 0).to(d.dtype)
-            scale = (g32 * save_invstd).to(d.dtype)
+            scale = (gamma.float() * save_invstd).to(d.dtype)
             dx = d * scale
             xh = (x.float() - save_mean) * save_invstd
             dgamma = (d.float() * xh).reshape(-1, C).sum(0)
             dbeta = d.float().reshape(-1, C).sum(0)
-            return dx, dgamma.to(ctx.gdtype), dbeta.to(ctx.bdtype), None, None, (d if ctx.has_res else None), None, None, None, None
+            return dx, dgamma.to(gamma.dtype), dbeta.to(gamma.dtype), None, None, (d if ctx.has_res else None), None, None, None, None
         grid = L.mxb_bn_grid(M, C)
         scratch = torch.empty((grid * 2 + 3) * C, dtype=torch.float32, device=x.device)
         dx = torch.empty_like(x)
         dres = torch.empty_like(x) if ctx.has_res else None
-        dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
-        dbeta = torch.empty(C, dtype=torch.float32, device=x.device)
-        check(L.mxb_bn_backward(dt(x), ptr(x), ptr(dy), ptr(y), ptr(g32), ptr(save_mean), ptr(save_invstd), ptr(scratch),
-                                ptr(dx), ptr(dres), ptr(dgamma), ptr(dbeta), M, C, 1 if ctx.relu else 0,
-                                stream_ptr(x.device)), 'bn_backward')
+        dgb = torch.empty(2 * C, dtype=gamma.dtype, device=x.device)
+        dgamma, dbeta = dgb[:C], dgb[C:]
+        check(L.mxb_bn_backward(dt(x), ptr(x), ptr(dy), ptr(y), ptr(gamma), dt(gamma), ptr(save_mean), ptr(save_invstd),
+                                ptr(scale_shift), ptr(scratch), ptr(dx), ptr(dres), ptr(dgamma), ptr(dbeta), M, C,
+                                1 if ctx.relu else 0, stream_ptr(x.device)), 'bn_backward')
         count_launch(3)
-        return dx, dgamma.to(ctx.gdtype), dbeta.to(ctx.bdtype), None, None, dres, None, None, None, None
+        return dx, dgamma, dbeta, None, None, dres, None, None, None, None
 
 
-def batch_norm_nhwc(x, gamma, beta, rmean, rvar, eps, momentum, training, act_type, residual):
-    """Returns (y, mean, var) like the BatchNorm operator with ``output_mean_var``."""
+def batch_norm_nhwc(x, gamma, beta, rmean, rvar, eps, momentum, training, act_type, residual, want_stats=True):
+    """Returns (y, mean, var) like the BatchNorm operator with ``output_mean_var``; ``want_stats=False``
+    skips the conversion of the saved inverse standard deviation back to a variance."""
     y, mean, invstd = _BatchNormNHWC.apply(x, gamma, beta, rmean, rvar, residual, float(eps), float(momentum),
                                            bool(training), act_type == 'relu')
+    if not want_stats:
+        return y, None, None
     var = 1.0 / (invstd * invstd) - eps
     return y, mean, var
 
@@ -87,6 +102,9 @@ class _LayerNorm(torch.autograd.Function):
         mean = torch.empty(rows, dtype=torch.float32, device=x.device)
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
         g32, b32 = f32(gamma), f32(beta)
+        require(x, 'data')
+        require(g32, 'gamma', numel=C, device=x.device)
+        require(b32, 'beta', numel=C, device=x.device)
         check(L.mxb_ln_forward(dt(x), ptr(x), ptr(g32), ptr(b32), ptr(y), ptr(mean), ptr(rstd), rows, C, eps,
                                stream_ptr(x.device)), 'ln_forward')
         count_launch(1)
@@ -100,7 +118,7 @@ class _LayerNorm(torch.autograd.Function):
         L = lib()
         C = x.shape[-1]
         rows = x.numel() // C
-        dy = dy.contiguous()
+        dy = require(dy.contiguous(), 'out_grad', dtype=x.dtype, device=x.device, shape=x.shape)
         dx = torch.empty_like(x)
         dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
         dbeta = torch.empty(C, dtype=torch.float32, device=x.device)

@@ -4,7 +4,7 @@ import ctypes as C
 import torch
 
 from . import lib, ptr, stream_ptr, count_launch, check
-from ._util import DT
+from ._util import DT, require
 
 
 def _parr(tensors):
@@ -19,6 +19,14 @@ def multi_sgd(ws, gs, moms, w32, lrs, wds, momentum, rescale, clip):
         sl = slice(i, i + cap)
         w, g = ws[sl], gs[sl]
         n = len(w)
+        dev = w[0].device
+        for j in range(n):
+            require(w[j], 'weight', dtype=dtype, device=dev)
+            require(g[j], 'grad', numel=w[j].numel(), dtype=dtype, device=dev)
+            if moms is not None:
+                require(moms[i + j], 'mom', numel=w[j].numel(), dtype=torch.float32, device=dev)
+            if w32 is not None:
+                require(w32[i + j], 'weight32', numel=w[j].numel(), dtype=torch.float32, device=dev)
         m = _parr(moms[sl]) if moms is not None else None
         mp = _parr(w32[sl]) if w32 is not None else None
         check(L.mxb_multi_sgd(DT[dtype], n, _parr(w), _parr(g), m, mp, (C.c_float * n)(*lrs[sl]), (C.c_float * n)(*wds[sl]),

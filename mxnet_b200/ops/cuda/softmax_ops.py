@@ -2,7 +2,7 @@
 import torch
 
 from . import lib, ptr, stream_ptr, count_launch, check
-from ._util import dt
+from ._util import dt, require
 
 
 def supported(x):
@@ -15,6 +15,7 @@ class _Softmax(torch.autograd.Function):
         L = lib()
         C = x.shape[-1]
         rows = x.numel() // C
+        require(x, 'data')
         y = torch.empty_like(x)
         check(L.mxb_softmax_forward(dt(x), ptr(x), ptr(y), rows, C, 1 if log else 0, stream_ptr(x.device)), 'softmax_forward')
         count_launch(1)
@@ -28,7 +29,7 @@ class _Softmax(torch.autograd.Function):
         L = lib()
         C = y.shape[-1]
         rows = y.numel() // C
-        dy = dy.contiguous()
+        dy = require(dy.contiguous(), 'out_grad', dtype=y.dtype, device=y.device, shape=y.shape)
         dx = torch.empty_like(y)
         check(L.mxb_softmax_backward(dt(y), ptr(y), ptr(dy), ptr(dx), rows, C, 1 if ctx.log else 0, stream_ptr(y.device)),
               'softmax_backward')
@@ -46,7 +47,8 @@ class _SoftmaxCE(torch.autograd.Function):
         L = lib()
         C = x.shape[-1]
         rows = x.numel() // C
-        lab = label.reshape(-1).to(torch.int64).contiguous()
+        require(x, 'data')
+        lab = require(label.reshape(-1).to(torch.int64).contiguous(), 'label', numel=rows, device=x.device)
         loss = torch.empty(rows, dtype=torch.float32, device=x.device)
         lse = torch.empty(rows, dtype=torch.float32, device=x.device)
         use_ignore = ignore_label is not None
@@ -64,7 +66,7 @@ class _SoftmaxCE(torch.autograd.Function):
         L = lib()
         C = x.shape[-1]
         rows = x.numel() // C
-        g = gout.reshape(-1).float().contiguous()
+        g = require(gout.reshape(-1).float().contiguous(), 'out_grad', numel=rows, device=x.device)
         dx = torch.empty_like(x)
         use_ignore = ctx.ignore is not None
         check(L.mxb_softmax_ce_backward(dt(x), ptr(x), ptr(lab), ptr(lse), ptr(g), ptr(dx), rows, C,

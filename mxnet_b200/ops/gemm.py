@@ -14,7 +14,7 @@ from .. import env
 def _kernel_ok(a, b):
     if not (a.is_cuda and b.is_cuda) or a.dtype != b.dtype or a.dtype not in (torch.float16, torch.bfloat16):
         return False
-    if not env.get('MXNET_B200_KERNELS'):
+    if not (env.get('MXNET_B200_KERNELS') and env.get('MXNET_B200_GEMM')):
         return False
     from . import cuda
     return cuda.available()

@@ -152,9 +152,10 @@ def batch_norm(data, gamma, beta, moving_mean, moving_var, residual=None, eps=1e
     if axis == data.dim() - 1 and data.dim() == 4 and _use_kernels(data) and \
             data.dtype in (torch.float16, torch.bfloat16) and data.is_contiguous():
         from .cuda import norm_ops
-        if norm_ops.bn_supported(data):
+        if norm_ops.bn_supported(data) and moving_mean.dtype == torch.float32 and moving_var.dtype == torch.float32 \
+                and moving_mean.is_contiguous() and moving_var.is_contiguous():
             out, mean, var = norm_ops.batch_norm_nhwc(data, gamma, beta, moving_mean, moving_var, eps, momentum,
-                                                      training, act_type, residual)
+                                                      training, act_type, residual, want_stats=bool(output_mean_var))
             return (out, mean, var) if output_mean_var else out
     red = tuple(i for i in range(data.dim()) if i != axis)
     shape = [1] * data.dim()
@@ -272,6 +273,12 @@ def lrn(data, alpha=1e-4, beta=0.75, knorm=2.0, nsize=5):
 def pooling(data, kernel=(), pool_type='max', global_pool=False, cudnn_off=False, pooling_convention='valid',
             stride=(), pad=(), p_value=None, count_include_pad=None, layout=None, output_size=None):
     nsp = data.dim() - 2
+    if layout in _CHANNEL_LAST and nsp == 2 and pool_type == 'max' and not global_pool and _use_kernels(data) \
+            and pooling_convention in ('valid', 'full'):
+        from .cuda import pool_ops
+        k2, s2, p2 = _tup(kernel, 2), _tup(stride, 2) or (1, 1), _tup(pad, 2) or (0, 0)
+        if pool_ops.supported(data, k2, s2, p2):
+            return pool_ops.max_pool2d_nhwc(data, k2, s2, p2, pooling_convention == 'full')
     x = _to_channel_first(data, layout)
     if global_pool:
         red = tuple(range(2, x.dim()))

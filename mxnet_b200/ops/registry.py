@@ -172,6 +172,11 @@ def invoke(op, args, attrs, out=None, kind=None):
     tracer = st.tracer
     if tracer is not None:
         tracer.record(op, args, attrs, wrapped)
+    elif st.recording:
+        # provenance for autograd.get_symbol: which operator call produced each recorded output
+        for i, o in enumerate(wrapped):
+            if isinstance(o, base):
+                o._prov = (op, args, attrs, i, len(wrapped))
     mon = _state.op_monitor
     if mon is not None:
         mon(op.name, wrapped)

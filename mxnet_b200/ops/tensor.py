@@ -1058,14 +1058,14 @@ def np_nonzero(data):
 def sort(data, axis=-1, is_ascend=True):
     if axis is None:
         data, axis = data.reshape(-1), 0
-    return torch.sort(data, axis, descending=not is_ascend, stable=True)[0]
+    return torch.sort(data, dim=axis, descending=not is_ascend, stable=True)[0]
 
 
 @register('argsort', '_npi_argsort', inputs=('data',), defaults={'axis': -1, 'is_ascend': True, 'dtype': 'float32'})
 def argsort(data, axis=-1, is_ascend=True, dtype='float32'):
     if axis is None:
         data, axis = data.reshape(-1), 0
-    return torch.sort(data, axis, descending=not is_ascend, stable=True)[1].to(to_torch_dtype(dtype))
+    return torch.sort(data, dim=axis, descending=not is_ascend, stable=True)[1].to(to_torch_dtype(dtype))
 
 
 def _topk_nout(attrs):

@@ -22,6 +22,9 @@ class Updater(object):
             indices, grads, weights = [index], [grad], [weight]
         else:
             indices, grads, weights = list(index), list(grad), list(weight)
+        if weights:
+            # update counts are kept per device (updater.py:51), so replicas advance `t` in lock step
+            self.optimizer._set_current_device(weights[0].context.device_id)
         for i, idx in enumerate(indices):
             if isinstance(idx, bytes):
                 indices[i] = idx = idx.decode('utf-8')

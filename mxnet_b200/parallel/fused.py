@@ -71,7 +71,7 @@ def supports(optimizer, params):
         if p._data is None or p._stype != 'default' or p._grad_stype != 'default':
             return False
         arr = next(iter(p._data.values()))
-        if not arr._data.is_cuda:
+        if not arr._data.is_cuda or arr._data.numel() == 0:
             return False
         dtypes.add(arr._data.dtype)
     if len(dtypes) != 1:
@@ -124,15 +124,18 @@ class FusedStep(object):
             raise MXNetError('cudaMalloc of the parameter arena failed: %s' % L.mxb_error_string(rc).decode())
         self.slab = ptr.value
         self._w_off, self._g_off = self.ctrl_bytes, self.ctrl_bytes + arena_bytes
-        self._buf = _DevBuf(self.slab, self.slab_bytes)
-        raw = torch.as_tensor(self._buf, device=self.device)
-        self._raw = raw
-        self.ctrl = raw[:self.ctrl_bytes]
-        self.weights = raw[self._w_off:self._w_off + arena_bytes].view(self.dtype)
-        self.grads = raw[self._g_off:self._g_off + arena_bytes].view(self.dtype)
+        # Each tensor below wraps its own piece of the slab as an independent storage: tensors that were
+        # views of one base would share a version counter, and the in-place gradient accumulation of one
+        # parameter would then invalidate every weight the autograd graph has saved for backward.
+        self._bufs = []
+        self.ctrl = self._blob(0, self.ctrl_bytes)
+        self.weights = self._blob(self._w_off, arena_bytes).view(self.dtype)
+        self.grads = self._blob(self._g_off, arena_bytes).view(self.dtype)
         for p, off, n in zip(self.params, offs, self.sizes):
             shape = p._data[ctx]._data.shape
-            p._rebind(ctx, self.weights[off:off + n].view(shape), self.grads[off:off + n].view(shape))
+            w = self._blob(self._w_off + off * self.esize, n * self.esize).view(self.dtype).view(shape)
+            g = self._blob(self._g_off + off * self.esize, n * self.esize).view(self.dtype).view(shape)
+            p._rebind(ctx, w, g)
         # ---- peers ---------------------------------------------------------------------------------
         self.peer_base = [self.slab] * self.nranks
         self._opened = []
@@ -179,6 +182,7 @@ class FusedStep(object):
         self._status_host = torch.zeros(2, dtype=torch.int32).pin_memory()
         self._status_event = None
         self._grad_arrays = [p._grad[ctx] for p in self.params]
+        self._data_arrays = [p._data[ctx] for p in self.params]
         self._scaler_attached = None
         self.max_norm = -1.0
         self._dt_code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[self.dtype]
@@ -187,6 +191,12 @@ class FusedStep(object):
         if self.nranks > 1:
             torch.cuda.synchronize(self.device)
             dist.barrier()
+
+    def _blob(self, byte_offset, nbytes):
+        """A uint8 tensor over ``nbytes`` of the slab starting at ``byte_offset`` (its own storage object)."""
+        buf = _DevBuf(self.slab + byte_offset, nbytes)
+        self._bufs.append(buf)
+        return torch.as_tensor(buf, device=self.device)
 
     # ------------------------------------------------------------------------------------------------
     def set_global_norm_clip(self, max_norm):
@@ -275,7 +285,7 @@ class FusedStep(object):
     def step(self, rescale, scaler=None):
         use_ls = self._attach_scaler(scaler)
         self._launch(rescale, self.mode, use_ls)
-        autograd.mark_grads_consumed(self._grad_arrays)
+        autograd.mark_grads_consumed(self._data_arrays)
 
     def allreduce_only(self):
         """Sum the gradient arenas of all ranks in place (``Trainer.allreduce_grads``)."""
@@ -286,7 +296,7 @@ class FusedStep(object):
         ranks is compensated by 1/nranks."""
         use_ls = self._attach_scaler(scaler)
         self._launch(rescale / self.nranks, self.mode, use_ls)
-        autograd.mark_grads_consumed(self._grad_arrays)
+        autograd.mark_grads_consumed(self._data_arrays)
 
     def wait_probe(self, timeout_ms=50):
         """Launch a wait on a flag that nothing sets and return the status code it leaves behind (the
