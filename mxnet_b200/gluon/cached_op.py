@@ -41,12 +41,13 @@ class _Graphed(object):
         self.ctx = arrays[0]._ctx
         dev = arrays[0]._data.device
         params = [p for p in block.collect_params().values() if p._data is not None]
-        self.param_tensors = []
+        self.param_arrays, self.param_tensors = [], []
         for p in params:
             arr = p._data.get(self.ctx)
             if arr is None:
                 arr = next(iter(p._data.values()))
             if arr._data.requires_grad:
+                self.param_arrays.append(arr)
                 self.param_tensors.append(arr._data)
         self.static_in = []
         for a in arrays:
@@ -54,14 +55,21 @@ class _Graphed(object):
             if recording and a._data.requires_grad:
                 t.requires_grad_(True)
             self.static_in.append(t)
-        self.grad_inputs = [t for t in self.static_in if t.requires_grad] + (self.param_tensors if recording else [])
+        stream = torch.cuda.Stream(device=dev)
+        stream.wait_stream(torch.cuda.current_stream(dev))
+        # The graphs differentiate with respect to fresh leaf aliases of the parameters (same storage).  The
+        # parameters' own gradient accumulators were created by earlier eager passes on the default stream;
+        # differentiating with respect to them would make the autograd engine order the legacy stream after
+        # the capturing stream, which stream capture forbids.  The aliases only ever see the capture stream,
+        # and they carry none of the parameters' Python hooks.
+        with torch.cuda.stream(stream):
+            self.alias = [t.detach().requires_grad_(True) for t in self.param_tensors] if recording else []
+        self.grad_inputs = [t for t in self.static_in if t.requires_grad] + self.alias
         from ..ops import cuda as _kernels
         self._kernels = _kernels
         self.pool = torch.cuda.graph_pool_handle()
         self.fwd = torch.cuda.CUDAGraph()
         n0 = _kernels.launches()
-        stream = torch.cuda.Stream(device=dev)
-        stream.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(stream):
             with torch.cuda.graph(self.fwd, pool=self.pool, stream=stream):
                 outs = self._run_forward()
@@ -96,6 +104,8 @@ class _Graphed(object):
             args = [args]
         prev_r, prev_t = _state.state.recording, _state.state.training
         _state.state.recording, _state.state.training = self.recording, self.training
+        for arr, a in zip(self.param_arrays, self.alias):
+            arr._data = a
         try:
             if self.recording:
                 with torch.enable_grad():
@@ -104,6 +114,9 @@ class _Graphed(object):
                 return self.block.forward(*args)
         finally:
             _state.state.recording, _state.state.training = prev_r, prev_t
+            if self.alias:
+                for arr, t in zip(self.param_arrays, self.param_tensors):
+                    arr._data = t
 
     def __call__(self, args):
         from .block import _flatten, _regroup
@@ -206,7 +219,8 @@ class CachedOp(object):
             g = _Graphed(self.block, args, _state.state.training, _state.state.recording)
         except Exception as e:  # pylint: disable=broad-except
             self._disabled = True
-            _log.warning('CUDA graph capture failed (%s); block %s runs eagerly', e, type(self.block).__name__)
+            _log.warning('CUDA graph capture failed (%s); block %s runs eagerly', e, type(self.block).__name__,
+                         exc_info=bool(env.get('MXNET_CUDA_GRAPHS_VERBOSE')))
             return self.block._call_forward(*args)
         self._graphs[sig] = g
         if env.get('MXNET_CUDA_GRAPHS_VERBOSE'):

@@ -236,7 +236,9 @@ class Parameter(object):
             with torch.no_grad():
                 grad_tensor.copy_(g._data)
             g._data = grad_tensor
+            fresh, last_pass = arr._fresh_grad, arr._grad_pass
             autograd.mark_variables([arr], [g], self.grad_req)
+            arr._fresh_grad, arr._grad_pass = fresh, last_pass       # the gradient moved with its history
         from . import block
         block._bump_storage_version()
 

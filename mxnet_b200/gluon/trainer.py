@@ -235,11 +235,11 @@ class Trainer(object):
             self._init_params()
         if self._fused is not None:
             if not ignore_stale_grad:
-                for arr in self._fused._data_arrays:
+                for p, arr in zip(self._fused.params, self._fused._data_arrays):
                     if not arr._fresh_grad:
-                        raise UserWarning('Gradient of a Parameter on device %s has not been updated by backward since '
-                                          'last `step`; call step with ignore_stale_grad=True to suppress this check'
-                                          % str(arr.context))
+                        raise UserWarning('Gradient of Parameter `%s` on device %s has not been updated by backward '
+                                          'since last `step`; call step with ignore_stale_grad=True to suppress this '
+                                          'check' % (p.name, str(arr.context)))
             self._fused.step(rescale_grad, self._amp_loss_scaler)
             return
         self._allreduce_grads()

@@ -24,7 +24,7 @@ def build(force=False, verbose=False):
     srcs = [s for s in SOURCES if os.path.exists(os.path.join(HERE, s))]
     bdir = os.path.join(HERE, 'build')
     os.makedirs(bdir, exist_ok=True)
-    deps = [os.path.join(HERE, 'common.cuh')]
+    deps = [os.path.join(HERE, h) for h in os.listdir(HERE) if h.endswith(('.cuh', '.h'))]
 
     def stale(obj, src):
         if force or not os.path.exists(obj):

@@ -717,9 +717,10 @@ def Group(symbols):
     return Symbol(outs)
 
 
-def _make_op_symbol(op, sym_inputs, attrs, name, user_attrs=None):
-    hint = op.name.lower().lstrip('_')
-    name = NameManager.current().get(name, hint)
+def _make_op_symbol(op, sym_inputs, attrs, name, user_attrs=None, resolved=False):
+    if not resolved:      # `resolved`: the caller already passed the name through the NameManager
+        hint = op.name.lower().lstrip('_')
+        name = NameManager.current().get(name, hint)
     inputs = []
     for s in sym_inputs:
         if s is None:
@@ -793,7 +794,7 @@ def _op_frontend(op):
                     raise MXNetError('operator %s needs input %s' % (op.name, nm))
                 s = var('%s_%s' % (name, nm))
             out_syms.append(s)
-        return _make_op_symbol(op, out_syms, attrs, name, user_attrs)
+        return _make_op_symbol(op, out_syms, attrs, name, user_attrs, resolved=True)
     fn.__name__ = op.name
     fn.__doc__ = op.doc
     return fn

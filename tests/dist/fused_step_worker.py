@@ -1,0 +1,79 @@
+"""Worker of the multi-GPU fused-step test: launched once per GPU by ``torch.distributed.run``.
+
+Every rank trains the same small network on its own slice of a fixed batch, once with the fused
+peer-memory optimizer step and once with the plain NCCL all-reduce + per-parameter update path, and
+rank 0 reports whether both runs agree and whether all ranks hold identical weights."""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+import mxnet_b200 as mx                                   # noqa: E402
+from mxnet_b200 import autograd, env, gluon, nd           # noqa: E402
+from mxnet_b200.gluon import nn                           # noqa: E402
+from mxnet_b200.parallel import dist                      # noqa: E402
+
+
+def build(ctx, dtype):
+    mx.random.seed(7)
+    np.random.seed(7)
+    net = nn.HybridSequential()
+    net.add(nn.Dense(96, activation='relu', in_units=48), nn.Dense(33, activation='relu', in_units=96),
+            nn.Dense(10, in_units=33))
+    net.initialize(mx.init.Xavier(), ctx=ctx)
+    if dtype != 'float32':
+        net.cast(dtype)
+    return net
+
+
+def run(fused, dtype, steps, ctx, rank, world):
+    with env.scope('MXNET_KVSTORE_FUSED', '1' if fused else '0'):
+        net = build(ctx, dtype)
+        trainer = gluon.Trainer(net.collect_params(), 'sgd', {'learning_rate': 0.05, 'momentum': 0.9, 'wd': 1e-3,
+                                                              'multi_precision': dtype != 'float32'}, kvstore='device')
+        loss_fn = gluon.loss.SoftmaxCrossEntropyLoss()
+        rng = np.random.RandomState(123)
+        per = 8
+        for step in range(steps):
+            x_all = rng.randn(per * world, 48).astype('float32')
+            y_all = rng.randint(0, 10, (per * world,))
+            x = nd.array(x_all[rank * per:(rank + 1) * per], ctx=ctx, dtype=dtype)
+            y = nd.array(y_all[rank * per:(rank + 1) * per], ctx=ctx)
+            with autograd.record():
+                loss = loss_fn(net(x), y)
+            loss.backward()
+            trainer.step(per * world)
+        torch.cuda.synchronize()
+        assert (trainer._fused is not None) == fused, 'fused path selection'
+        if fused:
+            trainer._fused._check_status()
+        return [p.data(ctx)._data.detach().float().clone() for p in net.collect_params().values()]
+
+
+def main():
+    dist.ensure_initialized('nccl')
+    rank, world = dist.rank(), dist.world_size()
+    torch.cuda.set_device(dist.local_rank())
+    ctx = mx.gpu(dist.local_rank())
+    report = {'world': world}
+    for dtype in ('float32', 'float16'):
+        w_fused = run(True, dtype, 6, ctx, rank, world)
+        w_plain = run(False, dtype, 6, ctx, rank, world)
+        err = max(float((a - b).abs().max()) for a, b in zip(w_fused, w_plain))
+        flat = torch.cat([w.reshape(-1) for w in w_fused])
+        gathered = [torch.empty_like(flat) for _ in range(world)]
+        torch.distributed.all_gather(gathered, flat)
+        same = all(bool(torch.equal(gathered[0], g)) for g in gathered)
+        report[dtype] = {'max_abs_diff_vs_nccl_path': err, 'ranks_identical': same}
+    if rank == 0:
+        print('REPORT ' + json.dumps(report))
+    dist.barrier()
+    dist.destroy()
+
+
+if __name__ == '__main__':
+    main()

@@ -1,0 +1,35 @@
+"""Multi-GPU checks (one process per GPU, launched as child processes)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _launch(script, nproc, port, extra_env=None, timeout=600):
+    env = dict(os.environ)
+    env.update({'NCCL_NVLS_ENABLE': '0'})
+    env.update(extra_env or {})
+    cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node', str(nproc),
+           '--master-addr', '127.0.0.1', '--master-port', str(port), os.path.join(HERE, 'dist', script)]
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+
+
+@pytest.mark.parametrize('nproc', [2, 4, 8])
+def test_fused_step_matches_nccl_path_across_ranks(nproc):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip('needs %d GPUs' % nproc)
+    r = _launch('fused_step_worker.py', nproc, 29611 + nproc)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith('REPORT ')][-1]
+    rep = json.loads(line[len('REPORT '):])
+    assert rep['world'] == nproc
+    assert rep['float32']['ranks_identical'] and rep['float16']['ranks_identical']
+    assert rep['float32']['max_abs_diff_vs_nccl_path'] < 1e-5
+    assert rep['float16']['max_abs_diff_vs_nccl_path'] < 5e-3

@@ -1,0 +1,172 @@
+"""Symbol graphs: composition, attributes, JSON round trip, shape/type inference, executors (reference:
+tests/python/unittest/test_symbol.py, test_executor.py, test_infer_shape.py)."""
+import json
+
+import numpy as np
+import pytest
+
+import mxnet_b200 as mx
+from mxnet_b200 import nd, sym
+from mxnet_b200.test_utils import assert_almost_equal, same
+
+
+def _mlp():
+    data = sym.Variable('data')
+    fc1 = sym.FullyConnected(data=data, name='fc1', num_hidden=16)
+    act = sym.Activation(data=fc1, name='relu1', act_type='relu')
+    fc2 = sym.FullyConnected(data=act, name='fc2', num_hidden=4)
+    return sym.SoftmaxOutput(data=fc2, name='softmax')
+
+
+def test_compose_and_list():
+    net = _mlp()
+    assert net.list_arguments() == ['data', 'fc1_weight', 'fc1_bias', 'fc2_weight', 'fc2_bias', 'softmax_label']
+    assert net.list_outputs() == ['softmax_output']
+    assert net.name == 'softmax'
+    internals = net.get_internals()
+    assert 'fc1_output' in internals.list_outputs()
+    fc1 = internals['fc1_output']
+    assert fc1.list_arguments() == ['data', 'fc1_weight', 'fc1_bias']
+    children = net.get_children()
+    assert children.list_outputs() == ['fc2_output', 'softmax_label']
+
+
+def test_json_round_trip_and_format():
+    net = _mlp()
+    js = net.tojson()
+    graph = json.loads(js)
+    assert set(graph) >= {'nodes', 'arg_nodes', 'node_row_ptr', 'heads', 'attrs'}
+    assert graph['attrs']['mxnet_version'][0] == 'int'
+    node = [n for n in graph['nodes'] if n['name'] == 'fc1'][0]
+    assert node['op'] == 'FullyConnected' and node['attrs'] == {'num_hidden': '16'}
+    assert node['inputs'] == [[0, 0, 0], [1, 0, 0], [2, 0, 0]]
+    assert [graph['nodes'][i]['op'] for i in graph['arg_nodes']] == ['null'] * len(graph['arg_nodes'])
+    back = sym.load_json(js)
+    assert back.list_arguments() == net.list_arguments()
+    assert json.loads(back.tojson())['nodes'] == graph['nodes']
+
+
+def test_attribute_stringification():
+    data = sym.Variable('data')
+    conv = sym.Convolution(data=data, kernel=(3, 3), num_filter=8, pad=(1, 1), no_bias=True, name='conv')
+    pool = sym.Pooling(data=conv, kernel=(2, 2), stride=(2, 2), pool_type='max', name='pool')
+    graph = json.loads(pool.tojson())
+    attrs = {n['name']: n.get('attrs', {}) for n in graph['nodes']}
+    assert attrs['conv'] == {'kernel': '(3, 3)', 'no_bias': 'True', 'num_filter': '8', 'pad': '(1, 1)'}
+    assert attrs['pool']['pool_type'] == 'max' and attrs['pool']['stride'] == '(2, 2)'
+    back = sym.load_json(pool.tojson())
+    arg_shapes, out_shapes, _ = back.infer_shape(data=(2, 3, 8, 8))
+    assert out_shapes == [(2, 8, 4, 4)]
+
+
+def test_load_reference_style_json():
+    """A graph written the way the reference serialises it (string attrs, legacy `param`/`attr` keys accepted)."""
+    js = json.dumps({
+        'nodes': [
+            {'op': 'null', 'name': 'data', 'inputs': []},
+            {'op': 'null', 'name': 'w', 'attrs': {'__shape__': '(5, 7)', '__lr_mult__': '2.0'}, 'inputs': []},
+            {'op': 'FullyConnected', 'name': 'fc', 'attrs': {'num_hidden': '5', 'no_bias': 'True', 'flatten': 'True'},
+             'inputs': [[0, 0, 0], [1, 0, 0]]},
+            {'op': 'Activation', 'name': 'act', 'attrs': {'act_type': 'tanh'}, 'inputs': [[2, 0, 0]]}],
+        'arg_nodes': [0, 1], 'node_row_ptr': [0, 1, 2, 3, 4], 'heads': [[3, 0, 0]],
+        'attrs': {'mxnet_version': ['int', 10600]}})
+    s = sym.load_json(js)
+    assert s.list_arguments() == ['data', 'w']
+    assert s.attr_dict()['w']['__lr_mult__'] == '2.0'
+    x, w = np.random.randn(3, 7).astype('float32'), np.random.randn(5, 7).astype('float32')
+    out = s.eval(data=nd.array(x), w=nd.array(w))[0]
+    assert_almost_equal(out.asnumpy(), np.tanh(x @ w.T), rtol=1e-5, atol=1e-6)
+
+
+def test_infer_shape_and_type():
+    net = _mlp()
+    arg_shapes, out_shapes, aux_shapes = net.infer_shape(data=(8, 10))
+    assert dict(zip(net.list_arguments(), arg_shapes)) == {
+        'data': (8, 10), 'fc1_weight': (16, 10), 'fc1_bias': (16,), 'fc2_weight': (4, 16), 'fc2_bias': (4,),
+        'softmax_label': (8,)}
+    assert out_shapes == [(8, 4)] and aux_shapes == []
+    arg_types, out_types, _ = net.infer_type(data='float32')
+    assert all(t == np.float32 for t in arg_types) and out_types == [np.float32]
+    data = sym.Variable('data')
+    bn = sym.BatchNorm(data=data, name='bn')
+    assert bn.list_auxiliary_states() == ['bn_moving_mean', 'bn_moving_var']
+    a, o, x = bn.infer_shape(data=(2, 5, 3, 3))
+    assert x == [(5,), (5,)] and o == [(2, 5, 3, 3)]
+    partial = net.infer_shape_partial()
+    assert partial[0][0] in ((), None) or partial[0][0] == ()
+
+
+def test_symbol_arithmetic_and_grouping():
+    a, b = sym.Variable('a'), sym.Variable('b')
+    c = (a + b) * 2 - a / b + a ** 2
+    av, bv = np.array([1., 2.], 'float32'), np.array([4., 5.], 'float32')
+    out = c.eval(a=nd.array(av), b=nd.array(bv))[0].asnumpy()
+    assert_almost_equal(out, (av + bv) * 2 - av / bv + av ** 2, rtol=1e-6)
+    g = sym.Group([a + b, a * b])
+    assert len(g.list_outputs()) == 2
+    o1, o2 = g.eval(a=nd.array(av), b=nd.array(bv))
+    assert same(o1.asnumpy(), av + bv) and same(o2.asnumpy(), av * bv)
+    assert g[1].list_outputs() == g.list_outputs()[1:]
+
+
+def test_simple_bind_forward_backward():
+    net = _mlp()
+    ex = net.simple_bind(mx.cpu(), data=(6, 10), grad_req='write')
+    for name, arr in ex.arg_dict.items():
+        if name.endswith('weight'):
+            arr[:] = nd.array(np.random.randn(*arr.shape) * 0.1)
+    x = np.random.randn(6, 10).astype('float32')
+    y = np.random.randint(0, 4, (6,)).astype('float32')
+    ex.arg_dict['data'][:] = nd.array(x)
+    ex.arg_dict['softmax_label'][:] = nd.array(y)
+    out = ex.forward(is_train=True)[0].asnumpy()
+    assert out.shape == (6, 4) and np.allclose(out.sum(1), 1, atol=1e-5)
+    ex.backward()
+    # SoftmaxOutput gradient w.r.t. its input is (p - onehot); chain to fc2_bias = column sums
+    p = out.copy()
+    p[np.arange(6), y.astype(int)] -= 1
+    assert_almost_equal(ex.grad_dict['fc2_bias'].asnumpy(), p.sum(0), rtol=1e-4, atol=1e-5)
+    assert float(abs(ex.grad_dict['fc1_weight']).sum().asscalar()) > 0
+
+
+def test_bind_with_explicit_arrays_and_grad_req_add():
+    a, b = sym.Variable('a'), sym.Variable('b')
+    c = a * b
+    av, bv = nd.array([1., 2., 3.]), nd.array([4., 5., 6.])
+    ga, gb = nd.zeros((3,)), nd.zeros((3,))
+    ex = c.bind(mx.cpu(), args={'a': av, 'b': bv}, args_grad={'a': ga, 'b': gb}, grad_req='add')
+    for _ in range(2):
+        ex.forward(is_train=True)
+        ex.backward(out_grads=nd.ones((3,)))
+    assert same(ga.asnumpy(), 2 * bv.asnumpy()) and same(gb.asnumpy(), 2 * av.asnumpy())
+
+
+def test_variable_attributes_and_scopes():
+    with mx.AttrScope(ctx_group='dev1', lr_mult='0.5'):
+        v = sym.Variable('v')
+        fc = sym.FullyConnected(v, num_hidden=3, name='fc')
+    assert v.attr('ctx_group') == 'dev1' and fc.attr('lr_mult') == '0.5'
+    w = sym.Variable('w', shape=(3, 4), lr_mult=2.0, wd_mult=0.0, dtype='float16', init=mx.init.One())
+    ad = w.attr_dict()['w']
+    assert ad['__shape__'] == '(3, 4)' and ad['__lr_mult__'] == '2.0' and ad['__wd_mult__'] == '0.0'
+    assert ad['__dtype__'] in ('2', 'float16')
+    with mx.name.Prefix('stage1_'):
+        s = sym.Activation(sym.Variable('x'), act_type='relu')
+    assert s.name.startswith('stage1_activation')
+
+
+def test_save_load_file(tmp_path):
+    net = _mlp()
+    f = str(tmp_path / 'net-symbol.json')
+    net.save(f)
+    back = sym.load(f)
+    assert back.tojson() == net.tojson()
+
+
+def test_symbol_numpy_namespace_and_optimize_for():
+    x = sym.Variable('x')
+    y = sym.relu(x) + sym.sigmoid(x)
+    out = y.eval(x=nd.array([-1., 1.]))[0].asnumpy()
+    assert_almost_equal(out, np.maximum([-1., 1.], 0) + 1 / (1 + np.exp(-np.array([-1., 1.]))), rtol=1e-6)
+    z = y.optimize_for('default')
+    assert z.list_arguments() == ['x']
