@@ -214,3 +214,58 @@ MXB_EXPORT int mxb_multi_sum_sq(int count, void** p, const int64_t* sizes, const
   multi_sum_sq_final_kernel<<<count, 128, 0, st>>>(tab, scratch, out, out_offset);
   return (int)cudaGetLastError();
 }
+
+// ---- sum of squares with a fixed scratch array (see optim_noalloc.h) ---------------------------------------
+#include <mutex>
+
+#include "optim_noalloc.h"
+
+static_assert(MXB_SUM_SQ_CHUNK_ELEMS == mxb::kChunk, "header and kernels disagree on the chunk size");
+
+// Stage-1 partial sums of mxb_multi_sum_sq_static: one slot per chunk, shared by every call on the device.
+static __device__ __align__(256) float g_sum_sq_static_scratch[MXB_SUM_SQ_STATIC_MAX_CHUNKS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+std::mutex g_static_scratch_mutex;
+
+// Device address of the array on the current device, looked up once per device.
+int static_scratch(float** out) {
+  int dev = 0;
+  cudaError_t rc = cudaGetDevice(&dev);
+  if (rc != cudaSuccess) return (int)rc;
+  if (dev < 0 || dev >= kMaxDevices) return MXB_SUM_SQ_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_ptr[dev]) {
+    float* ptr = nullptr;
+    rc = cudaGetSymbolAddress((void**)&ptr, g_sum_sq_static_scratch);
+    if (rc != cudaSuccess) return (int)rc;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+MXB_EXPORT int mxb_multi_sum_sq_static(int count, void** p, const int64_t* sizes, const int* dtypes, float* out,
+                                       int out_offset, void* stream) {
+  if (count > kMaxTensors || count <= 0) return MXB_SUM_SQ_ERR_BAD_COUNT;
+  int64_t chunks = 0;
+  for (int i = 0; i < count; ++i) {
+    if (sizes[i] < 0) return MXB_SUM_SQ_ERR_TOO_LARGE;
+    chunks += (sizes[i] + kChunk - 1) / kChunk;
+    if (chunks > MXB_SUM_SQ_STATIC_MAX_CHUNKS) return MXB_SUM_SQ_ERR_TOO_LARGE;
+  }
+  float* scratch = nullptr;
+  int rc = static_scratch(&scratch);
+  if (rc != 0) return rc;
+  PtrTable tab;
+  int acc = fill_ptr_table(&tab, count, p, sizes, dtypes);
+  cudaStream_t st = (cudaStream_t)stream;
+  int grid = acc < sm_count() * 8 ? acc : sm_count() * 8;
+  if (grid < 1) grid = 1;
+  multi_sum_sq_partial_kernel<<<grid, 256, 0, st>>>(tab, scratch);
+  multi_sum_sq_final_kernel<<<count, 128, 0, st>>>(tab, scratch, out, out_offset);
+  return (int)cudaGetLastError();
+}
