@@ -1,0 +1,250 @@
+#!/usr/bin/env python
+"""Per-operator forward/backward timing (the counterpart of the reference's ``benchmark/opperf``).
+
+    python benchmark/opperf/opperf.py                               # default operator set, JSON lines
+    python benchmark/opperf/opperf.py --op BatchNorm --dtype float16 --runs 20
+    python benchmark/opperf/opperf.py --list
+
+Each case runs through the public ``mx.nd`` operators (so it times what a user gets), after ``--warmup``
+untimed runs, with CUDA events around ``--runs`` repetitions on the launching stream and a write of a
+buffer larger than the L2 cache between repetitions.  Output: one JSON object per case with mean forward
+and backward milliseconds, the algorithmic bytes / FLOPs of the case and the achieved GB/s or TFLOP/s.
+On a machine without a GPU the cases run on the CPU with wall-clock timing (functional check only).
+"""
+import argparse
+import json
+import os
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+import numpy as np                                          # noqa: E402
+import torch                                                # noqa: E402
+
+import mxnet_b200 as mx                                     # noqa: E402
+from mxnet_b200 import autograd, nd                         # noqa: E402
+
+
+def _rand(shape, ctx, dtype, scale=1.0):
+    t = torch.randn(*shape, device=ctx.torch_device) * scale
+    return nd.NDArray._from_tensor(t.to(mx.base.to_torch_dtype(dtype)), ctx)
+
+
+def _esize(dtype):
+    return np.dtype(dtype).itemsize
+
+
+# Each case: name -> function(ctx, dtype, small) returning dict(inputs=[...], fn=callable(*inputs) -> output,
+# fwd_bytes, bwd_bytes, fwd_flops, bwd_flops).  Shapes follow the ResNet-50 / BERT-base hot spots.
+def case_batchnorm(ctx, dtype, small, relu=False, residual=False):
+    n, h, c = (32, 56, 256) if small else (256, 56, 256)
+    x = _rand((n, h, h, c), ctx, dtype)
+    res = _rand((n, h, h, c), ctx, dtype) if residual else None
+    gamma, beta = _rand((c,), ctx, dtype), _rand((c,), ctx, dtype)
+    mean, var = nd.zeros((c,), ctx=ctx), nd.ones((c,), ctx=ctx)
+    kw = dict(eps=1e-5, momentum=0.9, fix_gamma=False, axis=3)
+    if relu:
+        kw['act_type'] = 'relu'
+    ins = [x, gamma, beta] + ([res] if residual else [])
+
+    def fn(x, gamma, beta, res=None):
+        return nd.BatchNorm(x, gamma, beta, mean, var, res, **kw) if res is not None else \
+            nd.BatchNorm(x, gamma, beta, mean, var, **kw)
+    nb = x.size * _esize(dtype)
+    return dict(inputs=ins, fn=fn, fwd_bytes=nb * (3 + residual), bwd_bytes=nb * (5 + 3 * residual + (0 if not relu else 0)))
+
+
+def case_conv(ctx, dtype, small, cin=64, cout=64, k=3, hw=56, stride=1):
+    n = 32 if small else 256
+    x = _rand((n, hw, hw, cin), ctx, dtype)
+    w = _rand((cout, k, k, cin), ctx, dtype, 0.05)
+
+    def fn(x, w):
+        return nd.Convolution(x, w, kernel=(k, k), stride=(stride, stride), pad=(k // 2, k // 2), num_filter=cout,
+                              no_bias=True, layout='NHWC')
+    ho = hw // stride
+    fl = 2.0 * n * ho * ho * cout * cin * k * k
+    return dict(inputs=[x, w], fn=fn, fwd_flops=fl, bwd_flops=2 * fl)
+
+
+def case_fc(ctx, dtype, small, m=8192, k=768, n=3072):
+    if small:
+        m //= 8
+    x, w, b = _rand((m, k), ctx, dtype), _rand((n, k), ctx, dtype, 0.05), _rand((n,), ctx, dtype)
+
+    def fn(x, w, b):
+        return nd.FullyConnected(x, w, b, num_hidden=n, flatten=False)
+    fl = 2.0 * m * n * k
+    return dict(inputs=[x, w, b], fn=fn, fwd_flops=fl, bwd_flops=2 * fl)
+
+
+def case_softmax(ctx, dtype, small, log=False):
+    rows, c = (4096, 1000) if small else (65536, 1000)
+    x = _rand((rows, c), ctx, dtype)
+    fn = (lambda x: nd.log_softmax(x, axis=-1)) if log else (lambda x: nd.softmax(x, axis=-1))
+    nb = x.size * _esize(dtype)
+    return dict(inputs=[x], fn=fn, fwd_bytes=2 * nb, bwd_bytes=3 * nb)
+
+
+def case_layernorm(ctx, dtype, small):
+    rows, c = (4096, 768) if small else (65536, 768)
+    x, g, b = _rand((rows, c), ctx, dtype), _rand((c,), ctx, 'float32'), _rand((c,), ctx, 'float32')
+    nb = x.size * _esize(dtype)
+    return dict(inputs=[x, g, b], fn=lambda x, g, b: nd.LayerNorm(x, g, b, axis=-1, eps=1e-5), fwd_bytes=2 * nb,
+                bwd_bytes=3 * nb)
+
+
+def case_maxpool(ctx, dtype, small):
+    n = 32 if small else 256
+    x = _rand((n, 112, 112, 64), ctx, dtype)
+    nb = x.size * _esize(dtype)
+
+    def fn(x):
+        return nd.Pooling(x, kernel=(3, 3), stride=(2, 2), pad=(1, 1), pool_type='max', layout='NHWC')
+    return dict(inputs=[x], fn=fn, fwd_bytes=nb * 1.25 + nb / 8, bwd_bytes=nb * 1.25 + nb / 8)
+
+
+def case_add(ctx, dtype, small):
+    n = 2 ** 24 if small else 2 ** 28
+    a, b = _rand((n,), ctx, dtype), _rand((n,), ctx, dtype)
+    return dict(inputs=[a, b], fn=lambda a, b: a + b, fwd_bytes=3 * n * _esize(dtype), bwd_bytes=0, no_backward=True)
+
+
+CASES = {
+    'BatchNorm': case_batchnorm,
+    'BatchNormReLU': lambda c, d, s: case_batchnorm(c, d, s, relu=True),
+    'BatchNormAddReLU': lambda c, d, s: case_batchnorm(c, d, s, relu=True, residual=True),
+    'Convolution3x3': case_conv,
+    'Convolution1x1': lambda c, d, s: case_conv(c, d, s, cin=256, cout=64, k=1),
+    'Convolution1x1_wide': lambda c, d, s: case_conv(c, d, s, cin=512, cout=2048, k=1, hw=7),
+    'FullyConnected': case_fc,
+    'FullyConnected_resnet_head': lambda c, d, s: case_fc(c, d, False, m=256, k=2048, n=1000),
+    'softmax': case_softmax,
+    'log_softmax': lambda c, d, s: case_softmax(c, d, s, log=True),
+    'LayerNorm': case_layernorm,
+    'MaxPool3x3s2': case_maxpool,
+    'elemwise_add': case_add,
+}
+
+
+def run_case(name, ctx, dtype, runs, warmup, small):
+    spec = CASES[name](ctx, dtype, small)
+    ins, fn = spec['inputs'], spec['fn']
+    cuda = ctx.device_type == 'gpu'
+    flush = torch.empty(160 * 2 ** 20, dtype=torch.uint8, device=ctx.torch_device) if cuda else None
+    backward = not spec.get('no_backward')
+    for a in ins:
+        if backward:
+            a.attach_grad()
+    out = None
+
+    def fwd():
+        nonlocal out
+        if backward:
+            with autograd.record():
+                out = fn(*ins)
+        else:
+            out = fn(*ins)
+        return out
+    head = None
+    fwd_ms, bwd_ms = [], []
+    for it in range(warmup + runs):
+        if cuda:
+            flush.zero_()
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record()
+            o = fwd()
+            e[1].record()
+            if backward:
+                if head is None:
+                    head = nd.ones(o.shape, ctx=ctx, dtype=o.dtype)
+                o.backward(head)
+            e[2].record()
+            torch.cuda.synchronize()
+            t_f, t_b = e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])
+        else:
+            t0 = time.perf_counter()
+            o = fwd()
+            t1 = time.perf_counter()
+            if backward:
+                if head is None:
+                    head = nd.ones(o.shape, ctx=ctx, dtype=o.dtype)
+                o.backward(head)
+            t2 = time.perf_counter()
+            t_f, t_b = (t1 - t0) * 1e3, (t2 - t1) * 1e3
+        if it >= warmup:
+            fwd_ms.append(t_f)
+            bwd_ms.append(t_b)
+    res = {'op': name, 'dtype': dtype, 'device': str(ctx), 'runs': runs,
+           'inputs': [list(a.shape) for a in ins], 'fwd_ms': float(np.mean(fwd_ms)),
+           'bwd_ms': float(np.mean(bwd_ms)) if backward else None}
+    for tag, ms in (('fwd', res['fwd_ms']), ('bwd', res['bwd_ms'])):
+        if ms is None or ms <= 0:
+            continue
+        if spec.get(tag + '_bytes'):
+            res[tag + '_GBps'] = spec[tag + '_bytes'] / ms / 1e6
+        if spec.get(tag + '_flops'):
+            res[tag + '_TFLOPs'] = spec[tag + '_flops'] / ms / 1e9
+    return res
+
+
+def gemm_burst(ctx, dtype, reps=50):
+    """Kernel-only GEMM throughput: `reps` back-to-back launches between two events, so that host launch
+    overhead does not count; the in-tree tcgen05 kernel and the library GEMM on identical operands."""
+    from mxnet_b200.ops.cuda import gemm_ops
+    td = mx.base.to_torch_dtype(dtype)
+    out = []
+    for m, n, k in [(8192, 3072, 768), (8192, 768, 3072), (4096, 4096, 4096), (16384, 1024, 1024), (8192, 8192, 8192),
+                    (802816, 64, 256), (200704, 512, 128)]:
+        a = torch.randn(m, k, device=ctx.torch_device).to(td)
+        b = torch.randn(n, k, device=ctx.torch_device).to(td)
+        d = torch.empty(m, n, device=ctx.torch_device, dtype=td)
+        res = {'op': 'gemm_burst', 'M': m, 'N': n, 'K': k, 'dtype': dtype, 'reps': reps}
+        for name, fn in (('tcgen05', lambda: gemm_ops.gemm_tn(a, b, out=d)), ('library', lambda: torch.matmul(a, b.t(), out=d))):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            res[name + '_us'] = ms * 1e3
+            res[name + '_TFLOPs'] = 2.0 * m * n * k / ms / 1e9
+        gemm_ops.check_errors()
+        res['ratio'] = res['tcgen05_TFLOPs'] / res['library_TFLOPs']
+        out.append(res)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--op', action='append', help='case name (repeatable); default: all')
+    ap.add_argument('--dtype', default='float16')
+    ap.add_argument('--runs', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--small', action='store_true', help='shapes sized for a profiler capture (a few hundred MB)')
+    ap.add_argument('--list', action='store_true')
+    args = ap.parse_args()
+    if args.list:
+        print('\n'.join(CASES))
+        return 0
+    cuda = torch.cuda.is_available()
+    ctx = mx.gpu(0) if cuda else mx.cpu(0)
+    dtype = args.dtype if cuda else 'float32'
+    small = args.small or not cuda
+    for name in (args.op or list(CASES)):
+        if name == 'gemm_burst':
+            if cuda:
+                for r in gemm_burst(ctx, dtype):
+                    print(json.dumps(r), flush=True)
+            continue
+        print(json.dumps(run_case(name, ctx, dtype, args.runs, args.warmup, small)), flush=True)
+    return 0
+
+
+if __name__ == '__main__':
+    sys.exit(main())

@@ -46,6 +46,7 @@ struct Opr {
   int priority = 0;
   uint64_t seq = 0;
   std::string name;
+  bool always = false;        // runs even when an input var carries an error (synchronisation markers)
 };
 
 struct OprOrder {
@@ -80,9 +81,10 @@ class Engine {
   }
 
   void Push(TaskFn fn, void* arg, std::vector<Var*> reads, std::vector<Var*> writes, int priority,
-            const char* name, bool delete_written = false) {
+            const char* name, bool delete_written = false, bool always = false) {
     Opr* op = new Opr();
     op->fn = fn; op->arg = arg; op->priority = priority; op->name = name ? name : "";
+    op->always = always;
     op->reads = std::move(reads); op->writes = std::move(writes);
     op->seq = seq_.fetch_add(1);
     if (delete_written) for (Var* v : op->writes) v->to_delete = true;
@@ -124,7 +126,7 @@ class Engine {
                s->cv.notify_all();
              }
              return 0;
-           }, &s, {v}, {}, 1 << 20, "WaitForVar");
+           }, &s, {v}, {}, 1 << 20, "WaitForVar", false, /*always=*/true);
       std::unique_lock<std::mutex> lk(s.mu);
       s.cv.wait(lk, [&] { return s.done; });
     }
@@ -189,7 +191,10 @@ class Engine {
       std::lock_guard<std::mutex> lk(v->mu);
       if (!v->error.empty()) { err = v->error; break; }
     }
-    if (err.empty() && op->fn) {
+    if (op->always) {
+      if (op->fn) op->fn(op->arg, nullptr, 0);
+      err.clear();                        // a marker neither fails nor forwards a failure
+    } else if (err.empty() && op->fn) {
       char buf[2048];
       buf[0] = 0;
       int rc = op->fn(op->arg, buf, sizeof(buf));

@@ -6,29 +6,37 @@
 // reference sends all of them to cuBLAS (src/operator/linalg_impl.h: cublasGemmEx, pseudo-fp16 with fp32
 // accumulation) followed by a separate add_bias_kernel (src/operator/nn/fully_connected-inl.h:165-367).
 //
-// Structure of one CTA (192 threads, one 128 x BN output tile, BN = 128):
-//   warp 0     : TMA producer.  One elected lane issues cp.async.bulk.tensor.2d loads of a 128x64 A tile and
-//                a BNx64 B tile per k-step into a 4-stage shared-memory ring (128-byte swizzle), completion
-//                is signalled on an mbarrier with the transaction byte count.
-//   warp 1     : MMA issuer.  One elected lane issues four tcgen05.mma (M128 x N128 x K16, kind::f16) per
-//                k-step from shared-memory matrix descriptors into a TMEM accumulator (128 lanes x BN fp32
-//                columns) and commits each stage back to the producer with tcgen05.commit.
-//   warps 2..5 : epilogue.  After the last commit arrives, each warp reads its 32-lane quarter of TMEM with
-//                tcgen05.ld (32 columns at a time), adds the bias, applies ReLU/GELU, converts and stores.
+// Persistent, warp-specialised kernel: one CTA per SM walks output tiles of 128 x BN (BN = 64, 128 or 256).
+//   warp 0     : TMA producer.  One elected lane issues cp.async.bulk.tensor.2d loads of a 128x64 A tile and a
+//                BNx64 B tile per k-step into a shared-memory ring (128-byte swizzle); completion is signalled
+//                on an mbarrier with the transaction byte count.  It runs ahead across tile boundaries, so the
+//                ring is already full of the next tile's operands when the tensor cores finish the current one.
+//   warp 1     : MMA issuer.  One elected lane issues four tcgen05.mma (M128 x N(BN) x K16, kind::f16) per k-step
+//                from shared-memory matrix descriptors into one of TWO TMEM accumulators (128 lanes x BN fp32
+//                columns each) and hands each ring stage back to the producer with tcgen05.commit.
+//   warps 2..5 : epilogue.  They drain accumulator `t & 1` with tcgen05.ld (32 columns at a time), add the bias,
+//                apply ReLU/GELU, convert and store, while the MMA warp already fills the other accumulator.
 // No cluster features and no multicast loads are used, so the same binary runs in multi-GPU jobs.
-// Every mbarrier wait is bounded; on expiry the CTA raises an error flag for the host, skips its remaining
-// work, frees its TMEM columns and exits.
+// Every mbarrier wait is bounded; on expiry the CTA raises an error flag for the host, every role leaves its
+// loop, copies still in flight are waited for (bounded), the TMEM columns are freed and the CTA exits.
 #include <cuda.h>
 
 #include "common.cuh"
 
 namespace mxb {
 
-constexpr int BM = 128, BN = 128, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int kGemmThreads = 192;
-constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t A_BYTES = BM * BK * 2;
 constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr int kMaxStages = 8;
+
+// ring depth that fits the 227 KB shared-memory budget for a given tile width
+template <int BN> struct TileCfg {
+  static constexpr uint32_t B_BYTES = BN * BK * 2;
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /*alignment slack*/ + 512 /*barriers*/;
+};
 
 enum Act { kActNone = 0, kActRelu = 1, kActGelu = 2 };
 
@@ -77,8 +85,8 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
 }
 
 // Instruction descriptor for kind::f16: D fp32, A/B fp16 or bf16, both K-major, N and M tile sizes.
-__host__ __device__ constexpr uint32_t make_idesc(int bf16) {
-  return (1u << 4) | ((uint32_t)bf16 << 7) | ((uint32_t)bf16 << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc(int bf16, int bn) {
+  return (1u << 4) | ((uint32_t)bf16 << 7) | ((uint32_t)bf16 << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -104,38 +112,48 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
 
-template <typename T>
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <typename T, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, T* __restrict__ D,
                const T* __restrict__ bias, int M, int N, int K, int ldd, int act, int bf16, int* __restrict__ error_flag) {
+  using Cfg = TileCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr uint32_t B_BYTES = Cfg::B_BYTES;
   extern __shared__ uint8_t smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle pattern
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
-  uint64_t* full = bars;                  // [STAGES] producer -> MMA
-  uint64_t* empty = bars + STAGES;        // [STAGES] MMA -> producer
-  uint64_t* acc_full = bars + 2 * STAGES; // accumulator ready for the epilogue
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  uint64_t* full = bars;                        // [STAGES] producer -> MMA
+  uint64_t* empty = bars + kMaxStages;          // [STAGES] MMA -> producer
+  uint64_t* acc_full = bars + 2 * kMaxStages;   // [2] accumulator ready for the epilogue
+  uint64_t* acc_empty = acc_full + 2;           // [2] accumulator drained by the epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* issued_kt = abort_flag + 1;      // k-steps whose TMA loads were issued
-  volatile int* consumed_kt = abort_flag + 2;    // k-steps whose loads were observed complete by the MMA warp
+  volatile int* issued_it = abort_flag + 1;     // k-steps whose TMA loads were issued
+  volatile int* consumed_it = abort_flag + 2;   // k-steps whose loads were observed complete by the MMA warp
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_m = blockIdx.y, tile_n = blockIdx.x;
   const int num_k = (K + BK - 1) / BK;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;     // two accumulators; a power of two >= 32
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    mbar_init(acc_full, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     *abort_flag = 0;
-    *issued_kt = 0;
-    *consumed_kt = 0;
+    *issued_it = 0;
+    *consumed_it = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {   // TMEM allocation is a warp-wide operation; BN fp32 columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+  if (warp == 1) {   // TMEM allocation is a warp-wide operation
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -143,80 +161,123 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
+  // Tile order: consecutive CTAs take consecutive row tiles of the same column tile, so the B (weight) tile is
+  // shared through L2 by the CTAs that run at the same time and A is streamed once.
   if (warp == 0) {
     if (lane == 0) {
-      for (int kt = 0; kt < num_k; ++kt) {
-        const int s = kt % STAGES;
-        const uint32_t phase = (uint32_t)(kt / STAGES) & 1u;
-        if (!mbar_wait(&empty[s], phase ^ 1u)) { *abort_flag = 1; break; }
-        mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-        tma_load_2d(sA + s * A_BYTES, &map_a, kt * BK, tile_m * BM, &full[s]);
-        tma_load_2d(sB + s * B_BYTES, &map_b, kt * BK, tile_n * BN, &full[s]);
-        *issued_kt = kt + 1;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+        const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+        for (int kt = 0; kt < num_k; ++kt, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+          if (!mbar_wait(&empty[s], phase ^ 1u)) { *abort_flag = 1; break; }
+          mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+          tma_load_2d(sA + s * A_BYTES, &map_a, kt * BK, tile_m * BM, &full[s]);
+          tma_load_2d(sB + s * B_BYTES, &map_b, kt * BK, tile_n * BN, &full[s]);
+          *issued_it = it + 1;
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(bf16);
-      bool ok = true;
-      for (int kt = 0; kt < num_k && ok; ++kt) {
-        const int s = kt % STAGES;
-        const uint32_t phase = (uint32_t)(kt / STAGES) & 1u;
-        if (!mbar_wait(&full[s], phase)) { *abort_flag = 1; ok = false; break; }
-        *consumed_kt = kt + 1;
+      const uint32_t idesc = make_idesc(bf16, BN);
+      int it = 0, t = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++t) {
+        const int buf = t & 1;
+        // wait until the epilogue has drained this accumulator (its first use passes immediately)
+        if (!mbar_wait(&acc_empty[buf], (((uint32_t)t >> 1) & 1u) ^ 1u)) { *abort_flag = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t adesc = make_desc(smem_u32(sA + s * A_BYTES));
-        const uint64_t bdesc = make_desc(smem_u32(sB + s * B_BYTES));
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        bool ok = true;
+        for (int kt = 0; kt < num_k; ++kt, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+          if (!mbar_wait(&full[s], phase)) { *abort_flag = 1; ok = false; break; }
+          *consumed_it = it + 1;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t adesc = make_desc(smem_u32(sA + s * A_BYTES));
+          const uint64_t bdesc = make_desc(smem_u32(sB + s * B_BYTES));
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          // advancing K by 16 elements = 32 bytes inside the swizzle atom: +2 in the 16-byte address field
-          umma(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing K by 16 elements = 32 bytes inside the swizzle atom: +2 in the 16-byte address field
+            umma(tmem_d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);        // the stage is free once these MMAs have read it
         }
-        umma_commit(&empty[s]);        // stage is free once these MMAs have read it
+        if (!ok) break;
+        umma_commit(&acc_full[buf]);     // arrives when every MMA of this tile has completed
       }
-      umma_commit(acc_full);           // arrives when every MMA issued above has completed
     }
   } else {
     // epilogue warps 2..5: TMEM lane quarter = warp index modulo 4
     const int q = warp & 3;
-    const bool ready = mbar_wait(acc_full, 0);
-    if (!ready) *abort_flag = 1;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int row = tile_m * BM + q * 32 + lane;
-    if (ready && !*abort_flag) {
+    int t = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+      const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+      const int buf = t & 1;
+      const bool ready = mbar_wait(&acc_full[buf], ((uint32_t)t >> 1) & 1u);
+      if (!ready) *abort_flag = 1;
+      if (!ready || *abort_flag) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = tile_m * BM + q * 32 + lane;
+      const bool bias_vec = bias != nullptr && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
+      const bool row_vec = (ldd % 8) == 0;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int col0 = tile_n * BN + c0;
+        const bool full_cols = col0 + 32 <= N;
+        // bias of these 32 columns first, so its latency overlaps the TMEM load (registers only: every index
+        // below is a compile-time constant after unrolling)
+        float bv[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) bv[j] = 0.f;
+        if (bias != nullptr && col0 < N) {
+          if (bias_vec && full_cols) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const Vec16<T> b = ld16(bias + col0 + v * 8);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) bv[v * 8 + j] = Cvt<T>::to_f(b.v[j]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < N) bv[j] = Cvt<T>::to_f(bias[col0 + j]);
+          }
+        }
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float x = __uint_as_float(r[j]) + bv[j];
+          if (act == kActRelu) x = fmaxf(x, 0.f);
+          else if (act == kActGelu) x = gelu_erf(x);
+          f[j] = x;
+        }
         if (row < M && col0 < N) {
           T* drow = D + (size_t)row * ldd + col0;
-          if (col0 + 32 <= N && (ldd % 8 == 0)) {
+          if (full_cols && row_vec) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               Vec16<T> o;
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float f = __uint_as_float(r[v * 8 + j]);
-                if (bias) f += Cvt<T>::to_f(bias[col0 + v * 8 + j]);
-                if (act == kActRelu) f = fmaxf(f, 0.f);
-                else if (act == kActGelu) f = gelu_erf(f);
-                o.v[j] = Cvt<T>::from_f(f);
-              }
+              for (int j = 0; j < 8; ++j) o.v[j] = Cvt<T>::from_f(f[v * 8 + j]);
               st16(drow + v * 8, o);
             }
           } else {
-            for (int j = 0; j < 32 && col0 + j < N; ++j) {
-              float f = __uint_as_float(r[j]);
-              if (bias) f += Cvt<T>::to_f(bias[col0 + j]);
-              if (act == kActRelu) f = fmaxf(f, 0.f);
-              else if (act == kActGelu) f = gelu_erf(f);
-              drow[j] = Cvt<T>::from_f(f);
-            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < N) drow[j] = Cvt<T>::from_f(f[j]);
           }
         }
       }
+      // this warp has finished reading the accumulator: let the MMA warp reuse it
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -224,13 +285,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (threadIdx.x == 0 && *abort_flag) {
     // gave up somewhere: before the shared memory is released, wait (bounded) for bulk copies that were
     // issued but never consumed, so none is still in flight when the CTA exits
-    for (int kt = *consumed_kt; kt < *issued_kt; ++kt) mbar_wait(&full[kt % STAGES], (uint32_t)(kt / STAGES) & 1u);
+    for (int it = *consumed_it; it < *issued_it; ++it) mbar_wait(&full[it % STAGES], (uint32_t)(it / STAGES) & 1u);
     if (error_flag) atomicExch(error_flag, 1);
   }
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -262,6 +323,32 @@ static int make_map(CUtensorMap* map, const void* base, int bf16, int64_t rows, 
   return rc == CUDA_SUCCESS ? 0 : -11;
 }
 
+template <typename T, int BN>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, void* D, const void* bias, int M, int N, int K, int ldd,
+                       int act, int bf16, int* error_flag, cudaStream_t st) {
+  using Cfg = TileCfg<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t rc = cudaFuncSetAttribute(gemm_tn_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (rc != cudaSuccess) return (int)rc;
+    attr_set = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_tn_kernel<T, BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ma, mb, (T*)D, (const T*)bias, M, N, K, ldd, act, bf16,
+                                                                     error_flag);
+  return (int)cudaGetLastError();
+}
+
+// Tile width: the widest tile that still gives every SM work; narrow outputs take the narrow tile.
+static int pick_bn(int M, int N) {
+  const int tm = (M + BM - 1) / BM;
+  if (N <= 64) return 64;
+  if (N <= 128) return 128;
+  if ((int64_t)tm * ((N + 255) / 256) >= sm_count()) return 256;
+  return 128;
+}
+
 }  // namespace mxb
 
 using namespace mxb;
@@ -272,26 +359,20 @@ using namespace mxb;
 MXB_EXPORT int mxb_gemm_tn(int dtype, const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
                            int lda, int ldb, int ldd, int act, int* error_flag, void* stream) {
   if (dtype != kF16 && dtype != kBF16) return -1;
+  if (M < 1 || N < 1 || K < 1) return -2;
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A % 16) || ((uintptr_t)B % 16) || ((uintptr_t)D % 16)) return -3;
   const int bf16 = dtype == kBF16;
+  const int bn = pick_bn(M, N);
   CUtensorMap ma, mb;
   int rc = make_map(&ma, A, bf16, M, K, lda, BM);
   if (rc) return rc;
-  rc = make_map(&mb, B, bf16, N, K, ldb, BN);
+  rc = make_map(&mb, B, bf16, N, K, ldb, bn);
   if (rc) return rc;
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   cudaStream_t st = (cudaStream_t)stream;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(gemm_tn_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    cudaFuncSetAttribute(gemm_tn_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    attr_set = true;
-  }
-  if (bf16)
-    gemm_tn_kernel<__nv_bfloat16><<<grid, kGemmThreads, SMEM_BYTES, st>>>(ma, mb, (__nv_bfloat16*)D, (const __nv_bfloat16*)bias,
-                                                                         M, N, K, ldd, act, 1, error_flag);
-  else
-    gemm_tn_kernel<__half><<<grid, kGemmThreads, SMEM_BYTES, st>>>(ma, mb, (__half*)D, (const __half*)bias, M, N, K, ldd, act,
-                                                                  0, error_flag);
-  return (int)cudaGetLastError();
+#define MXB_GEMM(T)                                                                                          \
+  (bn == 256 ? launch_gemm<T, 256>(ma, mb, D, bias, M, N, K, ldd, act, bf16, error_flag, st)                  \
+   : bn == 128 ? launch_gemm<T, 128>(ma, mb, D, bias, M, N, K, ldd, act, bf16, error_flag, st)                \
+               : launch_gemm<T, 64>(ma, mb, D, bias, M, N, K, ldd, act, bf16, error_flag, st))
+  return bf16 ? MXB_GEMM(__nv_bfloat16) : MXB_GEMM(__half);
+#undef MXB_GEMM
 }

@@ -104,13 +104,23 @@ bn_reduce_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __r
 
 // Sum the per-CTA partials of 32 channels with a (32 x 16) thread block: coalesced along the channel
 // axis, 16-way split along the partial axis, fixed-order tree in shared memory (deterministic).
-constexpr int kFinX = 32, kFinY = 16;
+constexpr int kFinX = 32, kFinY = 32;
 __device__ __forceinline__ bool finalize_sums(const float* __restrict__ partial, int nblocks, int C, float& s, float& q) {
   __shared__ float red[2][kFinY][kFinX];
   const int c = blockIdx.x * kFinX + threadIdx.x;
   float a = 0.f, b = 0.f;
   if (c < C) {
-    for (int k = threadIdx.y; k < nblocks; k += kFinY) {
+    // four independent loads per trip keep the L2 round trips overlapped; the order of additions is fixed
+    int k = threadIdx.y;
+    for (; k + 3 * kFinY < nblocks; k += 4 * kFinY) {
+      const float a0 = partial[((int64_t)k * 2) * C + c], b0 = partial[((int64_t)k * 2 + 1) * C + c];
+      const float a1 = partial[((int64_t)(k + kFinY) * 2) * C + c], b1 = partial[((int64_t)(k + kFinY) * 2 + 1) * C + c];
+      const float a2 = partial[((int64_t)(k + 2 * kFinY) * 2) * C + c], b2 = partial[((int64_t)(k + 2 * kFinY) * 2 + 1) * C + c];
+      const float a3 = partial[((int64_t)(k + 3 * kFinY) * 2) * C + c], b3 = partial[((int64_t)(k + 3 * kFinY) * 2 + 1) * C + c];
+      a += (a0 + a1) + (a2 + a3);
+      b += (b0 + b1) + (b2 + b3);
+    }
+    for (; k < nblocks; k += kFinY) {
       a += partial[((int64_t)k * 2) * C + c];
       b += partial[((int64_t)k * 2 + 1) * C + c];
     }

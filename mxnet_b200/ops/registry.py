@@ -150,6 +150,12 @@ def invoke(op, args, attrs, out=None, kind=None):
                     res = op.fn(*tensors, **attrs)
             else:
                 res = op.fn(*tensors, **attrs)
+    except MXNetError:
+        raise
+    except RuntimeError as e:
+        # operator failures (shape mismatch, bad arguments caught by the tensor library) surface as
+        # MXNetError like the reference's dmlc::Error -> MXNetError path (python/mxnet/base.py:246)
+        raise MXNetError('%s: %s' % (op.name, e)) from e
     finally:
         if pctx is not None:
             pctx.__exit__(None, None, None)

@@ -1,0 +1,199 @@
+"""Native runtime: dependency engine, storage pools, profiler, exception propagation (reference:
+tests/cpp/engine/threaded_engine_test.cc, tests/cpp/storage/storage_test.cc,
+tests/python/unittest/test_engine.py, test_exc_handling.py, test_profiler.py)."""
+import json
+import os
+import threading
+import time
+
+import numpy as np
+import pytest
+
+import mxnet_b200 as mx
+from mxnet_b200 import nd, profiler
+from mxnet_b200.csrc import runtime
+
+
+def test_engine_orders_writes_and_parallelises_reads():
+    eng = runtime.Engine(num_workers=4)
+    v = eng.new_var()
+    log, lock = [], threading.Lock()
+
+    def writer(tag):
+        def fn():
+            with lock:
+                log.append(('w', tag))
+            time.sleep(0.01)
+        return fn
+
+    active, peak = [0], [0]
+
+    def reader():
+        with lock:
+            active[0] += 1
+            peak[0] = max(peak[0], active[0])
+        time.sleep(0.05)
+        with lock:
+            active[0] -= 1
+    eng.push(writer(0), write_vars=[v])
+    for _ in range(4):
+        eng.push(reader, read_vars=[v])
+    eng.push(writer(1), write_vars=[v])
+    eng.push(writer(2), write_vars=[v])
+    eng.wait_for_var(v)
+    assert log == [('w', 0), ('w', 1), ('w', 2)]
+    assert peak[0] >= 2, 'reads of one variable must run concurrently'
+    assert v.version == 3
+    eng.wait_all()
+    assert eng.num_pending == 0
+
+
+def test_engine_dependency_chain_across_vars():
+    eng = runtime.Engine(num_workers=4)
+    a, b, c = eng.new_var(), eng.new_var(), eng.new_var()
+    vals = {'a': 0, 'b': 0, 'c': 0}
+
+    def set_a():
+        time.sleep(0.03)
+        vals['a'] = 2
+
+    def a_to_b():
+        vals['b'] = vals['a'] * 10
+
+    def ab_to_c():
+        vals['c'] = vals['a'] + vals['b']
+    eng.push(set_a, write_vars=[a])
+    eng.push(a_to_b, read_vars=[a], write_vars=[b])
+    eng.push(ab_to_c, read_vars=[a, b], write_vars=[c])
+    eng.wait_for_var(c)
+    assert vals == {'a': 2, 'b': 20, 'c': 22}
+
+
+def test_engine_exception_propagates_to_dependents_and_waits():
+    eng = runtime.Engine(num_workers=2)
+    a, b, other = eng.new_var(), eng.new_var(), eng.new_var()
+    ran = []
+
+    def boom():
+        raise ValueError('bad op')
+    eng.push(boom, write_vars=[a])
+    eng.push(lambda: ran.append('dependent'), read_vars=[a], write_vars=[b])
+    eng.push(lambda: ran.append('independent'), write_vars=[other])
+    eng.wait_for_var(other)                      # unrelated work is not poisoned
+    assert 'independent' in ran
+    with pytest.raises(Exception) as ei:
+        eng.wait_for_var(b)                      # the error travels var -> op -> var
+    assert 'bad op' in str(ei.value)
+    assert 'dependent' not in ran
+    # the engine keeps working; the first failure is reported once more by wait_all, then it is cleared
+    eng.push(lambda: ran.append('later'), write_vars=[other])
+    with pytest.raises(ValueError):
+        eng.wait_all()
+    assert 'later' in ran
+    eng.wait_all()
+
+
+def test_engine_priority_and_naive_mode():
+    eng = runtime.Engine(num_workers=1, num_priority_workers=1)
+    gate, order = eng.new_var(), []
+    block = threading.Event()
+    eng.push(block.wait, write_vars=[gate])
+    for i, pr in enumerate([0, 5, 1, 9]):
+        eng.push((lambda i=i: order.append(i)), read_vars=[gate], priority=pr)
+    block.set()
+    eng.wait_all()
+    assert sorted(order) == [0, 1, 2, 3]
+    naive = runtime.Engine(naive=True)
+    seen = []
+    v = naive.new_var()
+    naive.push(lambda: seen.append(threading.get_ident()), write_vars=[v])
+    assert seen == [threading.get_ident()]       # runs inline on the pushing thread
+
+
+def test_async_error_surfaces_at_waitall():
+    from mxnet_b200 import engine
+    engine.push_async_error(mx.MXNetError('late failure'))
+    with pytest.raises(mx.MXNetError):
+        nd.waitall()
+    nd.waitall()                                  # reported once
+
+
+def test_invalid_op_arguments_raise_mxnet_error():
+    with pytest.raises(mx.MXNetError):
+        nd.dot(nd.ones((2, 3)), nd.ones((4, 5)))
+    with pytest.raises(mx.MXNetError):
+        nd.Convolution(nd.ones((1, 3, 5, 5)), nd.ones((4, 2, 3, 3)), kernel=(3, 3), num_filter=4, no_bias=True)
+
+
+def test_storage_pool_rounding_and_reuse():
+    pool = runtime.Pool(1, 0, strategy='Round', page=4096)          # device type 1: host memory
+    assert pool.round_size(1) >= 1 and pool.round_size(5000) >= 5000
+    p1, r1 = pool.alloc(5000)
+    pool.free(p1, r1)
+    p2, r2 = pool.alloc(4500)
+    assert p2 == p1, 'a freed block of the same bucket is reused'
+    st = pool.stats()
+    assert st['hits'] >= 1 and st['misses'] >= 1 and st['used'] >= 4500 and st['peak'] >= st['used']
+    pool.free(p2, r2)
+    assert pool.stats()['pooled'] > 0
+    pool.release_all()
+    assert pool.stats()['pooled'] == 0
+    unpooled = runtime.Pool(1, 0, strategy='Unpooled')
+    p, r = unpooled.alloc(100)
+    unpooled.free(p, r)
+    assert unpooled.stats()['pooled'] == 0
+
+
+def test_profiler_chrome_trace_and_aggregate(tmp_path):
+    f = str(tmp_path / 'profile.json')
+    profiler.set_config(profile_all=True, aggregate_stats=True, filename=f)
+    profiler.set_state('run')
+    a = nd.ones((64, 64))
+    for _ in range(3):
+        b = nd.dot(a, a)
+        b = nd.relu(b)
+    dom = profiler.Domain('mydomain')
+    with dom.new_task('stage'):
+        nd.sum(b).asscalar()
+    cnt = dom.new_counter('items', 5)
+    cnt += 3
+    dom.new_marker('here').mark('process')
+    nd.waitall()
+    profiler.set_state('stop')
+    table = profiler.dumps(reset=False)
+    assert 'dot' in table and 'relu' in table
+    stats = json.loads(profiler.dumps(format='json'))
+    names = json.dumps(stats)
+    assert 'dot' in names
+    profiler.dump()
+    trace = json.load(open(f))
+    events = trace['traceEvents']
+    assert any(e.get('name') == 'dot' for e in events)
+    assert any(e.get('name') == 'stage' for e in events)
+    assert any(e.get('ph') == 'C' and e.get('name') == 'items' for e in events)
+    assert all('ts' in e for e in events if e.get('ph') in ('X', 'B', 'E', 'C', 'i'))
+
+
+def test_profiler_pause_resume_and_scope():
+    profiler.set_config(profile_all=True, aggregate_stats=True, filename=os.devnull)
+    profiler.set_state('run')
+    profiler.dumps(reset=True)
+    profiler.pause()
+    nd.exp(nd.ones((4,)))
+    profiler.resume()
+    with profiler.scope('blockA:'):
+        nd.log(nd.ones((4,)))
+    profiler.set_state('stop')
+    table = profiler.dumps(reset=True)
+    assert 'log' in table and 'exp' not in table
+
+
+def test_feature_flags_and_env_registry():
+    feats = mx.runtime.Features()
+    assert feats.is_enabled('CUDA') in (True, False) and 'CUDA' in feats
+    assert isinstance(mx.runtime.feature_list(), list)
+    from mxnet_b200 import env
+    assert env.get('MXNET_KVSTORE_WAIT_MS') == 20000
+    with env.scope('MXNET_KVSTORE_WAIT_MS', 5):
+        assert env.get('MXNET_KVSTORE_WAIT_MS') == 5
+    assert 'MXNET_ENGINE_TYPE' in env.describe()
