@@ -1,0 +1,62 @@
+"""Shared timing harness of the model benchmarks: warm-up, CUDA-event timing with a barrier and a device
+synchronisation on both sides, maximum over ranks, clock sampling during the timed region, one JSON line."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def run(name, unit, items_per_step_per_gpu, make_step, args, config, baseline=None):
+    """``make_step(ctx, rank, world)`` returns ``step()`` which runs one training iteration and returns
+    the loss NDArray."""
+    import torch
+    import mxnet_b200 as mx
+    from mxnet_b200.ops import cuda as kernels
+    from mxnet_b200.parallel import dist
+    from mxnet_b200.utils import ClockSampler
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    if world > 1:
+        dist.ensure_initialized('nccl')
+    rank, local = dist.rank(), dist.local_rank()
+    torch.cuda.set_device(local)
+    ctx = mx.gpu(local)
+    mx.random.seed(4321 + rank)
+    step = make_step(ctx, rank, world)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+    for _ in range(max(args.warmup, 3)):
+        loss = step()
+    barrier()
+    sampler = ClockSampler(local).start()
+    l0 = kernels.launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = step()
+    e1.record()
+    barrier()
+    launches = kernels.launches() - l0
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=ctx.torch_device, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item())
+    value = items_per_step_per_gpu * world * args.steps / (ms / 1e3)
+    if rank == 0:
+        cfg = dict(config)
+        cfg['parallelism'] = 'dp%d' % world
+        print(json.dumps({'metric': name, 'value': value, 'unit': unit, 'n_gpus': world, 'steps': args.steps,
+                          'warmup': max(args.warmup, 3), 'ms_per_step': ms / args.steps, 'higher_is_better': True,
+                          'scaling': 'weak', 'vs_baseline': (value / baseline) if baseline else None, 'data': 'synthetic',
+                          'config': cfg, 'clocks': {k: clocks[k] for k in ('sm_mhz', 'sm_max_mhz', 'reasons')},
+                          'gpu_launches': int(launches), 'final_loss': float(loss.mean().asscalar())}))
+    if world > 1:
+        barrier()
+        dist.destroy()
+    return 0

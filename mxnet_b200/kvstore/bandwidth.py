@@ -53,6 +53,10 @@ def measure(path, num_keys, nbytes, dtype, iters, warmup, ctx, rank, world):
             g = p.grad(ctx)._data
             if not bool((g.float() == expect * (1 + i % 3)).all()):
                 raise RuntimeError('all-reduce result is wrong on rank %d key %d' % (rank, i))
+        # timed exchanges run on zeros: repeated in-place sums of non-zero values would overflow fp16 after a
+        # few rounds, and the time does not depend on the values
+        for p in params:
+            p.grad(ctx)._data.zero_()
         for _ in range(warmup):
             trainer.allreduce_grads()
         torch.cuda.synchronize()

@@ -46,3 +46,4 @@ def declare(L):
     sig('mxb_memcpy_h2d', i32, vp, vp, u64, vp)
     sig('mxb_error_string', C.c_char_p, i32)
     sig('mxb_gemm_tn', i32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp)
+    sig('mxb_gemm', i32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp)

@@ -191,7 +191,8 @@ __global__ void __launch_bounds__(256) fused_update_kernel(const __grid_constant
     nonfinite += src[0];
     sumsq += src[1];
   }
-  const bool skip = !alive || (nonfinite != 0.f);
+  // a plain all-reduce passes inf/nan through like any sum; only an optimizer step is skipped on overflow
+  const bool skip = !alive || (nonfinite != 0.f && p.mode != kModePlain);
   float coef = 1.f;
   if (p.max_norm > 0.f) coef = fminf(1.f, p.max_norm / (sqrtf(sumsq) + 1e-8f));
   if (!skip) {

@@ -1,9 +1,8 @@
 """FullyConnected / matmul on the tcgen05 GEMM kernel (``gemm_tcgen05.cu``).
 
-Forward and the data gradient run on the hand-written kernel (both are "TN" products: the second
-operand is stored with the contraction axis contiguous).  The weight gradient contracts over the
-row axis of both operands (an "NT" product in row-major terms); it needs MN-major operand
-descriptors and is served by the library GEMM for now."""
+Forward, data gradient and weight gradient all run on the hand-written kernel: it takes each operand
+either with the contraction axis contiguous ("K-major") or with the output axis contiguous
+("MN-major"), so no transposed copies are made."""
 import torch
 
 from . import lib, ptr, stream_ptr, count_launch, check
@@ -56,6 +55,37 @@ def gemm_tn(a, b, bias=None, act=None, out=None):
     return d
 
 
+def gemm(a, b, a_mn=False, b_mn=False, bias=None, act=None, out=None):
+    """``act(op(a) @ op(b) + bias)``.  ``a`` is [M, K] (``a_mn=False``) or [K, M] (``a_mn=True``); ``b`` is
+    [N, K] (``b_mn=False``) or [K, N] (``b_mn=True``); all row-major contiguous."""
+    if not a.is_contiguous():
+        a = a.contiguous()
+    if not b.is_contiguous():
+        b = b.contiguous()
+    K, M = (a.shape if a_mn else a.shape[::-1])
+    Kb, N = (b.shape if b_mn else b.shape[::-1])
+    require(a, 'a')
+    require(b, 'b', dtype=a.dtype, device=a.device)
+    if K != Kb:
+        raise ValueError('contraction sizes differ: %d vs %d' % (K, Kb))
+    d = out if out is not None else torch.empty(M, N, dtype=a.dtype, device=a.device)
+    require(d, 'out', dtype=a.dtype, device=a.device, shape=(M, N))
+    if bias is not None:
+        if bias.dtype != a.dtype:
+            bias = bias.to(a.dtype)
+        require(bias, 'bias', numel=N, device=a.device)
+    rc = lib().mxb_gemm(dt(a), ptr(a), ptr(b), ptr(d), ptr(bias), M, N, K, a.shape[1], b.shape[1], N,
+                        1 if a_mn else 0, 1 if b_mn else 0, _ACT[act], ptr(_error_flag(a.device)), stream_ptr(a.device))
+    check(rc, 'gemm')
+    count_launch(1)
+    return d
+
+
+def operand_ok(t):
+    """Row pitch a multiple of 8 elements and a 16-byte aligned base: what a TMA descriptor needs."""
+    return t.dim() == 2 and t.shape[1] % 8 == 0 and t.shape[0] >= 1 and t.data_ptr() % 16 == 0
+
+
 class LinearFn(torch.autograd.Function):
     """y = act(x @ w.T + b)."""
 
@@ -76,34 +106,34 @@ class LinearFn(torch.autograd.Function):
         elif ctx.act == 'gelu':
             raise RuntimeError('gelu epilogue has no fused backward; use act=None for training')
         dx = dw = db = None
+        ok = operand_ok(dy) and operand_ok(w) and operand_ok(x)
         if ctx.needs_input_grad[0]:
-            wt = w.t().contiguous()                    # [K, N]: contraction axis N contiguous
-            if supported(dy.shape[0], wt.shape[0], wt.shape[1]):
-                dx = gemm_tn(dy, wt)
-            else:
-                dx = dy @ w
+            # dx[M, K] = dy[M, N] . w[N, K]: w is read as an MN-major operand ([contraction, output])
+            dx = gemm(dy, w, False, True) if ok else dy @ w
         if ctx.needs_input_grad[1]:
-            dw = torch.matmul(dy.t(), x)               # library GEMM (see module docstring)
+            # dw[N, K] = dy[M, N]^T . x[M, K]: both operands MN-major, contraction over the batch axis
+            dw = gemm(dy, x, True, True) if ok else torch.matmul(dy.t(), x)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy.float().sum(0).to(ctx.bias_dtype)
         return dx, dw, db, None
 
 
 class MatmulFn(torch.autograd.Function):
-    """c = a @ b for 2-D operands."""
+    """c = a @ b for 2-D row-major operands."""
 
     @staticmethod
     def forward(ctx, a, b):
         ctx.save_for_backward(a, b)
-        return gemm_tn(a, b.t().contiguous())
+        return gemm(a, b, False, True)
 
     @staticmethod
     def backward(ctx, dc):
         a, b = ctx.saved_tensors
         dc = dc.contiguous()
         da = db = None
+        ok = operand_ok(dc) and operand_ok(a) and operand_ok(b)
         if ctx.needs_input_grad[0]:
-            da = gemm_tn(dc, b) if supported(dc.shape[0], b.shape[0], b.shape[1]) else dc @ b.t()
+            da = gemm(dc, b, False, False) if ok else dc @ b.t()          # dc[M, N] . b[K, N]^T
         if ctx.needs_input_grad[1]:
-            db = torch.matmul(a.t(), dc)
+            db = gemm(a, dc, True, True) if ok else torch.matmul(a.t(), dc)  # a[M, K]^T . dc[M, N]
         return da, db

@@ -1,6 +1,11 @@
 // Dense GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) fed by TMA, for sm_100a.
 //
-//   D[M, N] = act( A[M, K] · B[N, K]^T + bias[N] )        A, B, D: fp16 or bf16, accumulation in fp32
+//   D[M, N] = act( op(A) · op(B) + bias[N] )        A, B, D: fp16 or bf16, accumulation in fp32
+//
+// Each operand is either "K-major" (A stored [M, K], B stored [N, K]: the contraction axis is contiguous) or
+// "MN-major" (A stored [K, M], B stored [K, N]).  The four combinations cover the forward product of a
+// FullyConnected layer (K, K), its data gradient dY·W (K, MN), its weight gradient dYᵀ·X (MN, MN) and a plain
+// row-major matmul A·B (K, MN) without any transposed copy.
 //
 // This is the contraction behind FullyConnected / dot / batch_dot and 1x1 NHWC convolutions; the
 // reference sends all of them to cuBLAS (src/operator/linalg_impl.h: cublasGemmEx, pseudo-fp16 with fp32
@@ -84,9 +89,25 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
   return d;
 }
 
+// MN-major operand: the tile is a row of chunks, each 64 elements (128 bytes) of the M/N axis by 64 k-rows, written
+// by one TMA box with the 128-byte swizzle.  Leading byte offset = distance between chunks, stride byte offset =
+// distance between groups of 8 k-rows.
+constexpr uint32_t kMnChunkBytes = 64 * BK * 2;     // 8192
+__device__ __forceinline__ uint64_t make_desc_mn(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(kMnChunkBytes >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::f16: D fp32, A/B fp16 or bf16, both K-major, N and M tile sizes.
-__host__ __device__ constexpr uint32_t make_idesc(int bf16, int bn) {
-  return (1u << 4) | ((uint32_t)bf16 << 7) | ((uint32_t)bf16 << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// (bits 15 / 16 select MN-major A / B)
+__host__ __device__ constexpr uint32_t make_idesc(int bf16, int bn, int a_mn, int b_mn) {
+  return (1u << 4) | ((uint32_t)bf16 << 7) | ((uint32_t)bf16 << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+         ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -119,7 +140,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 template <typename T, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, T* __restrict__ D,
-               const T* __restrict__ bias, int M, int N, int K, int ldd, int act, int bf16, int* __restrict__ error_flag) {
+               const T* __restrict__ bias, int M, int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn,
+               int* __restrict__ error_flag) {
   using Cfg = TileCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr uint32_t B_BYTES = Cfg::B_BYTES;
@@ -173,15 +195,30 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
           if (!mbar_wait(&empty[s], phase ^ 1u)) { *abort_flag = 1; break; }
           mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-          tma_load_2d(sA + s * A_BYTES, &map_a, kt * BK, tile_m * BM, &full[s]);
-          tma_load_2d(sB + s * B_BYTES, &map_b, kt * BK, tile_n * BN, &full[s]);
+          if (!a_mn) {
+            tma_load_2d(sA + s * A_BYTES, &map_a, kt * BK, tile_m * BM, &full[s]);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(sA + s * A_BYTES + c * kMnChunkBytes, &map_a, tile_m * BM + c * 64, kt * BK, &full[s]);
+          }
+          if (!b_mn) {
+            tma_load_2d(sB + s * B_BYTES, &map_b, kt * BK, tile_n * BN, &full[s]);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sB + s * B_BYTES + c * kMnChunkBytes, &map_b, tile_n * BN + c * 64, kt * BK, &full[s]);
+          }
           *issued_it = it + 1;
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(bf16, BN);
+      const uint32_t idesc = make_idesc(bf16, BN, a_mn, b_mn);
+      // one UMMA_K step (16 elements of K): 32 bytes inside the swizzle atom for a K-major operand, 16 k-rows of
+      // 128 bytes for an MN-major operand; in units of the descriptor's 16-byte address field
+      const uint64_t a_step = a_mn ? (16 * 128) >> 4 : 2, b_step = b_mn ? (16 * 128) >> 4 : 2;
       int it = 0, t = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++t) {
         const int buf = t & 1;
@@ -196,13 +233,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (!mbar_wait(&full[s], phase)) { *abort_flag = 1; ok = false; break; }
           *consumed_it = it + 1;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint64_t adesc = make_desc(smem_u32(sA + s * A_BYTES));
-          const uint64_t bdesc = make_desc(smem_u32(sB + s * B_BYTES));
+          const uint32_t a_addr = smem_u32(sA + s * A_BYTES), b_addr = smem_u32(sB + s * B_BYTES);
+          const uint64_t adesc = a_mn ? make_desc_mn(a_addr) : make_desc(a_addr);
+          const uint64_t bdesc = b_mn ? make_desc_mn(b_addr) : make_desc(b_addr);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // advancing K by 16 elements = 32 bytes inside the swizzle atom: +2 in the 16-byte address field
-            umma(tmem_d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kt > 0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma(tmem_d, adesc + a_step * (uint64_t)k, bdesc + b_step * (uint64_t)k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
           umma_commit(&empty[s]);        // the stage is free once these MMAs have read it
         }
         if (!ok) break;
@@ -323,9 +359,14 @@ static int make_map(CUtensorMap* map, const void* base, int bf16, int64_t rows, 
   return rc == CUDA_SUCCESS ? 0 : -11;
 }
 
+// MN-major operand: global tensor [K rows, MN columns] with row pitch `ld`; box = 64 k-rows x 64 columns.
+static int make_map_mn(CUtensorMap* map, const void* base, int bf16, int64_t krows, int64_t mn, int64_t ld) {
+  return make_map(map, base, bf16, krows, mn, ld, BK);
+}
+
 template <typename T, int BN>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, void* D, const void* bias, int M, int N, int K, int ldd,
-                       int act, int bf16, int* error_flag, cudaStream_t st) {
+                       int act, int bf16, int a_mn, int b_mn, int* error_flag, cudaStream_t st) {
   using Cfg = TileCfg<BN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -336,7 +377,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, void* D, co
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   gemm_tn_kernel<T, BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ma, mb, (T*)D, (const T*)bias, M, N, K, ldd, act, bf16,
-                                                                     error_flag);
+                                                                     a_mn, b_mn, error_flag);
   return (int)cudaGetLastError();
 }
 
@@ -353,26 +394,34 @@ static int pick_bn(int M, int N) {
 
 using namespace mxb;
 
-// D[M,N] = act(A[M,K] * B[N,K]^T + bias).  lda/ldb/ldd are row pitches in elements.  Requirements: base
-// pointers 16-byte aligned, lda and ldb multiples of 8 elements, K >= 1.  `error_flag` is a device int set to
-// 1 when a CTA gave up waiting (the output is then incomplete).
-MXB_EXPORT int mxb_gemm_tn(int dtype, const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
-                           int lda, int ldb, int ldd, int act, int* error_flag, void* stream) {
+// D[M,N] = act(op(A) * op(B) + bias).  a_mn = 0: A is [M, K] with row pitch lda; a_mn = 1: A is [K, M] with row pitch
+// lda.  b_mn = 0: B is [N, K]; b_mn = 1: B is [K, N]; row pitch ldb.  ldd: row pitch of D.  All pitches in elements.
+// Requirements: base pointers 16-byte aligned, lda and ldb multiples of 8 elements.  `error_flag` is a device int set
+// to 1 when a CTA gave up waiting (the output is then incomplete).
+MXB_EXPORT int mxb_gemm(int dtype, const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda,
+                        int ldb, int ldd, int a_mn, int b_mn, int act, int* error_flag, void* stream) {
   if (dtype != kF16 && dtype != kBF16) return -1;
   if (M < 1 || N < 1 || K < 1) return -2;
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A % 16) || ((uintptr_t)B % 16) || ((uintptr_t)D % 16)) return -3;
+  if (lda < (a_mn ? M : K) || ldb < (b_mn ? N : K) || ldd < N) return -3;
   const int bf16 = dtype == kBF16;
   const int bn = pick_bn(M, N);
   CUtensorMap ma, mb;
-  int rc = make_map(&ma, A, bf16, M, K, lda, BM);
+  int rc = a_mn ? make_map_mn(&ma, A, bf16, K, M, lda) : make_map(&ma, A, bf16, M, K, lda, BM);
   if (rc) return rc;
-  rc = make_map(&mb, B, bf16, N, K, ldb, bn);
+  rc = b_mn ? make_map_mn(&mb, B, bf16, K, N, ldb) : make_map(&mb, B, bf16, N, K, ldb, bn);
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-#define MXB_GEMM(T)                                                                                          \
-  (bn == 256 ? launch_gemm<T, 256>(ma, mb, D, bias, M, N, K, ldd, act, bf16, error_flag, st)                  \
-   : bn == 128 ? launch_gemm<T, 128>(ma, mb, D, bias, M, N, K, ldd, act, bf16, error_flag, st)                \
-               : launch_gemm<T, 64>(ma, mb, D, bias, M, N, K, ldd, act, bf16, error_flag, st))
+#define MXB_GEMM(T)                                                                                                  \
+  (bn == 256 ? launch_gemm<T, 256>(ma, mb, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, error_flag, st)              \
+   : bn == 128 ? launch_gemm<T, 128>(ma, mb, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, error_flag, st)            \
+               : launch_gemm<T, 64>(ma, mb, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, error_flag, st))
   return bf16 ? MXB_GEMM(__nv_bfloat16) : MXB_GEMM(__half);
 #undef MXB_GEMM
+}
+
+// D[M,N] = act(A[M,K] * B[N,K]^T + bias): both operands K-major.
+MXB_EXPORT int mxb_gemm_tn(int dtype, const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
+                           int lda, int ldb, int ldd, int act, int* error_flag, void* stream) {
+  return mxb_gemm(dtype, A, B, D, bias, M, N, K, lda, ldb, ldd, 0, 0, act, error_flag, stream);
 }

@@ -209,6 +209,24 @@ def test_tcgen05_gemm_matches_fp32_reference(M, N, K, dtype):
     gemm_ops.check_errors()
 
 
+@pytest.mark.parametrize('a_mn,b_mn', [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize('M,N,K', [(128, 128, 64), (384, 200, 136), (72, 1000, 264), (1000, 72, 520), (4096, 512, 64)])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_tcgen05_gemm_operand_layouts(a_mn, b_mn, M, N, K, dtype):
+    """K-major and MN-major operands (stored [rows, K] or [K, rows]) in every combination."""
+    from mxnet_b200.ops.cuda import gemm_ops
+    torch.manual_seed(8)
+    a = torch.randn(M, K, device=_dev()).to(dtype)
+    b = torch.randn(N, K, device=_dev()).to(dtype)
+    ref = a.float() @ b.float().t()
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    d = gemm_ops.gemm(a_in, b_in, a_mn, b_mn)
+    gemm_ops.check_errors()
+    tol = (1e-2, 1e-2 * K ** 0.5) if dtype == torch.float16 else (2e-2, 4e-2 * K ** 0.5)
+    _close(d, ref, *tol)
+
+
 def test_linear_autograd_through_tcgen05():
     from mxnet_b200.ops.cuda import gemm_ops
     torch.manual_seed(6)
