@@ -20,6 +20,7 @@ def main():
     ap.add_argument('--masked', type=int, default=20)
     ap.add_argument('--dtype', default='float16', choices=['float16', 'bfloat16'])
     ap.add_argument('--layers', type=int, default=12)
+    ap.add_argument('--graphs', type=int, default=1, help='hybridize(static_alloc, static_shape): CUDA-graph replay')
     args = ap.parse_args()
 
     def make_step(ctx, rank, world):
@@ -31,9 +32,13 @@ def main():
         net = BERTForPretrain(vocab_size=30522, units=768, hidden_size=3072, num_layers=args.layers, num_heads=12,
                               max_length=512, dropout=0.1)
         net.initialize(mx.init.Normal(0.02), ctx=ctx)
-        trainer = gluon.Trainer(net.collect_params(), 'lamb', {'learning_rate': 1e-4, 'wd': 0.01, 'epsilon': 1e-6},
-                                kvstore='device')
+        # low-precision weights, fp32 master copies inside the optimizer: no per-step casts of 110 M parameters
+        net.cast(args.dtype)
+        trainer = gluon.Trainer(net.collect_params(), 'lamb', {'learning_rate': 1e-4, 'wd': 0.01, 'epsilon': 1e-6,
+                                                               'multi_precision': True}, kvstore='device')
         amp.init_trainer(trainer)
+        if args.graphs:
+            net.hybridize(static_alloc=True, static_shape=True)
         loss_fn = gluon.loss.SoftmaxCrossEntropyLoss()
         B, T, P = args.batch, args.seq_len, args.masked
         rng = np.random.RandomState(rank)
@@ -59,7 +64,7 @@ def main():
             return loss
         return step
     cfg = {'model': 'bert_base' if args.layers == 12 else 'bert_%dL' % args.layers, 'batch_per_gpu': args.batch,
-           'seq_len': args.seq_len, 'masked_per_seq': args.masked, 'optimizer': 'lamb', 'amp': args.dtype}
+           'seq_len': args.seq_len, 'masked_per_seq': args.masked, 'optimizer': 'lamb (multi-precision)', 'amp': args.dtype, 'cuda_graphs': bool(args.graphs)}
     return _harness.run('bert_pretrain_seq_per_s', 'seq/s', args.batch, make_step, args, cfg)
 
 

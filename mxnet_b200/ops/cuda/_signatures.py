@@ -35,6 +35,7 @@ def declare(L):
     sig('mxb_step_ctrl_offset', i32, i32)
     sig('mxb_fused_reduce', i32, i32, vp, vp)
     sig('mxb_fused_update', i32, i32, vp, vp)
+    sig('mxb_fused_lamb', i32, i32, vp, vp)
     sig('mxb_wait_probe', i32, vp, i32, u32, C.c_ulonglong, vp)
     sig('mxb_dev_alloc', i32, pvp, u64)
     sig('mxb_dev_free', i32, vp)

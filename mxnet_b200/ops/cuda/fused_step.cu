@@ -29,17 +29,18 @@ namespace mxb {
 
 constexpr int kMaxRanks = 8;
 
-enum StepMode { kModeSGD = 0, kModeNAG = 1, kModePlain = 2 };
-enum StepError { kOk = 0, kErrWaitReady = 1, kErrWaitReduced = 2, kErrWaitGather = 3 };
+enum StepMode { kModeSGD = 0, kModeNAG = 1, kModePlain = 2, kModeAdam = 3, kModeAdamW = 4, kModeLamb = 5 };
+enum StepError { kOk = 0, kErrWaitReady = 1, kErrWaitReduced = 2, kErrWaitGather = 3, kErrWaitNorms = 4 };
 
 struct __align__(256) Ctrl {
   // written by peers (index = sender rank)
   uint32_t ready[kMaxRanks];
   uint32_t reduced[kMaxRanks];
   uint32_t agdone[kMaxRanks];
+  uint32_t normed[kMaxRanks];
   float payload[kMaxRanks][4];
   // local
-  uint32_t ticket_a, ticket_b;
+  uint32_t ticket_a, ticket_b, ticket_c, pad0;
   uint32_t nonfinite;
   float sumsq;
   uint32_t status;          // first StepError seen (sticky until the host clears it)
@@ -68,6 +69,13 @@ struct StepParams {
   float scale_window, scale_max;
   int mode;
   unsigned long long timeout_ns;
+  // Adam / AdamW / LAMB
+  float* var;                       // second moment of the shard (`mom` holds the first moment)
+  float beta1, beta2, epsilon;
+  float coef1, coef2;               // 1 - beta1^t, 1 - beta2^t of this step (1 when bias correction is off)
+  float lower_bound, upper_bound;   // LAMB clamps of ||w|| (negative = off)
+  float* norm_acc;                  // local [2][nseg]: per-parameter partial sums of w^2 and u^2 over this shard
+  float* norm_in[kMaxRanks];        // every rank's receive area [kMaxRanks][2][nseg] (own entry = local pointer)
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -179,6 +187,63 @@ __device__ __forceinline__ int find_segment(const int64_t* seg_end, int nseg, in
   return lo;
 }
 
+// Common end of an optimizer step: clear the local gradient arena, adapt the loss scale, and leave only after every
+// rank's stores into this GPU's weight arena have landed.
+template <typename T>
+__device__ void finish_step(const StepParams& p, Ctrl* me, bool skip, float sumsq) {
+  constexpr int N = Vec16<T>::N;
+  if (p.mode != kModePlain) {
+    // every rank has finished reading this arena (all `reduced` flags seen): clear it for the next backward
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    T* ga = (T*)p.grads[p.rank];
+    const int64_t nv = p.total / N;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (int64_t)gridDim.x * blockDim.x)
+      *reinterpret_cast<uint4*>(ga + v * N) = z;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t ticket = atomicAdd(&me->ticket_b, 1u);
+    if (ticket == gridDim.x - 1) {
+      __threadfence();
+      me->scale_state[3] = sqrtf(sumsq);
+      if (p.use_loss_scale && p.mode != kModePlain) {
+        float s = me->scale_state[0], good = me->scale_state[1];
+        if (skip) { s = fmaxf(s * 0.5f, 1.f); good = 0.f; me->scale_state[2] += 1.f; }
+        else {
+          good += 1.f;
+          if (good >= p.scale_window) { s = fminf(s * 2.f, p.scale_max); good = 0.f; }
+        }
+        me->scale_state[0] = s;
+        me->scale_state[1] = good;
+      } else if (skip && p.mode != kModePlain) {
+        me->scale_state[2] += 1.f;
+      }
+      me->ticket_b = 0u;
+      if (p.nranks > 1) {
+        __threadfence_system();
+        for (int r = 0; r < p.nranks; ++r) st_release_sys(&p.ctrl[r]->agdone[p.rank], p.step);
+        // do not return before every rank's stores into this GPU's arena have landed
+        const unsigned long long t0 = now_ns();
+        for (int r = 0; r < p.nranks; ++r) {
+          unsigned spins = 0;
+          while ((int32_t)(ld_acquire_sys(&me->agdone[r]) - p.step) < 0) {
+            if ((++spins & 63u) == 0) {
+              if (now_ns() - t0 > p.timeout_ns) {
+                atomicCAS(&me->status, (uint32_t)kOk, (uint32_t)kErrWaitGather);
+                me->status_step = p.step;
+                r = p.nranks;
+                break;
+              }
+              __nanosleep(200);
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) fused_update_kernel(const __grid_constant__ StepParams p) {
   Ctrl* me = p.ctrl[p.rank];
@@ -233,18 +298,41 @@ __global__ void __launch_bounds__(256) fused_update_kernel(const __grid_constant
           m[j] = t.x; m[j + 1] = t.y; m[j + 2] = t.z; m[j + 3] = t.w;
         }
       }
+      const bool adam = p.mode == kModeAdam || p.mode == kModeAdamW;
+      float s2[N];
+      if (adam) {
+#pragma unroll
+        for (int j = 0; j < N; j += 4) {
+          float4 t = *reinterpret_cast<const float4*>(p.var + le + j);
+          s2[j] = t.x; s2[j + 1] = t.y; s2[j + 2] = t.z; s2[j + 3] = t.w;
+        }
+      }
+      // Adam folds the bias correction into the step size (python/mxnet/optimizer/adam.py: lr *= sqrt(c2) / c1)
+      const float lr_t = adam ? lr * sqrtf(p.coef2) / p.coef1 : lr;
 #pragma unroll
       for (int j = 0; j < N; ++j) {
         float gr = g[j] * coef;
         if (p.clip_gradient >= 0.f) gr = fminf(fmaxf(gr, -p.clip_gradient), p.clip_gradient);
-        gr += wd * w[j];
-        if (p.mom) {
-          m[j] = p.momentum * m[j] - lr * gr;
-          w[j] += (p.mode == kModeNAG) ? (p.momentum * m[j] - lr * gr) : m[j];
+        if (adam) {
+          if (p.mode == kModeAdam) gr += wd * w[j];
+          m[j] = p.beta1 * m[j] + (1.f - p.beta1) * gr;
+          s2[j] = p.beta2 * s2[j] + (1.f - p.beta2) * gr * gr;
+          w[j] -= lr_t * m[j] / (sqrtf(s2[j]) + p.epsilon);
+          if (p.mode == kModeAdamW && wd > 0.f) w[j] -= lr_t * wd * w[j];    // decoupled decay on the updated weight
         } else {
-          w[j] -= lr * gr;
+          gr += wd * w[j];
+          if (p.mom) {
+            m[j] = p.momentum * m[j] - lr * gr;
+            w[j] += (p.mode == kModeNAG) ? (p.momentum * m[j] - lr * gr) : m[j];
+          } else {
+            w[j] -= lr * gr;
+          }
         }
         out.v[j] = Cvt<T>::from_f(w[j]);
+      }
+      if (adam) {
+#pragma unroll
+        for (int j = 0; j < N; j += 4) *reinterpret_cast<float4*>(p.var + le + j) = make_float4(s2[j], s2[j + 1], s2[j + 2], s2[j + 3]);
       }
       if (p.master) {
 #pragma unroll
@@ -257,56 +345,152 @@ __global__ void __launch_bounds__(256) fused_update_kernel(const __grid_constant
       for (int r = 0; r < p.nranks; ++r) st16((T*)p.weights[r] + e, out);       // all-gather of the new weights
     }
   }
-  if (p.mode != kModePlain) {
-    // every rank has finished reading this arena (all `reduced` flags seen): clear it for the next backward
-    const uint4 z = make_uint4(0, 0, 0, 0);
-    T* ga = (T*)p.grads[p.rank];
-    const int64_t nv = p.total / N;
-    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (int64_t)gridDim.x * blockDim.x)
-      *reinterpret_cast<uint4*>(ga + v * N) = z;
+  finish_step<T>(p, me, skip, sumsq);
+}
+
+// ---- LAMB (python/mxnet/optimizer/lamb.py; src/operator/contrib/multi_lamb.cu) -----------------------------------
+// Phase 1: moments and the raw update u = m_hat / (sqrt(v_hat) + eps) + wd * w for this rank's shard (u replaces the
+// reduced gradient in `gred`), plus per-parameter partial sums of w^2 and u^2; the partial sums of every rank are
+// exchanged through peer stores.  Phase 2: trust ratio per parameter from the summed norms, weight update, all-gather.
+__device__ __forceinline__ void load_f(const float* p, float* out, int n) {
+  for (int j = 0; j < n; j += 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p + j);
+    out[j] = t.x; out[j + 1] = t.y; out[j + 2] = t.z; out[j + 3] = t.w;
   }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const uint32_t ticket = atomicAdd(&me->ticket_b, 1u);
-    if (ticket == gridDim.x - 1) {
-      __threadfence();
-      me->scale_state[3] = sqrtf(sumsq);
-      if (p.use_loss_scale && p.mode != kModePlain) {
-        float s = me->scale_state[0], good = me->scale_state[1];
-        if (skip) { s = fmaxf(s * 0.5f, 1.f); good = 0.f; me->scale_state[2] += 1.f; }
-        else {
-          good += 1.f;
-          if (good >= p.scale_window) { s = fminf(s * 2.f, p.scale_max); good = 0.f; }
-        }
-        me->scale_state[0] = s;
-        me->scale_state[1] = good;
-      } else if (skip && p.mode != kModePlain) {
-        me->scale_state[2] += 1.f;
+}
+__device__ __forceinline__ void store_f(float* p, const float* in, int n) {
+  for (int j = 0; j < n; j += 4) *reinterpret_cast<float4*>(p + j) = make_float4(in[j], in[j + 1], in[j + 2], in[j + 3]);
+}
+
+__device__ __forceinline__ bool step_verdict(const StepParams& p, Ctrl* me, bool alive, float* sumsq_out) {
+  float nonfinite = 0.f, sumsq = 0.f;
+  for (int r = 0; r < p.nranks; ++r) {
+    volatile float* src = me->payload[r];
+    nonfinite += src[0];
+    sumsq += src[1];
+  }
+  *sumsq_out = sumsq;
+  return !alive || nonfinite != 0.f;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) fused_lamb1_kernel(const __grid_constant__ StepParams p) {
+  Ctrl* me = p.ctrl[p.rank];
+  constexpr int N = Vec16<T>::N;
+  const bool alive = wait_flags(me->reduced, p.nranks, p.step, p.timeout_ns);
+  if (!alive && threadIdx.x == 0) { atomicCAS(&me->status, (uint32_t)kOk, (uint32_t)kErrWaitReduced); me->status_step = p.step; }
+  float sumsq;
+  const bool skip = step_verdict(p, me, alive, &sumsq);
+  float coef = 1.f;
+  if (p.max_norm > 0.f) coef = fminf(1.f, p.max_norm / (sqrtf(sumsq) + 1e-8f));
+  if (!skip) {
+    const int64_t v0 = p.shard_begin / N, v1 = p.shard_end / N;
+    for (int64_t v = v0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < v1; v += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t e = v * N, le = e - p.shard_begin;
+      const int seg = find_segment(p.seg_end, p.nseg, e);
+      const float wd = p.wd * p.wd_mult[seg];
+      float g[N], w[N], m[N], s2[N];
+      load_f(p.gred + le, g, N);
+      load_f(p.mom + le, m, N);
+      load_f(p.var + le, s2, N);
+      if (p.master) {
+        load_f(p.master + le, w, N);
+      } else {
+        const Vec16<T> cur = ld16((const T*)p.weights[p.rank] + e);
+#pragma unroll
+        for (int j = 0; j < N; ++j) w[j] = Cvt<T>::to_f(cur.v[j]);
       }
-      me->ticket_b = 0u;
-      if (p.nranks > 1) {
-        __threadfence_system();
-        for (int r = 0; r < p.nranks; ++r) st_release_sys(&p.ctrl[r]->agdone[p.rank], p.step);
-        // do not return before every rank's stores into this GPU's arena have landed
-        const unsigned long long t0 = now_ns();
-        for (int r = 0; r < p.nranks; ++r) {
-          unsigned spins = 0;
-          while ((int32_t)(ld_acquire_sys(&me->agdone[r]) - p.step) < 0) {
-            if ((++spins & 63u) == 0) {
-              if (now_ns() - t0 > p.timeout_ns) {
-                atomicCAS(&me->status, (uint32_t)kOk, (uint32_t)kErrWaitGather);
-                me->status_step = p.step;
-                r = p.nranks;
-                break;
-              }
-              __nanosleep(200);
-            }
-          }
-        }
+      float w2 = 0.f, u2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        float gr = g[j] * coef;
+        if (p.clip_gradient >= 0.f) gr = fminf(fmaxf(gr, -p.clip_gradient), p.clip_gradient);
+        m[j] = p.beta1 * m[j] + (1.f - p.beta1) * gr;
+        s2[j] = p.beta2 * s2[j] + (1.f - p.beta2) * gr * gr;
+        const float u = (m[j] / p.coef1) / (sqrtf(s2[j] / p.coef2) + p.epsilon) + wd * w[j];
+        g[j] = u;
+        w2 += w[j] * w[j];
+        u2 += u * u;
       }
+      store_f(p.gred + le, g, N);
+      store_f(p.mom + le, m, N);
+      store_f(p.var + le, s2, N);
+      // lanes of a warp that work on the same parameter combine their sums before the atomic
+      const unsigned peers = __match_any_sync(__activemask(), seg);
+      const int leader = __ffs(peers) - 1, lane = threadIdx.x & 31;
+      float a = w2, b = u2;
+      for (int o = 16; o > 0; o >>= 1) {
+        const float a2 = __shfl_down_sync(peers, a, o), b2 = __shfl_down_sync(peers, b, o);
+        if (lane + o < 32 && ((peers >> (lane + o)) & 1u)) { a += a2; b += b2; }
+      }
+      if (lane == leader) { atomicAdd(p.norm_acc + seg, a); atomicAdd(p.norm_acc + p.nseg + seg, b); }
     }
   }
+  __threadfence();
+  __syncthreads();
+  __shared__ int last;
+  if (threadIdx.x == 0) last = atomicAdd(&me->ticket_c, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (last) {                                  // last CTA of this rank: publish the partial norms to every rank
+    __threadfence();
+    const int n2 = 2 * p.nseg;
+    for (int i = threadIdx.x; i < n2; i += blockDim.x) {
+      const float val = __ldcg(p.norm_acc + i);
+      for (int r = 0; r < p.nranks; ++r) p.norm_in[r][(int64_t)p.rank * n2 + i] = val;
+      p.norm_acc[i] = 0.f;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < p.nranks) st_release_sys(&p.ctrl[threadIdx.x]->normed[p.rank], p.step);
+    if (threadIdx.x == 0) me->ticket_c = 0u;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) fused_lamb2_kernel(const __grid_constant__ StepParams p) {
+  Ctrl* me = p.ctrl[p.rank];
+  constexpr int N = Vec16<T>::N;
+  bool alive = wait_flags(me->reduced, p.nranks, p.step, p.timeout_ns);
+  const bool normed = wait_flags(me->normed, p.nranks, p.step, p.timeout_ns);
+  if (!normed && threadIdx.x == 0) { atomicCAS(&me->status, (uint32_t)kOk, (uint32_t)kErrWaitNorms); me->status_step = p.step; }
+  alive = alive && normed;
+  float sumsq;
+  const bool skip = step_verdict(p, me, alive, &sumsq);
+  if (!skip) {
+    const int n2 = 2 * p.nseg;
+    const float* recv = p.norm_in[p.rank];
+    const int64_t v0 = p.shard_begin / N, v1 = p.shard_end / N;
+    for (int64_t v = v0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < v1; v += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t e = v * N, le = e - p.shard_begin;
+      const int seg = find_segment(p.seg_end, p.nseg, e);
+      float w2 = 0.f, u2 = 0.f;
+      for (int r = 0; r < p.nranks; ++r) {       // fixed order: every rank computes the same ratio
+        w2 += __ldcg(recv + (int64_t)r * n2 + seg);
+        u2 += __ldcg(recv + (int64_t)r * n2 + p.nseg + seg);
+      }
+      float r1 = sqrtf(w2);
+      const float r2 = sqrtf(u2);
+      if (p.lower_bound >= 0.f) r1 = fmaxf(r1, p.lower_bound);
+      if (p.upper_bound >= 0.f) r1 = fminf(r1, p.upper_bound);
+      const float ratio = (r1 == 0.f || r2 == 0.f) ? 1.f : r1 / r2;
+      const float lr = p.lr * p.lr_mult[seg] * ratio;
+      float u[N], w[N];
+      load_f(p.gred + le, u, N);
+      if (p.master) {
+        load_f(p.master + le, w, N);
+      } else {
+        const Vec16<T> cur = ld16((const T*)p.weights[p.rank] + e);
+#pragma unroll
+        for (int j = 0; j < N; ++j) w[j] = Cvt<T>::to_f(cur.v[j]);
+      }
+      Vec16<T> out;
+#pragma unroll
+      for (int j = 0; j < N; ++j) { w[j] -= lr * u[j]; out.v[j] = Cvt<T>::from_f(w[j]); }
+      if (p.master) store_f(p.master + le, w, N);
+      for (int r = 0; r < p.nranks; ++r) st16((T*)p.weights[r] + e, out);
+    }
+  }
+  finish_step<T>(p, me, skip, sumsq);
 }
 
 // A wait that nothing satisfies: used by tests of the time-out path (flag index `slot` of `ready`).
@@ -360,6 +544,23 @@ MXB_EXPORT int mxb_fused_update(int dtype, const void* params, void* stream) {
   else if (dtype == kF16) fused_update_kernel<__half><<<step_grid(p.shard_end - p.shard_begin, p.total, 8), 256, 0, st>>>(p);
   else if (dtype == kBF16) fused_update_kernel<__nv_bfloat16><<<step_grid(p.shard_end - p.shard_begin, p.total, 8), 256, 0, st>>>(p);
   else return -1;
+  return (int)cudaGetLastError();
+}
+
+// LAMB: phase 1 (moments, raw update, partial norms) and phase 2 (trust ratio, update, all-gather) after mxb_fused_reduce.
+MXB_EXPORT int mxb_fused_lamb(int dtype, const void* params, void* stream) {
+  StepParams p = *static_cast<const StepParams*>(params);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (p.nranks < 1 || p.nranks > kMaxRanks) return -2;
+  if (!p.mom || !p.var || !p.norm_acc || !p.norm_in[p.rank] || p.nseg < 1) return -3;
+#define MXB_LAMB(T, n)                                                                                   \
+  fused_lamb1_kernel<T><<<step_grid(p.shard_end - p.shard_begin, 0, n), 256, 0, st>>>(p);                  \
+  fused_lamb2_kernel<T><<<step_grid(p.shard_end - p.shard_begin, p.total, n), 256, 0, st>>>(p);
+  if (dtype == kF32) { MXB_LAMB(float, 4) }
+  else if (dtype == kF16) { MXB_LAMB(__half, 8) }
+  else if (dtype == kBF16) { MXB_LAMB(__nv_bfloat16, 8) }
+  else return -1;
+#undef MXB_LAMB
   return (int)cudaGetLastError();
 }
 

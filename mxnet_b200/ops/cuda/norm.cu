@@ -384,12 +384,12 @@ ln_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const float* __
   }
 }
 
-__global__ void ln_bwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int C, float* __restrict__ dgamma,
-                                       float* __restrict__ dbeta) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float a = 0.f, b = 0.f;
-  for (int k = 0; k < nblocks; ++k) { a += partial[((int64_t)k * 2) * C + c]; b += partial[((int64_t)k * 2 + 1) * C + c]; }
+__global__ void __launch_bounds__(kFinX * kFinY)
+ln_bwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int C, float* __restrict__ dgamma,
+                       float* __restrict__ dbeta) {
+  float a, b;
+  if (!finalize_sums(partial, nblocks, C, a, b)) return;
+  const int c = blockIdx.x * kFinX + threadIdx.x;
   dgamma[c] = a;
   dbeta[c] = b;
 }
@@ -454,7 +454,7 @@ static int ln_bwd_t(const void* x, const void* dy, const float* gamma, const flo
                     float* dgamma, float* dbeta, float* scratch, int64_t rows, int C, cudaStream_t st) {
   int grid = ln_grid(rows);
   ln_bwd_kernel<T><<<grid, kLnThreads, 0, st>>>((const T*)x, (const T*)dy, gamma, mean, rstd, (T*)dx, scratch, rows, C);
-  ln_bwd_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(scratch, grid, C, dgamma, dbeta);
+  ln_bwd_finalize_kernel<<<(C + kFinX - 1) / kFinX, dim3(kFinX, kFinY), 0, st>>>(scratch, grid, C, dgamma, dbeta);
   return (int)cudaGetLastError();
 }
 

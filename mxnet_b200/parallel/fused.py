@@ -29,10 +29,11 @@ from ..base import MXNetError
 from . import dist
 
 _MAXR = 8
-MODE_SGD, MODE_NAG, MODE_PLAIN = 0, 1, 2
+MODE_SGD, MODE_NAG, MODE_PLAIN, MODE_ADAM, MODE_ADAMW, MODE_LAMB = 0, 1, 2, 3, 4, 5
 _ERRORS = {1: 'waiting for the other ranks to finish their backward pass',
            2: 'waiting for the other ranks to publish their reduced shard',
-           3: 'waiting for the other ranks to finish writing weights'}
+           3: 'waiting for the other ranks to finish writing weights',
+           4: 'waiting for the other ranks to publish their parameter norms'}
 
 
 class StepParams(C.Structure):
@@ -43,7 +44,9 @@ class StepParams(C.Structure):
                 ('step', C.c_uint32), ('rescale', C.c_float), ('use_loss_scale', C.c_int), ('lr', C.c_float),
                 ('wd', C.c_float), ('momentum', C.c_float), ('clip_gradient', C.c_float), ('max_norm', C.c_float),
                 ('scale_window', C.c_float), ('scale_max', C.c_float), ('mode', C.c_int),
-                ('timeout_ns', C.c_ulonglong)]
+                ('timeout_ns', C.c_ulonglong), ('var', C.c_void_p), ('beta1', C.c_float), ('beta2', C.c_float),
+                ('epsilon', C.c_float), ('coef1', C.c_float), ('coef2', C.c_float), ('lower_bound', C.c_float),
+                ('upper_bound', C.c_float), ('norm_acc', C.c_void_p), ('norm_in', C.c_void_p * _MAXR)]
 
 
 class _DevBuf(object):
@@ -60,9 +63,12 @@ def _lib():
 
 
 def supports(optimizer, params):
-    """SGD / NAG on dense parameters of one floating dtype living on one CUDA device."""
+    """SGD / NAG / Adam / AdamW / LAMB on dense parameters of one floating dtype living on one CUDA device."""
     from ..optimizer import optimizer as opt
-    if type(optimizer) not in (opt.SGD, opt.NAG):
+    if type(optimizer) not in (opt.SGD, opt.NAG, opt.Adam, opt.AdamW, opt.LAMB):
+        return False
+    if type(optimizer) is opt.Adam and getattr(optimizer, 'lazy_update', False) and any(
+            p._grad_stype != 'default' for p in params):
         return False
     dtypes = set()
     for p in params:
@@ -115,7 +121,9 @@ class FusedStep(object):
         shard = self.total // self.nranks
         self.shard_begin, self.shard_end = self.rank * shard, (self.rank + 1) * shard
         # ---- one IPC-exportable slab: [control block | weight arena | gradient arena] ---------------
-        self.ctrl_bytes = (L.mxb_step_ctrl_bytes() + 255) // 256 * 256
+        self.nseg = len(arrs)
+        self._norm_off = (L.mxb_step_ctrl_bytes() + 255) // 256 * 256
+        self.ctrl_bytes = (self._norm_off + _MAXR * 2 * self.nseg * 4 + 255) // 256 * 256
         arena_bytes = self.total * self.esize
         self.slab_bytes = self.ctrl_bytes + 2 * arena_bytes
         ptr = C.c_void_p()
@@ -166,7 +174,14 @@ class FusedStep(object):
         self.master = None
         if self.dtype != torch.float32:
             self.master = self.weights[self.shard_begin:self.shard_end].float()
-        self.mom = torch.zeros(n_shard, dtype=torch.float32, device=self.device) if optimizer.momentum != 0.0 else None
+        from ..optimizer import optimizer as _opt
+        kind = type(optimizer)
+        self.mode = {_opt.NAG: MODE_NAG, _opt.Adam: MODE_ADAM, _opt.AdamW: MODE_ADAMW, _opt.LAMB: MODE_LAMB}.get(kind, MODE_SGD)
+        two_moments = self.mode in (MODE_ADAM, MODE_ADAMW, MODE_LAMB)
+        need_mom = two_moments or getattr(optimizer, 'momentum', 0.0) != 0.0
+        self.mom = torch.zeros(n_shard, dtype=torch.float32, device=self.device) if need_mom else None
+        self.var = torch.zeros(n_shard, dtype=torch.float32, device=self.device) if two_moments else None
+        self.norm_acc = torch.zeros(2 * self.nseg, dtype=torch.float32, device=self.device)
         seg_end = np.asarray([o + (s + vec - 1) // vec * vec for o, s in zip(offs, self.sizes)], dtype=np.int64)
         seg_end[-1] = self.total
         self.seg_end = torch.from_numpy(seg_end).to(self.device)
@@ -186,8 +201,6 @@ class FusedStep(object):
         self._scaler_attached = None
         self.max_norm = -1.0
         self._dt_code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[self.dtype]
-        from ..optimizer import optimizer as opt
-        self.mode = MODE_NAG if type(optimizer) is opt.NAG else MODE_SGD
         if self.nranks > 1:
             torch.cuda.synchronize(self.device)
             dist.barrier()
@@ -230,6 +243,20 @@ class FusedStep(object):
             sp.scale_max = float(self._scaler_attached._max_loss_scale)
         sp.mode = mode
         sp.timeout_ns = self.timeout_ms * 1000000
+        if self.var is not None:
+            sp.var = self.var.data_ptr()
+            sp.beta1, sp.beta2, sp.epsilon = float(opt.beta1), float(opt.beta2), float(opt.epsilon)
+            t = opt._index_update_count.get(self.param_ids[0], opt.begin_num_update) if self.param_ids else 1
+            t = max(int(t), 1)
+            correct = getattr(opt, 'bias_correction', True) if mode == MODE_LAMB else getattr(opt, 'correct_bias', True)
+            sp.coef1 = 1.0 - opt.beta1 ** t if correct else 1.0
+            sp.coef2 = 1.0 - opt.beta2 ** t if correct else 1.0
+            lo, hi = getattr(opt, 'lower_bound', None), getattr(opt, 'upper_bound', None)
+            sp.lower_bound = -1.0 if lo is None else float(lo)
+            sp.upper_bound = -1.0 if hi is None else float(hi)
+        sp.norm_acc = self.norm_acc.data_ptr()
+        for r in range(self.nranks):
+            sp.norm_in[r] = self.peer_base[r] + self._norm_off
         return sp
 
     def _check_status(self):
@@ -256,10 +283,11 @@ class FusedStep(object):
         st = cuda.stream_ptr(self.device)
         rc = L.mxb_fused_reduce(self._dt_code, C.byref(sp), st)
         if rc == 0:
-            rc = L.mxb_fused_update(self._dt_code, C.byref(sp), st)
+            rc = L.mxb_fused_lamb(self._dt_code, C.byref(sp), st) if mode == MODE_LAMB else \
+                L.mxb_fused_update(self._dt_code, C.byref(sp), st)
         if rc != 0:
-            raise MXNetError('fused step launch failed: %s' % L.mxb_error_string(rc).decode())
-        cuda.count_launch(2)
+            raise MXNetError('fused step launch failed: %s' % (L.mxb_error_string(rc).decode() if rc > 0 else rc))
+        cuda.count_launch(3 if mode == MODE_LAMB else 2)
         self._status_host.copy_(self.status, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream(self.device))
@@ -323,18 +351,20 @@ class FusedStep(object):
         return torch.cat(parts)
 
     def export_states(self, updater):
-        """Write the sharded state into ``updater.states`` in the layout the generic optimizers use
-        (``(master, momentum)`` per index for multi-precision, else ``momentum``)."""
+        """Write the sharded state into ``updater.states`` in the layout the generic optimizers use:
+        ``momentum`` (SGD/NAG) or ``(mean, var)`` (Adam/AdamW/LAMB), wrapped as ``(master, inner)`` for
+        multi-precision."""
         from ..ndarray.ndarray import NDArray
         master = self._gather(self.master) if self.master is not None else None
         mom = self._gather(self.mom) if self.mom is not None else None
+        var = self._gather(self.var) if self.var is not None else None
         for p, idx, off, n in zip(self.params, self.param_ids, self.offsets, self.sizes):
             shape = p._data[self.ctx]._data.shape
-            m = NDArray._from_tensor(mom[off:off + n].view(shape).clone(), self.ctx) if mom is not None else None
-            if master is not None:
-                updater.states[idx] = (NDArray._from_tensor(master[off:off + n].view(shape).clone(), self.ctx), m)
-            else:
-                updater.states[idx] = m
+
+            def piece(flat):
+                return NDArray._from_tensor(flat[off:off + n].view(shape).clone(), self.ctx) if flat is not None else None
+            inner = (piece(mom), piece(var)) if var is not None else piece(mom)
+            updater.states[idx] = (piece(master), inner) if master is not None else inner
             updater.states_synced[idx] = True
 
     def import_states(self, updater, optimizer):
@@ -343,16 +373,16 @@ class FusedStep(object):
             st = updater.states.get(idx)
             if st is None:
                 continue
-            master, mom = (st if isinstance(st, (tuple, list)) else (None, st))
+            master, inner = (st if self.master is not None and isinstance(st, (tuple, list)) else (None, st))
+            mom, var = (inner if self.var is not None and isinstance(inner, (tuple, list)) else (inner, None))
             lo, hi = max(off, self.shard_begin), min(off + n, self.shard_end)
             if lo >= hi:
                 continue
             src = slice(lo - off, hi - off)
             dst = slice(lo - self.shard_begin, hi - self.shard_begin)
-            if master is not None and self.master is not None:
-                self.master[dst].copy_(master._data.reshape(-1)[src].to(self.device))
-            if mom is not None and self.mom is not None:
-                self.mom[dst].copy_(mom._data.reshape(-1)[src].to(self.device))
+            for mine, theirs in ((self.master, master), (self.mom, mom), (self.var, var)):
+                if mine is not None and theirs is not None:
+                    mine[dst].copy_(theirs._data.reshape(-1)[src].to(self.device))
 
     def __del__(self):
         try:

@@ -182,7 +182,8 @@ def unpack(s):
 def unpack_img(s, iscolor=-1):
     header, s = unpack(s)
     from .image import _decode_to_numpy
-    return header, _decode_to_numpy(s, iscolor)
+    # OpenCV convention of the reference (cv2.imdecode): colour images come back in BGR order
+    return header, _decode_to_numpy(s, 1 if iscolor != 0 else 0, to_rgb=False)
 
 
 def pack_img(header, img, quality=95, img_fmt='.jpg'):

@@ -30,11 +30,12 @@ def build(ctx, dtype):
     return net
 
 
-def run(fused, dtype, steps, ctx, rank, world):
+def run(fused, dtype, steps, ctx, rank, world, optimizer='sgd'):
     with env.scope('MXNET_KVSTORE_FUSED', '1' if fused else '0'):
         net = build(ctx, dtype)
-        trainer = gluon.Trainer(net.collect_params(), 'sgd', {'learning_rate': 0.05, 'momentum': 0.9, 'wd': 1e-3,
-                                                              'multi_precision': dtype != 'float32'}, kvstore='device')
+        opts = {'sgd': {'learning_rate': 0.05, 'momentum': 0.9, 'wd': 1e-3, 'multi_precision': dtype != 'float32'},
+                'lamb': {'learning_rate': 0.01, 'wd': 0.01}, 'adam': {'learning_rate': 0.01, 'wd': 0.01}}[optimizer]
+        trainer = gluon.Trainer(net.collect_params(), optimizer, opts, kvstore='device')
         loss_fn = gluon.loss.SoftmaxCrossEntropyLoss()
         rng = np.random.RandomState(123)
         per = 8
@@ -69,6 +70,15 @@ def main():
         torch.distributed.all_gather(gathered, flat)
         same = all(bool(torch.equal(gathered[0], g)) for g in gathered)
         report[dtype] = {'max_abs_diff_vs_nccl_path': err, 'ranks_identical': same}
+    for optimizer in ('lamb', 'adam'):
+        w_fused = run(True, 'float32', 5, ctx, rank, world, optimizer)
+        w_plain = run(False, 'float32', 5, ctx, rank, world, optimizer)
+        err = max(float((a - b).abs().max()) for a, b in zip(w_fused, w_plain))
+        flat = torch.cat([w.reshape(-1) for w in w_fused])
+        gathered = [torch.empty_like(flat) for _ in range(world)]
+        torch.distributed.all_gather(gathered, flat)
+        report[optimizer] = {'max_abs_diff_vs_nccl_path': err,
+                             'ranks_identical': all(bool(torch.equal(gathered[0], g)) for g in gathered)}
     if rank == 0:
         print('REPORT ' + json.dumps(report))
     dist.barrier()

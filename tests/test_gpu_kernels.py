@@ -287,6 +287,57 @@ def test_fused_step_matches_multi_precision_sgd(dtype):
             assert float(p.grad(ctx)._data.abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize('name,kwargs', [('adam', {'learning_rate': 0.01, 'wd': 0.01}),
+                                         ('adamw', {'learning_rate': 0.01, 'wd': 0.1}),
+                                         ('lamb', {'learning_rate': 0.01, 'wd': 0.01}),
+                                         ('lamb', {'learning_rate': 0.01, 'wd': 0.01, 'lower_bound': 0.5, 'upper_bound': 2.0}),
+                                         ('nag', {'learning_rate': 0.05, 'momentum': 0.9, 'wd': 1e-3})])
+def test_fused_step_matches_generic_optimizer(name, kwargs):
+    """The fused kernels against the per-parameter optimizer path of the same framework, fp32 weights."""
+    from mxnet_b200 import env
+    ctx = mx.gpu(0)
+    results = []
+    for fused in (True, False):
+        with env.scope('MXNET_KVSTORE_FUSED', '1' if fused else '0'):
+            mx.random.seed(3)
+            np.random.seed(3)
+            net = _tiny_net(ctx, 'float32')
+            trainer = gluon.Trainer(net.collect_params(), name, dict(kwargs), kvstore='device')
+            loss_fn = gluon.loss.SoftmaxCrossEntropyLoss()
+            rng = np.random.RandomState(5)
+            for step in range(5):
+                x = nd.array(rng.randn(16, 32).astype('float32'), ctx=ctx)
+                y = nd.array(rng.randint(0, 10, (16,)), ctx=ctx)
+                with autograd.record():
+                    loss = loss_fn(net(x), y)
+                loss.backward()
+                trainer.step(16)
+            assert (trainer._fused is not None) == fused
+            results.append([p.data(ctx)._data.detach().clone() for p in net.collect_params().values()])
+    for a, b in zip(*results):
+        _close(a, b, 2e-4, 2e-5)
+
+
+def test_fused_step_states_round_trip(tmp_path):
+    ctx = mx.gpu(0)
+    net = _tiny_net(ctx, 'float32')
+    trainer = gluon.Trainer(net.collect_params(), 'lamb', {'learning_rate': 0.01}, kvstore='device')
+    x, y = nd.array(np.random.randn(8, 32).astype('float32'), ctx=ctx), nd.array(np.random.randint(0, 10, (8,)), ctx=ctx)
+    loss_fn = gluon.loss.SoftmaxCrossEntropyLoss()
+    for _ in range(2):
+        with autograd.record():
+            loss = loss_fn(net(x), y)
+        loss.backward()
+        trainer.step(8)
+    f = str(tmp_path / 'lamb.states')
+    trainer.save_states(f)
+    mean0 = trainer._fused.mom.clone()
+    trainer._fused.mom.zero_()
+    trainer._fused.var.zero_()
+    trainer.load_states(f)
+    assert torch.equal(trainer._fused.mom, mean0) and float(trainer._fused.var.abs().sum()) > 0
+
+
 def test_fused_step_skips_on_overflow_and_halves_loss_scale():
     from mxnet_b200 import amp
     ctx = mx.gpu(0)

@@ -33,3 +33,5 @@ def test_fused_step_matches_nccl_path_across_ranks(nproc):
     assert rep['float32']['ranks_identical'] and rep['float16']['ranks_identical']
     assert rep['float32']['max_abs_diff_vs_nccl_path'] < 1e-5
     assert rep['float16']['max_abs_diff_vs_nccl_path'] < 5e-3
+    for name in ('lamb', 'adam'):
+        assert rep[name]['ranks_identical'] and rep[name]['max_abs_diff_vs_nccl_path'] < 1e-4
