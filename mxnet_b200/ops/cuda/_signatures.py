@@ -17,6 +17,10 @@ def declare(L):
     sig('mxb_bn_backward', i32, i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, vp)
     sig('mxb_maxpool_forward', i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp)
     sig('mxb_maxpool_backward', i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp)
+    sig('mxb_lstm_supported', i32, i32, i32)
+    sig('mxb_lstm_forward', i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp)
+    sig('mxb_lstm_backward', i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp)
+    sig('mxb_lstm_exchange_bytes', i64, i32, i32)
     sig('mxb_ln_forward', i32, i32, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp)
     sig('mxb_ln_backward', i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, vp)
     sig('mxb_softmax_forward', i32, i32, vp, vp, i64, i32, i32, vp)

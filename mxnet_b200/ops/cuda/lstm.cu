@@ -1,0 +1,425 @@
+// Persistent LSTM recurrence kernels for sm_100a.
+//
+// Reference behaviour: the `RNN` operator in lstm mode (src/operator/rnn-inl.h, cudnnRNNForwardTraining /
+// cudnnRNNBackwardData / cudnnRNNBackwardWeights; CPU math in src/operator/rnn_impl.h).  Gate order i, f, g, o.
+//
+// The input projection x_t·W_ihᵀ + b_ih + b_hh of all time steps is one large GEMM done before these kernels
+// (tensor cores); what remains is the strictly sequential part
+//     a_t = xproj_t + h_{t-1}·W_hhᵀ,  i,f,o = sigmoid(a), g = tanh(a),  c_t = f·c_{t-1} + i·g,  h_t = o·tanh(c_t)
+// which is latency-bound: a (batch x H) by (H x 4H) product per step.  One cooperative launch covers all time steps:
+//   * every CTA owns a slice of `U` hidden units and keeps the 4U rows of W_hh that produce their gates in shared
+//     memory for the whole sequence (no weight traffic per step);
+//   * h_{t-1} lives in a k-major exchange buffer in global memory ([H][batch]); per step a CTA streams it through shared
+//     memory in tiles with double-buffered 16-byte cp.async copies, each thread owns a pair of batch rows and a residue
+//     class of the tile's k rows and multiplies against the resident weights (broadcast reads), partial sums are
+//     combined through shared memory, then the cell update of the CTA's units is done in place;
+//   * the new h slice goes to the other half of the exchange buffer and all CTAs meet at a grid barrier (an arrival
+//     counter with a bounded spin); c and the carried gradients never leave the CTA.
+// The backward kernel walks the time steps in reverse with the same ownership: phase A turns dh_t, dc_t into the gate
+// gradients of the CTA's units, the barrier publishes them, phase B contracts all 4H gate gradients with the CTA's
+// columns of W_hh (also resident in shared memory) to obtain dh_{t-1} for its units.  Weight and input gradients are
+// large GEMMs over the saved gate gradients, done outside.
+// A barrier that does not complete within its time budget sets an error flag and every CTA leaves the loop.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace mxb {
+
+constexpr int kLstmThreads = 256;
+constexpr unsigned long long kLstmBarrierNs = 2000000000ull;    // 2 s per barrier
+
+struct LstmParams {
+  const void* xproj;     // [T, B, 4H]  x·W_ihᵀ + b_ih + b_hh
+  const void* whh;       // [4H, H]
+  const void* h0;        // [B, H]
+  const void* c0;        // [B, H]
+  void* y;               // [T, B, H]
+  void* hT;              // [B, H]
+  void* cT;              // [B, H]
+  void* gates;           // [T, B, 4H] activated gates (saved for backward; may be null for inference)
+  float* cs;             // [T, B, H] cell states in fp32 (saved for backward; may be null)
+  void* hbuf;            // exchange buffer, k-major: forward [2][H][Bp] of h, backward [4H][Bp] of gate gradients
+  int Bp;                // batch rounded up to a multiple of 8 (row length of the exchange buffer)
+  unsigned int* bar;     // [2] arrival counter, error flag
+  int T, B, H, U;        // U: hidden units per CTA
+  // backward only
+  const void* dy;        // [T, B, H]
+  const void* dhT;       // [B, H] or null
+  const void* dcT;       // [B, H] or null
+  void* dgates;          // [T, B, 4H] gradient w.r.t. the pre-activation gates
+  void* dh0;             // [B, H]
+  void* dc0;             // [B, H]
+};
+
+__device__ __forceinline__ unsigned long long lstm_now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// All CTAs arrive; returns false when the others did not show up in time (or an error was already flagged).
+__device__ bool grid_barrier(unsigned int* bar, unsigned int target) {
+  __shared__ int ok;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ok = 1;
+    atomicAdd(bar, 1u);
+    const unsigned long long t0 = lstm_now_ns();
+    unsigned spins = 0;
+    while ((int)(*(volatile unsigned int*)bar - target) < 0) {
+      if (*(volatile unsigned int*)(bar + 1) != 0u) { ok = 0; break; }
+      if ((++spins & 63u) == 0 && lstm_now_ns() - t0 > kLstmBarrierNs) {
+        atomicExch(bar + 1, 1u);
+        ok = 0;
+        break;
+      }
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  return ok != 0;
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+template <typename T>
+__device__ __forceinline__ float ldf(const void* p, int64_t i) { return Cvt<T>::to_f(static_cast<const T*>(p)[i]); }
+template <typename T>
+__device__ __forceinline__ void stf(void* p, int64_t i, float v) { static_cast<T*>(p)[i] = Cvt<T>::from_f(v); }
+
+// ---- streaming a [K][Bp] matrix from global memory through shared memory against resident weights ------------------
+// The exchanged operand (h_{t-1}, or the gate gradients of step t) is kept K-major in global memory: row k holds the
+// values of all batch rows.  A CTA copies it in tiles of kTileK rows with 16-byte cp.async (double buffered) and every
+// thread owns one pair of batch rows and a residue class of the tile's k rows, so a warp reads consecutive words of
+// the staged tile (no bank conflicts) and the weight row of that k as a broadcast.
+constexpr int kTileK = 48;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename X>
+__device__ __forceinline__ void issue_tile(const X* __restrict__ src, X* __restrict__ stage, int k0, int K, int Bp) {
+  const int rows = min(kTileK, K - k0);
+  const int chunks_per_row = Bp * (int)sizeof(X) / 16;
+  const int total = rows * chunks_per_row;
+  const char* g = reinterpret_cast<const char*>(src + (int64_t)k0 * Bp);
+  char* s = reinterpret_cast<char*>(stage);
+  for (int c = threadIdx.x; c < total; c += blockDim.x) cp_async16(s + (size_t)c * 16, g + (size_t)c * 16);
+}
+
+// acc[2][OUT] += sum_k src[k][b0 + {0,1}] * W[k][0..OUT) over all K rows; W: shared memory, row stride OUT floats.
+template <typename X, int OUT>
+__device__ __forceinline__ void stream_matmul(const X* __restrict__ src, int K, int Bp, const float* __restrict__ W,
+                                              X* __restrict__ stage /* 2 tiles of kTileK*Bp */, int kg, int KG, int b0,
+                                              bool active, float (&acc)[2][OUT]) {
+#pragma unroll
+  for (int o = 0; o < OUT; ++o) { acc[0][o] = 0.f; acc[1][o] = 0.f; }
+  const int ntiles = (K + kTileK - 1) / kTileK;
+  issue_tile(src, stage, 0, K, Bp);
+  cp_async_commit();
+  for (int tile = 0; tile < ntiles; ++tile) {
+    X* cur = stage + (size_t)(tile & 1) * kTileK * Bp;
+    if (tile + 1 < ntiles) {
+      issue_tile(src, stage + (size_t)((tile + 1) & 1) * kTileK * Bp, (tile + 1) * kTileK, K, Bp);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (active) {
+      const int k0 = tile * kTileK, rows = min(kTileK, K - k0);
+      for (int k = kg; k < rows; k += KG) {
+        const float x0 = Cvt<X>::to_f(cur[(size_t)k * Bp + b0]), x1 = Cvt<X>::to_f(cur[(size_t)k * Bp + b0 + 1]);
+        const float* w = W + (size_t)(k0 + k) * OUT;
+        if constexpr (OUT % 4 == 0) {
+          const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+          for (int q = 0; q < OUT / 4; ++q) {
+            const float4 wv = w4[q];
+            acc[0][4 * q] += x0 * wv.x; acc[0][4 * q + 1] += x0 * wv.y; acc[0][4 * q + 2] += x0 * wv.z; acc[0][4 * q + 3] += x0 * wv.w;
+            acc[1][4 * q] += x1 * wv.x; acc[1][4 * q + 1] += x1 * wv.y; acc[1][4 * q + 2] += x1 * wv.z; acc[1][4 * q + 3] += x1 * wv.w;
+          }
+        } else {
+#pragma unroll
+          for (int o = 0; o < OUT; ++o) {
+            const float wv = w[o];
+            acc[0][o] += x0 * wv;
+            acc[1][o] += x1 * wv;
+          }
+        }
+      }
+    }
+    __syncthreads();          // the tile may be overwritten by the copy issued in the next trip
+  }
+}
+
+// Forward.  Shared memory: Wt [H][4U] (W_hh rows of this CTA's units, k-major), red [KG][Bp][4U], cst [Bp][U],
+// stage [2][kTileK][Bp] of the exchange type X (float for fp32 models, T otherwise).
+template <typename T, typename X, int U>
+__global__ void __launch_bounds__(kLstmThreads) lstm_fwd_kernel(const LstmParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int H = p.H, B = p.B, Bp = p.Bp;
+  constexpr int R = 4 * U;
+  const int j0 = blockIdx.x * U;
+  const int nu = min(U, H - j0);
+  const int NB2 = Bp / 2;
+  const int KG = max(1, kLstmThreads / NB2);
+  float* Wt = reinterpret_cast<float*>(smem_raw);                 // [H][R]
+  float* red = Wt + (size_t)H * R;                                // [KG][Bp][R]
+  float* cst = red + (size_t)KG * Bp * R;                         // [Bp][U]
+  X* stage = reinterpret_cast<X*>(cst + (size_t)Bp * U);          // [2][kTileK][Bp]
+  X* hx = static_cast<X*>(p.hbuf);                                // [2][H][Bp] k-major exchange buffer
+  for (int idx = threadIdx.x; idx < H * R; idx += blockDim.x) {
+    const int k = idx / R, r = idx % R;
+    const int g = r / U, jj = r % U;
+    Wt[idx] = jj < nu ? ldf<T>(p.whh, (int64_t)(g * H + j0 + jj) * H + k) : 0.f;
+  }
+  for (int idx = threadIdx.x; idx < Bp * U; idx += blockDim.x) {
+    const int b = idx / U, jj = idx % U;
+    cst[idx] = (jj < nu && b < B) ? ldf<T>(p.c0, (int64_t)b * H + j0 + jj) : 0.f;
+  }
+  for (int idx = threadIdx.x; idx < Bp * nu; idx += blockDim.x) {    // h_{-1} into slot 0 (padding rows = 0)
+    const int jj = idx / Bp, b = idx % Bp;
+    hx[(int64_t)(j0 + jj) * Bp + b] = Cvt<X>::from_f(b < B ? ldf<T>(p.h0, (int64_t)b * H + j0 + jj) : 0.f);
+  }
+  unsigned int target = gridDim.x;
+  bool alive = grid_barrier(p.bar, target);
+  const int kg = threadIdx.x / NB2, b0 = (threadIdx.x % NB2) * 2;
+  const bool active = kg < KG;
+  for (int t = 0; t < p.T && alive; ++t) {
+    const X* hprev = hx + (int64_t)(t & 1) * H * Bp;
+    X* hnext = hx + (int64_t)((t + 1) & 1) * H * Bp;
+    float acc[2][R];
+    stream_matmul<X, R>(hprev, H, Bp, Wt, stage, kg, KG, b0, active, acc);
+    if (active) {
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        float* dst = red + ((size_t)kg * Bp + b0 + rr) * R;
+#pragma unroll
+        for (int o = 0; o < R; ++o) dst[o] = acc[rr][o];
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < Bp * nu; idx += blockDim.x) {
+      const int jj = idx / Bp, b = idx % Bp, j = j0 + jj;
+      if (b >= B) { hnext[(int64_t)j * Bp + b] = Cvt<X>::from_f(0.f); continue; }
+      float a[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        float s = ldf<T>(p.xproj, ((int64_t)t * B + b) * 4 * H + g * H + j);
+        for (int q = 0; q < KG; ++q) s += red[((size_t)q * Bp + b) * R + g * U + jj];
+        a[g] = s;
+      }
+      const float ig = sigmoidf_(a[0]), fg = sigmoidf_(a[1]), gg = tanhf(a[2]), og = sigmoidf_(a[3]);
+      const float c = fg * cst[b * U + jj] + ig * gg;
+      const float h = og * tanhf(c);
+      cst[b * U + jj] = c;
+      hnext[(int64_t)j * Bp + b] = Cvt<X>::from_f(h);
+      stf<T>(p.y, ((int64_t)t * B + b) * H + j, h);
+      if (p.gates) {
+        const int64_t gb = ((int64_t)t * B + b) * 4 * H + j;
+        stf<T>(p.gates, gb, ig); stf<T>(p.gates, gb + H, fg); stf<T>(p.gates, gb + 2 * H, gg); stf<T>(p.gates, gb + 3 * H, og);
+      }
+      if (p.cs) p.cs[((int64_t)t * B + b) * H + j] = c;
+      if (t == p.T - 1) { stf<T>(p.hT, (int64_t)b * H + j, h); stf<T>(p.cT, (int64_t)b * H + j, c); }
+    }
+    target += gridDim.x;
+    alive = grid_barrier(p.bar, target);
+  }
+}
+
+// Backward.  Shared memory: Wc [4H][U] (columns of W_hh of this CTA's units), red [KG][Bp][U], dh_rec [Bp][U],
+// dc_car [Bp][U], stage [2][kTileK][Bp].  p.hbuf is reused as the k-major exchange buffer of the gate gradients
+// ([4H][Bp] of X).
+template <typename T, typename X, int U>
+__global__ void __launch_bounds__(kLstmThreads) lstm_bwd_kernel(const LstmParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int H = p.H, B = p.B, Bp = p.Bp, H4 = 4 * p.H;
+  const int j0 = blockIdx.x * U;
+  const int nu = min(U, H - j0);
+  const int NB2 = Bp / 2;
+  const int KG = max(1, kLstmThreads / NB2);
+  float* Wc = reinterpret_cast<float*>(smem_raw);                 // [4H][U]
+  float* red = Wc + (size_t)H4 * U;                               // [KG][Bp][U]
+  float* dh_rec = red + (size_t)KG * Bp * U;                      // [Bp][U]
+  float* dc_car = dh_rec + (size_t)Bp * U;                        // [Bp][U]
+  X* stage = reinterpret_cast<X*>(dc_car + (size_t)Bp * U);
+  X* dgx = static_cast<X*>(p.hbuf);                               // [4H][Bp]
+  for (int idx = threadIdx.x; idx < H4 * U; idx += blockDim.x) {
+    const int r = idx / U, jj = idx % U;
+    Wc[idx] = jj < nu ? ldf<T>(p.whh, (int64_t)r * H + j0 + jj) : 0.f;
+  }
+  for (int idx = threadIdx.x; idx < Bp * U; idx += blockDim.x) {
+    const int b = idx / U, jj = idx % U;
+    const bool in = jj < nu && b < B;
+    dh_rec[idx] = (in && p.dhT) ? ldf<T>(p.dhT, (int64_t)b * H + j0 + jj) : 0.f;
+    dc_car[idx] = (in && p.dcT) ? ldf<T>(p.dcT, (int64_t)b * H + j0 + jj) : 0.f;
+  }
+  __syncthreads();
+  unsigned int target = 0;
+  bool alive = true;
+  const int kg = threadIdx.x / NB2, b0 = (threadIdx.x % NB2) * 2;
+  const bool active = kg < KG;
+  for (int t = p.T - 1; t >= 0 && alive; --t) {
+    // ---- phase A: gate gradients of this CTA's units (saved copy [T,B,4H] and k-major exchange copy)
+    for (int idx = threadIdx.x; idx < Bp * nu; idx += blockDim.x) {
+      const int jj = idx / Bp, b = idx % Bp, j = j0 + jj;
+      float dai = 0.f, daf = 0.f, dag = 0.f, dao = 0.f;
+      if (b < B) {
+        const int64_t gb = ((int64_t)t * B + b) * H4 + j;
+        const float ig = ldf<T>(p.gates, gb), fg = ldf<T>(p.gates, gb + H), gg = ldf<T>(p.gates, gb + 2 * H),
+                    og = ldf<T>(p.gates, gb + 3 * H);
+        const float c = p.cs[((int64_t)t * B + b) * H + j];
+        const float cprev = t > 0 ? p.cs[((int64_t)(t - 1) * B + b) * H + j] : ldf<T>(p.c0, (int64_t)b * H + j);
+        const float dh = ldf<T>(p.dy, ((int64_t)t * B + b) * H + j) + dh_rec[b * U + jj];
+        const float tc = tanhf(c);
+        const float dc = dc_car[b * U + jj] + dh * og * (1.f - tc * tc);
+        dai = dc * gg * ig * (1.f - ig);
+        daf = dc * cprev * fg * (1.f - fg);
+        dag = dc * ig * (1.f - gg * gg);
+        dao = dh * tc * og * (1.f - og);
+        dc_car[b * U + jj] = dc * fg;
+        stf<T>(p.dgates, gb, dai); stf<T>(p.dgates, gb + H, daf); stf<T>(p.dgates, gb + 2 * H, dag); stf<T>(p.dgates, gb + 3 * H, dao);
+      }
+      dgx[(int64_t)j * Bp + b] = Cvt<X>::from_f(dai);
+      dgx[(int64_t)(H + j) * Bp + b] = Cvt<X>::from_f(daf);
+      dgx[(int64_t)(2 * H + j) * Bp + b] = Cvt<X>::from_f(dag);
+      dgx[(int64_t)(3 * H + j) * Bp + b] = Cvt<X>::from_f(dao);
+    }
+    target += gridDim.x;
+    alive = grid_barrier(p.bar, target);
+    if (!alive) break;
+    // ---- phase B: dh_{t-1}[b, j] = sum_r dgates[t, b, r] * W_hh[r, j] for this CTA's units j
+    float acc[2][U];
+    stream_matmul<X, U>(dgx, H4, Bp, Wc, stage, kg, KG, b0, active, acc);
+    if (active) {
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        float* dst = red + ((size_t)kg * Bp + b0 + rr) * U;
+#pragma unroll
+        for (int o = 0; o < U; ++o) dst[o] = acc[rr][o];
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < Bp * U; idx += blockDim.x) {
+      const int b = idx / U, jj = idx % U;
+      float s = 0.f;
+      for (int q = 0; q < KG; ++q) s += red[((size_t)q * Bp + b) * U + jj];
+      dh_rec[idx] = s;
+    }
+    // every CTA must be done reading the exchange buffer before phase A of the next step overwrites it
+    target += gridDim.x;
+    alive = grid_barrier(p.bar, target);
+  }
+  if (alive) {
+    for (int idx = threadIdx.x; idx < B * nu; idx += blockDim.x) {
+      const int b = idx / nu, jj = idx % nu;
+      stf<T>(p.dh0, (int64_t)b * H + j0 + jj, dh_rec[b * U + jj]);
+      stf<T>(p.dc0, (int64_t)b * H + j0 + jj, dc_car[b * U + jj]);
+    }
+  }
+}
+
+static int lstm_units_per_cta(int H) {
+  int u = (H + sm_count() - 1) / sm_count();
+  return u < 1 ? 1 : u;
+}
+static int lstm_bp(int B) { return (B + 7) / 8 * 8; }
+static size_t lstm_fwd_smem(int B, int H, int U, size_t xsize) {
+  const int Bp = lstm_bp(B), NB2 = Bp / 2;
+  const int KG = kLstmThreads / NB2 > 1 ? kLstmThreads / NB2 : 1;
+  return ((size_t)H * 4 * U + (size_t)KG * Bp * 4 * U + (size_t)Bp * U) * sizeof(float) + (size_t)2 * kTileK * Bp * xsize;
+}
+static size_t lstm_bwd_smem(int B, int H, int U, size_t xsize) {
+  const int Bp = lstm_bp(B), NB2 = Bp / 2;
+  const int KG = kLstmThreads / NB2 > 1 ? kLstmThreads / NB2 : 1;
+  return ((size_t)4 * H * U + (size_t)KG * Bp * U + (size_t)2 * Bp * U) * sizeof(float) + (size_t)2 * kTileK * Bp * xsize;
+}
+constexpr size_t kLstmSmemLimit = 220 * 1024;
+
+template <typename T, typename X, int U>
+static int launch_lstm(bool backward, LstmParams& p, cudaStream_t st) {
+  const size_t smem = backward ? lstm_bwd_smem(p.B, p.H, U, sizeof(X)) : lstm_fwd_smem(p.B, p.H, U, sizeof(X));
+  const void* fn = backward ? (const void*)lstm_bwd_kernel<T, X, U> : (const void*)lstm_fwd_kernel<T, X, U>;
+  cudaError_t rc = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (rc != cudaSuccess) return (int)rc;
+  const int grid = (p.H + U - 1) / U;
+  int per_sm = 0;
+  rc = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kLstmThreads, smem);
+  if (rc != cudaSuccess) return (int)rc;
+  if ((int64_t)per_sm * sm_count() < grid) return -4;      // the grid barrier needs every CTA resident
+  p.U = U;
+  p.Bp = lstm_bp(p.B);
+  void* args[] = {&p};
+  rc = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kLstmThreads), args, smem, st);
+  return (int)rc;
+}
+
+template <typename T, typename X>
+static int dispatch_lstm(bool backward, LstmParams& p, cudaStream_t st) {
+  const int U = lstm_units_per_cta(p.H);
+  switch (U) {
+    case 1: return launch_lstm<T, X, 1>(backward, p, st);
+    case 2: return launch_lstm<T, X, 2>(backward, p, st);
+    case 3: return launch_lstm<T, X, 3>(backward, p, st);
+    case 4: return launch_lstm<T, X, 4>(backward, p, st);
+    case 5: return launch_lstm<T, X, 5>(backward, p, st);
+    case 6: return launch_lstm<T, X, 6>(backward, p, st);
+    case 7: return launch_lstm<T, X, 7>(backward, p, st);
+    case 8: return launch_lstm<T, X, 8>(backward, p, st);
+    default: return -4;
+  }
+}
+
+}  // namespace mxb
+
+using namespace mxb;
+
+// 1 when the persistent kernels can run this shape on the current device (shared-memory and residency limits).
+MXB_EXPORT int mxb_lstm_supported(int B, int H) {
+  if (B < 1 || H < 1 || lstm_bp(B) > 2 * kLstmThreads) return 0;
+  const int U = lstm_units_per_cta(H);
+  if (U > 8) return 0;
+  return lstm_fwd_smem(B, H, U, 4) <= kLstmSmemLimit && lstm_bwd_smem(B, H, U, 4) <= kLstmSmemLimit;
+}
+
+// Bytes of the exchange buffer `hbuf` both kernels need for (B, H): [4H][Bp] floats covers every case.
+MXB_EXPORT int64_t mxb_lstm_exchange_bytes(int B, int H) { return (int64_t)4 * H * lstm_bp(B) * 4; }
+
+// `bar`: two zero-initialised 32-bit words (arrival counter, error flag); after the kernel bar[1] != 0 means a barrier
+// timed out and the outputs are incomplete.  `hbuf`: mxb_lstm_exchange_bytes(B, H) bytes of scratch.
+MXB_EXPORT int mxb_lstm_forward(int dtype, const void* xproj, const void* whh, const void* h0, const void* c0, void* y,
+                                void* hT, void* cT, void* gates, float* cs, void* hbuf, unsigned int* bar, int T, int B,
+                                int H, void* stream) {
+  if (!mxb_lstm_supported(B, H) || T < 1) return -4;
+  LstmParams p{};
+  p.xproj = xproj; p.whh = whh; p.h0 = h0; p.c0 = c0; p.y = y; p.hT = hT; p.cT = cT; p.gates = gates; p.cs = cs;
+  p.hbuf = hbuf; p.bar = bar; p.T = T; p.B = B; p.H = H;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == kF32) return dispatch_lstm<float, float>(false, p, st);
+  if (dtype == kF16) return dispatch_lstm<__half, __half>(false, p, st);
+  if (dtype == kBF16) return dispatch_lstm<__nv_bfloat16, __nv_bfloat16>(false, p, st);
+  return -1;
+}
+
+MXB_EXPORT int mxb_lstm_backward(int dtype, const void* dy, const void* dhT, const void* dcT, const void* gates,
+                                 const float* cs, const void* c0, const void* whh, void* dgates, void* dh0, void* dc0,
+                                 void* hbuf, unsigned int* bar, int T, int B, int H, void* stream) {
+  if (!mxb_lstm_supported(B, H) || T < 1) return -4;
+  LstmParams p{};
+  p.dy = dy; p.dhT = dhT; p.dcT = dcT; p.gates = const_cast<void*>(gates); p.cs = const_cast<float*>(cs); p.c0 = c0;
+  p.whh = whh; p.dgates = dgates; p.dh0 = dh0; p.dc0 = dc0; p.hbuf = hbuf; p.bar = bar; p.T = T; p.B = B; p.H = H;
+  cudaStream_t st = (cudaStream_t)stream;
+  // the gate gradients cross CTAs in fp32 for every model type: their dynamic range is that of the loss scale
+  if (dtype == kF32) return dispatch_lstm<float, float>(true, p, st);
+  if (dtype == kF16) return dispatch_lstm<__half, float>(true, p, st);
+  if (dtype == kBF16) return dispatch_lstm<__nv_bfloat16, float>(true, p, st);
+  return -1;
+}

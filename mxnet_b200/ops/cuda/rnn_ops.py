@@ -1,5 +1,115 @@
-"""Fused LSTM entry (``lstm.cu``)."""
+"""Fused LSTM on the persistent recurrence kernels (``lstm.cu``).
+
+One layer = an input-projection GEMM over all time steps (tcgen05 kernel for half precision), the
+cooperative recurrence kernel, and in backward the reverse recurrence plus three GEMMs over the saved
+gate gradients (weight gradients contract over time*batch: MN-major operands)."""
+import torch
+
+from . import lib, ptr, stream_ptr, count_launch, check
+from ._util import dt, require
 
 
 def supported(data, state_size, num_layers):
-    return False
+    if not data.is_cuda or data.dim() != 3 or data.numel() == 0:
+        return False
+    return bool(lib().mxb_lstm_supported(int(data.shape[1]), int(state_size)))
+
+
+def _mm(a, b, a_mn, b_mn):
+    """op(a) @ op(b) with the tcgen05 kernel when the operands qualify, else the library."""
+    from . import gemm_ops
+    if a.dtype in (torch.float16, torch.bfloat16) and gemm_ops.operand_ok(a) and gemm_ops.operand_ok(b):
+        return gemm_ops.gemm(a, b, a_mn, b_mn)
+    aa = a.t() if a_mn else a
+    bb = b if b_mn else b.t()
+    return aa @ bb
+
+
+def _barrier_words(device):
+    return torch.zeros(2, dtype=torch.int32, device=device)
+
+
+class _LSTMLayer(torch.autograd.Function):
+    """y, hT, cT = lstm(x[T,B,I], w_ih[4H,I], w_hh[4H,H], b_ih[4H], b_hh[4H], h0[B,H], c0[B,H])."""
+
+    @staticmethod
+    def forward(ctx, x, w_ih, w_hh, b_ih, b_hh, h0, c0, training):
+        L = lib()
+        T, B, I = x.shape
+        H = w_hh.shape[1]
+        x = x.contiguous()
+        w_ih, w_hh, h0, c0 = w_ih.contiguous(), w_hh.contiguous(), h0.contiguous(), c0.contiguous()
+        for t, name, shape in ((w_ih, 'w_ih', (4 * H, I)), (w_hh, 'w_hh', (4 * H, H)), (h0, 'h0', (B, H)), (c0, 'c0', (B, H))):
+            require(t, name, dtype=x.dtype, device=x.device, shape=shape)
+        bias = (b_ih.float() + b_hh.float()).to(x.dtype)
+        require(bias, 'bias', numel=4 * H, device=x.device)
+        from . import gemm_ops
+        x2 = x.reshape(T * B, I)
+        if x.dtype in (torch.float16, torch.bfloat16) and gemm_ops.operand_ok(x2) and gemm_ops.operand_ok(w_ih):
+            xproj = gemm_ops.gemm(x2, w_ih, False, False, bias)
+        else:
+            xproj = torch.addmm(bias, x2, w_ih.t())
+        y = torch.empty(T, B, H, dtype=x.dtype, device=x.device)
+        hT, cT = torch.empty_like(h0), torch.empty_like(c0)
+        gates = torch.empty(T, B, 4 * H, dtype=x.dtype, device=x.device) if training else None
+        cs = torch.empty(T, B, H, dtype=torch.float32, device=x.device) if training else None
+        hbuf = torch.empty(L.mxb_lstm_exchange_bytes(B, H), dtype=torch.uint8, device=x.device)
+        bar = _barrier_words(x.device)
+        check(L.mxb_lstm_forward(dt(x), ptr(xproj), ptr(w_hh), ptr(h0), ptr(c0), ptr(y), ptr(hT), ptr(cT), ptr(gates), ptr(cs),
+                                 ptr(hbuf), ptr(bar), T, B, H, stream_ptr(x.device)), 'lstm_forward')
+        count_launch(1)
+        ctx.save_for_backward(x, w_ih, w_hh, h0, c0, y, gates, cs)
+        ctx.bias_dtypes = (b_ih.dtype, b_hh.dtype)
+        ctx.fwd_bar = bar
+        ctx.set_materialize_grads(False)
+        return y, hT, cT
+
+    @staticmethod
+    def backward(ctx, dy, dhT, dcT):
+        x, w_ih, w_hh, h0, c0, y, gates, cs = ctx.saved_tensors
+        if gates is None:
+            raise RuntimeError('LSTM backward needs a forward pass in training mode')
+        L = lib()
+        T, B, I = x.shape
+        H = w_hh.shape[1]
+        dy = torch.zeros_like(y) if dy is None else dy.contiguous()
+        require(dy, 'out_grad', dtype=x.dtype, device=x.device, shape=y.shape)
+        dhT = dhT.contiguous() if dhT is not None else None
+        dcT = dcT.contiguous() if dcT is not None else None
+        dgates = torch.empty_like(gates)
+        dh0, dc0 = torch.empty_like(h0), torch.empty_like(c0)
+        bar = _barrier_words(x.device)
+        hbuf = torch.empty(L.mxb_lstm_exchange_bytes(B, H), dtype=torch.uint8, device=x.device)
+        check(L.mxb_lstm_backward(dt(x), ptr(dy), ptr(dhT), ptr(dcT), ptr(gates), ptr(cs), ptr(c0), ptr(w_hh), ptr(dgates),
+                                  ptr(dh0), ptr(dc0), ptr(hbuf), ptr(bar), T, B, H, stream_ptr(x.device)), 'lstm_backward')
+        count_launch(1)
+        dg2 = dgates.reshape(T * B, 4 * H)
+        hprev = torch.cat([h0.unsqueeze(0), y[:-1]], 0).reshape(T * B, H)
+        dx = _mm(dg2, w_ih, False, True).reshape(T, B, I) if ctx.needs_input_grad[0] else None   # dg[TB,4H] . w_ih[4H,I]
+        dw_ih = _mm(dg2, x.reshape(T * B, I), True, True)                                         # dg^T . x
+        dw_hh = _mm(dg2, hprev, True, True)                                                        # dg^T . h_{t-1}
+        db = dg2.float().sum(0)
+        return dx, dw_ih, dw_hh, db.to(ctx.bias_dtypes[0]), db.to(ctx.bias_dtypes[1]), dh0, dc0, None
+
+
+def check_errors(bar):
+    """Raise when a grid barrier of the recurrence timed out (outputs incomplete)."""
+    if int(bar[1].item()) != 0:
+        raise RuntimeError('LSTM recurrence kernel: grid barrier timed out')
+
+
+def lstm(data, parameters, state, state_cell, state_size, num_layers, p, training):
+    """Multi-layer unidirectional LSTM over (T, N, C) data with the flat parameter vector of the RNN operator."""
+    from ..nn import rnn_unpack
+    T, N, I = data.shape
+    layers = rnn_unpack(parameters, 'lstm', num_layers, I, state_size, False, None)
+    x = data
+    hs, cs = [], []
+    for l in range(num_layers):
+        w_ih, w_hh, _w_hr, b_ih, b_hh = layers[l]
+        x, h, c = _LSTMLayer.apply(x, w_ih, w_hh, b_ih, b_hh, state[l], state_cell[l], bool(training))
+        hs.append(h)
+        cs.append(c)
+        if p > 0 and training and l < num_layers - 1:
+            x = torch.nn.functional.dropout(x, p, True)
+    return x, torch.stack(hs, 0), torch.stack(cs, 0)

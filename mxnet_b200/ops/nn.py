@@ -848,6 +848,19 @@ def rnn(data, parameters, state, state_cell=None, sequence_length=None, state_si
             out, hy, cy = rnn_ops.lstm(data, parameters, state, state_cell, state_size, num_layers, p, training)
             return (out, hy, cy) if state_outputs else out
     layers = rnn_unpack(parameters, mode, num_layers, I, state_size, bidirectional, projection_size)
+    if data.is_cuda and projection_size is None and seq_len is None and clip is None and not env.get('MXNET_RNN_UNROLLED'):
+        # library recurrence (cuDNN through the tensor library) for the configurations the in-tree kernel does not
+        # take: GRU / vanilla RNN / bidirectional stacks.  Same gate order and per-(layer, direction) weight order.
+        flat = []
+        for w_ih, w_hh, _w_hr, b_ih, b_hh in layers:
+            flat += [w_ih.contiguous(), w_hh.contiguous(), b_ih.contiguous(), b_hh.contiguous()]
+        args = (flat, True, num_layers, float(p), bool(training), bool(bidirectional), False)
+        if mode == 'lstm':
+            out, hn, cn = torch._VF.lstm(data, (state.contiguous(), state_cell.contiguous()), *args)
+            return (out, hn, cn) if state_outputs else out
+        fn = {'gru': torch._VF.gru, 'rnn_tanh': torch._VF.rnn_tanh, 'rnn_relu': torch._VF.rnn_relu}[mode]
+        out, hn = fn(data, state.contiguous(), *args)
+        return (out, hn) if state_outputs else out
     x = data
     hy, cy = [], []
     for l in range(num_layers):

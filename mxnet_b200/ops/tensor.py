@@ -398,9 +398,15 @@ def where(condition, x, y):
     return torch.where(c, x, y)
 
 
-@register('Cast', 'cast', '_npi_cast', 'amp_cast', inputs=('data',), defaults={'dtype': 'float32'})
+@register('Cast', 'cast', '_npi_cast', inputs=('data',), defaults={'dtype': 'float32'})
 def cast(data, dtype='float32'):
     return data.to(to_torch_dtype(dtype))
+
+
+@register('amp_cast', inputs=('data',), defaults={'dtype': 'float32'})
+def amp_cast(data, dtype='float32'):
+    """Cast inserted by the mixed-precision graph pass (src/operator/tensor/amp_cast.cc): floating inputs only."""
+    return data.to(to_torch_dtype(dtype)) if data.dtype.is_floating_point else data
 
 
 @register('amp_multicast', inputs=('*data',), nout=lambda a: a.get('num_outputs', 1),

@@ -42,7 +42,7 @@ def remove_amp_cast(sym):
     def tf(n, ins):
         if n.op is not None and n.op.name in ('Cast',) and n.name.startswith('amp_cast'):
             return [ins[0]]
-        if n.op is not None and 'amp_cast' in n.op.aliases and n.name.startswith('amp_cast'):
+        if n.op is not None and n.op.name == 'amp_cast':
             return [ins[0]]
         if n.op is not None and n.op.name == 'amp_multicast':
             return list(ins)

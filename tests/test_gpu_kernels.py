@@ -393,6 +393,85 @@ def test_device_wait_times_out_with_status_not_a_hang():
     assert float(torch.ones(4, device='cuda').sum()) == 4.0
 
 
+# ---------------------------------------------------------------------------------------- LSTM
+@pytest.mark.parametrize('T,B,I,H,layers', [(5, 3, 8, 16, 1), (7, 4, 24, 40, 2), (35, 80, 650, 650, 2), (3, 1, 16, 200, 1),
+                                             (4, 33, 64, 1184, 1)])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float16])
+def test_fused_lstm_matches_library_lstm(T, B, I, H, layers, dtype):
+    from mxnet_b200.ops.cuda import rnn_ops
+    from mxnet_b200.ops.nn import rnn_param_size
+    torch.manual_seed(9)
+    ref = torch.nn.LSTM(I, H, layers).float()            # exact fp32 reference on the host
+    # flat parameter vector in the RNN operator's order: all weights (layer by layer: w_ih, w_hh), then all biases
+    ws, bs = [], []
+    for l in range(layers):
+        ws += [getattr(ref, 'weight_ih_l%d' % l).detach().reshape(-1), getattr(ref, 'weight_hh_l%d' % l).detach().reshape(-1)]
+        bs += [getattr(ref, 'bias_ih_l%d' % l).detach(), getattr(ref, 'bias_hh_l%d' % l).detach()]
+    flat = torch.cat(ws + bs).to(_dev()).to(dtype).requires_grad_(True)
+    assert flat.numel() == rnn_param_size('lstm', layers, I, H)
+    x = torch.randn(T, B, I, device=_dev()).to(dtype).requires_grad_(True)
+    h0 = (torch.randn(layers, B, H, device=_dev()) * 0.5).to(dtype).requires_grad_(True)
+    c0 = (torch.randn(layers, B, H, device=_dev()) * 0.5).to(dtype).requires_grad_(True)
+    assert rnn_ops.supported(x, H, layers)
+    y, hT, cT = rnn_ops.lstm(x, flat, h0, c0, H, layers, 0.0, True)
+    gy, gh, gc = torch.randn_like(y), torch.randn_like(hT), torch.randn_like(cT)
+    torch.autograd.backward([y, hT, cT], [gy, gh, gc])
+    # reference in fp32 on the same (rounded) values
+    with torch.no_grad():
+        off = 0
+        for l in range(layers):
+            for name, shape in (('weight_ih_l%d' % l, (4 * H, I if l == 0 else H)), ('weight_hh_l%d' % l, (4 * H, H))):
+                n = shape[0] * shape[1]
+                getattr(ref, name).copy_(flat[off:off + n].float().reshape(shape).cpu())
+                off += n
+        for l in range(layers):
+            for name in ('bias_ih_l%d' % l, 'bias_hh_l%d' % l):
+                getattr(ref, name).copy_(flat[off:off + 4 * H].float().cpu())
+                off += 4 * H
+    xr = x.detach().float().cpu().requires_grad_(True)
+    hr, cr = h0.detach().float().cpu().requires_grad_(True), c0.detach().float().cpu().requires_grad_(True)
+    yr, (hTr, cTr) = ref(xr, (hr, cr))
+    torch.autograd.backward([yr, hTr, cTr], [gy.float().cpu(), gh.float().cpu(), gc.float().cpu()])
+    tol = (1e-3, 1e-3) if dtype == torch.float32 else (3e-2, 3e-2)     # fast exp/tanh intrinsics in the kernel
+    _close(y, yr, *tol)
+    _close(hT, hTr, *tol)
+    _close(cT, cTr, *tol)
+    _close(x.grad, xr.grad, tol[0] * 3, tol[1] * 3)
+    _close(h0.grad, hr.grad, tol[0] * 3, tol[1] * 3)
+    _close(c0.grad, cr.grad, tol[0] * 3, tol[1] * 3)
+    gref = torch.cat([getattr(ref, 'weight_%s_l%d' % (k, l)).grad.reshape(-1) for l in range(layers) for k in ('ih', 'hh')] +
+                     [getattr(ref, 'bias_%s_l%d' % (k, l)).grad for l in range(layers) for k in ('ih', 'hh')])
+    scale = float(gref.abs().max())
+    _close(flat.grad.cpu() / scale, gref / scale, tol[0] * 5, tol[1] * 2)
+
+
+@pytest.mark.parametrize('mode,bidir', [('gru', False), ('lstm', True), ('rnn_tanh', True), ('rnn_relu', False)])
+def test_rnn_operator_gpu_matches_cpu_unrolled(mode, bidir):
+    """The RNN operator on the GPU (library recurrence) against the per-step CPU implementation of the same operator."""
+    from mxnet_b200.ops.nn import rnn_param_size
+    T, B, I, H, layers = 6, 3, 5, 7, 2
+    d = 2 if bidir else 1
+    rng = np.random.RandomState(3)
+    params = (rng.randn(rnn_param_size(mode, layers, I, H, bidir)) * 0.3).astype('float32')
+    x = rng.randn(T, B, I).astype('float32')
+    h0 = rng.randn(layers * d, B, H).astype('float32')
+    c0 = rng.randn(layers * d, B, H).astype('float32')
+    outs = []
+    for ctx in (mx.cpu(), mx.gpu(0)):
+        args = [nd.array(x, ctx=ctx), nd.array(params, ctx=ctx), nd.array(h0, ctx=ctx)]
+        if mode == 'lstm':
+            args.append(nd.array(c0, ctx=ctx))
+        args[0].attach_grad()
+        args[1].attach_grad()
+        with autograd.record():
+            res = nd.RNN(*args, state_size=H, num_layers=layers, mode=mode, bidirectional=bidir, state_outputs=True)
+            loss = sum((r * r).sum() for r in res)
+        loss.backward()
+        outs.append([r.asnumpy() for r in res] + [args[0].grad.asnumpy(), args[1].grad.asnumpy()])
+    for a, b in zip(*outs):
+        np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-4)
+
+
 # ---------------------------------------------------------------------------------------- pooling
 @pytest.mark.parametrize('shape,k,s,p,ceil', [((2, 13, 17, 16), 3, 2, 1, False), ((3, 8, 8, 64), 2, 2, 0, False),
                                               ((1, 9, 11, 8), 3, 1, 1, False), ((2, 10, 10, 24), 3, 2, 0, True),
