@@ -24,12 +24,29 @@ class GradientCompression(object):
         per_word = 16 if self.type == '2bit' else 32
         return (n + per_word - 1) // per_word
 
+    @staticmethod
+    def _kernels(t):
+        from .. import env
+        if not t.is_cuda or not env.get('MXNET_B200_KERNELS'):
+            return None
+        from ..ops import cuda
+        return cuda if cuda.available() else None
+
     def quantize(self, key, grad):
-        """Returns packed int32 codes; updates the residual kept for ``key``."""
+        """Returns packed codes (one 32-bit word per 16 or 32 values); updates the residual kept for ``key``."""
         g = grad.reshape(-1).float()
         res = self._residual.get(key)
         if res is None or res.shape != g.shape or res.device != g.device:
             res = self._residual[key] = torch.zeros_like(g)
+        cuda = self._kernels(g)
+        if cuda is not None:
+            g = g.contiguous()
+            bits = 2 if self.type == '2bit' else 1
+            packed = torch.empty(self.compressed_size(g.numel()), dtype=torch.int32, device=g.device)
+            cuda.check(cuda.lib().mxb_gc_quantize(bits, cuda.ptr(g), cuda.ptr(res), cuda.ptr(packed), g.numel(), self.threshold,
+                                                  cuda.stream_ptr(g.device)), 'gc_quantize')
+            cuda.count_launch(1)
+            return packed
         res.add_(g)
         t = self.threshold
         if self.type == '2bit':
@@ -52,6 +69,14 @@ class GradientCompression(object):
         return (packed & 0xFFFFFFFF).to(torch.int64)
 
     def dequantize(self, packed, n, dtype=torch.float32):
+        cuda = self._kernels(packed)
+        if cuda is not None and packed.dtype == torch.int32:
+            out = torch.empty(n, dtype=torch.float32, device=packed.device)
+            cuda.check(cuda.lib().mxb_gc_dequantize(2 if self.type == '2bit' else 1, cuda.ptr(packed), cuda.ptr(out), n,
+                                                    self.threshold, 0, cuda.stream_ptr(packed.device)), 'gc_dequantize')
+            cuda.count_launch(1)
+            return out.to(dtype)
+        packed = packed.to(torch.int64) & 0xFFFFFFFF
         per, bits = (16, 2) if self.type == '2bit' else (32, 1)
         shifts = torch.arange(per, device=packed.device, dtype=torch.int64) * bits
         codes = ((packed.reshape(-1, 1) >> shifts) & ((1 << bits) - 1)).reshape(-1)[:n]

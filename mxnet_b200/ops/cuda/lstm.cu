@@ -37,17 +37,19 @@ struct LstmParams {
   void* y;               // [T, B, H]
   void* hT;              // [B, H]
   void* cT;              // [B, H]
-  void* gates;           // [T, B, 4H] activated gates (saved for backward; may be null for inference)
-  float* cs;             // [T, B, H] cell states in fp32 (saved for backward; may be null)
-  void* hbuf;            // exchange buffer, k-major: forward [2][H][Bp] of h, backward [4H][Bp] of gate gradients
+  void* gates;           // [T, 4H, Bp] activated gates, k-major like the exchange buffer (saved for backward; may be null)
+  float* cs;             // [T, H, Bp] cell states in fp32, k-major (saved for backward; may be null)
+  void* hbuf;            // forward exchange buffer, k-major: [2][H][Bp] of h
   int Bp;                // batch rounded up to a multiple of 8 (row length of the exchange buffer)
+  int tileK;             // rows of the exchange buffer staged in shared memory per copy (two buffers)
   unsigned int* bar;     // [2] arrival counter, error flag
   int T, B, H, U;        // U: hidden units per CTA
   // backward only
   const void* dy;        // [T, B, H]
   const void* dhT;       // [B, H] or null
   const void* dcT;       // [B, H] or null
-  void* dgates;          // [T, B, 4H] gradient w.r.t. the pre-activation gates
+  void* dgates;          // [T, 4H, Bp] gradient w.r.t. the pre-activation gates, k-major: step t is also the
+                         // operand that phase B of that step streams (no separate exchange copy)
   void* dh0;             // [B, H]
   void* dc0;             // [B, H]
 };
@@ -91,10 +93,11 @@ __device__ __forceinline__ void stf(void* p, int64_t i, float v) { static_cast<T
 
 // ---- streaming a [K][Bp] matrix from global memory through shared memory against resident weights ------------------
 // The exchanged operand (h_{t-1}, or the gate gradients of step t) is kept K-major in global memory: row k holds the
-// values of all batch rows.  A CTA copies it in tiles of kTileK rows with 16-byte cp.async (double buffered) and every
+// values of all batch rows.  A CTA copies it in tiles of `tileK` rows (as many as the shared memory left over by the
+// weights allows, so that few round trips to L2 are exposed) with 16-byte cp.async, double buffered, and every
 // thread owns one pair of batch rows and a residue class of the tile's k rows, so a warp reads consecutive words of
 // the staged tile (no bank conflicts) and the weight row of that k as a broadcast.
-constexpr int kTileK = 48;
+constexpr int kMinTileK = 48;
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -104,8 +107,8 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <typename X>
-__device__ __forceinline__ void issue_tile(const X* __restrict__ src, X* __restrict__ stage, int k0, int K, int Bp) {
-  const int rows = min(kTileK, K - k0);
+__device__ __forceinline__ void issue_tile(const X* __restrict__ src, X* __restrict__ stage, int k0, int K, int Bp, int tileK) {
+  const int rows = min(tileK, K - k0);
   const int chunks_per_row = Bp * (int)sizeof(X) / 16;
   const int total = rows * chunks_per_row;
   const char* g = reinterpret_cast<const char*>(src + (int64_t)k0 * Bp);
@@ -116,17 +119,17 @@ __device__ __forceinline__ void issue_tile(const X* __restrict__ src, X* __restr
 // acc[2][OUT] += sum_k src[k][b0 + {0,1}] * W[k][0..OUT) over all K rows; W: shared memory, row stride OUT floats.
 template <typename X, int OUT>
 __device__ __forceinline__ void stream_matmul(const X* __restrict__ src, int K, int Bp, const float* __restrict__ W,
-                                              X* __restrict__ stage /* 2 tiles of kTileK*Bp */, int kg, int KG, int b0,
-                                              bool active, float (&acc)[2][OUT]) {
+                                              X* __restrict__ stage /* 2 tiles of tileK*Bp */, int tileK, int kg, int KG,
+                                              int b0, bool active, float (&acc)[2][OUT]) {
 #pragma unroll
   for (int o = 0; o < OUT; ++o) { acc[0][o] = 0.f; acc[1][o] = 0.f; }
-  const int ntiles = (K + kTileK - 1) / kTileK;
-  issue_tile(src, stage, 0, K, Bp);
+  const int ntiles = (K + tileK - 1) / tileK;
+  issue_tile(src, stage, 0, K, Bp, tileK);
   cp_async_commit();
   for (int tile = 0; tile < ntiles; ++tile) {
-    X* cur = stage + (size_t)(tile & 1) * kTileK * Bp;
+    X* cur = stage + (size_t)(tile & 1) * tileK * Bp;
     if (tile + 1 < ntiles) {
-      issue_tile(src, stage + (size_t)((tile + 1) & 1) * kTileK * Bp, (tile + 1) * kTileK, K, Bp);
+      issue_tile(src, stage + (size_t)((tile + 1) & 1) * tileK * Bp, (tile + 1) * tileK, K, Bp, tileK);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -134,7 +137,7 @@ __device__ __forceinline__ void stream_matmul(const X* __restrict__ src, int K, 
     }
     __syncthreads();
     if (active) {
-      const int k0 = tile * kTileK, rows = min(kTileK, K - k0);
+      const int k0 = tile * tileK, rows = min(tileK, K - k0);
       for (int k = kg; k < rows; k += KG) {
         const float x0 = Cvt<X>::to_f(cur[(size_t)k * Bp + b0]), x1 = Cvt<X>::to_f(cur[(size_t)k * Bp + b0 + 1]);
         const float* w = W + (size_t)(k0 + k) * OUT;
@@ -161,7 +164,7 @@ __device__ __forceinline__ void stream_matmul(const X* __restrict__ src, int K, 
 }
 
 // Forward.  Shared memory: Wt [H][4U] (W_hh rows of this CTA's units, k-major), red [KG][Bp][4U], cst [Bp][U],
-// stage [2][kTileK][Bp] of the exchange type X (float for fp32 models, T otherwise).
+// stage [2][tileK][Bp] of the exchange type X (float for fp32 models, T otherwise).
 template <typename T, typename X, int U>
 __global__ void __launch_bounds__(kLstmThreads) lstm_fwd_kernel(const LstmParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -174,7 +177,7 @@ __global__ void __launch_bounds__(kLstmThreads) lstm_fwd_kernel(const LstmParams
   float* Wt = reinterpret_cast<float*>(smem_raw);                 // [H][R]
   float* red = Wt + (size_t)H * R;                                // [KG][Bp][R]
   float* cst = red + (size_t)KG * Bp * R;                         // [Bp][U]
-  X* stage = reinterpret_cast<X*>(cst + (size_t)Bp * U);          // [2][kTileK][Bp]
+  X* stage = reinterpret_cast<X*>(cst + (size_t)Bp * U);          // [2][tileK][Bp]
   X* hx = static_cast<X*>(p.hbuf);                                // [2][H][Bp] k-major exchange buffer
   for (int idx = threadIdx.x; idx < H * R; idx += blockDim.x) {
     const int k = idx / R, r = idx % R;
@@ -196,8 +199,19 @@ __global__ void __launch_bounds__(kLstmThreads) lstm_fwd_kernel(const LstmParams
   for (int t = 0; t < p.T && alive; ++t) {
     const X* hprev = hx + (int64_t)(t & 1) * H * Bp;
     X* hnext = hx + (int64_t)((t + 1) & 1) * H * Bp;
+    // this step's input projections for the (at most two) cells this thread will update: issued before the product
+    // so that their latency is hidden behind it
+    float xp[2][4];
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int idx = threadIdx.x + it * kLstmThreads;
+      const int jj = idx / Bp, b = idx % Bp;
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+        xp[it][g] = (idx < Bp * nu && b < B) ? ldf<T>(p.xproj, ((int64_t)t * B + b) * 4 * H + g * H + j0 + jj) : 0.f;
+    }
     float acc[2][R];
-    stream_matmul<X, R>(hprev, H, Bp, Wt, stage, kg, KG, b0, active, acc);
+    stream_matmul<X, R>(hprev, H, Bp, Wt, stage, p.tileK, kg, KG, b0, active, acc);
     if (active) {
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
@@ -207,13 +221,13 @@ __global__ void __launch_bounds__(kLstmThreads) lstm_fwd_kernel(const LstmParams
       }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < Bp * nu; idx += blockDim.x) {
+    auto update_cell = [&](int idx, const float (&xg)[4]) {
       const int jj = idx / Bp, b = idx % Bp, j = j0 + jj;
-      if (b >= B) { hnext[(int64_t)j * Bp + b] = Cvt<X>::from_f(0.f); continue; }
+      if (b >= B) { hnext[(int64_t)j * Bp + b] = Cvt<X>::from_f(0.f); return; }
       float a[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
-        float s = ldf<T>(p.xproj, ((int64_t)t * B + b) * 4 * H + g * H + j);
+        float s = xg[g];
         for (int q = 0; q < KG; ++q) s += red[((size_t)q * Bp + b) * R + g * U + jj];
         a[g] = s;
       }
@@ -223,12 +237,21 @@ __global__ void __launch_bounds__(kLstmThreads) lstm_fwd_kernel(const LstmParams
       cst[b * U + jj] = c;
       hnext[(int64_t)j * Bp + b] = Cvt<X>::from_f(h);
       stf<T>(p.y, ((int64_t)t * B + b) * H + j, h);
-      if (p.gates) {
-        const int64_t gb = ((int64_t)t * B + b) * 4 * H + j;
-        stf<T>(p.gates, gb, ig); stf<T>(p.gates, gb + H, fg); stf<T>(p.gates, gb + 2 * H, gg); stf<T>(p.gates, gb + 3 * H, og);
+      if (p.gates) {        // consecutive threads = consecutive batch rows: contiguous stores
+        const int64_t gb = ((int64_t)t * 4 * H + j) * Bp + b, gs = (int64_t)H * Bp;
+        stf<T>(p.gates, gb, ig); stf<T>(p.gates, gb + gs, fg); stf<T>(p.gates, gb + 2 * gs, gg); stf<T>(p.gates, gb + 3 * gs, og);
       }
-      if (p.cs) p.cs[((int64_t)t * B + b) * H + j] = c;
+      if (p.cs) p.cs[((int64_t)t * H + j) * Bp + b] = c;
       if (t == p.T - 1) { stf<T>(p.hT, (int64_t)b * H + j, h); stf<T>(p.cT, (int64_t)b * H + j, c); }
+    };
+    if ((int)threadIdx.x < Bp * nu) update_cell(threadIdx.x, xp[0]);
+    if ((int)threadIdx.x + kLstmThreads < Bp * nu) update_cell(threadIdx.x + kLstmThreads, xp[1]);
+    for (int idx = threadIdx.x + 2 * kLstmThreads; idx < Bp * nu; idx += blockDim.x) {
+      const int jj = idx / Bp, b = idx % Bp;
+      float xg[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) xg[g] = b < B ? ldf<T>(p.xproj, ((int64_t)t * B + b) * 4 * H + g * H + j0 + jj) : 0.f;
+      update_cell(idx, xg);
     }
     target += gridDim.x;
     alive = grid_barrier(p.bar, target);
@@ -236,8 +259,7 @@ __global__ void __launch_bounds__(kLstmThreads) lstm_fwd_kernel(const LstmParams
 }
 
 // Backward.  Shared memory: Wc [4H][U] (columns of W_hh of this CTA's units), red [KG][Bp][U], dh_rec [Bp][U],
-// dc_car [Bp][U], stage [2][kTileK][Bp].  p.hbuf is reused as the k-major exchange buffer of the gate gradients
-// ([4H][Bp] of X).
+// dc_car [Bp][U], stage [2][tileK][Bp].
 template <typename T, typename X, int U>
 __global__ void __launch_bounds__(kLstmThreads) lstm_bwd_kernel(const LstmParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -251,7 +273,6 @@ __global__ void __launch_bounds__(kLstmThreads) lstm_bwd_kernel(const LstmParams
   float* dh_rec = red + (size_t)KG * Bp * U;                      // [Bp][U]
   float* dc_car = dh_rec + (size_t)Bp * U;                        // [Bp][U]
   X* stage = reinterpret_cast<X*>(dc_car + (size_t)Bp * U);
-  X* dgx = static_cast<X*>(p.hbuf);                               // [4H][Bp]
   for (int idx = threadIdx.x; idx < H4 * U; idx += blockDim.x) {
     const int r = idx / U, jj = idx % U;
     Wc[idx] = jj < nu ? ldf<T>(p.whh, (int64_t)r * H + j0 + jj) : 0.f;
@@ -273,11 +294,11 @@ __global__ void __launch_bounds__(kLstmThreads) lstm_bwd_kernel(const LstmParams
       const int jj = idx / Bp, b = idx % Bp, j = j0 + jj;
       float dai = 0.f, daf = 0.f, dag = 0.f, dao = 0.f;
       if (b < B) {
-        const int64_t gb = ((int64_t)t * B + b) * H4 + j;
-        const float ig = ldf<T>(p.gates, gb), fg = ldf<T>(p.gates, gb + H), gg = ldf<T>(p.gates, gb + 2 * H),
-                    og = ldf<T>(p.gates, gb + 3 * H);
-        const float c = p.cs[((int64_t)t * B + b) * H + j];
-        const float cprev = t > 0 ? p.cs[((int64_t)(t - 1) * B + b) * H + j] : ldf<T>(p.c0, (int64_t)b * H + j);
+        const int64_t gb = ((int64_t)t * H4 + j) * Bp + b, gs = (int64_t)H * Bp;
+        const float ig = ldf<T>(p.gates, gb), fg = ldf<T>(p.gates, gb + gs), gg = ldf<T>(p.gates, gb + 2 * gs),
+                    og = ldf<T>(p.gates, gb + 3 * gs);
+        const float c = p.cs[((int64_t)t * H + j) * Bp + b];
+        const float cprev = t > 0 ? p.cs[((int64_t)(t - 1) * H + j) * Bp + b] : ldf<T>(p.c0, (int64_t)b * H + j);
         const float dh = ldf<T>(p.dy, ((int64_t)t * B + b) * H + j) + dh_rec[b * U + jj];
         const float tc = tanhf(c);
         const float dc = dc_car[b * U + jj] + dh * og * (1.f - tc * tc);
@@ -286,19 +307,20 @@ __global__ void __launch_bounds__(kLstmThreads) lstm_bwd_kernel(const LstmParams
         dag = dc * ig * (1.f - gg * gg);
         dao = dh * tc * og * (1.f - og);
         dc_car[b * U + jj] = dc * fg;
-        stf<T>(p.dgates, gb, dai); stf<T>(p.dgates, gb + H, daf); stf<T>(p.dgates, gb + 2 * H, dag); stf<T>(p.dgates, gb + 3 * H, dao);
       }
-      dgx[(int64_t)j * Bp + b] = Cvt<X>::from_f(dai);
-      dgx[(int64_t)(H + j) * Bp + b] = Cvt<X>::from_f(daf);
-      dgx[(int64_t)(2 * H + j) * Bp + b] = Cvt<X>::from_f(dag);
-      dgx[(int64_t)(3 * H + j) * Bp + b] = Cvt<X>::from_f(dao);
+      X* dgt = static_cast<X*>(p.dgates) + (int64_t)t * H4 * Bp;       // padding rows get zeros
+      dgt[(int64_t)j * Bp + b] = Cvt<X>::from_f(dai);
+      dgt[(int64_t)(H + j) * Bp + b] = Cvt<X>::from_f(daf);
+      dgt[(int64_t)(2 * H + j) * Bp + b] = Cvt<X>::from_f(dag);
+      dgt[(int64_t)(3 * H + j) * Bp + b] = Cvt<X>::from_f(dao);
     }
     target += gridDim.x;
     alive = grid_barrier(p.bar, target);
     if (!alive) break;
     // ---- phase B: dh_{t-1}[b, j] = sum_r dgates[t, b, r] * W_hh[r, j] for this CTA's units j
     float acc[2][U];
-    stream_matmul<X, U>(dgx, H4, Bp, Wc, stage, kg, KG, b0, active, acc);
+    stream_matmul<X, U>(static_cast<const X*>(p.dgates) + (int64_t)t * H4 * Bp, H4, Bp, Wc, stage, p.tileK, kg, KG, b0, active,
+                        acc);
     if (active) {
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
@@ -314,9 +336,7 @@ __global__ void __launch_bounds__(kLstmThreads) lstm_bwd_kernel(const LstmParams
       for (int q = 0; q < KG; ++q) s += red[((size_t)q * Bp + b) * U + jj];
       dh_rec[idx] = s;
     }
-    // every CTA must be done reading the exchange buffer before phase A of the next step overwrites it
-    target += gridDim.x;
-    alive = grid_barrier(p.bar, target);
+    __syncthreads();
   }
   if (alive) {
     for (int idx = threadIdx.x; idx < B * nu; idx += blockDim.x) {
@@ -332,21 +352,34 @@ static int lstm_units_per_cta(int H) {
   return u < 1 ? 1 : u;
 }
 static int lstm_bp(int B) { return (B + 7) / 8 * 8; }
-static size_t lstm_fwd_smem(int B, int H, int U, size_t xsize) {
+// shared memory without the staging buffers
+static size_t lstm_fwd_fixed(int B, int H, int U) {
   const int Bp = lstm_bp(B), NB2 = Bp / 2;
   const int KG = kLstmThreads / NB2 > 1 ? kLstmThreads / NB2 : 1;
-  return ((size_t)H * 4 * U + (size_t)KG * Bp * 4 * U + (size_t)Bp * U) * sizeof(float) + (size_t)2 * kTileK * Bp * xsize;
+  return ((size_t)H * 4 * U + (size_t)KG * Bp * 4 * U + (size_t)Bp * U) * sizeof(float);
 }
-static size_t lstm_bwd_smem(int B, int H, int U, size_t xsize) {
+static size_t lstm_bwd_fixed(int B, int H, int U) {
   const int Bp = lstm_bp(B), NB2 = Bp / 2;
   const int KG = kLstmThreads / NB2 > 1 ? kLstmThreads / NB2 : 1;
-  return ((size_t)4 * H * U + (size_t)KG * Bp * U + (size_t)2 * Bp * U) * sizeof(float) + (size_t)2 * kTileK * Bp * xsize;
+  return ((size_t)4 * H * U + (size_t)KG * Bp * U + (size_t)2 * Bp * U) * sizeof(float);
 }
 constexpr size_t kLstmSmemLimit = 220 * 1024;
+// rows per staged tile: whatever fits beside the fixed part, at most the whole operand
+static int lstm_tile_rows(size_t fixed, int K, int Bp, size_t xsize) {
+  if (fixed >= kLstmSmemLimit) return 0;
+  const size_t rows = (kLstmSmemLimit - fixed) / (2 * (size_t)Bp * xsize);
+  return (int)(rows < (size_t)K ? rows : (size_t)K);
+}
 
 template <typename T, typename X, int U>
 static int launch_lstm(bool backward, LstmParams& p, cudaStream_t st) {
-  const size_t smem = backward ? lstm_bwd_smem(p.B, p.H, U, sizeof(X)) : lstm_fwd_smem(p.B, p.H, U, sizeof(X));
+  const int Bp = lstm_bp(p.B);
+  const size_t fixed = backward ? lstm_bwd_fixed(p.B, p.H, U) : lstm_fwd_fixed(p.B, p.H, U);
+  const int K = backward ? 4 * p.H : p.H;
+  const int tileK = lstm_tile_rows(fixed, K, Bp, sizeof(X));
+  if (tileK < kMinTileK && tileK < K) return -4;
+  const size_t smem = fixed + (size_t)2 * tileK * Bp * sizeof(X);
+  p.tileK = tileK;
   const void* fn = backward ? (const void*)lstm_bwd_kernel<T, X, U> : (const void*)lstm_fwd_kernel<T, X, U>;
   cudaError_t rc = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (rc != cudaSuccess) return (int)rc;
@@ -387,11 +420,15 @@ MXB_EXPORT int mxb_lstm_supported(int B, int H) {
   if (B < 1 || H < 1 || lstm_bp(B) > 2 * kLstmThreads) return 0;
   const int U = lstm_units_per_cta(H);
   if (U > 8) return 0;
-  return lstm_fwd_smem(B, H, U, 4) <= kLstmSmemLimit && lstm_bwd_smem(B, H, U, 4) <= kLstmSmemLimit;
+  const int Bp = lstm_bp(B);
+  const int tf = lstm_tile_rows(lstm_fwd_fixed(B, H, U), H, Bp, 4), tb = lstm_tile_rows(lstm_bwd_fixed(B, H, U), 4 * H, Bp, 4);
+  return (tf >= kMinTileK || tf >= H) && (tb >= kMinTileK || tb >= 4 * H);
 }
 
-// Bytes of the exchange buffer `hbuf` both kernels need for (B, H): [4H][Bp] floats covers every case.
-MXB_EXPORT int64_t mxb_lstm_exchange_bytes(int B, int H) { return (int64_t)4 * H * lstm_bp(B) * 4; }
+// Bytes of the forward exchange buffer `hbuf` for (B, H): [2][H][Bp] floats covers every element type.
+MXB_EXPORT int64_t mxb_lstm_exchange_bytes(int B, int H) { return (int64_t)2 * H * lstm_bp(B) * 4; }
+// Row length of the k-major arrays (`gates` [T,4H,Bp], `cs` [T,H,Bp], `dgates` [T,4H,Bp]).
+MXB_EXPORT int mxb_lstm_bp(int B) { return lstm_bp(B); }
 
 // `bar`: two zero-initialised 32-bit words (arrival counter, error flag); after the kernel bar[1] != 0 means a barrier
 // timed out and the outputs are incomplete.  `hbuf`: mxb_lstm_exchange_bytes(B, H) bytes of scratch.
@@ -411,15 +448,15 @@ MXB_EXPORT int mxb_lstm_forward(int dtype, const void* xproj, const void* whh, c
 
 MXB_EXPORT int mxb_lstm_backward(int dtype, const void* dy, const void* dhT, const void* dcT, const void* gates,
                                  const float* cs, const void* c0, const void* whh, void* dgates, void* dh0, void* dc0,
-                                 void* hbuf, unsigned int* bar, int T, int B, int H, void* stream) {
+                                 unsigned int* bar, int T, int B, int H, void* stream) {
   if (!mxb_lstm_supported(B, H) || T < 1) return -4;
   LstmParams p{};
   p.dy = dy; p.dhT = dhT; p.dcT = dcT; p.gates = const_cast<void*>(gates); p.cs = const_cast<float*>(cs); p.c0 = c0;
-  p.whh = whh; p.dgates = dgates; p.dh0 = dh0; p.dc0 = dc0; p.hbuf = hbuf; p.bar = bar; p.T = T; p.B = B; p.H = H;
+  p.whh = whh; p.dgates = dgates; p.dh0 = dh0; p.dc0 = dc0; p.bar = bar; p.T = T; p.B = B; p.H = H;
   cudaStream_t st = (cudaStream_t)stream;
-  // the gate gradients cross CTAs in fp32 for every model type: their dynamic range is that of the loss scale
+  // the gate gradients cross CTAs in the model type: the copy saved for the weight-gradient GEMMs has that type too
   if (dtype == kF32) return dispatch_lstm<float, float>(true, p, st);
-  if (dtype == kF16) return dispatch_lstm<__half, float>(true, p, st);
-  if (dtype == kBF16) return dispatch_lstm<__nv_bfloat16, float>(true, p, st);
+  if (dtype == kF16) return dispatch_lstm<__half, __half>(true, p, st);
+  if (dtype == kBF16) return dispatch_lstm<__nv_bfloat16, __nv_bfloat16>(true, p, st);
   return -1;
 }

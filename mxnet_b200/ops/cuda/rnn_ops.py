@@ -51,8 +51,9 @@ class _LSTMLayer(torch.autograd.Function):
             xproj = torch.addmm(bias, x2, w_ih.t())
         y = torch.empty(T, B, H, dtype=x.dtype, device=x.device)
         hT, cT = torch.empty_like(h0), torch.empty_like(c0)
-        gates = torch.empty(T, B, 4 * H, dtype=x.dtype, device=x.device) if training else None
-        cs = torch.empty(T, B, H, dtype=torch.float32, device=x.device) if training else None
+        Bp = L.mxb_lstm_bp(B)        # the kernels keep their own tensors k-major: [T, rows, Bp]
+        gates = torch.empty(T, 4 * H, Bp, dtype=x.dtype, device=x.device) if training else None
+        cs = torch.empty(T, H, Bp, dtype=torch.float32, device=x.device) if training else None
         hbuf = torch.empty(L.mxb_lstm_exchange_bytes(B, H), dtype=torch.uint8, device=x.device)
         bar = _barrier_words(x.device)
         check(L.mxb_lstm_forward(dt(x), ptr(xproj), ptr(w_hh), ptr(h0), ptr(c0), ptr(y), ptr(hT), ptr(cT), ptr(gates), ptr(cs),
@@ -76,14 +77,13 @@ class _LSTMLayer(torch.autograd.Function):
         require(dy, 'out_grad', dtype=x.dtype, device=x.device, shape=y.shape)
         dhT = dhT.contiguous() if dhT is not None else None
         dcT = dcT.contiguous() if dcT is not None else None
-        dgates = torch.empty_like(gates)
+        dgates_t = torch.empty_like(gates)                      # [T, 4H, Bp], k-major
         dh0, dc0 = torch.empty_like(h0), torch.empty_like(c0)
         bar = _barrier_words(x.device)
-        hbuf = torch.empty(L.mxb_lstm_exchange_bytes(B, H), dtype=torch.uint8, device=x.device)
-        check(L.mxb_lstm_backward(dt(x), ptr(dy), ptr(dhT), ptr(dcT), ptr(gates), ptr(cs), ptr(c0), ptr(w_hh), ptr(dgates),
-                                  ptr(dh0), ptr(dc0), ptr(hbuf), ptr(bar), T, B, H, stream_ptr(x.device)), 'lstm_backward')
+        check(L.mxb_lstm_backward(dt(x), ptr(dy), ptr(dhT), ptr(dcT), ptr(gates), ptr(cs), ptr(c0), ptr(w_hh), ptr(dgates_t),
+                                  ptr(dh0), ptr(dc0), ptr(bar), T, B, H, stream_ptr(x.device)), 'lstm_backward')
         count_launch(1)
-        dg2 = dgates.reshape(T * B, 4 * H)
+        dg2 = dgates_t[:, :, :B].permute(0, 2, 1).reshape(T * B, 4 * H)      # row-major copy for the GEMMs
         hprev = torch.cat([h0.unsqueeze(0), y[:-1]], 0).reshape(T * B, H)
         dx = _mm(dg2, w_ih, False, True).reshape(T, B, I) if ctx.needs_input_grad[0] else None   # dg[TB,4H] . w_ih[4H,I]
         dw_ih = _mm(dg2, x.reshape(T * B, I), True, True)                                         # dg^T . x
