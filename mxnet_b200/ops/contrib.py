@@ -97,13 +97,13 @@ def fused_self_attention(qkv, mask=None, heads=1, dropout=0.0, layout='NTC'):
         N, T, _ = qkv.shape
         x = qkv.reshape(N, T, 3, heads, -1)
         q, k, v = (x[:, :, i].permute(0, 2, 1, 3) for i in range(3))   # (N, H, T, D)
-    if qkv.is_cuda and env.get('MXNET_B200_KERNELS') and layout == 'NTC' and p == 0.0 and \
+    if qkv.is_cuda and env.get('MXNET_B200_KERNELS') and env.get('MXNET_B200_ATTENTION') and layout == 'NTC' and \
             qkv.dtype in (torch.float16, torch.bfloat16):
         from . import cuda
         if cuda.available():
             from .cuda import attn_ops
             if attn_ops.supported(qkv, heads):
-                return attn_ops.fused_self_attention(qkv, mask, heads)
+                return attn_ops.fused_self_attention(qkv.contiguous(), mask, heads, p)
     am = None
     if mask is not None:
         am = (mask != 0)[:, None, None, :]

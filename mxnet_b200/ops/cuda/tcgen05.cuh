@@ -113,7 +113,19 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// cuTensorMapEncodeTiled is a driver entry point and needs a context current on the calling thread.  A thread that has
+// only touched cached allocations so far (a worker thread of the autograd engine) may not have one bound yet: a
+// runtime call that requires the device binds the primary context.
+inline void ensure_context() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 inline EncodeTiledFn encode_fn() {
+  ensure_context();
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;

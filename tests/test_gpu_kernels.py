@@ -393,6 +393,76 @@ def test_device_wait_times_out_with_status_not_a_hang():
     assert float(torch.ones(4, device='cuda').sum()) == 4.0
 
 
+# ---------------------------------------------------------------------------------------- attention
+def _attention_reference(qkv, mask, heads):
+    N, T, C3 = qkv.shape
+    C = C3 // 3
+    x = qkv.float().reshape(N, T, 3, heads, C // heads)
+    q, k, v = (x[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    s = q @ k.transpose(-1, -2) / (C // heads) ** 0.5
+    if mask is not None:
+        s = s.masked_fill((mask == 0)[:, None, None, :], float('-inf'))
+    return (torch.softmax(s, -1) @ v).permute(0, 2, 1, 3).reshape(N, T, C)
+
+
+@pytest.mark.parametrize('N,T,heads', [(2, 128, 2), (3, 100, 12), (1, 17, 1), (5, 128, 4)])
+@pytest.mark.parametrize('use_mask', [False, True])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_fused_self_attention_matches_reference(N, T, heads, use_mask, dtype):
+    from mxnet_b200.ops.cuda import attn_ops
+    torch.manual_seed(12)
+    C = heads * 64
+    qkv = (torch.randn(N, T, 3 * C, device=_dev()) * 0.7).to(dtype).requires_grad_(True)
+    mask = None
+    if use_mask:
+        lens = torch.randint(1, T + 1, (N,), device=_dev())
+        mask = (torch.arange(T, device=_dev())[None, :] < lens[:, None]).float()
+    assert attn_ops.supported(qkv, heads)
+    out = attn_ops.fused_self_attention(qkv, mask, heads, 0.0)
+    g = torch.randn_like(out)
+    out.backward(g)
+    attn_ops.check_errors()
+    ref_in = qkv.detach().float().requires_grad_(True)
+    ref = _attention_reference(ref_in, mask, heads)
+    ref.backward(g.float())
+    tol = (2e-2, 2e-2) if dtype == torch.float16 else (6e-2, 6e-2)
+    _close(out, ref, *tol)
+    _close(qkv.grad, ref_in.grad, tol[0] * 2, tol[1] * 2)
+
+
+def test_fused_self_attention_dropout_is_unbiased_and_consistent():
+    from mxnet_b200.ops.cuda import attn_ops
+    torch.manual_seed(13)
+    N, T, heads, C = 4, 128, 4, 256
+    qkv = torch.zeros(N, T, 3 * C, device=_dev(), dtype=torch.float16)
+    qkv[:, :, 2 * C:] = 1.0                                   # V = 1, Q = K = 0: out = sum of kept weights / (1 - p)
+    out = attn_ops.fused_self_attention(qkv, None, heads, 0.5)
+    attn_ops.check_errors()
+    o = out.float()
+    assert abs(float(o.mean()) - 1.0) < 0.02 and 0.05 < float(o.std()) < 0.2
+    # with the dropout word pinned, forward is linear in V and backward is its adjoint: <dV, W> == <g, f(W)>
+    base = (torch.randn(N, T, 3 * C, device=_dev()) * 0.5).half()
+    state = attn_ops._seed[_dev()]
+
+    def run(v_block, need_grad=False):
+        state.fill_(1234567)
+        x = base.clone()
+        x[:, :, 2 * C:] = v_block
+        x.requires_grad_(need_grad)
+        return x, attn_ops.fused_self_attention(x, None, heads, 0.3)
+    v1 = (torch.randn(N, T, C, device=_dev()) * 0.5).half()
+    w = (torch.randn(N, T, C, device=_dev()) * 0.5).half()
+    x, y = run(v1, True)
+    g = torch.randn_like(y)
+    y.backward(g)
+    dv = x.grad[:, :, 2 * C:].float()
+    _, fw = run(w)
+    lhs, rhs = float((dv * w.float()).sum()), float((g.float() * fw.float()).sum())
+    assert abs(lhs - rhs) < 2e-2 * max(1.0, abs(rhs))
+    _, y2 = run(v1)
+    assert torch.equal(y, y2)                                  # same word, same pattern
+
+
 # ---------------------------------------------------------------------------------------- gradient compression
 @pytest.mark.parametrize('kind,threshold', [('2bit', 0.5), ('1bit', 0.0)])
 @pytest.mark.parametrize('n', [1, 15, 16, 33, 100003])
