@@ -105,6 +105,18 @@ def case_maxpool(ctx, dtype, small):
     return dict(inputs=[x], fn=fn, fwd_bytes=nb * 1.25 + nb / 8, bwd_bytes=nb * 1.25 + nb / 8)
 
 
+def case_attention(ctx, dtype, small, dropout=0.0):
+    n, t, heads = (16, 128, 12) if small else (64, 128, 12)
+    c = heads * 64
+    qkv = _rand((n, t, 3 * c), ctx, dtype, 0.5)
+    fl = 4.0 * n * heads * t * t * 64            # QKt and PV
+
+    def fn(qkv):
+        return nd.contrib.fused_self_attention(qkv, heads=heads, dropout=dropout, layout='NTC')
+    nb = qkv.size * _esize(dtype)
+    return dict(inputs=[qkv], fn=fn, fwd_flops=fl, bwd_flops=2.5 * fl, fwd_bytes=nb * 4 / 3, bwd_bytes=nb * (2 + 2 / 3))
+
+
 def case_add(ctx, dtype, small):
     n = 2 ** 24 if small else 2 ** 28
     a, b = _rand((n,), ctx, dtype), _rand((n,), ctx, dtype)
@@ -124,6 +136,7 @@ CASES = {
     'log_softmax': lambda c, d, s: case_softmax(c, d, s, log=True),
     'LayerNorm': case_layernorm,
     'MaxPool3x3s2': case_maxpool,
+    'fused_self_attention': case_attention,
     'elemwise_add': case_add,
 }
 
