@@ -113,13 +113,12 @@ def array(object, dtype=None, ctx=None, device=None, copy=True):  # pylint: disa
         return ndarray._from_tensor(t, ctx)
     if dtype is None:
         a = _np.asarray(object)
-        if a.dtype == _np.float64:
-            td = _np_default_float()
-        elif a.dtype.kind == 'O':
+        if a.dtype.kind == 'O':
             a = _np.asarray([x.asnumpy() if isinstance(x, NDArray) else x for x in object])
-            td = to_torch_dtype(a.dtype) if a.dtype != _np.float64 else _np_default_float()
-        else:
-            td = to_torch_dtype(a.dtype)
+        # python/mxnet/numpy/multiarray.py:2747-2760: without an explicit dtype everything that is not already an
+        # mx.np.ndarray becomes float32, unless the NumPy default-dtype mode is on (then NumPy's own rules apply)
+        from ..util import is_np_default_dtype
+        td = to_torch_dtype(a.dtype) if is_np_default_dtype() else torch.float32
         return ndarray._from_tensor(torch.from_numpy(_np.ascontiguousarray(a)).to(device=ctx.torch_device, dtype=td), ctx)
     if isinstance(object, (list, tuple)) and any(isinstance(x, NDArray) for x in object):
         object = [x.asnumpy() if isinstance(x, NDArray) else x for x in object]

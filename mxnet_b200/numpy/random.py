@@ -118,4 +118,4 @@ logistic = lambda loc=0.0, scale=1.0, size=None, ctx=None, out=None, device=None
 rayleigh = lambda scale=1.0, size=None, ctx=None, out=None, device=None: _dist('rayleigh')(scale, size=size, ctx=ctx, out=out, device=device)
 weibull = lambda a, size=None, ctx=None, out=None, device=None: _dist('weibull')(a, size=size, ctx=ctx, out=out, device=device)
 pareto = lambda a, size=None, ctx=None, out=None, device=None: _dist('pareto')(a, size=size, ctx=ctx, out=out, device=device)
-power = lambda a, size=None, ctx=None, out=None, device=None: _dist('power')(a, size=size, ctx=ctx, out=out, device=device)
+power = lambda a, size=None, ctx=None, out=None, device=None: _dist('powerd')(a, size=size, ctx=ctx, out=out, device=device)

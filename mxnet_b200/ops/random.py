@@ -308,7 +308,7 @@ _np_dist('logistic', lambda u, loc, scale: loc + scale * (torch.log(u) - torch.l
 _np_dist('rayleigh', lambda u, scale: scale * torch.sqrt(-2 * torch.log1p(-u)))
 _np_dist('weibull', lambda u, a: torch.pow(-torch.log1p(-u), 1.0 / a))
 _np_dist('pareto', lambda u, a: torch.exp(-torch.log1p(-u) / a) - 1)
-_np_dist('power', lambda u, a: torch.pow(u, 1.0 / a))
+_np_dist('powerd', lambda u, a: torch.pow(u, 1.0 / a))      # _npi_powerd: `_npi_power` is the arithmetic operator
 
 
 # ---- pdf ops (src/operator/random/pdf_op.cc) --------------------------------------------------
