@@ -26,15 +26,14 @@ class BERTEncoderLayer(HybridBlock):
         self.ffn1 = nn.Dense(hidden_size, flatten=False, in_units=units)
         self.ffn2 = nn.Dense(units, flatten=False, in_units=hidden_size)
         self.ln2 = nn.LayerNorm(epsilon=layer_norm_eps, in_channels=units)
-        self.drop = nn.Dropout(dropout)
 
     def forward(self, x, mask=None):
         qkv = self.attn_qkv(x)
         args = [qkv] if mask is None else [qkv, mask]
         ctx_vec = _op('_contrib_fused_self_attention', args, heads=self._heads, dropout=self._dropout, layout='NTC')
-        x = self.ln1(x + self.drop(self.attn_proj(ctx_vec)))
+        x = self.ln1(_op('_contrib_dropout_add', [self.attn_proj(ctx_vec), x], p=self._dropout))
         h = _op('LeakyReLU', [self.ffn1(x)], act_type='gelu')
-        return self.ln2(x + self.drop(self.ffn2(h)))
+        return self.ln2(_op('_contrib_dropout_add', [self.ffn2(h), x], p=self._dropout))
 
 
 class BERTModel(HybridBlock):

@@ -80,6 +80,42 @@ def interleaved_matmul_encdec_valatt(keys_values, attention, heads=1):
     return out.reshape(N, heads, Tq, D).permute(2, 0, 1, 3).reshape(Tq, N, heads * D)
 
 
+def _ew_kernels(t):
+    if not (t.is_cuda and env.get('MXNET_B200_KERNELS')):
+        return None
+    from . import cuda
+    if not cuda.available():
+        return None
+    from .cuda import elementwise_ops
+    return elementwise_ops
+
+
+@register('_contrib_dropout_add', 'dropout_add', '_npx_dropout_add', inputs=('data', 'residual', 'bias'),
+          defaults={'p': 0.5, 'mode': 'training'})
+def dropout_add(data, residual, bias=None, p=0.5, mode='training'):
+    """residual + Dropout(data + bias, p) in one pass over the tensors (the sub-layer output of a transformer block;
+    the reference composes Dropout (src/operator/nn/dropout-inl.h) and elemwise_add)."""
+    active = (mode == 'always') or _state.state.training
+    p = float(p) if active else 0.0
+    ew = _ew_kernels(data)
+    if ew is not None and ew.pointwise_supported(data, data.shape[-1]) and residual.shape == data.shape and \
+            residual.dtype == data.dtype and residual.is_contiguous() and (bias is None or bias.dtype == data.dtype):
+        return ew.dropout(data, p, bias, residual)
+    x = data if bias is None else data + bias
+    return residual + (F.dropout(x, p, True) if p > 0 else x)
+
+
+@register('_contrib_bias_gelu', 'bias_gelu', '_npx_bias_gelu', inputs=('data', 'bias'))
+def bias_gelu(data, bias=None):
+    """gelu(data + bias), erf form, bias broadcast over the last axis (one pass; the reference composes broadcast_add
+    and LeakyReLU(act_type='gelu'), src/operator/leaky_relu-inl.h)."""
+    ew = _ew_kernels(data)
+    if ew is not None and ew.pointwise_supported(data, data.shape[-1]) and (bias is None or (bias.dtype == data.dtype and
+                                                                                         bias.is_contiguous())):
+        return ew.gelu(data, bias)
+    return F.gelu(data if bias is None else data + bias)
+
+
 @register('_contrib_fused_self_attention', 'fused_self_attention', '_npx_fused_self_attention',
           inputs=('qkv', 'mask'), defaults={'heads': 1, 'dropout': 0.0, 'layout': 'NTC'})
 def fused_self_attention(qkv, mask=None, heads=1, dropout=0.0, layout='NTC'):

@@ -1,28 +1,207 @@
-"""NHWC convolution on the sm_100a kernels.
+"""NHWC stride-1 convolution on the tcgen05 implicit-GEMM kernels (``conv_tcgen05.cu``).
 
-1x1 stride-1 convolutions are GEMMs over the flattened pixels ([N*H*W, Cin] x [Cout, Cin]^T) and run on
-the tcgen05 kernel when ``MXNET_B200_CONV1X1=1``; other shapes go to the library convolution on a
-channels-last view (no layout copies)."""
+``MXNET_B200_CONV`` selects which directions run on the in-tree kernels: ``auto`` (default) times the
+in-tree kernel against the library convolution the first time a (shape, direction) is seen outside of
+graph capture and keeps the faster one (the counterpart of the reference's ``cudnn_tune``,
+src/operator/nn/cudnn/cudnn_algoreg-inl.h); a comma-separated subset of ``fwd,dgrad,wgrad`` or ``1``
+forces the in-tree kernels, ``0`` the library.  Unsupported shapes (strided, grouped, channel counts
+that are not multiples of 8) always go to the library convolution on a channels-last view.  The forward kernel also accumulates the per-channel sums that a following
+BatchNorm needs; they travel as an attribute of the output tensor and are used when that tensor
+reaches the BatchNorm kernels unmodified.
+"""
 import os
 
 import torch
 
-from . import gemm_ops
+from . import lib, ptr, stream_ptr, count_launch, check
+from ._util import dt, require
+from .gemm_ops import _error_flag
+
+_DEFAULT = 'auto'
+_ALL = frozenset(('fwd', 'dgrad', 'wgrad'))
+_tuned = {}          # (direction, dtype, geometry) -> True when the in-tree kernel won
+# achieved rate of the separate BatchNorm statistics pass that the forward epilogue replaces, bytes per microsecond
+_BN_REDUCE_BYTES_PER_US = 4.8e6
+
+
+def directions():
+    v = os.environ.get('MXNET_B200_CONV', _DEFAULT).strip().lower()
+    if v in ('0', '', 'none', 'off'):
+        return frozenset()
+    if v == 'auto':
+        return frozenset(('auto',))
+    if v in ('1', 'all', 'on'):
+        return _ALL
+    return frozenset(p.strip() for p in v.split(','))
+
+
+def _time_us(fn, reps=3):
+    fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / reps
+
+
+def use_own(direction, dirs, key, own_fn, lib_fn, lib_extra_us=0.0):
+    """Whether `direction` of the convolution described by `key` runs on the in-tree kernel."""
+    if 'auto' not in dirs:
+        return direction in dirs
+    k = (direction,) + key
+    hit = _tuned.get(k)
+    if hit is None:
+        if torch.cuda.is_current_stream_capturing():
+            return False                   # cannot time inside a capture; the eager warm-up run normally comes first
+        with torch.no_grad():
+            hit = _tuned[k] = _time_us(own_fn) <= _time_us(lib_fn) + lib_extra_us
+    return hit
+
+
+def tuned_choices():
+    """{(direction, dtype, N, H, W, Cin, Cout, R, S, pad, dilate): in-tree kernel chosen} of the auto mode so far."""
+    return dict(_tuned)
+
+
+def out_hw(h, w, kernel, pad, dilate):
+    return h + 2 * pad[0] - dilate[0] * (kernel[0] - 1), w + 2 * pad[1] - dilate[1] * (kernel[1] - 1)
+
+
+def shape_ok(data, weight, stride, dilate, pad, num_group):
+    if data.dtype not in (torch.float16, torch.bfloat16) or weight.dtype != data.dtype or num_group != 1:
+        return False
+    if data.dim() != 4 or weight.dim() != 4 or tuple(stride) != (1, 1):
+        return False
+    cin, cout = data.shape[-1], weight.shape[0]
+    if cin % 8 or cout % 8 or weight.shape[3] != cin or not data.is_contiguous() or not weight.is_contiguous():
+        return False
+    ho, wo = out_hw(data.shape[1], data.shape[2], weight.shape[1:3], pad, dilate)
+    return ho >= 1 and wo >= 1 and data.numel() > 0 and max(pad) < 256
 
 
 def supported(data, weight, stride, dilate, pad, num_group):
-    if os.environ.get('MXNET_B200_CONV1X1', '0') != '1':
-        return False
-    if data.dtype not in (torch.float16, torch.bfloat16) or num_group != 1:
-        return False
-    kh, kw = weight.shape[1], weight.shape[2]
-    if (kh, kw) != (1, 1) or tuple(stride) != (1, 1) or tuple(pad) != (0, 0) or tuple(dilate) != (1, 1):
-        return False
-    return data.is_contiguous() and gemm_ops.supported(data.numel() // data.shape[-1], weight.shape[0], data.shape[-1])
+    return bool(directions()) and shape_ok(data, weight, stride, dilate, pad, num_group)
 
 
-def conv2d_nhwc(data, weight, bias, stride, pad):
-    n, h, w, c = data.shape
-    cout = weight.shape[0]
-    y = gemm_ops.LinearFn.apply(data.reshape(-1, c), weight.reshape(cout, c), bias, None)
-    return y.reshape(n, h, w, cout)
+def conv_forward(x, w, bias=None, res=None, pad=(0, 0), dilate=(1, 1), relu=False, want_stats=False):
+    """y = act(conv(x, w) + bias + res) and, optionally, the [rows, 2, Cout] partial sums of y and y*y."""
+    L = lib()
+    n, h, wd, cin = x.shape
+    cout, r, s, _ = w.shape
+    require(x, 'data')
+    require(w, 'weight', dtype=x.dtype, device=x.device, shape=(cout, r, s, cin))
+    ho, wo = out_hw(h, wd, (r, s), pad, dilate)
+    y = torch.empty((n, ho, wo, cout), dtype=x.dtype, device=x.device)
+    if bias is not None:
+        bias = require(bias.to(x.dtype).contiguous(), 'bias', numel=cout, device=x.device)
+    if res is not None:
+        require(res, 'residual', dtype=x.dtype, device=x.device, shape=y.shape)
+    stats = torch.empty((L.mxb_conv_stat_rows(), 2, cout), dtype=torch.float32, device=x.device) if want_stats else None
+    check(L.mxb_conv_forward(dt(x), ptr(x), ptr(w), ptr(y), ptr(bias), ptr(res), ptr(stats), n, h, wd, cin, cout, r, s,
+                             pad[0], pad[1], dilate[0], dilate[1], 1 if relu else 0, ptr(_error_flag(x.device)),
+                             stream_ptr(x.device)), 'conv_forward')
+    count_launch(1)
+    return y, stats
+
+
+def conv_dgrad(dy, w, in_hw, pad=(0, 0), dilate=(1, 1), res=None):
+    """Gradient with respect to the input of the stride-1 convolution (optionally added to ``res``)."""
+    L = lib()
+    n, ho, wo, cout = dy.shape
+    _, r, s, cin = w.shape
+    h, wd = in_hw
+    require(dy, 'out_grad', shape=(n,) + out_hw(h, wd, (r, s), pad, dilate) + (cout,))
+    require(w, 'weight', dtype=dy.dtype, device=dy.device, shape=(cout, r, s, cin))
+    dx = torch.empty((n, h, wd, cin), dtype=dy.dtype, device=dy.device)
+    if res is not None:
+        require(res, 'residual', dtype=dy.dtype, device=dy.device, shape=dx.shape)
+    check(L.mxb_conv_dgrad(dt(dy), ptr(dy), ptr(w), ptr(dx), ptr(res), n, h, wd, cin, cout, r, s, pad[0], pad[1],
+                           dilate[0], dilate[1], ptr(_error_flag(dy.device)), stream_ptr(dy.device)), 'conv_dgrad')
+    count_launch(1)
+    return dx
+
+
+def conv_wgrad(x, dy, kernel, pad=(0, 0), dilate=(1, 1)):
+    """Gradient with respect to the [Cout, R, S, Cin] filter."""
+    L = lib()
+    n, h, wd, cin = x.shape
+    cout = dy.shape[-1]
+    r, s = kernel
+    require(x, 'data')
+    require(dy, 'out_grad', dtype=x.dtype, device=x.device, shape=(n,) + out_hw(h, wd, (r, s), pad, dilate) + (cout,))
+    dw32 = torch.empty((cout, r, s, cin), dtype=torch.float32, device=x.device)
+    dw = torch.empty((cout, r, s, cin), dtype=x.dtype, device=x.device)
+    check(L.mxb_conv_wgrad(dt(x), ptr(x), ptr(dy), ptr(dw), ptr(dw32), n, h, wd, cin, cout, r, s, pad[0], pad[1],
+                           dilate[0], dilate[1], ptr(_error_flag(x.device)), stream_ptr(x.device)), 'conv_wgrad')
+    count_launch(2)
+    return dw
+
+
+def _library_backward(x, w, dy, pad, dilate, need_dx, need_dw):
+    """Library data / weight gradient on channels-last views of the NHWC tensors."""
+    xc, wc, dyc = x.permute(0, 3, 1, 2), w.permute(0, 3, 1, 2), dy.permute(0, 3, 1, 2)
+    dx, dw, _ = torch.ops.aten.convolution_backward(dyc, xc, wc, None, [1, 1], list(pad), list(dilate), False, [0, 0], 1,
+                                                    [need_dx, need_dw, False])
+    if dx is not None:
+        dx = dx.permute(0, 2, 3, 1).contiguous()
+    if dw is not None:
+        dw = dw.permute(0, 2, 3, 1).contiguous()
+    return dx, dw
+
+
+def _library_forward(x, w, bias, pad, dilate):
+    y = torch.nn.functional.conv2d(x.permute(0, 3, 1, 2), w.permute(0, 3, 1, 2), bias, 1, pad, dilate)
+    return y.permute(0, 2, 3, 1).contiguous()
+
+
+class _ConvNHWC(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, pad, dilate, dirs, want_stats):
+        key = (x.dtype,) + tuple(x.shape) + (w.shape[0], w.shape[1], w.shape[2]) + tuple(pad) + tuple(dilate)
+        ho, wo = out_hw(x.shape[1], x.shape[2], w.shape[1:3], pad, dilate)
+        credit = x.shape[0] * ho * wo * w.shape[0] * x.element_size() / _BN_REDUCE_BYTES_PER_US if want_stats else 0.0
+        if use_own('fwd', dirs, key, lambda: conv_forward(x, w, bias, None, pad, dilate, False, want_stats),
+                   lambda: _library_forward(x, w, bias, pad, dilate), credit):
+            y, stats = conv_forward(x, w, bias, None, pad, dilate, False, want_stats)
+        else:
+            y, stats = _library_forward(x, w, bias, pad, dilate), None
+        ctx.save_for_backward(x, w)
+        ctx.geom = (pad, dilate, dirs, bias is not None, key)
+        if stats is None:
+            stats = x.new_empty(0, dtype=torch.float32)
+        ctx.mark_non_differentiable(stats)
+        return y, stats
+
+    @staticmethod
+    def backward(ctx, dy, _ds):
+        x, w = ctx.saved_tensors
+        pad, dilate, dirs, has_bias, key = ctx.geom
+        dy = dy.contiguous()
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        dx = dw = None
+        if need_dx and use_own('dgrad', dirs, key, lambda: conv_dgrad(dy, w, x.shape[1:3], pad, dilate),
+                               lambda: _library_backward(x, w, dy, pad, dilate, True, False)):
+            dx = conv_dgrad(dy, w, x.shape[1:3], pad, dilate)
+        if need_dw and use_own('wgrad', dirs, key, lambda: conv_wgrad(x, dy, w.shape[1:3], pad, dilate),
+                               lambda: _library_backward(x, w, dy, pad, dilate, False, True)):
+            dw = conv_wgrad(x, dy, w.shape[1:3], pad, dilate)
+        lib_dx, lib_dw = need_dx and dx is None, need_dw and dw is None
+        if lib_dx or lib_dw:
+            ldx, ldw = _library_backward(x, w, dy, pad, dilate, lib_dx, lib_dw)
+            dx = ldx if lib_dx else dx
+            dw = ldw if lib_dw else dw
+        db = dy.sum((0, 1, 2)) if has_bias and ctx.needs_input_grad[2] else None
+        return dx, dw, db, None, None, None, None
+
+
+def conv2d_nhwc(data, weight, bias, stride, pad, dilate=(1, 1), want_stats=True):
+    dirs = directions()
+    want_stats = want_stats and ('fwd' in dirs or 'auto' in dirs) and torch.is_grad_enabled()
+    y, stats = _ConvNHWC.apply(data, weight, bias, tuple(pad), tuple(dilate), dirs, want_stats)
+    if stats.numel():
+        # per-channel partial sums of this tensor for a BatchNorm that consumes it unmodified
+        y._mxb_bn_partials = (stats, y._version)
+    return y

@@ -249,15 +249,18 @@ inline int apply_grid(int64_t nvec) {
 template <typename T>
 int bn_forward_t(const T* x, const T* res, const void* gamma, const void* beta, int pdtype, float* rmean, float* rvar,
                  float* save_mean, float* save_invstd, float* scale_shift, float* scratch, T* y, int64_t M, int C, float eps,
-                 float momentum, int training, int relu, cudaStream_t st) {
-  const int grid = bn_grid(M, C);
+                 float momentum, int training, int relu, cudaStream_t st, const float* ext_partial = nullptr,
+                 int ext_rows = 0) {
+  const int grid = ext_partial ? ext_rows : bn_grid(M, C);
   float* scale = scale_shift;
   float* shift = scale_shift + C;
-  if (training)
+  // batch statistics: reduced here, or taken from partial sums that the producer of x already accumulated
+  if (training && !ext_partial)
     bn_reduce_kernel<T, false, kReluNone><<<grid, kBnThreads, 0, st>>>(x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
                                                                        M, C, scratch);
   bn_fwd_finalize_kernel<<<(C + kFinX - 1) / kFinX, dim3(kFinX, kFinY), 0, st>>>(
-      scratch, grid, C, M, eps, momentum, gamma, beta, pdtype, rmean, rvar, save_mean, save_invstd, scale, shift, training);
+      ext_partial ? ext_partial : scratch, grid, C, M, eps, momentum, gamma, beta, pdtype, rmean, rvar, save_mean, save_invstd,
+      scale, shift, training);
   const int64_t nvec = M * (C >> 3);
   const int g2 = apply_grid(nvec);
   const int L = C >> 3;
@@ -423,6 +426,25 @@ MXB_EXPORT int mxb_bn_forward(int dtype, const void* x, const void* res, const v
     return bn_forward_t<__nv_bfloat16>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, gamma, beta, pdtype, rmean, rvar,
                                        save_mean, save_invstd, scale_shift, scratch, (__nv_bfloat16*)y, M, C, eps, momentum,
                                        training, relu, st);
+  return -1;
+}
+
+// Training-mode forward whose batch statistics come from `partial` ([rows][2][C] floats: per-channel sums of x and
+// x*x, any split over the rows), e.g. from the epilogue of the convolution that produced x.
+MXB_EXPORT int mxb_bn_forward_stats(int dtype, const void* x, const void* res, const void* gamma, const void* beta,
+                                    int pdtype, float* rmean, float* rvar, float* save_mean, float* save_invstd,
+                                    float* scale_shift, const float* partial, int rows, void* y, int64_t M, int C, float eps,
+                                    float momentum, int relu, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (pdtype != kF32 && pdtype != kF16 && pdtype != kBF16) return -1;
+  if (!partial || rows < 1) return -2;
+  if (dtype == kF16)
+    return bn_forward_t<__half>((const __half*)x, (const __half*)res, gamma, beta, pdtype, rmean, rvar, save_mean,
+                                save_invstd, scale_shift, nullptr, (__half*)y, M, C, eps, momentum, 1, relu, st, partial, rows);
+  if (dtype == kBF16)
+    return bn_forward_t<__nv_bfloat16>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, gamma, beta, pdtype, rmean, rvar,
+                                       save_mean, save_invstd, scale_shift, nullptr, (__nv_bfloat16*)y, M, C, eps, momentum,
+                                       1, relu, st, partial, rows);
   return -1;
 }
 

@@ -13,7 +13,7 @@ def bn_supported(x):
 
 class _BatchNormNHWC(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, gamma, beta, rmean, rvar, residual, eps, momentum, training, relu):
+    def forward(ctx, x, gamma, beta, rmean, rvar, residual, eps, momentum, training, relu, partials=None):
         L = lib()
         C = x.shape[-1]
         M = x.numel() // C
@@ -28,15 +28,26 @@ class _BatchNormNHWC(torch.autograd.Function):
         res = residual.contiguous() if residual is not None else None
         if res is not None:
             require(res, 'residual', dtype=x.dtype, device=x.device, shape=x.shape)
-        grid = L.mxb_bn_grid(M, C)
-        scratch = torch.empty(grid * 2 * C, dtype=torch.float32, device=x.device)
         stats = torch.empty(4 * C, dtype=torch.float32, device=x.device)    # mean | invstd | scale | shift
         save_mean, save_invstd, scale_shift = stats[:C], stats[C:2 * C], stats[2 * C:]
         y = torch.empty_like(x)
-        check(L.mxb_bn_forward(dt(x), ptr(x), ptr(res), ptr(gamma), ptr(beta), dt(gamma), ptr(rmean), ptr(rvar),
-                               ptr(save_mean), ptr(save_invstd), ptr(scale_shift), ptr(scratch), ptr(y), M, C, eps,
-                               momentum, 1 if training else 0, 1 if relu else 0, stream_ptr(x.device)), 'bn_forward')
-        count_launch(3 if training else 2)
+        if training and partials is not None:
+            # the producer of x (a convolution epilogue) already accumulated sum x and sum x^2 per channel
+            require(partials, 'partials', dtype=torch.float32, device=x.device)
+            if partials.dim() != 3 or partials.shape[1] != 2 or partials.shape[2] != C:
+                raise ValueError('partials must be [rows, 2, %d], got %s' % (C, tuple(partials.shape)))
+            check(L.mxb_bn_forward_stats(dt(x), ptr(x), ptr(res), ptr(gamma), ptr(beta), dt(gamma), ptr(rmean), ptr(rvar),
+                                         ptr(save_mean), ptr(save_invstd), ptr(scale_shift), ptr(partials),
+                                         partials.shape[0], ptr(y), M, C, eps, momentum, 1 if relu else 0,
+                                         stream_ptr(x.device)), 'bn_forward_stats')
+            count_launch(2)
+        else:
+            grid = L.mxb_bn_grid(M, C)
+            scratch = torch.empty(grid * 2 * C, dtype=torch.float32, device=x.device)
+            check(L.mxb_bn_forward(dt(x), ptr(x), ptr(res), ptr(gamma), ptr(beta), dt(gamma), ptr(rmean), ptr(rvar),
+                                   ptr(save_mean), ptr(save_invstd), ptr(scale_shift), ptr(scratch), ptr(y), M, C, eps,
+                                   momentum, 1 if training else 0, 1 if relu else 0, stream_ptr(x.device)), 'bn_forward')
+            count_launch(3 if training else 2)
         ctx.save_for_backward(x, y if (relu and residual is not None) or not training else None, gamma, stats)
         ctx.relu, ctx.has_res, ctx.training = relu, residual is not None, training
         ctx.set_materialize_grads(False)
@@ -47,7 +58,7 @@ class _BatchNormNHWC(torch.autograd.Function):
     def backward(ctx, dy, _gm, _gv):
         x, y, gamma, stats = ctx.saved_tensors
         if dy is None:
-            return (None,) * 10
+            return (None,) * 11
         L = lib()
         C = x.shape[-1]
         M = x.numel() // C
@@ -63,7 +74,7 @@ class _BatchNormNHWC(torch.autograd.Function):
             xh = (x.float() - save_mean) * save_invstd
             dgamma = (d.float() * xh).reshape(-1, C).sum(0)
             dbeta = d.float().reshape(-1, C).sum(0)
-            return dx, dgamma.to(gamma.dtype), dbeta.to(gamma.dtype), None, None, (d if ctx.has_res else None), None, None, None, None
+            return dx, dgamma.to(gamma.dtype), dbeta.to(gamma.dtype), None, None, (d if ctx.has_res else None), None, None, None, None, None
         grid = L.mxb_bn_grid(M, C)
         scratch = torch.empty((grid * 2 + 3) * C, dtype=torch.float32, device=x.device)
         dx = torch.empty_like(x)
@@ -74,14 +85,16 @@ class _BatchNormNHWC(torch.autograd.Function):
                                 ptr(scale_shift), ptr(scratch), ptr(dx), ptr(dres), ptr(dgamma), ptr(dbeta), M, C,
                                 1 if ctx.relu else 0, stream_ptr(x.device)), 'bn_backward')
         count_launch(3)
-        return dx, dgamma, dbeta, None, None, dres, None, None, None, None
+        return dx, dgamma, dbeta, None, None, dres, None, None, None, None, None
 
 
 def batch_norm_nhwc(x, gamma, beta, rmean, rvar, eps, momentum, training, act_type, residual, want_stats=True):
     """Returns (y, mean, var) like the BatchNorm operator with ``output_mean_var``; ``want_stats=False``
     skips the conversion of the saved inverse standard deviation back to a variance."""
+    hint = getattr(x, '_mxb_bn_partials', None)
+    partials = hint[0] if (training and hint is not None and hint[1] == x._version) else None
     y, mean, invstd = _BatchNormNHWC.apply(x, gamma, beta, rmean, rvar, residual, float(eps), float(momentum),
-                                           bool(training), act_type == 'relu')
+                                           bool(training), act_type == 'relu', partials)
     if not want_stats:
         return y, None, None
     var = 1.0 / (invstd * invstd) - eps

@@ -66,6 +66,58 @@ multi_sgd_kernel(const __grid_constant__ TensorTable tab, float momentum, float 
   }
 }
 
+struct AdamTable {
+  void* w[kMaxTensors];
+  const void* g[kMaxTensors];
+  float* mean[kMaxTensors];
+  float* var[kMaxTensors];
+  float* w32[kMaxTensors];            // fp32 master weights (or null)
+  float lr[kMaxTensors];
+  float wd[kMaxTensors];
+  float eta[kMaxTensors];
+  int64_t n[kMaxTensors];
+  int chunk_start[kMaxTensors + 1];
+  int count;
+};
+
+// Adam (kDecoupled = false: weight decay folded into the gradient, optimizer_op-inl.h AdamUpdate) and AdamW
+// (kDecoupled = true: w -= eta * (lr * m / (sqrt(v) + eps) + wd * w), src/operator/contrib/adamw-inl.h) over a table of
+// tensors.  `rescale_ptr` is a device float (the reference passes rescale_grad as a tensor so that the loss scaler never
+// synchronises with the host): a zero or non-finite value skips the whole update.
+template <typename T, bool kMP, bool kDecoupled>
+__global__ void __launch_bounds__(256)
+multi_adam_kernel(const __grid_constant__ AdamTable tab, float beta1, float beta2, float eps, float clip,
+                  const float* __restrict__ rescale_ptr, float rescale_host) {
+  const float rescale = rescale_ptr ? *rescale_ptr : rescale_host;
+  if (!(fabsf(rescale) <= 3.0e38f) || rescale == 0.f) return;
+  const int total = tab.chunk_start[tab.count];
+  for (int chunk = blockIdx.x; chunk < total; chunk += gridDim.x) {
+    const int t = find_tensor(tab.chunk_start, tab.count, chunk);
+    const int64_t base = (int64_t)(chunk - tab.chunk_start[t]) * kChunk;
+    const int64_t n = tab.n[t];
+    T* w = (T*)tab.w[t];
+    const T* g = (const T*)tab.g[t];
+    float* mean = tab.mean[t];
+    float* var = tab.var[t];
+    float* w32 = tab.w32[t];
+    const float lr = tab.lr[t], wd = tab.wd[t], eta = tab.eta[t];
+    for (int64_t i = base + threadIdx.x; i < base + kChunk && i < n; i += blockDim.x) {
+      float gr = Cvt<T>::to_f(g[i]) * rescale;
+      if (clip >= 0.f) gr = fminf(fmaxf(gr, -clip), clip);
+      float wv = kMP ? w32[i] : Cvt<T>::to_f(w[i]);
+      if (!kDecoupled) gr += wd * wv;
+      const float m = beta1 * mean[i] + (1.f - beta1) * gr;
+      const float v = beta2 * var[i] + (1.f - beta2) * gr * gr;
+      mean[i] = m;
+      var[i] = v;
+      const float step = lr * m / (sqrtf(v) + eps);
+      wv -= kDecoupled ? eta * (step + wd * wv) : step;
+      if (kMP) w32[i] = wv;
+      w[i] = Cvt<T>::from_f(wv);
+    }
+  }
+}
+
 struct PtrTable {
   const void* p[kMaxTensors];
   int64_t n[kMaxTensors];
@@ -161,6 +213,41 @@ MXB_EXPORT int mxb_multi_sgd(int dtype, int count, void** w, void** g, float** m
   else if (mom) multi_sgd_kernel<T, true, false><<<grid, 256, 0, st>>>(tab, momentum, rescale, clip);        \
   else if (mp) multi_sgd_kernel<T, false, true><<<grid, 256, 0, st>>>(tab, momentum, rescale, clip);         \
   else multi_sgd_kernel<T, false, false><<<grid, 256, 0, st>>>(tab, momentum, rescale, clip);
+  if (dtype == kF32) { LAUNCH(float) }
+  else if (dtype == kF16) { LAUNCH(__half) }
+  else if (dtype == kBF16) { LAUNCH(__nv_bfloat16) }
+  else return -1;
+#undef LAUNCH
+  return (int)cudaGetLastError();
+}
+
+// Adam / AdamW over up to mxb_max_tensors() tensors in one launch.  mean, var: fp32 states; w32: fp32 masters or null;
+// rescale_ptr: device float or null (then rescale_host is used); decoupled: 0 = Adam, 1 = AdamW (etas used).
+MXB_EXPORT int mxb_multi_adam(int dtype, int count, void** w, void** g, float** mean, float** var, float** w32,
+                              const float* lrs, const float* wds, const float* etas, const int64_t* sizes, float beta1,
+                              float beta2, float eps, float clip, const float* rescale_ptr, float rescale_host,
+                              int decoupled, void* stream) {
+  if (count > kMaxTensors || count <= 0 || !mean || !var) return -2;
+  AdamTable tab;
+  tab.count = count;
+  int acc = 0;
+  for (int i = 0; i < count; ++i) {
+    tab.w[i] = w[i]; tab.g[i] = g[i]; tab.mean[i] = mean[i]; tab.var[i] = var[i];
+    tab.w32[i] = w32 ? w32[i] : nullptr;
+    tab.lr[i] = lrs[i]; tab.wd[i] = wds[i]; tab.eta[i] = etas ? etas[i] : 1.f; tab.n[i] = sizes[i];
+    tab.chunk_start[i] = acc;
+    acc += chunks_of(sizes[i]);
+  }
+  tab.chunk_start[count] = acc;
+  int grid = acc < sm_count() * 8 ? acc : sm_count() * 8;
+  if (grid < 1) grid = 1;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool mp = w32 != nullptr;
+#define LAUNCH(T)                                                                                                              \
+  if (mp && decoupled) multi_adam_kernel<T, true, true><<<grid, 256, 0, st>>>(tab, beta1, beta2, eps, clip, rescale_ptr, rescale_host);   \
+  else if (mp) multi_adam_kernel<T, true, false><<<grid, 256, 0, st>>>(tab, beta1, beta2, eps, clip, rescale_ptr, rescale_host);          \
+  else if (decoupled) multi_adam_kernel<T, false, true><<<grid, 256, 0, st>>>(tab, beta1, beta2, eps, clip, rescale_ptr, rescale_host);   \
+  else multi_adam_kernel<T, false, false><<<grid, 256, 0, st>>>(tab, beta1, beta2, eps, clip, rescale_ptr, rescale_host);
   if (dtype == kF32) { LAUNCH(float) }
   else if (dtype == kF16) { LAUNCH(__half) }
   else if (dtype == kBF16) { LAUNCH(__nv_bfloat16) }

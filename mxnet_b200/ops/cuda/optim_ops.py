@@ -35,6 +35,37 @@ def multi_sgd(ws, gs, moms, w32, lrs, wds, momentum, rescale, clip):
         count_launch(1)
 
 
+def multi_adam(ws, gs, means, vars_, w32, lrs, wds, etas, beta1, beta2, eps, clip, rescale, decoupled):
+    """Adam (decoupled=False) or AdamW over lists of tensors; `rescale` is a float or a one-element fp32 device tensor
+    (a zero or non-finite value skips the update on the device, without a host synchronisation)."""
+    L = lib()
+    cap = L.mxb_max_tensors()
+    dtype = ws[0].dtype
+    rs_ptr, rs_host = (ptr(rescale), 1.0) if isinstance(rescale, torch.Tensor) else (None, float(rescale))
+    if isinstance(rescale, torch.Tensor):
+        require(rescale, 'rescale_grad', numel=1, dtype=torch.float32, device=ws[0].device)
+    for i in range(0, len(ws), cap):
+        sl = slice(i, i + cap)
+        w, g = ws[sl], gs[sl]
+        n = len(w)
+        dev = w[0].device
+        for j in range(n):
+            require(w[j], 'weight', dtype=dtype, device=dev)
+            require(g[j], 'grad', numel=w[j].numel(), dtype=dtype, device=dev)
+            require(means[i + j], 'mean', numel=w[j].numel(), dtype=torch.float32, device=dev)
+            require(vars_[i + j], 'var', numel=w[j].numel(), dtype=torch.float32, device=dev)
+            if w32 is not None:
+                require(w32[i + j], 'weight32', numel=w[j].numel(), dtype=torch.float32, device=dev)
+        mp = _parr(w32[sl]) if w32 is not None else None
+        et = (C.c_float * n)(*etas[sl]) if etas is not None else None
+        check(L.mxb_multi_adam(DT[dtype], n, _parr(w), _parr(g), _parr(means[sl]), _parr(vars_[sl]), mp,
+                               (C.c_float * n)(*lrs[sl]), (C.c_float * n)(*wds[sl]), et,
+                               (C.c_int64 * n)(*[t.numel() for t in w]), float(beta1), float(beta2), float(eps),
+                               float(-1.0 if clip is None else clip), rs_ptr, rs_host, 1 if decoupled else 0,
+                               stream_ptr(dev)), 'multi_adam')
+        count_launch(1)
+
+
 def multi_all_finite(tensors):
     L = lib()
     cap = L.mxb_max_tensors()

@@ -89,7 +89,7 @@ def convolution(data, weight, bias=None, kernel=(), stride=(), dilate=(), pad=()
     if layout in _CHANNEL_LAST and nsp == 2 and _use_kernels(data):
         from .cuda import conv_ops
         if conv_ops.supported(data, weight, stride, dilate, pad, num_group):
-            return conv_ops.conv2d_nhwc(data, weight, bias, stride, pad)
+            return conv_ops.conv2d_nhwc(data, weight, bias, stride, pad, dilate)
     x = _to_channel_first(data, layout)
     w = _to_channel_first(weight, layout)
     fn = (F.conv1d, F.conv2d, F.conv3d)[nsp - 1]
@@ -279,6 +279,16 @@ def pooling(data, kernel=(), pool_type='max', global_pool=False, cudnn_off=False
         k2, s2, p2 = _tup(kernel, 2), _tup(stride, 2) or (1, 1), _tup(pad, 2) or (0, 0)
         if pool_ops.supported(data, k2, s2, p2):
             return pool_ops.max_pool2d_nhwc(data, k2, s2, p2, pooling_convention == 'full')
+    if layout in _CHANNEL_LAST and nsp == 2 and pool_type == 'avg' and _use_kernels(data) \
+            and pooling_convention in ('valid', 'full'):
+        from .cuda import elementwise_ops as ew
+        if ew.avgpool_supported(data):
+            if global_pool:
+                return ew.global_avg_pool_nhwc(data)
+            k2, s2, p2 = _tup(kernel, 2), _tup(stride, 2) or (1, 1), _tup(pad, 2) or (0, 0)
+            if p2[0] < k2[0] and p2[1] < k2[1]:
+                return ew.avg_pool2d_nhwc(data, k2, s2, p2, pooling_convention == 'full',
+                                          True if count_include_pad is None else bool(count_include_pad))
     x = _to_channel_first(data, layout)
     if global_pool:
         red = tuple(range(2, x.dim()))
@@ -393,6 +403,10 @@ def leaky_relu(data, gamma=None, act_type='leaky', slope=0.25, lower_bound=0.125
     if act_type == 'selu':
         return F.selu(data)
     if act_type == 'gelu':
+        if _use_kernels(data):
+            from .cuda import elementwise_ops as ew
+            if ew.pointwise_supported(data, data.shape[-1] if data.dim() else 1):
+                return ew.gelu(data)
         return F.gelu(data)
     if act_type == 'gelu_tanh':
         return F.gelu(data, approximate='tanh')
@@ -433,6 +447,10 @@ def dropout(data, p=0.5, mode='training', axes=(), cudnn_off=False):
             shape[a] = 1
         mask = (torch.rand(shape, device=data.device) >= p).to(data.dtype) / (1 - p)
         return data * mask
+    if _use_kernels(data) and 0 < p < 1:
+        from .cuda import elementwise_ops as ew
+        if ew.pointwise_supported(data, data.shape[-1] if data.dim() else 1):
+            return ew.dropout(data, p)
     return F.dropout(data, p, True)
 
 

@@ -147,10 +147,37 @@ for _k, _s in (('sgd', 2), ('sgd_mom', 3), ('mp_sgd', 3), ('mp_sgd_mom', 4)):
           defaults=dict(_COMMON, beta1=0.9, beta2=0.999, epsilon=1e-8, lazy_update=True))
 def adam_update(weight, grad, mean, var, lr=0.01, beta1=0.9, beta2=0.999, epsilon=1e-8, wd=0.0, rescale_grad=1.0,
                 clip_gradient=-1.0, lazy_update=True):
+    if _adam_kernel_ok(weight, grad, mean, var):
+        from .cuda import optim_ops
+        optim_ops.multi_adam([weight], [grad], [mean], [var], None, [lr], [wd], None, beta1, beta2, epsilon,
+                             clip_gradient, float(rescale_grad), False)
+        return weight
     g = _prep(grad, rescale_grad, clip_gradient) + wd * weight
     mean.mul_(beta1).add_(g, alpha=1 - beta1)
     var.mul_(beta2).addcmul_(g, g, value=1 - beta2)
     return weight.addcdiv_(mean, var.sqrt().add_(epsilon), value=-lr)
+
+
+def _adam_kernel_ok(weight, grad, mean, var, weight32=None):
+    """The multi-tensor Adam kernel takes contiguous CUDA tensors with fp32 states."""
+    if not (weight.is_cuda and env.get('MXNET_B200_KERNELS')):
+        return False
+    from . import cuda
+    if not cuda.available():
+        return False
+    ts = [weight, grad, mean, var] + ([weight32] if weight32 is not None else [])
+    return (all(t.is_contiguous() and t.device == weight.device for t in ts) and grad.dtype == weight.dtype
+            and weight.dtype in (torch.float32, torch.float16, torch.bfloat16) and mean.dtype == torch.float32
+            and var.dtype == torch.float32 and (weight32 is None or weight32.dtype == torch.float32))
+
+
+def _rescale_arg(rescale_grad, device):
+    """rescale_grad for the kernel: the device tensor itself (no host read) or a float."""
+    if isinstance(rescale_grad, torch.Tensor):
+        if rescale_grad.is_cuda and rescale_grad.device == device and rescale_grad.numel() == 1:
+            return rescale_grad.reshape(1).float() if rescale_grad.dtype != torch.float32 else rescale_grad.reshape(1)
+        return float(rescale_grad.item())
+    return float(rescale_grad)
 
 
 def _adamw_core(w, g, mean, var, lr, eta, beta1, beta2, epsilon, wd):
@@ -168,6 +195,11 @@ def _rescale_tensor(rescale_grad):
           defaults={'lr': 0.01, 'beta1': 0.9, 'beta2': 0.999, 'epsilon': 1e-8, 'wd': 0.0, 'eta': 1.0, 'clip_gradient': -1.0})
 def adamw_update(weight, grad, mean, var, rescale_grad=1.0, lr=0.01, beta1=0.9, beta2=0.999, epsilon=1e-8, wd=0.0,
                  eta=1.0, clip_gradient=-1.0):
+    if _adam_kernel_ok(weight, grad, mean, var):
+        from .cuda import optim_ops
+        optim_ops.multi_adam([weight], [grad], [mean], [var], None, [lr], [wd], [eta], beta1, beta2, epsilon,
+                             clip_gradient, _rescale_arg(rescale_grad, weight.device), True)
+        return weight
     rs = _rescale_tensor(rescale_grad)
     if not math.isfinite(rs) or rs == 0:
         return weight
@@ -181,6 +213,11 @@ def adamw_update(weight, grad, mean, var, rescale_grad=1.0, lr=0.01, beta1=0.9, 
           defaults={'lr': 0.01, 'beta1': 0.9, 'beta2': 0.999, 'epsilon': 1e-8, 'wd': 0.0, 'eta': 1.0, 'clip_gradient': -1.0})
 def mp_adamw_update(weight, grad, mean, var, weight32, rescale_grad=1.0, lr=0.01, beta1=0.9, beta2=0.999,
                     epsilon=1e-8, wd=0.0, eta=1.0, clip_gradient=-1.0):
+    if _adam_kernel_ok(weight, grad, mean, var, weight32):
+        from .cuda import optim_ops
+        optim_ops.multi_adam([weight], [grad], [mean], [var], [weight32], [lr], [wd], [eta], beta1, beta2, epsilon,
+                             clip_gradient, _rescale_arg(rescale_grad, weight.device), True)
+        return weight
     rs = _rescale_tensor(rescale_grad)
     if not math.isfinite(rs) or rs == 0:
         return weight
@@ -196,6 +233,13 @@ def _multi_adamw(mp):
         n = num_weights
         rs = data[-1]
         lrs, wds, etas = _seq(lrs, n), _seq(wds, n), _seq(etas, n)
+        cols = [[data[i * stride + k] for i in range(n)] for k in range(stride)]
+        if all(_adam_kernel_ok(*[c[i] for c in cols]) for i in range(n)) and len({c.dtype for c in cols[0]}) == 1:
+            # one launch per 48 tensors; the rescale tensor is read on the device
+            from .cuda import optim_ops
+            optim_ops.multi_adam(cols[0], cols[1], cols[2], cols[3], cols[4] if mp else None, lrs, wds, etas, beta1, beta2,
+                                 epsilon, clip_gradient, _rescale_arg(rs, cols[0][0].device), True)
+            return tuple(cols[0])
         outs = []
         for i in range(n):
             a = data[i * stride:(i + 1) * stride]
@@ -219,6 +263,11 @@ register('_multi_mp_adamw_update', '_contrib_multi_mp_adamw_update', inputs=('*d
           defaults={'lr': 0.01, 'beta1': 0.9, 'beta2': 0.999, 'epsilon': 1e-8, 'wd': 0.0, 'eta': 1.0, 'clip_gradient': -1.0})
 def adabelief_update(weight, grad, mean, var, rescale_grad=1.0, lr=0.01, beta1=0.9, beta2=0.999, epsilon=1e-8, wd=0.0,
                      eta=1.0, clip_gradient=-1.0):
+    if _adam_kernel_ok(weight, grad, mean, var):
+        from .cuda import optim_ops
+        optim_ops.multi_adam([weight], [grad], [mean], [var], None, [lr], [wd], [eta], beta1, beta2, epsilon,
+                             clip_gradient, _rescale_arg(rescale_grad, weight.device), True)
+        return weight
     rs = _rescale_tensor(rescale_grad)
     if not math.isfinite(rs) or rs == 0:
         return weight

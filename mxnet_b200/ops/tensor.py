@@ -17,6 +17,15 @@ import torch.nn.functional as F
 
 from .registry import register, alias
 from ..base import MXNetError, to_torch_dtype
+from .. import env as _env
+
+
+def _use_kernels(t):
+    """True when CUDA tensors should take the hand-written sm_100a kernels."""
+    if not t.is_cuda or not _env.get('MXNET_B200_KERNELS'):
+        return False
+    from . import cuda
+    return cuda.available()
 
 # ------------------------------------------------------------------------------------------
 # helpers
@@ -380,6 +389,10 @@ def clip(data, a_min=None, a_max=None):
 @register('add_n', 'ElementWiseSum', '_grad_add', inputs=('*args',))
 def add_n(*args):
     out = args[0]
+    if len(args) > 1 and _use_kernels(out):
+        from .cuda import elementwise_ops as ew
+        if ew.add_n_supported(args):
+            return ew.add_n(args)
     if len(args) > 1:
         out = torch.stack(args, 0).sum(0) if len(args) > 4 else sum(args[1:], args[0])
     return out
@@ -406,7 +419,14 @@ def cast(data, dtype='float32'):
 @register('amp_cast', inputs=('data',), defaults={'dtype': 'float32'})
 def amp_cast(data, dtype='float32'):
     """Cast inserted by the mixed-precision graph pass (src/operator/tensor/amp_cast.cc): floating inputs only."""
-    return data.to(to_torch_dtype(dtype)) if data.dtype.is_floating_point else data
+    if not data.dtype.is_floating_point:
+        return data
+    target = to_torch_dtype(dtype)
+    if _use_kernels(data):
+        from .cuda import elementwise_ops as ew
+        if ew.cast_supported(data, target):
+            return ew.cast(data, target)
+    return data.to(target)
 
 
 @register('amp_multicast', inputs=('*data',), nout=lambda a: a.get('num_outputs', 1),
@@ -1039,6 +1059,11 @@ def one_hot(indices, depth=1, on_value=1.0, off_value=0.0, dtype='float32'):
 @register('Embedding', '_npx_embedding', inputs=('data', 'weight'),
           defaults={'input_dim': 0, 'output_dim': 0, 'dtype': 'float32', 'sparse_grad': False})
 def embedding(data, weight, input_dim=None, output_dim=None, dtype=None, sparse_grad=False):
+    if _use_kernels(weight):
+        from .cuda import elementwise_ops as ew
+        idx = data if data.dtype in (torch.int32, torch.int64) else data.long()
+        if ew.embedding_supported(idx, weight):
+            return ew.embedding(idx, weight)
     idx = torch.clamp(data.long(), 0, weight.shape[0] - 1)
     return F.embedding(idx, weight)
 

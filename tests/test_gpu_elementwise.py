@@ -1,0 +1,223 @@
+"""Numerics of the pointwise / gather / pooling kernels against plain fp32 PyTorch references."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+import mxnet_b200 as mx
+from mxnet_b200 import autograd, nd
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.float16, torch.bfloat16]
+
+
+def _dev():
+    return torch.device('cuda', 0)
+
+
+def _tol(dtype):
+    return {torch.float32: (1e-5, 1e-5), torch.float16: (2e-3, 2e-3), torch.bfloat16: (2e-2, 2e-2)}[dtype]
+
+
+def _close(a, b, rtol, atol):
+    np.testing.assert_allclose(a.detach().float().cpu().numpy(), b.detach().float().cpu().numpy(), rtol=rtol, atol=atol)
+
+
+@pytest.mark.parametrize('shape', [(64, 3072), (3, 5, 768), (16,)])
+@pytest.mark.parametrize('with_bias', [False, True])
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_gelu_forward_backward(shape, with_bias, dtype):
+    from mxnet_b200.ops.cuda import elementwise_ops as ew
+    torch.manual_seed(0)
+    x = torch.randn(*shape, device=_dev()).to(dtype).requires_grad_(True)
+    bias = torch.randn(shape[-1], device=_dev()).to(dtype).requires_grad_(True) if with_bias else None
+    y = ew.gelu(x, bias)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(True)
+    br = bias.detach().float().requires_grad_(True) if with_bias else None
+    ref = F.gelu(xr + br if with_bias else xr)
+    ref.backward(dy.float())
+    _close(y, ref, *_tol(dtype))
+    _close(x.grad, xr.grad, *_tol(dtype))
+    if with_bias:
+        rows = x.numel() // shape[-1]
+        _close(bias.grad, br.grad, _tol(dtype)[0] * 4, _tol(dtype)[1] * rows ** 0.5 * 4)
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_dropout_is_unbiased_consistent_and_fuses_bias_residual(dtype):
+    from mxnet_b200.ops.cuda import elementwise_ops as ew
+    torch.manual_seed(1)
+    p = 0.25
+    x = torch.ones(512, 1024, device=_dev(), dtype=dtype).requires_grad_(True)
+    y = ew.dropout(x, p)
+    kept = (y != 0).float().mean().item()
+    assert abs(kept - (1 - p)) < 0.01
+    _close(y[y != 0], torch.full_like(y[y != 0], 1 / (1 - p)), 1e-2, 1e-2)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    # the backward pass recomputes the same mask
+    _close(x.grad, dy.float() * (y != 0).float() / (1 - p), *_tol(dtype))
+    y2 = ew.dropout(x.detach(), p)
+    assert (y2 != y).any()                     # a new pattern on the next call
+    # residual + dropout(x + bias)
+    bias = torch.randn(1024, device=_dev()).to(dtype)
+    res = torch.randn(512, 1024, device=_dev()).to(dtype)
+    xb = torch.randn(512, 1024, device=_dev()).to(dtype)
+    y3 = ew.dropout(xb, 0.0, bias, res)
+    _close(y3, xb.float() + bias.float() + res.float(), *_tol(dtype))
+    y4 = ew.dropout(xb, p, bias, res)
+    d = (y4.float() - res.float())
+    mask = d.abs() > 1e-3
+    _close(d[mask], ((xb.float() + bias.float()) / (1 - p))[mask], 5e-2, 5e-2)
+
+
+@pytest.mark.parametrize('count', [2, 3, 8, 11])
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_add_n(count, dtype):
+    from mxnet_b200.ops.cuda import elementwise_ops as ew
+    torch.manual_seed(2)
+    ts = [torch.randn(33, 128, device=_dev()).to(dtype) for _ in range(count)]
+    ref = sum(t.float() for t in ts)
+    out = ew.add_n(ts)
+    rt, at = _tol(dtype)
+    _close(out, ref, rt * 2, at * count)
+
+
+@pytest.mark.parametrize('src,dst', [(torch.float32, torch.float16), (torch.float16, torch.float32),
+                                     (torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32),
+                                     (torch.float16, torch.bfloat16)])
+@pytest.mark.parametrize('n', [8, 1000, 100003])
+def test_cast(src, dst, n):
+    from mxnet_b200.ops.cuda import elementwise_ops as ew
+    torch.manual_seed(3)
+    x = torch.randn(n, device=_dev()).to(src)
+    y = ew.cast(x, dst)
+    assert y.dtype == dst
+    assert torch.equal(y, x.to(dst))
+
+
+@pytest.mark.parametrize('idx_dtype', [torch.int32, torch.int64])
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_embedding_forward_and_sorted_gradient(idx_dtype, dtype):
+    from mxnet_b200.ops.cuda import elementwise_ops as ew
+    torch.manual_seed(4)
+    rows, D = 1000, 72 if dtype != torch.float32 else 68
+    w = torch.randn(rows, D, device=_dev()).to(dtype).requires_grad_(True)
+    idx = torch.randint(0, 50, (7, 129), device=_dev()).to(idx_dtype)        # many repeated rows
+    idx[0, 0] = rows + 5                                                      # clipped like take(mode='clip')
+    out = ew.embedding(idx, w)
+    ref_idx = idx.long().clamp(0, rows - 1)
+    assert torch.equal(out, w.detach()[ref_idx])
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    ref = torch.zeros(rows, D, device=_dev()).index_add_(0, ref_idx.reshape(-1), dy.float().reshape(-1, D))
+    rt, at = _tol(dtype)
+    _close(w.grad, ref, rt * 4, at * 8)
+    g1 = w.grad.clone()
+    w.grad = None
+    ew.embedding(idx, w).backward(dy)
+    assert torch.equal(g1, w.grad)                                            # bitwise reproducible
+
+
+@pytest.mark.parametrize('shape,k,s,p,ceil,include', [((2, 13, 17, 16), 3, 2, 1, False, True), ((3, 8, 8, 64), 2, 2, 0, False, True),
+                                                      ((2, 7, 7, 2048), 7, 1, 0, False, True), ((2, 9, 9, 8), 3, 2, 1, True, False),
+                                                      ((1, 10, 12, 24), 3, 1, 1, False, False)])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.float32])
+def test_avgpool_nhwc(shape, k, s, p, ceil, include, dtype):
+    from mxnet_b200.ops.cuda import elementwise_ops as ew
+    torch.manual_seed(5)
+    x = torch.randn(*shape, device=_dev()).to(dtype).requires_grad_(True)
+    y = ew.avg_pool2d_nhwc(x, (k, k), (s, s), (p, p), ceil, include)
+    xr = x.detach().float().requires_grad_(True)
+    ref = F.avg_pool2d(xr.permute(0, 3, 1, 2), k, s, p, ceil, include).permute(0, 2, 3, 1)
+    assert y.shape == ref.shape
+    _close(y, ref, *_tol(dtype))
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ref.backward(dy.float())
+    _close(x.grad, xr.grad, _tol(dtype)[0] * 2, _tol(dtype)[1] * 4)
+
+
+def test_global_avg_pool_and_operator_dispatch():
+    x = nd.array(np.random.RandomState(0).randn(4, 7, 7, 64).astype('float32'), ctx=mx.gpu(0), dtype='float16')
+    x.attach_grad()
+    with autograd.record():
+        y = nd.Pooling(x, global_pool=True, pool_type='avg', kernel=(1, 1), layout='NHWC')
+        z = (y * y).sum()
+    z.backward()
+    ref = x.asnumpy().astype('float32').mean((1, 2), keepdims=True)
+    np.testing.assert_allclose(y.asnumpy().astype('float32'), ref, rtol=2e-3, atol=2e-3)
+    np.testing.assert_allclose(x.grad.asnumpy().astype('float32'), np.broadcast_to(2 * ref / 49, x.shape), rtol=1e-2, atol=1e-3)
+
+
+@pytest.mark.parametrize('shape', [(100, 37), (5, 64, 128), (3, 2, 33, 65)])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.float32])
+def test_transpose_last2(shape, dtype):
+    from mxnet_b200.ops.cuda import elementwise_ops as ew
+    x = torch.randn(*shape, device=_dev()).to(dtype)
+    assert torch.equal(ew.transpose_last2(x), x.transpose(-1, -2).contiguous())
+
+
+def test_operators_reach_the_kernels():
+    """LeakyReLU(gelu), Dropout, Embedding, add_n and amp_cast route CUDA tensors to the kernel library."""
+    from mxnet_b200.ops import cuda
+    ctx = mx.gpu(0)
+    before = cuda.launches()
+    x = nd.array(np.random.RandomState(1).randn(8, 64).astype('float32'), ctx=ctx)
+    w = nd.array(np.random.RandomState(2).randn(20, 64).astype('float32'), ctx=ctx)
+    idx = nd.array(np.arange(8) % 20, ctx=ctx)
+    g = nd.LeakyReLU(x, act_type='gelu')
+    np.testing.assert_allclose(g.asnumpy(), F.gelu(torch.from_numpy(x.asnumpy())).numpy(), rtol=1e-5, atol=1e-5)
+    e = nd.Embedding(idx, w, input_dim=20, output_dim=64)
+    np.testing.assert_allclose(e.asnumpy(), w.asnumpy()[np.arange(8) % 20])
+    s = nd.add_n(x, g, e)
+    np.testing.assert_allclose(s.asnumpy(), x.asnumpy() + g.asnumpy() + e.asnumpy(), rtol=1e-5, atol=1e-5)
+    h = nd.amp_cast(x, dtype='float16')
+    assert h.dtype == np.float16
+    with autograd.record(train_mode=True):
+        d = nd.Dropout(x, p=0.5)
+    assert 0.2 < float((d.asnumpy() == 0).mean()) < 0.8
+    assert cuda.launches() - before >= 5
+
+
+@pytest.mark.parametrize('mp', [False, True])
+def test_multi_adamw_kernel_matches_tensor_op_rule(mp):
+    """_multi_(mp_)adamw_update on CUDA (one kernel, rescale read on the device) against the same operator on CPU."""
+    rng = np.random.RandomState(7)
+    shapes = [(33,), (128, 65), (9000,), (3, 5, 7)]
+    wdt = 'float16' if mp else 'float32'
+
+    def run(ctx):
+        data = []
+        for s in shapes:
+            w32 = rng_w[s]
+            w = nd.array(w32, ctx=ctx, dtype=wdt)
+            g = nd.array(rng_g[s], ctx=ctx, dtype=wdt)
+            m = nd.array(rng_m[s], ctx=ctx)
+            v = nd.array(rng_v[s], ctx=ctx)
+            data += [w, g, m, v] + ([nd.array(w.asnumpy().astype('float32'), ctx=ctx)] if mp else [])
+        rescale = nd.array([0.5], ctx=ctx)
+        op = nd.contrib.multi_mp_adamw_update if mp else nd.contrib.multi_adamw_update
+        for _ in range(3):
+            op(*data, rescale, lrs=[0.01, 0.02, 0.03, 0.04], wds=[0.0, 0.1, 0.01, 0.0], etas=[1.0, 0.9, 1.0, 0.5],
+               beta1=0.9, beta2=0.99, epsilon=1e-6, clip_gradient=0.8, num_weights=len(shapes), out=data[::5 if mp else 4])
+        return [d.asnumpy().astype('float32') for d in data]
+
+    rng_w = {s: rng.randn(*s).astype('float32') for s in shapes}
+    rng_g = {s: rng.randn(*s).astype('float32') for s in shapes}
+    rng_m = {s: rng.randn(*s).astype('float32') * 0.1 for s in shapes}
+    rng_v = {s: np.abs(rng.randn(*s)).astype('float32') * 0.1 for s in shapes}
+    gpu = run(mx.gpu(0))
+    cpu = run(mx.cpu())
+    for a, b in zip(gpu, cpu):
+        np.testing.assert_allclose(a, b, rtol=2e-3 if mp else 1e-5, atol=2e-3 if mp else 1e-6)
+    # a non-finite rescale (overflowed loss scale) skips the update on the device
+    ctx = mx.gpu(0)
+    w = nd.array(rng_w[(33,)], ctx=ctx)
+    before = w.asnumpy().copy()
+    nd.contrib.multi_adamw_update(w, nd.array(rng_g[(33,)], ctx=ctx), nd.zeros((33,), ctx=ctx), nd.zeros((33,), ctx=ctx),
+                                  nd.array([float('inf')], ctx=ctx), lrs=[0.1], wds=[0.0], etas=[1.0], num_weights=1, out=[w])
+    np.testing.assert_array_equal(w.asnumpy(), before)
