@@ -88,6 +88,11 @@ class MXRecordIO(object):
         if rc != 0:
             raise MXNetError('record too large')
 
+    def tell(self):
+        """Byte offset of the next record to be read or written."""
+        L = _rt()
+        return L.mxb_rec_writer_tell(self.handle) if self.writable else L.mxb_rec_reader_tell(self.handle)
+
     def read(self):
         assert not self.writable
         self._check_pid(allow_reset=True)
