@@ -670,3 +670,278 @@ def calibrate_entropy(hist, hist_edges, num_quantized_bins=255):
         if kl < best:
             best, best_t = kl, float(edges[hi]) if hi < edges.size else float(edges[-1])
     return torch.tensor([best_t], dtype=torch.float32), torch.tensor([best], dtype=torch.float32)
+
+
+# ------------------------------------------------------------------------------------------
+# Region-proposal, position-sensitive pooling and deformable convolution operators
+# (src/operator/contrib/{proposal,multi_proposal,psroi_pooling,deformable_psroi_pooling,deformable_convolution,
+#  modulated_deformable_convolution,mrcnn_mask_target}*).  Cold-path detection operators: tensor operations and the
+#  library's detection primitives; differentiable with respect to the feature maps through autograd.
+# ------------------------------------------------------------------------------------------
+def _rpn_anchors(feature_stride, ratios, scales, device):
+    """Base anchors of the region-proposal network (proposal-inl.h:188-226): for every ratio, then every scale."""
+    base = float(feature_stride)
+    ctr = 0.5 * (base - 1.0)
+    out = []
+    for ratio in ratios:
+        size_ratios = math.floor(base * base / ratio)
+        for scale in scales:
+            w = math.floor(math.sqrt(size_ratios) + 0.5) * scale
+            h = math.floor((w / scale * ratio) + 0.5) * scale
+            out.append([ctr - 0.5 * (w - 1.0), ctr - 0.5 * (h - 1.0), ctr + 0.5 * (w - 1.0), ctr + 0.5 * (h - 1.0)])
+    return torch.tensor(out, dtype=torch.float32, device=device)
+
+
+def _greedy_nms(boxes, thresh, max_keep):
+    """Greedy suppression in score order with the +1 pixel area convention (proposal.cc:204-256)."""
+    n = boxes.shape[0]
+    area = (boxes[:, 2] - boxes[:, 0] + 1) * (boxes[:, 3] - boxes[:, 1] + 1)
+    xx1 = torch.maximum(boxes[:, None, 0], boxes[None, :, 0])
+    yy1 = torch.maximum(boxes[:, None, 1], boxes[None, :, 1])
+    xx2 = torch.minimum(boxes[:, None, 2], boxes[None, :, 2])
+    yy2 = torch.minimum(boxes[:, None, 3], boxes[None, :, 3])
+    inter = (xx2 - xx1 + 1).clamp(min=0) * (yy2 - yy1 + 1).clamp(min=0)
+    over = (inter / (area[:, None] + area[None, :] - inter) > thresh).cpu()
+    suppressed = torch.zeros(n, dtype=torch.bool)
+    keep = []
+    for i in range(n):
+        if len(keep) >= max_keep:
+            break
+        if suppressed[i]:
+            continue
+        keep.append(i)
+        suppressed[i + 1:] |= over[i, i + 1:]
+    return keep
+
+
+def _proposal_one(scores, deltas, im_info, pre_n, post_n, threshold, min_size, scales, ratios, stride, iou_loss):
+    A, H, W = scores.shape
+    dev = scores.device
+    anchors = _rpn_anchors(stride, ratios, scales, dev)                                   # (A, 4)
+    shift_x = torch.arange(W, device=dev, dtype=torch.float32) * stride
+    shift_y = torch.arange(H, device=dev, dtype=torch.float32) * stride
+    shifts = torch.stack([shift_x[None, :].expand(H, W), shift_y[:, None].expand(H, W)] * 2, -1)   # (H, W, 4)
+    boxes = (anchors[None, None] + shifts[:, :, None]).reshape(-1, 4)                     # index = (h*W + w)*A + a
+    d = deltas.float().reshape(A, 4, H, W).permute(2, 3, 0, 1).reshape(-1, 4)
+    score = scores.float().permute(1, 2, 0).reshape(-1).clone()
+    im_h, im_w, im_scale = float(im_info[0]), float(im_info[1]), float(im_info[2])
+    if iou_loss:
+        pred = boxes + d
+    else:
+        w = boxes[:, 2] - boxes[:, 0] + 1.0
+        h = boxes[:, 3] - boxes[:, 1] + 1.0
+        cx = boxes[:, 0] + 0.5 * (w - 1.0)
+        cy = boxes[:, 1] + 0.5 * (h - 1.0)
+        pcx, pcy = d[:, 0] * w + cx, d[:, 1] * h + cy
+        pw, ph = torch.exp(d[:, 2]) * w, torch.exp(d[:, 3]) * h
+        pred = torch.stack([pcx - 0.5 * (pw - 1.0), pcy - 0.5 * (ph - 1.0), pcx + 0.5 * (pw - 1.0), pcy + 0.5 * (ph - 1.0)], 1)
+    pred = torch.stack([pred[:, 0].clamp(0, im_w - 1), pred[:, 1].clamp(0, im_h - 1),
+                        pred[:, 2].clamp(0, im_w - 1), pred[:, 3].clamp(0, im_h - 1)], 1)
+    # positions beyond the real (unpadded) image get score -1
+    real_h, real_w = int(im_h / stride), int(im_w / stride)
+    hh = torch.arange(H, device=dev)[:, None, None].expand(H, W, A).reshape(-1)
+    ww = torch.arange(W, device=dev)[None, :, None].expand(H, W, A).reshape(-1)
+    score[(hh >= real_h) | (ww >= real_w)] = -1.0
+    # boxes below the minimum size are grown by min_size/2 on every side and demoted
+    ms = min_size * im_scale
+    small = ((pred[:, 2] - pred[:, 0] + 1.0) < ms) | ((pred[:, 3] - pred[:, 1] + 1.0) < ms)
+    grow = torch.tensor([-ms / 2, -ms / 2, ms / 2, ms / 2], device=dev)
+    pred = torch.where(small[:, None], pred + grow, pred)
+    score[small] = -1.0
+    count = score.numel()
+    pre_n = count if pre_n <= 0 else min(pre_n, count)
+    post_n_eff = min(post_n, pre_n)
+    order = torch.sort(score, descending=True, stable=True)[1][:pre_n]
+    props, sc = pred[order], score[order]
+    keep = _greedy_nms(props, threshold, post_n_eff)
+    idx = torch.tensor([keep[i] if i < len(keep) else keep[i % len(keep)] for i in range(post_n)], device=dev)
+    return props[idx], sc[idx]
+
+
+def _proposal_nout(attrs):
+    return 2 if attrs.get('output_score') in (True, 'True', 1, '1') else 1
+
+
+_PROPOSAL_DEFAULTS = {'rpn_pre_nms_top_n': 6000, 'rpn_post_nms_top_n': 300, 'threshold': 0.7, 'rpn_min_size': 16,
+                      'scales': (4.0, 8.0, 16.0, 32.0), 'ratios': (0.5, 1.0, 2.0), 'feature_stride': 16,
+                      'output_score': False, 'iou_loss': False}
+
+
+@register('_contrib_MultiProposal', 'MultiProposal', '_contrib_Proposal', 'Proposal', inputs=('cls_prob', 'bbox_pred', 'im_info'),
+          nout=_proposal_nout, defaults=_PROPOSAL_DEFAULTS)
+def multi_proposal(cls_prob, bbox_pred, im_info, rpn_pre_nms_top_n=6000, rpn_post_nms_top_n=300, threshold=0.7,
+                   rpn_min_size=16, scales=(4.0, 8.0, 16.0, 32.0), ratios=(0.5, 1.0, 2.0), feature_stride=16,
+                   output_score=False, iou_loss=False):
+    """Region proposals from RPN scores and box deltas: anchors -> decoded boxes -> clip -> min-size filter -> top-k ->
+    greedy NMS -> fixed-size output (batch index, x1, y1, x2, y2), padded by cycling through the kept boxes.
+    ``Proposal`` is the single-image form of the same computation."""
+    N, A2, H, W = cls_prob.shape
+    A = A2 // 2
+    rois, scores = [], []
+    with torch.no_grad():
+        for b in range(N):
+            r, s = _proposal_one(cls_prob[b, A:], bbox_pred[b], im_info[b].tolist(), int(rpn_pre_nms_top_n),
+                                 int(rpn_post_nms_top_n), float(threshold), float(rpn_min_size), tuple(scales), tuple(ratios),
+                                 int(feature_stride), bool(iou_loss))
+            rois.append(torch.cat([torch.full((r.shape[0], 1), float(b), device=r.device), r], 1))
+            scores.append(s[:, None])
+    rois = torch.cat(rois, 0).to(cls_prob.dtype)
+    if output_score:
+        return rois, torch.cat(scores, 0).to(cls_prob.dtype)
+    return rois
+
+
+@register('_contrib_PSROIPooling', 'PSROIPooling', inputs=('data', 'rois'),
+          defaults={'spatial_scale': 1.0, 'output_dim': 1, 'pooled_size': 1, 'group_size': 0})
+def psroi_pooling(data, rois, spatial_scale=1.0, output_dim=1, pooled_size=1, group_size=0):
+    """Position-sensitive ROI average pooling (R-FCN): output channel c of bin (ph, pw) averages input channel
+    (c * G + gh) * G + gw over the bin (psroi_pooling.cu:36-90)."""
+    P = int(pooled_size)
+    G = int(group_size) or P
+    N, C, H, W = data.shape
+    out = data.new_zeros((rois.shape[0], int(output_dim), P, P))
+    r_cpu = rois.detach().float().cpu()
+    ctop = torch.arange(int(output_dim), device=data.device)
+    for n in range(rois.shape[0]):
+        b = int(r_cpu[n, 0])
+        x1 = round(float(r_cpu[n, 1])) * spatial_scale
+        y1 = round(float(r_cpu[n, 2])) * spatial_scale
+        x2 = (round(float(r_cpu[n, 3])) + 1.0) * spatial_scale
+        y2 = (round(float(r_cpu[n, 4])) + 1.0) * spatial_scale
+        rw, rh = max(x2 - x1, 0.1), max(y2 - y1, 0.1)
+        bh, bw = rh / P, rw / P
+        for ph in range(P):
+            hs = min(max(int(math.floor(ph * bh + y1)), 0), H)
+            he = min(max(int(math.ceil((ph + 1) * bh + y1)), 0), H)
+            gh = min(max(int(math.floor(ph * G / P)), 0), G - 1)
+            for pw in range(P):
+                ws = min(max(int(math.floor(pw * bw + x1)), 0), W)
+                we = min(max(int(math.ceil((pw + 1) * bw + x1)), 0), W)
+                gw = min(max(int(math.floor(pw * G / P)), 0), G - 1)
+                if he <= hs or we <= ws:
+                    continue
+                chan = (ctop * G + gh) * G + gw
+                out[n, :, ph, pw] = data[b, chan, hs:he, ws:we].float().mean((1, 2)).to(data.dtype)
+    return out
+
+
+def _bilinear_at(plane, h, w):
+    """plane: (K, H, W); bilinear value at the (already clamped) real position (h, w)."""
+    H, W = plane.shape[-2:]
+    h0, w0 = int(math.floor(h)), int(math.floor(w))
+    h1, w1 = min(h0 + 1, H - 1), min(w0 + 1, W - 1)
+    dh, dw = h - h0, w - w0
+    return (plane[:, h0, w0] * (1 - dh) * (1 - dw) + plane[:, h0, w1] * (1 - dh) * dw +
+            plane[:, h1, w0] * dh * (1 - dw) + plane[:, h1, w1] * dh * dw)
+
+
+@register('_contrib_DeformablePSROIPooling', 'DeformablePSROIPooling', inputs=('data', 'rois', 'trans'),
+          defaults={'spatial_scale': 1.0, 'output_dim': 1, 'group_size': 1, 'pooled_size': 1, 'part_size': 0,
+                    'sample_per_part': 1, 'trans_std': 0.0, 'no_trans': False})
+def deformable_psroi_pooling(data, rois, trans=None, spatial_scale=1.0, output_dim=1, group_size=1, pooled_size=1,
+                             part_size=0, sample_per_part=1, trans_std=0.0, no_trans=False):
+    """Position-sensitive ROI pooling whose bins are shifted by learned normalised offsets and sampled bilinearly
+    (deformable_psroi_pooling.cu:45-140)."""
+    P, G, S = int(pooled_size), int(group_size), int(sample_per_part)
+    part = int(part_size) or P
+    no_trans = bool(no_trans) or trans is None
+    N, C, H, W = data.shape
+    D = int(output_dim)
+    ncls = 1 if no_trans else trans.shape[1] // 2
+    per_cls = D if no_trans else D // ncls
+    x = data.float()
+    out = x.new_zeros((rois.shape[0], D, P, P))
+    r_cpu = rois.detach().float().cpu()
+    t_cpu = None if no_trans else trans.detach().float().cpu()
+    ctop = torch.arange(D, device=data.device)
+    cls_of = (ctop // per_cls).cpu()
+    for n in range(rois.shape[0]):
+        b = int(r_cpu[n, 0])
+        x1 = round(float(r_cpu[n, 1])) * spatial_scale - 0.5
+        y1 = round(float(r_cpu[n, 2])) * spatial_scale - 0.5
+        x2 = (round(float(r_cpu[n, 3])) + 1.0) * spatial_scale - 0.5
+        y2 = (round(float(r_cpu[n, 4])) + 1.0) * spatial_scale - 0.5
+        rw, rh = max(x2 - x1, 0.1), max(y2 - y1, 0.1)
+        bh, bw = rh / P, rw / P
+        sh, sw = bh / S, bw / S
+        for ph in range(P):
+            gh = min(max(int(math.floor(ph * G / P)), 0), G - 1)
+            p_h = int(math.floor(ph / P * part))
+            for pw in range(P):
+                gw = min(max(int(math.floor(pw * G / P)), 0), G - 1)
+                p_w = int(math.floor(pw / P * part))
+                chan = (ctop * G + gh) * G + gw
+                for cls in range(ncls):
+                    sel = (cls_of == cls).nonzero().reshape(-1).to(data.device)
+                    if sel.numel() == 0:
+                        continue
+                    tx = 0.0 if no_trans else float(t_cpu[n, cls * 2, p_h, p_w]) * trans_std
+                    ty = 0.0 if no_trans else float(t_cpu[n, cls * 2 + 1, p_h, p_w]) * trans_std
+                    ws = pw * bw + x1 + tx * rw
+                    hs = ph * bh + y1 + ty * rh
+                    total, cnt = 0.0, 0
+                    for ih in range(S):
+                        for iw in range(S):
+                            w_, h_ = ws + iw * sw, hs + ih * sh
+                            if w_ < -0.5 or w_ > W - 0.5 or h_ < -0.5 or h_ > H - 0.5:
+                                continue
+                            w_, h_ = min(max(w_, 0.0), W - 1.0), min(max(h_, 0.0), H - 1.0)
+                            total = total + _bilinear_at(x[b, chan[sel]], h_, w_)
+                            cnt += 1
+                    if cnt:
+                        out[n, sel, ph, pw] = total / cnt
+    return out.to(data.dtype)
+
+
+@register('_contrib_DeformableConvolution', 'DeformableConvolution', inputs=('data', 'offset', 'weight', 'bias'),
+          defaults={'kernel': (), 'stride': (), 'dilate': (), 'pad': (), 'num_filter': 0, 'num_group': 1,
+                    'num_deformable_group': 1, 'workspace': 1024, 'no_bias': False, 'layout': None})
+def deformable_convolution(data, offset, weight, bias=None, kernel=(), stride=(), dilate=(), pad=(), num_filter=0,
+                           num_group=1, num_deformable_group=1, workspace=1024, no_bias=False, layout=None):
+    """Convolution whose sampling grid is displaced by per-position (dy, dx) offsets, bilinear sampling
+    (deformable_im2col.cuh + GEMM in the reference; the library's deformable convolution here)."""
+    from torchvision.ops import deform_conv2d
+    stride = tuple(stride) or (1, 1)
+    dilate = tuple(dilate) or (1, 1)
+    pad = tuple(pad) or (0, 0)
+    b = None if no_bias else bias
+    return deform_conv2d(data, offset.to(data.dtype), weight, b, stride, pad, dilate)
+
+
+@register('_contrib_ModulatedDeformableConvolution', 'ModulatedDeformableConvolution',
+          inputs=('data', 'offset', 'mask', 'weight', 'bias'),
+          defaults={'kernel': (), 'stride': (), 'dilate': (), 'pad': (), 'num_filter': 0, 'num_group': 1,
+                    'num_deformable_group': 1, 'workspace': 1024, 'no_bias': False, 'im2col_step': 64, 'layout': None})
+def modulated_deformable_convolution(data, offset, mask, weight, bias=None, kernel=(), stride=(), dilate=(), pad=(),
+                                     num_filter=0, num_group=1, num_deformable_group=1, workspace=1024, no_bias=False,
+                                     im2col_step=64, layout=None):
+    """Deformable convolution v2: every sampled value is additionally scaled by a learned mask
+    (modulated_deformable_im2col.cuh)."""
+    from torchvision.ops import deform_conv2d
+    stride = tuple(stride) or (1, 1)
+    dilate = tuple(dilate) or (1, 1)
+    pad = tuple(pad) or (0, 0)
+    b = None if no_bias else bias
+    return deform_conv2d(data, offset.to(data.dtype), weight, b, stride, pad, dilate, mask.to(data.dtype))
+
+
+@register('_contrib_mrcnn_mask_target', 'mrcnn_mask_target', inputs=('rois', 'gt_masks', 'matches', 'cls_targets'), nout=2,
+          defaults={'num_rois': 0, 'num_classes': 0, 'mask_size': (14, 14), 'sample_ratio': 2, 'aligned': False})
+def mrcnn_mask_target(rois, gt_masks, matches, cls_targets, num_rois=0, num_classes=0, mask_size=(14, 14), sample_ratio=2,
+                      aligned=False):
+    """Mask R-CNN training targets: the matched ground-truth mask of every ROI resampled to `mask_size` with ROIAlign,
+    repeated over classes, and a one-hot class weight of the same shape (mrcnn_mask_target.cu)."""
+    from torchvision.ops import roi_align as tv_roi_align
+    B, N = rois.shape[0], rois.shape[1]
+    C = int(num_classes)
+    ms = tuple(mask_size) if not isinstance(mask_size, int) else (mask_size, mask_size)
+    targets = []
+    for b in range(B):
+        m = gt_masks[b].float()[matches[b].long()][:, None]                      # (N, 1, H, W)
+        boxes = torch.cat([torch.arange(N, device=rois.device, dtype=torch.float32)[:, None], rois[b].float()], 1)
+        t = tv_roi_align(m, boxes, ms, 1.0, int(sample_ratio), bool(aligned))    # (N, 1, ms, ms)
+        targets.append(t[:, 0])
+    t = torch.stack(targets, 0)[:, :, None].expand(B, N, C, ms[0], ms[1]).contiguous()
+    cls = (cls_targets.long()[:, :, None] == torch.arange(C, device=rois.device)[None, None, :])
+    w = cls[:, :, :, None, None].expand(B, N, C, ms[0], ms[1]).to(t.dtype).contiguous()
+    return t.to(gt_masks.dtype), w.to(gt_masks.dtype)

@@ -116,12 +116,15 @@ def _conv_bn_step(x_np, w_np, env):
 def test_convolution_operator_feeds_batchnorm_statistics():
     """Convolution -> BatchNorm through the operator registry: the kernels' epilogue statistics give the same
     normalisation, running averages and gradients as the library convolution followed by a separate reduction."""
-    from mxnet_b200.ops.cuda import gemm_ops
+    from mxnet_b200.ops.cuda import gemm_ops, norm_ops
     rng = np.random.RandomState(0)
     x = rng.randn(4, 12, 12, 64).astype('float32')
     w = (rng.randn(128, 3, 3, 64) / 24).astype('float32')
+    hits = norm_ops.hint_hits
     own = _conv_bn_step(x, w, 'fwd,dgrad,wgrad')
     gemm_ops.check_errors()
+    assert norm_ops.hint_hits == hits + 1          # the BatchNorm took its statistics from the convolution epilogue
     lib = _conv_bn_step(x, w, '0')
+    assert norm_ops.hint_hits == hits + 1
     for a, b, tol in zip(own, lib, (2e-2, 5e-2, 5e-1, 5e-1, 1e-3, 1e-3)):
         np.testing.assert_allclose(a, b, rtol=2e-2, atol=tol)
