@@ -48,6 +48,9 @@ def main():
     ap.add_argument('--iters', type=int, default=10)
     ap.add_argument('--dtype', default='float16')
     ap.add_argument('--layers', default='')
+    ap.add_argument('--dirs', default='fwd,dgrad,wgrad')
+    ap.add_argument('--profile', action='store_true', help='print the cycle accounting of CTA 0 of the in-tree kernel')
+    ap.add_argument('--no-stats', action='store_true', help='forward without the BatchNorm statistics epilogue')
     args = ap.parse_args()
     from mxnet_b200.ops.cuda import conv_ops, gemm_ops
     dtype = getattr(torch, args.dtype)
@@ -65,7 +68,7 @@ def main():
         xc, wc, dyc = x.permute(0, 3, 1, 2), w.permute(0, 3, 1, 2), dy.permute(0, 3, 1, 2)
         flops = 2.0 * args.batch * hw * hw * cin * cout * r * r
         runs = {
-            'fwd': (lambda: conv_ops.conv_forward(x, w, None, None, pad, (1, 1), False, True),
+            'fwd': (lambda: conv_ops.conv_forward(x, w, None, None, pad, (1, 1), False, not args.no_stats),
                     lambda: torch.nn.functional.conv2d(xc, wc, None, 1, pad, 1)),
             'dgrad': (lambda: conv_ops.conv_dgrad(dy, w, (hw, hw), pad, (1, 1)),
                       lambda: torch.ops.aten.convolution_backward(dyc, xc, wc, None, [1, 1], list(pad), [1, 1], False, [0, 0],
@@ -75,6 +78,19 @@ def main():
                                                                   1, [False, True, False])),
         }
         for d, (own, libf) in runs.items():
+            if d not in args.dirs.split(','):
+                continue
+            if args.profile and d != 'wgrad':
+                import ctypes
+                from mxnet_b200.ops import cuda as _cuda
+                buf = torch.zeros(16, dtype=torch.int64, device=dev)
+                _cuda.lib().mxb_conv_set_profile(ctypes.c_void_p(buf.data_ptr()))
+                own()
+                torch.cuda.synchronize()
+                _cuda.lib().mxb_conv_set_profile(None)
+                names = ['prod_wait_stage', 'prod_total', 'ksteps', 'mma_wait_operands', 'mma_wait_accumulator', 'mma_total',
+                         'tiles', 'epi_wait', 'epi_total']
+                print(json.dumps({'layer': name, 'dir': d, 'cycles_cta0': dict(zip(names, buf.tolist()))}), flush=True)
             t_own = timed(own, flush, args.iters)
             t_lib = timed(libf, flush, args.iters)
             gemm_ops.check_errors()

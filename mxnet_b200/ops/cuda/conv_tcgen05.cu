@@ -18,6 +18,8 @@
 // follows) so that the normalisation does not have to read the tensor again to reduce it.
 //
 // Roles, ring, TMEM double buffering and the bounded waits are those of the GEMM kernel (gemm_tcgen05.cu).
+#include <cstdlib>
+
 #include "tcgen05.cuh"
 
 namespace mxb {
@@ -61,9 +63,13 @@ template <typename T, int BN>
 __global__ void __launch_bounds__(kIgemmThreads, 1)
 conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, T* __restrict__ Y,
                   const T* __restrict__ bias, const T* __restrict__ res, float* __restrict__ stat_partial,
-                  const ConvGeom g, int* __restrict__ error_flag) {
+                  const ConvGeom g, int* __restrict__ error_flag, long long* __restrict__ prof) {
   using Cfg = ConvCfg<BN>;
   constexpr uint32_t B_BYTES = Cfg::B_BYTES;
+  // optional cycle accounting of CTA 0 (prof != nullptr): where each role spends its time
+  const bool profiling = prof != nullptr && blockIdx.x == 0;
+  long long pc[4] = {0, 0, 0, 0};
+  const long long t_begin = clock64();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int kchunks = (g.KC + CBK - 1) / CBK;
@@ -152,7 +158,9 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             for (int kc = 0; kc < kchunks; ++kc, ++it) {
               const int st = it % STAGES;
               const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+              const long long tw0 = clock64();
               if (!mbar_wait(&empty[st], phase ^ 1u)) { *abort_flag = 1; ok = false; break; }
+              pc[0] += clock64() - tw0;
               mbar_expect_tx(&full[st], g.stationary ? CA_BYTES : CA_BYTES + B_BYTES);
               tma_load_4d(sA + st * CA_BYTES, &map_x, kc * CBK, iw, ih, n0, &full[st]);
               if (!g.stationary) {
@@ -169,6 +177,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           }
         }
       }
+      if (profiling) { prof[0] = pc[0]; prof[1] = clock64() - t_begin; prof[2] = it; }
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -184,14 +193,18 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           *w_consumed = wloads;
           cur_tn = tile_n;
         }
+        const long long ta0 = clock64();
         if (!mbar_wait(&acc_empty[buf], (((uint32_t)t >> 1) & 1u) ^ 1u)) { *abort_flag = 1; break; }
+        pc[1] += clock64() - ta0;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
         bool ok = true;
         for (int kt = 0; kt < num_k; ++kt, ++it) {
           const int s = it % STAGES;
           const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+          const long long tf0 = clock64();
           if (!mbar_wait(&full[s], phase)) { *abort_flag = 1; ok = false; break; }
+          pc[0] += clock64() - tf0;
           *consumed_it = it + 1;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_addr = smem_u32(sA + s * CA_BYTES);
@@ -210,6 +223,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           if (next < num_tiles && next / tiles_m != tile_n) umma_commit(w_free);   // last tile of this column tile
         }
       }
+      if (profiling) { prof[3] = pc[0]; prof[4] = pc[1]; prof[5] = clock64() - t_begin; prof[6] = t; }
     }
   } else {
     // Epilogue warps 2..9.  A warp may only read the TMEM lanes of its quarter (warp index modulo 4); the two warps of
@@ -223,9 +237,11 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
       const int buf = t & 1;
+      const long long te0 = clock64();
       const bool ready = mbar_wait(&acc_full[buf], ((uint32_t)t >> 1) & 1u);
       if (!ready) *abort_flag = 1;
       if (!ready || *abort_flag) break;
+      pc[0] += clock64() - te0;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (stat_partial != nullptr && stat_tile_n != tile_n) {
         if (stat_tile_n >= 0) {
@@ -343,6 +359,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
+    if (profiling && warp == 2 && lane == 0) { prof[7] = pc[0]; prof[8] = clock64() - t_begin; }
     if (stat_partial != nullptr && stat_tile_n >= 0) {
       __syncwarp();
       float* prow = stat_partial + (size_t)(blockIdx.x * 4 + q) * 2 * g.NC;
@@ -414,6 +431,9 @@ static int make_map_filter(CUtensorMap* map, const void* base, int bf16, int Cou
   return rc == CUDA_SUCCESS ? 0 : -11;
 }
 
+// Device buffer of 16 cycle counters filled by CTA 0 of the next launches (null = off), see mxb_conv_set_profile.
+static long long* g_conv_prof = nullptr;
+
 template <typename T, int BN>
 static int launch_conv(const CUtensorMap& mx, const CUtensorMap& mw, void* Y, const void* bias, const void* res, float* stats,
                        ConvGeom g, int* error_flag, cudaStream_t st) {
@@ -429,7 +449,11 @@ static int launch_conv(const CUtensorMap& mx, const CUtensorMap& mw, void* Y, co
   const int num_k = g.R * g.S * ((g.KC + CBK - 1) / CBK);
   const long wbytes = (long)num_k * Cfg::B_BYTES;
   const long a_stages = ((long)Cfg::OPERAND_BUDGET - wbytes) / CA_BYTES;
-  if (a_stages >= 4) {
+  static const bool allow_resident = [] {
+    const char* e = getenv("MXNET_B200_CONV_RESIDENT_WEIGHTS");
+    return !(e && e[0] == '0');
+  }();
+  if (allow_resident && a_stages >= 4) {
     g.stationary = 1;
     g.stages = a_stages > kConvMaxStages ? kConvMaxStages : (int)a_stages;
   } else {
@@ -447,7 +471,7 @@ static int launch_conv(const CUtensorMap& mx, const CUtensorMap& mw, void* Y, co
     if (rc != cudaSuccess) return (int)rc;
   }
   conv_igemm_kernel<T, BN><<<grid, kIgemmThreads, smem_bytes, st>>>(mx, mw, (T*)Y, (const T*)bias, (const T*)res, stats, g,
-                                                                    error_flag);
+                                                                    error_flag, g_conv_prof);
   return (int)cudaGetLastError();
 }
 
@@ -493,6 +517,12 @@ static int conv_run(int dtype, const void* in, const void* w, void* out, const v
 }  // namespace mxb
 
 using namespace mxb;
+
+// Cycle accounting of CTA 0 for the forward / data-gradient kernel: `buf` (16 int64 on the device, or null to switch it
+// off) receives [0] producer cycles waiting for a free stage, [1] producer total, [2] k-steps issued, [3] MMA cycles
+// waiting for operands, [4] MMA cycles waiting for a drained accumulator, [5] MMA total, [6] tiles, [7] first
+// epilogue warp cycles waiting for an accumulator, [8] its total.
+MXB_EXPORT void mxb_conv_set_profile(long long* buf) { g_conv_prof = buf; }
 
 // Rows of the statistics buffer written by mxb_conv_forward: [rows][2][Cout] floats (sum, sum of squares).
 MXB_EXPORT int mxb_conv_stat_rows() { return sm_count() * 4; }

@@ -131,13 +131,13 @@ def test_avgpool_nhwc(shape, k, s, p, ceil, include, dtype):
     torch.manual_seed(5)
     x = torch.randn(*shape, device=_dev()).to(dtype).requires_grad_(True)
     y = ew.avg_pool2d_nhwc(x, (k, k), (s, s), (p, p), ceil, include)
-    xr = x.detach().float().requires_grad_(True)
+    xr = x.detach().float().cpu().requires_grad_(True)          # fp32 reference evaluated on the host
     ref = F.avg_pool2d(xr.permute(0, 3, 1, 2), k, s, p, ceil, include).permute(0, 2, 3, 1)
     assert y.shape == ref.shape
     _close(y, ref, *_tol(dtype))
     dy = torch.randn_like(y)
     y.backward(dy)
-    ref.backward(dy.float())
+    ref.backward(dy.float().cpu())
     _close(x.grad, xr.grad, _tol(dtype)[0] * 2, _tol(dtype)[1] * 4)
 
 
