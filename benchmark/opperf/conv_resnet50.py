@@ -89,7 +89,8 @@ def main():
                 torch.cuda.synchronize()
                 _cuda.lib().mxb_conv_set_profile(None)
                 names = ['prod_wait_stage', 'prod_total', 'ksteps', 'mma_wait_operands', 'mma_wait_accumulator', 'mma_total',
-                         'tiles', 'epi_wait', 'epi_total']
+                         'tiles', 'epi_wait', 'epi_total', 'prod_expect_tx', 'prod_tma_issue', 'mma_issue', 'mma_commit',
+                         'prod_loop', 'mma_loop']
                 print(json.dumps({'layer': name, 'dir': d, 'cycles_cta0': dict(zip(names, buf.tolist()))}), flush=True)
             t_own = timed(own, flush, args.iters)
             t_lib = timed(libf, flush, args.iters)

@@ -80,6 +80,25 @@ __device__ __forceinline__ float block_max(float v, float* red) {
   return red[0];
 }
 
+// Division by a run-time constant without the hardware's long division sequence: q = (umulhi(m, x) + x) >> s, exact for
+// x < 2^31 (round-up method); the host prepares (m, s) once per launch.
+struct FastDiv {
+  uint32_t d, m, s;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+  FastDiv f;
+  f.d = d < 1 ? 1 : d;
+  f.s = 0;
+  while ((1ull << f.s) < f.d) ++f.s;
+  f.m = (uint32_t)((((1ull << 32) * ((1ull << f.s) - f.d)) / f.d) + 1);
+  return f;
+}
+__device__ __forceinline__ uint32_t fd_div(uint32_t x, const FastDiv& f) { return (__umulhi(f.m, x) + x) >> f.s; }
+__device__ __forceinline__ void fd_divmod(uint32_t x, const FastDiv& f, uint32_t* q, uint32_t* r) {
+  *q = fd_div(x, f);
+  *r = x - *q * f.d;
+}
+
 inline int sm_count() {
   static int n = 0;
   if (!n) {

@@ -30,7 +30,7 @@ constexpr int kIgemmThreads = 320;         // forward / data-gradient kernel: pr
 constexpr uint32_t CA_BYTES = CBM * CBK * 2;
 constexpr int kConvMaxStages = 8;
 constexpr uint32_t kSmemLimit = 232448;    // 227 KB per CTA
-constexpr uint32_t kScrBytes = 8 * 32 * 17 * 4;   // per epilogue warp: 32 rows x 16 columns of floats, padded
+constexpr uint32_t kStgBytes = 8 * 2048;           // per epilogue warp: 32 rows x 64 bytes staged for the TMA store
 
 template <int BN> struct ConvCfg {
   static constexpr uint32_t B_BYTES = BN * CBK * 2;
@@ -38,7 +38,7 @@ template <int BN> struct ConvCfg {
   static constexpr uint32_t STAT_BYTES = 4 * 2 * BN * 4;     // [TMEM lane quarter][sum | sumsq][BN] floats
   static constexpr uint32_t SMEM_BYTES = STAGES * (CA_BYTES + B_BYTES) + STAT_BYTES + 1024 /*alignment*/ + 512 /*barriers*/;
   // forward / data-gradient kernel: everything except the operand buffers
-  static constexpr uint32_t FIXED_BYTES = STAT_BYTES + kScrBytes + 512;
+  static constexpr uint32_t FIXED_BYTES = STAT_BYTES + kStgBytes + 512;
   static constexpr uint32_t OPERAND_BUDGET = kSmemLimit - 1024 - FIXED_BYTES;
 };
 
@@ -55,21 +55,48 @@ struct ConvGeom {
   int bf16;
   int stages;                            // depth of the operand ring
   int stationary;                        // 1: all weight slices of a column tile stay in shared memory, the ring holds A only
+  int log_bw, log_bh;                    // the pixel box sides are powers of two
+  FastDiv fd_tiles_m, fd_tiles_w, fd_tiles_h;
 };
 
+// tile index -> (column tile, first pixel of the row tile), without hardware division
+struct TilePos {
+  int tile_n, w0, h0, n0;
+};
+__device__ __forceinline__ TilePos tile_pos(int tile, const ConvGeom& g) {
+  uint32_t tn, tm, rest, tw, tnb, th;
+  fd_divmod((uint32_t)tile, g.fd_tiles_m, &tn, &tm);
+  fd_divmod(tm, g.fd_tiles_w, &rest, &tw);
+  fd_divmod(rest, g.fd_tiles_h, &tnb, &th);
+  TilePos p;
+  p.tile_n = (int)tn;
+  p.w0 = (int)tw << g.log_bw;
+  p.h0 = (int)th << g.log_bh;
+  p.n0 = (int)tnb * g.bnb;
+  return p;
+}
+
 // Shared-memory carve-up (after 1024-byte alignment):
-//   [A ring: stages x 16 KB][B: ring of stages x B_BYTES, or taps*kchunks resident slices][stat][transpose scratch][barriers]
+//   [A ring: stages x 16 KB][B: ring of stages x B_BYTES, or taps*kchunks resident slices][store staging][stat][barriers]
 template <typename T, int BN>
 __global__ void __launch_bounds__(kIgemmThreads, 1)
-conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, T* __restrict__ Y,
-                  const T* __restrict__ bias, const T* __restrict__ res, float* __restrict__ stat_partial,
+conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                  const __grid_constant__ CUtensorMap map_y, const T* __restrict__ bias, const T* __restrict__ res, float* __restrict__ stat_partial,
                   const ConvGeom g, int* __restrict__ error_flag, long long* __restrict__ prof) {
   using Cfg = ConvCfg<BN>;
   constexpr uint32_t B_BYTES = Cfg::B_BYTES;
   // optional cycle accounting of CTA 0 (prof != nullptr): where each role spends its time
   const bool profiling = prof != nullptr && blockIdx.x == 0;
-  long long pc[4] = {0, 0, 0, 0};
+  long long pc[6] = {0, 0, 0, 0, 0, 0};
   const long long t_begin = clock64();
+  long long t_last = t_begin;
+  // attribute the cycles since the previous mark to bucket b (a full partition of a role's time)
+#define MXB_PROF_MARK(b)                 \
+  if (profiling) {                       \
+    const long long t_now = clock64();   \
+    pc[b] += t_now - t_last;             \
+    t_last = t_now;                      \
+  }
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int kchunks = (g.KC + CBK - 1) / CBK;
@@ -78,9 +105,9 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   const uint32_t b_region = (g.stationary ? (uint32_t)num_k : (uint32_t)STAGES) * B_BYTES;
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * CA_BYTES;
-  float* sstat = reinterpret_cast<float*>(sB + b_region);
-  float* sscr = reinterpret_cast<float*>(sB + b_region + Cfg::STAT_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sB + b_region + Cfg::STAT_BYTES + kScrBytes);
+  uint8_t* sstg = sB + b_region;                                   // 1024-byte aligned: both regions before it are
+  float* sstat = reinterpret_cast<float*>(sB + b_region + kStgBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sB + b_region + kStgBytes + Cfg::STAT_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + kConvMaxStages;
   uint64_t* acc_full = bars + 2 * kConvMaxStages;
@@ -122,20 +149,25 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
+  // Producer and MMA warps: the whole warp walks the loops (waits, ring counters, descriptor arithmetic), so every value
+  // is warp-uniform, and lane 0 alone issues the TMA / tcgen05 instructions.  Ring position and parity are running
+  // counters (no divisions) and descriptors advance by additions: the per-k-step instruction count of these two warps
+  // bounds narrow tiles.
   if (warp == 0) {
-    if (lane == 0) {
-      int it = 0, cur_tn = -1, wloads = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
-        const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
-        const int w0 = (tile_m % g.tiles_w) * g.bw;
-        const int h0 = ((tile_m / g.tiles_w) % g.tiles_h) * g.bh;
-        const int n0 = (tile_m / (g.tiles_w * g.tiles_h)) * g.bnb;
-        bool ok = true;
-        if (g.stationary && tile_n != cur_tn) {
-          // a new column tile: (re)load all of its weight slices, once the MMAs of the previous column tile are done
-          if (wloads > 0 && !mbar_wait(w_free, (uint32_t)(wloads - 1) & 1u)) { *abort_flag = 1; break; }
+    int it = 0, st = 0, cur_tn = -1, wloads = 0;
+    uint32_t ph = 0;
+    const uint32_t stage_bytes = g.stationary ? CA_BYTES : CA_BYTES + B_BYTES;
+    const int taps = g.R * g.S;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok && !*abort_flag; tile += gridDim.x) {
+      const TilePos tp = tile_pos(tile, g);
+      const int tile_n = tp.tile_n, w0 = tp.w0, h0 = tp.h0, n0 = tp.n0;
+      if (g.stationary && tile_n != cur_tn) {
+        // a new column tile: (re)load all of its weight slices, once the MMAs of the previous column tile are done
+        if (wloads > 0 && !mbar_wait_warp(w_free, (uint32_t)(wloads - 1) & 1u)) { *abort_flag = 1; break; }
+        if (lane == 0) {
           mbar_expect_tx(w_full, (uint32_t)num_k * B_BYTES);
-          for (int tap = 0; tap < g.R * g.S; ++tap) {
+          for (int tap = 0; tap < taps; ++tap) {
             for (int kc = 0; kc < kchunks; ++kc) {
               uint8_t* dst = sB + (size_t)(tap * kchunks + kc) * B_BYTES;
               if (!g.b_mn) {
@@ -147,21 +179,24 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
               }
             }
           }
-          ++wloads;
-          *w_issued = wloads;
-          cur_tn = tile_n;
         }
-        for (int r = 0; r < g.R && ok; ++r) {
-          for (int s = 0; s < g.S && ok; ++s) {
-            const int tap = r * g.S + s;
-            const int ih = h0 + g.off_h + r * g.step_h, iw = w0 + g.off_w + s * g.step_w;
-            for (int kc = 0; kc < kchunks; ++kc, ++it) {
-              const int st = it % STAGES;
-              const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
-              const long long tw0 = clock64();
-              if (!mbar_wait(&empty[st], phase ^ 1u)) { *abort_flag = 1; ok = false; break; }
-              pc[0] += clock64() - tw0;
-              mbar_expect_tx(&full[st], g.stationary ? CA_BYTES : CA_BYTES + B_BYTES);
+        ++wloads;
+        if (lane == 0) *w_issued = wloads;
+        cur_tn = tile_n;
+        __syncwarp();
+      }
+      int tap = 0;
+      for (int r = 0; r < g.R && ok; ++r) {
+        const int ih = h0 + g.off_h + r * g.step_h;
+        for (int s = 0; s < g.S && ok; ++s, ++tap) {
+          const int iw = w0 + g.off_w + s * g.step_w;
+          for (int kc = 0; kc < kchunks; ++kc) {
+            MXB_PROF_MARK(4)                                       // loop overhead since the previous k-step
+            if (!mbar_wait_warp(&empty[st], ph ^ 1u)) { *abort_flag = 1; ok = false; break; }
+            MXB_PROF_MARK(0)                                       // waiting for a free stage
+            if (lane == 0) {
+              mbar_expect_tx(&full[st], stage_bytes);
+              MXB_PROF_MARK(2)
               tma_load_4d(sA + st * CA_BYTES, &map_x, kc * CBK, iw, ih, n0, &full[st]);
               if (!g.stationary) {
                 if (!g.b_mn) {
@@ -172,58 +207,74 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     tma_load_3d(sB + st * B_BYTES + c * kMnChunkBytes, &map_w, tile_n * BN + c * 64, tap, kc * CBK, &full[st]);
                 }
               }
-              *issued_it = it + 1;
+              MXB_PROF_MARK(3)
             }
+            __syncwarp();
+            ++it;
+            if (++st == STAGES) { st = 0; ph ^= 1u; }
           }
         }
       }
-      if (profiling) { prof[0] = pc[0]; prof[1] = clock64() - t_begin; prof[2] = it; }
+    }
+    if (lane == 0) {
+      *issued_it = it;
+      if (profiling) { prof[0] = pc[0]; prof[1] = clock64() - t_begin; prof[2] = it; prof[9] = pc[2]; prof[10] = pc[3]; prof[13] = pc[4]; }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc(g.bf16, BN, 0, g.b_mn);
-      const uint64_t b_step = g.b_mn ? (16 * 128) >> 4 : 2;
-      int it = 0, t = 0, cur_tn = -1, wloads = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++t) {
-        const int tile_n = tile / tiles_m;
-        const int buf = t & 1;
-        if (g.stationary && tile_n != cur_tn) {
-          if (!mbar_wait(w_full, (uint32_t)wloads & 1u)) { *abort_flag = 1; break; }
-          ++wloads;
-          *w_consumed = wloads;
-          cur_tn = tile_n;
-        }
-        const long long ta0 = clock64();
-        if (!mbar_wait(&acc_empty[buf], (((uint32_t)t >> 1) & 1u) ^ 1u)) { *abort_flag = 1; break; }
-        pc[1] += clock64() - ta0;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-        bool ok = true;
-        for (int kt = 0; kt < num_k; ++kt, ++it) {
-          const int s = it % STAGES;
-          const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
-          const long long tf0 = clock64();
-          if (!mbar_wait(&full[s], phase)) { *abort_flag = 1; ok = false; break; }
-          pc[0] += clock64() - tf0;
-          *consumed_it = it + 1;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_u32(sA + s * CA_BYTES);
-          const uint32_t b_addr = smem_u32(sB + (size_t)(g.stationary ? kt : s) * B_BYTES);
-          const uint64_t adesc = make_desc(a_addr);
-          const uint64_t bdesc = g.b_mn ? make_desc_mn(b_addr) : make_desc(b_addr);
+    const uint32_t idesc = make_idesc(g.bf16, BN, 0, g.b_mn);
+    const uint64_t b_step = g.b_mn ? (16 * 128) >> 4 : 2;
+    // descriptors of stage 0 / slice 0; the start-address field (16-byte units, 14 bits) takes plain additions
+    const uint64_t adesc0 = make_desc(smem_u32(sA));
+    const uint64_t bdesc0 = g.b_mn ? make_desc_mn(smem_u32(sB)) : make_desc(smem_u32(sB));
+    int it = 0, st = 0, t = 0, cur_tn = -1, wloads = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok && !*abort_flag; tile += gridDim.x, ++t) {
+      const int tile_n = (int)fd_div((uint32_t)tile, g.fd_tiles_m);
+      const int buf = t & 1;
+      if (g.stationary && tile_n != cur_tn) {
+        if (!mbar_wait_warp(w_full, (uint32_t)wloads & 1u)) { *abort_flag = 1; break; }
+        ++wloads;
+        if (lane == 0) *w_consumed = wloads;
+        cur_tn = tile_n;
+      }
+      MXB_PROF_MARK(4)
+      if (!mbar_wait_warp(&acc_empty[buf], (((uint32_t)t >> 1) & 1u) ^ 1u)) { *abort_flag = 1; break; }
+      MXB_PROF_MARK(1)                                             // waiting for a drained accumulator
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+      for (int kt = 0; kt < num_k; ++kt) {
+        MXB_PROF_MARK(4)                                           // loop overhead since the previous k-step
+        if (!mbar_wait_warp(&full[st], ph)) { *abort_flag = 1; ok = false; break; }
+        MXB_PROF_MARK(0)                                           // waiting for operands
+        const uint64_t adesc = adesc0 + (uint64_t)(st * (int)(CA_BYTES >> 4));
+        const uint64_t bdesc = bdesc0 + (uint64_t)((g.stationary ? kt : st) * (int)(B_BYTES >> 4));
+        if (lane == 0) {
+          umma(tmem_d, adesc, bdesc, idesc, kt > 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < CBK / CUMMA_K; ++k)
-            umma(tmem_d, adesc + 2 * (uint64_t)k, bdesc + b_step * (uint64_t)k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
-          umma_commit(&empty[s]);
+          for (int k = 1; k < CBK / CUMMA_K; ++k)
+            umma(tmem_d, adesc + 2 * (uint64_t)k, bdesc + b_step * (uint64_t)k, idesc, 1u);
+          MXB_PROF_MARK(2)
+          umma_commit(&empty[st]);
+          MXB_PROF_MARK(3)
         }
-        if (!ok) break;
+        __syncwarp();
+        ++it;
+        if (++st == STAGES) { st = 0; ph ^= 1u; }
+      }
+      if (!ok) break;
+      if (lane == 0) {
         umma_commit(&acc_full[buf]);
         if (g.stationary) {
           const int next = tile + gridDim.x;
-          if (next < num_tiles && next / tiles_m != tile_n) umma_commit(w_free);   // last tile of this column tile
+          if (next < num_tiles && (int)fd_div((uint32_t)next, g.fd_tiles_m) != tile_n) umma_commit(w_free);   // last tile of this column tile
         }
       }
-      if (profiling) { prof[3] = pc[0]; prof[4] = pc[1]; prof[5] = clock64() - t_begin; prof[6] = t; }
+      __syncwarp();
+    }
+    if (lane == 0) {
+      *consumed_it = it;
+      if (profiling) { prof[3] = pc[0]; prof[4] = pc[1]; prof[5] = clock64() - t_begin; prof[6] = t; prof[11] = pc[2]; prof[12] = pc[3]; prof[14] = pc[4]; }
     }
   } else {
     // Epilogue warps 2..9.  A warp may only read the TMEM lanes of its quarter (warp index modulo 4); the two warps of
@@ -231,17 +282,23 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const int q = warp & 3, half = (warp - 2) >> 2;
     float* my_sum = sstat + (q * 2 + 0) * BN;
     float* my_sq = sstat + (q * 2 + 1) * BN;
-    float* scr = sscr + (warp - 2) * 32 * 17;
+    uint8_t* stg = sstg + (warp - 2) * 2048;                        // this warp's staging tile: 32 rows x 64 bytes
+    float* scr = reinterpret_cast<float*>(stg);                     // the same bytes as a 32 x 16 float transpose tile
     constexpr int HALF_COLS = BN / 2;
+    // the 32 accumulator rows of this warp are a sub-box (sbw x sbh x sbn) of the tile's pixel box
+    const int r0 = q * 32;
+    const int sub_w = r0 & (g.bw - 1), sub_h = (r0 >> g.log_bw) & (g.bh - 1), sub_n = r0 >> (g.log_bw + g.log_bh);
     int t = 0, stat_tile_n = -1;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
-      const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+      const TilePos tp = tile_pos(tile, g);
+      const int tile_n = tp.tile_n;
       const int buf = t & 1;
-      const long long te0 = clock64();
+      long long te0 = 0;
+      if (profiling) te0 = clock64();
       const bool ready = mbar_wait(&acc_full[buf], ((uint32_t)t >> 1) & 1u);
       if (!ready) *abort_flag = 1;
       if (!ready || *abort_flag) break;
-      pc[0] += clock64() - te0;
+      if (profiling) pc[0] += clock64() - te0;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (stat_partial != nullptr && stat_tile_n != tile_n) {
         if (stat_tile_n >= 0) {
@@ -256,10 +313,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         stat_tile_n = tile_n;
       }
       const int i = q * 32 + lane;
-      const int wl = i % g.bw, hl = (i / g.bw) % g.bh, nl = i / (g.bw * g.bh);
-      const int ow = (tile_m % g.tiles_w) * g.bw + wl;
-      const int oh = ((tile_m / g.tiles_w) % g.tiles_h) * g.bh + hl;
-      const int on = (tile_m / (g.tiles_w * g.tiles_h)) * g.bnb + nl;
+      const int wl = i & (g.bw - 1), hl = (i >> g.log_bw) & (g.bh - 1), nl = i >> (g.log_bw + g.log_bh);
+      const int ow = tp.w0 + wl, oh = tp.h0 + hl, on = tp.n0 + nl;
       const bool row_ok = ow < g.Wo && oh < g.Ho && on < g.N;
       const size_t pix = ((size_t)on * g.Ho + oh) * g.Wo + ow;
       const bool bias_vec = bias != nullptr && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
@@ -313,36 +368,23 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         // the next 32 columns travel from TMEM while these are converted and stored
         if (c0 + 32 < (half + 1) * HALF_COLS) tmem_ld32(taddr + (uint32_t)(c0 + 32), rr);
-        if (row_ok && col0 < g.NC) {
-          T* drow = Y + pix * g.ldy + col0;
-          if (full_cols && row_vec) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              Vec16<T> o;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) o.v[j] = Cvt<T>::from_f(f[v * 8 + j]);
-              st16(drow + v * 8, o);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < g.NC) drow[j] = Cvt<T>::from_f(f[j]);
-          }
-        }
+        // the staging tile is free once the previous store of this warp has read it
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
         if (stat_partial != nullptr) {
-          // column sums over the warp's 32 rows, 16 columns at a time through a padded shared-memory tile: thread
-          // (row) writes its 16 values, then lane l adds column (l & 15) over rows 16*(l >> 4) .. +15
+          // column sums over the warp's 32 rows, 16 columns at a time through the staging bytes as a 32 x 16 float
+          // tile (column index xor-ed with the row to spread the banks): thread (row) writes its 16 values, then lane
+          // l adds column (l & 15) over rows 16*(l >> 4) .. +15
 #pragma unroll
           for (int hcol = 0; hcol < 2; ++hcol) {
-            __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) scr[lane * 17 + j] = row_ok ? f[hcol * 16 + j] : 0.f;
+            for (int j = 0; j < 16; ++j) scr[lane * 16 + (j ^ (lane & 15))] = row_ok ? f[hcol * 16 + j] : 0.f;
             __syncwarp();
             float sa = 0.f, sb = 0.f;
-            const int cc = lane & 15, r0 = (lane >> 4) * 16;
+            const int cc = lane & 15, rb = (lane >> 4) * 16;
 #pragma unroll
             for (int r = 0; r < 16; ++r) {
-              const float v = scr[(r0 + r) * 17 + cc];
+              const float v = scr[(rb + r) * 16 + (cc ^ r)];
               sa += v;
               sb = fmaf(v, v, sb);
             }
@@ -352,6 +394,23 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
               my_sum[c0 + hcol * 16 + lane] += sa;
               my_sq[c0 + hcol * 16 + lane] += sb;
             }
+            __syncwarp();
+          }
+        }
+        if (col0 < g.NC) {
+          // this row's 32 values as four 16-byte pieces in the 64-byte-swizzled layout of the store's tensor map
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            Vec16<T> o;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o.v[j] = Cvt<T>::from_f(f[v * 8 + j]);
+            st16(reinterpret_cast<T*>(stg + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)), o);
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_4d(&map_y, stg, col0, tp.w0 + sub_w, tp.h0 + sub_h, tp.n0 + sub_n);
+            tma_store_commit();
           }
         }
       }
@@ -359,6 +418,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
+    if (lane == 0) tma_store_wait_all();            // the staging tile must outlive the last store
     if (profiling && warp == 2 && lane == 0) { prof[7] = pc[0]; prof[8] = clock64() - t_begin; }
     if (stat_partial != nullptr && stat_tile_n >= 0) {
       __syncwarp();
@@ -417,6 +477,20 @@ static int make_map_nhwc(CUtensorMap* map, const void* base, int bf16, int N, in
   return rc == CUDA_SUCCESS ? 0 : -11;
 }
 
+// Output tensor [N, Ho, Wo, C] for the epilogue's stores: box {32 channels, sw, sh, sn} (32 pixels), 64-byte swizzle.
+static int make_map_store(CUtensorMap* map, const void* base, int bf16, int N, int H, int W, int C, int sw, int sh, int sn) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -10;
+  cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+  cuuint64_t strides[3] = {(cuuint64_t)C * 2, (cuuint64_t)W * C * 2, (cuuint64_t)H * W * C * 2};
+  cuuint32_t box[4] = {32, (cuuint32_t)sw, (cuuint32_t)sh, (cuuint32_t)sn};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base),
+                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : -11;
+}
+
 // Filter [Cout, taps, Cin] as a 3-D map {Cin, taps, Cout}; box {64, 1, box_co}.
 static int make_map_filter(CUtensorMap* map, const void* base, int bf16, int Cout, int taps, int Cin, int box_co) {
   EncodeTiledFn fn = encode_fn();
@@ -435,8 +509,8 @@ static int make_map_filter(CUtensorMap* map, const void* base, int bf16, int Cou
 static long long* g_conv_prof = nullptr;
 
 template <typename T, int BN>
-static int launch_conv(const CUtensorMap& mx, const CUtensorMap& mw, void* Y, const void* bias, const void* res, float* stats,
-                       ConvGeom g, int* error_flag, cudaStream_t st) {
+static int launch_conv(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my, const void* bias, const void* res,
+                       float* stats, ConvGeom g, int* error_flag, cudaStream_t st) {
   using Cfg = ConvCfg<BN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -470,7 +544,7 @@ static int launch_conv(const CUtensorMap& mx, const CUtensorMap& mw, void* Y, co
     cudaError_t rc = cudaMemsetAsync(stats, 0, (size_t)sm_count() * 4 * 2 * g.NC * sizeof(float), st);
     if (rc != cudaSuccess) return (int)rc;
   }
-  conv_igemm_kernel<T, BN><<<grid, kIgemmThreads, smem_bytes, st>>>(mx, mw, (T*)Y, (const T*)bias, (const T*)res, stats, g,
+  conv_igemm_kernel<T, BN><<<grid, kIgemmThreads, smem_bytes, st>>>(mx, mw, my, (const T*)bias, (const T*)res, stats, g,
                                                                     error_flag, g_conv_prof);
   return (int)cudaGetLastError();
 }
@@ -498,18 +572,30 @@ static int conv_run(int dtype, const void* in, const void* w, void* out, const v
   g.tiles_h = (Ho + g.bh - 1) / g.bh;
   g.tiles_nb = (N + g.bnb - 1) / g.bnb;
   g.ldy = NC; g.b_mn = b_mn; g.act = act; g.bf16 = dtype == kBF16;
+  g.log_bw = 0; g.log_bh = 0;
+  while ((1 << g.log_bw) < g.bw) ++g.log_bw;
+  while ((1 << g.log_bh) < g.bh) ++g.log_bh;
+  g.fd_tiles_m = make_fastdiv((uint32_t)(g.tiles_w * g.tiles_h * g.tiles_nb));
+  g.fd_tiles_w = make_fastdiv((uint32_t)g.tiles_w);
+  g.fd_tiles_h = make_fastdiv((uint32_t)g.tiles_h);
   const long tiles_m = (long)g.tiles_w * g.tiles_h * g.tiles_nb;
   if (tiles_m * ((NC + 63) / 64) > 0x7fffffffL) return -2;
   const int bn = conv_pick_bn(tiles_m, NC);
-  CUtensorMap mx, mw;
+  CUtensorMap mx, mw, my;
   int rc = make_map_nhwc(&mx, in, g.bf16, N, Hi, Wi, KC, g.bw, g.bh, g.bnb);
   if (rc) return rc;
   rc = make_map_filter(&mw, w, g.bf16, w_cout, R * S, w_cin, b_mn ? 64 : bn);
   if (rc) return rc;
+  // every epilogue warp stores its 32 accumulator rows: a (sw x sh x sn) sub-box of the tile's pixel box
+  const int sw = g.bw < 32 ? g.bw : 32;
+  const int sh = g.bh < 32 / sw ? g.bh : 32 / sw;
+  const int sn = 32 / (sw * sh);
+  rc = make_map_store(&my, out, g.bf16, N, Ho, Wo, NC, sw, sh, sn);
+  if (rc) return rc;
 #define MXB_CONV(T)                                                                              \
-  (bn == 256 ? launch_conv<T, 256>(mx, mw, out, bias, res, stats, g, error_flag, st)              \
-   : bn == 128 ? launch_conv<T, 128>(mx, mw, out, bias, res, stats, g, error_flag, st)            \
-               : launch_conv<T, 64>(mx, mw, out, bias, res, stats, g, error_flag, st))
+  (bn == 256 ? launch_conv<T, 256>(mx, mw, my, bias, res, stats, g, error_flag, st)               \
+   : bn == 128 ? launch_conv<T, 128>(mx, mw, my, bias, res, stats, g, error_flag, st)             \
+               : launch_conv<T, 64>(mx, mw, my, bias, res, stats, g, error_flag, st))
   return g.bf16 ? MXB_CONV(__nv_bfloat16) : MXB_CONV(__half);
 #undef MXB_CONV
 }
@@ -521,7 +607,9 @@ using namespace mxb;
 // Cycle accounting of CTA 0 for the forward / data-gradient kernel: `buf` (16 int64 on the device, or null to switch it
 // off) receives [0] producer cycles waiting for a free stage, [1] producer total, [2] k-steps issued, [3] MMA cycles
 // waiting for operands, [4] MMA cycles waiting for a drained accumulator, [5] MMA total, [6] tiles, [7] first
-// epilogue warp cycles waiting for an accumulator, [8] its total.
+// epilogue warp cycles waiting for an accumulator, [8] its total, [9] producer cycles in expect_tx, [10] in the TMA
+// instruction, [11] MMA cycles in the four tcgen05.mma, [12] in tcgen05.commit, [13] / [14] remaining loop cycles of the
+// producer / MMA warp.
 MXB_EXPORT void mxb_conv_set_profile(long long* buf) { g_conv_prof = buf; }
 
 // Rows of the statistics buffer written by mxb_conv_forward: [rows][2][Cout] floats (sum, sum of squares).
@@ -622,21 +710,20 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
 
   if (warp == 0) {
     if (lane == 0) {
-      int it = 0;
-      for (int u = blockIdx.x; u < num_units && !*abort_flag; u += gridDim.x) {
+      int it = 0, st = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < num_units && ok && !*abort_flag; u += gridDim.x) {
         const int ks = u / per_k, rest = u % per_k;
         const int tap = rest % taps, tm = (rest / taps) % tiles_m, tn = rest / (taps * tiles_m);
         const int r = tap / g.S, s = tap % g.S;
         const int dh = g.off_h + r * g.step_h, dw = g.off_w + s * g.step_w;
         const int k0 = ks * g.ksteps_per, k1 = min(total_k, k0 + g.ksteps_per);
-        bool ok = true;
-        for (int kt = k0; kt < k1; ++kt, ++it) {
-          const int w0 = (kt % g.tiles_w) * g.kw;
-          const int h0 = ((kt / g.tiles_w) % g.tiles_h) * g.kh;
-          const int n0 = (kt / (g.tiles_w * g.tiles_h)) * g.knb;
-          const int st = it % STAGES;
-          const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
-          if (!mbar_wait(&empty[st], phase ^ 1u)) { *abort_flag = 1; ok = false; break; }
+        // pixel-box position of k-step k0, then advanced incrementally (w fastest, then h, then image group)
+        int iw = k0 % g.tiles_w, ih = (k0 / g.tiles_w) % g.tiles_h, in = k0 / (g.tiles_w * g.tiles_h);
+        for (int kt = k0; kt < k1; ++kt) {
+          const int w0 = iw * g.kw, h0 = ih * g.kh, n0 = in * g.knb;
+          if (!mbar_wait(&empty[st], ph ^ 1u)) { *abort_flag = 1; ok = false; break; }
           mbar_expect_tx(&full[st], CA_BYTES + B_BYTES);
 #pragma unroll
           for (int c = 0; c < CBM / 64; ++c)
@@ -644,40 +731,47 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
 #pragma unroll
           for (int c = 0; c < BN / 64; ++c)
             tma_load_4d(sB + st * B_BYTES + c * kMnChunkBytes, &map_x, tn * BN + c * 64, w0 + dw, h0 + dh, n0, &full[st]);
-          *issued_it = it + 1;
+          ++it;
+          if (++st == STAGES) { st = 0; ph ^= 1u; }
+          if (++iw == g.tiles_w) {
+            iw = 0;
+            if (++ih == g.tiles_h) { ih = 0; ++in; }
+          }
         }
-        if (!ok) break;
       }
+      *issued_it = it;
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(g.bf16, BN, 1, 1);
       constexpr uint64_t kstep = (16 * 128) >> 4;
-      int it = 0, t = 0;
-      for (int u = blockIdx.x; u < num_units && !*abort_flag; u += gridDim.x, ++t) {
+      const uint64_t adesc0 = make_desc_mn(smem_u32(sA)), bdesc0 = make_desc_mn(smem_u32(sB));
+      int it = 0, st = 0, t = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < num_units && ok && !*abort_flag; u += gridDim.x, ++t) {
         const int ks = u / per_k;
         const int k0 = ks * g.ksteps_per, k1 = min(total_k, k0 + g.ksteps_per);
         const int buf = t & 1;
         if (!mbar_wait(&acc_empty[buf], (((uint32_t)t >> 1) & 1u) ^ 1u)) { *abort_flag = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-        bool ok = true;
-        for (int kt = k0; kt < k1; ++kt, ++it) {
-          const int s = it % STAGES;
-          const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
-          if (!mbar_wait(&full[s], phase)) { *abort_flag = 1; ok = false; break; }
-          *consumed_it = it + 1;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint64_t adesc = make_desc_mn(smem_u32(sA + s * CA_BYTES));
-          const uint64_t bdesc = make_desc_mn(smem_u32(sB + s * B_BYTES));
+        for (int kt = k0; kt < k1; ++kt) {
+          if (!mbar_wait(&full[st], ph)) { *abort_flag = 1; ok = false; break; }
+          const uint64_t adesc = adesc0 + (uint64_t)(st * (int)(CA_BYTES >> 4));
+          const uint64_t bdesc = bdesc0 + (uint64_t)(st * (int)(B_BYTES >> 4));
+          umma(tmem_d, adesc, bdesc, idesc, kt > k0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < CBK / CUMMA_K; ++k)
-            umma(tmem_d, adesc + kstep * (uint64_t)k, bdesc + kstep * (uint64_t)k, idesc, (kt > k0 || k > 0) ? 1u : 0u);
-          umma_commit(&empty[s]);
+          for (int k = 1; k < CBK / CUMMA_K; ++k)
+            umma(tmem_d, adesc + kstep * (uint64_t)k, bdesc + kstep * (uint64_t)k, idesc, 1u);
+          umma_commit(&empty[st]);
+          ++it;
+          if (++st == STAGES) { st = 0; ph ^= 1u; }
         }
         if (!ok) break;
         umma_commit(&acc_full[buf]);
       }
+      *consumed_it = it;
     }
   } else {
     const int q = warp & 3;

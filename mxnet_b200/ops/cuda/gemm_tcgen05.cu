@@ -92,33 +92,38 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   // Tile order: consecutive CTAs take consecutive row tiles of the same column tile, so the B (weight) tile is
   // shared through L2 by the CTAs that run at the same time and A is streamed once.
+  // The two single-thread roles keep their per-k-step instruction count minimal (ring position and parity as running
+  // counters, descriptors advanced by additions, progress counters written to shared memory only when a loop ends):
+  // their issue time is what bounds narrow tiles.
   if (warp == 0) {
     if (lane == 0) {
-      int it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+      int it = 0, st = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok && !*abort_flag; tile += gridDim.x) {
         const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
-        for (int kt = 0; kt < num_k; ++kt, ++it) {
-          const int s = it % STAGES;
-          const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
-          if (!mbar_wait(&empty[s], phase ^ 1u)) { *abort_flag = 1; break; }
-          mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+        for (int kt = 0; kt < num_k; ++kt) {
+          if (!mbar_wait(&empty[st], ph ^ 1u)) { *abort_flag = 1; ok = false; break; }
+          mbar_expect_tx(&full[st], A_BYTES + B_BYTES);
           if (!a_mn) {
-            tma_load_2d(sA + s * A_BYTES, &map_a, kt * BK, tile_m * BM, &full[s]);
+            tma_load_2d(sA + st * A_BYTES, &map_a, kt * BK, tile_m * BM, &full[st]);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
-              tma_load_2d(sA + s * A_BYTES + c * kMnChunkBytes, &map_a, tile_m * BM + c * 64, kt * BK, &full[s]);
+              tma_load_2d(sA + st * A_BYTES + c * kMnChunkBytes, &map_a, tile_m * BM + c * 64, kt * BK, &full[st]);
           }
           if (!b_mn) {
-            tma_load_2d(sB + s * B_BYTES, &map_b, kt * BK, tile_n * BN, &full[s]);
+            tma_load_2d(sB + st * B_BYTES, &map_b, kt * BK, tile_n * BN, &full[st]);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sB + s * B_BYTES + c * kMnChunkBytes, &map_b, tile_n * BN + c * 64, kt * BK, &full[s]);
+              tma_load_2d(sB + st * B_BYTES + c * kMnChunkBytes, &map_b, tile_n * BN + c * 64, kt * BK, &full[st]);
           }
-          *issued_it = it + 1;
+          ++it;
+          if (++st == STAGES) { st = 0; ph ^= 1u; }
         }
       }
+      *issued_it = it;
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -126,31 +131,34 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // one UMMA_K step (16 elements of K): 32 bytes inside the swizzle atom for a K-major operand, 16 k-rows of
       // 128 bytes for an MN-major operand; in units of the descriptor's 16-byte address field
       const uint64_t a_step = a_mn ? (16 * 128) >> 4 : 2, b_step = b_mn ? (16 * 128) >> 4 : 2;
-      int it = 0, t = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++t) {
+      // descriptors of stage 0; the start-address field (16-byte units, 14 bits) takes plain additions
+      const uint64_t adesc0 = a_mn ? make_desc_mn(smem_u32(sA)) : make_desc(smem_u32(sA));
+      const uint64_t bdesc0 = b_mn ? make_desc_mn(smem_u32(sB)) : make_desc(smem_u32(sB));
+      int it = 0, st = 0, t = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok && !*abort_flag; tile += gridDim.x, ++t) {
         const int buf = t & 1;
         // wait until the epilogue has drained this accumulator (its first use passes immediately)
         if (!mbar_wait(&acc_empty[buf], (((uint32_t)t >> 1) & 1u) ^ 1u)) { *abort_flag = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-        bool ok = true;
-        for (int kt = 0; kt < num_k; ++kt, ++it) {
-          const int s = it % STAGES;
-          const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
-          if (!mbar_wait(&full[s], phase)) { *abort_flag = 1; ok = false; break; }
-          *consumed_it = it + 1;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_u32(sA + s * A_BYTES), b_addr = smem_u32(sB + s * B_BYTES);
-          const uint64_t adesc = a_mn ? make_desc_mn(a_addr) : make_desc(a_addr);
-          const uint64_t bdesc = b_mn ? make_desc_mn(b_addr) : make_desc(b_addr);
+        for (int kt = 0; kt < num_k; ++kt) {
+          if (!mbar_wait(&full[st], ph)) { *abort_flag = 1; ok = false; break; }
+          const uint64_t adesc = adesc0 + (uint64_t)(st * (int)(A_BYTES >> 4));
+          const uint64_t bdesc = bdesc0 + (uint64_t)(st * (int)(B_BYTES >> 4));
+          umma(tmem_d, adesc, bdesc, idesc, kt > 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma(tmem_d, adesc + a_step * (uint64_t)k, bdesc + b_step * (uint64_t)k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
-          umma_commit(&empty[s]);        // the stage is free once these MMAs have read it
+          for (int k = 1; k < BK / UMMA_K; ++k)
+            umma(tmem_d, adesc + a_step * (uint64_t)k, bdesc + b_step * (uint64_t)k, idesc, 1u);
+          umma_commit(&empty[st]);        // the stage is free once these MMAs have read it
+          ++it;
+          if (++st == STAGES) { st = 0; ph ^= 1u; }
         }
         if (!ok) break;
         umma_commit(&acc_full[buf]);     // arrives when every MMA of this tile has completed
       }
+      *consumed_it = it;
     }
   } else {
     // epilogue warps 2..5: TMEM lane quarter = warp index modulo 4

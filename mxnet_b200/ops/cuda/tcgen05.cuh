@@ -34,6 +34,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
+// The same wait executed by a whole (converged) warp: every lane polls, and the result is made uniform so that the warp
+// leaves its loop together when the wait expires.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity) ? 1 : 0) != 0;
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
