@@ -190,6 +190,10 @@ def main():
 
     if rank == 0:
         fused = trainer._fused is not None
+        from mxnet_b200.ops.cuda import conv_ops
+        tuned = conv_ops.tuned_choices()
+        conv_sel = {d: '%d of %d' % (sum(1 for k, v in tuned.items() if k[0] == d and v), sum(1 for k in tuned if k[0] == d))
+                    for d in ('fwd', 'dgrad', 'wgrad')}
         out = {
             'metric': 'resnet50_train_img_per_s', 'value': value, 'unit': 'img/s', 'n_gpus': world, 'steps': args.steps,
             'warmup': max(args.warmup, 3), 'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'weak',
@@ -197,6 +201,7 @@ def main():
             'config': {'model': 'resnet50_v1b', 'global_batch': global_batch, 'batch_per_gpu': B, 'image': S, 'layout': 'NHWC',
                        'parallelism': 'dp%d' % world, 'optimizer': 'sgd momentum 0.9 wd 1e-4 multi-precision',
                        'amp': 'fp16 dynamic loss scale (device resident)', 'fused_step': fused, 'cuda_graphs': bool(args.graphs),
+                       'conv_in_tree_kernel_chosen': conv_sel,
                        'l2': 'inputs larger than L2 (activations per step >> 126 MB); no explicit flush',
                        'baseline_ref': 'V100 fp32 bs128 363.69 img/s per GPU (perf.md) x n_gpus'},
             'clocks': {k: clocks[k] for k in ('sm_mhz', 'sm_max_mhz', 'reasons')},

@@ -81,7 +81,7 @@ def interleaved_matmul_encdec_valatt(keys_values, attention, heads=1):
 
 
 def _ew_kernels(t):
-    if not (t.is_cuda and env.get('MXNET_B200_KERNELS')):
+    if not (t.is_cuda and env.get('MXNET_B200_KERNELS') and env.get('MXNET_B200_ELEMENTWISE')):
         return None
     from . import cuda
     if not cuda.available():

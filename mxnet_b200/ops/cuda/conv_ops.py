@@ -20,8 +20,11 @@ from .gemm_ops import _error_flag
 _DEFAULT = 'auto'
 _ALL = frozenset(('fwd', 'dgrad', 'wgrad'))
 _tuned = {}          # (direction, dtype, geometry) -> True when the in-tree kernel won
-# achieved rate of the separate BatchNorm statistics pass that the forward epilogue replaces, bytes per microsecond
-_BN_REDUCE_BYTES_PER_US = 4.8e6
+# rate credited to the separate BatchNorm statistics pass that the forward epilogue replaces, bytes per microsecond
+# (the copy bandwidth: a conservative credit, the measured pass is slower)
+_BN_REDUCE_BYTES_PER_US = 6.5e6
+_MARGIN = 0.97       # the in-tree kernel must be at least 3 % faster to be chosen
+_flush = {}
 
 
 def directions():
@@ -35,16 +38,25 @@ def directions():
     return frozenset(p.strip() for p in v.split(','))
 
 
-def _time_us(fn, reps=3):
+def _time_us(fn, reps=5):
+    """Median device time of `fn` with the L2 cache flushed before every run (as inside a training step, where the
+    operands of a layer were evicted by the layers in between)."""
+    dev = torch.cuda.current_device()
+    flush = _flush.get(dev)
+    if flush is None:
+        flush = _flush[dev] = torch.empty(192 << 20, dtype=torch.uint8, device='cuda')
     fn()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
+    times = []
     for _ in range(reps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
         fn()
-    b.record()
-    torch.cuda.synchronize()
-    return a.elapsed_time(b) * 1e3 / reps
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3)
+    times.sort()
+    return times[len(times) // 2]
 
 
 def use_own(direction, dirs, key, own_fn, lib_fn, lib_extra_us=0.0):
@@ -57,7 +69,7 @@ def use_own(direction, dirs, key, own_fn, lib_fn, lib_extra_us=0.0):
         if torch.cuda.is_current_stream_capturing():
             return False                   # cannot time inside a capture; the eager warm-up run normally comes first
         with torch.no_grad():
-            hit = _tuned[k] = _time_us(own_fn) <= _time_us(lib_fn) + lib_extra_us
+            hit = _tuned[k] = _time_us(own_fn) <= _MARGIN * (_time_us(lib_fn) + lib_extra_us)
     return hit
 
 

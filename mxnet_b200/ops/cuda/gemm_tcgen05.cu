@@ -37,7 +37,8 @@ constexpr int kMaxStages = 8;
 template <int BN> struct TileCfg {
   static constexpr uint32_t B_BYTES = BN * BK * 2;
   static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  static constexpr uint32_t STG_BYTES = 4 * 2048;   // per epilogue warp: 32 rows x 64 bytes staged for the TMA store
+  static constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + STG_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
 enum Act { kActNone = 0, kActRelu = 1, kActGelu = 2 };
@@ -46,8 +47,9 @@ __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + er
 
 template <typename T, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, T* __restrict__ D,
-               const T* __restrict__ bias, int M, int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn,
+gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_d, int use_tma_store, T* __restrict__ D, const T* __restrict__ bias, int M,
+               int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, const FastDiv fd_tiles_m,
                int* __restrict__ error_flag) {
   using Cfg = TileCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
@@ -57,7 +59,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
+  uint8_t* sStg = smem + STAGES * (A_BYTES + B_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES) + Cfg::STG_BYTES);
   uint64_t* full = bars;                        // [STAGES] producer -> MMA
   uint64_t* empty = bars + kMaxStages;          // [STAGES] MMA -> producer
   uint64_t* acc_full = bars + 2 * kMaxStages;   // [2] accumulator ready for the epilogue
@@ -101,7 +104,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok && !*abort_flag; tile += gridDim.x) {
-        const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+        uint32_t tile_n_u, tile_m_u;
+        fd_divmod((uint32_t)tile, fd_tiles_m, &tile_n_u, &tile_m_u);
+        const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u;
         for (int kt = 0; kt < num_k; ++kt) {
           if (!mbar_wait(&empty[st], ph ^ 1u)) { *abort_flag = 1; ok = false; break; }
           mbar_expect_tx(&full[st], A_BYTES + B_BYTES);
@@ -163,9 +168,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else {
     // epilogue warps 2..5: TMEM lane quarter = warp index modulo 4
     const int q = warp & 3;
+    uint8_t* stg = sStg + q * 2048;       // this warp's staging tile: 32 rows x 64 bytes, 64-byte swizzle
     int t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
-      const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+      uint32_t tile_n_u, tile_m_u;
+        fd_divmod((uint32_t)tile, fd_tiles_m, &tile_n_u, &tile_m_u);
+        const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u;
       const int buf = t & 1;
       const bool ready = mbar_wait(&acc_full[buf], ((uint32_t)t >> 1) & 1u);
       if (!ready) *abort_flag = 1;
@@ -174,6 +182,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int row = tile_m * BM + q * 32 + lane;
       const bool bias_vec = bias != nullptr && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
       const bool row_vec = (ldd % 8) == 0;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+      uint32_t r[32];
+      tmem_ld32(taddr, r);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         const int col0 = tile_n * BN + c0;
@@ -197,9 +208,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               if (col0 + j < N) bv[j] = Cvt<T>::to_f(bias[col0 + j]);
           }
         }
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0), r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        tmem_wait_ld32(r);
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -208,7 +217,29 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           else if (act == kActGelu) x = gelu_erf(x);
           f[j] = x;
         }
-        if (row < M && col0 < N) {
+        // the next 32 columns travel from TMEM while these are converted and stored
+        if (c0 + 32 < BN) tmem_ld32(taddr + (uint32_t)(c0 + 32), r);
+        if (use_tma_store) {
+          // rows as four 16-byte pieces in the swizzled layout of the store's tensor map; one bulk store per 32 x 32
+          // block (rows and columns outside the matrix are clipped by the copy engine)
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+          if (col0 < N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              Vec16<T> o;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o.v[j] = Cvt<T>::from_f(f[v * 8 + j]);
+              st16(reinterpret_cast<T*>(stg + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)), o);
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&map_d, stg, col0, tile_m * BM + q * 32);
+              tma_store_commit();
+            }
+          }
+        } else if (row < M && col0 < N) {
           T* drow = D + (size_t)row * ldd + col0;
           if (full_cols && row_vec) {
 #pragma unroll
@@ -230,6 +261,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
+    if (lane == 0) tma_store_wait_all();    // the staging tile must outlive the last store
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -265,9 +297,24 @@ static int make_map_mn(CUtensorMap* map, const void* base, int bf16, int64_t kro
   return make_map(map, base, bf16, krows, mn, ld, BK);
 }
 
+// Output matrix [M, N] with row pitch ldd for the epilogue's stores: box = 32 rows x 32 columns, 64-byte swizzle.
+static int make_map_store(CUtensorMap* map, const void* base, int bf16, int64_t rows, int64_t cols, int64_t ld) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -10;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base),
+                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : -11;
+}
+
 template <typename T, int BN>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, void* D, const void* bias, int M, int N, int K, int ldd,
-                       int act, int bf16, int a_mn, int b_mn, int* error_flag, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, int use_tma_store, void* D,
+                       const void* bias, int M, int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, int* error_flag,
+                       cudaStream_t st) {
   using Cfg = TileCfg<BN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -277,8 +324,9 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, void* D, co
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_tn_kernel<T, BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ma, mb, (T*)D, (const T*)bias, M, N, K, ldd, act, bf16,
-                                                                     a_mn, b_mn, error_flag);
+  gemm_tn_kernel<T, BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ma, mb, md, use_tma_store, (T*)D, (const T*)bias, M, N, K,
+                                                                     ldd, act, bf16, a_mn, b_mn,
+                                                                     make_fastdiv((uint32_t)((M + BM - 1) / BM)), error_flag);
   return (int)cudaGetLastError();
 }
 
@@ -312,11 +360,19 @@ MXB_EXPORT int mxb_gemm(int dtype, const void* A, const void* B, void* D, const 
   if (rc) return rc;
   rc = b_mn ? make_map_mn(&mb, B, bf16, K, N, ldb) : make_map(&mb, B, bf16, N, K, ldb, bn);
   if (rc) return rc;
+  // the epilogue stores through the copy engine when D meets a tensor map's rules (16-byte row pitch); otherwise with
+  // per-thread stores
+  CUtensorMap md = ma;
+  const int use_tma_store = (ldd % 8) == 0 ? 1 : 0;
+  if (use_tma_store) {
+    rc = make_map_store(&md, D, bf16, M, N, ldd);
+    if (rc) return rc;
+  }
   cudaStream_t st = (cudaStream_t)stream;
-#define MXB_GEMM(T)                                                                                                  \
-  (bn == 256 ? launch_gemm<T, 256>(ma, mb, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, error_flag, st)              \
-   : bn == 128 ? launch_gemm<T, 128>(ma, mb, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, error_flag, st)            \
-               : launch_gemm<T, 64>(ma, mb, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, error_flag, st))
+#define MXB_GEMM(T)                                                                                                        \
+  (bn == 256 ? launch_gemm<T, 256>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, error_flag, st)  \
+   : bn == 128 ? launch_gemm<T, 128>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, error_flag, st) \
+               : launch_gemm<T, 64>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, error_flag, st))
   return bf16 ? MXB_GEMM(__nv_bfloat16) : MXB_GEMM(__half);
 #undef MXB_GEMM
 }

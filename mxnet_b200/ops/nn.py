@@ -30,6 +30,11 @@ def _use_kernels(t):
     return cuda.available()
 
 
+def _use_ew(t):
+    """The pointwise / gather / pooling vector kernels (``MXNET_B200_ELEMENTWISE``)."""
+    return env.get('MXNET_B200_ELEMENTWISE') and _use_kernels(t)
+
+
 def _tup(v, n):
     if v is None or v == ():
         return None
@@ -279,7 +284,7 @@ def pooling(data, kernel=(), pool_type='max', global_pool=False, cudnn_off=False
         k2, s2, p2 = _tup(kernel, 2), _tup(stride, 2) or (1, 1), _tup(pad, 2) or (0, 0)
         if pool_ops.supported(data, k2, s2, p2):
             return pool_ops.max_pool2d_nhwc(data, k2, s2, p2, pooling_convention == 'full')
-    if layout in _CHANNEL_LAST and nsp == 2 and pool_type == 'avg' and _use_kernels(data) \
+    if layout in _CHANNEL_LAST and nsp == 2 and pool_type == 'avg' and _use_ew(data) \
             and pooling_convention in ('valid', 'full'):
         from .cuda import elementwise_ops as ew
         if ew.avgpool_supported(data):
@@ -403,7 +408,7 @@ def leaky_relu(data, gamma=None, act_type='leaky', slope=0.25, lower_bound=0.125
     if act_type == 'selu':
         return F.selu(data)
     if act_type == 'gelu':
-        if _use_kernels(data):
+        if _use_ew(data):
             from .cuda import elementwise_ops as ew
             if ew.pointwise_supported(data, data.shape[-1] if data.dim() else 1):
                 return ew.gelu(data)
@@ -447,7 +452,7 @@ def dropout(data, p=0.5, mode='training', axes=(), cudnn_off=False):
             shape[a] = 1
         mask = (torch.rand(shape, device=data.device) >= p).to(data.dtype) / (1 - p)
         return data * mask
-    if _use_kernels(data) and 0 < p < 1:
+    if _use_ew(data) and 0 < p < 1:
         from .cuda import elementwise_ops as ew
         if ew.pointwise_supported(data, data.shape[-1] if data.dim() else 1):
             return ew.dropout(data, p)

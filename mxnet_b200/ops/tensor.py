@@ -22,7 +22,7 @@ from .. import env as _env
 
 def _use_kernels(t):
     """True when CUDA tensors should take the hand-written sm_100a kernels."""
-    if not t.is_cuda or not _env.get('MXNET_B200_KERNELS'):
+    if not t.is_cuda or not _env.get('MXNET_B200_KERNELS') or not _env.get('MXNET_B200_ELEMENTWISE'):
         return False
     from . import cuda
     return cuda.available()
