@@ -51,6 +51,12 @@ def run(name, unit, items_per_step_per_gpu, make_step, args, config, baseline=No
     if rank == 0:
         cfg = dict(config)
         cfg['parallelism'] = 'dp%d' % world
+        from mxnet_b200.ops.cuda import gemm_ops
+        tuned = gemm_ops.tuned_choices()
+        if tuned:
+            cfg['gemm_in_tree_kernel_chosen'] = {p: '%d of %d' % (sum(1 for k, v in tuned.items() if k[0] == p and v),
+                                                                  sum(1 for k in tuned if k[0] == p))
+                                                 for p in ('fwd', 'dgrad', 'wgrad')}
         print(json.dumps({'metric': name, 'value': value, 'unit': unit, 'n_gpus': world, 'steps': args.steps,
                           'warmup': max(args.warmup, 3), 'ms_per_step': ms / args.steps, 'higher_is_better': True,
                           'scaling': 'weak', 'vs_baseline': (value / baseline) if baseline else None, 'data': 'synthetic',

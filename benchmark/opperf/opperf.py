@@ -233,6 +233,44 @@ def gemm_burst(ctx, dtype, reps=50):
     return out
 
 
+def gemm_layouts(ctx, dtype, reps=30):
+    """The three products of a FullyConnected layer on BERT-base shapes (8192 tokens): forward y = x w^T (both K-major),
+    data gradient dx = dy w (w MN-major), weight gradient dw = dy^T x (both MN-major); in-tree kernel against the
+    library on identical operands, `reps` back-to-back launches between two events."""
+    from mxnet_b200.ops.cuda import gemm_ops
+    td = mx.base.to_torch_dtype(dtype)
+    out = []
+    tokens = 8192
+    for cin, cout in [(768, 2304), (768, 768), (768, 3072), (3072, 768)]:
+        x = torch.randn(tokens, cin, device=ctx.torch_device).to(td)
+        w = torch.randn(cout, cin, device=ctx.torch_device).to(td)
+        dy = torch.randn(tokens, cout, device=ctx.torch_device).to(td)
+        cases = {
+            'fwd': (lambda: gemm_ops.gemm_tn(x, w), lambda: torch.matmul(x, w.t())),
+            'dgrad': (lambda: gemm_ops.gemm(dy, w, False, True), lambda: torch.matmul(dy, w)),
+            'wgrad': (lambda: gemm_ops.gemm(dy, x, True, True), lambda: torch.matmul(dy.t(), x)),
+        }
+        for kind, (own, libf) in cases.items():
+            res = {'op': 'gemm_layouts', 'layer': '%d->%d' % (cin, cout), 'product': kind, 'dtype': dtype, 'reps': reps}
+            for name, fn in (('tcgen05', own), ('library', libf)):
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / reps
+                res[name + '_us'] = round(ms * 1e3, 1)
+                res[name + '_TFLOPs'] = round(2.0 * tokens * cin * cout / ms / 1e9, 1)
+            gemm_ops.check_errors()
+            res['ratio'] = round(res['tcgen05_TFLOPs'] / res['library_TFLOPs'], 3)
+            out.append(res)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--op', action='append', help='case name (repeatable); default: all')
@@ -250,6 +288,11 @@ def main():
     dtype = args.dtype if cuda else 'float32'
     small = args.small or not cuda
     for name in (args.op or list(CASES)):
+        if name == 'gemm_layouts':
+            if ctx.device_type == 'gpu':
+                for r in gemm_layouts(ctx, dtype):
+                    print(json.dumps(r), flush=True)
+            continue
         if name == 'gemm_burst':
             if cuda:
                 for r in gemm_burst(ctx, dtype):

@@ -123,6 +123,7 @@ declare('MXNET_B200_ATTENTION', bool, True, 'fused self-attention on the tcgen05
 declare('MXNET_B200_CONV', str, 'auto', 'stride-1 NHWC convolutions on the tcgen05 implicit-GEMM kernels: auto = time against the library per shape and direction, subset of fwd,dgrad,wgrad or 1 = force, 0 = library convolution')
 declare('MXNET_B200_CONV_RESIDENT_WEIGHTS', bool, True, 'keep the weight slices of a column tile resident in shared memory in the convolution kernels when they fit (0 = stream them with the activations)')
 declare('MXNET_B200_ELEMENTWISE', bool, True, 'GELU, dropout, embedding, add_n, cast and average pooling on the in-tree vector kernels (0 = library kernels)')
+declare('MXNET_B200_GEMM_AUTOTUNE', bool, True, 'time the tcgen05 GEMM against the library GEMM per shape and product (forward, data gradient, weight gradient) on first use and keep the faster')
 declare('MXNET_B200_GEMM', bool, True, 'route half-precision FullyConnected/dot to the tcgen05 GEMM kernel (0 = library GEMM)')
 # ---- graph --------------------------------------------------------------------------------
 declare('MXNET_USE_FUSION', bool, True, 'pointwise fusion')

@@ -196,41 +196,103 @@ embedding_fwd_kernel(const I* __restrict__ idx, const T* __restrict__ weight, T*
   }
 }
 
-// Gradient of the gather: `sorted` holds the indices in ascending order and `perm` the position each came from.  One
-// CTA-column group per run of equal indices sums the run's rows of dy in order (fp32), so the result does not depend
-// on scheduling; rows that no index selects are left as they are (the caller zeroes dw first, or accumulates).
+// Gradient of the gather: `sorted` holds the indices in ascending order and `perm` the position each came from.
+// Stage 1: one warp per block of 32 sorted positions sums the rows of dy run by run (fp32, in order).  A run that lies
+// inside its block is written to dw directly; a run that crosses a block boundary leaves a partial sum ([block][0] when
+// it continues from the previous block, [block][1] when it starts here and continues into the next).  Stage 2: one warp
+// per run that starts in one block and continues adds its partials block by block.  The order of additions is fixed by
+// the sorted order, so the result does not depend on scheduling, and a table with a few distinct indices (a run of
+// thousands of positions) is still spread over all warps.
+constexpr int kEmbBlock = 32;
+
 template <typename T, typename I>
 __global__ void __launch_bounds__(kEwThreads)
-embedding_bwd_kernel(const I* __restrict__ sorted, const int64_t* __restrict__ perm, const T* __restrict__ dy, T* __restrict__ dw,
-                     int64_t n, int D, int64_t rows, int accumulate) {
+embedding_bwd_stage1_kernel(const I* __restrict__ sorted, const int64_t* __restrict__ perm, const T* __restrict__ dy,
+                            T* __restrict__ dw, float* __restrict__ partial, int64_t n, int D, int64_t rows, int accumulate) {
   constexpr int V = Vec16<T>::N;
-  const int L = D / V;                       // vectors per row
-  const int groups = kEwThreads / 32;        // warps per CTA, one run start per warp per trip
+  const int L = D / V;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int64_t p = (int64_t)blockIdx.x * groups + warp; p < n; p += (int64_t)gridDim.x * groups) {
-    int64_t k = (int64_t)sorted[p];
-    if (p > 0 && (int64_t)sorted[p - 1] == k) continue;          // not the first element of its run
-    int64_t e = p + 1;
-    while (e < n && (int64_t)sorted[e] == k) ++e;
-    k = k < 0 ? 0 : (k >= rows ? rows - 1 : k);
+  const int64_t nblocks = (n + kEmbBlock - 1) / kEmbBlock;
+  for (int64_t b = (int64_t)blockIdx.x * (kEwThreads / 32) + warp; b < nblocks; b += (int64_t)gridDim.x * (kEwThreads / 32)) {
+    const int64_t p0 = b * kEmbBlock, p1 = (p0 + kEmbBlock < n) ? p0 + kEmbBlock : n;
     for (int c = lane; c < L; c += 32) {
       float acc[V];
 #pragma unroll
       for (int j = 0; j < V; ++j) acc[j] = 0.f;
-      if (accumulate) {
-        const Vec16<T> w = ld16(dw + k * D + c * V);
+      int64_t cur = (int64_t)sorted[p0], seg = p0;
+      for (int64_t p = p0; p <= p1; ++p) {
+        const bool end = p == p1;
+        const int64_t k = end ? -1 : (int64_t)sorted[p];
+        if (end || k != cur) {
+          // flush the run [seg, p) of index `cur`
+          const bool from_prev = seg == p0 && p0 > 0 && (int64_t)sorted[p0 - 1] == cur;
+          const bool into_next = end && p1 < n && (int64_t)sorted[p1] == cur;
+          if (!from_prev && !into_next) {
+            int64_t kk = cur < 0 ? 0 : (cur >= rows ? rows - 1 : cur);
+            if (accumulate) {
+              const Vec16<T> w = ld16(dw + kk * D + c * V);
 #pragma unroll
-        for (int j = 0; j < V; ++j) acc[j] = Cvt<T>::to_f(w.v[j]);
+              for (int j = 0; j < V; ++j) acc[j] += Cvt<T>::to_f(w.v[j]);
+            }
+            Vec16<T> o;
+#pragma unroll
+            for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(acc[j]);
+            st16(dw + kk * D + c * V, o);
+          } else {
+            float* dst = partial + ((b * 2 + (from_prev ? 0 : 1)) * (int64_t)D) + c * V;
+#pragma unroll
+            for (int j = 0; j < V; ++j) dst[j] = acc[j];
+          }
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] = 0.f;
+          cur = k;
+          seg = p;
+        }
+        if (!end) {
+          const Vec16<T> g = ld16(dy + perm[p] * D + c * V);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] += Cvt<T>::to_f(g.v[j]);
+        }
       }
-      for (int64_t q = p; q < e; ++q) {
-        const Vec16<T> g = ld16(dy + perm[q] * D + c * V);
+    }
+  }
+}
+
+template <typename T, typename I>
+__global__ void __launch_bounds__(kEwThreads)
+embedding_bwd_stage2_kernel(const I* __restrict__ sorted, const float* __restrict__ partial, T* __restrict__ dw, int64_t n,
+                            int D, int64_t rows, int accumulate) {
+  constexpr int V = Vec16<T>::N;
+  const int L = D / V;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t nblocks = (n + kEmbBlock - 1) / kEmbBlock;
+  for (int64_t b = (int64_t)blockIdx.x * (kEwThreads / 32) + warp; b < nblocks; b += (int64_t)gridDim.x * (kEwThreads / 32)) {
+    const int64_t p0 = b * kEmbBlock, p1 = p0 + kEmbBlock;
+    if (p1 >= n) continue;
+    const int64_t k = (int64_t)sorted[p1 - 1];
+    if ((int64_t)sorted[p1] != k) continue;                        // the last run of this block ends here
+    // does that run start in this block?  (otherwise an earlier block owns it)
+    if ((int64_t)sorted[p0] == k && p0 > 0 && (int64_t)sorted[p0 - 1] == k) continue;
+    const int64_t kk = k < 0 ? 0 : (k >= rows ? rows - 1 : k);
+    for (int c = lane; c < L; c += 32) {
+      float acc[V];
+      const float* src = partial + (b * 2 + 1) * (int64_t)D + c * V;
 #pragma unroll
-        for (int j = 0; j < V; ++j) acc[j] += Cvt<T>::to_f(g.v[j]);
+      for (int j = 0; j < V; ++j) acc[j] = src[j];
+      for (int64_t b2 = b + 1; b2 < nblocks && (int64_t)sorted[b2 * kEmbBlock] == k; ++b2) {
+        const float* s2 = partial + (b2 * 2) * (int64_t)D + c * V;
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] += s2[j];
+      }
+      if (accumulate) {
+        const Vec16<T> w = ld16(dw + kk * D + c * V);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] += Cvt<T>::to_f(w.v[j]);
       }
       Vec16<T> o;
 #pragma unroll
       for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(acc[j]);
-      st16(dw + k * D + c * V, o);
+      st16(dw + kk * D + c * V, o);
     }
   }
 }
@@ -460,15 +522,23 @@ MXB_EXPORT int mxb_embedding_forward(int dtype, const void* idx, int idx_is_64, 
   });
 }
 
-// dw[rows, D] (+)= scatter of dy[n, D] by the indices; `sorted` ascending with `perm` (int64) the original positions.
+// dw[rows, D] (+)= scatter of dy[n, D] by the indices; `sorted` ascending with `perm` (int64) the original positions;
+// `partial`: ceil(n / 32) * 2 * D floats of scratch.
 MXB_EXPORT int mxb_embedding_backward(int dtype, const void* sorted, int idx_is_64, const int64_t* perm, const void* dy, void* dw,
-                                      int64_t n, int D, int64_t rows, int accumulate, void* stream) {
-  if (n < 1 || D < 1 || rows < 1 || D % vec_of(dtype) || !aligned16(dy) || !aligned16(dw)) return -3;
+                                      float* partial, int64_t n, int D, int64_t rows, int accumulate, void* stream) {
+  if (n < 1 || D < 1 || rows < 1 || D % vec_of(dtype) || !aligned16(dy) || !aligned16(dw) || !partial || !aligned16(partial))
+    return -3;
   cudaStream_t st = (cudaStream_t)stream;
   return MXB_DISPATCH_FLOAT(dtype, {
-    const int grid = ew_grid(n * 32);
-    if (idx_is_64) embedding_bwd_kernel<T, int64_t><<<grid, kEwThreads, 0, st>>>((const int64_t*)sorted, perm, (const T*)dy, (T*)dw, n, D, rows, accumulate);
-    else embedding_bwd_kernel<T, int32_t><<<grid, kEwThreads, 0, st>>>((const int32_t*)sorted, perm, (const T*)dy, (T*)dw, n, D, rows, accumulate);
+    const int64_t nblocks = (n + kEmbBlock - 1) / kEmbBlock;
+    const int grid = ew_grid(nblocks * 32);
+    if (idx_is_64) {
+      embedding_bwd_stage1_kernel<T, int64_t><<<grid, kEwThreads, 0, st>>>((const int64_t*)sorted, perm, (const T*)dy, (T*)dw, partial, n, D, rows, accumulate);
+      embedding_bwd_stage2_kernel<T, int64_t><<<grid, kEwThreads, 0, st>>>((const int64_t*)sorted, partial, (T*)dw, n, D, rows, accumulate);
+    } else {
+      embedding_bwd_stage1_kernel<T, int32_t><<<grid, kEwThreads, 0, st>>>((const int32_t*)sorted, perm, (const T*)dy, (T*)dw, partial, n, D, rows, accumulate);
+      embedding_bwd_stage2_kernel<T, int32_t><<<grid, kEwThreads, 0, st>>>((const int32_t*)sorted, partial, (T*)dw, n, D, rows, accumulate);
+    }
     return (int)cudaGetLastError();
   });
 }

@@ -193,9 +193,11 @@ class _Embedding(torch.autograd.Function):
         dy = require(dy.contiguous(), 'out_grad', numel=idx.numel() * D)
         sorted_idx, perm = torch.sort(idx.reshape(-1), stable=True)
         dw = torch.zeros((rows, D), dtype=dy.dtype, device=dy.device)
+        partial = torch.empty(((idx.numel() + 31) // 32, 2, D), dtype=torch.float32, device=dy.device)
         check(lib().mxb_embedding_backward(dt(dy), ptr(sorted_idx), 1 if idx.dtype == torch.int64 else 0, ptr(perm), ptr(dy),
-                                           ptr(dw), idx.numel(), D, rows, 0, stream_ptr(dy.device)), 'embedding_backward')
-        count_launch(1)
+                                           ptr(dw), ptr(partial), idx.numel(), D, rows, 0, stream_ptr(dy.device)),
+              'embedding_backward')
+        count_launch(2)
         return None, dw
 
 

@@ -10,6 +10,52 @@ from ._util import dt, require
 
 _ACT = {None: 0, 'relu': 1, 'gelu': 2}
 _err = {}
+_tuned = {}          # (product, dtype, M, N, K, bias, act) -> True when the in-tree kernel won
+_flush = {}
+_MARGIN = 0.98
+
+
+def _autotune():
+    from ... import env
+    return env.get('MXNET_B200_GEMM_AUTOTUNE')
+
+
+def _time_us(fn, reps=5):
+    """Median device time with the L2 cache flushed before every run."""
+    dev = torch.cuda.current_device()
+    flush = _flush.get(dev)
+    if flush is None:
+        flush = _flush[dev] = torch.empty(192 << 20, dtype=torch.uint8, device='cuda')
+    fn()
+    times = []
+    for _ in range(reps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def use_own(key, own_fn, lib_fn):
+    """Per-shape choice between the in-tree kernel and the library GEMM (``MXNET_B200_GEMM_AUTOTUNE``, the counterpart
+    of the convolution autotune): timed once, outside of graph capture, on the first call with this key."""
+    if not _autotune():
+        return True
+    hit = _tuned.get(key)
+    if hit is None:
+        if torch.cuda.is_current_stream_capturing():
+            return True
+        with torch.no_grad():
+            hit = _tuned[key] = _time_us(own_fn) <= _MARGIN * _time_us(lib_fn)
+    return hit
+
+
+def tuned_choices():
+    return dict(_tuned)
 
 
 def _error_flag(device):
@@ -45,14 +91,7 @@ def gemm_tn(a, b, bias=None, act=None, out=None):
         require(out, 'out', dtype=a.dtype, device=a.device, shape=(M, N))
     if bias is not None:
         require(bias, 'bias', numel=N, device=a.device)
-    d = out if out is not None else torch.empty(M, N, dtype=a.dtype, device=a.device)
-    if bias is not None and bias.dtype != a.dtype:
-        bias = bias.to(a.dtype)
-    rc = lib().mxb_gemm_tn(dt(a), ptr(a), ptr(b), ptr(d), ptr(bias), M, N, K, K, K, N, _ACT[act],
-                           ptr(_error_flag(a.device)), stream_ptr(a.device))
-    check(rc, 'gemm_tn')
-    count_launch(1)
-    return d
+    return gemm(a, b, False, False, bias, act, out)
 
 
 def gemm(a, b, a_mn=False, b_mn=False, bias=None, act=None, out=None):
@@ -74,7 +113,16 @@ def gemm(a, b, a_mn=False, b_mn=False, bias=None, act=None, out=None):
         if bias.dtype != a.dtype:
             bias = bias.to(a.dtype)
         require(bias, 'bias', numel=N, device=a.device)
-    rc = lib().mxb_gemm(dt(a), ptr(a), ptr(b), ptr(d), ptr(bias), M, N, K, a.shape[1], b.shape[1], N,
+    L = lib()
+    if L.mxb_gemm_wants_workspace(M, N, K):
+        # few output tiles and a long contraction (a weight gradient): split-K through an fp32 workspace
+        ws = torch.empty(M * N, dtype=torch.float32, device=a.device)
+        rc = L.mxb_gemm_ws(dt(a), ptr(a), ptr(b), ptr(d), ptr(bias), M, N, K, a.shape[1], b.shape[1], N,
+                           1 if a_mn else 0, 1 if b_mn else 0, _ACT[act], ptr(ws), ptr(_error_flag(a.device)),
+                           stream_ptr(a.device))
+        count_launch(2)
+    else:
+        rc = L.mxb_gemm(dt(a), ptr(a), ptr(b), ptr(d), ptr(bias), M, N, K, a.shape[1], b.shape[1], N,
                         1 if a_mn else 0, 1 if b_mn else 0, _ACT[act], ptr(_error_flag(a.device)), stream_ptr(a.device))
     check(rc, 'gemm')
     count_launch(1)
@@ -86,12 +134,25 @@ def operand_ok(t):
     return t.dim() == 2 and t.shape[1] % 8 == 0 and t.shape[0] >= 1 and t.data_ptr() % 16 == 0
 
 
+def _lib_linear(x, w, bias, act):
+    y = torch.nn.functional.linear(x, w, bias.to(x.dtype) if bias is not None and bias.dtype != x.dtype else bias)
+    if act == 'relu':
+        y = torch.relu(y)
+    elif act == 'gelu':
+        y = torch.nn.functional.gelu(y)
+    return y
+
+
 class LinearFn(torch.autograd.Function):
     """y = act(x @ w.T + b)."""
 
     @staticmethod
     def forward(ctx, x, w, bias, act):
-        y = gemm_tn(x, w, bias, act)
+        key = ('fwd', x.dtype, x.shape[0], w.shape[0], x.shape[1], bias is not None, act)
+        if use_own(key, lambda: gemm_tn(x, w, bias, act), lambda: _lib_linear(x, w, bias, act)):
+            y = gemm_tn(x, w, bias, act)
+        else:
+            y = _lib_linear(x, w, bias, act)
         ctx.save_for_backward(x, w, y if act is not None else None)
         ctx.act, ctx.has_bias = act, bias is not None
         ctx.bias_dtype = bias.dtype if bias is not None else None
@@ -107,14 +168,21 @@ class LinearFn(torch.autograd.Function):
             raise RuntimeError('gelu epilogue has no fused backward; use act=None for training')
         dx = dw = db = None
         ok = operand_ok(dy) and operand_ok(w) and operand_ok(x)
+        shape = (x.dtype, x.shape[0], w.shape[0], x.shape[1])
         if ctx.needs_input_grad[0]:
             # dx[M, K] = dy[M, N] . w[N, K]: w is read as an MN-major operand ([contraction, output])
-            dx = gemm(dy, w, False, True) if ok else dy @ w
+            if ok and use_own(('dgrad',) + shape, lambda: gemm(dy, w, False, True), lambda: dy @ w):
+                dx = gemm(dy, w, False, True)
+            else:
+                dx = dy @ w
         if ctx.needs_input_grad[1]:
             # dw[N, K] = dy[M, N]^T . x[M, K]: both operands MN-major, contraction over the batch axis
-            dw = gemm(dy, x, True, True) if ok else torch.matmul(dy.t(), x)
+            if ok and use_own(('wgrad',) + shape, lambda: gemm(dy, x, True, True), lambda: torch.matmul(dy.t(), x)):
+                dw = gemm(dy, x, True, True)
+            else:
+                dw = torch.matmul(dy.t(), x)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy.float().sum(0).to(ctx.bias_dtype)
+            db = dy.sum(0, dtype=torch.float32).to(ctx.bias_dtype)      # fp32 accumulation without an fp32 copy of dy
         return dx, dw, db, None
 
 

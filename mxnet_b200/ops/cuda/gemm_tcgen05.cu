@@ -36,7 +36,10 @@ constexpr int kMaxStages = 8;
 // ring depth that fits the 227 KB shared-memory budget for a given tile width
 template <int BN> struct TileCfg {
   static constexpr uint32_t B_BYTES = BN * BK * 2;
-  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 192 ? 5 : (BN == 128 ? 6 : 8));
+  // TMEM columns between the two accumulators and the (power-of-two) allocation that holds both
+  static constexpr int ACC_STRIDE = BN == 192 ? 256 : BN;
+  static constexpr uint32_t TMEM_COLS = 2 * ACC_STRIDE < 32 ? 32 : 2 * ACC_STRIDE;
   static constexpr uint32_t STG_BYTES = 4 * 2048;   // per epilogue warp: 32 rows x 64 bytes staged for the TMA store
   static constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + STG_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
@@ -50,6 +53,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_d, int use_tma_store, T* __restrict__ D, const T* __restrict__ bias, int M,
                int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, const FastDiv fd_tiles_m,
+               int ksplit, int ksteps_per, const FastDiv fd_num_tiles, float* __restrict__ ws, int a3d, int b3d,
                int* __restrict__ error_flag) {
   using Cfg = TileCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
@@ -74,7 +78,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int num_k = (K + BK - 1) / BK;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
-  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;     // two accumulators; a power of two >= 32
+  // Split-K: a work unit is (k-range, tile); with ksplit == 1 a unit is a tile.  Units of one k-range are adjacent.
+  const int num_units = num_tiles * ksplit;
+  constexpr uint32_t kTmemCols = Cfg::TMEM_COLS;     // two accumulators; a power of two >= 32
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -103,15 +109,20 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int it = 0, st = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok && !*abort_flag; tile += gridDim.x) {
-        uint32_t tile_n_u, tile_m_u;
-        fd_divmod((uint32_t)tile, fd_tiles_m, &tile_n_u, &tile_m_u);
+      for (int unit = blockIdx.x; unit < num_units && ok && !*abort_flag; unit += gridDim.x) {
+        uint32_t ks_u, tile_u, tile_n_u, tile_m_u;
+        fd_divmod((uint32_t)unit, fd_num_tiles, &ks_u, &tile_u);
+        fd_divmod(tile_u, fd_tiles_m, &tile_n_u, &tile_m_u);
         const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u;
-        for (int kt = 0; kt < num_k; ++kt) {
+        const int k0 = (int)ks_u * ksteps_per, k1 = min(num_k, k0 + ksteps_per);
+        for (int kt = k0; kt < k1; ++kt) {
           if (!mbar_wait(&empty[st], ph ^ 1u)) { *abort_flag = 1; ok = false; break; }
           mbar_expect_tx(&full[st], A_BYTES + B_BYTES);
           if (!a_mn) {
             tma_load_2d(sA + st * A_BYTES, &map_a, kt * BK, tile_m * BM, &full[st]);
+          } else if (a3d) {
+            // all 64-column chunks of the tile in one box {64 columns, 64 k-rows, BM/64 chunks}
+            tma_load_3d(sA + st * A_BYTES, &map_a, 0, kt * BK, tile_m * (BM / 64), &full[st]);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
@@ -119,6 +130,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           if (!b_mn) {
             tma_load_2d(sB + st * B_BYTES, &map_b, kt * BK, tile_n * BN, &full[st]);
+          } else if (b3d) {
+            tma_load_3d(sB + st * B_BYTES, &map_b, 0, kt * BK, tile_n * (BN / 64), &full[st]);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
@@ -142,17 +155,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int it = 0, st = 0, t = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok && !*abort_flag; tile += gridDim.x, ++t) {
+      for (int unit = blockIdx.x; unit < num_units && ok && !*abort_flag; unit += gridDim.x, ++t) {
+        const int ks = (int)fd_div((uint32_t)unit, fd_num_tiles);
+        const int k0 = ks * ksteps_per, k1 = min(num_k, k0 + ksteps_per);
         const int buf = t & 1;
         // wait until the epilogue has drained this accumulator (its first use passes immediately)
         if (!mbar_wait(&acc_empty[buf], (((uint32_t)t >> 1) & 1u) ^ 1u)) { *abort_flag = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-        for (int kt = 0; kt < num_k; ++kt) {
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * Cfg::ACC_STRIDE);
+        for (int kt = k0; kt < k1; ++kt) {
           if (!mbar_wait(&full[st], ph)) { *abort_flag = 1; ok = false; break; }
           const uint64_t adesc = adesc0 + (uint64_t)(st * (int)(A_BYTES >> 4));
           const uint64_t bdesc = bdesc0 + (uint64_t)(st * (int)(B_BYTES >> 4));
-          umma(tmem_d, adesc, bdesc, idesc, kt > 0 ? 1u : 0u);
+          umma(tmem_d, adesc, bdesc, idesc, kt > k0 ? 1u : 0u);
 #pragma unroll
           for (int k = 1; k < BK / UMMA_K; ++k)
             umma(tmem_d, adesc + a_step * (uint64_t)k, bdesc + b_step * (uint64_t)k, idesc, 1u);
@@ -170,10 +185,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int q = warp & 3;
     uint8_t* stg = sStg + q * 2048;       // this warp's staging tile: 32 rows x 64 bytes, 64-byte swizzle
     int t = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
-      uint32_t tile_n_u, tile_m_u;
-        fd_divmod((uint32_t)tile, fd_tiles_m, &tile_n_u, &tile_m_u);
-        const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u;
+    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++t) {
+      uint32_t ks_u, tile_u, tile_n_u, tile_m_u;
+      fd_divmod((uint32_t)unit, fd_num_tiles, &ks_u, &tile_u);
+      fd_divmod(tile_u, fd_tiles_m, &tile_n_u, &tile_m_u);
+      const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u;
       const int buf = t & 1;
       const bool ready = mbar_wait(&acc_full[buf], ((uint32_t)t >> 1) & 1u);
       if (!ready) *abort_flag = 1;
@@ -182,7 +198,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int row = tile_m * BM + q * 32 + lane;
       const bool bias_vec = bias != nullptr && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
       const bool row_vec = (ldd % 8) == 0;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::ACC_STRIDE);
       uint32_t r[32];
       tmem_ld32(taddr, r);
 #pragma unroll 1
@@ -209,6 +225,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
         tmem_wait_ld32(r);
+        if (ws != nullptr) {
+          // split-K: add this k-range's partial tile to the fp32 workspace (bias and activation are applied by the
+          // finishing kernel once every k-range has been added)
+          if (row < M && col0 < N) {
+            float* wrow = ws + (size_t)row * N + col0;
+            if (full_cols && (N % 4) == 0) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(wrow + v * 4), "f"(__uint_as_float(r[v * 4])),
+                             "f"(__uint_as_float(r[v * 4 + 1])), "f"(__uint_as_float(r[v * 4 + 2])),
+                             "f"(__uint_as_float(r[v * 4 + 3])) : "memory");
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) atomicAdd(wrow + j, __uint_as_float(r[j]));
+            }
+          }
+          if (c0 + 32 < BN) tmem_ld32(taddr + (uint32_t)(c0 + 32), r);
+          continue;
+        }
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -278,6 +314,30 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// Split-K finish: D = act(ws + bias), one thread per 8 columns of a row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gemm_splitk_finish_kernel(const float* __restrict__ ws, const T* __restrict__ bias, T* __restrict__ D, int M, int N, int ldd,
+                          int act) {
+  const int nv = N / 8;
+  const int64_t total = (int64_t)M * nv;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int row = (int)(i / nv), c = (int)(i % nv) * 8;
+    const float4 a = *reinterpret_cast<const float4*>(ws + (size_t)row * N + c);
+    const float4 b = *reinterpret_cast<const float4*>(ws + (size_t)row * N + c + 4);
+    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    Vec16<T> o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float x = v[j] + (bias ? Cvt<T>::to_f(bias[c + j]) : 0.f);
+      if (act == kActRelu) x = fmaxf(x, 0.f);
+      else if (act == kActGelu) x = gelu_erf(x);
+      o.v[j] = Cvt<T>::from_f(x);
+    }
+    st16(D + (size_t)row * ldd + c, o);
+  }
+}
+
 // 2-D row-major [rows, cols] half tensor, row pitch `ld` elements; box = box_rows x 64 columns, 128-byte swizzle.
 static int make_map(CUtensorMap* map, const void* base, int bf16, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
   EncodeTiledFn fn = encode_fn();
@@ -297,6 +357,21 @@ static int make_map_mn(CUtensorMap* map, const void* base, int bf16, int64_t kro
   return make_map(map, base, bf16, krows, mn, ld, BK);
 }
 
+// The same operand when MN is a multiple of 64: a 3-D view {64 columns, K rows, MN/64 chunks} (chunk stride 128 bytes)
+// whose box {64, 64, chunks} brings every chunk of a tile with one copy, chunk after chunk in shared memory.
+static int make_map_mn3(CUtensorMap* map, const void* base, int bf16, int64_t krows, int64_t mn, int64_t ld, int chunks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -10;
+  cuuint64_t dims[3] = {64, (cuuint64_t)krows, (cuuint64_t)(mn / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128};
+  cuuint32_t box[3] = {64, (cuuint32_t)BK, (cuuint32_t)chunks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base),
+                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : -11;
+}
+
 // Output matrix [M, N] with row pitch ldd for the epilogue's stores: box = 32 rows x 32 columns, 64-byte swizzle.
 static int make_map_store(CUtensorMap* map, const void* base, int bf16, int64_t rows, int64_t cols, int64_t ld) {
   EncodeTiledFn fn = encode_fn();
@@ -313,8 +388,8 @@ static int make_map_store(CUtensorMap* map, const void* base, int bf16, int64_t 
 
 template <typename T, int BN>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, int use_tma_store, void* D,
-                       const void* bias, int M, int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, int* error_flag,
-                       cudaStream_t st) {
+                       const void* bias, int M, int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, float* ws, int a3d,
+                       int b3d, int* error_flag, cudaStream_t st) {
   using Cfg = TileCfg<BN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -323,19 +398,46 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
     attr_set = true;
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_tn_kernel<T, BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ma, mb, md, use_tma_store, (T*)D, (const T*)bias, M, N, K,
-                                                                     ldd, act, bf16, a_mn, b_mn,
-                                                                     make_fastdiv((uint32_t)((M + BM - 1) / BM)), error_flag);
+  const int num_k = (K + BK - 1) / BK;
+  // Split-K when the output has too few tiles to occupy the SMs and a workspace was given: every k-range adds its partial
+  // tile to the zeroed fp32 workspace, a second kernel applies bias / activation and converts.
+  int ksplit = 1;
+  if (ws != nullptr && tiles * 10 < sm_count() * 7 && (N % 8) == 0 && (ldd % 8) == 0) {
+    ksplit = sm_count() / tiles;
+    if (ksplit > num_k / 4) ksplit = num_k / 4;
+    if (ksplit < 1) ksplit = 1;
+  }
+  int ksteps_per = (num_k + ksplit - 1) / ksplit;
+  ksplit = (num_k + ksteps_per - 1) / ksteps_per;
+  float* kws = ksplit > 1 ? ws : nullptr;
+  if (kws) {
+    cudaError_t rc = cudaMemsetAsync(kws, 0, (size_t)M * N * sizeof(float), st);
+    if (rc != cudaSuccess) return (int)rc;
+  }
+  const long units = (long)tiles * ksplit;
+  const int grid = units < sm_count() ? (int)units : sm_count();
+  gemm_tn_kernel<T, BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ma, mb, md, kws ? 0 : use_tma_store, (T*)D, (const T*)bias, M,
+                                                                     N, K, ldd, act, bf16, a_mn, b_mn,
+                                                                     make_fastdiv((uint32_t)((M + BM - 1) / BM)), ksplit,
+                                                                     ksteps_per, make_fastdiv((uint32_t)tiles), kws, a3d, b3d, error_flag);
+  if (kws) {
+    const int64_t total = (int64_t)M * (N / 8);
+    const int fgrid = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
+    gemm_splitk_finish_kernel<T><<<fgrid, 256, 0, st>>>(kws, (const T*)bias, (T*)D, M, N, ldd, act);
+  }
   return (int)cudaGetLastError();
 }
 
-// Tile width: the widest tile that still gives every SM work; narrow outputs take the narrow tile.
+// Tile width: the widest tile that still gives every SM work, or the widest tile with split-K when the output has too
+// few tiles for the SMs anyway; narrow outputs take the narrow tile.  (A 192-wide tile is compiled but not selected: it
+// measured no faster than 128 or 256 on the shapes where it divides N.)
 static int pick_bn(int M, int N) {
-  const int tm = (M + BM - 1) / BM;
+  const long tm = (M + BM - 1) / BM;
   if (N <= 64) return 64;
   if (N <= 128) return 128;
-  if ((int64_t)tm * ((N + 255) / 256) >= sm_count()) return 256;
+  const long tiles256 = tm * ((N + 255) / 256);
+  if (tiles256 >= sm_count()) return 256;
+  if (tiles256 * 10 < (long)sm_count() * 7) return 256;      // split-K fills the machine
   return 128;
 }
 
@@ -347,8 +449,8 @@ using namespace mxb;
 // lda.  b_mn = 0: B is [N, K]; b_mn = 1: B is [K, N]; row pitch ldb.  ldd: row pitch of D.  All pitches in elements.
 // Requirements: base pointers 16-byte aligned, lda and ldb multiples of 8 elements.  `error_flag` is a device int set
 // to 1 when a CTA gave up waiting (the output is then incomplete).
-MXB_EXPORT int mxb_gemm(int dtype, const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda,
-                        int ldb, int ldd, int a_mn, int b_mn, int act, int* error_flag, void* stream) {
+static int gemm_run(int dtype, const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda, int ldb,
+                    int ldd, int a_mn, int b_mn, int act, float* ws, int* error_flag, void* stream) {
   if (dtype != kF16 && dtype != kBF16) return -1;
   if (M < 1 || N < 1 || K < 1) return -2;
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A % 16) || ((uintptr_t)B % 16) || ((uintptr_t)D % 16)) return -3;
@@ -356,9 +458,12 @@ MXB_EXPORT int mxb_gemm(int dtype, const void* A, const void* B, void* D, const 
   const int bf16 = dtype == kBF16;
   const int bn = pick_bn(M, N);
   CUtensorMap ma, mb;
-  int rc = a_mn ? make_map_mn(&ma, A, bf16, K, M, lda) : make_map(&ma, A, bf16, M, K, lda, BM);
+  const int a3d = a_mn && (M % 64) == 0, b3d = b_mn && (N % 64) == 0;
+  int rc = a3d ? make_map_mn3(&ma, A, bf16, K, M, lda, BM / 64)
+               : (a_mn ? make_map_mn(&ma, A, bf16, K, M, lda) : make_map(&ma, A, bf16, M, K, lda, BM));
   if (rc) return rc;
-  rc = b_mn ? make_map_mn(&mb, B, bf16, K, N, ldb) : make_map(&mb, B, bf16, N, K, ldb, bn);
+  rc = b3d ? make_map_mn3(&mb, B, bf16, K, N, ldb, bn / 64)
+           : (b_mn ? make_map_mn(&mb, B, bf16, K, N, ldb) : make_map(&mb, B, bf16, N, K, ldb, bn));
   if (rc) return rc;
   // the epilogue stores through the copy engine when D meets a tensor map's rules (16-byte row pitch); otherwise with
   // per-thread stores
@@ -370,11 +475,33 @@ MXB_EXPORT int mxb_gemm(int dtype, const void* A, const void* B, void* D, const 
   }
   cudaStream_t st = (cudaStream_t)stream;
 #define MXB_GEMM(T)                                                                                                        \
-  (bn == 256 ? launch_gemm<T, 256>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, error_flag, st)  \
-   : bn == 128 ? launch_gemm<T, 128>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, error_flag, st) \
-               : launch_gemm<T, 64>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, error_flag, st))
+  (bn == 256 ? launch_gemm<T, 256>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, ws, a3d, b3d, error_flag, st)  \
+   : bn == 192 ? launch_gemm<T, 192>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, ws, a3d, b3d, error_flag, st) \
+   : bn == 128 ? launch_gemm<T, 128>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, ws, a3d, b3d, error_flag, st) \
+               : launch_gemm<T, 64>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, ws, a3d, b3d, error_flag, st))
   return bf16 ? MXB_GEMM(__nv_bfloat16) : MXB_GEMM(__half);
 #undef MXB_GEMM
+}
+
+MXB_EXPORT int mxb_gemm(int dtype, const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda,
+                        int ldb, int ldd, int a_mn, int b_mn, int act, int* error_flag, void* stream) {
+  return gemm_run(dtype, A, B, D, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, act, nullptr, error_flag, stream);
+}
+
+// The same product with an fp32 workspace of M*N floats: outputs with too few tiles for the SMs (a weight gradient with
+// a long contraction) are then computed as split-K partial products added into the workspace.
+MXB_EXPORT int mxb_gemm_ws(int dtype, const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda,
+                           int ldb, int ldd, int a_mn, int b_mn, int act, float* workspace, int* error_flag, void* stream) {
+  if (workspace && ((uintptr_t)workspace % 16)) return -3;
+  return gemm_run(dtype, A, B, D, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, act, workspace, error_flag, stream);
+}
+
+// Whether mxb_gemm_ws would split the contraction of this shape (so that callers allocate the workspace only then).
+MXB_EXPORT int mxb_gemm_wants_workspace(int M, int N, int K) {
+  const int bn = pick_bn(M, N);
+  const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+  const int num_k = (K + BK - 1) / BK;
+  return (tiles * 10 < sm_count() * 7 && (N % 8) == 0 && num_k >= 8) ? 1 : 0;
 }
 
 // D[M,N] = act(A[M,K] * B[N,K]^T + bias): both operands K-major.

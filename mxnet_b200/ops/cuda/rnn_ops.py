@@ -88,7 +88,7 @@ class _LSTMLayer(torch.autograd.Function):
         dx = _mm(dg2, w_ih, False, True).reshape(T, B, I) if ctx.needs_input_grad[0] else None   # dg[TB,4H] . w_ih[4H,I]
         dw_ih = _mm(dg2, x.reshape(T * B, I), True, True)                                         # dg^T . x
         dw_hh = _mm(dg2, hprev, True, True)                                                        # dg^T . h_{t-1}
-        db = dg2.float().sum(0)
+        db = dg2.sum(0, dtype=torch.float32)
         return dx, dw_ih, dw_hh, db.to(ctx.bias_dtypes[0]), db.to(ctx.bias_dtypes[1]), dh0, dc0, None
 
 

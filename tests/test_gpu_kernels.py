@@ -227,6 +227,24 @@ def test_tcgen05_gemm_operand_layouts(a_mn, b_mn, M, N, K, dtype):
     _close(d, ref, *tol)
 
 
+@pytest.mark.parametrize('M,N,K', [(768, 768, 8192), (256, 136, 4096), (128, 64, 2048)])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_tcgen05_gemm_split_k_weight_gradient_shapes(M, N, K, dtype):
+    """Few output tiles and a long contraction: the kernel splits K over the SMs through an fp32 workspace."""
+    from mxnet_b200.ops import cuda
+    from mxnet_b200.ops.cuda import gemm_ops
+    assert cuda.lib().mxb_gemm_wants_workspace(M, N, K) == 1
+    torch.manual_seed(9)
+    a = (torch.randn(K, M, device=_dev()) / 8).to(dtype)          # MN-major operands, as in dW = dY^T X
+    b = (torch.randn(K, N, device=_dev()) / 8).to(dtype)
+    bias = torch.randn(N, device=_dev()).to(dtype)
+    d = gemm_ops.gemm(a, b, True, True, bias, 'relu')
+    gemm_ops.check_errors()
+    ref = torch.relu(a.float().t() @ b.float() + bias.float())
+    tol = (1e-2, 2e-2) if dtype == torch.float16 else (3e-2, 8e-2)
+    _close(d, ref, *tol)
+
+
 def test_linear_autograd_through_tcgen05():
     from mxnet_b200.ops.cuda import gemm_ops
     torch.manual_seed(6)
