@@ -117,6 +117,44 @@ def case_attention(ctx, dtype, small, dropout=0.0):
     return dict(inputs=[qkv], fn=fn, fwd_flops=fl, bwd_flops=2.5 * fl, fwd_bytes=nb * 4 / 3, bwd_bytes=nb * (2 + 2 / 3))
 
 
+def case_gelu(ctx, dtype, small):
+    rows, c = (8192, 3072) if small else (65536, 3072)
+    x = _rand((rows, c), ctx, dtype)
+    nb = x.size * _esize(dtype)
+    return dict(inputs=[x], fn=lambda x: nd.LeakyReLU(x, act_type='gelu'), fwd_bytes=2 * nb, bwd_bytes=3 * nb)
+
+
+def case_dropout_add(ctx, dtype, small):
+    rows, c = (8192, 768) if small else (262144, 768)
+    x, r = _rand((rows, c), ctx, dtype), _rand((rows, c), ctx, dtype)
+    nb = x.size * _esize(dtype)
+
+    def fn(x, r):
+        with mx.autograd.train_mode():
+            return nd.contrib.dropout_add(x, r, p=0.1)
+    return dict(inputs=[x, r], fn=fn, fwd_bytes=3 * nb, bwd_bytes=2 * nb)
+
+
+def case_embedding(ctx, dtype, small):
+    n, rows, d = (8192, 30522, 768) if small else (65536, 30522, 768)
+    idx = nd.array(np.random.RandomState(0).randint(0, rows, (n,)), ctx=ctx, dtype='int32')
+    w = _rand((rows, d), ctx, dtype)
+    nb = n * d * _esize(dtype)
+    # forward: gather n rows, write n rows; backward: read n rows of dy, zero and write the table gradient
+    return dict(inputs=[w], fn=lambda w: nd.Embedding(idx, w, input_dim=rows, output_dim=d), fwd_bytes=2 * nb,
+                bwd_bytes=nb + 2 * rows * d * _esize(dtype))
+
+
+def case_avgpool(ctx, dtype, small):
+    n = 256
+    x = _rand((n, 7, 7, 2048), ctx, dtype)
+    nb = x.size * _esize(dtype)
+
+    def fn(x):
+        return nd.Pooling(x, global_pool=True, pool_type='avg', kernel=(1, 1), layout='NHWC')
+    return dict(inputs=[x], fn=fn, fwd_bytes=nb * (1 + 1 / 49), bwd_bytes=nb * (1 + 1 / 49))
+
+
 def case_add(ctx, dtype, small):
     n = 2 ** 24 if small else 2 ** 28
     a, b = _rand((n,), ctx, dtype), _rand((n,), ctx, dtype)
@@ -138,6 +176,10 @@ CASES = {
     'MaxPool3x3s2': case_maxpool,
     'fused_self_attention': case_attention,
     'elemwise_add': case_add,
+    'GELU': case_gelu,
+    'dropout_add': case_dropout_add,
+    'Embedding': case_embedding,
+    'GlobalAvgPool': case_avgpool,
 }
 
 

@@ -23,7 +23,7 @@ _tuned = {}          # (direction, dtype, geometry) -> True when the in-tree ker
 # rate credited to the separate BatchNorm statistics pass that the forward epilogue replaces, bytes per microsecond
 # (the copy bandwidth: a conservative credit, the measured pass is slower)
 _BN_REDUCE_BYTES_PER_US = 6.5e6
-_MARGIN = 0.97       # the in-tree kernel must be at least 3 % faster to be chosen
+_MARGIN = 1.0        # the in-tree kernel is chosen when it is not slower
 _flush = {}
 
 

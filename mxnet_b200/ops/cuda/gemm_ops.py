@@ -12,7 +12,7 @@ _ACT = {None: 0, 'relu': 1, 'gelu': 2}
 _err = {}
 _tuned = {}          # (product, dtype, M, N, K, bias, act) -> True when the in-tree kernel won
 _flush = {}
-_MARGIN = 0.98
+_MARGIN = 1.02      # ties (within 2 %) go to the in-tree kernel
 
 
 def _autotune():
