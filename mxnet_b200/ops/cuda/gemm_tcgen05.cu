@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_d, int use_tma_store, T* __restrict__ D, const T* __restrict__ bias, int M,
                int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, const FastDiv fd_tiles_m,
-               int ksplit, int ksteps_per, const FastDiv fd_num_tiles, float* __restrict__ ws, int a3d, int b3d,
+               int ksplit, int ksteps_per, int full_tiles, const FastDiv fd_rem_tiles, float* __restrict__ ws, int a3d, int b3d,
                int* __restrict__ error_flag) {
   using Cfg = TileCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
@@ -78,8 +78,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int num_k = (K + BK - 1) / BK;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
-  // Split-K: a work unit is (k-range, tile); with ksplit == 1 a unit is a tile.  Units of one k-range are adjacent.
-  const int num_units = num_tiles * ksplit;
+  // Work units: the first `full_tiles` tiles are computed whole; each of the remaining tiles (the last, partial round of
+  // the persistent grid, or all tiles of a small output) is split into `ksplit` k-ranges whose partial products are
+  // added into the fp32 workspace.  Units of one k-range are adjacent.
+  const int rem_tiles = num_tiles - full_tiles;
+  const int num_units = full_tiles + rem_tiles * ksplit;
   constexpr uint32_t kTmemCols = Cfg::TMEM_COLS;     // two accumulators; a power of two >= 32
 
   if (threadIdx.x == 0) {
@@ -110,11 +113,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t ph = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < num_units && ok && !*abort_flag; unit += gridDim.x) {
-        uint32_t ks_u, tile_u, tile_n_u, tile_m_u;
-        fd_divmod((uint32_t)unit, fd_num_tiles, &ks_u, &tile_u);
+        uint32_t ks_u = 0, tile_u = (uint32_t)unit, tile_n_u, tile_m_u;
+        if (unit >= full_tiles) {
+          fd_divmod((uint32_t)(unit - full_tiles), fd_rem_tiles, &ks_u, &tile_u);
+          tile_u += (uint32_t)full_tiles;
+        }
         fd_divmod(tile_u, fd_tiles_m, &tile_n_u, &tile_m_u);
         const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u;
-        const int k0 = (int)ks_u * ksteps_per, k1 = min(num_k, k0 + ksteps_per);
+        const int k0 = unit >= full_tiles ? (int)ks_u * ksteps_per : 0;
+        const int k1 = unit >= full_tiles ? min(num_k, k0 + ksteps_per) : num_k;
         for (int kt = k0; kt < k1; ++kt) {
           if (!mbar_wait(&empty[st], ph ^ 1u)) { *abort_flag = 1; ok = false; break; }
           mbar_expect_tx(&full[st], A_BYTES + B_BYTES);
@@ -156,8 +163,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t ph = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < num_units && ok && !*abort_flag; unit += gridDim.x, ++t) {
-        const int ks = (int)fd_div((uint32_t)unit, fd_num_tiles);
-        const int k0 = ks * ksteps_per, k1 = min(num_k, k0 + ksteps_per);
+        const int ks = unit >= full_tiles ? (int)fd_div((uint32_t)(unit - full_tiles), fd_rem_tiles) : 0;
+        const int k0 = unit >= full_tiles ? ks * ksteps_per : 0;
+        const int k1 = unit >= full_tiles ? min(num_k, k0 + ksteps_per) : num_k;
         const int buf = t & 1;
         // wait until the epilogue has drained this accumulator (its first use passes immediately)
         if (!mbar_wait(&acc_empty[buf], (((uint32_t)t >> 1) & 1u) ^ 1u)) { *abort_flag = 1; break; }
@@ -186,10 +194,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint8_t* stg = sStg + q * 2048;       // this warp's staging tile: 32 rows x 64 bytes, 64-byte swizzle
     int t = 0;
     for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++t) {
-      uint32_t ks_u, tile_u, tile_n_u, tile_m_u;
-      fd_divmod((uint32_t)unit, fd_num_tiles, &ks_u, &tile_u);
+      uint32_t ks_u = 0, tile_u = (uint32_t)unit, tile_n_u, tile_m_u;
+      if (unit >= full_tiles) {
+        fd_divmod((uint32_t)(unit - full_tiles), fd_rem_tiles, &ks_u, &tile_u);
+        tile_u += (uint32_t)full_tiles;
+      }
       fd_divmod(tile_u, fd_tiles_m, &tile_n_u, &tile_m_u);
       const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u;
+      const bool to_ws = ws != nullptr && unit >= full_tiles;
       const int buf = t & 1;
       const bool ready = mbar_wait(&acc_full[buf], ((uint32_t)t >> 1) & 1u);
       if (!ready) *abort_flag = 1;
@@ -225,7 +237,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
         tmem_wait_ld32(r);
-        if (ws != nullptr) {
+        if (to_ws) {
           // split-K: add this k-range's partial tile to the fp32 workspace (bias and activation are applied by the
           // finishing kernel once every k-range has been added)
           if (row < M && col0 < N) {
@@ -314,17 +326,27 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
-// Split-K finish: D = act(ws + bias), one thread per 8 columns of a row.
-template <typename T>
+// Split-K helpers over the tiles [first_tile, first_tile + gridDim.x) of a 128 x BN tiling (tile = tile_n * tiles_m +
+// tile_m): `zero` clears their region of the fp32 workspace before the GEMM, `finish` computes D = act(ws + bias) there
+// afterwards.  One CTA per tile, one thread per 8 columns of a row.
+template <typename T, bool kFinish>
 __global__ void __launch_bounds__(256)
-gemm_splitk_finish_kernel(const float* __restrict__ ws, const T* __restrict__ bias, T* __restrict__ D, int M, int N, int ldd,
-                          int act) {
-  const int nv = N / 8;
-  const int64_t total = (int64_t)M * nv;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int row = (int)(i / nv), c = (int)(i % nv) * 8;
-    const float4 a = *reinterpret_cast<const float4*>(ws + (size_t)row * N + c);
-    const float4 b = *reinterpret_cast<const float4*>(ws + (size_t)row * N + c + 4);
+gemm_splitk_tiles_kernel(float* __restrict__ ws, const T* __restrict__ bias, T* __restrict__ D, int M, int N, int ldd, int act,
+                         int bn, int tiles_m, int first_tile) {
+  const int tile = first_tile + blockIdx.x;
+  const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+  const int vec_per_row = bn / 8;
+  for (int i = threadIdx.x; i < BM * vec_per_row; i += blockDim.x) {
+    const int row = tile_m * BM + i / vec_per_row, c = tile_n * bn + (i % vec_per_row) * 8;
+    if (row >= M || c >= N) continue;
+    float* w = ws + (size_t)row * N + c;
+    if (!kFinish) {
+      *reinterpret_cast<float4*>(w) = make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(w + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      continue;
+    }
+    const float4 a = *reinterpret_cast<const float4*>(w);
+    const float4 b = *reinterpret_cast<const float4*>(w + 4);
     float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     Vec16<T> o;
 #pragma unroll
@@ -397,34 +419,37 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
     if (rc != cudaSuccess) return (int)rc;
     attr_set = true;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int tiles_m = (M + BM - 1) / BM;
+  const int tiles = tiles_m * ((N + BN - 1) / BN);
   const int num_k = (K + BK - 1) / BK;
-  // Split-K when the output has too few tiles to occupy the SMs and a workspace was given: every k-range adds its partial
-  // tile to the zeroed fp32 workspace, a second kernel applies bias / activation and converts.
-  int ksplit = 1;
-  if (ws != nullptr && tiles * 10 < sm_count() * 7 && (N % 8) == 0 && (ldd % 8) == 0) {
-    ksplit = sm_count() / tiles;
-    if (ksplit > num_k / 4) ksplit = num_k / 4;
-    if (ksplit < 1) ksplit = 1;
+  // Split-K (needs the workspace) when the output has too few tiles to occupy the SMs.  The kernel can also split only
+  // the tiles of a last, partial round (full_tiles > 0); measured on N = 768 outputs of 8192 rows that was slower than
+  // leaving the round partial (the fp32 reductions and the two helper launches cost more than the idle SMs), so the
+  // host does not select it.
+  int full_tiles = tiles, ksplit = 1;
+  const int sms = sm_count();
+  if (ws != nullptr && (N % 8) == 0 && (ldd % 8) == 0 && num_k >= 8) {
+    if (tiles * 10 < sms * 7) full_tiles = 0;
+    if (full_tiles < tiles) {
+      ksplit = sms / (tiles - full_tiles);
+      if (ksplit > num_k / 4) ksplit = num_k / 4;
+      if (ksplit < 2) { ksplit = 1; full_tiles = tiles; }
+    }
   }
   int ksteps_per = (num_k + ksplit - 1) / ksplit;
   ksplit = (num_k + ksteps_per - 1) / ksteps_per;
-  float* kws = ksplit > 1 ? ws : nullptr;
-  if (kws) {
-    cudaError_t rc = cudaMemsetAsync(kws, 0, (size_t)M * N * sizeof(float), st);
-    if (rc != cudaSuccess) return (int)rc;
-  }
-  const long units = (long)tiles * ksplit;
-  const int grid = units < sm_count() ? (int)units : sm_count();
-  gemm_tn_kernel<T, BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ma, mb, md, kws ? 0 : use_tma_store, (T*)D, (const T*)bias, M,
-                                                                     N, K, ldd, act, bf16, a_mn, b_mn,
-                                                                     make_fastdiv((uint32_t)((M + BM - 1) / BM)), ksplit,
-                                                                     ksteps_per, make_fastdiv((uint32_t)tiles), kws, a3d, b3d, error_flag);
-  if (kws) {
-    const int64_t total = (int64_t)M * (N / 8);
-    const int fgrid = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
-    gemm_splitk_finish_kernel<T><<<fgrid, 256, 0, st>>>(kws, (const T*)bias, (T*)D, M, N, ldd, act);
-  }
+  if (ksplit < 2) { ksplit = 1; full_tiles = tiles; ksteps_per = num_k; }
+  const int rem_tiles = tiles - full_tiles;
+  float* kws = rem_tiles > 0 ? ws : nullptr;
+  if (kws) gemm_splitk_tiles_kernel<T, false><<<rem_tiles, 256, 0, st>>>(kws, nullptr, nullptr, M, N, ldd, act, BN, tiles_m, full_tiles);
+  const long units = (long)full_tiles + (long)rem_tiles * ksplit;
+  const int grid = units < sms ? (int)units : sms;
+  gemm_tn_kernel<T, BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ma, mb, md, use_tma_store, (T*)D, (const T*)bias, M, N, K, ldd,
+                                                                     act, bf16, a_mn, b_mn, make_fastdiv((uint32_t)tiles_m), ksplit,
+                                                                     ksteps_per, full_tiles,
+                                                                     make_fastdiv((uint32_t)(rem_tiles > 0 ? rem_tiles : 1)), kws, a3d,
+                                                                     b3d, error_flag);
+  if (kws) gemm_splitk_tiles_kernel<T, true><<<rem_tiles, 256, 0, st>>>(kws, (const T*)bias, (T*)D, M, N, ldd, act, BN, tiles_m, full_tiles);
   return (int)cudaGetLastError();
 }
 
@@ -501,7 +526,8 @@ MXB_EXPORT int mxb_gemm_wants_workspace(int M, int N, int K) {
   const int bn = pick_bn(M, N);
   const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
   const int num_k = (K + BK - 1) / BK;
-  return (tiles * 10 < sm_count() * 7 && (N % 8) == 0 && num_k >= 8) ? 1 : 0;
+  if ((N % 8) != 0 || num_k < 8) return 0;
+  return tiles * 10 < sm_count() * 7 ? 1 : 0;
 }
 
 // D[M,N] = act(A[M,K] * B[N,K]^T + bias): both operands K-major.
