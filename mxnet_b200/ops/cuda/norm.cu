@@ -102,9 +102,10 @@ bn_reduce_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __r
   }
 }
 
-// Sum the per-CTA partials of 32 channels with a (32 x 16) thread block: coalesced along the channel
-// axis, 16-way split along the partial axis, fixed-order tree in shared memory (deterministic).
-constexpr int kFinX = 32, kFinY = 32;
+// Sum the per-CTA partials of 8 channels with an (8 x 128) thread block: a few hundred partial rows are one or two
+// independent loads per thread, so the kernel is one memory round trip instead of a dependent chain, and C / 8 blocks
+// spread it over the SMs; fixed-order tree in shared memory (deterministic).
+constexpr int kFinX = 8, kFinY = 128;
 __device__ __forceinline__ bool finalize_sums(const float* __restrict__ partial, int nblocks, int C, float& s, float& q) {
   __shared__ float red[2][kFinY][kFinX];
   const int c = blockIdx.x * kFinX + threadIdx.x;
@@ -128,10 +129,19 @@ __device__ __forceinline__ bool finalize_sums(const float* __restrict__ partial,
   red[0][threadIdx.y][threadIdx.x] = a;
   red[1][threadIdx.y][threadIdx.x] = b;
   __syncthreads();
+  // 128 -> 32 rows in parallel, then one thread per channel adds the 32 rows in order
+  if (threadIdx.y < 32) {
+    const int y = threadIdx.y;
+    red[0][y][threadIdx.x] = (red[0][y][threadIdx.x] + red[0][y + 32][threadIdx.x]) +
+                             (red[0][y + 64][threadIdx.x] + red[0][y + 96][threadIdx.x]);
+    red[1][y][threadIdx.x] = (red[1][y][threadIdx.x] + red[1][y + 32][threadIdx.x]) +
+                             (red[1][y + 64][threadIdx.x] + red[1][y + 96][threadIdx.x]);
+  }
+  __syncthreads();
   if (threadIdx.y != 0 || c >= C) return false;
   s = 0.f; q = 0.f;
 #pragma unroll
-  for (int k = 0; k < kFinY; ++k) { s += red[0][k][threadIdx.x]; q += red[1][k][threadIdx.x]; }
+  for (int k = 0; k < 32; ++k) { s += red[0][k][threadIdx.x]; q += red[1][k][threadIdx.x]; }
   return true;
 }
 
