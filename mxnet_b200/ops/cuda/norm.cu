@@ -397,6 +397,138 @@ ln_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const float* __
   }
 }
 
+// Warp-per-row variants for half-precision rows of up to 1024 columns (C a multiple of 8): lane l owns the 16-byte
+// vectors l, l + 32, ... of the row (NV of them), statistics are warp shuffles, so a row costs no block-wide barrier;
+// eight rows are in flight per CTA.  The backward kernel keeps dgamma / dbeta per lane in registers over all rows of
+// the warp and adds the eight warps of a CTA in a fixed order in shared memory before writing the CTA's partial row.
+constexpr int kLnWarps = 8;
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(kLnWarps * 32)
+ln_fwd_warp_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta, T* __restrict__ y,
+                   float* __restrict__ mean_out, float* __restrict__ rstd_out, int64_t rows, int C, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = C >> 3;
+  for (int64_t row = (int64_t)blockIdx.x * kLnWarps + warp; row < rows; row += (int64_t)gridDim.x * kLnWarps) {
+    const T* xr = x + row * C;
+    float v[NV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        const Vec16<T> a = ld16(xr + vi * 8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[k][j] = Cvt<T>::to_f(a.v[j]); s += v[k][j]; }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[k][j] = 0.f;
+      }
+    }
+    const float mean = warp_sum(s) / (float)C;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (lane + 32 * k < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float d = v[k][j] - mean; q += d * d; }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(q) / (float)C + eps);
+    if (lane == 0) { mean_out[row] = mean; rstd_out[row] = rstd; }
+    T* yr = y + row * C;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        const float4 g0 = *reinterpret_cast<const float4*>(gamma + vi * 8), g1 = *reinterpret_cast<const float4*>(gamma + vi * 8 + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(beta + vi * 8), b1 = *reinterpret_cast<const float4*>(beta + vi * 8 + 4);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.v[j] = Cvt<T>::from_f((v[k][j] - mean) * rstd * gg[j] + bb[j]);
+        st16(yr + vi * 8, o);
+      }
+    }
+  }
+}
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(kLnWarps * 32, 2)
+ln_bwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ dy, const float* __restrict__ gamma,
+                   const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
+                   float* __restrict__ partial /*[grid][2][C]*/, int64_t rows, int C) {
+  extern __shared__ float ln_acc[];          // [2][C]: dgamma | dbeta of this CTA
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = C >> 3;
+  float dg[NV][8], db[NV][8];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dg[k][j] = 0.f; db[k][j] = 0.f; }
+  }
+  for (int64_t row = (int64_t)blockIdx.x * kLnWarps + warp; row < rows; row += (int64_t)gridDim.x * kLnWarps) {
+    const T* xr = x + row * C;
+    const T* gr = dy + row * C;
+    const float mu = mean[row], rs = rstd[row];
+    float xh[NV][8], g[NV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        const Vec16<T> a = ld16(xr + vi * 8), d = ld16(gr + vi * 8);
+        const float4 g0 = *reinterpret_cast<const float4*>(gamma + vi * 8), g1 = *reinterpret_cast<const float4*>(gamma + vi * 8 + 4);
+        const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[k][j] = (Cvt<T>::to_f(a.v[j]) - mu) * rs;
+          const float dd = Cvt<T>::to_f(d.v[j]);
+          dg[k][j] += dd * xh[k][j];
+          db[k][j] += dd;
+          g[k][j] = dd * gm[j];
+          s1 += g[k][j];
+          s2 += g[k][j] * xh[k][j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { xh[k][j] = 0.f; g[k][j] = 0.f; }
+      }
+    }
+    s1 = warp_sum(s1) / (float)C;
+    s2 = warp_sum(s2) / (float)C;
+    T* dr = dx + row * C;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.v[j] = Cvt<T>::from_f(rs * (g[k][j] - s1 - xh[k][j] * s2));
+        st16(dr + vi * 8, o);
+      }
+    }
+  }
+  // the eight warps add their sums one after the other (fixed order) into the CTA's accumulators
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) ln_acc[i] = 0.f;
+  __syncthreads();
+  for (int w = 0; w < kLnWarps; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int vi = lane + 32 * k;
+        if (vi < nvec) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { ln_acc[vi * 8 + j] += dg[k][j]; ln_acc[C + vi * 8 + j] += db[k][j]; }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) partial[(int64_t)blockIdx.x * 2 * C + i] = ln_acc[i];
+}
+
 __global__ void __launch_bounds__(kFinX * kFinY)
 ln_bwd_finalize_kernel(const float* __restrict__ partial, int nblocks, int C, float* __restrict__ dgamma,
                        float* __restrict__ dbeta) {
@@ -475,9 +607,27 @@ MXB_EXPORT int mxb_bn_backward(int dtype, const void* x, const void* dy, const v
   return -1;
 }
 
+// rows of half-precision values with C % 8 == 0 and C <= 1024, 16-byte aligned: the warp-per-row kernels
+template <typename T>
+static bool ln_warp_ok(const void* x, const void* y, const float* gamma, const float* beta, int C) {
+  return sizeof(T) == 2 && (C % 8) == 0 && C <= 1024 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0 &&
+         ((uintptr_t)gamma % 16) == 0 && (beta == nullptr || ((uintptr_t)beta % 16) == 0);
+}
+inline int ln_warp_grid(int64_t rows) {
+  const int64_t want = (rows + kLnWarps - 1) / kLnWarps, cap = (int64_t)sm_count() * 4;
+  return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
+}
+
 template <typename T>
 static int ln_fwd_t(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd, int64_t rows,
                     int C, float eps, cudaStream_t st) {
+  if constexpr (sizeof(T) == 2) if (ln_warp_ok<T>(x, y, gamma, beta, C)) {
+    const int grid = ln_warp_grid(rows), nv = (C / 8 + 31) / 32;
+#define MXB_LN_FWD(NV) ln_fwd_warp_kernel<T, NV><<<grid, kLnWarps * 32, 0, st>>>((const T*)x, gamma, beta, (T*)y, mean, rstd, rows, C, eps)
+    if (nv == 1) MXB_LN_FWD(1); else if (nv == 2) MXB_LN_FWD(2); else if (nv == 3) MXB_LN_FWD(3); else MXB_LN_FWD(4);
+#undef MXB_LN_FWD
+    return (int)cudaGetLastError();
+  }
   ln_fwd_kernel<T><<<ln_grid(rows), kLnThreads, 0, st>>>((const T*)x, gamma, beta, (T*)y, mean, rstd, rows, C, eps);
   return (int)cudaGetLastError();
 }
@@ -485,7 +635,20 @@ template <typename T>
 static int ln_bwd_t(const void* x, const void* dy, const float* gamma, const float* mean, const float* rstd, void* dx,
                     float* dgamma, float* dbeta, float* scratch, int64_t rows, int C, cudaStream_t st) {
   int grid = ln_grid(rows);
-  ln_bwd_kernel<T><<<grid, kLnThreads, 0, st>>>((const T*)x, (const T*)dy, gamma, mean, rstd, (T*)dx, scratch, rows, C);
+  bool warp_path = false;
+  if constexpr (sizeof(T) == 2) warp_path = ln_warp_ok<T>(x, dx, gamma, nullptr, C) && ((uintptr_t)dy % 16) == 0;
+  if constexpr (sizeof(T) == 2) if (warp_path) {
+    // at most ln_grid(rows) CTAs, so the scratch sized for the block-per-row kernel is large enough
+    const int wgrid = ln_warp_grid(rows) < grid ? ln_warp_grid(rows) : grid;
+    const int nv = (C / 8 + 31) / 32;
+    const size_t smem = (size_t)2 * C * sizeof(float);
+#define MXB_LN_BWD(NV) ln_bwd_warp_kernel<T, NV><<<wgrid, kLnWarps * 32, smem, st>>>((const T*)x, (const T*)dy, gamma, mean, rstd, (T*)dx, scratch, rows, C)
+    if (nv == 1) MXB_LN_BWD(1); else if (nv == 2) MXB_LN_BWD(2); else if (nv == 3) MXB_LN_BWD(3); else MXB_LN_BWD(4);
+#undef MXB_LN_BWD
+    grid = wgrid;
+  }
+  if (!warp_path)
+    ln_bwd_kernel<T><<<grid, kLnThreads, 0, st>>>((const T*)x, (const T*)dy, gamma, mean, rstd, (T*)dx, scratch, rows, C);
   ln_bwd_finalize_kernel<<<(C + kFinX - 1) / kFinX, dim3(kFinX, kFinY), 0, st>>>(scratch, grid, C, dgamma, dbeta);
   return (int)cudaGetLastError();
 }

@@ -76,7 +76,7 @@ def test_batchnorm_inference_uses_running_stats():
 
 
 # ---------------------------------------------------------------------------------------- LayerNorm
-@pytest.mark.parametrize('shape', [(3, 128, 768), (17, 33), (5, 2048)])
+@pytest.mark.parametrize('shape', [(3, 128, 768), (17, 33), (5, 2048), (4099, 768), (1000, 1024), (513, 264), (70, 8)])
 @pytest.mark.parametrize('dtype', [torch.float32, torch.float16, torch.bfloat16])
 def test_layernorm(shape, dtype):
     from mxnet_b200.ops.cuda import norm_ops
