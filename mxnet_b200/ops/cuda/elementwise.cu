@@ -264,36 +264,56 @@ embedding_bwd_stage2_kernel(const I* __restrict__ sorted, const float* __restric
                             int D, int64_t rows, int accumulate) {
   constexpr int V = Vec16<T>::N;
   const int L = D / V;
+  const int groups = (L + 31) / 32;              // a warp handles 32 vectors of one run: `groups` warps per block
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t nblocks = (n + kEmbBlock - 1) / kEmbBlock;
-  for (int64_t b = (int64_t)blockIdx.x * (kEwThreads / 32) + warp; b < nblocks; b += (int64_t)gridDim.x * (kEwThreads / 32)) {
+  const int64_t items = nblocks * groups;
+  for (int64_t it = (int64_t)blockIdx.x * (kEwThreads / 32) + warp; it < items; it += (int64_t)gridDim.x * (kEwThreads / 32)) {
+    const int64_t b = it / groups;
+    const int c = (int)(it % groups) * 32 + lane;
     const int64_t p0 = b * kEmbBlock, p1 = p0 + kEmbBlock;
     if (p1 >= n) continue;
     const int64_t k = (int64_t)sorted[p1 - 1];
     if ((int64_t)sorted[p1] != k) continue;                        // the last run of this block ends here
     // does that run start in this block?  (otherwise an earlier block owns it)
     if ((int64_t)sorted[p0] == k && p0 > 0 && (int64_t)sorted[p0 - 1] == k) continue;
+    int64_t b_end = b + 1;                                           // blocks b+1 .. b_end-1 begin with this run
+    while (b_end < nblocks && (int64_t)sorted[b_end * kEmbBlock] == k) ++b_end;
+    if (c >= L) continue;
     const int64_t kk = k < 0 ? 0 : (k >= rows ? rows - 1 : k);
-    for (int c = lane; c < L; c += 32) {
-      float acc[V];
-      const float* src = partial + (b * 2 + 1) * (int64_t)D + c * V;
+    float acc[V];
+    const float* src = partial + (b * 2 + 1) * (int64_t)D + c * V;
 #pragma unroll
-      for (int j = 0; j < V; ++j) acc[j] = src[j];
-      for (int64_t b2 = b + 1; b2 < nblocks && (int64_t)sorted[b2 * kEmbBlock] == k; ++b2) {
-        const float* s2 = partial + (b2 * 2) * (int64_t)D + c * V;
+    for (int j = 0; j < V; ++j) acc[j] = src[j];
+    // the following blocks' partials: independent loads, added in block order
+    int64_t b2 = b + 1;
+    for (; b2 + 3 < b_end; b2 += 4) {
+      float t[4][V];
 #pragma unroll
-        for (int j = 0; j < V; ++j) acc[j] += s2[j];
+      for (int u = 0; u < 4; ++u) {
+        const float* s2 = partial + ((b2 + u) * 2) * (int64_t)D + c * V;
+#pragma unroll
+        for (int j = 0; j < V; ++j) t[u][j] = s2[j];
       }
-      if (accumulate) {
-        const Vec16<T> w = ld16(dw + kk * D + c * V);
 #pragma unroll
-        for (int j = 0; j < V; ++j) acc[j] += Cvt<T>::to_f(w.v[j]);
-      }
-      Vec16<T> o;
+      for (int u = 0; u < 4; ++u)
 #pragma unroll
-      for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(acc[j]);
-      st16(dw + kk * D + c * V, o);
+        for (int j = 0; j < V; ++j) acc[j] += t[u][j];
     }
+    for (; b2 < b_end; ++b2) {
+      const float* s2 = partial + (b2 * 2) * (int64_t)D + c * V;
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += s2[j];
+    }
+    if (accumulate) {
+      const Vec16<T> w = ld16(dw + kk * D + c * V);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += Cvt<T>::to_f(w.v[j]);
+    }
+    Vec16<T> o;
+#pragma unroll
+    for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(acc[j]);
+    st16(dw + kk * D + c * V, o);
   }
 }
 
@@ -384,6 +404,54 @@ __global__ void __launch_bounds__(kEwThreads) avgpool_bwd_kernel(const T* __rest
     for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(acc[j]);
     st16(dx + i * V, o);
   }
+}
+
+// ---------------------------------------------------------------------------------------------- column sums
+// out[c] = sum over rows of x[r, c] (the bias gradient of a FullyConnected layer; the reference's two-phase
+// AddBiasGradKernelPhase1/2, src/operator/nn/fully_connected-inl.h).  Stage 1: CTA (bx, by) sums a chunk of rows for 32
+// vector columns (8 row lanes x 32 column lanes, 16-byte loads, fp32 accumulation) into partial[by][c]; stage 2 adds the
+// partials in order.  Deterministic.
+constexpr int kColRowsLanes = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_stage1_kernel(const T* __restrict__ x, float* __restrict__ partial, int64_t rows, int C, int64_t rows_per_cta) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float red[kColRowsLanes][32][V + 1];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int L = C / V;
+  const int cv = blockIdx.x * 32 + tx;
+  const int64_t r0 = (int64_t)blockIdx.y * rows_per_cta, r1 = (r0 + rows_per_cta < rows) ? r0 + rows_per_cta : rows;
+  float acc[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) acc[j] = 0.f;
+  if (cv < L) {
+    for (int64_t r = r0 + ty; r < r1; r += kColRowsLanes) {
+      const Vec16<T> a = ld16(x + r * C + cv * V);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += Cvt<T>::to_f(a.v[j]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) red[ty][tx][j] = acc[j];
+  __syncthreads();
+  if (ty == 0 && cv < L) {
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      float t = 0.f;
+#pragma unroll
+      for (int k = 0; k < kColRowsLanes; ++k) t += red[k][tx][j];
+      partial[(int64_t)blockIdx.y * C + cv * V + j] = t;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int C, int ny) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float t = 0.f;
+  for (int k = 0; k < ny; ++k) t += partial[(int64_t)k * C + c];
+  out[c] = t;
 }
 
 // ---------------------------------------------------------------------------------------------- transpose
@@ -532,12 +600,13 @@ MXB_EXPORT int mxb_embedding_backward(int dtype, const void* sorted, int idx_is_
   return MXB_DISPATCH_FLOAT(dtype, {
     const int64_t nblocks = (n + kEmbBlock - 1) / kEmbBlock;
     const int grid = ew_grid(nblocks * 32);
+    const int grid2 = ew_grid(nblocks * 32 * ((D / Vec16<T>::N + 31) / 32));
     if (idx_is_64) {
       embedding_bwd_stage1_kernel<T, int64_t><<<grid, kEwThreads, 0, st>>>((const int64_t*)sorted, perm, (const T*)dy, (T*)dw, partial, n, D, rows, accumulate);
-      embedding_bwd_stage2_kernel<T, int64_t><<<grid, kEwThreads, 0, st>>>((const int64_t*)sorted, partial, (T*)dw, n, D, rows, accumulate);
+      embedding_bwd_stage2_kernel<T, int64_t><<<grid2, kEwThreads, 0, st>>>((const int64_t*)sorted, partial, (T*)dw, n, D, rows, accumulate);
     } else {
       embedding_bwd_stage1_kernel<T, int32_t><<<grid, kEwThreads, 0, st>>>((const int32_t*)sorted, perm, (const T*)dy, (T*)dw, partial, n, D, rows, accumulate);
-      embedding_bwd_stage2_kernel<T, int32_t><<<grid, kEwThreads, 0, st>>>((const int32_t*)sorted, partial, (T*)dw, n, D, rows, accumulate);
+      embedding_bwd_stage2_kernel<T, int32_t><<<grid2, kEwThreads, 0, st>>>((const int32_t*)sorted, partial, (T*)dw, n, D, rows, accumulate);
     }
     return (int)cudaGetLastError();
   });
@@ -587,4 +656,28 @@ MXB_EXPORT int mxb_transpose(int elem_bytes, const void* in, void* out, int batc
   else if (elem_bytes == 4) transpose_kernel<uint32_t><<<grid, block, 0, st>>>((const uint32_t*)in, (uint32_t*)out, R, C);
   else return -1;
   return (int)cudaGetLastError();
+}
+
+// Row chunks used by mxb_colsum for (rows, C): the partial buffer holds that many rows of C floats.
+MXB_EXPORT int mxb_colsum_chunks(int dtype, int64_t rows, int C) {
+  const int L = C / vec_of(dtype);
+  const int nx = (L + 31) / 32;
+  int64_t ny = ((int64_t)sm_count() * 4 + nx - 1) / nx;
+  if (ny > (rows + 63) / 64) ny = (rows + 63) / 64;          // at least 64 rows per chunk
+  return (int)(ny < 1 ? 1 : ny);
+}
+
+// out[C] (fp32) = column sums of x[rows, C]; partial: mxb_colsum_chunks(...) * C floats.
+MXB_EXPORT int mxb_colsum(int dtype, const void* x, float* partial, float* out, int64_t rows, int C, void* stream) {
+  if (rows < 1 || C < 1 || C % vec_of(dtype) || !aligned16(x) || !partial || !out) return -3;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int ny = mxb_colsum_chunks(dtype, rows, C);
+  const int64_t per = (rows + ny - 1) / ny;
+  return MXB_DISPATCH_FLOAT(dtype, {
+    const int L = C / Vec16<T>::N;
+    dim3 grid((L + 31) / 32, ny);
+    colsum_stage1_kernel<T><<<grid, 256, 0, st>>>((const T*)x, partial, rows, C, per);
+    colsum_stage2_kernel<<<(C + 255) / 256, 256, 0, st>>>(partial, out, C, ny);
+    return (int)cudaGetLastError();
+  });
 }

@@ -247,6 +247,24 @@ def global_avg_pool_nhwc(x):
     return _AvgPoolNHWC.apply(x, (x.shape[1], x.shape[2]), (1, 1), (0, 0), (1, 1), True)
 
 
+# ----------------------------------------------------------------------------------------------- column sums
+def colsum_supported(x):
+    return (x.is_cuda and x.dim() == 2 and x.dtype in DT and x.is_contiguous() and x.numel() > 0
+            and x.shape[1] % _vec(x) == 0 and x.data_ptr() % 16 == 0)
+
+
+def colsum(x):
+    """fp32 column sums of a 2-D tensor (a bias gradient), two deterministic stages."""
+    L = lib()
+    rows, C = x.shape
+    ny = L.mxb_colsum_chunks(dt(x), rows, C)
+    partial = torch.empty((ny, C), dtype=torch.float32, device=x.device)
+    out = torch.empty(C, dtype=torch.float32, device=x.device)
+    check(L.mxb_colsum(dt(x), ptr(x), ptr(partial), ptr(out), rows, C, stream_ptr(x.device)), 'colsum')
+    count_launch(2)
+    return out
+
+
 # ----------------------------------------------------------------------------------------------- transpose
 def transpose_supported(x):
     return (x.is_cuda and x.dim() >= 2 and x.element_size() in (2, 4) and x.is_contiguous() and x.numel() > 0

@@ -383,11 +383,28 @@ __global__ void __launch_bounds__(256) fused_lamb1_kernel(const __grid_constant_
   const bool skip = step_verdict(p, me, alive, &sumsq);
   float coef = 1.f;
   if (p.max_norm > 0.f) coef = fminf(1.f, p.max_norm / (sqrtf(sumsq) + 1e-8f));
+  // Every CTA takes one contiguous chunk of the shard, so it meets few parameters (segments): the per-parameter sums
+  // are collected in shared memory and reach the global accumulators once per CTA and segment.  (One global atomic per
+  // warp and vector, all warps of a large parameter on the same two addresses, made this kernel several times slower
+  // than its memory traffic.)
+  constexpr int kSpan = 64;
+  __shared__ float sacc[2][kSpan];
+  const int64_t v0 = p.shard_begin / N, v1 = p.shard_end / N;
+  const int64_t chunk = (v1 - v0 + gridDim.x - 1) / gridDim.x;
+  const int64_t c0 = v0 + (int64_t)blockIdx.x * chunk, c1 = (c0 + chunk < v1) ? c0 + chunk : v1;
+  int seg_first = 0, span = 0;
+  if (c0 < c1) {
+    seg_first = find_segment(p.seg_end, p.nseg, c0 * N);
+    span = find_segment(p.seg_end, p.nseg, c1 * N - 1) - seg_first + 1;
+  }
+  const bool in_smem = span <= kSpan;
+  for (int i = threadIdx.x; i < 2 * kSpan; i += blockDim.x) (&sacc[0][0])[i] = 0.f;
+  __syncthreads();
   if (!skip) {
-    const int64_t v0 = p.shard_begin / N, v1 = p.shard_end / N;
-    for (int64_t v = v0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < v1; v += (int64_t)gridDim.x * blockDim.x) {
+    int seg = seg_first;                   // positions of a thread only grow: the segment index is advanced, not searched
+    for (int64_t v = c0 + threadIdx.x; v < c1; v += blockDim.x) {
       const int64_t e = v * N, le = e - p.shard_begin;
-      const int seg = find_segment(p.seg_end, p.nseg, e);
+      while (seg < p.nseg - 1 && e >= p.seg_end[seg]) ++seg;
       const float wd = p.wd * p.wd_mult[seg];
       float g[N], w[N], m[N], s2[N];
       load_f(p.gred + le, g, N);
@@ -423,7 +440,17 @@ __global__ void __launch_bounds__(256) fused_lamb1_kernel(const __grid_constant_
         const float a2 = __shfl_down_sync(peers, a, o), b2 = __shfl_down_sync(peers, b, o);
         if (lane + o < 32 && ((peers >> (lane + o)) & 1u)) { a += a2; b += b2; }
       }
-      if (lane == leader) { atomicAdd(p.norm_acc + seg, a); atomicAdd(p.norm_acc + p.nseg + seg, b); }
+      if (lane == leader) {
+        if (in_smem) { atomicAdd(&sacc[0][seg - seg_first], a); atomicAdd(&sacc[1][seg - seg_first], b); }
+        else { atomicAdd(p.norm_acc + seg, a); atomicAdd(p.norm_acc + p.nseg + seg, b); }
+      }
+    }
+  }
+  __syncthreads();
+  if (!skip && in_smem) {
+    for (int i = threadIdx.x; i < span; i += blockDim.x) {
+      atomicAdd(p.norm_acc + seg_first + i, sacc[0][i]);
+      atomicAdd(p.norm_acc + p.nseg + seg_first + i, sacc[1][i]);
     }
   }
   __threadfence();

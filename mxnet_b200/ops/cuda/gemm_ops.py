@@ -134,6 +134,15 @@ def operand_ok(t):
     return t.dim() == 2 and t.shape[1] % 8 == 0 and t.shape[0] >= 1 and t.data_ptr() % 16 == 0
 
 
+def _bias_grad(dy):
+    """fp32 column sums of dy: the two-stage kernel, or the library reduction with fp32 accumulation."""
+    from . import elementwise_ops as ew
+    from ... import env
+    if env.get('MXNET_B200_ELEMENTWISE') and ew.colsum_supported(dy):
+        return ew.colsum(dy)
+    return dy.sum(0, dtype=torch.float32)
+
+
 def _lib_linear(x, w, bias, act):
     y = torch.nn.functional.linear(x, w, bias.to(x.dtype) if bias is not None and bias.dtype != x.dtype else bias)
     if act == 'relu':
@@ -182,7 +191,7 @@ class LinearFn(torch.autograd.Function):
             else:
                 dw = torch.matmul(dy.t(), x)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy.sum(0, dtype=torch.float32).to(ctx.bias_dtype)      # fp32 accumulation without an fp32 copy of dy
+            db = _bias_grad(dy).to(ctx.bias_dtype)
         return dx, dw, db, None
 
 

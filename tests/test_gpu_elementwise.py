@@ -221,3 +221,15 @@ def test_multi_adamw_kernel_matches_tensor_op_rule(mp):
     nd.contrib.multi_adamw_update(w, nd.array(rng_g[(33,)], ctx=ctx), nd.zeros((33,), ctx=ctx), nd.zeros((33,), ctx=ctx),
                                   nd.array([float('inf')], ctx=ctx), lrs=[0.1], wds=[0.0], etas=[1.0], num_weights=1, out=[w])
     np.testing.assert_array_equal(w.asnumpy(), before)
+
+
+@pytest.mark.parametrize('rows,C', [(8192, 3072), (1000, 768), (5, 8), (70000, 136)])
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_column_sums(rows, C, dtype):
+    from mxnet_b200.ops.cuda import elementwise_ops as ew
+    torch.manual_seed(6)
+    x = torch.randn(rows, C, device=_dev()).to(dtype)
+    out = ew.colsum(x)
+    ref = x.double().sum(0)
+    np.testing.assert_allclose(out.cpu().numpy(), ref.cpu().numpy(), rtol=1e-4, atol=1e-3 * rows ** 0.5)
+    assert torch.equal(out, ew.colsum(x))              # deterministic
