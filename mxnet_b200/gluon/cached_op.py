@@ -89,6 +89,19 @@ class _Graphed(object):
                 with torch.cuda.graph(self.bwd, pool=self.pool, stream=stream):
                     gin = torch.autograd.grad([o for o in self.static_out if o.requires_grad], self.grad_inputs,
                                               [g for g in self.static_gout if g is not None], allow_unused=True)
+                    # Parameter gradients are added to the parameters' gradient buffers by nodes of this graph, instead
+                    # of being handed to the autograd engine, which would launch one accumulation kernel per parameter
+                    # after every replay.  The buffers are kept alive here; a parameter whose buffer is replaced later
+                    # falls back to the engine (see _Replay.backward).
+                    n_in = sum(1 for t in self.static_in if t.requires_grad)
+                    self.grad_targets = []
+                    for arr, gi in zip(self.param_arrays, gin[n_in:]):
+                        tgt = arr._grad._data if getattr(arr, '_grad', None) is not None else None
+                        ok = (gi is not None and tgt is not None and arr._grad_req in ('write', 'add')
+                              and tgt.shape == gi.shape and tgt.dtype == gi.dtype and tgt.device == gi.device)
+                        if ok:
+                            tgt.add_(gi)
+                        self.grad_targets.append(tgt if ok else None)
             self.static_gin = list(gin)
             self.bwd_launches = _kernels.launches() - n1
         torch.cuda.current_stream(dev).wait_stream(stream)
@@ -140,9 +153,21 @@ class _Graphed(object):
                 for dst, src in zip(g.static_gout, gouts):
                     if dst is not None and src is not None and dst.data_ptr() != src.data_ptr():
                         dst.copy_(src)
+                # what the leaf hook of a parameter does before the engine accumulates into its buffer, for the
+                # parameters whose gradients the graph itself adds to their buffers
+                cur = autograd._pass_id[0]
+                direct = []
+                for arr, tgt in zip(g.param_arrays, g.grad_targets):
+                    buf = arr._grad._data if getattr(arr, '_grad', None) is not None else None
+                    d = tgt is not None and buf is not None and buf.data_ptr() == tgt.data_ptr() and arr._grad_req != 'null'
+                    if d:
+                        if arr._grad_req == 'write' and arr._fresh_grad and arr._grad_pass != cur:
+                            buf.zero_()
+                        arr._fresh_grad = True
+                        arr._grad_pass = cur
+                    direct.append(d)
                 g.bwd.replay()
                 g._kernels.count_launch(g.bwd_launches)
-                n_in = len(g.static_in)
                 res, k = [], 0
                 for t in g.static_in:
                     if t.requires_grad:
@@ -151,8 +176,8 @@ class _Graphed(object):
                         k += 1
                     else:
                         res.append(None)
-                for gi in g.static_gin[k:]:
-                    res.append(gi.detach() if gi is not None else None)
+                for gi, d in zip(g.static_gin[k:], direct):
+                    res.append(None if d else (gi.detach() if gi is not None else None))
                 return tuple(res)
 
         tensors = [a._data for a in arrays]
