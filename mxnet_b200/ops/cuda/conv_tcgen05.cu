@@ -464,11 +464,14 @@ static void choose_box(int Wo, int Ho, int N, int total, int* bw, int* bh, int* 
 }
 
 // NHWC activation tensor [N, H, W, C] as a 4-D map {C, W, H, N}; box {64, bw, bh, bnb}; 128-byte swizzle; zero fill.
-static int make_map_nhwc(CUtensorMap* map, const void* base, int bf16, int N, int H, int W, int C, int bw, int bh, int bnb) {
+// (sh, sw) > 1 describes every sh-th row and sw-th column of the stored tensor (the input of a strided 1x1 convolution):
+// a view of ceil(H / sh) x ceil(W / sw) pixels with the strides multiplied accordingly.
+static int make_map_nhwc(CUtensorMap* map, const void* base, int bf16, int N, int H, int W, int C, int bw, int bh, int bnb,
+                         int sh = 1, int sw = 1) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -10;
-  cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
-  cuuint64_t strides[3] = {(cuuint64_t)C * 2, (cuuint64_t)W * C * 2, (cuuint64_t)H * W * C * 2};
+  cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)((W + sw - 1) / sw), (cuuint64_t)((H + sh - 1) / sh), (cuuint64_t)N};
+  cuuint64_t strides[3] = {(cuuint64_t)sw * C * 2, (cuuint64_t)sh * W * C * 2, (cuuint64_t)H * W * C * 2};
   cuuint32_t box[4] = {64, (cuuint32_t)bw, (cuuint32_t)bh, (cuuint32_t)bnb};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base),
@@ -478,11 +481,14 @@ static int make_map_nhwc(CUtensorMap* map, const void* base, int bf16, int N, in
 }
 
 // Output tensor [N, Ho, Wo, C] for the epilogue's stores: box {32 channels, sw, sh, sn} (32 pixels), 64-byte swizzle.
-static int make_map_store(CUtensorMap* map, const void* base, int bf16, int N, int H, int W, int C, int sw, int sh, int sn) {
+static int make_map_store(CUtensorMap* map, const void* base, int bf16, int N, int H, int W, int C, int sw, int sh, int sn,
+                          int ph = 1, int pw = 1) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -10;
-  cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
-  cuuint64_t strides[3] = {(cuuint64_t)C * 2, (cuuint64_t)W * C * 2, (cuuint64_t)H * W * C * 2};
+  // (ph, pw) > 1: the stores go to every ph-th row and pw-th column of the stored tensor (the data gradient of a
+  // strided 1x1 convolution, whose other positions are zero)
+  cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)((W + pw - 1) / pw), (cuuint64_t)((H + ph - 1) / ph), (cuuint64_t)N};
+  cuuint64_t strides[3] = {(cuuint64_t)pw * C * 2, (cuuint64_t)ph * W * C * 2, (cuuint64_t)H * W * C * 2};
   cuuint32_t box[4] = {32, (cuuint32_t)sw, (cuuint32_t)sh, (cuuint32_t)sn};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base),
@@ -559,7 +565,8 @@ static int conv_pick_bn(long tiles_m, int NC) {
 // Shared by the forward and data-gradient entry points.  `in` is [N, Hi, Wi, KC], the result [N, Ho, Wo, NC].
 static int conv_run(int dtype, const void* in, const void* w, void* out, const void* bias, const void* res, float* stats,
                     int N, int Hi, int Wi, int KC, int Ho, int Wo, int NC, int R, int S, int off_h, int step_h, int off_w,
-                    int step_w, int w_cout, int w_cin, int b_mn, int act, int* error_flag, cudaStream_t st) {
+                    int step_w, int w_cout, int w_cin, int b_mn, int act, int* error_flag, cudaStream_t st, int in_sh = 1,
+                    int in_sw = 1, int out_sh = 1, int out_sw = 1, int out_full_h = 0, int out_full_w = 0) {
   if (dtype != kF16 && dtype != kBF16) return -1;
   if (N < 1 || Hi < 1 || Wi < 1 || Ho < 1 || Wo < 1 || KC < 8 || NC < 8 || R < 1 || S < 1) return -2;
   if ((KC % 8) || (NC % 8) || ((uintptr_t)in % 16) || ((uintptr_t)w % 16) || ((uintptr_t)out % 16)) return -3;
@@ -582,7 +589,7 @@ static int conv_run(int dtype, const void* in, const void* w, void* out, const v
   if (tiles_m * ((NC + 63) / 64) > 0x7fffffffL) return -2;
   const int bn = conv_pick_bn(tiles_m, NC);
   CUtensorMap mx, mw, my;
-  int rc = make_map_nhwc(&mx, in, g.bf16, N, Hi, Wi, KC, g.bw, g.bh, g.bnb);
+  int rc = make_map_nhwc(&mx, in, g.bf16, N, Hi, Wi, KC, g.bw, g.bh, g.bnb, in_sh, in_sw);
   if (rc) return rc;
   rc = make_map_filter(&mw, w, g.bf16, w_cout, R * S, w_cin, b_mn ? 64 : bn);
   if (rc) return rc;
@@ -590,7 +597,9 @@ static int conv_run(int dtype, const void* in, const void* w, void* out, const v
   const int sw = g.bw < 32 ? g.bw : 32;
   const int sh = g.bh < 32 / sw ? g.bh : 32 / sw;
   const int sn = 32 / (sw * sh);
-  rc = make_map_store(&my, out, g.bf16, N, Ho, Wo, NC, sw, sh, sn);
+  // with an output stride the stored tensor (out_full_h x out_full_w) is larger than the (Ho, Wo) pixel space of the tiles
+  rc = make_map_store(&my, out, g.bf16, N, out_full_h > 0 ? out_full_h : Ho, out_full_w > 0 ? out_full_w : Wo, NC, sw, sh, sn,
+                      out_sh, out_sw);
   if (rc) return rc;
 #define MXB_CONV(T)                                                                              \
   (bn == 256 ? launch_conv<T, 256>(mx, mw, my, bias, res, stats, g, error_flag, st)               \
@@ -624,6 +633,29 @@ MXB_EXPORT int mxb_conv_forward(int dtype, const void* x, const void* w, void* y
   const int Ho = H + 2 * pad_h - dil_h * (R - 1), Wo = W + 2 * pad_w - dil_w * (S - 1);
   return conv_run(dtype, x, w, y, bias, res, stats, N, H, W, Cin, Ho, Wo, Cout, R, S, -pad_h, dil_h, -pad_w, dil_w, Cout, Cin,
                   0, act, error_flag, (cudaStream_t)stream);
+}
+
+// Strided 1x1 convolution (the down-sampling shortcut of a residual network): y[N, Ho, Wo, Cout] with Ho = ceil(H / sh),
+// Wo = ceil(W / sw) reads every sh-th row and sw-th column of x through a strided tensor map; same kernel.
+MXB_EXPORT int mxb_conv1x1_strided_forward(int dtype, const void* x, const void* w, void* y, const void* bias, float* stats,
+                                           int N, int H, int W, int Cin, int Cout, int sh, int sw, int act, int* error_flag,
+                                           void* stream) {
+  if (sh < 1 || sw < 1) return -2;
+  const int Ho = (H + sh - 1) / sh, Wo = (W + sw - 1) / sw;
+  return conv_run(dtype, x, w, y, bias, nullptr, stats, N, H, W, Cin, Ho, Wo, Cout, 1, 1, 0, 1, 0, 1, Cout, Cin, 0, act, error_flag,
+                  (cudaStream_t)stream, sh, sw);
+}
+
+// Its data gradient: dx[N, H, W, Cin] is zero except at the sampled positions, which receive dy . w.  dx is cleared
+// first, then the tiles are stored through a strided tensor map.
+MXB_EXPORT int mxb_conv1x1_strided_dgrad(int dtype, const void* dy, const void* w, void* dx, int N, int H, int W, int Cin,
+                                         int Cout, int sh, int sw, int* error_flag, void* stream) {
+  if (sh < 1 || sw < 1) return -2;
+  const int Ho = (H + sh - 1) / sh, Wo = (W + sw - 1) / sw;
+  cudaError_t rc = cudaMemsetAsync(dx, 0, (size_t)N * H * W * Cin * 2, (cudaStream_t)stream);
+  if (rc != cudaSuccess) return (int)rc;
+  return conv_run(dtype, dy, w, dx, nullptr, nullptr, nullptr, N, Ho, Wo, Cout, Ho, Wo, Cin, 1, 1, 0, -1, 0, -1, Cout, Cin, 1, 0,
+                  error_flag, (cudaStream_t)stream, 1, 1, sh, sw, H, W);
 }
 
 // dx[N, H, W, Cin] = sum_{r,s,co} dy[n, h + pad_h - r*dil_h, w + pad_w - s*dil_w, co] * w[co, r, s, Cin] (+ res):
@@ -857,14 +889,14 @@ static int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, float* dW
 
 // dw[Cout, R, S, Cin] (type `dtype`; may be null to keep only the fp32 result) and dw32 (fp32 workspace of the same
 // element count, overwritten) from x[N, H, W, Cin] and dy[N, Ho, Wo, Cout] of the stride-1 convolution above.
-MXB_EXPORT int mxb_conv_wgrad(int dtype, const void* x, const void* dy, void* dw, float* dw32, int N, int H, int W, int Cin,
-                              int Cout, int R, int S, int pad_h, int pad_w, int dil_h, int dil_w, int* error_flag,
-                              void* stream) {
+static int wgrad_run(int dtype, const void* x, const void* dy, void* dw, float* dw32, int N, int H, int W, int Cin, int Cout,
+                     int R, int S, int pad_h, int pad_w, int dil_h, int dil_w, int sh, int sw, int* error_flag, void* stream) {
   if (dtype != kF16 && dtype != kBF16) return -1;
   if (N < 1 || H < 1 || W < 1 || Cin < 8 || Cout < 8 || R < 1 || S < 1 || !dw32) return -2;
   if ((Cin % 8) || (Cout % 8) || ((uintptr_t)x % 16) || ((uintptr_t)dy % 16) || ((uintptr_t)dw32 % 16)) return -3;
   WgradGeom g;
   g.N = N; g.Ho = H + 2 * pad_h - dil_h * (R - 1); g.Wo = W + 2 * pad_w - dil_w * (S - 1);
+  if (sh > 1 || sw > 1) { g.Ho = (H + sh - 1) / sh; g.Wo = (W + sw - 1) / sw; }      // strided 1x1: a sampled view of x
   if (g.Ho < 1 || g.Wo < 1) return -2;
   g.Cout = Cout; g.Cin = Cin; g.R = R; g.S = S;
   g.off_h = -pad_h; g.step_h = dil_h; g.off_w = -pad_w; g.step_w = dil_w;
@@ -885,7 +917,7 @@ MXB_EXPORT int mxb_conv_wgrad(int dtype, const void* x, const void* dy, void* dw
   CUtensorMap mdy, mx;
   int rc = make_map_nhwc(&mdy, dy, g.bf16, N, g.Ho, g.Wo, Cout, g.kw, g.kh, g.knb);
   if (rc) return rc;
-  rc = make_map_nhwc(&mx, x, g.bf16, N, H, W, Cin, g.kw, g.kh, g.knb);
+  rc = make_map_nhwc(&mx, x, g.bf16, N, H, W, Cin, g.kw, g.kh, g.knb, sh, sw);
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
 #define MXB_WGRAD(T)                                                                      \
@@ -894,4 +926,17 @@ MXB_EXPORT int mxb_conv_wgrad(int dtype, const void* x, const void* dy, void* dw
                : launch_wgrad<T, 64>(mdy, mx, dw32, dw, g, error_flag, st))
   return g.bf16 ? MXB_WGRAD(__nv_bfloat16) : MXB_WGRAD(__half);
 #undef MXB_WGRAD
+}
+
+MXB_EXPORT int mxb_conv_wgrad(int dtype, const void* x, const void* dy, void* dw, float* dw32, int N, int H, int W, int Cin,
+                              int Cout, int R, int S, int pad_h, int pad_w, int dil_h, int dil_w, int* error_flag,
+                              void* stream) {
+  return wgrad_run(dtype, x, dy, dw, dw32, N, H, W, Cin, Cout, R, S, pad_h, pad_w, dil_h, dil_w, 1, 1, error_flag, stream);
+}
+
+// Weight gradient of the strided 1x1 convolution: dy is [N, ceil(H / sh), ceil(W / sw), Cout].
+MXB_EXPORT int mxb_conv1x1_strided_wgrad(int dtype, const void* x, const void* dy, void* dw, float* dw32, int N, int H, int W,
+                                         int Cin, int Cout, int sh, int sw, int* error_flag, void* stream) {
+  if (sh < 1 || sw < 1) return -2;
+  return wgrad_run(dtype, x, dy, dw, dw32, N, H, W, Cin, Cout, 1, 1, 0, 0, 1, 1, sh, sw, error_flag, stream);
 }

@@ -52,6 +52,10 @@ def ensure_initialized(backend=None, timeout_s=None):
     return True
 
 
+def backend():
+    return tdist.get_backend() if is_initialized() else None
+
+
 def rank():
     return tdist.get_rank() if is_initialized() else 0
 
@@ -161,6 +165,19 @@ def num_dead_nodes(timeout=60):
     return dead
 
 
+def _small_allreduce(t):
+    """Sum of a small fp32 tensor over the ranks: the peer-memory kernel on one NVLink node, else the library."""
+    from . import peer_reduce
+    if t.dtype == torch.float32 and t.is_cuda and peer_reduce.available(t.device):
+        flat = t.contiguous().reshape(-1)
+        pr = peer_reduce.get(t.device)
+        if flat.numel() <= pr.cap:
+            return pr.allreduce(flat).reshape(t.shape)
+    t = t.contiguous()
+    tdist.all_reduce(t)
+    return t
+
+
 class SyncMoments(torch.autograd.Function):
     """Mean/variance over the batch of every rank (SyncBatchNorm statistics) with exact gradients."""
 
@@ -170,10 +187,10 @@ class SyncMoments(torch.autograd.Function):
         for a in red:
             n_local *= x.shape[a]
         s = torch.stack([x.sum(red), (x * x).sum(red)])
-        cnt = torch.tensor([float(n_local)], device=x.device)
-        tdist.all_reduce(s)
-        tdist.all_reduce(cnt)
-        n = cnt.item()
+        # every rank contributes the same number of rows in data-parallel training; unequal batches take the general
+        # path with the counts reduced as well
+        n = float(n_local) * world_size()
+        s = _small_allreduce(s)
         mean = s[0] / n
         var = s[1] / n - mean * mean
         ctx.save_for_backward(x, mean)
@@ -183,8 +200,7 @@ class SyncMoments(torch.autograd.Function):
     @staticmethod
     def backward(ctx, gmean, gvar):
         x, mean = ctx.saved_tensors
-        g = torch.stack([gmean, gvar])
-        tdist.all_reduce(g)
+        g = _small_allreduce(torch.stack([gmean, gvar]))
         shape = [1] * x.dim()
         for i in range(x.dim()):
             if i not in ctx.red:

@@ -87,6 +87,31 @@ def test_conv_data_and_weight_gradients(N, H, W, Cin, Cout, R, pad, dil, dtype):
     _close(dx2, xr.grad + res.float(), *tol)
 
 
+@pytest.mark.parametrize('N,H,W,Cin,Cout,stride', [(4, 56, 56, 64, 128, 2), (3, 7, 9, 16, 24, 2), (2, 14, 14, 256, 512, 2),
+                                                  (2, 10, 10, 8, 8, 3)])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_strided_1x1_convolution_all_directions(N, H, W, Cin, Cout, stride, dtype):
+    """The down-sampling shortcut: a 1x1 filter with stride, read and written through strided tensor maps."""
+    from mxnet_b200.ops.cuda import conv_ops, gemm_ops
+    x, w = _inputs(N, H, W, Cin, Cout, 1, dtype, seed=6)
+    xr, wr = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    ref = F.conv2d(xr.permute(0, 3, 1, 2), wr.permute(0, 3, 1, 2), None, stride).permute(0, 2, 3, 1).contiguous()
+    dy = (torch.randn_like(ref) / 4).to(dtype)
+    ref.backward(dy.float())
+    st = (stride, stride)
+    y, stats = conv_ops.conv_forward(x, w, None, None, (0, 0), (1, 1), False, True, st)
+    dx = conv_ops.conv_dgrad(dy, w, (H, W), (0, 0), (1, 1), None, st)
+    dw = conv_ops.conv_wgrad(x, dy, (1, 1), (0, 0), (1, 1), st)
+    gemm_ops.check_errors()
+    tol = (1e-2, 1e-2) if dtype == torch.float16 else (3e-2, 3e-2)
+    assert y.shape == ref.shape
+    _close(y, ref, *tol)
+    _close(stats.sum(0)[0] / (ref.numel() // Cout), ref.reshape(-1, Cout).mean(0), 1e-2, 2e-3)
+    _close(dx, xr.grad, *tol)
+    k = dy.numel() // Cout
+    _close(dw, wr.grad, tol[0], (2e-3 if dtype == torch.float16 else 8e-3) * k ** 0.5)
+
+
 def _conv_bn_step(x_np, w_np, env):
     import os
     old = os.environ.get('MXNET_B200_CONV')

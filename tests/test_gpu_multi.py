@@ -35,3 +35,18 @@ def test_fused_step_matches_nccl_path_across_ranks(nproc):
     assert rep['float16']['max_abs_diff_vs_nccl_path'] < 5e-3
     for name in ('lamb', 'adam'):
         assert rep[name]['ranks_identical'] and rep[name]['max_abs_diff_vs_nccl_path'] < 1e-4
+
+
+@pytest.mark.parametrize('nproc', [2, 4])
+def test_sync_batchnorm_over_peer_memory(nproc):
+    """SyncBatchNorm statistics through the peer-memory all-reduce kernel: same sums as the library collective, same
+    normalisation and gradients as BatchNorm over the whole batch."""
+    if torch.cuda.device_count() < nproc:
+        pytest.skip('needs %d GPUs' % nproc)
+    r = _launch('sync_bn_worker.py', nproc, 29651 + nproc)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith('REPORT ')][-1]
+    rep = json.loads(line[len('REPORT '):])
+    assert rep['world'] == nproc and rep['status'] == 0 and rep['status_after'] == 0
+    assert rep['allreduce_max_abs_diff'] == 0.0
+    assert rep['y_diff'] < 1e-4 and rep['dx_diff'] < 1e-4 and rep['mean_diff'] < 1e-5
