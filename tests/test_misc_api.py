@@ -1,0 +1,238 @@
+"""Smaller public modules: initializers, schedulers, callbacks, checkpoints, custom operators, sparse arrays,
+control flow, random and linear-algebra operators, model zoo shapes, visualisation, image augmenters, quantization."""
+import logging
+import os
+
+import numpy as np
+import pytest
+
+import mxnet_b200 as mx
+from mxnet_b200 import autograd, gluon, nd
+
+
+# ------------------------------------------------------------------------------------------- initializers
+def test_initializers_statistics_and_patterns():
+    mx.random.seed(11)
+    shape = (64, 128)
+    cases = {
+        'xavier_uniform': (mx.init.Xavier(rnd_type='uniform', factor_type='avg', magnitude=3), (3.0 / ((64 + 128) / 2)) ** 0.5),
+        'msra': (mx.init.MSRAPrelu(factor_type='in', slope=0.0), None),
+        'normal': (mx.init.Normal(0.02), 0.02),
+        'uniform': (mx.init.Uniform(0.1), 0.1),
+    }
+    for name, (init, scale) in cases.items():
+        p = gluon.Parameter('weight', shape=shape, init=init)
+        p.initialize()
+        w = p.data().asnumpy()
+        assert abs(w.mean()) < 0.02, name
+        if name == 'normal':
+            np.testing.assert_allclose(w.std(), scale, rtol=0.1)
+        if name in ('uniform', 'xavier_uniform'):
+            assert np.abs(w).max() <= scale + 1e-6
+        if name == 'msra':
+            np.testing.assert_allclose(w.std(), (2.0 / 128) ** 0.5, rtol=0.1)
+    p = gluon.Parameter('weight', shape=(8, 8), init=mx.init.Orthogonal())
+    p.initialize()
+    w = p.data().asnumpy()
+    np.testing.assert_allclose(w @ w.T, np.eye(8) * (w @ w.T)[0, 0], atol=1e-4)
+    for init, val in ((mx.init.Zero(), 0.0), (mx.init.One(), 1.0), (mx.init.Constant(2.5), 2.5)):
+        p = gluon.Parameter('weight', shape=(3, 3), init=init)
+        p.initialize()
+        assert (p.data().asnumpy() == val).all()
+    b = gluon.Parameter('bias', shape=(8,), init=mx.init.LSTMBias(forget_bias=1.0))
+    b.initialize()
+    np.testing.assert_array_equal(b.data().asnumpy(), [0, 0, 1, 1, 0, 0, 0, 0])
+
+
+def test_lr_schedulers():
+    f = mx.lr_scheduler.FactorScheduler(step=10, factor=0.5, base_lr=1.0, stop_factor_lr=0.2)
+    assert f(1) == 1.0 and f(11) == 0.5 and f(21) == 0.25 and f(100) == 0.2
+    m = mx.lr_scheduler.MultiFactorScheduler(step=[5, 8], factor=0.1, base_lr=1.0)
+    np.testing.assert_allclose([m(1), m(6), m(9)], [1.0, 0.1, 0.01])
+    p = mx.lr_scheduler.PolyScheduler(max_update=100, base_lr=1.0, pwr=2, final_lr=0.0)
+    np.testing.assert_allclose(p(50), 0.25, rtol=1e-6)
+    c = mx.lr_scheduler.CosineScheduler(max_update=100, base_lr=1.0, final_lr=0.0, warmup_steps=10, warmup_begin_lr=0.0)
+    np.testing.assert_allclose(c(5), 0.5, rtol=1e-6)          # linear warm-up
+    np.testing.assert_allclose(c(55), 0.5, rtol=1e-6)         # halfway down the cosine
+    assert abs(c(100)) < 1e-12 and abs(c(200)) < 1e-12     # past max_update the last value is kept
+
+
+def test_speedometer_and_checkpoint_callbacks(tmp_path, caplog):
+    from collections import namedtuple
+    Param = namedtuple('BatchEndParam', ['epoch', 'nbatch', 'eval_metric', 'locals'])
+    metric = mx.gluon.metric.Accuracy()
+    metric.update([nd.array([0, 1])], [nd.array([[0.9, 0.1], [0.2, 0.8]])])
+    sp = mx.callback.Speedometer(batch_size=2, frequent=2, auto_reset=False)
+    with caplog.at_level(logging.INFO):
+        for i in range(5):
+            sp(Param(0, i, metric, None))
+    assert any('samples/sec' in r.getMessage() for r in caplog.records)
+    sym = mx.sym.FullyConnected(mx.sym.var('data'), num_hidden=3, name='fc')
+    arg = {'fc_weight': nd.array(np.arange(6, dtype='float32').reshape(3, 2)), 'fc_bias': nd.array([1.0, 2.0, 3.0])}
+    prefix = str(tmp_path / 'model')
+    mx.model.save_checkpoint(prefix, 3, sym, arg, {})
+    assert os.path.exists(prefix + '-0003.params') and os.path.exists(prefix + '-symbol.json')
+    sym2, arg2, aux2 = mx.model.load_checkpoint(prefix, 3)
+    assert sym2.list_arguments() == sym.list_arguments() and aux2 == {}
+    for k in arg:
+        np.testing.assert_array_equal(arg[k].asnumpy(), arg2[k].asnumpy())
+
+
+# ------------------------------------------------------------------------------------------- custom operator
+def test_custom_operator_forward_backward():
+    class Scale2(mx.operator.CustomOp):
+        def forward(self, is_train, req, in_data, out_data, aux):
+            self.assign(out_data[0], req[0], in_data[0] * 2)
+
+        def backward(self, req, out_grad, in_data, out_data, in_grad, aux):
+            self.assign(in_grad[0], req[0], out_grad[0] * 2)
+
+    @mx.operator.register('scale2_test')
+    class Scale2Prop(mx.operator.CustomOpProp):
+        def list_arguments(self):
+            return ['data']
+
+        def infer_shape(self, in_shape):
+            return in_shape, [in_shape[0]], []
+
+        def create_operator(self, ctx, shapes, dtypes):
+            return Scale2()
+
+    x = nd.array([1.0, -2.0, 3.0])
+    x.attach_grad()
+    with autograd.record():
+        y = nd.Custom(x, op_type='scale2_test')
+        z = (y * y).sum()
+    z.backward()
+    np.testing.assert_allclose(y.asnumpy(), [2, -4, 6])
+    np.testing.assert_allclose(x.grad.asnumpy(), 8 * x.asnumpy())
+
+
+# ------------------------------------------------------------------------------------------- sparse
+def test_sparse_arrays_round_trip_and_dot():
+    dense = np.array([[0, 1.5, 0], [0, 0, 0], [2.0, 0, 3.0]], dtype='float32')
+    csr = nd.array(dense).tostype('csr')
+    assert csr.stype == 'csr'
+    np.testing.assert_array_equal(csr.indices.asnumpy(), [1, 0, 2])
+    np.testing.assert_array_equal(csr.indptr.asnumpy(), [0, 1, 1, 3])
+    np.testing.assert_array_equal(csr.tostype('default').asnumpy(), dense)
+    rsp = nd.array(dense).tostype('row_sparse')
+    np.testing.assert_array_equal(rsp.indices.asnumpy(), [0, 2])
+    np.testing.assert_array_equal(rsp.tostype('default').asnumpy(), dense)
+    rhs = np.arange(6, dtype='float32').reshape(3, 2)
+    np.testing.assert_allclose(nd.dot(csr, nd.array(rhs)).asnumpy(), dense @ rhs)
+    made = nd.sparse.csr_matrix((csr.data, csr.indices, csr.indptr), shape=(3, 3))
+    np.testing.assert_array_equal(made.asnumpy(), dense)
+
+
+# ------------------------------------------------------------------------------------------- control flow
+def test_contrib_foreach_while_cond():
+    def step(x, state):
+        new = state[0] + x
+        return new * 2, [new]
+    outs, states = nd.contrib.foreach(step, nd.array([[1.0], [2.0], [3.0]]), [nd.zeros((1,))])
+    np.testing.assert_allclose(outs.asnumpy().reshape(-1), [2, 6, 12])
+    np.testing.assert_allclose(states[0].asnumpy(), [6])
+    outs, final = nd.contrib.while_loop(lambda i, s: i < 4, lambda i, s: ([s], [i + 1, s + i]),
+                                        [nd.array([0.0]), nd.array([0.0])], max_iterations=6)
+    np.testing.assert_allclose(final[1].asnumpy(), [6])           # 0 + 1 + 2 + 3
+    assert outs[0].shape[0] == 6
+    r = nd.contrib.cond(nd.array([1.0]), lambda: nd.array([10.0]), lambda: nd.array([20.0]))
+    np.testing.assert_allclose(r.asnumpy(), [10])
+
+
+# ------------------------------------------------------------------------------------------- random / linalg
+def test_random_operators_moments_and_seed():
+    mx.random.seed(42)
+    a = nd.random.normal(2.0, 3.0, shape=(50000,)).asnumpy()
+    np.testing.assert_allclose([a.mean(), a.std()], [2.0, 3.0], rtol=0.05)
+    u = nd.random.uniform(-1, 1, shape=(50000,)).asnumpy()
+    assert u.min() >= -1 and u.max() <= 1 and abs(u.mean()) < 0.02
+    g = nd.random.gamma(2.0, 2.0, shape=(50000,)).asnumpy()
+    np.testing.assert_allclose(g.mean(), 4.0, rtol=0.05)
+    r = nd.random.randint(0, 5, shape=(10000,)).asnumpy()
+    assert set(np.unique(r)) <= {0, 1, 2, 3, 4}
+    mx.random.seed(7)
+    x1 = nd.random.normal(shape=(5,)).asnumpy()
+    mx.random.seed(7)
+    np.testing.assert_array_equal(x1, nd.random.normal(shape=(5,)).asnumpy())
+    m = nd.random.multinomial(nd.array([0.0, 0.0, 1.0]), shape=(20,)).asnumpy()
+    assert (m == 2).all()
+    p = nd.array(np.arange(10, dtype='float32'))
+    s = nd.random.shuffle(p).asnumpy()
+    assert sorted(s.tolist()) == list(range(10))
+
+
+def test_linalg_operators():
+    rng = np.random.RandomState(0)
+    a = rng.randn(4, 4).astype('float32')
+    spd = a @ a.T + 4 * np.eye(4, dtype='float32')
+    L = nd.linalg.potrf(nd.array(spd)).asnumpy()
+    np.testing.assert_allclose(L @ L.T, spd, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(nd.linalg.potri(nd.array(L)).asnumpy(), np.linalg.inv(spd), rtol=1e-3, atol=1e-4)
+    np.testing.assert_allclose(nd.linalg.sumlogdiag(nd.array(L)).asnumpy(), np.log(np.diag(L)).sum(), rtol=1e-5)
+    b = rng.randn(4, 3).astype('float32')
+    np.testing.assert_allclose(nd.linalg.gemm2(nd.array(a), nd.array(b), alpha=2.0).asnumpy(), 2 * a @ b, rtol=1e-4, atol=1e-5)
+    x = nd.linalg.trsm(nd.array(L), nd.array(b)).asnumpy()
+    np.testing.assert_allclose(L @ x, b, rtol=1e-3, atol=1e-4)
+    u, lam = nd.linalg.syevd(nd.array(spd))
+    np.testing.assert_allclose(np.sort(lam.asnumpy()), np.sort(np.linalg.eigvalsh(spd)), rtol=1e-4)
+    np.testing.assert_allclose(nd.linalg.det(nd.array(spd)).asnumpy(), np.linalg.det(spd), rtol=1e-3)
+    np.testing.assert_allclose(nd.linalg.inverse(nd.array(spd)).asnumpy(), np.linalg.inv(spd), rtol=1e-3, atol=1e-4)
+
+
+# ------------------------------------------------------------------------------------------- model zoo / visualisation
+@pytest.mark.parametrize('name,size', [('resnet18_v1', 64), ('resnet18_v2', 64), ('mobilenet0_25', 64), ('squeezenet1_1', 96),
+                                       ('vgg11', 64), ('densenet121', 224), ('alexnet', 224), ('mobilenet_v2_0_25', 64)])
+def test_model_zoo_forward_shapes(name, size):
+    from mxnet_b200.gluon.model_zoo import vision
+    net = vision.get_model(name, classes=10)
+    net.initialize()
+    out = net(nd.array(np.random.RandomState(0).randn(1, 3, size, size).astype('float32')))
+    assert out.shape == (1, 10)
+    assert np.isfinite(out.asnumpy()).all()
+
+
+def test_print_summary_and_block_summary(capsys):
+    data = mx.sym.var('data')
+    net = mx.sym.FullyConnected(data, num_hidden=8, name='fc1')
+    net = mx.sym.Activation(net, act_type='relu', name='relu1')
+    net = mx.sym.FullyConnected(net, num_hidden=2, name='fc2')
+    mx.viz.print_summary(net, shape={'data': (1, 4)})
+    out = capsys.readouterr().out
+    assert 'fc1' in out and 'fc2' in out and 'Total params' in out
+    blk = gluon.nn.HybridSequential()
+    blk.add(gluon.nn.Dense(8, in_units=4), gluon.nn.Dense(2, in_units=8))
+    blk.initialize()
+    blk.summary(nd.zeros((1, 4)))
+    assert 'Dense' in capsys.readouterr().out
+
+
+# ------------------------------------------------------------------------------------------- image
+def test_image_augmenters_and_resize():
+    rng = np.random.RandomState(0)
+    img = nd.array(rng.randint(0, 255, (40, 60, 3)).astype('uint8'), dtype='uint8')
+    out = mx.image.resize_short(img, 20)
+    assert min(out.shape[:2]) == 20 and out.shape[2] == 3
+    crop, rect = mx.image.center_crop(img, (30, 20))
+    assert crop.shape == (20, 30, 3) and rect == (15, 10, 30, 20)
+    augs = mx.image.CreateAugmenter(data_shape=(3, 24, 24), resize=32, rand_crop=True, rand_mirror=True, mean=True, std=True)
+    x = img
+    for a in augs:
+        x = a(x)
+    assert x.shape == (24, 24, 3) and x.dtype == np.float32
+    flipped = mx.image.HorizontalFlipAug(1.0)(img)
+    np.testing.assert_array_equal(flipped.asnumpy(), img.asnumpy()[:, ::-1])
+    t = gluon.data.vision.transforms.Compose([gluon.data.vision.transforms.Resize(16), gluon.data.vision.transforms.ToTensor(),
+                                              gluon.data.vision.transforms.Normalize(0.5, 0.25)])
+    y = t(img)
+    assert y.shape == (3, 16, 16)
+
+
+# ------------------------------------------------------------------------------------------- quantization
+def test_quantize_dequantize_round_trip():
+    x = nd.array(np.linspace(-3, 3, 64, dtype='float32').reshape(8, 8))
+    q, mn, mxv = nd.contrib.quantize_v2(x, out_type='int8')
+    assert q.dtype == np.int8
+    back = nd.contrib.dequantize(q, mn, mxv, out_type='float32')
+    np.testing.assert_allclose(back.asnumpy(), x.asnumpy(), atol=3.0 / 127 + 1e-6)
