@@ -98,18 +98,27 @@ def check_errors(bar):
         raise RuntimeError('LSTM recurrence kernel: grid barrier timed out')
 
 
-def lstm(data, parameters, state, state_cell, state_size, num_layers, p, training):
-    """Multi-layer unidirectional LSTM over (T, N, C) data with the flat parameter vector of the RNN operator."""
+def lstm(data, parameters, state, state_cell, state_size, num_layers, p, training, bidirectional=False):
+    """Multi-layer LSTM over (T, N, C) data with the flat parameter vector of the RNN operator.  A bidirectional layer
+    runs the recurrence kernel twice, the second time on the time-reversed sequence with the reverse direction's
+    weights, and concatenates the two outputs along the feature axis (states are ordered layer * 2 + direction)."""
     from ..nn import rnn_unpack
     T, N, I = data.shape
-    layers = rnn_unpack(parameters, 'lstm', num_layers, I, state_size, False, None)
+    d = 2 if bidirectional else 1
+    layers = rnn_unpack(parameters, 'lstm', num_layers, I, state_size, bool(bidirectional), None)
     x = data
     hs, cs = [], []
     for l in range(num_layers):
-        w_ih, w_hh, _w_hr, b_ih, b_hh = layers[l]
-        x, h, c = _LSTMLayer.apply(x, w_ih, w_hh, b_ih, b_hh, state[l], state_cell[l], bool(training))
-        hs.append(h)
-        cs.append(c)
+        outs = []
+        for di in range(d):
+            w_ih, w_hh, _w_hr, b_ih, b_hh = layers[l * d + di]
+            xin = x if di == 0 else x.flip(0)
+            y, h, c = _LSTMLayer.apply(xin.contiguous(), w_ih, w_hh, b_ih, b_hh, state[l * d + di], state_cell[l * d + di],
+                                       bool(training))
+            outs.append(y if di == 0 else y.flip(0))
+            hs.append(h)
+            cs.append(c)
+        x = outs[0] if d == 1 else torch.cat(outs, -1)
         if p > 0 and training and l < num_layers - 1:
             x = torch.nn.functional.dropout(x, p, True)
     return x, torch.stack(hs, 0), torch.stack(cs, 0)

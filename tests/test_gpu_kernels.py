@@ -557,6 +557,41 @@ def test_fused_lstm_matches_library_lstm(T, B, I, H, layers, dtype):
     _close(flat.grad.cpu() / scale, gref / scale, tol[0] * 5, tol[1] * 2)
 
 
+@pytest.mark.parametrize('T,B,I,H,layers', [(6, 4, 24, 40, 2), (5, 3, 16, 16, 1)])
+def test_fused_lstm_bidirectional(T, B, I, H, layers):
+    """Both directions through the recurrence kernel (the reverse one on the time-flipped sequence) against an exact
+    fp32 bidirectional LSTM on the host with the same parameters."""
+    from mxnet_b200.ops.cuda import rnn_ops
+    from mxnet_b200.ops.nn import rnn_param_size
+    torch.manual_seed(11)
+    ref = torch.nn.LSTM(I, H, layers, bidirectional=True).float()
+    sfx = ['l%d%s' % (l, r) for l in range(layers) for r in ('', '_reverse')]
+    ws = [getattr(ref, 'weight_%s_%s' % (k, s)).detach().reshape(-1) for s in sfx for k in ('ih', 'hh')]
+    bs = [getattr(ref, 'bias_%s_%s' % (k, s)).detach() for s in sfx for k in ('ih', 'hh')]
+    flat = torch.cat(ws + bs).to(_dev()).requires_grad_(True)
+    assert flat.numel() == rnn_param_size('lstm', layers, I, H, True)
+    x = torch.randn(T, B, I, device=_dev()).requires_grad_(True)
+    h0 = (torch.randn(layers * 2, B, H, device=_dev()) * 0.5).requires_grad_(True)
+    c0 = (torch.randn(layers * 2, B, H, device=_dev()) * 0.5).requires_grad_(True)
+    assert rnn_ops.supported(x, H, layers)
+    y, hT, cT = rnn_ops.lstm(x, flat, h0, c0, H, layers, 0.0, True, True)
+    assert y.shape == (T, B, 2 * H)
+    gy, gh, gc = torch.randn_like(y), torch.randn_like(hT), torch.randn_like(cT)
+    torch.autograd.backward([y, hT, cT], [gy, gh, gc])
+    xr = x.detach().cpu().requires_grad_(True)
+    hr, cr = h0.detach().cpu().requires_grad_(True), c0.detach().cpu().requires_grad_(True)
+    yr, (hTr, cTr) = ref(xr, (hr, cr))
+    torch.autograd.backward([yr, hTr, cTr], [gy.cpu(), gh.cpu(), gc.cpu()])
+    for a, b in ((y, yr), (hT, hTr), (cT, cTr)):
+        _close(a, b, 1e-3, 1e-3)
+    for a, b in ((x.grad, xr.grad), (h0.grad, hr.grad), (c0.grad, cr.grad)):
+        _close(a, b, 3e-3, 3e-3)
+    gref = torch.cat([getattr(ref, 'weight_%s_%s' % (k, s)).grad.reshape(-1) for s in sfx for k in ('ih', 'hh')] +
+                     [getattr(ref, 'bias_%s_%s' % (k, s)).grad for s in sfx for k in ('ih', 'hh')])
+    scale = float(gref.abs().max())
+    _close(flat.grad.cpu() / scale, gref / scale, 5e-3, 2e-3)
+
+
 @pytest.mark.parametrize('mode,bidir', [('gru', False), ('lstm', True), ('rnn_tanh', True), ('rnn_relu', False)])
 def test_rnn_operator_gpu_matches_cpu_unrolled(mode, bidir):
     """The RNN operator on the GPU (library recurrence) against the per-step CPU implementation of the same operator."""
