@@ -13,6 +13,8 @@
  * and optionally
  *     int                mxb_lib_init(int framework_version);     called once after loading; non-zero = refuse
  *     const char*        mxb_lib_last_error(void);                text for the last non-zero return
+ *     int                mxb_lib_num_passes(void);                graph passes, usable as
+ *     const MXBPassDesc* mxb_lib_pass(int index);                 Symbol.optimize_for("<pass name>", ...)
  *
  * Every callback returns 0 on success.  Tensors are dense, row-major and contiguous.  For tensors on a GPU the
  * callbacks receive the CUDA stream (a cudaStream_t) on which the framework ordered the inputs; the work must be
@@ -85,6 +87,14 @@ typedef struct MXBOpDesc {
   int (*create_state)(const MXBAttrs* attrs, MXBOpState* state);
   void (*destroy_state)(MXBOpState state);
 } MXBOpDesc;
+
+/* A graph pass: rewrites a Symbol given in the framework's JSON form ("nodes", "arg_nodes", "heads").  On success
+ * *out_json points to a NUL-terminated text owned by the library that stays valid until the next call into the library
+ * from the same thread.  Options are the keyword arguments of optimize_for, as text. */
+typedef struct MXBPassDesc {
+  const char* name;
+  int (*run)(const char* graph_json, const MXBAttrs* options, const char** out_json);
+} MXBPassDesc;
 
 #ifdef __cplusplus
 }  /* extern "C" */

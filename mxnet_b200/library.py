@@ -46,6 +46,13 @@ _CREATE_STATE = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.POINTER(_Attrs), ctypes.PO
 _DESTROY_STATE = ctypes.CFUNCTYPE(None, ctypes.c_void_p)
 
 
+_PASS_RUN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_char_p, ctypes.POINTER(_Attrs), ctypes.POINTER(ctypes.c_char_p))
+
+
+class _PassDesc(ctypes.Structure):
+    _fields_ = [('name', ctypes.c_char_p), ('run', _PASS_RUN)]
+
+
 class _OpDesc(ctypes.Structure):
     _fields_ = [('name', ctypes.c_char_p), ('doc', ctypes.c_char_p), ('num_inputs', ctypes.c_int32),
                 ('num_outputs', ctypes.c_int32), ('input_names', ctypes.POINTER(ctypes.c_char_p)),
@@ -248,7 +255,39 @@ def _load_shared_object(path, verbose):
             print('loaded operator %s (%d inputs, %d outputs%s%s) from %s' % (
                 op.name, op.nin, op.nout, ', differentiable' if op.differentiable else '',
                 ', stateful' if op.stateful else '', os.path.basename(path)))
+    if hasattr(lib, 'mxb_lib_num_passes'):
+        from .symbol import passes
+        lib.mxb_lib_pass.restype = ctypes.POINTER(_PassDesc)
+        lib.mxb_lib_pass.argtypes = [ctypes.c_int]
+        for i in range(lib.mxb_lib_num_passes()):
+            desc = lib.mxb_lib_pass(i).contents
+            pname = desc.name.decode()
+            passes.register_backend(pname, _ExtPass(lib, desc, path))
+            names.append(pname)
+            if verbose:
+                print('loaded graph pass %s from %s' % (pname, os.path.basename(path)))
     return lib, names
+
+
+class _ExtPass(object):
+    """A graph pass of a loaded library as a partitioning backend: Symbol -> JSON -> library -> JSON -> Symbol."""
+
+    def __init__(self, lib, desc, path):
+        self.lib, self.desc, self.path = lib, desc, path
+
+    def __call__(self, sym, args=None, aux=None, **options):
+        from .symbol import load_json
+        cattrs, _keep = _pack_attrs(options)
+        out = ctypes.c_char_p()
+        rc = self.desc.run(sym.tojson().encode(), ctypes.byref(cattrs), ctypes.byref(out))
+        if rc != 0 or not out.value:
+            msg = ''
+            if hasattr(self.lib, 'mxb_lib_last_error'):
+                self.lib.mxb_lib_last_error.restype = ctypes.c_char_p
+                m = self.lib.mxb_lib_last_error()
+                msg = ': ' + m.decode() if m else ''
+            raise MXNetError('graph pass %s from %s returned %d%s' % (self.desc.name.decode(), self.path, rc, msg))
+        return load_json(out.value.decode())
 
 
 def load(path, verbose=True):

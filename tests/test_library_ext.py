@@ -94,3 +94,20 @@ def test_cuda_operator_library_runs_on_the_callers_stream(tmp_path):
         loss.backward()
         np.testing.assert_allclose(y.asnumpy(), np.maximum(v, 0))
         np.testing.assert_allclose(x.grad.asnumpy(), 3.0 * (v > 0))
+
+
+def test_graph_pass_from_library(tmp_path):
+    if shutil.which('g++') is None:
+        pytest.skip('no host compiler')
+    out = str(tmp_path / 'libpass_lib.so')
+    subprocess.check_call(['g++', '-O2', '-shared', '-fPIC', '-I', mx.library.include_dir(),
+                           os.path.join(ROOT, 'example', 'extensions', 'lib_pass', 'pass_lib.cc'), '-o', out])
+    mx.library.load(out, verbose=False)
+    x = mx.sym.var('x')
+    s = mx.sym.sigmoid(x * 2.0)
+    t = s.optimize_for('swap_op', **{'from': 'sigmoid', 'to': 'tanh'})
+    v = np.linspace(-1, 1, 7).astype('float32')
+    got = t._bind(mx.cpu(), {'x': nd.array(v)}).forward()[0].asnumpy()
+    np.testing.assert_allclose(got, np.tanh(2 * v), rtol=1e-5, atol=1e-6)
+    with pytest.raises(MXNetError, match='needs the options'):
+        s.optimize_for('swap_op')
