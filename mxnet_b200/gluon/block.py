@@ -388,6 +388,7 @@ class HybridBlock(Block):
     def _clear_cached_op(self):
         self._cached_graph = None
         self._cached_op = None
+        self._partitioned = None
 
     def hybridize(self, active=True, partition_if_dynamic=True, static_alloc=False, static_shape=False,
                   inline_limit=2, forward_bulk_size=None, backward_bulk_size=None, backend=None, backend_opts=None,
@@ -482,7 +483,35 @@ class HybridBlock(Block):
             out = self._call_forward(*args)
             self._cached_op = CachedOp(self, self._flags)
             return out
+        if self._backend not in (None, '', 'default'):
+            return self._call_partitioned(*args)
         return self._cached_op(*args)
+
+    def _call_partitioned(self, *args):
+        """``hybridize(backend=...)`` / ``optimize_for``: run the traced graph after the backend's graph pass
+        (``HybridBlock._build_cache`` with ``MXOptimizeForBackend`` in the reference, ``python/mxnet/gluon/block.py``)."""
+        flat, in_format = _flatten(args, 'input')
+        if self._cached_graph is None or in_format != self._in_format:
+            self._trace(*args)
+            self._partitioned = None
+        if getattr(self, '_partitioned', None) is None:
+            self._partitioned = self._cached_graph[1].optimize_for(self._backend, **self._backend_opts)
+        inputs, _ = self._cached_graph
+        arrays = [a for a in flat if isinstance(a, NDArray)]
+        ctx = arrays[0]._ctx
+        feed = {v.name: a._data for v, a in zip(inputs, arrays)}
+        needed = set(self._partitioned.list_inputs())
+        for name, p in self.collect_params().items():
+            if name in needed:
+                feed[name] = p.data(ctx)._data
+        if _state.state.recording:
+            with torch.enable_grad():
+                outs = self._partitioned._run(feed)
+        else:
+            with torch.no_grad():
+                outs = self._partitioned._run(feed)
+        res = [arrays[0].__class__._from_tensor(o, ctx) for o in outs]
+        return _regroup(res, self._out_format)[0]
 
     def export(self, path, epoch=0, remove_amp_cast=True):
         """Write ``path-symbol.json`` and ``path-%04d.params`` (``arg:``/``aux:`` prefixes)."""

@@ -16,6 +16,9 @@ def register_backend(name, fn):
 def optimize_for(sym, backend, args=None, aux=None, **kwargs):
     if backend in (None, '', 'default'):
         return sym
+    if backend == 'pointwise_fusion':
+        from .fusion import fuse_pointwise
+        return fuse_pointwise(sym)
     if backend not in _BACKENDS:
         raise MXNetError('subgraph backend %s is not registered (available: %s)' % (backend, sorted(_BACKENDS)))
     return _BACKENDS[backend](sym, args, aux, **kwargs)

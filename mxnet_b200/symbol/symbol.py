@@ -23,6 +23,7 @@ import numpy as _np
 import torch
 
 from .. import _state
+from .. import env as _env
 from ..attribute import AttrScope
 from ..base import MXNetError, to_torch_dtype, dtype_name, to_numpy_dtype
 from ..name import NameManager
@@ -134,11 +135,12 @@ def _topo(outputs):
 
 class Symbol(object):
     """Symbolic graph handle: a list of output entries over shared nodes."""
-    __slots__ = ('_outputs',)
+    __slots__ = ('_outputs', '_fused')
     __array_priority__ = 1000.0
 
     def __init__(self, outputs):
         self._outputs = list(outputs)
+        self._fused = None            # this graph after pointwise fusion (False: nothing to fuse), built on first GPU run
 
     # ------------------------------------------------------------------ introspection
     @property
@@ -268,6 +270,7 @@ class Symbol(object):
 
     def _compose(self, *args, **kwargs):
         kwargs.pop('name', None)
+        self._fused = None
         if args and kwargs:
             raise TypeError('compose only accept input Symbols either as positional or keyword arguments, not both')
         variables = [n for n in _topo(self._outputs) if n.op is None]
@@ -353,9 +356,18 @@ class Symbol(object):
 
     # ------------------------------------------------------------------ execution / inference
     def _run(self, feed, training=None):
-        """Evaluate the graph.  ``feed``: {variable name: tensor}.  Returns list of tensors."""
+        """Evaluate the graph.  ``feed``: {variable name: tensor}.  Returns list of tensors.  On a GPU the graph runs
+        with its elementwise groups fused into generated kernels (``MXNET_USE_FUSION``)."""
+        graph = self
+        if self._fused is not False and _env.get('MXNET_USE_FUSION') and any(
+                isinstance(t, torch.Tensor) and t.is_cuda for t in feed.values()):
+            if self._fused is None:
+                from .fusion import fuse_pointwise
+                fused = fuse_pointwise(self)
+                self._fused = fused if fused is not self else False
+            graph = self._fused or self
         values = {}
-        for node in _topo(self._outputs):
+        for node in _topo(graph._outputs):
             if node.op is None:
                 if node.name not in feed:
                     raise MXNetError('missing input %s' % node.name)
@@ -369,7 +381,7 @@ class Symbol(object):
                 ins = hook(node.op.name, ins)
             res = node.op.fn(*ins, **node.attrs)
             values[id(node)] = tuple(res) if isinstance(res, (tuple, list)) else (res,)
-        return [values[id(n)][k] for n, k in self._outputs]
+        return [values[id(n)][k] for n, k in graph._outputs]
 
     def _infer(self, shapes, dtypes, partial=False):
         feed, unknown = {}, []
