@@ -61,4 +61,5 @@ from . import registry
 from . import parallel
 from . import models
 from . import onnx
+from . import notebook
 from .ndarray import waitall

@@ -4,4 +4,5 @@ uses OpenCV); decoded arrays are HWC uint8 in RGB order like ``mx.image.imdecode
 from .image import *       # noqa: F401,F403
 from .image import _decode_to_numpy
 from . import detection
+from .detection import *     # noqa: F401,F403
 from .detection import ImageDetIter, CreateDetAugmenter

@@ -253,6 +253,15 @@ def index_add(a, ind, val):
     return out
 
 
+@register('_npx_constraint_check', inputs=('input',), defaults={'msg': 'Constraint violated.'})
+def constraint_check(input, msg='Constraint violated.'):   # pylint: disable=redefined-builtin
+    """``array(True)`` when every element of the boolean input holds, else ValueError(msg)
+    (``src/operator/numpy/np_constraint_check.cc``).  The value is read on the host, like the reference's check."""
+    if input.device.type != 'meta' and not bool(input.all()):
+        raise ValueError(msg)
+    return torch.ones((), dtype=torch.bool, device=input.device)
+
+
 @register('_npx_index_update', 'index_update', inputs=('a', 'ind', 'val'))
 def index_update(a, ind, val):
     out = a.clone()

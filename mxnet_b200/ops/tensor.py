@@ -250,7 +250,12 @@ def _reg_binary(name, fn, legacy_names, result_bool=False, np_name=None):
         return fn(lhs, rhs)
 
     def ts_legacy(data, scalar=0.0, is_int=None):
-        r = fn(data, _maybe_float(data, scalar))
+        s = _maybe_float(data, scalar)
+        try:
+            r = fn(data, s)
+        except TypeError:             # functions that take tensors only (maximum, minimum, hypot ...)
+            r = fn(data, torch.as_tensor(s, device=data.device,
+                                         dtype=data.dtype if data.dtype.is_floating_point or isinstance(s, int) else torch.float32))
         return r.to(data.dtype) if result_bool else r
 
     def rts_legacy(data, scalar=0.0, is_int=None):

@@ -550,36 +550,57 @@ def compile_cubin(source, arch='sm_100a'):
     return cubin
 
 
-_kernels = {}                                     # source -> (module, function), per process
+_kernels = {}                                     # (device, source, name) -> (module, function), per process
 
 
-def _get_function(source, name):
-    hit = _kernels.get((source, name))
-    if hit is not None:
-        return hit[1]
+def _driver():
     try:
         from cuda.bindings import driver as cu
     except Exception:   # pylint: disable=broad-except
         from cuda import cuda as cu
-    major, minor = torch.cuda.get_device_capability()
+    return cu
+
+
+def _ensure_context(index):
+    """Make the device's primary context current on this thread for driver-API calls.  The tensor library binds it
+    through the runtime API on the threads it computes on, but a thread that has only run cached allocations so far
+    (an autograd worker) may have none."""
+    cu = _driver()
+    err, ctx = cu.cuCtxGetCurrent()
+    if int(err) == 0 and ctx is not None and int(ctx) != 0:
+        return
+    torch.cuda.current_stream(index)              # initialises the runtime and the primary context
+    err, dev = cu.cuDeviceGet(index)
+    err, pctx = cu.cuDevicePrimaryCtxRetain(dev)
+    if int(err) != 0:
+        raise MXNetError('cuDevicePrimaryCtxRetain failed: %s' % err)
+    err, = cu.cuCtxSetCurrent(pctx)
+    if int(err) != 0:
+        raise MXNetError('cuCtxSetCurrent failed: %s' % err)
+
+
+def _get_function(source, name, index=0):
+    hit = _kernels.get((index, source, name))
+    if hit is not None:
+        return hit[1]
+    cu = _driver()
+    major, minor = torch.cuda.get_device_capability(index)
     cubin = compile_cubin(source, 'sm_%d%d%s' % (major, minor, 'a' if major >= 9 else ''))
-    torch.cuda.current_stream()                   # a context exists from here on
+    _ensure_context(index)
     err, module = cu.cuModuleLoadData(cubin)
     if int(err) != 0:
         raise MXNetError('cuModuleLoadData failed on a fused kernel: %s' % err)
     err, fn = cu.cuModuleGetFunction(module, name.encode())
     if int(err) != 0:
         raise MXNetError('kernel %s not found in its module: %s' % (name, err))
-    _kernels[(source, name)] = (module, fn, cu)
+    _kernels[(index, source, name)] = (module, fn)
     return fn
 
 
 def _launch(fn, n_vec, c_vec, pointers, device):
     import ctypes
-    try:
-        from cuda.bindings import driver as cu
-    except Exception:   # pylint: disable=broad-except
-        from cuda import cuda as cu
+    cu = _driver()
+    _ensure_context(device.index or 0)
     holders = [ctypes.c_longlong(n_vec), ctypes.c_longlong(c_vec)] + [ctypes.c_void_p(p) for p in pointers]
     arr = (ctypes.c_void_p * len(holders))(*[ctypes.addressof(h) for h in holders])
     blocks = max(1, min((n_vec + 255) // 256, 148 * 8))
@@ -664,7 +685,7 @@ class FusedGroup(object):
     def run_forward(self, tensors, plan):
         modes, out_dtypes, shape, vec = plan
         src = kernel_source(self, [t.dtype for t in tensors], modes, out_dtypes, vec)
-        fn = _get_function(src, 'fused_fwd')
+        fn = _get_function(src, 'fused_fwd', tensors[0].device.index or 0)
         dev = tensors[0].device
         outs = [torch.empty(shape, dtype=d, device=dev) for d in out_dtypes]
         n = outs[0].numel()
@@ -678,7 +699,7 @@ class FusedGroup(object):
         if vec == 4 and any(g.data_ptr() % (4 * g.element_size()) for g in ograds):
             vec = 1
         src = kernel_source(self, [t.dtype for t in tensors], modes, out_dtypes, vec, True, need_grad)
-        fn = _get_function(src, 'fused_bwd')
+        fn = _get_function(src, 'fused_bwd', tensors[0].device.index or 0)
         grads = [torch.empty(shape, dtype=(t.dtype if m == FULL else torch.float32), device=dev) if ng else None
                  for t, m, ng in zip(tensors, modes, need_grad)]
         n = ograds[0].numel()

@@ -236,3 +236,53 @@ def test_quantize_dequantize_round_trip():
     assert q.dtype == np.int8
     back = nd.contrib.dequantize(q, mn, mxv, out_type='float32')
     np.testing.assert_allclose(back.asnumpy(), x.asnumpy(), atol=3.0 / 127 + 1e-6)
+
+
+def test_notebook_pandas_logger_collects_metrics():
+    pd = pytest.importorskip('pandas')
+    from collections import namedtuple
+    from mxnet_b200.notebook.callback import PandasLogger, LiveLearningCurve, args_wrapper
+    Param = namedtuple('Param', 'epoch nbatch eval_metric')
+    metric = mx.gluon.metric.Accuracy()
+    metric.update([mx.nd.array([0, 1, 1])], [mx.nd.array([[0.9, 0.1], [0.2, 0.8], [0.7, 0.3]])])
+    log = PandasLogger(batch_size=3, frequent=2)
+    for i in range(5):
+        log.train_cb(Param(0, i, metric))
+    log.eval_cb(Param(0, 5, metric))
+    log.epoch_cb()
+    assert isinstance(log.train_df, pd.DataFrame) and len(log.train_df) == 3          # batches 0, 2, 4
+    assert abs(log.train_df['accuracy'].iloc[-1] - 2 / 3) < 1e-6
+    assert {'records_per_sec', 'minibatch_count', 'epoch'} <= set(log.train_df.columns)
+    assert len(log.eval_df) == 1 and len(log.epoch_df) == 1
+    curve = LiveLearningCurve('accuracy', display_freq=1000, frequent=1)       # collects without a chart when bokeh is absent
+    curve.batch_cb(Param(0, 0, metric))
+    curve.eval_cb(Param(0, 0, metric))
+    assert len(curve._data['train']['accuracy']) == 1 and len(curve._data['eval']['accuracy']) == 1
+    merged = args_wrapper(log, curve)
+    assert len(merged['batch_end_callback']) == 2
+
+
+def test_dataloader_iter_pads_the_last_batch():
+    from mxnet_b200.contrib.io import DataLoaderIter
+    data = np.arange(10 * 4, dtype='float32').reshape(10, 4)
+    label = np.arange(10, dtype='float32')
+    loader = mx.gluon.data.DataLoader(mx.gluon.data.ArrayDataset(data, label), batch_size=4)
+    it = DataLoaderIter(loader)
+    assert it.provide_data[0].shape == (4, 4) and it.provide_label[0].name == 'softmax_label'
+    batches = list(it)
+    assert [b.pad for b in batches] == [0, 0, 2]
+    assert batches[-1].data[0].shape == (4, 4)
+    np.testing.assert_allclose(batches[-1].data[0].asnumpy()[:2], data[8:])
+    it.reset()
+    assert len(list(it)) == 3
+
+
+def test_constraint_check_operator():
+    mx.npx.set_np()
+    try:
+        ok = mx.npx.constraint_check(mx.np.array([1.0, 2.0]) > 0, 'Scale should be larger than zero')
+        assert bool(ok.asnumpy())
+        with pytest.raises(ValueError, match='larger than zero'):
+            mx.npx.constraint_check(mx.np.array([1.0, -2.0]) > 0, 'Scale should be larger than zero')
+    finally:
+        mx.npx.reset_np()
