@@ -52,6 +52,11 @@ struct LstmParams {
                          // operand that phase B of that step streams (no separate exchange copy)
   void* dh0;             // [B, H]
   void* dc0;             // [B, H]
+  // GRU / vanilla RNN kernels only
+  const void* bhn;       // [H] hidden-side bias of the GRU candidate gate (inside r * (...))
+  void* hnb;             // [T, H, Bp] h_{t-1}.W_hn + b_hn, k-major (GRU, saved for backward; may be null)
+  void* dan;             // [T, H, Bp] gradient w.r.t. the candidate pre-activation, k-major (GRU backward)
+  int relu;              // vanilla RNN: 1 = relu, 0 = tanh
 };
 
 __device__ __forceinline__ unsigned long long lstm_now_ns() {
@@ -347,6 +352,204 @@ __global__ void __launch_bounds__(kLstmThreads) lstm_bwd_kernel(const LstmParams
   }
 }
 
+// ---- GRU and vanilla RNN --------------------------------------------------------------------------------------------
+// Same ownership and exchange as the LSTM kernels with NG gates per unit (3: GRU in the order r, z, n; 1: vanilla RNN).
+//   GRU:      r = sigmoid(xr + hr), z = sigmoid(xz + hz), n = tanh(xn + r * (hn + b_hn)), h_t = (1 - z) * n + z * h_{t-1}
+//             where x* = x_t.W_ih^T + b_ih (+ b_hh for r and z) comes from the input GEMM and h* = h_{t-1}.W_hh^T
+//   vanilla:  h_t = act(x + h_{t-1}.W_hh^T), act = tanh or relu, x including both biases
+// (src/operator/rnn_impl.h: GruForwardTraining, VanillaRNNForwardTraining in the reference.)
+// Forward shared memory: Wt [H][NG*U], red [KG][Bp][NG*U], hst [Bp][U] (fp32 copy of the CTA's own h), stage.
+__host__ __device__ __forceinline__ size_t rnn_align4(size_t floats) { return (floats + 3) & ~(size_t)3; }
+
+template <typename T, typename X, int U, int NG>
+__global__ void __launch_bounds__(kLstmThreads) rnn_fwd_kernel(const LstmParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int H = p.H, B = p.B, Bp = p.Bp;
+  constexpr int R = NG * U;
+  const int j0 = blockIdx.x * U;
+  const int nu = min(U, H - j0);
+  const int NB2 = Bp / 2;
+  const int KG = max(1, kLstmThreads / NB2);
+  float* Wt = reinterpret_cast<float*>(smem_raw);                 // [H][R]
+  float* red = Wt + (size_t)H * R;                                // [KG][Bp][R]
+  float* hst = red + (size_t)KG * Bp * R;                         // [Bp][U]
+  // [2][tileK][Bp], on a 16-byte boundary for the cp.async copies (H * R need not be a multiple of four floats)
+  X* stage = reinterpret_cast<X*>(Wt + rnn_align4((size_t)H * R + (size_t)KG * Bp * R + (size_t)Bp * U));
+  X* hx = static_cast<X*>(p.hbuf);
+  for (int idx = threadIdx.x; idx < H * R; idx += blockDim.x) {
+    const int k = idx / R, r = idx % R;
+    const int g = r / U, jj = r % U;
+    Wt[idx] = jj < nu ? ldf<T>(p.whh, (int64_t)(g * H + j0 + jj) * H + k) : 0.f;
+  }
+  for (int idx = threadIdx.x; idx < Bp * U; idx += blockDim.x) {
+    const int b = idx / U, jj = idx % U;
+    hst[idx] = (jj < nu && b < B) ? ldf<T>(p.h0, (int64_t)b * H + j0 + jj) : 0.f;
+  }
+  for (int idx = threadIdx.x; idx < Bp * nu; idx += blockDim.x) {
+    const int jj = idx / Bp, b = idx % Bp;
+    hx[(int64_t)(j0 + jj) * Bp + b] = Cvt<X>::from_f(b < B ? ldf<T>(p.h0, (int64_t)b * H + j0 + jj) : 0.f);
+  }
+  unsigned int target = gridDim.x;
+  bool alive = grid_barrier(p.bar, target);
+  const int kg = threadIdx.x / NB2, b0 = (threadIdx.x % NB2) * 2;
+  const bool active = kg < KG;
+  for (int t = 0; t < p.T && alive; ++t) {
+    const X* hprev = hx + (int64_t)(t & 1) * H * Bp;
+    X* hnext = hx + (int64_t)((t + 1) & 1) * H * Bp;
+    float xp[2][NG];
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int idx = threadIdx.x + it * kLstmThreads;
+      const int jj = idx / Bp, b = idx % Bp;
+#pragma unroll
+      for (int g = 0; g < NG; ++g)
+        xp[it][g] = (idx < Bp * nu && b < B) ? ldf<T>(p.xproj, ((int64_t)t * B + b) * NG * H + g * H + j0 + jj) : 0.f;
+    }
+    float acc[2][R];
+    stream_matmul<X, R>(hprev, H, Bp, Wt, stage, p.tileK, kg, KG, b0, active, acc);
+    if (active) {
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        float* dst = red + ((size_t)kg * Bp + b0 + rr) * R;
+#pragma unroll
+        for (int o = 0; o < R; ++o) dst[o] = acc[rr][o];
+      }
+    }
+    __syncthreads();
+    auto update_cell = [&](int idx, const float (&xg)[NG]) {
+      const int jj = idx / Bp, b = idx % Bp, j = j0 + jj;
+      if (b >= B) { hnext[(int64_t)j * Bp + b] = Cvt<X>::from_f(0.f); return; }
+      float a[NG];
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        float s = 0.f;
+        for (int q = 0; q < KG; ++q) s += red[((size_t)q * Bp + b) * R + g * U + jj];
+        a[g] = s;
+      }
+      float h;
+      if constexpr (NG == 3) {
+        const float rg = sigmoidf_(xg[0] + a[0]), zg = sigmoidf_(xg[1] + a[1]);
+        const float hn = a[2] + ldf<T>(p.bhn, j);
+        const float ng = tanhf(xg[2] + rg * hn);
+        h = (1.f - zg) * ng + zg * hst[b * U + jj];
+        if (p.gates) {
+          const int64_t gb = ((int64_t)t * 3 * H + j) * Bp + b, gs = (int64_t)H * Bp;
+          stf<T>(p.gates, gb, rg); stf<T>(p.gates, gb + gs, zg); stf<T>(p.gates, gb + 2 * gs, ng);
+          stf<T>(p.hnb, ((int64_t)t * H + j) * Bp + b, hn);
+        }
+      } else {
+        const float s = xg[0] + a[0];
+        h = p.relu ? fmaxf(s, 0.f) : tanhf(s);
+      }
+      hst[b * U + jj] = h;
+      hnext[(int64_t)j * Bp + b] = Cvt<X>::from_f(h);
+      stf<T>(p.y, ((int64_t)t * B + b) * H + j, h);
+      if (t == p.T - 1) stf<T>(p.hT, (int64_t)b * H + j, h);
+    };
+    if ((int)threadIdx.x < Bp * nu) update_cell(threadIdx.x, xp[0]);
+    if ((int)threadIdx.x + kLstmThreads < Bp * nu) update_cell(threadIdx.x + kLstmThreads, xp[1]);
+    for (int idx = threadIdx.x + 2 * kLstmThreads; idx < Bp * nu; idx += blockDim.x) {
+      const int jj = idx / Bp, b = idx % Bp;
+      float xg[NG];
+#pragma unroll
+      for (int g = 0; g < NG; ++g) xg[g] = b < B ? ldf<T>(p.xproj, ((int64_t)t * B + b) * NG * H + g * H + j0 + jj) : 0.f;
+      update_cell(idx, xg);
+    }
+    target += gridDim.x;
+    alive = grid_barrier(p.bar, target);
+  }
+}
+
+// Backward shared memory: Wc [NG*H][U], red [KG][Bp][U], dh_rec [Bp][U], dh_dir [Bp][U] (the z * dh term of the GRU),
+// stage.  The exchanged array `dgates` [T, NG*H, Bp] holds the gradients w.r.t. the hidden-side products (GRU: dar, daz,
+// dan * r); the GRU's gradient w.r.t. the candidate pre-activation itself goes to `dan` for the input-side GEMMs.
+template <typename T, typename X, int U, int NG>
+__global__ void __launch_bounds__(kLstmThreads) rnn_bwd_kernel(const LstmParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int H = p.H, B = p.B, Bp = p.Bp, K = NG * p.H;
+  const int j0 = blockIdx.x * U;
+  const int nu = min(U, H - j0);
+  const int NB2 = Bp / 2;
+  const int KG = max(1, kLstmThreads / NB2);
+  float* Wc = reinterpret_cast<float*>(smem_raw);                 // [K][U]
+  float* red = Wc + (size_t)K * U;                                // [KG][Bp][U]
+  float* dh_rec = red + (size_t)KG * Bp * U;                      // [Bp][U]
+  float* dh_dir = dh_rec + (size_t)Bp * U;                        // [Bp][U]
+  X* stage = reinterpret_cast<X*>(Wc + rnn_align4((size_t)K * U + (size_t)KG * Bp * U + (size_t)2 * Bp * U));   // 16-byte boundary
+  for (int idx = threadIdx.x; idx < K * U; idx += blockDim.x) {
+    const int r = idx / U, jj = idx % U;
+    Wc[idx] = jj < nu ? ldf<T>(p.whh, (int64_t)r * H + j0 + jj) : 0.f;
+  }
+  for (int idx = threadIdx.x; idx < Bp * U; idx += blockDim.x) {
+    const int b = idx / U, jj = idx % U;
+    dh_rec[idx] = (jj < nu && b < B && p.dhT) ? ldf<T>(p.dhT, (int64_t)b * H + j0 + jj) : 0.f;
+    dh_dir[idx] = 0.f;
+  }
+  __syncthreads();
+  unsigned int target = 0;
+  bool alive = true;
+  const int kg = threadIdx.x / NB2, b0 = (threadIdx.x % NB2) * 2;
+  const bool active = kg < KG;
+  for (int t = p.T - 1; t >= 0 && alive; --t) {
+    X* dgt = static_cast<X*>(p.dgates) + (int64_t)t * K * Bp;
+    for (int idx = threadIdx.x; idx < Bp * nu; idx += blockDim.x) {
+      const int jj = idx / Bp, b = idx % Bp, j = j0 + jj;
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, dn = 0.f, direct = 0.f;
+      if (b < B) {
+        const float dh = ldf<T>(p.dy, ((int64_t)t * B + b) * H + j) + dh_rec[b * U + jj];
+        if constexpr (NG == 3) {
+          const int64_t gb = ((int64_t)t * 3 * H + j) * Bp + b, gs = (int64_t)H * Bp;
+          const float rg = ldf<T>(p.gates, gb), zg = ldf<T>(p.gates, gb + gs), ng = ldf<T>(p.gates, gb + 2 * gs);
+          const float hn = ldf<T>(p.hnb, ((int64_t)t * H + j) * Bp + b);
+          const float hp = t > 0 ? ldf<T>(p.y, ((int64_t)(t - 1) * B + b) * H + j) : ldf<T>(p.h0, (int64_t)b * H + j);
+          dn = dh * (1.f - zg) * (1.f - ng * ng);
+          d1 = dh * (hp - ng) * zg * (1.f - zg);
+          d0 = dn * hn * rg * (1.f - rg);
+          d2 = dn * rg;
+          direct = dh * zg;
+        } else {
+          const float yv = ldf<T>(p.y, ((int64_t)t * B + b) * H + j);
+          d0 = p.relu ? (yv > 0.f ? dh : 0.f) : dh * (1.f - yv * yv);
+        }
+      }
+      dh_dir[b * U + jj] = direct;
+      dgt[(int64_t)j * Bp + b] = Cvt<X>::from_f(d0);
+      if constexpr (NG == 3) {
+        dgt[(int64_t)(H + j) * Bp + b] = Cvt<X>::from_f(d1);
+        dgt[(int64_t)(2 * H + j) * Bp + b] = Cvt<X>::from_f(d2);
+        stf<T>(p.dan, ((int64_t)t * H + j) * Bp + b, dn);
+      }
+    }
+    target += gridDim.x;
+    alive = grid_barrier(p.bar, target);
+    if (!alive) break;
+    float acc[2][U];
+    stream_matmul<X, U>(dgt, K, Bp, Wc, stage, p.tileK, kg, KG, b0, active, acc);
+    if (active) {
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        float* dst = red + ((size_t)kg * Bp + b0 + rr) * U;
+#pragma unroll
+        for (int o = 0; o < U; ++o) dst[o] = acc[rr][o];
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < Bp * U; idx += blockDim.x) {
+      const int b = idx / U, jj = idx % U;
+      float s = dh_dir[idx];
+      for (int q = 0; q < KG; ++q) s += red[((size_t)q * Bp + b) * U + jj];
+      dh_rec[idx] = s;
+    }
+    __syncthreads();
+  }
+  if (alive) {
+    for (int idx = threadIdx.x; idx < B * nu; idx += blockDim.x) {
+      const int b = idx / nu, jj = idx % nu;
+      stf<T>(p.dh0, (int64_t)b * H + j0 + jj, dh_rec[b * U + jj]);
+    }
+  }
+}
+
 static int lstm_units_per_cta(int H) {
   int u = (H + sm_count() - 1) / sm_count();
   return u < 1 ? 1 : u;
@@ -411,6 +614,65 @@ static int dispatch_lstm(bool backward, LstmParams& p, cudaStream_t st) {
   }
 }
 
+static size_t rnn_fwd_fixed(int B, int H, int U, int NG) {
+  const int Bp = lstm_bp(B), NB2 = Bp / 2;
+  const int KG = kLstmThreads / NB2 > 1 ? kLstmThreads / NB2 : 1;
+  return rnn_align4((size_t)H * NG * U + (size_t)KG * Bp * NG * U + (size_t)Bp * U) * sizeof(float);
+}
+static size_t rnn_bwd_fixed(int B, int H, int U, int NG) {
+  const int Bp = lstm_bp(B), NB2 = Bp / 2;
+  const int KG = kLstmThreads / NB2 > 1 ? kLstmThreads / NB2 : 1;
+  return rnn_align4((size_t)NG * H * U + (size_t)KG * Bp * U + (size_t)2 * Bp * U) * sizeof(float);
+}
+
+template <typename T, typename X, int U, int NG>
+static int launch_rnn(bool backward, LstmParams& p, cudaStream_t st) {
+  const int Bp = lstm_bp(p.B);
+  const size_t fixed = backward ? rnn_bwd_fixed(p.B, p.H, U, NG) : rnn_fwd_fixed(p.B, p.H, U, NG);
+  const int K = backward ? NG * p.H : p.H;
+  const int tileK = lstm_tile_rows(fixed, K, Bp, sizeof(X));
+  if (tileK < kMinTileK && tileK < K) return -4;
+  const size_t smem = fixed + (size_t)2 * tileK * Bp * sizeof(X);
+  p.tileK = tileK;
+  const void* fn = backward ? (const void*)rnn_bwd_kernel<T, X, U, NG> : (const void*)rnn_fwd_kernel<T, X, U, NG>;
+  cudaError_t rc = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (rc != cudaSuccess) return (int)rc;
+  const int grid = (p.H + U - 1) / U;
+  int per_sm = 0;
+  rc = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kLstmThreads, smem);
+  if (rc != cudaSuccess) return (int)rc;
+  if ((int64_t)per_sm * sm_count() < grid) return -4;      // the grid barrier needs every CTA resident
+  p.U = U;
+  p.Bp = Bp;
+  void* args[] = {&p};
+  rc = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kLstmThreads), args, smem, st);
+  return (int)rc;
+}
+
+template <typename T, typename X, int NG>
+static int dispatch_rnn(bool backward, LstmParams& p, cudaStream_t st) {
+  const int U = lstm_units_per_cta(p.H);
+  switch (U) {
+    case 1: return launch_rnn<T, X, 1, NG>(backward, p, st);
+    case 2: return launch_rnn<T, X, 2, NG>(backward, p, st);
+    case 3: return launch_rnn<T, X, 3, NG>(backward, p, st);
+    case 4: return launch_rnn<T, X, 4, NG>(backward, p, st);
+    case 5: return launch_rnn<T, X, 5, NG>(backward, p, st);
+    case 6: return launch_rnn<T, X, 6, NG>(backward, p, st);
+    case 7: return launch_rnn<T, X, 7, NG>(backward, p, st);
+    case 8: return launch_rnn<T, X, 8, NG>(backward, p, st);
+    default: return -4;
+  }
+}
+
+template <int NG>
+static int dispatch_rnn_dtype(int dtype, bool backward, LstmParams& p, cudaStream_t st) {
+  if (dtype == kF32) return dispatch_rnn<float, float, NG>(backward, p, st);
+  if (dtype == kF16) return dispatch_rnn<__half, __half, NG>(backward, p, st);
+  if (dtype == kBF16) return dispatch_rnn<__nv_bfloat16, __nv_bfloat16, NG>(backward, p, st);
+  return -1;
+}
+
 }  // namespace mxb
 
 using namespace mxb;
@@ -459,4 +721,34 @@ MXB_EXPORT int mxb_lstm_backward(int dtype, const void* dy, const void* dhT, con
   if (dtype == kF16) return dispatch_lstm<__half, __half>(true, p, st);
   if (dtype == kBF16) return dispatch_lstm<__nv_bfloat16, __nv_bfloat16>(true, p, st);
   return -1;
+}
+
+// GRU (mode 0), vanilla RNN with tanh (1) or relu (2).  `xproj` [T, B, NG*H] holds x.W_ih^T + b_ih, plus b_hh except for
+// the GRU's candidate gate whose hidden-side bias is `bhn` [H].  `gates` [T, 3H, Bp] and `hnb` [T, H, Bp] are written
+// for the GRU when non-null (training).  Shapes accepted: mxb_lstm_supported(B, H).
+MXB_EXPORT int mxb_rnn_forward(int dtype, int mode, const void* xproj, const void* whh, const void* bhn, const void* h0,
+                               void* y, void* hT, void* gates, void* hnb, void* hbuf, unsigned int* bar, int T, int B, int H,
+                               void* stream) {
+  if (!mxb_lstm_supported(B, H) || T < 1 || mode < 0 || mode > 2) return -4;
+  if (mode == 0 && bhn == nullptr) return -2;
+  LstmParams p{};
+  p.xproj = xproj; p.whh = whh; p.bhn = bhn; p.h0 = h0; p.y = y; p.hT = hT; p.gates = gates; p.hnb = hnb; p.hbuf = hbuf;
+  p.bar = bar; p.T = T; p.B = B; p.H = H; p.relu = mode == 2;
+  cudaStream_t st = (cudaStream_t)stream;
+  return mode == 0 ? dispatch_rnn_dtype<3>(dtype, false, p, st) : dispatch_rnn_dtype<1>(dtype, false, p, st);
+}
+
+// `dgates` [T, NG*H, Bp]: gradients w.r.t. the hidden-side products (output; also the exchanged operand).  GRU only:
+// `gates`, `hnb` from the forward pass, `dan` [T, H, Bp] receives the gradient w.r.t. the candidate pre-activation.
+MXB_EXPORT int mxb_rnn_backward(int dtype, int mode, const void* dy, const void* dhT, const void* gates, const void* hnb,
+                                const void* y, const void* h0, const void* whh, void* dgates, void* dan, void* dh0,
+                                unsigned int* bar, int T, int B, int H, void* stream) {
+  if (!mxb_lstm_supported(B, H) || T < 1 || mode < 0 || mode > 2) return -4;
+  if (mode == 0 && (gates == nullptr || hnb == nullptr || dan == nullptr)) return -2;
+  LstmParams p{};
+  p.dy = dy; p.dhT = dhT; p.gates = const_cast<void*>(gates); p.hnb = const_cast<void*>(hnb); p.y = const_cast<void*>(y);
+  p.h0 = h0; p.whh = whh; p.dgates = dgates; p.dan = dan; p.dh0 = dh0; p.bar = bar; p.T = T; p.B = B; p.H = H;
+  p.relu = mode == 2;
+  cudaStream_t st = (cudaStream_t)stream;
+  return mode == 0 ? dispatch_rnn_dtype<3>(dtype, true, p, st) : dispatch_rnn_dtype<1>(dtype, true, p, st);
 }

@@ -98,6 +98,111 @@ def check_errors(bar):
         raise RuntimeError('LSTM recurrence kernel: grid barrier timed out')
 
 
+_MODES = {'gru': 0, 'rnn_tanh': 1, 'rnn_relu': 2}
+
+
+class _RecurrentLayer(torch.autograd.Function):
+    """y, hT = layer(x[T,B,I], w_ih[G*H,I], w_hh[G*H,H], b_ih[G*H], b_hh[G*H], h0[B,H]) for a GRU (G = 3, gates r, z, n)
+    or a vanilla RNN (G = 1).  The input projection of all steps is one GEMM; the recurrence is one cooperative kernel."""
+
+    @staticmethod
+    def forward(ctx, x, w_ih, w_hh, b_ih, b_hh, h0, mode, training):
+        L = lib()
+        T, B, I = x.shape
+        H = w_hh.shape[1]
+        G = 3 if mode == 0 else 1
+        x = x.contiguous()
+        w_ih, w_hh, h0 = w_ih.contiguous(), w_hh.contiguous(), h0.contiguous()
+        for t, name, shape in ((w_ih, 'w_ih', (G * H, I)), (w_hh, 'w_hh', (G * H, H)), (h0, 'h0', (B, H))):
+            require(t, name, dtype=x.dtype, device=x.device, shape=shape)
+        bias = b_ih.float() + b_hh.float()
+        bhn = None
+        if mode == 0:                    # the candidate gate's hidden-side bias stays inside r * (...)
+            bias[2 * H:] = b_ih.float()[2 * H:]
+            bhn = b_hh[2 * H:].to(x.dtype).contiguous()
+        bias = bias.to(x.dtype)
+        from . import gemm_ops
+        x2 = x.reshape(T * B, I)
+        if x.dtype in (torch.float16, torch.bfloat16) and gemm_ops.operand_ok(x2) and gemm_ops.operand_ok(w_ih):
+            xproj = gemm_ops.gemm(x2, w_ih, False, False, bias)
+        else:
+            xproj = torch.addmm(bias, x2, w_ih.t())
+        y = torch.empty(T, B, H, dtype=x.dtype, device=x.device)
+        hT = torch.empty_like(h0)
+        Bp = L.mxb_lstm_bp(B)
+        save = training and mode == 0
+        gates = torch.empty(T, 3 * H, Bp, dtype=x.dtype, device=x.device) if save else None
+        hnb = torch.empty(T, H, Bp, dtype=x.dtype, device=x.device) if save else None
+        hbuf = torch.empty(L.mxb_lstm_exchange_bytes(B, H), dtype=torch.uint8, device=x.device)
+        bar = _barrier_words(x.device)
+        check(L.mxb_rnn_forward(dt(x), mode, ptr(xproj), ptr(w_hh), ptr(bhn), ptr(h0), ptr(y), ptr(hT), ptr(gates), ptr(hnb),
+                                ptr(hbuf), ptr(bar), T, B, H, stream_ptr(x.device)), 'rnn_forward')
+        count_launch(1)
+        ctx.save_for_backward(x, w_ih, w_hh, h0, y, gates, hnb)
+        ctx.mode, ctx.trained = mode, bool(training)
+        ctx.bias_dtypes = (b_ih.dtype, b_hh.dtype)
+        ctx.fwd_bar = bar
+        ctx.set_materialize_grads(False)
+        return y, hT
+
+    @staticmethod
+    def backward(ctx, dy, dhT):
+        x, w_ih, w_hh, h0, y, gates, hnb = ctx.saved_tensors
+        mode = ctx.mode
+        if not ctx.trained:
+            raise RuntimeError('RNN backward needs a forward pass in training mode')
+        L = lib()
+        T, B, I = x.shape
+        H = w_hh.shape[1]
+        G = 3 if mode == 0 else 1
+        Bp = L.mxb_lstm_bp(B)
+        dy = torch.zeros_like(y) if dy is None else dy.contiguous()
+        require(dy, 'out_grad', dtype=x.dtype, device=x.device, shape=y.shape)
+        dhT = dhT.contiguous() if dhT is not None else None
+        dgh = torch.empty(T, G * H, Bp, dtype=x.dtype, device=x.device)          # hidden-side gate gradients, k-major
+        dan = torch.empty(T, H, Bp, dtype=x.dtype, device=x.device) if mode == 0 else None
+        dh0 = torch.empty_like(h0)
+        bar = _barrier_words(x.device)
+        check(L.mxb_rnn_backward(dt(x), mode, ptr(dy), ptr(dhT), ptr(gates), ptr(hnb), ptr(y), ptr(h0), ptr(w_hh), ptr(dgh),
+                                 ptr(dan), ptr(dh0), ptr(bar), T, B, H, stream_ptr(x.device)), 'rnn_backward')
+        count_launch(1)
+        dgh2 = dgh[:, :, :B].permute(0, 2, 1).reshape(T * B, G * H)
+        if mode == 0:                    # the input side sees the candidate gradient without the factor r
+            dgx2 = torch.cat([dgh2[:, :2 * H], dan[:, :, :B].permute(0, 2, 1).reshape(T * B, H)], 1)
+        else:
+            dgx2 = dgh2
+        hprev = torch.cat([h0.unsqueeze(0), y[:-1]], 0).reshape(T * B, H)
+        dx = _mm(dgx2, w_ih, False, True).reshape(T, B, I) if ctx.needs_input_grad[0] else None
+        dw_ih = _mm(dgx2, x.reshape(T * B, I), True, True)
+        dw_hh = _mm(dgh2, hprev, True, True)
+        db_ih = dgx2.sum(0, dtype=torch.float32)
+        db_hh = dgh2.sum(0, dtype=torch.float32) if mode == 0 else db_ih
+        return dx, dw_ih, dw_hh, db_ih.to(ctx.bias_dtypes[0]), db_hh.to(ctx.bias_dtypes[1]), dh0, None, None
+
+
+def recurrent(mode, data, parameters, state, state_size, num_layers, p, training, bidirectional=False):
+    """Multi-layer GRU / vanilla RNN over (T, N, C) data with the flat parameter vector of the RNN operator; layout and
+    direction handling as in :func:`lstm`."""
+    from ..nn import rnn_unpack
+    T, N, I = data.shape
+    d = 2 if bidirectional else 1
+    layers = rnn_unpack(parameters, mode, num_layers, I, state_size, bool(bidirectional), None)
+    x = data
+    hs = []
+    for l in range(num_layers):
+        outs = []
+        for di in range(d):
+            w_ih, w_hh, _w_hr, b_ih, b_hh = layers[l * d + di]
+            xin = x if di == 0 else x.flip(0)
+            y, h = _RecurrentLayer.apply(xin.contiguous(), w_ih, w_hh, b_ih, b_hh, state[l * d + di], _MODES[mode], bool(training))
+            outs.append(y if di == 0 else y.flip(0))
+            hs.append(h)
+        x = outs[0] if d == 1 else torch.cat(outs, -1)
+        if p > 0 and training and l < num_layers - 1:
+            x = torch.nn.functional.dropout(x, p, True)
+    return x, torch.stack(hs, 0)
+
+
 def lstm(data, parameters, state, state_cell, state_size, num_layers, p, training, bidirectional=False):
     """Multi-layer LSTM over (T, N, C) data with the flat parameter vector of the RNN operator.  A bidirectional layer
     runs the recurrence kernel twice, the second time on the time-reversed sequence with the reverse direction's

@@ -871,10 +871,17 @@ def rnn(data, parameters, state, state_cell=None, sequence_length=None, state_si
             out, hy, cy = rnn_ops.lstm(data, parameters, state, state_cell, state_size, num_layers, p, training,
                                        bidirectional)
             return (out, hy, cy) if state_outputs else out
+    if mode in ('gru', 'rnn_tanh', 'rnn_relu') and projection_size is None and seq_len is None \
+            and _use_kernels(data) and data.dtype in (torch.float16, torch.bfloat16, torch.float32) \
+            and env.get('MXNET_B200_RNN_KERNELS'):
+        from .cuda import rnn_ops
+        if rnn_ops.supported(data, state_size, num_layers):
+            out, hy = rnn_ops.recurrent(mode, data, parameters, state, state_size, num_layers, p, training, bidirectional)
+            return (out, hy) if state_outputs else out
     layers = rnn_unpack(parameters, mode, num_layers, I, state_size, bidirectional, projection_size)
     if data.is_cuda and projection_size is None and seq_len is None and clip is None and not env.get('MXNET_RNN_UNROLLED'):
         # library recurrence (cuDNN through the tensor library) for the configurations the in-tree kernel does not
-        # take: GRU / vanilla RNN stacks.  Same gate order and per-(layer, direction) weight order.
+        # take (projection, or the kernels switched off).  Same gate order and per-(layer, direction) weight order.
         flat = []
         for w_ih, w_hh, _w_hr, b_ih, b_hh in layers:
             flat += [w_ih.contiguous(), w_hh.contiguous(), b_ih.contiguous(), b_hh.contiguous()]

@@ -265,7 +265,13 @@ def _reg_binary(name, fn, legacy_names, result_bool=False, np_name=None):
         return r.to(data.dtype) if result_bool else r
 
     def ts_np(data, scalar=0.0, is_int=None):
-        return fn(data, _maybe_float(data, scalar))
+        s = _maybe_float(data, scalar)
+        try:
+            return fn(data, s)
+        except TypeError:             # functions that take tensors only (maximum, minimum, hypot ...)
+            return fn(data, torch.as_tensor(s, device=data.device,
+                                            dtype=data.dtype if data.dtype.is_floating_point or isinstance(s, (int, bool))
+                                            else torch.float32))
 
     def rts_np(data, scalar=0.0, is_int=None):
         s = torch.as_tensor(scalar, device=data.device,

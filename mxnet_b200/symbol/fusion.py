@@ -675,11 +675,14 @@ class FusedGroup(object):
                 return None
         if FULL not in modes:
             return None
-        vec = 4
-        if n % 4 or (LAST in modes and shape[-1] % 4):
-            vec = 1
-        elif any(t.data_ptr() % (4 * t.element_size()) for t, m in zip(tensors, modes) if m != ONE):
-            vec = 1
+        moving = [t for t, m in zip(tensors, modes) if m != ONE]
+        widths = ([8] if any(t.element_size() == 2 for t in moving) or any(d.itemsize == 2 for d in out_dtypes) else []) + [4]
+        vec = 1
+        for v in widths:                          # 16-byte accesses for the narrowest type when sizes and addresses allow
+            if n % v == 0 and (LAST not in modes or shape[-1] % v == 0) and \
+                    all(t.data_ptr() % (v * t.element_size()) == 0 for t in moving):
+                vec = v
+                break
         return tuple(modes), out_dtypes, shape, vec
 
     def run_forward(self, tensors, plan):
@@ -696,7 +699,7 @@ class FusedGroup(object):
     def run_backward(self, tensors, plan, ograds, need_grad):
         modes, out_dtypes, shape, vec = plan
         dev = tensors[0].device
-        if vec == 4 and any(g.data_ptr() % (4 * g.element_size()) for g in ograds):
+        if vec > 1 and any(g.data_ptr() % (vec * g.element_size()) for g in ograds):
             vec = 1
         src = kernel_source(self, [t.dtype for t in tensors], modes, out_dtypes, vec, True, need_grad)
         fn = _get_function(src, 'fused_bwd', tensors[0].device.index or 0)

@@ -82,7 +82,7 @@ def test_generated_source_compiles_for_sm100a(backward):
     groups = [n.attrs['group'] for n in _topo(f._outputs) if n.op is not None and n.op.name == '_FusedOp']
     g = groups[0]
     assert g.nin == 3 and len(g.outputs) == 1
-    for vec in (1, 4):
+    for vec in (1, 4, 8):
         src = fusion.kernel_source(g, [torch.float16, torch.bfloat16, torch.float32], (fusion.FULL, fusion.LAST, fusion.ONE),
                                    (torch.float16,), vec, backward, [True, True, False])
         assert ('fused_bwd' if backward else 'fused_fwd') in src
@@ -189,7 +189,8 @@ def test_every_template_on_the_gpu_against_the_operators():
                     feed['y'] = yv.clone().requires_grad_(True)
                 calls = fusion.stats['kernel_calls']
                 out = mx.sym.Group([s])._run(feed)[0]
-                out.sum().backward()
+                if out.requires_grad:             # BlockGrad and friends: nothing to differentiate when run one by one
+                    out.sum().backward()
                 if fuse == '1':
                     assert fusion.stats['kernel_calls'] == calls + 2, name
                 res.append([out.detach()] + [v.grad if v.grad is not None else torch.zeros_like(v) for v in feed.values()])

@@ -592,9 +592,52 @@ def test_fused_lstm_bidirectional(T, B, I, H, layers):
     _close(flat.grad.cpu() / scale, gref / scale, 5e-3, 2e-3)
 
 
+@pytest.mark.parametrize('mode', ['gru', 'rnn_tanh', 'rnn_relu'])
+@pytest.mark.parametrize('T,B,I,H,layers,bidir', [(6, 4, 24, 40, 2, False), (5, 3, 16, 16, 1, True), (12, 33, 64, 300, 1, False)])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float16])
+def test_gru_and_vanilla_rnn_kernels(mode, T, B, I, H, layers, bidir, dtype):
+    """The GRU / vanilla RNN recurrence kernels against an exact fp32 module on the host with the same parameters."""
+    from mxnet_b200.ops.cuda import rnn_ops
+    from mxnet_b200.ops.nn import rnn_param_size
+    torch.manual_seed(13)
+    if mode == 'gru':
+        ref = torch.nn.GRU(I, H, layers, bidirectional=bidir).float()
+    else:
+        ref = torch.nn.RNN(I, H, layers, nonlinearity=mode[4:], bidirectional=bidir).float()
+    d = 2 if bidir else 1
+    sfx = ['l%d%s' % (l, r) for l in range(layers) for r in (('', '_reverse') if bidir else ('',))]
+    names = [('weight_%s_%s' % (k, s_)) for s_ in sfx for k in ('ih', 'hh')] + [('bias_%s_%s' % (k, s_)) for s_ in sfx for k in ('ih', 'hh')]
+    flat = torch.cat([getattr(ref, n).detach().reshape(-1) for n in names]).to(_dev()).to(dtype).requires_grad_(True)
+    assert flat.numel() == rnn_param_size(mode, layers, I, H, bidir)
+    with torch.no_grad():                              # the reference sees the rounded parameters
+        off = 0
+        for n in names:
+            w = getattr(ref, n)
+            w.copy_(flat[off:off + w.numel()].float().reshape(w.shape).cpu())
+            off += w.numel()
+    x = torch.randn(T, B, I, device=_dev()).to(dtype).requires_grad_(True)
+    h0 = (torch.randn(layers * d, B, H, device=_dev()) * 0.5).to(dtype).requires_grad_(True)
+    assert rnn_ops.supported(x, H, layers)
+    y, hT = rnn_ops.recurrent(mode, x, flat, h0, H, layers, 0.0, True, bidir)
+    gy, gh = torch.randn_like(y), torch.randn_like(hT)
+    torch.autograd.backward([y, hT], [gy, gh])
+    xr, hr = x.detach().float().cpu().requires_grad_(True), h0.detach().float().cpu().requires_grad_(True)
+    yr, hTr = ref(xr, hr)
+    torch.autograd.backward([yr, hTr], [gy.float().cpu(), gh.float().cpu()])
+    tol = (1e-3, 1e-3) if dtype == torch.float32 else (3e-2, 3e-2)
+    _close(y, yr, *tol)
+    _close(hT, hTr, *tol)
+    scale = max(1.0, float(xr.grad.abs().max()))
+    _close(x.grad / scale, xr.grad / scale, tol[0] * 3, tol[1] * 3)
+    _close(h0.grad / scale, hr.grad / scale, tol[0] * 3, tol[1] * 3)
+    gref = torch.cat([getattr(ref, n).grad.reshape(-1) for n in names])
+    scale = float(gref.abs().max())
+    _close(flat.grad.cpu() / scale, gref / scale, tol[0] * 5, tol[1] * 2)
+
+
 @pytest.mark.parametrize('mode,bidir', [('gru', False), ('lstm', True), ('rnn_tanh', True), ('rnn_relu', False)])
 def test_rnn_operator_gpu_matches_cpu_unrolled(mode, bidir):
-    """The RNN operator on the GPU (library recurrence) against the per-step CPU implementation of the same operator."""
+    """The RNN operator on the GPU (recurrence kernels) against the per-step CPU implementation of the same operator."""
     from mxnet_b200.ops.nn import rnn_param_size
     T, B, I, H, layers = 6, 3, 5, 7, 2
     d = 2 if bidir else 1
