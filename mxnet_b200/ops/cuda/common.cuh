@@ -43,6 +43,19 @@ __device__ __forceinline__ void st16(T* p, const Vec16<T>& r) {
   *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&r);
 }
 
+// erf by the rational approximation 7.1.26 of Abramowitz & Stegun (one reciprocal, one exponential, five multiply-adds):
+// absolute error below 7e-7 in fp32, which keeps GELU within 5e-7 of the exact value; about half the instructions
+// of erff, which is what bounds the GELU kernels at 16-bit storage.
+__device__ __forceinline__ float erf_fast(float x) {
+  const float ax = fabsf(x);
+  const float t = __fdividef(1.f, fmaf(0.3275911f, ax, 1.f));
+  float p = fmaf(1.061405429f, t, -1.453152027f);
+  p = fmaf(p, t, 1.421413741f);
+  p = fmaf(p, t, -0.284496736f);
+  p = fmaf(p, t, 0.254829592f);
+  return copysignf(1.f - p * t * __expf(-ax * ax), x);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

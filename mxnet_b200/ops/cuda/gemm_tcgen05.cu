@@ -46,7 +46,7 @@ template <int BN> struct TileCfg {
 
 enum Act { kActNone = 0, kActRelu = 1, kActGelu = 2 };
 
-__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erf_fast(x * 0.70710678118654752f)); }
 
 template <typename T, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)

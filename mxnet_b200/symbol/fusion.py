@@ -75,8 +75,8 @@ _UNARY = {
     'mish': ('({x} * tanhf(fmaxf({x}, 0.f) + log1pf(__expf(-fabsf({x})))))',
              '({g} * mxb_mish_grad({x}))'),
     'softrelu': ('(fmaxf({x}, 0.f) + log1pf(__expf(-fabsf({x}))))', '({g} / (1.f + __expf(-{x})))'),
-    'gelu': ('(0.5f * {x} * (1.f + erff({x} * 0.707106781f)))',
-             '({g} * (0.5f * (1.f + erff({x} * 0.707106781f)) + {x} * 0.398942280f * __expf(-0.5f * {x} * {x})))'),
+    'gelu': ('(0.5f * {x} * (1.f + mxb_erf_fast({x} * 0.707106781f)))',
+             '({g} * (0.5f * (1.f + mxb_erf_fast({x} * 0.707106781f)) + {x} * 0.398942280f * __expf(-0.5f * {x} * {x})))'),
     'floor': ('floorf({x})', None), 'ceil': ('ceilf({x})', None), 'trunc': ('truncf({x})', None),
     'rint': ('rintf({x})', None), 'fix': ('truncf({x})', None),
     'degrees': ('({x} * 57.2957795f)', '({g} * 57.2957795f)'),
@@ -86,6 +86,16 @@ _UNARY = {
 }
 
 _PRELUDE_FUNCS = '''
+// Abramowitz & Stegun 7.1.26: absolute error below 7e-7 in fp32, about half the instructions of erff
+__device__ __forceinline__ float mxb_erf_fast(float x) {
+  const float ax = fabsf(x);
+  const float t = __fdividef(1.f, fmaf(0.3275911f, ax, 1.f));
+  float p = fmaf(1.061405429f, t, -1.453152027f);
+  p = fmaf(p, t, 1.421413741f);
+  p = fmaf(p, t, -0.284496736f);
+  p = fmaf(p, t, 0.254829592f);
+  return copysignf(1.f - p * t * __expf(-ax * ax), x);
+}
 __device__ __forceinline__ float mxb_mish_grad(float x) {
   const float sp = fmaxf(x, 0.f) + log1pf(__expf(-fabsf(x)));
   const float t = tanhf(sp);

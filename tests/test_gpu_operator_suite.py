@@ -1,0 +1,75 @@
+"""The CPU operator, array, autograd, loss and optimizer tests once more with the GPU as the default device: every
+array the tests create without an explicit device lands on ``gpu(0)``, so the same assertions check the GPU code paths
+(the scheme of ``tests/python/gpu/test_operator_gpu.py`` in the reference, which re-imports the CPU suite after
+``set_default_device(mx.gpu(0))``)."""
+import importlib
+import inspect
+import itertools
+import os
+import sys
+
+import pytest
+
+import mxnet_b200 as mx
+
+pytestmark = pytest.mark.gpu
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+MODULES = ['test_ndarray', 'test_numpy_frontend', 'test_autograd', 'test_loss_metric', 'test_optimizer', 'test_probability',
+           'test_contrib_misc', 'test_contrib_detection']
+
+# tests that are about the host itself (files, pinned host memory, CPU shared memory, numpy interop of host buffers)
+HOST_ONLY = {
+}
+
+
+def _expand(fn):
+    """(id suffix, kwargs) for every combination of the test's parametrize marks; fixture-taking tests are left out."""
+    marks = [m for m in getattr(fn, 'pytestmark', []) if m.name == 'parametrize']
+    if any(m.name in ('gpu', 'skip') for m in getattr(fn, 'pytestmark', [])):
+        return
+    axes = []
+    for m in marks:
+        names = m.args[0]
+        names = [n.strip() for n in names.split(',')] if isinstance(names, str) else list(names)
+        values = []
+        for v in m.args[1]:
+            v = v.values if hasattr(v, 'values') else v
+            values.append(dict(zip(names, v if len(names) > 1 else [v if not isinstance(v, tuple) or len(names) != 1 else v])))
+        axes.append(values)
+    params = set(inspect.signature(fn).parameters)
+    covered = set()
+    for ax in axes:
+        covered |= set(ax[0]) if ax else set()
+    if params - covered:
+        return                                   # needs a fixture
+    if not axes:
+        yield '', {}
+        return
+    for i, combo in enumerate(itertools.product(*axes)):
+        kw = {}
+        for c in combo:
+            kw.update(c)
+        yield '[%d]' % i, kw
+
+
+def _cases():
+    out = []
+    for m in MODULES:
+        mod = importlib.import_module(m)
+        for name, fn in sorted(vars(mod).items()):
+            if not name.startswith('test_') or not inspect.isfunction(fn) or fn.__module__ != mod.__name__:
+                continue
+            if (m, name) in HOST_ONLY or name in HOST_ONLY.get(m, ()):
+                continue
+            for suffix, kw in _expand(fn):
+                out.append(pytest.param(fn, kw, id='%s::%s%s' % (m, name, suffix)))
+    return out
+
+
+@pytest.mark.parametrize('fn,kwargs', _cases())
+def test_cpu_suite_with_gpu_default_device(fn, kwargs):
+    with mx.gpu(0):
+        fn(**kwargs)
+    mx.nd.waitall()
