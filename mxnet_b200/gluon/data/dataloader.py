@@ -50,9 +50,15 @@ _worker_dataset = None
 
 
 def _worker_initializer(dataset):
+    """Runs once in every forked worker.  Workers build their batches on the host whatever default device the parent
+    had when it forked (the reference's workers always batchify into CPU shared memory,
+    ``python/mxnet/gluon/data/dataloader.py``); a forked process cannot use the parent's CUDA context anyway."""
     global _worker_dataset
     _worker_dataset = dataset
     torch.set_num_threads(1)
+    from ...device import Device
+    Device._default.stack = []
+    Device._process_default = Device('cpu', 0)
 
 
 def _worker_fn(samples, batchify_fn, dataset=None):

@@ -17,10 +17,12 @@ pytestmark = pytest.mark.gpu
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 MODULES = ['test_ndarray', 'test_numpy_frontend', 'test_autograd', 'test_loss_metric', 'test_optimizer', 'test_probability',
-           'test_contrib_misc', 'test_contrib_detection']
+           'test_contrib_misc', 'test_contrib_detection', 'test_gluon', 'test_symbol', 'test_rnn_estimator', 'test_amp',
+           'test_misc_api']
 
 # tests that are about the host itself (files, pinned host memory, CPU shared memory, numpy interop of host buffers)
 HOST_ONLY = {
+    'test_ndarray': ('test_copy_and_context', 'test_creation_and_basic_properties'),   # assert cpu(0) as the default device
 }
 
 
@@ -61,7 +63,7 @@ def _cases():
         for name, fn in sorted(vars(mod).items()):
             if not name.startswith('test_') or not inspect.isfunction(fn) or fn.__module__ != mod.__name__:
                 continue
-            if (m, name) in HOST_ONLY or name in HOST_ONLY.get(m, ()):
+            if name in HOST_ONLY.get(m, ()):
                 continue
             for suffix, kw in _expand(fn):
                 out.append(pytest.param(fn, kw, id='%s::%s%s' % (m, name, suffix)))
