@@ -57,6 +57,11 @@ def run(name, unit, items_per_step_per_gpu, make_step, args, config, baseline=No
             cfg['gemm_in_tree_kernel_chosen'] = {p: '%d of %d' % (sum(1 for k, v in tuned.items() if k[0] == p and v),
                                                                   sum(1 for k in tuned if k[0] == p))
                                                  for p in ('fwd', 'dgrad', 'wgrad')}
+        from mxnet_b200.ops.cuda import rnn_ops
+        if rnn_ops.tuned_choices():
+            cfg['rnn_in_tree_kernel_chosen'] = {'%s T=%d N=%d I=%d H=%d L=%d %s' % (k[0], k[2], k[3], k[4], k[5], k[6],
+                                                                                   'train' if k[8] else 'eval'): bool(v)
+                                                for k, v in rnn_ops.tuned_choices().items()}
         print(json.dumps({'metric': name, 'value': value, 'unit': unit, 'n_gpus': world, 'steps': args.steps,
                           'warmup': max(args.warmup, 3), 'ms_per_step': ms / args.steps, 'higher_is_better': True,
                           'scaling': 'weak', 'vs_baseline': (value / baseline) if baseline else None, 'data': 'synthetic',

@@ -161,7 +161,32 @@ def case_add(ctx, dtype, small):
     return dict(inputs=[a, b], fn=lambda a, b: a + b, fwd_bytes=3 * n * _esize(dtype), bwd_bytes=0, no_backward=True)
 
 
+def case_rnn(ctx, dtype, small, mode='lstm', bidirectional=False):
+    """The RNN operator on the shape of the LSTM language model: 2 layers of 650 units, 35 steps, batch 80."""
+    from mxnet_b200.ops.nn import rnn_param_size
+    T, B, I, H, layers = (35, 80, 650, 650, 2) if not small else (12, 32, 128, 128, 2)
+    d = 2 if bidirectional else 1
+    rng = np.random.RandomState(0)
+    x = _rand((T, B, I), ctx, dtype)
+    params = nd.array(rng.uniform(-0.05, 0.05, (rnn_param_size(mode, layers, I, H, bidirectional),)), ctx=ctx, dtype=dtype)
+    h0 = nd.zeros((layers * d, B, H), ctx=ctx, dtype=dtype)
+    states = [h0] + ([nd.zeros((layers * d, B, H), ctx=ctx, dtype=dtype)] if mode == 'lstm' else [])
+    gates = {'lstm': 4, 'gru': 3}.get(mode, 1)
+    fl = 2.0 * T * B * gates * H * (I + H) * layers * d          # layer 0 input size equals H here
+    if bidirectional:
+        fl += 2.0 * T * B * gates * H * H * d                    # second layer reads 2H features
+
+    def fn(x, params):
+        with mx.autograd.train_mode():
+            return nd.RNN(x, params, *states, state_size=H, num_layers=layers, mode=mode, bidirectional=bidirectional)
+    return dict(inputs=[x, params], fn=fn, fwd_flops=fl, bwd_flops=2 * fl)
+
+
 CASES = {
+    'RNN_lstm': case_rnn,
+    'RNN_gru': lambda c, d, s: case_rnn(c, d, s, mode='gru'),
+    'RNN_tanh': lambda c, d, s: case_rnn(c, d, s, mode='rnn_tanh'),
+    'RNN_lstm_bidirectional': lambda c, d, s: case_rnn(c, d, s, bidirectional=True),
     'BatchNorm': case_batchnorm,
     'BatchNormReLU': lambda c, d, s: case_batchnorm(c, d, s, relu=True),
     'BatchNormAddReLU': lambda c, d, s: case_batchnorm(c, d, s, relu=True, residual=True),

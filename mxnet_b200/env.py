@@ -126,7 +126,7 @@ declare('MXNET_B200_ELEMENTWISE', bool, True, 'GELU, dropout, embedding, add_n, 
 declare('MXNET_B200_GEMM_AUTOTUNE', bool, True, 'time the tcgen05 GEMM against the library GEMM per shape and product (forward, data gradient, weight gradient) on first use and keep the faster')
 declare('MXNET_B200_GEMM', bool, True, 'route half-precision FullyConnected/dot to the tcgen05 GEMM kernel (0 = library GEMM)')
 # ---- graph --------------------------------------------------------------------------------
-declare('MXNET_B200_RNN_KERNELS', bool, True, 'GRU / vanilla RNN through the in-tree recurrence kernels (off: library recurrence)')
+declare('MXNET_B200_RNN', str, 'auto', 'RNN operator on the in-tree recurrence kernels: auto = time forward + backward against the library recurrence per configuration, 1 = force, 0 = library')
 declare('MXNET_USE_FUSION', bool, True, 'pointwise fusion')
 declare('MXNET_ELIMINATE_COMMON_EXPR', bool, True, 'common-subexpression elimination on symbols')
 declare('MXNET_MEMORY_OPT', bool, False, 'recompute cheap activations in backward')

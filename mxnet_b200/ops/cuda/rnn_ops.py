@@ -15,6 +15,51 @@ def supported(data, state_size, num_layers):
     return bool(lib().mxb_lstm_supported(int(data.shape[1]), int(state_size)))
 
 
+_tuned = {}
+
+
+def use_own(key, own_fn, lib_fn, inputs, training):
+    """Whether the RNN configuration `key` runs on the in-tree recurrence kernels (``MXNET_B200_RNN``).  In auto mode
+    both implementations run the forward pass (plus the backward pass when training) on the caller's tensors once,
+    timed on the device, and the faster one is remembered for the configuration."""
+    from ... import env
+    mode = str(env.get('MXNET_B200_RNN')).lower()
+    if mode in ('1', 'true', 'on', 'force'):
+        return True
+    if mode in ('0', 'false', 'off'):
+        return False
+    hit = _tuned.get(key)
+    if hit is None:
+        if torch.cuda.is_current_stream_capturing():
+            return True                    # cannot time inside a capture; the eager warm-up run normally comes first
+        from .conv_ops import _time_us
+
+        def run(fn):
+            def step():
+                if not training:
+                    with torch.no_grad():
+                        fn(*inputs)
+                    return
+                leaves = [t.detach().requires_grad_(True) if t.is_floating_point() else t for t in inputs]
+                with torch.enable_grad():
+                    out = fn(*leaves)
+                    outs = [o for o in (out if isinstance(out, (tuple, list)) else (out,)) if o.requires_grad]
+                    torch.autograd.grad([o.float().sum() for o in outs], [l for l in leaves if l.requires_grad],
+                                        allow_unused=True)
+            return step
+        rng = torch.cuda.get_rng_state()
+        try:
+            hit = _tuned[key] = _time_us(run(own_fn), reps=3) <= 1.02 * _time_us(run(lib_fn), reps=3)
+        finally:
+            torch.cuda.set_rng_state(rng)
+    return hit
+
+
+def tuned_choices():
+    """{(mode, dtype, T, N, input size, state size, layers, bidirectional, training): in-tree kernels chosen}."""
+    return dict(_tuned)
+
+
 def _mm(a, b, a_mn, b_mn):
     """op(a) @ op(b) with the tcgen05 kernel when the operands qualify, else the library."""
     from . import gemm_ops

@@ -864,34 +864,37 @@ def rnn(data, parameters, state, state_cell=None, sequence_length=None, state_si
     seq_len = sequence_length if use_sequence_length else None
     clip = (lstm_state_clip_min, lstm_state_clip_max) if lstm_state_clip_min is not None else None
     training = _state.state.training
-    if mode == 'lstm' and projection_size is None and seq_len is None and clip is None \
-            and _use_kernels(data) and data.dtype in (torch.float16, torch.bfloat16, torch.float32):
-        from .cuda import rnn_ops
-        if rnn_ops.supported(data, state_size, num_layers):
-            out, hy, cy = rnn_ops.lstm(data, parameters, state, state_cell, state_size, num_layers, p, training,
-                                       bidirectional)
-            return (out, hy, cy) if state_outputs else out
-    if mode in ('gru', 'rnn_tanh', 'rnn_relu') and projection_size is None and seq_len is None \
-            and _use_kernels(data) and data.dtype in (torch.float16, torch.bfloat16, torch.float32) \
-            and env.get('MXNET_B200_RNN_KERNELS'):
-        from .cuda import rnn_ops
-        if rnn_ops.supported(data, state_size, num_layers):
-            out, hy = rnn_ops.recurrent(mode, data, parameters, state, state_size, num_layers, p, training, bidirectional)
-            return (out, hy) if state_outputs else out
     layers = rnn_unpack(parameters, mode, num_layers, I, state_size, bidirectional, projection_size)
-    if data.is_cuda and projection_size is None and seq_len is None and clip is None and not env.get('MXNET_RNN_UNROLLED'):
-        # library recurrence (cuDNN through the tensor library) for the configurations the in-tree kernel does not
-        # take (projection, or the kernels switched off).  Same gate order and per-(layer, direction) weight order.
+    plain = projection_size is None and seq_len is None and clip is None
+
+    def library(data, parameters, state, state_cell=None):
+        """Library recurrence (cuDNN through the tensor library): same gate order and per-(layer, direction) weights."""
         flat = []
-        for w_ih, w_hh, _w_hr, b_ih, b_hh in layers:
+        for w_ih, w_hh, _w_hr, b_ih, b_hh in rnn_unpack(parameters, mode, num_layers, I, state_size, bidirectional, None):
             flat += [w_ih.contiguous(), w_hh.contiguous(), b_ih.contiguous(), b_hh.contiguous()]
         args = (flat, True, num_layers, float(p), bool(training), bool(bidirectional), False)
         if mode == 'lstm':
-            out, hn, cn = torch._VF.lstm(data, (state.contiguous(), state_cell.contiguous()), *args)
-            return (out, hn, cn) if state_outputs else out
+            return torch._VF.lstm(data, (state.contiguous(), state_cell.contiguous()), *args)
         fn = {'gru': torch._VF.gru, 'rnn_tanh': torch._VF.rnn_tanh, 'rnn_relu': torch._VF.rnn_relu}[mode]
-        out, hn = fn(data, state.contiguous(), *args)
-        return (out, hn) if state_outputs else out
+        return fn(data, state.contiguous(), *args)
+
+    if plain and _use_kernels(data) and data.dtype in (torch.float16, torch.bfloat16, torch.float32):
+        from .cuda import rnn_ops
+        if rnn_ops.supported(data, state_size, num_layers):
+            if mode == 'lstm':
+                def own(data, parameters, state, state_cell):
+                    return rnn_ops.lstm(data, parameters, state, state_cell, state_size, num_layers, p, training, bidirectional)
+                inputs = (data, parameters, state, state_cell)
+            else:
+                def own(data, parameters, state):
+                    return rnn_ops.recurrent(mode, data, parameters, state, state_size, num_layers, p, training, bidirectional)
+                inputs = (data, parameters, state)
+            key = (mode, str(data.dtype), T, N, I, state_size, num_layers, bool(bidirectional), bool(training))
+            res = (own if rnn_ops.use_own(key, own, library, inputs, training) else library)(*inputs)
+            return tuple(res) if state_outputs else res[0]
+    if data.is_cuda and plain and not env.get('MXNET_RNN_UNROLLED'):
+        res = library(data, parameters, state, state_cell) if mode == 'lstm' else library(data, parameters, state)
+        return tuple(res) if state_outputs else res[0]
     x = data
     hy, cy = [], []
     for l in range(num_layers):

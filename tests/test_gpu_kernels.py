@@ -637,7 +637,8 @@ def test_gru_and_vanilla_rnn_kernels(mode, T, B, I, H, layers, bidir, dtype):
 
 @pytest.mark.parametrize('mode,bidir', [('gru', False), ('lstm', True), ('rnn_tanh', True), ('rnn_relu', False)])
 def test_rnn_operator_gpu_matches_cpu_unrolled(mode, bidir):
-    """The RNN operator on the GPU (recurrence kernels) against the per-step CPU implementation of the same operator."""
+    """The RNN operator on the GPU (recurrence kernels, library recurrence, and the timed choice between them) against
+    the per-step CPU implementation of the same operator."""
     from mxnet_b200.ops.nn import rnn_param_size
     T, B, I, H, layers = 6, 3, 5, 7, 2
     d = 2 if bidir else 1
@@ -647,19 +648,25 @@ def test_rnn_operator_gpu_matches_cpu_unrolled(mode, bidir):
     h0 = rng.randn(layers * d, B, H).astype('float32')
     c0 = rng.randn(layers * d, B, H).astype('float32')
     outs = []
-    for ctx in (mx.cpu(), mx.gpu(0)):
-        args = [nd.array(x, ctx=ctx), nd.array(params, ctx=ctx), nd.array(h0, ctx=ctx)]
-        if mode == 'lstm':
-            args.append(nd.array(c0, ctx=ctx))
-        args[0].attach_grad()
-        args[1].attach_grad()
-        with autograd.record():
-            res = nd.RNN(*args, state_size=H, num_layers=layers, mode=mode, bidirectional=bidir, state_outputs=True)
-            loss = sum((r * r).sum() for r in res)
-        loss.backward()
-        outs.append([r.asnumpy() for r in res] + [args[0].grad.asnumpy(), args[1].grad.asnumpy()])
-    for a, b in zip(*outs):
-        np.testing.assert_allclose(a, b, rtol=1e-2, atol=1e-2)      # the library recurrence may use TF32
+    from mxnet_b200 import env
+    from mxnet_b200.ops.cuda import rnn_ops
+    for ctx, flag in ((mx.cpu(), 'auto'), (mx.gpu(0), '1'), (mx.gpu(0), '0'), (mx.gpu(0), 'auto')):
+        with env.scope('MXNET_B200_RNN', flag):
+            args = [nd.array(x, ctx=ctx), nd.array(params, ctx=ctx), nd.array(h0, ctx=ctx)]
+            if mode == 'lstm':
+                args.append(nd.array(c0, ctx=ctx))
+            args[0].attach_grad()
+            args[1].attach_grad()
+            with autograd.record():
+                res = nd.RNN(*args, state_size=H, num_layers=layers, mode=mode, bidirectional=bidir, state_outputs=True)
+                loss = sum((r * r).sum() for r in res)
+            loss.backward()
+            outs.append([r.asnumpy() for r in res] + [args[0].grad.asnumpy(), args[1].grad.asnumpy()])
+    key = (mode, 'torch.float32', T, B, I, H, layers, bidir, True)
+    assert key in rnn_ops.tuned_choices()                           # the auto run timed both implementations
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            np.testing.assert_allclose(a, b, rtol=1e-2, atol=1e-2)      # the library recurrence may use TF32
 
 
 # ---------------------------------------------------------------------------------------- pooling
