@@ -375,17 +375,24 @@ def box_nms(data, overlap_thresh=0.5, valid_thresh=0.0, topk=-1, coord_start=2, 
         if topk > 0:
             order = order[:topk]
         boxes = d[order, coord_start:coord_start + 4]
-        iou = _iou_matrix(boxes, boxes, in_format)
-        keep = torch.ones(order.numel(), dtype=torch.bool, device=d.device)
         ids = d[order, id_index] if id_index >= 0 else None
-        for i in range(order.numel()):
-            if not keep[i]:
-                continue
-            sup = iou[i] > overlap_thresh
-            if ids is not None and not force_suppress:
-                sup = sup & (ids == ids[i])
-            sup[:i + 1] = False
-            keep = keep & ~sup
+        det = _ew_kernels(d)
+        if det is not None:
+            from .cuda import detection_ops
+            corners = boxes if in_format == 'corner' else torch.cat([boxes[:, :2] - boxes[:, 2:] / 2,
+                                                                     boxes[:, :2] + boxes[:, 2:] / 2], 1)
+            keep = detection_ops.nms_keep(corners, overlap_thresh, None if force_suppress else ids)
+        else:
+            iou = _iou_matrix(boxes, boxes, in_format)
+            keep = torch.ones(order.numel(), dtype=torch.bool, device=d.device)
+            for i in range(order.numel()):
+                if not keep[i]:
+                    continue
+                sup = iou[i] > overlap_thresh
+                if ids is not None and not force_suppress:
+                    sup = sup & (ids == ids[i])
+                sup[:i + 1] = False
+                keep = keep & ~sup
         kept = d[order[keep]]
         if in_format != out_format:
             c = kept[:, coord_start:coord_start + 4]
@@ -426,25 +433,55 @@ def bipartite_matching(data, is_ascend=False, threshold=0.0, topk=-1):
 @register('_contrib_ROIAlign', 'ROIAlign', inputs=('data', 'rois'),
           defaults={'pooled_size': (1, 1), 'spatial_scale': 1.0, 'sample_ratio': -1, 'position_sensitive': False, 'aligned': False})
 def roi_align(data, rois, pooled_size=(1, 1), spatial_scale=1.0, sample_ratio=-1, position_sensitive=False, aligned=False):
+    """Average of bilinear samples per output bin (``src/operator/contrib/roi_align.cc``): sampling points more than one
+    pixel outside the map count as zero, points in the one-pixel border are clamped onto the edge."""
     ph, pw = pooled_size
-    N, C, H, W = data.shape
+    N, CI, H, W = data.shape
+    C = CI // (ph * pw) if position_sensitive else CI
+    if _ew_kernels(data) is not None:
+        from .cuda import detection_ops
+        if detection_ops.roi_align_supported(data, rois):
+            return detection_ops.roi_align(data, rois, (ph, pw), spatial_scale, sample_ratio, position_sensitive, aligned)
     outs = []
     off = 0.5 if aligned else 0.0
-    for r in rois:
+    rois_host = rois.detach().float().cpu()
+    dev = data.device
+    for r in rois_host:
         b = int(r[0].item())
-        x1, y1, x2, y2 = [(v.item() * spatial_scale - off) for v in r[1:5]]
+        if b < 0:
+            outs.append(data.new_zeros(C, ph, pw))
+            continue
+        x1, y1, x2, y2 = [(float(v) * spatial_scale - off) for v in r[1:5]]
         rw, rh = x2 - x1, y2 - y1
         if not aligned:
             rw, rh = max(rw, 1.0), max(rh, 1.0)
         sh = sample_ratio if sample_ratio > 0 else max(int(math.ceil(rh / ph)), 1)
         sw = sample_ratio if sample_ratio > 0 else max(int(math.ceil(rw / pw)), 1)
-        ys = y1 + (torch.arange(ph * sh, device=data.device, dtype=torch.float32) + 0.5) * (rh / (ph * sh))
-        xs = x1 + (torch.arange(pw * sw, device=data.device, dtype=torch.float32) + 0.5) * (rw / (pw * sw))
-        gy = (ys / max(H - 1, 1)) * 2 - 1
-        gx = (xs / max(W - 1, 1)) * 2 - 1
-        grid = torch.stack(torch.meshgrid(gy, gx, indexing='ij')[::-1], -1)[None]
-        samp = F.grid_sample(data[b:b + 1].float(), grid, mode='bilinear', padding_mode='border', align_corners=True)
-        outs.append(samp.reshape(C, ph, sh, pw, sw).mean((2, 4)).to(data.dtype))
+        ys = y1 + (torch.arange(ph * sh, device=dev, dtype=torch.float32) + 0.5) * (rh / (ph * sh))
+        xs = x1 + (torch.arange(pw * sw, device=dev, dtype=torch.float32) + 0.5) * (rw / (pw * sw))
+
+        def axis(v, n):
+            inside = (v >= -1.0) & (v <= n)
+            v = v.clamp(min=0)
+            lo = v.floor().long()
+            top = lo >= n - 1
+            lo = torch.where(top, torch.full_like(lo, n - 1), lo)
+            hi = torch.where(top, lo, lo + 1)
+            frac = torch.where(top, torch.zeros_like(v), v - lo)
+            return lo, hi, frac, inside
+        y0, y1i, ly, iny = axis(ys, H)
+        x0, x1i, lx, inx = axis(xs, W)
+        plane = data[b].float()                                          # (CI, H, W)
+        top_rows, bot_rows = plane[:, y0], plane[:, y1i]                 # (CI, Sy, W)
+        val = ((1 - ly)[None, :, None] * ((1 - lx) * top_rows[:, :, x0] + lx * top_rows[:, :, x1i]) +
+               ly[None, :, None] * ((1 - lx) * bot_rows[:, :, x0] + lx * bot_rows[:, :, x1i]))
+        val = val * (iny[:, None] & inx[None, :]).to(val.dtype)
+        pooled = val.reshape(CI, ph, sh, pw, sw).mean((2, 4))
+        if position_sensitive:
+            pooled = pooled.reshape(C, ph, pw, ph, pw)
+            ii, jj = torch.arange(ph, device=dev), torch.arange(pw, device=dev)
+            pooled = pooled[:, ii[:, None], jj[None, :], ii[:, None], jj[None, :]]
+        outs.append(pooled.to(data.dtype))
     return torch.stack(outs, 0) if outs else data.new_zeros(0, C, ph, pw)
 
 
@@ -704,6 +741,10 @@ def _rpn_anchors(feature_stride, ratios, scales, device):
 def _greedy_nms(boxes, thresh, max_keep):
     """Greedy suppression in score order with the +1 pixel area convention (proposal.cc:204-256)."""
     n = boxes.shape[0]
+    if _ew_kernels(boxes) is not None and n > 0:
+        from .cuda import detection_ops
+        keep = detection_ops.nms_keep(boxes, thresh, None, max_keep, plus_one=True)
+        return torch.nonzero(keep).reshape(-1).tolist()
     area = (boxes[:, 2] - boxes[:, 0] + 1) * (boxes[:, 3] - boxes[:, 1] + 1)
     xx1 = torch.maximum(boxes[:, None, 0], boxes[None, :, 0])
     yy1 = torch.maximum(boxes[:, None, 1], boxes[None, :, 1])

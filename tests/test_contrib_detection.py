@@ -1,5 +1,6 @@
 """Region-proposal, position-sensitive pooling, deformable convolution and mask-target operators (CPU)."""
 import numpy as np
+import pytest
 
 import mxnet_b200 as mx
 from mxnet_b200 import autograd, nd
@@ -118,3 +119,111 @@ def test_mrcnn_mask_target_shapes_and_class_weights():
     np.testing.assert_allclose(t[0, 1], 1.0, atol=1e-5)
     np.testing.assert_allclose(t[0, 2], 1.0, atol=1e-5)
     np.testing.assert_array_equal(w[0, :, :, 0, 0], [[0, 0, 1], [1, 0, 0], [0, 1, 0]])
+
+
+# ---------------------------------------------------------------------------------------- ROIAlign, box_nms
+def _roi_align_scalar(data, rois, pooled, scale, sample_ratio, position_sensitive, aligned):
+    """Loop restatement of the operator's rules (roi_align.cc): samples more than one pixel outside the map are zero,
+    samples in the border are clamped to the edge, bins average sample_ratio^2 (or ceil(roi/bin)^2) samples."""
+    N, CI, H, W = data.shape
+    ph, pw = pooled
+    C = CI // (ph * pw) if position_sensitive else CI
+    out = np.zeros((len(rois), C, ph, pw), dtype=np.float64)
+
+    def sample(plane, y, x):
+        if y < -1.0 or y > H or x < -1.0 or x > W:
+            return 0.0
+        y, x = max(y, 0.0), max(x, 0.0)
+        y0, x0 = int(y), int(x)
+        if y0 >= H - 1:
+            y1 = y0 = H - 1
+            y = float(y0)
+        else:
+            y1 = y0 + 1
+        if x0 >= W - 1:
+            x1 = x0 = W - 1
+            x = float(x0)
+        else:
+            x1 = x0 + 1
+        ly, lx = y - y0, x - x0
+        return ((1 - ly) * (1 - lx) * plane[y0, x0] + (1 - ly) * lx * plane[y0, x1] + ly * (1 - lx) * plane[y1, x0] +
+                ly * lx * plane[y1, x1])
+    off = 0.5 if aligned else 0.0
+    for r, roi in enumerate(rois):
+        b = int(roi[0])
+        if b < 0:
+            continue
+        x1, y1, x2, y2 = [v * scale - off for v in roi[1:]]
+        rw, rh = x2 - x1, y2 - y1
+        if not aligned:
+            rw, rh = max(rw, 1.0), max(rh, 1.0)
+        gh = sample_ratio if sample_ratio > 0 else max(int(np.ceil(rh / ph)), 1)
+        gw = sample_ratio if sample_ratio > 0 else max(int(np.ceil(rw / pw)), 1)
+        for c in range(C):
+            for i in range(ph):
+                for j in range(pw):
+                    ci = (c * ph + i) * pw + j if position_sensitive else c
+                    acc = 0.0
+                    for iy in range(gh):
+                        for ix in range(gw):
+                            acc += sample(data[b, ci], y1 + i * rh / ph + (iy + 0.5) * rh / ph / gh,
+                                          x1 + j * rw / pw + (ix + 0.5) * rw / pw / gw)
+                    out[r, c, i, j] = acc / (gh * gw)
+    return out
+
+
+_ROI_CASES = [dict(pooled=(2, 2), scale=1.0, sample_ratio=2, position_sensitive=False, aligned=False),
+              dict(pooled=(3, 2), scale=0.5, sample_ratio=-1, position_sensitive=False, aligned=True),
+              dict(pooled=(2, 2), scale=1.0, sample_ratio=2, position_sensitive=True, aligned=False)]
+_ROIS = np.array([[0, 1.0, 1.5, 6.0, 7.0], [1, -3.0, -2.0, 4.0, 5.0], [0, 5.0, 5.0, 12.0, 11.0], [-1, 0, 0, 4, 4],
+                  [1, 2.2, 3.1, 2.4, 3.3]], dtype='float32')
+
+
+@pytest.mark.parametrize('case', _ROI_CASES)
+def test_roi_align_follows_the_boundary_rules(case):
+    rng = np.random.RandomState(0)
+    data = rng.randn(2, 8, 9, 10).astype('float32')
+    out = mx.nd.contrib.ROIAlign(mx.nd.array(data), mx.nd.array(_ROIS), pooled_size=case['pooled'], spatial_scale=case['scale'],
+                                 sample_ratio=case['sample_ratio'], position_sensitive=case['position_sensitive'],
+                                 aligned=case['aligned'])
+    ref = _roi_align_scalar(data, _ROIS, **case)
+    assert out.shape == ref.shape
+    np.testing.assert_allclose(out.asnumpy(), ref, rtol=1e-4, atol=1e-5)
+
+
+def _nms_input(rng, n, classes=3):
+    xy = rng.uniform(0, 50, (n, 2))
+    wh = rng.uniform(5, 25, (n, 2))
+    return np.concatenate([rng.randint(0, classes, (n, 1)).astype('float64'), rng.uniform(0, 1, (n, 1)), xy, xy + wh],
+                          1).astype('float32')
+
+
+def _nms_scalar(rows, thresh, valid, topk, force):
+    order = [i for i in np.argsort(-rows[:, 1], kind='stable') if rows[i, 1] > valid]
+    if topk > 0:
+        order = order[:topk]
+    kept = []
+    for i in order:
+        ok = True
+        for k in kept:
+            if not force and rows[k, 0] != rows[i, 0]:
+                continue
+            a, b = rows[k, 2:6], rows[i, 2:6]
+            w, h = max(min(a[2], b[2]) - max(a[0], b[0]), 0), max(min(a[3], b[3]) - max(a[1], b[1]), 0)
+            inter = w * h
+            if inter / ((a[2] - a[0]) * (a[3] - a[1]) + (b[2] - b[0]) * (b[3] - b[1]) - inter) > thresh:
+                ok = False
+                break
+        if ok:
+            kept.append(i)
+    out = np.full_like(rows, -1.0)
+    out[:len(kept)] = rows[kept]
+    return out
+
+
+@pytest.mark.parametrize('force,topk', [(False, -1), (True, -1), (False, 20)])
+def test_box_nms_keeps_the_greedy_selection(force, topk):
+    rows = _nms_input(np.random.RandomState(2), 60)
+    out = mx.nd.contrib.box_nms(mx.nd.array(rows[None]), overlap_thresh=0.4, valid_thresh=0.1, topk=topk, coord_start=2,
+                                score_index=1, id_index=0, force_suppress=force)
+    np.testing.assert_allclose(out.asnumpy()[0], _nms_scalar(rows, 0.4, 0.1, topk, force), rtol=1e-6)

@@ -233,3 +233,41 @@ def test_column_sums(rows, C, dtype):
     ref = x.double().sum(0)
     np.testing.assert_allclose(out.cpu().numpy(), ref.cpu().numpy(), rtol=1e-4, atol=1e-3 * rows ** 0.5)
     assert torch.equal(out, ew.colsum(x))              # deterministic
+
+
+# ---------------------------------------------------------------------------------------- detection kernels
+@pytest.mark.parametrize('dtype', ['float32', 'float16'])
+@pytest.mark.parametrize('position_sensitive,aligned,sample_ratio', [(False, False, 2), (False, True, -1), (True, False, 2)])
+def test_roi_align_kernels_against_the_host_operator(dtype, position_sensitive, aligned, sample_ratio):
+    import mxnet_b200 as mx
+    from mxnet_b200 import autograd, nd
+    rng = np.random.RandomState(5)
+    data = rng.randn(2, 8, 9, 10).astype('float32')
+    rois = np.array([[0, 1.0, 1.5, 6.0, 7.0], [1, -3.0, -2.0, 4.0, 5.0], [0, 5.0, 5.0, 12.0, 11.0], [-1, 0, 0, 4, 4],
+                     [1, 2.25, 3.0, 2.5, 3.25]], dtype='float32')
+    res = []
+    for ctx in (mx.cpu(), mx.gpu(0)):
+        x = nd.array(data, ctx=ctx, dtype=dtype if ctx.device_type == 'gpu' else 'float32')
+        r = nd.array(rois, ctx=ctx, dtype=x.dtype)
+        x.attach_grad()
+        with autograd.record():
+            y = nd.contrib.ROIAlign(x, r, pooled_size=(2, 2), spatial_scale=1.0, sample_ratio=sample_ratio,
+                                    position_sensitive=position_sensitive, aligned=aligned)
+            loss = (y * y).sum()
+        loss.backward()
+        res.append((y.asnumpy().astype('float32'), x.grad.asnumpy().astype('float32')))
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == 'float32' else dict(rtol=2e-2, atol=2e-2)
+    np.testing.assert_allclose(res[1][0], res[0][0], **tol)
+    np.testing.assert_allclose(res[1][1], res[0][1], **tol)
+
+
+@pytest.mark.parametrize('n,force', [(60, False), (300, True), (1000, False)])
+def test_nms_kernels_against_the_host_operator(n, force):
+    import mxnet_b200 as mx
+    from mxnet_b200 import nd
+    rng = np.random.RandomState(n)
+    xy, wh = rng.uniform(0, 120, (2, n, 2)), rng.uniform(5, 40, (2, n, 2))
+    rows = np.concatenate([rng.randint(0, 3, (2, n, 1)).astype('float64'), rng.uniform(0, 1, (2, n, 1)), xy, xy + wh], 2).astype('float32')
+    outs = [nd.contrib.box_nms(nd.array(rows, ctx=ctx), overlap_thresh=0.45, valid_thresh=0.05, topk=400, coord_start=2, score_index=1,
+                               id_index=0, force_suppress=force).asnumpy() for ctx in (mx.cpu(), mx.gpu(0))]
+    np.testing.assert_allclose(outs[1], outs[0], rtol=1e-6)

@@ -12,6 +12,8 @@ import pytest
 
 import mxnet_b200 as mx
 
+_PARAM_SET = type(pytest.param(0))
+
 pytestmark = pytest.mark.gpu
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -37,8 +39,9 @@ def _expand(fn):
         names = [n.strip() for n in names.split(',')] if isinstance(names, str) else list(names)
         values = []
         for v in m.args[1]:
-            v = v.values if hasattr(v, 'values') else v
-            values.append(dict(zip(names, v if len(names) > 1 else [v if not isinstance(v, tuple) or len(names) != 1 else v])))
+            if isinstance(v, _PARAM_SET):            # pytest.param(...)
+                v = v.values if len(names) > 1 else v.values[0]
+            values.append(dict(zip(names, v if len(names) > 1 else [v])))
         axes.append(values)
     params = set(inspect.signature(fn).parameters)
     covered = set()
