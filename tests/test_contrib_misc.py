@@ -47,7 +47,10 @@ def test_onnx_export_writes_a_loadable_graph(tmp_path):
     x = rng.randn(2, 5).astype('float32')
     ref = net._bind(mx.cpu(), dict(params, data=nd.array(x))).forward()[0].asnumpy()
     np.testing.assert_allclose(mx.onnx.run_model(out, {'data': x})[0], ref, rtol=1e-5, atol=1e-6)
-    onnx = pytest.importorskip('onnx')                 # with the package at hand: its checker accepts the file too
+    try:                                               # with the package at hand: its checker accepts the file too
+        import onnx
+    except ImportError:
+        return
     onnx.checker.check_model(onnx.load(out))
 
 
