@@ -49,3 +49,65 @@ def matrix_power(a, n):
 def cond(x, p=None):
     s = svd(x)[1]
     return s.max(axis=-1) / s.min(axis=-1)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# array-API additions of python/mxnet/numpy/linalg.py
+# ---------------------------------------------------------------------------------------------------------
+def _mx_np():
+    from . import multiarray
+    return multiarray
+
+
+def cross(a, b, axis=-1): return _mx_np().cross(a, b, axis=axis)
+def diagonal(a, offset=0): return _mx_np().diagonal(a, offset=offset, axis1=-2, axis2=-1)
+def outer(a, b): return _mx_np().outer(a, b)
+def tensordot(a, b, axes=2): return _mx_np().tensordot(a, b, axes)
+def trace(a, offset=0): return _mx_np().trace(a, offset=offset, axis1=-2, axis2=-1)
+def matrix_transpose(a): return _mx_np().swapaxes(a, -1, -2)
+
+
+def vecdot(a, b, axis=-1):
+    """Sum of products over ``axis`` with broadcasting of the other axes."""
+    return _mx_np().sum(a * b, axis=axis)
+
+
+def svdvals(a):
+    """Singular values in descending order."""
+    return svd(a)[1]
+
+
+def vector_norm(x, axis=None, keepdims=False, ord=2):  # pylint: disable=redefined-builtin
+    np_ = _mx_np()
+    if axis is None:
+        x, axis = x.reshape(-1), 0
+    if isinstance(axis, (tuple, list)) and len(axis) > 1:      # flatten the reduced axes into one
+        rest = [d for d in range(x.ndim) if d not in [ax % x.ndim for ax in axis]]
+        lead = np_.transpose(x, rest + [ax % x.ndim for ax in axis])
+        shape = tuple(x.shape[d] for d in rest)
+        out = vector_norm(lead.reshape(shape + (-1,)), axis=-1, keepdims=False, ord=ord)
+        if keepdims:
+            full = [1 if d in [ax % x.ndim for ax in axis] else x.shape[d] for d in range(x.ndim)]
+            out = out.reshape(tuple(full))
+        return out
+    if isinstance(axis, (tuple, list)):
+        axis = axis[0]
+    if ord == float('inf'):
+        return np_.max(np_.abs(x), axis=axis, keepdims=keepdims)
+    if ord == -float('inf'):
+        return np_.min(np_.abs(x), axis=axis, keepdims=keepdims)
+    if ord == 0:
+        return np_.sum((x != 0).astype(x.dtype), axis=axis, keepdims=keepdims)
+    if ord == 1:
+        return np_.sum(np_.abs(x), axis=axis, keepdims=keepdims)
+    if ord == 2:
+        return np_.sqrt(np_.sum(x * x, axis=axis, keepdims=keepdims))
+    return np_.power(np_.sum(np_.power(np_.abs(x), ord), axis=axis, keepdims=keepdims), 1.0 / ord)
+
+
+def matrix_norm(x, keepdims=False, ord='fro'):  # pylint: disable=redefined-builtin
+    return norm(x, ord=ord, axis=(-2, -1), keepdims=keepdims)
+
+
+__all__ += ['cross', 'diagonal', 'outer', 'tensordot', 'trace', 'matrix_transpose', 'vecdot', 'svdvals', 'vector_norm',
+            'matrix_norm']

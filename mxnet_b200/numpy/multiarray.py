@@ -589,3 +589,31 @@ for _n in ['intersect1d', 'union1d', 'setdiff1d', 'setxor1d', 'in1d', 'isin', 'd
            'isrealobj', 'min_scalar_type', 'promote_types', 'common_type', 'tensorinv', 'squeeze_']:
     if hasattr(_np, _n) and _n not in globals():
         globals()[_n] = _host_fallback(_n)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# names of the array API standard (python/mxnet/numpy/multiarray.py: pow, atan2, asin ..., concat, permute_dims,
+# bitwise_invert, bitwise_left_shift / bitwise_right_shift, from_dlpack)
+# ---------------------------------------------------------------------------------------------------------
+pow = power                      # pylint: disable=redefined-builtin
+atan2 = arctan2
+asin, acos, atan, asinh, acosh, atanh = arcsin, arccos, arctan, arcsinh, arccosh, arctanh
+bitwise_invert = invert
+bitwise_left_shift, bitwise_right_shift = left_shift, right_shift
+
+
+def concat(arrays, axis=0, out=None):
+    """``concatenate`` under its array-API name; ``axis=None`` joins the flattened inputs."""
+    if axis is None:
+        return concatenate([a.reshape(-1) for a in arrays], axis=0, out=out)
+    return concatenate(arrays, axis=axis, out=out)
+
+
+def permute_dims(a, axes=None):
+    return transpose(a, axes)
+
+
+def from_dlpack(x):
+    """An ndarray sharing memory with any object that implements ``__dlpack__`` (or a DLPack capsule)."""
+    import torch
+    return ndarray._from_tensor(torch.utils.dlpack.from_dlpack(x))

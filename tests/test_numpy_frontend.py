@@ -152,3 +152,40 @@ def test_random_module():
     assert sorted(p.tolist()) == list(range(10))
     g = np.random.gamma(2.0, 1.0, size=(5000,)).asnumpy()
     assert abs(g.mean() - 2) < 0.15
+
+
+def test_array_api_names_and_linalg_additions():
+    """pow / atan2 / asin ... / concat / permute_dims / bitwise_* / from_dlpack and the array-API part of np.linalg."""
+    import torch
+    np_ = mx.np
+    a = np_.array([[1., 2., 3.], [4., 5., 6.]])
+    b = np_.array([[1., 0., 2.], [0., 3., 1.]])
+    an, bn = a.asnumpy(), b.asnumpy()
+    onp.testing.assert_allclose(np_.pow(a, 2).asnumpy(), an ** 2)
+    onp.testing.assert_allclose(np_.atan2(a, b).asnumpy(), onp.arctan2(an, bn), rtol=1e-6)
+    for new, old in (('asin', 'arcsin'), ('acos', 'arccos'), ('atan', 'arctan'), ('asinh', 'arcsinh'), ('atanh', 'arctanh')):
+        v = np_.array([0.1, 0.5])
+        onp.testing.assert_allclose(getattr(np_, new)(v).asnumpy(), getattr(onp, old)(v.asnumpy()), rtol=1e-6)
+    onp.testing.assert_allclose(np_.acosh(a).asnumpy(), onp.arccosh(an), rtol=1e-6)
+    assert np_.concat([a, b], axis=None).shape == (12,) and np_.concat([a, b], axis=1).shape == (2, 6)
+    assert np_.permute_dims(a, (1, 0)).shape == (3, 2)
+    i = np_.array([1, 2], dtype='int32')
+    onp.testing.assert_array_equal(np_.bitwise_invert(i).asnumpy(), [-2, -3])
+    onp.testing.assert_array_equal(np_.bitwise_left_shift(i, i).asnumpy(), [2, 8])
+    onp.testing.assert_array_equal(np_.bitwise_right_shift(np_.array([8, 8], dtype='int32'), i).asnumpy(), [4, 2])
+    t = torch.arange(4.)
+    shared = np_.from_dlpack(t)
+    t[0] = 9
+    onp.testing.assert_array_equal(shared.asnumpy(), [9, 1, 2, 3])           # same memory
+    L = np_.linalg
+    onp.testing.assert_allclose(L.vecdot(a, b).asnumpy(), (an * bn).sum(-1))
+    onp.testing.assert_allclose(L.vector_norm(a).asnumpy(), onp.linalg.norm(an.ravel()), rtol=1e-6)
+    onp.testing.assert_allclose(L.vector_norm(a, axis=1, ord=1).asnumpy(), onp.abs(an).sum(1))
+    assert L.vector_norm(a, axis=(0, 1), keepdims=True).shape == (1, 1)
+    onp.testing.assert_allclose(L.matrix_norm(a).asnumpy(), onp.linalg.norm(an), rtol=1e-6)
+    onp.testing.assert_allclose(L.svdvals(a).asnumpy(), onp.linalg.svd(an)[1], rtol=1e-5)
+    onp.testing.assert_allclose(L.cross(a, b).asnumpy(), onp.cross(an, bn))
+    onp.testing.assert_allclose(L.tensordot(a, np_.transpose(b), 1).asnumpy(), an @ bn.T)
+    assert L.matrix_transpose(a).shape == (3, 2) and L.outer(a[0], b[0]).shape == (3, 3)
+    onp.testing.assert_allclose(L.diagonal(a).asnumpy(), [1, 5])
+    onp.testing.assert_allclose(L.trace(np_.array([[1., 2.], [3., 4.]])).asnumpy(), 5)
