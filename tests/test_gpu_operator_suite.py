@@ -75,6 +75,9 @@ def _cases():
 
 @pytest.mark.parametrize('fn,kwargs', _cases())
 def test_cpu_suite_with_gpu_default_device(fn, kwargs):
-    with mx.gpu(0):
+    from mxnet_b200 import env
+    # recurrent layers on the in-tree kernels: exact fp32 arithmetic, where the library recurrence may use TF32 and then
+    # misses the 1e-4 tolerances that the host tests put on fp32 results
+    with env.scope('MXNET_B200_RNN', '1'), mx.gpu(0):
         fn(**kwargs)
     mx.nd.waitall()
