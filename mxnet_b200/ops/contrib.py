@@ -485,6 +485,49 @@ def roi_align(data, rois, pooled_size=(1, 1), spatial_scale=1.0, sample_ratio=-1
     return torch.stack(outs, 0) if outs else data.new_zeros(0, C, ph, pw)
 
 
+def _bilinear_points(plane, y, x):
+    """Bilinear samples of plane (C, H, W) at points (y, x) with the ROIAlign boundary rules: points more than one pixel
+    outside the map give zero, points in the border are clamped onto the edge."""
+    C, H, W = plane.shape
+    inside = (y >= -1.0) & (y <= H) & (x >= -1.0) & (x <= W)
+    y, x = y.clamp(min=0), x.clamp(min=0)
+    y0, x0 = y.floor().long(), x.floor().long()
+    ty, tx = y0 >= H - 1, x0 >= W - 1
+    y0 = torch.where(ty, torch.full_like(y0, H - 1), y0)
+    x0 = torch.where(tx, torch.full_like(x0, W - 1), x0)
+    y1, x1 = torch.where(ty, y0, y0 + 1), torch.where(tx, x0, x0 + 1)
+    ly, lx = torch.where(ty, torch.zeros_like(y), y - y0), torch.where(tx, torch.zeros_like(x), x - x0)
+    flat = plane.reshape(C, H * W)
+    val = ((1 - ly) * (1 - lx) * flat[:, y0 * W + x0] + (1 - ly) * lx * flat[:, y0 * W + x1] +
+           ly * (1 - lx) * flat[:, y1 * W + x0] + ly * lx * flat[:, y1 * W + x1])
+    return val * inside.to(val.dtype)
+
+
+@register('_contrib_RROIAlign', 'RROIAlign', inputs=('data', 'rois'), defaults={'pooled_size': (1, 1), 'spatial_scale': 1.0, 'sampling_ratio': -1})
+def rroi_align(data, rois, pooled_size=(1, 1), spatial_scale=1.0, sampling_ratio=-1):
+    """ROIAlign over rotated boxes (batch index, centre x, centre y, width, height, angle in degrees): the sampling grid
+    of every bin is rotated around the box centre (``src/operator/contrib/rroi_align.cc``)."""
+    ph, pw = pooled_size
+    N, C, H, W = data.shape
+    dev = data.device
+    outs = []
+    for r in rois.detach().float().cpu():
+        b = int(r[0].item())
+        cx, cy = float(r[1]) * spatial_scale, float(r[2]) * spatial_scale
+        rw, rh = max(float(r[3]) * spatial_scale, 1.0), max(float(r[4]) * spatial_scale, 1.0)
+        theta = float(r[5]) * math.pi / 180.0
+        gh = sampling_ratio if sampling_ratio > 0 else max(int(math.ceil(rh / ph)), 1)
+        gw = sampling_ratio if sampling_ratio > 0 else max(int(math.ceil(rw / pw)), 1)
+        yy = -rh / 2 + (torch.arange(ph * gh, device=dev, dtype=torch.float32) + 0.5) * (rh / (ph * gh))
+        xx = -rw / 2 + (torch.arange(pw * gw, device=dev, dtype=torch.float32) + 0.5) * (rw / (pw * gw))
+        yy, xx = torch.meshgrid(yy, xx, indexing='ij')
+        x = xx * math.cos(theta) + yy * math.sin(theta) + cx
+        y = yy * math.cos(theta) - xx * math.sin(theta) + cy
+        val = _bilinear_points(data[b].float(), y.reshape(-1), x.reshape(-1))
+        outs.append(val.reshape(C, ph, gh, pw, gw).mean((2, 4)).to(data.dtype))
+    return torch.stack(outs, 0) if outs else data.new_zeros(0, C, ph, pw)
+
+
 @register('_contrib_MultiBoxPrior', 'MultiBoxPrior', inputs=('data',),
           defaults={'sizes': (1.0,), 'ratios': (1.0,), 'clip': False, 'steps': (-1.0, -1.0), 'offsets': (0.5, 0.5)})
 def multibox_prior(data, sizes=(1.0,), ratios=(1.0,), clip=False, steps=(-1.0, -1.0), offsets=(0.5, 0.5)):

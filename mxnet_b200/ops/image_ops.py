@@ -155,3 +155,54 @@ def cv_copy_make_border(data, top=0, bot=0, left=0, right=0, type=0, value=0.0, 
     x = data.permute(2, 0, 1)[None].float()
     y = F.pad(x, (left, right, top, bot), 'constant', value)
     return y[0].permute(1, 2, 0).to(data.dtype)
+
+
+# ---- random crops and the file / buffer decoders as operators (image/crop.cc, io/image_io.cc) -----------------------
+@register('_image_random_crop', '_npx__image_random_crop', inputs=('data',), nout=1,
+          defaults={'xrange': (0.0, 1.0), 'yrange': (0.0, 1.0), 'width': 1, 'height': 1, 'interp': 1})
+def random_crop(data, xrange=(0.0, 1.0), yrange=(0.0, 1.0), width=1, height=1, interp=1):   # pylint: disable=redefined-builtin
+    """Crop of ``width`` x ``height`` whose left / top edge is drawn uniformly from the given fractions of the free
+    range; images smaller than the crop are resized up to it.  Layout (H, W, C) or (N, H, W, C)."""
+    import random as _pyrandom
+    h, w = data.shape[-3], data.shape[-2]
+    if h < height or w < width:
+        return resize(data, size=(width, height), interp=interp)
+    x0 = int(round((xrange[0] + (xrange[1] - xrange[0]) * _pyrandom.random()) * (w - width)))
+    y0 = int(round((yrange[0] + (yrange[1] - yrange[0]) * _pyrandom.random()) * (h - height)))
+    return crop(data, x=x0, y=y0, width=width, height=height)
+
+
+@register('_image_random_resized_crop', '_npx__image_random_resized_crop', inputs=('data',),
+          defaults={'width': 1, 'height': 1, 'area': (0.08, 1.0), 'ratio': (3.0 / 4.0, 4.0 / 3.0), 'interp': 1, 'max_trial': 10})
+def random_resized_crop(data, width=1, height=1, area=(0.08, 1.0), ratio=(3.0 / 4.0, 4.0 / 3.0), interp=1, max_trial=10):
+    """A crop of random area (fraction of the image) and aspect ratio, resized to ``width`` x ``height``; after
+    ``max_trial`` failed draws the centre crop of the target aspect ratio is used."""
+    import math
+    import random as _pyrandom
+    h, w = data.shape[-3], data.shape[-2]
+    area = (area, 1.0) if isinstance(area, (int, float)) else tuple(area)
+    for _ in range(int(max_trial)):
+        target = _pyrandom.uniform(*area) * h * w
+        log_ratio = (math.log(ratio[0]), math.log(ratio[1]))
+        aspect = math.exp(_pyrandom.uniform(*log_ratio))
+        cw, ch = int(round(math.sqrt(target * aspect))), int(round(math.sqrt(target / aspect)))
+        if 0 < cw <= w and 0 < ch <= h:
+            x0, y0 = _pyrandom.randint(0, w - cw), _pyrandom.randint(0, h - ch)
+            return resize(crop(data, x=x0, y=y0, width=cw, height=ch), size=(width, height), interp=interp)
+    scale = min(w / width, h / height)
+    cw, ch = int(width * scale), int(height * scale)
+    return resize(crop(data, x=(w - cw) // 2, y=(h - ch) // 2, width=cw, height=ch), size=(width, height), interp=interp)
+
+
+@register('_cvimdecode', inputs=('buf',), defaults={'flag': 1, 'to_rgb': True})
+def cvimdecode(buf, flag=1, to_rgb=True):
+    """Encoded image bytes (a uint8 vector) -> (H, W, C) uint8 image."""
+    from ..image.image import _decode_to_numpy
+    return torch.from_numpy(_decode_to_numpy(buf.detach().cpu().numpy().tobytes(), flag, to_rgb).copy())
+
+
+@register('_cvimread', inputs=(), defaults={'filename': '', 'flag': 1, 'to_rgb': True})
+def cvimread(filename='', flag=1, to_rgb=True):
+    from ..image.image import _decode_to_numpy
+    with open(filename, 'rb') as f:
+        return torch.from_numpy(_decode_to_numpy(f.read(), flag, to_rgb).copy())

@@ -227,3 +227,21 @@ def test_box_nms_keeps_the_greedy_selection(force, topk):
     out = mx.nd.contrib.box_nms(mx.nd.array(rows[None]), overlap_thresh=0.4, valid_thresh=0.1, topk=topk, coord_start=2,
                                 score_index=1, id_index=0, force_suppress=force)
     np.testing.assert_allclose(out.asnumpy()[0], _nms_scalar(rows, 0.4, 0.1, topk, force), rtol=1e-6)
+
+
+def test_rotated_roi_align_reduces_to_roi_align_at_zero_angle_and_rotates_by_ninety_degrees():
+    rng = np.random.RandomState(4)
+    data = rng.randn(1, 3, 12, 12).astype('float32')
+    # an axis-aligned box given by corners and the same box given by centre / size / angle 0
+    corner = np.array([[0, 2.0, 3.0, 8.0, 9.0]], dtype='float32')
+    rotated = np.array([[0, 5.0, 6.0, 6.0, 6.0, 0.0]], dtype='float32')
+    a = mx.nd.contrib.ROIAlign(mx.nd.array(data), mx.nd.array(corner), pooled_size=(3, 3), spatial_scale=1.0, sample_ratio=2).asnumpy()
+    b = mx.nd.contrib.RROIAlign(mx.nd.array(data), mx.nd.array(rotated), pooled_size=(3, 3), spatial_scale=1.0, sampling_ratio=2).asnumpy()
+    np.testing.assert_allclose(b, a, rtol=1e-5, atol=1e-6)
+    # a quarter turn of the sampling grid equals sampling the map turned the other way
+    turned = np.array([[0, 5.5, 5.5, 6.0, 6.0, 90.0]], dtype='float32')
+    straight = np.array([[0, 5.5, 5.5, 6.0, 6.0, 0.0]], dtype='float32')
+    c = mx.nd.contrib.RROIAlign(mx.nd.array(data), mx.nd.array(turned), pooled_size=(2, 2), sampling_ratio=2).asnumpy()
+    d = mx.nd.contrib.RROIAlign(mx.nd.array(np.rot90(data, k=-1, axes=(2, 3)).copy()), mx.nd.array(straight), pooled_size=(2, 2),
+                                sampling_ratio=2).asnumpy()
+    np.testing.assert_allclose(c, d, rtol=1e-4, atol=1e-5)

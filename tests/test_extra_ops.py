@@ -159,3 +159,23 @@ def test_quantized_additions():
     np.testing.assert_allclose(out.reshape(4, 6).astype('float32') * hi[0] / 127, ref, atol=0.1)
     t, lo2, hi2 = _run('_npx_quantized_transpose', qa, la, ha, axes=(1, 0))
     np.testing.assert_array_equal(t, qa.T)
+
+
+def test_random_crop_and_decoder_operators(tmp_path):
+    import io
+    from PIL import Image
+    img = nd.array(np.random.RandomState(0).randint(0, 255, (20, 30, 3)), dtype='uint8')
+    assert nd.image.random_crop(img, width=10, height=8).shape == (8, 10, 3)
+    assert nd.image.random_crop(img, width=40, height=25).shape == (25, 40, 3)          # smaller images are resized up
+    assert nd.image.random_resized_crop(img, width=12, height=12).shape == (12, 12, 3)
+    corner = nd.image.random_crop(img, xrange=(0.0, 0.0), yrange=(1.0, 1.0), width=10, height=8).asnumpy()
+    np.testing.assert_array_equal(corner, img.asnumpy()[12:, :10])
+    b = io.BytesIO()
+    Image.fromarray(img.asnumpy()).save(b, format='PNG')
+    buf = nd.array(np.frombuffer(b.getvalue(), dtype='uint8'), dtype='uint8')
+    np.testing.assert_array_equal(nd._internal._cvimdecode(buf).asnumpy(), img.asnumpy())
+    path = tmp_path / 't.png'
+    path.write_bytes(b.getvalue())
+    np.testing.assert_array_equal(nd._internal._cvimread(filename=str(path)).asnumpy(), img.asnumpy())
+    gray = nd._internal._cvimread(filename=str(path), flag=0)
+    assert gray.shape == (20, 30, 1)
