@@ -38,5 +38,9 @@ def _populate():
 
 
 _populate()
+
+from . import control_flow   # noqa: E402
+for _n in control_flow.__all__:
+    setattr(contrib, _n, getattr(control_flow, _n))   # noqa: F821  (contrib is set by _populate)
 from . import numpy as np          # noqa: E402,F401
 from . import numpy_extension as npx   # noqa: E402,F401

@@ -337,7 +337,11 @@ class Symbol(object):
         for i, n in enumerate(nodes):
             entry = {'op': 'null' if n.op is None else n.op.name, 'name': n.name}
             attrs = {k: _fmt_attr(v) for k, v in n.attrs.items()
-                     if not (n.op is not None and k in n.op.defaults and n.op.defaults[k] == v and v is None)}
+                     if not (n.op is not None and k in n.op.defaults and n.op.defaults[k] == v and v is None)
+                     and not isinstance(v, Symbol)}
+            subgraphs = [v for k, v in sorted(n.attrs.items()) if isinstance(v, Symbol)]      # control-flow bodies
+            if subgraphs:
+                entry['subgraphs'] = [json.loads(g.tojson(remove_amp_cast)) for g in subgraphs]
             attrs.update(n.user_attrs)
             if attrs:
                 entry['attrs'] = attrs
@@ -836,6 +840,8 @@ def load_json(json_str):
             else:
                 attrs[k] = _parse_attr(v)
         inputs = [(nodes[i[0]], i[1]) for i in jn['inputs']]
+        for k, sg in enumerate(jn.get('subgraphs', ())):
+            attrs['__subgraph__%d' % k] = load_json(json.dumps(sg))
         node = _Node(op, jn['name'], attrs, inputs, 1, user)
         node.nout = op.num_outputs(attrs) or 1
         # files written before auxiliary states became explicit inputs

@@ -170,3 +170,54 @@ def test_symbol_numpy_namespace_and_optimize_for():
     assert_almost_equal(out, np.maximum([-1., 1.], 0) + 1 / (1 + np.exp(-np.array([-1., 1.]))), rtol=1e-6)
     z = y.optimize_for('default')
     assert z.list_arguments() == ['x']
+
+
+def test_symbolic_control_flow_foreach_while_cond(tmp_path):
+    """mx.sym.contrib.foreach / while_loop / cond: evaluation, shape inference, gradients and the JSON round trip."""
+    import numpy as onp
+    rng = onp.random.RandomState(0)
+    data, init, w = mx.sym.var('data'), mx.sym.var('init'), mx.sym.var('w')
+
+    def step(x, state):
+        new = mx.sym.tanh(mx.sym.dot(x, w) + state)
+        return new * 2.0, new
+    outs, final = mx.sym.contrib.foreach(step, data, init)
+    g = mx.sym.Group([outs, final])
+    assert g.list_arguments() == ['data', 'init', 'w']
+    xv, hv, wv = rng.randn(5, 3, 4).astype('float32'), rng.randn(3, 4).astype('float32'), rng.randn(4, 4).astype('float32') * 0.5
+    ref, h = [], hv
+    for t in range(5):
+        h = onp.tanh(xv[t] @ wv + h)
+        ref.append(2 * h)
+    _, out_shapes, _ = g.infer_shape(data=(5, 3, 4), init=(3, 4), w=(4, 4))
+    assert out_shapes == [(5, 3, 4), (3, 4)]
+    for sym in (g, mx.sym.load_json(g.tojson())):                       # as built, and after a trip through JSON
+        args = {'data': nd.array(xv), 'init': nd.array(hv), 'w': nd.array(wv)}
+        grads = {k: nd.zeros(v.shape) for k, v in args.items()}
+        ex = sym._bind(mx.cpu(), args, args_grad=grads)
+        res = ex.forward(is_train=True)
+        onp.testing.assert_allclose(res[0].asnumpy(), onp.stack(ref), rtol=1e-5, atol=1e-6)
+        onp.testing.assert_allclose(res[1].asnumpy(), h, rtol=1e-5, atol=1e-6)
+        ex.backward([nd.ones((5, 3, 4)), nd.zeros((3, 4))])
+        assert float(grads['w'].abs().sum().asscalar()) > 0 and float(grads['data'].abs().sum().asscalar()) > 0
+    saved = str(tmp_path / 'loop-symbol.json')
+    g.save(saved)
+    import json
+    node = [n for n in json.load(open(saved))['nodes'] if n['op'] == '_foreach'][0]
+    assert len(node['subgraphs']) == 1 and any(m['op'] == 'tanh' for m in node['subgraphs'][0]['nodes'])
+
+    # while_loop: s += i for i < 4, outputs padded to max_iterations
+    i0, s0 = mx.sym.var('i'), mx.sym.var('s')
+    outs, (i_f, s_f) = mx.sym.contrib.while_loop(lambda i, s: i < 4, lambda i, s: (s + i, [i + 1, s + i]), [i0, s0], max_iterations=6)
+    wl = mx.sym.load_json(mx.sym.Group([outs, i_f, s_f]).tojson())
+    r = wl._bind(mx.cpu(), {'i': nd.array([0.0]), 's': nd.array([10.0])}).forward()
+    onp.testing.assert_allclose(r[0].asnumpy().ravel(), [10, 11, 13, 16, 0, 0])
+    assert float(r[1].asscalar()) == 4 and float(r[2].asscalar()) == 16
+
+    # cond with outer variables captured by the branches
+    p, a, b = mx.sym.var('p'), mx.sym.var('a'), mx.sym.var('b')
+    c = mx.sym.contrib.cond(p, lambda: a * 2.0, lambda: b - 1.0)
+    c = mx.sym.load_json(c.tojson())
+    for pv, expect in ((1.0, [2.0, 4.0]), (0.0, [4.0, 5.0])):
+        got = c._bind(mx.cpu(), {'p': nd.array([pv]), 'a': nd.array([1.0, 2.0]), 'b': nd.array([5.0, 6.0])}).forward()[0]
+        onp.testing.assert_allclose(got.asnumpy(), expect)
