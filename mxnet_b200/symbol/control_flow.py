@@ -191,3 +191,5 @@ def _cond_op(pred, *free, num_outs=1, free_names=(), **subgraphs):
 _reg.register('_foreach', inputs=('*data',), nout=lambda a: int(a.get('num_outs', 1)) + int(a.get('num_states', 0)))(_foreach_op)
 _reg.register('_while_loop', inputs=('*data',), nout=lambda a: int(a.get('num_outs', 0)) + int(a.get('num_vars', 1)))(_while_loop_op)
 _reg.register('_cond', inputs=('pred', '*data'), nout=lambda a: int(a.get('num_outs', 1)))(_cond_op)
+for _old, _new in (('_foreach', '_npx_foreach'), ('_while_loop', '_npx_while_loop'), ('_cond', '_npx_cond')):
+    _reg.alias(_old, _new)
