@@ -1,2 +1,3 @@
-"""``gluon.contrib``."""
-from . import estimator
+"""``gluon.contrib``: the estimator API and contributed data loaders / transforms."""
+from . import estimator   # noqa: F401
+from . import data        # noqa: F401

@@ -4,9 +4,9 @@ import random
 
 import numpy as np
 
-from ......ndarray.ndarray import NDArray
-from ..... import block as _block
-from ...... import image as _image
+from mxnet_b200.ndarray.ndarray import NDArray
+from mxnet_b200.gluon import block as _block
+from mxnet_b200 import image as _image
 from .utils import bbox_crop, bbox_flip, bbox_random_crop_with_constraints, bbox_resize, bbox_translate
 
 __all__ = ['ImageBboxRandomFlipLeftRight', 'ImageBboxCrop', 'ImageBboxRandomCropWithConstraints', 'ImageBboxRandomExpand',
@@ -21,7 +21,7 @@ def _like(arr, ref, dtype=None):
     """A framework array of the class of ``ref`` (legacy or NumPy-semantics) holding ``arr``."""
     if not isinstance(ref, NDArray):
         return arr
-    from ...... import nd
+    from mxnet_b200 import nd
     out = nd.array(arr, dtype=dtype or arr.dtype)
     return out.as_np_ndarray() if type(ref).__name__ == 'ndarray' else out
 
@@ -110,7 +110,7 @@ class ImageBboxResize(_block.Block):
 
     def forward(self, img, bbox):
         im = _np(img)
-        from ...... import nd
+        from mxnet_b200 import nd
         interp = self._interp if self._interp != 10 else random.randint(0, 4)
         resized = _image.imresize(nd.array(im, dtype=im.dtype), self._size[0], self._size[1], interp=interp).asnumpy()
         return _like(resized, img), _like(bbox_resize(_np(bbox), (im.shape[-2], im.shape[-3]), self._size), bbox)
