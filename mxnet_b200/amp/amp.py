@@ -204,3 +204,20 @@ def list_conditional_fp32_ops(target_dtype='float16'): return list(_lists(target
 def list_widest_type_cast(target_dtype='float16'): return list(_lists(target_dtype).WIDEST_TYPE_CASTS)
 def list_loss_output_functions(target_dtype='float16'): return list(_lists(target_dtype).LOSS_OUTPUT_FUNCTIONS)
 def list_lp16_use_fp32_params(target_dtype='float16'): return ['BatchNorm', 'LayerNorm', 'GroupNorm', 'InstanceNorm']
+
+
+def warn_if_model_exists():
+    """Warn when ``amp.init()`` is called after a Block was already built: layers created earlier keep the operator
+    functions they captured and are not patched."""
+    import gc
+    import warnings
+    from ..gluon.block import Block
+    for obj in gc.get_objects():
+        try:
+            if isinstance(obj, Block):
+                warnings.warn('Block {} created in [{}] was not patched by AMP: create the network after amp.init()'.format(
+                    type(obj).__name__, type(obj).__module__))
+                return True
+        except ReferenceError:
+            continue
+    return False

@@ -139,3 +139,14 @@ def quantize_net(network, quantized_dtype='auto', quantize_mode='full', quantize
     inputs, sym = network._cached_graph
     qsym = quantize_graph(sym, exclude_layers or (), exclude_operators or (), 'int8')
     return SymbolBlock(qsym, inputs, dict(network.collect_params().items()))
+
+
+def quantize_model_onednn(sym, arg_params, aux_params, data_names=('data',), device=None, excluded_sym_names=None,
+                          excluded_op_names=None, calib_mode='entropy', calib_data=None, num_calib_batches=None,
+                          quantized_dtype='int8', quantize_mode='smart', quantize_granularity='tensor-wise', logger=None):
+    """The reference quantises and then fuses for its oneDNN CPU back end; there is no such back end here, so this is
+    :func:`quantize_model` (the int8 operators run through the tensor library on the given device)."""
+    return quantize_model(sym, arg_params, aux_params, data_names=data_names, device=device,
+                          excluded_sym_names=excluded_sym_names, excluded_op_names=excluded_op_names, calib_mode=calib_mode,
+                          calib_data=calib_data, num_calib_batches=num_calib_batches, quantized_dtype=quantized_dtype,
+                          quantize_mode=quantize_mode, quantize_granularity=quantize_granularity, logger=logger)

@@ -626,3 +626,23 @@ def np(numpy_feval, name=None, allow_extra_outputs=False):
         return numpy_feval(label, pred)
     feval.__name__ = numpy_feval.__name__
     return CustomMetric(feval, name, allow_extra_outputs)
+
+
+def predict_with_threshold(pred, threshold=0.5):
+    """Binary decisions of probabilities: ``pred > threshold`` with one threshold or one per class (last axis)."""
+    import numpy as _onp
+    if isinstance(threshold, float):
+        return pred > threshold
+    if hasattr(threshold, 'asnumpy'):
+        threshold = threshold.asnumpy()
+    threshold = _onp.asarray(threshold)
+    num_classes = pred.shape[-1]
+    assert threshold.shape[-1] == num_classes, 'shape mismatch: %s vs. %s' % (pred.shape[-1], threshold.shape[-1])
+    return pred > threshold
+
+
+def one_hot(idx, num):
+    """(len(idx), num) int32 indicator matrix."""
+    import numpy as _onp
+    idx = _onp.asarray(idx)
+    return (_onp.arange(num).astype(idx.dtype) == idx[:, None]).astype('int32')

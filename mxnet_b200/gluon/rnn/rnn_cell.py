@@ -517,3 +517,24 @@ class VariationalDropoutCell(ModifierCell):
                 self.drop_outputs_mask = self._mask(self.drop_outputs, next_output)
             next_output = next_output * self.drop_outputs_mask
         return next_output, next_states
+
+
+def dynamic_unroll(cell, inputs, begin_state, drop_inputs=0, drop_outputs=0, layout='TNC', valid_length=None):
+    """Unroll ``cell`` over the time axis of ``inputs`` (one merged array in ``layout``), with optional dropout shared
+    across time on the inputs / outputs.  With ``valid_length`` (batch,) the outputs beyond each sequence's length are
+    zero and the returned states are those of its last valid step."""
+    from ... import numpy_extension as npx, ndarray as nd
+    axis = layout.find('T')
+    legacy = type(inputs).__name__ != 'ndarray'
+
+    def dropout(x, p):
+        if legacy:
+            return nd.Dropout(x, p=p, axes=(axis,))
+        return npx.dropout(x, p=p, axes=(axis,))
+    if drop_inputs:
+        inputs = dropout(inputs, drop_inputs)
+    outputs, states = cell.unroll(inputs.shape[axis], inputs, begin_state, layout=layout, merge_outputs=True,
+                                  valid_length=valid_length)
+    if drop_outputs:
+        outputs = dropout(outputs, drop_outputs)
+    return outputs, states

@@ -145,3 +145,28 @@ def split_rnn_params(param, mode, num_layers, input_size, hidden_size, bidirecti
         out[pre + 'i2h_bias'] = cls._from_tensor(b_ih, param._ctx)
         out[pre + 'h2h_bias'] = cls._from_tensor(b_hh, param._ctx)
     return out
+
+
+class HookHandle(object):
+    """A handle that can attach a hook to a dict of hooks and detach it again (also usable in a ``with`` block)."""
+
+    def __init__(self):
+        self._hooks_dict_ref, self._id = None, None
+
+    def attach(self, hooks_dict, hook):
+        import weakref
+        assert not self._hooks_dict_ref, 'The same handle cannot be attached twice.'
+        self._id = id(hook)
+        hooks_dict[self._id] = hook
+        self._hooks_dict_ref = weakref.ref(hooks_dict) if not isinstance(hooks_dict, dict) else (lambda d=hooks_dict: d)
+
+    def detach(self):
+        hooks = self._hooks_dict_ref() if self._hooks_dict_ref else None
+        if hooks is not None and self._id in hooks:
+            del hooks[self._id]
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, ptype, value, trace):
+        self.detach()

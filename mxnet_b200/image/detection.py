@@ -242,3 +242,24 @@ class ImageDetIter(ImageIter):
         return DataBatch([nd.array(batch_data)], [nd.array(batch_label)], pad=batch_size - i)
 
     __next__ = next
+
+
+def CreateMultiRandCropAugmenter(min_object_covered=0.1, aspect_ratio_range=(0.75, 1.33), area_range=(0.05, 1.0),
+                                 min_eject_coverage=0.3, max_attempts=50, skip_prob=0):
+    """Several random-crop augmenters of which one is picked per sample (or none, with probability ``skip_prob``).  Every
+    parameter may be a single value (shared) or a list with one value per augmenter."""
+    params = [min_object_covered, aspect_ratio_range, area_range, min_eject_coverage, max_attempts]
+    num = max([len(p) for p in params if isinstance(p, list)] + [1])
+    aligned = []
+    for p in params:
+        if isinstance(p, list):
+            assert len(p) == num, 'all list parameters must have the same length'
+            aligned.append(p)
+        else:
+            aligned.append([p] * num)
+    augs = [DetRandomCropAug(min_object_covered=moc, aspect_ratio_range=arr, area_range=ar, min_eject_coverage=mec, max_attempts=ma)
+            for moc, arr, ar, mec, ma in zip(*aligned)]
+    return DetRandomSelectAug(augs, skip_prob=skip_prob)
+
+
+__all__ += ['CreateMultiRandCropAugmenter']

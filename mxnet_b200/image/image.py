@@ -559,3 +559,60 @@ class ImageIter(object):
 
     def postprocess_data(self, datum):
         return _reg.invoke('transpose', [datum], {'axes': (2, 0, 1)})
+
+
+def imrotate(src, rotation_degrees, zoom_in=False, zoom_out=False):
+    """Rotate a float32 image (C, H, W) or batch (N, C, H, W) counter-clockwise by ``rotation_degrees`` (a scalar, or one
+    angle per image) around its centre with bilinear sampling and zero padding.  ``zoom_in`` scales so that no padding
+    shows, ``zoom_out`` so that the whole source stays visible."""
+    import math
+    import torch
+    import torch.nn.functional as F
+    if zoom_in and zoom_out:
+        raise ValueError('`zoom_in` and `zoom_out` cannot be both True')
+    t = src._data
+    if t.dtype != torch.float32:
+        raise TypeError('Only `float32` images are supported by this function')
+    single = t.dim() == 3
+    if not single and t.dim() != 4:
+        raise TypeError('Only 3D (CHW) or 4D (NCHW) images are supported')
+    batch = t[None] if single else t
+    n, _, h, w = batch.shape
+    if isinstance(rotation_degrees, NDArray):
+        if single:
+            raise TypeError('When a single image is passed the rotation angle is required to be a scalar.')
+        ang = rotation_degrees._data.float().to(t.device)
+        if ang.numel() != n:
+            raise ValueError('The number of images must be equal to the number of rotation angles')
+    else:
+        ang = torch.full((n,), float(rotation_degrees), device=t.device)
+    rad = ang * (math.pi / 180.0)
+    cos, sin = torch.cos(rad), torch.sin(rad)
+    scale = torch.ones_like(rad)
+    ac, as_ = cos.abs(), sin.abs()
+    if zoom_out:          # the bounding box of the rotated image, relative to the frame: sample a larger source area
+        scale = torch.maximum((w * ac + h * as_) / w, (w * as_ + h * ac) / h)
+    elif zoom_in:         # the largest rectangle of the frame's aspect ratio inside the rotated image
+        scale = 1.0 / (ac + as_ * max(h / w, w / h))
+        scale = scale * ((min(h, w) - 1.0) / min(h, w))      # outermost samples at pixel centres: no blend with padding
+    # normalised sampling grid: output pixel -> source location (inverse rotation), aspect corrected
+    theta = torch.zeros(n, 2, 3, device=t.device)
+    theta[:, 0, 0], theta[:, 0, 1] = cos * scale, -sin * scale * (h / w)
+    theta[:, 1, 0], theta[:, 1, 1] = sin * scale * (w / h), cos * scale
+    grid = F.affine_grid(theta, list(batch.shape), align_corners=False)
+    out = F.grid_sample(batch, grid, mode='bilinear', padding_mode='zeros', align_corners=False)
+    return src.__class__._from_tensor(out[0] if single else out, src.context)
+
+
+def random_rotate(src, angle_limits, zoom_in=False, zoom_out=False):
+    """:func:`imrotate` by an angle drawn uniformly from ``angle_limits`` (one draw per image of a batch)."""
+    import numpy as _np
+    if src.ndim == 3:
+        degrees = float(_np.random.uniform(*angle_limits))
+    else:
+        from .. import ndarray as nd
+        degrees = nd.array(_np.random.uniform(*angle_limits, size=src.shape[0]), ctx=src.context, dtype='float32')
+    return imrotate(src, degrees, zoom_in=zoom_in, zoom_out=zoom_out)
+
+
+__all__ += ['imrotate', 'random_rotate']

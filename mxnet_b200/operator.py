@@ -126,3 +126,133 @@ def _install_frontends():
 
 
 _install_frontends()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# legacy Python operators (PythonOp / NumpyOp / NDArrayOp of python/mxnet/operator.py): adapters onto CustomOp
+# ---------------------------------------------------------------------------------------------------------
+class PythonOp(object):
+    """Base class of the deprecated Python operators: override ``forward``, ``backward``, ``infer_shape``,
+    ``list_arguments``, ``list_outputs``; calling the object composes a Symbol node."""
+    _ref_holder = []
+    _counter = [0]
+
+    def __init__(self, need_top_grad=True):
+        self.info_ = None
+        self.need_top_grad_ = need_top_grad
+
+    def __call__(self, *args, **kwargs):
+        return self.get_symbol(*args, **kwargs)
+
+    def get_symbol(self, *args, **kwargs):
+        raise NotImplementedError('Must override this')
+
+    def forward(self, in_data, out_data):
+        out_data[0][:] = in_data[0]
+
+    def backward(self, out_grad, in_data, out_data, in_grad):
+        in_grad[0][:] = 1.0
+
+    def infer_shape(self, in_shape):
+        return in_shape, [in_shape[0]]
+
+    def list_outputs(self):
+        return ['output']
+
+    def list_arguments(self):
+        return ['data']
+
+    def need_top_grad(self):
+        return self.need_top_grad_
+
+    # -- shared by NumpyOp and NDArrayOp
+    def _as_custom(self, convert, write_back):
+        owner = self
+
+        class _Op(CustomOp):
+            def forward(self, is_train, req, in_data, out_data, aux):
+                ins, outs = [convert(a) for a in in_data], [convert(a) for a in out_data]
+                owner.forward(in_data=ins, out_data=outs)
+                write_back(out_data, outs, req, self)
+
+            def backward(self, req, out_grad, in_data, out_data, in_grad, aux):
+                og, ins, outs, ig = ([convert(a) for a in group] for group in (out_grad, in_data, out_data, in_grad))
+                owner.backward(out_grad=og, in_data=ins, out_data=outs, in_grad=ig)
+                write_back(in_grad, ig, req, self)
+
+        class _Prop(CustomOpProp):
+            def __init__(self, **_kwargs):
+                super().__init__(need_top_grad=owner.need_top_grad())
+
+            def list_arguments(self):
+                return owner.list_arguments()
+
+            def list_outputs(self):
+                return owner.list_outputs()
+
+            def infer_shape(self, in_shape):
+                ishape, oshape = owner.infer_shape([list(s) for s in in_shape])
+                return ishape, oshape, []
+
+            def create_operator(self, ctx, in_shapes, in_dtypes):
+                return _Op()
+        PythonOp._counter[0] += 1
+        name = '_legacy_%s_%d' % (type(self).__name__.lower(), PythonOp._counter[0])
+        register(name)(_Prop)
+        PythonOp._ref_holder.append(self)
+        return name
+
+    def _compose(self, op_type, *args, **kwargs):
+        from . import symbol as sym
+        return sym.Custom(*args, op_type=op_type, **kwargs)
+
+
+class NumpyOp(PythonOp):
+    """Deprecated: forward / backward receive NumPy arrays (outputs and input gradients are written in place)."""
+
+    def __init__(self, need_top_grad=True):
+        super().__init__(need_top_grad)
+        import warnings
+        warnings.warn('NumpyOp has been deprecated. Please use CustomOp')
+
+    def get_symbol(self, *args, **kwargs):
+        def write_back(dst, arrays, req, op):
+            for d, a, r in zip(dst, arrays, req):
+                op.assign(d, r, NDArray._from_tensor(torch.from_numpy(a).to(d._data.device), d.context))
+        op_type = self._as_custom(lambda a: a.asnumpy().copy(), write_back)
+        return self._compose(op_type, *args, **kwargs)
+
+
+class NDArrayOp(PythonOp):
+    """Deprecated: forward / backward receive the framework's arrays and write into them."""
+
+    def __init__(self, need_top_grad=True):
+        super().__init__(need_top_grad)
+        import warnings
+        warnings.warn('NDArrayOp has been deprecated. Please use CustomOp')
+
+    def get_symbol(self, *args, **kwargs):
+        op_type = self._as_custom(lambda a: a, lambda dst, arrays, req, op: None)
+        return self._compose(op_type, *args, **kwargs)
+
+    def declare_backward_dependency(self, out_grad, in_data, out_data):
+        deps = []
+        if self.need_top_grad():
+            deps.extend(out_grad)
+        deps.extend(in_data)
+        deps.extend(out_data)
+        return deps
+
+
+def get_all_registered_operators_grouped():
+    """{operator name: [the name and all its aliases]} for every registered operator."""
+    grouped = {}
+    for name in _reg.list_ops():
+        op = _reg.get(name)
+        grouped.setdefault(op.name, [op.name])
+        if name != op.name and name not in grouped[op.name]:
+            grouped[op.name].append(name)
+    return grouped
+
+
+__all__ += ['PythonOp', 'NumpyOp', 'NDArrayOp', 'get_all_registered_operators_grouped']

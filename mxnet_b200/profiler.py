@@ -254,3 +254,13 @@ def scope(name='<unk>:', append_mode=False):
 if os.environ.get('MXNET_PROFILER_AUTOSTART', '0') == '1':
     set_config(profile_all=True)
     set_state('run')
+
+
+_kvstore_handle = None
+
+
+def set_kvstore_handle(handle):
+    """Remember the kvstore whose servers ``profile_process='server'`` commands address.  Distributed stores here have
+    no separate server processes (every rank is a worker over NCCL / gloo), so server-side calls profile this process."""
+    global _kvstore_handle
+    _kvstore_handle = handle

@@ -53,3 +53,24 @@ class Features(collections.OrderedDict):
         if feature_name not in self:
             raise RuntimeError("Feature '{}' is unknown, known features are: {}".format(feature_name, list(self.keys())))
         return self[feature_name].enabled
+
+
+def _git(*args):
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    try:
+        out = subprocess.run(['git', '-C', root] + list(args), capture_output=True, text=True, timeout=10)
+        return out.stdout.strip() if out.returncode == 0 and out.stdout.strip() else 'unknown'
+    except Exception:   # pylint: disable=broad-except
+        return 'unknown'
+
+
+def get_branch():
+    """Branch of the source tree this package runs from ('unknown' outside a git checkout)."""
+    return _git('rev-parse', '--abbrev-ref', 'HEAD')
+
+
+def get_commit_hash():
+    """Commit of the source tree this package runs from ('unknown' outside a git checkout)."""
+    return _git('rev-parse', 'HEAD')

@@ -523,3 +523,390 @@ def new_matrix_with_real_eigvals_2d(n):
 def new_sym_matrix_with_real_eigvals_2d(n):
     a = np.random.uniform(-1., 1., (n, n))
     return (a + a.T) / 2
+
+
+# ---------------------------------------------------------------------------------------------------------
+# further helpers of python/mxnet/test_utils.py
+# ---------------------------------------------------------------------------------------------------------
+def default_numeric_eps():
+    """Step of the finite differences of ``check_numeric_gradient`` per dtype."""
+    return {np.dtype(np.float16): 1.0 / 2 ** 6, np.dtype(np.float32): 1.0 / 2 ** 9, np.dtype(np.float64): 1.0 / 2 ** 14}
+
+
+def get_etol(etol=None):
+    """Allowed fraction of mismatching elements (0 when not given)."""
+    return 0 if etol is None else etol
+
+
+def shuffle_csr_column_indices(csr):
+    """Shuffle the column indices inside every row of a scipy CSR matrix (unordered rows are still a valid matrix)."""
+    for i in range(len(csr.indptr) - 1):
+        lo, hi = csr.indptr[i], csr.indptr[i + 1]
+        part = np.array(csr.indices[lo:hi])
+        np.random.shuffle(part)
+        csr.indices[lo:hi] = part
+
+
+def assign_each(the_input, function):
+    """``function`` applied to every element, as float64 (a plain copy when ``function`` is None)."""
+    if function is None:
+        return np.array(the_input)
+    return np.vectorize(function, otypes=[np.float64])(np.asarray(the_input))
+
+
+def assign_each2(input1, input2, function):
+    if function is None:
+        return np.array(input1)
+    assert input1.shape == input2.shape
+    return np.vectorize(function, otypes=[np.float64])(np.asarray(input1), np.asarray(input2))
+
+
+def create_2d_np_tensor(rows, columns, dtype=np.int64):
+    """(rows, columns) NumPy-semantics array whose row r is filled with r."""
+    from . import numpy as mxnp
+    return mxnp.broadcast_to(mxnp.arange(0, rows, dtype=dtype).reshape(rows, 1), (rows, columns))
+
+
+def create_2d_tensor(rows, columns, dtype=np.int64):
+    from . import ndarray as nd
+    return nd.broadcast_to(nd.arange(0, rows, dtype=dtype).reshape((rows, 1)), shape=(rows, columns))
+
+
+def create_vector(size, dtype=np.int64):
+    from . import ndarray as nd
+    return nd.arange(0, size, dtype=dtype)
+
+
+def rand_sparse_ndarray(shape, stype, density=None, dtype=None, distribution=None, data_init=None, rsp_indices=None,
+                        modifier_func=None, shuffle_csr_indices=False, ctx=None):
+    """A random sparse array and its parts: (array, (data, indices)) for ``row_sparse``, (array, (indptr, indices, data))
+    for ``csr``.  ``distribution='powerlaw'`` makes row i hold about twice the non-zeros of row i - 1 (csr only)."""
+    from . import ndarray as nd
+    ctx = ctx or default_device()
+    density = np.random.rand() if density is None else density
+    dtype = np.dtype(dtype or 'float32')
+    distribution = distribution or 'uniform'
+    if stype == 'row_sparse':
+        assert distribution == 'uniform', 'Distribution %s not supported for row_sparse' % distribution
+        if rsp_indices is not None:
+            indices = np.asarray(sorted(rsp_indices), dtype=np.int64)
+        else:
+            indices = np.nonzero(np.random.rand(shape[0]) < density)[0].astype(np.int64)
+        if indices.size == 0:
+            arr = nd.zeros(shape, ctx=ctx, dtype=dtype).tostype('row_sparse')
+            return arr, (np.zeros((0,) + tuple(shape[1:]), dtype=dtype), indices)
+        vals = np.random.uniform(-1, 1, (indices.size,) + tuple(shape[1:])).astype(dtype)
+        if data_init is not None:
+            vals.fill(data_init)
+        if modifier_func is not None:
+            vals = assign_each(vals, modifier_func).astype(dtype)
+        dense = np.zeros(shape, dtype=dtype)
+        dense[indices] = vals
+        return nd.array(dense, ctx=ctx, dtype=dtype).tostype('row_sparse'), (vals, indices)
+    if stype == 'csr':
+        assert len(shape) == 2
+        import scipy.sparse as sp
+        if distribution == 'uniform':
+            mat = sp.random(shape[0], shape[1], density=density, format='csr', dtype=np.float64)
+        elif distribution == 'powerlaw':
+            dense = np.zeros(shape)
+            budget = max(int(density * shape[0] * shape[1]), 1)
+            per_row = 1
+            for r in range(shape[0]):
+                n = min(per_row, shape[1], budget)
+                if n <= 0:
+                    break
+                dense[r, np.random.choice(shape[1], n, replace=False)] = np.random.rand(n) + 0.1
+                budget -= n
+                per_row *= 2
+            mat = sp.csr_matrix(dense)
+        else:
+            raise AssertionError('Distribution not supported: %s' % distribution)
+        if data_init is not None:
+            mat.data.fill(data_init)
+        if modifier_func is not None:
+            mat.data = assign_each(mat.data, modifier_func)
+        if shuffle_csr_indices:
+            shuffle_csr_column_indices(mat)
+        arr = nd.sparse.csr_matrix((mat.data.astype(dtype), mat.indices.astype(np.int64), mat.indptr.astype(np.int64)), shape=shape,
+                                   ctx=ctx, dtype=dtype)
+        return arr, (mat.indptr, mat.indices, mat.data.astype(dtype))
+    raise AssertionError('unknown storage type %s' % stype)
+
+
+def create_sparse_array(shape, stype, data_init=None, rsp_indices=None, dtype=None, modifier_func=None, density=.5,
+                        shuffle_csr_indices=False):
+    """A sparse array of the given storage type with optional fixed fill value / row set."""
+    if stype == 'row_sparse':
+        arr, _ = rand_sparse_ndarray(shape, stype, density=density, data_init=data_init, rsp_indices=rsp_indices, dtype=dtype,
+                                     modifier_func=modifier_func)
+    elif stype == 'csr':
+        arr, _ = rand_sparse_ndarray(shape, stype, density=density, data_init=data_init, dtype=dtype, modifier_func=modifier_func,
+                                     shuffle_csr_indices=shuffle_csr_indices)
+    else:
+        raise AssertionError('Unknown storage type: %s' % stype)
+    return arr
+
+
+def create_sparse_array_zd(shape, stype, density, data_init=None, rsp_indices=None, dtype=None, modifier_func=None,
+                           shuffle_csr_indices=False):
+    """``create_sparse_array`` that also accepts density 0 (an all-zero array of the storage type)."""
+    if stype == 'row_sparse' and density == 0.0 and rsp_indices is None:
+        rsp_indices = []
+    if density == 0.0:
+        from . import ndarray as nd
+        return nd.zeros(shape, dtype=dtype or 'float32').tostype(stype)
+    return create_sparse_array(shape, stype, data_init=data_init, rsp_indices=rsp_indices, dtype=dtype, modifier_func=modifier_func,
+                               density=density, shuffle_csr_indices=shuffle_csr_indices)
+
+
+def rand_coord_2d(x_low, x_high, y_low, y_high):
+    return np.random.randint(x_low, x_high, dtype=np.int64), np.random.randint(y_low, y_high, dtype=np.int64)
+
+
+def checkShapes(a, b):   # pylint: disable=invalid-name
+    if a.shape != b.shape:
+        raise AssertionError('a.shape = %s and b.shape = %s are not equal' % (a.shape, b.shape))
+
+
+def locationError(a, b, index, names, maxError=False):   # pylint: disable=invalid-name
+    """One line naming where two arrays differ (most)."""
+    return 'Location of %serror: %s, %s=%.8f, %s=%.8f' % ('maximum ' if maxError else '', str(index), names[0], a[index], names[1],
+                                                           b[index])
+
+
+def assert_almost_equal_ignore_nan(a, b, rtol=None, atol=None, names=('a', 'b')):
+    """``assert_almost_equal`` where positions holding NaN in either array are not compared."""
+    a = np.copy(a.asnumpy() if isinstance(a, NDArray) else a)
+    b = np.copy(b.asnumpy() if isinstance(b, NDArray) else b)
+    nan = np.logical_or(np.isnan(a), np.isnan(b))
+    a[nan] = 0
+    b[nan] = 0
+    assert_almost_equal(a, b, rtol, atol, names)
+
+
+def check_speed(sym, location=None, ctx=None, N=20, grad_req=None, typ='whole', **kwargs):   # pylint: disable=invalid-name
+    """Seconds per iteration of a bound Symbol: forward + backward (``typ='whole'``) or forward only; shapes come from
+    ``location`` or from keyword arguments."""
+    import time
+    from . import ndarray as nd
+    ctx = ctx or default_device()
+    grad_req = grad_req or 'write'
+    if location is None:
+        arg_shapes, _, _ = sym.infer_shape(**kwargs)
+        location = {n: np.random.normal(size=s, scale=1.0) for n, s in zip(sym.list_arguments(), arg_shapes)}
+    args = {k: nd.array(v, ctx=ctx, dtype=getattr(v, 'dtype', 'float32')) for k, v in location.items()}
+    grads = {k: nd.zeros(v.shape, ctx=ctx, dtype=v.dtype) for k, v in args.items()} if typ == 'whole' else None
+    exe = sym._bind(ctx, args, args_grad=grads, grad_req=grad_req if typ == 'whole' else 'null')
+    if typ not in ('whole', 'forward'):
+        raise ValueError('typ can only be "whole" or "forward".')
+
+    def step():
+        outs = exe.forward(is_train=typ == 'whole')
+        if typ == 'whole':
+            exe.backward(out_grads=[nd.ones(o.shape, ctx=ctx, dtype=o.dtype) for o in outs])
+    step()
+    nd.waitall()
+    tic = time.time()
+    for _ in range(N):
+        step()
+    nd.waitall()
+    return (time.time() - tic) / N
+
+
+def download(url, fname=None, dirname=None, overwrite=False, retries=5):
+    """``gluon.utils.download`` with the argument order of the test helper."""
+    from .gluon.utils import download as _download
+    path = fname if dirname is None else os.path.join(dirname, fname or url.split('/')[-1])
+    return _download(url, path=path, overwrite=overwrite, retries=retries)
+
+
+def _need_files(directory, names, what):
+    missing = [n for n in names if not os.path.exists(os.path.join(directory, n))]
+    if missing:
+        raise IOError('%s: %s not found under %s and this build does not fetch data sets; place the files there'
+                      % (what, ', '.join(missing), directory))
+
+
+def get_mnist_ubyte(path='data'):
+    """The four idx files of MNIST must be present under ``path`` (no download here)."""
+    _need_files(path, ['train-images-idx3-ubyte', 'train-labels-idx1-ubyte', 't10k-images-idx3-ubyte', 't10k-labels-idx1-ubyte'],
+                'get_mnist_ubyte')
+
+
+def get_cifar10(path='data'):
+    _need_files(os.path.join(path, 'cifar'), ['train.rec', 'test.rec'], 'get_cifar10')
+
+
+def get_bz2_data(data_dir, data_name, url, data_origin_name):
+    """Unpack ``data_origin_name`` (a .bz2 file already in ``data_dir``) to ``data_name`` unless that exists."""
+    import bz2
+    target = os.path.join(data_dir, data_name)
+    if os.path.exists(target):
+        return
+    src = os.path.join(data_dir, data_origin_name)
+    _need_files(data_dir, [data_origin_name], 'get_bz2_data')
+    with bz2.BZ2File(src) as fin, open(target, 'wb') as fout:
+        fout.write(fin.read())
+
+
+def get_mnist_iterator(batch_size, input_shape, num_parts=1, part_index=0, path='data'):
+    """Training and validation ``MNISTIter`` over the idx files under ``path``."""
+    from . import io as mxio
+    get_mnist_ubyte(path)
+    flat = len(input_shape) != 3
+    common = dict(input_shape=input_shape, batch_size=batch_size, flat=flat, num_parts=num_parts, part_index=part_index)
+    train = mxio.MNISTIter(image=os.path.join(path, 'train-images-idx3-ubyte'), label=os.path.join(path, 'train-labels-idx1-ubyte'),
+                           shuffle=True, **common)
+    val = mxio.MNISTIter(image=os.path.join(path, 't10k-images-idx3-ubyte'), label=os.path.join(path, 't10k-labels-idx1-ubyte'),
+                         **common)
+    return train, val
+
+
+def same_array(array1, array2):
+    """Whether two arrays share memory: a write through one must show in the other."""
+    array1[:] += 1
+    if not same(array1.asnumpy(), array2.asnumpy()):
+        array1[:] -= 1
+        return False
+    array1[:] -= 1
+    return same(array1.asnumpy(), array2.asnumpy())
+
+
+@contextlib.contextmanager
+def discard_stderr():
+    """Send everything written to the process's stderr descriptor to the null device inside the block."""
+    import sys
+    with open(os.devnull, 'w') as sink:
+        try:
+            fd = sys.stderr.fileno()
+            saved = os.dup(fd)
+        except (AttributeError, OSError, ValueError):
+            yield                                # stderr is not a real file (captured by a test runner)
+            return
+        try:
+            os.dup2(sink.fileno(), fd)
+            yield
+        finally:
+            os.dup2(saved, fd)
+            os.close(saved)
+
+
+def mean_check(generator, mu, sigma, nsamples=1000000):
+    """Sample mean of ``generator(nsamples)`` within mu +- 3 sigma / sqrt(n)."""
+    sample_mean = np.asarray(generator(nsamples)).mean()
+    return (sample_mean > mu - 3 * sigma / np.sqrt(nsamples)) and (sample_mean < mu + 3 * sigma / np.sqrt(nsamples))
+
+
+def var_check(generator, sigma, nsamples=1000000):
+    """Sample variance of ``generator(nsamples)`` within sigma^2 +- 3 sqrt(2 sigma^4 / (n - 1))."""
+    sample_var = np.asarray(generator(nsamples)).var(ddof=1)
+    half = 3 * np.sqrt(2 * sigma ** 4 / (nsamples - 1))
+    return (sample_var > sigma ** 2 - half) and (sample_var < sigma ** 2 + half)
+
+
+def get_im2rec_path(home_env='MXNET_HOME'):
+    """Path of the im2rec tool (``mxnet_b200/tools/im2rec.py``; ``$MXNET_HOME/tools/im2rec.py`` when that is set)."""
+    if home_env in os.environ:
+        cand = os.path.join(os.environ[home_env], 'tools', 'im2rec.py')
+        if os.path.isfile(cand):
+            return cand
+    cand = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'tools', 'im2rec.py')
+    if os.path.isfile(cand):
+        return cand
+    raise IOError('Could not find path to tools/im2rec.py')
+
+
+def compare_ndarray_tuple(t1, t2, rtol=None, atol=None):
+    """Compare (nested tuples of) arrays element-wise; None entries are skipped."""
+    if t1 is None or t2 is None:
+        return
+    if isinstance(t1, (tuple, list)):
+        for s1, s2 in zip(t1, t2):
+            compare_ndarray_tuple(s1, s2, rtol, atol)
+    else:
+        assert_almost_equal(t1, t2, rtol=rtol, atol=atol)
+
+
+def compare_optimizer_noise_seeded(opt1, opt2, shapes, dtype, noise_seed, w_stype='default', g_stype='default', rtol=1e-4,
+                                   atol=1e-5, compare_states=True):
+    """``compare_optimizer`` for optimizers that draw noise in their update (SGLD): the generator is seeded with
+    ``noise_seed`` before each of the two updates so both see the same draws."""
+    from . import ndarray as nd
+    from . import random as mxrandom
+    ctx = default_device()
+    w1, w2, g1, g2, s1, s2 = [], [], [], [], [], []
+    for i, shape in enumerate(shapes):
+        w = np.random.uniform(-1, 1, size=shape).astype(dtype)
+        g = np.random.uniform(-1, 1, size=shape).astype(dtype)
+        w1.append(nd.array(w, ctx=ctx, dtype=dtype)); w2.append(nd.array(w, ctx=ctx, dtype=dtype))   # noqa: E702
+        g1.append(nd.array(g, ctx=ctx, dtype=dtype)); g2.append(nd.array(g, ctx=ctx, dtype=dtype))   # noqa: E702
+        s1.append(opt1.create_state_multi_precision(i, w1[-1]))
+        s2.append(opt2.create_state_multi_precision(i, w2[-1]))
+    if compare_states:
+        compare_ndarray_tuple(tuple(s1), tuple(s2))
+    idx = list(range(len(shapes)))
+    mxrandom.seed(noise_seed)
+    opt1.update_multi_precision(idx, w1, g1, s1)
+    mxrandom.seed(noise_seed)
+    opt2.update_multi_precision(idx, w2, g2, s2)
+    if compare_states:
+        compare_ndarray_tuple(tuple(s1), tuple(s2), rtol=rtol, atol=atol)
+    for a, b in zip(w1, w2):
+        assert_almost_equal(a, b, rtol=rtol, atol=atol)
+
+
+def same_symbol_structure(sym1, sym2):
+    """Whether the two graphs have the same operator at every node position."""
+    import json
+    n1, n2 = json.loads(sym1.tojson())['nodes'], json.loads(sym2.tojson())['nodes']
+    return all(a['op'] == b['op'] for a, b in zip(n1, n2))
+
+
+def collapse_sum_like(a, shape):
+    """Sum ``a`` over the axes along which an array of ``shape`` was broadcast to give ``a`` (the gradient of a
+    broadcast)."""
+    assert len(a.shape) >= len(shape)
+    if np.prod(shape) == 0 or a.size == 0:
+        return np.zeros(shape, dtype=a.dtype)
+    diff = len(a.shape) - len(shape)
+    axes = [i for i in range(len(a.shape)) if i < diff or shape[i - diff] != a.shape[i]]
+    return np.sum(a, axis=tuple(axes)).reshape(shape)
+
+
+def new_matrix_with_real_eigvals_nd(shape):
+    """Random batch of square matrices with real eigenvalues (D P D^-1 form)."""
+    n = int(np.prod(shape[:-2])) if len(shape) > 2 else 1
+    return np.array([new_matrix_with_real_eigvals_2d(shape[-1]) for _ in range(n)]).reshape(shape)
+
+
+def new_matrix_with_real_eigvals_2d(n):
+    """One n x n matrix with real eigenvalues: Q diag(d) Q^-1 with a random invertible Q."""
+    shape = (n, n)
+    q = np.ones(shape)
+    while 1:
+        q = np.random.uniform(-1, 1, shape)
+        if np.linalg.cond(q, 2) < 3:
+            break
+    d = np.diag(np.random.uniform(-1.0, 1.0, shape[-1]))
+    return q.dot(d).dot(np.linalg.inv(q))
+
+
+def new_orthonormal_matrix_2d(n):
+    """A random n x n orthonormal matrix (Q of a QR factorisation)."""
+    x = np.random.randn(n, n)
+    x_trans = x.T
+    sym_mat = np.matmul(x_trans, x)
+    return np.linalg.qr(sym_mat)[0]
+
+
+def new_sym_matrix_with_real_eigvals_2d(n):
+    """Symmetric n x n matrix Q diag(d) Q^T."""
+    q = new_orthonormal_matrix_2d(n)
+    d = np.diag(np.random.uniform(-1.0, 1.0, n))
+    return q.dot(d).dot(q.T)
+
+
+def new_sym_matrix_with_real_eigvals_nd(shape):
+    n = int(np.prod(shape[:-2])) if len(shape) > 2 else 1
+    return np.array([new_sym_matrix_with_real_eigvals_2d(shape[-1]) for _ in range(n)]).reshape(shape)

@@ -286,3 +286,110 @@ def test_constraint_check_operator():
             mx.npx.constraint_check(mx.np.array([1.0, -2.0]) > 0, 'Scale should be larger than zero')
     finally:
         mx.npx.reset_np()
+
+
+def test_image_rotation_and_small_api_additions():
+    import torch
+    from mxnet_b200 import image, util
+    img = nd.array(np.arange(3 * 8 * 8, dtype='float32').reshape(3, 8, 8))
+    r90 = image.imrotate(img, 90).asnumpy()
+    np.testing.assert_allclose(r90, np.rot90(img.asnumpy(), k=1, axes=(1, 2)), atol=1e-4)
+    batch = nd.array(np.ones((2, 1, 6, 10), dtype='float32'))
+    out = image.imrotate(batch, nd.array([30.0, -45.0]), zoom_in=True).asnumpy()
+    assert out.min() > 0.999                                             # no padding shows
+    plain = image.imrotate(batch, 30.0).asnumpy()
+    assert plain.min() < 0.5
+    small = image.imrotate(batch, 30.0, zoom_out=True).asnumpy()
+    assert abs(small.sum() - batch.asnumpy().sum() / 1.0) < batch.asnumpy().sum()       # the whole source is inside
+    assert small[:, :, 0, 0].max() < 0.5                                                  # corners are padding
+    with pytest.raises(ValueError):
+        image.imrotate(img, 10, zoom_in=True, zoom_out=True)
+    assert image.random_rotate(batch, (-10, 10)).shape == (2, 1, 6, 10)
+    aug = image.detection.CreateMultiRandCropAugmenter(min_object_covered=[0.1, 0.5], area_range=[(0.1, 1.0), (0.3, 1.0)])
+    assert len(aug.aug_list) == 2 and aug.aug_list[1].min_object_covered == 0.5
+    from mxnet_b200.gluon import metric
+    np.testing.assert_array_equal(metric.one_hot(np.array([0, 2]), 3), [[1, 0, 0], [0, 0, 1]])
+    np.testing.assert_array_equal(metric.predict_with_threshold(np.array([[0.2, 0.9]]), np.array([0.5, 0.95])), [[False, False]])
+    handle = mx.gluon.utils.HookHandle()
+    hooks = {}
+    handle.attach(hooks, lambda *a: None)
+    assert len(hooks) == 1
+    handle.detach()
+    assert not hooks
+    assert isinstance(mx.runtime.get_branch(), str) and len(mx.runtime.get_commit_hash()) >= 7
+    mx.profiler.set_kvstore_handle(None)
+    assert util.get_rtc_compile_opts.__doc__ and util.np_ufunc_legal_option('casting', 'safe')
+    assert callable(mx.contrib.quantization.quantize_model_onednn) and callable(mx.amp.amp.warn_if_model_exists)
+
+
+def test_legacy_python_operators_and_dynamic_unroll():
+    import warnings
+    from mxnet_b200 import operator as mxop
+
+    class Square(mxop.NumpyOp):
+        def forward(self, in_data, out_data):
+            out_data[0][:] = in_data[0] ** 2
+
+        def backward(self, out_grad, in_data, out_data, in_grad):
+            in_grad[0][:] = 2 * in_data[0] * out_grad[0]
+
+    class Scale(mxop.NDArrayOp):
+        def forward(self, in_data, out_data):
+            out_data[0][:] = in_data[0] * 3
+
+        def backward(self, out_grad, in_data, out_data, in_grad):
+            in_grad[0][:] = out_grad[0] * 3
+    with warnings.catch_warnings():
+        warnings.simplefilter('ignore')
+        s = Scale()(Square()(mx.sym.var('data')))
+    x = nd.array([1.0, -2.0, 3.0])
+    g = nd.zeros((3,))
+    ex = s._bind(mx.cpu(), {'data': x}, args_grad={'data': g})
+    np.testing.assert_allclose(ex.forward(is_train=True)[0].asnumpy(), [3, 12, 27])
+    ex.backward([nd.ones((3,))])
+    np.testing.assert_allclose(g.asnumpy(), [6, -12, 18])
+    grouped = mxop.get_all_registered_operators_grouped()
+    assert 'broadcast_add' in grouped and 'elemwise_add' in grouped['broadcast_add']
+
+    from mxnet_b200.gluon import rnn
+    from mxnet_b200.gluon.rnn.rnn_cell import dynamic_unroll
+    cell = rnn.LSTMCell(5, input_size=4)
+    cell.initialize()
+    data = nd.array(np.random.RandomState(0).randn(3, 2, 4))
+    states = cell.begin_state(batch_size=2)
+    out, new_states = dynamic_unroll(cell, data, states, valid_length=nd.array([2, 3]), layout='TNC')
+    assert out.shape == (3, 2, 5) and not out.asnumpy()[2, 0].any() and out.asnumpy()[2, 1].any()
+    full, _ = dynamic_unroll(cell, data, states, layout='TNC')
+    np.testing.assert_allclose(out.asnumpy()[:2], full.asnumpy()[:2], rtol=1e-6)
+
+
+def test_more_test_utils_helpers():
+    from mxnet_b200 import test_utils as tu
+    a, (vals, rows) = tu.rand_sparse_ndarray((6, 4), 'row_sparse', density=0.5)
+    assert a.stype == 'row_sparse' and vals.shape[0] == len(rows)
+    np.testing.assert_allclose(a.asnumpy()[rows], vals)
+    c, (indptr, indices, data) = tu.rand_sparse_ndarray((6, 5), 'csr', density=0.4, shuffle_csr_indices=True)
+    assert c.stype == 'csr' and indptr[-1] == len(data) == len(indices)
+    p = tu.rand_sparse_ndarray((8, 8), 'csr', density=0.3, distribution='powerlaw')[0].asnumpy()
+    assert list((p != 0).sum(1)[:3]) == [1, 2, 4]
+    assert tu.create_sparse_array_zd((3, 3), 'csr', 0.0).asnumpy().sum() == 0
+    assert tu.create_2d_tensor(3, 2).asnumpy().tolist() == [[0, 0], [1, 1], [2, 2]] and tu.create_vector(4).shape == (4,)
+    np.testing.assert_allclose(tu.collapse_sum_like(np.ones((2, 3, 4)), (3, 1)), [[8.0]] * 3)
+    np.testing.assert_allclose(tu.assign_each2(np.array([1., 2.]), np.array([3., 4.]), lambda x, y: x * y), [3, 8])
+    x = nd.ones((3,))
+    assert tu.same_array(x, x) and not tu.same_array(x, x.copy())
+    s = mx.sym.FullyConnected(mx.sym.var('data'), num_hidden=4)
+    assert tu.check_speed(s, data=(8, 16), N=2) > 0 and tu.check_speed(s, data=(8, 16), N=2, typ='forward') > 0
+    assert tu.same_symbol_structure(s, s) and os.path.isfile(tu.get_im2rec_path())
+    m = tu.new_sym_matrix_with_real_eigvals_nd((2, 3, 3))
+    np.testing.assert_allclose(m, m.transpose(0, 2, 1), atol=1e-12)
+    q = tu.new_orthonormal_matrix_2d(4)
+    np.testing.assert_allclose(q @ q.T, np.eye(4), atol=1e-10)
+    assert np.isreal(np.linalg.eigvals(tu.new_matrix_with_real_eigvals_nd((2, 3, 3)))).all()
+    tu.compare_optimizer_noise_seeded(mx.optimizer.SGLD(learning_rate=0.1), mx.optimizer.SGLD(learning_rate=0.1), [(3, 4)], 'float32', 7)
+    tu.assert_almost_equal_ignore_nan(np.array([1.0, np.nan]), np.array([1.0, 5.0]))
+    with pytest.raises(IOError):
+        tu.get_mnist_ubyte('/nonexistent-directory')
+    with tu.discard_stderr():
+        pass
+    assert tu.default_numeric_eps()[np.dtype('float32')] == 1.0 / 512 and tu.get_etol() == 0
