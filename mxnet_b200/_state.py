@@ -15,6 +15,7 @@ class _State(threading.local):
         self.np_shape = False
         self.np_array = False
         self.np_default_dtype = False
+        self.opt_constraints = 0      # HybridBlock.OptConstraint flags (bit 0: AMP casts off)
         self.tracer = None          # active deferred-compute tracer (symbol/_trace.py) or None
         self.bulk_size = 0
         self.profiler_scope = '<unk>:'

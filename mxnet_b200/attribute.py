@@ -39,3 +39,8 @@ class AttrScope(object):
         if v is None:
             v = AttrScope._current.value = AttrScope()
         return v
+
+
+def current():
+    """The AttrScope in effect for the calling thread."""
+    return AttrScope.current()

@@ -7,6 +7,7 @@ written into ``.params`` files and therefore has to keep its numbering.
 """
 from __future__ import annotations
 
+import os
 import numpy as _np
 import torch
 
@@ -179,3 +180,106 @@ def check_call(ret):
     """Kept for API familiarity: native calls here raise directly, so a non-zero code is an error."""
     if ret != 0:
         raise MXNetError('native call failed with code %d' % ret)
+
+
+def data_dir_default():
+    """Default directory for downloaded files: ``~/.mxnet`` (``%APPDATA%/mxnet`` on Windows)."""
+    import platform
+    if platform.system() == 'Windows':
+        return os.path.join(os.environ.get('APPDATA'), 'mxnet')
+    return os.path.join(os.path.expanduser('~'), '.mxnet')
+
+
+def data_dir():
+    """Directory for downloaded models and data sets: ``$MXNET_HOME`` or the default."""
+    return os.getenv('MXNET_HOME', data_dir_default())
+
+
+def c_str(string):
+    """A ``ctypes`` char pointer for a Python string."""
+    import ctypes
+    return ctypes.c_char_p(string.encode('utf-8'))
+
+
+def c_str_array(strings):
+    import ctypes
+    arr = (ctypes.c_char_p * len(strings))()
+    arr[:] = [s.encode('utf-8') for s in strings]
+    return arr
+
+
+def c_array(ctype, values):
+    """A ``ctypes`` array of ``ctype`` from a Python sequence."""
+    out = (ctype * len(values))()
+    out[:] = values
+    return out
+
+
+def c_array_buf(ctype, buf):
+    """A ``ctypes`` array of ``ctype`` over an object with the buffer interface (no copy)."""
+    return (ctype * len(buf)).from_buffer(buf)
+
+
+def c_handle_array(objs):
+    import ctypes
+    arr = (ctypes.c_void_p * len(objs))()
+    arr[:] = [getattr(o, 'handle', None) for o in objs]
+    return arr
+
+
+def ctypes2buffer(cptr, length):
+    """Bytes of ``length`` copied from a ``ctypes`` char pointer."""
+    import ctypes
+    if not isinstance(cptr, ctypes.POINTER(ctypes.c_char)):
+        raise TypeError('expected char pointer')
+    res = bytearray(length)
+    rptr = (ctypes.c_char * length).from_buffer(res)
+    if not ctypes.memmove(rptr, cptr, length):
+        raise RuntimeError('memmove failed')
+    return res
+
+
+def ctypes2numpy_shared(cptr, shape):
+    """A float32 NumPy view of the memory behind a ``ctypes`` float pointer."""
+    import ctypes
+    if not isinstance(cptr, ctypes.POINTER(ctypes.c_float)):
+        raise RuntimeError('expected float pointer')
+    size = 1
+    for s in shape:
+        size *= s
+    dbuffer = (ctypes.c_float * size).from_address(ctypes.addressof(cptr.contents))
+    return _np.frombuffer(dbuffer, dtype=_np.float32).reshape(shape)
+
+
+def build_param_doc(arg_names, arg_types, arg_descs, remove_dup=True):
+    """The "Parameters" section of a generated operator docstring."""
+    seen, lines = set(), []
+    for name, type_info, desc in zip(arg_names, arg_types, arg_descs):
+        if name in seen and remove_dup or name == 'num_args':
+            continue
+        seen.add(name)
+        line = '%s : %s' % (name, type_info)
+        if desc:
+            line += '\n    ' + desc
+        lines.append(line)
+    return 'Parameters\n----------\n%s\n' % '\n'.join(lines)
+
+
+def add_fileline_to_docstring(module, incursive=True):
+    """The reference appends "From:<file>:<line>" of the C++ definition to operator docstrings; operators here are defined
+    in Python, where that information is part of every traceback, so docstrings stay as written."""
+    return None
+
+
+_registered_errors = {}
+
+
+def register_error(func_name=None, cls=None):
+    """Register an exception class under a name so that errors raised by native code with that prefix map to it."""
+    if callable(func_name):
+        cls, func_name = func_name, func_name.__name__
+
+    def register(mycls):
+        _registered_errors[func_name if isinstance(func_name, str) else mycls.__name__] = mycls
+        return mycls
+    return register(cls) if cls is not None else register

@@ -659,3 +659,49 @@ class SymbolBlock(HybridBlock):
     def reset_ctx(self, ctx):
         for p in self._reg_params.values():
             p.reset_ctx(ctx)
+
+
+# ---- optimisation constraints (HybridBlock.OptConstraint, python/mxnet/gluon/block.py:1048): a scope in which
+# graph-level optimisations are held back; the one flag that exists switches the AMP casts off.
+import enum as _enum
+
+
+class _OptConstraint(object):
+    class Flag(_enum.Flag):
+        DisableAMP = _enum.auto()
+
+    def __init__(self, flag):
+        self.flag = flag
+        self.enter_state = None
+
+    def __enter__(self):
+        self.enter_state = get_optimization_constraints()
+        set_optimization_constraints(self.enter_state | self.flag)
+
+    def __exit__(self, ptype, value, trace):
+        set_optimization_constraints(self.enter_state)
+
+    @staticmethod
+    def disable_all():
+        flag = _OptConstraint.Flag(0)
+        for f in _OptConstraint.Flag:
+            flag |= f
+        return _OptConstraint(flag)
+
+    @staticmethod
+    def disable_amp():
+        return _OptConstraint(_OptConstraint.Flag.DisableAMP)
+
+
+HybridBlock.OptConstraint = _OptConstraint
+
+
+def set_optimization_constraints(state):
+    """Set the current thread's optimisation constraints; returns the previous ones."""
+    prev = _OptConstraint.Flag(_state.state.opt_constraints)
+    _state.state.opt_constraints = int(state.value)
+    return prev
+
+
+def get_optimization_constraints():
+    return _OptConstraint.Flag(_state.state.opt_constraints)

@@ -179,3 +179,12 @@ class DataLoader(object):
                     self._worker_pool.terminate()
             except Exception:  # pylint: disable=broad-except
                 pass
+
+
+def default_mp_batchify_fn(data):
+    """Batchify used inside worker processes.  The reference stacks into CPU shared memory there; workers here already
+    build their batches on the host and hand them over through pickled shared buffers, so this is the default function."""
+    return default_batchify_fn(data)
+
+
+DataLoaderV1 = DataLoader          # the first-generation loader of the reference had the same interface

@@ -27,3 +27,12 @@ def purge(root=None):
     for f in os.listdir(root) if os.path.isdir(root) else []:
         if f.endswith('.params'):
             os.remove(os.path.join(root, f))
+
+
+def short_hash(name, root=None):
+    """The 8-character hash in the file name ``<name>-<hash>.params`` of a pretrained model present under ``root``."""
+    root = os.path.expanduser(root or os.path.join(env.get('MXNET_HOME'), 'models'))
+    for fn in sorted(os.listdir(root)) if os.path.isdir(root) else []:
+        if fn.startswith(name + '-') and fn.endswith('.params'):
+            return fn[len(name) + 1:-len('.params')][:8]
+    raise ValueError('Pretrained model for {name} is not available.'.format(name=name))

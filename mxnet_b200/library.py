@@ -348,3 +348,8 @@ def _refresh_frontends():
 
 def compiled_with_cxx11_abi():
     return True
+
+
+def compiled_with_gcc_cxx11_abi():
+    """Whether the native libraries use the C++11 ABI of libstdc++ (they are built in-tree with the system g++)."""
+    return True

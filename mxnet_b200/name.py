@@ -43,3 +43,8 @@ class Prefix(NameManager):
 
     def get(self, name, hint):
         return self._prefix + super().get(name, hint)
+
+
+def current():
+    """The NameManager in effect for the calling thread."""
+    return NameManager.current()

@@ -617,3 +617,17 @@ def from_dlpack(x):
     """An ndarray sharing memory with any object that implements ``__dlpack__`` (or a DLPack capsule)."""
     import torch
     return ndarray._from_tensor(torch.utils.dlpack.from_dlpack(x))
+
+
+def genfromtxt(*args, **kwargs):
+    """``numpy.genfromtxt`` returning a framework array on ``ctx`` / ``device`` (default: the current device)."""
+    ctx = kwargs.pop('ctx', None) or kwargs.pop('device', None)
+    ret = _np.genfromtxt(*args, **kwargs)
+    return array(ret, dtype=ret.dtype, ctx=ctx)
+
+
+def set_printoptions(precision=None, threshold=None, **kwarg):
+    """Printing of framework arrays goes through NumPy: this sets NumPy's print options."""
+    if kwarg:
+        raise NotImplementedError('mxnet_b200.numpy.set_printoptions only supports parameters precision and threshold for now.')
+    _np.set_printoptions(precision=precision, threshold=threshold)

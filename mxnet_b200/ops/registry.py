@@ -131,7 +131,7 @@ def invoke(op, args, attrs, out=None, kind=None):
     if kind is None:
         kind = 'np' if st.np_array else 'nd'
     hook = _state.amp_hook
-    if hook is not None:
+    if hook is not None and not st.opt_constraints & 1:
         tensors = hook(op.name, tensors)
     prof = _state.profiler_hook
     pctx = prof(op.name) if prof is not None else None

@@ -44,3 +44,24 @@ for _n in control_flow.__all__:
     setattr(contrib, _n, getattr(control_flow, _n))   # noqa: F821  (contrib is set by _populate)
 from . import numpy as np          # noqa: E402,F401
 from . import numpy_extension as npx   # noqa: E402,F401
+
+
+def _random_extras():
+    from .symbol import _make_op_symbol
+
+    def randn(*shape, loc=0.0, scale=1.0, dtype=None, name=None, **kwargs):
+        """Normal samples of the given shape (positional extents), mean ``loc``, standard deviation ``scale``."""
+        return _make_op_symbol(_reg.get('_random_normal'), [], {'loc': loc, 'scale': scale, 'shape': tuple(shape),
+                                                                 'dtype': dtype or 'float32'}, name)
+
+    def categorical(data, shape=(), get_prob=False, dtype='int32', name=None, **kwargs):
+        """Draws from the categorical distributions in the last axis of ``data`` (alias of ``multinomial``)."""
+        return _make_op_symbol(_reg.get('_sample_multinomial'), [data], {'shape': shape, 'get_prob': get_prob, 'dtype': dtype}, name)
+
+    def shuffle(data, name=None, **kwargs):
+        """Random permutation along the first axis."""
+        return _make_op_symbol(_reg.get('_shuffle'), [data], {}, name)
+    random.randn, random.categorical, random.shuffle = randn, categorical, shuffle   # noqa: F821
+
+
+_random_extras()

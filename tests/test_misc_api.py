@@ -393,3 +393,40 @@ def test_more_test_utils_helpers():
     with tu.discard_stderr():
         pass
     assert tu.default_numeric_eps()[np.dtype('float32')] == 1.0 / 512 and tu.get_etol() == 0
+
+
+def test_second_batch_of_api_names(tmp_path):
+    from mxnet_b200 import amp as _amp   # noqa: F401
+    from mxnet_b200.gluon.block import get_optimization_constraints, set_optimization_constraints
+    Flag = mx.gluon.HybridBlock.OptConstraint.Flag
+    assert get_optimization_constraints() == Flag(0)
+    with mx.gluon.HybridBlock.OptConstraint.disable_amp():
+        assert get_optimization_constraints() == Flag.DisableAMP
+    assert get_optimization_constraints() == Flag(0)
+    prev = set_optimization_constraints(Flag.DisableAMP)
+    assert prev == Flag(0)
+    set_optimization_constraints(prev)
+    s = mx.sym.random.randn(2, 3, loc=1.0, scale=0.0)
+    np.testing.assert_allclose(s._bind(mx.cpu(), {}).forward()[0].asnumpy(), np.ones((2, 3)))
+    sh = mx.sym.random.shuffle(mx.sym.var('x'))
+    out = sh._bind(mx.cpu(), {'x': nd.array(np.arange(6.0))}).forward()[0].asnumpy()
+    assert sorted(out.tolist()) == list(range(6))
+    cat = mx.sym.random.categorical(mx.sym.var('p'), shape=(50,))
+    draws = cat._bind(mx.cpu(), {'p': nd.array([[0.0, 1.0, 0.0]])}).forward()[0].asnumpy()
+    assert draws.shape == (1, 50) and (draws == 1).all()
+    txt = tmp_path / 't.csv'
+    txt.write_text('1,2,3\n4,5,6\n')
+    g = mx.np.genfromtxt(str(txt), delimiter=',')
+    assert g.shape == (2, 3) and float(g.sum()) == 21
+    mx.np.set_printoptions(precision=3)
+    np.set_printoptions(precision=8)
+    assert mx.base.data_dir().endswith('mxnet') or 'MXNET_HOME' in os.environ
+    assert mx.base.c_array(__import__('ctypes').c_int, [1, 2, 3])[2] == 3 and mx.base.c_str('ab').value == b'ab'
+    assert 'Parameters' in mx.base.build_param_doc(['a'], ['int'], ['first'])
+    assert mx.name.current() is mx.name.NameManager.current() and mx.attribute.current() is mx.attribute.AttrScope.current()
+    with pytest.raises(ValueError):
+        mx.gluon.model_zoo.model_store.short_hash('no_such_model', root=str(tmp_path))
+    (tmp_path / 'resnet18_v1-a0666292.params').write_bytes(b'')
+    assert mx.gluon.model_zoo.model_store.short_hash('resnet18_v1', root=str(tmp_path)) == 'a0666292'
+    assert mx.gluon.data.dataloader.DataLoaderV1 is mx.gluon.data.DataLoader
+    assert mx.library.compiled_with_gcc_cxx11_abi() is True
