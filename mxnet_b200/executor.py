@@ -120,5 +120,10 @@ class Executor(object):
             if self.grad_dict else None
         return Executor(self._symbol, self._ctx, new_args, new_grads, self._grad_req, self.aux_dict)
 
+    def get_optimized_symbol(self):
+        """The graph as it runs: with pointwise groups fused once the executor has run on a GPU, else the bound Symbol."""
+        fused = getattr(self._symbol, '_fused', None)
+        return fused if fused else self._symbol
+
     def debug_str(self):
         return self._symbol.debug_str()

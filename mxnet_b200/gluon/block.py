@@ -705,3 +705,75 @@ def set_optimization_constraints(state):
 
 def get_optimization_constraints():
     return _OptConstraint.Flag(_state.state.opt_constraints)
+
+
+# ---- Block.save / Block.load (python/mxnet/gluon/block.py:579-700): configuration + parameters of a constructed model
+def _block_save(self, prefix):
+    """Write ``<prefix>-model.json`` (per block, in construction order: its parameter names, and for hybridized blocks the
+    traced graph with its input / output formats) and ``<prefix>-model.params``."""
+    import json
+    model = {}
+
+    def visit(blk, structure, index=0):
+        mdl = {}
+        structure[type(blk).__name__.lower() + str(index)] = mdl
+        index += 1
+        if isinstance(blk, HybridBlock):
+            graph = getattr(blk, '_cached_graph', None)
+            if not graph and blk._active and getattr(blk, '_last_args', None) is not None:
+                blk._trace(*blk._last_args)          # hybridized and called, but not traced yet
+                graph = blk._cached_graph
+            if graph:
+                inputs, out = graph
+                mdl.update(in_format=blk._in_format, out_format=blk._out_format, inputs=[s.tojson() for s in inputs],
+                           symbol=out.tojson(), hybridized=True)
+            else:
+                mdl['hybridized'] = False
+        mdl['params'] = {name: name for name in blk._reg_params}
+        for child in blk._children.values():
+            index = visit(child, mdl, index)
+        return index
+    visit(self, model)
+    with open(prefix + '-model.json', 'w') as fp:
+        json.dump(model, fp)
+    self.save_parameters(prefix + '-model.params')
+
+
+def _block_load(self, prefix):
+    """Restore what :meth:`save` wrote into a model that was constructed the same way (same blocks in the same order):
+    traced graphs and hybridization state per block, then the parameters."""
+    import json
+    from ..symbol import fromjson
+    with open(prefix + '-model.json') as fp:
+        model = json.load(fp)
+
+    def visit(blk, structure, index=0):
+        key = type(blk).__name__.lower() + str(index)
+        if key not in structure:
+            raise ValueError('the saved model has no block %s here: the model must be constructed exactly as when it was saved' % key)
+        mdl = structure[key]
+        index += 1
+        if isinstance(blk, HybridBlock) and mdl.get('hybridized'):
+            blk._in_format, blk._out_format = mdl['in_format'], mdl['out_format']
+            blk._cached_graph = ([fromjson(s) for s in mdl['inputs']], fromjson(mdl['symbol']))
+            blk._active = True
+        missing = [p for p in mdl.get('params', {}) if p not in blk._reg_params]
+        if missing:
+            raise ValueError('block %s lacks the saved parameters %s' % (key, missing))
+        for child in blk._children.values():
+            index = visit(child, mdl, index)
+        return index
+    visit(self, model)
+    self.load_parameters(prefix + '-model.params')
+
+
+Block.save = _block_save
+Block.load = _block_load
+
+
+def _generate_arg_names(self, arg_num):
+    """Names of the traced graph's data inputs: ``data`` for one argument, else ``data0``, ``data1`` ..."""
+    return ['data'] if arg_num == 1 else ['data%d' % i for i in range(arg_num)]
+
+
+HybridBlock.generate_arg_names = _generate_arg_names

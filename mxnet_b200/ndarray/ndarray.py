@@ -759,3 +759,22 @@ def _make_fluent(name):
 for _name in _FLUENT:
     if _name not in NDArray.__dict__:
         setattr(NDArray, _name, _make_fluent(_name))
+
+
+# ---- NDArray.drop_grad / slice_assign_scalar (python/mxnet/ndarray/ndarray.py) -------------------------------------
+def _drop_grad(self):
+    """Free the gradient buffer attached by ``attach_grad`` and stop recording gradients for this array."""
+    from .. import autograd
+    autograd.mark_variables([self], [None], 'null')
+
+
+def _slice_assign_scalar(self, value, begin, end, step):
+    """``self[begin:end:step] = value`` per axis (None entries keep the whole axis); returns self."""
+    index = tuple(slice(b, e, s) for b, e, s in zip(begin, end, step if step is not None else (None,) * len(begin)))
+    with torch.no_grad():
+        self._data[index] = value
+    return self
+
+
+NDArray.drop_grad = _drop_grad
+NDArray.slice_assign_scalar = _slice_assign_scalar

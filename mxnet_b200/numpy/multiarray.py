@@ -631,3 +631,19 @@ def set_printoptions(precision=None, threshold=None, **kwarg):
     if kwarg:
         raise NotImplementedError('mxnet_b200.numpy.set_printoptions only supports parameters precision and threshold for now.')
     _np.set_printoptions(precision=precision, threshold=threshold)
+
+
+def _nd_diagonal(self, offset=0, axis1=0, axis2=1):
+    return diagonal(self, offset=offset, axis1=axis1, axis2=axis2)
+
+
+def _nd_reshape_view(self, *shape, **kwargs):
+    """A reshaped view sharing memory with this array (a copy only when the layout makes a view impossible)."""
+    if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
+        shape = tuple(shape[0])
+    return ndarray._from_tensor(self._data.reshape(shape), self._ctx)
+
+
+ndarray.diagonal = _nd_diagonal
+ndarray.reshape_view = _nd_reshape_view
+ndarray.mT = property(lambda self: swapaxes(self, -1, -2), doc='The array with its last two axes transposed.')

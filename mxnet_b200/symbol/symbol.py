@@ -881,3 +881,49 @@ def full(shape, val, dtype=None, **kwargs):
 def arange(start, stop=None, step=1.0, repeat=1, infer_range=False, name=None, dtype=None):
     return _make_op_symbol(_reg.get('_arange'), [], {'start': start, 'stop': stop, 'step': step, 'repeat': repeat,
                                                       'dtype': dtype or 'float32'}, name)
+
+
+# ---- Symbol methods that complete the NDArray-like surface (python/mxnet/symbol/symbol.py) ----------------------
+class NotImplementedForSymbol(MXNetError):
+    """Raised by NDArray-only methods called on a Symbol."""
+
+    def __init__(self, function, alias, *args):
+        super().__init__()
+        self.function, self.alias, self.args_ = function.__name__, alias, [str(type(a)) for a in args]
+
+    def __str__(self):
+        msg = 'Function {}'.format(self.function)
+        if self.alias:
+            msg += ' (namely operator "{}")'.format(self.alias)
+        if self.args_:
+            msg += ' with arguments ({})'.format(', '.join(self.args_))
+        return msg + ' is not supported for Symbol and only available in NDArray.'
+
+
+def _symbol_astype(self, dtype, name=None):
+    """A Symbol of the same values cast to ``dtype``."""
+    return _op_frontend(_reg.get('Cast'))(self, dtype=dtype_name(to_torch_dtype(dtype)), name=name)
+
+
+_DYNAMIC_SHAPE_OPS = ('_contrib_boolean_mask', '_npi_nonzero', '_npi_unique', '_npx_nonzero', '_contrib_dynamic_reshape',
+                      '_npi_boolean_mask', '_npi_advanced_indexing', '_npi_delete', '_npi_insert_tensor')
+
+
+def _symbol_has_dynamic_shape_op(self):
+    """Whether the graph contains an operator whose output shape depends on input values."""
+    return any(n.op is not None and (n.op.name in _DYNAMIC_SHAPE_OPS or any(a in _DYNAMIC_SHAPE_OPS for a in n.op.aliases))
+               for n in _topo(self._outputs))
+
+
+def _only_ndarray(name):
+    def method(self, *args, **kwargs):
+        raise NotImplementedForSymbol(method, None, *args)
+    method.__name__ = name
+    return method
+
+
+Symbol.astype = _symbol_astype
+Symbol.has_dynamic_shape_op = _symbol_has_dynamic_shape_op
+for _n in ('as_in_context', 'as_in_ctx', 'asnumpy', 'asscalar', 'backward', 'copy', 'detach', 'wait_to_read'):
+    if _n not in Symbol.__dict__:
+        setattr(Symbol, _n, _only_ndarray(_n))

@@ -430,3 +430,49 @@ def test_second_batch_of_api_names(tmp_path):
     assert mx.gluon.model_zoo.model_store.short_hash('resnet18_v1', root=str(tmp_path)) == 'a0666292'
     assert mx.gluon.data.dataloader.DataLoaderV1 is mx.gluon.data.DataLoader
     assert mx.library.compiled_with_gcc_cxx11_abi() is True
+
+
+def test_block_save_load_and_method_additions(tmp_path):
+    from mxnet_b200.gluon import nn
+    from mxnet_b200.symbol.symbol import NotImplementedForSymbol
+
+    def build():
+        net = nn.HybridSequential()
+        net.add(nn.Dense(8, activation='relu', in_units=4), nn.Dense(3, in_units=8))
+        return net
+    net = build()
+    net.initialize()
+    net.hybridize()
+    x = nd.array(np.random.RandomState(0).randn(2, 4))
+    net(x)
+    ref = net(x).asnumpy()
+    prefix = str(tmp_path / 'mymodel')
+    net.save(prefix)
+    assert os.path.exists(prefix + '-model.json') and os.path.exists(prefix + '-model.params')
+    other = build()
+    other.load(prefix)
+    np.testing.assert_allclose(other(x).asnumpy(), ref, rtol=1e-6)
+    assert other._active and other._cached_graph is not None
+    wrong = nn.HybridSequential()
+    wrong.add(nn.Dense(8, in_units=4))
+    wrong_seq = nn.Sequential()
+    with pytest.raises(ValueError):
+        wrong_seq.load(prefix)
+    assert net.generate_arg_names(1) == ['data'] and net.generate_arg_names(2) == ['data0', 'data1']
+    s = mx.sym.var('x')
+    c = s.astype('float16')
+    assert c._bind(mx.cpu(), {'x': nd.ones((2,))}).forward()[0].dtype == np.float16
+    assert not s.has_dynamic_shape_op() and mx.sym.contrib.boolean_mask(s, mx.sym.var('m')).has_dynamic_shape_op()
+    with pytest.raises(NotImplementedForSymbol):
+        s.asnumpy()
+    a = nd.ones((3, 4))
+    a.attach_grad()
+    assert a.grad is not None
+    a.drop_grad()
+    assert a.grad is None
+    a.slice_assign_scalar(5.0, (0, 1), (2, 3), (None, None))
+    assert a.asnumpy()[:2, 1:3].sum() == 20 and a.asnumpy().sum() == 28
+    m = mx.np.arange(6).reshape(2, 3)
+    assert m.mT.shape == (3, 2) and m.diagonal().shape == (2,) and m.reshape_view(3, 2).shape == (3, 2)
+    ex = mx.sym.relu(s)._bind(mx.cpu(), {'x': nd.ones((2,))})
+    assert ex.get_optimized_symbol().list_arguments() == ['x']
