@@ -63,3 +63,5 @@ from . import models
 from . import onnx
 from . import notebook
 from .ndarray import waitall
+from .util import is_np_default_dtype   # noqa: F401
+from .kvstore import kvstore_server    # noqa: F401

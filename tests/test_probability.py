@@ -124,3 +124,46 @@ def test_stochastic_block_collects_losses():
     net.initialize()
     out = net(mnp.ones((4, 3)))
     assert out.shape == (4, 2) and len(net.losses) == 1 and net.losses[0].shape == (4, 2)
+
+
+def test_constraints_and_distribution_utils():
+    from mxnet_b200.gluon.probability.distributions import constraint as C, utils as U
+    import mxnet_b200.gluon.probability.distributions.constraint as C2
+    assert C is C2
+    mx.npx.set_np()
+    try:
+        v = mx.np.array([0.2, 0.8])
+        assert C.UnitInterval().check(v) is v and C.Simplex().check(v) is v and C.Real().check(v) is v
+        bad = [(C.Positive(), [-1.0]), (C.NonNegative(), [-0.5]), (C.IntegerInterval(0, 5), [1.5]), (C.OpenInterval(0, 1), [1.0]),
+               (C.HalfOpenInterval(0, 1), [1.0]), (C.LessThan(2), [2.0]), (C.LessThanEq(2), [2.5]), (C.GreaterThanEq(1), [0.5]),
+               (C.PositiveInteger(), [0.0]), (C.NonNegativeInteger(), [0.5]), (C.Boolean(), [2.0]), (C.Simplex(), [0.5, 0.6]),
+               (C.LowerTriangular(), [[1., 2.], [0., 1.]]), (C.LowerCholesky(), [[-1., 0.], [0., 1.]]),
+               (C.PositiveDefinite(), [[1., 2.], [2., 1.]])]
+        for c, value in bad:
+            with pytest.raises(ValueError, match='Constraint violated'):
+                c.check(mx.np.array(value))
+        ok = [(C.HalfOpenInterval(0, 1), [0.0]), (C.IntegerGreaterThan(1), [2.0]), (C.IntegerLessThanEq(3), [3.0]),
+              (C.LowerCholesky(), [[1., 0.], [2., 3.]]), (C.PositiveDefinite(), [[2., 1.], [1., 2.]])]
+        for c, value in ok:
+            c.check(mx.np.array(value))
+        assert C.Stack([C.Positive(), C.Real()]).check(mx.np.array([1.0, -3.0])).shape == (2,)
+        with pytest.raises(ValueError):
+            C.Cat([C.Positive(), C.NonNegative()], lengths=[1, 2]).check(mx.np.array([1.0, -1.0, 2.0]))
+        assert C.is_dependent(C.dependent) and not C.is_dependent(C.Real())
+        np.testing.assert_allclose(U.prob2logit(mx.np.array([0.5])).asnumpy(), [0.0], atol=1e-6)
+        np.testing.assert_allclose(U.logit2prob(mx.np.array([[0.0, 0.0]]), False).asnumpy(), [[0.5, 0.5]])
+        np.testing.assert_allclose(U.prob2logit(mx.np.array([0.25, 0.75]), False).asnumpy(), np.log([0.25, 0.75]), rtol=1e-6)
+        assert U.sample_n_shape_converter(3) == (3,) and U.sample_n_shape_converter(None) == ()
+        np.testing.assert_allclose(U.gammaln()(mx.np.array([4.0])).asnumpy(), [np.log(6.0)], rtol=1e-6)
+
+        class Holder(object):
+            calls = 0
+
+            @U.cached_property
+            def value(self):
+                Holder.calls += 1
+                return 7
+        h = Holder()
+        assert h.value == 7 and h.value == 7 and Holder.calls == 1
+    finally:
+        mx.npx.reset_np()
