@@ -248,3 +248,40 @@ def test_hybridize_with_the_fusion_backend_runs_the_partitioned_graph():
         np.testing.assert_allclose(net.bn.running_mean.data().asnumpy(), ref_mean, rtol=1e-5, atol=1e-7)
     finally:
         mx.npx.reset_np()
+
+
+@pytest.mark.gpu
+def test_hybridized_block_with_fusion_backend_on_the_gpu():
+    from mxnet_b200.gluon import nn
+
+    class Net(mx.gluon.HybridBlock):
+        def __init__(self):
+            super().__init__()
+            self.fc1, self.fc2 = nn.Dense(64, in_units=32), nn.Dense(8, in_units=64)
+
+        def forward(self, x):
+            h = self.fc1(x)
+            h = mx.npx.activation(h, 'tanh') * 0.5 + mx.np.exp(-mx.np.square(h))
+            return self.fc2(h)
+
+    mx.npx.set_np()
+    try:
+        ctx = mx.gpu(0)
+        net = Net()
+        net.initialize(ctx=ctx)
+        x = mx.np.array(np.random.RandomState(0).randn(16, 32).astype('float32'), ctx=ctx)
+        with autograd.record():
+            ref = net(x)
+            ref.sum().backward()
+        ref_out, ref_grad = ref.asnumpy(), net.fc1.weight.grad().asnumpy().copy()
+        net.hybridize(backend='pointwise_fusion')
+        net(x)
+        before = fusion.stats['kernel_calls']
+        with autograd.record():
+            out = net(x)
+            out.sum().backward()
+        assert fusion.stats['kernel_calls'] >= before + 2            # the fused group ran forward and backward
+        np.testing.assert_allclose(out.asnumpy(), ref_out, rtol=1e-4, atol=1e-5)
+        np.testing.assert_allclose(net.fc1.weight.grad().asnumpy(), ref_grad, rtol=1e-3, atol=1e-4)
+    finally:
+        mx.npx.reset_np()
