@@ -39,7 +39,7 @@ def parse():
 
 def reference_arm(args):
     print(json.dumps({'impl': 'reference', 'unavailable':
-                      'reference is not installable offline: /root/reference has no setup.py/pyproject.toml at its root, '
+                      'reference is not installable offline: the reference tree has no setup.py/pyproject.toml at its root, '
                       'python/setup.py needs a compiled libmxnet.so and the dmlc-core/tvm(nnvm)/ps-lite/cub submodules '
                       'are empty, so it cannot be built (pip: "Neither setup.py nor pyproject.toml found")'}))
     return 0
