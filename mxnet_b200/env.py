@@ -144,3 +144,20 @@ declare('MXNET_USE_OPERATOR_TUNING', bool, True, 'tune OpenMP use per CPU op')
 declare('MXNET_OMP_MAX_THREADS', int, 0, 'cap of intra-op host threads (0 = auto)')
 declare('MXNET_OPTIMIZER_AGGREGATION_SIZE', int, 4, 'tensors per multi-tensor optimizer call')
 declare('MXNET_STORAGE_FALLBACK_LOG_VERBOSE', bool, True, 'log dense fallbacks of sparse inputs')
+
+
+def markdown():
+    """The flag table as a Markdown document (``docs/env_var.md`` is this text; the reference documents its flags in
+    ``docs/static_site/src/pages/api/faq/env_var.md``)."""
+    lines = ['# Environment variables', '',
+             'Every flag is read through `mxnet_b200.env.get(name)`; the environment wins over the default, and '
+             '`mxnet_b200.env.scope(NAME=value)` / `mxnet_b200.test_utils.environment` set one for a `with` block.', '',
+             '| variable | type | default | meaning |', '|---|---|---|---|']
+    for f in sorted(FLAGS.values(), key=lambda f: f.name):
+        lines.append('| `%s` | %s | `%r` | %s |' % (f.name, f.type.__name__, f.default, f.doc.replace('|', '\\|')))
+    return '\n'.join(lines) + '\n'
+
+
+if __name__ == '__main__':
+    import sys
+    sys.stdout.write(markdown())

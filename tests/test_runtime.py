@@ -197,3 +197,12 @@ def test_feature_flags_and_env_registry():
     with env.scope('MXNET_KVSTORE_WAIT_MS', 5):
         assert env.get('MXNET_KVSTORE_WAIT_MS') == 5
     assert 'MXNET_ENGINE_TYPE' in env.describe()
+
+
+def test_environment_variable_document_is_current():
+    """docs/env_var.md is generated from the flag registry: regenerate with `python -m mxnet_b200.env > docs/env_var.md`."""
+    import os
+    from mxnet_b200 import env
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with open(os.path.join(root, 'docs', 'env_var.md')) as f:
+        assert f.read() == env.markdown()
