@@ -179,3 +179,32 @@ def test_random_crop_and_decoder_operators(tmp_path):
     np.testing.assert_array_equal(nd._internal._cvimread(filename=str(path)).asnumpy(), img.asnumpy())
     gray = nd._internal._cvimread(filename=str(path), flag=0)
     assert gray.shape == (20, 30, 1)
+
+
+def test_dgl_graph_operators():
+    x = np.array([[1, 0, 0, 2], [3, 0, 4, 0], [0, 5, 0, 0], [0, 6, 7, 0]], dtype='float32')
+    new, old = _run('_contrib_dgl_subgraph', x, np.array([0, 1, 2]), num_args=2, return_mapping=True)
+    np.testing.assert_array_equal(new, [[1, 0, 0], [2, 0, 3], [0, 4, 0]])
+    np.testing.assert_array_equal(old, [[1, 0, 0], [3, 0, 4], [0, 5, 0]])
+    # a complete graph on five vertices with edge ids 1..20
+    g = np.zeros((5, 5), dtype='float32')
+    g[~np.eye(5, dtype=bool)] = np.arange(1, 21)
+    np.random.seed(0)
+    vid, sub, layer = _run('_contrib_dgl_csr_neighbor_uniform_sample', g, np.array([0, 1]), num_args=2, num_hops=1, num_neighbor=2,
+                           max_num_vertices=5)
+    n = int(vid[-1])
+    assert vid.shape == (6,) and sub.shape == (5, 5) and layer.shape == (5,) and 2 <= n <= 5
+    verts = vid[:n]
+    assert list(verts) == sorted(verts) and {0, 1} <= set(verts.tolist())
+    assert sorted(layer[:n].tolist())[:2] == [0, 0] and (layer[n:] == -1).all()
+    rows = [list(verts).index(s) for s in (0, 1)]
+    for r, s in zip(rows, (0, 1)):
+        picked = np.nonzero(sub[r])[0]
+        assert 1 <= len(picked) <= 2 and all(sub[r, c] == g[s, c] for c in picked)      # parent edge ids on sampled edges
+    prob = np.array([0.0, 0.0, 1.0, 1.0, 0.0], dtype='float32')
+    vid2, sub2, pr, layer2 = _run('_contrib_dgl_csr_neighbor_non_uniform_sample', g, prob, np.array([0]), num_args=3, num_hops=1,
+                                  num_neighbor=2, max_num_vertices=4)
+    assert set(vid2[:int(vid2[-1])].tolist()) == {0, 2, 3}                              # only vertices with weight are drawn
+    np.testing.assert_allclose(pr[:3], [0.0, 1.0, 1.0])
+    compact = _run('_contrib_dgl_graph_compact', sub2, vid2, num_args=2, graph_sizes=(3,), return_mapping=False)
+    assert compact.shape == (3, 3) and sorted(compact[compact != 0].tolist()) == [1.0, 2.0]
