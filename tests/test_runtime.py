@@ -206,3 +206,42 @@ def test_environment_variable_document_is_current():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     with open(os.path.join(root, 'docs', 'env_var.md')) as f:
         assert f.read() == env.markdown()
+
+
+def test_clock_sampler_against_a_fake_nvml(monkeypatch):
+    """The sampler that bench.py runs during the timed region: median SM clock under load, maximum clock and the
+    throttle reasons seen, read through NVML (here a stand-in module; nothing is ever written to the device)."""
+    import sys
+    import time
+    import types
+    from mxnet_b200.utils import ClockSampler
+    fake = types.ModuleType('pynvml')
+    fake.NVML_CLOCK_SM = 1
+    fake.nvmlClocksThrottleReasonSwPowerCap = 0x4
+    fake.nvmlClocksThrottleReasonHwSlowdown = 0x8
+    fake.nvmlClocksThrottleReasonSwThermalSlowdown = 0x20
+    fake.nvmlClocksThrottleReasonHwThermalSlowdown = 0x40
+    calls = {'n': 0, 'writes': 0}
+    clocks = [1965, 1400, 1350, 1300, 1320]
+    fake.nvmlInit = lambda: None
+    fake.nvmlDeviceGetHandleByIndex = lambda i: ('gpu', i)
+    fake.nvmlDeviceGetMaxClockInfo = lambda h, kind: 1965
+
+    def clock(h, kind):
+        calls['n'] += 1
+        return clocks[min(calls['n'] - 1, len(clocks) - 1)]
+    fake.nvmlDeviceGetClockInfo = clock
+    fake.nvmlDeviceGetUtilizationRates = lambda h: types.SimpleNamespace(gpu=10 if calls['n'] <= 1 else 99)
+    fake.nvmlDeviceGetCurrentClocksThrottleReasons = lambda h: 0x4 if calls['n'] >= 3 else 0
+    monkeypatch.setitem(sys.modules, 'pynvml', fake)
+    sampler = ClockSampler(0, interval=0.01).start()
+    deadline = time.time() + 5
+    while calls['n'] < 6 and time.time() < deadline:
+        time.sleep(0.01)
+    res = sampler.stop()
+    assert res['sm_max_mhz'] == 1965 and res['reasons'] == ['sw_power_cap'] and res['samples'] >= 5
+    assert 1300 <= res['sm_mhz'] <= 1400                       # the idle 1965 MHz sample is not part of the loaded median
+    # without NVML the sampler degrades to "no data" instead of failing the benchmark
+    broken = types.ModuleType('pynvml')
+    monkeypatch.setitem(sys.modules, 'pynvml', broken)
+    assert ClockSampler(0).start().stop()['sm_mhz'] is None
