@@ -285,3 +285,44 @@ def test_hybridized_block_with_fusion_backend_on_the_gpu():
         np.testing.assert_allclose(net.fc1.weight.grad().asnumpy(), ref_grad, rtol=1e-3, atol=1e-4)
     finally:
         mx.npx.reset_np()
+
+
+def _two_output_graph():
+    x, b, s = mx.sym.var('x'), mx.sym.var('b'), mx.sym.var('s')
+    h = mx.sym.broadcast_add(x, b)                       # bias over the last axis
+    u = mx.sym.broadcast_mul(mx.sym.tanh(h), s)          # one-element scale
+    v = mx.sym.exp(-mx.sym.square(h)) + u                # reads u inside the group
+    return mx.sym.Group([mx.sym.sum(u, axis=1), mx.sym.FullyConnected(v, num_hidden=3, no_bias=True, name='fc')])
+
+
+def test_group_with_two_outputs_and_broadcast_inputs():
+    g = _two_output_graph()
+    f = fusion.fuse_pointwise(g)
+    groups = [n.attrs['group'] for n in _topo(f._outputs) if n.op is not None and n.op.name == '_FusedOp']
+    assert len(groups) == 1 and len(groups[0].outputs) == 2 and groups[0].nin == 3
+    rng = np.random.RandomState(0)
+    feed = {'x': torch.tensor(rng.randn(4, 6), dtype=torch.float32), 'b': torch.tensor(rng.randn(6), dtype=torch.float32),
+            's': torch.tensor([1.5]), 'fc_weight': torch.tensor(rng.randn(3, 6), dtype=torch.float32)}
+    for a, b in zip(g._run(feed), f._run(feed)):
+        torch.testing.assert_close(a, b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('rows,cols', [(64, 96), (7, 13)])       # vector and scalar code paths
+def test_two_output_kernels_with_bias_and_scalar_inputs_on_the_gpu(rows, cols):
+    from mxnet_b200 import env
+    g = _two_output_graph()
+    rng = np.random.RandomState(1)
+    base = {'x': rng.randn(rows, cols), 'b': rng.randn(cols), 's': np.array([1.5]), 'fc_weight': rng.randn(3, cols) * 0.3}
+    res = []
+    for fuse in ('1', '0'):
+        with env.scope('MXNET_USE_FUSION', fuse):
+            feed = {k: torch.tensor(v, dtype=torch.float32, device='cuda').requires_grad_(True) for k, v in base.items()}
+            calls = fusion.stats['kernel_calls']
+            outs = mx.sym.Group(list(g))._run(feed)
+            (outs[0].sum() + (outs[1] ** 2).sum()).backward()
+            if fuse == '1':
+                assert fusion.stats['kernel_calls'] == calls + 2
+            res.append([o.detach().cpu() for o in outs] + [feed[k].grad.cpu() for k in sorted(feed)])
+    for a, b in zip(*res):
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-4)
