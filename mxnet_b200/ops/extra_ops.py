@@ -43,7 +43,8 @@ if not has('_npi_bitwise_left_shift'):
     register('_npi_bitwise_left_shift', inputs=('lhs', 'rhs'))(lambda lhs, rhs: torch.bitwise_left_shift(lhs, rhs))
     register('_npi_bitwise_right_shift', inputs=('lhs', 'rhs'))(lambda lhs, rhs: torch.bitwise_right_shift(lhs, rhs))
 
-for _new, _old in (('_npi_deg2rad', '_npi_radians'), ('_npi_rad2deg', '_npi_degrees'), ('_npx_relu', 'relu'), ('_npx_sigmoid', 'sigmoid'),
+for _new, _old in (('_sample_categorical', '_sample_multinomial'), ('sample_categorical', '_sample_multinomial'),
+                   ('_npi_deg2rad', '_npi_radians'), ('_npi_rad2deg', '_npi_degrees'), ('_npx_relu', 'relu'), ('_npx_sigmoid', 'sigmoid'),
                    ('_npx_nonzero', '_npi_nonzero'), ('_copyto', '_copy')):
     if has(_old) and not has(_new):
         alias(get(_old).name, _new)
@@ -419,3 +420,18 @@ def quantized_reshape(data, min_data, max_data, newshape=(), reverse=False, **kw
 @register('_npx_quantized_transpose', inputs=('data', 'min_data', 'max_data'), nout=3, defaults={'axes': None})
 def quantized_transpose(data, min_data, max_data, axes=None):
     return (data.permute(*axes) if axes else data.permute(*reversed(range(data.dim())))), min_data, max_data
+
+
+@register('_contrib_quantized_rnn', 'quantized_rnn', inputs=('data', 'parameters', 'state', 'state_cell', 'data_scale', 'data_shift'),
+          nout=lambda a: (1 + (2 if a.get('mode', 'lstm') == 'lstm' else 1)) if a.get('state_outputs') else 1,
+          defaults=dict(get('RNN').defaults))
+def quantized_rnn(data, parameters, state, state_cell=None, data_scale=None, data_shift=None, **attrs):
+    """The RNN operator on asymmetrically quantised uint8 input (``q = round(scale * x + shift)``, the output of
+    ``_contrib_quantize_asym``): the input is brought back to floating point and the recurrence runs in the precision of
+    the parameters (``src/operator/quantization/quantized_rnn.cc``; lstm only in the reference)."""
+    mode = attrs.get('mode', 'lstm')
+    if mode != 'lstm':
+        state_cell, data_scale, data_shift = None, state_cell, data_scale       # no cell state input for the other modes
+    x = (data.to(parameters.dtype) - data_shift.reshape(()).to(parameters.dtype)) / data_scale.reshape(()).to(parameters.dtype)
+    fn = get('RNN').fn
+    return fn(x, parameters, state, state_cell, **attrs) if mode == 'lstm' else fn(x, parameters, state, **attrs)

@@ -39,7 +39,7 @@ def _populate():
 
 _populate()
 
-from . import control_flow   # noqa: E402
+from . import control_flow, fusion   # noqa: E402,F401  (fusion registers _FusedOp)
 for _n in control_flow.__all__:
     setattr(contrib, _n, getattr(control_flow, _n))   # noqa: F821  (contrib is set by _populate)
 from . import numpy as np          # noqa: E402,F401

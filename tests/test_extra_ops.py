@@ -208,3 +208,16 @@ def test_dgl_graph_operators():
     np.testing.assert_allclose(pr[:3], [0.0, 1.0, 1.0])
     compact = _run('_contrib_dgl_graph_compact', sub2, vid2, num_args=2, graph_sizes=(3,), return_mapping=False)
     assert compact.shape == (3, 3) and sorted(compact[compact != 0].tolist()) == [1.0, 2.0]
+
+
+def test_quantized_rnn_follows_the_float_operator():
+    from mxnet_b200.ops.nn import rnn_param_size
+    rng = np.random.RandomState(5)
+    T, B, I, H = 4, 2, 6, 5
+    x = rng.rand(T, B, I).astype('float32')
+    params = (rng.randn(rnn_param_size('lstm', 1, I, H)) * 0.3).astype('float32')
+    h0, c0 = np.zeros((1, B, H), 'float32'), np.zeros((1, B, H), 'float32')
+    q, scale, shift = _run('_contrib_quantize_asym', x)
+    ref = _run('RNN', x, params, h0, c0, state_size=H, num_layers=1, mode='lstm')
+    got = _run('_contrib_quantized_rnn', q, params, h0, c0, scale, shift, state_size=H, num_layers=1, mode='lstm')
+    np.testing.assert_allclose(got, ref, atol=5e-3)
