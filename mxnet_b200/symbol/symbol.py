@@ -381,7 +381,7 @@ class Symbol(object):
             if not node.op.variadic and len(ins) < len(node.op.inputs):
                 ins = ins + [None] * 0
             hook = _state.amp_hook
-            if hook is not None:
+            if hook is not None and not _state.state.opt_constraints & 1:
                 ins = hook(node.op.name, ins)
             res = node.op.fn(*ins, **node.attrs)
             values[id(node)] = tuple(res) if isinstance(res, (tuple, list)) else (res,)

@@ -127,3 +127,25 @@ def test_convert_hybrid_block_and_symbol():
     conv = amp.convert_symbol(sym, target_dtype='float16')
     ops = [n['op'] for n in __import__('json').loads(conv.tojson())['nodes']]
     assert 'amp_cast' in ops
+
+
+def test_opt_constraint_scope_switches_amp_casts_off():
+    """HybridBlock.OptConstraint.disable_amp(): inside the scope operators see their inputs uncast."""
+    from mxnet_b200 import _state
+    seen = []
+    prev = _state.amp_hook
+    _state.amp_hook = lambda name, tensors: (seen.append(name), tensors)[1]
+    try:
+        a = mx.nd.ones((2, 2))
+        (a + a).wait_to_read()
+        n = len(seen)
+        assert n >= 1
+        with mx.gluon.HybridBlock.OptConstraint.disable_amp():
+            (a * a).wait_to_read()
+            s = mx.sym.relu(mx.sym.var('x'))
+            s._bind(mx.cpu(), {'x': a}).forward()
+        assert len(seen) == n
+        (a - a).wait_to_read()
+        assert len(seen) == n + 1
+    finally:
+        _state.amp_hook = prev
