@@ -62,6 +62,7 @@ from . import parallel
 from . import models
 from . import onnx
 from . import notebook
+from . import tvmop
 from .ndarray import waitall
 from .util import is_np_default_dtype   # noqa: F401
 from .kvstore import kvstore_server    # noqa: F401
