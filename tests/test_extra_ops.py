@@ -10,7 +10,7 @@ from mxnet_b200.ops import registry
 
 def _run(name, *tensors, **attrs):
     out = registry.get(name).fn(*[torch.as_tensor(t) if t is not None else None for t in tensors], **attrs)
-    return [o.numpy() for o in out] if isinstance(out, (tuple, list)) else out.numpy()
+    return [o.cpu().numpy() for o in out] if isinstance(out, (tuple, list)) else out.cpu().numpy()
 
 
 def test_scalar_variants_of_binary_functions():
@@ -66,7 +66,7 @@ def test_random_additions_have_the_right_moments():
     np.testing.assert_allclose(s.std(0), [1, 2], rtol=0.05)
     u = _run('_npi_uniform_n', np.array([0., 2.], 'float32'), np.array([1., 6.], 'float32'), size=(20000,))
     np.testing.assert_allclose(u.mean(0), [0.5, 4.0], atol=0.05)
-    b = registry.get('_random_binomial').fn(n=10, p=0.3, shape=(20000,)).numpy()
+    b = registry.get('_random_binomial').fn(n=10, p=0.3, shape=(20000,)).cpu().numpy()
     np.testing.assert_allclose(b.mean(), 3.0, atol=0.1)
     sb = _run('_sample_binomial', np.array([10., 20.], 'float32'), np.array([0.5, 0.1], 'float32'), shape=(5000,))
     assert sb.shape == (2, 5000)
