@@ -3,6 +3,7 @@ in the module that caused them (the reference's root ``conftest.py:62-230`` does
 import os
 import random
 import sys
+import zlib
 
 import numpy as np
 import pytest
@@ -38,7 +39,8 @@ def _seed_everything(request):
     elif env_seed:
         seed = int(env_seed)
     else:
-        seed = abs(hash(request.node.nodeid)) % (2 ** 31)
+        # crc32 of the node id: the same seed in every process (hash() of a str is salted per interpreter)
+        seed = zlib.crc32(request.node.nodeid.encode()) % (2 ** 31)
     np.random.seed(seed)
     random.seed(seed)
     mx.random.seed(seed)

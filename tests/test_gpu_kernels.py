@@ -690,7 +690,23 @@ def test_maxpool_nhwc(shape, k, s, p, ceil, dtype):
 
 
 # ---------------------------------------------------------------------------------------- model-level checks
-def test_resnet_block_kernels_match_library_path():
+def _flip_tolerant_close(got, ref, tol, max_bad_frac, what):
+    """Element-wise closeness that tolerates a bounded share of outliers plus a bound on the relative L2 error.
+
+    A half-precision value that lands on the other side of a ReLU edge than the fp32 oracle switches one mask bit, and
+    that changes whole gradient elements downstream; such flips are rare, so they are bounded by count, while the norm
+    bound still catches a wrong kernel."""
+    err = np.abs(got - ref)
+    bad = err > (tol + tol * np.abs(ref))
+    frac = float(bad.mean())
+    rel = float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-12))
+    assert frac <= max_bad_frac, '%s: %.4f of the elements differ by more than %g (max err %g)' % (what, frac, tol, err.max())
+    assert rel <= 5e-2, '%s: relative L2 error %g' % (what, rel)
+
+
+def test_resnet_block_kernels_match_fp32_oracle():
+    """Both half-precision paths of a bottleneck block (in-tree kernels, library kernels) against an fp32 evaluation of
+    the same block with the same weights."""
     from mxnet_b200 import env
     from mxnet_b200.gluon.model_zoo.vision.resnet import BottleneckV1
     ctx = mx.gpu(0)
@@ -701,20 +717,27 @@ def test_resnet_block_kernels_match_library_path():
             p.cast('float16')
     x = nd.array(np.random.randn(4, 8, 8, 32).astype('float16'), ctx=ctx, dtype='float16')
     blk(x)                       # finishes the deferred initialisation of the BatchNorm parameters
-    outs = []
-    for flag in ('1', '0'):
+
+    def run(flag, dtype):
         with env.scope('MXNET_B200_KERNELS', flag):
-            xx = x.copy()
+            xx = x.astype(dtype)
             xx.attach_grad()
             for p in blk.collect_params().values():
                 if p.grad_req == 'null':
                     p.set_data(nd.zeros(p.shape, ctx=ctx) if 'mean' in p.name else nd.ones(p.shape, ctx=ctx))
             with autograd.record():
                 y = blk(xx)
-            y.backward(nd.ones(y.shape, ctx=ctx, dtype='float16'))
-            outs.append((y.asnumpy().astype('float32'), xx.grad.asnumpy().astype('float32')))
-    np.testing.assert_allclose(outs[0][0], outs[1][0], rtol=3e-2, atol=3e-2)
-    np.testing.assert_allclose(outs[0][1], outs[1][1], rtol=6e-2, atol=6e-2)
+            y.backward(nd.ones(y.shape, ctx=ctx, dtype=dtype))
+            return y.asnumpy().astype('float32'), xx.grad.asnumpy().astype('float32')
+
+    half = {flag: run(flag, 'float16') for flag in ('1', '0')}
+    for p in blk.collect_params().values():
+        if p.grad_req != 'null':
+            p.cast('float32')
+    ref_y, ref_dx = run('0', 'float32')
+    for flag, (y, dx) in half.items():
+        _flip_tolerant_close(y, ref_y, 3e-2, 0.002, 'y (MXNET_B200_KERNELS=%s)' % flag)
+        _flip_tolerant_close(dx, ref_dx, 6e-2, 0.03, 'dx (MXNET_B200_KERNELS=%s)' % flag)
 
 
 def test_hybridize_cuda_graph_matches_eager():
