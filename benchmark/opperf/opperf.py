@@ -281,7 +281,9 @@ def gemm_burst(ctx, dtype, reps=50):
         b = torch.randn(n, k, device=ctx.torch_device).to(td)
         d = torch.empty(m, n, device=ctx.torch_device, dtype=td)
         res = {'op': 'gemm_burst', 'M': m, 'N': n, 'K': k, 'dtype': dtype, 'reps': reps}
-        for name, fn in (('tcgen05', lambda: gemm_ops.gemm_tn(a, b, out=d)), ('library', lambda: torch.matmul(a, b.t(), out=d))):
+        for name, fn in (('tcgen05', lambda: gemm_ops.gemm_tn(a, b, out=d)), ('single_cta', lambda: gemm_ops.gemm_tn(a, b, out=d)),
+                         ('library', lambda: torch.matmul(a, b.t(), out=d))):
+            gemm_ops.set_variant(1 if name == 'single_cta' else 0)
             for _ in range(3):
                 fn()
             torch.cuda.synchronize()
@@ -319,7 +321,8 @@ def gemm_layouts(ctx, dtype, reps=30):
         }
         for kind, (own, libf) in cases.items():
             res = {'op': 'gemm_layouts', 'layer': '%d->%d' % (cin, cout), 'product': kind, 'dtype': dtype, 'reps': reps}
-            for name, fn in (('tcgen05', own), ('library', libf)):
+            for name, fn in (('tcgen05', own), ('single_cta', own), ('library', libf)):
+                gemm_ops.set_variant(1 if name == 'single_cta' else 0)
                 for _ in range(3):
                     fn()
                 torch.cuda.synchronize()

@@ -146,6 +146,9 @@ def unscale(optimizer_or_trainer):
             for g in p._grad.values():
                 g._data.div_(s)
     optimizer_or_trainer._scale = optimizer_or_trainer._amp_original_scale
+    # the next step must not divide by the scale again (the fused step does that division inside its reduce kernel); it
+    # still checks for overflow and adapts the scale
+    scaler._grads_unscaled = True
 
 
 def convert_symbol(sym, input_dtypes=None, param_dtypes=None, target_dtype='float16', target_dtype_ops=None,

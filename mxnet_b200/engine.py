@@ -73,7 +73,29 @@ def waitall():
                 torch.cuda.synchronize(i)
             except RuntimeError as e:
                 raise MXNetError(str(e))
+    _check_fused_steps()
     _rethrow_pending()
+
+
+def _check_fused_steps():
+    """A fused optimizer step reports a device-side wait time-out through a status word; look at it here (and at exit), so
+    that a failed LAST step is not silent."""
+    import sys
+    fused = sys.modules.get(__package__ + '.parallel.fused')
+    if fused is not None:
+        fused.check_all()
+
+
+def _at_exit():
+    try:
+        _check_fused_steps()
+    except MXNetError as e:          # no caller is left to catch it: say it on stderr
+        import sys
+        sys.stderr.write('mxnet_b200: %s\n' % e)
+
+
+import atexit as _atexit  # noqa: E402
+_atexit.register(_at_exit)
 
 
 def set_bulk_size(size):

@@ -234,13 +234,7 @@ class Trainer(object):
         if self._params_to_init:
             self._init_params()
         if self._fused is not None:
-            if not ignore_stale_grad:
-                for p, arr in zip(self._fused.params, self._fused._data_arrays):
-                    if not arr._fresh_grad:
-                        raise UserWarning('Gradient of Parameter `%s` on device %s has not been updated by backward '
-                                          'since last `step`; call step with ignore_stale_grad=True to suppress this '
-                                          'check' % (p.name, str(arr.context)))
-            self._fused.step(rescale_grad, self._amp_loss_scaler)
+            self._fused.step(rescale_grad, self._amp_loss_scaler, self._fused_stale(ignore_stale_grad))
             return
         self._allreduce_grads()
         self._update(ignore_stale_grad)
@@ -280,9 +274,19 @@ class Trainer(object):
             'to False when creating trainer.'
         self._check_and_rescale_grad(self._scale / batch_size)
         if self._fused is not None:
-            self._fused.update_only(self._optimizer.rescale_grad, self._amp_loss_scaler)
+            self._fused.update_only(self._optimizer.rescale_grad, self._amp_loss_scaler, self._fused_stale(ignore_stale_grad))
             return
         self._update(ignore_stale_grad)
+
+    def _fused_stale(self, ignore_stale_grad):
+        """Positions (in the fused step's parameter list) whose gradient backward has not refreshed: an error unless
+        ``ignore_stale_grad``, in which case the fused kernels leave those parameters and their state untouched."""
+        stale = [k for k, arr in enumerate(self._fused._data_arrays) if not arr._fresh_grad]
+        if stale and not ignore_stale_grad:
+            p, arr = self._fused.params[stale[0]], self._fused._data_arrays[stale[0]]
+            raise UserWarning('Gradient of Parameter `%s` on device %s has not been updated by backward since last `step`; '
+                              'call step with ignore_stale_grad=True to suppress this check' % (p.name, str(arr.context)))
+        return stale
 
     def _is_fresh(self, arr):
         """True when backward wrote this replica's gradient since the last update that consumed it
@@ -293,6 +297,7 @@ class Trainer(object):
     def _update(self, ignore_stale_grad=False):
         loss_scaler = self._amp_loss_scaler
         if loss_scaler is not None:
+            loss_scaler._grads_unscaled = False      # only the fused step needs to know about amp.unscale()
             if loss_scaler.has_overflow(self._params):
                 loss_scaler.update_scale(True)
                 return          # skip the step, gradients are garbage
@@ -329,6 +334,7 @@ class Trainer(object):
         if self._params_to_init:
             self._init_params()
         if self._fused is not None:
+            # local: this rank alone collects every shard through peer copies (no other rank has to call save_states)
             self._fused.export_states(self._updaters[0])
         if self._update_on_kvstore:
             assert not self._params_to_init, 'Cannot save trainer states when some parameters are not yet ' \

@@ -76,6 +76,8 @@ struct StepParams {
   float lower_bound, upper_bound;   // LAMB clamps of ||w|| (negative = off)
   float* norm_acc;                  // local [2][nseg]: per-parameter partial sums of w^2 and u^2 over this shard
   float* norm_in[kMaxRanks];        // every rank's receive area [kMaxRanks][2][nseg] (own entry = local pointer)
+  const int* seg_skip;              // per-parameter flag: 1 = leave this parameter and its state untouched (stale gradient); may be null
+  const float* seg_coef;            // per-parameter bias corrections [2][nseg] when the update counts differ; null = coef1 / coef2
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -278,6 +280,7 @@ __global__ void __launch_bounds__(256) fused_update_kernel(const __grid_constant
         continue;
       }
       const int seg = find_segment(p.seg_end, p.nseg, e);
+      if (p.seg_skip && p.seg_skip[seg]) continue;      // weights, master copy and state stay as they are on every rank
       const float lr = p.lr * p.lr_mult[seg], wd = p.wd * p.wd_mult[seg];
       float w[N], m[N];
       if (p.master) {
@@ -308,7 +311,8 @@ __global__ void __launch_bounds__(256) fused_update_kernel(const __grid_constant
         }
       }
       // Adam folds the bias correction into the step size (python/mxnet/optimizer/adam.py: lr *= sqrt(c2) / c1)
-      const float lr_t = adam ? lr * sqrtf(p.coef2) / p.coef1 : lr;
+      const float c1 = p.seg_coef ? p.seg_coef[seg] : p.coef1, c2 = p.seg_coef ? p.seg_coef[p.nseg + seg] : p.coef2;
+      const float lr_t = adam ? lr * sqrtf(c2) / c1 : lr;
 #pragma unroll
       for (int j = 0; j < N; ++j) {
         float gr = g[j] * coef;
@@ -405,7 +409,9 @@ __global__ void __launch_bounds__(256) fused_lamb1_kernel(const __grid_constant_
     for (int64_t v = c0 + threadIdx.x; v < c1; v += blockDim.x) {
       const int64_t e = v * N, le = e - p.shard_begin;
       while (seg < p.nseg - 1 && e >= p.seg_end[seg]) ++seg;
+      const bool stale = p.seg_skip && p.seg_skip[seg];      // nothing of this parameter changes; phase 2 skips it as well
       const float wd = p.wd * p.wd_mult[seg];
+      const float c1 = p.seg_coef ? p.seg_coef[seg] : p.coef1, c2 = p.seg_coef ? p.seg_coef[p.nseg + seg] : p.coef2;
       float g[N], w[N], m[N], s2[N];
       load_f(p.gred + le, g, N);
       load_f(p.mom + le, m, N);
@@ -424,14 +430,19 @@ __global__ void __launch_bounds__(256) fused_lamb1_kernel(const __grid_constant_
         if (p.clip_gradient >= 0.f) gr = fminf(fmaxf(gr, -p.clip_gradient), p.clip_gradient);
         m[j] = p.beta1 * m[j] + (1.f - p.beta1) * gr;
         s2[j] = p.beta2 * s2[j] + (1.f - p.beta2) * gr * gr;
-        const float u = (m[j] / p.coef1) / (sqrtf(s2[j] / p.coef2) + p.epsilon) + wd * w[j];
+        const float u = (m[j] / c1) / (sqrtf(s2[j] / c2) + p.epsilon) + wd * w[j];
         g[j] = u;
         w2 += w[j] * w[j];
         u2 += u * u;
       }
-      store_f(p.gred + le, g, N);
-      store_f(p.mom + le, m, N);
-      store_f(p.var + le, s2, N);
+      if (!stale) {
+        store_f(p.gred + le, g, N);
+        store_f(p.mom + le, m, N);
+        store_f(p.var + le, s2, N);
+      } else {
+        w2 = 0.f;
+        u2 = 0.f;
+      }
       // lanes of a warp that work on the same parameter combine their sums before the atomic
       const unsigned peers = __match_any_sync(__activemask(), seg);
       const int leader = __ffs(peers) - 1, lane = threadIdx.x & 31;
@@ -490,6 +501,7 @@ __global__ void __launch_bounds__(256) fused_lamb2_kernel(const __grid_constant_
     for (int64_t v = v0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < v1; v += (int64_t)gridDim.x * blockDim.x) {
       const int64_t e = v * N, le = e - p.shard_begin;
       const int seg = find_segment(p.seg_end, p.nseg, e);
+      if (p.seg_skip && p.seg_skip[seg]) continue;
       float w2 = 0.f, u2 = 0.f;
       for (int r = 0; r < p.nranks; ++r) {       // fixed order: every rank computes the same ratio
         w2 += __ldcg(recv + (int64_t)r * n2 + seg);
@@ -618,6 +630,9 @@ MXB_EXPORT int mxb_ipc_open(const void* handle, void** ptr) {
 MXB_EXPORT int mxb_ipc_close(void* ptr) { return (int)cudaIpcCloseMemHandle(ptr); }
 MXB_EXPORT int mxb_memcpy_d2h(void* dst, const void* src, uint64_t bytes, void* stream) {
   return (int)cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+}
+MXB_EXPORT int mxb_memcpy_d2d(void* dst, const void* src, uint64_t bytes, void* stream) {
+  return (int)cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
 }
 MXB_EXPORT int mxb_memcpy_h2d(void* dst, const void* src, uint64_t bytes, void* stream) {
   return (int)cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream);

@@ -12,6 +12,7 @@ _ACT = {None: 0, 'relu': 1, 'gelu': 2}
 _err = {}
 _tuned = {}          # (product, dtype, M, N, K, bias, act) -> True when the in-tree kernel won
 _flush = {}
+_ws = {}
 _MARGIN = 1.02      # ties (within 2 %) go to the in-tree kernel
 
 
@@ -65,12 +66,33 @@ def _error_flag(device):
     return f
 
 
+def _workspace(device):
+    """Stream-K workspace of the GEMM kernel (piece counters + fp32 slots): one zero-filled buffer per device, created on
+    first use and left clean by every launch.  Launches that share it must not overlap: the framework issues its GEMMs on
+    the device's compute stream (graph replays included).  Never created while a graph is being captured (the memory would
+    belong to that graph); such a call runs without stream-K."""
+    ws = _ws.get(device)
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        ws = _ws[device] = torch.zeros(int(lib().mxb_gemm_workspace_bytes()), dtype=torch.uint8, device=device)
+    return ws
+
+
 def check_errors():
     """Raise if any GEMM CTA gave up waiting on a barrier (the result would be incomplete)."""
     for dev, f in _err.items():
         if int(f.item()) != 0:
             f.zero_()
+            if dev in _ws:                          # a launch that gave up may have left piece counters behind
+                _ws[dev].zero_()
             raise RuntimeError('tcgen05 GEMM reported a barrier time-out on %s' % dev)
+
+
+def set_variant(v):
+    """Kernel selection of later ``gemm`` calls: 0 = per shape (CTA-pair kernel where it applies), 1 = single-CTA kernel
+    only.  For benchmarks and tests that compare the two."""
+    lib().mxb_gemm_set_variant(int(v))
 
 
 def supported(M, N, K):
@@ -114,16 +136,9 @@ def gemm(a, b, a_mn=False, b_mn=False, bias=None, act=None, out=None):
             bias = bias.to(a.dtype)
         require(bias, 'bias', numel=N, device=a.device)
     L = lib()
-    if L.mxb_gemm_wants_workspace(M, N, K):
-        # few output tiles and a long contraction (a weight gradient): split-K through an fp32 workspace
-        ws = torch.empty(M * N, dtype=torch.float32, device=a.device)
-        rc = L.mxb_gemm_ws(dt(a), ptr(a), ptr(b), ptr(d), ptr(bias), M, N, K, a.shape[1], b.shape[1], N,
-                           1 if a_mn else 0, 1 if b_mn else 0, _ACT[act], ptr(ws), ptr(_error_flag(a.device)),
-                           stream_ptr(a.device))
-        count_launch(2)
-    else:
-        rc = L.mxb_gemm(dt(a), ptr(a), ptr(b), ptr(d), ptr(bias), M, N, K, a.shape[1], b.shape[1], N,
-                        1 if a_mn else 0, 1 if b_mn else 0, _ACT[act], ptr(_error_flag(a.device)), stream_ptr(a.device))
+    rc = L.mxb_gemm_ws(dt(a), ptr(a), ptr(b), ptr(d), ptr(bias), M, N, K, a.shape[1], b.shape[1], N,
+                       1 if a_mn else 0, 1 if b_mn else 0, _ACT[act], ptr(_workspace(a.device)), ptr(_error_flag(a.device)),
+                       stream_ptr(a.device))
     check(rc, 'gemm')
     count_launch(1)
     return d

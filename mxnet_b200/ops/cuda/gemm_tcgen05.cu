@@ -29,6 +29,8 @@
 namespace mxb {
 
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
+// kernel selection: 0 = per shape, 1 = always the single-CTA kernel, 2 = the CTA-pair kernel wherever it applies
+static int g_gemm_variant = 0;
 constexpr int kGemmThreads = 192;
 constexpr uint32_t A_BYTES = BM * BK * 2;
 constexpr int kMaxStages = 8;
@@ -48,12 +50,170 @@ enum Act { kActNone = 0, kActRelu = 1, kActGelu = 2 };
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erf_fast(x * 0.70710678118654752f)); }
 
+// Epilogue of one warp: drains 32 accumulator rows (TMEM lanes) by BN columns starting at TMEM address `taddr`, adds
+// the bias, applies the activation and stores rows [row0, row0 + 32) x columns [tile_col0, tile_col0 + BN) of D, either
+// through the copy engine (32 x 32 blocks staged in `stg`) or with per-thread stores.
+// Stream-K pieces: with `part_out` set, the fp32 partial products of this k-range are written to that slot
+// ([128][BN] floats, this warp's rows starting at `part_row0`) and nothing else happens; with `n_others` > 0 the
+// partial products found in the slots `others[0 .. n_others)` are added to the accumulator before the bias.
+template <typename T, int BN>
+__device__ __forceinline__ void drain_quarter(uint32_t taddr, uint8_t* stg, const CUtensorMap* map_d, int use_tma_store,
+                                              T* __restrict__ D, const T* __restrict__ bias, int M, int N, int ldd, int act,
+                                              int row0, int tile_col0, int lane, float* __restrict__ part_out = nullptr,
+                                              const float* const* others = nullptr, int n_others = 0, int part_row0 = 0) {
+  const int row = row0 + lane;
+  const bool to_ws = part_out != nullptr;
+  const bool bias_vec = bias != nullptr && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
+  const bool row_vec = (ldd % 8) == 0;
+  uint32_t r[32];
+  tmem_ld32(taddr, r);
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    const int col0 = tile_col0 + c0;
+    const bool full_cols = col0 + 32 <= N;
+    // bias of these 32 columns first, so its latency overlaps the TMEM load (registers only: every index
+    // below is a compile-time constant after unrolling)
+    float bv[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) bv[j] = 0.f;
+    if (bias != nullptr && col0 < N) {
+      if (bias_vec && full_cols) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const Vec16<T> b = ld16(bias + col0 + v * 8);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) bv[v * 8 + j] = Cvt<T>::to_f(b.v[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < N) bv[j] = Cvt<T>::to_f(bias[col0 + j]);
+      }
+    }
+    tmem_wait_ld32(r);
+    if (to_ws) {
+      float* prow = part_out + (size_t)(part_row0 + lane) * BN + c0;
+#pragma unroll
+      for (int v = 0; v < 8; ++v)
+        __stcg(reinterpret_cast<float4*>(prow) + v, make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
+                                                               __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3])));
+      if (c0 + 32 < BN) tmem_ld32(taddr + (uint32_t)(c0 + 32), r);
+      continue;
+    }
+    for (int o = 0; o < n_others; ++o) {
+      // the other k-ranges of this tile, written by other CTAs (read through L2, never from this SM's L1)
+      const float* prow = others[o] + (size_t)(part_row0 + lane) * BN + c0;
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        const float4 t = __ldcg(reinterpret_cast<const float4*>(prow) + v);
+        r[v * 4] = __float_as_uint(__uint_as_float(r[v * 4]) + t.x);
+        r[v * 4 + 1] = __float_as_uint(__uint_as_float(r[v * 4 + 1]) + t.y);
+        r[v * 4 + 2] = __float_as_uint(__uint_as_float(r[v * 4 + 2]) + t.z);
+        r[v * 4 + 3] = __float_as_uint(__uint_as_float(r[v * 4 + 3]) + t.w);
+      }
+    }
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float x = __uint_as_float(r[j]) + bv[j];
+      if (act == kActRelu) x = fmaxf(x, 0.f);
+      else if (act == kActGelu) x = gelu_erf(x);
+      f[j] = x;
+    }
+    // the next 32 columns travel from TMEM while these are converted and stored
+    if (c0 + 32 < BN) tmem_ld32(taddr + (uint32_t)(c0 + 32), r);
+    if (use_tma_store) {
+      // rows as four 16-byte pieces in the swizzled layout of the store's tensor map; one bulk store per 32 x 32
+      // block (rows and columns outside the matrix are clipped by the copy engine)
+      if (lane == 0) tma_store_wait_read();
+      __syncwarp();
+      if (col0 < N && row0 < M) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          Vec16<T> o;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o.v[j] = Cvt<T>::from_f(f[v * 8 + j]);
+          st16(reinterpret_cast<T*>(stg + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)), o);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(map_d, stg, col0, row0);
+          tma_store_commit();
+        }
+      }
+    } else if (row < M && col0 < N) {
+      T* drow = D + (size_t)row * ldd + col0;
+      if (full_cols && row_vec) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          Vec16<T> o;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o.v[j] = Cvt<T>::from_f(f[v * 8 + j]);
+          st16(drow + v * 8, o);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < N) drow[j] = Cvt<T>::from_f(f[j]);
+      }
+    }
+  }
+}
+
+// The work of one CTA of the persistent grid: first whole tiles (tile = blockIdx.x, + gridDim.x, ... below `full_tiles`),
+// then its share of the stream-K region: the `sk_tiles` tiles after `full_tiles` are a sequence of sk_tiles * num_k
+// k-steps that is cut into `sk_ctas` contiguous, equally long ranges, so a CTA computes the end of one tile, possibly
+// whole tiles, and the beginning of another.  A piece that is not a whole tile is `partial`; its fp32 result goes to
+// slot 0 of the CTA if the tile is the first one the CTA touches, else to slot 1.  The three roles walk the same sequence.
+struct UnitIter {
+  int tile, k0, k1, sk_tile, slot;
+  bool partial;
+  int next_full, full_tiles, num_k, first_t;
+  uint32_t a, b;
+  __device__ __forceinline__ void init(int full_tiles_, int sk_tiles, int sk_ctas, int num_k_) {
+    next_full = blockIdx.x;
+    full_tiles = full_tiles_;
+    num_k = num_k_;
+    a = b = 0;
+    if (sk_tiles > 0 && (int)blockIdx.x < sk_ctas) {
+      const uint64_t total = (uint64_t)sk_tiles * (uint64_t)num_k;
+      a = (uint32_t)((uint64_t)blockIdx.x * total / (uint64_t)sk_ctas);
+      b = (uint32_t)((uint64_t)(blockIdx.x + 1) * total / (uint64_t)sk_ctas);
+    }
+    first_t = (int)(a / (uint32_t)num_k);
+  }
+  __device__ __forceinline__ bool next() {
+    if (next_full < full_tiles) {
+      tile = next_full;
+      next_full += gridDim.x;
+      k0 = 0; k1 = num_k; partial = false; sk_tile = -1; slot = 0;
+      return true;
+    }
+    if (a < b) {
+      const int t = (int)(a / (uint32_t)num_k);
+      k0 = (int)(a - (uint32_t)t * (uint32_t)num_k);
+      int len = (int)(b - a);
+      if (len > num_k - k0) len = num_k - k0;
+      k1 = k0 + len;
+      tile = full_tiles + t;
+      sk_tile = t;
+      partial = len != num_k;
+      slot = t == first_t ? 0 : 1;
+      a += (uint32_t)len;
+      return true;
+    }
+    return false;
+  }
+};
+constexpr int kMaxOthers = 7;      // a tile of the stream-K region is cut into at most 8 pieces (the host guarantees it)
+
 template <typename T, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_d, int use_tma_store, T* __restrict__ D, const T* __restrict__ bias, int M,
                int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, const FastDiv fd_tiles_m,
-               int ksplit, int ksteps_per, int full_tiles, const FastDiv fd_rem_tiles, float* __restrict__ ws, int a3d, int b3d,
+               int full_tiles, int sk_tiles, int sk_ctas, float* __restrict__ sk_ws, int* __restrict__ sk_cnt, int a3d, int b3d,
                int* __restrict__ error_flag) {
   using Cfg = TileCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
@@ -73,16 +233,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* issued_it = abort_flag + 1;     // k-steps whose TMA loads were issued
   volatile int* consumed_it = abort_flag + 2;   // k-steps whose loads were observed complete by the MMA warp
+  // per epilogue warp: [last arriver?, number of other pieces] of its quarter of the current stream-K tile, and the
+  // other pieces' slots (8-byte aligned: `bars` + 208)
+  volatile int* sk_info = abort_flag + 3;       // [4][2]
+  const float** sk_others = reinterpret_cast<const float**>(const_cast<int*>(abort_flag) + 11);   // [4][kMaxOthers]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_k = (K + BK - 1) / BK;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
-  // Work units: the first `full_tiles` tiles are computed whole; each of the remaining tiles (the last, partial round of
-  // the persistent grid, or all tiles of a small output) is split into `ksplit` k-ranges whose partial products are
-  // added into the fp32 workspace.  Units of one k-range are adjacent.
-  const int rem_tiles = num_tiles - full_tiles;
-  const int num_units = full_tiles + rem_tiles * ksplit;
   constexpr uint32_t kTmemCols = Cfg::TMEM_COLS;     // two accumulators; a power of two >= 32
 
   if (threadIdx.x == 0) {
@@ -112,16 +271,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int it = 0, st = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < num_units && ok && !*abort_flag; unit += gridDim.x) {
-        uint32_t ks_u = 0, tile_u = (uint32_t)unit, tile_n_u, tile_m_u;
-        if (unit >= full_tiles) {
-          fd_divmod((uint32_t)(unit - full_tiles), fd_rem_tiles, &ks_u, &tile_u);
-          tile_u += (uint32_t)full_tiles;
-        }
-        fd_divmod(tile_u, fd_tiles_m, &tile_n_u, &tile_m_u);
+      UnitIter u;
+      u.init(full_tiles, sk_tiles, sk_ctas, num_k);
+      while (ok && !*abort_flag && u.next()) {
+        uint32_t tile_n_u, tile_m_u;
+        fd_divmod((uint32_t)u.tile, fd_tiles_m, &tile_n_u, &tile_m_u);
         const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u;
-        const int k0 = unit >= full_tiles ? (int)ks_u * ksteps_per : 0;
-        const int k1 = unit >= full_tiles ? min(num_k, k0 + ksteps_per) : num_k;
+        const int k0 = u.k0, k1 = u.k1;
         for (int kt = k0; kt < k1; ++kt) {
           if (!mbar_wait(&empty[st], ph ^ 1u)) { *abort_flag = 1; ok = false; break; }
           mbar_expect_tx(&full[st], A_BYTES + B_BYTES);
@@ -162,10 +318,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int it = 0, st = 0, t = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < num_units && ok && !*abort_flag; unit += gridDim.x, ++t) {
-        const int ks = unit >= full_tiles ? (int)fd_div((uint32_t)(unit - full_tiles), fd_rem_tiles) : 0;
-        const int k0 = unit >= full_tiles ? ks * ksteps_per : 0;
-        const int k1 = unit >= full_tiles ? min(num_k, k0 + ksteps_per) : num_k;
+      UnitIter u;
+      u.init(full_tiles, sk_tiles, sk_ctas, num_k);
+      for (; ok && !*abort_flag && u.next(); ++t) {
+        const int k0 = u.k0, k1 = u.k1;
         const int buf = t & 1;
         // wait until the epilogue has drained this accumulator (its first use passes immediately)
         if (!mbar_wait(&acc_empty[buf], (((uint32_t)t >> 1) & 1u) ^ 1u)) { *abort_flag = 1; break; }
@@ -193,116 +349,57 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int q = warp & 3;
     uint8_t* stg = sStg + q * 2048;       // this warp's staging tile: 32 rows x 64 bytes, 64-byte swizzle
     int t = 0;
-    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++t) {
-      uint32_t ks_u = 0, tile_u = (uint32_t)unit, tile_n_u, tile_m_u;
-      if (unit >= full_tiles) {
-        fd_divmod((uint32_t)(unit - full_tiles), fd_rem_tiles, &ks_u, &tile_u);
-        tile_u += (uint32_t)full_tiles;
-      }
-      fd_divmod(tile_u, fd_tiles_m, &tile_n_u, &tile_m_u);
+    UnitIter u;
+    u.init(full_tiles, sk_tiles, sk_ctas, num_k);
+    for (; u.next(); ++t) {
+      uint32_t tile_n_u, tile_m_u;
+      fd_divmod((uint32_t)u.tile, fd_tiles_m, &tile_n_u, &tile_m_u);
       const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u;
-      const bool to_ws = ws != nullptr && unit >= full_tiles;
       const int buf = t & 1;
       const bool ready = mbar_wait(&acc_full[buf], ((uint32_t)t >> 1) & 1u);
       if (!ready) *abort_flag = 1;
       if (!ready || *abort_flag) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row = tile_m * BM + q * 32 + lane;
-      const bool bias_vec = bias != nullptr && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
-      const bool row_vec = (ldd % 8) == 0;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::ACC_STRIDE);
-      uint32_t r[32];
-      tmem_ld32(taddr, r);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        const int col0 = tile_n * BN + c0;
-        const bool full_cols = col0 + 32 <= N;
-        // bias of these 32 columns first, so its latency overlaps the TMEM load (registers only: every index
-        // below is a compile-time constant after unrolling)
-        float bv[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) bv[j] = 0.f;
-        if (bias != nullptr && col0 < N) {
-          if (bias_vec && full_cols) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const Vec16<T> b = ld16(bias + col0 + v * 8);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) bv[v * 8 + j] = Cvt<T>::to_f(b.v[j]);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < N) bv[j] = Cvt<T>::to_f(bias[col0 + j]);
-          }
-        }
-        tmem_wait_ld32(r);
-        if (to_ws) {
-          // split-K: add this k-range's partial tile to the fp32 workspace (bias and activation are applied by the
-          // finishing kernel once every k-range has been added)
-          if (row < M && col0 < N) {
-            float* wrow = ws + (size_t)row * N + col0;
-            if (full_cols && (N % 4) == 0) {
-#pragma unroll
-              for (int v = 0; v < 8; ++v)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(wrow + v * 4), "f"(__uint_as_float(r[v * 4])),
-                             "f"(__uint_as_float(r[v * 4 + 1])), "f"(__uint_as_float(r[v * 4 + 2])),
-                             "f"(__uint_as_float(r[v * 4 + 3])) : "memory");
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < N) atomicAdd(wrow + j, __uint_as_float(r[j]));
+      const int row0 = tile_m * BM + q * 32, col0 = tile_n * BN;
+      if (!u.partial) {
+        drain_quarter<T, BN>(taddr, stg, &map_d, use_tma_store, D, bias, M, N, ldd, act, row0, col0, lane);
+      } else {
+        // A piece of a stream-K tile: publish the fp32 partial products of this warp's 32 rows, then count the piece in
+        // (one counter per tile and row quarter, so the four epilogue warps never wait for each other).  The CTA whose
+        // piece arrives last adds the other pieces to its own accumulator (still in tensor memory) and writes the
+        // rows; no CTA ever waits for another one.
+        constexpr size_t kSlot = (size_t)BM * BN;
+        drain_quarter<T, BN>(taddr, stg, &map_d, use_tma_store, D, bias, M, N, ldd, act, row0, col0, lane,
+                             sk_ws + ((size_t)blockIdx.x * 2 + (size_t)u.slot) * kSlot, nullptr, 0, q * 32);
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          const uint64_t total = (uint64_t)sk_tiles * (uint64_t)num_k, lo = (uint64_t)u.sk_tile * (uint64_t)num_k;
+          const int c_lo = (int)(((lo + 1) * (uint64_t)sk_ctas - 1) / total);
+          const int c_hi = (int)(((lo + (uint64_t)num_k) * (uint64_t)sk_ctas - 1) / total);
+          const int pieces = c_hi - c_lo + 1;
+          int* cnt = sk_cnt + u.sk_tile * 4 + q;
+          const int last = atomicAdd(cnt, 1) == pieces - 1 ? 1 : 0;
+          int n = 0;
+          if (last) {
+            *cnt = 0;            // every piece has arrived: the counter is clean for the next launch
+            for (int c = c_lo; c <= c_hi && n < kMaxOthers; ++c) {
+              if (c == (int)blockIdx.x) continue;
+              const int first_c = (int)(((uint64_t)c * total / (uint64_t)sk_ctas) / (uint64_t)num_k);
+              sk_others[q * kMaxOthers + n++] = sk_ws + ((size_t)c * 2 + (u.sk_tile == first_c ? 0 : 1)) * kSlot;
             }
           }
-          if (c0 + 32 < BN) tmem_ld32(taddr + (uint32_t)(c0 + 32), r);
-          continue;
+          sk_info[q * 2] = last;
+          sk_info[q * 2 + 1] = n;
         }
-        float f[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float x = __uint_as_float(r[j]) + bv[j];
-          if (act == kActRelu) x = fmaxf(x, 0.f);
-          else if (act == kActGelu) x = gelu_erf(x);
-          f[j] = x;
+        __syncwarp();
+        if (sk_info[q * 2]) {
+          __threadfence();
+          drain_quarter<T, BN>(taddr, stg, &map_d, use_tma_store, D, bias, M, N, ldd, act, row0, col0, lane, nullptr,
+                               sk_others + q * kMaxOthers, sk_info[q * 2 + 1], q * 32);
         }
-        // the next 32 columns travel from TMEM while these are converted and stored
-        if (c0 + 32 < BN) tmem_ld32(taddr + (uint32_t)(c0 + 32), r);
-        if (use_tma_store) {
-          // rows as four 16-byte pieces in the swizzled layout of the store's tensor map; one bulk store per 32 x 32
-          // block (rows and columns outside the matrix are clipped by the copy engine)
-          if (lane == 0) tma_store_wait_read();
-          __syncwarp();
-          if (col0 < N) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              Vec16<T> o;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) o.v[j] = Cvt<T>::from_f(f[v * 8 + j]);
-              st16(reinterpret_cast<T*>(stg + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)), o);
-            }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&map_d, stg, col0, tile_m * BM + q * 32);
-              tma_store_commit();
-            }
-          }
-        } else if (row < M && col0 < N) {
-          T* drow = D + (size_t)row * ldd + col0;
-          if (full_cols && row_vec) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              Vec16<T> o;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) o.v[j] = Cvt<T>::from_f(f[v * 8 + j]);
-              st16(drow + v * 8, o);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < N) drow[j] = Cvt<T>::from_f(f[j]);
-          }
-        }
+        __syncwarp();
       }
       // this warp has finished reading the accumulator: let the MMA warp reuse it
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -326,37 +423,197 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
-// Split-K helpers over the tiles [first_tile, first_tile + gridDim.x) of a 128 x BN tiling (tile = tile_n * tiles_m +
-// tile_m): `zero` clears their region of the fp32 workspace before the GEMM, `finish` computes D = act(ws + bias) there
-// afterwards.  One CTA per tile, one thread per 8 columns of a row.
-template <typename T, bool kFinish>
-__global__ void __launch_bounds__(256)
-gemm_splitk_tiles_kernel(float* __restrict__ ws, const T* __restrict__ bias, T* __restrict__ D, int M, int N, int ldd, int act,
-                         int bn, int tiles_m, int first_tile) {
-  const int tile = first_tile + blockIdx.x;
-  const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
-  const int vec_per_row = bn / 8;
-  for (int i = threadIdx.x; i < BM * vec_per_row; i += blockDim.x) {
-    const int row = tile_m * BM + i / vec_per_row, c = tile_n * bn + (i % vec_per_row) * 8;
-    if (row >= M || c >= N) continue;
-    float* w = ws + (size_t)row * N + c;
-    if (!kFinish) {
-      *reinterpret_cast<float4*>(w) = make_float4(0.f, 0.f, 0.f, 0.f);
-      *reinterpret_cast<float4*>(w + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-      continue;
-    }
-    const float4 a = *reinterpret_cast<const float4*>(w);
-    const float4 b = *reinterpret_cast<const float4*>(w + 4);
-    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    Vec16<T> o;
+// ---- CTA-pair variant -------------------------------------------------------------------------------------------------
+// Two CTAs on neighbouring SMs (a cluster of 2) compute one 256 x BN output tile with tcgen05.mma.cta_group::2.  Each CTA
+// stages ITS 128 rows of A and ITS BN/2 rows of B per k-step (plain per-CTA tiled loads whose transaction bytes are
+// counted on the leader's mbarrier), so a CTA moves (128 + BN/2) x 64 operands for a 128 x BN share of the output: a third
+// fewer L2-to-SM bytes per FLOP than the single-CTA kernel at BN = 256, and half the MMA instructions per FLOP.  The
+// leader's MMA thread issues for both; its commits arrive on the ring / accumulator barriers of both CTAs.  Each CTA's
+// epilogue drains the 128 accumulator rows that live in its own tensor memory.
+// Roles per CTA as in the kernel above.  The ring's `empty` barriers and the `acc_full` barriers exist in both CTAs
+// (signalled by the leader's commits); `full` and `acc_empty` are the leader's (the partner's loads and epilogue warps
+// signal them through shared::cluster addresses).
+template <int BN> struct PairCfg {
+  static constexpr int BNH = BN / 2;                 // rows of B staged by each CTA
+  static constexpr uint32_t B_BYTES = BNH * BK * 2;
+  static constexpr int STAGES = BN == 256 ? 6 : (BN == 192 ? 6 : 8);
+  static constexpr int ACC_STRIDE = BN == 192 ? 256 : BN;
+  static constexpr uint32_t TMEM_COLS = 2 * ACC_STRIDE;
+  static constexpr uint32_t STG_BYTES = 4 * 2048;
+  static constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + STG_BYTES + 1024 + 512;
+};
+constexpr int BM2 = 256;     // rows of a pair's tile
+
+template <typename T, int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_d, int use_tma_store, T* __restrict__ D, const T* __restrict__ bias, int M,
+                 int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, const FastDiv fd_tiles_m, int a3d,
+                 int b3d, int* __restrict__ error_flag) {
+  using Cfg = PairCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int BNH = Cfg::BNH;
+  constexpr uint32_t B_BYTES = Cfg::B_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  // the dynamic shared memory starts at the same offset in both CTAs, so the rounded-up tile addresses agree too
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint8_t* sStg = smem + STAGES * (A_BYTES + B_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES) + Cfg::STG_BYTES);
+  uint64_t* full = bars;                        // [STAGES] leader only: both CTAs' loads of a stage have landed
+  uint64_t* empty = bars + kMaxStages;          // [STAGES] each CTA: the pair's MMAs have read this stage
+  uint64_t* acc_full = bars + 2 * kMaxStages;   // [2] each CTA: accumulator complete
+  uint64_t* acc_empty = acc_full + 2;           // [2] leader only: drained by the 8 epilogue warps of the pair
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* issued_it = abort_flag + 1;
+  volatile int* consumed_it = abort_flag + 2;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();      // 0 = leader
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_k = (K + BK - 1) / BK;
+  const int tiles_m = (M + BM2 - 1) / BM2, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_units = num_tiles;      // whole tiles only: this kernel is chosen for outputs with many rounds of tiles
+  constexpr uint32_t kTmemCols = Cfg::TMEM_COLS;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+    *abort_flag = 0;
+    *issued_it = 0;
+    *consumed_it = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // the same warp of both CTAs allocates the pair's tensor memory
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();      // the partner's barriers exist before anything signals them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t full_leader = mapa_u32(smem_u32(&full[0]), 0);
+      int it = 0, st = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int unit = pair; unit < num_units && ok && !*abort_flag; unit += num_pairs) {
+        uint32_t tile_n_u, tile_m_u;
+        fd_divmod((uint32_t)unit, fd_tiles_m, &tile_n_u, &tile_m_u);
+        const int row_a = (int)tile_m_u * BM2 + (int)rank * BM;      // this CTA's rows of A (= rows of D)
+        const int row_b = (int)tile_n_u * BN + (int)rank * BNH;      // this CTA's rows of B (= columns of D)
+        const int k0 = 0, k1 = num_k;
+        for (int kt = k0; kt < k1; ++kt) {
+          if (!mbar_wait(&empty[st], ph ^ 1u)) { *abort_flag = 1; ok = false; break; }
+          const uint32_t fb = full_leader + (uint32_t)st * 8u;
+          if (rank == 0) mbar_expect_tx(&full[st], 2u * (A_BYTES + B_BYTES));
+          if (!a_mn) {
+            tma_pair_load_2d(sA + st * A_BYTES, &map_a, kt * BK, row_a, fb);
+          } else if (a3d) {
+            tma_pair_load_3d(sA + st * A_BYTES, &map_a, 0, kt * BK, row_a / 64, fb);
+          } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float x = v[j] + (bias ? Cvt<T>::to_f(bias[c + j]) : 0.f);
-      if (act == kActRelu) x = fmaxf(x, 0.f);
-      else if (act == kActGelu) x = gelu_erf(x);
-      o.v[j] = Cvt<T>::from_f(x);
+            for (int c = 0; c < BM / 64; ++c)
+              tma_pair_load_2d(sA + st * A_BYTES + c * kMnChunkBytes, &map_a, row_a + c * 64, kt * BK, fb);
+          }
+          if (!b_mn) {
+            tma_pair_load_2d(sB + st * B_BYTES, &map_b, kt * BK, row_b, fb);
+          } else if (b3d) {
+            tma_pair_load_3d(sB + st * B_BYTES, &map_b, 0, kt * BK, row_b / 64, fb);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BNH / 64; ++c)
+              tma_pair_load_2d(sB + st * B_BYTES + c * kMnChunkBytes, &map_b, row_b + c * 64, kt * BK, fb);
+          }
+          ++it;
+          if (++st == STAGES) { st = 0; ph ^= 1u; }
+        }
+      }
+      *issued_it = it;
     }
-    st16(D + (size_t)row * ldd + c, o);
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc(bf16, BN, a_mn, b_mn, BM2);
+      const uint64_t a_step = a_mn ? (16 * 128) >> 4 : 2, b_step = b_mn ? (16 * 128) >> 4 : 2;
+      const uint64_t adesc0 = a_mn ? make_desc_mn(smem_u32(sA)) : make_desc(smem_u32(sA));
+      const uint64_t bdesc0 = b_mn ? make_desc_mn(smem_u32(sB)) : make_desc(smem_u32(sB));
+      int it = 0, st = 0, t = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int unit = pair; unit < num_units && ok && !*abort_flag; unit += num_pairs, ++t) {
+        const int k0 = 0, k1 = num_k;
+        const int buf = t & 1;
+        if (!mbar_wait(&acc_empty[buf], (((uint32_t)t >> 1) & 1u) ^ 1u)) { *abort_flag = 1; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * Cfg::ACC_STRIDE);
+        for (int kt = k0; kt < k1; ++kt) {
+          if (!mbar_wait(&full[st], ph)) { *abort_flag = 1; ok = false; break; }
+          const uint64_t adesc = adesc0 + (uint64_t)(st * (int)(A_BYTES >> 4));
+          const uint64_t bdesc = bdesc0 + (uint64_t)(st * (int)(B_BYTES >> 4));
+          umma_pair(tmem_d, adesc, bdesc, idesc, kt > k0 ? 1u : 0u);
+#pragma unroll
+          for (int k = 1; k < BK / UMMA_K; ++k)
+            umma_pair(tmem_d, adesc + a_step * (uint64_t)k, bdesc + b_step * (uint64_t)k, idesc, 1u);
+          umma_pair_commit(&empty[st], 3);      // the stage is free in both CTAs once these MMAs have read it
+          ++it;
+          if (++st == STAGES) { st = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        umma_pair_commit(&acc_full[buf], 3);    // both CTAs' epilogues: every MMA of this tile has completed
+      }
+      *consumed_it = it;
+    }
+  } else {
+    const int q = warp & 3;
+    uint8_t* stg = sStg + q * 2048;
+    const uint32_t acc_empty_leader = mapa_u32(smem_u32(&acc_empty[0]), 0);
+    int t = 0;
+    for (int unit = pair; unit < num_units; unit += num_pairs, ++t) {
+      uint32_t tile_n_u, tile_m_u;
+      fd_divmod((uint32_t)unit, fd_tiles_m, &tile_n_u, &tile_m_u);
+      const int buf = t & 1;
+      const bool ready = mbar_wait(&acc_full[buf], ((uint32_t)t >> 1) & 1u);
+      if (!ready) *abort_flag = 1;
+      if (!ready || *abort_flag) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::ACC_STRIDE);
+      drain_quarter<T, BN>(taddr, stg, &map_d, use_tma_store, D, bias, M, N, ldd, act,
+                           (int)tile_m_u * BM2 + (int)rank * BM + q * 32, (int)tile_n_u * BN, lane);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader + (uint32_t)buf * 8u);
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  // Both CTAs have left their loops: nothing new is issued.  Neither may release its shared or tensor memory while the
+  // other could still signal or read it, hence the cluster-wide barriers around the clean-up.
+  cluster_sync_all();
+  if (threadIdx.x == 0 && *abort_flag && error_flag) atomicExch(error_flag, 1);
+  if (threadIdx.x == 0 && rank == 0) {
+    // If either CTA gave up, wait (bounded) for the loads that were issued but never consumed: every stage completes
+    // on the leader's `full` barrier only when both halves have landed.
+    const int peer_abort = (int)ld_cluster_u32(mapa_u32(smem_u32((const void*)abort_flag), 1));
+    if (*abort_flag || peer_abort) {
+      int issued = *issued_it;
+      const int peer_issued = (int)ld_cluster_u32(mapa_u32(smem_u32((const void*)issued_it), 1));
+      if (peer_issued < issued) issued = peer_issued;      // a stage completes only if both CTAs loaded it
+      for (int it = *consumed_it; it < issued; ++it)
+        if (!mbar_wait(&full[it % STAGES], (uint32_t)(it / STAGES) & 1u)) break;
+    }
+  }
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -408,6 +665,36 @@ static int make_map_store(CUtensorMap* map, const void* base, int bf16, int64_t 
   return rc == CUDA_SUCCESS ? 0 : -11;
 }
 
+// Stream-K plan for `tiles` output tiles of `num_k` k-steps on a grid of G CTAs: whole rounds of tiles are computed
+// tile by tile; the tiles of a last, partial round (or all tiles, when there are fewer than CTAs) become the stream-K
+// region when cutting their k-steps evenly over the CTAs is shorter than one more round.  A tile is cut into at most
+// 1 + kMaxOthers pieces and a piece is at least 6 k-steps long.
+struct SkPlan {
+  int full_tiles, sk_tiles, sk_ctas;
+};
+static SkPlan plan_streamk(int tiles, int num_k, int G, bool allowed) {
+  SkPlan p = {tiles, 0, 0};
+  const int rem = tiles % G;
+  if (!allowed || num_k < 8 || rem == 0) return p;
+  const long total = (long)rem * num_k;
+  int min_per = (num_k + 5) / 6;
+  if (min_per < 6) min_per = 6;
+  long ctas = total / min_per;
+  if (ctas > G) ctas = G;
+  if (ctas < 2) return p;
+  const long per = (total + ctas - 1) / ctas;
+  if (per + 4 >= num_k) return p;          // no shorter than one more round of whole tiles (4: the cost of combining)
+  p.full_tiles = tiles - rem;
+  p.sk_tiles = rem;
+  p.sk_ctas = (int)ctas;
+  return p;
+}
+
+// Workspace of the stream-K pieces: [4 counters per tile of a round][2 slots of 128 x 256 floats per CTA].  It must be
+// zero when first used; the kernels leave the counters at zero.
+constexpr size_t kSkCounterBytes = 4096 * sizeof(int);
+static size_t sk_workspace_bytes() { return kSkCounterBytes + (size_t)sm_count() * 2 * BM * 256 * sizeof(float); }
+
 template <typename T, int BN>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, int use_tma_store, void* D,
                        const void* bias, int M, int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, float* ws, int a3d,
@@ -422,50 +709,107 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   const int tiles_m = (M + BM - 1) / BM;
   const int tiles = tiles_m * ((N + BN - 1) / BN);
   const int num_k = (K + BK - 1) / BK;
-  // Split-K (needs the workspace) when the output has too few tiles to occupy the SMs.  The kernel can also split only
-  // the tiles of a last, partial round (full_tiles > 0); measured on N = 768 outputs of 8192 rows that was slower than
-  // leaving the round partial (the fp32 reductions and the two helper launches cost more than the idle SMs), so the
-  // host does not select it.
-  int full_tiles = tiles, ksplit = 1;
   const int sms = sm_count();
-  if (ws != nullptr && (N % 8) == 0 && (ldd % 8) == 0 && num_k >= 8) {
-    if (tiles * 10 < sms * 7) full_tiles = 0;
-    if (full_tiles < tiles) {
-      ksplit = sms / (tiles - full_tiles);
-      if (ksplit > num_k / 4) ksplit = num_k / 4;
-      if (ksplit < 2) { ksplit = 1; full_tiles = tiles; }
-    }
-  }
-  int ksteps_per = (num_k + ksplit - 1) / ksplit;
-  ksplit = (num_k + ksteps_per - 1) / ksteps_per;
-  if (ksplit < 2) { ksplit = 1; full_tiles = tiles; ksteps_per = num_k; }
-  const int rem_tiles = tiles - full_tiles;
-  float* kws = rem_tiles > 0 ? ws : nullptr;
-  if (kws) gemm_splitk_tiles_kernel<T, false><<<rem_tiles, 256, 0, st>>>(kws, nullptr, nullptr, M, N, ldd, act, BN, tiles_m, full_tiles);
-  const long units = (long)full_tiles + (long)rem_tiles * ksplit;
-  const int grid = units < sms ? (int)units : sms;
+  const SkPlan plan = plan_streamk(tiles, num_k, sms, ws != nullptr && sms <= 1024);
+  int grid = tiles < sms ? tiles : sms;
+  if (plan.sk_tiles > 0 && plan.full_tiles == 0) grid = plan.sk_ctas > tiles ? plan.sk_ctas : tiles;
+  if (plan.sk_tiles > 0 && plan.full_tiles > 0) grid = sms;
+  if (grid > sms) grid = sms;
+  int* cnt = reinterpret_cast<int*>(ws);
+  float* slots = ws ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + kSkCounterBytes) : nullptr;
   gemm_tn_kernel<T, BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ma, mb, md, use_tma_store, (T*)D, (const T*)bias, M, N, K, ldd,
-                                                                     act, bf16, a_mn, b_mn, make_fastdiv((uint32_t)tiles_m), ksplit,
-                                                                     ksteps_per, full_tiles,
-                                                                     make_fastdiv((uint32_t)(rem_tiles > 0 ? rem_tiles : 1)), kws, a3d,
+                                                                     act, bf16, a_mn, b_mn, make_fastdiv((uint32_t)tiles_m),
+                                                                     plan.full_tiles, plan.sk_tiles, plan.sk_ctas, slots, cnt, a3d,
                                                                      b3d, error_flag);
-  if (kws) gemm_splitk_tiles_kernel<T, true><<<rem_tiles, 256, 0, st>>>(kws, (const T*)bias, (T*)D, M, N, ldd, act, BN, tiles_m, full_tiles);
   return (int)cudaGetLastError();
 }
 
-// Tile width: the widest tile that still gives every SM work, or the widest tile with split-K when the output has too
-// few tiles for the SMs anyway; narrow outputs take the narrow tile.  (A 192-wide tile is compiled but not selected: it
-// measured no faster than 128 or 256 on the shapes where it divides N.)
+// Tile width of the single-CTA kernel: narrow outputs take the narrow tile; otherwise the width with the lowest
+// column-tiles x (width + fixed cost per tile), which avoids a mostly empty last column tile (N = 384 -> 2 x 192).  Rounds
+// of tiles that do not fill the grid are handled by the stream-K plan, not by narrower tiles.
 static int pick_bn(int M, int N) {
-  const long tm = (M + BM - 1) / BM;
   if (N <= 64) return 64;
   if (N <= 128) return 128;
-  const long tiles256 = tm * ((N + 255) / 256);
-  if (tiles256 >= sm_count()) return 256;
-  if (tiles256 * 10 < (long)sm_count() * 7) return 256;      // split-K fills the machine
-  return 128;
+  int best = 256;
+  long best_cost = 0;
+  for (int bn = 256; bn >= 128; bn -= 64) {
+    const long cost = (long)((N + bn - 1) / bn) * (bn + 32);
+    if (bn == 256 || cost < best_cost) { best = bn; best_cost = cost; }
+  }
+  return best;
 }
 
+// How many CTA pairs of the pair kernel can be resident at once (asked from the runtime once per tile width; the
+// persistent grid is never larger).
+template <typename T, int BN>
+static int pair_capacity() {
+  static int cap = 0;
+  if (cap) return cap;
+  using Cfg = PairCfg<BN>;
+  if (cudaFuncSetAttribute(gemm_pair_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) {
+    cudaGetLastError();
+    return cap = -1;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * sm_count());
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<T, BN>, &cfg) != cudaSuccess || n < 1) {
+    cudaGetLastError();
+    return cap = -1;
+  }
+  const int half = sm_count() / 2;
+  return cap = n < half ? n : half;
+}
+
+template <typename T, int BN>
+static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, int use_tma_store, void* D,
+                            const void* bias, int M, int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, float* ws,
+                            int a3d, int b3d, int* error_flag, cudaStream_t st) {
+  using Cfg = PairCfg<BN>;
+  const int pairs = pair_capacity<T, BN>();
+  if (pairs < 1) return -20;
+  const int tiles_m = (M + BM2 - 1) / BM2;
+  const int tiles = tiles_m * ((N + BN - 1) / BN);
+  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  gemm_pair_kernel<T, BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ma, mb, md, use_tma_store, (T*)D, (const T*)bias, M, N, K, ldd,
+                                                                       act, bf16, a_mn, b_mn, make_fastdiv((uint32_t)tiles_m), a3d,
+                                                                       b3d, error_flag);
+  return (int)cudaGetLastError();
+}
+
+
+// Tile width of the pair kernel for an M x N x K product, or 0 for the single-CTA kernel.  Measured: the pair kernel
+// wins where the operands do not stay in L2 and the grid runs many rounds of tiles (8192^3: 1.25x the single-CTA kernel,
+// 1.36x the library); on products that fit in L2 its longer load-to-MMA path (the partner's loads and the commits cross
+// to the other SM) makes it slower, so those stay on the single-CTA kernel.  Width: among 256, 192 (K-major B only: each
+// CTA would hold one and a half 64-column chunks of an MN-major B) and 128 the lowest rounds x (width + fixed cost).
+static int pick_pair_bn(int M, int N, int K, int b_mn) {
+  if (g_gemm_variant == 1 || M <= BM || N <= 64) return 0;
+  const long pairs = sm_count() / 2, tm = (M + BM2 - 1) / BM2;
+  if (g_gemm_variant != 2) {
+    const double operand_bytes = ((double)M + (double)N) * (double)K * 2.0;
+    if (operand_bytes < 96e6 || tm * ((N + 255) / 256) < 6 * pairs) return 0;
+  }
+  if (N <= 128) return 128;
+  int best = 0;
+  long best_cost = 0;
+  for (int bn = 256; bn >= 128; bn -= 64) {
+    if (bn == 192 && b_mn) continue;
+    const long units = tm * ((N + bn - 1) / bn);
+    const long cost = ((units + pairs - 1) / pairs) * (bn + 32);
+    if (!best || cost < best_cost) { best = bn; best_cost = cost; }
+  }
+  return best;
+}
 }  // namespace mxb
 
 using namespace mxb;
@@ -481,14 +825,16 @@ static int gemm_run(int dtype, const void* A, const void* B, void* D, const void
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A % 16) || ((uintptr_t)B % 16) || ((uintptr_t)D % 16)) return -3;
   if (lda < (a_mn ? M : K) || ldb < (b_mn ? N : K) || ldd < N) return -3;
   const int bf16 = dtype == kBF16;
-  const int bn = pick_bn(M, N);
+  const int pbn = pick_pair_bn(M, N, K, b_mn);
+  const int bn = pbn ? pbn : pick_bn(M, N);
+  const int b_rows = pbn ? pbn / 2 : bn;          // rows of B one CTA stages per k-step
   CUtensorMap ma, mb;
   const int a3d = a_mn && (M % 64) == 0, b3d = b_mn && (N % 64) == 0;
   int rc = a3d ? make_map_mn3(&ma, A, bf16, K, M, lda, BM / 64)
                : (a_mn ? make_map_mn(&ma, A, bf16, K, M, lda) : make_map(&ma, A, bf16, M, K, lda, BM));
   if (rc) return rc;
-  rc = b3d ? make_map_mn3(&mb, B, bf16, K, N, ldb, bn / 64)
-           : (b_mn ? make_map_mn(&mb, B, bf16, K, N, ldb) : make_map(&mb, B, bf16, N, K, ldb, bn));
+  rc = b3d ? make_map_mn3(&mb, B, bf16, K, N, ldb, b_rows / 64)
+           : (b_mn ? make_map_mn(&mb, B, bf16, K, N, ldb) : make_map(&mb, B, bf16, N, K, ldb, b_rows));
   if (rc) return rc;
   // the epilogue stores through the copy engine when D meets a tensor map's rules (16-byte row pitch); otherwise with
   // per-thread stores
@@ -499,35 +845,48 @@ static int gemm_run(int dtype, const void* A, const void* B, void* D, const void
     if (rc) return rc;
   }
   cudaStream_t st = (cudaStream_t)stream;
-#define MXB_GEMM(T)                                                                                                        \
-  (bn == 256 ? launch_gemm<T, 256>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, ws, a3d, b3d, error_flag, st)  \
-   : bn == 192 ? launch_gemm<T, 192>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, ws, a3d, b3d, error_flag, st) \
-   : bn == 128 ? launch_gemm<T, 128>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, ws, a3d, b3d, error_flag, st) \
-               : launch_gemm<T, 64>(ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, ws, a3d, b3d, error_flag, st))
+#define MXB_GEMM_ARGS ma, mb, md, use_tma_store, D, bias, M, N, K, ldd, act, bf16, a_mn, b_mn, ws, a3d, b3d, error_flag, st
+  if (pbn) {
+#define MXB_GEMM_PAIR(T) \
+  (pbn == 256 ? launch_gemm_pair<T, 256>(MXB_GEMM_ARGS) : pbn == 192 ? launch_gemm_pair<T, 192>(MXB_GEMM_ARGS) : launch_gemm_pair<T, 128>(MXB_GEMM_ARGS))
+    return bf16 ? MXB_GEMM_PAIR(__nv_bfloat16) : MXB_GEMM_PAIR(__half);
+#undef MXB_GEMM_PAIR
+  }
+#define MXB_GEMM(T)                                                                                 \
+  (bn == 256 ? launch_gemm<T, 256>(MXB_GEMM_ARGS) : bn == 192 ? launch_gemm<T, 192>(MXB_GEMM_ARGS)   \
+   : bn == 128 ? launch_gemm<T, 128>(MXB_GEMM_ARGS) : launch_gemm<T, 64>(MXB_GEMM_ARGS))
   return bf16 ? MXB_GEMM(__nv_bfloat16) : MXB_GEMM(__half);
 #undef MXB_GEMM
+#undef MXB_GEMM_ARGS
 }
+
+// Kernel selection for later calls: 0 = per shape (the default), 1 = single-CTA kernel only, 2 = the CTA-pair kernel
+// wherever it applies.  For benchmarks and tests that compare the two.
+MXB_EXPORT void mxb_gemm_set_variant(int v) { g_gemm_variant = v; }
 
 MXB_EXPORT int mxb_gemm(int dtype, const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda,
                         int ldb, int ldd, int a_mn, int b_mn, int act, int* error_flag, void* stream) {
   return gemm_run(dtype, A, B, D, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, act, nullptr, error_flag, stream);
 }
 
-// The same product with an fp32 workspace of M*N floats: outputs with too few tiles for the SMs (a weight gradient with
-// a long contraction) are then computed as split-K partial products added into the workspace.
+// Bytes of the stream-K workspace that mxb_gemm_ws takes: allocate once per device and stream, fill with zeros once.
+MXB_EXPORT uint64_t mxb_gemm_workspace_bytes() { return (uint64_t)sk_workspace_bytes(); }
+
+// The same product with the stream-K workspace: a last round of tiles that would leave SMs idle (or an output with
+// fewer tiles than SMs, such as a weight gradient with a long contraction) is cut evenly over the CTAs by k-steps; the
+// pieces of a tile are combined by the CTA whose piece finishes last.  Launches that use one workspace must not overlap.
 MXB_EXPORT int mxb_gemm_ws(int dtype, const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda,
                            int ldb, int ldd, int a_mn, int b_mn, int act, float* workspace, int* error_flag, void* stream) {
   if (workspace && ((uintptr_t)workspace % 16)) return -3;
   return gemm_run(dtype, A, B, D, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, act, workspace, error_flag, stream);
 }
 
-// Whether mxb_gemm_ws would split the contraction of this shape (so that callers allocate the workspace only then).
+// Whether mxb_gemm_ws would cut this product by k-steps (for reports; callers may always pass the workspace).
 MXB_EXPORT int mxb_gemm_wants_workspace(int M, int N, int K) {
+  if (pick_pair_bn(M, N, K, 0)) return 0;
   const int bn = pick_bn(M, N);
   const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-  const int num_k = (K + BK - 1) / BK;
-  if ((N % 8) != 0 || num_k < 8) return 0;
-  return tiles * 10 < sm_count() * 7 ? 1 : 0;
+  return plan_streamk(tiles, (K + BK - 1) / BK, sm_count(), true).sk_tiles > 0 ? 1 : 0;
 }
 
 // D[M,N] = act(A[M,K] * B[N,K]^T + bias): both operands K-major.

@@ -112,6 +112,65 @@ __device__ __forceinline__ void tmem_wait_ld32(uint32_t* r) {
       :: "memory");
 }
 
+// ---- CTA pairs (cluster of two CTAs on neighbouring SMs driving one tcgen05.mma.cta_group::2) -----------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the location `saddr` (a shared::cta address of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ uint32_t ld_cluster_u32(uint32_t cluster_addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+// all threads of both CTAs; not the .aligned form, so lanes of a warp may arrive from different code paths
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+// arrive on an mbarrier of any CTA of the cluster, given by its shared::cluster address
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Tiled loads of a CTA pair: the data lands in THIS CTA's shared memory, the transaction bytes are counted on the
+// mbarrier at `bar_cluster_addr`, which may belong to the partner CTA (the pair's leader collects both halves of a
+// stage on one barrier).  Plain per-CTA loads: every CTA fetches its own half, nothing is replicated across CTAs.
+__device__ __forceinline__ void tma_pair_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_pair_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_pair_load_4d(void* dst, const CUtensorMap* map, int x, int y, int z, int w,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar_cluster_addr) : "memory");
+}
+// One MMA of the pair: M = 256 (128 rows from each CTA's A tile), N columns (half of the B rows from each CTA); the
+// accumulator rows of each CTA stay in that CTA's tensor memory.  Issued by one thread of the leader CTA.
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives (once the pair's earlier MMAs have completed) on the mbarrier at the same shared-memory offset in every CTA
+// of `cta_mask`: this is a barrier arrival sent to both CTAs, not a data copy.
+__device__ __forceinline__ void umma_pair_commit(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(cta_mask) : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }

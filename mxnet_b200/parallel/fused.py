@@ -20,6 +20,7 @@ bounded; a time-out is reported through a status word that the next ``step`` tur
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 
 import numpy as np
 import torch
@@ -36,6 +37,16 @@ _ERRORS = {1: 'waiting for the other ranks to finish their backward pass',
            4: 'waiting for the other ranks to publish their parameter norms'}
 
 
+_live = weakref.WeakSet()          # FusedStep objects whose status word `check_all` looks at
+
+
+def check_all():
+    """Wait for the launched steps of every live ``FusedStep`` of this process and raise if one of them recorded a
+    device-side wait time-out (called by ``nd.waitall`` and at interpreter exit, so a failed last step is not silent)."""
+    for fs in list(_live):
+        fs.check_status(wait=True)
+
+
 class StepParams(C.Structure):
     _fields_ = [('grads', C.c_void_p * _MAXR), ('weights', C.c_void_p * _MAXR), ('ctrl', C.c_void_p * _MAXR),
                 ('rank', C.c_int), ('nranks', C.c_int), ('total', C.c_int64), ('shard_begin', C.c_int64),
@@ -46,7 +57,8 @@ class StepParams(C.Structure):
                 ('scale_window', C.c_float), ('scale_max', C.c_float), ('mode', C.c_int),
                 ('timeout_ns', C.c_ulonglong), ('var', C.c_void_p), ('beta1', C.c_float), ('beta2', C.c_float),
                 ('epsilon', C.c_float), ('coef1', C.c_float), ('coef2', C.c_float), ('lower_bound', C.c_float),
-                ('upper_bound', C.c_float), ('norm_acc', C.c_void_p), ('norm_in', C.c_void_p * _MAXR)]
+                ('upper_bound', C.c_float), ('norm_acc', C.c_void_p), ('norm_in', C.c_void_p * _MAXR),
+                ('seg_skip', C.c_void_p), ('seg_coef', C.c_void_p)]
 
 
 class _DevBuf(object):
@@ -125,7 +137,23 @@ class FusedStep(object):
         self._norm_off = (L.mxb_step_ctrl_bytes() + 255) // 256 * 256
         self.ctrl_bytes = (self._norm_off + _MAXR * 2 * self.nseg * 4 + 255) // 256 * 256
         arena_bytes = self.total * self.esize
-        self.slab_bytes = self.ctrl_bytes + 2 * arena_bytes
+        # The rank's fp32 state (master weights, first and second moment of its shard) sits in the same IPC-visible slab,
+        # so that ONE rank can collect every shard with peer copies when it writes a checkpoint: saving optimizer states is
+        # a local call in the reference (python/mxnet/gluon/trainer.py:489-516), not a collective.
+        from ..optimizer import optimizer as _opt
+        kind = type(optimizer)
+        self.mode = {_opt.NAG: MODE_NAG, _opt.Adam: MODE_ADAM, _opt.AdamW: MODE_ADAMW, _opt.LAMB: MODE_LAMB}.get(kind, MODE_SGD)
+        two_moments = self.mode in (MODE_ADAM, MODE_ADAMW, MODE_LAMB)
+        need_mom = two_moments or getattr(optimizer, 'momentum', 0.0) != 0.0
+        shard_bytes = (shard * 4 + 255) // 256 * 256
+        self._state_off = {}
+        cur_off = self.ctrl_bytes + 2 * arena_bytes
+        cur_off = (cur_off + 255) // 256 * 256
+        for name, wanted in (('master', self.dtype != torch.float32), ('mom', need_mom), ('var', two_moments)):
+            if wanted:
+                self._state_off[name] = cur_off
+                cur_off += shard_bytes
+        self.slab_bytes = cur_off
         ptr = C.c_void_p()
         rc = L.mxb_dev_alloc(C.byref(ptr), self.slab_bytes)
         if rc != 0:
@@ -171,22 +199,23 @@ class FusedStep(object):
         # ---- shard-local state ---------------------------------------------------------------------
         n_shard = self.shard_end - self.shard_begin
         self.gred = torch.zeros(n_shard, dtype=torch.float32, device=self.device)
-        self.master = None
-        if self.dtype != torch.float32:
-            self.master = self.weights[self.shard_begin:self.shard_end].float()
-        from ..optimizer import optimizer as _opt
-        kind = type(optimizer)
-        self.mode = {_opt.NAG: MODE_NAG, _opt.Adam: MODE_ADAM, _opt.AdamW: MODE_ADAMW, _opt.LAMB: MODE_LAMB}.get(kind, MODE_SGD)
-        two_moments = self.mode in (MODE_ADAM, MODE_ADAMW, MODE_LAMB)
-        need_mom = two_moments or getattr(optimizer, 'momentum', 0.0) != 0.0
-        self.mom = torch.zeros(n_shard, dtype=torch.float32, device=self.device) if need_mom else None
-        self.var = torch.zeros(n_shard, dtype=torch.float32, device=self.device) if two_moments else None
+
+        def state(name):
+            off = self._state_off.get(name)
+            return self._blob(off, n_shard * 4).view(torch.float32) if off is not None else None
+        self.master, self.mom, self.var = state('master'), state('mom'), state('var')     # the slab starts zeroed
+        if self.master is not None:
+            self.master.copy_(self.weights[self.shard_begin:self.shard_end])
         self.norm_acc = torch.zeros(2 * self.nseg, dtype=torch.float32, device=self.device)
         seg_end = np.asarray([o + (s + vec - 1) // vec * vec for o, s in zip(offs, self.sizes)], dtype=np.int64)
         seg_end[-1] = self.total
         self.seg_end = torch.from_numpy(seg_end).to(self.device)
-        self.lr_mult = torch.tensor([p.lr_mult for p in self.params], dtype=torch.float32, device=self.device)
-        self.wd_mult = torch.tensor([p.wd_mult for p in self.params], dtype=torch.float32, device=self.device)
+        self._mults = ([float(p.lr_mult) for p in self.params], [float(p.wd_mult) for p in self.params])
+        self.lr_mult = torch.tensor(self._mults[0], dtype=torch.float32, device=self.device)
+        self.wd_mult = torch.tensor(self._mults[1], dtype=torch.float32, device=self.device)
+        self.seg_skip = torch.zeros(self.nseg, dtype=torch.int32, device=self.device)
+        self.seg_coef = torch.ones(2 * self.nseg, dtype=torch.float32, device=self.device)
+        self._skip_set = False
         self.step_no = 0
         self.timeout_ms = int(env.get('MXNET_KVSTORE_WAIT_MS'))
         off_status = L.mxb_step_ctrl_offset(0)
@@ -204,6 +233,7 @@ class FusedStep(object):
         if self.nranks > 1:
             torch.cuda.synchronize(self.device)
             dist.barrier()
+        _live.add(self)
 
     def _blob(self, byte_offset, nbytes):
         """A uint8 tensor over ``nbytes`` of the slab starting at ``byte_offset`` (its own storage object)."""
@@ -246,21 +276,33 @@ class FusedStep(object):
         if self.var is not None:
             sp.var = self.var.data_ptr()
             sp.beta1, sp.beta2, sp.epsilon = float(opt.beta1), float(opt.beta2), float(opt.epsilon)
-            t = opt._index_update_count.get(self.param_ids[0], opt.begin_num_update) if self.param_ids else 1
-            t = max(int(t), 1)
+            # every parameter keeps its own update count (a parameter skipped for a stale gradient falls behind); the
+            # bias corrections travel as scalars while the counts agree and as a per-parameter table otherwise
+            counts = [max(int(opt._index_update_count.get(i, opt.begin_num_update)), 1) for i in self.param_ids] or [1]
             correct = getattr(opt, 'bias_correction', True) if mode == MODE_LAMB else getattr(opt, 'correct_bias', True)
+            t = counts[0]
             sp.coef1 = 1.0 - opt.beta1 ** t if correct else 1.0
             sp.coef2 = 1.0 - opt.beta2 ** t if correct else 1.0
+            if correct and any(c != t for c in counts):
+                table = [1.0 - opt.beta1 ** c for c in counts] + [1.0 - opt.beta2 ** c for c in counts]
+                self.seg_coef.copy_(torch.tensor(table, dtype=torch.float32))
+                sp.seg_coef = self.seg_coef.data_ptr()
             lo, hi = getattr(opt, 'lower_bound', None), getattr(opt, 'upper_bound', None)
             sp.lower_bound = -1.0 if lo is None else float(lo)
             sp.upper_bound = -1.0 if hi is None else float(hi)
         sp.norm_acc = self.norm_acc.data_ptr()
         for r in range(self.nranks):
             sp.norm_in[r] = self.peer_base[r] + self._norm_off
+        if self._skip_set:
+            sp.seg_skip = self.seg_skip.data_ptr()
         return sp
 
-    def _check_status(self):
+    def check_status(self, wait=False):
+        """Raise if a launched step recorded a wait time-out.  ``wait=False`` only looks at steps that have finished
+        (what the next ``step`` does); ``wait=True`` first waits for the last launched step."""
         ev = self._status_event
+        if ev is not None and wait:
+            ev.synchronize()
         if ev is not None and ev.query():
             self._status_event = None
             code = int(self._status_host[0])
@@ -270,14 +312,38 @@ class FusedStep(object):
                 raise MXNetError('fused optimizer step %d timed out after %d ms while %s (rank %d of %d)' % (
                     step, self.timeout_ms, _ERRORS.get(code, 'waiting'), self.rank, self.nranks))
 
-    def _launch(self, rescale, mode, use_ls):
+    _check_status = check_status
+
+    def _refresh_multipliers(self):
+        lr_m, wd_m = [float(p.lr_mult) for p in self.params], [float(p.wd_mult) for p in self.params]
+        if lr_m != self._mults[0]:
+            self.lr_mult.copy_(torch.tensor(lr_m, dtype=torch.float32))
+        if wd_m != self._mults[1]:
+            self.wd_mult.copy_(torch.tensor(wd_m, dtype=torch.float32))
+        self._mults = (lr_m, wd_m)
+
+    def _set_stale(self, stale):
+        """``stale``: positions (in ``self.params``) of parameters whose gradient was not refreshed; they are left out of
+        this step (``ignore_stale_grad=True``, python/mxnet/gluon/trainer.py:437-458)."""
+        if stale:
+            flags = torch.zeros(self.nseg, dtype=torch.int32)
+            flags[list(stale)] = 1
+            self.seg_skip.copy_(flags)
+            self._skip_set = True
+        else:
+            self._skip_set = False
+
+    def _launch(self, rescale, mode, use_ls, stale=()):
         from ..ops import cuda
         L = _lib()
         self._check_status()
         self.step_no += 1
         opt = self.optimizer
+        self._set_stale(stale if mode != MODE_PLAIN else ())
         if mode != MODE_PLAIN:
-            opt._update_count(self.param_ids)
+            self._refresh_multipliers()
+            skip = set(stale)
+            opt._update_count([i for k, i in enumerate(self.param_ids) if k not in skip])
         lr = float(opt.learning_rate)
         sp = self._params(float(rescale), mode, use_ls, lr, float(opt.wd))
         st = cuda.stream_ptr(self.device)
@@ -298,8 +364,10 @@ class FusedStep(object):
         the kernel divides by the device scale, 2 when the host already folded 1/scale into ``rescale``."""
         if scaler is None:
             return 0
+        unscaled = getattr(scaler, '_grads_unscaled', False)      # amp.unscale() already divided the gradients
+        scaler._grads_unscaled = False
         if self._scaler_attached is scaler:
-            return 1
+            return 2 if unscaled else 1
         self.scale_state[0] = float(scaler._loss_scale)
         self.scale_state[1] = float(scaler._unskipped)
         scaler._device_state = self.scale_state
@@ -310,20 +378,20 @@ class FusedStep(object):
         if scaler is not None and self._scaler_attached is not scaler:
             self._attach_scaler(scaler)
 
-    def step(self, rescale, scaler=None):
+    def step(self, rescale, scaler=None, stale=()):
         use_ls = self._attach_scaler(scaler)
-        self._launch(rescale, self.mode, use_ls)
+        self._launch(rescale, self.mode, use_ls, stale)
         autograd.mark_grads_consumed(self._data_arrays)
 
     def allreduce_only(self):
         """Sum the gradient arenas of all ranks in place (``Trainer.allreduce_grads``)."""
         self._launch(1.0, MODE_PLAIN, 0)
 
-    def update_only(self, rescale, scaler=None):
+    def update_only(self, rescale, scaler=None, stale=()):
         """Update after ``allreduce_only``: every arena already holds the sum, so the reduction over
         ranks is compensated by 1/nranks."""
         use_ls = self._attach_scaler(scaler)
-        self._launch(rescale / self.nranks, self.mode, use_ls)
+        self._launch(rescale / self.nranks, self.mode, use_ls, stale)
         autograd.mark_grads_consumed(self._data_arrays)
 
     def wait_probe(self, timeout_ms=50):
@@ -342,22 +410,35 @@ class FusedStep(object):
         return code
 
     # ---- optimizer state exchange with the generic Updater (checkpoints) ---------------------------------
-    def _gather(self, shard):
+    def _gather(self, name):
+        """The whole fp32 state vector `name`, collected by THIS rank alone: its own shard plus peer copies
+        (``cudaMemcpyAsync`` from the other ranks' slabs).  No other rank takes part, so `if rank == 0: save_states(...)`
+        works.  The caller runs between steps: the last step's update kernel returns only after every rank has finished
+        writing its state, and no rank can start the next update before this rank launches its next step."""
+        shard = getattr(self, name)
+        if shard is None:
+            return None
         if self.nranks == 1:
             return shard
-        parts = [torch.empty_like(shard) for _ in range(self.nranks)]
-        import torch.distributed as tdist
-        tdist.all_gather(parts, shard)
-        return torch.cat(parts)
+        from ..ops import cuda
+        L = _lib()
+        n = shard.numel()
+        out = torch.empty(n * self.nranks, dtype=torch.float32, device=self.device)
+        st = cuda.stream_ptr(self.device)
+        for r in range(self.nranks):
+            rc = L.mxb_memcpy_d2d(C.c_void_p(out.data_ptr() + r * n * 4), C.c_void_p(self.peer_base[r] + self._state_off[name]),
+                                  n * 4, st)
+            if rc != 0:
+                raise MXNetError('peer copy of optimizer state from rank %d failed: %s' % (r, L.mxb_error_string(rc).decode()))
+        return out
 
     def export_states(self, updater):
         """Write the sharded state into ``updater.states`` in the layout the generic optimizers use:
         ``momentum`` (SGD/NAG) or ``(mean, var)`` (Adam/AdamW/LAMB), wrapped as ``(master, inner)`` for
         multi-precision."""
         from ..ndarray.ndarray import NDArray
-        master = self._gather(self.master) if self.master is not None else None
-        mom = self._gather(self.mom) if self.mom is not None else None
-        var = self._gather(self.var) if self.var is not None else None
+        self.check_status(wait=True)
+        master, mom, var = self._gather('master'), self._gather('mom'), self._gather('var')
         for p, idx, off, n in zip(self.params, self.param_ids, self.offsets, self.sizes):
             shape = p._data[self.ctx]._data.shape
 

@@ -227,10 +227,38 @@ def test_tcgen05_gemm_operand_layouts(a_mn, b_mn, M, N, K, dtype):
     _close(d, ref, *tol)
 
 
+@pytest.mark.parametrize('a_mn,b_mn', [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize('M,N,K', [(256, 256, 64), (8192, 768, 768), (304, 200, 136), (136, 72, 264), (1000, 1000, 520),
+                                   (4096, 192, 1024), (640, 384, 4096)])
+def test_tcgen05_gemm_cta_pair_kernel(a_mn, b_mn, M, N, K):
+    """The CTA-pair kernel (256-row tiles, two SMs per tile) against an fp32 product and against the single-CTA kernel,
+    on shapes with partial row tiles, partial column tiles and a partner CTA whose rows lie entirely outside."""
+    from mxnet_b200.ops.cuda import gemm_ops
+    torch.manual_seed(12)
+    dtype = torch.float16
+    a = (torch.randn(M, K, device=_dev()) / 4).to(dtype)
+    b = (torch.randn(N, K, device=_dev()) / 4).to(dtype)
+    bias = torch.randn(N, device=_dev()).to(dtype)
+    ref = a.float() @ b.float().t() + bias.float()
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    try:
+        gemm_ops.set_variant(1)
+        single = gemm_ops.gemm(a_in, b_in, a_mn, b_mn, bias)
+        gemm_ops.set_variant(2)
+        pair = gemm_ops.gemm(a_in, b_in, a_mn, b_mn, bias)
+    finally:
+        gemm_ops.set_variant(0)
+    gemm_ops.check_errors()
+    _close(pair, ref, 1e-2, 2e-3 * K ** 0.5)
+    _close(pair, single, 2e-3, 1e-3 * K ** 0.5)       # same products in the same order per k-step; split-K may differ
+
+
 @pytest.mark.parametrize('M,N,K', [(768, 768, 8192), (256, 136, 4096), (128, 64, 2048)])
 @pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
 def test_tcgen05_gemm_split_k_weight_gradient_shapes(M, N, K, dtype):
-    """Few output tiles and a long contraction: the kernel splits K over the SMs through an fp32 workspace."""
+    """Few output tiles and a long contraction: the k-steps are cut evenly over the SMs (stream-K), twice in a row so that
+    the second launch meets the piece counters the first one left behind."""
     from mxnet_b200.ops import cuda
     from mxnet_b200.ops.cuda import gemm_ops
     assert cuda.lib().mxb_gemm_wants_workspace(M, N, K) == 1
@@ -238,11 +266,30 @@ def test_tcgen05_gemm_split_k_weight_gradient_shapes(M, N, K, dtype):
     a = (torch.randn(K, M, device=_dev()) / 8).to(dtype)          # MN-major operands, as in dW = dY^T X
     b = (torch.randn(K, N, device=_dev()) / 8).to(dtype)
     bias = torch.randn(N, device=_dev()).to(dtype)
-    d = gemm_ops.gemm(a, b, True, True, bias, 'relu')
-    gemm_ops.check_errors()
     ref = torch.relu(a.float().t() @ b.float() + bias.float())
     tol = (1e-2, 2e-2) if dtype == torch.float16 else (3e-2, 8e-2)
-    _close(d, ref, *tol)
+    for _ in range(2):
+        d = gemm_ops.gemm(a, b, True, True, bias, 'relu')
+        gemm_ops.check_errors()
+        _close(d, ref, *tol)
+
+
+@pytest.mark.parametrize('M,N,K', [(8192, 768, 3072), (24000, 256, 1024), (128 * 150, 256, 640), (200, 520, 4096),
+                                   (19000, 192, 512)])
+def test_tcgen05_gemm_stream_k_last_round(M, N, K):
+    """Outputs whose tiles do not fill the last round of the persistent grid: whole rounds tile by tile, the rest cut by
+    k-steps over all CTAs and combined by the CTA that finishes last; against an fp32 product, bias and ReLU included."""
+    from mxnet_b200.ops import cuda
+    from mxnet_b200.ops.cuda import gemm_ops
+    torch.manual_seed(13)
+    a = (torch.randn(M, K, device=_dev()) / 8).half()
+    b = (torch.randn(N, K, device=_dev()) / 8).half()
+    bias = torch.randn(N, device=_dev()).half()
+    ref = torch.relu(a.float() @ b.float().t() + bias.float())
+    for _ in range(2):
+        d = gemm_ops.gemm_tn(a, b, bias, 'relu')
+        gemm_ops.check_errors()
+        _close(d, ref, 1e-2, 2e-2)
 
 
 def test_linear_autograd_through_tcgen05():
