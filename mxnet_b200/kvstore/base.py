@@ -1,119 +1,97 @@
-"""KVStore plug-in base class, registry and the pure-Python ``TestStore``
-(``python/mxnet/kvstore/base.py:243-459``)."""
+"""Plug-in interface of the key-value stores (API of ``python/mxnet/kvstore/base.py``): the abstract ``KVStoreBase``,
+its class registry (``KVStoreBase.register`` -> ``kv_registry``, looked up by lower-cased class name in ``create``),
+and ``TestStore``, an in-process store without optimizer capability that the Trainer tests use as a stand-in for
+Horovod-like back ends.
+"""
 from ..ndarray.ndarray import NDArray
 
 __all__ = ['KVStoreBase', 'TestStore', 'create']
 
 
+def _listify(x):
+    return list(x) if isinstance(x, (list, tuple)) else [x]
+
+
 def _ctype_key_value(keys, vals):
-    if isinstance(keys, (tuple, list)):
-        assert len(keys) == len(vals)
-        return list(keys), list(vals)
-    return [keys], [vals]
+    """``(keys, values)`` as two equally long lists (a single key with a single value becomes lists of one)."""
+    if not isinstance(keys, (tuple, list)):
+        return [keys], [vals]
+    if len(keys) != len(vals):
+        raise AssertionError('keys and values differ in length')
+    return list(keys), list(vals)
+
+
+def _abstract(*_args, **_kwargs):
+    raise NotImplementedError()
 
 
 class KVStoreBase(object):
-    """Abstract key-value store for data-parallel parameter synchronisation."""
-    kv_registry = {}
+    """What a store must offer to a Trainer: ``broadcast`` (initial values), ``pushpull`` (reduce over devices and
+    workers, then deliver), and, when ``is_capable(OPTIMIZER)``, running the optimizer where the reduced value lives."""
+
     OPTIMIZER = 'optimizer'
+    kv_registry = {}
 
-    def broadcast(self, key, value, out, priority=0):
-        raise NotImplementedError()
-
-    def pushpull(self, key, value, out=None, priority=0):
-        raise NotImplementedError()
-
-    def set_optimizer(self, optimizer):
-        raise NotImplementedError()
-
-    @staticmethod
-    def is_capable(capability):
-        raise NotImplementedError()
-
-    def save_optimizer_states(self, fname, dump_optimizer=False):
-        raise NotImplementedError()
-
-    def load_optimizer_states(self, fname):
-        raise NotImplementedError()
-
-    @property
-    def type(self):
-        raise NotImplementedError()
-
-    @property
-    def rank(self):
-        raise NotImplementedError()
-
-    @property
-    def num_workers(self):
-        raise NotImplementedError()
+    broadcast = _abstract            # (key, value, out, priority=0)
+    pushpull = _abstract             # (key, value, out=None, priority=0)
+    set_optimizer = _abstract        # (optimizer)
+    save_optimizer_states = _abstract    # (fname, dump_optimizer=False)
+    load_optimizer_states = _abstract    # (fname)
+    is_capable = staticmethod(_abstract)     # (capability) -> bool
+    type = property(_abstract)
+    rank = property(_abstract)
+    num_workers = property(_abstract)
 
     @staticmethod
     def register(klass):
-        assert isinstance(klass, type)
-        name = klass.__name__.lower()
-        KVStoreBase.kv_registry[name] = klass
+        """Class decorator: make ``klass`` available to ``create`` under its lower-cased name."""
+        if not isinstance(klass, type):
+            raise AssertionError('register expects a class')
+        KVStoreBase.kv_registry[klass.__name__.lower()] = klass
         return klass
 
 
 @KVStoreBase.register
 class TestStore(KVStoreBase):
-    """In-process fake used to test Trainer logic: sums values, no optimizer capability."""
+    """Single-worker store for tests: ``pushpull`` sums the values of the devices; no optimizer on the store."""
 
-    def broadcast(self, key, value, out, priority=0):
-        out = out if isinstance(out, list) else [out]
-        v = value[0] if isinstance(value, (list, tuple)) else value
-        for o in out:
-            o[:] = v
-
-    def pushpull(self, key, value, out=None, priority=0):
-        values = value if isinstance(value, list) else [value]
-        ctx = values[0].context
-        reduced = sum([v.as_in_context(ctx) for v in values[1:]], values[0].copy()) if len(values) > 1 else values[0]
-        if out is None:
-            for v in values:
-                if v is not reduced:
-                    v[:] = reduced.as_in_context(v.context)
-            return
-        outs = out if isinstance(out, list) else [out]
-        for o in outs:
-            o[:] = reduced.as_in_context(o.context)
+    type = property(lambda self: 'teststore')
+    rank = property(lambda self: 0)
+    num_workers = property(lambda self: 1)
 
     @staticmethod
     def is_capable(capability):
-        if capability.lower() == KVStoreBase.OPTIMIZER:
-            return False
-        raise ValueError('Unknown capability: {}'.format(capability))
+        if capability.lower() != KVStoreBase.OPTIMIZER:
+            raise ValueError('Unknown capability: {}'.format(capability))
+        return False
 
-    @property
-    def type(self):
-        return 'teststore'
+    def broadcast(self, key, value, out, priority=0):
+        src = _listify(value)[0]
+        for dst in _listify(out):
+            dst[:] = src
 
-    @property
-    def rank(self):
-        return 0
-
-    @property
-    def num_workers(self):
-        return 1
+    def pushpull(self, key, value, out=None, priority=0):
+        values = _listify(value)
+        total = values[0]
+        if len(values) > 1:
+            total = values[0].copy()
+            for v in values[1:]:
+                total += v.as_in_context(total.context)
+        for dst in (_listify(out) if out is not None else values):
+            if dst is not total:
+                dst[:] = total.as_in_context(dst.context)
 
     def set_optimizer(self, optimizer):
         raise NotImplementedError('TestStore does not support optimizer on the store')
 
-    def save_optimizer_states(self, fname, dump_optimizer=False):
-        raise NotImplementedError()
-
-    def load_optimizer_states(self, fname):
-        raise NotImplementedError()
-
 
 def create(name='local'):
-    """Create a store: 'local' | 'device' | 'nccl' | 'dist_sync' | 'dist_async' | 'dist_device_sync' |
-    'dist_sync_device' | 'horovod' | 'byteps' | any registered plug-in class name."""
+    """A store by name: ``local``, ``device``, ``nccl``, the ``dist_*`` family, ``horovod``, ``byteps``, or the
+    lower-cased class name of any registered plug-in."""
     if not isinstance(name, str):
         raise TypeError('name must be a string')
-    name = name.lower()
-    if name in KVStoreBase.kv_registry:
-        return KVStoreBase.kv_registry[name]()
+    plugin = KVStoreBase.kv_registry.get(name.lower())
+    if plugin is not None:
+        return plugin()
     from .kvstore import KVStore
-    return KVStore(name)
+    return KVStore(name.lower())

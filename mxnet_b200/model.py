@@ -1,6 +1,15 @@
-"""Legacy checkpoint helpers and kvstore selection (``python/mxnet/model.py:74-113,189-264``)."""
+"""Checkpoint files of the symbolic API and the kvstore choice of the legacy training loop (API of
+``python/mxnet/model.py``: ``BatchEndParam``, ``save_checkpoint``, ``load_params``, ``load_checkpoint``,
+``_create_kvstore``, ``_create_sparse_kvstore``).
+
+A checkpoint is two files: ``<prefix>-symbol.json`` and ``<prefix>-<epoch:04d>.params``, the latter a name -> array
+dictionary whose keys carry an ``arg:`` or ``aux:`` tag.
+"""
 import logging
+import os
 from collections import namedtuple
+
+import numpy as np
 
 from . import kvstore as kvs
 from . import ndarray as nd
@@ -8,70 +17,77 @@ from . import symbol as sym
 
 BatchEndParam = namedtuple('BatchEndParams', ['epoch', 'nbatch', 'eval_metric', 'locals'])
 
+_BIG_PARAM = 16 * 1024 * 1024     # elements; above this a `local` store leaves the update to the workers
+
+
+def _params_file(prefix, epoch):
+    return '%s-%04d.params' % (prefix, epoch)
+
+
+def _as_store(kvstore, what):
+    if isinstance(kvstore, kvs.KVStoreBase):
+        return kvstore
+    if isinstance(kvstore, str):
+        return kvs.create(kvstore)
+    raise TypeError(what)
+
 
 def _create_sparse_kvstore(kvstore):
-    if isinstance(kvstore, kvs.KVStoreBase):
-        kv = kvstore
-    elif isinstance(kvstore, str):
-        kv = kvs.create(kvstore)
-    else:
-        raise TypeError("Cannot create '%s' KVStore with row_sparse parameters. The type must be KVStore or str." % kvstore)
-    assert kv.is_capable(kvs.KVStoreBase.OPTIMIZER), 'KVStore with sparse weight requires optimizer support.'
-    return (kv, True)
+    """Store for row-sparse parameters: always updates on the store, so it must be able to run an optimizer."""
+    kv = _as_store(kvstore, "Cannot create '%s' KVStore with row_sparse parameters. The type must be KVStore or str."
+                   % kvstore)
+    if not kv.is_capable(kvs.KVStoreBase.OPTIMIZER):
+        raise AssertionError('KVStore with sparse weight requires optimizer support.')
+    return kv, True
 
 
 def _create_kvstore(kvstore, num_device, arg_params):
-    """Select a store and whether updates run on it: none for a single device unless ``dist`` is in
-    the name; ``local`` stores update on the workers when a parameter is larger than 16M elements."""
-    update_on_kvstore = bool(int(__import__('os').environ.get('MXNET_UPDATE_ON_KVSTORE', '1')))
-    if kvstore is None:
-        kv = None
-    elif isinstance(kvstore, kvs.KVStoreBase):
-        kv = kvstore
-    elif isinstance(kvstore, str):
-        if num_device == 1 and 'dist' not in kvstore:
-            kv = None
-        else:
+    """``(store, update_on_kvstore)`` for a training run on ``num_device`` devices.
+
+    No store at all for one device unless the name asks for a distributed one.  Updates run on the store when
+    ``MXNET_UPDATE_ON_KVSTORE`` (default 1) says so and the store can run an optimizer, except for a ``local`` store with
+    a parameter of more than 16M elements."""
+    on_store = bool(int(os.environ.get('MXNET_UPDATE_ON_KVSTORE', '1')))
+    kv = None
+    if isinstance(kvstore, str):
+        if num_device > 1 or 'dist' in kvstore:
             kv = kvs.create(kvstore)
-            if kvstore == 'local':
-                max_size = max(int(__import__('numpy').prod(param.shape)) for param in arg_params.values())
-                if max_size > 1024 * 1024 * 16:
-                    update_on_kvstore = False
-    else:
-        raise TypeError('kvstore must be KVStore, str or None')
+            if kvstore == 'local' and max(int(np.prod(p.shape)) for p in arg_params.values()) > _BIG_PARAM:
+                on_store = False
+    elif kvstore is not None:
+        kv = _as_store(kvstore, 'kvstore must be KVStore, str or None')
     if kv is None:
-        update_on_kvstore = False
-    else:
-        update_on_kvstore &= kv.is_capable(kvs.KVStoreBase.OPTIMIZER)
-    return (kv, update_on_kvstore)
+        return None, False
+    return kv, on_store and kv.is_capable(kvs.KVStoreBase.OPTIMIZER)
 
 
 def save_checkpoint(prefix, epoch, symbol, arg_params, aux_params, remove_amp_cast=True):
+    """Write the graph (if given) and the tagged parameter dictionary of one epoch."""
     if symbol is not None:
-        symbol.save('%s-symbol.json' % prefix, remove_amp_cast=remove_amp_cast)
-    save_dict = {('arg:%s' % k): v.as_nd_ndarray() for k, v in arg_params.items()}
-    save_dict.update({('aux:%s' % k): v.as_nd_ndarray() for k, v in aux_params.items()})
-    param_name = '%s-%04d.params' % (prefix, epoch)
-    nd.save(param_name, save_dict)
-    logging.info('Saved checkpoint to "%s"', param_name)
+        symbol.save(prefix + '-symbol.json', remove_amp_cast=remove_amp_cast)
+    tagged = {}
+    for tag, params in (('arg', arg_params), ('aux', aux_params)):
+        for name, value in params.items():
+            tagged['%s:%s' % (tag, name)] = value.as_nd_ndarray()
+    fname = _params_file(prefix, epoch)
+    nd.save(fname, tagged)
+    logging.info('Saved checkpoint to "%s"', fname)
 
 
 def load_params(prefix, epoch):
-    save_dict = nd.load('%s-%04d.params' % (prefix, epoch))
-    arg_params, aux_params = {}, {}
-    if not save_dict:
-        logging.warning('Params file "%s" is empty', '%s-%04d.params' % (prefix, epoch))
-        return (arg_params, aux_params)
-    for k, v in save_dict.items():
-        tp, name = k.split(':', 1)
-        if tp == 'arg':
-            arg_params[name] = v
-        if tp == 'aux':
-            aux_params[name] = v
-    return (arg_params, aux_params)
+    """``(arg_params, aux_params)`` of one epoch; keys without an ``arg:`` / ``aux:`` tag are ignored."""
+    fname = _params_file(prefix, epoch)
+    loaded = nd.load(fname)
+    out = {'arg': {}, 'aux': {}}
+    if not loaded:
+        logging.warning('Params file "%s" is empty', fname)
+    for key, value in (loaded or {}).items():
+        tag, _, name = key.partition(':')
+        if tag in out:
+            out[tag][name] = value
+    return out['arg'], out['aux']
 
 
 def load_checkpoint(prefix, epoch):
-    symbol = sym.load('%s-symbol.json' % prefix)
-    arg_params, aux_params = load_params(prefix, epoch)
-    return (symbol, arg_params, aux_params)
+    """``(symbol, arg_params, aux_params)``."""
+    return (sym.load(prefix + '-symbol.json'),) + load_params(prefix, epoch)

@@ -67,15 +67,15 @@ def _error_flag(device):
 
 
 def _workspace(device):
-    """Stream-K workspace of the GEMM kernel (piece counters + fp32 slots): one zero-filled buffer per device, created on
-    first use and left clean by every launch.  Launches that share it must not overlap: the framework issues its GEMMs on
+    """Stream-K workspace of the GEMM kernel (fp32 slots for partial tiles): one buffer per device, created on first
+    use.  Launches that share it must not overlap: the framework issues its GEMMs on
     the device's compute stream (graph replays included).  Never created while a graph is being captured (the memory would
     belong to that graph); such a call runs without stream-K."""
     ws = _ws.get(device)
     if ws is None:
         if torch.cuda.is_current_stream_capturing():
             return None
-        ws = _ws[device] = torch.zeros(int(lib().mxb_gemm_workspace_bytes()), dtype=torch.uint8, device=device)
+        ws = _ws[device] = torch.empty(int(lib().mxb_gemm_workspace_bytes()), dtype=torch.uint8, device=device)
     return ws
 
 
@@ -84,8 +84,6 @@ def check_errors():
     for dev, f in _err.items():
         if int(f.item()) != 0:
             f.zero_()
-            if dev in _ws:                          # a launch that gave up may have left piece counters behind
-                _ws[dev].zero_()
             raise RuntimeError('tcgen05 GEMM reported a barrier time-out on %s' % dev)
 
 

@@ -31,6 +31,7 @@ namespace mxb {
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 // kernel selection: 0 = per shape, 1 = always the single-CTA kernel, 2 = the CTA-pair kernel wherever it applies
 static int g_gemm_variant = 0;
+static int g_gemm_streamk = 1;      // 0: never cut a last round of tiles by k-steps
 constexpr int kGemmThreads = 192;
 constexpr uint32_t A_BYTES = BM * BK * 2;
 constexpr int kMaxStages = 8;
@@ -50,19 +51,23 @@ enum Act { kActNone = 0, kActRelu = 1, kActGelu = 2 };
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erf_fast(x * 0.70710678118654752f)); }
 
+// fp32 slot of a stream-K tile: [BN / 32 column chunks][8 float4 per chunk][128 rows] float4, so that the 32 lanes of a
+// warp (32 consecutive rows) touch 512 contiguous bytes per access.
+__device__ __forceinline__ float4* sk_slot_ptr(float* slot, int c0, int v, int row_in_tile) {
+  return reinterpret_cast<float4*>(slot) + ((size_t)((c0 >> 5) * 8 + v) * 128 + (size_t)row_in_tile);
+}
+
 // Epilogue of one warp: drains 32 accumulator rows (TMEM lanes) by BN columns starting at TMEM address `taddr`, adds
 // the bias, applies the activation and stores rows [row0, row0 + 32) x columns [tile_col0, tile_col0 + BN) of D, either
 // through the copy engine (32 x 32 blocks staged in `stg`) or with per-thread stores.
-// Stream-K pieces: with `part_out` set, the fp32 partial products of this k-range are written to that slot
-// ([128][BN] floats, this warp's rows starting at `part_row0`) and nothing else happens; with `n_others` > 0 the
-// partial products found in the slots `others[0 .. n_others)` are added to the accumulator before the bias.
+// Stream-K pieces: with `slot` set, the fp32 partial products of this k-range are stored into that slot (this warp's
+// rows at `part_row0`) and nothing else is written; gemm_sk_finish_kernel adds the pieces of a tile up afterwards.
 template <typename T, int BN>
 __device__ __forceinline__ void drain_quarter(uint32_t taddr, uint8_t* stg, const CUtensorMap* map_d, int use_tma_store,
                                               T* __restrict__ D, const T* __restrict__ bias, int M, int N, int ldd, int act,
-                                              int row0, int tile_col0, int lane, float* __restrict__ part_out = nullptr,
-                                              const float* const* others = nullptr, int n_others = 0, int part_row0 = 0) {
+                                              int row0, int tile_col0, int lane, float* __restrict__ slot = nullptr,
+                                              int part_row0 = 0) {
   const int row = row0 + lane;
-  const bool to_ws = part_out != nullptr;
   const bool bias_vec = bias != nullptr && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
   const bool row_vec = (ldd % 8) == 0;
   uint32_t r[32];
@@ -71,12 +76,12 @@ __device__ __forceinline__ void drain_quarter(uint32_t taddr, uint8_t* stg, cons
   for (int c0 = 0; c0 < BN; c0 += 32) {
     const int col0 = tile_col0 + c0;
     const bool full_cols = col0 + 32 <= N;
-    // bias of these 32 columns first, so its latency overlaps the TMEM load (registers only: every index
+    // bias of these 32 columns first, so its latency overlaps the fetch (registers only: every index
     // below is a compile-time constant after unrolling)
     float bv[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) bv[j] = 0.f;
-    if (bias != nullptr && col0 < N) {
+    if (slot == nullptr && bias != nullptr && col0 < N) {
       if (bias_vec && full_cols) {
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
@@ -91,26 +96,13 @@ __device__ __forceinline__ void drain_quarter(uint32_t taddr, uint8_t* stg, cons
       }
     }
     tmem_wait_ld32(r);
-    if (to_ws) {
-      float* prow = part_out + (size_t)(part_row0 + lane) * BN + c0;
+    if (slot != nullptr) {
 #pragma unroll
       for (int v = 0; v < 8; ++v)
-        __stcg(reinterpret_cast<float4*>(prow) + v, make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
-                                                               __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3])));
+        __stcg(sk_slot_ptr(slot, c0, v, part_row0 + lane), make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
+                                                                       __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3])));
       if (c0 + 32 < BN) tmem_ld32(taddr + (uint32_t)(c0 + 32), r);
       continue;
-    }
-    for (int o = 0; o < n_others; ++o) {
-      // the other k-ranges of this tile, written by other CTAs (read through L2, never from this SM's L1)
-      const float* prow = others[o] + (size_t)(part_row0 + lane) * BN + c0;
-#pragma unroll
-      for (int v = 0; v < 8; ++v) {
-        const float4 t = __ldcg(reinterpret_cast<const float4*>(prow) + v);
-        r[v * 4] = __float_as_uint(__uint_as_float(r[v * 4]) + t.x);
-        r[v * 4 + 1] = __float_as_uint(__uint_as_float(r[v * 4 + 1]) + t.y);
-        r[v * 4 + 2] = __float_as_uint(__uint_as_float(r[v * 4 + 2]) + t.z);
-        r[v * 4 + 3] = __float_as_uint(__uint_as_float(r[v * 4 + 3]) + t.w);
-      }
     }
     float f[32];
 #pragma unroll
@@ -164,8 +156,9 @@ __device__ __forceinline__ void drain_quarter(uint32_t taddr, uint8_t* stg, cons
 // The work of one CTA of the persistent grid: first whole tiles (tile = blockIdx.x, + gridDim.x, ... below `full_tiles`),
 // then its share of the stream-K region: the `sk_tiles` tiles after `full_tiles` are a sequence of sk_tiles * num_k
 // k-steps that is cut into `sk_ctas` contiguous, equally long ranges, so a CTA computes the end of one tile, possibly
-// whole tiles, and the beginning of another.  A piece that is not a whole tile is `partial`; its fp32 result goes to
-// slot 0 of the CTA if the tile is the first one the CTA touches, else to slot 1.  The three roles walk the same sequence.
+// whole tiles, and the beginning of another.  A piece that is not a whole tile is `partial`: its fp32 result goes to
+// slot 0 of the CTA if the tile is the first one the CTA touches, else to slot 1 (a CTA has at most two partial pieces:
+// the end of its first tile and the beginning of its last).  The three roles walk the same sequence.
 struct UnitIter {
   int tile, k0, k1, sk_tile, slot;
   bool partial;
@@ -206,14 +199,13 @@ struct UnitIter {
     return false;
   }
 };
-constexpr int kMaxOthers = 7;      // a tile of the stream-K region is cut into at most 8 pieces (the host guarantees it)
 
 template <typename T, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_d, int use_tma_store, T* __restrict__ D, const T* __restrict__ bias, int M,
                int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, const FastDiv fd_tiles_m,
-               int full_tiles, int sk_tiles, int sk_ctas, float* __restrict__ sk_ws, int* __restrict__ sk_cnt, int a3d, int b3d,
+               int full_tiles, int sk_tiles, int sk_ctas, float* __restrict__ sk_ws, int a3d, int b3d,
                int* __restrict__ error_flag) {
   using Cfg = TileCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
@@ -233,10 +225,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* issued_it = abort_flag + 1;     // k-steps whose TMA loads were issued
   volatile int* consumed_it = abort_flag + 2;   // k-steps whose loads were observed complete by the MMA warp
-  // per epilogue warp: [last arriver?, number of other pieces] of its quarter of the current stream-K tile, and the
-  // other pieces' slots (8-byte aligned: `bars` + 208)
-  volatile int* sk_info = abort_flag + 3;       // [4][2]
-  const float** sk_others = reinterpret_cast<const float**>(const_cast<int*>(abort_flag) + 11);   // [4][kMaxOthers]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_k = (K + BK - 1) / BK;
@@ -365,41 +353,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!u.partial) {
         drain_quarter<T, BN>(taddr, stg, &map_d, use_tma_store, D, bias, M, N, ldd, act, row0, col0, lane);
       } else {
-        // A piece of a stream-K tile: publish the fp32 partial products of this warp's 32 rows, then count the piece in
-        // (one counter per tile and row quarter, so the four epilogue warps never wait for each other).  The CTA whose
-        // piece arrives last adds the other pieces to its own accumulator (still in tensor memory) and writes the
-        // rows; no CTA ever waits for another one.
-        constexpr size_t kSlot = (size_t)BM * BN;
+        // A piece of a stream-K tile: store this warp's 32 rows of fp32 partial products into this CTA's slot; the
+        // finishing kernel that follows on the stream adds the pieces of each tile in a fixed order.
         drain_quarter<T, BN>(taddr, stg, &map_d, use_tma_store, D, bias, M, N, ldd, act, row0, col0, lane,
-                             sk_ws + ((size_t)blockIdx.x * 2 + (size_t)u.slot) * kSlot, nullptr, 0, q * 32);
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) {
-          const uint64_t total = (uint64_t)sk_tiles * (uint64_t)num_k, lo = (uint64_t)u.sk_tile * (uint64_t)num_k;
-          const int c_lo = (int)(((lo + 1) * (uint64_t)sk_ctas - 1) / total);
-          const int c_hi = (int)(((lo + (uint64_t)num_k) * (uint64_t)sk_ctas - 1) / total);
-          const int pieces = c_hi - c_lo + 1;
-          int* cnt = sk_cnt + u.sk_tile * 4 + q;
-          const int last = atomicAdd(cnt, 1) == pieces - 1 ? 1 : 0;
-          int n = 0;
-          if (last) {
-            *cnt = 0;            // every piece has arrived: the counter is clean for the next launch
-            for (int c = c_lo; c <= c_hi && n < kMaxOthers; ++c) {
-              if (c == (int)blockIdx.x) continue;
-              const int first_c = (int)(((uint64_t)c * total / (uint64_t)sk_ctas) / (uint64_t)num_k);
-              sk_others[q * kMaxOthers + n++] = sk_ws + ((size_t)c * 2 + (u.sk_tile == first_c ? 0 : 1)) * kSlot;
-            }
-          }
-          sk_info[q * 2] = last;
-          sk_info[q * 2 + 1] = n;
-        }
-        __syncwarp();
-        if (sk_info[q * 2]) {
-          __threadfence();
-          drain_quarter<T, BN>(taddr, stg, &map_d, use_tma_store, D, bias, M, N, ldd, act, row0, col0, lane, nullptr,
-                               sk_others + q * kMaxOthers, sk_info[q * 2 + 1], q * 32);
-        }
-        __syncwarp();
+                             sk_ws + ((size_t)blockIdx.x * 2 + (size_t)u.slot) * ((size_t)BM * BN), q * 32);
       }
       // this warp has finished reading the accumulator: let the MMA warp reuse it
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -420,6 +377,67 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 1) {
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// Second half of a stream-K product: adds up the pieces of every tile of the stream-K region (in CTA order, so the result
+// does not depend on timing), applies bias and activation and writes D.  One CTA per tile and 32-column chunk, one thread
+// per (float4 of the chunk, row): it reads the slots in the layout the GEMM epilogue wrote (consecutive rows contiguous),
+// all pieces with independent loads so that their latencies overlap.
+constexpr int kSkMaxPieces = 8;      // the plan cuts a tile into at most this many pieces
+template <typename T>
+__global__ void __launch_bounds__(1024)
+gemm_sk_finish_kernel(const float* __restrict__ sk_ws, const T* __restrict__ bias, T* __restrict__ D, int M, int N, int ldd, int act,
+                      int bn, int tiles_m, int full_tiles, int sk_tiles, int sk_ctas, int num_k) {
+  __shared__ const float* piece[kSkMaxPieces];
+  __shared__ int n_pieces;
+  const int chunks = bn >> 5;
+  const int t = blockIdx.x / chunks, chunk = blockIdx.x - t * chunks;
+  if (threadIdx.x == 0) {
+    const uint64_t total = (uint64_t)sk_tiles * (uint64_t)num_k, lo = (uint64_t)t * (uint64_t)num_k;
+    const int c_lo = (int)(((lo + 1) * (uint64_t)sk_ctas - 1) / total);
+    const int c_hi = (int)(((lo + (uint64_t)num_k) * (uint64_t)sk_ctas - 1) / total);
+    int n = 0;
+    if (c_hi > c_lo) {                              // otherwise one CTA computed the whole tile and wrote it itself
+      for (int c = c_lo; c <= c_hi && n < kSkMaxPieces; ++c) {
+        const int first_c = (int)(((uint64_t)c * total / (uint64_t)sk_ctas) / (uint64_t)num_k);
+        piece[n++] = sk_ws + ((size_t)c * 2 + (t == first_c ? 0 : 1)) * ((size_t)BM * bn);
+      }
+    }
+    n_pieces = n;
+  }
+  __syncthreads();
+  const int n = n_pieces;
+  if (n == 0) return;
+  const int tile = full_tiles + t;
+  const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+  const int v = threadIdx.x >> 7, r = threadIdx.x & (BM - 1);
+  const size_t off = (size_t)(chunk * 8 + v) * BM + r;
+  float4 p[kSkMaxPieces];
+#pragma unroll
+  for (int c = 0; c < kSkMaxPieces; ++c)
+    p[c] = c < n ? __ldcg(reinterpret_cast<const float4*>(piece[c]) + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 acc = p[0];
+#pragma unroll
+  for (int c = 1; c < kSkMaxPieces; ++c) { acc.x += p[c].x; acc.y += p[c].y; acc.z += p[c].z; acc.w += p[c].w; }
+  const int row = tile_m * BM + r, col = tile_n * bn + chunk * 32 + v * 4;
+  if (row >= M || col >= N) return;
+  const float x[4] = {acc.x, acc.y, acc.z, acc.w};
+  T out[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float y = x[j] + ((bias && col + j < N) ? Cvt<T>::to_f(bias[col + j]) : 0.f);
+    if (act == kActRelu) y = fmaxf(y, 0.f);
+    else if (act == kActGelu) y = gelu_erf(y);
+    out[j] = Cvt<T>::from_f(y);
+  }
+  T* drow = D + (size_t)row * ldd + col;
+  if (col + 4 <= N && (ldd & 3) == 0) {
+    *reinterpret_cast<uint2*>(drow) = *reinterpret_cast<const uint2*>(out);      // col is a multiple of 4: 8-byte aligned
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (col + j < N) drow[j] = out[j];
   }
 }
 
@@ -667,11 +685,12 @@ static int make_map_store(CUtensorMap* map, const void* base, int bf16, int64_t 
 
 // Stream-K plan for `tiles` output tiles of `num_k` k-steps on a grid of G CTAs: whole rounds of tiles are computed
 // tile by tile; the tiles of a last, partial round (or all tiles, when there are fewer than CTAs) become the stream-K
-// region when cutting their k-steps evenly over the CTAs is shorter than one more round.  A tile is cut into at most
-// 1 + kMaxOthers pieces and a piece is at least 6 k-steps long.
+// region when cutting their k-steps evenly over the CTAs is shorter than one more round.  A piece is at least 6 k-steps
+// long and at least a sixth of a tile.
 struct SkPlan {
   int full_tiles, sk_tiles, sk_ctas;
 };
+constexpr int kSkCombineCost = 16;      // writing, the second launch and the summation, in k-steps of a CTA
 static SkPlan plan_streamk(int tiles, int num_k, int G, bool allowed) {
   SkPlan p = {tiles, 0, 0};
   const int rem = tiles % G;
@@ -683,17 +702,15 @@ static SkPlan plan_streamk(int tiles, int num_k, int G, bool allowed) {
   if (ctas > G) ctas = G;
   if (ctas < 2) return p;
   const long per = (total + ctas - 1) / ctas;
-  if (per + 4 >= num_k) return p;          // no shorter than one more round of whole tiles (4: the cost of combining)
+  if (per + kSkCombineCost >= num_k) return p;     // no shorter than one more round of whole tiles
   p.full_tiles = tiles - rem;
   p.sk_tiles = rem;
   p.sk_ctas = (int)ctas;
   return p;
 }
 
-// Workspace of the stream-K pieces: [4 counters per tile of a round][2 slots of 128 x 256 floats per CTA].  It must be
-// zero when first used; the kernels leave the counters at zero.
-constexpr size_t kSkCounterBytes = 4096 * sizeof(int);
-static size_t sk_workspace_bytes() { return kSkCounterBytes + (size_t)sm_count() * 2 * BM * 256 * sizeof(float); }
+// Workspace of the stream-K pieces: two slots of 128 x 256 floats per CTA of the grid (no initial contents required).
+static size_t sk_workspace_bytes() { return (size_t)sm_count() * 2 * BM * 256 * sizeof(float); }
 
 template <typename T, int BN>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, int use_tma_store, void* D,
@@ -710,17 +727,18 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   const int tiles = tiles_m * ((N + BN - 1) / BN);
   const int num_k = (K + BK - 1) / BK;
   const int sms = sm_count();
-  const SkPlan plan = plan_streamk(tiles, num_k, sms, ws != nullptr && sms <= 1024);
+  const SkPlan plan = plan_streamk(tiles, num_k, sms, g_gemm_streamk && ws != nullptr && sms <= 1024);
   int grid = tiles < sms ? tiles : sms;
   if (plan.sk_tiles > 0 && plan.full_tiles == 0) grid = plan.sk_ctas > tiles ? plan.sk_ctas : tiles;
   if (plan.sk_tiles > 0 && plan.full_tiles > 0) grid = sms;
   if (grid > sms) grid = sms;
-  int* cnt = reinterpret_cast<int*>(ws);
-  float* slots = ws ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + kSkCounterBytes) : nullptr;
   gemm_tn_kernel<T, BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ma, mb, md, use_tma_store, (T*)D, (const T*)bias, M, N, K, ldd,
                                                                      act, bf16, a_mn, b_mn, make_fastdiv((uint32_t)tiles_m),
-                                                                     plan.full_tiles, plan.sk_tiles, plan.sk_ctas, slots, cnt, a3d,
-                                                                     b3d, error_flag);
+                                                                     plan.full_tiles, plan.sk_tiles, plan.sk_ctas, ws, a3d, b3d,
+                                                                     error_flag);
+  if (plan.sk_tiles > 0)
+    gemm_sk_finish_kernel<T><<<plan.sk_tiles * (BN / 32), 1024, 0, st>>>(ws, (const T*)bias, (T*)D, M, N, ldd, act, BN, tiles_m,
+                                                                        plan.full_tiles, plan.sk_tiles, plan.sk_ctas, num_k);
   return (int)cudaGetLastError();
 }
 
@@ -863,6 +881,7 @@ static int gemm_run(int dtype, const void* A, const void* B, void* D, const void
 // Kernel selection for later calls: 0 = per shape (the default), 1 = single-CTA kernel only, 2 = the CTA-pair kernel
 // wherever it applies.  For benchmarks and tests that compare the two.
 MXB_EXPORT void mxb_gemm_set_variant(int v) { g_gemm_variant = v; }
+MXB_EXPORT void mxb_gemm_set_streamk(int on) { g_gemm_streamk = on; }
 
 MXB_EXPORT int mxb_gemm(int dtype, const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda,
                         int ldb, int ldd, int a_mn, int b_mn, int act, int* error_flag, void* stream) {

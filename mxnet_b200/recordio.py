@@ -1,5 +1,12 @@
-"""RecordIO files (``python/mxnet/recordio.py``) over the native reader/writer (``csrc/recordio.cc``)."""
+"""RecordIO files from Python (API of ``python/mxnet/recordio.py``: ``MXRecordIO``, ``MXIndexedRecordIO``, ``IRHeader``,
+``pack`` / ``unpack`` / ``pack_img`` / ``unpack_img``).
+
+Reading and writing of the framed records is done by the native runtime (``csrc/recordio.cc``); this module owns the
+handle life cycle (open / close / reset, pickling for data-loader workers, the per-process guard), the text index of the
+indexed variant (``key<TAB>byte offset`` per line) and the image-record header.
+"""
 import ctypes
+import io
 import numbers
 import os
 import struct
@@ -18,97 +25,105 @@ def _rt():
 
 
 class MXRecordIO(object):
+    """Sequential reader (``flag='r'``) or writer (``flag='w'``) of one RecordIO file."""
+
+    _MODES = {'w': True, 'r': False}
+
     def __init__(self, uri, flag):
-        self.uri, self.flag = str(uri), flag
+        self.uri = str(uri)
+        self.flag = flag
         self.handle = None
         self.is_open = False
+        self.writable = False
+        self.pid = None
         self.open()
 
+    # ---- handle life cycle ----------------------------------------------------------------------------------
     def open(self):
-        L = _rt()
-        if self.flag == 'w':
-            self.handle = L.mxb_rec_writer_open(self.uri.encode(), 0)
-            self.writable = True
-        elif self.flag == 'r':
-            self.handle = L.mxb_rec_reader_open(self.uri.encode())
-            self.writable = False
-        else:
+        if self.flag not in self._MODES:
             raise ValueError('Invalid flag %s' % self.flag)
+        self.writable = self._MODES[self.flag]
+        lib = _rt()
+        path = self.uri.encode()
+        self.handle = lib.mxb_rec_writer_open(path, 0) if self.writable else lib.mxb_rec_reader_open(path)
         if not self.handle:
             raise MXNetError('cannot open %s' % self.uri)
         self.pid = os.getpid()
         self.is_open = True
 
+    def close(self):
+        if not getattr(self, 'is_open', False):
+            return
+        lib = _rt()
+        (lib.mxb_rec_writer_close if self.writable else lib.mxb_rec_reader_close)(self.handle)
+        self.handle = None
+        self.is_open = False
+        self.pid = None
+
+    def reset(self):
+        """Back to the first record (a writer truncates and starts over)."""
+        self.close()
+        self.open()
+
     def __del__(self):
         self.close()
 
     def __getstate__(self):
-        is_open = self.is_open
+        # a native handle cannot travel to another process: remember whether to reopen on the other side
+        was_open = self.is_open
         self.close()
-        d = dict(self.__dict__)
-        d['is_open'] = is_open
-        d['handle'] = None
-        return d
+        state = dict(self.__dict__)
+        state.update(is_open=was_open, handle=None)
+        return state
 
-    def __setstate__(self, d):
-        self.__dict__ = d
-        is_open = d['is_open']
+    def __setstate__(self, state):
+        reopen = state['is_open']
+        self.__dict__ = state
         self.is_open = False
         self.handle = None
-        if is_open:
+        if reopen:
             self.open()
 
     def _check_pid(self, allow_reset=False):
-        if not self.pid == os.getpid():
-            if allow_reset:
-                self.reset()
-            else:
-                raise RuntimeError('Forbidden operation in multiple processes')
-
-    def close(self):
-        if not getattr(self, 'is_open', False):
+        """A handle opened before a fork is reopened in the child (readers) or refused (writers)."""
+        if self.pid == os.getpid():
             return
-        L = _rt()
-        if self.writable:
-            L.mxb_rec_writer_close(self.handle)
-        else:
-            L.mxb_rec_reader_close(self.handle)
-        self.is_open = False
-        self.handle = None
-        self.pid = None
+        if not allow_reset:
+            raise RuntimeError('Forbidden operation in multiple processes')
+        self.reset()
 
-    def reset(self):
-        self.close()
-        self.open()
-
+    # ---- records --------------------------------------------------------------------------------------------
     def write(self, buf):
-        assert self.writable
+        if not self.writable:
+            raise AssertionError('file was opened for reading')
         self._check_pid(allow_reset=False)
-        rc = _rt().mxb_rec_writer_write(self.handle, ctypes.c_char_p(bytes(buf)), len(buf))
-        if rc != 0:
+        data = bytes(buf)
+        if _rt().mxb_rec_writer_write(self.handle, ctypes.c_char_p(data), len(data)) != 0:
             raise MXNetError('record too large')
+
+    def read(self):
+        """The next record as bytes, ``None`` at the end of the file."""
+        if self.writable:
+            raise AssertionError('file was opened for writing')
+        self._check_pid(allow_reset=True)
+        size = ctypes.c_uint64(0)
+        ptr = _rt().mxb_rec_reader_next(self.handle, ctypes.byref(size))
+        return ctypes.string_at(ptr, size.value) if ptr else None
 
     def tell(self):
         """Byte offset of the next record to be read or written."""
-        L = _rt()
-        return L.mxb_rec_writer_tell(self.handle) if self.writable else L.mxb_rec_reader_tell(self.handle)
-
-    def read(self):
-        assert not self.writable
-        self._check_pid(allow_reset=True)
-        size = ctypes.c_uint64(0)
-        p = _rt().mxb_rec_reader_next(self.handle, ctypes.byref(size))
-        if not p:
-            return None
-        return ctypes.string_at(p, size.value)
+        lib = _rt()
+        return (lib.mxb_rec_writer_tell if self.writable else lib.mxb_rec_reader_tell)(self.handle)
 
 
 class MXIndexedRecordIO(MXRecordIO):
+    """RecordIO file with a side index ``idx_path`` for random access by key (``key_type`` converts the key column)."""
+
     def __init__(self, idx_path, uri, flag, key_type=int):
         self.idx_path = idx_path
+        self.key_type = key_type
         self.idx = {}
         self.keys = []
-        self.key_type = key_type
         self.fidx = None
         super().__init__(uri, flag)
 
@@ -116,12 +131,15 @@ class MXIndexedRecordIO(MXRecordIO):
         super().open()
         self.idx, self.keys = {}, []
         self.fidx = open(self.idx_path, self.flag)
-        if not self.writable:
-            for line in iter(self.fidx.readline, ''):
-                line = line.strip().split('\t')
-                key = self.key_type(line[0])
-                self.idx[key] = int(line[1])
-                self.keys.append(key)
+        if self.writable:
+            return
+        for line in self.fidx:
+            fields = line.strip().split('\t')
+            if len(fields) < 2:
+                continue
+            key = self.key_type(fields[0])
+            self.idx[key] = int(fields[1])
+            self.keys.append(key)
 
     def close(self):
         if not getattr(self, 'is_open', False):
@@ -132,17 +150,20 @@ class MXIndexedRecordIO(MXRecordIO):
             self.fidx = None
 
     def __getstate__(self):
-        d = super().__getstate__()
-        d['fidx'] = None
-        return d
+        state = super().__getstate__()
+        state['fidx'] = None
+        return state
 
     def seek(self, idx):
-        assert not self.writable
+        """Position the reader at the record stored under key ``idx``."""
+        if self.writable:
+            raise AssertionError('file was opened for writing')
         self._check_pid(allow_reset=True)
         _rt().mxb_rec_reader_seek(self.handle, self.idx[idx])
 
     def tell(self):
-        assert self.writable
+        if not self.writable:
+            raise AssertionError('tell() of an indexed file is defined for writers')
         return _rt().mxb_rec_writer_tell(self.handle)
 
     def read_idx(self, idx):
@@ -150,56 +171,60 @@ class MXIndexedRecordIO(MXRecordIO):
         return self.read()
 
     def write_idx(self, idx, buf):
+        """Append a record and note its offset under key ``idx``."""
         key = self.key_type(idx)
-        pos = self.tell()
+        offset = self.tell()
         self.write(buf)
-        self.fidx.write('%s\t%d\n' % (str(key), pos))
-        self.idx[key] = pos
+        self.fidx.write('%s\t%d\n' % (key, offset))
+        self.idx[key] = offset
         self.keys.append(key)
 
 
+# ---- image records: a fixed header in front of the payload ---------------------------------------------------------
+# flag (uint32): 0 for a scalar label, else the number of float32 labels that follow the header; label (float32);
+# id, id2 (uint64).
 IRHeader = namedtuple('HEADER', ['flag', 'label', 'id', 'id2'])
-_IR_FORMAT = 'IfQQ'
-_IR_SIZE = struct.calcsize(_IR_FORMAT)
+_HEADER = struct.Struct('IfQQ')
 
 
 def pack(header, s):
-    """Pack a string with an image-record header (flag, label, id, id2); extra labels follow as floats."""
+    """Header + payload as one record.  A scalar label sits in the header; an array of labels is stored as float32 values
+    between header and payload, with its length in ``flag``."""
     header = IRHeader(*header)
     if isinstance(header.label, numbers.Number):
-        header = header._replace(flag=0)
-    else:
-        label = np.asarray(header.label, dtype=np.float32)
-        header = header._replace(flag=label.size, label=0)
-        s = label.tobytes() + s
-    return struct.pack(_IR_FORMAT, *header) + s
+        return _HEADER.pack(0, header.label, header.id, header.id2) + s
+    labels = np.asarray(header.label, dtype=np.float32)
+    return _HEADER.pack(labels.size, 0, header.id, header.id2) + labels.tobytes() + s
 
 
 def unpack(s):
-    header = IRHeader(*struct.unpack(_IR_FORMAT, s[:_IR_SIZE]))
-    s = s[_IR_SIZE:]
+    """Inverse of ``pack``: ``(IRHeader, payload)``; a label array comes back as a float32 NumPy array."""
+    header = IRHeader(*_HEADER.unpack_from(s))
+    body = s[_HEADER.size:]
     if header.flag > 0:
-        header = header._replace(label=np.frombuffer(s, np.float32, header.flag))
-        s = s[header.flag * 4:]
-    return header, s
+        nbytes = 4 * header.flag
+        header = header._replace(label=np.frombuffer(body[:nbytes], dtype=np.float32))
+        body = body[nbytes:]
+    return header, body
 
 
 def unpack_img(s, iscolor=-1):
-    header, s = unpack(s)
+    """``(IRHeader, image)`` with the image decoded to an HxWxC (or HxW) uint8 array in BGR channel order, the order
+    OpenCV-based writers of such files use."""
     from .image import _decode_to_numpy
-    # OpenCV convention of the reference (cv2.imdecode): colour images come back in BGR order
-    return header, _decode_to_numpy(s, 1 if iscolor != 0 else 0, to_rgb=False)
+    header, payload = unpack(s)
+    return header, _decode_to_numpy(payload, 1 if iscolor != 0 else 0, to_rgb=False)
 
 
 def pack_img(header, img, quality=95, img_fmt='.jpg'):
-    import io
+    """Encode a BGR (or grey) uint8 image as JPEG (``quality`` 1-100) or PNG and pack it."""
     from PIL import Image
-    arr = np.asarray(img)
-    im = Image.fromarray(arr[..., ::-1] if arr.ndim == 3 else arr)   # stored BGR like OpenCV callers expect
-    buf = io.BytesIO()
-    fmt = 'JPEG' if img_fmt.lower() in ('.jpg', '.jpeg') else 'PNG'
-    if fmt == 'JPEG':
-        im.save(buf, format=fmt, quality=quality)
+    pixels = np.asarray(img)
+    if pixels.ndim == 3:
+        pixels = pixels[..., ::-1]          # BGR -> RGB for the encoder
+    out = io.BytesIO()
+    if img_fmt.lower() in ('.jpg', '.jpeg'):
+        Image.fromarray(pixels).save(out, format='JPEG', quality=quality)
     else:
-        im.save(buf, format=fmt)
-    return pack(header, buf.getvalue())
+        Image.fromarray(pixels).save(out, format='PNG')
+    return pack(header, out.getvalue())
