@@ -17,47 +17,52 @@ class Sampler(object):
         raise NotImplementedError
 
 
-class SequentialSampler(Sampler):
-    """``start, start + 1, ..., start + length - 1``."""
+class _FixedLength(Sampler):
+    """Samplers over a known number of positions: subclasses give ``_positions()``."""
 
-    def __init__(self, length, start=0):
-        self._length = length
-        self._start = start
+    _length = 0
+
+    def _positions(self):
+        raise NotImplementedError
 
     def __iter__(self):
-        return iter(range(self._start, self._start + self._length))
+        return iter(self._positions())
 
     def __len__(self):
         return self._length
 
 
-class RandomSampler(Sampler):
+class SequentialSampler(_FixedLength):
+    """``start, start + 1, ..., start + length - 1``."""
+
+    def __init__(self, length, start=0):
+        self._length, self._start = length, start
+
+    def _positions(self):
+        return range(self._start, self._start + self._length)
+
+
+class RandomSampler(_FixedLength):
     """A fresh permutation of ``range(length)`` per pass (drawn from NumPy's global generator, so ``mx.random.seed`` /
     ``np.random.seed`` make it repeatable)."""
 
     def __init__(self, length):
         self._length = length
 
-    def __iter__(self):
-        return iter(np.random.permutation(self._length).tolist())
-
-    def __len__(self):
-        return self._length
+    def _positions(self):
+        return np.random.permutation(self._length).tolist()
 
 
-class FilterSampler(Sampler):
+class FilterSampler(_FixedLength):
     """Positions of the items for which ``fn(item)`` holds (evaluated once, at construction)."""
 
     def __init__(self, fn, dataset):
-        self._fn = fn
-        self._dataset = dataset
+        self._fn, self._dataset = fn, dataset
         self._indices = [pos for pos, item in enumerate(dataset) if fn(item)]
+        self._length = len(self._indices)
 
-    def __iter__(self):
-        return iter(self._indices)
-
-    def __len__(self):
-        return len(self._indices)
+    def _positions(self):
+        return self._indices
 
 
 class IntervalSampler(Sampler):

@@ -695,6 +695,10 @@ static SkPlan plan_streamk(int tiles, int num_k, int G, bool allowed) {
   SkPlan p = {tiles, 0, 0};
   const int rem = tiles % G;
   if (!allowed || num_k < 8 || rem == 0) return p;
+  // Measured: with whole rounds before it, the stream-K remainder (fp32 pieces + the finishing launch, about 15 us on
+  // 8192-row outputs) costs more than the idle SMs of a partial last round; it pays when there are fewer tiles than CTAs
+  // (a weight gradient with a long contraction: 45.7 -> 37.6 us for 2304 x 768 x 8192).
+  if (tiles >= G) return p;
   const long total = (long)rem * num_k;
   int min_per = (num_k + 5) / 6;
   if (min_per < 6) min_per = 6;
