@@ -8,8 +8,23 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
 def run(name, unit, items_per_step_per_gpu, make_step, args, config, baseline=None):
+    """Measure, print the JSON line on rank 0 and shut the process group down (the stand-alone benchmark scripts)."""
+    from mxnet_b200.parallel import dist
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rec = measure(name, unit, items_per_step_per_gpu, make_step, args, config, baseline)
+    if dist.rank() == 0:
+        print(json.dumps(rec))
+    if world > 1:
+        import torch
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy()
+    return 0
+
+
+def measure(name, unit, items_per_step_per_gpu, make_step, args, config, baseline=None):
     """``make_step(ctx, rank, world)`` returns ``step()`` which runs one training iteration and returns
-    the loss NDArray."""
+    the loss NDArray.  Returns the result record (the same on every rank up to rank-0-only fields)."""
     import torch
     import mxnet_b200 as mx
     from mxnet_b200.ops import cuda as kernels
@@ -48,26 +63,21 @@ def run(name, unit, items_per_step_per_gpu, make_step, args, config, baseline=No
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms = float(t.item())
     value = items_per_step_per_gpu * world * args.steps / (ms / 1e3)
-    if rank == 0:
-        cfg = dict(config)
-        cfg['parallelism'] = 'dp%d' % world
-        from mxnet_b200.ops.cuda import gemm_ops
-        tuned = gemm_ops.tuned_choices()
-        if tuned:
-            cfg['gemm_in_tree_kernel_chosen'] = {p: '%d of %d' % (sum(1 for k, v in tuned.items() if k[0] == p and v),
-                                                                  sum(1 for k in tuned if k[0] == p))
-                                                 for p in ('fwd', 'dgrad', 'wgrad')}
-        from mxnet_b200.ops.cuda import rnn_ops
-        if rnn_ops.tuned_choices():
-            cfg['rnn_in_tree_kernel_chosen'] = {'%s T=%d N=%d I=%d H=%d L=%d %s' % (k[0], k[2], k[3], k[4], k[5], k[6],
-                                                                                   'train' if k[8] else 'eval'): bool(v)
-                                                for k, v in rnn_ops.tuned_choices().items()}
-        print(json.dumps({'metric': name, 'value': value, 'unit': unit, 'n_gpus': world, 'steps': args.steps,
-                          'warmup': max(args.warmup, 3), 'ms_per_step': ms / args.steps, 'higher_is_better': True,
-                          'scaling': 'weak', 'vs_baseline': (value / baseline) if baseline else None, 'data': 'synthetic',
-                          'config': cfg, 'clocks': {k: clocks[k] for k in ('sm_mhz', 'sm_max_mhz', 'reasons')},
-                          'gpu_launches': int(launches), 'final_loss': float(loss.mean().asscalar())}))
-    if world > 1:
-        barrier()
-        dist.destroy()
-    return 0
+    cfg = dict(config)
+    cfg['parallelism'] = 'dp%d' % world
+    from mxnet_b200.ops.cuda import gemm_ops
+    tuned = gemm_ops.tuned_choices()
+    if tuned:
+        cfg['gemm_in_tree_kernel_chosen'] = {p: '%d of %d' % (sum(1 for k, v in tuned.items() if k[0] == p and v),
+                                                              sum(1 for k in tuned if k[0] == p))
+                                             for p in ('fwd', 'dgrad', 'wgrad')}
+    from mxnet_b200.ops.cuda import rnn_ops
+    if rnn_ops.tuned_choices():
+        cfg['rnn_in_tree_kernel_chosen'] = {'%s T=%d N=%d I=%d H=%d L=%d %s' % (k[0], k[2], k[3], k[4], k[5], k[6],
+                                                                               'train' if k[8] else 'eval'): bool(v)
+                                            for k, v in rnn_ops.tuned_choices().items()}
+    return {'metric': name, 'value': value, 'unit': unit, 'n_gpus': world, 'steps': args.steps,
+            'warmup': max(args.warmup, 3), 'ms_per_step': ms / args.steps, 'higher_is_better': True,
+            'scaling': 'weak', 'vs_baseline': (value / baseline) if baseline else None, 'data': 'synthetic',
+            'config': cfg, 'clocks': {k: clocks[k] for k in ('sm_mhz', 'sm_max_mhz', 'reasons')},
+            'gpu_launches': int(launches), 'final_loss': float(loss.mean().asscalar())}

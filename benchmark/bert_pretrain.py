@@ -11,7 +11,7 @@ import sys
 import _harness
 
 
-def main():
+def parser():
     ap = argparse.ArgumentParser()
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
@@ -21,8 +21,11 @@ def main():
     ap.add_argument('--dtype', default='float16', choices=['float16', 'bfloat16'])
     ap.add_argument('--layers', type=int, default=12)
     ap.add_argument('--graphs', type=int, default=1, help='hybridize(static_alloc, static_shape): CUDA-graph replay')
-    args = ap.parse_args()
+    return ap
 
+
+def spec(args):
+    """``(metric, unit, items per step and GPU, make_step, config)`` of this benchmark for the shared harness."""
     def make_step(ctx, rank, world):
         import numpy as np
         import mxnet_b200 as mx
@@ -65,7 +68,13 @@ def main():
         return step
     cfg = {'model': 'bert_base' if args.layers == 12 else 'bert_%dL' % args.layers, 'batch_per_gpu': args.batch,
            'seq_len': args.seq_len, 'masked_per_seq': args.masked, 'optimizer': 'lamb (multi-precision)', 'amp': args.dtype, 'cuda_graphs': bool(args.graphs)}
-    return _harness.run('bert_pretrain_seq_per_s', 'seq/s', args.batch, make_step, args, cfg)
+    return 'bert_pretrain_seq_per_s', 'seq/s', args.batch, make_step, cfg
+
+
+def main():
+    args = parser().parse_args()
+    name, unit, items, make_step, cfg = spec(args)
+    return _harness.run(name, unit, items, make_step, args, cfg)
 
 
 if __name__ == '__main__':

@@ -11,15 +11,18 @@ import sys
 import _harness
 
 
-def main():
+def parser():
     ap = argparse.ArgumentParser()
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--batch', type=int, default=80)
     ap.add_argument('--bptt', type=int, default=35)
     ap.add_argument('--dtype', default='float32', choices=['float32', 'float16'])
-    args = ap.parse_args()
+    return ap
 
+
+def spec(args):
+    """``(metric, unit, items per step and GPU, make_step, config)`` of this benchmark for the shared harness."""
     def make_step(ctx, rank, world):
         import numpy as np
         import mxnet_b200 as mx
@@ -58,7 +61,13 @@ def main():
         return step
     cfg = {'model': 'lstm_lm_2x650', 'batch_per_gpu': args.batch, 'bptt': args.bptt, 'vocab': 33278,
            'optimizer': 'sgd + global-norm clip 0.25', 'dtype': args.dtype}
-    return _harness.run('lstm_lm_tokens_per_s', 'tokens/s', args.batch * args.bptt, make_step, args, cfg)
+    return 'lstm_lm_tokens_per_s', 'tokens/s', args.batch * args.bptt, make_step, cfg
+
+
+def main():
+    args = parser().parse_args()
+    name, unit, items, make_step, cfg = spec(args)
+    return _harness.run(name, unit, items, make_step, args, cfg)
 
 
 if __name__ == '__main__':

@@ -33,3 +33,15 @@ def require(t, name, numel=None, dtype=None, device=None, shape=None):
     if shape is not None and tuple(t.shape) != tuple(shape):
         raise ValueError('%s has shape %s, expected %s' % (name, tuple(t.shape), tuple(shape)))
     return t
+
+
+def job_wide(choice):
+    """The autotuning verdict of rank 0 for every rank of a multi-process job: each rank times the candidates itself (so
+    all of them reach this point together, after the same work), then adopts rank 0's choice, so that one layer runs the
+    same kernel, with the same rounding, on every GPU of the job.  A single process returns its own verdict."""
+    from ...parallel import dist
+    if not dist.is_initialized() or dist.world_size() < 2:
+        return bool(choice)
+    flag = torch.tensor([1 if choice else 0], dtype=torch.int32, device='cuda')
+    dist.broadcast_(flag, 0)
+    return bool(int(flag.item()))

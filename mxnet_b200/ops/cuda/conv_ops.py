@@ -14,7 +14,7 @@ import os
 import torch
 
 from . import lib, ptr, stream_ptr, count_launch, check
-from ._util import dt, require
+from ._util import dt, require, job_wide
 from .gemm_ops import _error_flag
 
 _DEFAULT = 'auto'
@@ -69,7 +69,7 @@ def use_own(direction, dirs, key, own_fn, lib_fn, lib_extra_us=0.0):
         if torch.cuda.is_current_stream_capturing():
             return False                   # cannot time inside a capture; the eager warm-up run normally comes first
         with torch.no_grad():
-            hit = _tuned[k] = _time_us(own_fn) <= _MARGIN * (_time_us(lib_fn) + lib_extra_us)
+            hit = _tuned[k] = job_wide(_time_us(own_fn) <= _MARGIN * (_time_us(lib_fn) + lib_extra_us))
     return hit
 
 
