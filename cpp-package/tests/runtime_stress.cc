@@ -140,9 +140,12 @@ void failure_propagation() {
     CHECK(mxb_engine_wait_var(e, c, err, sizeof(err)) == 0, "unrelated var carries an error: %s", err);
     CHECK(mxb_engine_wait_var(e, b, err, sizeof(err)) != 0 && std::strstr(err, "expected failure") != nullptr,
           "dependant var has no error (naive=%d): '%s'", naive, err);
-    CHECK(mxb_engine_wait_var(e, b, err, sizeof(err)) != 0, "the error is gone on the second wait");
+    CHECK(mxb_engine_wait_var(e, b, err, sizeof(err)) == 0, "a failure is reported by one wait only");
     CHECK(ran_dependant.load() == 0, "the dependant ran although its input failed");
     CHECK(ran_other.load() == 1, "the unrelated operation did not run");
+    CHECK(mxb_engine_wait_all(e, err, sizeof(err)) == 0, "wait_all repeats a failure that a wait on a var has reported");
+    // a failure that no wait on a var picks up is reported by wait_all, once
+    mxb_engine_push(e, fail_op, nullptr, nullptr, 0, &a, 1, 0, "fails again");
     CHECK(mxb_engine_wait_all(e, err, sizeof(err)) != 0, "wait_all did not report the failure");
     CHECK(mxb_engine_wait_all(e, err, sizeof(err)) == 0, "wait_all reports the failure twice");
     std::atomic<int> after{0};

@@ -25,6 +25,7 @@ class _State(threading.local):
 state = _State()
 
 # process-wide hooks (set by mxnet_b200.amp / profiler); kept here to avoid import cycles
+naive_engine = __import__('os').environ.get('MXNET_ENGINE_TYPE') == 'NaiveEngine'   # kept current by env.set
 amp_hook = None          # callable(opname, tensors:list) -> list, or None
 op_monitor = None        # callable(opname, outputs) for register_op_hook style monitors
 profiler_hook = None     # callable(opname) -> context manager, or None

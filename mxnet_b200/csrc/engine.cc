@@ -6,7 +6,7 @@
 //    one of them has granted access; dispatch order among ready operations follows priority,
 //    then submission order;
 //  * a failing operation stores its error in the vars it mutates; operations that depend on a
-//    failed var are skipped and pass the error on; WaitForVar / WaitForAll rethrow it;
+//    failed var are skipped and pass the error on; WaitForVar / WaitForAll rethrow it, once;
 //  * a naive mode runs everything inline in the pushing thread (deterministic debugging).
 // What differs: GPU work is ordered by CUDA streams and events, so this engine only schedules host
 // tasks (data pipeline stages, checkpoint writers, KVStore control messages, Python callbacks).
@@ -58,9 +58,14 @@ struct OprOrder {
 
 class Engine {
  public:
-  Engine(bool naive, int nworkers) : naive_(naive) {
+  // nprio == 0: one pool of workers serves one priority queue (the pooled policy, src/engine/threaded_engine_pooled.cc).
+  // nprio > 0: `nprio` further workers serve ONLY operations pushed with a positive priority, which have a queue of
+  // their own, so urgent work (gradient exchange control, batch hand-over) never waits behind long ordinary tasks
+  // that already occupy every ordinary worker (the high-priority CPU pool of src/engine/threaded_engine_perdevice.cc).
+  Engine(bool naive, int nworkers, int nprio = 0) : naive_(naive), split_(nprio > 0) {
     if (!naive_) {
-      for (int i = 0; i < nworkers; ++i) workers_.emplace_back([this] { WorkerLoop(); });
+      for (int i = 0; i < nworkers; ++i) workers_.emplace_back([this] { WorkerLoop(&ready_); });
+      for (int i = 0; i < nprio; ++i) workers_.emplace_back([this] { WorkerLoop(&urgent_); });
     }
   }
   ~Engine() {
@@ -130,9 +135,20 @@ class Engine {
       std::unique_lock<std::mutex> lk(s.mu);
       s.cv.wait(lk, [&] { return s.done; });
     }
-    std::lock_guard<std::mutex> lk(v->mu);
-    if (!v->error.empty()) { Copy(v->error, err, errlen); return 1; }
-    return 0;
+    // A failure is reported once: the wait that raises it clears it from the var (later readers run again) and from
+    // the engine-wide record that WaitForAll reports (src/engine/threaded_engine.h ThrowException does the same).
+    std::string e;
+    {
+      std::lock_guard<std::mutex> lk(v->mu);
+      e.swap(v->error);
+    }
+    if (e.empty()) return 0;
+    {
+      std::lock_guard<std::mutex> lk(emu_);
+      if (first_error_ == e) first_error_.clear();
+    }
+    Copy(e, err, errlen);
+    return 1;
   }
 
   int WaitForAll(char* err, int errlen) {
@@ -165,21 +181,23 @@ class Engine {
     if (op->wait.fetch_sub(1) == 1) {
       {
         std::lock_guard<std::mutex> lk(qmu_);
-        ready_.push(op);
+        (split_ && op->priority > 0 ? urgent_ : ready_).push(op);
       }
-      qcv_.notify_one();
+      qcv_.notify_all();
     }
   }
 
-  void WorkerLoop() {
+  using Queue = std::priority_queue<Opr*, std::vector<Opr*>, OprOrder>;
+
+  void WorkerLoop(Queue* q) {
     for (;;) {
       Opr* op;
       {
         std::unique_lock<std::mutex> lk(qmu_);
-        qcv_.wait(lk, [this] { return stop_ || !ready_.empty(); });
-        if (stop_ && ready_.empty()) return;
-        op = ready_.top();
-        ready_.pop();
+        qcv_.wait(lk, [this, q] { return stop_ || !q->empty(); });
+        if (stop_ && q->empty()) return;
+        op = q->top();
+        q->pop();
       }
       Execute(op);
     }
@@ -254,8 +272,10 @@ class Engine {
   }
 
   bool naive_;
+  bool split_;
   std::vector<std::thread> workers_;
   std::priority_queue<Opr*, std::vector<Opr*>, OprOrder> ready_;
+  std::priority_queue<Opr*, std::vector<Opr*>, OprOrder> urgent_;
   std::mutex qmu_;
   std::condition_variable qcv_;
   bool stop_ = false;
@@ -272,6 +292,12 @@ class Engine {
 extern "C" {
 
 void* mxb_engine_create(int naive, int nworkers) { return new mxb::Engine(naive != 0, nworkers < 1 ? 1 : nworkers); }
+// kind: 0 = pooled (one queue, `nworkers` workers), 1 = naive (inline), 2 = ordinary pool + `nprio` workers that serve
+// only positive-priority operations
+void* mxb_engine_create_ex(int kind, int nworkers, int nprio) {
+  if (kind == 1) return new mxb::Engine(true, 1);
+  return new mxb::Engine(false, nworkers < 1 ? 1 : nworkers, kind == 2 ? (nprio < 1 ? 1 : nprio) : 0);
+}
 void mxb_engine_destroy(void* e) { delete static_cast<mxb::Engine*>(e); }
 void* mxb_engine_new_var(void* e) { return static_cast<mxb::Engine*>(e)->NewVar(); }
 void mxb_engine_delete_var(void* e, void* v) { static_cast<mxb::Engine*>(e)->DeleteVar(static_cast<mxb::Var*>(v)); }

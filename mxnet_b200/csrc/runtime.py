@@ -58,6 +58,7 @@ def _declare(L):
         f.restype = res
         f.argtypes = list(args)
     sig('mxb_engine_create', c_vp, c_int, c_int)
+    sig('mxb_engine_create_ex', c_vp, c_int, c_int, c_int)
     sig('mxb_engine_destroy', None, c_vp)
     sig('mxb_engine_new_var', c_vp, c_vp)
     sig('mxb_engine_delete_var', None, c_vp, c_vp)
@@ -77,6 +78,8 @@ def _declare(L):
     sig('mxb_cuda_runtime_found', c_int)
     sig('mxb_shm_open', c_vp, c_cp, c_u64, c_int, ctypes.POINTER(c_u64))
     sig('mxb_shm_close', c_int, c_cp, c_vp)
+    sig('mxb_shm_detach', c_int, c_vp)
+    sig('mxb_shm_adopt', c_vp, c_cp, ctypes.POINTER(c_u64))
     sig('mxb_ndlist_load_file', c_vp, c_cp)
     sig('mxb_ndlist_load_buffer', c_vp, c_vp, c_u64)
     sig('mxb_ndlist_free', None, c_vp)
@@ -145,8 +148,20 @@ class Engine(object):
     """Python view of the native dependency engine.  ``push(fn, read_vars, write_vars, priority)``
     schedules ``fn()``; exceptions raised by ``fn`` are carried through the vars it mutates."""
 
-    def __init__(self, naive=False, num_workers=2, num_priority_workers=2):
-        self._h = lib().mxb_engine_create(1 if naive else 0, int(num_workers + num_priority_workers))
+    def __init__(self, naive=False, num_workers=2, num_priority_workers=2, kind=None):
+        """``kind``: ``'NaiveEngine'`` (inline), ``'ThreadedEngine'`` (one pool of ``num_workers + num_priority_workers``
+        workers on one queue) or ``'ThreadedEnginePerDevice'`` (the default: ``num_priority_workers`` workers are reserved
+        for positive-priority operations)."""
+        if kind is None:
+            kind = 'NaiveEngine' if naive else 'ThreadedEnginePerDevice'
+        naive = kind == 'NaiveEngine'
+        if naive:
+            self._h = lib().mxb_engine_create_ex(1, 1, 0)
+        elif kind == 'ThreadedEngine':
+            self._h = lib().mxb_engine_create_ex(0, int(num_workers + num_priority_workers), 0)
+        else:
+            self._h = lib().mxb_engine_create_ex(2, int(num_workers), int(num_priority_workers))
+        self.kind = kind
         self.naive = naive
         self._tasks = {}
         self._errors = {}

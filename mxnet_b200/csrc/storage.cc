@@ -247,4 +247,26 @@ int mxb_shm_close(const char* name, void* payload) {
   return left;
 }
 
+// Unmaps a segment WITHOUT dropping its reference: the segment stays alive for a process that attaches later and takes
+// the reference over with mxb_shm_adopt (a data-loader worker hands a finished batch to its parent this way).
+int mxb_shm_detach(void* payload) {
+  auto* h = reinterpret_cast<mxb::ShmHeader*>(static_cast<char*>(payload) - sizeof(mxb::ShmHeader));
+  return munmap(h, h->size + sizeof(mxb::ShmHeader));
+}
+
+// Attaches to an existing segment and takes over the reference its creator left behind (no increment): the adopter's
+// mxb_shm_close is then the one that unlinks the name.
+void* mxb_shm_adopt(const char* name, uint64_t* out_size) {
+  int fd = shm_open(name, O_RDWR, 0600);
+  if (fd < 0) return nullptr;
+  struct stat st;
+  if (fstat(fd, &st) != 0) { close(fd); return nullptr; }
+  void* base = mmap(nullptr, st.st_size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (base == MAP_FAILED) return nullptr;
+  auto* h = static_cast<mxb::ShmHeader*>(base);
+  if (out_size) *out_size = h->size;
+  return static_cast<char*>(base) + sizeof(mxb::ShmHeader);
+}
+
 }  // extern "C"

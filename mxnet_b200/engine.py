@@ -18,13 +18,15 @@ from __future__ import annotations
 
 import contextlib
 import threading
+import weakref
 
 import torch
 
 from . import _state, env
 from .base import MXNetError
 
-__all__ = ['bulk', 'set_bulk_size', 'waitall', 'streams', 'is_naive', 'push_async_error', 'native']
+__all__ = ['bulk', 'set_bulk_size', 'waitall', 'streams', 'is_naive', 'push_async_error', 'native', 'push', 'wait_for',
+           'var_of', 'to_device_async', 'pinned_pool']
 
 _pending = []
 _pending_lock = threading.Lock()
@@ -197,7 +199,132 @@ def native():
     global _native
     if _native is None:
         from .csrc import runtime
-        _native = runtime.Engine(naive=is_naive(),
+        kind = env.get('MXNET_ENGINE_TYPE')
+        _native = runtime.Engine(kind=kind if kind in ('NaiveEngine', 'ThreadedEngine') else 'ThreadedEnginePerDevice',
                                  num_workers=max(1, int(env.get('MXNET_CPU_WORKER_NTHREADS'))),
                                  num_priority_workers=max(1, int(env.get('MXNET_CPU_PRIORITY_NTHREADS'))))
     return _native
+
+
+# ---- host tasks with array dependencies --------------------------------------------------------------------------
+# Arrays take part in the host engine's ordering through a variable that is created the first time a host task names
+# the array (reference: every NDArray owns an engine variable, include/mxnet/ndarray.h `var()`).  Device work is ordered
+# by streams and events; the variable orders HOST tasks (prefetching, file I/O, asynchronous loads) among themselves and
+# against the sync points `wait_to_read`, `asnumpy` and `waitall`, and carries their exceptions there.
+_vars = {}                      # id(array) -> (weak reference, variable): identity, not ==, decides (arrays compare elementwise)
+_vars_lock = threading.Lock()
+
+
+_tls = threading.local()
+
+
+def in_task():
+    """True on an engine worker thread while it runs a task (sync points must not wait on the engine from there: the
+    task's dependencies are already satisfied, and a nested wait would occupy a second worker)."""
+    return getattr(_tls, 'depth', 0) > 0
+
+
+def _as_task(fn):
+    def run():
+        _tls.depth = getattr(_tls, 'depth', 0) + 1
+        try:
+            fn()
+        finally:
+            _tls.depth -= 1
+    return run
+
+
+def var_of(arr, create=True):
+    """The engine variable of an array (or of any weak-referenceable object), created on first use."""
+    key = id(arr)
+    with _vars_lock:
+        hit = _vars.get(key)
+        if hit is not None and hit[0]() is arr:
+            return hit[1]
+        if not create:
+            return None
+        v = native().new_var()
+
+        def forget(_ref, key=key):
+            with _vars_lock:
+                cur = _vars.get(key)
+                if cur is not None and cur[0] is _ref:
+                    del _vars[key]
+        _vars[key] = (weakref.ref(arr, forget), v)
+        return v
+
+
+def _as_vars(items):
+    from .csrc.runtime import Var
+    return [x if isinstance(x, Var) else var_of(x) for x in items]
+
+
+def push(fn, reads=(), writes=(), priority=0, name='task'):
+    """Schedule the host function ``fn()`` after every earlier task that writes one of ``reads`` / ``writes`` and after
+    every earlier reader of ``writes`` (``Engine::PushAsync``, include/mxnet/engine.h:213-300).  ``reads`` / ``writes``
+    hold arrays or engine variables.  An exception raised by ``fn`` is stored in the variables it writes and raised by
+    the next ``wait_to_read`` / ``asnumpy`` of such an array, or by ``waitall``; tasks that depend on a failed variable
+    are not run and pass the failure on.  Under ``MXNET_ENGINE_TYPE=NaiveEngine`` the task runs before ``push``
+    returns and its exception is raised here."""
+    eng = native()
+    r, w = _as_vars(reads), _as_vars(writes)
+    if _state.naive_engine or eng.naive:
+        for v in r + w:                 # earlier asynchronous tasks on these variables (and their failures) first
+            eng.wait_for_var(v)
+        fn()
+        return
+    eng.push(_as_task(fn), r, w, priority, name)
+
+
+def wait_for(arr):
+    """Block until the host tasks that write ``arr`` have finished; raise what they raised."""
+    if _native is None or in_task():
+        return
+    v = var_of(arr, create=False)
+    if v is not None:
+        _native.wait_for_var(v)
+
+
+# ---- pinned staging memory and asynchronous host -> device copies ----------------------------------------------------
+_pinned = None
+
+
+def pinned_pool():
+    """The pool of page-locked host buffers (native storage manager, rounded size classes) that stages batches for
+    host -> device copies; ``None`` without a CUDA runtime."""
+    global _pinned
+    if _pinned is None and torch.cuda.is_available():
+        from .csrc import runtime
+        _pinned = runtime.Pool(3, 0, 'Round')
+    return _pinned
+
+
+def pinned_like(t):
+    """A page-locked tensor of the shape and dtype of the host tensor ``t``, from the pinned pool (handed back to the pool
+    when the tensor is collected), filled with ``t``'s values."""
+    pool = pinned_pool()
+    if pool is None or t.is_cuda or t.numel() == 0:
+        return t
+    import ctypes
+    nbytes = t.numel() * t.element_size()
+    ptr, rounded = pool.alloc(nbytes)
+    raw = (ctypes.c_uint8 * nbytes).from_address(ptr)
+    out = torch.frombuffer(raw, dtype=torch.uint8).view(t.dtype).view(t.shape)
+    weakref.finalize(raw, pool.free, ptr, rounded)        # `raw` lives as long as the tensor's storage refers to it
+    out.copy_(t)
+    return out
+
+
+def to_device_async(t, device):
+    """Copy a host tensor to ``device`` on the device's copy-in stream and make the compute stream wait for it with an
+    event (no host block): compute that is already queued keeps running while the bytes travel.  Pageable memory falls
+    back to an ordinary copy."""
+    if t.is_cuda or not t.is_pinned():
+        return t.to(device, non_blocking=True)
+    st = streams(device)
+    compute = torch.cuda.current_stream(device)
+    with torch.cuda.stream(st.copy_in):
+        out = t.to(device, non_blocking=True)
+    st.order(st.copy_in, compute)
+    out.record_stream(compute)
+    return out

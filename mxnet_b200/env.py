@@ -50,6 +50,14 @@ def set(name, value):  # pylint: disable=redefined-builtin
         os.environ.pop(name, None)
     else:
         os.environ[name] = str(int(value)) if isinstance(value, bool) else str(value)
+    if name == 'MXNET_ENGINE_TYPE':
+        _refresh_engine_type()
+
+
+def _refresh_engine_type():
+    """Mirror ``MXNET_ENGINE_TYPE`` into the flag the operator entry point reads on every call."""
+    from . import _state
+    _state.naive_engine = os.environ.get('MXNET_ENGINE_TYPE') == 'NaiveEngine'
 
 
 @contextlib.contextmanager

@@ -1,12 +1,20 @@
 """DataLoader (``python/mxnet/gluon/data/dataloader.py``): batches a Dataset with worker processes or
 threads, optional pinned-memory staging and prefetching.
 
-Worker processes return batches as NumPy arrays through POSIX shared memory (the reference rebuilds
-NDArrays over ``cpu_shared`` storage, ``dataloader.py:47-95``); the parent wraps them, optionally
-into page-locked buffers so the host→device copy can overlap compute on the copy-in stream."""
+Worker processes put the arrays of a batch into POSIX shared-memory segments of the native storage
+manager (``csrc/storage.cc``) and send only the segment names; the parent maps the segments and wraps
+them without another copy (the reference rebuilds NDArrays over ``cpu_shared`` storage,
+``dataloader.py:47-95``).  With ``pin_memory`` the batch is staged in page-locked buffers from the
+native pinned pool, so the host→device copy runs on the copy-in stream and overlaps compute."""
+import atexit
+import ctypes
+import glob
+import itertools
 import multiprocessing
+import os
 import pickle
 import threading
+import weakref
 from concurrent.futures import ThreadPoolExecutor
 
 import numpy as np
@@ -20,22 +28,84 @@ from .batchify import default_batchify_fn
 __all__ = ['DataLoader']
 
 
-def _to_numpy_tree(batch):
+shm_batches = 0          # arrays received through shared-memory segments (observable by tests)
+_segment_counter = itertools.count()
+
+
+def _rt():
+    from ...csrc import runtime
+    return runtime.lib()
+
+
+def _segment_prefix(owner_pid):
+    return '/mxb_dl_%d_' % owner_pid
+
+
+def _to_shared(a, owner_pid):
+    """Copy a NumPy array into a fresh shared segment named after the process that will own it; returns what the owner
+    needs to map it.  The creating process unmaps without dropping the reference: the owner adopts it."""
+    a = np.ascontiguousarray(a)
+    name = '%s%d_%d' % (_segment_prefix(owner_pid), os.getpid(), next(_segment_counter))
+    L = _rt()
+    ptr = L.mxb_shm_open(name.encode(), max(a.nbytes, 1), 1, None)
+    if not ptr:
+        return None
+    if a.nbytes:
+        ctypes.memmove(ptr, a.ctypes.data, a.nbytes)
+    L.mxb_shm_detach(ctypes.c_void_p(ptr))
+    return name, a.shape, a.dtype.str
+
+
+def _from_shared(name, shape, dtype):
+    """Map a segment created by a worker; the returned array views the mapping, which is released (and the name
+    unlinked) when the array's buffer is collected."""
+    global shm_batches
+    L = _rt()
+    size = ctypes.c_uint64(0)
+    ptr = L.mxb_shm_adopt(name.encode(), ctypes.byref(size))
+    if not ptr:
+        raise RuntimeError('shared-memory segment %s of a data-loader worker is gone' % name)
+    nbytes = int(np.prod(shape, dtype=np.int64)) * np.dtype(dtype).itemsize
+    raw = (ctypes.c_uint8 * max(nbytes, 1)).from_address(ptr)
+    weakref.finalize(raw, L.mxb_shm_close, name.encode(), ctypes.c_void_p(ptr))
+    shm_batches += 1
+    return np.frombuffer(raw, dtype=np.dtype(dtype), count=int(np.prod(shape, dtype=np.int64))).reshape(shape)
+
+
+def _cleanup_segments():
+    """Segments addressed to this process that were never adopted (a worker finished after the iterator was dropped)."""
+    for path in glob.glob('/dev/shm' + _segment_prefix(os.getpid()) + '*'):
+        try:
+            os.unlink(path)
+        except OSError:
+            pass
+
+
+atexit.register(_cleanup_segments)
+
+
+def _to_numpy_tree(batch, owner_pid=None):
+    """A batch as a picklable tree; with ``owner_pid`` the arrays travel as shared-memory segments for that process."""
     if isinstance(batch, NDArray):
-        return ('nd', batch.asnumpy(), str(batch._data.dtype))
+        a = batch.asnumpy()
+        shared = _to_shared(a, owner_pid) if owner_pid is not None and a.nbytes >= 1024 else None
+        if shared is not None:
+            return ('shm', shared, str(batch._data.dtype))
+        return ('nd', a, str(batch._data.dtype))
     if isinstance(batch, (list, tuple)):
-        return ('seq', [_to_numpy_tree(b) for b in batch], isinstance(batch, tuple))
+        return ('seq', [_to_numpy_tree(b, owner_pid) for b in batch], isinstance(batch, tuple))
     return ('raw', batch, None)
 
 
 def _from_numpy_tree(tree, pin_memory=False):
     kind, val, extra = tree
-    if kind == 'nd':
-        t = torch.from_numpy(val)
+    if kind in ('nd', 'shm'):
+        t = torch.from_numpy(_from_shared(*val) if kind == 'shm' else val)
         if extra == 'torch.bfloat16':
             t = t.to(torch.bfloat16)
         if pin_memory and torch.cuda.is_available():
-            t = t.pin_memory()
+            from ... import engine
+            t = engine.pinned_like(t)          # pooled page-locked staging buffer; the shared segment is released
         if is_np_array():
             from ...numpy.multiarray import ndarray
             return ndarray._from_tensor(t)
@@ -65,7 +135,7 @@ def _worker_fn(samples, batchify_fn, dataset=None):
     global _worker_dataset
     ds = dataset if dataset is not None else _worker_dataset
     batch = batchify_fn([ds[i] for i in samples])
-    return pickle.dumps(_to_numpy_tree(batch), pickle.HIGHEST_PROTOCOL)
+    return pickle.dumps(_to_numpy_tree(batch, os.getppid()), pickle.HIGHEST_PROTOCOL)
 
 
 def _thread_worker_fn(samples, batchify_fn, dataset):

@@ -249,43 +249,45 @@ class ResizeIter(DataIter):
 
 
 class PrefetchingIter(DataIter):
-    """Fetch batches of one or several iterators on background threads."""
+    """Fetches the next batch of one or several iterators ahead of time as tasks of the host engine (one engine
+    variable per iterator serialises its fetches); ``next`` waits for those variables, so a failure inside an
+    underlying iterator is raised by ``next`` instead of being lost on a background thread."""
 
     def __init__(self, iters, rename_data=None, rename_label=None):
         super().__init__()
+        from .. import engine
         if not isinstance(iters, list):
             iters = [iters]
         self.n_iter = len(iters)
         assert self.n_iter > 0
         self.iters, self.rename_data, self.rename_label = iters, rename_data, rename_label
         self.batch_size = self.provide_data[0][1][0]
-        self.data_ready = [threading.Event() for _ in range(self.n_iter)]
-        self.data_taken = [threading.Event() for _ in range(self.n_iter)]
-        for e in self.data_taken:
-            e.set()
-        self.started = True
-        self.current_batch = [None] * self.n_iter
+        self.current_batch = None
         self.next_batch = [None] * self.n_iter
+        self._engine = engine
+        self._vars = [engine.native().new_var() for _ in range(self.n_iter)]
+        self.started = True
+        self._fetch()
 
-        def prefetch_func(self, i):
-            while True:
-                self.data_taken[i].wait()
-                if not self.started:
-                    break
-                try:
-                    self.next_batch[i] = self.iters[i].next()
-                except StopIteration:
-                    self.next_batch[i] = None
-                self.data_taken[i].clear()
-                self.data_ready[i].set()
-        self.prefetch_threads = [threading.Thread(target=prefetch_func, args=[self, i], daemon=True) for i in range(self.n_iter)]
-        for t in self.prefetch_threads:
-            t.start()
+    def _fetch(self):
+        def load(i):
+            try:
+                self.next_batch[i] = self.iters[i].next()
+            except StopIteration:
+                self.next_batch[i] = None
+        for i in range(self.n_iter):
+            self._engine.push(lambda i=i: load(i), writes=[self._vars[i]], name='prefetch')
+
+    def _wait(self, swallow=False):
+        for v in self._vars:
+            try:
+                self._engine.native().wait_for_var(v)
+            except Exception:  # pylint: disable=broad-except
+                if not swallow:
+                    raise
 
     def __del__(self):
         self.started = False
-        for e in self.data_taken:
-            e.set()
 
     @property
     def provide_data(self):
@@ -302,18 +304,13 @@ class PrefetchingIter(DataIter):
                     for r, i in zip(self.rename_label, self.iters)], [])
 
     def reset(self):
-        for e in self.data_ready:
-            e.wait()
+        self._wait(swallow=True)         # the fetch in flight ends first; what it raised belongs to the old epoch
         for i in self.iters:
             i.reset()
-        for e in self.data_ready:
-            e.clear()
-        for e in self.data_taken:
-            e.set()
+        self._fetch()
 
     def iter_next(self):
-        for e in self.data_ready:
-            e.wait()
+        self._wait()
         if self.next_batch[0] is None:
             for i in self.next_batch:
                 assert i is None, 'Number of entry mismatches between iterators'
@@ -324,10 +321,7 @@ class PrefetchingIter(DataIter):
                                        sum([batch.label for batch in self.next_batch], []),
                                        self.next_batch[0].pad, self.next_batch[0].index,
                                        provide_data=self.provide_data, provide_label=self.provide_label)
-        for e in self.data_ready:
-            e.clear()
-        for e in self.data_taken:
-            e.set()
+        self._fetch()
         return True
 
     def next(self):

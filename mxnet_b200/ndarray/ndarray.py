@@ -155,6 +155,8 @@ class NDArray(object):
     # ------------------------------------------------------------------ host transfer / sync
     def asnumpy(self):
         """Blocking copy to a ``numpy.ndarray`` (``SyncCopyToCPU``)."""
+        from .. import engine
+        engine.wait_for(self)                   # host tasks that write this array (and their exceptions)
         t = self._data.detach()
         if t.dtype == torch.bfloat16:
             t = t.float()
@@ -175,11 +177,11 @@ class NDArray(object):
 
     def wait_to_read(self):
         """Block until every pending write to this array has finished (``WaitToRead``)."""
+        from .. import engine
+        engine.wait_for(self)
         if self._data.is_cuda:
-            from .. import engine
             engine._sync_device(self._data.device)
-        from .. import engine as _e
-        _e._rethrow_pending()
+        engine._rethrow_pending()
 
     wait_to_write = wait_to_read
 
@@ -217,6 +219,10 @@ class NDArray(object):
             return r
         if _state.state.recording and self._data.requires_grad:
             t = self._data.to(context.torch_device)
+        elif context.torch_device.type == 'cuda' and not self._data.is_cuda:
+            from .. import engine
+            engine.wait_for(self)
+            t = engine.to_device_async(self._data.detach(), context.torch_device)   # copy-in stream when the source is pinned
         else:
             t = self._data.detach().to(context.torch_device, non_blocking=True)
         return self.__class__._from_tensor(t, context)

@@ -99,8 +99,7 @@ def _build_writer(data):
     return L, w
 
 
-def save(fname, data):
-    """Save arrays (list or ``{name: array}``) in the legacy binary container."""
+def _save_now(fname, data):
     L, w = _build_writer(data)
     try:
         rc = L.mxb_ndwriter_save(w, str(fname).encode())
@@ -108,6 +107,23 @@ def save(fname, data):
         L.mxb_ndwriter_free(w)
     if rc != 0:
         raise MXNetError('cannot write %s' % fname)
+
+
+def save(fname, data):
+    """Save arrays (list or ``{name: array}``) in the legacy binary container.
+
+    The write runs as a task of the host engine that READS the arrays: it starts after every pending host task that
+    writes one of them (an asynchronous load, a prefetch) and host tasks pushed later that write them wait for it; the
+    call returns when the file is complete and raises what the writer raised (``MXNDArraySave`` waits on its arrays the
+    same way, src/c_api/c_api.cc)."""
+    from .. import engine
+    arrays = [a for a in (data.values() if isinstance(data, dict) else
+                          (data if isinstance(data, (list, tuple)) else [data])) if isinstance(a, NDArray)]
+    if engine.in_task():
+        return _save_now(fname, data)
+    done = engine.native().new_var()
+    engine.push(lambda: _save_now(fname, data), reads=arrays, writes=[done], name='ndarray_save')
+    engine.native().wait_for_var(done)
 
 
 def save_tobuffer(data):

@@ -150,6 +150,10 @@ def invoke(op, args, attrs, out=None, kind=None):
                     res = op.fn(*tensors, **attrs)
             else:
                 res = op.fn(*tensors, **attrs)
+        if _state.naive_engine and ctx is not None and ctx.device_typeid == 2 and not torch.cuda.is_current_stream_capturing():
+            # MXNET_ENGINE_TYPE=NaiveEngine: every operator has finished (or failed) before its call returns, so a device
+            # error is raised by the operator that caused it (src/engine/naive_engine.cc runs each op inline)
+            torch.cuda.current_stream(ctx.torch_device).synchronize()
     except MXNetError:
         raise
     except RuntimeError as e:
