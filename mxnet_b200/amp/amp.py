@@ -121,12 +121,15 @@ def scale_loss(loss, optimizer_or_trainer):
         # the scale lives on the device (fused optimizer step): multiply by the device scalar, the
         # kernels divide it out again; the host never reads it, so there is no synchronisation here
         optimizer_or_trainer._scale = optimizer_or_trainer._amp_original_scale
-        first = loss[0] if isinstance(loss, (list, tuple)) else loss
-        s_arr = first.__class__._from_tensor(scaler._device_state[0:1], first.context)
+        def scaled(l):
+            # the copy of the scale that lives on the loss's own GPU (a single-process group keeps one per GPU)
+            state = scaler._device_states.get(l._data.device, scaler._device_state)
+            s_arr = l.__class__._from_tensor(state[0:1], l.context)
+            return l * (s_arr.astype(l.dtype) if l.dtype != s_arr.dtype else s_arr)
         if isinstance(loss, (list, tuple)):
-            yield [l * s_arr.astype(l.dtype) if l.dtype != s_arr.dtype else l * s_arr for l in loss]
+            yield [scaled(l) for l in loss]
         else:
-            yield loss * (s_arr.astype(loss.dtype) if loss.dtype != s_arr.dtype else s_arr)
+            yield scaled(loss)
         return
     s = scaler.loss_scale
     optimizer_or_trainer._scale = optimizer_or_trainer._amp_original_scale / s

@@ -17,6 +17,7 @@ class LossScaler(object):
         self._scale_seq_len = scale_seq_len
         self._unskipped = 0
         self._device_state = None       # float32[2] on device: [scale, clean steps], owned by the fused path
+        self._device_states = {}        # the same state on every GPU of a single-process group, by torch device
 
     @property
     def loss_scale(self):

@@ -162,8 +162,11 @@ class Trainer(object):
         if self._update_on_kvstore or self._contains_sparse_grad or self._contains_sparse_weight:
             return
         devices = self._devices or []
-        if len(devices) != 1 or devices[0].device_type != 'gpu' or not torch.cuda.is_available():
+        if not devices or any(d.device_type != 'gpu' for d in devices) or not torch.cuda.is_available():
             return
+        from ..parallel import dist
+        if len(devices) > 1 and dist.is_initialized() and dist.world_size() > 1:
+            return                       # several GPUs per process AND several processes: the generic kvstore path
         kv = self._kvstore
         if kv is not None and kv.type not in ('device', 'nccl', 'dist_sync', 'dist_device_sync', 'dist_sync_device'):
             return
@@ -172,7 +175,11 @@ class Trainer(object):
         from ..parallel import fused
         if not fused.supports(self._optimizer, self._params):
             return
-        self._fused = fused.FusedStep(self._params, self._optimizer, devices[0])
+        if len(devices) == 1:
+            self._fused = fused.FusedStep(self._params, self._optimizer, devices[0])
+        else:
+            # the reference's main multi-GPU mode: one process, ctx=[gpu(0), gpu(1), ...]
+            self._fused = fused.FusedStepGroup(self._params, self._optimizer, devices)
 
     def _init_params(self):
         assert self._kv_initialized, 'Cannot initialize parameters in KVStore when KVStore is not initialized.'
@@ -281,7 +288,8 @@ class Trainer(object):
     def _fused_stale(self, ignore_stale_grad):
         """Positions (in the fused step's parameter list) whose gradient backward has not refreshed: an error unless
         ``ignore_stale_grad``, in which case the fused kernels leave those parameters and their state untouched."""
-        stale = [k for k, arr in enumerate(self._fused._data_arrays) if not arr._fresh_grad]
+        replicas = self._fused.replica_arrays() if hasattr(self._fused, 'replica_arrays') else [self._fused._data_arrays]
+        stale = [k for k in range(len(replicas[0])) if not all(arrs[k]._fresh_grad for arrs in replicas)]
         if stale and not ignore_stale_grad:
             p, arr = self._fused.params[stale[0]], self._fused._data_arrays[stale[0]]
             raise UserWarning('Gradient of Parameter `%s` on device %s has not been updated by backward since last `step`; '
@@ -320,10 +328,11 @@ class Trainer(object):
             for upd, arr, grad, ok in zip(updates, datas, param.list_grad(), fresh):
                 if ok:
                     upd.append((i, grad, arr))
-                    self._consumed_pass[id(arr)] = arr._grad_pass
         for updater, upd in zip(self._updaters, updates):
             if upd:
                 i, g, w = zip(*upd)
+                for arr in w:                    # consumed only now: a step refused for a stale gradient consumes nothing
+                    self._consumed_pass[id(arr)] = arr._grad_pass
                 updater(list(i), list(g), list(w))
 
     # ------------------------------------------------------------------ states

@@ -628,6 +628,21 @@ MXB_EXPORT int mxb_ipc_open(const void* handle, void** ptr) {
   return (int)cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
 }
 MXB_EXPORT int mxb_ipc_close(void* ptr) { return (int)cudaIpcCloseMemHandle(ptr); }
+// Lets kernels and copies of device `dev` address the memory of device `peer` (both of this process).  Returns 0 also
+// when the access was enabled before; the caller's current device is left as it was.
+MXB_EXPORT int mxb_enable_peer_access(int dev, int peer) {
+  int prev = 0, can = 0;
+  cudaGetDevice(&prev);
+  cudaError_t rc = cudaDeviceCanAccessPeer(&can, dev, peer);
+  if (rc == cudaSuccess && !can) rc = cudaErrorPeerAccessUnsupported;
+  if (rc == cudaSuccess) rc = cudaSetDevice(dev);
+  if (rc == cudaSuccess) {
+    rc = cudaDeviceEnablePeerAccess(peer, 0);
+    if (rc == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); rc = cudaSuccess; }
+  }
+  cudaSetDevice(prev);
+  return (int)rc;
+}
 MXB_EXPORT int mxb_memcpy_d2h(void* dst, const void* src, uint64_t bytes, void* stream) {
   return (int)cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
 }

@@ -103,7 +103,10 @@ def supports(optimizer, params):
 
 
 class FusedStep(object):
-    def __init__(self, params, optimizer, ctx):
+    """The fused step of ONE GPU.  Its peers are either the other processes of the job (one GPU each, connected through
+    CUDA IPC) or, with ``local_group=(i, n)``, the other GPUs of this process (see :class:`FusedStepGroup`)."""
+
+    def __init__(self, params, optimizer, ctx, local_group=None):
         L = _lib()
         assert L.mxb_step_params_bytes() == C.sizeof(StepParams), 'StepParams layout mismatch'
         self.optimizer = optimizer
@@ -116,8 +119,12 @@ class FusedStep(object):
         arrs = [p._data[ctx] for p in self.params]
         self.dtype = arrs[0]._data.dtype
         self.esize = arrs[0]._data.element_size()
-        self.rank = dist.rank() if dist.is_initialized() else 0
-        self.nranks = dist.world_size() if dist.is_initialized() else 1
+        self.local_group = local_group
+        if local_group is not None:
+            self.rank, self.nranks = local_group
+        else:
+            self.rank = dist.rank() if dist.is_initialized() else 0
+            self.nranks = dist.world_size() if dist.is_initialized() else 1
         if self.nranks > _MAXR:
             raise MXNetError('the fused step supports at most %d ranks per node' % _MAXR)
         # ---- layout: every segment starts on a 16-byte boundary ------------------------------------
@@ -175,6 +182,14 @@ class FusedStep(object):
         # ---- peers ---------------------------------------------------------------------------------
         self.peer_base = [self.slab] * self.nranks
         self._opened = []
+        self._layout = (offs, vec)
+        if local_group is None:
+            self._connect_processes()
+            self._init_state()
+
+    def _connect_processes(self):
+        """Open the slabs of the other processes through CUDA IPC and start from rank 0's weights."""
+        L = _lib()
         if self.nranks > 1:
             hb = L.mxb_ipc_handle_bytes()
             handle = C.create_string_buffer(hb)
@@ -196,7 +211,11 @@ class FusedStep(object):
                 self._opened.append(p2.value)
             # every rank starts from rank 0's values
             dist.broadcast_(self.weights, 0)
-        # ---- shard-local state ---------------------------------------------------------------------
+
+    def _init_state(self):
+        """Shard-local optimizer state and the per-parameter tables (after the peers are known and the weights agree)."""
+        L = _lib()
+        offs, vec = self._layout
         n_shard = self.shard_end - self.shard_begin
         self.gred = torch.zeros(n_shard, dtype=torch.float32, device=self.device)
 
@@ -230,7 +249,7 @@ class FusedStep(object):
         self._scaler_attached = None
         self.max_norm = -1.0
         self._dt_code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[self.dtype]
-        if self.nranks > 1:
+        if self.nranks > 1 and self.local_group is None:
             torch.cuda.synchronize(self.device)
             dist.barrier()
         _live.add(self)
@@ -333,31 +352,49 @@ class FusedStep(object):
         else:
             self._skip_set = False
 
-    def _launch(self, rescale, mode, use_ls, stale=()):
-        from ..ops import cuda
-        L = _lib()
+    def _begin_step(self, mode, stale=(), count_updates=True):
+        """Host bookkeeping of one step: status of the previous one, step number, stale flags, multipliers, update counts
+        (``count_updates=False`` for the followers of a group: the optimizer object is shared)."""
         self._check_status()
         self.step_no += 1
-        opt = self.optimizer
         self._set_stale(stale if mode != MODE_PLAIN else ())
         if mode != MODE_PLAIN:
             self._refresh_multipliers()
-            skip = set(stale)
-            opt._update_count([i for k, i in enumerate(self.param_ids) if k not in skip])
-        lr = float(opt.learning_rate)
-        sp = self._params(float(rescale), mode, use_ls, lr, float(opt.wd))
-        st = cuda.stream_ptr(self.device)
-        rc = L.mxb_fused_reduce(self._dt_code, C.byref(sp), st)
-        if rc == 0:
-            rc = L.mxb_fused_lamb(self._dt_code, C.byref(sp), st) if mode == MODE_LAMB else \
-                L.mxb_fused_update(self._dt_code, C.byref(sp), st)
+            if count_updates:
+                skip = set(stale)
+                self.optimizer._update_count([i for k, i in enumerate(self.param_ids) if k not in skip])
+        opt = self.optimizer
+        return self._params(float(self._rescale), mode, self._use_ls, float(opt.learning_rate), float(opt.wd))
+
+    def _launch_reduce(self, sp):
+        from ..ops import cuda
+        L = _lib()
+        with torch.cuda.device(self.device):
+            rc = L.mxb_fused_reduce(self._dt_code, C.byref(sp), cuda.stream_ptr(self.device))
         if rc != 0:
             raise MXNetError('fused step launch failed: %s' % (L.mxb_error_string(rc).decode() if rc > 0 else rc))
-        cuda.count_launch(3 if mode == MODE_LAMB else 2)
-        self._status_host.copy_(self.status, non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record(torch.cuda.current_stream(self.device))
+        cuda.count_launch(1)
+
+    def _launch_update(self, sp, mode):
+        from ..ops import cuda
+        L = _lib()
+        with torch.cuda.device(self.device):
+            st = cuda.stream_ptr(self.device)
+            rc = L.mxb_fused_lamb(self._dt_code, C.byref(sp), st) if mode == MODE_LAMB else \
+                L.mxb_fused_update(self._dt_code, C.byref(sp), st)
+            if rc != 0:
+                raise MXNetError('fused step launch failed: %s' % (L.mxb_error_string(rc).decode() if rc > 0 else rc))
+            cuda.count_launch(2 if mode == MODE_LAMB else 1)
+            self._status_host.copy_(self.status, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
         self._status_event = ev
+
+    def _launch(self, rescale, mode, use_ls, stale=()):
+        self._rescale, self._use_ls = rescale, use_ls
+        sp = self._begin_step(mode, stale)
+        self._launch_reduce(sp)
+        self._launch_update(sp, mode)
 
     def _attach_scaler(self, scaler):
         """Move the loss scale onto the device.  Returns the ``use_loss_scale`` code for this step: 1 when
@@ -370,7 +407,9 @@ class FusedStep(object):
             return 2 if unscaled else 1
         self.scale_state[0] = float(scaler._loss_scale)
         self.scale_state[1] = float(scaler._unskipped)
-        scaler._device_state = self.scale_state
+        if scaler._device_state is None:
+            scaler._device_state = self.scale_state
+        scaler._device_states[self.device] = self.scale_state        # one copy per GPU of a group; they evolve alike
         self._scaler_attached = scaler
         return 2
 
@@ -472,3 +511,96 @@ class FusedStep(object):
                 L.mxb_ipc_close(C.c_void_p(p))
         except Exception:  # pylint: disable=broad-except
             pass
+
+
+class FusedStepGroup(object):
+    """The fused step over the GPUs of ONE process: the reference's main multi-GPU mode (``kvstore='device'`` with
+    ``ctx=[gpu(0), ...]``, src/kvstore/comm.h:482-654 reduces on a merge buffer and copies back).  Here every GPU runs the
+    same two kernels as in the one-process-per-GPU mode on its own stream: GPU ``i`` owns shard ``i`` of the arena,
+    reads the gradient arenas of the other GPUs through peer access, and stores the new weights into every arena.  The
+    kernels of different GPUs wait for each other's flags; the host launches them back to back without blocking."""
+
+    def __init__(self, params, optimizer, ctxs):
+        L = _lib()
+        n = len(ctxs)
+        if n > _MAXR:
+            raise MXNetError('the fused step supports at most %d GPUs per process' % _MAXR)
+        for a in ctxs:
+            for b in ctxs:
+                if a.device_id != b.device_id:
+                    rc = L.mxb_enable_peer_access(a.device_id, b.device_id)
+                    if rc != 0:
+                        raise MXNetError('no peer access from gpu(%d) to gpu(%d): %s'
+                                         % (a.device_id, b.device_id, L.mxb_error_string(rc).decode()))
+        self.members = [FusedStep(params, optimizer, ctx, local_group=(i, n)) for i, ctx in enumerate(ctxs)]
+        lead = self.members[0]
+        for m in self.members:
+            m.peer_base = [t.slab for t in self.members]
+        for m in self.members[1:]:
+            if (m.total, m.sizes) != (lead.total, lead.sizes):
+                raise MXNetError('the replicas of the parameters differ in shape between devices')
+            m.weights.copy_(lead.weights)           # every replica starts from the first device's values
+        for m in self.members:
+            with torch.cuda.device(m.device):
+                m._init_state()
+        for m in self.members:
+            torch.cuda.synchronize(m.device)
+        self.optimizer = optimizer
+        self.params = lead.params
+        self.nranks = n
+
+    # what the Trainer reads
+    @property
+    def _data_arrays(self):
+        return self.members[0]._data_arrays
+
+    def replica_arrays(self):
+        return [m._data_arrays for m in self.members]
+
+    def set_global_norm_clip(self, max_norm):
+        for m in self.members:
+            m.set_global_norm_clip(max_norm)
+
+    def attach_scaler(self, scaler):
+        for m in self.members:
+            m.attach_scaler(scaler)
+
+    def check_status(self, wait=False):
+        for m in self.members:
+            m.check_status(wait)
+
+    def _run(self, rescale, mode, scaler, stale):
+        sps = []
+        for k, m in enumerate(self.members):
+            # the unscaled flag is consumed by the first member; the others follow its verdict
+            if k == 0:
+                use_ls = m._attach_scaler(scaler)
+            else:
+                m.attach_scaler(scaler)
+                use_ls = use_ls if scaler is not None else 0
+            m._rescale, m._use_ls = rescale, use_ls
+            sps.append(m._begin_step(mode, stale, count_updates=(k == 0)))
+        for m, sp in zip(self.members, sps):       # every GPU's reduce is in flight before the first update is queued
+            m._launch_reduce(sp)
+        for m, sp in zip(self.members, sps):
+            m._launch_update(sp, mode)
+        if mode != MODE_PLAIN:
+            for m in self.members:
+                autograd.mark_grads_consumed(m._data_arrays)
+
+    def step(self, rescale, scaler=None, stale=()):
+        self._run(rescale, self.members[0].mode, scaler, stale)
+
+    def allreduce_only(self):
+        self._run(1.0, MODE_PLAIN, None, ())
+
+    def update_only(self, rescale, scaler=None, stale=()):
+        self._run(rescale / self.nranks, self.members[0].mode, scaler, stale)
+
+    def export_states(self, updater):
+        self.members[0].export_states(updater)      # collects the other GPUs' shards with peer copies
+
+    def import_states(self, updater, optimizer):
+        self.optimizer = optimizer
+        for m in self.members:
+            m.import_states(updater, optimizer)

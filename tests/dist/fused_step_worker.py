@@ -52,6 +52,17 @@ def run(fused, dtype, steps, ctx, rank, world, optimizer='sgd'):
         assert (trainer._fused is not None) == fused, 'fused path selection'
         if fused:
             trainer._fused._check_status()
+            if rank == 0 and optimizer == 'adam':
+                # a checkpoint written by ONE rank while the others do nothing: the shards of the other ranks are read
+                # through peer copies, so no collective is entered (`if rank == 0: trainer.save_states(...)`)
+                import pickle, tempfile
+                fname = os.path.join(tempfile.mkdtemp(), 'rank0.states')
+                trainer.save_states(fname)
+                states = pickle.loads(open(fname, 'rb').read())[0]
+                numel = sum(int(np.prod(p.shape)) for p in net.collect_params().values())
+                mean_numel = sum(int(st[0].size) for st in states.values())
+                assert mean_numel == numel, 'rank 0 did not collect every shard of the Adam state'
+                assert all(float(abs(st[0].asnumpy()).sum()) > 0 for st in states.values()), 'an Adam moment is all zero'
         return [p.data(ctx)._data.detach().float().clone() for p in net.collect_params().values()]
 
 

@@ -383,6 +383,87 @@ def test_fused_step_matches_generic_optimizer(name, kwargs):
         _close(a, b, 2e-4, 2e-5)
 
 
+def test_amp_unscale_then_step_divides_by_the_loss_scale_once():
+    """``amp.unscale(trainer)`` (the documented flow for clipping gradients by hand) followed by ``trainer.step`` on the
+    fused path: the step must not divide by the loss scale a second time.  Checked on the first step (scale still on the
+    host) and on later ones (scale on the device) against fp32 training without AMP."""
+    from mxnet_b200 import amp, env
+    ctx = mx.gpu(0)
+    rng = np.random.RandomState(21)
+    xs = [rng.randn(16, 32).astype('float32') for _ in range(3)]
+    ys = [rng.randint(0, 10, (16,)) for _ in range(3)]
+    loss_fn = gluon.loss.SoftmaxCrossEntropyLoss()
+
+    def train(use_amp):
+        mx.random.seed(3)
+        np.random.seed(3)
+        net = _tiny_net(ctx, 'float32')
+        trainer = gluon.Trainer(net.collect_params(), 'sgd', {'learning_rate': 0.1}, kvstore='device')
+        if use_amp:
+            amp.init_trainer(trainer)
+        for x, y in zip(xs, ys):
+            with autograd.record():
+                loss = loss_fn(net(nd.array(x, ctx=ctx)), nd.array(y, ctx=ctx))
+                if use_amp:
+                    with amp.scale_loss(loss, trainer) as scaled:
+                        autograd.backward(scaled)
+                else:
+                    loss.backward()
+            if use_amp:
+                amp.unscale(trainer)
+                g = net.collect_params()
+                assert max(float(p.grad(ctx).abs().max().asscalar()) for p in g.values()) < 100.0   # really unscaled
+            trainer.step(16)
+        assert trainer._fused is not None
+        return [p.data(ctx).asnumpy() for p in net.collect_params().values()]
+    ref = train(False)
+    amp._reset()
+    amp.init('float16', target_precision_ops=[], fp32_ops=[])      # loss scaling only: the arithmetic stays fp32
+    try:
+        got = train(True)
+    finally:
+        amp._reset()
+    for a, b in zip(got, ref):
+        np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-5)
+
+
+def test_fused_step_skips_stale_parameters_and_follows_multiplier_changes():
+    """``step(ignore_stale_grad=True)`` leaves a parameter without a fresh gradient untouched (no weight decay, no
+    momentum drift), and a changed ``lr_mult`` takes effect: both against the generic per-parameter path."""
+    from mxnet_b200 import env
+    from mxnet_b200.gluon import nn
+    ctx = mx.gpu(0)
+    results = []
+    for fused in (True, False):
+        with env.scope('MXNET_KVSTORE_FUSED', '1' if fused else '0'):
+            mx.random.seed(4)
+            np.random.seed(4)
+            used, unused = nn.Dense(8, in_units=16), nn.Dense(4, in_units=16)
+            for blk in (used, unused):
+                blk.initialize(mx.init.Xavier(), ctx=ctx)
+            params = list(used.collect_params().values()) + list(unused.collect_params().values())
+            trainer = gluon.Trainer(params, 'adam', {'learning_rate': 0.05, 'wd': 0.1}, kvstore='device')
+            rng = np.random.RandomState(6)
+            for step in range(4):
+                x = nd.array(rng.randn(8, 16).astype('float32'), ctx=ctx)
+                with autograd.record():
+                    out = used(x) if step != 1 else (used(x).sum() + unused(x).sum())
+                    loss = (out * out).sum() if step != 1 else out * out
+                loss.backward()
+                if step == 2:
+                    used.weight.lr_mult = 0.25
+                trainer.step(8, ignore_stale_grad=(step != 1))
+            assert (trainer._fused is not None) == fused
+            with autograd.record():
+                loss = (used(x) * 2).sum()
+            loss.backward()
+            with pytest.raises(UserWarning):
+                trainer.step(8)                      # a stale gradient is an error unless the caller says otherwise
+            results.append([p.data(ctx).asnumpy() for p in params])
+    for a, b in zip(*results):
+        np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-5)
+
+
 def test_fused_step_states_round_trip(tmp_path):
     ctx = mx.gpu(0)
     net = _tiny_net(ctx, 'float32')

@@ -50,3 +50,20 @@ def test_sync_batchnorm_over_peer_memory(nproc):
     assert rep['world'] == nproc and rep['status'] == 0 and rep['status_after'] == 0
     assert rep['allreduce_max_abs_diff'] == 0.0
     assert rep['y_diff'] < 1e-4 and rep['dx_diff'] < 1e-4 and rep['mean_diff'] < 1e-5
+
+
+@pytest.mark.parametrize('ngpu', [2, 4])
+def test_single_process_multi_gpu_trainer_runs_on_the_fused_kernels(ngpu):
+    """``Trainer`` over ``ctx=[gpu(0), ..., gpu(n-1)]`` in ONE process (the reference's main multi-GPU mode): the fused
+    peer-memory step over the process's GPUs gives every replica the same weights, equal to one-GPU training on the
+    whole batch up to summation order."""
+    if torch.cuda.device_count() < ngpu:
+        pytest.skip('needs %d GPUs' % ngpu)
+    r = subprocess.run([sys.executable, os.path.join(HERE, 'dist', 'single_process_worker.py'), str(ngpu)],
+                       capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE='0'))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    rep = json.loads([l for l in r.stdout.splitlines() if l.startswith('REPORT ')][-1][len('REPORT '):])
+    assert rep['gpus'] == ngpu and rep['states_round_trip']
+    for key, tol in (('float32_sgd', 1e-5), ('float16_sgd', 5e-3), ('float32_adam', 1e-4), ('float32_lamb', 1e-4)):
+        assert rep[key]['replicas_identical'], key
+        assert rep[key]['max_abs_diff_vs_one_gpu'] < tol, (key, rep[key])
