@@ -15,7 +15,7 @@ from ..base import MXNetError
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, 'libmxb200_rt.so')
-SOURCES = ['engine.cc', 'storage.cc', 'ndarray_io.cc', 'recordio.cc', 'profiler.cc']
+SOURCES = ['engine.cc', 'storage.cc', 'ndarray_io.cc', 'recordio.cc', 'profiler.cc', 'c_api.cc']
 _lib = None
 _lock = threading.Lock()
 

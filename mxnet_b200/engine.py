@@ -294,6 +294,7 @@ def pinned_pool():
     host -> device copies; ``None`` without a CUDA runtime."""
     global _pinned
     if _pinned is None and torch.cuda.is_available():
+        torch.cuda.init()            # the tensor library reports page-locked memory as such only once it has set CUDA up
         from .csrc import runtime
         _pinned = runtime.Pool(3, 0, 'Round')
     return _pinned

@@ -41,6 +41,14 @@ def available():
 
 
 def stream_ptr(device=None):
+    """The current stream of ``device`` as a raw handle for a kernel launch that follows immediately.  The launchers
+    of the kernel library start their kernels on the CURRENT device, so this also makes ``device`` current when it is
+    not (a process that drives several GPUs runs operators on arrays of any of them; the tensor library's own
+    operators switch devices by themselves, the raw launchers cannot)."""
+    if device is not None:
+        index = device.index if isinstance(device, torch.device) else int(device)
+        if index is not None and index != torch.cuda.current_device():
+            torch.cuda.set_device(index)
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 

@@ -474,11 +474,10 @@ MXB_EXPORT int mxb_attn_forward(int dtype, const void* qkv, const float* mask, v
   p.drop_threshold = dropout > 0.f ? (uint32_t)((double)dropout * 4294967296.0) : 0u;
   p.seed = seed; p.error_flag = error_flag;
   cudaStream_t st = (cudaStream_t)stream;
-  static bool attr = false;
-  if (!attr) {
+  static unsigned long long attr_seen = 0;
+  if (first_on_device(&attr_seen)) {
     cudaFuncSetAttribute(attn_fwd_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
     cudaFuncSetAttribute(attn_fwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
-    attr = true;
   }
   if (bf16) attn_fwd_kernel<__nv_bfloat16><<<N * heads, kAttThreads, kFwdSmem, st>>>(map, p, 1);
   else attn_fwd_kernel<__half><<<N * heads, kAttThreads, kFwdSmem, st>>>(map, p, 0);
@@ -506,11 +505,10 @@ MXB_EXPORT int mxb_attn_backward(int dtype, const void* qkv, const float* mask, 
   p.drop_threshold = dropout > 0.f ? (uint32_t)((double)dropout * 4294967296.0) : 0u;
   p.seed = seed; p.error_flag = error_flag;
   cudaStream_t st = (cudaStream_t)stream;
-  static bool attr = false;
-  if (!attr) {
+  static unsigned long long attr_seen = 0;
+  if (first_on_device(&attr_seen)) {
     cudaFuncSetAttribute(attn_bwd_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
     cudaFuncSetAttribute(attn_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
-    attr = true;
   }
   if (bf16) attn_bwd_kernel<__nv_bfloat16><<<N * heads, kAttThreads, kBwdSmem, st>>>(map, map_do, p, 1);
   else attn_bwd_kernel<__half><<<N * heads, kAttThreads, kBwdSmem, st>>>(map, map_do, p, 0);

@@ -112,6 +112,17 @@ __device__ __forceinline__ void fd_divmod(uint32_t x, const FastDiv& f, uint32_t
   *r = x - *q * f.d;
 }
 
+// True the first time it is called on the current device for the bit set `seen` (one per call site): kernel function
+// attributes such as the dynamic shared-memory limit belong to a device, and one process may drive several.
+inline bool first_on_device(unsigned long long* seen) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (*seen & bit) return false;
+  *seen |= bit;
+  return true;
+}
+
 inline int sm_count() {
   static int n = 0;
   if (!n) {

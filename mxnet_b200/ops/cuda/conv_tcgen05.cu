@@ -518,11 +518,10 @@ template <typename T, int BN>
 static int launch_conv(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my, const void* bias, const void* res,
                        float* stats, ConvGeom g, int* error_flag, cudaStream_t st) {
   using Cfg = ConvCfg<BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static unsigned long long attr_seen = 0;
+  if (first_on_device(&attr_seen)) {
     cudaError_t rc = cudaFuncSetAttribute(conv_igemm_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (rc != cudaSuccess) return (int)rc;
-    attr_set = true;
   }
   // Operand buffers: when all weight slices of one column tile fit beside at least four A stages they are loaded once
   // per column tile and stay resident (the ring then carries activations only); otherwise A and B share the ring.
@@ -866,11 +865,10 @@ template <typename T, int BN>
 static int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, float* dW32, void* dW, const WgradGeom& g, int* error_flag,
                         cudaStream_t st) {
   using Cfg = ConvCfg<BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static unsigned long long attr_seen = 0;
+  if (first_on_device(&attr_seen)) {
     cudaError_t rc = cudaFuncSetAttribute(conv_wgrad_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (rc != cudaSuccess) return (int)rc;
-    attr_set = true;
   }
   const int64_t nw = (int64_t)g.Cout * g.R * g.S * g.Cin;
   cudaError_t rc = cudaMemsetAsync(dW32, 0, (size_t)nw * sizeof(float), st);

@@ -721,11 +721,10 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
                        const void* bias, int M, int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, float* ws, int a3d,
                        int b3d, int* error_flag, cudaStream_t st) {
   using Cfg = TileCfg<BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static unsigned long long attr_seen = 0;
+  if (first_on_device(&attr_seen)) {
     cudaError_t rc = cudaFuncSetAttribute(gemm_tn_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (rc != cudaSuccess) return (int)rc;
-    attr_set = true;
   }
   const int tiles_m = (M + BM - 1) / BM;
   const int tiles = tiles_m * ((N + BN - 1) / BN);
@@ -765,7 +764,10 @@ static int pick_bn(int M, int N) {
 // persistent grid is never larger).
 template <typename T, int BN>
 static int pair_capacity() {
-  static int cap = 0;
+  static int caps[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int& cap = caps[dev & 63];           // the function attribute below is per device, so is the answer
   if (cap) return cap;
   using Cfg = PairCfg<BN>;
   if (cudaFuncSetAttribute(gemm_pair_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) {

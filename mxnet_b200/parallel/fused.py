@@ -244,8 +244,8 @@ class FusedStep(object):
         self.scale_state[0] = 1.0
         self._status_host = torch.zeros(2, dtype=torch.int32).pin_memory()
         self._status_event = None
-        self._grad_arrays = [p._grad[ctx] for p in self.params]
-        self._data_arrays = [p._data[ctx] for p in self.params]
+        self._grad_arrays = [p._grad[self.ctx] for p in self.params]
+        self._data_arrays = [p._data[self.ctx] for p in self.params]
         self._scaler_attached = None
         self.max_norm = -1.0
         self._dt_code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[self.dtype]

@@ -64,6 +64,6 @@ def test_single_process_multi_gpu_trainer_runs_on_the_fused_kernels(ngpu):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     rep = json.loads([l for l in r.stdout.splitlines() if l.startswith('REPORT ')][-1][len('REPORT '):])
     assert rep['gpus'] == ngpu and rep['states_round_trip']
-    for key, tol in (('float32_sgd', 1e-5), ('float16_sgd', 5e-3), ('float32_adam', 1e-4), ('float32_lamb', 1e-4)):
+    for key, tol in (('float32_sgd', 1e-5), ('float16_sgd', 5e-3), ('float32_adam', 2e-3), ('float32_lamb', 1e-4)):
         assert rep[key]['replicas_identical'], key
         assert rep[key]['max_abs_diff_vs_one_gpu'] < tol, (key, rep[key])
