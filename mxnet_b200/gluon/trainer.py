@@ -270,6 +270,8 @@ class Trainer(object):
                     self._kvstore.pushpull(idx, grad_list, out=grad_list, priority=-i)
                 else:
                     self._kvstore.pushpull(idx, grad_list, out=param.list_data(), priority=-i)
+        if hasattr(self._kvstore, 'wait_pending'):
+            self._kvstore.wait_pending()       # the update that follows reads what the communication streams wrote
 
     def update(self, batch_size, ignore_stale_grad=False):
         if not self._kv_initialized:

@@ -19,6 +19,7 @@ of ``parallel.fused`` for dense half/float gradients and fall back to NCCL colle
 from __future__ import annotations
 
 import pickle
+from contextlib import nullcontext as _nullcontext
 
 import torch
 
@@ -46,6 +47,10 @@ class KVStore(KVStoreBase):
         self._updater_func = None
         self._str_keys = None
         self._compression = None
+        self._pending_remote = []     # (other CUDA device, event): copies of merged values onto replicas of that device
+        self._pending = {}            # CUDA device -> event of the last reduction queued on its communication streams
+        self.rows_pulled = 0          # rows moved by row_sparse_pull (observable by tests)
+        self.wire_bytes = 0           # bytes of compressed gradients sent to other devices / ranks (observable by tests)
         self._barrier_before_exit = True
         from ..parallel import dist
         self._dist = dist
@@ -101,7 +106,31 @@ class KVStore(KVStoreBase):
             return [(key, [])]
         return [(key, list(value) if isinstance(value, (list, tuple)) else [value])]
 
-    def _reduce(self, key, values, target_ctx=None):
+    # ---- communication streams: the key's priority picks the stream its reduction runs on ------------------------
+    _URGENT = -8        # the Trainer pushes parameter i with priority -i: the first few are needed first by the next forward
+
+    def _comm_stream(self, dev, priority):
+        """The side stream for a reduction whose merge buffer lives on the CUDA device ``dev``: high priority for the
+        keys the next forward pass needs first, low for the rest (src/engine/threaded_engine_perdevice.cc gives copy
+        operations their own prioritised workers).  The stream starts after everything queued so far on the compute
+        stream (the backward pass that produced the values)."""
+        from .. import engine
+        st = engine.streams(dev)
+        comm = st.comm_high if priority >= self._URGENT else st.comm_low
+        comm.wait_stream(torch.cuda.current_stream(dev))
+        return comm
+
+    def wait_pending(self):
+        """Make the compute streams wait (on the device, not the host) for the reductions still running on the
+        communication streams; called before anything consumes the merged values."""
+        for dev, ev in self._pending.items():
+            torch.cuda.current_stream(dev).wait_event(ev)
+        for dev, ev in self._pending_remote:
+            torch.cuda.current_stream(dev).wait_event(ev)
+        self._pending.clear()
+        del self._pending_remote[:]
+
+    def _reduce(self, key, values, target_ctx=None, priority=0):
         """Sum replicas on the device of the stored value (merge buffer), then across ranks."""
         if self._type == 'nccl':
             for v in values:
@@ -109,8 +138,35 @@ class KVStore(KVStoreBase):
                     raise MXNetError('kvstore nccl does not support sparse values')
         first = values[0]
         dev = first._data.device
+        side = dev.type == 'cuda' and len(values) > 1 and not torch.cuda.is_current_stream_capturing()
+        if not side:
+            return self._reduce_on_current(key, values)
+        comm = self._comm_stream(dev, priority)
+        for v in values:                          # replicas on other GPUs: their producers must have finished too
+            if v._data.is_cuda and v._data.device != dev:
+                comm.wait_stream(torch.cuda.current_stream(v._data.device))
+        with torch.cuda.stream(comm):
+            merged = self._reduce_on_current(key, values)
+            for v in values:
+                v._data.record_stream(comm)
+        ev = torch.cuda.Event()
+        ev.record(comm)
+        self._pending[dev] = ev                   # later reductions on this device are ordered after this one or ahead of it
+        merged._data.record_stream(torch.cuda.current_stream(dev))
+        return merged
+
+    def _reduce_on_current(self, key, values):
+        first = values[0]
+        dev = first._data.device
         if self._compression is not None and first._data.dtype == torch.float32:
-            parts = [self._compression.compress_roundtrip((key, i), v._data).to(dev) for i, v in enumerate(values)]
+            # what crosses to the merge device are the packed 2-bit / 1-bit codes (a sixteenth / thirty-second of the
+            # bytes); they are expanded where they are summed (src/kvstore/comm.h Reduce with gradient compression)
+            n, shape = first._data.numel(), first._data.shape
+            parts = []
+            for i, v in enumerate(values):
+                packed = self._compression.quantize((key, i), v._data)
+                self.wire_bytes += packed.numel() * packed.element_size() if v._data.device != dev else 0
+                parts.append(self._compression.dequantize(packed.to(dev, non_blocking=True), n, torch.float32).reshape(shape))
         else:
             parts = [v._data if v._data.device == dev else v._data.to(dev, non_blocking=True) for v in values]
         if len(parts) == 1:
@@ -122,7 +178,16 @@ class KVStore(KVStoreBase):
             merged = acc.to(parts[0].dtype)
         if self._dist.is_initialized() and self._dist.world_size() > 1 and \
                 (self._type.startswith('dist') or self._type in ('nccl', 'device', 'p3')):
-            merged = self._dist.all_reduce_sum(merged)
+            if self._compression is not None and merged.dtype == torch.float32:
+                # between workers the packed codes travel as well: every rank gathers the others' words and expands them
+                # (the reference's workers send compressed gradients to the server, which decompresses and sums)
+                packed = self._compression.quantize((key, 'wire'), merged).contiguous()
+                words = self._dist.all_gather_tensor(packed)
+                self.wire_bytes += packed.numel() * packed.element_size() * (len(words) - 1)
+                n, shape = merged.numel(), merged.shape
+                merged = sum(self._compression.dequantize(w, n, torch.float32) for w in words).reshape(shape)
+            else:
+                merged = self._dist.all_reduce_sum(merged)
         cls = first.__class__ if not isinstance(first, _sparse.BaseSparseNDArray) else NDArray
         return cls._from_tensor(merged, first._ctx)
 
@@ -142,9 +207,10 @@ class KVStore(KVStoreBase):
         for k, vals in self._group(key, value):
             if k not in self._store:
                 raise MXNetError('key %s has not been initialized' % str(k))
-            merged = self._reduce(k, vals)
+            merged = self._reduce(k, vals, priority=priority)
             stored = self._store[k]
             if self._updater is not None:
+                self.wait_pending()
                 if merged._data.device != stored._data.device:
                     merged = merged.as_in_context(stored._ctx)
                 self._updater(k if not isinstance(k, str) else k, merged, stored)
@@ -156,6 +222,7 @@ class KVStore(KVStoreBase):
 
     def pull(self, key, out=None, priority=0, ignore_sparse=True):
         assert out is not None
+        self.wait_pending()
         for k, outs in self._group(key, out):
             if k not in self._store:
                 raise MXNetError('key %s has not been initialized' % str(k))
@@ -172,14 +239,30 @@ class KVStore(KVStoreBase):
         if self._updater is None:
             # fast path without touching the stored value when no updater is installed
             for (k, vals), (_, outs) in zip(self._group(key, value), self._group(key, out)):
-                merged = self._reduce(k, vals)
-                if k in self._store and self._store[k]._data.shape == merged._data.shape:
+                merged = self._reduce(k, vals, priority=priority)
+                dev = merged._data.device
+                ev = self._pending.get(dev)
+                # the copies back to the replicas stay on the communication stream of the reduction; the compute
+                # streams pick the result up at `wait_pending` (the Trainer calls it once after the last key)
+                comm = None
+                if ev is not None and dev.type == 'cuda':
+                    from .. import engine
+                    st = engine.streams(dev)
+                    comm = st.comm_high if priority >= self._URGENT else st.comm_low
+                with torch.cuda.stream(comm) if comm is not None else _nullcontext():
                     with torch.no_grad():
-                        self._store[k]._data.copy_(merged._data)
-                for o in outs:
-                    with torch.no_grad():
-                        if o._data is not merged._data:
-                            o._data.copy_(merged._data, non_blocking=True)
+                        if k in self._store and self._store[k]._data.shape == merged._data.shape:
+                            self._store[k]._data.copy_(merged._data)
+                        for o in outs:
+                            if o._data is not merged._data:
+                                o._data.copy_(merged._data, non_blocking=True)
+                    if comm is not None:
+                        ev = torch.cuda.Event()
+                        ev.record(comm)
+                        self._pending[dev] = ev
+                        for o in outs:          # replicas on other GPUs wait for their copy as well
+                            if o._data.is_cuda and o._data.device != dev:
+                                self._pending_remote.append((o._data.device, ev))
             return
         self.push(key, value, priority)
         self.pull(key, out, priority)
@@ -196,6 +279,7 @@ class KVStore(KVStoreBase):
     def row_sparse_pull(self, key, out=None, priority=0, row_ids=None):
         """Pull only the rows named by ``row_ids`` (unique, sorted on device like ``kvstore_utils.cu``)."""
         assert out is not None and row_ids is not None
+        self.wait_pending()
         groups = self._group(key, out)
         if isinstance(row_ids, NDArray):
             row_ids = [row_ids]
@@ -206,11 +290,14 @@ class KVStore(KVStoreBase):
         for (k, outs), ids in zip(groups, flat_ids):
             stored = self._store[k]
             for o, rid in zip(outs, ids):
+                # only the requested rows leave the store's device: unique ids (sorted on the device like
+                # src/kvstore/kvstore_utils.cu), a gather of those rows, one copy, a scatter into the cleared output
                 idx = torch.unique(rid._data.long().reshape(-1).to(stored._data.device))
-                res = torch.zeros_like(stored._data)
-                res[idx] = stored._data[idx]
+                rows = stored._data.index_select(0, idx)
                 with torch.no_grad():
-                    o._data.copy_(res.to(o._data.device))
+                    o._data.zero_()
+                    o._data.index_copy_(0, idx.to(o._data.device), rows.to(o._data.device, non_blocking=True))
+                self.rows_pulled += int(idx.numel())
 
     def set_gradient_compression(self, compression_params):
         if self._type == 'nccl':

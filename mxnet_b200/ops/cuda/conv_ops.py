@@ -79,9 +79,13 @@ def tuned_choices():
 
 
 def out_hw(h, w, kernel, pad, dilate, stride=(1, 1)):
-    if tuple(stride) != (1, 1):          # strided 1x1 without padding: every stride-th pixel
-        return (h + stride[0] - 1) // stride[0], (w + stride[1] - 1) // stride[1]
-    return h + 2 * pad[0] - dilate[0] * (kernel[0] - 1), w + 2 * pad[1] - dilate[1] * (kernel[1] - 1)
+    eh, ew = h + 2 * pad[0] - dilate[0] * (kernel[0] - 1), w + 2 * pad[1] - dilate[1] * (kernel[1] - 1)
+    return (eh - 1) // stride[0] + 1, (ew - 1) // stride[1] + 1
+
+
+def _pointwise_strided(weight, pad, stride):
+    """The strided 1x1 convolution without padding: forward, data and weight gradient on sampled views of the tensors."""
+    return _strided(stride) and tuple(weight.shape[1:3]) == (1, 1) and tuple(pad) == (0, 0)
 
 
 def _strided(stride):
@@ -93,8 +97,8 @@ def shape_ok(data, weight, stride, dilate, pad, num_group):
         return False
     if data.dim() != 4 or weight.dim() != 4:
         return False
-    if _strided(stride) and (tuple(weight.shape[1:3]) != (1, 1) or tuple(pad) != (0, 0) or min(stride) < 1):
-        return False                     # strides only for the 1x1 down-sampling convolution
+    if _strided(stride) and (min(stride) < 1 or max(stride) > 2):
+        return False                     # strided filters: traversal strides of the input boxes, up to 2
     cin, cout = data.shape[-1], weight.shape[0]
     if cin % 8 or cout % 8 or weight.shape[3] != cin or not data.is_contiguous() or not weight.is_contiguous():
         return False
@@ -116,9 +120,21 @@ def conv_forward(x, w, bias=None, res=None, pad=(0, 0), dilate=(1, 1), relu=Fals
     require(w, 'weight', dtype=x.dtype, device=x.device, shape=(cout, r, s, cin))
     ho, wo = out_hw(h, wd, (r, s), pad, dilate, stride)
     y = torch.empty((n, ho, wo, cout), dtype=x.dtype, device=x.device)
+    if _strided(stride) and not _pointwise_strided(w, pad, stride):
+        # any filter size: the input boxes are fetched with traversal strides
+        if res is not None:
+            raise ValueError('the strided convolution takes no residual input')
+        if bias is not None:
+            bias = require(bias.to(x.dtype).contiguous(), 'bias', numel=cout, device=x.device)
+        stats = torch.empty((L.mxb_conv_stat_rows(), 2, cout), dtype=torch.float32, device=x.device) if want_stats else None
+        check(L.mxb_conv_strided_forward(dt(x), ptr(x), ptr(w), ptr(y), ptr(bias), ptr(stats), n, h, wd, cin, cout, r, s,
+                                         pad[0], pad[1], dilate[0], dilate[1], stride[0], stride[1], 1 if relu else 0,
+                                         ptr(_error_flag(x.device)), stream_ptr(x.device)), 'conv_strided_forward')
+        count_launch(1)
+        return y, stats
     if _strided(stride):
-        if (r, s) != (1, 1) or tuple(pad) != (0, 0) or res is not None:
-            raise ValueError('strided convolution on this kernel: 1x1 filter, no padding, no residual')
+        if res is not None:
+            raise ValueError('the strided convolution takes no residual input')
         if bias is not None:
             bias = require(bias.to(x.dtype).contiguous(), 'bias', numel=cout, device=x.device)
         stats = torch.empty((L.mxb_conv_stat_rows(), 2, cout), dtype=torch.float32, device=x.device) if want_stats else None
@@ -149,6 +165,8 @@ def conv_dgrad(dy, w, in_hw, pad=(0, 0), dilate=(1, 1), res=None, stride=(1, 1))
     require(w, 'weight', dtype=dy.dtype, device=dy.device, shape=(cout, r, s, cin))
     dx = torch.empty((n, h, wd, cin), dtype=dy.dtype, device=dy.device)
     if _strided(stride):
+        if not _pointwise_strided(w, pad, stride):
+            raise ValueError('the data gradient of a strided filter larger than 1x1 has no in-tree kernel')
         if res is not None:
             raise ValueError('no residual input for the strided data gradient')
         check(L.mxb_conv1x1_strided_dgrad(dt(dy), ptr(dy), ptr(w), ptr(dx), n, h, wd, cin, cout, stride[0], stride[1],
@@ -173,6 +191,12 @@ def conv_wgrad(x, dy, kernel, pad=(0, 0), dilate=(1, 1), stride=(1, 1)):
     require(dy, 'out_grad', dtype=x.dtype, device=x.device, shape=(n,) + out_hw(h, wd, (r, s), pad, dilate, stride) + (cout,))
     dw32 = torch.empty((cout, r, s, cin), dtype=torch.float32, device=x.device)
     dw = torch.empty((cout, r, s, cin), dtype=x.dtype, device=x.device)
+    if _strided(stride) and not ((r, s) == (1, 1) and tuple(pad) == (0, 0)):
+        check(L.mxb_conv_strided_wgrad(dt(x), ptr(x), ptr(dy), ptr(dw), ptr(dw32), n, h, wd, cin, cout, r, s, pad[0], pad[1],
+                                       dilate[0], dilate[1], stride[0], stride[1], ptr(_error_flag(x.device)),
+                                       stream_ptr(x.device)), 'conv_strided_wgrad')
+        count_launch(2)
+        return dw
     if _strided(stride):
         check(L.mxb_conv1x1_strided_wgrad(dt(x), ptr(x), ptr(dy), ptr(dw), ptr(dw32), n, h, wd, cin, cout, stride[0], stride[1],
                                           ptr(_error_flag(x.device)), stream_ptr(x.device)), 'conv1x1_strided_wgrad')
@@ -226,7 +250,8 @@ class _ConvNHWC(torch.autograd.Function):
         dy = dy.contiguous()
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         dx = dw = None
-        if need_dx and use_own('dgrad', dirs, key, lambda: conv_dgrad(dy, w, x.shape[1:3], pad, dilate, None, stride),
+        own_dgrad = not _strided(stride) or _pointwise_strided(w, pad, stride)      # strided R x S filters: library dgrad
+        if need_dx and own_dgrad and use_own('dgrad', dirs, key, lambda: conv_dgrad(dy, w, x.shape[1:3], pad, dilate, None, stride),
                                lambda: _library_backward(x, w, dy, pad, dilate, True, False, stride)):
             dx = conv_dgrad(dy, w, x.shape[1:3], pad, dilate, None, stride)
         if need_dw and use_own('wgrad', dirs, key, lambda: conv_wgrad(x, dy, w.shape[1:3], pad, dilate, stride),

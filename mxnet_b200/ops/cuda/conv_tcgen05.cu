@@ -46,7 +46,8 @@ struct ConvGeom {
   int N, Ho, Wo;                         // output pixel space
   int NC, KC;                            // output channels of this launch (GEMM N), reduction channels (per tap)
   int R, S;
-  int off_h, step_h, off_w, step_w;      // input row of tap r for output row h: h + off_h + r * step_h
+  int off_h, step_h, off_w, step_w;      // input row of tap r for output row h: h * str_h + off_h + r * step_h
+  int str_h, str_w;                      // convolution stride (1 except for the strided forward convolution)
   int bw, bh, bnb;                       // pixel box, bw * bh * bnb = 128
   int tiles_w, tiles_h, tiles_nb;
   int ldy;                               // channel pitch of Y and of the residual, in elements
@@ -187,9 +188,9 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       }
       int tap = 0;
       for (int r = 0; r < g.R && ok; ++r) {
-        const int ih = h0 + g.off_h + r * g.step_h;
+        const int ih = h0 * g.str_h + g.off_h + r * g.step_h;
         for (int s = 0; s < g.S && ok; ++s, ++tap) {
-          const int iw = w0 + g.off_w + s * g.step_w;
+          const int iw = w0 * g.str_w + g.off_w + s * g.step_w;
           for (int kc = 0; kc < kchunks; ++kc) {
             MXB_PROF_MARK(4)                                       // loop overhead since the previous k-step
             if (!mbar_wait_warp(&empty[st], ph ^ 1u)) { *abort_flag = 1; ok = false; break; }
@@ -466,14 +467,18 @@ static void choose_box(int Wo, int Ho, int N, int total, int* bw, int* bh, int* 
 // NHWC activation tensor [N, H, W, C] as a 4-D map {C, W, H, N}; box {64, bw, bh, bnb}; 128-byte swizzle; zero fill.
 // (sh, sw) > 1 describes every sh-th row and sw-th column of the stored tensor (the input of a strided 1x1 convolution):
 // a view of ceil(H / sh) x ceil(W / sw) pixels with the strides multiplied accordingly.
+// (th, tw) > 1 are traversal strides: a box still delivers bw x bh pixels, but every tw-th column and th-th row
+// starting at the box origin, which may have any parity (the input of a strided convolution with a filter larger than
+// 1x1, whose taps shift the origin by single pixels).
 static int make_map_nhwc(CUtensorMap* map, const void* base, int bf16, int N, int H, int W, int C, int bw, int bh, int bnb,
-                         int sh = 1, int sw = 1) {
+                         int sh = 1, int sw = 1, int th = 1, int tw = 1) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -10;
+  if ((bw - 1) * tw + 1 > 256 || (bh - 1) * th + 1 > 256) return -12;      // a box spans at most 256 elements per axis
   cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)((W + sw - 1) / sw), (cuuint64_t)((H + sh - 1) / sh), (cuuint64_t)N};
   cuuint64_t strides[3] = {(cuuint64_t)sw * C * 2, (cuuint64_t)sh * W * C * 2, (cuuint64_t)H * W * C * 2};
-  cuuint32_t box[4] = {64, (cuuint32_t)bw, (cuuint32_t)bh, (cuuint32_t)bnb};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
+  cuuint32_t box[4] = {64, (cuuint32_t)((bw - 1) * tw + 1), (cuuint32_t)((bh - 1) * th + 1), (cuuint32_t)bnb};
+  cuuint32_t estr[4] = {1, (cuuint32_t)tw, (cuuint32_t)th, 1};
   CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base),
                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -565,7 +570,8 @@ static int conv_pick_bn(long tiles_m, int NC) {
 static int conv_run(int dtype, const void* in, const void* w, void* out, const void* bias, const void* res, float* stats,
                     int N, int Hi, int Wi, int KC, int Ho, int Wo, int NC, int R, int S, int off_h, int step_h, int off_w,
                     int step_w, int w_cout, int w_cin, int b_mn, int act, int* error_flag, cudaStream_t st, int in_sh = 1,
-                    int in_sw = 1, int out_sh = 1, int out_sw = 1, int out_full_h = 0, int out_full_w = 0) {
+                    int in_sw = 1, int out_sh = 1, int out_sw = 1, int out_full_h = 0, int out_full_w = 0, int str_h = 1,
+                    int str_w = 1) {
   if (dtype != kF16 && dtype != kBF16) return -1;
   if (N < 1 || Hi < 1 || Wi < 1 || Ho < 1 || Wo < 1 || KC < 8 || NC < 8 || R < 1 || S < 1) return -2;
   if ((KC % 8) || (NC % 8) || ((uintptr_t)in % 16) || ((uintptr_t)w % 16) || ((uintptr_t)out % 16)) return -3;
@@ -573,6 +579,7 @@ static int conv_run(int dtype, const void* in, const void* w, void* out, const v
   ConvGeom g;
   g.N = N; g.Ho = Ho; g.Wo = Wo; g.NC = NC; g.KC = KC; g.R = R; g.S = S;
   g.off_h = off_h; g.step_h = step_h; g.off_w = off_w; g.step_w = step_w;
+  g.str_h = str_h; g.str_w = str_w;
   choose_box(Wo, Ho, N, CBM, &g.bw, &g.bh, &g.bnb);
   g.tiles_w = (Wo + g.bw - 1) / g.bw;
   g.tiles_h = (Ho + g.bh - 1) / g.bh;
@@ -588,7 +595,7 @@ static int conv_run(int dtype, const void* in, const void* w, void* out, const v
   if (tiles_m * ((NC + 63) / 64) > 0x7fffffffL) return -2;
   const int bn = conv_pick_bn(tiles_m, NC);
   CUtensorMap mx, mw, my;
-  int rc = make_map_nhwc(&mx, in, g.bf16, N, Hi, Wi, KC, g.bw, g.bh, g.bnb, in_sh, in_sw);
+  int rc = make_map_nhwc(&mx, in, g.bf16, N, Hi, Wi, KC, g.bw, g.bh, g.bnb, in_sh, in_sw, str_h, str_w);
   if (rc) return rc;
   rc = make_map_filter(&mw, w, g.bf16, w_cout, R * S, w_cin, b_mn ? 64 : bn);
   if (rc) return rc;
@@ -632,6 +639,19 @@ MXB_EXPORT int mxb_conv_forward(int dtype, const void* x, const void* w, void* y
   const int Ho = H + 2 * pad_h - dil_h * (R - 1), Wo = W + 2 * pad_w - dil_w * (S - 1);
   return conv_run(dtype, x, w, y, bias, res, stats, N, H, W, Cin, Ho, Wo, Cout, R, S, -pad_h, dil_h, -pad_w, dil_w, Cout, Cin,
                   0, act, error_flag, (cudaStream_t)stream);
+}
+
+// Strided convolution with any filter size: Ho = (H + 2*pad_h - dil_h*(R-1) - 1) / sh + 1, Wo likewise.  The input boxes are
+// fetched with traversal strides (sh, sw), so the contraction is the same loop over (tap, channel chunk).
+MXB_EXPORT int mxb_conv_strided_forward(int dtype, const void* x, const void* w, void* y, const void* bias, float* stats, int N,
+                                        int H, int W, int Cin, int Cout, int R, int S, int pad_h, int pad_w, int dil_h, int dil_w,
+                                        int sh, int sw, int act, int* error_flag, void* stream) {
+  if (sh < 1 || sw < 1) return -2;
+  const int eh = H + 2 * pad_h - dil_h * (R - 1), ew = W + 2 * pad_w - dil_w * (S - 1);
+  if (eh < 1 || ew < 1) return -2;
+  const int Ho = (eh - 1) / sh + 1, Wo = (ew - 1) / sw + 1;
+  return conv_run(dtype, x, w, y, bias, nullptr, stats, N, H, W, Cin, Ho, Wo, Cout, R, S, -pad_h, dil_h, -pad_w, dil_w, Cout, Cin, 0,
+                  act, error_flag, (cudaStream_t)stream, 1, 1, 1, 1, 0, 0, sh, sw);
 }
 
 // Strided 1x1 convolution (the down-sampling shortcut of a residual network): y[N, Ho, Wo, Cout] with Ho = ceil(H / sh),
@@ -683,6 +703,7 @@ struct WgradGeom {
   int N, Ho, Wo;                 // pixel space of dY
   int Cout, Cin, R, S;
   int off_h, step_h, off_w, step_w;
+  int str_h, str_w;              // convolution stride: the x box of a k-step starts at (w0 * str_w + dw, h0 * str_h + dh)
   int kw, kh, knb;               // pixel box of one k-step, kw * kh * knb = 64
   int tiles_w, tiles_h, tiles_nb;
   int ksteps_per, ksplit;
@@ -761,7 +782,8 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
             tma_load_4d(sA + st * CA_BYTES + c * kMnChunkBytes, &map_dy, tm * CBM + c * 64, w0, h0, n0, &full[st]);
 #pragma unroll
           for (int c = 0; c < BN / 64; ++c)
-            tma_load_4d(sB + st * B_BYTES + c * kMnChunkBytes, &map_x, tn * BN + c * 64, w0 + dw, h0 + dh, n0, &full[st]);
+            tma_load_4d(sB + st * B_BYTES + c * kMnChunkBytes, &map_x, tn * BN + c * 64, w0 * g.str_w + dw, h0 * g.str_h + dh, n0,
+                        &full[st]);
           ++it;
           if (++st == STAGES) { st = 0; ph ^= 1u; }
           if (++iw == g.tiles_w) {
@@ -888,7 +910,8 @@ static int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, float* dW
 // dw[Cout, R, S, Cin] (type `dtype`; may be null to keep only the fp32 result) and dw32 (fp32 workspace of the same
 // element count, overwritten) from x[N, H, W, Cin] and dy[N, Ho, Wo, Cout] of the stride-1 convolution above.
 static int wgrad_run(int dtype, const void* x, const void* dy, void* dw, float* dw32, int N, int H, int W, int Cin, int Cout,
-                     int R, int S, int pad_h, int pad_w, int dil_h, int dil_w, int sh, int sw, int* error_flag, void* stream) {
+                     int R, int S, int pad_h, int pad_w, int dil_h, int dil_w, int sh, int sw, int* error_flag, void* stream,
+                     int str_h = 1, int str_w = 1) {
   if (dtype != kF16 && dtype != kBF16) return -1;
   if (N < 1 || H < 1 || W < 1 || Cin < 8 || Cout < 8 || R < 1 || S < 1 || !dw32) return -2;
   if ((Cin % 8) || (Cout % 8) || ((uintptr_t)x % 16) || ((uintptr_t)dy % 16) || ((uintptr_t)dw32 % 16)) return -3;
@@ -896,6 +919,8 @@ static int wgrad_run(int dtype, const void* x, const void* dy, void* dw, float* 
   g.N = N; g.Ho = H + 2 * pad_h - dil_h * (R - 1); g.Wo = W + 2 * pad_w - dil_w * (S - 1);
   if (sh > 1 || sw > 1) { g.Ho = (H + sh - 1) / sh; g.Wo = (W + sw - 1) / sw; }      // strided 1x1: a sampled view of x
   if (g.Ho < 1 || g.Wo < 1) return -2;
+  if (str_h > 1 || str_w > 1) { g.Ho = (g.Ho - 1) / str_h + 1; g.Wo = (g.Wo - 1) / str_w + 1; }      // strided R x S filter
+  g.str_h = str_h; g.str_w = str_w;
   g.Cout = Cout; g.Cin = Cin; g.R = R; g.S = S;
   g.off_h = -pad_h; g.step_h = dil_h; g.off_w = -pad_w; g.step_w = dil_w;
   choose_box(g.Wo, g.Ho, N, 64, &g.kw, &g.kh, &g.knb);
@@ -915,7 +940,7 @@ static int wgrad_run(int dtype, const void* x, const void* dy, void* dw, float* 
   CUtensorMap mdy, mx;
   int rc = make_map_nhwc(&mdy, dy, g.bf16, N, g.Ho, g.Wo, Cout, g.kw, g.kh, g.knb);
   if (rc) return rc;
-  rc = make_map_nhwc(&mx, x, g.bf16, N, H, W, Cin, g.kw, g.kh, g.knb, sh, sw);
+  rc = make_map_nhwc(&mx, x, g.bf16, N, H, W, Cin, g.kw, g.kh, g.knb, sh, sw, str_h, str_w);
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
 #define MXB_WGRAD(T)                                                                      \
@@ -930,6 +955,15 @@ MXB_EXPORT int mxb_conv_wgrad(int dtype, const void* x, const void* dy, void* dw
                               int Cout, int R, int S, int pad_h, int pad_w, int dil_h, int dil_w, int* error_flag,
                               void* stream) {
   return wgrad_run(dtype, x, dy, dw, dw32, N, H, W, Cin, Cout, R, S, pad_h, pad_w, dil_h, dil_w, 1, 1, error_flag, stream);
+}
+
+// Weight gradient of the strided convolution with any filter size: dy is [N, Ho, Wo, Cout] with Ho, Wo as in
+// mxb_conv_strided_forward.
+MXB_EXPORT int mxb_conv_strided_wgrad(int dtype, const void* x, const void* dy, void* dw, float* dw32, int N, int H, int W, int Cin,
+                                      int Cout, int R, int S, int pad_h, int pad_w, int dil_h, int dil_w, int sh, int sw,
+                                      int* error_flag, void* stream) {
+  if (sh < 1 || sw < 1) return -2;
+  return wgrad_run(dtype, x, dy, dw, dw32, N, H, W, Cin, Cout, R, S, pad_h, pad_w, dil_h, dil_w, 1, 1, error_flag, stream, sh, sw);
 }
 
 // Weight gradient of the strided 1x1 convolution: dy is [N, ceil(H / sh), ceil(W / sw), Cout].

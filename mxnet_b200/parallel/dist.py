@@ -93,6 +93,13 @@ def all_reduce_sum(t):
     return t
 
 
+def all_gather_tensor(t):
+    """The tensor ``t`` of every rank (same shape and dtype everywhere), as a list in rank order."""
+    parts = [torch.empty_like(t) for _ in range(world_size())]
+    tdist.all_gather(parts, t.contiguous())
+    return parts
+
+
 def broadcast_(t, src=0):
     tdist.broadcast(t, src)
     return t

@@ -53,6 +53,18 @@ def main():
     o2 = nd.empty((2,))
     store2.pull('w', out=o2)
     rep['optimizer_on_store'] = bool(np.allclose(o2.asnumpy(), 1 - 0.1 * (world + 1) / 2))
+    # gradient compression between workers: the packed 2-bit codes travel (all-gather of the words), every rank expands
+    # and sums them; 64 values = 4 words per rank instead of 256 bytes
+    store3 = kv.create('dist_sync')
+    store3.set_gradient_compression({'type': '2bit', 'threshold': 0.5})
+    store3.init('g', nd.zeros((64,)))
+    g = nd.array(np.where(np.arange(64) % 3 == rank % 3, 0.75, -0.1).astype('float32'))
+    o3 = nd.empty((64,))
+    store3.pushpull('g', g, out=o3)
+    expect = np.zeros(64, 'float32')
+    for r in range(world):
+        expect += np.where(np.arange(64) % 3 == r % 3, 0.5, 0.0)
+    rep['compressed_wire'] = bool(np.array_equal(o3.asnumpy(), expect)) and store3.wire_bytes == 4 * 4 * (world - 1)
     store.barrier()
     if rank == 0:
         print('REPORT ' + json.dumps(rep))

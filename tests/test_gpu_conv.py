@@ -112,6 +112,61 @@ def test_strided_1x1_convolution_all_directions(N, H, W, Cin, Cout, stride, dtyp
     _close(dw, wr.grad, tol[0], (2e-3 if dtype == torch.float16 else 8e-3) * k ** 0.5)
 
 
+@pytest.mark.parametrize('N,H,W,Cin,Cout,R,pad', [(4, 56, 56, 128, 128, 3, 1), (2, 28, 28, 256, 256, 3, 1), (3, 15, 17, 16, 24, 3, 1),
+                                                 (2, 14, 14, 512, 512, 3, 1), (2, 32, 32, 8, 64, 7, 3), (2, 9, 9, 16, 16, 3, 0)])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_strided_filter_forward_and_weight_gradient(N, H, W, Cin, Cout, R, pad, dtype):
+    """Stride-2 convolutions with 3x3 and 7x7 filters (the down-sampling layers of a residual network): the input boxes are
+    fetched with traversal strides.  Forward (with the statistics epilogue) and weight gradient against fp32."""
+    from mxnet_b200.ops.cuda import conv_ops, gemm_ops
+    x, w = _inputs(N, H, W, Cin, Cout, R, dtype, seed=16)
+    xr, wr = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    ref = F.conv2d(xr.permute(0, 3, 1, 2), wr.permute(0, 3, 1, 2), None, 2, pad).permute(0, 2, 3, 1).contiguous()
+    dy = (torch.randn_like(ref) / 4).to(dtype)
+    ref.backward(dy.float())
+    y, stats = conv_ops.conv_forward(x, w, None, None, (pad, pad), (1, 1), False, True, (2, 2))
+    dw = conv_ops.conv_wgrad(x, dy, (R, R), (pad, pad), (1, 1), (2, 2))
+    gemm_ops.check_errors()
+    tol = (1e-2, 1e-2) if dtype == torch.float16 else (3e-2, 3e-2)
+    assert y.shape == ref.shape
+    _close(y, ref, *tol)
+    _close(stats.sum(0)[0] / (ref.numel() // Cout), ref.reshape(-1, Cout).mean(0), 1e-2, 2e-3)
+    k = dy.numel() // Cout
+    _close(dw, wr.grad, tol[0], (2e-3 if dtype == torch.float16 else 8e-3) * k ** 0.5)
+
+
+def test_strided_convolution_operator_trains_through_the_kernels():
+    """``Convolution(kernel=3, stride=2)`` through the operator registry with the in-tree kernels forced: forward and
+    weight gradient on the strided kernels, data gradient from the library, all against fp32."""
+    import os
+    old = os.environ.get('MXNET_B200_CONV')
+    os.environ['MXNET_B200_CONV'] = '1'
+    try:
+        rng = np.random.RandomState(2)
+        x_np = rng.randn(2, 12, 12, 32).astype('float32')
+        w_np = (rng.randn(64, 3, 3, 32) / 17).astype('float32')
+        ctx = mx.gpu(0)
+        x, w = nd.array(x_np, ctx=ctx, dtype='float16'), nd.array(w_np, ctx=ctx, dtype='float16')
+        x.attach_grad()
+        w.attach_grad()
+        with autograd.record():
+            y = nd.Convolution(x, w, kernel=(3, 3), stride=(2, 2), pad=(1, 1), num_filter=64, no_bias=True, layout='NHWC')
+            loss = (y * y).sum()
+        loss.backward()
+        xr = torch.tensor(x_np, device='cuda').half().float().requires_grad_(True)
+        wr = torch.tensor(w_np, device='cuda').half().float().requires_grad_(True)
+        ref = F.conv2d(xr.permute(0, 3, 1, 2), wr.permute(0, 3, 1, 2), None, 2, 1)
+        (ref * ref).sum().backward()
+        _close(y._data, ref.permute(0, 2, 3, 1), 1e-2, 1e-2)
+        _close(x.grad._data, xr.grad, 2e-2, 5e-2)
+        _close(w.grad._data, wr.grad, 2e-2, 2e-1)
+    finally:
+        if old is None:
+            os.environ.pop('MXNET_B200_CONV', None)
+        else:
+            os.environ['MXNET_B200_CONV'] = old
+
+
 def _conv_bn_step(x_np, w_np, env):
     import os
     old = os.environ.get('MXNET_B200_CONV')

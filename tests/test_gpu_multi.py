@@ -67,3 +67,39 @@ def test_single_process_multi_gpu_trainer_runs_on_the_fused_kernels(ngpu):
     for key, tol in (('float32_sgd', 1e-5), ('float16_sgd', 5e-3), ('float32_adam', 2e-3), ('float32_lamb', 1e-4)):
         assert rep[key]['replicas_identical'], key
         assert rep[key]['max_abs_diff_vs_one_gpu'] < tol, (key, rep[key])
+
+
+def test_device_kvstore_reduces_on_prioritised_communication_streams():
+    """The generic ``device`` store over two GPUs of one process (fused step off): reductions run on the high / low
+    priority communication streams picked by the key's priority, the compute streams wait for them by events, and
+    2-bit compressed gradients cross between the GPUs as packed words."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    import numpy as np
+    import mxnet_b200 as mx
+    from mxnet_b200 import engine, kv, nd
+    ctxs = [mx.gpu(0), mx.gpu(1)]
+    store = kv.create('device')
+    n = 1 << 20
+    for k in range(12):
+        store.init(k, nd.zeros((n,), ctx=ctxs[0]))
+    vals = [[nd.full((n,), float(k + 1 + d), ctx=c) for d, c in enumerate(ctxs)] for k in range(12)]
+    outs = [[nd.zeros((n,), ctx=c) for c in ctxs] for k in range(12)]
+    for k in range(12):
+        store.pushpull(k, vals[k], out=outs[k], priority=-k)
+    assert store._pending, 'reductions of multi-GPU keys are queued on the communication streams'
+    st = engine.streams(0)
+    assert st.comm_high.cuda_stream != st.comm_low.cuda_stream
+    store.wait_pending()
+    for k in range(12):
+        for o in outs[k]:
+            assert float(o.asnumpy()[0]) == 2 * k + 3 and float(o.asnumpy()[-1]) == 2 * k + 3
+    comp = kv.create('device')
+    comp.set_gradient_compression({'type': '2bit', 'threshold': 0.5})
+    comp.init('g', nd.zeros((n,), ctx=ctxs[0]))
+    g = [nd.full((n,), 0.75, ctx=c) for c in ctxs]
+    out = nd.zeros((n,), ctx=ctxs[0])
+    comp.pushpull('g', g, out=out)
+    comp.wait_pending()
+    assert float(out.asnumpy()[7]) == 1.0                       # 0.5 from each GPU
+    assert comp.wire_bytes == n // 16 * 4                       # only GPU 1's packed words crossed

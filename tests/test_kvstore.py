@@ -127,6 +127,7 @@ def test_row_sparse_pull():
     expect = np.zeros_like(w)
     expect[[1, 4]] = w[[1, 4]]
     assert same(dense, expect)
+    assert store.rows_pulled == 2          # the two distinct rows were gathered and moved, not the whole table
 
 
 def test_gradient_compression_2bit_residual():
@@ -205,7 +206,8 @@ def test_dist_sync_kvstore_over_gloo():
     r = _torchrun('dist_kvstore_worker.py', 3, 29641)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     rep = json.loads([l for l in r.stdout.splitlines() if l.startswith('REPORT ')][-1][7:])
-    assert rep == {'world': 3, 'pushpull': True, 'broadcast': True, 'trainer_identical': True, 'optimizer_on_store': True}
+    assert rep == {'world': 3, 'pushpull': True, 'broadcast': True, 'trainer_identical': True, 'optimizer_on_store': True,
+                   'compressed_wire': True}
 
 
 @pytest.mark.integration
