@@ -164,7 +164,7 @@ class KVStore(KVStoreBase):
             n, shape = first._data.numel(), first._data.shape
             parts = []
             for i, v in enumerate(values):
-                packed = self._compression.quantize((key, i), v._data)
+                packed = self._compression.quantize((key, i), v._data).to(torch.int32)      # 32-bit words on the wire
                 self.wire_bytes += packed.numel() * packed.element_size() if v._data.device != dev else 0
                 parts.append(self._compression.dequantize(packed.to(dev, non_blocking=True), n, torch.float32).reshape(shape))
         else:
@@ -181,7 +181,7 @@ class KVStore(KVStoreBase):
             if self._compression is not None and merged.dtype == torch.float32:
                 # between workers the packed codes travel as well: every rank gathers the others' words and expands them
                 # (the reference's workers send compressed gradients to the server, which decompresses and sums)
-                packed = self._compression.quantize((key, 'wire'), merged).contiguous()
+                packed = self._compression.quantize((key, 'wire'), merged).to(torch.int32).contiguous()
                 words = self._dist.all_gather_tensor(packed)
                 self.wire_bytes += packed.numel() * packed.element_size() * (len(words) - 1)
                 n, shape = merged.numel(), merged.shape
