@@ -66,3 +66,5 @@ from . import tvmop
 from .ndarray import waitall
 from .util import is_np_default_dtype   # noqa: F401
 from .kvstore import kvstore_server    # noqa: F401
+from . import initialize as _initialize
+_initialize.install()

@@ -85,6 +85,8 @@ def describe():
 
 
 # ---- engine -------------------------------------------------------------------------------
+declare('MXNET_USE_SIGNAL_HANDLER', bool, True,
+        'Print the Python stack of every thread when the process receives a fatal signal (SIGSEGV, SIGFPE, SIGABRT, SIGBUS, SIGILL).')
 declare('MXNET_ENGINE_TYPE', str, 'ThreadedEnginePerDevice',
         'NaiveEngine = fully synchronous; ThreadedEngine / ThreadedEnginePerDevice / ...Async = stream engine')
 declare('MXNET_CPU_WORKER_NTHREADS', int, 1, 'host worker threads of the native dependency engine')
@@ -161,8 +163,12 @@ def markdown():
              'Every flag is read through `mxnet_b200.env.get(name)`; the environment wins over the default, and '
              '`mxnet_b200.env.scope(NAME=value)` / `mxnet_b200.test_utils.environment` set one for a `with` block.', '',
              '| variable | type | default | meaning |', '|---|---|---|---|']
+    home = os.path.expanduser('~')
     for f in sorted(FLAGS.values(), key=lambda f: f.name):
-        lines.append('| `%s` | %s | `%r` | %s |' % (f.name, f.type.__name__, f.default, f.doc.replace('|', '\\|')))
+        default = f.default
+        if isinstance(default, str) and home not in ('', '/') and default.startswith(home):
+            default = '~' + default[len(home):]         # the document must not depend on who generated it
+        lines.append('| `%s` | %s | `%r` | %s |' % (f.name, f.type.__name__, default, f.doc.replace('|', '\\|')))
     return '\n'.join(lines) + '\n'
 
 

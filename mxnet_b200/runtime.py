@@ -8,6 +8,15 @@ __all__ = ['Feature', 'Features', 'feature_list']
 Feature = collections.namedtuple('Feature', ['name', 'enabled'])
 
 
+def _nvrtc_bindings():
+    """Whether run-time compilation (``mx.rtc.CudaModule``, the pointwise-fusion pass) can load NVRTC."""
+    try:
+        from cuda import nvrtc  # noqa: F401
+        return True
+    except Exception:  # pylint: disable=broad-except
+        return False
+
+
 def _probe():
     cuda = torch.cuda.is_available() or torch.version.cuda is not None
     try:
@@ -17,7 +26,7 @@ def _probe():
         nccl = False
     feats = {
         'CUDA': cuda, 'CUDNN': cuda and torch.backends.cudnn.is_available() if torch.cuda.is_available() else cuda,
-        'NCCL': nccl, 'TENSORRT': False, 'CUTENSOR': False, 'CUDA_RTC': False,
+        'NCCL': nccl, 'TENSORRT': False, 'CUTENSOR': False, 'CUDA_RTC': cuda and _nvrtc_bindings(),
         'CPU_SSE': True, 'CPU_SSE2': True, 'CPU_SSE3': True, 'CPU_SSE4_1': True, 'CPU_SSE4_2': True, 'CPU_SSE4A': False,
         'CPU_AVX': True, 'CPU_AVX2': True, 'OPENMP': True, 'SSE': True, 'F16C': True, 'JEMALLOC': False,
         'BLAS_OPEN': False, 'BLAS_ATLAS': False, 'BLAS_MKL': True, 'BLAS_APPLE': False, 'LAPACK': True,

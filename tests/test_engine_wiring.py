@@ -166,3 +166,23 @@ def test_per_device_policy_keeps_workers_for_urgent_operations():
         release.set()
         eng.wait_all()
         assert ran.is_set()
+
+
+def test_forked_child_gets_a_fresh_engine():
+    """Worker threads do not survive fork(): the child drops the parent's engine and builds its own on first use."""
+    a = nd.zeros((3,))
+    engine.push(lambda: a._data.fill_(1.0), writes=[a])
+    a.wait_to_read()
+    pid = os.fork()
+    if pid == 0:
+        code = 1
+        try:
+            b = nd.zeros((3,))
+            engine.push(lambda: b._data.fill_(5.0), writes=[b])
+            code = 0 if float(b.asnumpy().sum()) == 15.0 else 2
+        finally:
+            os._exit(code)
+    _, status = os.waitpid(pid, 0)
+    assert os.WIFEXITED(status) and os.WEXITSTATUS(status) == 0
+    engine.push(lambda: a._data.fill_(2.0), writes=[a])          # the parent's engine is untouched
+    assert float(a.asnumpy().sum()) == 6.0

@@ -271,3 +271,37 @@ def test_nms_kernels_against_the_host_operator(n, force):
     outs = [nd.contrib.box_nms(nd.array(rows, ctx=ctx), overlap_thresh=0.45, valid_thresh=0.05, topk=400, coord_start=2, score_index=1,
                                id_index=0, force_suppress=force).asnumpy() for ctx in (mx.cpu(), mx.gpu(0))]
     np.testing.assert_allclose(outs[1], outs[0], rtol=1e-6)
+
+
+def test_rtc_cuda_module_compiles_and_launches_a_user_kernel():
+    """``mx.rtc.CudaModule``: source compiled at run time for the running GPU (reference: python/mxnet/rtc.py, the
+    `axpy` example of its docstring), launched on arrays of the framework; a compile error is reported with the log."""
+    import mxnet_b200 as mx
+    from mxnet_b200 import nd
+    assert mx.runtime.Features().is_enabled('CUDA_RTC')
+    source = r"""
+    extern "C" __global__ void axpy(const float* x, float* y, float alpha, int n) {
+        int i = threadIdx.x + blockIdx.x * blockDim.x;
+        if (i < n) y[i] += alpha * x[i];
+    }
+    extern "C" __global__ void scale_half(__half* x, float s, int n) {
+        int i = threadIdx.x + blockIdx.x * blockDim.x;
+        if (i < n) x[i] = __float2half(__half2float(x[i]) * s);
+    }
+    """
+    module = mx.rtc.CudaModule('#include <cuda_fp16.h>\n' + source, exports=['axpy', 'scale_half'])
+    axpy = module.get_kernel('axpy', 'const float *x, float *y, float alpha, int n')
+    ctx = mx.gpu(0)
+    n = 1000
+    x = nd.array(np.arange(n, dtype='float32'), ctx=ctx)
+    y = nd.ones((n,), ctx=ctx)
+    axpy.launch([x, y, 3.0, n], ctx, ((n + 255) // 256, 1, 1), (256, 1, 1))
+    np.testing.assert_allclose(y.asnumpy(), 1 + 3 * np.arange(n, dtype='float32'))
+    half = module.get_kernel('scale_half', '__half *x, float s, int n')
+    h = nd.array(np.arange(16, dtype='float16'), ctx=ctx, dtype='float16')
+    half.launch([h, 0.5, 16], ctx, (1, 1, 1), (32, 1, 1))
+    np.testing.assert_allclose(h.asnumpy().astype('float32'), np.arange(16) * 0.5)
+    with pytest.raises(mx.MXNetError, match='NVRTC compilation failed'):
+        mx.rtc.CudaModule('__global__ void broken( { }')
+    with pytest.raises(ValueError):
+        module.get_kernel('axpy', 'const float x[3]')

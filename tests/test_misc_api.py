@@ -476,3 +476,20 @@ def test_block_save_load_and_method_additions(tmp_path):
     assert m.mT.shape == (3, 2) and m.diagonal().shape == (2,) and m.reshape_view(3, 2).shape == (3, 2)
     ex = mx.sym.relu(s)._bind(mx.cpu(), {'x': nd.ones((2,))})
     assert ex.get_optimized_symbol().list_arguments() == ['x']
+
+
+def test_tensor_inspector(tmp_path):
+    from mxnet_b200.inspector import CheckerType, TensorInspector
+    a = nd.array(np.array([[1.0, -2.0, 0.0], [np.nan, np.inf, -np.inf]], dtype='float32'))
+    ti = TensorInspector(a)
+    text = ti.to_string()
+    assert 'float32 Tensor 2x3' in text and 'nan' in text
+    assert ti.check_value(CheckerType.NaNChecker) == [(1, 0)]
+    assert ti.check_value(CheckerType.NegativeChecker) == [(0, 1), (1, 2)]
+    assert ti.check_value(CheckerType.InfChecker) == [(1, 1), (1, 2)]
+    assert ti.check_value(CheckerType.AbnormalChecker) == [(0, 2), (1, 0), (1, 1), (1, 2)]
+    assert ti.check_value(lambda v: v == 1.0) == [(0, 0)]
+    f1 = ti.dump_to_file('probe', str(tmp_path))
+    f2 = ti.dump_to_file('probe', str(tmp_path))
+    assert f1.endswith('probe_1.npy') and f2.endswith('probe_2.npy')
+    np.testing.assert_array_equal(np.load(f1), a.asnumpy())
