@@ -279,7 +279,7 @@ def main():
         from mxnet_b200.ops.cuda import conv_ops
         tuned = conv_ops.tuned_choices()
         conv_sel = {d: '%d of %d' % (sum(1 for k, v in tuned.items() if k[0] == d and v), sum(1 for k in tuned if k[0] == d))
-                    for d in ('fwd', 'dgrad', 'wgrad')}
+                    for d in ('fwd', 'dgrad', 'dgrad+skip', 'wgrad')}
         res = {'value': value, 'ms_per_step': ms / steps, 'launches': int(launches), 'clocks': clocks, 'final_loss': final_loss,
                'e2e': e2e, 'fused': trainer._fused is not None, 'conv_sel': conv_sel, 'global_batch': global_batch}
         del net, trainer

@@ -302,6 +302,37 @@ def gemm_burst(ctx, dtype, reps=50):
     return out
 
 
+def gemm_batched(ctx, dtype, reps=30):
+    """Batched products: the in-tree batched tcgen05 launch against the library's strided-batched GEMM on identical
+    operands (the per-head attention products of BERT-base at 64 x 128 tokens, and 32 square products of 1024)."""
+    from mxnet_b200.ops.cuda import gemm_ops
+    td = mx.base.to_torch_dtype(dtype)
+    out = []
+    for b, m, n, k, tb in [(768, 128, 128, 64, True), (768, 128, 64, 128, False), (32, 1024, 1024, 1024, False),
+                           (32, 1024, 1024, 1024, True)]:
+        x = torch.randn(b, m, k, device=ctx.torch_device).to(td)
+        y = (torch.randn(b, n, k, device=ctx.torch_device) if tb else torch.randn(b, k, n, device=ctx.torch_device)).to(td)
+        res = {'op': 'gemm_batched', 'batch': b, 'M': m, 'N': n, 'K': k, 'transpose_b': tb, 'dtype': dtype, 'reps': reps}
+        for name, fn in (('tcgen05', lambda: gemm_ops.bgemm(x, False, y, not tb)),
+                         ('library', lambda: torch.bmm(x, y.transpose(1, 2) if tb else y))):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            res[name + '_us'] = round(ms * 1e3, 1)
+            res[name + '_TFLOPs'] = round(2.0 * b * m * n * k / ms / 1e9, 1)
+        gemm_ops.check_errors()
+        res['ratio'] = round(res['tcgen05_TFLOPs'] / res['library_TFLOPs'], 3)
+        out.append(res)
+    return out
+
+
 def gemm_layouts(ctx, dtype, reps=30):
     """The three products of a FullyConnected layer on BERT-base shapes (8192 tokens): forward y = x w^T (both K-major),
     data gradient dx = dy w (w MN-major), weight gradient dw = dy^T x (both MN-major); in-tree kernel against the
@@ -361,6 +392,11 @@ def main():
         if name == 'gemm_layouts':
             if ctx.device_type == 'gpu':
                 for r in gemm_layouts(ctx, dtype):
+                    print(json.dumps(r), flush=True)
+            continue
+        if name == 'gemm_batched':
+            if cuda:
+                for r in gemm_batched(ctx, dtype):
                     print(json.dumps(r), flush=True)
             continue
         if name == 'gemm_burst':

@@ -95,13 +95,22 @@ class _Graphed(object):
                     # falls back to the engine (see _Replay.backward).
                     n_in = sum(1 for t in self.static_in if t.requires_grad)
                     self.grad_targets = []
+                    acc_dst, acc_src = [], []
                     for arr, gi in zip(self.param_arrays, gin[n_in:]):
                         tgt = arr._grad._data if getattr(arr, '_grad', None) is not None else None
                         ok = (gi is not None and tgt is not None and arr._grad_req in ('write', 'add')
                               and tgt.shape == gi.shape and tgt.dtype == gi.dtype and tgt.device == gi.device)
                         if ok:
-                            tgt.add_(gi)
+                            acc_dst.append(tgt)
+                            acc_src.append(gi)
                         self.grad_targets.append(tgt if ok else None)
+                    if acc_dst:
+                        if env.get('MXNET_B200_KERNELS') and _kernels.available():
+                            from ..ops.cuda import optim_ops
+                            optim_ops.multi_add_(acc_dst, acc_src)      # one launch per 48 parameters
+                        else:
+                            for tgt, gi in zip(acc_dst, acc_src):
+                                tgt.add_(gi)
             self.static_gin = list(gin)
             self.bwd_launches = _kernels.launches() - n1
         torch.cuda.current_stream(dev).wait_stream(stream)

@@ -75,7 +75,14 @@ class BottleneckV1(HybridBlock):
         if self.ds_conv is not None:
             residual = self.ds_bn(self.ds_conv(x))
         if self.fused:
-            out = self.bn1(self.conv1(x))
+            if self.ds_conv is None and self.conv1._kwargs.get('stride') in ((1, 1), 1):
+                # identity block: the convolution and the skip connection leave the same tensor as one operator, so the
+                # backward pass adds the skip gradient inside the data-gradient kernel
+                out, residual = _reg.invoke('_contrib_conv_skip', [x, self.conv1.weight.data(x.context)],
+                                            {k: v for k, v in self.conv1._kwargs.items() if k != 'no_bias'})
+                out = self.bn1(out)
+            else:
+                out = self.bn1(self.conv1(x))
             out = self.bn2(self.conv2(out))
             return self.bn3(self.conv3(out), residual)
         relu = lambda t: _reg.invoke('Activation', [t], {'act_type': 'relu'})

@@ -35,6 +35,13 @@ def _split_qkv(qkv, heads):
     return x[:, :, :, 0], x[:, :, :, 1], x[:, :, :, 2]
 
 
+def _batch_matmul(a, b, transpose_a=False, transpose_b=False):
+    """The per-head products of the interleaved attention operators: one batched launch of the tcgen05 GEMM for
+    half-precision CUDA operands (the reference uses cublasGemmStridedBatchedEx, src/operator/contrib/transformer.cu:39-245)."""
+    from . import gemm as _gemm
+    return _gemm.batch_matmul(a, b, transpose_a, transpose_b)
+
+
 @register('_contrib_interleaved_matmul_selfatt_qk', 'interleaved_matmul_selfatt_qk', inputs=('queries_keys_values',),
           defaults={'heads': 1})
 def interleaved_matmul_selfatt_qk(queries_keys_values, heads=1):
@@ -42,7 +49,7 @@ def interleaved_matmul_selfatt_qk(queries_keys_values, heads=1):
     T, N, H, D = q.shape
     q2 = q.permute(1, 2, 0, 3).reshape(N * H, T, D)
     k2 = k.permute(1, 2, 0, 3).reshape(N * H, T, D)
-    return torch.bmm(q2 / math.sqrt(D), k2.transpose(1, 2))
+    return _batch_matmul(q2 / math.sqrt(D), k2, False, True)
 
 
 @register('_contrib_interleaved_matmul_selfatt_valatt', 'interleaved_matmul_selfatt_valatt',
@@ -51,7 +58,7 @@ def interleaved_matmul_selfatt_valatt(queries_keys_values, attention, heads=1):
     _, _, v = _split_qkv(queries_keys_values, heads)
     T, N, H, D = v.shape
     v2 = v.permute(1, 2, 0, 3).reshape(N * H, T, D)
-    out = torch.bmm(attention, v2)
+    out = _batch_matmul(attention, v2)
     return out.reshape(N, H, T, D).permute(2, 0, 1, 3).reshape(T, N, H * D)
 
 
@@ -65,7 +72,7 @@ def interleaved_matmul_encdec_qk(queries, keys_values, heads=1):
     kv = keys_values.reshape(Tk, N, heads, 2, D)
     q2 = q.permute(1, 2, 0, 3).reshape(N * heads, Tq, D)
     k2 = kv[:, :, :, 0].permute(1, 2, 0, 3).reshape(N * heads, Tk, D)
-    return torch.bmm(q2 / math.sqrt(D), k2.transpose(1, 2))
+    return _batch_matmul(q2 / math.sqrt(D), k2, False, True)
 
 
 @register('_contrib_interleaved_matmul_encdec_valatt', 'interleaved_matmul_encdec_valatt',
@@ -75,7 +82,7 @@ def interleaved_matmul_encdec_valatt(keys_values, attention, heads=1):
     kv = keys_values.reshape(Tk, N, heads, 2, -1)
     D = kv.shape[-1]
     v2 = kv[:, :, :, 1].permute(1, 2, 0, 3).reshape(N * heads, Tk, D)
-    out = torch.bmm(attention, v2)
+    out = _batch_matmul(attention, v2)
     Tq = attention.shape[1]
     return out.reshape(N, heads, Tq, D).permute(2, 0, 1, 3).reshape(Tq, N, heads * D)
 

@@ -62,7 +62,7 @@ def _time_us(fn, reps=5):
 def use_own(direction, dirs, key, own_fn, lib_fn, lib_extra_us=0.0):
     """Whether `direction` of the convolution described by `key` runs on the in-tree kernel."""
     if 'auto' not in dirs:
-        return direction in dirs
+        return direction.split('+')[0] in dirs          # 'dgrad+skip' follows the setting of 'dgrad'
     k = (direction,) + key
     hit = _tuned.get(k)
     if hit is None:
@@ -264,6 +264,67 @@ class _ConvNHWC(torch.autograd.Function):
             dw = ldw if lib_dw else dw
         db = dy.sum((0, 1, 2)) if has_bias and ctx.needs_input_grad[2] else None
         return dx, dw, db, None, None, None, None, None
+
+
+class _ConvSkipNHWC(torch.autograd.Function):
+    """``(conv(x, w), x)``: a stride-1 convolution whose input also continues down a skip connection (the first
+    convolution of an identity residual block).  Both gradients of ``x`` reach this node together, so the backward pass
+    can add the skip gradient inside the data-gradient kernel's epilogue instead of a separate pass that reads both
+    tensors and writes the sum (three passes over the largest activation of the block).  The choice between the fused
+    in-tree kernel and library data gradient + add is timed per shape like every other direction."""
+
+    @staticmethod
+    def forward(ctx, x, w, pad, dilate, dirs, want_stats):
+        key = (x.dtype,) + tuple(x.shape) + (w.shape[0], w.shape[1], w.shape[2]) + tuple(pad) + tuple(dilate) + (1, 1)
+        ho, wo = out_hw(x.shape[1], x.shape[2], w.shape[1:3], pad, dilate)
+        credit = x.shape[0] * ho * wo * w.shape[0] * x.element_size() / _BN_REDUCE_BYTES_PER_US if want_stats else 0.0
+        if use_own('fwd', dirs, key, lambda: conv_forward(x, w, None, None, pad, dilate, False, want_stats),
+                   lambda: _library_forward(x, w, None, pad, dilate), credit):
+            y, stats = conv_forward(x, w, None, None, pad, dilate, False, want_stats)
+        else:
+            y, stats = _library_forward(x, w, None, pad, dilate), None
+        ctx.save_for_backward(x, w)
+        ctx.geom = (pad, dilate, dirs, key)
+        if stats is None:
+            stats = x.new_empty(0, dtype=torch.float32)
+        ctx.mark_non_differentiable(stats)
+        return y, stats, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, _ds, dskip):
+        x, w = ctx.saved_tensors
+        pad, dilate, dirs, key = ctx.geom
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            if dskip is None:
+                if use_own('dgrad', dirs, key, lambda: conv_dgrad(dy, w, x.shape[1:3], pad, dilate),
+                           lambda: _library_backward(x, w, dy, pad, dilate, True, False)):
+                    dx = conv_dgrad(dy, w, x.shape[1:3], pad, dilate)
+                else:
+                    dx = _library_backward(x, w, dy, pad, dilate, True, False)[0]
+            else:
+                dskip = dskip.contiguous()
+                fused = lambda: conv_dgrad(dy, w, x.shape[1:3], pad, dilate, dskip)
+                separate = lambda: _library_backward(x, w, dy, pad, dilate, True, False)[0].add_(dskip)
+                dx = fused() if use_own('dgrad+skip', dirs, key, fused, separate) else separate()
+        if ctx.needs_input_grad[1]:
+            if use_own('wgrad', dirs, key, lambda: conv_wgrad(x, dy, w.shape[1:3], pad, dilate),
+                       lambda: _library_backward(x, w, dy, pad, dilate, False, True)):
+                dw = conv_wgrad(x, dy, w.shape[1:3], pad, dilate)
+            else:
+                dw = _library_backward(x, w, dy, pad, dilate, False, True)[1]
+        return dx, dw, None, None, None, None
+
+
+def conv2d_skip_nhwc(data, weight, pad, dilate=(1, 1), want_stats=True):
+    """``(conv(data, weight), data)`` for a stride-1 convolution without bias; see :class:`_ConvSkipNHWC`."""
+    dirs = directions()
+    want_stats = want_stats and ('fwd' in dirs or 'auto' in dirs) and torch.is_grad_enabled()
+    y, stats, skip = _ConvSkipNHWC.apply(data, weight, tuple(pad), tuple(dilate), dirs, want_stats)
+    if stats.numel():
+        y._mxb_bn_partials = (stats, y._version)
+    return y, skip
 
 
 def conv2d_nhwc(data, weight, bias, stride, pad, dilate=(1, 1), want_stats=True):

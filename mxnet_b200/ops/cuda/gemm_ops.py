@@ -227,3 +227,72 @@ class MatmulFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             db = gemm(a, dc, True, True) if ok else torch.matmul(a.t(), dc)  # a[M, K]^T . dc[M, N]
         return da, db
+
+
+def bgemm(a, a_mn, b, b_mn, out=None):
+    """Batched product on the tcgen05 kernel: ``out[i] = op(a[i]) @ op(b[i])`` for 3-D contiguous half-precision operands.
+    ``a`` is ``[batch, rows, k]`` (``a_mn=False``) or ``[batch, k, rows]``; ``b`` is ``[batch, cols, k]`` (``b_mn=False``) or
+    ``[batch, k, cols]``; the result is ``[batch, rows, cols]``.  All matrices of the batch form one persistent grid."""
+    if not a.is_contiguous():
+        a = a.contiguous()
+    if not b.is_contiguous():
+        b = b.contiguous()
+    nb = a.shape[0]
+    K, M = (a.shape[1], a.shape[2]) if a_mn else (a.shape[2], a.shape[1])
+    Kb, N = (b.shape[1], b.shape[2]) if b_mn else (b.shape[2], b.shape[1])
+    require(a, 'a')
+    require(b, 'b', dtype=a.dtype, device=a.device)
+    if K != Kb or b.shape[0] != nb:
+        raise ValueError('batched product: operands disagree (%s, %s)' % (tuple(a.shape), tuple(b.shape)))
+    d = out if out is not None else torch.empty(nb, M, N, dtype=a.dtype, device=a.device)
+    require(d, 'out', dtype=a.dtype, device=a.device, shape=(nb, M, N))
+    rc = lib().mxb_gemm_batched(dt(a), ptr(a), ptr(b), ptr(d), None, nb, M, N, K, a.shape[2], b.shape[2], N,
+                                a.shape[1] * a.shape[2], b.shape[1] * b.shape[2], M * N, 1 if a_mn else 0, 1 if b_mn else 0, 0,
+                                ptr(_workspace(a.device)), ptr(_error_flag(a.device)), stream_ptr(a.device))
+    check(rc, 'batched gemm')
+    count_launch(1)
+    return d
+
+
+def bgemm_supported(a, b):
+    """3-D half-precision CUDA operands whose innermost extents are multiples of 8 (16-byte rows for the copy engine)."""
+    return (a.dim() == 3 and b.dim() == 3 and a.is_cuda and a.dtype == b.dtype and a.dtype in (torch.float16, torch.bfloat16)
+            and a.shape[0] == b.shape[0] and a.shape[0] >= 1 and a.shape[2] % 8 == 0 and b.shape[2] % 8 == 0
+            and a.shape[1] % 8 == 0 and b.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0)
+
+
+def _lib_bmm(a, ta, b, tb):
+    return torch.bmm(a.transpose(1, 2) if ta else a, b.transpose(1, 2) if tb else b)
+
+
+class BatchMatmulFn(torch.autograd.Function):
+    """``c[i] = op(a[i]) @ op(b[i])`` (``batch_dot`` with its ``transpose_a`` / ``transpose_b`` flags): forward and both
+    gradients are batched products on the same kernel, each read in the layout it is stored in (no transposed copies);
+    per shape and product the faster of this kernel and the library's strided-batched GEMM is kept
+    (``MXNET_B200_GEMM_AUTOTUNE``)."""
+
+    @staticmethod
+    def forward(ctx, a, b, ta, tb):
+        ctx.save_for_backward(a, b)
+        ctx.flags = (ta, tb)
+        key = ('bfwd', a.dtype, tuple(a.shape), tuple(b.shape), ta, tb)
+        if use_own(key, lambda: bgemm(a, ta, b, not tb), lambda: _lib_bmm(a, ta, b, tb)):
+            return bgemm(a, ta, b, not tb)
+        return _lib_bmm(a, ta, b, tb)
+
+    @staticmethod
+    def backward(ctx, dc):
+        a, b = ctx.saved_tensors
+        ta, tb = ctx.flags
+        dc = dc.contiguous()
+        da = db = None
+        ok = bgemm_supported(dc, dc)
+        if ctx.needs_input_grad[0]:
+            own = (lambda: bgemm(dc, False, b, tb)) if not ta else (lambda: bgemm(b, tb, dc, False))
+            ref = (lambda: _lib_bmm(dc, False, b, not tb)) if not ta else (lambda: _lib_bmm(b, tb, dc, True))
+            da = own() if ok and use_own(('bdgrad_a', a.dtype, tuple(a.shape), tuple(b.shape), ta, tb), own, ref) else ref()
+        if ctx.needs_input_grad[1]:
+            own = (lambda: bgemm(a, not ta, dc, True)) if not tb else (lambda: bgemm(dc, True, a, not ta))
+            ref = (lambda: _lib_bmm(a, not ta, dc, False)) if not tb else (lambda: _lib_bmm(dc, True, a, ta))
+            db = own() if ok and use_own(('bdgrad_b', a.dtype, tuple(a.shape), tuple(b.shape), ta, tb), own, ref) else ref()
+        return da, db, None, None

@@ -59,13 +59,14 @@ __device__ __forceinline__ float4* sk_slot_ptr(float* slot, int c0, int v, int r
 
 // Epilogue of one warp: drains 32 accumulator rows (TMEM lanes) by BN columns starting at TMEM address `taddr`, adds
 // the bias, applies the activation and stores rows [row0, row0 + 32) x columns [tile_col0, tile_col0 + BN) of D, either
-// through the copy engine (32 x 32 blocks staged in `stg`) or with per-thread stores.
+// through the copy engine (32 x 32 blocks staged in `stg`; `zb` = matrix of a batch, D is then that matrix's base for the
+// per-thread path) or with per-thread stores.
 // Stream-K pieces: with `slot` set, the fp32 partial products of this k-range are stored into that slot (this warp's
 // rows at `part_row0`) and nothing else is written; gemm_sk_finish_kernel adds the pieces of a tile up afterwards.
 template <typename T, int BN>
 __device__ __forceinline__ void drain_quarter(uint32_t taddr, uint8_t* stg, const CUtensorMap* map_d, int use_tma_store,
                                               T* __restrict__ D, const T* __restrict__ bias, int M, int N, int ldd, int act,
-                                              int row0, int tile_col0, int lane, float* __restrict__ slot = nullptr,
+                                              int row0, int tile_col0, int lane, int zb, float* __restrict__ slot = nullptr,
                                               int part_row0 = 0) {
   const int row = row0 + lane;
   const bool bias_vec = bias != nullptr && ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
@@ -130,7 +131,7 @@ __device__ __forceinline__ void drain_quarter(uint32_t taddr, uint8_t* stg, cons
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(map_d, stg, col0, row0);
+          tma_store_3d(map_d, stg, col0, row0, zb);
           tma_store_commit();
         }
       }
@@ -206,7 +207,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                const __grid_constant__ CUtensorMap map_d, int use_tma_store, T* __restrict__ D, const T* __restrict__ bias, int M,
                int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, const FastDiv fd_tiles_m,
                int full_tiles, int sk_tiles, int sk_ctas, float* __restrict__ sk_ws, int a3d, int b3d,
-               int* __restrict__ error_flag) {
+               const FastDiv fd_tiles_batch, long long stride_d, int* __restrict__ error_flag) {
   using Cfg = TileCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr uint32_t B_BYTES = Cfg::B_BYTES;
@@ -262,31 +263,32 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       UnitIter u;
       u.init(full_tiles, sk_tiles, sk_ctas, num_k);
       while (ok && !*abort_flag && u.next()) {
-        uint32_t tile_n_u, tile_m_u;
-        fd_divmod((uint32_t)u.tile, fd_tiles_m, &tile_n_u, &tile_m_u);
-        const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u;
+        uint32_t zb_u, in_batch, tile_n_u, tile_m_u;
+        fd_divmod((uint32_t)u.tile, fd_tiles_batch, &zb_u, &in_batch);      // the outermost coordinate of every map: the matrix of a batch
+        fd_divmod(in_batch, fd_tiles_m, &tile_n_u, &tile_m_u);
+        const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u, zb = (int)zb_u;
         const int k0 = u.k0, k1 = u.k1;
         for (int kt = k0; kt < k1; ++kt) {
           if (!mbar_wait(&empty[st], ph ^ 1u)) { *abort_flag = 1; ok = false; break; }
           mbar_expect_tx(&full[st], A_BYTES + B_BYTES);
           if (!a_mn) {
-            tma_load_2d(sA + st * A_BYTES, &map_a, kt * BK, tile_m * BM, &full[st]);
+            tma_load_3d(sA + st * A_BYTES, &map_a, kt * BK, tile_m * BM, zb, &full[st]);
           } else if (a3d) {
             // all 64-column chunks of the tile in one box {64 columns, 64 k-rows, BM/64 chunks}
-            tma_load_3d(sA + st * A_BYTES, &map_a, 0, kt * BK, tile_m * (BM / 64), &full[st]);
+            tma_load_4d(sA + st * A_BYTES, &map_a, 0, kt * BK, tile_m * (BM / 64), zb, &full[st]);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
-              tma_load_2d(sA + st * A_BYTES + c * kMnChunkBytes, &map_a, tile_m * BM + c * 64, kt * BK, &full[st]);
+              tma_load_3d(sA + st * A_BYTES + c * kMnChunkBytes, &map_a, tile_m * BM + c * 64, kt * BK, zb, &full[st]);
           }
           if (!b_mn) {
-            tma_load_2d(sB + st * B_BYTES, &map_b, kt * BK, tile_n * BN, &full[st]);
+            tma_load_3d(sB + st * B_BYTES, &map_b, kt * BK, tile_n * BN, zb, &full[st]);
           } else if (b3d) {
-            tma_load_3d(sB + st * B_BYTES, &map_b, 0, kt * BK, tile_n * (BN / 64), &full[st]);
+            tma_load_4d(sB + st * B_BYTES, &map_b, 0, kt * BK, tile_n * (BN / 64), zb, &full[st]);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sB + st * B_BYTES + c * kMnChunkBytes, &map_b, tile_n * BN + c * 64, kt * BK, &full[st]);
+              tma_load_3d(sB + st * B_BYTES + c * kMnChunkBytes, &map_b, tile_n * BN + c * 64, kt * BK, zb, &full[st]);
           }
           ++it;
           if (++st == STAGES) { st = 0; ph ^= 1u; }
@@ -340,9 +342,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     UnitIter u;
     u.init(full_tiles, sk_tiles, sk_ctas, num_k);
     for (; u.next(); ++t) {
-      uint32_t tile_n_u, tile_m_u;
-      fd_divmod((uint32_t)u.tile, fd_tiles_m, &tile_n_u, &tile_m_u);
-      const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u;
+      uint32_t zb_u, in_batch, tile_n_u, tile_m_u;
+      fd_divmod((uint32_t)u.tile, fd_tiles_batch, &zb_u, &in_batch);
+      fd_divmod(in_batch, fd_tiles_m, &tile_n_u, &tile_m_u);
+      const int tile_m = (int)tile_m_u, tile_n = (int)tile_n_u, zb = (int)zb_u;
+      T* Db = D + (long long)zb * stride_d;
       const int buf = t & 1;
       const bool ready = mbar_wait(&acc_full[buf], ((uint32_t)t >> 1) & 1u);
       if (!ready) *abort_flag = 1;
@@ -351,11 +355,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::ACC_STRIDE);
       const int row0 = tile_m * BM + q * 32, col0 = tile_n * BN;
       if (!u.partial) {
-        drain_quarter<T, BN>(taddr, stg, &map_d, use_tma_store, D, bias, M, N, ldd, act, row0, col0, lane);
+        drain_quarter<T, BN>(taddr, stg, &map_d, use_tma_store, Db, bias, M, N, ldd, act, row0, col0, lane, zb);
       } else {
         // A piece of a stream-K tile: store this warp's 32 rows of fp32 partial products into this CTA's slot; the
         // finishing kernel that follows on the stream adds the pieces of each tile in a fixed order.
-        drain_quarter<T, BN>(taddr, stg, &map_d, use_tma_store, D, bias, M, N, ldd, act, row0, col0, lane,
+        drain_quarter<T, BN>(taddr, stg, &map_d, use_tma_store, Db, bias, M, N, ldd, act, row0, col0, lane, zb,
                              sk_ws + ((size_t)blockIdx.x * 2 + (size_t)u.slot) * ((size_t)BM * BN), q * 32);
       }
       // this warp has finished reading the accumulator: let the MMA warp reuse it
@@ -388,7 +392,8 @@ constexpr int kSkMaxPieces = 8;      // the plan cuts a tile into at most this m
 template <typename T>
 __global__ void __launch_bounds__(1024)
 gemm_sk_finish_kernel(const float* __restrict__ sk_ws, const T* __restrict__ bias, T* __restrict__ D, int M, int N, int ldd, int act,
-                      int bn, int tiles_m, int full_tiles, int sk_tiles, int sk_ctas, int num_k) {
+                      int bn, int tiles_m, int full_tiles, int sk_tiles, int sk_ctas, int num_k, int tiles_per_batch,
+                      long long stride_d) {
   __shared__ const float* piece[kSkMaxPieces];
   __shared__ int n_pieces;
   const int chunks = bn >> 5;
@@ -410,7 +415,9 @@ gemm_sk_finish_kernel(const float* __restrict__ sk_ws, const T* __restrict__ bia
   const int n = n_pieces;
   if (n == 0) return;
   const int tile = full_tiles + t;
-  const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+  const int zb = tile / tiles_per_batch, in_batch = tile - zb * tiles_per_batch;
+  const int tile_m = in_batch % tiles_m, tile_n = in_batch / tiles_m;
+  D += (long long)zb * stride_d;
   const int v = threadIdx.x >> 7, r = threadIdx.x & (BM - 1);
   const size_t off = (size_t)(chunk * 8 + v) * BM + r;
   float4 p[kSkMaxPieces];
@@ -532,22 +539,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint32_t fb = full_leader + (uint32_t)st * 8u;
           if (rank == 0) mbar_expect_tx(&full[st], 2u * (A_BYTES + B_BYTES));
           if (!a_mn) {
-            tma_pair_load_2d(sA + st * A_BYTES, &map_a, kt * BK, row_a, fb);
+            tma_pair_load_3d(sA + st * A_BYTES, &map_a, kt * BK, row_a, 0, fb);
           } else if (a3d) {
-            tma_pair_load_3d(sA + st * A_BYTES, &map_a, 0, kt * BK, row_a / 64, fb);
+            tma_pair_load_4d(sA + st * A_BYTES, &map_a, 0, kt * BK, row_a / 64, 0, fb);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
-              tma_pair_load_2d(sA + st * A_BYTES + c * kMnChunkBytes, &map_a, row_a + c * 64, kt * BK, fb);
+              tma_pair_load_3d(sA + st * A_BYTES + c * kMnChunkBytes, &map_a, row_a + c * 64, kt * BK, 0, fb);
           }
           if (!b_mn) {
-            tma_pair_load_2d(sB + st * B_BYTES, &map_b, kt * BK, row_b, fb);
+            tma_pair_load_3d(sB + st * B_BYTES, &map_b, kt * BK, row_b, 0, fb);
           } else if (b3d) {
-            tma_pair_load_3d(sB + st * B_BYTES, &map_b, 0, kt * BK, row_b / 64, fb);
+            tma_pair_load_4d(sB + st * B_BYTES, &map_b, 0, kt * BK, row_b / 64, 0, fb);
           } else {
 #pragma unroll
             for (int c = 0; c < BNH / 64; ++c)
-              tma_pair_load_2d(sB + st * B_BYTES + c * kMnChunkBytes, &map_b, row_b + c * 64, kt * BK, fb);
+              tma_pair_load_3d(sB + st * B_BYTES + c * kMnChunkBytes, &map_b, row_b + c * 64, kt * BK, 0, fb);
           }
           ++it;
           if (++st == STAGES) { st = 0; ph ^= 1u; }
@@ -602,7 +609,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::ACC_STRIDE);
       drain_quarter<T, BN>(taddr, stg, &map_d, use_tma_store, D, bias, M, N, ldd, act,
-                           (int)tile_m_u * BM2 + (int)rank * BM + q * 32, (int)tile_n_u * BN, lane);
+                           (int)tile_m_u * BM2 + (int)rank * BM + q * 32, (int)tile_n_u * BN, lane, 0);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader + (uint32_t)buf * 8u);
@@ -635,33 +642,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
-// 2-D row-major [rows, cols] half tensor, row pitch `ld` elements; box = box_rows x 64 columns, 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, int bf16, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+// Every tensor map carries the batch as its outermost dimension (extent 1 for a plain product), `bstride` elements
+// apart, so that one kernel serves single and batched products and a tile never reads across matrices.
+//
+// Row-major [rows, cols] half matrices, row pitch `ld` elements; box = box_rows x 64 columns, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int bf16, int64_t rows, int64_t cols, int64_t ld, int box_rows,
+                    int64_t batch, int64_t bstride) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -10;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base),
-                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return rc == CUDA_SUCCESS ? 0 : -11;
-}
-
-// MN-major operand: global tensor [K rows, MN columns] with row pitch `ld`; box = 64 k-rows x 64 columns.
-static int make_map_mn(CUtensorMap* map, const void* base, int bf16, int64_t krows, int64_t mn, int64_t ld) {
-  return make_map(map, base, bf16, krows, mn, ld, BK);
-}
-
-// The same operand when MN is a multiple of 64: a 3-D view {64 columns, K rows, MN/64 chunks} (chunk stride 128 bytes)
-// whose box {64, 64, chunks} brings every chunk of a tile with one copy, chunk after chunk in shared memory.
-static int make_map_mn3(CUtensorMap* map, const void* base, int bf16, int64_t krows, int64_t mn, int64_t ld, int chunks) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return -10;
-  cuuint64_t dims[3] = {64, (cuuint64_t)krows, (cuuint64_t)(mn / 64)};
-  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128};
-  cuuint32_t box[3] = {64, (cuuint32_t)BK, (cuuint32_t)chunks};
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch > 1 ? bstride : rows * ld) * 2};
+  cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base),
                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -669,15 +660,38 @@ static int make_map_mn3(CUtensorMap* map, const void* base, int bf16, int64_t kr
   return rc == CUDA_SUCCESS ? 0 : -11;
 }
 
-// Output matrix [M, N] with row pitch ldd for the epilogue's stores: box = 32 rows x 32 columns, 64-byte swizzle.
-static int make_map_store(CUtensorMap* map, const void* base, int bf16, int64_t rows, int64_t cols, int64_t ld) {
+// MN-major operand: global tensor [K rows, MN columns] with row pitch `ld`; box = 64 k-rows x 64 columns.
+static int make_map_mn(CUtensorMap* map, const void* base, int bf16, int64_t krows, int64_t mn, int64_t ld, int64_t batch,
+                       int64_t bstride) {
+  return make_map(map, base, bf16, krows, mn, ld, BK, batch, bstride);
+}
+
+// The same operand when MN is a multiple of 64: a view {64 columns, K rows, MN/64 chunks, batch} (chunk stride 128
+// bytes) whose box {64, 64, chunks, 1} brings every chunk of a tile with one copy, chunk after chunk in shared memory.
+static int make_map_mn3(CUtensorMap* map, const void* base, int bf16, int64_t krows, int64_t mn, int64_t ld, int chunks,
+                        int64_t batch, int64_t bstride) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -10;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {32, 32};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base),
+  cuuint64_t dims[4] = {64, (cuuint64_t)krows, (cuuint64_t)(mn / 64), (cuuint64_t)batch};
+  cuuint64_t strides[3] = {(cuuint64_t)ld * 2, 128, (cuuint64_t)(batch > 1 ? bstride : krows * ld) * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)BK, (cuuint32_t)chunks, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base),
+                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : -11;
+}
+
+// Output matrices [batch][M, N] with row pitch ldd for the epilogue's stores: box = 32 rows x 32 columns, 64-byte swizzle.
+static int make_map_store(CUtensorMap* map, const void* base, int bf16, int64_t rows, int64_t cols, int64_t ld, int64_t batch,
+                          int64_t bstride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -10;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch > 1 ? bstride : rows * ld) * 2};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base),
                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return rc == CUDA_SUCCESS ? 0 : -11;
@@ -719,7 +733,7 @@ static size_t sk_workspace_bytes() { return (size_t)sm_count() * 2 * BM * 256 * 
 template <typename T, int BN>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, int use_tma_store, void* D,
                        const void* bias, int M, int N, int K, int ldd, int act, int bf16, int a_mn, int b_mn, float* ws, int a3d,
-                       int b3d, int* error_flag, cudaStream_t st) {
+                       int b3d, int* error_flag, cudaStream_t st, int batch = 1, long long stride_d = 0) {
   using Cfg = TileCfg<BN>;
   static unsigned long long attr_seen = 0;
   if (first_on_device(&attr_seen)) {
@@ -727,7 +741,9 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
     if (rc != cudaSuccess) return (int)rc;
   }
   const int tiles_m = (M + BM - 1) / BM;
-  const int tiles = tiles_m * ((N + BN - 1) / BN);
+  const int tiles_batch = tiles_m * ((N + BN - 1) / BN);
+  if ((long)tiles_batch * batch > 0x3fffffffL) return -2;
+  const int tiles = tiles_batch * batch;
   const int num_k = (K + BK - 1) / BK;
   const int sms = sm_count();
   const SkPlan plan = plan_streamk(tiles, num_k, sms, g_gemm_streamk && ws != nullptr && sms <= 1024);
@@ -738,10 +754,11 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   gemm_tn_kernel<T, BN><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ma, mb, md, use_tma_store, (T*)D, (const T*)bias, M, N, K, ldd,
                                                                      act, bf16, a_mn, b_mn, make_fastdiv((uint32_t)tiles_m),
                                                                      plan.full_tiles, plan.sk_tiles, plan.sk_ctas, ws, a3d, b3d,
-                                                                     error_flag);
+                                                                     make_fastdiv((uint32_t)tiles_batch), stride_d, error_flag);
   if (plan.sk_tiles > 0)
     gemm_sk_finish_kernel<T><<<plan.sk_tiles * (BN / 32), 1024, 0, st>>>(ws, (const T*)bias, (T*)D, M, N, ldd, act, BN, tiles_m,
-                                                                        plan.full_tiles, plan.sk_tiles, plan.sk_ctas, num_k);
+                                                                        plan.full_tiles, plan.sk_tiles, plan.sk_ctas, num_k,
+                                                                        tiles_batch, stride_d);
   return (int)cudaGetLastError();
 }
 
@@ -843,29 +860,32 @@ using namespace mxb;
 // Requirements: base pointers 16-byte aligned, lda and ldb multiples of 8 elements.  `error_flag` is a device int set
 // to 1 when a CTA gave up waiting (the output is then incomplete).
 static int gemm_run(int dtype, const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda, int ldb,
-                    int ldd, int a_mn, int b_mn, int act, float* ws, int* error_flag, void* stream) {
+                    int ldd, int a_mn, int b_mn, int act, float* ws, int* error_flag, void* stream, int batch = 1,
+                    long long sa = 0, long long sb = 0, long long sd = 0) {
   if (dtype != kF16 && dtype != kBF16) return -1;
   if (M < 1 || N < 1 || K < 1) return -2;
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A % 16) || ((uintptr_t)B % 16) || ((uintptr_t)D % 16)) return -3;
   if (lda < (a_mn ? M : K) || ldb < (b_mn ? N : K) || ldd < N) return -3;
+  if (batch < 1) return -2;
+  if (batch > 1 && ((sa % 8) || (sb % 8) || (sd % 8) || sd < (long long)(M - 1) * ldd + N)) return -3;      // 16-byte aligned matrices
   const int bf16 = dtype == kBF16;
-  const int pbn = pick_pair_bn(M, N, K, b_mn);
+  const int pbn = batch > 1 ? 0 : pick_pair_bn(M, N, K, b_mn);
   const int bn = pbn ? pbn : pick_bn(M, N);
   const int b_rows = pbn ? pbn / 2 : bn;          // rows of B one CTA stages per k-step
   CUtensorMap ma, mb;
   const int a3d = a_mn && (M % 64) == 0, b3d = b_mn && (N % 64) == 0;
-  int rc = a3d ? make_map_mn3(&ma, A, bf16, K, M, lda, BM / 64)
-               : (a_mn ? make_map_mn(&ma, A, bf16, K, M, lda) : make_map(&ma, A, bf16, M, K, lda, BM));
+  int rc = a3d ? make_map_mn3(&ma, A, bf16, K, M, lda, BM / 64, batch, sa)
+               : (a_mn ? make_map_mn(&ma, A, bf16, K, M, lda, batch, sa) : make_map(&ma, A, bf16, M, K, lda, BM, batch, sa));
   if (rc) return rc;
-  rc = b3d ? make_map_mn3(&mb, B, bf16, K, N, ldb, b_rows / 64)
-           : (b_mn ? make_map_mn(&mb, B, bf16, K, N, ldb) : make_map(&mb, B, bf16, N, K, ldb, b_rows));
+  rc = b3d ? make_map_mn3(&mb, B, bf16, K, N, ldb, b_rows / 64, batch, sb)
+           : (b_mn ? make_map_mn(&mb, B, bf16, K, N, ldb, batch, sb) : make_map(&mb, B, bf16, N, K, ldb, b_rows, batch, sb));
   if (rc) return rc;
   // the epilogue stores through the copy engine when D meets a tensor map's rules (16-byte row pitch); otherwise with
   // per-thread stores
   CUtensorMap md = ma;
   const int use_tma_store = (ldd % 8) == 0 ? 1 : 0;
   if (use_tma_store) {
-    rc = make_map_store(&md, D, bf16, M, N, ldd);
+    rc = make_map_store(&md, D, bf16, M, N, ldd, batch, sd);
     if (rc) return rc;
   }
   cudaStream_t st = (cudaStream_t)stream;
@@ -876,9 +896,9 @@ static int gemm_run(int dtype, const void* A, const void* B, void* D, const void
     return bf16 ? MXB_GEMM_PAIR(__nv_bfloat16) : MXB_GEMM_PAIR(__half);
 #undef MXB_GEMM_PAIR
   }
-#define MXB_GEMM(T)                                                                                 \
-  (bn == 256 ? launch_gemm<T, 256>(MXB_GEMM_ARGS) : bn == 192 ? launch_gemm<T, 192>(MXB_GEMM_ARGS)   \
-   : bn == 128 ? launch_gemm<T, 128>(MXB_GEMM_ARGS) : launch_gemm<T, 64>(MXB_GEMM_ARGS))
+#define MXB_GEMM(T)                                                                                                 \
+  (bn == 256 ? launch_gemm<T, 256>(MXB_GEMM_ARGS, batch, sd) : bn == 192 ? launch_gemm<T, 192>(MXB_GEMM_ARGS, batch, sd)    \
+   : bn == 128 ? launch_gemm<T, 128>(MXB_GEMM_ARGS, batch, sd) : launch_gemm<T, 64>(MXB_GEMM_ARGS, batch, sd))
   return bf16 ? MXB_GEMM(__nv_bfloat16) : MXB_GEMM(__half);
 #undef MXB_GEMM
 #undef MXB_GEMM_ARGS
@@ -904,6 +924,18 @@ MXB_EXPORT int mxb_gemm_ws(int dtype, const void* A, const void* B, void* D, con
                            int ldb, int ldd, int a_mn, int b_mn, int act, float* workspace, int* error_flag, void* stream) {
   if (workspace && ((uintptr_t)workspace % 16)) return -3;
   return gemm_run(dtype, A, B, D, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, act, workspace, error_flag, stream);
+}
+
+// `batch` products of identical shape: matrix i of A, B, D starts `stride_a`, `stride_b`, `stride_d` elements (multiples of 8)
+// after matrix i-1; the bias (one value per column) is shared.  Tiles of all matrices form one persistent grid; the
+// stream-K workspace is used as for a single product.  This is the contraction behind batch_dot and the per-head
+// products of attention (the reference calls cublasGemmStridedBatchedEx, src/operator/linalg_impl.h:538-544).
+MXB_EXPORT int mxb_gemm_batched(int dtype, const void* A, const void* B, void* D, const void* bias, int batch, int M, int N, int K,
+                                int lda, int ldb, int ldd, long long stride_a, long long stride_b, long long stride_d, int a_mn,
+                                int b_mn, int act, float* workspace, int* error_flag, void* stream) {
+  if (workspace && ((uintptr_t)workspace % 16)) return -3;
+  return gemm_run(dtype, A, B, D, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, act, workspace, error_flag, stream, batch, stride_a,
+                  stride_b, stride_d);
 }
 
 // Whether mxb_gemm_ws would cut this product by k-steps (for reports; callers may always pass the workspace).

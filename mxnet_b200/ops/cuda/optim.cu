@@ -184,8 +184,72 @@ inline int chunks_of(int64_t n) { return (int)((n + kChunk - 1) / kChunk); }
 
 using namespace mxb;
 
+// dst[t] += src[t] for up to kMaxTensors tensors of one dtype in one launch (16-byte vectors where both pointers allow
+// it).  Used where many small accumulations follow each other: the parameter-gradient accumulation at the end of a
+// captured backward pass (one tensor library launch per parameter otherwise).
+struct AddTable {
+  void* dst[kMaxTensors];
+  const void* src[kMaxTensors];
+  int64_t n[kMaxTensors];
+  int chunk_start[kMaxTensors + 1];
+  int count;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) multi_add_inplace_kernel(const __grid_constant__ AddTable tab) {
+  constexpr int N = Vec16<T>::N;
+  const int total = tab.chunk_start[tab.count];
+  for (int chunk = blockIdx.x; chunk < total; chunk += gridDim.x) {
+    const int t = find_tensor(tab.chunk_start, tab.count, chunk);
+    const int64_t base = (int64_t)(chunk - tab.chunk_start[t]) * kChunk;
+    const int64_t n = tab.n[t];
+    const int64_t end = base + kChunk < n ? base + kChunk : n;
+    T* d = (T*)tab.dst[t];
+    const T* s = (const T*)tab.src[t];
+    const bool vec = (((uintptr_t)d | (uintptr_t)s) & 15) == 0;      // chunk starts are multiples of 8192 elements
+    int64_t i = base + (int64_t)threadIdx.x * N;
+    if (vec) {
+      for (; i + N <= end; i += (int64_t)blockDim.x * N) {
+        Vec16<T> a = ld16(d + i);
+        const Vec16<T> b = ld16(s + i);
+#pragma unroll
+        for (int j = 0; j < N; ++j) a.v[j] = Cvt<T>::from_f(Cvt<T>::to_f(a.v[j]) + Cvt<T>::to_f(b.v[j]));
+        st16(d + i, a);
+      }
+      // the ragged tail of the last chunk: the first lanes past the last whole vector
+      const int64_t tail = base + ((end - base) / N) * N;
+      const int64_t k = tail + threadIdx.x;
+      if (k < end) d[k] = Cvt<T>::from_f(Cvt<T>::to_f(d[k]) + Cvt<T>::to_f(s[k]));
+    } else {
+      for (int64_t k = base + threadIdx.x; k < end; k += blockDim.x) d[k] = Cvt<T>::from_f(Cvt<T>::to_f(d[k]) + Cvt<T>::to_f(s[k]));
+    }
+  }
+}
+
 MXB_EXPORT int mxb_max_tensors() { return kMaxTensors; }
 MXB_EXPORT int mxb_chunk_elems() { return kChunk; }
+
+MXB_EXPORT int mxb_multi_add_inplace(int dtype, int count, void** dst, void** src, const int64_t* sizes, void* stream) {
+  if (count > kMaxTensors || count <= 0) return -2;
+  AddTable tab;
+  tab.count = count;
+  int acc = 0;
+  for (int i = 0; i < count; ++i) {
+    if (sizes[i] < 0) return -2;
+    tab.dst[i] = dst[i]; tab.src[i] = src[i]; tab.n[i] = sizes[i];
+    tab.chunk_start[i] = acc;
+    acc += chunks_of(sizes[i]);
+  }
+  tab.chunk_start[count] = acc;
+  int grid = acc < sm_count() * 8 ? acc : sm_count() * 8;
+  if (grid < 1) grid = 1;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == kF32) multi_add_inplace_kernel<float><<<grid, 256, 0, st>>>(tab);
+  else if (dtype == kF16) multi_add_inplace_kernel<__half><<<grid, 256, 0, st>>>(tab);
+  else if (dtype == kBF16) multi_add_inplace_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(tab);
+  else return -1;
+  return (int)cudaGetLastError();
+}
 
 // dtype: storage type of weights and gradients.  moms / w32 may be null arrays.
 MXB_EXPORT int mxb_multi_sgd(int dtype, int count, void** w, void** g, float** m, float** w32, const float* lrs,
@@ -341,7 +405,7 @@ MXB_EXPORT int mxb_multi_sum_sq_static(int count, void** p, const int64_t* sizes
   int64_t chunks = 0;
   for (int i = 0; i < count; ++i) {
     if (sizes[i] < 0) return MXB_SUM_SQ_ERR_TOO_LARGE;
-    chunks += (sizes[i] + kChunk - 1) / kChunk;
+    chunks += sizes[i] / kChunk + (sizes[i] % kChunk != 0);      // no rounding-up addition: it would overflow near INT64_MAX
     if (chunks > MXB_SUM_SQ_STATIC_MAX_CHUNKS) return MXB_SUM_SQ_ERR_TOO_LARGE;
   }
   float* scratch = nullptr;

@@ -20,9 +20,12 @@
 //   * every call on a device uses the same array.  Calls issued to one stream run in order and are safe;
 //     two calls that can overlap (different streams, or different host threads without ordering between
 //     their streams) race on the array and give wrong sums;
-//   * the first call on each device looks up the array's device address (a runtime query, no launch, no
-//     allocation) and caches it.  Make that first call with the device current and before a stream
-//     capture begins on that device.
+//   * the first call on each device looks up the array's device address and caches it.  The look-up launches
+//     nothing, but it can be the moment the CUDA runtime loads this library's device code onto that device
+//     (lazy module loading), and loading does allocate: the code image and this 256 KiB array.  So make the
+//     first call on every device at start-up, with the device current, before any stream capture begins there
+//     and well before the situations listed above (an out-of-memory handler must not be the first caller).
+//     Later calls on that device allocate nothing.
 // The call does not use cudaMalloc, cudaFree, nor any library routine that allocates.
 #pragma once
 #include <stdint.h>

@@ -43,3 +43,13 @@ def matmul(a, b):
         if gemm_ops.supported(a.shape[0], b.shape[1], a.shape[1]):
             return gemm_ops.MatmulFn.apply(a, b)
     return torch.matmul(a, b)
+
+
+def batch_matmul(a, b, transpose_a=False, transpose_b=False):
+    """``op(a[i]) @ op(b[i])`` over the leading batch axis (``batch_dot``).  Half-precision CUDA operands run as one
+    batched launch of the tcgen05 kernel, reading ``a`` / ``b`` in their stored layout whatever the transpose flags."""
+    if a.dim() == 3 and b.dim() == 3 and _kernel_ok(a, b):
+        from .cuda import gemm_ops
+        if gemm_ops.bgemm_supported(a, b):
+            return gemm_ops.BatchMatmulFn.apply(a, b, bool(transpose_a), bool(transpose_b))
+    return torch.matmul(a.transpose(-1, -2) if transpose_a else a, b.transpose(-1, -2) if transpose_b else b)

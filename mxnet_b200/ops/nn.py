@@ -102,6 +102,26 @@ def convolution(data, weight, bias=None, kernel=(), stride=(), dilate=(), pad=()
     return _to_layout(y, layout)
 
 
+@register('_contrib_conv_skip', inputs=('data', 'weight'),
+          defaults={'kernel': (), 'stride': (), 'dilate': (), 'pad': (), 'num_filter': 0, 'num_group': 1, 'layout': None})
+def conv_skip(data, weight, kernel=(), stride=(), dilate=(), pad=(), num_filter=0, num_group=1, layout=None):
+    """``(Convolution(data, weight, no_bias=True), data)``: the first convolution of an identity residual block together
+    with the skip connection that starts at the same tensor.  Mathematically the second output is the input; as one
+    operator its gradient node receives the gradients of both branches at once, and on the GPU kernels the data gradient
+    adds the skip gradient in its epilogue (the reference sums the two branches with a separate ElementWiseSum,
+    src/nnvm/gradient.cc)."""
+    nsp = data.dim() - 2
+    stride = _tup(stride, nsp) or (1,) * nsp
+    dilate = _tup(dilate, nsp) or (1,) * nsp
+    pad = _tup(pad, nsp) or (0,) * nsp
+    if layout in _CHANNEL_LAST and nsp == 2 and tuple(stride) == (1, 1) and _use_kernels(data):
+        from .cuda import conv_ops
+        if conv_ops.supported(data, weight, stride, dilate, pad, num_group):
+            return conv_ops.conv2d_skip_nhwc(data, weight, pad, dilate)
+    y = convolution(data, weight, None, kernel, stride, dilate, pad, num_filter, num_group, no_bias=True, layout=layout)
+    return y, data
+
+
 @register('Deconvolution', '_npx_deconvolution', inputs=('data', 'weight', 'bias'),
           defaults={'kernel': (), 'stride': (), 'dilate': (), 'pad': (), 'adj': (), 'target_shape': (),
                     'num_filter': 0, 'num_group': 1, 'workspace': 512, 'no_bias': True, 'cudnn_tune': None,

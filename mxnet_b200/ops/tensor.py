@@ -1241,10 +1241,8 @@ def dot(lhs, rhs, transpose_a=False, transpose_b=False, forward_stype=None):
 
 @register('batch_dot', '_npx_batch_dot', inputs=('lhs', 'rhs'), defaults={'transpose_a': False, 'transpose_b': False})
 def batch_dot(lhs, rhs, transpose_a=False, transpose_b=False, forward_stype=None):
-    a = lhs.transpose(-1, -2) if transpose_a else lhs
-    b = rhs.transpose(-1, -2) if transpose_b else rhs
     from . import gemm as _gemm
-    return _gemm.matmul(a, b)
+    return _gemm.batch_matmul(lhs, rhs, transpose_a, transpose_b)
 
 
 @register('_npi_matmul', inputs=('a', 'b'))

@@ -305,3 +305,20 @@ def test_rtc_cuda_module_compiles_and_launches_a_user_kernel():
         mx.rtc.CudaModule('__global__ void broken( { }')
     with pytest.raises(ValueError):
         module.get_kernel('axpy', 'const float x[3]')
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16, torch.float32])
+def test_multi_tensor_add_inplace(dtype):
+    """One launch adds many (destination, source) pairs: odd lengths, lengths around the 8192-element chunk, sources that
+    are not 16-byte aligned, and more pairs than one launch takes."""
+    from mxnet_b200.ops.cuda import optim_ops
+    torch.manual_seed(4)
+    sizes = [1, 7, 8, 9, 8191, 8192, 8193, 100003, 64 * 3 * 7 * 7] + [33 + i for i in range(60)]
+    dsts = [torch.randn(n, device='cuda').to(dtype) for n in sizes]
+    backing = [torch.randn(n + 1, device='cuda').to(dtype) for n in sizes]
+    srcs = [b[1:] if i % 3 == 0 else b[:-1] for i, b in enumerate(backing)]          # every third source is misaligned
+    expect = [(d.float() + s.float()).to(dtype) for d, s in zip(dsts, srcs)]
+    optim_ops.multi_add_(dsts, srcs)
+    torch.cuda.synchronize()
+    for d, e, n in zip(dsts, expect, sizes):
+        assert torch.equal(d, e), n

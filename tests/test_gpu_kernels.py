@@ -292,6 +292,35 @@ def test_tcgen05_gemm_stream_k_last_round(M, N, K):
         _close(d, ref, 1e-2, 2e-2)
 
 
+@pytest.mark.parametrize('ta,tb', [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize('B,M,N,K', [(3, 128, 128, 64), (5, 200, 72, 136), (12, 128, 64, 128), (2, 1024, 1024, 1024), (7, 8, 8, 8)])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_tcgen05_batched_gemm_and_batch_dot_gradients(ta, tb, B, M, N, K, dtype):
+    """``batch_dot`` with every combination of its transpose flags on the batched tcgen05 kernel: forward and both
+    gradients against fp32, with matrices whose tiles are partial (no tile may read its neighbour in the batch)."""
+    from mxnet_b200 import env
+    torch.manual_seed(14)
+    a = (torch.randn(B, K, M, device=_dev()) if ta else torch.randn(B, M, K, device=_dev())).div(4).to(dtype)
+    b = (torch.randn(B, N, K, device=_dev()) if tb else torch.randn(B, K, N, device=_dev())).div(4).to(dtype)
+    af, bf = a.float().requires_grad_(True), b.float().requires_grad_(True)
+    ref = torch.bmm(af.transpose(1, 2) if ta else af, bf.transpose(1, 2) if tb else bf)
+    dc = (torch.randn_like(ref) / 4).to(dtype)
+    ref.backward(dc.float())
+    with env.scope('MXNET_B200_GEMM_AUTOTUNE', '0'):          # always the in-tree kernel
+        x, y = nd.NDArray._from_tensor(a.clone(), mx.gpu(0)), nd.NDArray._from_tensor(b.clone(), mx.gpu(0))
+        x.attach_grad()
+        y.attach_grad()
+        with autograd.record():
+            c = nd.batch_dot(x, y, transpose_a=ta, transpose_b=tb)
+        c.backward(nd.NDArray._from_tensor(dc, mx.gpu(0)))
+    from mxnet_b200.ops.cuda import gemm_ops
+    gemm_ops.check_errors()
+    tol = (1e-2, 2e-3 * K ** 0.5) if dtype == torch.float16 else (3e-2, 1.5e-2 * K ** 0.5)
+    _close(c._data, ref, *tol)
+    _close(x.grad._data, af.grad, tol[0], tol[1] * (N / K) ** 0.5 + 1e-2)
+    _close(y.grad._data, bf.grad, tol[0], tol[1] * (M / K) ** 0.5 + 1e-2)
+
+
 def test_linear_autograd_through_tcgen05():
     from mxnet_b200.ops.cuda import gemm_ops
     torch.manual_seed(6)
@@ -832,22 +861,24 @@ def _flip_tolerant_close(got, ref, tol, max_bad_frac, what):
     assert rel <= 5e-2, '%s: relative L2 error %g' % (what, rel)
 
 
-def test_resnet_block_kernels_match_fp32_oracle():
+@pytest.mark.parametrize('downsample,cin', [(True, 32), (False, 64)])
+def test_resnet_block_kernels_match_fp32_oracle(downsample, cin):
     """Both half-precision paths of a bottleneck block (in-tree kernels, library kernels) against an fp32 evaluation of
-    the same block with the same weights."""
+    the same block with the same weights: the down-sampling block, and the identity block whose first convolution and
+    skip connection are one operator (skip gradient added in the data-gradient epilogue)."""
     from mxnet_b200 import env
     from mxnet_b200.gluon.model_zoo.vision.resnet import BottleneckV1
     ctx = mx.gpu(0)
-    blk = BottleneckV1(64, 1, True, in_channels=32, layout='NHWC', fused=True, v1b=True)
+    blk = BottleneckV1(64, 1, downsample, in_channels=cin, layout='NHWC', fused=True, v1b=True)
     blk.initialize(mx.init.Xavier(), ctx=ctx)
     for p in blk.collect_params().values():
         if p.grad_req != 'null':
             p.cast('float16')
-    x = nd.array(np.random.randn(4, 8, 8, 32).astype('float16'), ctx=ctx, dtype='float16')
+    x = nd.array(np.random.randn(4, 8, 8, cin).astype('float16'), ctx=ctx, dtype='float16')
     blk(x)                       # finishes the deferred initialisation of the BatchNorm parameters
 
     def run(flag, dtype):
-        with env.scope('MXNET_B200_KERNELS', flag):
+        with env.scope('MXNET_B200_KERNELS', flag), env.scope('MXNET_B200_CONV', '1'):      # every direction in-tree
             xx = x.astype(dtype)
             xx.attach_grad()
             for p in blk.collect_params().values():

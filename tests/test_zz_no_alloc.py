@@ -64,6 +64,10 @@ def test_static_scratch_rejects_requests_beyond_its_size():
     dts = (C.c_int * n)(0, 0)
     rc = fn(n, ptrs, sizes, dts, C.c_void_p(out.data_ptr()), 0, C.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == ERR_TOO_LARGE
+    # element counts near the top of int64: the chunk count must not wrap around into an acceptable number
+    for huge in (2 ** 63 - 1, 2 ** 63 - 8191, 2 ** 62):
+        sizes_huge = (C.c_int64 * n)(huge, 1)
+        assert fn(n, ptrs, sizes_huge, dts, C.c_void_p(out.data_ptr()), 0, None) == ERR_TOO_LARGE
     assert fn(0, ptrs, sizes, dts, C.c_void_p(out.data_ptr()), 0, None) == ERR_BAD_COUNT
     assert fn(49, ptrs, sizes, dts, C.c_void_p(out.data_ptr()), 0, None) == ERR_BAD_COUNT
     torch.cuda.synchronize()
