@@ -333,6 +333,39 @@ def gemm_batched(ctx, dtype, reps=30):
     return out
 
 
+def gemm_int8(ctx, reps=30):
+    """int8 x int8 -> int32 products: the in-tree ``tcgen05.mma.kind::i8`` kernel against the library's int8 GEMM
+    (``torch._int_mm``, cuBLASLt) on identical operands; TOP/s counts 2 M N K integer operations."""
+    from mxnet_b200.ops.cuda import gemm_ops
+    out = []
+    for m, n, k in [(8192, 8192, 8192), (8192, 3072, 768), (8192, 768, 3072), (4096, 4096, 4096), (256, 1000, 2048)]:
+        a = torch.randint(-128, 128, (m, k), device=ctx.torch_device, dtype=torch.int32).to(torch.int8)
+        b = torch.randint(-128, 128, (n, k), device=ctx.torch_device, dtype=torch.int32).to(torch.int8)
+        d = torch.empty(m, n, dtype=torch.int32, device=ctx.torch_device)
+        res = {'op': 'gemm_int8', 'M': m, 'N': n, 'K': k, 'reps': reps}
+        cases = [('tcgen05', lambda: gemm_ops.gemm_i8(a, b, out=d))]
+        if n % 8 == 0:
+            cases.append(('library', lambda: torch._int_mm(a, b.t())))
+        for name, fn in cases:
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            res[name + '_us'] = round(ms * 1e3, 1)
+            res[name + '_TOPs'] = round(2.0 * m * n * k / ms / 1e9, 1)
+        gemm_ops.check_errors()
+        if 'library_TOPs' in res:
+            res['ratio'] = round(res['tcgen05_TOPs'] / res['library_TOPs'], 3)
+        out.append(res)
+    return out
+
+
 def gemm_layouts(ctx, dtype, reps=30):
     """The three products of a FullyConnected layer on BERT-base shapes (8192 tokens): forward y = x w^T (both K-major),
     data gradient dx = dy w (w MN-major), weight gradient dw = dy^T x (both MN-major); in-tree kernel against the
@@ -397,6 +430,11 @@ def main():
         if name == 'gemm_batched':
             if cuda:
                 for r in gemm_batched(ctx, dtype):
+                    print(json.dumps(r), flush=True)
+            continue
+        if name == 'gemm_int8':
+            if cuda:
+                for r in gemm_int8(ctx):
                     print(json.dumps(r), flush=True)
             continue
         if name == 'gemm_burst':

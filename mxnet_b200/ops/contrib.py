@@ -677,20 +677,43 @@ def requantize(data, min_range, max_range, out_type='int8', min_calib_range=None
     return quantize(real, mn, mx, 'int8')
 
 
+def _int8_kernel_ok(x, w):
+    if not (x.is_cuda and x.dtype == torch.int8 and w.dtype == torch.int8):
+        return False
+    if not (env.get('MXNET_B200_KERNELS') and env.get('MXNET_B200_GEMM')):
+        return False
+    from . import cuda
+    from .cuda import gemm_ops
+    return cuda.available() and gemm_ops.gemm_i8_supported(x, w)
+
+
 @register('_contrib_quantized_fully_connected', inputs=('data', 'weight', 'bias', 'min_data', 'max_data', 'min_weight',
                                                         'max_weight', 'min_bias', 'max_bias'), nout=3,
           defaults={'num_hidden': 0, 'no_bias': False, 'flatten': True})
 def quantized_fully_connected(data, weight, bias=None, min_data=None, max_data=None, min_weight=None, max_weight=None,
                               min_bias=None, max_bias=None, num_hidden=0, no_bias=False, flatten=True):
     x = data.reshape(data.shape[0], -1) if flatten else data
-    acc = torch.matmul(x.to(torch.int32).float(), weight.to(torch.int32).float().t())
     sd = torch.maximum(min_data.abs(), max_data.abs()).reshape(()) / 127.0
     sw = torch.maximum(min_weight.abs(), max_weight.abs()).reshape(()) / 127.0
+    qbias = None
     if bias is not None and not no_bias:
         sb = torch.maximum(min_bias.abs(), max_bias.abs()).reshape(()) / 127.0
-        acc = acc + torch.round(bias.float() * sb / (sd * sw))
+        qbias = torch.round(bias.float() * sb / (sd * sw))
     out_range = sd * sw * 2147483647.0
-    return acc.to(torch.int32), (-out_range).reshape(1), out_range.reshape(1)
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if _int8_kernel_ok(x2, weight):
+        # tensor-core path: exact int8 x int8 products with int32 accumulation (tcgen05.mma.kind::i8)
+        from .cuda import gemm_ops
+        acc = gemm_ops.gemm_i8(x2, weight, qbias.to(torch.int32) if qbias is not None else None)
+    else:
+        # integer-valued float arithmetic: exact while the sums stay below 2**24 (fp32) / 2**53 (fp64 for long rows)
+        ft = torch.float32 if x2.shape[-1] * 127 * 127 < (1 << 24) else torch.float64
+        acc = torch.matmul(x2.to(ft), weight.to(ft).t())
+        if qbias is not None:
+            acc = acc + qbias.to(ft)
+        acc = acc.to(torch.int32)
+    return acc.reshape(*lead, weight.shape[0]), (-out_range).reshape(1), out_range.reshape(1)
 
 
 @register('_contrib_quantized_conv', inputs=('data', 'weight', 'bias', 'min_data', 'max_data', 'min_weight', 'max_weight',

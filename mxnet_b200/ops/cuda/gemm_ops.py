@@ -142,6 +142,36 @@ def gemm(a, b, a_mn=False, b_mn=False, bias=None, act=None, out=None):
     return d
 
 
+def gemm_i8_supported(a, b):
+    """int8 CUDA operands [M, K] and [N, K] whose rows a TMA descriptor can address (K a multiple of 16)."""
+    return (a.is_cuda and b.is_cuda and a.dtype == torch.int8 and b.dtype == torch.int8 and a.dim() == 2 and b.dim() == 2
+            and a.shape[1] == b.shape[1] and a.shape[1] % 16 == 0 and a.shape[0] >= 1 and b.shape[0] >= 1)
+
+
+def gemm_i8(a, b, bias=None, out=None):
+    """``a @ b.T + bias`` with int8 ``a`` [M, K], ``b`` [N, K], int32 ``bias`` [N] and int32 result, on the
+    ``tcgen05.mma.kind::i8`` kernel (``gemm_i8.cu``): exact integer arithmetic with 32-bit accumulation."""
+    if not a.is_contiguous():
+        a = a.contiguous()
+    if not b.is_contiguous():
+        b = b.contiguous()
+    require(a, 'a', dtype=torch.int8)
+    require(b, 'b', dtype=torch.int8, device=a.device)
+    (M, K), (N, Kb) = a.shape, b.shape
+    if K != Kb:
+        raise ValueError('contraction sizes differ: %d vs %d' % (K, Kb))
+    if K % 16:
+        raise ValueError('the int8 kernel needs K to be a multiple of 16, got %d' % K)
+    d = out if out is not None else torch.empty(M, N, dtype=torch.int32, device=a.device)
+    require(d, 'out', dtype=torch.int32, device=a.device, shape=(M, N))
+    if bias is not None:
+        require(bias, 'bias', numel=N, dtype=torch.int32, device=a.device)
+    rc = lib().mxb_gemm_i8(ptr(a), ptr(b), ptr(d), ptr(bias), M, N, K, K, K, N, ptr(_error_flag(a.device)), stream_ptr(a.device))
+    check(rc, 'gemm_i8')
+    count_launch(1)
+    return d
+
+
 def operand_ok(t):
     """Row pitch a multiple of 8 elements and a 16-byte aligned base: what a TMA descriptor needs."""
     return t.dim() == 2 and t.shape[1] % 8 == 0 and t.shape[0] >= 1 and t.data_ptr() % 16 == 0

@@ -15,10 +15,30 @@ _DTYPE_CPP_TO_NP = {'float': np.float32, 'double': np.float64, '__half': np.floa
                     'int': np.int32, 'int32_t': np.int32, 'int8_t': np.int8, 'char': np.int8, 'int64_t': np.int64}
 
 
+def _include_dirs():
+    """Directories holding the toolkit's device headers (``cuda_fp16.h`` and friends): NVRTC searches none by itself."""
+    import os
+    found = []
+    roots = [os.environ.get('CUDA_HOME'), os.environ.get('CUDA_PATH'), '/usr/local/cuda']
+    try:
+        import nvidia.cuda_runtime as rt   # the pip wheel of the runtime ships the same headers
+        roots.append(os.path.dirname(rt.__file__))
+    except Exception:   # pylint: disable=broad-except
+        pass
+    for root in roots:
+        inc = os.path.join(root, 'include') if root else None
+        if inc and os.path.isfile(os.path.join(inc, 'cuda_fp16.h')) and inc not in found:
+            found.append(inc)
+    return found
+
+
 class CudaModule(object):
     def __init__(self, source, options=(), exports=()):
         try:
-            from cuda import nvrtc   # cuda-python
+            try:
+                from cuda.bindings import nvrtc   # cuda-python >= 12.8
+            except ImportError:
+                from cuda import nvrtc
         except Exception as e:   # pylint: disable=broad-except
             raise MXNetError('NVRTC bindings are unavailable: %s' % e)
         self._nvrtc = nvrtc
@@ -27,7 +47,8 @@ class CudaModule(object):
         major, minor = torch.cuda.get_device_capability()
         arch = 'sm_%d%d%s' % (major, minor, 'a' if major >= 9 else '')
         err, prog = nvrtc.nvrtcCreateProgram(source.encode(), b'mxb_rtc.cu', 0, [], [])
-        opts = [('--gpu-architecture=' + arch).encode()] + [o.encode() for o in options]
+        opts = [('--gpu-architecture=' + arch).encode()] + [('--include-path=' + d).encode() for d in _include_dirs()]
+        opts += [o.encode() for o in options]
         err, = nvrtc.nvrtcCompileProgram(prog, len(opts), opts)
         if int(err) != 0:
             _, n = nvrtc.nvrtcGetProgramLogSize(prog)
@@ -37,7 +58,10 @@ class CudaModule(object):
         _, n = nvrtc.nvrtcGetCUBINSize(prog)
         cubin = b' ' * n
         nvrtc.nvrtcGetCUBIN(prog, cubin)
-        from cuda import cuda as cu
+        try:
+            from cuda.bindings import driver as cu
+        except ImportError:
+            from cuda import cuda as cu
         self._cu = cu
         torch.cuda.current_stream()   # make sure a context exists
         err, self._module = cu.cuModuleLoadData(cubin)

@@ -920,3 +920,51 @@ def test_hybridize_cuda_graph_matches_eager():
         for p, g in zip(net.collect_params().values(), ref_grads):
             np.testing.assert_allclose(p.grad(ctx).asnumpy(), g, rtol=1e-4, atol=1e-5)
     assert net._cached_op is not None and not net._cached_op._disabled and len(net._cached_op._graphs) == 1
+
+
+@pytest.mark.parametrize('M,N,K', [(1, 16, 16), (128, 128, 128), (130, 200, 144), (64, 1000, 2048), (1024, 1024, 1024),
+                                   (300, 77, 4096), (4096, 512, 16)])
+@pytest.mark.parametrize('with_bias', [False, True])
+def test_tcgen05_int8_gemm_is_exact(M, N, K, with_bias):
+    """``tcgen05.mma.kind::i8``: int8 x int8 products with int32 accumulation are exact, so the result must equal the
+    integer reference bit for bit (fp64 matmul of the same integers is exact for these sizes), bias included; full
+    range values (-128 .. 127) are used."""
+    from mxnet_b200.ops.cuda import gemm_ops
+    g = torch.Generator(device='cuda').manual_seed(M * 7 + N * 3 + K)
+    a = torch.randint(-128, 128, (M, K), device='cuda', generator=g, dtype=torch.int32).to(torch.int8)
+    b = torch.randint(-128, 128, (N, K), device='cuda', generator=g, dtype=torch.int32).to(torch.int8)
+    bias = torch.randint(-100000, 100000, (N,), device='cuda', generator=g, dtype=torch.int32) if with_bias else None
+    assert gemm_ops.gemm_i8_supported(a, b)
+    d = gemm_ops.gemm_i8(a, b, bias)
+    torch.cuda.synchronize()
+    assert int(gemm_ops._error_flag(a.device).item()) == 0
+    ref = torch.matmul(a.double(), b.double().t())
+    if with_bias:
+        ref = ref + bias.double()
+    assert torch.equal(d, ref.to(torch.int32))
+
+
+def test_quantized_fully_connected_runs_on_the_int8_kernel():
+    """``_contrib_quantized_fully_connected`` with int8 CUDA inputs (reference: quantized_fully_connected.cu): the int32
+    output equals the integer oracle, the launch counter shows that the tensor-core kernel ran, and the output range is
+    the product of the input scales."""
+    import mxnet_b200 as mx
+    from mxnet_b200 import nd
+    from mxnet_b200.ops import cuda as kc
+    rng = np.random.RandomState(3)
+    x = rng.randint(-127, 128, (48, 256)).astype('int8')
+    w = rng.randint(-127, 128, (72, 256)).astype('int8')
+    bias = rng.randint(-127, 128, (72,)).astype('int8')
+    ctx = mx.gpu(0)
+    args = [nd.array(x, ctx=ctx, dtype='int8'), nd.array(w, ctx=ctx, dtype='int8'), nd.array(bias, ctx=ctx, dtype='int8')]
+    ranges = [nd.array([v], ctx=ctx) for v in (-2.0, 2.0, -0.5, 0.5, -1.0, 1.0)]
+    before = kc.launches()
+    out, lo, hi = nd.contrib.quantized_fully_connected(*args, *ranges, num_hidden=72)
+    assert kc.launches() == before + 1
+    sd, sw, sb = 2.0 / 127, 0.5 / 127, 1.0 / 127
+    qb = np.round(bias.astype('float64') * np.float32(sb) / (np.float32(sd) * np.float32(sw)))
+    ref = x.astype('int64') @ w.astype('int64').T + qb.astype('int64')
+    assert out.dtype == np.int32
+    np.testing.assert_array_equal(out.asnumpy(), ref.astype('int32'))
+    np.testing.assert_allclose(hi.asnumpy(), [sd * sw * 2147483647.0], rtol=1e-5)
+    np.testing.assert_allclose(lo.asnumpy(), [-sd * sw * 2147483647.0], rtol=1e-5)
