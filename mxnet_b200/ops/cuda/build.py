@@ -10,7 +10,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ['norm.cu', 'softmax.cu', 'optim.cu', 'fused_step.cu', 'gemm_tcgen05.cu', 'pool.cu', 'compress.cu', 'elementwise.cu', 'lstm.cu',
-           'attention.cu', 'conv_tcgen05.cu', 'peer_reduce.cu', 'detection.cu', 'gemm_i8.cu']
+           'attention.cu', 'conv_tcgen05.cu', 'peer_reduce.cu', 'detection.cu', 'gemm_i8.cu', 'lstm_tc.cu']
 LIB = os.path.join(HERE, 'libmxb200_kernels.so')
 FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17', '--use_fast_math',
          '-Xcompiler', '-fPIC', '-Xptxas', '-v']
@@ -24,7 +24,7 @@ def build(force=False, verbose=False):
     srcs = [s for s in SOURCES if os.path.exists(os.path.join(HERE, s))]
     bdir = os.path.join(HERE, 'build')
     os.makedirs(bdir, exist_ok=True)
-    deps = [os.path.join(HERE, h) for h in os.listdir(HERE) if h.endswith(('.cuh', '.h'))]
+    deps = [os.path.join(HERE, h) for h in os.listdir(HERE) if h.endswith(('.cuh', '.h', '.inl'))]
 
     def stale(obj, src):
         if force or not os.path.exists(obj):

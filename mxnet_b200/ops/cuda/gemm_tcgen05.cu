@@ -763,16 +763,23 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
 }
 
 // Tile width of the single-CTA kernel: narrow outputs take the narrow tile; otherwise the width with the lowest
-// column-tiles x (width + fixed cost per tile), which avoids a mostly empty last column tile (N = 384 -> 2 x 192).  Rounds
-// of tiles that do not fill the grid are handled by the stream-K plan, not by narrower tiles.
-static int pick_bn(int M, int N) {
+// rounds x (width + tile height), where a round is one tile on every CTA of the persistent grid: this avoids a
+// mostly empty last column tile (N = 384 -> 2 x 192) and a mostly empty last round (M = 8192, N = 768: 256 tiles of 192
+// columns take two rounds of 320 instead of two rounds of 384).  Outputs with fewer tiles than CTAs are cut by k-steps
+// (stream-K plan), so their rounds are fractional.
+static int pick_bn(int M, int N, int K) {
   if (N <= 64) return 64;
   if (N <= 128) return 128;
+  const long G = sm_count(), tm = (M + BM - 1) / BM;
   int best = 256;
-  long best_cost = 0;
+  double best_cost = 0;
   for (int bn = 256; bn >= 128; bn -= 64) {
-    const long cost = (long)((N + bn - 1) / bn) * (bn + 32);
-    if (bn == 256 || cost < best_cost) { best = bn; best_cost = cost; }
+    const long tiles = tm * ((N + bn - 1) / bn);
+    // short products (under 24 k-steps) are bound by the epilogue, whose cost per output element does not depend on the
+    // tile width: they only avoid the empty last column tile
+    const double rounds = K < 24 * BK ? (double)tiles : tiles < G ? (double)tiles / (double)G : (double)((tiles + G - 1) / G);
+    const double cost = rounds * (bn + BM);              // a tile's time follows the operand bytes it loads per k-step
+    if (bn == 256 || cost < 0.9 * best_cost) { best = bn; best_cost = cost; }      // narrower only for a clear gain
   }
   return best;
 }
@@ -870,7 +877,7 @@ static int gemm_run(int dtype, const void* A, const void* B, void* D, const void
   if (batch > 1 && ((sa % 8) || (sb % 8) || (sd % 8) || sd < (long long)(M - 1) * ldd + N)) return -3;      // 16-byte aligned matrices
   const int bf16 = dtype == kBF16;
   const int pbn = batch > 1 ? 0 : pick_pair_bn(M, N, K, b_mn);
-  const int bn = pbn ? pbn : pick_bn(M, N);
+  const int bn = pbn ? pbn : pick_bn(M, N, K);
   const int b_rows = pbn ? pbn / 2 : bn;          // rows of B one CTA stages per k-step
   CUtensorMap ma, mb;
   const int a3d = a_mn && (M % 64) == 0, b3d = b_mn && (N % 64) == 0;
@@ -941,7 +948,7 @@ MXB_EXPORT int mxb_gemm_batched(int dtype, const void* A, const void* B, void* D
 // Whether mxb_gemm_ws would cut this product by k-steps (for reports; callers may always pass the workspace).
 MXB_EXPORT int mxb_gemm_wants_workspace(int M, int N, int K) {
   if (pick_pair_bn(M, N, K, 0)) return 0;
-  const int bn = pick_bn(M, N);
+  const int bn = pick_bn(M, N, K);
   const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
   return plan_streamk(tiles, (K + BK - 1) / BK, sm_count(), true).sk_tiles > 0 ? 1 : 0;
 }

@@ -9,9 +9,11 @@ from . import lib, ptr, stream_ptr, count_launch, check
 from ._util import dt, require, job_wide
 
 
-def supported(data, state_size, num_layers):
+def supported(data, state_size, num_layers, mode='lstm'):
     if not data.is_cuda or data.dim() != 3 or data.numel() == 0:
         return False
+    if mode == 'lstm' and tc_supported(data.dtype, int(data.shape[1]), int(state_size)):
+        return True
     return bool(lib().mxb_lstm_supported(int(data.shape[1]), int(state_size)))
 
 
@@ -60,13 +62,28 @@ def tuned_choices():
     return dict(_tuned)
 
 
-def _mm(a, b, a_mn, b_mn):
+class _tf32_products(object):
+    """fp32 library GEMMs inside the block run with tf32 operands and fp32 accumulation: the precision of the
+    tensor-core recurrence they surround (and of the library recurrence, whose internal products are tf32 as well)."""
+
+    def __enter__(self):
+        self._old = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+
+    def __exit__(self, *exc):
+        torch.backends.cuda.matmul.allow_tf32 = self._old
+
+
+def _mm(a, b, a_mn, b_mn, tf32=False):
     """op(a) @ op(b) with the tcgen05 kernel when the operands qualify, else the library."""
     from . import gemm_ops
     if a.dtype in (torch.float16, torch.bfloat16) and gemm_ops.operand_ok(a) and gemm_ops.operand_ok(b):
         return gemm_ops.gemm(a, b, a_mn, b_mn)
     aa = a.t() if a_mn else a
     bb = b if b_mn else b.t()
+    if tf32 and a.dtype == torch.float32:
+        with _tf32_products():
+            return aa @ bb
     return aa @ bb
 
 
@@ -134,6 +151,136 @@ class _LSTMLayer(torch.autograd.Function):
         dw_ih = _mm(dg2, x.reshape(T * B, I), True, True)                                         # dg^T . x
         dw_hh = _mm(dg2, hprev, True, True)                                                        # dg^T . h_{t-1}
         db = dg2.sum(0, dtype=torch.float32)
+        return dx, dw_ih, dw_hh, db.to(ctx.bias_dtypes[0]), db.to(ctx.bias_dtypes[1]), dh0, dc0, None
+
+
+def tc_supported(dtype, B, H):
+    """Whether the tensor-core LSTM recurrence (``lstm_tc.cu``) takes this (dtype, batch, hidden size)."""
+    from ... import env
+    if not env.get('MXNET_B200_RNN_TC') or dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        return False
+    code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dtype]
+    return bool(lib().mxb_lstm_tc_supported(code, int(B), int(H)))
+
+
+def _tc_dims(x, B, H):
+    import ctypes
+    out = (ctypes.c_int32 * 8)()
+    check(lib().mxb_lstm_tc_dims(dt(x), int(B), int(H), out), 'lstm_tc_dims')
+    return tuple(int(v) for v in out[:6])
+
+
+def _tc_perm_rows(w, dims):
+    """Rows of a [4H, X] gate-major matrix (or a [4H] vector) regrouped per CTA: row c*4U + g*U + u = row g*H + c*U + u,
+    zero rows for the padded units of the last CTA.  Result [KK, X]."""
+    U, _Bp, _Hp, C, Hc, KK = dims
+    H = w.shape[0] // 4
+    tail = w.shape[1:]
+    out = w.new_zeros((4, Hc) + tuple(tail))
+    out[:, :H] = w.reshape((4, H) + tuple(tail))
+    lead = list(range(4, 4 + len(tail)))
+    return out.reshape((4, C, U) + tuple(tail)).permute(1, 0, 2, *[i - 1 for i in lead]).reshape((KK,) + tuple(tail)).contiguous()
+
+
+def _tc_unperm_rows(w, dims, H):
+    """Inverse of :func:`_tc_perm_rows`: [KK, X] in the per-CTA order back to [4H, X] gate-major."""
+    U, _Bp, _Hp, C, Hc, _KK = dims
+    tail = w.shape[1:]
+    lead = list(range(3, 3 + len(tail)))
+    g = w.reshape((C, 4, U) + tuple(tail)).permute(1, 0, 2, *lead).reshape((4, Hc) + tuple(tail))
+    return g[:, :H].reshape((4 * H,) + tuple(tail))
+
+
+def _tc_pack_forward(w_hh, dims):
+    """[KK, Hp]: the gate rows of W_hh regrouped per CTA, the contraction axis zero padded to whole 128-byte chunks."""
+    Hp = dims[2]
+    H = w_hh.shape[1]
+    w = _tc_perm_rows(w_hh, dims)
+    return w if Hp == H else torch.nn.functional.pad(w, (0, Hp - H))
+
+
+def _tc_pack_backward(w_hh, dims):
+    """[Hc, KK]: row n holds column n of W_hh with the gate rows in the per-CTA order of the saved gates."""
+    Hc = dims[4]
+    H = w_hh.shape[1]
+    w = _tc_perm_rows(w_hh, dims)                 # [KK, H]
+    if Hc != H:
+        w = torch.nn.functional.pad(w, (0, Hc - H))
+    return w.t().contiguous()
+
+
+class _LSTMLayerTC(torch.autograd.Function):
+    """The LSTM layer of :class:`_LSTMLayer` with the recurrence on the tensor cores (``lstm_tc.cu``): h is exchanged
+    row-major, the packed recurrent weights stay in shared memory, one tcgen05 product per time step and CTA.  The gate
+    axis of the input projection, of the saved gates and of the gate gradients is kept in the kernel's per-CTA order
+    (so each thread moves whole 16-byte vectors); only weight-sized tensors are regrouped, before and after."""
+
+    @staticmethod
+    def forward(ctx, x, w_ih, w_hh, b_ih, b_hh, h0, c0, training):
+        L = lib()
+        T, B, I = x.shape
+        H = w_hh.shape[1]
+        x = x.contiguous()
+        w_ih, w_hh, h0, c0 = w_ih.contiguous(), w_hh.contiguous(), h0.contiguous(), c0.contiguous()
+        for t, name, shape in ((w_ih, 'w_ih', (4 * H, I)), (w_hh, 'w_hh', (4 * H, H)), (h0, 'h0', (B, H)), (c0, 'c0', (B, H))):
+            require(t, name, dtype=x.dtype, device=x.device, shape=shape)
+        dims = _tc_dims(x, B, H)
+        _U, Bp, Hp, _C, Hc, KK = dims
+        bias = _tc_perm_rows((b_ih.float() + b_hh.float()).to(x.dtype), dims)
+        require(bias, 'bias', numel=KK, device=x.device)
+        wi = _tc_perm_rows(w_ih, dims)                                     # [KK, I]
+        x2 = x.reshape(T * B, I)
+        from . import gemm_ops
+        if x.dtype in (torch.float16, torch.bfloat16) and gemm_ops.operand_ok(x2) and gemm_ops.operand_ok(wi):
+            xproj = gemm_ops.gemm(x2, wi, False, False, bias)
+        else:
+            with _tf32_products():
+                xproj = torch.addmm(bias, x2, wi.t())
+        wp = _tc_pack_forward(w_hh, dims)
+        y = torch.empty(T, B, H, dtype=x.dtype, device=x.device)
+        hT, cT = torch.empty_like(h0), torch.empty_like(c0)
+        gates = torch.empty(T, B, KK, dtype=x.dtype, device=x.device) if training else None
+        cs = torch.empty(T, B, Hc, dtype=torch.float32, device=x.device) if training else None
+        hbuf = torch.zeros(2, Bp, Hp, dtype=x.dtype, device=x.device)
+        bar = _barrier_words(x.device)
+        check(L.mxb_lstm_tc_forward(dt(x), ptr(xproj), ptr(wp), ptr(h0), ptr(c0), ptr(y), ptr(hT), ptr(cT), ptr(gates), ptr(cs),
+                                    ptr(hbuf), ptr(bar), T, B, H, stream_ptr(x.device)), 'lstm_tc_forward')
+        count_launch(1)
+        ctx.save_for_backward(x, wi, w_hh, h0, c0, y, gates, cs)
+        ctx.bias_dtypes = (b_ih.dtype, b_hh.dtype)
+        ctx.dims = dims
+        ctx.fwd_bar = bar
+        ctx.set_materialize_grads(False)
+        return y, hT, cT
+
+    @staticmethod
+    def backward(ctx, dy, dhT, dcT):
+        x, wi, w_hh, h0, c0, y, gates, cs = ctx.saved_tensors
+        if gates is None:
+            raise RuntimeError('LSTM backward needs a forward pass in training mode')
+        L = lib()
+        T, B, I = x.shape
+        H = w_hh.shape[1]
+        dims = ctx.dims
+        KK = dims[5]
+        dy = torch.zeros_like(y) if dy is None else dy.contiguous()
+        require(dy, 'out_grad', dtype=x.dtype, device=x.device, shape=y.shape)
+        dhT = dhT.contiguous() if dhT is not None else None
+        dcT = dcT.contiguous() if dcT is not None else None
+        wb = _tc_pack_backward(w_hh, dims)
+        dgates = torch.empty(T, B, KK, dtype=x.dtype, device=x.device)          # per-CTA column order, row-major
+        dh0, dc0 = torch.empty_like(h0), torch.empty_like(c0)
+        bar = _barrier_words(x.device)
+        check(L.mxb_lstm_tc_backward(dt(x), ptr(dy), ptr(dhT), ptr(dcT), ptr(gates), ptr(cs), ptr(c0), ptr(wb), ptr(dgates),
+                                     ptr(dh0), ptr(dc0), ptr(bar), T, B, H, stream_ptr(x.device)), 'lstm_tc_backward')
+        count_launch(1)
+        ctx.bwd_bar = bar
+        dg2 = dgates.view(T * B, KK)
+        hprev = torch.cat([h0.unsqueeze(0), y[:-1]], 0).reshape(T * B, H)
+        dx = _mm(dg2, wi, False, True, True).reshape(T, B, I) if ctx.needs_input_grad[0] else None      # dg[TB,KK] . wi[KK,I]
+        dw_ih = _tc_unperm_rows(_mm(dg2, x.reshape(T * B, I), True, True, True), dims, H)                # (dg^T . x) regrouped
+        dw_hh = _tc_unperm_rows(_mm(dg2, hprev, True, True, True), dims, H)
+        db = _tc_unperm_rows(dg2.sum(0, dtype=torch.float32), dims, H)
         return dx, dw_ih, dw_hh, db.to(ctx.bias_dtypes[0]), db.to(ctx.bias_dtypes[1]), dh0, dc0, None
 
 
@@ -263,8 +410,9 @@ def lstm(data, parameters, state, state_cell, state_size, num_layers, p, trainin
         for di in range(d):
             w_ih, w_hh, _w_hr, b_ih, b_hh = layers[l * d + di]
             xin = x if di == 0 else x.flip(0)
-            y, h, c = _LSTMLayer.apply(xin.contiguous(), w_ih, w_hh, b_ih, b_hh, state[l * d + di], state_cell[l * d + di],
-                                       bool(training))
+            layer = _LSTMLayerTC if tc_supported(xin.dtype, N, state_size) else _LSTMLayer
+            y, h, c = layer.apply(xin.contiguous(), w_ih, w_hh, b_ih, b_hh, state[l * d + di], state_cell[l * d + di],
+                                  bool(training))
             outs.append(y if di == 0 else y.flip(0))
             hs.append(h)
             cs.append(c)

@@ -900,7 +900,7 @@ def rnn(data, parameters, state, state_cell=None, sequence_length=None, state_si
 
     if plain and _use_kernels(data) and data.dtype in (torch.float16, torch.bfloat16, torch.float32):
         from .cuda import rnn_ops
-        if rnn_ops.supported(data, state_size, num_layers):
+        if rnn_ops.supported(data, state_size, num_layers, mode):
             if mode == 'lstm':
                 def own(data, parameters, state, state_cell):
                     return rnn_ops.lstm(data, parameters, state, state_cell, state_size, num_layers, p, training, bidirectional)

@@ -666,9 +666,13 @@ def test_gradient_compression_kernels_match_tensor_ops(kind, threshold, n):
 @pytest.mark.parametrize('T,B,I,H,layers', [(5, 3, 8, 16, 1), (7, 4, 24, 40, 2), (35, 80, 650, 650, 2), (3, 1, 16, 200, 1),
                                              (4, 33, 64, 888, 1)])
 @pytest.mark.parametrize('dtype', [torch.float32, torch.float16])
-def test_fused_lstm_matches_library_lstm(T, B, I, H, layers, dtype):
+@pytest.mark.parametrize('tc', [True, False])
+def test_fused_lstm_matches_library_lstm(T, B, I, H, layers, dtype, tc, monkeypatch):
+    """tc=True: the tcgen05 recurrence (tf32 products for fp32 models); tc=False: the fp32-pipe recurrence kernels."""
     from mxnet_b200.ops.cuda import rnn_ops
     from mxnet_b200.ops.nn import rnn_param_size
+    monkeypatch.setenv('MXNET_B200_RNN_TC', '1' if tc else '0')
+    assert rnn_ops.tc_supported(dtype, B, H) == tc
     torch.manual_seed(9)
     ref = torch.nn.LSTM(I, H, layers).float()            # exact fp32 reference on the host
     # flat parameter vector in the RNN operator's order: all weights (layer by layer: w_ih, w_hh), then all biases
@@ -702,6 +706,8 @@ def test_fused_lstm_matches_library_lstm(T, B, I, H, layers, dtype):
     yr, (hTr, cTr) = ref(xr, (hr, cr))
     torch.autograd.backward([yr, hTr, cTr], [gy.float().cpu(), gh.float().cpu(), gc.float().cpu()])
     tol = (1e-3, 1e-3) if dtype == torch.float32 else (3e-2, 3e-2)     # fast exp/tanh intrinsics in the kernel
+    if tc and dtype == torch.float32:
+        tol = (6e-3, 6e-3)                  # tf32 operands: 10 mantissa bits in the recurrent product
     _close(y, yr, *tol)
     _close(hT, hTr, *tol)
     _close(cT, cTr, *tol)
