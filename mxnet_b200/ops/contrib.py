@@ -106,7 +106,8 @@ def dropout_add(data, residual, bias=None, p=0.5, mode='training'):
     p = float(p) if active else 0.0
     ew = _ew_kernels(data)
     if ew is not None and ew.pointwise_supported(data, data.shape[-1]) and residual.shape == data.shape and \
-            residual.dtype == data.dtype and residual.is_contiguous() and (bias is None or bias.dtype == data.dtype):
+            residual.dtype == data.dtype and residual.is_contiguous() and \
+            (bias is None or (bias.dtype == data.dtype and bias.dim() == 1 and bias.numel() == data.shape[-1])):
         return ew.dropout(data, p, bias, residual)
     x = data if bias is None else data + bias
     return residual + (F.dropout(x, p, True) if p > 0 else x)
@@ -117,8 +118,9 @@ def bias_gelu(data, bias=None):
     """gelu(data + bias), erf form, bias broadcast over the last axis (one pass; the reference composes broadcast_add
     and LeakyReLU(act_type='gelu'), src/operator/leaky_relu-inl.h)."""
     ew = _ew_kernels(data)
-    if ew is not None and ew.pointwise_supported(data, data.shape[-1]) and (bias is None or (bias.dtype == data.dtype and
-                                                                                         bias.is_contiguous())):
+    if ew is not None and ew.pointwise_supported(data, data.shape[-1]) and \
+            (bias is None or (bias.dtype == data.dtype and bias.is_contiguous() and bias.dim() == 1 and
+                              bias.numel() == data.shape[-1])):
         return ew.gelu(data, bias)
     return F.gelu(data if bias is None else data + bias)
 

@@ -263,11 +263,8 @@ register('_multi_mp_adamw_update', '_contrib_multi_mp_adamw_update', inputs=('*d
           defaults={'lr': 0.01, 'beta1': 0.9, 'beta2': 0.999, 'epsilon': 1e-8, 'wd': 0.0, 'eta': 1.0, 'clip_gradient': -1.0})
 def adabelief_update(weight, grad, mean, var, rescale_grad=1.0, lr=0.01, beta1=0.9, beta2=0.999, epsilon=1e-8, wd=0.0,
                      eta=1.0, clip_gradient=-1.0):
-    if _adam_kernel_ok(weight, grad, mean, var):
-        from .cuda import optim_ops
-        optim_ops.multi_adam([weight], [grad], [mean], [var], None, [lr], [wd], [eta], beta1, beta2, epsilon,
-                             clip_gradient, _rescale_arg(rescale_grad, weight.device), True)
-        return weight
+    # tensor operations on every device: the second moment follows (g - mean)^2, which the multi-tensor Adam kernel does
+    # not compute
     rs = _rescale_tensor(rescale_grad)
     if not math.isfinite(rs) or rs == 0:
         return weight

@@ -1481,7 +1481,10 @@ def np_pinv(A, rcond=1e-15, hermitian=False):
 
 @register('_npi_matrix_rank', '_npi_matrix_rank_none_tol', inputs=('M',), defaults={'tol': None, 'hermitian': False})
 def np_matrix_rank(M, tol=None, hermitian=False, finfoEps32=None, finfoEps64=None):
-    return torch.linalg.matrix_rank(M, tol=tol, hermitian=hermitian)
+    if tol is None:
+        return torch.linalg.matrix_rank(M, hermitian=bool(hermitian))
+    tol = tol if isinstance(tol, torch.Tensor) else float(tol)
+    return torch.linalg.matrix_rank(M, atol=tol, rtol=0.0, hermitian=bool(hermitian))     # numpy: singular values > tol
 
 
 @register('_npi_tensorinv', inputs=('a',), defaults={'ind': 2})
