@@ -122,6 +122,7 @@ declare('MXNET_UPDATE_ON_KVSTORE', bool, True, 'default of Trainer.update_on_kvs
 declare('MXNET_KVSTORE_FUSED', bool, True, 'use the fused reduce-scatter+update+all-gather kernels')
 declare('MXNET_KVSTORE_BUCKET_MB', int, 32, 'gradient bucket size of the fused path')
 declare('MXNET_KVSTORE_WAIT_MS', int, 20000, 'bound of device-side peer waits before an error status')
+declare('MXNET_KVSTORE_NVLS', bool, False, 'fused optimizer step / all-reduce of a multi-process job through the NVLink switch: the arenas are allocated as symmetric memory with a multicast mapping, gradients are summed by multimem.ld_reduce and weights broadcast by multimem.st (falls back to peer loads and stores where the machine has no multicast support). Leave off in jobs whose ranks may exit one by one: a multicast binding must be torn down by all ranks together')
 # ---- numerics -----------------------------------------------------------------------------
 declare('MXNET_SAFE_ACCUMULATION', bool, True, 'accumulate fp16 reductions in fp32')
 declare('MXNET_ENFORCE_DETERMINISM', bool, False, 'refuse non-deterministic kernels')

@@ -7,9 +7,13 @@ from .ndarray.ndarray import NDArray
 
 
 class Executor(object):
-    def __init__(self, sym, ctx, args, args_grad=None, grad_req='write', aux_states=None):
+    def __init__(self, sym, ctx, args, args_grad=None, grad_req='write', aux_states=None, group2ctx=None):
         self._symbol = sym
         self._ctx = ctx
+        self._group2ctx = dict(group2ctx) if group2ctx else None
+        # model parallelism: each operator runs on the context of its `ctx_group` (python/mxnet/symbol/symbol.py bind)
+        self._placement = sym._place(ctx, self._group2ctx) if self._group2ctx else None
+        self._stats = {'copies': 0}
         arg_names = sym.list_arguments()
         aux_names = sym.list_auxiliary_states()
         if isinstance(args, dict):
@@ -37,6 +41,11 @@ class Executor(object):
         self._leafs = None
 
     @property
+    def cross_device_copies(self):
+        """Values that crossed contexts in the last forward pass of a model-parallel executor."""
+        return self._stats['copies']
+
+    @property
     def output_dict(self):
         return dict(zip(self._symbol.list_outputs(), self.outputs))
 
@@ -61,10 +70,10 @@ class Executor(object):
         with autograd.record(train_mode=is_train) if is_train else autograd.pause(train_mode=False):
             if is_train:
                 with torch.enable_grad():
-                    outs = self._symbol._run(feed)
+                    outs = self._symbol._run(feed, placement=self._placement, stats=self._stats)
             else:
                 with torch.no_grad():
-                    outs = self._symbol._run(feed)
+                    outs = self._symbol._run(feed, placement=self._placement, stats=self._stats)
         self._out_tensors, self._leafs = outs, leafs
         cls = type(self.arg_arrays[0]) if self.arg_arrays else NDArray
         self.outputs = [cls._from_tensor(o.detach()) for o in outs]
@@ -118,7 +127,7 @@ class Executor(object):
             new_args[n] = old if tuple(old.shape) == tuple(s) else nd.zeros(s, ctx=self._ctx, dtype=old.dtype)
         new_grads = {n: nd.zeros(new_args[n].shape, ctx=self._ctx, dtype=new_args[n].dtype) for n in self.grad_dict} \
             if self.grad_dict else None
-        return Executor(self._symbol, self._ctx, new_args, new_grads, self._grad_req, self.aux_dict)
+        return Executor(self._symbol, self._ctx, new_args, new_grads, self._grad_req, self.aux_dict, group2ctx=self._group2ctx)
 
     def get_optimized_symbol(self):
         """The graph as it runs: with pointwise groups fused once the executor has run on a GPU, else the bound Symbol."""

@@ -29,7 +29,8 @@ def measure(path, num_keys, nbytes, dtype, iters, warmup, ctx, rank, world):
     from mxnet_b200.parallel import dist
     esize = 4 if dtype == 'float32' else 2
     n = max(1, nbytes // esize)
-    with env.scope('MXNET_KVSTORE_FUSED', '1' if path == 'fused' else '0'):
+    fused = path in ('fused', 'fused_nvls')
+    with env.scope('MXNET_KVSTORE_FUSED', '1' if fused else '0'), env.scope('MXNET_KVSTORE_NVLS', '1' if path == 'fused_nvls' else '0'):
         params = []
         for i in range(num_keys):
             p = gluon.Parameter('key%d' % i, shape=(n,), dtype=dtype)
@@ -38,7 +39,7 @@ def measure(path, num_keys, nbytes, dtype, iters, warmup, ctx, rank, world):
         trainer = gluon.Trainer(params, 'sgd', {'learning_rate': 0.0, 'multi_precision': dtype != 'float32'},
                                 kvstore='nccl' if path == 'nccl' else 'device', update_on_kvstore=False)
         trainer._init_kvstore()
-        if (trainer._fused is not None) != (path == 'fused'):
+        if (trainer._fused is not None) != fused:
             raise RuntimeError('path %s was not selected' % path)
 
         def fill():
@@ -75,9 +76,10 @@ def measure(path, num_keys, nbytes, dtype, iters, warmup, ctx, rank, world):
             trainer._fused._check_status()
         t = float(ms.item()) / 1e3
         total = num_keys * n * esize
+        multicast = bool(trainer._fused is not None and getattr(trainer._fused, 'mc_base', 0))
         del trainer, params
         torch.cuda.empty_cache()
-        return {'path': path, 'key_bytes': n * esize, 'num_keys': num_keys, 'total_bytes': total, 'ms': t * 1e3,
+        return {'path': path, 'multicast': multicast, 'key_bytes': n * esize, 'num_keys': num_keys, 'total_bytes': total, 'ms': t * 1e3,
                 'algbw_GBps': total / t / 1e9, 'busbw_GBps': total * 2 * (world - 1) / world / t / 1e9}
 
 
@@ -88,7 +90,7 @@ def main():
     ap.add_argument('--max-size', type=int, default=1 << 30, help='bytes per key')
     ap.add_argument('--max-total', type=int, default=8 << 30, help='cap on bytes exchanged per iteration (fewer keys above it)')
     ap.add_argument('--dtype', default='float16', choices=['float16', 'float32', 'bfloat16'])
-    ap.add_argument('--paths', default='fused,nccl')
+    ap.add_argument('--paths', default='fused,nccl', help='comma list of fused, fused_nvls (through the NVLink switch), nccl')
     ap.add_argument('--iters', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     args = ap.parse_args()

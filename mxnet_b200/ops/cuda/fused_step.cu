@@ -78,6 +78,12 @@ struct StepParams {
   float* norm_in[kMaxRanks];        // every rank's receive area [kMaxRanks][2][nseg] (own entry = local pointer)
   const int* seg_skip;              // per-parameter flag: 1 = leave this parameter and its state untouched (stale gradient); may be null
   const float* seg_coef;            // per-parameter bias corrections [2][nseg] when the update counts differ; null = coef1 / coef2
+  // NVLink-switch multicast (NVLS) addresses of the gradient and weight arenas: one address that stands for the same
+  // offset in every rank's arena.  A multimem.ld_reduce on it returns the sum over all ranks, formed inside the switch
+  // (one load instead of nranks peer loads); a multimem.st on it writes every rank's copy with one store.  Null = plain
+  // peer loads and stores.
+  const void* grads_mc;
+  void* weights_mc;
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -92,6 +98,47 @@ __device__ __forceinline__ unsigned long long now_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+
+// ---- multimem (NVLS) accesses: 16 bytes per instruction ---------------------------------------------------------------
+template <typename T> __device__ __forceinline__ Vec16<T> mc_ld_reduce(const T* p);
+template <> __device__ __forceinline__ Vec16<float> mc_ld_reduce<float>(const float* p) {
+  Vec16<float> r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]) : "l"(p) : "memory");
+  return r;
+}
+template <> __device__ __forceinline__ Vec16<__half> mc_ld_reduce<__half>(const __half* p) {
+  uint32_t a, b, c, d;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "l"(p) : "memory");
+  Vec16<__half> r;
+  *reinterpret_cast<uint4*>(&r) = make_uint4(a, b, c, d);
+  return r;
+}
+template <> __device__ __forceinline__ Vec16<__nv_bfloat16> mc_ld_reduce<__nv_bfloat16>(const __nv_bfloat16* p) {
+  uint32_t a, b, c, d;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "l"(p) : "memory");
+  Vec16<__nv_bfloat16> r;
+  *reinterpret_cast<uint4*>(&r) = make_uint4(a, b, c, d);
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ void mc_st16(T* p, const Vec16<T>& v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(&v);
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(p), "f"(__uint_as_float(u.x)), "f"(__uint_as_float(u.y)), "f"(__uint_as_float(u.z)), "f"(__uint_as_float(u.w))
+               : "memory");
+}
+// One value for every rank's arena at element offset e: through the switch when a multicast address is known.
+template <typename T>
+__device__ __forceinline__ void store_all(void* const* arenas, void* mc, int nranks, int64_t e, const Vec16<T>& v) {
+  if (mc) {
+    mc_st16((T*)mc + e, v);
+  } else {
+    for (int r = 0; r < nranks; ++r) st16((T*)arenas[r] + e, v);
+  }
 }
 
 // Threads 0..n-1 of the CTA each poll one flag until it reaches `step`; returns false on time-out.
@@ -131,19 +178,26 @@ __global__ void __launch_bounds__(256) fused_reduce_kernel(const __grid_constant
     constexpr int N = Vec16<T>::N;
     const int64_t v0 = p.shard_begin / N, v1 = p.shard_end / N;
     for (int64_t v = v0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < v1; v += (int64_t)gridDim.x * blockDim.x) {
-      Vec16<T> in[kMaxRanks];
-#pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < p.nranks) in[r] = ld16((const T*)p.grads[r] + v * N);
       float acc[N];
+      if (p.grads_mc) {
+        // the switch adds the ranks' values (fp32 accumulation) and returns the sum in the element type
+        const Vec16<T> sum = mc_ld_reduce<T>((const T*)p.grads_mc + v * N);
 #pragma unroll
-      for (int j = 0; j < N; ++j) acc[j] = 0.f;
+        for (int j = 0; j < N; ++j) acc[j] = Cvt<T>::to_f(sum.v[j]);
+      } else {
+        Vec16<T> in[kMaxRanks];
 #pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < p.nranks) {
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < p.nranks) in[r] = ld16((const T*)p.grads[r] + v * N);
 #pragma unroll
-          for (int j = 0; j < N; ++j) acc[j] += Cvt<T>::to_f(in[r].v[j]);
-        }
+        for (int j = 0; j < N; ++j) acc[j] = 0.f;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < p.nranks) {
+#pragma unroll
+            for (int j = 0; j < N; ++j) acc[j] += Cvt<T>::to_f(in[r].v[j]);
+          }
+      }
       float* out = p.gred + (v * N - p.shard_begin);
 #pragma unroll
       for (int j = 0; j < N; ++j) {
@@ -276,7 +330,7 @@ __global__ void __launch_bounds__(256) fused_update_kernel(const __grid_constant
       if (p.mode == kModePlain) {
 #pragma unroll
         for (int j = 0; j < N; ++j) out.v[j] = Cvt<T>::from_f(g[j]);
-        for (int r = 0; r < p.nranks; ++r) st16((T*)p.grads[r] + e, out);     // all-gather of the reduced gradient
+        store_all<T>((void* const*)p.grads, const_cast<void*>(p.grads_mc), p.nranks, e, out);     // all-gather of the reduced gradient
         continue;
       }
       const int seg = find_segment(p.seg_end, p.nseg, e);
@@ -346,7 +400,7 @@ __global__ void __launch_bounds__(256) fused_update_kernel(const __grid_constant
 #pragma unroll
         for (int j = 0; j < N; j += 4) *reinterpret_cast<float4*>(p.mom + le + j) = make_float4(m[j], m[j + 1], m[j + 2], m[j + 3]);
       }
-      for (int r = 0; r < p.nranks; ++r) st16((T*)p.weights[r] + e, out);       // all-gather of the new weights
+      store_all<T>(p.weights, p.weights_mc, p.nranks, e, out);       // all-gather of the new weights
     }
   }
   finish_step<T>(p, me, skip, sumsq);
@@ -526,7 +580,7 @@ __global__ void __launch_bounds__(256) fused_lamb2_kernel(const __grid_constant_
 #pragma unroll
       for (int j = 0; j < N; ++j) { w[j] -= lr * u[j]; out.v[j] = Cvt<T>::from_f(w[j]); }
       if (p.master) store_f(p.master + le, w, N);
-      for (int r = 0; r < p.nranks; ++r) st16((T*)p.weights[r] + e, out);
+      store_all<T>(p.weights, p.weights_mc, p.nranks, e, out);
     }
   }
   finish_step<T>(p, me, skip, sumsq);

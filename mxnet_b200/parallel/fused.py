@@ -58,7 +58,7 @@ class StepParams(C.Structure):
                 ('timeout_ns', C.c_ulonglong), ('var', C.c_void_p), ('beta1', C.c_float), ('beta2', C.c_float),
                 ('epsilon', C.c_float), ('coef1', C.c_float), ('coef2', C.c_float), ('lower_bound', C.c_float),
                 ('upper_bound', C.c_float), ('norm_acc', C.c_void_p), ('norm_in', C.c_void_p * _MAXR),
-                ('seg_skip', C.c_void_p), ('seg_coef', C.c_void_p)]
+                ('seg_skip', C.c_void_p), ('seg_coef', C.c_void_p), ('grads_mc', C.c_void_p), ('weights_mc', C.c_void_p)]
 
 
 class _DevBuf(object):
@@ -161,11 +161,16 @@ class FusedStep(object):
                 self._state_off[name] = cur_off
                 cur_off += shard_bytes
         self.slab_bytes = cur_off
-        ptr = C.c_void_p()
-        rc = L.mxb_dev_alloc(C.byref(ptr), self.slab_bytes)
-        if rc != 0:
-            raise MXNetError('cudaMalloc of the parameter arena failed: %s' % L.mxb_error_string(rc).decode())
-        self.slab = ptr.value
+        self.mc_base = 0                  # NVLS multicast address of the slab (0: plain peer loads and stores)
+        self._symm = self._alloc_symmetric() if (local_group is None and self.nranks > 1 and env.get('MXNET_KVSTORE_NVLS')) else None
+        if self._symm is not None:
+            self.slab = self._symm[0].data_ptr()
+        else:
+            ptr = C.c_void_p()
+            rc = L.mxb_dev_alloc(C.byref(ptr), self.slab_bytes)
+            if rc != 0:
+                raise MXNetError('cudaMalloc of the parameter arena failed: %s' % L.mxb_error_string(rc).decode())
+            self.slab = ptr.value
         self._w_off, self._g_off = self.ctrl_bytes, self.ctrl_bytes + arena_bytes
         # Each tensor below wraps its own piece of the slab as an independent storage: tensors that were
         # views of one base would share a version counter, and the in-place gradient accumulation of one
@@ -187,10 +192,38 @@ class FusedStep(object):
             self._connect_processes()
             self._init_state()
 
+    def _alloc_symmetric(self):
+        """The slab as symmetric memory of the job (CUDA virtual-memory allocations that every rank maps, bound to an
+        NVLink-switch multicast object where the machine has one): the kernels can then reduce and broadcast through the
+        switch (``multimem`` instructions).  The tensor library does the allocation and the handle exchange; all ranks
+        fall back to ``cudaMalloc`` + CUDA IPC together when any of them cannot allocate."""
+        t = None
+        try:
+            import torch.distributed._symmetric_memory as symm
+            t = symm.empty(self.slab_bytes, dtype=torch.uint8, device=self.device)
+            t.zero_()
+        except Exception:   # pylint: disable=broad-except
+            t = None
+        oks = dist.all_gather_object(t is not None)
+        return (t,) if all(oks) else None
+
     def _connect_processes(self):
-        """Open the slabs of the other processes through CUDA IPC and start from rank 0's weights."""
+        """Open the slabs of the other processes (symmetric-memory rendezvous, or CUDA IPC) and start from rank 0's
+        weights."""
         L = _lib()
-        if self.nranks > 1:
+        if self.nranks > 1 and self._symm is not None:
+            import torch.distributed._symmetric_memory as symm
+            layout = (self.total, [int(s) for s in self.sizes])
+            for r, lay in enumerate(dist.all_gather_object(layout)):
+                if lay != layout:
+                    raise MXNetError('rank %d has a different parameter layout than rank %d' % (r, self.rank))
+            hdl = symm.rendezvous(self._symm[0], torch.distributed.group.WORLD)
+            self._symm = (self._symm[0], hdl)
+            self.peer_base = [int(p) for p in hdl.buffer_ptrs]
+            self.peer_base[self.rank] = self.slab
+            self.mc_base = int(hdl.multicast_ptr or 0)
+            dist.broadcast_(self.weights, 0)
+        elif self.nranks > 1:
             hb = L.mxb_ipc_handle_bytes()
             handle = C.create_string_buffer(hb)
             rc = L.mxb_ipc_get_handle(C.c_void_p(self.slab), handle)
@@ -272,6 +305,8 @@ class FusedStep(object):
             sp.grads[r] = self.peer_base[r] + self._g_off
             sp.weights[r] = self.peer_base[r] + self._w_off
             sp.ctrl[r] = self.peer_base[r]
+        if self.mc_base:
+            sp.grads_mc, sp.weights_mc = self.mc_base + self._g_off, self.mc_base + self._w_off
         sp.rank, sp.nranks, sp.total = self.rank, self.nranks, self.total
         sp.shard_begin, sp.shard_end = self.shard_begin, self.shard_end
         sp.gred = self.gred.data_ptr()

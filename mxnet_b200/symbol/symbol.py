@@ -359,10 +359,43 @@ class Symbol(object):
             f.write(self.tojson(remove_amp_cast))
 
     # ------------------------------------------------------------------ execution / inference
-    def _run(self, feed, training=None):
+    def _place(self, default_ctx, group2ctx):
+        """Device of every node for model-parallel execution (the reference's PlaceDevice pass,
+        src/executor/graph_executor.cc AssignContext): a node whose ``ctx_group`` attribute names a key of ``group2ctx``
+        runs on that context; a node without one takes the device of its first placed input, else of its first placed
+        consumer, else the default.  Returns {id(node): Context}; values cross contexts with a copy at the consumer."""
+        devices = {}
+        for g, c in (group2ctx or {}).items():
+            devices[g] = c[0] if isinstance(c, (list, tuple)) else c
+        order = _topo(self._outputs)
+        placed = {}
+        for n in order:
+            g = n.user_attrs.get('ctx_group', n.user_attrs.get('__ctx_group__'))
+            if g is not None and g in devices:
+                placed[id(n)] = devices[g]
+        for n in order:                                   # forward: follow the first placed input
+            if id(n) not in placed:
+                for i, _ in n.inputs:
+                    if id(i) in placed:
+                        placed[id(n)] = placed[id(i)]
+                        break
+        for n in reversed(order):                         # backward: follow a placed consumer
+            if id(n) in placed:
+                for i, _ in n.inputs:
+                    placed.setdefault(id(i), placed[id(n)])
+        for n in order:
+            placed.setdefault(id(n), default_ctx)
+        return placed
+
+    def _run(self, feed, training=None, placement=None, stats=None):
         """Evaluate the graph.  ``feed``: {variable name: tensor}.  Returns list of tensors.  On a GPU the graph runs
-        with its elementwise groups fused into generated kernels (``MXNET_USE_FUSION``)."""
+        with its elementwise groups fused into generated kernels (``MXNET_USE_FUSION``).  With ``placement`` (from
+        :meth:`_place`) every operator runs on its assigned device: inputs that live elsewhere are copied there first (the
+        ``_CrossDeviceCopy`` nodes of the reference; the copies are differentiable, so gradients flow back across devices),
+        and ``stats['copies']`` counts them."""
         graph = self
+        if placement is not None:
+            return self._run_placed(feed, placement, stats)
         if self._fused is not False and _env.get('MXNET_USE_FUSION') and any(
                 isinstance(t, torch.Tensor) and t.is_cuda for t in feed.values()):
             if self._fused is None:
@@ -386,6 +419,41 @@ class Symbol(object):
             res = node.op.fn(*ins, **node.attrs)
             values[id(node)] = tuple(res) if isinstance(res, (tuple, list)) else (res,)
         return [values[id(n)][k] for n, k in graph._outputs]
+
+    def _run_placed(self, feed, placement, stats=None):
+        values = {}
+        where = {}
+        copies = 0
+        for node in _topo(self._outputs):
+            if node.op is None:
+                if node.name not in feed:
+                    raise MXNetError('missing input %s' % node.name)
+                values[id(node)] = (feed[node.name],)
+                where[id(node)] = placement[id(node)]
+                continue
+            ctx = placement[id(node)]
+            dev = ctx.torch_device
+            where[id(node)] = ctx
+            ins = []
+            for i, k in node.inputs:
+                t = values[id(i)][k]
+                if isinstance(t, torch.Tensor) and where[id(i)] != ctx:
+                    copies += 1                            # a _CrossDeviceCopy of the reference
+                    if t.device != dev:
+                        t = t.to(dev)
+                ins.append(t)
+            hook = _state.amp_hook
+            if hook is not None and not _state.state.opt_constraints & 1:
+                ins = hook(node.op.name, ins)
+            if dev.type == 'cuda':
+                with torch.cuda.device(dev):
+                    res = node.op.fn(*ins, **node.attrs)
+            else:
+                res = node.op.fn(*ins, **node.attrs)
+            values[id(node)] = tuple(res) if isinstance(res, (tuple, list)) else (res,)
+        if stats is not None:
+            stats['copies'] = copies
+        return [values[id(n)][k] for n, k in self._outputs]
 
     def _infer(self, shapes, dtypes, partial=False):
         feed, unknown = {}, []
@@ -453,7 +521,7 @@ class Symbol(object):
 
     def _bind(self, ctx, args, args_grad=None, grad_req='write', aux_states=None, group2ctx=None, shared_exec=None):
         from ..executor import Executor
-        return Executor(self, ctx, args, args_grad, grad_req, aux_states)
+        return Executor(self, ctx, args, args_grad, grad_req, aux_states, group2ctx=group2ctx)
 
     bind = _bind
 
@@ -464,11 +532,19 @@ class Symbol(object):
         if arg_shapes is None or any(s is None for s in arg_shapes):
             raise MXNetError('cannot infer shapes for simple_bind')
         type_dict = type_dict or {}
-        args = {n: nd.zeros(s, ctx=ctx, dtype=type_dict.get(n, 'float32')) for n, s in zip(self.list_arguments(), arg_shapes)}
-        grads = {n: nd.zeros(s, ctx=ctx, dtype=type_dict.get(n, 'float32')) for n, s in zip(self.list_arguments(), arg_shapes)} \
-            if grad_req != 'null' else None
-        aux = {n: nd.zeros(s, ctx=ctx) for n, s in zip(self.list_auxiliary_states(), aux_shapes)}
-        return self._bind(ctx, args, grads, grad_req, aux)
+        # arguments and their gradients live on the context of their group (model parallelism), else on `ctx`
+        where = {}
+        if group2ctx:
+            placed = self._place(ctx, group2ctx)
+            for n in _topo(self._outputs):
+                if n.op is None:
+                    where[n.name] = placed[id(n)]
+        args = {n: nd.zeros(s, ctx=where.get(n, ctx), dtype=type_dict.get(n, 'float32'))
+                for n, s in zip(self.list_arguments(), arg_shapes)}
+        grads = {n: nd.zeros(s, ctx=where.get(n, ctx), dtype=type_dict.get(n, 'float32'))
+                 for n, s in zip(self.list_arguments(), arg_shapes)} if grad_req != 'null' else None
+        aux = {n: nd.zeros(s, ctx=where.get(n, ctx)) for n, s in zip(self.list_auxiliary_states(), aux_shapes)}
+        return self._bind(ctx, args, grads, grad_req, aux, group2ctx=group2ctx)
 
     _simple_bind = simple_bind
 

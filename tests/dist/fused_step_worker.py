@@ -18,6 +18,9 @@ from mxnet_b200.gluon import nn                           # noqa: E402
 from mxnet_b200.parallel import dist                      # noqa: E402
 
 
+_MULTICAST = []          # one entry per fused step that ran through an NVLink-switch multicast mapping
+
+
 def build(ctx, dtype):
     mx.random.seed(7)
     np.random.seed(7)
@@ -50,6 +53,8 @@ def run(fused, dtype, steps, ctx, rank, world, optimizer='sgd'):
             trainer.step(per * world)
         torch.cuda.synchronize()
         assert (trainer._fused is not None) == fused, 'fused path selection'
+        if fused and getattr(trainer._fused, 'mc_base', 0):
+            _MULTICAST.append(True)
         if fused:
             trainer._fused._check_status()
             if rank == 0 and optimizer == 'adam':
@@ -71,7 +76,7 @@ def main():
     rank, world = dist.rank(), dist.world_size()
     torch.cuda.set_device(dist.local_rank())
     ctx = mx.gpu(dist.local_rank())
-    report = {'world': world}
+    report = {'world': world, 'nvls_requested': bool(env.get('MXNET_KVSTORE_NVLS'))}
     for dtype in ('float32', 'float16'):
         w_fused = run(True, dtype, 6, ctx, rank, world)
         w_plain = run(False, dtype, 6, ctx, rank, world)
@@ -90,6 +95,7 @@ def main():
         torch.distributed.all_gather(gathered, flat)
         report[optimizer] = {'max_abs_diff_vs_nccl_path': err,
                              'ranks_identical': all(bool(torch.equal(gathered[0], g)) for g in gathered)}
+    report['multicast_steps'] = len(_MULTICAST)
     if rank == 0:
         print('REPORT ' + json.dumps(report))
     dist.barrier()

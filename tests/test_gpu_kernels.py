@@ -974,3 +974,28 @@ def test_quantized_fully_connected_runs_on_the_int8_kernel():
     np.testing.assert_array_equal(out.asnumpy(), ref.astype('int32'))
     np.testing.assert_allclose(hi.asnumpy(), [sd * sw * 2147483647.0], rtol=1e-5)
     np.testing.assert_allclose(lo.asnumpy(), [-sd * sw * 2147483647.0], rtol=1e-5)
+
+
+def test_quantized_network_runs_its_dense_layers_on_the_int8_kernel():
+    """``contrib.quantization.quantize_net`` on a small MLP (reference: python/mxnet/contrib/quantization.py,
+    quantize_graph_pass.cc): every FullyConnected becomes quantize -> int8 FullyConnected -> dequantize, the int8 products
+    run on the tensor-core kernel (launch counter), and the outputs stay close to the float network's."""
+    from mxnet_b200.contrib import quantization
+    from mxnet_b200.gluon import nn
+    from mxnet_b200.ops import cuda as kc
+    from mxnet_b200.ops.cuda import gemm_ops
+    ctx = mx.gpu(0)
+    mx.random.seed(5)
+    net = nn.HybridSequential()
+    net.add(nn.Dense(512, activation='relu', in_units=256), nn.Dense(128, activation='relu', in_units=512), nn.Dense(64, in_units=128))
+    net.initialize(mx.init.Xavier(), ctx=ctx)
+    net.hybridize()
+    x = nd.array(np.random.RandomState(1).randn(96, 256).astype('float32'), ctx=ctx)
+    ref = net(x).asnumpy()
+    qnet = quantization.quantize_net(net, data_shapes=[(96, 256)], ctx=ctx)
+    before = kc.launches()
+    out = qnet(x).asnumpy()
+    assert kc.launches() - before >= 3                      # three int8 GEMM launches (plus whatever else is in-tree)
+    assert int(gemm_ops._error_flag(torch.device('cuda', 0)).item()) == 0
+    err = np.abs(out - ref).max() / np.abs(ref).max()
+    assert err < 0.05, err

@@ -221,3 +221,41 @@ def test_symbolic_control_flow_foreach_while_cond(tmp_path):
     for pv, expect in ((1.0, [2.0, 4.0]), (0.0, [4.0, 5.0])):
         got = c._bind(mx.cpu(), {'p': nd.array([pv]), 'a': nd.array([1.0, 2.0]), 'b': nd.array([5.0, 6.0])}).forward()[0]
         onp.testing.assert_allclose(got.asnumpy(), expect)
+
+
+def test_group2ctx_places_operators_and_arguments():
+    """Model parallelism through ``ctx_group`` attributes and ``group2ctx`` (python/mxnet/symbol/symbol.py bind;
+    tests/python/unittest/test_model_parallel.py in the reference): operators and their arguments live on the context of
+    their group, ungrouped nodes follow their inputs, one value crosses between the stages, and the results and gradients
+    equal those of the unplaced graph."""
+    import numpy as np
+    import mxnet_b200 as mx
+    from mxnet_b200 import nd
+    with mx.AttrScope(ctx_group='stage1'):
+        x = mx.sym.var('data')
+        w1 = mx.sym.var('w1')
+        h = mx.sym.FullyConnected(x, w1, num_hidden=8, no_bias=True, name='fc1')
+    h = mx.sym.relu(h, name='act')                                   # no group: follows its input
+    with mx.AttrScope(ctx_group='stage2'):
+        w2 = mx.sym.var('w2')
+        out = mx.sym.FullyConnected(h, w2, num_hidden=3, no_bias=True, name='fc2')
+    shapes = dict(data=(4, 5), w1=(8, 5), w2=(3, 8))
+    placed = out.simple_bind(mx.cpu(0), group2ctx={'stage1': mx.cpu(1), 'stage2': mx.cpu(2)}, **shapes)
+    plain = out.simple_bind(mx.cpu(0), **shapes)
+    where = {n.name: placed._placement[id(n)] for n in mx.symbol.symbol._topo(out._outputs)}
+    assert where == {'data': mx.cpu(1), 'w1': mx.cpu(1), 'fc1': mx.cpu(1), 'act': mx.cpu(1), 'w2': mx.cpu(2), 'fc2': mx.cpu(2)}
+    assert placed.arg_dict['w1'].context == mx.cpu(1) and placed.arg_dict['w2'].context == mx.cpu(2)
+    assert placed.grad_dict['w2'].context == mx.cpu(2)
+    rng = np.random.RandomState(0)
+    for k, s in shapes.items():
+        v = rng.randn(*s).astype('float32')
+        placed.arg_dict[k][:] = v
+        plain.arg_dict[k][:] = v
+    a = placed.forward(is_train=True)[0]
+    b = plain.forward(is_train=True)[0]
+    assert placed.cross_device_copies == 1
+    np.testing.assert_allclose(a.asnumpy(), b.asnumpy(), rtol=1e-6)
+    placed.backward(nd.ones(a.shape))
+    plain.backward(nd.ones(b.shape))
+    for k in shapes:
+        np.testing.assert_allclose(placed.grad_dict[k].asnumpy(), plain.grad_dict[k].asnumpy(), rtol=1e-5, atol=1e-6)
