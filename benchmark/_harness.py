@@ -76,6 +76,8 @@ def measure(name, unit, items_per_step_per_gpu, make_step, args, config, baselin
         cfg['rnn_in_tree_kernel_chosen'] = {'%s T=%d N=%d I=%d H=%d L=%d %s' % (k[0], k[2], k[3], k[4], k[5], k[6],
                                                                                'train' if k[8] else 'eval'): bool(v)
                                             for k, v in rnn_ops.tuned_choices().items()}
+        cfg['rnn_autotune_us'] = {'%s T=%d N=%d H=%d L=%d' % (k[0], k[2], k[3], k[5], k[6]): {'in_tree': v[0], 'library': v[1]}
+                                  for k, v in rnn_ops.tuned_times().items()}
     return {'metric': name, 'value': value, 'unit': unit, 'n_gpus': world, 'steps': args.steps,
             'warmup': max(args.warmup, 3), 'ms_per_step': ms / args.steps, 'higher_is_better': True,
             'scaling': 'weak', 'vs_baseline': (value / baseline) if baseline else None, 'data': 'synthetic',

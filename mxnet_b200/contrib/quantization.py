@@ -130,7 +130,11 @@ def quantize_net(network, quantized_dtype='auto', quantize_mode='full', quantize
         assert data_shapes is not None or calib_data is not None, 'data_shapes or calib_data is needed to trace the network'
         if data_shapes is not None:
             shapes = [d.shape if hasattr(d, 'shape') and not isinstance(d, tuple) else tuple(d) for d in data_shapes]
-            args = [nd.zeros(s) for s in shapes]
+            where = device or ctx
+            if where is None:                     # trace where the parameters live
+                first_param = next(iter(network.collect_params().values()), None)
+                where = first_param.list_ctx()[0] if first_param is not None and first_param._data else None
+            args = [nd.zeros(s, ctx=where) for s in shapes]
         else:
             first = next(iter(calib_data))
             args = [first[0] if isinstance(first, (list, tuple)) else first]

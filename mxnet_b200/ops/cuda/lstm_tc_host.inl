@@ -4,8 +4,8 @@ namespace mxb {
 struct TcPlan {
   int ok;
   int U, KC, esz, Bp, Hp, C, Hc, KK;
-  int stages_f, stages_b;
-  size_t smem_f, smem_b;
+  int stages_f, stages_b, stages_c;
+  size_t smem_f, smem_b, smem_c;       // forward, backward, backward with the contraction cut over a cluster (0: does not fit)
 };
 
 constexpr size_t kTcSmemMax = 232448;                       // 227 KB per CTA
@@ -24,7 +24,7 @@ static TcPlan tc_plan(int dtype, int B, int H) {
   pl.KC = 128 / pl.esz;
   pl.Bp = (B + 7) / 8 * 8;
   pl.Hp = (H + pl.KC - 1) / pl.KC * pl.KC;
-  pl.C = (H + pl.U - 1) / pl.U;
+  pl.C = ((H + pl.U - 1) / pl.U + kTcCluster - 1) / kTcCluster * kTcCluster;      // whole clusters (idle CTAs own no unit)
   pl.Hc = pl.C * pl.U;
   pl.KK = 4 * pl.Hc;                                        // a multiple of KC for both element sizes
   if (pl.C > sm_count()) return pl;
@@ -37,6 +37,14 @@ static TcPlan tc_plan(int dtype, int B, int H) {
   pl.stages_b = (int)(sb > (size_t)kTcMaxStages ? (size_t)kTcMaxStages : sb);
   pl.smem_f = wf + kTcFixed + (size_t)pl.stages_f * stage;
   pl.smem_b = wb + kTcFixed + (size_t)pl.stages_b * stage;
+  // cluster variant of the backward pass: a quarter of the contraction axis per CTA, 4U units per cluster
+  const size_t wc = (size_t)(pl.KK / kTcCluster / pl.KC) * kTcCluster * pl.U * 128;
+  const size_t xc = (size_t)kTcCluster * 128 * pl.U * 4 + 64;
+  if (wc + xc + kTcFixed + 3 * stage <= kTcSmemMax) {
+    size_t sc = (kTcSmemMax - kTcFixed - wc - xc) / stage;
+    pl.stages_c = (int)(sc > (size_t)kTcMaxStages ? (size_t)kTcMaxStages : sc);
+    pl.smem_c = wc + xc + kTcFixed + (size_t)pl.stages_c * stage;
+  }
   pl.ok = 1;
   return pl;
 }
@@ -76,6 +84,44 @@ static int tc_launch(K kernel, unsigned long long* seen, int grid, size_t smem, 
   cfg.numAttrs = 1;
   return (int)cudaLaunchKernelEx(&cfg, kernel, m0, m1, p);
 }
+
+// Backward with clusters of four: cooperative (grid barriers) and clustered launch.  Returns -100 when the device cannot
+// hold all clusters at once (the caller then uses the plain kernel).
+template <typename K>
+static int tc_launch_cluster(K kernel, unsigned long long* seen, int grid, size_t smem, cudaStream_t st, const CUtensorMap& m0,
+                             const CUtensorMap& m1, const LstmTcParams& p) {
+  if (first_on_device(seen)) {
+    cudaError_t rc = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemMax - 64);
+    if (rc != cudaSuccess) return (int)rc;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kTcCluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeCooperative;
+  attr[1].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); return -100; }
+  if (clusters * kTcCluster < grid) return -100;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, m0, m1, p);
+}
+
+template <typename T, typename X, int U>
+static int tc_backward_cluster(const TcPlan& pl, const CUtensorMap& md, const CUtensorMap& mw, LstmTcParams p, cudaStream_t st) {
+  static unsigned long long seen = 0;
+  p.stages = pl.stages_c;
+  return tc_launch_cluster(lstm_tc_bwdc_kernel<T, X, U>, &seen, pl.C, pl.smem_c, st, md, mw, p);
+}
+
+static int g_tc_bwd_variant = 0;      // 0: cluster kernel where it fits, 1: plain kernel only
 
 template <typename T, typename X, int U>
 static int tc_forward(const TcPlan& pl, const CUtensorMap& mh, const CUtensorMap& mw, const LstmTcParams& p, cudaStream_t st) {
@@ -139,15 +185,26 @@ MXB_EXPORT int mxb_lstm_tc_backward(int dtype, const void* dy, const void* dhT, 
   CUtensorMap md, mw;
   int rc = tc_make_map(&md, dgates, dtype, (int64_t)T * B, pl.KK, pl.Bp);
   if (rc) return rc;
-  rc = tc_make_map(&mw, wb, dtype, (int64_t)pl.C * pl.U, pl.KK, pl.U);
-  if (rc) return rc;
   LstmTcParams p = {};
   p.dy = dy; p.dhT = dhT; p.dcT = dcT; p.gates = const_cast<void*>(gates); p.cs = (float*)const_cast<void*>(cs); p.c0 = c0;
   p.dgates = dgates; p.dh0 = dh0; p.dc0 = dc0; p.bar = (unsigned int*)bar;
   p.T = T; p.B = B; p.H = H; p.Bp = pl.Bp; p.Hp = pl.Hp; p.Hc = pl.Hc; p.KK = pl.KK; p.stages = pl.stages_b;
   p.yalign = tc_row_align(H, pl.esz);
   cudaStream_t st = (cudaStream_t)stream;
+  if (pl.smem_c && g_tc_bwd_variant == 0) {
+    rc = tc_make_map(&mw, wb, dtype, (int64_t)pl.C * pl.U, pl.KK, kTcCluster * pl.U);
+    if (rc) return rc;
+    rc = dtype == kF32 ? tc_backward_cluster<float, float, 8>(pl, md, mw, p, st)
+         : dtype == kF16 ? tc_backward_cluster<__half, __half, 16>(pl, md, mw, p, st)
+                         : tc_backward_cluster<__nv_bfloat16, __nv_bfloat16, 16>(pl, md, mw, p, st);
+    if (rc != -100) return rc;
+  }
+  rc = tc_make_map(&mw, wb, dtype, (int64_t)pl.C * pl.U, pl.KK, pl.U);
+  if (rc) return rc;
   if (dtype == kF32) return tc_backward<float, float, 8>(pl, md, mw, p, st);
   if (dtype == kF16) return tc_backward<__half, __half, 16>(pl, md, mw, p, st);
   return tc_backward<__nv_bfloat16, __nv_bfloat16, 16>(pl, md, mw, p, st);
 }
+
+// 0 (default): the backward pass cuts its contraction over clusters of four CTAs where they fit; 1: plain kernel only.
+MXB_EXPORT void mxb_lstm_tc_set_backward_variant(int v) { g_tc_bwd_variant = v; }

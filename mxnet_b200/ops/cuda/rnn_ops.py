@@ -18,6 +18,7 @@ def supported(data, state_size, num_layers, mode='lstm'):
 
 
 _tuned = {}
+_tuned_us = {}        # configuration -> (in-tree, library) microseconds measured by the autotuner on this rank
 
 
 def use_own(key, own_fn, lib_fn, inputs, training):
@@ -51,7 +52,9 @@ def use_own(key, own_fn, lib_fn, inputs, training):
             return step
         rng = torch.cuda.get_rng_state()
         try:
-            hit = _tuned[key] = job_wide(_time_us(run(own_fn), reps=3) <= 1.02 * _time_us(run(lib_fn), reps=3))
+            t_own, t_lib = _time_us(run(own_fn), reps=3), _time_us(run(lib_fn), reps=3)
+            _tuned_us[key] = (round(t_own, 1), round(t_lib, 1))
+            hit = _tuned[key] = job_wide(t_own <= 1.02 * t_lib)
         finally:
             torch.cuda.set_rng_state(rng)
     return hit
@@ -60,6 +63,11 @@ def use_own(key, own_fn, lib_fn, inputs, training):
 def tuned_choices():
     """{(mode, dtype, T, N, input size, state size, layers, bidirectional, training): in-tree kernels chosen}."""
     return dict(_tuned)
+
+
+def tuned_times():
+    """{configuration: (in-tree, library) microseconds of forward (+ backward) as timed by the autotuner}."""
+    return dict(_tuned_us)
 
 
 class _tf32_products(object):

@@ -666,13 +666,16 @@ def test_gradient_compression_kernels_match_tensor_ops(kind, threshold, n):
 @pytest.mark.parametrize('T,B,I,H,layers', [(5, 3, 8, 16, 1), (7, 4, 24, 40, 2), (35, 80, 650, 650, 2), (3, 1, 16, 200, 1),
                                              (4, 33, 64, 888, 1)])
 @pytest.mark.parametrize('dtype', [torch.float32, torch.float16])
-@pytest.mark.parametrize('tc', [True, False])
-def test_fused_lstm_matches_library_lstm(T, B, I, H, layers, dtype, tc, monkeypatch):
-    """tc=True: the tcgen05 recurrence (tf32 products for fp32 models); tc=False: the fp32-pipe recurrence kernels."""
-    from mxnet_b200.ops.cuda import rnn_ops
+@pytest.mark.parametrize('tc', ['cluster', 'plain', False])
+def test_fused_lstm_matches_library_lstm(T, B, I, H, layers, dtype, tc, monkeypatch, request):
+    """tc='cluster' / 'plain': the tcgen05 recurrence (tf32 products for fp32 models), its backward pass with the contraction
+    cut over clusters of four CTAs or with the plain kernel; tc=False: the fp32-pipe recurrence kernels."""
+    from mxnet_b200.ops.cuda import rnn_ops, lib
     from mxnet_b200.ops.nn import rnn_param_size
     monkeypatch.setenv('MXNET_B200_RNN_TC', '1' if tc else '0')
-    assert rnn_ops.tc_supported(dtype, B, H) == tc
+    lib().mxb_lstm_tc_set_backward_variant(1 if tc == 'plain' else 0)
+    request.addfinalizer(lambda: lib().mxb_lstm_tc_set_backward_variant(0))
+    assert rnn_ops.tc_supported(dtype, B, H) == bool(tc)
     torch.manual_seed(9)
     ref = torch.nn.LSTM(I, H, layers).float()            # exact fp32 reference on the host
     # flat parameter vector in the RNN operator's order: all weights (layer by layer: w_ih, w_hh), then all biases
