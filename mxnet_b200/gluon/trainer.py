@@ -62,6 +62,7 @@ class Trainer(object):
         if self._optimizer.aggregate_num > 1 and update_on_kvstore is not None:
             if update_on_kvstore:
                 raise ValueError('Cannot set update_on_kvstore=True when optimizer.aggregate_num > 1.')
+        self._update_on_kvstore_asked = update_on_kvstore       # what the caller passed (None: decide here)
         if update_on_kvstore is None and self._optimizer.aggregate_num > 1:
             update_on_kvstore = False
         self._kvstore_params = {'kvstore': kvstore, 'update_on_kvstore': update_on_kvstore}
@@ -140,6 +141,11 @@ class Trainer(object):
                 if update_on_kvstore:
                     raise ValueError('Please set update_on_kvstore=False when training with %s' % type(kv).__name__)
                 update_on_kvstore = False
+            elif 'async' in kv.type:
+                # asynchronous training has no merged gradient to update from: the optimizer runs on the server
+                if self._update_on_kvstore_asked is False:
+                    raise ValueError('Please set update_on_kvstore=True when training in async mode.')
+                update_on_kvstore = True
             elif update_on_kvstore is None:
                 update_on_kvstore = bool(env.get('MXNET_UPDATE_ON_KVSTORE')) and \
                     ('dist' in kv.type or self._contains_sparse_weight) and self._optimizer.aggregate_num <= 1

@@ -54,8 +54,25 @@ class KVStore(KVStoreBase):
         self._barrier_before_exit = True
         from ..parallel import dist
         self._dist = dist
+        self._server = self._client = None
         if name.startswith('dist') or name == 'p3':
             dist.ensure_initialized()
+        if name == 'dist_async':
+            self._connect_server()
+
+    def _connect_server(self):
+        """``dist_async``: a parameter server (``kvstore/server.py``, a thread in the process of rank 0) that applies
+        every push on arrival, as the reference's servers do in async mode (kvstore_dist_server.h ApplyUpdates): no worker
+        waits for another.  Every rank, rank 0 included, talks to it over its own connection."""
+        from .server import ParameterServer, ServerClient
+        world = self._dist.world_size() if self._dist.is_initialized() else 1
+        address = None
+        if self.rank == 0:
+            self._server = ParameterServer(world, sync_mode=False)
+            address = self._server.address
+        if world > 1:
+            address = [a for a in self._dist.all_gather_object(address) if a is not None][0]
+        self._client = ServerClient(address)
 
     # ------------------------------------------------------------------ properties
     @property
@@ -176,7 +193,7 @@ class KVStore(KVStoreBase):
             for p in parts[1:]:
                 acc.add_(p.to(acc.dtype))
             merged = acc.to(parts[0].dtype)
-        if self._dist.is_initialized() and self._dist.world_size() > 1 and \
+        if self._client is None and self._dist.is_initialized() and self._dist.world_size() > 1 and \
                 (self._type.startswith('dist') or self._type in ('nccl', 'device', 'p3')):
             if self._compression is not None and merged.dtype == torch.float32:
                 # between workers the packed codes travel as well: every rank gathers the others' words and expands them
@@ -199,7 +216,10 @@ class KVStore(KVStoreBase):
             v = vals[0]
             stored = v.__class__._from_tensor(v._data.detach().clone(), v._ctx)
             stored._stype = getattr(v, '_stype', 'default')
-            if self._dist.is_initialized() and self._dist.world_size() > 1 and self._type != 'local':
+            if self._client is not None:
+                self._client.init(k, stored._data)                    # the first value to arrive is kept
+                stored._data.copy_(self._client.pull(k).to(stored._data.device))
+            elif self._dist.is_initialized() and self._dist.world_size() > 1 and self._type != 'local':
                 self._dist.broadcast_(stored._data, src=0)
             self._store[k] = stored
 
@@ -209,6 +229,10 @@ class KVStore(KVStoreBase):
                 raise MXNetError('key %s has not been initialized' % str(k))
             merged = self._reduce(k, vals, priority=priority)
             stored = self._store[k]
+            if self._client is not None:
+                self.wait_pending()
+                self._client.push(k, merged._data)                   # applied by the server on arrival
+                continue
             if self._updater is not None:
                 self.wait_pending()
                 if merged._data.device != stored._data.device:
@@ -227,6 +251,9 @@ class KVStore(KVStoreBase):
             if k not in self._store:
                 raise MXNetError('key %s has not been initialized' % str(k))
             stored = self._store[k]
+            if self._client is not None:
+                with torch.no_grad():
+                    stored._data.copy_(self._client.pull(k).to(stored._data.device))     # whatever the server holds now
             for o in outs:
                 if ignore_sparse and getattr(o, '_stype', 'default') != 'default':
                     continue
@@ -236,7 +263,7 @@ class KVStore(KVStoreBase):
     def pushpull(self, key, value, out=None, priority=0):
         if out is None:
             out = value
-        if self._updater is None:
+        if self._updater is None and self._client is None:
             # fast path without touching the stored value when no updater is installed
             for (k, vals), (_, outs) in zip(self._group(key, value), self._group(key, out)):
                 merged = self._reduce(k, vals, priority=priority)
@@ -307,7 +334,13 @@ class KVStore(KVStoreBase):
         self._compression = GradientCompression(**compression_params)
 
     def set_optimizer(self, optimizer):
-        """Install an optimizer: updates then run where the merged value lives."""
+        """Install an optimizer: updates then run where the merged value lives (for ``dist_async``: on the server, which
+        receives the pickled optimizer like the reference's servers do)."""
+        if self._client is not None:
+            self._client.set_optimizer(optimizer)
+            if self._dist.is_initialized() and self._dist.world_size() > 1:
+                self._dist.barrier()                                # no push before every server-side updater exists
+            return
         self._set_updater(get_updater(optimizer))
 
     def _set_updater(self, updater):

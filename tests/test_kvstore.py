@@ -211,6 +211,62 @@ def test_dist_sync_kvstore_over_gloo():
 
 
 @pytest.mark.integration
+def test_dist_async_applies_every_push_on_arrival():
+    """``dist_async`` against the reference's server semantics (kvstore_dist_server.h ApplyUpdates, async branch): a lone
+    push completes without the other workers, every push is one server-side update, pulls see the server's value, and a
+    Trainer whose ranks take different numbers of steps does not block."""
+    r = _torchrun('dist_async_worker.py', 3, 29647)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    rep = json.loads([l for l in r.stdout.splitlines() if l.startswith('REPORT ')][-1][7:])
+    assert rep['world'] == 3 and rep['lone_push_applied'] and rep['lone_push_seconds'] < 5.0
+    assert rep['all_pushes_applied'] and rep['pull_same_everywhere']
+    assert rep['server_updates'] == 1 + 3 * 3
+    assert rep['uneven_steps_completed'] == [2, 3, 4] and rep['update_on_kvstore']
+
+
+def test_parameter_server_sync_mode_merges_a_round_before_applying():
+    """The server's sync mode: pushes of one round are summed, the updater runs once when the last worker has pushed, and
+    only then are the round's requests answered (kvstore_dist_server.h:349-404); without an updater the merged value
+    replaces the stored one."""
+    import threading
+    import torch
+    import mxnet_b200 as mx
+    from mxnet_b200.kvstore.server import ParameterServer, ServerClient
+    server = ParameterServer(num_workers=3, sync_mode=True)
+    clients = [ServerClient(server.address) for _ in range(3)]
+    clients[0].init('k', torch.zeros(4))
+    clients[0].set_optimizer(mx.optimizer.create('sgd', learning_rate=1.0, rescale_grad=1.0))
+    done, results = [], [None] * 3
+
+    def worker(i):
+        results[i] = clients[i].push('k', torch.full((4,), float(i + 1)), pull=True)
+        done.append(i)
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    import time
+    time.sleep(0.3)
+    assert not done and server.pushes_applied == 0            # two of three pushed: the round is still open
+    last = threading.Thread(target=worker, args=(2,))
+    last.start()
+    for t in threads + [last]:
+        t.join(10)
+    assert sorted(done) == [0, 1, 2] and server.pushes_applied == 1
+    for r in results:
+        assert torch.equal(r, torch.full((4,), -6.0))          # one SGD step on the merged gradient 1 + 2 + 3
+    # async mode needs an updater
+    async_server = ParameterServer(num_workers=1, sync_mode=False)
+    c = ServerClient(async_server.address)
+    c.init('k', torch.zeros(2))
+    with pytest.raises(mx.MXNetError, match='Updater needs to be set for async mode'):
+        c.push('k', torch.ones(2))
+    for cl in clients + [c]:
+        cl.close()
+    server.stop()
+    async_server.stop()
+
+
+@pytest.mark.integration
 def test_dead_rank_is_detected_by_heartbeat():
     r = _torchrun('dead_rank_worker.py', 3, 29643)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
