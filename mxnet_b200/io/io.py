@@ -483,9 +483,17 @@ class ImageRecordIter(MXDataIter):
                  preprocess_threads=4, prefetch_buffer=4, rand_crop=False, rand_mirror=False, resize=-1,
                  mean_r=0.0, mean_g=0.0, mean_b=0.0, std_r=1.0, std_g=1.0, std_b=1.0, scale=1.0, round_batch=True,
                  num_parts=1, part_index=0, data_name='data', label_name='softmax_label', mean_img=None,
-                 max_random_scale=1.0, min_random_scale=1.0, layout='NCHW', **kwargs):
+                 max_random_scale=1.0, min_random_scale=1.0, layout='NCHW', device=None, dtype=None, **kwargs):
         super().__init__(batch_size, data_name, label_name)
         self._path, self._shape, self._label_width = str(path_imgrec), tuple(data_shape), label_width
+        # device=mx.gpu(i): decode (nvJPEG) and augment on that GPU (io/gpu_pipeline.py); batches are born on the device in
+        # `dtype` (default float32) and only the compressed bytes cross the bus.  Host decode otherwise.
+        self._gpu_pipe = None
+        if device is not None and getattr(device, 'device_type', 'cpu') == 'gpu' and tuple(data_shape)[0] == 3:
+            from .gpu_pipeline import GPUImagePipeline
+            self._gpu_pipe = GPUImagePipeline(device, tuple(data_shape)[1:], layout=layout, dtype=dtype or 'float32',
+                                              mean=(mean_r, mean_g, mean_b), std=(std_r, std_g, std_b), scale=scale, resize=resize,
+                                              rand_crop=rand_crop, rand_mirror=rand_mirror, seed=seed, threads=preprocess_threads)
         self._shuffle, self._rng = shuffle, np.random.RandomState(seed)
         self._rand_crop, self._rand_mirror, self._resize = rand_crop, rand_mirror, resize
         self._mean = np.array([mean_r, mean_g, mean_b], dtype=np.float32).reshape(3, 1, 1)
@@ -596,6 +604,16 @@ class ImageRecordIter(MXDataIter):
             raise StopIteration
         while len(recs) < self.batch_size:
             recs.append(recs[len(recs) % max(1, self.batch_size - pad)])
+        if self._gpu_pipe is not None:
+            from .. import recordio
+            pairs = [recordio.unpack(r) for r in recs]
+            data = self._gpu_pipe([bytes(buf) for _, buf in pairs])
+            label = np.asarray([np.asarray(h.label, dtype=np.float32).reshape(-1)[:self._label_width] for h, _ in pairs],
+                               dtype=np.float32)
+            if self._label_width == 1:
+                label = label.reshape(-1)
+            return DataBatch([data], [nd.array(label, ctx=self._gpu_pipe.ctx)], pad=pad, provide_data=self.provide_data,
+                             provide_label=self.provide_label)
         out = list(self._pool.map(self._process, recs))
         data = self._finish([o[0] for o in out])
         label = np.asarray([np.asarray(o[1], dtype=np.float32).reshape(-1)[:self._label_width] for o in out], dtype=np.float32)

@@ -322,3 +322,94 @@ def test_multi_tensor_add_inplace(dtype):
     torch.cuda.synchronize()
     for d, e, n in zip(dsts, expect, sizes):
         assert torch.equal(d, e), n
+
+
+def _jpeg_bytes(img, quality=95):
+    import io as _io
+    from PIL import Image
+    b = _io.BytesIO()
+    Image.fromarray(img).save(b, format='JPEG', quality=quality, subsampling=0)
+    return b.getvalue()
+
+
+def _smooth_image(rng, h, w):
+    """A smooth colour image (low frequencies only), so that JPEG decoders agree to within a few levels."""
+    yy, xx = np.mgrid[0:h, 0:w].astype('float32')
+    chans = [127 + 100 * np.sin(yy / rng.uniform(15, 40) + rng.uniform(0, 6)) * np.cos(xx / rng.uniform(15, 40) + rng.uniform(0, 6))
+             for _ in range(3)]
+    return np.clip(np.stack(chans, -1), 0, 255).astype('uint8')
+
+
+def _bilinear_reference(img, x0, y0, cw, ch, H, W, mirror):
+    """NumPy restatement of the augmentation kernel's sampling on a decoded image (float64)."""
+    h, w = img.shape[:2]
+    ox = np.arange(W)
+    sx = (W - 1 - ox) if mirror else ox
+    fx = np.clip(x0 + (sx + 0.5) * (cw / W) - 0.5, 0, w - 1)
+    fy = np.clip(y0 + (np.arange(H) + 0.5) * (ch / H) - 0.5, 0, h - 1)
+    xa, ya = np.floor(fx).astype(int), np.floor(fy).astype(int)
+    xb, yb = np.minimum(xa + 1, w - 1), np.minimum(ya + 1, h - 1)
+    wx, wy = (fx - xa)[None, :, None], (fy - ya)[:, None, None]
+    im = img.astype('float64')
+    top = im[ya][:, xa] * (1 - wx) + im[ya][:, xb] * wx
+    bot = im[yb][:, xa] * (1 - wx) + im[yb][:, xb] * wx
+    return top * (1 - wy) + bot * wy
+
+
+@pytest.mark.parametrize('layout,dtype', [('NHWC', 'float16'), ('NCHW', 'float32')])
+def test_gpu_image_pipeline_decodes_and_augments_like_the_host_reference(layout, dtype):
+    """nvJPEG decode + the crop / resize / mirror / normalise kernel against PIL's decode followed by a NumPy restatement
+    of the same sampling (reference pipeline: src/io/iter_image_recordio_2.cc + image_aug_default.cc + iter_normalize.h).
+    JPEG decoders may differ by a few levels; the images are smooth, so the bound is 4 levels of 255."""
+    import io as _io
+    from PIL import Image
+    import mxnet_b200 as mx
+    from mxnet_b200.io import gpu_pipeline
+    assert gpu_pipeline.available()
+    rng = np.random.RandomState(3)
+    sizes = [(96, 128), (150, 100), (64, 64), (201, 77)]
+    imgs = [_smooth_image(rng, h, w) for h, w in sizes]
+    jpegs = [_jpeg_bytes(im) for im in imgs]
+    mean, std, scale = (123.68, 116.28, 103.53), (58.4, 57.1, 57.4), 1.0
+    pipe = gpu_pipeline.GPUImagePipeline(mx.gpu(0), (48, 40), layout=layout, dtype=dtype, mean=mean, std=std, scale=scale)
+    crops = [(3.0, 5.0, 80.0, 60.0), (0.0, 10.0, 100.0, 120.0), (0.0, 0.0, 64.0, 64.0), (10.5, 20.25, 50.0, 150.0)]
+    mirrors = [0, 1, 0, 1]
+    out = pipe(jpegs, crops=crops, mirrors=mirrors).asnumpy().astype('float64')
+    if layout == 'NCHW':
+        out = out.transpose(0, 2, 3, 1)
+    assert out.shape == (4, 48, 40, 3)
+    for i, jb in enumerate(jpegs):
+        dec = np.asarray(Image.open(_io.BytesIO(jb)).convert('RGB'))
+        ref = (_bilinear_reference(dec, *crops[i], 48, 40, mirrors[i]) - np.array(mean)) / np.array(std) * scale
+        err = np.abs(out[i] - ref).max() * max(std)
+        assert err < 4.0 + (0.5 if dtype == 'float16' else 0.0), (i, err)
+    assert pipe.bytes_to_device == sum(len(j) for j in jpegs)
+    with pytest.raises(mx.MXNetError, match='not a readable JPEG'):
+        pipe([b'not a jpeg at all'])
+
+
+def test_image_record_iter_on_the_gpu_matches_the_host_iterator(tmp_path):
+    """``ImageRecordIter(device=mx.gpu(0))``: records are read by the native prefetcher, decoded and augmented on the GPU, and
+    the batches (centre crop, mean / std) agree with the host iterator on the same file; labels are identical."""
+    import mxnet_b200 as mx
+    from mxnet_b200 import recordio
+    rng = np.random.RandomState(5)
+    path = str(tmp_path / 'imgs.rec')
+    w = recordio.MXRecordIO(path, 'w')
+    for i in range(10):
+        img = _smooth_image(rng, 72 + 4 * (i % 3), 80 + 8 * (i % 2))
+        w.write(recordio.pack(recordio.IRHeader(0, float(i % 4), i, 0), _jpeg_bytes(img)))
+    w.close()
+    kw = dict(path_imgrec=path, data_shape=(3, 56, 64), batch_size=4, mean_r=120.0, mean_g=110.0, mean_b=100.0, std_r=60.0, std_g=61.0,
+              std_b=62.0, round_batch=True)
+    host = mx.io.ImageRecordIter(**kw)
+    gpu = mx.io.ImageRecordIter(device=mx.gpu(0), **kw)
+    n = 0
+    for hb, gb in zip(host, gpu):
+        assert gb.data[0].context == mx.gpu(0) and gb.data[0].shape == (4, 3, 56, 64)
+        np.testing.assert_array_equal(hb.label[0].asnumpy(), gb.label[0].asnumpy())
+        diff = np.abs(hb.data[0].asnumpy() - gb.data[0].asnumpy()).max() * 62.0
+        assert diff < 4.0, diff
+        assert hb.pad == gb.pad
+        n += 1
+    assert n == 3
