@@ -87,7 +87,11 @@ def _slice(ins, a):
             e = min(max(e + n if e < 0 else e, 0), n)
             idx[ax] = slice(s, e, st)
         else:
-            raise NotImplementedError('negative steps')
+            # negative step: start is clamped to [0, n-1], end to [-1, n-1] (ONNX Slice-13)
+            s = min(max(s + n if s < 0 else s, 0), n - 1)
+            e = min(max(e + n if e < 0 else e, -1), n - 1) if e >= -n else -1
+            sel = torch.arange(s, e, st)
+            x = x.index_select(ax, sel)
     return x[tuple(idx)]
 
 
@@ -168,7 +172,12 @@ _UNARY = {'Relu': torch.relu, 'Sigmoid': torch.sigmoid, 'Tanh': torch.tanh, 'Sof
           'Identity': lambda x: x, 'Not': torch.logical_not}
 _BINARY = {'Add': torch.add, 'Sub': torch.sub, 'Mul': torch.mul, 'Div': torch.div, 'Pow': torch.pow,
            'Equal': torch.eq, 'Greater': torch.gt, 'Less': torch.lt, 'GreaterOrEqual': torch.ge, 'LessOrEqual': torch.le,
-           'And': torch.logical_and, 'Or': torch.logical_or, 'MatMul': torch.matmul}
+           'And': torch.logical_and, 'Or': torch.logical_or, 'Xor': torch.logical_xor, 'MatMul': torch.matmul}
+
+
+def _depth_to_space_dcr(x, b):
+    n, c, h, w = x.shape
+    return x.reshape(n, b, b, c // (b * b), h, w).permute(0, 3, 4, 1, 5, 2).reshape(n, c // (b * b), h * b, w * b)
 
 
 def _run_node(op, ins, a):
@@ -295,6 +304,28 @@ def _run_node(op, ins, a):
         return torch.from_numpy(np.asarray(a['value']))
     if op == 'Dropout':
         return ins[0]
+    if op == 'OneHot':
+        depth = int(ins[1].reshape(-1)[0])
+        idx = ins[0].long()
+        idx = torch.where(idx < 0, idx + depth, idx)
+        hot = F.one_hot(idx.clamp(0, depth - 1), depth).to(ins[2].dtype)
+        hot = hot * (ins[2][1] - ins[2][0]) + ins[2][0]
+        ax = a.get('axis', -1)
+        return hot if ax in (-1, hot.dim() - 1) else hot.movedim(-1, ax)
+    if op == 'DepthToSpace':
+        return F.pixel_shuffle(ins[0], a['blocksize']) if a.get('mode', 'DCR') == 'CRD' else _depth_to_space_dcr(ins[0], a['blocksize'])
+    if op == 'SpaceToDepth':
+        b = a['blocksize']
+        n, c, h, w = ins[0].shape
+        return ins[0].reshape(n, c, h // b, b, w // b, b).permute(0, 3, 5, 1, 2, 4).reshape(n, c * b * b, h // b, w // b)
+    if op == 'Size':
+        return torch.tensor(ins[0].numel(), dtype=torch.int64)
+    if op == 'TopK':
+        k = int(ins[1].reshape(-1)[0])
+        v, i = torch.topk(ins[0], k, dim=a.get('axis', -1), largest=bool(a.get('largest', 1)), sorted=True)
+        return [v, i]
+    if op == 'HardSigmoid':
+        return torch.clamp(a.get('alpha', 0.2) * ins[0] + a.get('beta', 0.5), 0, 1)
     raise NotImplementedError('ONNX operator %s is not implemented by this evaluator' % op)
 
 

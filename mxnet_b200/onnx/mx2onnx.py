@@ -568,6 +568,199 @@ def _matmul(node, ins, ex):
     return [ex.node('MatMul', ins[:2], node['name'])]
 
 
+# ---------------------------------------------------------------------------------------- comparisons, logic, indexing
+def _compare(onnx_op, negate=False):
+    """Comparison operators return 0/1 in the element type of their first input (not booleans)."""
+    def conv(node, ins, ex):
+        y = ins[1] if len(ins) > 1 else ex.scalar_like(float(node['attrs'].get('scalar', 0.0)), ins[0])
+        b = ex.node(onnx_op, [ins[0], y])
+        if negate:
+            b = ex.node('Not', [b])
+        return [ex.node('Cast', [b], node['name'], to=P.NP_TO_ONNX[np.dtype(ex.dtypes.get(ins[0]) or np.float32)])]
+    return conv
+
+
+for _names, _op, _neg in ((('broadcast_equal', '_equal_scalar', '_npi_equal'), 'Equal', False),
+                          (('broadcast_not_equal', '_not_equal_scalar', '_npi_not_equal'), 'Equal', True),
+                          (('broadcast_greater', '_greater_scalar', '_npi_greater'), 'Greater', False),
+                          (('broadcast_lesser', '_lesser_scalar', '_npi_less'), 'Less', False),
+                          (('broadcast_greater_equal', '_greater_equal_scalar', '_npi_greater_equal'), 'GreaterOrEqual', False),
+                          (('broadcast_lesser_equal', '_lesser_equal_scalar', '_npi_less_equal'), 'LessOrEqual', False)):
+    register(*_names)(_compare(_op, _neg))
+
+
+def _logical(onnx_op):
+    def conv(node, ins, ex):
+        dt = P.NP_TO_ONNX[np.dtype(ex.dtypes.get(ins[0]) or np.float32)]
+        zero = ex.scalar_like(0.0, ins[0])
+        bools = [ex.node('Not', [ex.node('Equal', [i, zero])]) for i in ins[:2]]
+        return [ex.node('Cast', [ex.node(onnx_op, bools)], node['name'], to=dt)]
+    return conv
+
+
+for _mx, _ox in (('broadcast_logical_and', 'And'), ('broadcast_logical_or', 'Or'), ('broadcast_logical_xor', 'Xor')):
+    register(_mx)(_logical(_ox))
+
+
+@register('logical_not')
+def _logical_not(node, ins, ex):
+    dt = P.NP_TO_ONNX[np.dtype(ex.dtypes.get(ins[0]) or np.float32)]
+    return [ex.node('Cast', [ex.node('Equal', [ins[0], ex.scalar_like(0.0, ins[0])])], node['name'], to=dt)]
+
+
+@register('take')
+def _take(node, ins, ex):
+    a = node['attrs']
+    idx = ex.node('Cast', [ins[1]], to=P.INT64)
+    if str(a.get('mode', 'clip')) == 'clip' and ex.shape(ins[0]):
+        hi = ex.shape(ins[0])[int(a.get('axis', 0) or 0)] - 1
+        idx = ex.node('Clip', [idx, ex.const(0, 'lo', np.int64), ex.const(hi, 'hi', np.int64)])
+    return [ex.node('Gather', [ins[0], idx], node['name'], axis=int(a.get('axis', 0) or 0))]
+
+
+@register('one_hot')
+def _one_hot(node, ins, ex):
+    a = node['attrs']
+    depth = ex.const([int(a['depth'])], 'depth', np.int64)
+    values = ex.const([float(a.get('off_value', 0.0)), float(a.get('on_value', 1.0))], 'values', np.float32)
+    out = ex.node('OneHot', [ex.node('Cast', [ins[0]], to=P.INT64), depth, values], axis=-1)
+    return [ex.node('Cast', [out], node['name'], to=P.NP_TO_ONNX[np.dtype(str(a.get('dtype', 'float32')))])]
+
+
+@register('stack')
+def _stack(node, ins, ex):
+    axis = int(node['attrs'].get('axis', 0) or 0)
+    parts = [ex.node('Unsqueeze', [i, ex.const([axis], 'axes', np.int64)]) for i in ins]
+    return [ex.node('Concat', parts, node['name'], axis=axis)]
+
+
+@register('repeat')
+def _repeat(node, ins, ex):
+    a = node['attrs']
+    shp = ex.shape(ins[0])
+    if shp is None or a.get('axis') is None:
+        raise AttributeError('repeat needs an explicit axis and a known input shape to be exported')
+    axis, r = int(a['axis']) % len(shp), int(a['repeats'])
+    x = ex.node('Unsqueeze', [ins[0], ex.const([axis + 1], 'axes', np.int64)])
+    reps = [1] * (len(shp) + 1)
+    reps[axis + 1] = r
+    x = ex.node('Tile', [x, ex.const(reps, 'reps', np.int64)])
+    new_shape = list(shp)
+    new_shape[axis] *= r
+    return [ex.node('Reshape', [x, ex.const(new_shape, 'shape', np.int64)], node['name'])]
+
+
+@register('reverse', 'flip')
+def _reverse(node, ins, ex):
+    shp = ex.shape(ins[0])
+    axes = node['attrs'].get('axis', 0)
+    axes = [axes] if isinstance(axes, int) else list(axes)
+    if shp is None:
+        raise AttributeError('reverse needs a known input shape to be exported')
+    n = len(axes)
+    return [ex.node('Slice', [ins[0], ex.const([-1] * n, 'starts', np.int64), ex.const([-(2 ** 62)] * n, 'ends', np.int64),
+                              ex.const([ax % len(shp) for ax in axes], 'axes', np.int64), ex.const([-1] * n, 'steps', np.int64)],
+                    node['name'])]
+
+
+@register('swapaxes', 'SwapAxis')
+def _swapaxes(node, ins, ex):
+    shp = ex.shape(ins[0])
+    if shp is None:
+        raise AttributeError('swapaxes needs a known input shape to be exported')
+    a = node['attrs']
+    d1, d2 = int(a.get('dim1', 0)) % len(shp), int(a.get('dim2', 0)) % len(shp)
+    perm = list(range(len(shp)))
+    perm[d1], perm[d2] = perm[d2], perm[d1]
+    return [ex.node('Transpose', [ins[0]], node['name'], perm=perm)]
+
+
+@register('depth_to_space', 'space_to_depth')
+def _d2s(node, ins, ex):
+    bs = int(node['attrs']['block_size'])
+    if node['op'] == 'depth_to_space':
+        return [ex.node('DepthToSpace', [ins[0]], node['name'], blocksize=bs, mode='DCR')]
+    return [ex.node('SpaceToDepth', [ins[0]], node['name'], blocksize=bs)]
+
+
+@register('shape_array')
+def _shape_array(node, ins, ex):
+    return [ex.node('Shape', [ins[0]], node['name'])]
+
+
+@register('size_array')
+def _size_array(node, ins, ex):
+    return [ex.node('Reshape', [ex.node('Size', [ins[0]]), ex.const([1], 'shape', np.int64)], node['name'])]      # one element, rank 1
+
+
+@register('topk')
+def _topk(node, ins, ex):
+    a = node['attrs']
+    k = ex.const([int(a.get('k', 1))], 'k', np.int64)
+    vals, idx = ex.node('TopK', [ins[0], k], [ex.fresh('topk_values'), ex.fresh('topk_indices')], axis=int(a.get('axis', -1)),
+                        largest=0 if a.get('is_ascend', False) else 1, sorted=1)
+    ret = str(a.get('ret_typ', 'indices'))
+    idx_f = ex.node('Cast', [idx], to=P.NP_TO_ONNX[np.dtype(str(a.get('dtype', 'float32')))])
+    if ret == 'value':
+        return [ex.node('Identity', [vals], node['name'])]
+    if ret == 'both':
+        return [ex.node('Identity', [vals], node['name'] + '_values'), ex.node('Identity', [idx_f], node['name'] + '_indices')]
+    return [ex.node('Identity', [idx_f], node['name'])]
+
+
+@register('hard_sigmoid')
+def _hard_sigmoid(node, ins, ex):
+    a = node['attrs']
+    return [ex.node('HardSigmoid', [ins[0]], node['name'], alpha=float(a.get('alpha', 0.2)), beta=float(a.get('beta', 0.5)))]
+
+
+@register('softmin')
+def _softmin(node, ins, ex):
+    return [ex.node('Softmax', [ex.node('Neg', [ins[0]])], node['name'], axis=int(node['attrs'].get('axis', -1)))]
+
+
+@register('log2', 'log10', 'log1p', 'expm1', 'cbrt', 'rcbrt', 'degrees', 'radians')
+def _derived_unary(node, ins, ex):
+    op, x = node['op'], ins[0]
+    c = lambda v: ex.scalar_like(v, x)       # noqa: E731
+    if op in ('log2', 'log10'):
+        return [ex.node('Div', [ex.node('Log', [x]), c(float(np.log(2.0 if op == 'log2' else 10.0)))], node['name'])]
+    if op == 'log1p':
+        return [ex.node('Log', [ex.node('Add', [x, c(1.0)])], node['name'])]
+    if op == 'expm1':
+        return [ex.node('Sub', [ex.node('Exp', [x]), c(1.0)], node['name'])]
+    if op in ('cbrt', 'rcbrt'):
+        mag = ex.node('Pow', [ex.node('Abs', [x]), c(1.0 / 3.0)])
+        y = ex.node('Mul', [ex.node('Sign', [x]), mag])
+        return [ex.node('Reciprocal', [y], node['name'])] if op == 'rcbrt' else [ex.node('Identity', [y], node['name'])]
+    return [ex.node('Mul', [x, c(180.0 / np.pi if op == 'degrees' else np.pi / 180.0)], node['name'])]
+
+
+@register('broadcast_like')
+def _broadcast_like(node, ins, ex):
+    return [ex.node('Expand', [ins[0], ex.node('Shape', [ins[1]])], node['name'])]
+
+
+@register('reshape_like')
+def _reshape_like(node, ins, ex):
+    return [ex.node('Reshape', [ins[0], ex.node('Shape', [ins[1]])], node['name'])]
+
+
+@register('SequenceMask')
+def _sequence_mask(node, ins, ex):
+    """(T, N, ...) data, positions t >= length[n] replaced by `value` (axis 0 is time, as in the operator's default)."""
+    a = node['attrs']
+    if not a.get('use_sequence_length', False) or len(ins) < 2:
+        return [ex.node('Identity', [ins[0]], node['name'])]
+    shp = ex.shape(ins[0])
+    if shp is None or int(a.get('axis', 0)) != 0:
+        raise AttributeError('SequenceMask is exported for axis 0 with a known input shape')
+    steps = ex.const(np.arange(shp[0]).reshape([shp[0], 1] + [1] * (len(shp) - 2)), 'steps', np.float32)
+    lens = ex.node('Reshape', [ex.node('Cast', [ins[1]], to=P.FLOAT), ex.const([1, shp[1]] + [1] * (len(shp) - 2), 'shape', np.int64)])
+    keep = ex.node('Less', [steps, lens])
+    return [ex.node('Where', [keep, ins[0], ex.scalar_like(float(a.get('value', 0.0)), ins[0])], node['name'])]
+
+
 # ---------------------------------------------------------------------------------------- driver
 def _canonical(op_name):
     """Operator names in a graph file may be aliases; converters are keyed by the registry's primary name too."""

@@ -119,7 +119,7 @@ def test_transformer_style_graph_with_shape_codes(tmp_path):
 def test_operator_table_and_unknown_operator(tmp_path):
     support = mx.onnx.get_operator_support()
     assert {'Convolution', 'FullyConnected', 'BatchNorm', 'Pooling', 'LayerNorm', 'Embedding', 'batch_dot', 'softmax'} <= set(support)
-    s = mx.sym.topk(mx.sym.var('data'), k=2)
+    s = mx.sym.sort(mx.sym.var('data'))
     with pytest.raises(AttributeError, match='No conversion function registered'):
         mx.onnx.export_model(s, {}, in_shapes=[(2, 5)], onnx_file_path=str(tmp_path / 'x.onnx'))
 
@@ -145,3 +145,73 @@ def test_dynamic_batch_declaration_and_nhwc_layers(tmp_path):
         ref = out._bind(mx.cpu(), dict(args, data=nd.array(x)), aux_states={'mm': params['mm'], 'mv': params['mv']}).forward(
             is_train=False)[0].asnumpy()
         np.testing.assert_allclose(backend.run_model(model, {'data': x})[0], ref, rtol=1e-4, atol=1e-5)
+
+
+def _export_and_compare(tmp_path, sym, feeds, rtol=1e-5, atol=1e-6):
+    import mxnet_b200 as mx
+    names = sym.list_inputs()
+    path = str(tmp_path / 'm.onnx')
+    mx.onnx.export_model(sym, {}, [feeds[n].shape for n in names], [feeds[n].dtype for n in names], path)
+    got = mx.onnx.run_model(path, feeds)
+    ex = sym.bind(mx.cpu(), {n: mx.nd.array(feeds[n], dtype=feeds[n].dtype) for n in names})
+    want = [o.asnumpy() for o in ex.forward()]
+    assert len(got) == len(want)
+    for g, w in zip(got, want):
+        assert g.shape == w.shape
+        np.testing.assert_allclose(g.astype('float64'), w.astype('float64'), rtol=rtol, atol=atol)
+
+
+@pytest.mark.parametrize('case', ['compare', 'logic', 'take', 'one_hot', 'stack_repeat', 'reverse_swap', 'd2s', 'shape_size',
+                                  'topk', 'unary', 'like', 'sequence_mask'])
+def test_more_operator_converters(tmp_path, case):
+    """Comparison / logical / indexing / layout operators: exported, evaluated by the in-tree ONNX evaluator and compared
+    with the Symbol executor on the same inputs."""
+    import mxnet_b200 as mx
+    rng = np.random.RandomState(2)
+    a, b = mx.sym.var('a'), mx.sym.var('b')
+    x = rng.randn(3, 4).astype('float32')
+    y = rng.randn(3, 4).astype('float32')
+    y[0] = x[0]
+    if case == 'compare':
+        sym = mx.sym.Group([mx.sym.broadcast_equal(a, b), mx.sym.broadcast_not_equal(a, b), mx.sym.broadcast_greater(a, b),
+                            mx.sym.broadcast_lesser_equal(a, b), a > 0.2, a <= -0.1])
+        feeds = {'a': x, 'b': y}
+    elif case == 'logic':
+        xa, xb = (x > 0).astype('float32'), (y > 0.3).astype('float32')
+        sym = mx.sym.Group([mx.sym.broadcast_logical_and(a, b), mx.sym.broadcast_logical_or(a, b),
+                            mx.sym.broadcast_logical_xor(a, b), mx.sym.logical_not(a)])
+        feeds = {'a': xa, 'b': xb}
+    elif case == 'take':
+        sym = mx.sym.Group([mx.sym.take(a, b, axis=0), mx.sym.take(a, b, axis=1)])
+        feeds = {'a': x, 'b': np.array([[0, 2], [1, 7]], dtype='float32')}          # 7 is clipped
+    elif case == 'one_hot':
+        sym = mx.sym.one_hot(a, depth=5, on_value=2.0, off_value=-1.0)
+        feeds = {'a': np.array([0, 3, 4, 1], dtype='float32')}
+    elif case == 'stack_repeat':
+        sym = mx.sym.Group([mx.sym.stack(a, b, axis=1), mx.sym.repeat(a, repeats=3, axis=1)])
+        feeds = {'a': x, 'b': y}
+    elif case == 'reverse_swap':
+        sym = mx.sym.Group([mx.sym.reverse(a, axis=1), mx.sym.swapaxes(a, dim1=0, dim2=1)])
+        feeds = {'a': x}
+    elif case == 'd2s':
+        sym = mx.sym.Group([mx.sym.depth_to_space(a, block_size=2), mx.sym.space_to_depth(b, block_size=2)])
+        feeds = {'a': rng.randn(2, 8, 3, 3).astype('float32'), 'b': rng.randn(2, 2, 4, 6).astype('float32')}
+    elif case == 'shape_size':
+        sym = mx.sym.Group([mx.sym.shape_array(a), mx.sym.size_array(a)])
+        feeds = {'a': x}
+    elif case == 'topk':
+        sym = mx.sym.Group([mx.sym.topk(a, k=2, axis=-1, ret_typ='value'), mx.sym.topk(a, k=2, axis=-1, ret_typ='indices'),
+                            mx.sym.topk(a, k=1, axis=0, ret_typ='value', is_ascend=True)])
+        feeds = {'a': x}
+    elif case == 'unary':
+        pos = np.abs(x) + 0.5
+        sym = mx.sym.Group([mx.sym.log2(a), mx.sym.log10(a), mx.sym.log1p(a), mx.sym.expm1(a), mx.sym.cbrt(b), mx.sym.rcbrt(a),
+                            mx.sym.degrees(b), mx.sym.radians(b), mx.sym.hard_sigmoid(b), mx.sym.softmin(b, axis=-1)])
+        feeds = {'a': pos, 'b': x}
+    elif case == 'like':
+        sym = mx.sym.Group([mx.sym.broadcast_like(a, b), mx.sym.reshape_like(b, mx.sym.var('c'))])
+        feeds = {'a': x[:1], 'b': y, 'c': np.zeros((2, 6), dtype='float32')}
+    else:
+        sym = mx.sym.SequenceMask(a, b, use_sequence_length=True, value=-7.0)
+        feeds = {'a': rng.randn(5, 3, 2).astype('float32'), 'b': np.array([2, 5, 0], dtype='float32')}
+    _export_and_compare(tmp_path, sym, feeds, rtol=1e-4, atol=1e-5)
