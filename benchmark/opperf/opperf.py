@@ -269,14 +269,14 @@ def run_case(name, ctx, dtype, runs, warmup, small):
     return res
 
 
-def gemm_burst(ctx, dtype, reps=50):
+def gemm_burst(ctx, dtype, reps=50, shapes=None):
     """Kernel-only GEMM throughput: `reps` back-to-back launches between two events, so that host launch
     overhead does not count; the in-tree tcgen05 kernel and the library GEMM on identical operands."""
     from mxnet_b200.ops.cuda import gemm_ops
     td = mx.base.to_torch_dtype(dtype)
     out = []
-    for m, n, k in [(8192, 3072, 768), (8192, 768, 3072), (4096, 4096, 4096), (16384, 1024, 1024), (8192, 8192, 8192),
-                    (802816, 64, 256), (200704, 512, 128)]:
+    for m, n, k in shapes or [(8192, 3072, 768), (8192, 768, 3072), (4096, 4096, 4096), (16384, 1024, 1024), (8192, 8192, 8192),
+                              (802816, 64, 256), (200704, 512, 128)]:
         a = torch.randn(m, k, device=ctx.torch_device).to(td)
         b = torch.randn(n, k, device=ctx.torch_device).to(td)
         d = torch.empty(m, n, device=ctx.torch_device, dtype=td)
@@ -413,6 +413,8 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--small', action='store_true', help='shapes sized for a profiler capture (a few hundred MB)')
     ap.add_argument('--list', action='store_true')
+    ap.add_argument('--shape', type=int, nargs=3, metavar=('M', 'N', 'K'), help='gemm_burst: this one product only')
+    ap.add_argument('--reps', type=int, default=50, help='gemm_burst: launches between the two events')
     args = ap.parse_args()
     if args.list:
         print('\n'.join(CASES))
@@ -439,7 +441,7 @@ def main():
             continue
         if name == 'gemm_burst':
             if cuda:
-                for r in gemm_burst(ctx, dtype):
+                for r in gemm_burst(ctx, dtype, reps=args.reps, shapes=[tuple(args.shape)] if args.shape else None):
                     print(json.dumps(r), flush=True)
             continue
         print(json.dumps(run_case(name, ctx, dtype, args.runs, args.warmup, small)), flush=True)

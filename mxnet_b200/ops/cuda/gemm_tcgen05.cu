@@ -43,7 +43,7 @@ template <int BN> struct TileCfg {
   // TMEM columns between the two accumulators and the (power-of-two) allocation that holds both
   static constexpr int ACC_STRIDE = BN == 192 ? 256 : BN;
   static constexpr uint32_t TMEM_COLS = 2 * ACC_STRIDE < 32 ? 32 : 2 * ACC_STRIDE;
-  static constexpr uint32_t STG_BYTES = 4 * 2048;   // per epilogue warp: 32 rows x 64 bytes staged for the TMA store
+  static constexpr uint32_t STG_BYTES = 4 * 4096;   // per epilogue warp: two staging tiles of 32 rows x 64 bytes for the TMA stores
   static constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + STG_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
@@ -118,7 +118,10 @@ __device__ __forceinline__ void drain_quarter(uint32_t taddr, uint8_t* stg, cons
     if (use_tma_store) {
       // rows as four 16-byte pieces in the swizzled layout of the store's tensor map; one bulk store per 32 x 32
       // block (rows and columns outside the matrix are clipped by the copy engine)
-      if (lane == 0) tma_store_wait_read();
+      // two staging tiles alternate (every tile width is an even number of 32-column blocks): the store issued two blocks
+      // ago has released the tile reused now, the previous one may still be reading its own
+      uint8_t* sb = stg + ((c0 >> 5) & 1) * 2048;
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
       __syncwarp();
       if (col0 < N && row0 < M) {
 #pragma unroll
@@ -126,14 +129,16 @@ __device__ __forceinline__ void drain_quarter(uint32_t taddr, uint8_t* stg, cons
           Vec16<T> o;
 #pragma unroll
           for (int j = 0; j < 8; ++j) o.v[j] = Cvt<T>::from_f(f[v * 8 + j]);
-          st16(reinterpret_cast<T*>(stg + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)), o);
+          st16(reinterpret_cast<T*>(sb + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)), o);
         }
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_3d(map_d, stg, col0, row0, zb);
+          tma_store_3d(map_d, sb, col0, row0, zb);
           tma_store_commit();
         }
+      } else if (lane == 0) {
+        tma_store_commit();            // an empty group keeps the count of groups per block, which the wait above relies on
       }
     } else if (row < M && col0 < N) {
       T* drow = D + (size_t)row * ldd + col0;
@@ -337,7 +342,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else {
     // epilogue warps 2..5: TMEM lane quarter = warp index modulo 4
     const int q = warp & 3;
-    uint8_t* stg = sStg + q * 2048;       // this warp's staging tile: 32 rows x 64 bytes, 64-byte swizzle
+    uint8_t* stg = sStg + q * 4096;       // this warp's two staging tiles: 32 rows x 64 bytes each, 64-byte swizzle
     int t = 0;
     UnitIter u;
     u.init(full_tiles, sk_tiles, sk_ctas, num_k);
@@ -464,7 +469,7 @@ template <int BN> struct PairCfg {
   static constexpr int STAGES = BN == 256 ? 6 : (BN == 192 ? 6 : 8);
   static constexpr int ACC_STRIDE = BN == 192 ? 256 : BN;
   static constexpr uint32_t TMEM_COLS = 2 * ACC_STRIDE;
-  static constexpr uint32_t STG_BYTES = 4 * 2048;
+  static constexpr uint32_t STG_BYTES = 4 * 4096;
   static constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + STG_BYTES + 1024 + 512;
 };
 constexpr int BM2 = 256;     // rows of a pair's tile
@@ -596,7 +601,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else {
     const int q = warp & 3;
-    uint8_t* stg = sStg + q * 2048;
+    uint8_t* stg = sStg + q * 4096;
     const uint32_t acc_empty_leader = mapa_u32(smem_u32(&acc_empty[0]), 0);
     int t = 0;
     for (int unit = pair; unit < num_units; unit += num_pairs, ++t) {
