@@ -138,7 +138,7 @@ declare('MXNET_B200_GEMM_AUTOTUNE', bool, True, 'time the tcgen05 GEMM against t
 declare('MXNET_B200_GEMM', bool, True, 'route half-precision FullyConnected/dot to the tcgen05 GEMM kernel (0 = library GEMM)')
 # ---- graph --------------------------------------------------------------------------------
 declare('MXNET_B200_RNN', str, 'auto', 'RNN operator on the in-tree recurrence kernels: auto = time forward + backward against the library recurrence per configuration, 1 = force, 0 = library')
-declare('MXNET_B200_RNN_TC', bool, True, 'LSTM recurrence of the in-tree path on the tensor-core kernels (tcgen05; tf32 products for fp32 models) where the shape allows; 0 = the fp32-pipe recurrence kernels')
+declare('MXNET_B200_RNN_TC', bool, True, 'LSTM recurrence of the in-tree path on the tensor-core kernels (tcgen05; tf32 products for fp32 models, as the library recurrence uses) for layers of 32 units or more where the shape allows; 0 = the fp32-pipe recurrence kernels (exact fp32 products)')
 declare('MXNET_USE_FUSION', bool, True, 'pointwise fusion')
 declare('MXNET_ELIMINATE_COMMON_EXPR', bool, True, 'common-subexpression elimination on symbols')
 declare('MXNET_MEMORY_OPT', bool, False, 'recompute cheap activations in backward')

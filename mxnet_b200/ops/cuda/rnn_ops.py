@@ -167,6 +167,8 @@ def tc_supported(dtype, B, H):
     from ... import env
     if not env.get('MXNET_B200_RNN_TC') or dtype not in (torch.float32, torch.float16, torch.bfloat16):
         return False
+    if int(H) < 32:
+        return False        # narrow layers gain nothing from the tensor cores and keep exact fp32 products (fp32-pipe kernels)
     code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dtype]
     return bool(lib().mxb_lstm_tc_supported(code, int(B), int(H)))
 

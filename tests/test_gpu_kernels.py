@@ -663,7 +663,7 @@ def test_gradient_compression_kernels_match_tensor_ops(kind, threshold, n):
 
 
 # ---------------------------------------------------------------------------------------- LSTM
-@pytest.mark.parametrize('T,B,I,H,layers', [(5, 3, 8, 16, 1), (7, 4, 24, 40, 2), (35, 80, 650, 650, 2), (3, 1, 16, 200, 1),
+@pytest.mark.parametrize('T,B,I,H,layers', [(5, 3, 8, 32, 1), (7, 4, 24, 40, 2), (35, 80, 650, 650, 2), (3, 1, 16, 200, 1),
                                              (4, 33, 64, 888, 1)])
 @pytest.mark.parametrize('dtype', [torch.float32, torch.float16])
 @pytest.mark.parametrize('tc', ['cluster', 'plain', False])

@@ -255,7 +255,7 @@ def test_group2ctx_places_operators_and_arguments():
     b = plain.forward(is_train=True)[0]
     assert placed.cross_device_copies == 1
     np.testing.assert_allclose(a.asnumpy(), b.asnumpy(), rtol=1e-6)
-    placed.backward(nd.ones(a.shape))
-    plain.backward(nd.ones(b.shape))
+    placed.backward(nd.ones(a.shape, ctx=a.context))
+    plain.backward(nd.ones(b.shape, ctx=b.context))
     for k in shapes:
         np.testing.assert_allclose(placed.grad_dict[k].asnumpy(), plain.grad_dict[k].asnumpy(), rtol=1e-5, atol=1e-6)
