@@ -95,6 +95,15 @@ def measure_extras(args, ctx, rank, world, measure_resnet, barrier):
     guarded('bert', lambda: sub_model('bert_pretrain', ['--steps', str(steps), '--warmup', str(warmup)], False))
     guarded('lstm_lm', lambda: sub_model('lstm_lm', ['--steps', str(steps), '--warmup', str(warmup), '--dtype', 'float32'], True))
 
+    # the same model with the fp32 GEMMs in the reference's math mode (tf32 operands: src/operator/linalg_impl.h:298 sets
+    # CUBLAS_TF32_TENSOR_OP_MATH for fp32 products); reported beside the exact-fp32 record, not instead of it
+    def lstm_tf32():
+        try:
+            return sub_model('lstm_lm', ['--steps', str(steps), '--warmup', str(warmup), '--dtype', 'float32', '--tf32'], True)
+        finally:
+            env.set('MXNET_CUDA_ALLOW_TF32', False)
+    guarded('lstm_lm_tf32', lstm_tf32)
+
     # ---- gradient-exchange bandwidth (needs peers) -----------------------------------------------------------------------
     if world > 1:
         def pushpull():

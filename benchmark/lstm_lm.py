@@ -18,6 +18,9 @@ def parser():
     ap.add_argument('--batch', type=int, default=80)
     ap.add_argument('--bptt', type=int, default=35)
     ap.add_argument('--dtype', default='float32', choices=['float32', 'float16'])
+    ap.add_argument('--tf32', action='store_true',
+                    help='fp32 GEMMs (the decoder above all) with tf32 operands: MXNET_CUDA_ALLOW_TF32=1, the math mode the '
+                         'reference sets for its fp32 cuBLAS calls (src/operator/linalg_impl.h:298)')
     return ap
 
 
@@ -27,7 +30,9 @@ def spec(args):
         import numpy as np
         import mxnet_b200 as mx
         from mxnet_b200 import autograd, gluon, nd
+        from mxnet_b200 import env
         from mxnet_b200.models.lstm_lm import LSTMLanguageModel
+        env.set('MXNET_CUDA_ALLOW_TF32', bool(args.tf32))
         net = LSTMLanguageModel(vocab_size=33278, embed_size=650, hidden_size=650, num_layers=2, dropout=0.5)
         net.initialize(mx.init.Xavier(), ctx=ctx)
         if args.dtype != 'float32':
@@ -60,7 +65,8 @@ def spec(args):
             return loss
         return step
     cfg = {'model': 'lstm_lm_2x650', 'batch_per_gpu': args.batch, 'bptt': args.bptt, 'vocab': 33278,
-           'optimizer': 'sgd + global-norm clip 0.25', 'dtype': args.dtype}
+           'optimizer': 'sgd + global-norm clip 0.25', 'dtype': args.dtype,
+           'fp32_gemm_math': 'tf32 operands, fp32 accumulation' if args.tf32 else 'fp32'}
     return 'lstm_lm_tokens_per_s', 'tokens/s', args.batch * args.bptt, make_step, cfg
 
 

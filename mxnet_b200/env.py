@@ -52,6 +52,17 @@ def set(name, value):  # pylint: disable=redefined-builtin
         os.environ[name] = str(int(value)) if isinstance(value, bool) else str(value)
     if name == 'MXNET_ENGINE_TYPE':
         _refresh_engine_type()
+    if name == 'MXNET_CUDA_ALLOW_TF32':
+        _refresh_tf32()
+
+
+def _refresh_tf32():
+    """Mirror ``MXNET_CUDA_ALLOW_TF32`` into the tensor library's math mode for fp32 GEMMs and convolutions (forward and
+    backward, on every thread)."""
+    import torch
+    on = bool(get('MXNET_CUDA_ALLOW_TF32'))
+    torch.backends.cuda.matmul.allow_tf32 = on
+    torch.backends.cudnn.allow_tf32 = on
 
 
 def _refresh_engine_type():
@@ -127,6 +138,7 @@ declare('MXNET_KVSTORE_NVLS', bool, False, 'fused optimizer step / all-reduce of
 declare('MXNET_SAFE_ACCUMULATION', bool, True, 'accumulate fp16 reductions in fp32')
 declare('MXNET_ENFORCE_DETERMINISM', bool, False, 'refuse non-deterministic kernels')
 declare('MXNET_CUDA_ALLOW_TENSOR_CORE', bool, True, 'allow tensor-core GEMM/conv')
+declare('MXNET_CUDA_ALLOW_TF32', bool, False, 'fp32 GEMMs and convolutions of the library path on tf32 tensor cores. The reference computes its fp32 cuBLAS products in this mode on CUDA 11+ (src/operator/linalg_impl.h:298, CUBLAS_TF32_TENSOR_OP_MATH); here fp32 stays exact unless this is set')
 declare('MXNET_FC_TRUE_FP16', bool, False, 'accumulate FullyConnected in fp16 (never on tcgen05)')
 declare('MXNET_B200_KERNELS', bool, True, 'use the hand-written sm_100a kernels (0 = library path)')
 declare('MXNET_RNN_UNROLLED', bool, False, 'run the RNN operator as per-step tensor operations even on a GPU (debugging)')
@@ -172,6 +184,10 @@ def markdown():
             default = '~' + default[len(home):]         # the document must not depend on who generated it
         lines.append('| `%s` | %s | `%r` | %s |' % (f.name, f.type.__name__, default, f.doc.replace('|', '\\|')))
     return '\n'.join(lines) + '\n'
+
+
+if os.environ.get('MXNET_CUDA_ALLOW_TF32') is not None:
+    _refresh_tf32()
 
 
 if __name__ == '__main__':
