@@ -483,17 +483,22 @@ class ImageRecordIter(MXDataIter):
                  preprocess_threads=4, prefetch_buffer=4, rand_crop=False, rand_mirror=False, resize=-1,
                  mean_r=0.0, mean_g=0.0, mean_b=0.0, std_r=1.0, std_g=1.0, std_b=1.0, scale=1.0, round_batch=True,
                  num_parts=1, part_index=0, data_name='data', label_name='softmax_label', mean_img=None,
-                 max_random_scale=1.0, min_random_scale=1.0, layout='NCHW', device=None, dtype=None, **kwargs):
+                 max_random_scale=1.0, min_random_scale=1.0, layout='NCHW', device=None, dtype=None, random_resized_crop=False,
+                 min_random_area=0.08, max_random_area=1.0, min_aspect_ratio=0.75, max_aspect_ratio=4.0 / 3.0, **kwargs):
         super().__init__(batch_size, data_name, label_name)
         self._path, self._shape, self._label_width = str(path_imgrec), tuple(data_shape), label_width
         # device=mx.gpu(i): decode (nvJPEG) and augment on that GPU (io/gpu_pipeline.py); batches are born on the device in
         # `dtype` (default float32) and only the compressed bytes cross the bus.  Host decode otherwise.
+        # random_resized_crop: a rectangle of random area and aspect ratio resampled to data_shape (image_aug_default.cc)
+        self._rrc = (float(min_random_area), float(max_random_area), float(min_aspect_ratio), float(max_aspect_ratio)) \
+            if random_resized_crop else None
         self._gpu_pipe = None
         if device is not None and getattr(device, 'device_type', 'cpu') == 'gpu' and tuple(data_shape)[0] == 3:
             from .gpu_pipeline import GPUImagePipeline
             self._gpu_pipe = GPUImagePipeline(device, tuple(data_shape)[1:], layout=layout, dtype=dtype or 'float32',
                                               mean=(mean_r, mean_g, mean_b), std=(std_r, std_g, std_b), scale=scale, resize=resize,
-                                              rand_crop=rand_crop, rand_mirror=rand_mirror, seed=seed, threads=preprocess_threads)
+                                              rand_crop=rand_crop, rand_mirror=rand_mirror, seed=seed, threads=preprocess_threads,
+                                              random_resized_crop=self._rrc)
         self._shuffle, self._rng = shuffle, np.random.RandomState(seed)
         self._rand_crop, self._rand_mirror, self._resize = rand_crop, rand_mirror, resize
         self._mean = np.array([mean_r, mean_g, mean_b], dtype=np.float32).reshape(3, 1, 1)
@@ -553,6 +558,28 @@ class ImageRecordIter(MXDataIter):
         header, buf = recordio.unpack(rec)
         img = _decode_to_numpy(buf, 1 if self._shape[0] == 3 else 0)
         c, h, w = self._shape
+        if self._rrc is not None:
+            from PIL import Image
+            ih, iw = img.shape[:2]
+            amin, amax, rmin, rmax = self._rrc
+            box = None
+            for _ in range(10):
+                area = np.random.uniform(amin, amax) * ih * iw
+                ratio = np.exp(np.random.uniform(np.log(rmin), np.log(rmax)))
+                cw, ch = int(round(np.sqrt(area * ratio))), int(round(np.sqrt(area / ratio)))
+                if 0 < cw <= iw and 0 < ch <= ih:
+                    x0, y0 = np.random.randint(0, iw - cw + 1), np.random.randint(0, ih - ch + 1)
+                    box = (x0, y0, x0 + cw, y0 + ch)
+                    break
+            if box is None:
+                side = min(ih, iw)
+                box = ((iw - side) // 2, (ih - side) // 2, (iw - side) // 2 + side, (ih - side) // 2 + side)
+            img = np.asarray(Image.fromarray(img.squeeze()).resize((w, h), Image.BILINEAR, box=box))
+            if img.ndim == 2:
+                img = img[:, :, None]
+            if self._rand_mirror and np.random.rand() < 0.5:
+                img = img[:, ::-1]
+            return img, header.label
         if self._resize > 0:
             from PIL import Image
             ih, iw = img.shape[:2]

