@@ -65,6 +65,14 @@ class _TokenEmbedding(Vocabulary):
         vecs = self.idx_to_vec[nd.array(indices, dtype='int64')]
         return vecs[0] if to_reduce else vecs
 
+    def _build_embedding_for_vocabulary(self, vocabulary):
+        """Keep only the tokens of ``vocabulary``, in its order; tokens without a loaded vector get the unknown vector."""
+        from ... import ndarray as nd
+        vecs = self.get_vecs_by_tokens(list(vocabulary.idx_to_token)).asnumpy()
+        self._idx_to_token = list(vocabulary.idx_to_token)
+        self._token_to_idx = dict(vocabulary.token_to_idx)
+        self._idx_to_vec = nd.array(vecs)
+
     def update_token_vectors(self, tokens, new_vectors):
         if not isinstance(tokens, list):
             tokens = [tokens]
@@ -79,6 +87,8 @@ class CustomEmbedding(_TokenEmbedding):
     def __init__(self, pretrained_file_path, elem_delim=' ', encoding='utf8', init_unknown_vec=np.zeros, vocabulary=None, **kwargs):
         super().__init__(**kwargs)
         self._load_embedding(pretrained_file_path, elem_delim, init_unknown_vec, encoding)
+        if vocabulary is not None:
+            self._build_embedding_for_vocabulary(vocabulary)
 
 
 @register

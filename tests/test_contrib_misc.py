@@ -30,6 +30,14 @@ def test_custom_embedding_file(tmp_path):
     np.testing.assert_allclose(v, [[1, 2, 3], [0, 0, 0], [0.1, 0.2, 0.3]], rtol=1e-6)
     emb.update_token_vectors('hello', nd.array([[9.0, 9.0, 9.0]]))
     np.testing.assert_allclose(emb.get_vecs_by_tokens('hello').asnumpy(), [9, 9, 9])
+    # restricted to a vocabulary: its tokens, in its order; tokens the file does not have get the unknown vector
+    vocab = text.Vocabulary(collections.Counter(['world', 'world', 'other', 'hello']), unknown_token='<unk>')
+    sub = text.embedding.CustomEmbedding(str(path), elem_delim=' ', vocabulary=vocab)
+    assert sub.idx_to_token == vocab.idx_to_token and len(sub) == len(vocab)
+    np.testing.assert_allclose(sub.idx_to_vec.asnumpy()[sub.token_to_idx['world']], [1, 2, 3])
+    np.testing.assert_allclose(sub.idx_to_vec.asnumpy()[sub.token_to_idx['other']], [0, 0, 0])
+    comp = text.embedding.CompositeEmbedding(vocab, [emb, emb])
+    assert comp.vec_len == 6 and comp.idx_to_vec.shape == (len(vocab), 6)
 
 
 def test_onnx_export_writes_a_loadable_graph(tmp_path):
