@@ -394,6 +394,7 @@ lstm_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_h, const __grid_const
 
 #include "lstm_tc_bwd.inl"
 #include "lstm_tc_bwdc.inl"
+#include "gru_tc.inl"
 
 }  // namespace mxb
 

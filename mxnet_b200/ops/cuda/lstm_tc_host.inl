@@ -208,3 +208,178 @@ MXB_EXPORT int mxb_lstm_tc_backward(int dtype, const void* dy, const void* dhT, 
 
 // 0 (default): the backward pass cuts its contraction over clusters of four CTAs where they fit; 1: plain kernel only.
 MXB_EXPORT void mxb_lstm_tc_set_backward_variant(int v) { g_tc_bwd_variant = v; }
+
+// ---- GRU (gru_tc.inl) -------------------------------------------------------------------------------------------------------
+namespace mxb {
+
+struct GruPlan {
+  int ok;
+  int U, KC, esz, Bp, Hp, C, Hc, KK, NGP;
+  int stages_f, stages_c;
+  size_t smem_f, smem_c;
+};
+
+static GruPlan gru_plan(int dtype, int B, int H) {
+  GruPlan pl = {};
+  if (B < 1 || B > 128 || H < 1) return pl;
+  pl.esz = dtype == kF32 ? 4 : 2;
+  pl.U = dtype == kF32 ? 8 : 16;
+  pl.KC = 128 / pl.esz;
+  pl.NGP = pl.KC;                                            // 3U gate columns padded to one chunk
+  pl.Bp = (B + 7) / 8 * 8;
+  pl.Hp = (H + pl.KC - 1) / pl.KC * pl.KC;
+  pl.C = ((H + pl.U - 1) / pl.U + kTcCluster - 1) / kTcCluster * kTcCluster;
+  pl.Hc = pl.C * pl.U;
+  pl.KK = pl.C * pl.NGP;
+  if (pl.C > sm_count()) return pl;
+  const size_t stage = (size_t)pl.Bp * 128;
+  const size_t wf = (size_t)(pl.Hp / pl.KC) * pl.NGP * 128;
+  const size_t wc = (size_t)(pl.KK / kTcCluster / pl.KC) * kTcCluster * pl.U * 128;
+  const size_t xc = (size_t)kTcCluster * 128 * pl.U * 4 + 64;
+  if (wf + kTcFixed + 3 * stage > kTcSmemMax || wc + xc + kTcFixed + 3 * stage > kTcSmemMax) return pl;
+  size_t sf = (kTcSmemMax - kTcFixed - wf) / stage, sc = (kTcSmemMax - kTcFixed - wc - xc) / stage;
+  pl.stages_f = (int)(sf > (size_t)kTcMaxStages ? (size_t)kTcMaxStages : sf);
+  pl.stages_c = (int)(sc > (size_t)kTcMaxStages ? (size_t)kTcMaxStages : sc);
+  pl.smem_f = wf + kTcFixed + (size_t)pl.stages_f * stage;
+  pl.smem_c = wc + xc + kTcFixed + (size_t)pl.stages_c * stage;
+  pl.ok = 1;
+  return pl;
+}
+
+template <typename K>
+static int gru_launch(K kernel, unsigned long long* seen, int grid, size_t smem, int cluster, cudaStream_t st, const CUtensorMap& m0,
+                      const CUtensorMap& m1, const GruTcParams& p) {
+  if (first_on_device(seen)) {
+    cudaError_t rc = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemMax - 64);
+    if (rc != cudaSuccess) return (int)rc;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (cluster > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = cluster;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  attr[na].id = cudaLaunchAttributeCooperative;
+  attr[na].val.cooperative = 1;
+  ++na;
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  if (cluster > 1) {
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); return -100; }
+    if (clusters * cluster < grid) return -100;
+  }
+  return (int)cudaLaunchKernelEx(&cfg, kernel, m0, m1, p);
+}
+
+template <typename T, typename X, int U>
+static int gru_forward(const GruPlan& pl, const CUtensorMap& mh, const CUtensorMap& mw, const GruTcParams& p, cudaStream_t st) {
+  static unsigned long long seen = 0;
+  return gru_launch(gru_tc_fwd_kernel<T, X, U>, &seen, pl.C, pl.smem_f, 1, st, mh, mw, p);
+}
+template <typename T, typename X, int U>
+static int gru_backward(const GruPlan& pl, const CUtensorMap& md, const CUtensorMap& mw, const GruTcParams& p, cudaStream_t st) {
+  static unsigned long long seen = 0;
+  return gru_launch(gru_tc_bwdc_kernel<T, X, U>, &seen, pl.C, pl.smem_c, kTcCluster, st, md, mw, p);
+}
+
+// Whether the device holds all clusters of the backward kernel at once (its grid barrier needs every CTA resident).
+template <typename K>
+static bool gru_clusters_fit(K kernel, const GruPlan& pl) {
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemMax - 64) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pl.C);
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = pl.smem_c;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kTcCluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); return false; }
+  return clusters * kTcCluster >= pl.C;
+}
+
+}  // namespace mxb
+
+// 1 when the tensor-core GRU recurrence can run (dtype, batch, hidden size) on the current device: the plan fits shared
+// memory and the device holds every cluster of the backward kernel at the same time.
+MXB_EXPORT int mxb_gru_tc_supported(int dtype, int B, int H) {
+  const GruPlan pl = gru_plan(dtype, B, H);
+  if (!pl.ok) return 0;
+  if (dtype == kF32) return gru_clusters_fit(gru_tc_bwdc_kernel<float, float, 8>, pl) ? 1 : 0;
+  if (dtype == kF16) return gru_clusters_fit(gru_tc_bwdc_kernel<__half, __half, 16>, pl) ? 1 : 0;
+  return gru_clusters_fit(gru_tc_bwdc_kernel<__nv_bfloat16, __nv_bfloat16, 16>, pl) ? 1 : 0;
+}
+
+// out[0..6] = U, Bp, Hp, C, Hc, KK, NGP (padded gate columns per CTA).
+MXB_EXPORT int mxb_gru_tc_dims(int dtype, int B, int H, int* out) {
+  const GruPlan pl = gru_plan(dtype, B, H);
+  if (!pl.ok) return -2;
+  out[0] = pl.U; out[1] = pl.Bp; out[2] = pl.Hp; out[3] = pl.C; out[4] = pl.Hc; out[5] = pl.KK; out[6] = pl.NGP;
+  return 0;
+}
+
+// Forward.  `xproj` [T, B, KK]: input projection in the per-CTA column order c*NGP + g*U + u (b_ih, plus b_hh for r and z).
+// `wp` [C * NGP, Hp]: packed W_hh rows in the same order.  `bhn` [Hc] fp32: hidden-side bias of the candidate gate.
+// `gates` [T, B, KK] and `hnb` [T, B, Hc] (fp32) are written when non-null.  `hbuf`: zero-initialised [2, Bp, Hp].
+MXB_EXPORT int mxb_gru_tc_forward(int dtype, const void* xproj, const void* wp, const void* bhn, const void* h0, void* y, void* hT,
+                                  void* gates, void* hnb, void* hbuf, void* bar, int T, int B, int H, void* stream) {
+  const GruPlan pl = gru_plan(dtype, B, H);
+  if (!pl.ok || T < 1) return -2;
+  CUtensorMap mh, mw;
+  int rc = tc_make_map(&mh, hbuf, dtype, 2 * (int64_t)pl.Bp, pl.Hp, pl.Bp);
+  if (rc) return rc;
+  rc = tc_make_map(&mw, wp, dtype, (int64_t)pl.C * pl.NGP, pl.Hp, pl.NGP);
+  if (rc) return rc;
+  GruTcParams g = {};
+  LstmTcParams& p = g.base;
+  p.xproj = xproj; p.y = y; p.hT = hT; p.gates = gates; p.hbuf = hbuf; p.bar = (unsigned int*)bar;
+  p.T = T; p.B = B; p.H = H; p.Bp = pl.Bp; p.Hp = pl.Hp; p.Hc = pl.Hc; p.KK = pl.KK; p.stages = pl.stages_f;
+  p.yalign = tc_row_align(H, pl.esz);
+  g.bhn = bhn; g.hnb = (float*)hnb; g.h0 = h0;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == kF32) return gru_forward<float, float, 8>(pl, mh, mw, g, st);
+  if (dtype == kF16) return gru_forward<__half, __half, 16>(pl, mh, mw, g, st);
+  return gru_forward<__nv_bfloat16, __nv_bfloat16, 16>(pl, mh, mw, g, st);
+}
+
+// Backward.  `wb` [Hc, KK]: row n = column n of W_hh with the gate rows in the order of `gates`.  `dgh` [T, B, KK] receives the
+// hidden-side gate gradients (dar, daz, dan * r), `dgx` [T, B, KK] the input-side ones (dar, daz, dan).  Returns -100 when the
+// device cannot hold all clusters at once.
+MXB_EXPORT int mxb_gru_tc_backward(int dtype, const void* dy, const void* dhT, const void* gates, const void* hnb, const void* y,
+                                   const void* h0, const void* wb, void* dgh, void* dgx, void* dh0, void* bar, int T, int B, int H,
+                                   void* stream) {
+  const GruPlan pl = gru_plan(dtype, B, H);
+  if (!pl.ok || T < 1) return -2;
+  CUtensorMap md, mw;
+  int rc = tc_make_map(&md, dgh, dtype, (int64_t)T * B, pl.KK, pl.Bp);
+  if (rc) return rc;
+  rc = tc_make_map(&mw, wb, dtype, (int64_t)pl.C * pl.U, pl.KK, kTcCluster * pl.U);
+  if (rc) return rc;
+  GruTcParams g = {};
+  LstmTcParams& p = g.base;
+  p.dy = dy; p.dhT = dhT; p.gates = const_cast<void*>(gates); p.y = const_cast<void*>(y); p.dgates = dgh; p.dh0 = dh0;
+  p.bar = (unsigned int*)bar;
+  p.T = T; p.B = B; p.H = H; p.Bp = pl.Bp; p.Hp = pl.Hp; p.Hc = pl.Hc; p.KK = pl.KK; p.stages = pl.stages_c;
+  p.yalign = tc_row_align(H, pl.esz);
+  g.hnb = (float*)const_cast<void*>(hnb); g.dgx = dgx; g.h0 = h0;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == kF32) return gru_backward<float, float, 8>(pl, md, mw, g, st);
+  if (dtype == kF16) return gru_backward<__half, __half, 16>(pl, md, mw, g, st);
+  return gru_backward<__nv_bfloat16, __nv_bfloat16, 16>(pl, md, mw, g, st);
+}

@@ -14,10 +14,13 @@ def supported(data, state_size, num_layers, mode='lstm'):
         return False
     if mode == 'lstm' and tc_supported(data.dtype, int(data.shape[1]), int(state_size)):
         return True
+    if mode == 'gru' and gru_tc_supported(data.dtype, int(data.shape[1]), int(state_size)):
+        return True
     return bool(lib().mxb_lstm_supported(int(data.shape[1]), int(state_size)))
 
 
 _tuned = {}
+_gru_ok = {}          # (dtype, batch, hidden size, device) -> the tensor-core GRU kernels fit the device
 _tuned_us = {}        # configuration -> (in-tree, library) microseconds measured by the autotuner on this rank
 
 
@@ -294,6 +297,132 @@ class _LSTMLayerTC(torch.autograd.Function):
         return dx, dw_ih, dw_hh, db.to(ctx.bias_dtypes[0]), db.to(ctx.bias_dtypes[1]), dh0, dc0, None
 
 
+# ---- GRU on the tensor cores (gru_tc.inl) ---------------------------------------------------------------------------------
+def gru_tc_supported(dtype, B, H):
+    """Whether the tensor-core GRU recurrence takes this (dtype, batch, hidden size); layers under 32 units stay on the exact
+    fp32-pipe kernels, like the LSTM."""
+    from ... import env
+    if not env.get('MXNET_B200_RNN_TC') or dtype not in (torch.float32, torch.float16, torch.bfloat16) or int(H) < 32:
+        return False
+    code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dtype]
+    key = (code, int(B), int(H), torch.cuda.current_device())
+    hit = _gru_ok.get(key)
+    if hit is None:
+        hit = _gru_ok[key] = bool(lib().mxb_gru_tc_supported(code, int(B), int(H)))
+    return hit
+
+
+def _gru_dims(x, B, H):
+    import ctypes
+    out = (ctypes.c_int32 * 8)()
+    check(lib().mxb_gru_tc_dims(dt(x), int(B), int(H), out), 'gru_tc_dims')
+    return tuple(int(v) for v in out[:7])             # U, Bp, Hp, C, Hc, KK, NGP
+
+
+def _gru_perm_rows(w, dims):
+    """Rows of a [3H, X] gate-major matrix (or a [3H] vector) regrouped per CTA and padded: row c*NGP + g*U + u = row
+    g*H + c*U + u; rows of padded units and the NGP - 3U filler rows of every CTA are zero.  Result [KK, X]."""
+    U, _Bp, _Hp, C, Hc, KK, NGP = dims
+    H = w.shape[0] // 3
+    tail = tuple(w.shape[1:])
+    g = w.new_zeros((3, Hc) + tail)
+    g[:, :H] = w.reshape((3, H) + tail)
+    lead = [i + 3 for i in range(len(tail))]
+    per_cta = g.reshape((3, C, U) + tail).permute(1, 0, 2, *lead).reshape((C, 3 * U) + tail)
+    out = w.new_zeros((C, NGP) + tail)
+    out[:, :3 * U] = per_cta
+    return out.reshape((KK,) + tail)
+
+
+def _gru_unperm_rows(w, dims, H):
+    U, _Bp, _Hp, C, Hc, _KK, NGP = dims
+    tail = tuple(w.shape[1:])
+    lead = [i + 3 for i in range(len(tail))]
+    g = w.reshape((C, NGP) + tail)[:, :3 * U].reshape((C, 3, U) + tail).permute(1, 0, 2, *lead).reshape((3, Hc) + tail)
+    return g[:, :H].reshape((3 * H,) + tail)
+
+
+class _GRULayerTC(torch.autograd.Function):
+    """y, hT = gru(x[T,B,I], w_ih[3H,I], w_hh[3H,H], b_ih[3H], b_hh[3H], h0[B,H]) with the recurrence on the tensor cores."""
+
+    @staticmethod
+    def forward(ctx, x, w_ih, w_hh, b_ih, b_hh, h0, training):
+        L = lib()
+        T, B, I = x.shape
+        H = w_hh.shape[1]
+        x = x.contiguous()
+        w_ih, w_hh, h0 = w_ih.contiguous(), w_hh.contiguous(), h0.contiguous()
+        for t, name, shape in ((w_ih, 'w_ih', (3 * H, I)), (w_hh, 'w_hh', (3 * H, H)), (h0, 'h0', (B, H))):
+            require(t, name, dtype=x.dtype, device=x.device, shape=shape)
+        dims = _gru_dims(x, B, H)
+        _U, Bp, Hp, _C, Hc, KK, _NGP = dims
+        bias = b_ih.float() + b_hh.float()
+        bias[2 * H:] = b_ih.float()[2 * H:]                  # the candidate gate's hidden-side bias stays inside r * (...)
+        bias = _gru_perm_rows(bias.to(x.dtype), dims)
+        bhn = torch.zeros(Hc, dtype=torch.float32, device=x.device)
+        bhn[:H] = b_hh.float()[2 * H:]
+        wi = _gru_perm_rows(w_ih, dims)                      # [KK, I]
+        x2 = x.reshape(T * B, I)
+        from . import gemm_ops
+        if x.dtype in (torch.float16, torch.bfloat16) and gemm_ops.operand_ok(x2) and gemm_ops.operand_ok(wi):
+            xproj = gemm_ops.gemm(x2, wi, False, False, bias)
+        else:
+            with _tf32_products():
+                xproj = torch.addmm(bias, x2, wi.t())
+        wp = _gru_perm_rows(w_hh, dims)
+        if Hp != H:
+            wp = torch.nn.functional.pad(wp, (0, Hp - H))
+        y = torch.empty(T, B, H, dtype=x.dtype, device=x.device)
+        hT = torch.empty_like(h0)
+        gates = torch.empty(T, B, KK, dtype=x.dtype, device=x.device) if training else None
+        hnb = torch.empty(T, B, Hc, dtype=torch.float32, device=x.device) if training else None
+        hbuf = torch.zeros(2, Bp, Hp, dtype=x.dtype, device=x.device)
+        bar = _barrier_words(x.device)
+        check(L.mxb_gru_tc_forward(dt(x), ptr(xproj), ptr(wp), ptr(bhn), ptr(h0), ptr(y), ptr(hT), ptr(gates), ptr(hnb), ptr(hbuf),
+                                   ptr(bar), T, B, H, stream_ptr(x.device)), 'gru_tc_forward')
+        count_launch(1)
+        ctx.save_for_backward(x, wi, w_hh, h0, y, gates, hnb)
+        ctx.bias_dtypes = (b_ih.dtype, b_hh.dtype)
+        ctx.dims = dims
+        ctx.fwd_bar = bar
+        ctx.set_materialize_grads(False)
+        return y, hT
+
+    @staticmethod
+    def backward(ctx, dy, dhT):
+        x, wi, w_hh, h0, y, gates, hnb = ctx.saved_tensors
+        if gates is None:
+            raise RuntimeError('GRU backward needs a forward pass in training mode')
+        L = lib()
+        T, B, I = x.shape
+        H = w_hh.shape[1]
+        dims = ctx.dims
+        Hc, KK = dims[4], dims[5]
+        dy = torch.zeros_like(y) if dy is None else dy.contiguous()
+        require(dy, 'out_grad', dtype=x.dtype, device=x.device, shape=y.shape)
+        dhT = dhT.contiguous() if dhT is not None else None
+        wb = _gru_perm_rows(w_hh, dims)                      # [KK, H]
+        if Hc != H:
+            wb = torch.nn.functional.pad(wb, (0, Hc - H))
+        wb = wb.t().contiguous()                             # [Hc, KK]
+        dgh = torch.empty(T, B, KK, dtype=x.dtype, device=x.device)
+        dgx = torch.empty(T, B, KK, dtype=x.dtype, device=x.device)
+        dh0 = torch.empty_like(h0)
+        bar = _barrier_words(x.device)
+        check(L.mxb_gru_tc_backward(dt(x), ptr(dy), ptr(dhT), ptr(gates), ptr(hnb), ptr(y), ptr(h0), ptr(wb), ptr(dgh), ptr(dgx),
+                                    ptr(dh0), ptr(bar), T, B, H, stream_ptr(x.device)), 'gru_tc_backward')
+        count_launch(1)
+        ctx.bwd_bar = bar
+        gh2, gx2 = dgh.view(T * B, KK), dgx.view(T * B, KK)
+        hprev = torch.cat([h0.unsqueeze(0), y[:-1]], 0).reshape(T * B, H)
+        dx = _mm(gx2, wi, False, True, True).reshape(T, B, I) if ctx.needs_input_grad[0] else None
+        dw_ih = _gru_unperm_rows(_mm(gx2, x.reshape(T * B, I), True, True, True), dims, H)
+        dw_hh = _gru_unperm_rows(_mm(gh2, hprev, True, True, True), dims, H)
+        db_ih = _gru_unperm_rows(gx2.sum(0, dtype=torch.float32), dims, H)
+        db_hh = _gru_unperm_rows(gh2.sum(0, dtype=torch.float32), dims, H)
+        return dx, dw_ih, dw_hh, db_ih.to(ctx.bias_dtypes[0]), db_hh.to(ctx.bias_dtypes[1]), dh0, None
+
+
 def check_errors(bar):
     """Raise when a grid barrier of the recurrence timed out (outputs incomplete)."""
     if int(bar[1].item()) != 0:
@@ -396,7 +525,11 @@ def recurrent(mode, data, parameters, state, state_size, num_layers, p, training
         for di in range(d):
             w_ih, w_hh, _w_hr, b_ih, b_hh = layers[l * d + di]
             xin = x if di == 0 else x.flip(0)
-            y, h = _RecurrentLayer.apply(xin.contiguous(), w_ih, w_hh, b_ih, b_hh, state[l * d + di], _MODES[mode], bool(training))
+            if mode == 'gru' and gru_tc_supported(xin.dtype, N, state_size):
+                y, h = _GRULayerTC.apply(xin.contiguous(), w_ih, w_hh, b_ih, b_hh, state[l * d + di], bool(training))
+            else:
+                y, h = _RecurrentLayer.apply(xin.contiguous(), w_ih, w_hh, b_ih, b_hh, state[l * d + di], _MODES[mode],
+                                             bool(training))
             outs.append(y if di == 0 else y.flip(0))
             hs.append(h)
         x = outs[0] if d == 1 else torch.cat(outs, -1)

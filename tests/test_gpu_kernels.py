@@ -761,10 +761,17 @@ def test_fused_lstm_bidirectional(T, B, I, H, layers):
 @pytest.mark.parametrize('mode', ['gru', 'rnn_tanh', 'rnn_relu'])
 @pytest.mark.parametrize('T,B,I,H,layers,bidir', [(6, 4, 24, 40, 2, False), (5, 3, 16, 16, 1, True), (12, 33, 64, 300, 1, False)])
 @pytest.mark.parametrize('dtype', [torch.float32, torch.float16])
-def test_gru_and_vanilla_rnn_kernels(mode, T, B, I, H, layers, bidir, dtype):
-    """The GRU / vanilla RNN recurrence kernels against an exact fp32 module on the host with the same parameters."""
+@pytest.mark.parametrize('tc', [True, False])
+def test_gru_and_vanilla_rnn_kernels(mode, T, B, I, H, layers, bidir, dtype, tc, monkeypatch):
+    """The GRU / vanilla RNN recurrence kernels against an exact fp32 module on the host with the same parameters.  tc=True:
+    the GRU recurrence of layers with 32 units or more runs on the tensor cores (gru_tc.inl); tc=False: fp32-pipe kernels."""
     from mxnet_b200.ops.cuda import rnn_ops
     from mxnet_b200.ops.nn import rnn_param_size
+    if tc and mode != 'gru':
+        pytest.skip('only the LSTM and the GRU have a tensor-core recurrence')
+    monkeypatch.setenv('MXNET_B200_RNN_TC', '1' if tc else '0')
+    assert rnn_ops.gru_tc_supported(dtype, B, H) == bool(tc and H >= 32)
+    on_tc = tc and H >= 32
     torch.manual_seed(13)
     if mode == 'gru':
         ref = torch.nn.GRU(I, H, layers, bidirectional=bidir).float()
@@ -791,6 +798,8 @@ def test_gru_and_vanilla_rnn_kernels(mode, T, B, I, H, layers, bidir, dtype):
     yr, hTr = ref(xr, hr)
     torch.autograd.backward([yr, hTr], [gy.float().cpu(), gh.float().cpu()])
     tol = (1e-3, 1e-3) if dtype == torch.float32 else (3e-2, 3e-2)
+    if on_tc and dtype == torch.float32:
+        tol = (6e-3, 6e-3)                  # tf32 operands: 10 mantissa bits in the recurrent product
     _close(y, yr, *tol)
     _close(hT, hTr, *tol)
     scale = max(1.0, float(xr.grad.abs().max()))
