@@ -105,8 +105,8 @@ def case_maxpool(ctx, dtype, small):
     return dict(inputs=[x], fn=fn, fwd_bytes=nb * 1.25 + nb / 8, bwd_bytes=nb * 1.25 + nb / 8)
 
 
-def case_attention(ctx, dtype, small, dropout=0.0):
-    n, t, heads = (16, 128, 12) if small else (64, 128, 12)
+def case_attention(ctx, dtype, small, dropout=0.0, t=128, heads=12):
+    n = max(1, (16 if small else 64) * 128 // t)            # the same number of tokens at every sequence length
     c = heads * 64
     qkv = _rand((n, t, 3 * c), ctx, dtype, 0.5)
     fl = 4.0 * n * heads * t * t * 64            # QKt and PV
@@ -200,6 +200,8 @@ CASES = {
     'LayerNorm': case_layernorm,
     'MaxPool3x3s2': case_maxpool,
     'fused_self_attention': case_attention,
+    'fused_self_attention_t256': lambda c, d, s: case_attention(c, d, s, t=256),
+    'fused_self_attention_t512': lambda c, d, s: case_attention(c, d, s, t=512, heads=16),
     'elemwise_add': case_add,
     'GELU': case_gelu,
     'dropout_add': case_dropout_add,

@@ -431,6 +431,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   }
 }
 
+#include "attention_long.inl"
+
 // 3-D tensor map over a packed [N, T, W] half tensor: box = 64 columns x 128 rows x 1 sample, 128-byte swizzle;
 // rows beyond T are filled with zeros.
 static int make_map_ntc(CUtensorMap* map, const void* base, int bf16, int64_t N, int64_t T, int64_t W) {
@@ -447,14 +449,21 @@ static int make_map_ntc(CUtensorMap* map, const void* base, int bf16, int64_t N,
 }
 
 static bool attn_shape_ok(int N, int T, int C, int heads) {
-  return N >= 1 && T >= 1 && T <= kAttT && heads >= 1 && C == heads * kAttD;
+  return N >= 1 && T >= 1 && T <= kAttLongMaxT && heads >= 1 && C == heads * kAttD;
 }
 
 }  // namespace mxb
 
 using namespace mxb;
 
+// 1 when the fused kernels take the shape: head size 64, T up to 1024 (one tile up to 128, the streaming kernels beyond).
 MXB_EXPORT int mxb_attn_supported(int T, int C, int heads) { return attn_shape_ok(1, T, C, heads) ? 1 : 0; }
+
+// Number of fp32 elements of the dQ workspace the backward call needs (0 for T <= 128).
+MXB_EXPORT long long mxb_attn_backward_workspace(int N, int T, int C) {
+  if (T <= kAttT) return 0;
+  return (long long)((T + kAttT - 1) / kAttT) * N * T * C;
+}
 
 // qkv: [N, T, 3C] (fp16 / bf16), mask: [N, T] float or null, out: [N, T, C], lse: [N, heads, T] floats.
 // dropout: probability of dropping an attention weight (0 = none); `seed`: device word that selects the pattern.
@@ -479,14 +488,27 @@ MXB_EXPORT int mxb_attn_forward(int dtype, const void* qkv, const float* mask, v
     cudaFuncSetAttribute(attn_fwd_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
     cudaFuncSetAttribute(attn_fwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
   }
+  if (T > kAttT) {
+    static unsigned long long long_seen = 0;
+    if (first_on_device(&long_seen)) {
+      cudaFuncSetAttribute(attn_fwd_long_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdLongSmem);
+      cudaFuncSetAttribute(attn_fwd_long_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdLongSmem);
+    }
+    const int64_t grid = (int64_t)N * heads * ((T + kAttT - 1) / kAttT);
+    if (grid > 0x7fffffff) return -2;
+    if (bf16) attn_fwd_long_kernel<__nv_bfloat16><<<(unsigned)grid, kAttThreads, kFwdLongSmem, st>>>(map, p, 1);
+    else attn_fwd_long_kernel<__half><<<(unsigned)grid, kAttThreads, kFwdLongSmem, st>>>(map, p, 0);
+    return (int)cudaGetLastError();
+  }
   if (bf16) attn_fwd_kernel<__nv_bfloat16><<<N * heads, kAttThreads, kFwdSmem, st>>>(map, p, 1);
   else attn_fwd_kernel<__half><<<N * heads, kAttThreads, kFwdSmem, st>>>(map, p, 0);
   return (int)cudaGetLastError();
 }
 
 // dqkv: [N, T, 3C] receives dQ | dK | dV.  o, dout: [N, T, C]; lse from the forward call; same dropout and seed.
+// `workspace`: mxb_attn_backward_workspace(N, T, C) floats (may be null when that is 0).
 MXB_EXPORT int mxb_attn_backward(int dtype, const void* qkv, const float* mask, const void* o, const void* dout,
-                                 const float* lse, void* dqkv, int N, int T, int C, int heads, float dropout,
+                                 const float* lse, void* dqkv, float* workspace, int N, int T, int C, int heads, float dropout,
                                  const uint32_t* seed, int* error_flag, void* stream) {
   if (dtype != kF16 && dtype != kBF16) return -1;
   if (!attn_shape_ok(N, T, C, heads) || dropout < 0.f || dropout >= 1.f || (dropout > 0.f && !seed)) return -2;
@@ -509,6 +531,26 @@ MXB_EXPORT int mxb_attn_backward(int dtype, const void* qkv, const float* mask, 
   if (first_on_device(&attr_seen)) {
     cudaFuncSetAttribute(attn_bwd_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
     cudaFuncSetAttribute(attn_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
+  }
+  if (T > kAttT) {
+    if (!workspace || ((uintptr_t)workspace % 16)) return -3;
+    static unsigned long long long_seen = 0;
+    if (first_on_device(&long_seen)) {
+      cudaFuncSetAttribute(attn_bwd_long_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdLongSmem);
+      cudaFuncSetAttribute(attn_bwd_long_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdLongSmem);
+    }
+    const int nblk = (T + kAttT - 1) / kAttT;
+    const int64_t grid = (int64_t)N * heads * nblk;
+    if (grid > 0x7fffffff) return -2;
+    if (bf16) attn_bwd_long_kernel<__nv_bfloat16><<<(unsigned)grid, kAttThreads, kBwdLongSmem, st>>>(map, map_do, p, workspace, 1);
+    else attn_bwd_long_kernel<__half><<<(unsigned)grid, kAttThreads, kBwdLongSmem, st>>>(map, map_do, p, workspace, 0);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    const int64_t rows = (int64_t)N * T, vecs = rows * (C / 8);
+    const int fgrid = (int)((vecs + 255) / 256 < 148 * 16 ? (vecs + 255) / 256 : 148 * 16);
+    if (bf16) attn_dq_finish_kernel<__nv_bfloat16><<<fgrid, 256, 0, st>>>(workspace, static_cast<__nv_bfloat16*>(dqkv), nblk, rows, C);
+    else attn_dq_finish_kernel<__half><<<fgrid, 256, 0, st>>>(workspace, static_cast<__half*>(dqkv), nblk, rows, C);
+    return (int)cudaGetLastError();
   }
   if (bf16) attn_bwd_kernel<__nv_bfloat16><<<N * heads, kAttThreads, kBwdSmem, st>>>(map, map_do, p, 1);
   else attn_bwd_kernel<__half><<<N * heads, kAttThreads, kBwdSmem, st>>>(map, map_do, p, 0);

@@ -63,10 +63,12 @@ class _SelfAttention(torch.autograd.Function):
         N, T, C3 = qkv.shape
         dout = require(dout.contiguous(), 'out_grad', dtype=qkv.dtype, device=qkv.device, shape=out.shape)
         dqkv = torch.empty_like(qkv)
-        check(lib().mxb_attn_backward(dt(qkv), ptr(qkv), ptr(m), ptr(out), ptr(dout), ptr(lse), ptr(dqkv), N, T, C3 // 3,
+        words = int(lib().mxb_attn_backward_workspace(N, T, C3 // 3))       # per-key-block dQ slots of the streaming kernels
+        work = torch.empty(words, dtype=torch.float32, device=qkv.device) if words else None
+        check(lib().mxb_attn_backward(dt(qkv), ptr(qkv), ptr(m), ptr(out), ptr(dout), ptr(lse), ptr(dqkv), ptr(work), N, T, C3 // 3,
                                       ctx.heads, ctx.dropout, ptr(seed), ptr(_error_flag(qkv.device)),
                                       stream_ptr(qkv.device)), 'attn_backward')
-        count_launch(1)
+        count_launch(2 if words else 1)
         return dqkv, None, None, None
 
 

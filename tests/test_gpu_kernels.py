@@ -580,7 +580,8 @@ def _attention_reference(qkv, mask, heads):
     return (torch.softmax(s, -1) @ v).permute(0, 2, 1, 3).reshape(N, T, C)
 
 
-@pytest.mark.parametrize('N,T,heads', [(2, 128, 2), (3, 100, 12), (1, 17, 1), (5, 128, 4)])
+@pytest.mark.parametrize('N,T,heads', [(2, 128, 2), (3, 100, 12), (1, 17, 1), (5, 128, 4),
+                                       (2, 256, 2), (1, 200, 3), (2, 384, 1), (2, 512, 4), (1, 129, 1), (1, 1000, 2)])   # T > 128: streaming kernels
 @pytest.mark.parametrize('use_mask', [False, True])
 @pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
 def test_fused_self_attention_matches_reference(N, T, heads, use_mask, dtype):
@@ -605,10 +606,11 @@ def test_fused_self_attention_matches_reference(N, T, heads, use_mask, dtype):
     _close(qkv.grad, ref_in.grad, tol[0] * 2, tol[1] * 2)
 
 
-def test_fused_self_attention_dropout_is_unbiased_and_consistent():
+@pytest.mark.parametrize('T', [128, 320])
+def test_fused_self_attention_dropout_is_unbiased_and_consistent(T):
     from mxnet_b200.ops.cuda import attn_ops
     torch.manual_seed(13)
-    N, T, heads, C = 4, 128, 4, 256
+    N, heads, C = 4, 4, 256
     qkv = torch.zeros(N, T, 3 * C, device=_dev(), dtype=torch.float16)
     qkv[:, :, 2 * C:] = 1.0                                   # V = 1, Q = K = 0: out = sum of kept weights / (1 - p)
     out = attn_ops.fused_self_attention(qkv, None, heads, 0.5)
