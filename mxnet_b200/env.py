@@ -153,7 +153,7 @@ declare('MXNET_B200_RNN', str, 'auto', 'RNN operator on the in-tree recurrence k
 declare('MXNET_B200_RNN_TC', bool, True, 'LSTM recurrence of the in-tree path on the tensor-core kernels (tcgen05; tf32 products for fp32 models, as the library recurrence uses) for layers of 32 units or more where the shape allows; 0 = the fp32-pipe recurrence kernels (exact fp32 products)')
 declare('MXNET_USE_FUSION', bool, True, 'pointwise fusion')
 declare('MXNET_ELIMINATE_COMMON_EXPR', bool, True, 'common-subexpression elimination on symbols')
-declare('MXNET_MEMORY_OPT', bool, False, 'recompute cheap activations in backward')
+declare('MXNET_MEMORY_OPT', bool, False, 'backward mirroring in graph executors and hybridized blocks: runs of cheap stateless operators keep only their inputs and are recomputed in backward')
 declare('MXNET_BACKWARD_DO_MIRROR', bool, False, 'legacy spelling of MXNET_MEMORY_OPT')
 declare('MXNET_SUBGRAPH_BACKEND', str, '', 'default subgraph backend')
 # ---- profiler / misc ----------------------------------------------------------------------

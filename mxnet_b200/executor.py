@@ -46,6 +46,12 @@ class Executor(object):
         return self._stats['copies']
 
     @property
+    def mirrored_nodes(self):
+        """Operators of the last training forward pass whose results are recomputed in backward (backward mirroring:
+        ``MXNET_BACKWARD_DO_MIRROR`` / ``MXNET_MEMORY_OPT`` or the ``force_mirroring`` attribute)."""
+        return self._stats.get('mirrored_nodes', 0)
+
+    @property
     def output_dict(self):
         return dict(zip(self._symbol.list_outputs(), self.outputs))
 

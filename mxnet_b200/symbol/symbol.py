@@ -115,6 +115,41 @@ def _parse_attr(s):
         return s
 
 
+# Operators the backward-mirroring pass never recomputes: the contraction-heavy ones (recomputing them costs what the pass
+# is meant to save), the ones with running state, and the sources of randomness.
+_NO_MIRROR = frozenset(['Convolution', 'Deconvolution', 'FullyConnected', 'Concat', 'SoftmaxOutput', 'BatchNorm', 'SyncBatchNorm',
+                        '_contrib_SyncBatchNorm', 'Dropout', 'RNN', 'Custom', 'dot', 'batch_dot', 'Embedding', '_FusedOp',
+                        '_contrib_fused_self_attention', '_contrib_interleaved_matmul_selfatt_qk',
+                        '_contrib_interleaved_matmul_selfatt_valatt', '_contrib_interleaved_matmul_encdec_qk',
+                        '_contrib_interleaved_matmul_encdec_valatt', '_npi_matmul', '_npi_dot', '_npi_tensordot', '_npi_einsum',
+                        '_foreach', '_while_loop', '_cond', 'CTCLoss', 'Correlation', '_contrib_DeformableConvolution'])
+
+
+def _forced_mirror(node):
+    v = node.user_attrs.get('force_mirroring', node.user_attrs.get('__force_mirroring__')) if node.op is not None else None
+    return v is not None and str(v).lower() in ('1', 'true')
+
+
+def _mirrorable(node, everything):
+    """The reference's mirror predicate: with the switch on, every operator outside the exclusion list; without it, the
+    operators marked ``force_mirroring``.  Operators with auxiliary or in-place inputs and random ones never qualify."""
+    op = node.op
+    if op.aux or op.mutate or op.name in _NO_MIRROR:
+        return False
+    low = op.name.lower()
+    if 'random' in low or 'sample' in low or 'shuffle' in low or 'dropout' in low:
+        return False
+    return everything or _forced_mirror(node)
+
+
+def _apply_node(node, ins):
+    hook = _state.amp_hook
+    if hook is not None and not _state.state.opt_constraints & 1:
+        ins = hook(node.op.name, ins)
+    res = node.op.fn(*ins, **node.attrs)
+    return tuple(res) if isinstance(res, (tuple, list)) else (res,)
+
+
 def _topo(outputs):
     order, seen = [], set()
     stack = [(n, False) for n, _ in reversed(outputs)]
@@ -403,6 +438,9 @@ class Symbol(object):
                 fused = fuse_pointwise(self)
                 self._fused = fused if fused is not self else False
             graph = self._fused or self
+        if torch.is_grad_enabled() and (_env.get('MXNET_MEMORY_OPT') or _env.get('MXNET_BACKWARD_DO_MIRROR') or
+                                        any(_forced_mirror(n) for n in _topo(graph._outputs))):
+            return graph._run_mirrored(feed, stats)
         values = {}
         for node in _topo(graph._outputs):
             if node.op is None:
@@ -411,14 +449,78 @@ class Symbol(object):
                 values[id(node)] = (feed[node.name],)
                 continue
             ins = [values[id(i)][k] for i, k in node.inputs]
-            if not node.op.variadic and len(ins) < len(node.op.inputs):
-                ins = ins + [None] * 0
-            hook = _state.amp_hook
-            if hook is not None and not _state.state.opt_constraints & 1:
-                ins = hook(node.op.name, ins)
-            res = node.op.fn(*ins, **node.attrs)
-            values[id(node)] = tuple(res) if isinstance(res, (tuple, list)) else (res,)
+            values[id(node)] = _apply_node(node, ins)
         return [values[id(n)][k] for n, k in graph._outputs]
+
+    def _run_mirrored(self, feed, stats=None):
+        """Evaluate the graph with backward mirroring (reference: src/nnvm/gradient.cc, the gradient pass with a
+        ``mirror_fun``; switches ``MXNET_BACKWARD_DO_MIRROR`` / ``MXNET_MEMORY_OPT`` and the node attribute
+        ``force_mirroring``).  Maximal runs of consecutive mirrorable operators (cheap, stateless, deterministic: everything
+        except convolutions, dense products, normalisation with running statistics, random and in-place operators) keep
+        only their inputs: their intermediate results are dropped after the forward pass and recomputed when the backward
+        pass reaches the run.  ``stats['mirrored_nodes']`` / ``stats['mirror_segments']`` report what was mirrored."""
+        from torch.utils.checkpoint import checkpoint
+        order = _topo(self._outputs)
+        everything = bool(_env.get('MXNET_MEMORY_OPT') or _env.get('MXNET_BACKWARD_DO_MIRROR'))
+        needed_later = {}                               # id(node) -> position of its last consumer (graph outputs: infinity)
+        for pos, node in enumerate(order):
+            for inp, _ in node.inputs:
+                needed_later[id(inp)] = pos
+        for n, _ in self._outputs:
+            needed_later[id(n)] = len(order)
+        values = {}
+        mirrored = segments = 0
+        pos = 0
+        while pos < len(order):
+            node = order[pos]
+            if node.op is None:
+                if node.name not in feed:
+                    raise MXNetError('missing input %s' % node.name)
+                values[id(node)] = (feed[node.name],)
+                pos += 1
+                continue
+            end = pos
+            while end < len(order) and order[end].op is not None and _mirrorable(order[end], everything):
+                end += 1
+            if end - pos < 2:                           # a run of one operator has nothing to drop
+                ins = [values[id(i)][k] for i, k in node.inputs]
+                values[id(node)] = _apply_node(node, ins)
+                pos += 1
+                continue
+            seg = order[pos:end]
+            inside = {id(n) for n in seg}
+            ext, ext_index = [], {}
+            for n in seg:
+                for inp, k in n.inputs:
+                    if id(inp) not in inside and (id(inp), k) not in ext_index:
+                        ext_index[(id(inp), k)] = len(ext)
+                        ext.append(values[id(inp)][k])
+            exported = [n for n in seg if needed_later.get(id(n), -1) >= end]
+
+            counts = []
+
+            def run_segment(*tensors, seg=seg, inside=inside, ext_index=ext_index, exported=exported, counts=counts):
+                local = {}
+                for n in seg:
+                    ins = [local[id(i)][k] if id(i) in inside else tensors[ext_index[(id(i), k)]] for i, k in n.inputs]
+                    local[id(n)] = _apply_node(n, ins)
+                counts[:] = [len(local[id(n)]) for n in exported]
+                return tuple(t for n in exported for t in local[id(n)])
+            if any(isinstance(t, torch.Tensor) and t.requires_grad for t in ext):
+                flat = checkpoint(run_segment, *ext, use_reentrant=False, preserve_rng_state=False)
+                mirrored += len(seg)
+                segments += 1
+            else:
+                flat = run_segment(*ext)
+            at = 0
+            for n, cnt in zip(exported, counts):
+                values[id(n)] = tuple(flat[at:at + cnt])
+                at += cnt
+            pos = end
+        if stats is not None:
+            stats['mirrored_nodes'] = mirrored
+            stats['mirror_segments'] = segments
+        return [values[id(n)][k] for n, k in self._outputs]
 
     def _run_placed(self, feed, placement, stats=None):
         values = {}

@@ -259,3 +259,68 @@ def test_group2ctx_places_operators_and_arguments():
     plain.backward(nd.ones(b.shape, ctx=b.context))
     for k in shapes:
         np.testing.assert_allclose(placed.grad_dict[k].asnumpy(), plain.grad_dict[k].asnumpy(), rtol=1e-5, atol=1e-6)
+
+
+def _mirror_net():
+    data = mx.sym.Variable('data')
+    x = mx.sym.Convolution(data, num_filter=4, kernel=(3, 3), pad=(1, 1), name='c1')
+    x = mx.sym.Activation(x, act_type='relu')
+    x = x * 2.0 + 1.0
+    x = mx.sym.tanh(x)
+    x = mx.sym.Pooling(x, kernel=(2, 2), stride=(2, 2), pool_type='max')
+    x = mx.sym.Convolution(x, num_filter=3, kernel=(1, 1), name='c2')
+    x = mx.sym.sigmoid(x)
+    x = mx.sym.Flatten(x)
+    x = mx.sym.FullyConnected(x, num_hidden=5, name='fc')
+    return mx.sym.sum(mx.sym.square(x))
+
+
+def _mirror_grads(flag, monkeypatch):
+    for name in ('MXNET_BACKWARD_DO_MIRROR', 'MXNET_MEMORY_OPT'):
+        monkeypatch.delenv(name, raising=False)
+    if flag:
+        monkeypatch.setenv(flag, '1')
+    net = _mirror_net()
+    ex = net.simple_bind(mx.cpu(), data=(2, 3, 8, 8))
+    rng = np.random.RandomState(0)
+    for name, arr in ex.arg_dict.items():
+        arr[:] = rng.uniform(-0.5, 0.5, arr.shape).astype('float32')
+    out = ex.forward(is_train=True)[0].asnumpy()
+    ex.backward()
+    return out, {k: v.asnumpy() for k, v in ex.grad_dict.items() if v is not None}, ex.mirrored_nodes
+
+
+@pytest.mark.parametrize('flag', ['MXNET_BACKWARD_DO_MIRROR', 'MXNET_MEMORY_OPT'])
+def test_backward_mirroring_recomputes_cheap_runs_and_keeps_gradients(flag, monkeypatch):
+    """Backward mirroring (reference: src/nnvm/gradient.cc with a mirror function; docs env_var MXNET_BACKWARD_DO_MIRROR):
+    runs of cheap operators between the convolutions are recomputed in backward; outputs and gradients are unchanged."""
+    out0, g0, m0 = _mirror_grads(None, monkeypatch)
+    out1, g1, m1 = _mirror_grads(flag, monkeypatch)
+    assert m0 == 0
+    assert m1 == 9          # three runs: relu, *2, +1, tanh, pooling | sigmoid, flatten | square, sum
+    np.testing.assert_array_equal(out0, out1)
+    assert set(g0) == set(g1)
+    for k in g0:
+        np.testing.assert_allclose(g0[k], g1[k], rtol=1e-6, atol=1e-7)
+
+
+def test_force_mirroring_attribute_marks_single_operators(monkeypatch):
+    for name in ('MXNET_BACKWARD_DO_MIRROR', 'MXNET_MEMORY_OPT'):
+        monkeypatch.delenv(name, raising=False)
+    data = mx.sym.Variable('data')
+    with mx.AttrScope(force_mirroring='True'):
+        x = mx.sym.tanh(data * 3.0)
+        x = mx.sym.sigmoid(x)
+    y = mx.sym.sum(mx.sym.FullyConnected(x, num_hidden=2, name='fc'))
+    ex = y.simple_bind(mx.cpu(), data=(4, 6))
+    for name, arr in ex.arg_dict.items():
+        arr[:] = np.random.RandomState(1).uniform(-1, 1, arr.shape).astype('float32')
+    ex.forward(is_train=True)
+    ex.backward()
+    assert ex.mirrored_nodes == 3
+    d = ex.arg_dict['data'].asnumpy()
+    w = ex.arg_dict['fc_weight'].asnumpy()
+    t = np.tanh(3 * d)
+    s = 1 / (1 + np.exp(-t))
+    expect = (w.sum(0)[None, :] * s * (1 - s)) * (1 - t * t) * 3
+    np.testing.assert_allclose(ex.grad_dict['data'].asnumpy(), expect, rtol=1e-5, atol=1e-6)
