@@ -76,6 +76,9 @@ def init(target_dtype='float16', target_precision_ops=None, conditional_fp32_ops
     _sets = (_expand(lp), _expand(f32), _expand(lists.WIDEST_TYPE_CASTS))
     _state.amp_hook = _hook
     _amp_initialized = True
+    if layout_optimization:
+        from ..symbol.layout import set_optimize_layout
+        set_optimize_layout(True)
 
 
 def _reset():

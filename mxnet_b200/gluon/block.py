@@ -485,17 +485,29 @@ class HybridBlock(Block):
             return out
         if self._backend not in (None, '', 'default'):
             return self._call_partitioned(*args)
+        from ..symbol import layout as _layout
+        if _layout.get_optimize_layout():
+            # layout management is on (amp.init(layout_optimization=True) / set_optimize_layout): run the traced graph after
+            # the pass that moves its convolutional trunk to NHWC (src/imperative/cached_op.h:213 in the reference)
+            return self._call_partitioned(*args, backend='optimize_layout')
         return self._cached_op(*args)
 
-    def _call_partitioned(self, *args):
+    def _call_partitioned(self, *args, backend=None):
         """``hybridize(backend=...)`` / ``optimize_for``: run the traced graph after the backend's graph pass
         (``HybridBlock._build_cache`` with ``MXOptimizeForBackend`` in the reference, ``python/mxnet/gluon/block.py``)."""
         flat, in_format = _flatten(args, 'input')
         if self._cached_graph is None or in_format != self._in_format:
             self._trace(*args)
             self._partitioned = None
+        if backend is not None and getattr(self, '_partitioned_by', None) != backend:
+            self._partitioned = None
         if getattr(self, '_partitioned', None) is None:
-            self._partitioned = self._cached_graph[1].optimize_for(self._backend, **self._backend_opts)
+            if backend is not None:
+                self._partitioned = self._cached_graph[1].optimize_for(backend)
+                self._partitioned_by = backend
+            else:
+                self._partitioned = self._cached_graph[1].optimize_for(self._backend, **self._backend_opts)
+                self._partitioned_by = None
         inputs, _ = self._cached_graph
         arrays = [a for a in flat if isinstance(a, NDArray)]
         ctx = arrays[0]._ctx

@@ -661,6 +661,15 @@ def flatten(data):
     return data.reshape(data.shape[0], -1) if data.dim() > 1 else data.reshape(-1, 1) if data.dim() == 1 else data
 
 
+@register('_layout_transpose', inputs=('data',), defaults={'axes': None})
+def layout_transpose(data, axes=None):
+    """Transpose that materialises its result (dense, in the new axis order): what the layout pass puts at the borders of
+    a channel-last region, where the consumer is a kernel that wants dense channel-last memory."""
+    if axes is None or len(axes) == 0:
+        axes = tuple(range(data.dim()))[::-1]
+    return data.permute(tuple(axes)).contiguous()
+
+
 @register('transpose', '_npi_transpose', inputs=('data',), defaults={'axes': None})
 def transpose(data, axes=None):
     if axes is None or len(axes) == 0:

@@ -19,6 +19,9 @@ def optimize_for(sym, backend, args=None, aux=None, **kwargs):
     if backend == 'pointwise_fusion':
         from .fusion import fuse_pointwise
         return fuse_pointwise(sym)
+    if backend == 'optimize_layout':
+        from .layout import optimize_layout
+        return optimize_layout(sym)
     if backend not in _BACKENDS:
         raise MXNetError('subgraph backend %s is not registered (available: %s)' % (backend, sorted(_BACKENDS)))
     return _BACKENDS[backend](sym, args, aux, **kwargs)

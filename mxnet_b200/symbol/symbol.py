@@ -820,6 +820,7 @@ def _shape_infer_graph(sym, feed, partial=False):
             var_dtypes[id(n)] = dt
     values = {}
     ok = True
+    deferred = []
     with torch.no_grad():
         for n in nodes:
             if n.op is None:
@@ -840,9 +841,26 @@ def _shape_infer_graph(sym, feed, partial=False):
                             if n.op.name in ('Embedding',) or (n.op.name == 'SoftmaxOutput' and pos == 1):
                                 dt = var_dtypes[id(inp)] or torch.float32
                             values[id(inp)] = (torch.empty(tuple(shp), dtype=dt, device='meta'),)
+                        elif inp.op.name in ('_layout_transpose', 'transpose') and inp.attrs.get('axes') and \
+                                inp.inputs[0][0].op is None and values[id(inp.inputs[0][0])][0] is None:
+                            # a parameter that reaches the layer through a transpose (the layout pass puts one on every
+                            # convolution weight): the variable has the inverse permutation of the shape the layer wants
+                            src = inp.inputs[0][0]
+                            axes = tuple(inp.attrs['axes'])
+                            vshape = [0] * len(axes)
+                            for pos_out, ax in enumerate(axes):
+                                vshape[ax] = shp[pos_out]
+                            var_shapes[id(src)] = tuple(vshape)
+                            first = values[id(n.inputs[0][0])][n.inputs[0][1]]
+                            dt = var_dtypes[id(src)] or (first.dtype if first is not None else torch.float32)
+                            values[id(src)] = (torch.empty(tuple(vshape), dtype=dt, device='meta'),)
+                            values[id(inp)] = (values[id(src)][0].permute(axes),)
             ins = [values[id(i)][k] for i, k in n.inputs]
             if any(v is None for v in ins):
-                ok = False
+                if n.op.name in ('_layout_transpose', 'transpose') and n.inputs[0][0].op is None:
+                    deferred.append(n)         # its consumer's rule may still give the variable a shape
+                else:
+                    ok = False
                 values[id(n)] = (None,) * n.nout
                 continue
             try:
@@ -861,6 +879,8 @@ def _shape_infer_graph(sym, feed, partial=False):
                         continue
                     raise MXNetError('Error in operator %s: %s' % (n.name, e))
             values[id(n)] = tuple(res) if isinstance(res, (tuple, list)) else (res,)
+    if any(values[id(n)][0] is None for n in deferred):
+        ok = False
     if not ok and not partial:
         return None
     vars_out = {n.name: var_shapes[id(n)] for n in nodes if n.op is None}

@@ -1013,3 +1013,37 @@ def test_quantized_network_runs_its_dense_layers_on_the_int8_kernel():
     assert int(gemm_ops._error_flag(torch.device('cuda', 0)).item()) == 0
     err = np.abs(out - ref).max() / np.abs(ref).max()
     assert err < 0.05, err
+
+
+# ---------------------------------------------------------------------------------------- layout management
+def test_layout_pass_puts_an_nchw_network_on_the_channel_last_kernels():
+    """A model written in NCHW (the reference's default layout) runs its convolutions on the tcgen05 NHWC kernels once
+    layout management is on (src/common/alm.cc in the reference): same results, in-tree convolution launches."""
+    import mxnet_b200 as mx
+    from mxnet_b200 import env
+    from mxnet_b200.ops import cuda
+    from mxnet_b200.symbol import layout
+    from mxnet_b200.gluon.model_zoo import vision
+    ctx = mx.gpu(0)
+    net = vision.resnet18_v1(classes=10)
+    net.initialize(mx.init.Xavier(), ctx=ctx)
+    net.cast('float16')
+    x = mx.nd.array(np.random.RandomState(6).uniform(-1, 1, (8, 3, 64, 64)).astype('float16'), ctx=ctx, dtype='float16')
+    net.hybridize()
+    net(x)
+    expect = net(x).asnumpy().astype('float32')
+    layout.set_optimize_layout(True)
+    try:
+        with env.scope('MXNET_B200_CONV', '1'):                   # take the in-tree kernels wherever they support the shape
+            before = cuda.launches()
+            got = net(x)
+            assert '_layout_transpose' in net._partitioned.tojson()
+            assert cuda.launches() - before >= 15                 # 20 convolutions; the 7x7 stem may stay with the library
+            np.testing.assert_allclose(got.asnumpy().astype('float32'), expect, rtol=5e-2, atol=5e-2)
+            with mx.autograd.record():
+                loss = net(x).astype('float32').sum()
+            loss.backward()
+            g = net.features[0].weight.grad().asnumpy().astype('float32')
+            assert np.isfinite(g).all() and np.abs(g).sum() > 0
+    finally:
+        layout.set_optimize_layout(False)

@@ -324,3 +324,92 @@ def test_force_mirroring_attribute_marks_single_operators(monkeypatch):
     s = 1 / (1 + np.exp(-t))
     expect = (w.sum(0)[None, :] * s * (1 - s)) * (1 - t * t) * 3
     np.testing.assert_allclose(ex.grad_dict['data'].asnumpy(), expect, rtol=1e-5, atol=1e-6)
+
+
+def _nchw_trunk():
+    data = mx.sym.Variable('data')
+    x = mx.sym.Convolution(data, num_filter=8, kernel=(3, 3), pad=(1, 1), no_bias=True, name='c1')
+    x = mx.sym.BatchNorm(x, fix_gamma=False, name='bn1')
+    x = mx.sym.Activation(x, act_type='relu')
+    skip = x
+    y = mx.sym.Convolution(x, num_filter=8, kernel=(3, 3), pad=(1, 1), name='c2')
+    y = mx.sym.BatchNorm(y, fix_gamma=False, name='bn2')
+    x = mx.sym.relu(y + skip) * 0.5
+    x = mx.sym.Pooling(x, kernel=(2, 2), stride=(2, 2), pool_type='max')
+    a = mx.sym.Convolution(x, num_filter=4, kernel=(1, 1), name='c3a')
+    b = mx.sym.Convolution(x, num_filter=6, kernel=(3, 3), pad=(1, 1), stride=(1, 1), name='c3b')
+    x = mx.sym.Concat(a, b, dim=1)
+    x = mx.sym.Pooling(x, global_pool=True, pool_type='avg', kernel=(1, 1))
+    x = mx.sym.Flatten(x)
+    return mx.sym.FullyConnected(x, num_hidden=3, name='fc')
+
+
+def test_layout_pass_moves_the_convolutional_trunk_to_nhwc():
+    """Automatic layout management (reference: src/common/alm.cc): same outputs, gradients and running statistics, with
+    transposes only at the borders of the trunk."""
+    from mxnet_b200.symbol.layout import optimize_layout
+    net = _nchw_trunk()
+    opt = optimize_layout(net)
+    nodes = json.loads(opt.tojson())['nodes']
+    ops = [n['op'] for n in nodes]
+    # one transpose for the image, one per convolution weight (4), one back to NCHW before Flatten
+    assert ops.count('_layout_transpose') == 6
+    for n in nodes:
+        if n['op'] == 'Convolution':
+            assert n['attrs']['layout'] == 'NHWC'
+        if n['op'] == 'BatchNorm':
+            assert n['attrs']['axis'] == '3'
+        if n['op'] == 'Concat':
+            assert n['attrs']['dim'] == '3'
+        if n['op'] == 'Pooling':
+            assert n['attrs']['layout'] == 'NHWC'
+    assert opt.list_arguments() == net.list_arguments() and opt.list_auxiliary_states() == net.list_auxiliary_states()
+    results = []
+    for graph in (net, opt):
+        ex = graph.simple_bind(mx.cpu(), data=(2, 3, 8, 8))
+        rng = np.random.RandomState(4)
+        for name, arr in ex.arg_dict.items():
+            arr[:] = rng.uniform(-0.5, 0.5, arr.shape).astype('float32')
+        out = ex.forward(is_train=True)[0].asnumpy()
+        ex.backward(mx.nd.ones((2, 3)))
+        results.append((out, {k: v.asnumpy() for k, v in ex.grad_dict.items() if v is not None},
+                        {k: v.asnumpy() for k, v in ex.aux_dict.items()}))
+    (o0, g0, a0), (o1, g1, a1) = results
+    np.testing.assert_allclose(o0, o1, rtol=1e-4, atol=1e-5)
+    for k in g0:
+        np.testing.assert_allclose(g0[k], g1[k], rtol=2e-4, atol=1e-5, err_msg=k)
+    for k in a0:
+        np.testing.assert_allclose(a0[k], a1[k], rtol=1e-5, atol=1e-6, err_msg=k)
+
+
+def test_layout_pass_leaves_graphs_without_convolutions_alone():
+    from mxnet_b200.symbol.layout import optimize_layout
+    x = mx.sym.Variable('x')
+    y = mx.sym.FullyConnected(mx.sym.relu(x), num_hidden=4, name='fc')
+    assert optimize_layout(y) is y
+
+
+def test_hybridized_block_runs_through_the_layout_pass_when_enabled():
+    from mxnet_b200.symbol import layout
+    from mxnet_b200.gluon import nn
+    net = nn.HybridSequential()
+    net.add(nn.Conv2D(6, 3, padding=1), nn.BatchNorm(), nn.Activation('relu'), nn.MaxPool2D(2), nn.Conv2D(4, 1),
+            nn.GlobalAvgPool2D(), nn.Flatten(), nn.Dense(3))
+    net.initialize()
+    x = mx.nd.array(np.random.RandomState(5).uniform(-1, 1, (2, 3, 8, 8)).astype('float32'))
+    expect = net(x).asnumpy()
+    net.hybridize()
+    net(x)
+    assert not layout.get_optimize_layout()
+    layout.set_optimize_layout(True)
+    try:
+        got = net(x)
+        assert net._partitioned_by == 'optimize_layout'
+        assert '_layout_transpose' in net._partitioned.tojson()
+        np.testing.assert_allclose(got.asnumpy(), expect, rtol=1e-4, atol=1e-5)
+        with mx.autograd.record():
+            loss = net(x).sum()
+        loss.backward()
+        assert float(np.abs(net[0].weight.grad().asnumpy()).sum()) > 0
+    finally:
+        layout.set_optimize_layout(False)
