@@ -10,7 +10,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ['norm.cu', 'softmax.cu', 'optim.cu', 'fused_step.cu', 'gemm_tcgen05.cu', 'pool.cu', 'compress.cu', 'elementwise.cu', 'lstm.cu',
-           'attention.cu', 'conv_tcgen05.cu', 'peer_reduce.cu', 'detection.cu', 'gemm_i8.cu', 'lstm_tc.cu', 'image_pipeline.cu']
+           'attention.cu', 'conv_tcgen05.cu', 'peer_reduce.cu', 'detection.cu', 'gemm_i8.cu', 'lstm_tc.cu', 'image_pipeline.cu', 'sparse.cu']
 LIB = os.path.join(HERE, 'libmxb200_kernels.so')
 FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17', '--use_fast_math',
          '-Xcompiler', '-fPIC', '-Xptxas', '-v']

@@ -108,11 +108,54 @@ class Optimizer(object):
             indices, weights, grads, states = [indices], [weights], [grads], [states]
         for w, g in zip(weights, grads):
             assert isinstance(w, NDArray) and isinstance(g, NDArray)
+        lazy = [self._is_lazy(g) for g in grads]
         with torch.no_grad():
+            if any(lazy):
+                for i, w, g, s, is_lazy in zip(indices, weights, grads, states, lazy):
+                    if is_lazy:
+                        self._lazy_rows_step(i, w, g, s)
+                rest = [k for k, is_lazy in enumerate(lazy) if not is_lazy]
+                if not rest:
+                    return
+                indices, weights, grads, states = ([x[k] for k in rest] for x in (indices, weights, grads, states))
             if not self.use_fused_step:
                 self.step(indices, weights, grads, states)
             else:
                 self.fused_step(indices, weights, grads, states)
+
+    def _is_lazy(self, grad):
+        return getattr(self, 'lazy_update', False) and getattr(grad, 'stype', 'default') == 'row_sparse'
+
+    def _lazy_rows_step(self, index, weight, grad, state):
+        """Lazy update with a row-sparse gradient (``lazy_update=True``; ``src/operator/optimizer_op.cc`` SGDUpdateRspImpl,
+        AdamLazyUpdate ...): only the rows present in the gradient are touched: weight decay, momentum decay and the moment
+        estimates of all other rows stay as they are.  The rows of the weight and of every state tensor are gathered, the
+        optimizer's ordinary step runs on them, and the results are scattered back."""
+        vals, rows = grad._components()
+        if rows.numel() == 0:
+            self._update_count([index])
+            return
+        rows = rows.long()
+        n = weight._data.shape[0]
+
+        def gather(x):
+            if isinstance(x, NDArray):
+                return NDArray._from_tensor(x._data[rows], x._ctx) if x._data.dim() and x._data.shape[0] == n else x
+            if isinstance(x, (list, tuple)):
+                return type(x)(gather(v) for v in x)
+            return x
+
+        def scatter(full, part):
+            if isinstance(full, NDArray):
+                if part is not full:
+                    full._data[rows] = part._data
+            elif isinstance(full, (list, tuple)):
+                for f, q in zip(full, part):
+                    scatter(f, q)
+        sub_w, sub_s = gather(weight), gather(state)
+        self.step([index], [sub_w], [NDArray._from_tensor(vals.to(sub_w._data.dtype), weight._ctx)], [sub_s])
+        scatter(weight, sub_w)
+        scatter(state, sub_s)
 
     def update_multi_precision(self, indices, weights, grads, states):
         if not isinstance(indices, (list, tuple)):
@@ -121,7 +164,7 @@ class Optimizer(object):
         if not any(mp):
             self.update(indices, weights, grads, states)
             return
-        if self.use_fused_step and all(mp) and hasattr(self, '_fused_step_mp'):
+        if self.use_fused_step and all(mp) and hasattr(self, '_fused_step_mp') and not any(self._is_lazy(g) for g in grads):
             with torch.no_grad():
                 self._fused_step_mp(indices, weights, grads, states)
             return
@@ -129,7 +172,7 @@ class Optimizer(object):
         for w, g, s, is_mp in zip(weights, grads, states, mp):
             if is_mp:
                 w32.append(s[0])
-                g32.append(g.__class__._from_tensor(g._data.float(), g._ctx))
+                g32.append(g.astype('float32') if self._is_lazy(g) else g.__class__._from_tensor(g._data.float(), g._ctx))
                 st.append(s[1])
             else:
                 w32.append(w); g32.append(g); st.append(s)
