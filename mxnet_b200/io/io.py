@@ -414,11 +414,14 @@ class LibSVMIter(MXDataIter):
         ptr = np.ctypeslib.as_array(indptr, shape=(n + 1,)).copy()
         for p in (labels, values, indices, indptr):
             L.mxb_free(p)
+        import scipy.sparse as sp
         dim = int(np.prod(data_shape))
-        dense = np.zeros((n, dim), dtype=np.float32)
-        for r in range(n):
-            dense[r, idx[ptr[r]:ptr[r + 1]]] = val[ptr[r]:ptr[r + 1]]
-        self._dense, self._label, self._n = dense, lab, n
+        if z and int(idx.max()) >= dim:
+            raise MXNetError('%s has feature index %d but data_shape is %s' % (data_libsvm, int(idx.max()), str(data_shape)))
+        # the file stays in compressed form: a feature space of millions of columns never becomes a dense [rows, dim] array
+        self._csr = sp.csr_matrix((val, idx, ptr), shape=(n, dim))
+        self._csr.sort_indices()
+        self._label, self._n, self._dim = lab, n, dim
         self._round = round_batch
         self._cursor = 0
 
@@ -427,7 +430,7 @@ class LibSVMIter(MXDataIter):
 
     @property
     def provide_data(self):
-        return [DataDesc('data', (self.batch_size, self._dense.shape[1]))]
+        return [DataDesc('data', (self.batch_size, self._dim))]
 
     @property
     def provide_label(self):
@@ -442,7 +445,7 @@ class LibSVMIter(MXDataIter):
         idx = np.arange(self._cursor, end) % self._n
         pad = max(0, end - self._n)
         self._cursor = end
-        return DataBatch([sparse.csr_matrix(self._dense[idx])], [nd.array(self._label[idx])], pad=pad)
+        return DataBatch([sparse.csr_matrix(self._csr[idx])], [nd.array(self._label[idx])], pad=pad)   # compressed CSR batch
 
     def iter_next(self):
         return self._cursor < self._n

@@ -152,3 +152,41 @@ def test_lazy_update_touches_only_the_rows_of_a_row_sparse_gradient(name, kwargs
     for _ in range(3):
         opt.update(0, w, mx.nd.array(gvals), state)
     np.testing.assert_allclose(results[True][rows], w.asnumpy(), rtol=1e-6, atol=1e-7)
+
+
+def test_libsvm_batches_stay_compressed_and_train_a_sparse_linear_model(tmp_path):
+    """The sparse linear-classification recipe of the reference (example/sparse/linear_classification): LibSVM batches in
+    CSR form over a feature space far too wide for dense batches, weights updated lazily from row-sparse gradients."""
+    dim, n = 2000000, 64
+    rng = np.random.RandomState(11)
+    truth = {}
+    lines = []
+    for i in range(n):
+        feats = np.sort(rng.choice(dim, 6, replace=False))
+        label = int(feats[0] % 2)
+        lines.append('%d %s' % (label, ' '.join('%d:1.0' % f for f in feats)))
+        truth[i] = label
+    path = str(tmp_path / 'wide.libsvm')
+    open(path, 'w').write('\n'.join(lines) + '\n')
+    it = mx.io.LibSVMIter(data_libsvm=path, data_shape=(dim,), batch_size=16)
+    assert it.provide_data[0].shape == (16, dim)
+    w = mx.nd.zeros((dim, 1))
+    opt = mx.optimizer.create('sgd', learning_rate=0.5, lazy_update=True, wd=0.0)
+    first = last = None
+    for epoch in range(30):
+        it.reset()
+        total = 0.0
+        for batch in it:
+            x, y = batch.data[0], batch.label[0]
+            assert x.stype == 'csr' and x.is_compressed and x.shape == (16, dim)
+            z = sparse.dot(x, w)                                              # [16, 1] from the components
+            p = 1 / (1 + np.exp(-z.asnumpy()[:, 0]))
+            yy = y.asnumpy()
+            total += float(-(yy * np.log(p + 1e-9) + (1 - yy) * np.log(1 - p + 1e-9)).sum())
+            dz = mx.nd.array(((p - yy) / len(yy)).reshape(-1, 1).astype('float32'))
+            g = sparse.dot(x, dz, transpose_a=True, forward_stype='row_sparse')   # gradient only for the features seen
+            assert g.is_compressed and g.indices.shape[0] <= 16 * 6
+            opt.update(0, w, g, None)
+        first = total if first is None else first
+        last = total
+    assert last < 0.5 * first
