@@ -161,6 +161,36 @@ def case_add(ctx, dtype, small):
     return dict(inputs=[a, b], fn=lambda a, b: a + b, fwd_bytes=3 * n * _esize(dtype), bwd_bytes=0, no_backward=True)
 
 
+def case_csr_dot(ctx, dtype, small, transpose_a=False, library=False):
+    """dot(csr, dense) from the compressed components: 200k x 1M features, 40 non-zeros per row, 64 dense columns (the
+    sparse linear / factorisation-machine shape).  ``library``: the tensor library's CSR product on the same data."""
+    import scipy.sparse as sp
+    from mxnet_b200.ndarray import sparse
+    m, k, per_row, n = (20000, 100000, 40, 64) if small else (200000, 1000000, 40, 64)
+    rng = np.random.RandomState(0)
+    cols = rng.randint(0, k, (m, per_row))
+    cols.sort(axis=1)
+    mat = sp.csr_matrix((rng.uniform(-1, 1, m * per_row).astype('float32'), cols.reshape(-1), np.arange(0, m * per_row + 1, per_row)),
+                        shape=(m, k))
+    a = sparse.csr_matrix(mat, ctx=ctx, dtype=dtype)
+    rhs = _rand((m if transpose_a else k, n), ctx, dtype)
+    es = _esize(dtype)
+    # every non-zero gathers (or scatters) one dense row of n values; plus the components and the result
+    nbytes = m * per_row * (n * es + es + 8) + (k if transpose_a else m) * n * (4 if transpose_a else es)
+    if library:
+        data, indices, indptr = a._comp
+        t = torch.sparse_csr_tensor(indptr, indices, data, size=(m, k))
+        if transpose_a:
+            t = t.to_sparse_coo().t().coalesce().to_sparse_csr()
+
+        def fn(rhs):
+            return nd.NDArray._from_tensor(t @ rhs._data, ctx)
+    else:
+        def fn(rhs):
+            return sparse.dot(a, rhs, transpose_a=transpose_a)
+    return dict(inputs=[rhs], fn=fn, fwd_bytes=nbytes, bwd_bytes=0, no_backward=True)
+
+
 def case_rnn(ctx, dtype, small, mode='lstm', bidirectional=False):
     """The RNN operator on the shape of the LSTM language model: 2 layers of 650 units, 35 steps, batch 80."""
     from mxnet_b200.ops.nn import rnn_param_size
@@ -183,6 +213,10 @@ def case_rnn(ctx, dtype, small, mode='lstm', bidirectional=False):
 
 
 CASES = {
+    'csr_dot_dense': case_csr_dot,
+    'csr_dot_dense_library': lambda c, d, s: case_csr_dot(c, d, s, library=True),
+    'csr_t_dot_dense': lambda c, d, s: case_csr_dot(c, d, s, transpose_a=True),
+    'csr_t_dot_dense_library': lambda c, d, s: case_csr_dot(c, d, s, transpose_a=True, library=True),
     'RNN_lstm': case_rnn,
     'RNN_gru': lambda c, d, s: case_rnn(c, d, s, mode='gru'),
     'RNN_tanh': lambda c, d, s: case_rnn(c, d, s, mode='rnn_tanh'),
