@@ -289,6 +289,11 @@ def main():
         tuned = conv_ops.tuned_choices()
         conv_sel = {d: '%d of %d' % (sum(1 for k, v in tuned.items() if k[0] == d and v), sum(1 for k in tuned if k[0] == d))
                     for d in ('fwd', 'dgrad', 'dgrad+skip', 'wgrad')}
+        # what the autotuner measured (microseconds with a cold L2: in-tree kernel, library), per direction and layer geometry
+        conv_us = {}
+        for k, (t_own, t_lib) in sorted(conv_ops.tuned_times().items(), key=lambda kv: (kv[0][0],) + tuple(kv[0][2:])):
+            conv_us.setdefault(k[0], {})['%dx%d %d>%d k%d s%d' % (k[3], k[4], k[5], k[6], k[7], k[-1])] = [t_own, t_lib]
+        conv_sel['autotune_us'] = conv_us
         res = {'value': value, 'ms_per_step': ms / steps, 'launches': int(launches), 'clocks': clocks, 'final_loss': final_loss,
                'e2e': e2e, 'fused': trainer._fused is not None, 'conv_sel': conv_sel, 'global_batch': global_batch}
         del net, trainer

@@ -71,6 +71,8 @@ def measure(name, unit, items_per_step_per_gpu, make_step, args, config, baselin
         cfg['gemm_in_tree_kernel_chosen'] = {p: '%d of %d' % (sum(1 for k, v in tuned.items() if k[0] == p and v),
                                                               sum(1 for k in tuned if k[0] == p))
                                              for p in ('fwd', 'dgrad', 'wgrad')}
+        cfg['gemm_autotune_us'] = {'%s %dx%dx%d' % (k[0], k[2], k[3], k[4]): [v[0], v[1]]
+                                   for k, v in sorted(gemm_ops.tuned_times().items(), key=lambda kv: (kv[0][0],) + tuple(kv[0][2:5]))}
     from mxnet_b200.ops.cuda import rnn_ops
     if rnn_ops.tuned_choices():
         cfg['rnn_in_tree_kernel_chosen'] = {'%s T=%d N=%d I=%d H=%d L=%d %s' % (k[0], k[2], k[3], k[4], k[5], k[6],

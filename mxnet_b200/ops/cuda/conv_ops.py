@@ -20,6 +20,7 @@ from .gemm_ops import _error_flag
 _DEFAULT = 'auto'
 _ALL = frozenset(('fwd', 'dgrad', 'wgrad'))
 _tuned = {}          # (direction, dtype, geometry) -> True when the in-tree kernel won
+_tuned_us = {}       # same keys -> (in-tree, library) microseconds measured by the autotuner on this rank
 # rate credited to the separate BatchNorm statistics pass that the forward epilogue replaces, bytes per microsecond
 # (the copy bandwidth: a conservative credit, the measured pass is slower)
 _BN_REDUCE_BYTES_PER_US = 6.5e6
@@ -69,13 +70,20 @@ def use_own(direction, dirs, key, own_fn, lib_fn, lib_extra_us=0.0):
         if torch.cuda.is_current_stream_capturing():
             return False                   # cannot time inside a capture; the eager warm-up run normally comes first
         with torch.no_grad():
-            hit = _tuned[k] = job_wide(_time_us(own_fn) <= _MARGIN * (_time_us(lib_fn) + lib_extra_us))
+            t_own, t_lib = _time_us(own_fn), _time_us(lib_fn) + lib_extra_us
+            _tuned_us[k] = (round(t_own, 1), round(t_lib, 1))
+            hit = _tuned[k] = job_wide(t_own <= _MARGIN * t_lib)
     return hit
 
 
 def tuned_choices():
     """{(direction, dtype, N, H, W, Cin, Cout, R, S, pad, dilate): in-tree kernel chosen} of the auto mode so far."""
     return dict(_tuned)
+
+
+def tuned_times():
+    """Same keys -> (in-tree, library) microseconds with a cold L2, as timed on this rank."""
+    return dict(_tuned_us)
 
 
 def out_hw(h, w, kernel, pad, dilate, stride=(1, 1)):

@@ -12,6 +12,7 @@ _ACT = {None: 0, 'relu': 1, 'gelu': 2}
 _err = {}
 _tuned = {}          # (product, dtype, M, N, K, bias, act) -> True when the in-tree kernel won
 _flush = {}
+_tuned_us = {}       # key -> (in-tree, library) microseconds measured by the autotuner on this rank
 _ws = {}
 _MARGIN = 1.02      # ties (within 2 %) go to the in-tree kernel
 
@@ -51,12 +52,19 @@ def use_own(key, own_fn, lib_fn):
         if torch.cuda.is_current_stream_capturing():
             return True
         with torch.no_grad():
-            hit = _tuned[key] = job_wide(_time_us(own_fn) <= _MARGIN * _time_us(lib_fn))
+            t_own, t_lib = _time_us(own_fn), _time_us(lib_fn)
+            _tuned_us[key] = (round(t_own, 1), round(t_lib, 1))
+            hit = _tuned[key] = job_wide(t_own <= _MARGIN * t_lib)
     return hit
 
 
 def tuned_choices():
     return dict(_tuned)
+
+
+def tuned_times():
+    """{(product, dtype, M, N, K, bias, act): (in-tree, library) microseconds with a cold L2, as timed on this rank}."""
+    return dict(_tuned_us)
 
 
 def _error_flag(device):
