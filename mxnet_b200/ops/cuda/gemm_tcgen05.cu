@@ -772,10 +772,17 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
 // mostly empty last column tile (N = 384 -> 2 x 192) and a mostly empty last round (M = 8192, N = 768: 256 tiles of 192
 // columns take two rounds of 320 instead of two rounds of 384).  Outputs with fewer tiles than CTAs are cut by k-steps
 // (stream-K plan), so their rounds are fractional.
-static int pick_bn(int M, int N, int K) {
+static int pick_bn(int M, int N, int K, int batch = 1) {
   if (N <= 64) return 64;
   if (N <= 128) return 128;
-  const long G = sm_count(), tm = (M + BM - 1) / BM;
+  const long G = sm_count(), tm = (long)((M + BM - 1) / BM) * batch;
+  // Few tiles and a short contraction (no stream-K): the product is one round whatever the width, and the round lasts as
+  // long as one tile, so the narrowest width that still fits one round wins (64 x 768 x 768: 12 tiles of 64 columns
+  // instead of 3 of 256).
+  if (K <= 32 * BK && tm * ((N + 255) / 256) < G / 2) {
+    for (int bn = 64; bn <= 192; bn += 64)
+      if (tm * ((N + bn - 1) / bn) <= G) return bn;
+  }
   int best = 256;
   double best_cost = 0;
   for (int bn = 256; bn >= 128; bn -= 64) {
@@ -882,7 +889,7 @@ static int gemm_run(int dtype, const void* A, const void* B, void* D, const void
   if (batch > 1 && ((sa % 8) || (sb % 8) || (sd % 8) || sd < (long long)(M - 1) * ldd + N)) return -3;      // 16-byte aligned matrices
   const int bf16 = dtype == kBF16;
   const int pbn = batch > 1 ? 0 : pick_pair_bn(M, N, K, b_mn);
-  const int bn = pbn ? pbn : pick_bn(M, N, K);
+  const int bn = pbn ? pbn : pick_bn(M, N, K, batch);
   const int b_rows = pbn ? pbn / 2 : bn;          // rows of B one CTA stages per k-step
   CUtensorMap ma, mb;
   const int a3d = a_mn && (M % 64) == 0, b3d = b_mn && (N % 64) == 0;
