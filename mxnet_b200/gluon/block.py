@@ -489,8 +489,11 @@ class HybridBlock(Block):
         if _layout.get_optimize_layout():
             # layout management is on (amp.init(layout_optimization=True) / set_optimize_layout): run the traced graph after
             # the pass that moves its convolutional trunk to NHWC (src/imperative/cached_op.h:213 in the reference)
-            return self._call_partitioned(*args, backend='optimize_layout')
+            return self._cached_op(*args, graph_forward=self._layout_forward, graph_tag='optimize_layout')
         return self._cached_op(*args)
+
+    def _layout_forward(self, *args):
+        return self._call_partitioned(*args, backend='optimize_layout')
 
     def _call_partitioned(self, *args, backend=None):
         """``hybridize(backend=...)`` / ``optimize_for``: run the traced graph after the backend's graph pass

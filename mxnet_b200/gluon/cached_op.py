@@ -29,8 +29,9 @@ _log = logging.getLogger('mxnet_b200.cached_op')
 class _Graphed(object):
     """Forward/backward graph pair for one call signature."""
 
-    def __init__(self, block, args, training, recording):
+    def __init__(self, block, args, training, recording, forward=None):
         self.block = block
+        self.forward = forward if forward is not None else block.forward    # a pass-rewritten graph of the block, or its code
         self.training, self.recording = training, recording
         from .block import _flatten
         flat, self.in_fmt = _flatten(args, 'input')
@@ -131,9 +132,9 @@ class _Graphed(object):
         try:
             if self.recording:
                 with torch.enable_grad():
-                    return self.block.forward(*args)
+                    return self.forward(*args)
             with torch.no_grad():
-                return self.block.forward(*args)
+                return self.forward(*args)
         finally:
             _state.state.recording, _state.state.training = prev_r, prev_t
             if self.alias:
@@ -236,26 +237,30 @@ class CachedOp(object):
                 sig.append(repr(a))
         return tuple(sig)
 
-    def __call__(self, *args):
+    def __call__(self, *args, graph_forward=None, graph_tag=None):
+        """``graph_forward``: a callable that evaluates the block's traced graph after a graph pass (layout management);
+        it replaces ``block.forward`` both in the eager runs and inside the captured graphs.  ``graph_tag`` names the pass
+        in the signature, so that switching it on or off never reuses the other form's graphs."""
         from .block import _flatten
         flat, _ = _flatten(args, 'input')
         arrays = [a for a in flat if isinstance(a, NDArray)]
+        eager = graph_forward if graph_forward is not None else self.block._call_forward
         if not self._use_graphs(arrays):
-            return self.block._call_forward(*args)
-        sig = self._signature(flat)
+            return eager(*args)
+        sig = self._signature(flat) + ((graph_tag,) if graph_forward is not None else ())
         g = self._graphs.get(sig)
         if g is not None:
             return g(args)
         if sig not in self._seen:
             self._seen[sig] = 1          # warm-up run with this signature stays eager
-            return self.block._call_forward(*args)
+            return eager(*args)
         try:
-            g = _Graphed(self.block, args, _state.state.training, _state.state.recording)
+            g = _Graphed(self.block, args, _state.state.training, _state.state.recording, forward=graph_forward)
         except Exception as e:  # pylint: disable=broad-except
             self._disabled = True
             _log.warning('CUDA graph capture failed (%s); block %s runs eagerly', e, type(self.block).__name__,
                          exc_info=bool(env.get('MXNET_CUDA_GRAPHS_VERBOSE')))
-            return self.block._call_forward(*args)
+            return eager(*args)
         self._graphs[sig] = g
         if env.get('MXNET_CUDA_GRAPHS_VERBOSE'):
             _log.info('captured CUDA graphs for %s signature %s', type(self.block).__name__, sig[:3])

@@ -182,6 +182,29 @@ def batch_norm(data, gamma, beta, moving_mean, moving_var, residual=None, eps=1e
             out, mean, var = norm_ops.batch_norm_nhwc(data, gamma, beta, moving_mean, moving_var, eps, momentum,
                                                       training, act_type, residual, want_stats=bool(output_mean_var))
             return (out, mean, var) if output_mean_var else out
+    if not output_mean_var and data.dim() >= 2 and data.is_floating_point() and data.dtype != torch.float64 and \
+            gamma.dtype == beta.dtype and gamma.dtype in (data.dtype, torch.float32):
+        # every other layout / precision: the tensor library's fused normalisation (one statistics pass and one apply pass,
+        # fused backward) on a channel-first view.  The running statistics are updated here, from the saved batch moments,
+        # with the population variance as the reference does (src/operator/nn/batch_norm.cc); the library's own update would
+        # use the sample variance.
+        x = data if axis == 1 else data.movedim(axis, 1)
+        if training:
+            y, mean, invstd = torch.native_batch_norm(x, gamma, beta, None, None, True, 0.0, eps)
+            with torch.no_grad():
+                var = invstd.float().pow(-2).sub_(eps).clamp_(min=0.0)
+                moving_mean.mul_(momentum).add_(mean.to(moving_mean.dtype), alpha=1 - momentum)
+                moving_var.mul_(momentum).add_(var.to(moving_var.dtype), alpha=1 - momentum)
+        else:
+            stat_dtype = torch.float32 if data.dtype in (torch.float16, torch.bfloat16) else data.dtype
+            y = torch.native_batch_norm(x, gamma, beta, moving_mean.to(stat_dtype), moving_var.to(stat_dtype), False, 0.0, eps)[0]
+        if axis != 1:
+            y = y.movedim(1, axis)
+        if residual is not None:
+            y = y + residual.to(y.dtype)
+        if act_type == 'relu':
+            y = torch.relu(y)
+        return y
     red = tuple(i for i in range(data.dim()) if i != axis)
     shape = [1] * data.dim()
     shape[axis] = data.shape[axis]

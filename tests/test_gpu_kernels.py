@@ -1045,5 +1045,12 @@ def test_layout_pass_puts_an_nchw_network_on_the_channel_last_kernels():
             loss.backward()
             g = net.features[0].weight.grad().asnumpy().astype('float32')
             assert np.isfinite(g).all() and np.abs(g).sum() > 0
+            # with static allocation the re-laid graph is what the CUDA graphs capture
+            net.hybridize(static_alloc=True, static_shape=True)
+            for _ in range(3):
+                again = net(x)
+            tags = [sig[-1] for sig in net._cached_op._graphs]
+            assert 'optimize_layout' in tags
+            np.testing.assert_allclose(again.asnumpy().astype('float32'), expect, rtol=5e-2, atol=5e-2)
     finally:
         layout.set_optimize_layout(False)
