@@ -288,6 +288,8 @@ def layer_norm(data, gamma, beta, axis=-1, eps=1e-5, output_mean_var=False):
           defaults={'num_groups': 1, 'eps': 1e-5, 'output_mean_var': False})
 def group_norm(data, gamma, beta, num_groups=1, eps=1e-5, output_mean_var=False):
     n, c = data.shape[0], data.shape[1]
+    if not output_mean_var and data.is_floating_point() and gamma.numel() == c and beta.numel() == c:
+        return F.group_norm(data, num_groups, gamma.to(data.dtype), beta.to(data.dtype), eps)     # fused forward and backward
     x = data.reshape(n, num_groups, -1)
     xf = x.float() if x.dtype in (torch.float16, torch.bfloat16) else x
     mean = xf.mean(-1, keepdim=True)
