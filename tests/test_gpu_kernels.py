@@ -1051,6 +1051,9 @@ def test_layout_pass_puts_an_nchw_network_on_the_channel_last_kernels():
                 again = net(x)
             tags = [sig[-1] for sig in net._cached_op._graphs]
             assert 'optimize_layout' in tags
-            np.testing.assert_allclose(again.asnumpy().astype('float32'), expect, rtol=5e-2, atol=5e-2)
+        # the training pass above moved the running statistics: compare with the block's own code on the same parameters
+        layout.set_optimize_layout(False)
+        net.hybridize(False)
+        np.testing.assert_allclose(again.asnumpy().astype('float32'), net(x).asnumpy().astype('float32'), rtol=5e-2, atol=5e-2)
     finally:
         layout.set_optimize_layout(False)
