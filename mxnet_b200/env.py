@@ -108,6 +108,7 @@ declare('MXNET_EXEC_BULK_EXEC_INFERENCE', bool, True, 'bulk (graph-capture) infe
 declare('MXNET_EXEC_BULK_EXEC_TRAIN', bool, True, 'bulk (graph-capture) training segments')
 declare('MXNET_EXEC_BULK_EXEC_MAX_NODE_TRAIN', int, 15, 'max nodes per bulked segment')
 declare('MXNET_ENABLE_CUDA_GRAPHS', bool, True, 'hybridize(static_alloc, static_shape) captures CUDA graphs')
+declare('MXNET_CUDA_GRAPHS_AUTO', bool, True, 'a block hybridized without static_alloc / static_shape is also captured once an input signature has repeated three times (at most four signatures per block); 0 = only blocks hybridized with both flags are captured')
 declare('MXNET_CUDA_GRAPHS_VERBOSE', bool, False, 'log graph capture / re-capture events')
 declare('MXNET_ENGINE_INFO', bool, False, 'verbose engine logging')
 # ---- memory -------------------------------------------------------------------------------

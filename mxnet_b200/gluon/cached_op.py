@@ -220,12 +220,17 @@ class CachedOp(object):
         self._graphs = {}
         self._disabled = False
 
+    def _static(self):
+        return bool(self.flags.get('static_alloc') and self.flags.get('static_shape'))
+
     def _use_graphs(self, arrays):
         if self._disabled or not env.get('MXNET_ENABLE_CUDA_GRAPHS'):
             return False
-        if not (self.flags.get('static_alloc') and self.flags.get('static_shape')):
+        if not self._static() and not env.get('MXNET_CUDA_GRAPHS_AUTO'):
             return False
-        return bool(arrays) and all(a._data.is_cuda for a in arrays)
+        if not (bool(arrays) and all(a._data.is_cuda for a in arrays)):
+            return False
+        return not torch.cuda.is_current_stream_capturing()      # a block called inside an outer block's capture is part of it
 
     def _signature(self, flat):
         from . import block as blk
@@ -251,8 +256,13 @@ class CachedOp(object):
         g = self._graphs.get(sig)
         if g is not None:
             return g(args)
-        if sig not in self._seen:
-            self._seen[sig] = 1          # warm-up run with this signature stays eager
+        # With static_alloc + static_shape the second call of a signature is captured.  A plain hybridize() makes no promise
+        # about shapes: a signature is captured once it has repeated (fourth call), and at most four signatures per block,
+        # so that a workload whose shapes keep changing stays eager instead of collecting graphs.
+        seen = self._seen.get(sig, 0)
+        need = 1 if self._static() else 3
+        if seen < need or (not self._static() and len(self._graphs) >= 4):
+            self._seen[sig] = seen + 1   # warm-up runs with this signature stay eager
             return eager(*args)
         try:
             g = _Graphed(self.block, args, _state.state.training, _state.state.recording, forward=graph_forward)

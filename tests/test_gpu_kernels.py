@@ -1057,3 +1057,47 @@ def test_layout_pass_puts_an_nchw_network_on_the_channel_last_kernels():
         np.testing.assert_allclose(again.asnumpy().astype('float32'), net(x).asnumpy().astype('float32'), rtol=5e-2, atol=5e-2)
     finally:
         layout.set_optimize_layout(False)
+
+
+def test_plain_hybridize_is_captured_once_a_signature_repeats():
+    """hybridize() without static_alloc / static_shape: eager for the first three calls of a signature, CUDA-graph replay
+    from then on, at most four signatures per block; MXNET_CUDA_GRAPHS_AUTO=0 keeps such blocks eager."""
+    import mxnet_b200 as mx
+    from mxnet_b200 import env
+    from mxnet_b200.gluon import nn
+    ctx = mx.gpu(0)
+    net = nn.HybridSequential()
+    net.add(nn.Dense(32, activation='relu'), nn.Dense(8))
+    net.initialize(ctx=ctx)
+    net.hybridize()
+    x = mx.nd.array(np.random.RandomState(0).uniform(-1, 1, (4, 16)).astype('float32'), ctx=ctx)
+    outs = []
+    for i in range(6):
+        outs.append(net(x).asnumpy())
+        assert len(net._cached_op._graphs) == (1 if i >= 4 else 0), i      # call 0 builds the op; calls 1-3 warm the signature
+    for o in outs[1:]:
+        np.testing.assert_allclose(o, outs[0], rtol=1e-6, atol=1e-6)
+    # training through the captured pair gives the gradients of the eager pass
+    x.attach_grad()
+    grads = []
+    for i in range(6):
+        with mx.autograd.record():
+            loss = (net(x) ** 2).sum()
+        loss.backward()
+        grads.append(x.grad.asnumpy().copy())
+    for g in grads[1:]:
+        np.testing.assert_allclose(g, grads[0], rtol=1e-5, atol=1e-6)
+    assert len(net._cached_op._graphs) == 2
+    for n in range(5, 12):                                               # changing shapes: no more than four signatures are kept
+        y = mx.nd.ones((n, 16), ctx=ctx)
+        for _ in range(5):
+            net(y)
+    assert len(net._cached_op._graphs) == 4
+    with env.scope('MXNET_CUDA_GRAPHS_AUTO', '0'):
+        net2 = nn.HybridSequential()
+        net2.add(nn.Dense(8))
+        net2.initialize(ctx=ctx)
+        net2.hybridize()
+        for _ in range(6):
+            net2(x)
+        assert len(net2._cached_op._graphs) == 0
