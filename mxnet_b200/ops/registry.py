@@ -99,6 +99,9 @@ def list_ops():
 _array_classes = {}   # 'nd' -> NDArray, 'np' -> ndarray
 
 
+_set_grad_enabled = torch._C._set_grad_enabled
+
+
 def _set_array_class(kind, cls):
     _array_classes[kind] = cls
 
@@ -138,18 +141,16 @@ def invoke(op, args, attrs, out=None, kind=None):
     if pctx is not None:
         pctx.__enter__()
     try:
-        if st.recording:
-            if torch.is_grad_enabled():
-                res = op.fn(*tensors, **attrs)
-            else:
-                with torch.enable_grad():
-                    res = op.fn(*tensors, **attrs)
+        # the tensor library's gradient mode follows the recording state; switched with the two C calls directly (the
+        # context-manager objects cost more host time than a small operator)
+        if st.recording == torch.is_grad_enabled():
+            res = op.fn(*tensors, **attrs)
         else:
-            if torch.is_grad_enabled():
-                with torch.no_grad():
-                    res = op.fn(*tensors, **attrs)
-            else:
+            _set_grad_enabled(st.recording)
+            try:
                 res = op.fn(*tensors, **attrs)
+            finally:
+                _set_grad_enabled(not st.recording)
         if _state.naive_engine and ctx is not None and ctx.device_typeid == 2 and not torch.cuda.is_current_stream_capturing():
             # MXNET_ENGINE_TYPE=NaiveEngine: every operator has finished (or failed) before its call returns, so a device
             # error is raised by the operator that caused it (src/engine/naive_engine.cc runs each op inline)
