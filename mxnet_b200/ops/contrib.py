@@ -725,14 +725,50 @@ def quantized_fully_connected(data, weight, bias=None, min_data=None, max_data=N
 def quantized_conv(data, weight, bias=None, min_data=None, max_data=None, min_weight=None, max_weight=None,
                    min_bias=None, max_bias=None, kernel=(), stride=(), dilate=(), pad=(), num_filter=0, num_group=1,
                    no_bias=False, layout=None, **_):
-    acc = F.conv2d(data.float(), weight.float(), None, tuple(stride) or 1, tuple(pad) or 0, tuple(dilate) or 1, num_group)
     sd = torch.maximum(min_data.abs(), max_data.abs()).reshape(()) / 127.0
     sw = torch.maximum(min_weight.abs(), max_weight.abs()).reshape(()) / 127.0
+    qbias = None
     if bias is not None and not no_bias:
         sb = torch.maximum(min_bias.abs(), max_bias.abs()).reshape(()) / 127.0
-        acc = acc + torch.round(bias.float() * sb / (sd * sw)).reshape(1, -1, 1, 1)
+        qbias = torch.round(bias.float() * sb / (sd * sw))
     out_range = sd * sw * 2147483647.0
-    return acc.to(torch.int32), (-out_range).reshape(1), out_range.reshape(1)
+    acc = _quantized_conv_i8(data, weight, qbias, stride, dilate, pad, num_group)
+    if acc is None:
+        # integer-valued float arithmetic (exact while the sums stay below 2**24)
+        acc = F.conv2d(data.float(), weight.float(), None, tuple(stride) or 1, tuple(pad) or 0, tuple(dilate) or 1, num_group)
+        if qbias is not None:
+            acc = acc + qbias.reshape(1, -1, 1, 1)
+        acc = acc.to(torch.int32)
+    return acc, (-out_range).reshape(1), out_range.reshape(1)
+
+
+def _quantized_conv_i8(data, weight, qbias, stride, dilate, pad, num_group):
+    """2-D int8 convolution (NCHW) on the int8 tensor-core GEMM (``tcgen05.mma.kind::i8``, exact int32 accumulation): the
+    receptive fields are gathered into rows (a strided view, one int8 copy: 1/4 of the bytes of the fp32 detour) and
+    multiplied with the filter matrix.  Returns None where the kernel does not apply (reference: cuDNN int8 convolution,
+    src/operator/quantization/quantized_conv.cu)."""
+    if data.dim() != 4 or num_group != 1 or not (data.is_cuda and data.dtype == torch.int8 and weight.dtype == torch.int8):
+        return None
+    sh, sw_ = (tuple(stride) or (1, 1)) if not isinstance(stride, int) else (stride, stride)
+    ph, pw = (tuple(pad) or (0, 0)) if not isinstance(pad, int) else (pad, pad)
+    dil = (tuple(dilate) or (1, 1)) if not isinstance(dilate, int) else (dilate, dilate)
+    if tuple(dil) != (1, 1):
+        return None
+    cout, cin, kh, kw = weight.shape
+    if (cin * kh * kw) % 16 or cin != data.shape[1]:
+        return None
+    x = F.pad(data, (pw, pw, ph, ph)) if (ph or pw) else data
+    if x.shape[2] < kh or x.shape[3] < kw:
+        return None
+    cols = x.unfold(2, kh, sh).unfold(3, kw, sw_)                     # [N, C, Ho, Wo, kh, kw], a view
+    n, _, ho, wo = cols.shape[:4]
+    a = cols.permute(0, 2, 3, 1, 4, 5).reshape(n * ho * wo, cin * kh * kw)
+    b = weight.reshape(cout, cin * kh * kw)
+    if not _int8_kernel_ok(a, b):
+        return None
+    from .cuda import gemm_ops
+    acc = gemm_ops.gemm_i8(a, b, qbias.to(torch.int32) if qbias is not None else None)
+    return acc.reshape(n, ho, wo, cout).permute(0, 3, 1, 2)
 
 
 def _passthrough_q(name, fn):

@@ -1015,6 +1015,67 @@ def test_quantized_network_runs_its_dense_layers_on_the_int8_kernel():
     assert err < 0.05, err
 
 
+@pytest.mark.parametrize('cin,cout,k,stride,pad,hw,bias', [(64, 128, 3, 1, 1, 14, True), (32, 64, 1, 1, 0, 9, False), (16, 48, 3, 2, 1, 17, True),
+                                                         (64, 32, 5, 1, 2, 8, True)])
+def test_quantized_convolution_runs_on_the_int8_kernel_and_is_exact(cin, cout, k, stride, pad, hw, bias):
+    """``_contrib_quantized_conv`` with int8 CUDA inputs: receptive fields gathered into rows, product on the
+    tcgen05 int8 GEMM (launch counter), int32 results equal to an integer convolution computed in float64 on the host."""
+    from mxnet_b200.ops import cuda as kc
+    from mxnet_b200.ops.cuda import gemm_ops
+    ctx = mx.gpu(0)
+    rng = np.random.RandomState(cin + k)
+    x = rng.randint(-127, 128, (3, cin, hw, hw)).astype('int8')
+    w = rng.randint(-127, 128, (cout, cin, k, k)).astype('int8')
+    b = rng.randint(-127, 128, (cout,)).astype('int8')
+    args = [nd.array(x, ctx=ctx, dtype='int8'), nd.array(w, ctx=ctx, dtype='int8')]
+    rng_args = [nd.array([-1.0], ctx=ctx), nd.array([1.0], ctx=ctx), nd.array([-0.5], ctx=ctx), nd.array([0.5], ctx=ctx)]
+    if bias:
+        args.append(nd.array(b, ctx=ctx, dtype='int8'))
+        rng_args += [nd.array([-2.0], ctx=ctx), nd.array([2.0], ctx=ctx)]
+    before = kc.launches()
+    if bias:
+        out, mn, mxr = nd.contrib.quantized_conv(args[0], args[1], args[2], *rng_args, kernel=(k, k), stride=(stride, stride),
+                                                 pad=(pad, pad), num_filter=cout)
+    else:
+        out, mn, mxr = nd.contrib.quantized_conv(args[0], args[1], None, *rng_args, kernel=(k, k), stride=(stride, stride),
+                                                 pad=(pad, pad), num_filter=cout, no_bias=True)
+    assert kc.launches() - before >= 1
+    assert int(gemm_ops._error_flag(torch.device('cuda', 0)).item()) == 0
+    ref = torch.nn.functional.conv2d(torch.from_numpy(x).double(), torch.from_numpy(w).double(), None, stride, pad)
+    if bias:
+        sd, sw, sb = 1.0 / 127, 0.5 / 127, 2.0 / 127
+        ref = ref + torch.round(torch.from_numpy(b).double() * sb / (np.float32(sd) * np.float32(sw))).reshape(1, -1, 1, 1)
+    got = out.asnumpy()
+    assert got.dtype == np.int32 and got.shape == tuple(ref.shape)
+    diff = np.abs(got.astype(np.int64) - ref.numpy().astype(np.int64))
+    assert diff.max() <= (1 if bias else 0)             # the bias is rounded from fp32 scale arithmetic: one unit at most
+    np.testing.assert_allclose(mxr.asnumpy(), [1.0 / 127 * 0.5 / 127 * 2147483647.0], rtol=1e-5)
+
+
+def test_quantized_convolutional_network_runs_on_the_int8_kernel():
+    """``quantize_net`` on a small CNN: the convolutions whose gathered rows are a multiple of 16 long and the dense layer run
+    their int8 products on the tensor-core kernel; outputs stay close to the float network's."""
+    from mxnet_b200.contrib import quantization
+    from mxnet_b200.gluon import nn
+    from mxnet_b200.ops import cuda as kc
+    ctx = mx.gpu(0)
+    mx.random.seed(7)
+    net = nn.HybridSequential()
+    net.add(nn.Conv2D(32, 3, padding=1, in_channels=16, activation='relu'), nn.Conv2D(64, 3, strides=2, padding=1, in_channels=32,
+                                                                                    activation='relu'),
+            nn.Conv2D(32, 1, in_channels=64), nn.GlobalAvgPool2D(), nn.Flatten(), nn.Dense(16, in_units=32))
+    net.initialize(mx.init.Xavier(), ctx=ctx)
+    net.hybridize()
+    x = nd.array(np.random.RandomState(2).randn(8, 16, 12, 12).astype('float32'), ctx=ctx)
+    ref = net(x).asnumpy()
+    qnet = quantization.quantize_net(net, data_shapes=[(8, 16, 12, 12)], ctx=ctx)
+    before = kc.launches()
+    out = qnet(x).asnumpy()
+    assert kc.launches() - before >= 4                      # three convolutions and the dense layer
+    err = np.abs(out - ref).max() / np.abs(ref).max()
+    assert err < 0.08, err
+
+
 # ---------------------------------------------------------------------------------------- layout management
 def test_layout_pass_puts_an_nchw_network_on_the_channel_last_kernels():
     """A model written in NCHW (the reference's default layout) runs its convolutions on the tcgen05 NHWC kernels once
