@@ -64,7 +64,7 @@ static int csr_launch(bool transposed, const void* vals, const int64_t* idx, con
                       int N, cudaStream_t st) {
   if (M == 0 || N == 0) return 0;
   const int64_t gx = (M + 3) / 4;                  // four rows (warps) per block
-  const int V = N > 32 ? 4 : 1;
+  const int V = N > 64 ? 4 : N > 32 ? 2 : 1;      // all 32 lanes of a warp get columns: 64 columns = 32 lanes x 2
   const int64_t gy = ((int64_t)N + 32 * V - 1) / (32 * V);
   if (gx > 0x7fffffffLL || gy > 65535) return -2;
   const dim3 grid((unsigned)gx, (unsigned)gy);
@@ -73,6 +73,9 @@ static int csr_launch(bool transposed, const void* vals, const int64_t* idx, con
   if (V == 4) {
     if (transposed) csr_t_dot_dense_kernel<T, 4><<<grid, 128, 0, st>>>(v, idx, ptr, b, static_cast<float*>(out), M, N);
     else csr_dot_dense_kernel<T, 4><<<grid, 128, 0, st>>>(v, idx, ptr, b, static_cast<T*>(out), M, N);
+  } else if (V == 2) {
+    if (transposed) csr_t_dot_dense_kernel<T, 2><<<grid, 128, 0, st>>>(v, idx, ptr, b, static_cast<float*>(out), M, N);
+    else csr_dot_dense_kernel<T, 2><<<grid, 128, 0, st>>>(v, idx, ptr, b, static_cast<T*>(out), M, N);
   } else {
     if (transposed) csr_t_dot_dense_kernel<T, 1><<<grid, 128, 0, st>>>(v, idx, ptr, b, static_cast<float*>(out), M, N);
     else csr_dot_dense_kernel<T, 1><<<grid, 128, 0, st>>>(v, idx, ptr, b, static_cast<T*>(out), M, N);
