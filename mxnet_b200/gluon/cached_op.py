@@ -71,6 +71,22 @@ class _Graphed(object):
         self.pool = torch.cuda.graph_pool_handle()
         self.fwd = torch.cuda.CUDAGraph()
         n0 = _kernels.launches()
+        # No garbage collection while a capture is open: a collection that frees the graphs of an earlier, dropped block
+        # destroys them in the middle of this capture ("operation not permitted when stream is capturing") and invalidates
+        # it.  Whatever is collectable is collected now, and the collector stays off until both graphs are recorded.
+        import gc
+        gc.collect()
+        self._gc_was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            self._capture(stream, n0, recording, dev)
+        finally:
+            if self._gc_was_enabled:
+                gc.enable()
+
+    def _capture(self, stream, n0, recording, dev):
+        from .block import _flatten
+        _kernels = self._kernels
         with torch.cuda.stream(stream):
             with torch.cuda.graph(self.fwd, pool=self.pool, stream=stream):
                 outs = self._run_forward()

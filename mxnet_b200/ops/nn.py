@@ -161,6 +161,23 @@ def _bn_nout(attrs):
     return 3 if attrs.get('output_mean_var') in (True, 'True', 1) else 1
 
 
+def _fused_bn_training(x, gamma, beta, eps):
+    """(y, batch mean, 1 / sqrt(batch variance + eps)) of a channel-first tensor with one of the library's fused kernels:
+    the cuDNN normalisation for dense 4-D / 5-D fp32 and fp16 CUDA tensors (its backward pass is several times faster than
+    the generic kernel's on NCHW data), the generic fused kernel otherwise."""
+    # (the size limits are the tensor library's own conditions for choosing this path)
+    if x.is_cuda and x.dim() in (4, 5) and x.dtype in (torch.float32, torch.float16) and eps >= 1e-5 and \
+            torch.backends.cudnn.enabled and 0 < x.numel() < (1 << 31) and x.shape[0] <= 880801 and \
+            (x.is_contiguous() or (x.dim() == 4 and x.is_contiguous(memory_format=torch.channels_last))):
+        w, b = (gamma.float(), beta.float()) if gamma.dtype != torch.float32 else (gamma, beta)
+        try:
+            y, mean, invstd, _ = torch.cudnn_batch_norm(x, w, b, None, None, True, 0.0, eps)
+            return y, mean, invstd
+        except RuntimeError:
+            pass                                # a shape the library's cuDNN path refuses: the generic kernel takes it
+    return torch.native_batch_norm(x, gamma, beta, None, None, True, 0.0, eps)
+
+
 @register('BatchNorm', '_npx_batch_norm', 'BatchNorm_v1', inputs=('data', 'gamma', 'beta', 'moving_mean', 'moving_var', 'residual'),
           nout=_bn_nout, aux=('moving_mean', 'moving_var'),
           defaults={'eps': 1e-3, 'momentum': 0.9, 'fix_gamma': True, 'use_global_stats': False,
@@ -190,7 +207,7 @@ def batch_norm(data, gamma, beta, moving_mean, moving_var, residual=None, eps=1e
         # use the sample variance.
         x = data if axis == 1 else data.movedim(axis, 1)
         if training:
-            y, mean, invstd = torch.native_batch_norm(x, gamma, beta, None, None, True, 0.0, eps)
+            y, mean, invstd = _fused_bn_training(x, gamma, beta, eps)
             with torch.no_grad():
                 var = invstd.float().pow(-2).sub_(eps).clamp_(min=0.0)
                 moving_mean.mul_(momentum).add_(mean.to(moving_mean.dtype), alpha=1 - momentum)
