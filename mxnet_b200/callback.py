@@ -8,6 +8,8 @@ import logging
 import math
 import time
 
+from .model import save_checkpoint   # noqa: F401  (re-exported as in python/mxnet/callback.py)
+
 __all__ = ['do_checkpoint', 'module_checkpoint', 'log_train_metric', 'Speedometer', 'ProgressBar',
            'LogValidationMetricsCallback']
 

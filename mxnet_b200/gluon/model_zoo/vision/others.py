@@ -4,7 +4,7 @@ from ....ops import registry as _reg
 from ...block import HybridBlock
 from ... import nn
 
-__all__ = ['AlexNet', 'alexnet', 'VGG', 'vgg11', 'vgg13', 'vgg16', 'vgg19', 'vgg11_bn', 'vgg13_bn', 'vgg16_bn',
+__all__ = ['get_vgg', 'get_mobilenet', 'get_mobilenet_v2', 'AlexNet', 'alexnet', 'VGG', 'vgg11', 'vgg13', 'vgg16', 'vgg19', 'vgg11_bn', 'vgg13_bn', 'vgg16_bn',
            'vgg19_bn', 'SqueezeNet', 'squeezenet1_0', 'squeezenet1_1', 'DenseNet', 'densenet121', 'densenet161',
            'densenet169', 'densenet201', 'MobileNet', 'MobileNetV2', 'mobilenet1_0', 'mobilenet0_75', 'mobilenet0_5',
            'mobilenet0_25', 'mobilenet_v2_1_0', 'mobilenet_v2_0_75', 'mobilenet_v2_0_5', 'mobilenet_v2_0_25',
@@ -65,6 +65,16 @@ def _vgg(n, bn=False):
         layers, filters = vgg_spec[n]
         return VGG(layers, filters, batch_norm=bn, **{k: v for k, v in kwargs.items() if k not in ('ctx', 'device', 'root')})
     return f
+
+
+def get_vgg(num_layers, pretrained=False, ctx=None, root=None, **kwargs):
+    """VGG with 11, 13, 16 or 19 layers (``batch_norm=True`` for the normalised variants), as
+    ``gluon/model_zoo/vision/vgg.py:get_vgg``."""
+    if num_layers not in vgg_spec:
+        raise ValueError('VGG has 11, 13, 16 or 19 layers, not %s' % num_layers)
+    layers, filters = vgg_spec[num_layers]
+    kwargs.pop('device', None)
+    return VGG(layers, filters, **kwargs)
 
 
 vgg11, vgg13, vgg16, vgg19 = _vgg(11), _vgg(13), _vgg(16), _vgg(19)
@@ -232,6 +242,18 @@ def _mobilenet(cls, m):
     def f(pretrained=False, **kwargs):
         return cls(m, **{k: v for k, v in kwargs.items() if k not in ('ctx', 'device', 'root')})
     return f
+
+
+def get_mobilenet(multiplier, pretrained=False, ctx=None, root=None, **kwargs):
+    """MobileNet (v1) with the given width multiplier (``gluon/model_zoo/vision/mobilenet.py:get_mobilenet``)."""
+    kwargs.pop('device', None)
+    return MobileNet(multiplier, **kwargs)
+
+
+def get_mobilenet_v2(multiplier, pretrained=False, ctx=None, root=None, **kwargs):
+    """MobileNetV2 with the given width multiplier."""
+    kwargs.pop('device', None)
+    return MobileNetV2(multiplier, **kwargs)
 
 
 mobilenet1_0, mobilenet0_75, mobilenet0_5, mobilenet0_25 = (_mobilenet(MobileNet, m) for m in (1.0, 0.75, 0.5, 0.25))

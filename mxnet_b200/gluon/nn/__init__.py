@@ -1,4 +1,5 @@
 """``gluon.nn`` layers."""
+from ..block import *           # noqa: F401,F403  (Block, HybridBlock, SymbolBlock: `nn.HybridBlock` as in the reference)
 from .activations import *     # noqa: F401,F403
 from .basic_layers import *    # noqa: F401,F403
 from .conv_layers import *     # noqa: F401,F403

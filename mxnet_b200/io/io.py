@@ -21,7 +21,7 @@ from ..ndarray.ndarray import NDArray
 
 __all__ = ['DataDesc', 'DataBatch', 'DataIter', 'NDArrayIter', 'ResizeIter', 'PrefetchingIter', 'MXDataIter',
            'CSVIter', 'LibSVMIter', 'MNISTIter', 'ImageRecordIter', 'ImageRecordUInt8Iter', 'ImageRecordInt8Iter',
-           'ImageDetRecordIter', 'ImageRecordIter_v1']
+           'ImageDetRecordIter', 'ImageRecordIter_v1', 'ImageRecordUInt8Iter_v1']
 
 
 class DataDesc(namedtuple('DataDesc', ['name', 'shape'])):
@@ -699,3 +699,6 @@ class ImageDetRecordIter(ImageRecordIter):
         raw = np.asarray(header.label, dtype=np.float32).reshape(-1)
         label[:min(raw.size, self._pad_width)] = raw[:self._pad_width]
         return img, label
+
+
+ImageRecordUInt8Iter_v1 = ImageRecordUInt8Iter        # the first-generation iterator of the reference: same arguments and batches

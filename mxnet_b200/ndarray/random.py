@@ -5,7 +5,7 @@ from ..ops.random import seed  # noqa: F401
 from .ndarray import NDArray
 
 __all__ = ['uniform', 'normal', 'randn', 'poisson', 'exponential', 'gamma', 'multinomial', 'negative_binomial',
-           'generalized_negative_binomial', 'shuffle', 'randint', 'seed']
+           'generalized_negative_binomial', 'shuffle', 'randint', 'seed', 'binomial', 'categorical']
 
 
 def _helper(scalar_op, sample_op, params, shape, dtype, ctx, out, kwargs):
@@ -53,6 +53,18 @@ def generalized_negative_binomial(mu=1, alpha=1, shape=None, dtype=None, ctx=Non
 
 def multinomial(data, shape=None, get_prob=False, out=None, dtype='int32', **kwargs):
     return _reg.invoke('_sample_multinomial', [data], {'shape': shape or (), 'get_prob': get_prob, 'dtype': dtype}, out=out)
+
+
+def binomial(n=1, p=0.5, shape=None, dtype=None, ctx=None, out=None, **kwargs):
+    """Samples of a binomial distribution with ``n`` trials and success probability ``p`` (scalars, or arrays that give one
+    distribution per element: ``python/mxnet/ndarray/random.py:386``)."""
+    return _helper('_random_binomial', '_sample_binomial', [('n', n), ('p', p)], shape, dtype, ctx, out, kwargs)
+
+
+def categorical(data, shape=None, get_prob=False, out=None, dtype='int32', **kwargs):
+    """Concurrent sampling from the categorical distributions in the rows of ``data`` (probabilities that sum to one along
+    the last axis); with ``get_prob`` also the log-likelihood of the samples (``python/mxnet/ndarray/random.py:552``)."""
+    return _reg.invoke('_sample_categorical', [data], {'shape': shape or (), 'get_prob': get_prob, 'dtype': dtype}, out=out)
 
 
 def shuffle(data, **kwargs):

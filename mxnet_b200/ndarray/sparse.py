@@ -400,3 +400,29 @@ def add_n(*args):
     for a in args[1:]:
         out += a._data
     return _tag(out, args[0]._ctx, args[0].__class__, args[0].stype)
+
+
+def _elementwise(name, torch_fn, keeps_zero_rows):
+    def fn(lhs, rhs):
+        """Element-wise arithmetic with sparse operands (``python/mxnet/ndarray/sparse.py``: add / subtract / multiply /
+        divide).  Two row-sparse arrays (or a row-sparse array and a scalar, for multiply and divide) give a row-sparse
+        result computed on the stored rows only; every other combination uses the dense tensors and returns a dense array."""
+        ls, rs = isinstance(lhs, RowSparseNDArray) and lhs.is_compressed, isinstance(rhs, RowSparseNDArray) and rhs.is_compressed
+        if ls and rs and name in ('add', 'subtract'):
+            return add_n(lhs, rhs if name == 'add' else RowSparseNDArray._from_components((-rhs._comp[0], rhs._comp[1]), rhs.shape,
+                                                                                          rhs._ctx))
+        if ls and not isinstance(rhs, NDArray) and keeps_zero_rows:
+            return RowSparseNDArray._from_components((torch_fn(lhs._comp[0], rhs), lhs._comp[1]), lhs.shape, lhs._ctx)
+        a = lhs._data if isinstance(lhs, NDArray) else lhs
+        b = rhs._data if isinstance(rhs, NDArray) else rhs
+        ctx = lhs._ctx if isinstance(lhs, NDArray) else rhs._ctx
+        return NDArray._from_tensor(torch_fn(a, b), ctx)
+    fn.__name__ = name
+    return fn
+
+
+add = _elementwise('add', torch.add, False)
+subtract = _elementwise('subtract', torch.sub, False)
+multiply = _elementwise('multiply', torch.mul, True)
+divide = _elementwise('divide', torch.true_divide, True)
+__all__ += ['add', 'subtract', 'multiply', 'divide']

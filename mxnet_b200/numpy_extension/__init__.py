@@ -89,3 +89,34 @@ def load(file):
     from ..ndarray.utils import load as _load
     from ..numpy.multiarray import ndarray
     return _load(file, cls=ndarray)
+
+
+# ---- utilities of python/mxnet/numpy_extension/utils.py -----------------------------------------------------------------
+from ..util import set_np_default_dtype, get_cuda_compute_capability   # noqa: E402,F401
+from ..ndarray import contrib_ext as control_flow   # noqa: E402,F401  (foreach / while_loop / cond)
+
+
+def from_dlpack(dlpack):
+    """An ``mx.np.ndarray`` that shares memory with a DLPack capsule (or any object with ``__dlpack__``)."""
+    import torch
+    from ..numpy.multiarray import ndarray
+    return ndarray._from_tensor(torch.utils.dlpack.from_dlpack(dlpack))
+
+
+def from_numpy(array, zero_copy=True):
+    """An ``mx.np.ndarray`` from a ``numpy.ndarray``; with ``zero_copy`` the two share memory (the array must be C-contiguous)."""
+    import torch
+    from ..numpy.multiarray import ndarray
+    if zero_copy and not array.flags['C_CONTIGUOUS']:
+        raise ValueError('Only c-contiguous arrays are supported for zero-copy')
+    return ndarray._from_tensor(torch.from_numpy(array if zero_copy else array.copy()))
+
+
+def to_dlpack_for_read(data):
+    """DLPack capsule of the array once every pending write has finished."""
+    return data.to_dlpack_for_read()
+
+
+def to_dlpack_for_write(data):
+    """DLPack capsule of the array once every pending read and write has finished."""
+    return data.to_dlpack_for_write()

@@ -910,3 +910,25 @@ def new_sym_matrix_with_real_eigvals_2d(n):
 def new_sym_matrix_with_real_eigvals_nd(shape):
     n = int(np.prod(shape[:-2])) if len(shape) > 2 else 1
     return np.array([new_sym_matrix_with_real_eigvals_2d(shape[-1]) for _ in range(n)]).reshape(shape)
+
+
+# ---- names the reference's test_utils re-exports or defines beside its checks ------------------------------------------
+from .util import get_cuda_compute_capability, get_rtc_compile_opts, getenv, setenv, use_np, use_np_default_dtype   # noqa: E402,F401
+from .runtime import Features   # noqa: E402,F401
+from .symbol import Symbol   # noqa: E402,F401
+
+
+def get_max_supported_compute_capability():
+    """Highest compute capability the toolkit used for run-time compilation can target (``major * 10 + minor``)."""
+    return 100
+
+
+def get_dtype_name(dtype):
+    """``'float32'`` for ``np.float32`` / ``'float32'`` / ``np.dtype('float32')``."""
+    import numpy as _np
+    return _np.dtype(dtype).name
+
+
+def np_symbol(sym):
+    """The same graph under NumPy semantics (``Symbol.as_np_ndarray``)."""
+    return sym.as_np_ndarray()

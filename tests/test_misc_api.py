@@ -493,3 +493,41 @@ def test_tensor_inspector(tmp_path):
     f2 = ti.dump_to_file('probe', str(tmp_path))
     assert f1.endswith('probe_1.npy') and f2.endswith('probe_2.npy')
     np.testing.assert_array_equal(np.load(f1), a.asnumpy())
+
+
+def test_reference_import_paths_and_helper_names():
+    """Names a reference user reaches by their import paths: ``gluon.nn.HybridBlock``, per-optimizer modules, model-zoo getters,
+    symbol helpers, npx interchange helpers, random.binomial / categorical."""
+    import numpy as np
+    import mxnet_b200 as mx
+    from mxnet_b200.gluon import nn
+    from mxnet_b200.gluon.model_zoo import vision
+    assert nn.HybridBlock is mx.gluon.HybridBlock and nn.Block is mx.gluon.Block and nn.SymbolBlock is mx.gluon.SymbolBlock
+    from mxnet_b200.optimizer.sgd import SGD
+    from mxnet_b200.optimizer.adamW import AdamW
+    from mxnet_b200.optimizer.contrib import GroupAdaGrad
+    assert SGD is mx.optimizer.SGD and AdamW is mx.optimizer.AdamW and GroupAdaGrad is mx.optimizer.GroupAdaGrad
+    assert type(vision.get_vgg(11)).__name__ == 'VGG' and type(vision.get_mobilenet(0.25)).__name__ == 'MobileNet'
+    assert type(vision.get_mobilenet_v2(0.25)).__name__ == 'MobileNetV2'
+    x, y = mx.sym.Variable('x'), mx.sym.Variable('y')
+    e = mx.sym.maximum(x, 2.0) + mx.sym.minimum(3.0, y) + mx.sym.power(x, y) + mx.sym.pow(2.0, x) + mx.sym.hypot(x, y)
+    got = e.bind(mx.cpu(), {'x': mx.nd.array([1., 3.]), 'y': mx.nd.array([2., 4.])}).forward()[0].asnumpy()
+    expect = np.maximum([1, 3], 2) + np.minimum(3, [2, 4]) + np.power([1., 3.], [2., 4.]) + np.power(2., [1, 3]) + np.hypot([1, 3], [2, 4])
+    np.testing.assert_allclose(got, expect, rtol=1e-6)
+    assert mx.sym.maximum(2, 3) == 3 and mx.sym.minimum(2, 3) == 2
+    parts = mx.sym.split_v2(x, (1, 3)).bind(mx.cpu(), {'x': mx.nd.array([1., 3., 5., 7.])}).forward()
+    assert [p.shape for p in parts] == [(1,), (2,), (1,)]
+    assert float(mx.sym.eye(3).bind(mx.cpu(), {}).forward()[0].asnumpy().trace()) == 3.0
+    np.testing.assert_allclose(mx.sym.linspace(0, 1, 5).bind(mx.cpu(), {}).forward()[0].asnumpy(), np.linspace(0, 1, 5))
+    assert callable(mx.sym.sparse.dot) and callable(mx.sym.sparse.cast_storage)
+    a = mx.npx.from_numpy(np.arange(6.).reshape(2, 3))
+    b = mx.npx.from_dlpack(mx.npx.to_dlpack_for_read(a))
+    assert type(b).__name__ == 'ndarray' and float(b.asnumpy().sum()) == 15.0
+    mx.random.seed(3)
+    draws = mx.random.binomial(10, 0.3, shape=(4000,))
+    assert abs(float(draws.mean().asscalar()) - 3.0) < 0.15
+    c, logp = mx.random.categorical(mx.nd.array([[0.1, 0.9]]), get_prob=True)
+    assert int(c.asnumpy()[0]) in (0, 1) and logp.shape == (1,)
+    assert mx.io.ImageRecordUInt8Iter_v1 is mx.io.ImageRecordUInt8Iter
+    from mxnet_b200 import callback, test_utils
+    assert callable(callback.save_checkpoint) and test_utils.get_dtype_name(np.float16) == 'float16'

@@ -190,3 +190,19 @@ def test_libsvm_batches_stay_compressed_and_train_a_sparse_linear_model(tmp_path
         first = total if first is None else first
         last = total
     assert last < 0.5 * first
+
+
+def test_sparse_elementwise_functions():
+    a = sparse.row_sparse_array((np.ones((2, 3), 'float32'), [0, 3]), shape=(5, 3))
+    b = sparse.row_sparse_array((2 * np.ones((2, 3), 'float32'), [3, 4]), shape=(5, 3))
+    s = sparse.add(a, b)
+    assert s.stype == 'row_sparse' and s.is_compressed
+    np.testing.assert_array_equal(s.indices.asnumpy(), [0, 3, 4])
+    d = sparse.subtract(a, b)
+    np.testing.assert_allclose(d.asnumpy()[[0, 3, 4]], [[1, 1, 1], [-1, -1, -1], [-2, -2, -2]])
+    m = sparse.multiply(a, 3.0)
+    assert m.is_compressed and float(m.asnumpy().sum()) == 18.0
+    q = sparse.divide(b, 4.0)
+    assert q.is_compressed and float(q.asnumpy().sum()) == 3.0
+    dense = sparse.add(a, mx.nd.ones((5, 3)))
+    assert dense.stype == 'default' and float(dense.asnumpy().sum()) == 21.0
