@@ -92,6 +92,35 @@ class BaseSparseNDArray(NDArray):
     def asscipy(self):
         raise NotImplementedError
 
+    def check_format(self, full_check=True):
+        """Raise if the components do not describe a valid array (``MXNDArraySyncCheckFormat``): sorted, in-range,
+        duplicate-free indices, consistent lengths; ``full_check=False`` checks lengths only."""
+        if self._comp is None:
+            return                                      # dense-backed: the components are derived, always consistent
+        if self._stype == 'csr':
+            data, indices, indptr = self._comp
+            if indptr.numel() != self._cshape[0] + 1 or data.numel() != indices.numel() or int(indptr[-1]) != indices.numel() \
+                    or int(indptr[0]) != 0:
+                raise MXNetError('invalid CSR array: inconsistent component lengths')
+            if full_check and indices.numel():
+                if bool((indptr[1:] < indptr[:-1]).any()):
+                    raise MXNetError('invalid CSR array: indptr is not non-decreasing')
+                if int(indices.min()) < 0 or int(indices.max()) >= self._cshape[1]:
+                    raise MXNetError('invalid CSR array: column index out of range')
+                rows = torch.repeat_interleave(torch.arange(self._cshape[0], device=indices.device), indptr[1:] - indptr[:-1])
+                key = rows * self._cshape[1] + indices
+                if bool((key[1:] <= key[:-1]).any()):
+                    raise MXNetError('invalid CSR array: column indices of a row are not strictly increasing')
+        else:
+            data, indices = self._comp
+            if data.shape[0] != indices.numel():
+                raise MXNetError('invalid row-sparse array: inconsistent component lengths')
+            if full_check and indices.numel():
+                if int(indices.min()) < 0 or int(indices.max()) >= self._cshape[0]:
+                    raise MXNetError('invalid row-sparse array: row index out of range')
+                if bool((indices[1:] <= indices[:-1]).any()):
+                    raise MXNetError('invalid row-sparse array: row indices are not strictly increasing')
+
     def tostype(self, stype):
         return cast_storage(self, stype)
 

@@ -362,6 +362,11 @@ class Symbol(object):
             def method(*args, **kwargs):
                 return _op_frontend(op)(self, *args, **kwargs)
             return method
+        if name == 'split_v2':
+            def split_v2(indices_or_sections, axis=0, squeeze_axis=False):
+                from .. import symbol as _sym_mod
+                return _sym_mod.split_v2(self, indices_or_sections, axis, squeeze_axis)
+            return split_v2
         raise AttributeError(name)
 
     # ------------------------------------------------------------------ serialisation

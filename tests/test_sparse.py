@@ -206,3 +206,18 @@ def test_sparse_elementwise_functions():
     assert q.is_compressed and float(q.asnumpy().sum()) == 3.0
     dense = sparse.add(a, mx.nd.ones((5, 3)))
     assert dense.stype == 'default' and float(dense.asnumpy().sum()) == 21.0
+
+
+def test_check_format_rejects_broken_components():
+    good = sparse.csr_matrix(([1., 2., 3.], [0, 2, 1], [0, 2, 3]), shape=(2, 3))
+    good.check_format()
+    bad = sparse.csr_matrix(([1., 2., 3.], [2, 0, 1], [0, 2, 3]), shape=(2, 3))        # unsorted columns in row 0
+    with pytest.raises(mx.MXNetError):
+        bad.check_format()
+    bad.check_format(full_check=False)
+    out_of_range = sparse.csr_matrix(([1.], [5], [0, 1, 1]), shape=(2, 3))
+    with pytest.raises(mx.MXNetError):
+        out_of_range.check_format()
+    rsp = sparse.row_sparse_array((np.ones((2, 2), 'float32'), [1, 3]), shape=(4, 2))
+    rsp.check_format()
+    assert mx.sym.Variable('x').split_v2(2).list_outputs() != []
