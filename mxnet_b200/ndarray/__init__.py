@@ -85,3 +85,42 @@ def eye(N, M=0, k=0, ctx=None, dtype=None, **kwargs):
 def linspace(start, stop, num, endpoint=True, ctx=None, dtype=None):
     return _reg.invoke('_linspace', [], {'start': start, 'stop': stop, 'num': num, 'endpoint': endpoint, 'ctx': ctx,
                                          'dtype': dtype or 'float32'}, kind='nd')
+
+
+def split_v2(ary, indices_or_sections, axis=0, squeeze_axis=False):
+    """Split along ``axis`` into equal sections (an int) or at the given indices (``python/mxnet/ndarray/ndarray.py:split_v2``)."""
+    from ..ops import registry as _r
+    ios = indices_or_sections if isinstance(indices_or_sections, int) else tuple(indices_or_sections)
+    return _r.invoke('_split_v2', [ary], {'indices_or_sections': ios, 'axis': axis, 'squeeze_axis': squeeze_axis})
+
+
+def dtype_np_to_mx(dtype):
+    """Type flag of a NumPy dtype (``include/mxnet/base.h`` type codes)."""
+    from ..base import dtype_flag
+    return dtype_flag(dtype)
+
+
+def dtype_mx_to_np(flag):
+    """NumPy type of a type flag."""
+    from ..base import flag_to_torch, to_numpy_dtype
+    d = to_numpy_dtype(flag_to_torch(int(flag)))
+    return getattr(d, 'type', d)
+
+
+def is_mx_dtype(dtype):
+    """Whether arrays of this dtype can be created."""
+    try:
+        dtype_np_to_mx(dtype)
+        return True
+    except Exception:   # pylint: disable=broad-except
+        return False
+
+
+def get_dtype_name(dtype):
+    import numpy as _np
+    return _np.dtype(dtype).name if str(dtype) != 'bfloat16' else 'bfloat16'
+
+
+def get_dtype_type(dtype):
+    import numpy as _np
+    return _np.dtype(dtype).type

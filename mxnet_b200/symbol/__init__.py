@@ -63,6 +63,33 @@ def _random_extras():
         return _make_op_symbol(_reg.get('_shuffle'), [data], {}, name)
     random.randn, random.categorical, random.shuffle = randn, categorical, shuffle   # noqa: F821
 
+    # Distribution samplers (``python/mxnet/symbol/random.py:_random_helper``): scalar parameters become attributes of the
+    # ``_random_*`` operator, Symbol parameters become inputs of the ``_sample_*`` operator (one distribution per element).
+    def sampler(pub, random_op, sample_op, params, defaults):
+        def fn(*args, shape=None, dtype=None, name=None, **kwargs):
+            values = dict(zip(params, defaults))
+            values.update(dict(zip(params, args)))
+            values.update({k: kwargs.pop(k) for k in list(kwargs) if k in params})
+            given = [values[p] for p in params]
+            if pub == 'exponential':                       # the operator is parametrised by the rate
+                given = [1.0 / given[0]]
+                values = {'lam': given[0]}
+            if any(isinstance(v, Symbol) for v in given):
+                if not all(isinstance(v, Symbol) for v in given):
+                    raise ValueError('Distribution parameters must all have the same type, but got both Symbol and scalars')
+                return _make_op_symbol(_reg.get(sample_op), given, {'shape': tuple(shape) if shape else (), 'dtype': dtype}, name)
+            attrs = dict(values, shape=tuple(shape) if shape is not None and not isinstance(shape, int) else
+                         ((shape,) if isinstance(shape, int) else (1,)), dtype=dtype or 'float32')
+            return _make_op_symbol(_reg.get(random_op), [], attrs, name)
+        fn.__name__ = pub
+        return fn
+    for pub, params, defaults in (('uniform', ('low', 'high'), (0.0, 1.0)), ('normal', ('loc', 'scale'), (0.0, 1.0)),
+                                  ('poisson', ('lam',), (1.0,)), ('exponential', ('scale',), (1.0,)),
+                                  ('gamma', ('alpha', 'beta'), (1.0, 1.0)), ('negative_binomial', ('k', 'p'), (1, 1.0)),
+                                  ('generalized_negative_binomial', ('mu', 'alpha'), (1.0, 1.0)), ('binomial', ('n', 'p'), (1, 0.5))):
+        if _reg.has('_random_' + pub) and _reg.has('_sample_' + pub):
+            setattr(random, pub, sampler(pub, '_random_' + pub, '_sample_' + pub, params, defaults))   # noqa: F821
+
 
 _random_extras()
 
@@ -121,3 +148,24 @@ def _legacy_helpers():
 
 
 _legacy_helpers()
+
+
+def _contrib_rand_zipfian():
+    import math
+
+    def rand_zipfian(true_classes, num_sampled, range_max):
+        """Symbolic form of ``mx.nd.contrib.rand_zipfian`` (``python/mxnet/symbol/contrib.py``): (samples, expected count of the
+        true classes, expected count of the samples) under P(class) = log((class + 2) / (class + 1)) / log(range_max + 1)."""
+        mod = _sys.modules[__name__]
+        log_range = math.log(range_max + 1)
+        rand = mod.random.uniform(0, log_range, shape=(num_sampled,), dtype='float64')
+        sampled = mod.cast(mod.exp(rand) - 1, dtype='int64') % range_max
+        true_cls = mod.cast(true_classes, dtype='float64')
+        expected_true = mod.log((true_cls + 2.0) / (true_cls + 1.0)) / log_range * num_sampled
+        sampled64 = mod.cast(sampled, dtype='float64')
+        expected_sampled = mod.log((sampled64 + 2.0) / (sampled64 + 1.0)) / log_range * num_sampled
+        return sampled, expected_true, expected_sampled
+    contrib.rand_zipfian = rand_zipfian   # noqa: F821  (contrib is set by _populate)
+
+
+_contrib_rand_zipfian()

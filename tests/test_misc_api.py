@@ -531,3 +531,48 @@ def test_reference_import_paths_and_helper_names():
     assert mx.io.ImageRecordUInt8Iter_v1 is mx.io.ImageRecordUInt8Iter
     from mxnet_b200 import callback, test_utils
     assert callable(callback.save_checkpoint) and test_utils.get_dtype_name(np.float16) == 'float16'
+
+
+def test_contrib_rand_zipfian_and_multi_tensor_lamb_wrappers():
+    import numpy as np
+    import mxnet_b200 as mx
+    mx.random.seed(5)
+    samples, exp_true, exp_sampled = mx.nd.contrib.rand_zipfian(mx.nd.array([3, 0]), 2000, 50)
+    s = samples.asnumpy()
+    assert s.dtype == np.int64 and s.min() >= 0 and s.max() < 50
+    log_range = np.log(51.0)
+    np.testing.assert_allclose(exp_true.asnumpy(), np.log(np.array([5 / 4, 2.0])) / log_range * 2000, rtol=1e-10)
+    np.testing.assert_allclose(exp_sampled.asnumpy(), np.log((s + 2.0) / (s + 1.0)) / log_range * 2000, rtol=1e-10)
+    assert abs((s == 0).mean() - np.log(2.0) / log_range) < 0.04           # the most frequent class
+    t = mx.sym.Variable('t')
+    outs = mx.sym.Group(list(mx.sym.contrib.rand_zipfian(t, 8, 5))).bind(mx.cpu(), {'t': mx.nd.array([3])}).forward()
+    assert outs[0].shape == (8,) and outs[1].shape == (1,) and outs[2].shape == (8,)
+    w = [mx.nd.ones((3,)), mx.nd.ones((2, 2))]
+    g = [mx.nd.ones((3,)) * 0.1, mx.nd.ones((2, 2)) * 0.2]
+    m = [mx.nd.zeros((3,)), mx.nd.zeros((2, 2))]
+    v = [mx.nd.zeros((3,)), mx.nd.zeros((2, 2))]
+    mx.nd.contrib.multi_lamb_update(w, g, m, v, [1, 1], [0.1, 0.1], [0.0, 0.0])
+    np.testing.assert_allclose(w[0].asnumpy(), 0.9, rtol=1e-5)             # unit trust ratio step of size lr
+    assert [p.shape for p in mx.nd.split_v2(mx.nd.ones((6, 2)), 3)] == [(2, 2)] * 3
+    assert mx.nd.dtype_mx_to_np(mx.nd.dtype_np_to_mx(np.float16)) is np.float16
+
+
+def test_symbolic_samplers_take_scalars_or_symbols():
+    """``mx.sym.random.<dist>``: scalar parameters are attributes (no graph inputs), Symbol parameters are inputs with one
+    distribution per element (python/mxnet/symbol/random.py)."""
+    import numpy as np
+    import mxnet_b200 as mx
+    mx.random.seed(11)
+    u = mx.sym.random.uniform(2.0, 4.0, shape=(3000,))
+    assert u.list_arguments() == []
+    vals = u.bind(mx.cpu(), {}).forward()[0].asnumpy()
+    assert vals.min() >= 2.0 and vals.max() <= 4.0 and abs(vals.mean() - 3.0) < 0.05
+    assert abs(mx.sym.random.exponential(2.0, shape=(6000,)).bind(mx.cpu(), {}).forward()[0].asnumpy().mean() - 2.0) < 0.1
+    assert abs(mx.sym.random.poisson(3.0, shape=(6000,)).bind(mx.cpu(), {}).forward()[0].asnumpy().mean() - 3.0) < 0.1
+    lo, hi = mx.sym.Variable('lo'), mx.sym.Variable('hi')
+    per = mx.sym.random.uniform(lo, hi, shape=(500,))
+    assert per.list_arguments() == ['lo', 'hi']
+    out = per.bind(mx.cpu(), {'lo': mx.nd.array([0., 10.]), 'hi': mx.nd.array([1., 11.])}).forward()[0].asnumpy()
+    assert out.shape == (2, 500) and out[0].max() <= 1.0 and out[1].min() >= 10.0
+    with pytest.raises(ValueError):
+        mx.sym.random.uniform(lo, 1.0)
