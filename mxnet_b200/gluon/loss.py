@@ -242,7 +242,7 @@ class PoissonNLLLoss(Loss):
             stirling = stirling * (target > 1)
             loss = loss + stirling
         loss = _apply_weighting(loss, self._weight, sample_weight)
-        return _op('mean', [loss])
+        return _mean_except(loss, self._batch_axis)      # one value per sample, as the other losses
 
 
 class CosineEmbeddingLoss(Loss):
@@ -253,9 +253,11 @@ class CosineEmbeddingLoss(Loss):
     def forward(self, input1, input2, label, sample_weight=None):
         input1 = _reshape_like(input1, input2)
         cos = self._cosine_similarity(input1, input2)
-        label = label.reshape(-1, 1) if label.ndim == 1 else label
-        loss = _op('where', [label == 1, 1 - cos, _op('relu', [cos - self._margin])])
-        return _apply_weighting(loss, self._weight, sample_weight)
+        label = _reshape_like(label, cos)
+        # dissimilar pairs: the part of the similarity above the margin, at most 1 - margin
+        loss = _op('where', [label == 1, 1 - cos, _op('clip', [cos - self._margin], a_min=0.0, a_max=1.0 - self._margin)])
+        loss = _apply_weighting(loss, self._weight, sample_weight)
+        return _mean_except(loss, self._batch_axis)      # one value per pair
 
     def _cosine_similarity(self, x, y, axis=-1):
         x_norm = _op('norm', [x], axis=axis).reshape(-1, 1)

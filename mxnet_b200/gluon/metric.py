@@ -293,8 +293,10 @@ class F1(EvalMetric):
         labels, preds = check_label_shapes(labels, preds, True)
         for label, pred in zip(labels, preds):
             self.metrics.update_stats(label, pred)
-        self.sum_metric = self.metrics.get_fscore(self.average)
-        self.num_inst = 1 if self.metrics.total_examples else 0
+        # the running score weighted by the number of examples seen, so that sum_metric / num_inst is the score and
+        # num_inst counts examples (python/mxnet/gluon/metric.py, F1.update)
+        self.sum_metric = self.metrics.get_fscore(self.average) * self.metrics.total_examples
+        self.num_inst = self.metrics.total_examples
 
     def get(self):
         if self.metrics.num_classes is None:
@@ -339,8 +341,8 @@ class MCC(EvalMetric):
         labels, preds = check_label_shapes(labels, preds, True)
         for label, pred in zip(labels, preds):
             self._metrics.update_stats(label, pred)
-        self.sum_metric = self._metrics.matthewscc()
-        self.num_inst = 1
+        self.sum_metric = self._metrics.matthewscc() * self._metrics.total_examples
+        self.num_inst = self._metrics.total_examples
 
     def get(self):
         if self._metrics.num_classes is None:

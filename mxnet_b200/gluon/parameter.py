@@ -33,8 +33,9 @@ class DeferredInitializationError(MXNetError):
 def _shape_known(shape):
     if shape is None:
         return False
-    unknown = -1 if _state.state.np_shape else 0
-    return all(s > 0 or (s == 0 and _state.state.np_shape) for s in shape) and unknown not in shape and -1 not in shape
+    # in a parameter's stored shape 0 (and -1) always mean "not known yet", under NumPy shape semantics too (the reference's
+    # Parameter.shape maps its zeros to -1 there before asking shape_is_known, python/mxnet/gluon/parameter.py)
+    return all(s > 0 for s in shape)
 
 
 class Parameter(object):

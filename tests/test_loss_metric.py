@@ -74,7 +74,7 @@ def test_bce_kl_cosine_triplet_poisson():
     assert_almost_equal(gluon.loss.TripletLoss(margin=1.0)(nd.array(a), nd.array(pos), nd.array(neg)).asnumpy(), ref, rtol=1e-4)
     rate, tgt = np.abs(rng.randn(4, 3)).astype('float32') + 0.1, rng.poisson(2, (4, 3)).astype('float32')
     out = gluon.loss.PoissonNLLLoss(from_logits=False)(nd.array(rate), nd.array(tgt))
-    assert_almost_equal(out.asnumpy(), (rate - tgt * np.log(rate + 1e-8)).mean(), rtol=1e-4)
+    assert_almost_equal(out.asnumpy(), (rate - tgt * np.log(rate + 1e-8)).mean(1), rtol=1e-4)     # one value per sample
 
 
 def test_ctc_loss_simple_case():
