@@ -112,13 +112,26 @@ def mark_variables(variables, gradients, grad_reqs='write'):
         grad_reqs = [grad_reqs] * len(variables)
     for var, g, req in zip(variables, gradients, grad_reqs):
         t = var._data
-        if t.grad_fn is not None or (t.requires_grad and not t.is_leaf):
-            t = t.detach()
-            var._data = t
         old = getattr(var, '_hook', None)
         if old is not None:
             old.remove()
             var._hook = None
+        if t.grad_fn is not None and req != 'null' and g is not None:
+            # An array produced by a recorded operator stays in its graph and keeps the gradient that flows through it
+            # (``Imperative::MarkVariables`` on an array that already has autograd information, src/imperative/imperative.cc):
+            # the hook copies (or adds) that gradient into the attached buffer in every backward pass.
+            var._grad_req = req
+            var._grad = g
+            var._fresh_grad = False
+            var._grad_pass = -1
+            var._hook = t.register_hook(_make_retain_hook(weakref.ref(var)))
+            continue
+        if t.grad_fn is not None and req == 'null':
+            var._grad_req, var._grad = 'null', None      # drop_grad of an intermediate: it stays part of its graph
+            continue
+        if t.grad_fn is not None or (t.requires_grad and not t.is_leaf):
+            t = t.detach()
+            var._data = t
         var._grad_req = req
         if req == 'null':
             var._grad = None
@@ -134,6 +147,21 @@ def mark_variables(variables, gradients, grad_reqs='write'):
         t.grad = g._data
         var._grad_pass = -1
         var._hook = t.register_hook(_make_hook(weakref.ref(var)))
+
+
+def _make_retain_hook(ref):
+    def hook(g):
+        var = ref()
+        if var is None or var._grad is None:
+            return None
+        with torch.no_grad():
+            if var._grad_req == 'add':
+                var._grad._data.add_(g)
+            else:
+                var._grad._data.copy_(g)
+        var._fresh_grad = True
+        return None
+    return hook
 
 
 def mark_grads_consumed(arrays):
@@ -166,6 +194,10 @@ def backward(heads, head_grads=None, retain_graph=False, train_mode=True):  # py
             raise MXNetError('Cannot differentiate node because it is not in a computational graph. '
                              'You need to set is_recording to true or use autograd.record() to save '
                              'computational graphs for backward.')
+    for t in tensors:
+        if getattr(t, '_mx_graph_freed', False):
+            raise MXNetError('The computational graph of this array was freed by an earlier backward pass; '
+                             'pass retain_graph=True to differentiate it more than once.')
     _pass_id[0] += 1
     grads = _head_grads(heads, head_grads)
     prev = set_training(train_mode)
@@ -173,6 +205,10 @@ def backward(heads, head_grads=None, retain_graph=False, train_mode=True):  # py
         torch.autograd.backward(tensors, grads, retain_graph=retain_graph)
     finally:
         set_training(prev)
+    if not retain_graph:
+        for t in tensors:
+            if t.grad_fn is not None:
+                t._mx_graph_freed = True         # the reference frees the recorded graph here (MXAutogradBackwardEx)
 
 
 def grad(heads, variables, head_grads=None, retain_graph=None, create_graph=False, train_mode=True):  # pylint: disable=redefined-outer-name

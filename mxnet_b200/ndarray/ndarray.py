@@ -266,7 +266,15 @@ class NDArray(object):
         (``src/imperative/imperative.cc:143-172``).
         """
         from .. import autograd
-        grad = self.__class__._from_tensor(torch.zeros_like(self._data), self._ctx)
+        stype = stype or getattr(self, '_stype', 'default')
+        if stype in ('csr', 'row_sparse'):
+            from . import sparse
+            cls = sparse.CSRNDArray if stype == 'csr' else sparse.RowSparseNDArray
+            grad = sparse._tag(torch.zeros_like(self._data), self._ctx, cls, stype)       # gradient with the asked storage type
+        else:
+            from .ndarray import NDArray as _Dense
+            base = self.__class__ if getattr(self, '_stype', 'default') == 'default' else _Dense
+            grad = base._from_tensor(torch.zeros_like(self._data), self._ctx)
         autograd.mark_variables([self], [grad], grad_req)
 
     @property
@@ -275,6 +283,7 @@ class NDArray(object):
 
     def detach(self):
         r = self.__class__._from_tensor(self._data.detach(), self._ctx)
+        r._stype = getattr(self, '_stype', 'default')
         return r
 
     def backward(self, out_grad=None, retain_graph=False, train_mode=True):

@@ -932,3 +932,13 @@ def get_dtype_name(dtype):
 def np_symbol(sym):
     """The same graph under NumPy semantics (``Symbol.as_np_ndarray``)."""
     return sym.as_np_ndarray()
+
+
+# Scripts written against the reference do ``from mxnet.test_utils import *`` and then use ``mx``, ``nd``, ``np`` (NumPy), ``sym``
+# that the reference module happens to import at its top; the same names are provided here.
+import sys as _sys   # noqa: E402
+mx = _sys.modules[__name__.rsplit('.', 1)[0]]   # the package itself
+from . import ndarray as nd, symbol as sym   # noqa: E402,F401
+from .ndarray import array   # noqa: E402,F401
+from .symbol import Symbol   # noqa: E402,F401,F811
+import numpy.testing as npt, numpy.random as rnd   # noqa: E402,F401
