@@ -283,3 +283,40 @@ def register_error(func_name=None, cls=None):
         _registered_errors[func_name if isinstance(func_name, str) else mycls.__name__] = mycls
         return mycls
     return register(cls) if cls is not None else register
+
+
+# ---- small names scripts import from ``mxnet.base`` ----------------------------------------------------------------------
+def py_str(x):
+    """Text of a bytes object (``c_char_p`` results in the reference's ctypes layer)."""
+    return x.decode('utf-8') if isinstance(x, (bytes, bytearray)) else str(x)
+
+
+def _as_list(obj):
+    """``obj`` if it is a list or tuple, else ``[obj]``."""
+    return obj if isinstance(obj, (list, tuple)) else [obj]
+
+
+def c2pyerror(err_msg):
+    """(message, error class) of an error string produced by the native side: ``'ValueError: ...'`` selects a registered
+    Python error class, anything else is an :class:`MXNetError`."""
+    head, _, rest = str(err_msg).partition(':')
+    cls = error_types.get(head.strip()) if head.strip().isidentifier() else None
+    return (rest.strip() if cls is not None else str(err_msg)), (cls or MXNetError)
+
+
+def get_last_ffi_error():
+    """The last error recorded by the native runtime as an exception object."""
+    from . import csrc
+    try:
+        msg = csrc.runtime.last_error()
+    except Exception:   # pylint: disable=broad-except
+        msg = ''
+    text, cls = c2pyerror(msg)
+    return cls(text)
+
+
+import numpy as _np   # noqa: E402
+mx_real_t = _np.float32
+import ctypes as _ct
+mx_uint, mx_int, mx_float = _ct.c_uint, _ct.c_int, _ct.c_float
+error_types = _registered_errors      # the reference's name for the registry filled by register_error

@@ -292,6 +292,11 @@ class Block(object):
         seen = set()
         hooks = []
 
+        def _no_active(block):
+            assert not (isinstance(block, HybridBlock) and block._active), \
+                '"{}" must not be hybridized to print summary.'.format(type(block).__name__)
+        self.apply(_no_active)
+
         def _get_shape_str(args):
             flat, _ = _flatten(args, 'output')
             shapes = [x.shape if isinstance(x, NDArray) else x for x in flat]

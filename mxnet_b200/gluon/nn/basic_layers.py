@@ -300,6 +300,9 @@ class LayerNorm(HybridBlock):
 
     def forward(self, data):
         ctx = data.context
+        known = self.gamma.shape[0] if self.gamma.shape else 0
+        assert known <= 0 or known == data.shape[self._axis], \
+            'LayerNorm was built for %d channels along axis %d but the input has %d' % (known, self._axis, data.shape[self._axis])
         return _op('LayerNorm', [data, self.gamma.data(ctx), self.beta.data(ctx)], axis=self._axis, eps=self._epsilon)
 
     def infer_shape(self, data, *args):

@@ -48,6 +48,7 @@ class Parameter(object):
         self._grad = None
         self._ctx_list = None
         self._deferred_init = ()
+        self._trainer = None                 # weak reference to the Trainer that updates this parameter
         self._differentiable = differentiable
         self._allow_deferred_init = allow_deferred_init
         self._grad_req = None
@@ -220,7 +221,14 @@ class Parameter(object):
             return
         self._grad = OrderedDict()
         for c, arr in self._data.items():
-            g = arr.__class__._from_tensor(torch.zeros_like(arr._data), c)
+            if self._grad_stype != 'default':
+                # the gradient buffer carries the asked storage type (dense-backed: autograd writes the dense tensor, the
+                # optimizer's lazy update and the key-value store read its non-zero rows)
+                from ..ndarray import sparse
+                cls = sparse.RowSparseNDArray if self._grad_stype == 'row_sparse' else sparse.CSRNDArray
+                g = sparse._tag(torch.zeros_like(arr._data), c, cls, self._grad_stype)
+            else:
+                g = arr.__class__._from_tensor(torch.zeros_like(arr._data), c)
             g._ctx = c
             self._grad[c] = g
             autograd.mark_variables([arr], [g], self.grad_req)
@@ -295,6 +303,12 @@ class Parameter(object):
     # ------------------------------------------------------------------ access
     def data(self, ctx=None, device=None):
         ctx = ctx if ctx is not None else device
+        if self._stype != 'default':
+            raise RuntimeError("Cannot return a copy of Parameter '%s' on ctx %s via data() because its storage type is %s. "
+                               "Please use row_sparse_data() instead." % (self.name, str(ctx), self._stype))
+        return self._dense_data(ctx)
+
+    def _dense_data(self, ctx=None):
         arr = self._check_and_get(self._data, ctx)
         want_np = is_np_array()
         if want_np != (arr._kind == 'np'):
@@ -304,6 +318,9 @@ class Parameter(object):
         return arr
 
     def list_data(self):
+        if self._stype != 'default':
+            raise RuntimeError("Cannot return copies of Parameter '%s' on all devices via list_data() because its storage "
+                               "type is %s. Please use row_sparse_data() instead." % (self.name, self._stype))
         return list(self._check_and_get(self._data, list))
 
     def grad(self, ctx=None, device=None):
@@ -343,7 +360,8 @@ class Parameter(object):
             for arr in self._data.values():
                 arr._data.copy_(src.to(arr._data.device))
 
-    def reset_ctx(self, ctx):
+    def reset_ctx(self, ctx=None, device=None):
+        ctx = ctx if ctx is not None else device
         if ctx is None:
             ctx = [current_device()]
         if isinstance(ctx, Device):
@@ -380,15 +398,33 @@ class Parameter(object):
                                    else self.init.dumps(), stype=self._stype)
         return self._var
 
+    def _set_trainer(self, trainer):
+        """Remember (weakly) the Trainer that updates this parameter; a sparse parameter accepts one Trainer only, because its
+        rows are pulled through that Trainer's key-value store."""
+        import weakref
+        if self._stype != 'default' and self._trainer and trainer and self._trainer() is not trainer:
+            raise RuntimeError("Failed to set the trainer for Parameter '%s' because it was already set. More than one "
+                               "trainers for a %s Parameter is not supported." % (self.name, self._stype))
+        self._trainer = weakref.ref(trainer) if trainer is not None else None
+
     def row_sparse_data(self, row_id):
         if self._stype != 'row_sparse':
             raise RuntimeError("Cannot return a copy of Parameter %s via row_sparse_data() because its storage "
                                "type is %s. Please use data() instead." % (self.name, self._stype))
+        if self._trainer is None or self._trainer() is None:
+            raise RuntimeError("Cannot get row_sparse data for Parameter '%s' when no Trainer is created with it." % self.name)
         from ..ndarray import sparse
-        return sparse.retain(sparse.cast_storage(self.data(row_id.context), 'row_sparse'), row_id)
+        return sparse.retain(sparse.cast_storage(self._dense_data(row_id.context), 'row_sparse'), row_id)
 
     def list_row_sparse_data(self, row_id):
-        return [self.row_sparse_data(row_id)]
+        if self._stype != 'row_sparse':
+            raise RuntimeError("Cannot return copies of Parameter '%s' on all devices via list_row_sparse_data() because its "
+                               "storage type is %s. Please use data() instead." % (self.name, self._stype))
+        if self._trainer is None or self._trainer() is None:
+            raise RuntimeError("Cannot get row_sparse data for Parameter '%s' when no Trainer is created with it." % self.name)
+        from ..ndarray import sparse
+        return [sparse.retain(sparse.cast_storage(arr, 'row_sparse'), row_id.as_in_context(arr.context))
+                for arr in self._check_and_get(self._data, list)]
 
 
 class Constant(Parameter):

@@ -49,7 +49,7 @@ class Trainer(object):
                 continue
             self._param2idx[param._uuid] = len(self._params)
             self._params.append(param)
-            param._trainer = self
+            param._set_trainer(self)
             if param._stype != 'default':
                 self._contains_sparse_weight = True
             if param._grad_stype != 'default':

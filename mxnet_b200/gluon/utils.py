@@ -20,16 +20,15 @@ def split_data(data, num_slice, batch_axis=0, even_split=True):
         raise ValueError("data with shape %s cannot be evenly split into %d slices along axis %d. Use a batch size "
                          "that's multiple of %d or set even_split=False to allow uneven partitioning of data." % (
                              str(data.shape), num_slice, batch_axis, num_slice))
-    n_each = size // num_slice
-    if not even_split and size < num_slice:
-        n_each, num_slice = 1, size
-    slices = []
-    for i in range(num_slice):
-        lo = i * n_each
-        hi = (i + 1) * n_each if i < num_slice - 1 else size
+    # uneven partitions follow numpy.array_split: the first (size % num_slice) slices get one element more
+    n_each, extras = divmod(size, num_slice)
+    sizes = extras * [n_each + 1] + (num_slice - extras) * [n_each]
+    slices, lo = [], 0
+    for n in sizes:
         idx = [slice(None)] * data.ndim
-        idx[batch_axis] = slice(lo, hi)
+        idx[batch_axis] = slice(lo, lo + n)
         slices.append(data[tuple(idx)])
+        lo += n
     return slices
 
 

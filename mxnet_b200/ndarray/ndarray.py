@@ -793,3 +793,9 @@ def _slice_assign_scalar(self, value, begin, end, step):
 
 NDArray.drop_grad = _drop_grad
 NDArray.slice_assign_scalar = _slice_assign_scalar
+
+
+# storage-type codes of include/mxnet/ndarray.h (names scripts import from this module)
+_STORAGE_TYPE_UNDEFINED, _STORAGE_TYPE_DEFAULT, _STORAGE_TYPE_ROW_SPARSE, _STORAGE_TYPE_CSR = -1, 0, 1, 2
+_STORAGE_TYPE_STR_TO_ID = {'undefined': -1, 'default': 0, 'row_sparse': 1, 'csr': 2}
+_STORAGE_TYPE_ID_TO_STR = {v: k for k, v in _STORAGE_TYPE_STR_TO_ID.items()}

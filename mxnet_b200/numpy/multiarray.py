@@ -137,6 +137,11 @@ def _shape(shape):
     return tuple(int(s) for s in shape)
 
 
+def _like(opname, a, attrs, out, ctx):
+    r = _reg.invoke(opname, [a], attrs, out=out, kind='np')
+    return r.as_in_context(ctx) if ctx is not None and out is None else r
+
+
 def _init(opname, **attrs):
     return _reg.invoke(opname, [], attrs, kind='np')
 
@@ -166,10 +171,10 @@ def full(shape, fill_value, dtype=None, order='C', ctx=None, device=None, out=No
     return r
 
 
-def zeros_like(a, dtype=None, order='C', ctx=None, out=None): return _reg.invoke('_npi_zeros_like', [a], {'dtype': dtype}, out=out, kind='np')
-def ones_like(a, dtype=None, order='C', ctx=None, out=None): return _reg.invoke('_npi_ones_like', [a], {'dtype': dtype}, out=out, kind='np')
+def zeros_like(a, dtype=None, order='C', ctx=None, out=None, device=None): return _like('_npi_zeros_like', a, {'dtype': dtype}, out, ctx or device)
+def ones_like(a, dtype=None, order='C', ctx=None, out=None, device=None): return _like('_npi_ones_like', a, {'dtype': dtype}, out, ctx or device)
 def empty_like(prototype, dtype=None, order='C', subok=False, shape=None): return zeros_like(prototype, dtype)
-def full_like(a, fill_value, dtype=None, order='C', ctx=None, out=None): return _reg.invoke('_npi_full_like', [a], {'fill_value': fill_value, 'dtype': dtype}, out=out, kind='np')
+def full_like(a, fill_value, dtype=None, order='C', ctx=None, out=None, device=None): return _like('_npi_full_like', a, {'fill_value': fill_value, 'dtype': dtype}, out, ctx or device)
 
 
 def arange(start, stop=None, step=1, dtype=None, ctx=None, device=None):

@@ -133,6 +133,10 @@ def invoke(op, args, attrs, out=None, kind=None):
             tensors.append(a)
     if kind is None:
         kind = 'np' if st.np_array else 'nd'
+    if ctx is None and attrs:
+        c = attrs.get('ctx')
+        if c is not None and hasattr(c, 'device_typeid'):
+            ctx = c                       # a creation operator: the result carries the device it was asked for (cpu(1) stays cpu(1))
     hook = _state.amp_hook
     if hook is not None and not st.opt_constraints & 1:
         tensors = hook(op.name, tensors)
