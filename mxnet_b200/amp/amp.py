@@ -61,6 +61,9 @@ def _hook(opname, tensors):
     return tensors
 
 
+from ..base import bfloat16   # noqa: E402,F401  (the dtype name scripts import from this module)
+
+
 def init(target_dtype='float16', target_precision_ops=None, conditional_fp32_ops=None, fp32_ops=None, layout_optimization=False):
     """Turn on AMP for all subsequently executed operators."""
     global _amp_initialized, _target, _sets

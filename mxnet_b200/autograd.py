@@ -140,7 +140,11 @@ def mark_variables(variables, gradients, grad_reqs='write'):
                 t.grad = None
             continue
         if not (t.dtype.is_floating_point or t.dtype.is_complex):
-            raise MXNetError('attach_grad needs a floating point array, got %s' % t.dtype)
+            # integer arrays may be marked too (the reference allows it); nothing differentiable flows into them, so the
+            # attached buffer simply stays zero
+            var._grad = g
+            var._fresh_grad = False
+            continue
         var._grad = g
         var._fresh_grad = False
         t.requires_grad_(True)

@@ -340,6 +340,10 @@ class NDArray(object):
         with torch.no_grad():
             if isinstance(v, torch.Tensor):
                 v = v.to(self._data.dtype)
+            elif isinstance(v, _np.generic):
+                v = v.item()                                   # numpy scalars (np.float32(1.5), ...)
+            elif isinstance(v, _np.ndarray):
+                v = torch.as_tensor(v, dtype=self._data.dtype, device=self._data.device)
             self._data[k] = v
 
     # ------------------------------------------------------------------ shape manipulation
@@ -350,27 +354,43 @@ class NDArray(object):
             shape = kwargs.get('shape')
         reverse = kwargs.get('reverse', False)
         if self._kind == 'nd':
-            return _reg.invoke('Reshape', [self], {'shape': tuple(shape), 'reverse': reverse})
+            try:
+                return _reg.invoke('Reshape', [self], {'shape': tuple(shape), 'reverse': reverse})
+            except MXNetError as e:
+                if 'invalid for input of size' in str(e):
+                    raise ValueError('cannot reshape array of size %d into shape %s' % (self.size, str(tuple(shape)))) from e
+                raise
         return _reg.invoke('_npi_reshape', [self], {'newshape': tuple(shape)})
 
     def reshape_like(self, other):
         return _reg.invoke('reshape_like', [self, other], {})
 
-    def transpose(self, *axes):
+    def transpose(self, *axes, **kwargs):
+        if not axes and 'axes' in kwargs:
+            axes = (kwargs['axes'],)
         if len(axes) == 1 and (isinstance(axes[0], (list, tuple)) or axes[0] is None):
             axes = axes[0]
         return _reg.invoke('transpose', [self], {'axes': tuple(axes) if axes else None})
 
+    # flatten / expand_dims / squeeze return a copy; with inplace=True a view that shares memory with this array
+    # (python/mxnet/ndarray/ndarray.py: the inplace forms reshape the same storage)
+    def _own(self, result, inplace):
+        if inplace or self._kind == 'np' or result._data.requires_grad:
+            return result
+        if result._data.untyped_storage().data_ptr() == self._data.untyped_storage().data_ptr():
+            result._data = result._data.clone()
+        return result
+
     def flatten(self, inplace=False):
         if self._kind == 'np':
             return self.reshape(-1)
-        return _reg.invoke('Flatten', [self], {})
+        return self._own(_reg.invoke('Flatten', [self], {}), inplace)
 
     def expand_dims(self, axis, inplace=False):
-        return _reg.invoke('expand_dims', [self], {'axis': axis})
+        return self._own(_reg.invoke('expand_dims', [self], {'axis': axis}), inplace)
 
     def squeeze(self, axis=None, inplace=False):
-        return _reg.invoke('squeeze', [self], {'axis': axis})
+        return self._own(_reg.invoke('squeeze', [self], {'axis': axis}), inplace)
 
     def swapaxes(self, dim1, dim2):
         return _reg.invoke('SwapAxis', [self], {'dim1': dim1, 'dim2': dim2})
@@ -539,8 +559,8 @@ class NDArray(object):
     def slice_axis(self, axis, begin, end):
         return _reg.invoke('slice_axis', [self], {'axis': axis, 'begin': begin, 'end': end})
 
-    def slice_like(self, other, axes=None):
-        return _reg.invoke('slice_like', [self, other], {'axes': axes})
+    def slice_like(self, other=None, axes=None, shape_like=None):
+        return _reg.invoke('slice_like', [self, other if other is not None else shape_like], {'axes': axes})
 
     def softmax(self, axis=-1, **kw):
         kw['axis'] = axis
@@ -560,10 +580,10 @@ class NDArray(object):
         with torch.no_grad():
             self._data.fill_(value)
 
-    def all(self, axis=None, keepdims=False):
+    def all(self, axis=None, keepdims=False, out=None, **_ignored):
         return _reg.invoke('_npi_all', [self], {'axis': axis, 'keepdims': keepdims})
 
-    def any(self, axis=None, keepdims=False):
+    def any(self, axis=None, keepdims=False, out=None, **_ignored):
         return _reg.invoke('_npi_any', [self], {'axis': axis, 'keepdims': keepdims})
 
     def std(self, axis=None, dtype=None, ddof=0, keepdims=False):
@@ -671,7 +691,11 @@ def empty(shape, ctx=None, dtype=None, device=None, stype=None):
                                             device=ctx.torch_device), ctx)
 
 
-def zeros(shape, ctx=None, dtype=None, stype=None, device=None, **kwargs):
+def zeros(shape, ctx=None, dtype=None, stype=None, device=None, out=None, **kwargs):
+    if out is not None:
+        with torch.no_grad():
+            out._data.zero_()
+        return out
     ctx = ctx or device or current_device()
     if isinstance(shape, integer_types):
         shape = (shape,)
@@ -682,7 +706,11 @@ def zeros(shape, ctx=None, dtype=None, stype=None, device=None, **kwargs):
                                             device=ctx.torch_device), ctx)
 
 
-def ones(shape, ctx=None, dtype=None, device=None, **kwargs):
+def ones(shape, ctx=None, dtype=None, device=None, out=None, **kwargs):
+    if out is not None:
+        with torch.no_grad():
+            out._data.fill_(1)
+        return out
     ctx = ctx or device or current_device()
     if isinstance(shape, integer_types):
         shape = (shape,)
@@ -717,6 +745,12 @@ def concatenate(arrays, axis=0, always_copy=True):
 
 
 def moveaxis(tensor, source, destination):
+    nd_ = tensor._data.dim()
+    for v in ([source] if isinstance(source, int) else list(source)) + ([destination] if isinstance(destination, int) else list(destination)):
+        if not -nd_ <= int(v) < nd_:
+            raise ValueError('Source/destination axis %d is out of bounds for an array with %d dimensions' % (int(v), nd_))
+    source = source if isinstance(source, int) else tuple(int(v) for v in source)
+    destination = destination if isinstance(destination, int) else tuple(int(v) for v in destination)
     return tensor.__class__._from_tensor(torch.movedim(tensor._data, source, destination), tensor._ctx)
 
 
@@ -799,3 +833,4 @@ NDArray.slice_assign_scalar = _slice_assign_scalar
 _STORAGE_TYPE_UNDEFINED, _STORAGE_TYPE_DEFAULT, _STORAGE_TYPE_ROW_SPARSE, _STORAGE_TYPE_CSR = -1, 0, 1, 2
 _STORAGE_TYPE_STR_TO_ID = {'undefined': -1, 'default': 0, 'row_sparse': 1, 'csr': 2}
 _STORAGE_TYPE_ID_TO_STR = {v: k for k, v in _STORAGE_TYPE_STR_TO_ID.items()}
+py_slice = slice                       # the reference keeps the builtin under this name (its module also defines an operator `slice`)

@@ -202,8 +202,8 @@ def _read_list(L, h, ctx, cls):
 
 def _load_npz(src, ctx, cls):
     z = _np.load(src, allow_pickle=False)
-    if isinstance(z, _np.ndarray):
-        return [cls(z, ctx=ctx, dtype=z.dtype if z.dtype != _np.float64 else None)]
+    if isinstance(z, _np.ndarray):                 # a .npy file holds one array (Fortran order becomes C order)
+        return cls(_np.ascontiguousarray(z), ctx=ctx, dtype=z.dtype if z.dtype != _np.float64 else None)
     out, sparse_parts = {}, {}
     for k in z.files:
         if '/' in k and k.rsplit('/', 1)[1] in ('data', 'indices', 'indptr', 'shape', 'format'):
@@ -221,9 +221,7 @@ def _load_npz(src, ctx, cls):
             out[base] = sparse.csr_matrix((p['data'], p['indices'], p['indptr']), shape=shape, ctx=ctx, dtype=p['data'].dtype)
         else:
             out[base] = sparse.row_sparse_array((p['data'], p['indices']), shape=shape, ctx=ctx, dtype=p['data'].dtype)
-    if out and all(k.startswith('arr_') for k in out):
-        return [out['arr_%d' % i] for i in range(len(out))]
-    return out
+    return out            # a dict in every case: positional members of savez keep numpy's names arr_0, arr_1, ...
 
 
 def _sniff(head):

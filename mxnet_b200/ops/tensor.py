@@ -160,6 +160,8 @@ register('_npi_copy', inputs=('data',))(lambda data: data.clone())
 
 @register('_npi_around', 'round_np', inputs=('data',), defaults={'decimals': 0})
 def _around(data, decimals=0):
+    if not data.dtype.is_floating_point:
+        return data.clone() if decimals >= 0 else (torch.round(data.double(), decimals=decimals)).to(data.dtype)
     return torch.round(data, decimals=decimals)
 
 
@@ -461,7 +463,7 @@ def _reg_reduce(name, fn, aliases=()):
         ax = _axes(axis, data.dim(), exclude)
         if data.dim() == 0:
             return data.clone()
-        r = fn(data, ax, keepdims)
+        r = fn(data, ax, bool(keepdims))
         if dtype is not None:
             r = r.to(to_torch_dtype(dtype))
         return r
@@ -548,7 +550,7 @@ def _arg_reduce(fn):
             if keepdims:
                 r = r.reshape((1,) * data.dim())
         else:
-            r = fn(data, axis, keepdims)
+            r = fn(data, axis, bool(keepdims))
         return r
     return op
 
@@ -1128,7 +1130,9 @@ def _topk_nout(attrs):
 @register('topk', '_npx_topk', inputs=('data',), nout=_topk_nout,
           defaults={'axis': -1, 'k': 1, 'ret_typ': 'indices', 'is_ascend': False, 'dtype': 'float32'})
 def topk(data, axis=-1, k=1, ret_typ='indices', is_ascend=False, dtype='float32'):
+    full_shape = None
     if axis is None:
+        full_shape = tuple(data.shape)
         data, axis = data.reshape(-1), 0
     if k <= 0:
         k = data.shape[axis]
@@ -1140,8 +1144,8 @@ def topk(data, axis=-1, k=1, ret_typ='indices', is_ascend=False, dtype='float32'
         return idx.to(td)
     if ret_typ == 'both':
         return vals, idx.to(td)
-    mask = torch.zeros_like(data)
-    return mask.scatter_(axis, idx, 1.0)
+    mask = torch.zeros_like(data).scatter_(axis, idx, 1.0)
+    return mask.reshape(full_shape) if full_shape is not None else mask     # the mask has the shape of the input
 
 
 @register('_npi_unique', inputs=('data',), nout=lambda a: 1 + bool(a.get('return_index')) +
@@ -1565,7 +1569,10 @@ def _arange(start=0, stop=None, step=1.0, repeat=1, infer_range=False, ctx=None,
 @register('_linspace', '_npi_linspace', inputs=(), defaults={'start': 0, 'stop': 1, 'num': 50, 'endpoint': True, 'ctx': None, 'dtype': 'float32'})
 def _linspace(start=0, stop=1, num=50, endpoint=True, ctx=None, dtype='float32'):
     if endpoint:
-        return torch.linspace(start, stop, num, dtype=to_torch_dtype(dtype or 'float32'), device=_dev(ctx))
+        # computed in float64 and then cast, as numpy.linspace does: an integer dtype truncates the exact values
+        td = to_torch_dtype(dtype or 'float32')
+        r = torch.linspace(start, stop, num, dtype=torch.float64, device=_dev(ctx))
+        return r.to(td) if td != torch.float64 else r
     step = (stop - start) / num
     return (torch.arange(num, device=_dev(ctx), dtype=torch.float64) * step + start).to(to_torch_dtype(dtype or 'float32'))
 
