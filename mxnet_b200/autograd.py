@@ -198,8 +198,8 @@ def backward(heads, head_grads=None, retain_graph=False, train_mode=True):  # py
             raise MXNetError('Cannot differentiate node because it is not in a computational graph. '
                              'You need to set is_recording to true or use autograd.record() to save '
                              'computational graphs for backward.')
-    for t in tensors:
-        if getattr(t, '_mx_graph_freed', False):
+    for h in heads:
+        if getattr(h, '_freed', False):
             raise MXNetError('The computational graph of this array was freed by an earlier backward pass; '
                              'pass retain_graph=True to differentiate it more than once.')
     _pass_id[0] += 1
@@ -210,9 +210,10 @@ def backward(heads, head_grads=None, retain_graph=False, train_mode=True):  # py
     finally:
         set_training(prev)
     if not retain_graph:
-        for t in tensors:
-            if t.grad_fn is not None:
-                t._mx_graph_freed = True         # the reference frees the recorded graph here (MXAutogradBackwardEx)
+        for h in heads:
+            if h._data.grad_fn is not None:
+                h._freed = True                  # the reference frees the recorded graph here (MXAutogradBackwardEx); the mark
+                                                 # lives on this array object, not on the tensor a graph replay hands out again
 
 
 def grad(heads, variables, head_grads=None, retain_graph=None, create_graph=False, train_mode=True):  # pylint: disable=redefined-outer-name

@@ -31,7 +31,8 @@ def _torch_device_of(ctx):
 
 class NDArray(object):
     """N-dimensional array on a device.  ``_kind`` selects legacy (``nd``) or NumPy (``np``) semantics."""
-    __slots__ = ('_data', '_ctx', '_grad', '_grad_req', '_stype', '_sym', '_fresh_grad', '_hook', '_grad_pass', '_prov', '__weakref__')
+    __slots__ = ('_data', '_ctx', '_grad', '_grad_req', '_stype', '_sym', '_fresh_grad', '_hook', '_grad_pass', '_prov', '_freed',
+                 '__weakref__')
     _kind = 'nd'
     __array_priority__ = 1000.0
 
