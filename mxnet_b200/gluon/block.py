@@ -171,6 +171,16 @@ class Block(object):
         if isinstance(param_dict, dict):
             param_dict = {(k[4:] if k.startswith('arg:') or k.startswith('aux:') else k): v for k, v in param_dict.items()}
         params = self.collect_params()
+        if isinstance(param_dict, dict):
+            # blocks may translate foreign parameter layouts of their own subtree (the fused recurrent layers accept the single
+            # flat `rnn_param` vector that later versions of the reference save)
+            def _translate(block, prefix):
+                hook = getattr(block, '_translate_loaded', None)
+                if hook is not None:
+                    hook(prefix, param_dict)
+                for cname, child in block._children.items():
+                    _translate(child, prefix + cname + '.')
+            _translate(self, '')
         if not allow_missing:
             params_inv = {}
             for k, v in params.items():

@@ -152,8 +152,17 @@ class _GatedCell(HybridRecurrentCell):
         self.h2h_bias = Parameter('h2h_bias', shape=(gates * hidden_size,), init=h2h_bias_initializer,
                                   allow_deferred_init=True)
 
-    def infer_shape(self, inputs, *args):
-        self.i2h_weight.shape = (self._gates * self._hidden_size, inputs.shape[inputs.ndim - 1])
+    def infer_shape(self, *args):
+        """``infer_shape(x)`` or, as stacked cells are asked by the reference, ``infer_shape(i, x, is_bidirect)``: position
+        of the cell in a stack, the stack's input, and whether the cell below is bidirectional (its output is then twice
+        the hidden size wide)."""
+        if args and isinstance(args[0], int):
+            i, x = args[0], args[1]
+            is_bidirect = bool(args[2]) if len(args) > 2 else False
+            width = x.shape[x.ndim - 1] if i == 0 else self._hidden_size * (2 if is_bidirect else 1)
+        else:
+            width = args[0].shape[args[0].ndim - 1]
+        self.i2h_weight.shape = (self._gates * self._hidden_size, width)
 
     def _proj(self, inputs, h):
         ctx = inputs.context
@@ -272,6 +281,23 @@ class SequentialRNNCell(RecurrentCell):
         self._layers.append(cell)
         self.register_child(cell)
 
+    def infer_shape(self, _, x, is_bidirect=False):
+        """Complete the deferred input widths of the stack: the first cell sees ``x``, every later cell the output of the
+        cell below (twice as wide under a bidirectional cell)."""
+        below_bidirectional, below_width = False, None
+        for i, child in enumerate(self._layers):
+            if i > 0 and below_width and hasattr(child, 'i2h_weight') and hasattr(child, '_gates'):
+                # the reference assumes every cell of a stack has the same size; here the width is the real output width of
+                # the cell below
+                child.i2h_weight.shape = (child._gates * child._hidden_size, below_width)
+            else:
+                child.infer_shape(i, x, below_bidirectional)
+            below_bidirectional = isinstance(child, BidirectionalCell)
+            info = child.state_info(0)
+            below_width = info[0]['shape'][-1] * (1 if not below_bidirectional else 1) if info else below_width
+            if below_bidirectional:
+                below_width = sum(s['shape'][-1] for s in (child.l_cell.state_info(0)[:1] + child.r_cell.state_info(0)[:1]))
+
     def state_info(self, batch_size=0):
         return sum([c.state_info(batch_size) for c in self._children.values()], [])
 
@@ -380,7 +406,7 @@ class ModifierCell(HybridRecurrentCell):
         return begin
 
     def infer_shape(self, *args):
-        pass
+        self.base_cell.infer_shape(*args)
 
 
 class ZoneoutCell(ModifierCell):
@@ -449,7 +475,8 @@ class BidirectionalCell(HybridRecurrentCell):
         return self.l_cell.begin_state(**kwargs) + self.r_cell.begin_state(**kwargs)
 
     def infer_shape(self, *args):
-        pass
+        self.l_cell.infer_shape(*args)
+        self.r_cell.infer_shape(*args)
 
     def unroll(self, length, inputs, begin_state=None, layout='NTC', merge_outputs=None, valid_length=None):
         self.reset()

@@ -88,6 +88,53 @@ class _RNNLayer(HybridBlock):
                 p.shape = (self._gates * self._hidden_size, ni)
             ni = nproj * self._dir
 
+    def _param_order(self):
+        """Names of the layer's parameters in the order of the flat vector the RNN operator takes: all weights (layer by layer,
+        direction by direction, input-to-hidden before hidden-to-hidden, then the projection), then all biases."""
+        order = []
+        for t in ('weight', 'bias'):
+            for i in range(self._num_layers):
+                for j in ['l', 'r'][:self._dir]:
+                    for g in ('i2h', 'h2h'):
+                        order.append('{}{}_{}_{}'.format(j, i, g, t))
+                    if t == 'weight' and self._projection_size:
+                        order.append('{}{}_h2r_weight'.format(j, i))
+        return order
+
+    def _translate_loaded(self, prefix, loaded):
+        """A checkpoint that stores this layer as one flat `rnn_param` vector (python/mxnet/gluon/rnn/rnn_layer.py of the
+        2.x reference) is cut into the per-matrix parameters of this layer; shapes that are still deferred are completed from
+        the length of the vector."""
+        key = prefix + 'rnn_param'
+        if key not in loaded:
+            return
+        flat = loaded.pop(key)
+        order = self._param_order()
+        first = getattr(self, order[0])
+        if first.shape is None or any(d <= 0 for d in first.shape):
+            H, G, D, L = self._hidden_size, self._gates, self._dir, self._num_layers
+            P = self._projection_size or H
+            rest = sum(D * (G * H * (P * D) + G * H * P + 2 * G * H + (P * H if self._projection_size else 0)) for _ in range(1, L))
+            per_input = D * G * H
+            fixed0 = D * (G * H * P + 2 * G * H + (P * H if self._projection_size else 0))
+            ni = (int(flat.size) - rest - fixed0) // per_input
+            for j in ['l', 'r'][:D]:
+                getattr(self, '{}0_i2h_weight'.format(j)).shape = (G * H, ni)
+            nin = P * D
+            for i in range(1, L):
+                for j in ['l', 'r'][:D]:
+                    getattr(self, '{}{}_i2h_weight'.format(j, i)).shape = (G * H, nin)
+        at = 0
+        for name in order:
+            p = getattr(self, name)
+            n = 1
+            for d in p.shape:
+                n *= d
+            loaded[prefix + name] = flat[at:at + n].reshape(p.shape)
+            at += n
+        if at != int(flat.size):
+            raise ValueError('rnn_param has %d elements, this layer needs %d' % (int(flat.size), at))
+
     def forward(self, inputs, states=None, sequence_length=None):
         batch_size = inputs.shape[self._layout.find('N')]
         skip_states = states is None
@@ -107,14 +154,7 @@ class _RNNLayer(HybridBlock):
         ctx = inputs.context
         if self._layout == 'NTC':
             inputs = _op('SwapAxis', [inputs], dim1=0, dim2=1)
-        order = []
-        for t in ('weight', 'bias'):
-            for i in range(self._num_layers):
-                for j in ['l', 'r'][:self._dir]:
-                    for g in ('i2h', 'h2h'):
-                        order.append('{}{}_{}_{}'.format(j, i, g, t))
-                    if t == 'weight' and self._projection_size:
-                        order.append('{}{}_h2r_weight'.format(j, i))
+        order = self._param_order()
         params = _op('_rnn_param_concat', [getattr(self, n).data(ctx) for n in order], dim=0)
         args = [inputs, params] + list(states)
         if self._use_sequence_length and sequence_length is not None:

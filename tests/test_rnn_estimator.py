@@ -117,3 +117,32 @@ def test_estimator_fit_with_handlers(tmp_path):
     ck2 = CheckpointHandler(str(tmp_path), model_prefix='toy', resume_from_checkpoint=True)
     est2.fit(data, epochs=7, event_handlers=[ck2])
     assert ck2.trained_epoch == 5 and ck2.current_epoch == 1      # epochs 0..5 came from the checkpoint, one more ran
+
+
+def test_flat_rnn_param_checkpoints_load_and_cells_infer_shapes(tmp_path):
+    """A checkpoint that stores a fused layer as one flat `rnn_param` vector (the 2.x reference's layout) loads into the
+    per-matrix parameters; `cell.infer_shape(i, x, is_bidirect)` completes deferred input widths of stacked cells."""
+    import numpy as np
+    import mxnet_b200 as mx
+    from mxnet_b200 import gluon
+    layer = gluon.rnn.LSTM(6, num_layers=2, bidirectional=True)
+    layer.initialize()
+    x = mx.nd.array(np.random.RandomState(0).randn(4, 3, 5).astype('float32'))
+    expect = layer(x).asnumpy()
+    flat = np.concatenate([getattr(layer, n).data().asnumpy().ravel() for n in layer._param_order()])
+    path = str(tmp_path / 'lstm.params')
+    mx.nd.save(path, {'rnn_param': mx.nd.array(flat)})
+    fresh = gluon.rnn.LSTM(6, num_layers=2, bidirectional=True)       # input width still deferred
+    fresh.load_parameters(path)
+    np.testing.assert_allclose(fresh(x).asnumpy(), expect, rtol=1e-6, atol=1e-6)
+    stack = gluon.rnn.SequentialRNNCell()
+    stack.add(gluon.rnn.LSTMCell(7))
+    stack.add(gluon.rnn.GRUCell(9))
+    stack.infer_shape(0, mx.nd.ones((2, 5)), False)
+    assert stack[0].i2h_weight.shape == (28, 5) and stack[1].i2h_weight.shape == (27, 7)
+    cell = gluon.rnn.RNNCell(10)
+    cell.infer_shape(0, mx.nd.ones((2, 4)), False)
+    assert cell.i2h_weight.shape == (10, 4)
+    cell2 = gluon.rnn.RNNCell(10)
+    cell2.infer_shape(1, mx.nd.ones((2, 4)), True)
+    assert cell2.i2h_weight.shape == (10, 20)
