@@ -488,6 +488,9 @@ class HybridBlock(Block):
             flat_out, self._out_format = _flatten(out, 'output')
             out_sym = tracer.get_symbol([o for o in flat_out if isinstance(o, NDArray)])
         self._cached_graph = (inputs, out_sym)
+        # arrays the forward made itself (a zero begin state, a lookup table): leaves of the graph that are neither inputs
+        # nor parameters; export writes them beside the parameters
+        self._trace_constants = dict(tracer.constants)
         return out
 
     def _call_cached_op(self, *args):
@@ -534,6 +537,9 @@ class HybridBlock(Block):
         for name, p in self.collect_params().items():
             if name in needed:
                 feed[name] = p.data(ctx)._data
+        for name, value in (getattr(self, '_trace_constants', None) or {}).items():
+            if name in needed:
+                feed[name] = value._data.to(arrays[0]._data.device)
         if _state.state.recording:
             with torch.enable_grad():
                 outs = self._partitioned._run(feed)
@@ -563,6 +569,9 @@ class HybridBlock(Block):
                 arg_dict['arg:%s' % name] = p._reduce().as_nd_ndarray()
             elif name in aux_names:
                 arg_dict['aux:%s' % name] = p._reduce().as_nd_ndarray()
+        for name, value in (getattr(self, '_trace_constants', None) or {}).items():
+            if name in arg_names:
+                arg_dict['arg:%s' % name] = value.as_nd_ndarray()
         params_file = None
         if arg_dict:
             params_file = '%s-%04d.params' % (path, epoch)

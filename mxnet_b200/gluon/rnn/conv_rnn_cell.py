@@ -33,10 +33,21 @@ class _ConvCell(HybridRecurrentCell):
             (s + 2 * p - d * (k - 1) - 1) + 1 for s, p, d, k in zip(input_shape[1:], self._i2h_pad, self._i2h_dilate,
                                                                    self._i2h_kernel))
         n = gates * hidden_channels
-        self.i2h_weight = Parameter('i2h_weight', shape=(n, in_c) + self._i2h_kernel, init=i2h_weight_initializer)
+        self.i2h_weight = Parameter('i2h_weight', shape=(n, in_c) + self._i2h_kernel, init=i2h_weight_initializer,
+                                    allow_deferred_init=True)
         self.h2h_weight = Parameter('h2h_weight', shape=(n, hidden_channels) + self._h2h_kernel, init=h2h_weight_initializer)
         self.i2h_bias = Parameter('i2h_bias', shape=(n,), init=i2h_bias_initializer)
         self.h2h_bias = Parameter('h2h_bias', shape=(n,), init=h2h_bias_initializer)
+
+    def infer_shape(self, *args):
+        """Complete a deferred input-channel count (``input_shape[0] == -1``) from the input; also takes the stacked
+        form ``infer_shape(i, x, is_bidirect)``."""
+        x = args[1] if args and isinstance(args[0], int) else args[0]
+        shape = tuple(self.i2h_weight.shape)
+        if shape[1] <= 0:
+            # counted from the end: ``x`` may be one step (N, C, ...) or a whole sequence (N, T, C, ...)
+            axis = x.ndim - (len(self._conv_layout) - self._conv_layout.find('C'))
+            self.i2h_weight.shape = shape[:1] + (x.shape[axis],) + shape[2:]
 
     def state_info(self, batch_size=0):
         n = 2 if self._gates == 4 else 1

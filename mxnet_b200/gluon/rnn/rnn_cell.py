@@ -286,7 +286,7 @@ class SequentialRNNCell(RecurrentCell):
         cell below (twice as wide under a bidirectional cell)."""
         below_bidirectional, below_width = False, None
         for i, child in enumerate(self._layers):
-            if i > 0 and below_width and hasattr(child, 'i2h_weight') and hasattr(child, '_gates'):
+            if i > 0 and below_width and hasattr(child, 'i2h_weight') and hasattr(child, '_hidden_size'):
                 # the reference assumes every cell of a stack has the same size; here the width is the real output width of
                 # the cell below
                 child.i2h_weight.shape = (child._gates * child._hidden_size, below_width)
@@ -452,6 +452,10 @@ class ResidualCell(ModifierCell):
         from ...ndarray.ndarray import NDArray
         merge_outputs = isinstance(outputs, NDArray) if merge_outputs is None else merge_outputs
         inputs, axis, _ = _format_sequence(length, inputs, layout, merge_outputs)
+        if valid_length is not None:            # the skip connection adds nothing beyond a sequence's end
+            merged = inputs if merge_outputs else _op('stack', list(inputs), axis=axis)
+            merged = _op('SequenceMask', [merged, valid_length], use_sequence_length=True, axis=axis)
+            inputs = merged if merge_outputs else [merged[(slice(None),) * axis + (t,)] for t in range(length)]
         if merge_outputs:
             outputs = outputs + inputs
         else:
@@ -503,7 +507,7 @@ class BidirectionalCell(HybridRecurrentCell):
             rev = _op('SequenceReverse', [seq, valid_length], use_sequence_length=True)
             reversed_r_outputs = [rev[t] for t in range(length)]
         outputs = [_op('Concat', [l_o, r_o], dim=1) for l_o, r_o in zip(l_outputs, reversed_r_outputs)]
-        if merge_outputs:
+        if merge_outputs or (merge_outputs is None and valid_length is not None):       # masked sequences come back merged
             outputs = _op('stack', outputs, axis=axis)
         return outputs, l_states + r_states
 

@@ -146,3 +146,53 @@ def test_flat_rnn_param_checkpoints_load_and_cells_infer_shapes(tmp_path):
     cell2 = gluon.rnn.RNNCell(10)
     cell2.infer_shape(1, mx.nd.ones((2, 4)), True)
     assert cell2.i2h_weight.shape == (10, 20)
+
+
+def test_conv_cell_deferred_channels_masked_residual_and_exported_constants(tmp_path):
+    """``python/mxnet/gluon/rnn/conv_rnn_cell.py`` (input_shape[0] == -1 completed by infer_shape),
+    ``rnn_cell.py`` ResidualCell / BidirectionalCell under ``valid_length`` (padded steps are zero, outputs come back
+    merged) and export of a graph whose forward made its own begin state."""
+    import mxnet_b200 as mx
+    from mxnet_b200 import gluon
+    seq = mx.np.ones((8, 3, 5, 7))
+    cell = gluon.rnn.Conv1DLSTMCell((-1, 7), 10, (3,), (3,))
+    cell.infer_shape(0, seq, False)
+    assert cell.i2h_weight.shape[1] == 5
+    cell.initialize()
+    out, _ = cell.unroll(3, seq, merge_outputs=True)
+    assert out.shape == (8, 3, 10, 5)
+
+    valid = [3, 6, 2, 5]
+    vl = mx.np.array(valid)
+    stack = gluon.rnn.SequentialRNNCell()
+    stack.add(gluon.rnn.ResidualCell(gluon.rnn.RNNCell(20)))
+    stack.add(gluon.rnn.ResidualCell(gluon.rnn.RNNCell(20)))
+    bidir = gluon.rnn.BidirectionalCell(gluon.rnn.GRUCell(20), gluon.rnn.GRUCell(20))
+    data = mx.np.random.normal(0, 1, size=(6, 4, 20))
+    for c in (stack, bidir):
+        c.infer_shape(0, data, False)
+        c.initialize()
+        outs, _ = c.unroll(6, data, valid_length=vl, layout='TNC')
+        assert not isinstance(outs, list)
+        for i, n in enumerate(valid):
+            one, _ = c.unroll(n, data[:n, i:i + 1, :], merge_outputs=True, layout='TNC')
+            np.testing.assert_allclose(outs[:n, i:i + 1, :].asnumpy(), one.asnumpy(), rtol=1e-4, atol=1e-5)
+            assert float(abs(outs[n:, i:i + 1, :]).sum()) == 0.0
+
+    class Layer(gluon.HybridBlock):
+        def __init__(self):
+            super().__init__()
+            self.cell = gluon.rnn.GRUCell(hidden_size=1)
+
+        def forward(self, s):
+            return self.cell.unroll(inputs=s, length=2, merge_outputs=True)[0]
+
+    net = Layer()
+    x = mx.np.ones((1, 2, 1))
+    net.cell.infer_shape(0, x, False)
+    net.initialize()
+    net.hybridize()
+    want = net(x)
+    sym_file, params_file = net.export(str(tmp_path / 'model'))
+    back = gluon.SymbolBlock.imports(sym_file, ['data'], params_file)
+    np.testing.assert_allclose(back(x).asnumpy(), want.asnumpy(), rtol=1e-5, atol=1e-6)
