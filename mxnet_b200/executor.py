@@ -66,15 +66,17 @@ class Executor(object):
         feed, leafs = {}, {}
         for n, a in self.arg_dict.items():
             t = a._data.detach()
-            if is_train and n in self.grad_dict and self.grad_dict[n] is not None and self._grad_req.get(n, 'write') != 'null' \
+            # an executor bound with gradient buffers records every forward; ``is_train`` only picks the mode of dropout /
+            # batch norm (python/mxnet/executor.py:128 in the reference)
+            if n in self.grad_dict and self.grad_dict[n] is not None and self._grad_req.get(n, 'write') != 'null' \
                     and t.dtype.is_floating_point:
-                t = t.clone().requires_grad_(True) if False else t.requires_grad_(True)
+                t = t.requires_grad_(True)
                 leafs[n] = t
             feed[n] = t
         for n, a in self.aux_dict.items():
             feed[n] = a._data
-        with autograd.record(train_mode=is_train) if is_train else autograd.pause(train_mode=False):
-            if is_train:
+        with autograd.record(train_mode=is_train) if (is_train or leafs) else autograd.pause(train_mode=False):
+            if is_train or leafs:
                 with torch.enable_grad():
                     outs = self._symbol._run(feed, placement=self._placement, stats=self._stats)
             else:
@@ -101,9 +103,11 @@ class Executor(object):
         grads = torch.autograd.grad([h[0] for h in heads], [self._leafs[n] for n in names], [h[1] for h in heads],
                                     allow_unused=True)
         for n, g in zip(names, grads):
-            if g is None:
-                continue
             buf = self.grad_dict[n]._data
+            if g is None:
+                if self._grad_req.get(n, 'write') != 'add':
+                    buf.zero_()
+                continue
             if self._grad_req.get(n, 'write') == 'add':
                 buf.add_(g)
             else:

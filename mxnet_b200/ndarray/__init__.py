@@ -46,6 +46,7 @@ def _populate():
 
 _populate()
 from . import random      # noqa: E402
+from .cached_op import CachedOp   # noqa: E402,F401
 from . import contrib_ext as _contrib_ext  # noqa: E402,F401  (foreach/while_loop/cond on nd.contrib)
 
 

@@ -222,10 +222,12 @@ class Symbol(object):
         return Symbol(outs)
 
     def get_children(self):
-        if len(self._outputs) != 1:
-            return None
-        node = self._outputs[0][0]
-        return Symbol(list(node.inputs)) if node.inputs else None
+        entries, seen = [], set()
+        for node, _ in self._outputs:
+            if id(node) not in seen:            # the heads of one multi-output operator share their inputs
+                seen.add(id(node))
+                entries.extend(node.inputs)
+        return Symbol(entries) if entries else None
 
     def get_inputs(self):
         return Symbol([(n, 0) for n in _topo(self._outputs) if n.op is None])
@@ -284,10 +286,13 @@ class Symbol(object):
         for k, v in kwargs.items():
             if not isinstance(v, str):
                 raise ValueError('Set Attr only accepts string values')
-            node.user_attrs[k] = v
+            if k == 'name':
+                node.name = v
+            else:
+                node.user_attrs[k] = v
 
     def __copy__(self):
-        return Symbol(list(self._outputs))
+        return self.__deepcopy__(None)
 
     def __deepcopy__(self, memo):
         return load_json(self.tojson())
@@ -344,6 +349,12 @@ class Symbol(object):
     def __pow__(self, o): return self._binop(o, 'broadcast_power', '_power_scalar')
     def __rpow__(self, o): return self._binop(o, 'broadcast_power', '_power_scalar', '_rpower_scalar', True)
     def __neg__(self): return self.__mul__(-1.0)
+
+    def __abs__(self):
+        return _op_frontend(_reg.get('abs'))(self)
+
+    def __bool__(self):
+        raise NotImplementedForSymbol(self.__bool__, 'bool')
     def __eq__(self, o): return self._binop(o, 'broadcast_equal', '_equal_scalar')
     def __ne__(self, o): return self._binop(o, 'broadcast_not_equal', '_not_equal_scalar')
     def __gt__(self, o): return self._binop(o, 'broadcast_greater', '_greater_scalar')
@@ -707,6 +718,20 @@ def _rule(opname):
     return deco
 
 
+def _same_shape_rule(node, in_shapes):
+    """Operators whose operands all have one shape (``elemwise_*``, ``add_n``): an unknown operand takes the known shape."""
+    known = [s for s in in_shapes if s is not None]
+    if not known:
+        return {}
+    return {pos: known[0] for pos, s in enumerate(in_shapes) if s is None}
+
+
+for _n in ('elemwise_add', 'elemwise_sub', 'elemwise_mul', 'elemwise_div', 'add_n'):
+    if _reg.has(_n):
+        _PARAM_SHAPE_RULES[_reg.get(_n).name] = _same_shape_rule
+
+
+
 @_rule('FullyConnected')
 def _fc_rule(node, ins):
     data = ins[0]
@@ -1009,8 +1034,8 @@ def _op_frontend(op):
                         pass
                     else:
                         continue
-                if nm == 'data' or nm == 'lhs':
-                    raise MXNetError('operator %s needs input %s' % (op.name, nm))
+                # a missing data input becomes the free variable ``<name>_data`` that composition fills later
+                # (``net(fc3_data=other)``), as every missing input does in the reference
                 s = var('%s_%s' % (name, nm))
             out_syms.append(s)
         return _make_op_symbol(op, out_syms, attrs, name, user_attrs, resolved=True)
@@ -1087,20 +1112,7 @@ def arange(start, stop=None, step=1.0, repeat=1, infer_range=False, name=None, d
 
 
 # ---- Symbol methods that complete the NDArray-like surface (python/mxnet/symbol/symbol.py) ----------------------
-class NotImplementedForSymbol(MXNetError):
-    """Raised by NDArray-only methods called on a Symbol."""
-
-    def __init__(self, function, alias, *args):
-        super().__init__()
-        self.function, self.alias, self.args_ = function.__name__, alias, [str(type(a)) for a in args]
-
-    def __str__(self):
-        msg = 'Function {}'.format(self.function)
-        if self.alias:
-            msg += ' (namely operator "{}")'.format(self.alias)
-        if self.args_:
-            msg += ' with arguments ({})'.format(', '.join(self.args_))
-        return msg + ' is not supported for Symbol and only available in NDArray.'
+from ..base import NotImplementedForSymbol          # noqa: E402  (one class for ``mx.base`` and ``mx.sym``)
 
 
 def _symbol_astype(self, dtype, name=None):

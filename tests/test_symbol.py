@@ -413,3 +413,52 @@ def test_hybridized_block_runs_through_the_layout_pass_when_enabled():
         assert float(np.abs(net[0].weight.grad().asnumpy()).sum()) > 0
     finally:
         layout.set_optimize_layout(False)
+
+
+def test_symbol_surface_found_by_the_reference_tests():
+    """``python/mxnet/symbol/symbol.py``: bool() raises, abs(), children of grouped heads, deep copies that can be renamed,
+    a missing data input becomes ``<name>_data`` for later composition, same-shape operands infer from one another;
+    ``python/mxnet/executor.py``: an executor bound with gradient buffers differentiates after a plain forward();
+    ``mx.nd.CachedOp`` runs a symbol on arrays."""
+    import copy
+    import numpy as np
+    import pytest
+    import mxnet_b200 as mx
+    from mxnet_b200.base import NotImplementedForSymbol
+    x = mx.sym.Variable('x')
+    with pytest.raises(NotImplementedForSymbol):
+        bool(x)
+    assert abs(x).list_arguments() == ['x']
+    b = copy.copy(x)
+    b._set_attr(name='b')
+    assert x.name == 'x' and b.name == 'b'
+
+    data = mx.sym.Variable('data')
+    sliced = mx.sym.SliceChannel(data, num_outputs=3, name='slice')
+    assert sliced.get_children().list_outputs() == ['data']
+    assert mx.sym.Concat(*list(sliced)).get_children().list_outputs() == ['slice_output0', 'slice_output1', 'slice_output2']
+
+    net1 = mx.sym.FullyConnected(data=data, name='fc1', num_hidden=10)
+    net2 = mx.sym.FullyConnected(name='fc3', num_hidden=10)
+    assert 'fc3_data' in net2.list_arguments()
+    composed = net2(fc3_data=net1, name='composed')
+    assert 'fc3_data' not in composed.list_arguments() and 'data' in composed.list_arguments()
+
+    a = mx.sym.Variable('a', shape=(2, 3))
+    c = mx.sym.elemwise_add(a, mx.sym.Variable('b'))
+    arg_shapes, out_shapes, _ = c.infer_shape()
+    assert arg_shapes == [(2, 3), (2, 3)] and out_shapes == [(2, 3)]
+
+    lhs, rhs = mx.nd.array([[1., 2.]]), mx.nd.array([[3., 4.]])
+    gl, gr = mx.nd.empty((1, 2)), mx.nd.empty((1, 2))
+    prod = mx.sym.Variable('lhs') * mx.sym.Variable('rhs')
+    exe = prod._bind(mx.cpu(), args=[lhs, rhs], args_grad=[gl, gr])
+    exe.forward()
+    exe.backward([mx.nd.ones((1, 2))])
+    np.testing.assert_allclose(gl.asnumpy(), rhs.asnumpy())
+    np.testing.assert_allclose(gr.asnumpy(), lhs.asnumpy())
+
+    op = mx.nd.CachedOp(prod, [('static_alloc', True)])
+    np.testing.assert_allclose(op(lhs, rhs).asnumpy(), [[3., 8.]])
+    z = mx.nd.CachedOp(mx.sym.zeros((3, 3)))(None, default_device=mx.cpu())
+    assert z.shape == (3, 3) and float(z.sum()) == 0.0
