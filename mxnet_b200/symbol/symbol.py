@@ -352,9 +352,6 @@ class Symbol(object):
 
     def __abs__(self):
         return _op_frontend(_reg.get('abs'))(self)
-
-    def __bool__(self):
-        raise NotImplementedForSymbol(self.__bool__, 'bool')
     def __eq__(self, o): return self._binop(o, 'broadcast_equal', '_equal_scalar')
     def __ne__(self, o): return self._binop(o, 'broadcast_not_equal', '_not_equal_scalar')
     def __gt__(self, o): return self._binop(o, 'broadcast_greater', '_greater_scalar')
